@@ -1,0 +1,277 @@
+// bf16 TN GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * W[N,K]^T (+ epilogue).
+//
+// Serves the manifest extern vocabulary `extern:cublaslt_bf16_tn`, `extern:cublaslt_bf16_tn_acc`
+// and `extern:cublas_bf16_tn_f32` (reference: crates/kern-runtime/src/cublas.rs:78-107,242-277,
+// 329-378 call cuBLASLt/cuBLAS for these) with one hand-written persistent kernel:
+//
+//   warp 0      TMA producer: cp.async.bulk.tensor 2-D tiles (128-byte swizzle) into a ring of
+//               shared-memory stages, completion on mbarriers
+//   warp 1      allocates TMEM, issues tcgen05.mma (128 x BN x 16 per instruction) from one thread,
+//               frees each stage / publishes each accumulator with tcgen05.commit
+//   warps 2..5  epilogue: tcgen05.ld the f32 accumulator out of TMEM, apply the epilogue, store
+//
+// Two accumulators live in TMEM (2*BN columns) so the epilogue of tile i overlaps the main loop
+// of tile i+1. Grid = min(tiles, SMs): each CTA walks tiles t = blockIdx.x + i*gridDim.x with M
+// fastest, so CTAs running at the same time share W tiles through L2.
+//
+// Epilogues: 0 bf16 store; 1 f32 store; 2 bf16 store of acc + R (R may alias C: the in-place
+// residual add, beta = 1); 3 SwiGLU over weights interleaved 16 gate rows / 16 up rows:
+// out[m, n/2] = silu(gate) * up, ldc counts output columns.
+//
+// Every mbarrier wait is bounded; a wait that runs out sets *err and the CTA unwinds.
+#include "common.cuh"
+
+namespace kern {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStageBytesA = BM * BK * 2;
+  static constexpr int kStageBytesB = BN * BK * 2;
+  static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  // 1024 B of slack for alignment + stages + barriers
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 256;
+};
+
+template <int BN, int EPI>
+__device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
+                                          void* Cv, const void* Rv,
+                                          int M, int N, int K, int ldc, int* err) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tfull_bar = empty_bar + kStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (M + BM - 1) / BM;
+  const int num_n = (N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);  // one arrive per epilogue warp
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(tma_a);
+    tma_prefetch_desc(tma_b);
+  }
+  pdl_wait();  // everything above touched only this CTA's own state and the descriptors
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int m_blk = t % num_m, n_blk = t / num_m;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            set_error(err, ERR_WAIT_EMPTY);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sa = tiles + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kStageBytesA;
+          mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          tma_load_2d(sa, tma_a, kb * BK, m_blk * BM, &full_bar[stage]);
+          tma_load_2d(sb, tma_b, kb * BK, n_blk * BN, &full_bar[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) {
+          set_error(err, ERR_WAIT_TMEM_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            set_error(err, ERR_WAIT_FULL);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + Cfg::kStageBytesA;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            umma_bf16(d_tmem, umma_desc_sw128(sa + k * 32), umma_desc_sw128(sb + k * 32), idesc,
+                      (kb | k) != 0);
+          }
+          tc_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&tfull_bar[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue warps 2..5 ----------------
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are this warp's
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      const int m_blk = t % num_m, n_blk = t / num_m;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) {
+        set_error(err, ERR_WAIT_TMEM_FULL);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const int row = m_blk * BM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col = n_blk * BN + c * 32;
+        if (row < M) {
+          if constexpr (EPI == 0 || EPI == 2) {
+            __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(Cv) + (size_t)row * ldc + col;
+            const __nv_bfloat16* R =
+                reinterpret_cast<const __nv_bfloat16*>(Rv) + (size_t)row * ldc + col;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col + v * 8 < N) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+                if constexpr (EPI == 2) {
+                  uint4 old = *reinterpret_cast<const uint4*>(R + v * 8);
+                  float2 a = unpack_bf16x2(old.x), b = unpack_bf16x2(old.y),
+                         cc = unpack_bf16x2(old.z), d = unpack_bf16x2(old.w);
+                  f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
+                  f[4] += cc.x; f[5] += cc.y; f[6] += d.x; f[7] += d.y;
+                }
+                uint4 o;
+                o.x = pack_bf16x2(f[0], f[1]);
+                o.y = pack_bf16x2(f[2], f[3]);
+                o.z = pack_bf16x2(f[4], f[5]);
+                o.w = pack_bf16x2(f[6], f[7]);
+                *reinterpret_cast<uint4*>(C + v * 8) = o;
+              }
+            }
+          } else if constexpr (EPI == 1) {
+            float* C = reinterpret_cast<float*>(Cv) + (size_t)row * ldc + col;
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              if (col + v * 4 < N) {
+                float4 o = make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
+                                       __uint_as_float(r[v * 4 + 2]),
+                                       __uint_as_float(r[v * 4 + 3]));
+                *reinterpret_cast<float4*>(C + v * 4) = o;
+              }
+            }
+          } else {  // EPI == 3: SwiGLU, 16 gate columns then 16 up columns
+            if (col < N) {
+              __nv_bfloat16* C =
+                  reinterpret_cast<__nv_bfloat16*>(Cv) + (size_t)row * ldc + (col >> 1);
+              float f[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                f[j] = silu(__uint_as_float(r[j])) * __uint_as_float(r[16 + j]);
+              uint4 o0, o1;
+              o0.x = pack_bf16x2(f[0], f[1]);   o0.y = pack_bf16x2(f[2], f[3]);
+              o0.z = pack_bf16x2(f[4], f[5]);   o0.w = pack_bf16x2(f[6], f[7]);
+              o1.x = pack_bf16x2(f[8], f[9]);   o1.y = pack_bf16x2(f[10], f[11]);
+              o1.z = pack_bf16x2(f[12], f[13]); o1.w = pack_bf16x2(f[14], f[15]);
+              *reinterpret_cast<uint4*>(C) = o0;
+              *reinterpret_cast<uint4*>(C + 8) = o1;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0 && threadIdx.x == 0) {
+    // give loads that were in flight time to land before the CTA (and its shared memory) retires
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) { __nanosleep(1000); }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+}  // namespace kern
+
+#define KERN_GEMM_ENTRY(name, BN, EPI)                                                        \
+  extern "C" __global__ void __launch_bounds__(192, 1)                                        \
+      name(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, \
+           void* C, const void* R, int M, int N, int K, int ldc, int* err) {                  \
+    kern::gemm_body<BN, EPI>(&tma_a, &tma_b, C, R, M, N, K, ldc, err);                        \
+  }
+
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_n256, 256, 0)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_n128, 128, 0)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_n64, 64, 0)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_n32, 32, 0)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_f32_n256, 256, 1)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_f32_n128, 128, 1)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_f32_n64, 64, 1)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_acc_n256, 256, 2)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_acc_n128, 128, 2)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_acc_n64, 64, 2)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_acc_n32, 32, 2)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_swiglu_n256, 256, 3)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_swiglu_n128, 128, 3)
+KERN_GEMM_ENTRY(kern_gemm_bf16_tn_swiglu_n64, 64, 3)

@@ -1,0 +1,172 @@
+"""In-tree build of the native pieces: sm_100a cubins (one per kernel source) and the C++ core.
+
+The cubins are *built-in modules* of the package format: a manifest names them by file and sha256
+exactly like any other pinned module (reference: crates/kern-runtime/src/cubin.rs:70-155 loads
+modules by content hash). ``kernels/index.json`` is written at build time with the hash of every
+cubin, so nothing hand-committed can go stale.
+
+Everything is rebuilt only when a source is newer than its product; the products stay in the tree
+(``kern_b200/kernels/*.cubin``, ``kern_b200/_native*.so``) so a copy of the tree runs without a
+build step.
+"""
+from __future__ import annotations
+
+import fcntl
+import hashlib
+import json
+import os
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+PKG = ROOT / "kern_b200"
+CSRC = ROOT / "csrc"
+KSRC = CSRC / "kernels" / "sm100"
+KOUT = PKG / "kernels"
+BUILD = ROOT / "build"
+
+NVCC = os.environ.get("KERN_NVCC", "/usr/local/cuda/bin/nvcc")
+CXX = os.environ.get("CXX", "g++")
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xptxas", "-v"]
+
+# sources with host code for nvcc (C entry points reached through ctypes), one library per file
+HSRC = CSRC / "kernels" / "host"
+
+
+def _newer(src: list[Path], out: Path) -> bool:
+    if not out.exists():
+        return True
+    t = out.stat().st_mtime
+    return any(s.stat().st_mtime > t for s in src)
+
+
+def _run(cmd: list[str], log: Path | None = None) -> str:
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if log is not None:
+        log.parent.mkdir(parents=True, exist_ok=True)
+        log.write_text(p.stdout)
+    if p.returncode != 0:
+        raise RuntimeError("build step failed: " + " ".join(cmd) + "\n" + p.stdout[-4000:])
+    return p.stdout
+
+
+def kernel_sources() -> list[Path]:
+    return sorted(KSRC.glob("*.cu"))
+
+
+def build_kernels(force: bool = False, verbose: bool = False) -> dict[str, dict]:
+    """Compile every kernel source to ``kernels/<stem>.cubin``; return the module index."""
+    KOUT.mkdir(parents=True, exist_ok=True)
+    headers = sorted(KSRC.glob("*.cuh"))
+    jobs = []
+    for src in kernel_sources():
+        out = KOUT / (src.stem + ".cubin")
+        if force or _newer([src, *headers], out):
+            jobs.append((src, out))
+
+    def one(job):
+        src, out = job
+        cmd = [NVCC, *ARCH, *NVCC_FLAGS, "-cubin", "-I", str(KSRC), "-o", str(out), str(src)]
+        text = _run(cmd, BUILD / "ptxas" / (src.stem + ".log"))
+        if verbose:
+            print(text)
+
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            list(ex.map(one, jobs))
+    index = {}
+    for src in kernel_sources():
+        out = KOUT / (src.stem + ".cubin")
+        data = out.read_bytes()
+        index[src.stem] = {"source": out.name, "sha256": hashlib.sha256(data).hexdigest()}
+    (KOUT / "index.json").write_text(json.dumps(index, indent=1, sort_keys=True))
+    return index
+
+
+def native_sources() -> list[Path]:
+    out = sorted((CSRC / "bindings").glob("*.cpp"))
+    for sub in ("manifest", "pool", "runtime"):
+        out += sorted((CSRC / sub).glob("*.cpp"))
+    return out
+
+
+def native_path() -> Path:
+    return PKG / ("_native" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_native(force: bool = False) -> Path:
+    """Compile the C++ core (manifest, pool, runtime, bindings) into ``kern_b200/_native*.so``."""
+    import pybind11
+
+    out = native_path()
+    srcs = native_sources()
+    headers = [p for p in CSRC.rglob("*.hpp")]
+    if not force and not _newer([*srcs, *headers], out):
+        return out
+    objdir = BUILD / "native"
+    objdir.mkdir(parents=True, exist_ok=True)
+    defs = []
+    if (CSRC / "bindings" / "bind_manifest.cpp").exists():
+        defs.append("-DKERN_WITH_MANIFEST")
+    if (CSRC / "bindings" / "bind_pool.cpp").exists():
+        defs.append("-DKERN_WITH_POOL")
+    if (CSRC / "bindings" / "bind_runtime.cpp").exists():
+        defs.append("-DKERN_WITH_RUNTIME")
+    inc = [
+        "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
+        "-I", "/usr/local/cuda/include", "-I", str(CSRC),
+    ]
+    flags = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function", *defs]
+
+    def one(src: Path):
+        obj = objdir / (src.parent.name + "_" + src.stem + ".o")
+        if force or _newer([src, *headers], obj):
+            _run([CXX, *flags, *inc, "-c", str(src), "-o", str(obj)])
+        return obj
+
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        objs = list(ex.map(one, srcs))
+    _run([CXX, "-shared", "-o", str(out), *map(str, objs), "-ldl", "-lpthread"])
+    return out
+
+
+def build_host_libs(force: bool = False) -> list[Path]:
+    """Shared libraries with host code compiled by nvcc (C entry points reached through ctypes)."""
+    outs = []
+    for src in sorted(HSRC.glob("*.cu")):
+        out = PKG / ("lib" + src.stem + ".so")
+        if force or _newer([src, *KSRC.glob("*.cuh")], out):
+            _run([NVCC, *ARCH, "-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC",
+                  "-I", str(KSRC), "-o", str(out), str(src), "-lcudart"])
+        outs.append(out)
+    return outs
+
+
+def build_all(force: bool = False, verbose: bool = False) -> None:
+    BUILD.mkdir(exist_ok=True)
+    with open(BUILD / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            build_kernels(force, verbose)
+            build_native(force)
+            build_host_libs(force)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def ensure_built() -> None:
+    """Build whatever is missing or stale. Cheap when everything is current."""
+    try:
+        build_all(False)
+    except FileNotFoundError as e:  # no compiler on this machine: use what is in the tree
+        if not native_path().exists():
+            raise RuntimeError(f"native core is not built and no toolchain was found: {e}")
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print("built:", native_path().name, "+", len(kernel_sources()), "cubins")

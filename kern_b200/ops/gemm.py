@@ -1,0 +1,98 @@
+"""bf16 TN GEMM on tcgen05: ``C[M,N] = A[M,K] @ W[N,K]^T`` with fused epilogues.
+
+The op behind the manifest externs ``extern:cublaslt_bf16_tn`` (store), ``extern:cublaslt_bf16_tn_acc``
+(C += A·Wᵀ) and ``extern:cublas_bf16_tn_f32`` (f32 out) — reference call sites:
+crates/kern-runtime/src/cublas.rs:78-107, 242-277, 329-378 — plus a SwiGLU epilogue that replaces
+the separate ``silu_mul`` launch (tools/kernels-src/silu_mul.cu:10).
+"""
+from __future__ import annotations
+
+import torch
+
+from .launcher import Kernels, i32, ptr
+
+BM, BK = 128, 64
+_STAGES = {256: 4, 128: 6, 64: 8, 32: 8}
+_EPI = {"store": "", "f32": "_f32", "acc": "_acc", "swiglu": "_swiglu"}
+_TILES = {"store": (256, 128, 64, 32), "f32": (256, 128, 64), "acc": (256, 128, 64, 32),
+          "swiglu": (256, 128, 64)}
+
+
+def smem_bytes(bn: int) -> int:
+    return 1024 + _STAGES[bn] * (BM * BK * 2 + bn * BK * 2) + 256
+
+
+def pick_bn(m: int, n: int, sms: int, epilogue: str = "store") -> int:
+    """Largest N tile that still gives every SM a tile; small problems fall to narrower tiles."""
+    num_m = (m + BM - 1) // BM
+    choices = _TILES[epilogue]
+    for bn in choices:
+        if num_m * ((n + bn - 1) // bn) >= sms:
+            return bn
+    return choices[-1]
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, rows: int = 16) -> torch.Tensor:
+    """Weights for the SwiGLU epilogue: ``rows`` gate rows, then ``rows`` up rows, repeating."""
+    i, k = gate.shape
+    assert up.shape == gate.shape and i % rows == 0
+    g = gate.reshape(i // rows, rows, k)
+    u = up.reshape(i // rows, rows, k)
+    return torch.stack([g, u], dim=1).reshape(2 * i, k).contiguous()
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *,
+         epilogue: str = "store", residual: torch.Tensor | None = None, bn: int | None = None,
+         m: int | None = None, pdl: bool = False) -> torch.Tensor:
+    """``a[M,K]`` bf16 row-major (row stride free), ``w[N,K]`` bf16; returns ``out``.
+
+    epilogue: ``store`` (bf16), ``f32``, ``acc`` (bf16 ``out = a·wᵀ + residual``; residual defaults
+    to ``out`` itself), ``swiglu`` (``out[M, N/2] = silu(gate)·up`` over interleaved weights).
+    ``m`` runs only the first m rows (the tensor maps are made for the whole buffer, so a decode
+    step with fewer rows reuses them).
+    """
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1]
+    M = a.shape[0] if m is None else m
+    N, K = w.shape
+    assert K % 8 == 0 and N % 8 == 0
+    k = Kernels.get(a.device)
+    out_cols = N // 2 if epilogue == "swiglu" else N
+    if out is None:
+        dt = torch.float32 if epilogue == "f32" else torch.bfloat16
+        out = torch.empty(a.shape[0], out_cols, dtype=dt, device=a.device)
+    assert out.stride(1) == 1 and out.shape[1] == out_cols
+    if epilogue == "acc" and residual is None:
+        residual = out
+    if residual is not None:
+        assert residual.stride(0) == out.stride(0) and residual.dtype == torch.bfloat16
+    if M == 0:
+        return out
+    if bn is None:
+        bn = pick_bn(M, N, k.sm_count, epilogue)
+    tma_a = k.tensor_map_2d(a, BM, BK)
+    tma_b = k.tensor_map_2d(w, bn, BK)
+    tiles = ((M + BM - 1) // BM) * ((N + bn - 1) // bn)
+    grid = min(tiles, k.sm_count)
+    entry = f"kern_gemm_bf16_tn{_EPI[epilogue]}_n{bn}"
+    k.launch("gemm_bf16", entry, (grid,), (192,),
+             [tma_a, tma_b, ptr(out), ptr(residual), i32(M), i32(N), i32(K), i32(out.stride(0)),
+              ptr(k.err_word())],
+             shared_mem=smem_bytes(bn), pdl=pdl)
+    return out
+
+
+def gemm_reference(a: torch.Tensor, w: torch.Tensor, epilogue: str = "store",
+                   residual: torch.Tensor | None = None) -> torch.Tensor:
+    """Plain PyTorch fp32 statement of the same op (the numerics oracle)."""
+    acc = a.float() @ w.float().t()
+    if epilogue == "f32":
+        return acc
+    if epilogue == "acc":
+        return (acc + residual.float()).to(torch.bfloat16)
+    if epilogue == "swiglu":
+        m, n = acc.shape
+        t = acc.reshape(m, n // 32, 2, 16)
+        g, u = t[:, :, 0], t[:, :, 1]
+        return (torch.nn.functional.silu(g) * u).reshape(m, n // 2).to(torch.bfloat16)
+    return acc.to(torch.bfloat16)
