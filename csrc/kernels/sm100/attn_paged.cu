@@ -1,0 +1,411 @@
+// Paged GQA attention over the KV cache written by kern_rope_kv_append_bf16: one kernel body for
+//   * decode / speculative-verify rows (few query rows per sequence; the four math warps split each
+//     64-token KV tile between them, optional split-KV over grid.z with a merge kernel), and
+//   * causal chunked prefill (each math warp owns 16 query rows of a 64-row block and walks the
+//     KV tiles up to its causal limit; earlier chunks / a cached prefix are simply more pages).
+// KV tiles are fetched by a producer warp with 2-D TMA boxes (128-byte swizzle, no multicast)
+// into a ring of stages guarded by bounded mbarrier waits; the math is bf16 mma.sync with f32
+// online softmax. The kernel is bandwidth-bound in decode (the KV cache is read exactly once) —
+// the roofline it is measured against is HBM, not the tensor cores.
+// (The reference takes this kernel as a mined trtllm-gen cubin; it has no source counterpart.)
+//
+// Layouts: q rows live inside the fused qkv buffer (row stride q_stride elements, head h at h*D);
+// out is [tokens][HQ*D]; kv pool as in attn_prep.cu; block_table [seqs][max_pages] i32;
+// seq_lens [seqs] i32 = context length including this step's rows; cu_q [seqs+1] i32 row starts
+// (nullptr: every sequence has rows_per_seq rows).
+#include "common.cuh"
+
+namespace kern {
+
+constexpr int TK = 64;  // tokens per KV tile
+
+KERN_DEVICE void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+KERN_DEVICE void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+KERN_DEVICE void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// byte offset of (token row, 16-byte chunk) inside a KV tile stored as D/64 column blocks of
+// [TK rows][128 bytes] with the TMA 128-byte swizzle
+KERN_DEVICE uint32_t kv_off(int tok, int chunk) {
+  const int cb = chunk >> 3, c = chunk & 7;
+  return (uint32_t)(cb * (TK * 128) + tok * 128 + ((c ^ (tok & 7)) << 4));
+}
+
+template <int D>
+struct AttnCfg {
+  static constexpr int kTileBytes = TK * D * 2;         // one of K or V
+  static constexpr int kStageBytes = 2 * kTileBytes;    // K then V
+  static constexpr int kStages = D >= 256 ? 3 : 4;
+  static constexpr int kQStride = D + 8;                // padded bf16 row of the q tile
+  static constexpr int kQBytes = 64 * kQStride * 2;
+  static constexpr int kSmem = 1024 + kStages * kStageBytes + kQBytes + 256;
+};
+
+struct AttnArgs {
+  const __nv_bfloat16* q;
+  __nv_bfloat16* out;
+  float* ws_o;       // split partials [token][hq][splits][D] (nullptr when splits == 1)
+  float* ws_ml;      // [token][hq][splits][2]
+  const int* block_table;
+  const int* seq_lens;
+  const int* cu_q;
+  int* err;
+  int seqs, hq, hk, q_stride, out_stride, max_pages, page_size, rows_per_seq, splits, pool_pages;
+  float scale_log2;
+};
+
+// PREFILL = false: decode/verify (warps split tokens); true: causal prefill (warps split rows)
+template <int D, bool PREFILL>
+KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a) {
+  using Cfg = AttnCfg<D>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int NT = PREFILL ? 8 : 2;        // 8-token n-tiles of S per warp per KV tile
+  constexpr int ROWS = PREFILL ? 64 : 16;    // query rows per CTA
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* stages = smem;
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem + kStages * Cfg::kStageBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kQBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kStages);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = a.hq / a.hk;
+  const int seq = blockIdx.y;
+  const int L = a.seq_lens[seq];
+  const int row0_tok = a.cu_q ? a.cu_q[seq] : seq * a.rows_per_seq;
+  const int R = a.cu_q ? a.cu_q[seq + 1] - row0_tok : a.rows_per_seq;  // this step's rows
+  const int toks_per_blk = PREFILL ? (64 / G) : (16 / G > 0 ? 16 / G : 1);
+  const int nblk = (R + toks_per_blk - 1) / toks_per_blk;
+  const int kvh = blockIdx.x % a.hk;
+  const int blk = blockIdx.x / a.hk;
+  const int split = blockIdx.z;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(kv_map);
+  }
+  __syncthreads();
+  pdl_wait();
+  if (blk >= nblk || L <= 0 || R <= 0) return;   // uniform per CTA
+
+  const int tok_lo = blk * toks_per_blk;                       // first query token of this block
+  const int tok_n = min(toks_per_blk, R - tok_lo);
+  const int valid_rows = tok_n * G;
+  // query token r (0-based among this step's R rows) sits at position L - R + r
+  const int last_pos = L - R + tok_lo + tok_n - 1;
+  const int ntiles_all = last_pos / TK + 1;
+  int tile_lo = 0, tile_hi = ntiles_all;
+  if (a.splits > 1) {
+    const int per = (ntiles_all + a.splits - 1) / a.splits;
+    tile_lo = split * per;
+    tile_hi = min(ntiles_all, tile_lo + per);
+    if (tile_hi < tile_lo) tile_hi = tile_lo;
+  }
+  const int ntiles = tile_hi - tile_lo;
+
+  // ---- q tile -> shared (all 5 warps help) ----
+  for (int i = threadIdx.x; i < ROWS * (D / 8); i += blockDim.x) {
+    const int r = i / (D / 8), c = i % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < valid_rows) {
+      const int tk = tok_lo + r / G, g = r % G;
+      v = *reinterpret_cast<const uint4*>(a.q + (size_t)(row0_tok + tk) * a.q_stride +
+                                          (size_t)(kvh * G + g) * D + c * 8);
+    }
+    *reinterpret_cast<uint4*>(qs + r * Cfg::kQStride + c * 8) = v;
+  }
+  __syncthreads();
+
+  if (warp == 4) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      const int box_rows = a.page_size < TK ? a.page_size : TK;
+      const int boxes = TK / box_rows;
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = 0; t < ntiles; ++t) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+          set_error(a.err, ERR_WAIT_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        uint8_t* sk = stages + stage * Cfg::kStageBytes;
+        uint8_t* sv = sk + Cfg::kTileBytes;
+        mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+        const int tok0 = (tile_lo + t) * TK;
+        for (int b = 0; b < boxes; ++b) {
+          const int tok = tok0 + b * box_rows;
+          int page = 0, in_page = 0;
+          const int pidx = tok / a.page_size;
+          if (tok < L && pidx < a.max_pages) {
+            page = a.block_table[(size_t)seq * a.max_pages + pidx];
+            in_page = tok % a.page_size;
+          }
+          if (page < 0 || page >= a.pool_pages) {
+            set_error(a.err, ERR_BOUNDS);
+            page = 0;
+          }
+          // rows of the 2-D view: ((page*2 + kv)*HK + head)*page_size + offset
+          const int krow = ((page * 2 + 0) * a.hk + kvh) * a.page_size + in_page;
+          const int vrow = ((page * 2 + 1) * a.hk + kvh) * a.page_size + in_page;
+#pragma unroll
+          for (int cb = 0; cb < D / 64; ++cb) {
+            tma_load_2d(sk + cb * (TK * 128) + b * box_rows * 128, kv_map, cb * 64, krow,
+                        &full_bar[stage]);
+            tma_load_2d(sv + cb * (TK * 128) + b * box_rows * 128, kv_map, cb * 64, vrow,
+                        &full_bar[stage]);
+          }
+        }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  }
+
+  float o[D / 8][4];
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  if (warp < 4) {
+    // ---------------- math warps ----------------
+    const int qrow_base = PREFILL ? warp * 16 : 0;
+    const int rA = qrow_base + (lane >> 2), rB = rA + 8;          // this thread's two rows
+    const int posA = rA < valid_rows ? (L - R + tok_lo + rA / G) : -1;
+    const int posB = rB < valid_rows ? (L - R + tok_lo + rB / G) : -1;
+    const uint32_t q_addr = smem_u32(qs) + ((qrow_base + (lane & 7) + ((lane >> 3) & 1) * 8) *
+                                            Cfg::kQStride + (lane >> 4) * 8) * 2;
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int t = 0; t < ntiles; ++t) {
+      if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+        set_error(a.err, ERR_WAIT_FULL);
+        *abort_flag = 1;
+        break;
+      }
+      const uint32_t sk = smem_u32(stages + stage * Cfg::kStageBytes);
+      const uint32_t sv = sk + Cfg::kTileBytes;
+      const int tok0 = (tile_lo + t) * TK;
+      const int wtok = PREFILL ? 0 : warp * 16;   // this warp's token offset inside the tile
+      // a whole tile above the causal limit of this warp's rows contributes nothing
+      const int warp_max_pos = L - R + tok_lo + min(valid_rows - 1, qrow_base + 15) / G;
+      const bool skip = PREFILL && (tok0 > warp_max_pos || qrow_base >= valid_rows);
+      if (!skip) {
+        // ---- S = Q K^T ----
+        float s[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; kk += 2) {
+          uint32_t qa[2][4];
+          ldsm_x4(q_addr + kk * 32, qa[0][0], qa[0][1], qa[0][2], qa[0][3]);
+          ldsm_x4(q_addr + kk * 32 + 32, qa[1][0], qa[1][1], qa[1][2], qa[1][3]);
+#pragma unroll
+          for (int n = 0; n < NT; ++n) {
+            // four 8x8 matrices: tokens n*8.., d chunks 2kk .. 2kk+3
+            const int tok = wtok + n * 8 + (lane & 7);
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4(sk + kv_off(tok, kk * 2 + (lane >> 3)), b0, b1, b2, b3);
+            mma_bf16_16816(s[n], qa[0][0], qa[0][1], qa[0][2], qa[0][3], b0, b1);
+            mma_bf16_16816(s[n], qa[1][0], qa[1][1], qa[1][2], qa[1][3], b2, b3);
+          }
+        }
+        // ---- mask + online softmax (base-2) ----
+        float mxA = -INFINITY, mxB = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          const int j = tok0 + wtok + n * 8 + 2 * (lane & 3);
+          s[n][0] = (j <= posA) ? s[n][0] * a.scale_log2 : -INFINITY;
+          s[n][1] = (j + 1 <= posA) ? s[n][1] * a.scale_log2 : -INFINITY;
+          s[n][2] = (j <= posB) ? s[n][2] * a.scale_log2 : -INFINITY;
+          s[n][3] = (j + 1 <= posB) ? s[n][3] * a.scale_log2 : -INFINITY;
+          mxA = fmaxf(mxA, fmaxf(s[n][0], s[n][1]));
+          mxB = fmaxf(mxB, fmaxf(s[n][2], s[n][3]));
+        }
+        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+        const float mA = fmaxf(m_run[0], mxA), mB = fmaxf(m_run[1], mxB);
+        const float mA_use = mA == -INFINITY ? 0.f : mA, mB_use = mB == -INFINITY ? 0.f : mB;
+        const float cA = exp2f(m_run[0] - mA_use), cB = exp2f(m_run[1] - mB_use);
+        m_run[0] = mA;
+        m_run[1] = mB;
+        float sumA = 0.f, sumB = 0.f;
+        uint32_t pa[NT][2];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          const float p0 = exp2f(s[n][0] - mA_use), p1 = exp2f(s[n][1] - mA_use);
+          const float p2 = exp2f(s[n][2] - mB_use), p3 = exp2f(s[n][3] - mB_use);
+          sumA += p0 + p1;
+          sumB += p2 + p3;
+          pa[n][0] = pack_bf16x2(p0, p1);
+          pa[n][1] = pack_bf16x2(p2, p3);
+        }
+        l_run[0] = l_run[0] * cA + sumA;
+        l_run[1] = l_run[1] * cB + sumB;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          o[i][0] *= cA; o[i][1] *= cA; o[i][2] *= cB; o[i][3] *= cB;
+        }
+        // ---- O += P V ----
+#pragma unroll
+        for (int ks = 0; ks < NT / 2; ++ks) {   // 16 tokens per k-step
+          const int tok = wtok + ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+          for (int dn = 0; dn < D / 16; ++dn) {  // two 8-wide d tiles per ldmatrix.x4.trans
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_t(sv + kv_off(tok, dn * 2 + (lane >> 4)), b0, b1, b2, b3);
+            mma_bf16_16816(o[dn * 2], pa[2 * ks][0], pa[2 * ks][1], pa[2 * ks + 1][0],
+                           pa[2 * ks + 1][1], b0, b1);
+            mma_bf16_16816(o[dn * 2 + 1], pa[2 * ks][0], pa[2 * ks][1], pa[2 * ks + 1][0],
+                           pa[2 * ks + 1][1], b2, b3);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+      if (++stage == kStages) { stage = 0; phase ^= 1; }
+    }
+    // row sums live spread over the quad
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+  }
+
+  // ---------------- combine + write ----------------
+  if (!PREFILL) {
+    // the four warps hold partial (m, l, O) of the same 16 rows over disjoint tokens: merge in smem
+    __syncthreads();  // every stage has been consumed: reuse the stage memory
+    float* mo = reinterpret_cast<float*>(stages);            // [4][16][D]
+    float* mm = mo + 4 * 16 * D;                             // [4][16]
+    float* ml = mm + 64;                                     // [4][16]
+    if (warp < 4) {
+      const int rA = lane >> 2, rB = rA + 8;
+      if ((lane & 3) == 0) {
+        mm[warp * 16 + rA] = m_run[0]; mm[warp * 16 + rB] = m_run[1];
+        ml[warp * 16 + rA] = l_run[0]; ml[warp * 16 + rB] = l_run[1];
+      }
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        const int c = i * 8 + 2 * (lane & 3);
+        *reinterpret_cast<float2*>(mo + (warp * 16 + rA) * D + c) = make_float2(o[i][0], o[i][1]);
+        *reinterpret_cast<float2*>(mo + (warp * 16 + rB) * D + c) = make_float2(o[i][2], o[i][3]);
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 16 * D; i += blockDim.x) {
+      const int r = i / D, c = i % D;
+      if (r >= valid_rows) continue;
+      float m = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) m = fmaxf(m, mm[w * 16 + r]);
+      const float m_use = m == -INFINITY ? 0.f : m;
+      float l = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = exp2f(mm[w * 16 + r] - m_use);
+        l += ml[w * 16 + r] * f;
+        acc += mo[(w * 16 + r) * D + c] * f;
+      }
+      const int tk = row0_tok + tok_lo + r / G, head = kvh * G + r % G;
+      if (a.splits == 1) {
+        a.out[(size_t)tk * a.out_stride + (size_t)head * D + c] =
+            __float2bfloat16(l > 0.f ? acc / l : 0.f);
+      } else {
+        const size_t base = ((size_t)tk * a.hq + head) * a.splits + split;
+        a.ws_o[base * D + c] = acc;
+        if (c == 0) {
+          a.ws_ml[base * 2] = m;
+          a.ws_ml[base * 2 + 1] = l;
+        }
+      }
+    }
+  } else if (warp < 4) {
+    const int rA = warp * 16 + (lane >> 2), rB = rA + 8;
+    const float iA = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, iB = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int c = i * 8 + 2 * (lane & 3);
+      if (rA < valid_rows) {
+        const int tk = row0_tok + tok_lo + rA / G, head = kvh * G + rA % G;
+        *reinterpret_cast<uint32_t*>(a.out + (size_t)tk * a.out_stride + (size_t)head * D + c) =
+            pack_bf16x2(o[i][0] * iA, o[i][1] * iA);
+      }
+      if (rB < valid_rows) {
+        const int tk = row0_tok + tok_lo + rB / G, head = kvh * G + rB % G;
+        *reinterpret_cast<uint32_t*>(a.out + (size_t)tk * a.out_stride + (size_t)head * D + c) =
+            pack_bf16x2(o[i][2] * iB, o[i][3] * iB);
+      }
+    }
+  }
+  pdl_launch_dependents();
+}
+
+}  // namespace kern
+
+using namespace kern;
+
+#define KERN_ATTN_ENTRY(name, D, PREFILL)                                                        \
+  extern "C" __global__ void __launch_bounds__(160, 1)                                           \
+      name(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* q,                   \
+           __nv_bfloat16* out, float* ws_o, float* ws_ml, const int* block_table,                \
+           const int* seq_lens, const int* cu_q, int seqs, int hq, int hk, int q_stride,         \
+           int out_stride, int max_pages, int page_size, int rows_per_seq, int splits,           \
+           int pool_pages, float scale_log2, int* err) {                                         \
+    AttnArgs a{q, out, ws_o, ws_ml, block_table, seq_lens, cu_q, err, seqs, hq, hk, q_stride,    \
+               out_stride, max_pages, page_size, rows_per_seq, splits, pool_pages, scale_log2};  \
+    attn_body<D, PREFILL>(&kv_map, a);                                                           \
+  }
+
+KERN_ATTN_ENTRY(kern_attn_decode_paged_d64, 64, false)
+KERN_ATTN_ENTRY(kern_attn_decode_paged_d128, 128, false)
+KERN_ATTN_ENTRY(kern_attn_decode_paged_d256, 256, false)
+KERN_ATTN_ENTRY(kern_attn_prefill_paged_d64, 64, true)
+KERN_ATTN_ENTRY(kern_attn_prefill_paged_d128, 128, true)
+KERN_ATTN_ENTRY(kern_attn_prefill_paged_d256, 256, true)
+
+// Merge split-KV partials: out[token][head][:] = sum_s O_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m)
+// grid = tokens * hq, block = D threads (<= 256)
+extern "C" __global__ void kern_attn_merge_splits(const float* ws_o, const float* ws_ml,
+                                                  __nv_bfloat16* out, int rows, int hq, int d,
+                                                  int splits, int out_stride) {
+  pdl_wait();
+  const int row = blockIdx.x;  // token * hq + head
+  if (row >= rows) return;
+  const int tk = row / hq, head = row % hq;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, ws_ml[((size_t)row * splits + s) * 2]);
+  const float m_use = m == -INFINITY ? 0.f : m;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float l = 0.f, acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const size_t b = (size_t)row * splits + s;
+      const float f = exp2f(ws_ml[b * 2] - m_use);
+      l += ws_ml[b * 2 + 1] * f;
+      acc += ws_o[b * d + c] * f;
+    }
+    out[(size_t)tk * out_stride + (size_t)head * d + c] = __float2bfloat16(l > 0.f ? acc / l : 0.f);
+  }
+}

@@ -1,0 +1,152 @@
+"""RoPE + paged KV append, and paged GQA attention (decode / speculative-verify rows / causal chunked
+prefill), with PyTorch fp32 reference statements of the same ops.
+
+KV cache of one layer: ``pool[pages, 2, kv_heads, page_size, head_dim]`` bf16 (k then v), slot =
+page * page_size + offset. Reference counterparts: tools/kernels-src/attn_prep.cu:152 (prep); the
+attention kernels are mined cubins in the reference (no source counterpart).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .launcher import Kernels, f32, i32, i64, ptr
+
+TK = 64
+
+
+def rope_tables(max_pos: int, rot: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """f32 ``cos, sin`` tables ``[max_pos, rot/2]`` computed on the device in double precision."""
+    k = Kernels.get(device)
+    cos = torch.empty(max_pos, rot // 2, dtype=torch.float32, device=device)
+    sin = torch.empty_like(cos)
+    import struct
+    k.launch("attn_prep", "kern_rope_table_f32", (min(1024, (cos.numel() + 255) // 256),), (256,),
+             [ptr(cos), ptr(sin), i32(max_pos), i32(rot), struct.pack("<d", float(theta))])
+    return cos, sin
+
+
+def rope_kv_append(qkv: torch.Tensor, pool: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                   cos: torch.Tensor, sin: torch.Tensor, hq: int, hk: int, d: int, rot: int | None = None,
+                   q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None,
+                   eps: float = 1e-6, norm_plus_one: bool = False, tokens: int | None = None) -> None:
+    """Rotate q (in place in ``qkv``) and k, append k/v of every token to ``pool`` at its slot."""
+    k = Kernels.get(qkv.device)
+    t = qkv.shape[0] if tokens is None else tokens
+    pages, two, hk_, page_size, d_ = pool.shape
+    assert two == 2 and hk_ == hk and d_ == d and qkv.shape[1] == (hq + 2 * hk) * d and d % 8 == 0
+    assert positions.dtype == torch.int64 and slots.dtype == torch.int64
+    rot = d if rot is None else rot
+    assert cos.shape[1] == rot // 2
+    k.launch("attn_prep", "kern_rope_kv_append_bf16", (t,), (128,),
+             [ptr(qkv), ptr(pool), ptr(positions), ptr(slots), ptr(cos), ptr(sin), ptr(q_norm),
+              ptr(k_norm), i32(t), i32(hq), i32(hk), i32(d), i32(rot), i32(page_size), f32(eps),
+              i32(int(norm_plus_one)), i64(pages * page_size), i32(cos.shape[0]), ptr(k.err_word())],
+             shared_mem=4 * d * 4)
+
+
+def _attn_smem(d: int) -> int:
+    stages = 3 if d >= 256 else 4
+    return 1024 + stages * (2 * TK * d * 2) + 64 * (d + 8) * 2 + 256
+
+
+def pick_splits(ctas_without_split: int, max_len: int, sms: int, max_splits: int = 32) -> int:
+    """Split the KV range only while it adds CTAs up to about one wave and leaves >= 4 tiles each."""
+    if ctas_without_split >= sms:
+        return 1
+    tiles = max(1, (max_len + TK - 1) // TK)
+    s = min(max_splits, max(1, sms // max(1, ctas_without_split)), max(1, tiles // 4))
+    return max(1, s)
+
+
+def paged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
+                    seq_lens: torch.Tensor, hq: int, *, out: torch.Tensor | None = None,
+                    prefill: bool = False, cu_q: torch.Tensor | None = None, rows_per_seq: int = 1,
+                    max_rows: int | None = None, seqs: int | None = None, splits: int | None = None,
+                    max_len: int | None = None, scale: float | None = None,
+                    workspace: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
+    """Attention of this step's query rows over each sequence's paged context.
+
+    ``q``: 2-D bf16 view whose row t holds the ``hq`` query heads of token t (a column slice of the
+    fused qkv buffer works: the row stride is free). ``seq_lens[s]`` counts the context *including*
+    this step's rows; rows of sequence s are ``cu_q[s]:cu_q[s+1]`` or ``s*rows_per_seq`` onward.
+    ``prefill=True`` picks the row-parallel causal kernel, else the token-parallel decode kernel
+    (with split-KV when few CTAs would run). Returns ``out[tokens, hq*d]``.
+    """
+    k = Kernels.get(q.device)
+    pages, _, hk, page_size, d = pool.shape
+    assert d in (64, 128, 256), "attention kernels are built for head_dim 64, 128, 256"
+    assert page_size >= 8 and (page_size <= TK and TK % page_size == 0 or page_size % TK == 0)
+    g = hq // hk
+    assert hq % hk == 0 and g <= 16
+    n_seqs = block_table.shape[0] if seqs is None else seqs
+    if out is None:
+        out = torch.empty(q.shape[0], hq * d, dtype=torch.bfloat16, device=q.device)
+    if max_rows is None:
+        max_rows = rows_per_seq if cu_q is None else q.shape[0]
+    toks_per_blk = (64 // g) if prefill else max(1, 16 // g)
+    nblk = (max_rows + toks_per_blk - 1) // toks_per_blk
+    if max_len is None:
+        max_len = block_table.shape[1] * page_size
+    if prefill:
+        splits = 1
+    elif splits is None:
+        splits = pick_splits(hk * nblk * n_seqs, max_len, k.sm_count)
+    ws_o = ws_ml = None
+    if splits > 1:
+        if workspace is not None:
+            ws_o, ws_ml = workspace
+        else:
+            ws_o = torch.empty(q.shape[0] * hq * splits * d, dtype=torch.float32, device=q.device)
+            ws_ml = torch.empty(q.shape[0] * hq * splits * 2, dtype=torch.float32, device=q.device)
+        assert ws_o.numel() >= q.shape[0] * hq * splits * d
+    view = pool.view(pages * 2 * hk * page_size, d)
+    kv_map = k.tensor_map_2d(view, min(page_size, TK), 64)
+    scale = (1.0 / math.sqrt(d)) if scale is None else scale
+    entry = f"kern_attn_{'prefill' if prefill else 'decode'}_paged_d{d}"
+    k.launch("attn_paged", entry, (hk * nblk, n_seqs, splits), (160,),
+             [kv_map, ptr(q), ptr(out), ptr(ws_o), ptr(ws_ml), ptr(block_table), ptr(seq_lens),
+              ptr(cu_q), i32(n_seqs), i32(hq), i32(hk), i32(q.stride(0)), i32(out.stride(0)),
+              i32(block_table.shape[1]), i32(page_size), i32(rows_per_seq), i32(splits), i32(pages),
+              f32(scale * 1.4426950408889634), ptr(k.err_word())],
+             shared_mem=_attn_smem(d))
+    if splits > 1:
+        rows = q.shape[0] * hq
+        k.launch("attn_paged", "kern_attn_merge_splits", (rows,), (min(256, d),),
+                 [ptr(ws_o), ptr(ws_ml), ptr(out), i32(rows), i32(hq), i32(d), i32(splits),
+                  i32(out.stride(0))])
+    return out
+
+
+# ---- PyTorch fp32 references ---------------------------------------------------------------------
+def rope_reference(x: torch.Tensor, positions: torch.Tensor, rot: int, theta: float) -> torch.Tensor:
+    """x [tokens, heads, d] -> rotate-half RoPE over the first ``rot`` dims, fp32 math."""
+    half = rot // 2
+    inv = theta ** (-torch.arange(0, half, dtype=torch.float64, device=x.device) * 2.0 / rot)
+    ang = positions.double()[:, None] * inv[None, :]
+    cos, sin = ang.cos().float()[:, None, :], ang.sin().float()[:, None, :]
+    xf = x.float()
+    a, b = xf[..., :half], xf[..., half:rot]
+    out = xf.clone()
+    out[..., :half] = a * cos - b * sin
+    out[..., half:rot] = b * cos + a * sin
+    return out
+
+
+def attention_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Tensor,
+                        scale: float | None = None) -> torch.Tensor:
+    """One sequence: q [R, hq, d], k/v [L, hk, d] (already rotated), q_pos [R] absolute positions.
+    Row r attends to keys 0..q_pos[r]. fp32 math; returns [R, hq*d] fp32."""
+    r, hq, d = q.shape
+    l, hk, _ = k.shape
+    g = hq // hk
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    kk = k.float().repeat_interleave(g, dim=1)
+    vv = v.float().repeat_interleave(g, dim=1)
+    s = torch.einsum("rhd,lhd->hrl", q.float(), kk) * scale
+    mask = torch.arange(l, device=q.device)[None, :] <= q_pos[:, None]
+    s = s.masked_fill(~mask[None], float("-inf"))
+    p = torch.softmax(s, -1)
+    o = torch.einsum("hrl,lhd->rhd", p, vv)
+    return o.reshape(r, hq * d)
