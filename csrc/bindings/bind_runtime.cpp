@@ -1,0 +1,110 @@
+// Python view of the executor (`kern_b200._native.Runtime`).
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "../manifest/verify.hpp"
+#include "../runtime/runtime.hpp"
+
+namespace py = pybind11;
+using namespace kern;
+
+void bind_runtime(py::module_& m) {
+  py::class_<Runtime, std::shared_ptr<Runtime>>(m, "Runtime")
+      .def(py::init([](const std::string& manifest_text, const std::string& kernels_dir, int gpu,
+                       std::map<std::string, std::pair<uint64_t, uint64_t>> topology, uint64_t tokens, uint64_t slots,
+                       double memory_fraction, uint64_t stream) {
+             Errors errs;
+             Manifest mf = parse_manifest_text(manifest_text, errs);
+             if (errs.empty()) errs = verify_manifest(mf);
+             if (!errs.empty()) {
+               std::string msg = "manifest does not verify:";
+               for (auto& e : errs) msg += "\n  - " + e;
+               throw py::value_error(msg);
+             }
+             std::map<std::string, GroupRank> topo;
+             for (auto& kv : topology) topo[kv.first] = GroupRank{kv.second.first, kv.second.second};
+             Capacity cap;
+             cap.tokens = tokens;
+             cap.slots = slots;
+             cap.memory_fraction = memory_fraction;
+             return std::make_shared<Runtime>(std::move(mf), kernels_dir, gpu, std::move(topo), cap, stream);
+           }),
+           py::arg("manifest"), py::arg("kernels"), py::arg("gpu") = 0,
+           py::arg("topology") = std::map<std::string, std::pair<uint64_t, uint64_t>>(), py::arg("tokens") = 0,
+           py::arg("slots") = 0, py::arg("memory_fraction") = 0.9, py::arg("stream") = 0)
+      .def("manifest_json", [](Runtime& r) { return manifest_to_json(r.manifest()).dump(1); })
+      .def("protocol_json", [](Runtime& r) -> py::object {
+        if (!r.protocol()) return py::none();
+        return py::str(r.protocol()->to_json().dump());
+      })
+      .def_property_readonly("stream", &Runtime::stream)
+      .def_property_readonly("page_unit", &Runtime::page_unit)
+      .def_property_readonly("pages", &Runtime::pages)
+      .def_property_readonly("slots", &Runtime::slots)
+      .def_property_readonly("launches_total", &Runtime::launches_total)
+      .def_property_readonly("graphs", &Runtime::graphs)
+      .def_property_readonly("awaits_host", &Runtime::awaits_host)
+      .def_property_readonly("weights_loaded", &Runtime::weights_loaded)
+      .def_property_readonly("peers_connected", &Runtime::peers_connected)
+      .def("rank", &Runtime::rank)
+      .def("banner", &Runtime::banner)
+      .def("load_weights", [](Runtime& r, std::vector<std::string> paths) {
+        py::gil_scoped_release rel;
+        r.load_weights(paths);
+      })
+      .def("region", &Runtime::region)
+      .def("write_input", [](Runtime& r, const std::string& name, py::buffer data, size_t offset) {
+        py::buffer_info info = data.request();
+        r.write_input(name, info.ptr, (size_t)info.size * (size_t)info.itemsize, offset);
+      }, py::arg("name"), py::arg("data"), py::arg("offset") = 0)
+      // raw pointer form: pinned host memory owned by the caller (a torch pinned tensor)
+      .def("write_input_ptr", [](Runtime& r, const std::string& name, uint64_t host_ptr, size_t bytes, size_t offset) {
+        r.write_input(name, reinterpret_cast<const void*>(host_ptr), bytes, offset);
+      }, py::arg("name"), py::arg("host_ptr"), py::arg("bytes"), py::arg("offset") = 0)
+      .def("read_output", [](Runtime& r, const std::string& name, size_t bytes, size_t offset) {
+        std::string out(bytes, '\0');
+        {
+          py::gil_scoped_release rel;
+          r.read_output(name, &out[0], bytes, offset);
+        }
+        return py::bytes(out);
+      }, py::arg("name"), py::arg("bytes"), py::arg("offset") = 0)
+      .def("read_output_ptr", [](Runtime& r, const std::string& name, uint64_t host_ptr, size_t bytes, size_t offset) {
+        py::gil_scoped_release rel;
+        r.read_output(name, reinterpret_cast<void*>(host_ptr), bytes, offset);
+      }, py::arg("name"), py::arg("host_ptr"), py::arg("bytes"), py::arg("offset") = 0)
+      .def("synchronize", [](Runtime& r) {
+        py::gil_scoped_release rel;
+        r.synchronize();
+      })
+      .def("run_once_programs", &Runtime::run_once_programs)
+      .def("issue", [](Runtime& r, const std::string& program, const VarMap& vars, bool eager) {
+        return r.issue(program, vars, eager);
+      }, py::arg("program"), py::arg("vars"), py::arg("eager") = false)
+      .def("run", [](Runtime& r, const std::string& program, const VarMap& vars) {
+        size_t n = r.issue(program, vars, false);
+        py::gil_scoped_release rel;
+        r.synchronize();
+        return n;
+      })
+      .def("is_captured", &Runtime::is_captured)
+      .def("enqueue_after", &Runtime::enqueue_after)
+      .def("zero_slot", &Runtime::zero_slot)
+      .def("copy_pages", &Runtime::copy_pages)
+      .def("copy_slot", &Runtime::copy_slot)
+      .def("export_handles", [](Runtime& r) {
+        py::dict d;
+        for (auto& kv : r.export_handles()) d[py::str(kv.first)] = py::bytes(kv.second);
+        return d;
+      })
+      .def("connect", [](Runtime& r, const std::string& group, std::vector<std::map<std::string, py::bytes>> members) {
+        std::vector<std::map<std::string, std::string>> ms;
+        for (auto& mm : members) {
+          std::map<std::string, std::string> one;
+          for (auto& kv : mm) one[kv.first] = std::string(kv.second);
+          ms.push_back(std::move(one));
+        }
+        r.connect(group, ms);
+      })
+      .def("bind_host", &Runtime::bind_host);
+}

@@ -63,6 +63,8 @@ struct AttnArgs {
   const int* block_table;
   const int* seq_lens;
   const int* cu_q;
+  const int* work;        // optional work list of (sequence, query block) pairs; blockIdx.y indexes it
+  const int* work_count;  // number of valid pairs
   int* err;
   int seqs, hq, hk, q_stride, out_stride, max_pages, page_size, rows_per_seq, splits, pool_pages;
   float scale_log2;
@@ -86,14 +88,18 @@ KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = a.hq / a.hk;
-  const int seq = blockIdx.y;
+  int seq = blockIdx.y, blk = blockIdx.x / a.hk;
+  if (a.work != nullptr) {
+    if ((int)blockIdx.y >= *a.work_count) return;   // uniform per CTA, before any barrier
+    seq = a.work[2 * blockIdx.y];
+    blk = a.work[2 * blockIdx.y + 1];
+  }
   const int L = a.seq_lens[seq];
   const int row0_tok = a.cu_q ? a.cu_q[seq] : seq * a.rows_per_seq;
   const int R = a.cu_q ? a.cu_q[seq + 1] - row0_tok : a.rows_per_seq;  // this step's rows
   const int toks_per_blk = PREFILL ? (64 / G) : (16 / G > 0 ? 16 / G : 1);
   const int nblk = (R + toks_per_blk - 1) / toks_per_blk;
   const int kvh = blockIdx.x % a.hk;
-  const int blk = blockIdx.x / a.hk;
   const int split = blockIdx.z;
 
   if (threadIdx.x == 0) {
@@ -371,10 +377,12 @@ using namespace kern;
   extern "C" __global__ void __launch_bounds__(160, 1)                                           \
       name(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* q,                   \
            __nv_bfloat16* out, float* ws_o, float* ws_ml, const int* block_table,                \
-           const int* seq_lens, const int* cu_q, int seqs, int hq, int hk, int q_stride,         \
+           const int* seq_lens, const int* cu_q, const int* work, const int* work_count,         \
+           int seqs, int hq, int hk, int q_stride,                                               \
            int out_stride, int max_pages, int page_size, int rows_per_seq, int splits,           \
            int pool_pages, float scale_log2, int* err) {                                         \
-    AttnArgs a{q, out, ws_o, ws_ml, block_table, seq_lens, cu_q, err, seqs, hq, hk, q_stride,    \
+    AttnArgs a{q, out, ws_o, ws_ml, block_table, seq_lens, cu_q, work, work_count, err, seqs, hq, \
+               hk, q_stride,                                                                     \
                out_stride, max_pages, page_size, rows_per_seq, splits, pool_pages, scale_log2};  \
     attn_body<D, PREFILL>(&kv_map, a);                                                           \
   }
@@ -385,6 +393,31 @@ KERN_ATTN_ENTRY(kern_attn_decode_paged_d256, 256, false)
 KERN_ATTN_ENTRY(kern_attn_prefill_paged_d64, 64, true)
 KERN_ATTN_ENTRY(kern_attn_prefill_paged_d128, 128, true)
 KERN_ATTN_ENTRY(kern_attn_prefill_paged_d256, 256, true)
+
+// Work list for ragged prefill: one (sequence, query block) pair per block of `toks_per_blk` new rows,
+// so the attention grid is sized by the rows of the call and not by sequences x the longest one.
+// One CTA; the plan is the same for every layer of a step.
+extern "C" __global__ void kern_attn_plan(const int* cu_q, int seqs, int toks_per_blk, int* work,
+                                          int* work_count, int max_items) {
+  pdl_wait();
+  __shared__ int base[1025];
+  if (threadIdx.x == 0) {
+    int n = 0;
+    for (int s = 0; s < seqs && s < 1024; ++s) {
+      base[s] = n;
+      const int r = cu_q[s + 1] - cu_q[s];
+      n += r > 0 ? (r + toks_per_blk - 1) / toks_per_blk : 0;
+    }
+    base[seqs < 1024 ? seqs : 1024] = n;
+    *work_count = n < max_items ? n : max_items;
+  }
+  __syncthreads();
+  for (int s = threadIdx.x; s < seqs && s < 1024; s += blockDim.x)
+    for (int i = base[s]; i < base[s + 1] && i < max_items; ++i) {
+      work[2 * i] = s;
+      work[2 * i + 1] = i - base[s];
+    }
+}
 
 // Merge split-KV partials: out[token][head][:] = sum_s O_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m)
 // grid = tokens * hq, block = D threads (<= 256)

@@ -1,0 +1,201 @@
+// The executor: loads a verified manifest onto one GPU, allocates every buffer at its var upper bound
+// and every pooled state as one allocation, resolves each launch to a function of a sha256-pinned
+// module (ABI checked against the driver's view of the kernel's parameters), compiles every program to
+// a flat launch list with its addresses baked in, and replays a program eagerly or as a CUDA graph
+// keyed by the call's var values.
+// Reference: crates/kern-runtime/src/lib.rs:90-400 (façade), load.rs:84-404, compile.rs:30-959,
+// exec.rs:409-821, peers.rs:45-369, lease.rs, derive.rs.
+#pragma once
+#include <array>
+#include <functional>
+#include <map>
+#include <memory>
+#include <optional>
+#include <string>
+#include <vector>
+
+#include "../manifest/protocol.hpp"
+#include "../manifest/types.hpp"
+#include "device.hpp"
+#include "safetensors.hpp"
+
+namespace kern {
+
+struct Capacity {
+  uint64_t tokens = 0;     // token capacity of the paged states (0: fit what the device has left)
+  uint64_t slots = 0;      // per-sequence state slots (excluding the null line)
+  double memory_fraction = 0.9;   // of free device memory the paged states may take when tokens == 0
+};
+
+struct GroupRank {
+  uint64_t index = 0, size = 1;
+};
+
+struct Allocation {
+  uint64_t ptr = 0;
+  uint64_t bytes = 0;
+  bool exported = false;
+  bool host = false;
+  bool borrowed = false;   // owned by someone else (host-bound state, resident weights)
+};
+
+struct StateAlloc : Allocation {
+  uint64_t unit_bytes = 0;   // bytes per page (paged) or per slot (per-sequence); 0 for a fixed state
+  uint64_t units = 0;        // pages or slots (including the null line)
+  bool paged = false, per_seq = false;
+};
+
+// one parameter slot of a compiled launch: a byte image plus the places patched per call
+struct Patch {
+  uint32_t at = 0, width = 4;
+  Expr expr;
+};
+struct CompiledArg {
+  std::vector<uint8_t> image;
+  std::vector<Patch> patches;
+};
+
+enum class ExternKind { None, GemmBf16, GemmBf16Acc, GemmBf16F32 };
+
+struct CompiledLaunch {
+  std::string label;           // op name / call label for traces
+  size_t call_index = 0;
+  CUfunction fn = nullptr;
+  ExternKind ext = ExternKind::None;
+  uint32_t block[3] = {1, 1, 1};
+  Expr grid[3];
+  std::optional<Expr> shared_mem;
+  uint32_t cluster[3] = {1, 1, 1};
+  bool pdl = false;
+  std::optional<When> when;
+  std::vector<CompiledArg> args;
+  uint8_t lane = 0;
+  std::vector<uint8_t> after;   // lanes to wait for before the first launch of this call
+  bool first_of_call = false;
+  // extern GEMM operands
+  uint64_t a_ptr = 0, w_ptr = 0, c_ptr = 0;
+  uint64_t a_rows = 0, w_rows = 0;
+  Expr m, n, k;
+  std::optional<Expr> ldc, lda;
+};
+
+struct CompiledProgram {
+  std::string name;
+  std::vector<CompiledLaunch> launches;
+  std::vector<std::string> vars;   // the vars its launches read: the graph key
+  bool graph = false;
+  uint8_t lanes = 1;
+};
+
+class Runtime {
+ public:
+  Runtime(Manifest manifest, std::string kernels_dir, int gpu, std::map<std::string, GroupRank> topology, Capacity cap,
+          uint64_t stream = 0);
+  ~Runtime();
+  Runtime(const Runtime&) = delete;
+
+  const Manifest& manifest() const { return m_; }
+  const Protocol* protocol() const { return proto_ ? &*proto_ : nullptr; }
+  Device& device() { return *dev_; }
+  uint64_t stream() const { return (uint64_t)stream_; }
+  uint64_t page_unit() const { return page_unit_; }
+  uint64_t pages() const { return pages_; }
+  uint64_t slots() const { return slots_; }
+  uint64_t rank(const std::string& group) const;
+
+  // ---- weights ----
+  void load_weights(const std::vector<std::string>& safetensors_paths);
+  bool weights_loaded() const { return weights_loaded_; }
+
+  // ---- IO ----
+  std::pair<uint64_t, uint64_t> region(const std::string& name) const;   // (device ptr, bytes) of a buffer or state
+  void write_input(const std::string& name, const void* data, size_t bytes, size_t offset = 0);
+  void read_output(const std::string& name, void* out, size_t bytes, size_t offset = 0);
+  void synchronize();
+
+  // ---- execution ----
+  void run_once_programs();
+  // eager or captured according to the program and `eager`; returns the number of kernel launches issued
+  // (a graph replay counts the launches its graph holds)
+  size_t issue(const std::string& program, const VarMap& vars, bool eager = false);
+  bool is_captured(const std::string& program, const VarMap& vars) const;
+  size_t graphs() const { return graphs_.size(); }
+  uint64_t launches_total() const { return launches_total_; }
+
+  // ---- pool support ----
+  void zero_slot(int32_t slot);
+  void copy_pages(const std::vector<std::pair<int32_t, int32_t>>& pages);
+  void copy_slot(int32_t src, int32_t dst);
+
+  // ---- peers ----
+  // handles of every exported buffer and state of this rank, keyed by name (64-byte IPC handles)
+  std::map<std::string, std::string> export_handles();
+  // handles of every member of `group` in member order -> fills each peer buffer of that group
+  void connect(const std::string& group, const std::vector<std::map<std::string, std::string>>& members);
+  bool peers_connected() const;
+
+  // ---- hosted mode ----
+  bool awaits_host() const;
+  void bind_host(const std::map<std::string, std::tuple<uint64_t, std::string, std::vector<uint64_t>, std::vector<uint64_t>>>& regions);
+  size_t enqueue_after(const std::string& program, const VarMap& vars, uint64_t host_stream);
+
+  std::string banner() const;   // every state / buffer size and op -> module resolution
+
+ private:
+  Manifest m_;
+  std::optional<Protocol> proto_;
+  std::string kernels_dir_;
+  std::shared_ptr<Device> dev_;
+  std::map<std::string, GroupRank> topo_;
+  Capacity cap_;
+  CUstream stream_ = nullptr;
+  bool own_stream_ = false;
+  std::vector<CUstream> lane_streams_;
+  std::vector<CUevent> lane_events_;
+  CUevent host_in_ = nullptr, host_out_ = nullptr;
+
+  std::map<std::string, CUmodule> modules_;
+  CUmodule builtin_gemm_ = nullptr;
+  std::map<std::string, CUfunction> gemm_fns_;
+  std::map<std::string, Allocation> buffers_;
+  std::map<std::string, StateAlloc> states_;
+  std::map<std::string, std::map<std::string, Allocation>> scratch_;   // op -> scratch name -> allocation
+  std::map<std::string, std::vector<uint64_t>> imported_;             // peer buffer -> mapped addresses
+  std::vector<uint64_t> imported_ptrs_;
+  uint64_t page_unit_ = 1, pages_ = 0, slots_ = 0;
+  uint64_t err_word_ = 0;
+  bool weights_loaded_ = false;
+  bool compiled_ = false;
+
+  std::map<std::string, CompiledProgram> programs_;
+  struct GraphKey {
+    std::string program;
+    std::vector<uint64_t> values;
+    bool operator<(const GraphKey& o) const { return std::tie(program, values) < std::tie(o.program, o.values); }
+  };
+  struct GraphEntry {
+    CUgraphExec exec = nullptr;
+    size_t launches = 0;
+  };
+  std::map<GraphKey, GraphEntry> graphs_;
+  uint64_t launches_total_ = 0;
+  void* staging_ = nullptr;
+  size_t staging_bytes_ = 0;
+
+  void load_modules();
+  void allocate();
+  void compile_all();
+  CompiledProgram compile_program(const std::string& name, const Program& p);
+  void compile_call(CompiledProgram& out, const std::string& pname, const Program& p, size_t ci);
+  CompiledArg pointer_arg(uint64_t ptr);
+  uint64_t arg_pointer(const Arg& a) const;
+  uint64_t arg_extent(const Arg& a) const;
+  size_t enqueue(const CompiledProgram& p, const VarMap& vars);
+  size_t launch_one(const CompiledLaunch& l, const VarMap& vars, CUstream s);
+  size_t launch_gemm(const CompiledLaunch& l, const VarMap& vars, CUstream s);
+  void ensure_staging(size_t bytes);
+  void upload(uint64_t dst, const uint8_t* src, size_t bytes);
+  void upload_2d(uint64_t dst, size_t dst_pitch, const uint8_t* src, size_t src_pitch, size_t width, size_t rows);
+};
+
+}  // namespace kern

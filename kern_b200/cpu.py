@@ -1,0 +1,436 @@
+"""A host-memory stand-in for the device: the same manifest executed by PyTorch on the CPU.
+
+``CpuRuntime`` has the interface of :class:`kern_b200.runtime.Runtime` (protocol, write / read, issue,
+pool support), allocates every buffer and state as host tensors, and runs each launch through a
+Python function with the *same parameter list as the CUDA kernel* it stands in for. It exists so that
+the control plane (engine, scheduler, ranks, pipeline, prefill/decode hand-off, fault paths) and whole
+manifests run and are tested on machines with no GPU, and it is the executor of the CPU-only toy
+decoder configuration. (The reference tests its harness the same way, with a host interpreter keyed by
+entry name: crates/kern-test/tests/common/mod.rs:1-130.)
+"""
+from __future__ import annotations
+
+import json
+import math
+import struct
+
+import numpy as np
+import torch
+
+from . import _native
+from .models.common import read_safetensors
+from .runtime import _NP, _TORCH, manifest_text
+
+_ES = {k: np.dtype(v).itemsize for k, v in _NP.items()}
+
+
+def _eval(e, vars_):
+    if isinstance(e, int):
+        return e
+    if isinstance(e, str):
+        return vars_[e]
+    (k, a), = e.items()
+    if k == "ceil_div":
+        return -(-_eval(a[0], vars_) // a[1])
+    if k == "mul":
+        return _eval(a[0], vars_) * a[1]
+    if k == "add":
+        return _eval(a[0], vars_) + _eval(a[1], vars_)
+    if k == "clamp":
+        return min(max(_eval(a[0], vars_) - a[1], 0), a[2])
+    raise ValueError(f"unknown expression {e}")
+
+
+# ---- CPU statements of the kernels (same parameter order as the CUDA entries) ------------------------
+def _f(t):
+    return t.float()
+
+
+def k_embedding(g, ids, table, out, tokens, hidden, vocab, err):
+    n = g[0]
+    out.view(-1, hidden)[:n] = table.view(-1, hidden)[ids[:n].long().clamp(0, vocab - 1)]
+
+
+def k_rms_norm(g, x, w, y, rows, n, xs, ys, eps, plus_one):
+    r = g[0]
+    xv = _f(torch.as_strided(x, (r, n), (xs, 1)))
+    ww = _f(w[:n]) + (1.0 if plus_one else 0.0)
+    torch.as_strided(y, (r, n), (ys, 1)).copy_((xv * torch.rsqrt(xv.pow(2).mean(-1, keepdim=True) + eps) * ww).to(y.dtype))
+
+
+def k_fused_add_rms_norm(g, x, res, w, y, rows, n, eps, plus_one):
+    r = g[0]
+    s = (_f(x[: r * n]) + _f(res[: r * n])).to(res.dtype)
+    res[: r * n] = s
+    k_rms_norm(g, res, w, y, rows, n, n, n, eps, plus_one)
+
+
+def _gemm(epi):
+    def run(g, a, w, c, r, m, n, k, ldc, err):
+        av = torch.as_strided(a, (m, k), (a_stride(a, k), 1))
+        acc = _f(av) @ _f(w[: n * k].view(n, k)).t()
+        if epi == "swiglu":
+            t = acc.view(m, n // 32, 2, 16)
+            acc = (torch.nn.functional.silu(t[:, :, 0]) * t[:, :, 1]).reshape(m, n // 2)
+        cv = torch.as_strided(c, (m, acc.shape[1]), (ldc, 1))
+        if epi == "acc":
+            acc = acc + _f(torch.as_strided(r, (m, n), (ldc, 1)))
+        cv.copy_(acc.to(c.dtype))
+    return run
+
+
+def a_stride(a, k):
+    return getattr(a, "_row_stride", k)
+
+
+def k_rope_append(g, qkv, kv, positions, slots, cos, sin, qn, kn, tokens, hq, hk, d, rot, page, eps, plus_one, kv_slots, max_pos, err):
+    t = g[0]
+    half = rot // 2
+    rows = qkv[: t * (hq + 2 * hk) * d].view(t, hq + 2 * hk, d)
+    pos = positions[:t].long().clamp(0, max_pos - 1)
+    c, s = cos.view(-1, half)[pos][:, None], sin.view(-1, half)[pos][:, None]
+    pool = kv.view(torch.bfloat16).view(-1, 2, hk, page, d)
+
+    def prep(x, w):
+        xf = _f(x)
+        if isinstance(w, torch.Tensor):
+            ww = _f(w[:d]) + (1.0 if plus_one else 0.0)
+            xf = _f((xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * ww).to(torch.bfloat16))
+        a, b = xf[..., :half], xf[..., half:rot]
+        return torch.cat([a * c - b * s, b * c + a * s, xf[..., rot:]], -1).to(torch.bfloat16)
+
+    q = prep(rows[:, :hq], qn)
+    k = prep(rows[:, hq:hq + hk], kn)
+    v = rows[:, hq + hk:].clone()
+    rows[:, :hq] = q
+    sl = slots[:t].long()
+    ok = sl >= 0
+    pg, off = sl[ok] // page, sl[ok] % page
+    pool[pg, 0, :, off] = k[ok]
+    pool[pg, 1, :, off] = v[ok]
+
+
+def _attention(prefill):
+    def run(g, kv, q, out, ws_o, ws_ml, table, seq_lens, cu_q, work, work_count, seqs, hq, hk, q_stride, out_stride,
+            max_pages, page, rows_per_seq, splits, pool_pages, scale_log2, err):
+        d = kv._head_dim
+        pool = kv.view(torch.bfloat16).view(-1, 2, hk, page, d)
+        n_seqs = g[1] if not prefill else None
+        if prefill:
+            n_seqs = int(kv._vars_seqs)
+        grp = hq // hk
+        scale = scale_log2 / 1.4426950408889634
+        tb = table.view(-1, max_pages)
+        for s in range(n_seqs):
+            L = int(seq_lens[s])
+            if isinstance(cu_q, torch.Tensor):
+                r0, r1 = int(cu_q[s]), int(cu_q[s + 1])
+            else:
+                r0, r1 = s * rows_per_seq, (s + 1) * rows_per_seq
+            R = r1 - r0
+            if R <= 0 or L <= 0:
+                continue
+            npg = -(-L // page)
+            pages = tb[s, :npg].long()
+            kk = _f(pool[pages, 0]).permute(0, 2, 1, 3).reshape(-1, hk, d)[:L]
+            vv = _f(pool[pages, 1]).permute(0, 2, 1, 3).reshape(-1, hk, d)[:L]
+            qq = _f(torch.as_strided(q, (R, hq, d), (q_stride, d, 1), q.storage_offset() + r0 * q_stride))
+            sc = torch.einsum("rhd,lhd->hrl", qq, kk.repeat_interleave(grp, 1)) * scale
+            posn = torch.arange(L - R, L)
+            mask = torch.arange(L)[None, :] <= posn[:, None]
+            sc = sc.masked_fill(~mask[None], float("-inf"))
+            o = torch.einsum("hrl,lhd->rhd", torch.softmax(sc, -1), vv.repeat_interleave(grp, 1))
+            torch.as_strided(out, (R, hq * d), (out_stride, 1), out.storage_offset() + r0 * out_stride).copy_(o.reshape(R, hq * d).to(out.dtype))
+    return run
+
+
+def k_noop(g, *a):
+    return None
+
+
+def k_last_row(g, src, dst, cu, seqs, row_bytes):
+    n = g[0]
+    w = row_bytes // src.element_size()
+    idx = cu[1:n + 1].long() - 1
+    dst.view(-1, w)[:n] = src.view(-1, w)[idx.clamp(min=0)]
+
+
+def k_argmax_partial(g, logits, pv, pi, rows, vocab, stride):
+    r = g[0]
+    lv = _f(torch.as_strided(logits, (r, vocab), (stride, 1)))
+    lv = torch.nan_to_num(lv, nan=float("-inf"))
+    mx = lv.max(-1, keepdim=True).values
+    idx = torch.where(lv == mx, torch.arange(vocab)[None], torch.full((1,), vocab)).min(-1).values
+    pv.view(-1)[:r] = mx[:, 0]
+    pi.view(-1)[:r] = idx.to(pi.dtype)
+
+
+def k_argmax_final(g, pv, pi, out, rows, parts):
+    r = g[0]
+    out[:r] = pi.view(-1)[:r].long()
+
+
+def k_sample(g, logits, probs, out, temperature, top_k, top_p, min_p, seeds, offsets, rows, vocab, stride):
+    from .ops.sampling_ref import sample_rows
+
+    r = g[0]
+    lv = _f(torch.as_strided(logits, (r, vocab), (stride, 1)))
+    out[:r] = sample_rows(lv, temperature[:r], top_k[:r], top_p[:r], min_p[:r], seeds[:r], offsets[:r])
+
+
+def k_rope_table(g, cos, sin, max_pos, rot, theta_bits):
+    theta = struct.unpack("<d", struct.pack("<q", theta_bits))[0]
+    half = rot // 2
+    inv = theta ** (-torch.arange(0, half, dtype=torch.float64) * 2.0 / rot)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None]
+    cos.view(-1)[: max_pos * half] = ang.cos().float().reshape(-1)
+    sin.view(-1)[: max_pos * half] = ang.sin().float().reshape(-1)
+
+
+def k_silu_mul(g, x, out, tokens, d):
+    t = g[0]
+    xv = _f(x[: t * 2 * d].view(t, 2 * d))
+    out[: t * d] = (torch.nn.functional.silu(xv[:, :d]) * xv[:, d:]).reshape(-1).to(out.dtype)
+
+
+def k_copy_rows(g, src, dst, idx, rows, row_bytes, ss, ds):
+    r = g[0]
+    s8, d8 = src.view(torch.uint8), dst.view(torch.uint8)
+    for i in range(r):
+        j = int(idx[i]) if isinstance(idx, torch.Tensor) else i
+        if j >= 0:
+            d8[i * ds:i * ds + row_bytes] = s8[j * ss:j * ss + row_bytes]
+
+
+def k_fill(g, p, n, v):
+    p[:n] = v
+
+
+CPU_KERNELS = {
+    "kern_embedding_i64_bf16": k_embedding, "kern_embedding_i32_bf16": k_embedding,
+    "kern_rms_norm_bf16": k_rms_norm, "kern_rms_norm_wide_bf16": k_rms_norm,
+    "kern_fused_add_rms_norm_bf16": k_fused_add_rms_norm,
+    "kern_rope_kv_append_bf16": k_rope_append, "kern_rope_table_f32": k_rope_table,
+    "kern_attn_plan": k_noop, "kern_attn_merge_splits": k_noop,
+    "kern_last_row": k_last_row, "kern_argmax_partial_bf16": k_argmax_partial, "kern_argmax_partial_f32": k_argmax_partial,
+    "kern_argmax_final_i64": k_argmax_final, "kern_sample_bf16": k_sample, "kern_sample_f32": k_sample,
+    "kern_silu_mul_bf16": k_silu_mul, "kern_copy_rows": k_copy_rows,
+    "kern_fill_f32": k_fill, "kern_fill_i32": k_fill, "kern_fill_i64": k_fill, "kern_fill_u8": k_fill,
+}
+for _bn in (256, 128, 64, 32):
+    for _epi, _sfx in (("store", ""), ("acc", "_acc"), ("f32", "_f32"), ("swiglu", "_swiglu")):
+        CPU_KERNELS[f"kern_gemm_bf16_tn{_sfx}_n{_bn}"] = _gemm(_epi)
+for _d in (16, 32, 64, 128, 256):
+    CPU_KERNELS[f"kern_attn_prefill_paged_d{_d}"] = _attention(True)
+    CPU_KERNELS[f"kern_attn_decode_paged_d{_d}"] = _attention(False)
+
+
+def register(entry: str, fn) -> None:
+    """Add the CPU statement of another kernel entry (model families register theirs on import)."""
+    CPU_KERNELS[entry] = fn
+
+
+class CpuRuntime:
+    def __init__(self, manifest, weights=None, tokens: int = 4096, slots: int = 0, topology=None, **_):
+        text = manifest_text(manifest)
+        m, errs = _native.verify(text)
+        if m is None:
+            raise ValueError("manifest does not verify:\n  - " + "\n  - ".join(errs))
+        self.doc = json.loads(m.to_json())
+        try:
+            self.protocol = json.loads(m.protocol())
+        except ValueError:
+            try:
+                self.protocol = json.loads(m.protocol(sampled=False))
+            except ValueError:
+                self.protocol = None
+        self.topology = dict(topology or {})
+        vmax = {k: v["max"] for k, v in self.doc["vars"].items()}
+        self.buffers, self.states = {}, {}
+        for name, b in self.doc["buffers"].items():
+            shape = [d if isinstance(d, int) else vmax[d] for d in b["shape"]]
+            self.buffers[name] = torch.zeros(int(np.prod(shape)) if shape else 1, dtype=_TORCH[b["dtype"]])
+        self.page_unit = 1
+        for b in self.doc["buffers"].values():
+            dom = b.get("domain") or {}
+            st = self.doc["states"].get(dom.get("index_into", ""))
+            if st and st.get("bytes_per_token") and "fill" not in b:
+                self.page_unit = math.lcm(self.page_unit, dom.get("stride", 1))
+        self.pages = max(1, tokens // self.page_unit)
+        self.slots = slots
+        for name, s in self.doc["states"].items():
+            if s.get("bytes_per_token"):
+                n = s["bytes_per_token"] * self.page_unit * self.pages
+            elif s.get("bytes_per_seq"):
+                n = s["bytes_per_seq"] * (slots + 1)
+            else:
+                n = s.get("bytes", 0)
+            self.states[name] = torch.zeros(n, dtype=torch.uint8)
+        self.scratch = {}
+        for oname, op in self.doc["ops"].items():
+            for sname, sc in op["impl"].get("scratch", {}).items():
+                shape = [d if isinstance(d, int) else vmax[d] for d in sc["shape"]]
+                self.scratch[(oname, sname)] = torch.zeros(int(np.prod(shape)), dtype=_TORCH[sc["dtype"]])
+        self.launches_total = 0
+        self.graphs = 0
+        self._vars = {}
+        if weights is not None:
+            self.load_weights(weights)
+
+    # ---- load ----
+    def load_weights(self, weights) -> None:
+        tensors = weights if isinstance(weights, dict) else read_safetensors(weights)
+        for name, b in self.doc["buffers"].items():
+            if b["kind"] not in ("weight", "source"):
+                continue
+            parts = []
+            for seg in b["bind"]:
+                t = tensors[self._pick(seg["tensor"])]
+                t2 = t.reshape(t.shape[0], -1) if t.dim() > 1 else t.reshape(-1, 1)
+                if "interleave" in seg:
+                    u = tensors[self._pick(seg["interleave"]["with"])].reshape(t2.shape)
+                    n = seg["interleave"]["rows"]
+                    parts.append(torch.stack([t2.view(-1, n, t2.shape[1]), u.view(-1, n, t2.shape[1])], 1).reshape(-1))
+                    continue
+                r = self._range(seg.get("rows"), t2.shape[0])
+                c = self._range(seg.get("cols"), t2.shape[1])
+                parts.append(t2[r[0]:r[1], c[0]:c[1]].reshape(-1))
+            flat = torch.cat(parts)
+            if flat.numel() != self.buffers[name].numel():
+                raise ValueError(f"buffer `{name}`: bound tensors hold {flat.numel()} elements, the buffer {self.buffers[name].numel()}")
+            self.buffers[name].copy_(flat.to(self.buffers[name].dtype))
+        for pname, p in self.doc["programs"].items():
+            if p.get("derive"):
+                self.issue(pname, {k: v["max"] for k, v in self.doc["vars"].items()})
+
+    def _pick(self, t):
+        return t if isinstance(t, str) else t["tensors"][self.rank(t["group"])]
+
+    def _range(self, r, whole):
+        if r is None:
+            return (0, whole)
+        return tuple(r) if isinstance(r, list) else tuple(r["ranges"][self.rank(r["group"])])
+
+    def rank(self, group: str) -> int:
+        return self.topology.get(group, (0, 1))[0]
+
+    def once(self) -> None:
+        for pname, p in self.doc["programs"].items():
+            if p.get("once"):
+                self.issue(pname, {k: v["max"] for k, v in self.doc["vars"].items()})
+
+    # ---- memory ----
+    def tensor(self, name: str) -> torch.Tensor:
+        if name in self.states:
+            return self.states[name]
+        b = self.doc["buffers"][name]
+        shape = [d if isinstance(d, int) else self.doc["vars"][d]["max"] for d in b["shape"]]
+        return self.buffers[name].view(shape)
+
+    def write(self, name: str, data, offset: int = 0) -> None:
+        buf = self.buffers[name]
+        src = data if isinstance(data, torch.Tensor) else torch.as_tensor(np.asarray(data))
+        src = src.reshape(-1)
+        at = offset // buf.element_size()
+        buf[at:at + src.numel()] = src.to(buf.dtype)
+
+    def read(self, name: str, count: int | None = None, offset: int = 0, out=None):
+        buf = self.buffers[name]
+        at = offset // buf.element_size()
+        if out is not None:
+            out.copy_(buf[at:at + out.numel()].to(out.dtype))
+            return out
+        n = buf.numel() - at if count is None else count
+        return buf[at:at + n].clone().numpy() if buf.dtype != torch.bfloat16 else buf[at:at + n].view(torch.int16).numpy().view(np.uint16).copy()
+
+    def synchronize(self) -> None:
+        pass
+
+    def check_error(self) -> None:
+        pass
+
+    def zero_slot(self, slot: int) -> None:
+        for name, s in self.doc["states"].items():
+            if s.get("bytes_per_seq"):
+                n = s["bytes_per_seq"]
+                self.states[name][slot * n:(slot + 1) * n] = 0
+
+    def run_copies(self, copies: dict) -> None:
+        for name, s in self.doc["states"].items():
+            st = self.states[name]
+            if s.get("bytes_per_token"):
+                n = s["bytes_per_token"] * self.page_unit
+                for a, b in copies["pages"]:
+                    st[b * n:(b + 1) * n] = st[a * n:(a + 1) * n].clone()
+            elif s.get("bytes_per_seq") and copies["slot"] is not None:
+                n = s["bytes_per_seq"]
+                a, b = copies["slot"]
+                st[b * n:(b + 1) * n] = st[a * n:(a + 1) * n].clone()
+
+    # ---- execution ----
+    def _resolve_call_arg(self, a, ptype):
+        if "buf" in a:
+            buf = self.buffers[a["buf"]]
+            return buf[a.get("offset", 0) // buf.element_size():]
+        if "state" in a:
+            return self.states[a["state"]][a.get("offset", 0):]
+        if "var" in a:
+            return self._vars[a["var"]]
+        if "expr" in a:
+            return _eval(a["expr"], self._vars)
+        if "rank" in a:
+            return self.rank(a["rank"])
+        return next(iter(a.values()))
+
+    def issue(self, program: str, vars: dict[str, int], eager: bool = False) -> int:
+        self._vars = dict(vars)
+        p = self.doc["programs"][program]
+        n = 0
+        for call in p["calls"]:
+            op = self.doc["ops"][call["op"]]
+            cargs = [self._resolve_call_arg(a, pt) for a, pt in zip(call["args"], op["params"])]
+            for l in op["impl"]["launches"]:
+                w = l.get("when")
+                if w and not (w.get("min", 0) <= vars[w["var"]] <= w.get("max", 1 << 62)):
+                    continue
+                largs = l.get("args") or [{"param": i} for i in range(len(op["params"]))]
+                vals = []
+                for la in largs:
+                    if "param" in la:
+                        vals.append(cargs[la["param"]])
+                    elif "scratch" in la:
+                        vals.append(self.scratch[(call["op"], la["scratch"])])
+                    elif "rank" in la:
+                        vals.append(self.rank(la["rank"]))
+                    elif "pack" in la:
+                        vals.append(self._pack(la["pack"], cargs, call["op"]))
+                    else:
+                        vals.append(next(iter(la.values())))
+                entry = l["entry"]
+                fn = CPU_KERNELS.get(entry)
+                if fn is None:
+                    raise NotImplementedError(f"no CPU statement of `{entry}` is registered")
+                grid = [_eval(g, vars) for g in l.get("grid", [1, 1, 1])]
+                if 0 in grid:
+                    continue
+                fn(grid, *vals)
+                n += 1
+        self.launches_total += n
+        return n
+
+    run = issue
+
+    def _pack(self, pack, cargs, opname):
+        """A pack holding one tensor map stands for the tensor it describes (row stride and head dim kept)."""
+        for f in pack["fields"]:
+            if "tensormap" in f:
+                tm = f["tensormap"]
+                t = cargs[tm["param"]]
+                es = {"bf16": 2, "f16": 2, "f32": 4, "u8": 1}.get(tm["dtype"], 2)
+                view = t.view(t.dtype)
+                holder = view[:]           # a fresh tensor object to carry attributes
+                holder._row_stride = tm["strides"][0] // es if tm.get("strides") else tm["dims"][0]
+                holder._head_dim = tm["dims"][0]
+                holder._vars_seqs = self._vars.get(self.protocol["groups"]["var"], 1) if self.protocol else 1
+                return holder
+        return pack

@@ -1,0 +1,340 @@
+"""Shared pieces of the manifest generators: the built-in kernel module index, op builders for the
+hand-written kernels (their launch ABI in one place), and a safetensors writer for synthetic
+random-init checkpoints.
+
+A generator is model knowledge (how weights concatenate, which tables are derived, which kernels a
+layer calls); the engine holds none of it. Reference counterparts: tools/kern_manifest.py (normalize,
+program helper), tools/once.py (load programs), tools/toy/gen.py:238-246 (safetensors writer).
+"""
+from __future__ import annotations
+
+import json
+import struct
+from pathlib import Path
+
+import torch
+
+KERNELS_DIR = Path(__file__).resolve().parent.parent / "kernels"
+SMS = 148                      # B200: the persistent kernels launch one CTA per SM
+I64_MAX = (1 << 63) - 1
+I32_MAX = (1 << 31) - 1
+BM, BK = 128, 64
+GEMM_STAGES = {256: 4, 128: 6, 64: 8, 32: 8}
+
+_ST_DTYPES = {torch.bfloat16: "BF16", torch.float16: "F16", torch.float32: "F32", torch.int64: "I64",
+              torch.int32: "I32", torch.uint8: "U8", torch.int8: "I8"}
+if hasattr(torch, "float8_e4m3fn"):
+    _ST_DTYPES[torch.float8_e4m3fn] = "F8_E4M3"
+
+
+def kernel_index() -> dict:
+    """sha256 pins of the in-tree cubins, written by the build."""
+    from .. import _build
+
+    _build.ensure_built()
+    return json.loads((KERNELS_DIR / "index.json").read_text())
+
+
+def modules_for(names) -> dict:
+    idx = kernel_index()
+    return {n: {"source": idx[n]["source"], "sha256": idx[n]["sha256"], "multicast": False} for n in names}
+
+
+def write_safetensors(path, tensors: dict[str, torch.Tensor], metadata: dict | None = None) -> None:
+    """8-byte little-endian header length, JSON header padded to 8 bytes, raw little-endian data."""
+    header, blobs, off = {}, [], 0
+    if metadata:
+        header["__metadata__"] = {k: str(v) for k, v in metadata.items()}
+    for name, t in tensors.items():
+        t = t.detach().contiguous().cpu()
+        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        header[name] = {"dtype": _ST_DTYPES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    hj = json.dumps(header, separators=(",", ":")).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)
+
+
+def read_safetensors(path) -> dict[str, torch.Tensor]:
+    inv = {v: k for k, v in _ST_DTYPES.items()}
+    data = Path(path).read_bytes()
+    (hlen,) = struct.unpack("<Q", data[:8])
+    header = json.loads(data[8:8 + hlen])
+    out = {}
+    for name, e in header.items():
+        if name == "__metadata__":
+            continue
+        lo, hi = e["data_offsets"]
+        buf = bytearray(data[8 + hlen + lo:8 + hlen + hi])
+        dt = inv[e["dtype"]]
+        out[name] = torch.frombuffer(buf, dtype=dt).reshape(e["shape"]).clone() if hi > lo else torch.empty(e["shape"], dtype=dt)
+    return out
+
+
+def f64_bits(v: float) -> int:
+    """A double passed through an 8-byte integer parameter slot."""
+    return struct.unpack("<q", struct.pack("<d", float(v)))[0]
+
+
+# ---- op builders: one place that knows each kernel's launch ABI ------------------------------------
+def gemm_smem(bn: int) -> int:
+    return 1024 + GEMM_STAGES[bn] * (BM * BK * 2 + bn * BK * 2) + 256
+
+
+def gemm_ranges(n: int, var_max: int, tiles=(256, 128, 64), sms: int = SMS):
+    """`when` ranges of the row count: the widest N tile that still gives every SM a tile."""
+    # 256-wide tiles once they fill every SM; 128-wide from half the SMs on (a narrower tile feeds the
+    # tensor cores worse than a partly idle grid does); 64-wide below that, where the op is weight-bound
+    fill = {256: 1.0, 128: 0.5}
+    out, hi = [], var_max
+    for i, bn in enumerate(tiles):
+        ncols = -(-n // bn)
+        need_m_tiles = -(-int(sms * fill.get(bn, 1.0)) // ncols)   # M tiles needed for that fill
+        lo = 1 if i == len(tiles) - 1 else (need_m_tiles - 1) * BM + 1
+        lo = max(1, lo)
+        if lo <= hi:
+            out.append((bn, lo, hi))
+            hi = lo - 1
+        if hi < 1:
+            break
+    return out
+
+
+def gemm_op(n: int, k: int, *, epilogue: str = "store", rows_var: str = "tokens", rows_max: int,
+            lda: int | None = None, ldc: int | None = None) -> dict:
+    """C[rows, n] = A[rows, k] · W[n, k]ᵀ through the tcgen05 GEMM, one launch per `when` range.
+
+    Interface: [a, w, c, rows, err]. epilogue store | acc (c += …, c is inout) | f32 | swiglu
+    (c is [rows, n/2] over weights interleaved 16 gate / 16 up rows)."""
+    lda = k if lda is None else lda
+    out_cols = n // 2 if epilogue == "swiglu" else n
+    ldc = out_cols if ldc is None else ldc
+    cdt = "f32" if epilogue == "f32" else "bf16"
+    cdir = "inout" if epilogue == "acc" else "out"
+    suffix = {"store": "", "acc": "_acc", "f32": "_f32", "swiglu": "_swiglu"}[epilogue]
+    iface = ["in buffer<bf16>", "in buffer<bf16>", f"{cdir} buffer<{cdt}>", "i32", "out buffer<i32>"]
+    lparams = ["bytes<128>", "bytes<128>", f"{cdir} buffer<{cdt}>", "in buffer<bf16>", "i32", "i32", "i32", "i32",
+               "out buffer<i32>"]
+    launches = []
+    for bn, lo, hi in gemm_ranges(n, rows_max):
+        when = {"var": rows_var}
+        if lo > 1:
+            when["min"] = lo
+        if hi < rows_max:
+            when["max"] = hi
+        launch = {
+            "module": "gemm_bf16", "entry": f"kern_gemm_bf16_tn{suffix}_n{bn}", "params": lparams,
+            "block": [192, 1, 1], "grid": [SMS, 1, 1], "shared_mem": gemm_smem(bn),
+            "args": [
+                {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+                    "param": 0, "dtype": "bf16", "dims": [k, 0], "strides": [lda * 2], "box": [BK, BM],
+                    "swizzle": 128, "l2_promotion": 256}}]}},
+                {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+                    "param": 1, "dtype": "bf16", "dims": [k, n], "strides": [k * 2], "box": [BK, bn],
+                    "swizzle": 128, "l2_promotion": 256}}]}},
+                {"param": 2}, {"param": 2 if epilogue == "acc" else 0}, {"param": 3}, {"i32": n}, {"i32": k},
+                {"i32": ldc}, {"param": 4}],
+        }
+        if len(when) > 1:
+            launch["when"] = when
+        launches.append(launch)
+    return {"params": iface, "impl": {"launches": launches}}
+
+
+def rms_norm_op(n: int, eps: float, plus_one: bool = False, rows_var: str = "tokens") -> dict:
+    """Interface [x, w, y]; one row per CTA."""
+    entry = "kern_rms_norm_bf16" if n <= 8192 else "kern_rms_norm_wide_bf16"
+    return {"params": ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>"],
+            "impl": {"launches": [{
+                "module": "norm_embed", "entry": entry, "block": [256, 1, 1], "grid": [rows_var, 1, 1],
+                "params": ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "i32", "i32", "i32", "i32", "f32", "i32"],
+                "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"i32": I32_MAX}, {"i32": n}, {"i32": n}, {"i32": n},
+                         {"f32": eps}, {"i32": int(plus_one)}]}]}}
+
+
+def embedding_op(hidden: int, vocab: int, ids_dtype: str = "i64") -> dict:
+    """Interface [ids, table, out, err]."""
+    return {"params": [f"in buffer<{ids_dtype}>", "in buffer<bf16>", "out buffer<bf16>", "out buffer<i32>"],
+            "impl": {"launches": [{
+                "module": "norm_embed", "entry": f"kern_embedding_{ids_dtype}_bf16",
+                "block": [min(256, max(32, hidden // 8)), 1, 1], "grid": ["tokens", 1, 1],
+                "params": [f"in buffer<{ids_dtype}>", "in buffer<bf16>", "out buffer<bf16>", "i32", "i32", "i32", "out buffer<i32>"],
+                "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"i32": I32_MAX}, {"i32": hidden}, {"i32": vocab}, {"param": 3}]}]}}
+
+
+def rope_append_op(hq: int, hk: int, d: int, rot: int, page_size: int, max_pos: int, eps: float,
+                   qk_norm: bool, norm_plus_one: bool = False) -> dict:
+    """Interface [qkv, kv state, positions, slots, cos, sin, (q_norm, k_norm,) err]."""
+    iface = ["inout buffer<bf16>", "inout state", "in buffer<i64>", "in buffer<i64>", "in buffer<f32>", "in buffer<f32>"]
+    lp = list(iface)
+    args = [{"param": i} for i in range(6)]
+    if qk_norm:
+        iface += ["in buffer<bf16>", "in buffer<bf16>"]
+        lp += ["in buffer<bf16>", "in buffer<bf16>"]
+        args += [{"param": 6}, {"param": 7}]
+    else:
+        lp += ["i64", "i64"]
+        args += [{"i64": 0}, {"i64": 0}]
+    iface.append("out buffer<i32>")
+    lp += ["i32"] * 6 + ["f32", "i32", "i64", "i32", "out buffer<i32>"]
+    args += [{"i32": I32_MAX}, {"i32": hq}, {"i32": hk}, {"i32": d}, {"i32": rot}, {"i32": page_size}, {"f32": eps},
+             {"i32": int(norm_plus_one)}, {"i64": I64_MAX}, {"i32": max_pos}, {"param": len(iface) - 1}]
+    return {"params": iface, "impl": {"launches": [{
+        "module": "attn_prep", "entry": "kern_rope_kv_append_bf16", "block": [128, 1, 1], "grid": ["tokens", 1, 1],
+        "shared_mem": 4 * d * 4, "params": lp, "args": args}]}}
+
+
+def attn_smem(d: int) -> int:
+    return 1024 + (3 if d >= 256 else 4) * (2 * 64 * d * 2) + 64 * (d + 8) * 2 + 256
+
+
+_ATTN_LP = ["bytes<128>", "in buffer<bf16>", "out buffer<bf16>", "i64", "i64", "in buffer<i32>", "in buffer<i32>",
+            "i64", "i64", "i64"] + ["i32"] * 10 + ["f32", "out buffer<i32>"]
+
+
+def _kv_map(d: int, page_size: int, state_param: int) -> dict:
+    return {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+        "param": state_param, "dtype": "bf16", "dims": [d, 0], "strides": [d * 2], "box": [64, min(page_size, 64)],
+        "swizzle": 128, "l2_promotion": 256}}]}}
+
+
+def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, q_stride: int) -> dict:
+    """Ragged causal attention over the paged context.
+    Interface [q(kv) buffer, kv state, out, block_table, seq_lens, cu_seqlens, work, work_count, err]."""
+    g = hq // hk
+    tpb = 64 // g
+    iface = ["in buffer<bf16>", "in state", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "in buffer<i32>",
+             "in buffer<i32>", "in buffer<i32>", "out buffer<i32>"]
+    lp = list(_ATTN_LP)
+    lp[7], lp[8], lp[9] = "in buffer<i32>", "in buffer<i32>", "in buffer<i32>"
+    args = [_kv_map(d, page_size, 1), {"param": 0}, {"param": 2}, {"i64": 0}, {"i64": 0}, {"param": 3}, {"param": 4},
+            {"param": 5}, {"param": 6}, {"param": 7}, {"i32": I32_MAX}, {"i32": hq}, {"i32": hk}, {"i32": q_stride},
+            {"i32": hq * d}, {"i32": table_width}, {"i32": page_size}, {"i32": 1}, {"i32": 1}, {"i32": I32_MAX},
+            {"f32": (d ** -0.5) * 1.4426950408889634}, {"param": 8}]
+    return {"params": iface, "impl": {"launches": [{
+        "module": "attn_paged", "entry": f"kern_attn_prefill_paged_d{d}", "block": [160, 1, 1],
+        "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1], "shared_mem": attn_smem(d),
+        "params": lp, "args": args}]}}
+
+
+def attn_plan_op(hq: int, hk: int, seqs_max: int) -> dict:
+    """Interface [cu_seqlens, work, work_count, seqs, max_items]; the attention grid's (sequence, block)
+    work list. A call passes ``{"var": "seqs"}`` and ``attn_plan_items(...)``."""
+    tpb = 64 // (hq // hk)
+    return {"params": ["in buffer<i32>", "out buffer<i32>", "out buffer<i32>", "i32", "i32"], "impl": {"launches": [{
+        "module": "attn_paged", "entry": "kern_attn_plan", "block": [256, 1, 1], "grid": [1, 1, 1],
+        "params": ["in buffer<i32>", "i32", "i32", "out buffer<i32>", "out buffer<i32>", "i32"],
+        "args": [{"param": 0}, {"param": 3}, {"i32": tpb}, {"param": 1}, {"param": 2}, {"param": 4}]}]}}
+
+
+def attn_plan_items(hq: int, hk: int) -> dict:
+    """Expression for the most work items a call can have: one per block of rows plus one per sequence."""
+    return {"add": [{"ceil_div": ["tokens", 64 // (hq // hk)]}, "seqs"]}
+
+
+def attn_decode_op(hq: int, hk: int, d: int, page_size: int, table_width: int, q_stride: int, seqs_max: int,
+                   rows: int = 1, sms: int = SMS) -> dict:
+    """Decode / verify rows over the paged context, split-KV chosen by `when` ranges of the batch.
+    Interface [q(kv) buffer, kv state, out, block_table, seq_lens, err]."""
+    g = hq // hk
+    nblk = -(-rows // max(1, 16 // g))
+    iface = ["in buffer<bf16>", "in state", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "out buffer<i32>"]
+    ranges, hi = [], seqs_max
+    for splits in (1, 2, 4, 8, 16, 32):
+        # enough sequences that hk * nblk * seqs * splits covers the SMs
+        lo = max(1, -(-sms // (hk * nblk * splits)))
+        if splits == 32:
+            lo = 1
+        if lo <= hi:
+            ranges.append((splits, lo, hi))
+            hi = lo - 1
+        if hi < 1:
+            break
+    launches, scratch = [], {}
+    max_splits = max(s for s, _, _ in ranges)
+    if max_splits > 1:
+        scratch = {"ws_o": {"dtype": "f32", "shape": ["tokens", hq * max_splits * d]},
+                   "ws_ml": {"dtype": "f32", "shape": ["tokens", hq * max_splits * 2]}}
+    for splits, lo, hi in ranges:
+        when = {"var": "seqs"}
+        if lo > 1:
+            when["min"] = lo
+        if hi < seqs_max:
+            when["max"] = hi
+        lp = list(_ATTN_LP)
+        ws = [{"i64": 0}, {"i64": 0}]
+        if splits > 1:
+            lp[3], lp[4] = "out buffer<f32>", "out buffer<f32>"
+            ws = [{"scratch": "ws_o"}, {"scratch": "ws_ml"}]
+        args = [_kv_map(d, page_size, 1), {"param": 0}, {"param": 2}, *ws, {"param": 3}, {"param": 4}, {"i64": 0},
+                {"i64": 0}, {"i64": 0}, {"i32": I32_MAX}, {"i32": hq}, {"i32": hk}, {"i32": q_stride}, {"i32": hq * d},
+                {"i32": table_width}, {"i32": page_size}, {"i32": rows}, {"i32": splits}, {"i32": I32_MAX},
+                {"f32": (d ** -0.5) * 1.4426950408889634}, {"param": 5}]
+        launch = {"module": "attn_paged", "entry": f"kern_attn_decode_paged_d{d}", "block": [160, 1, 1],
+                  "grid": [hk * nblk, "seqs", splits], "shared_mem": attn_smem(d), "params": lp, "args": args}
+        if len(when) > 1:
+            launch["when"] = when
+        launches.append(launch)
+        if splits > 1:
+            merge = {"module": "attn_paged", "entry": "kern_attn_merge_splits", "block": [min(256, d), 1, 1],
+                     "grid": [{"mul": ["tokens", hq]}, 1, 1],
+                     "params": ["in buffer<f32>", "in buffer<f32>", "out buffer<bf16>", "i32", "i32", "i32", "i32", "i32"],
+                     "args": [{"scratch": "ws_o"}, {"scratch": "ws_ml"}, {"param": 2}, {"i32": I32_MAX}, {"i32": hq},
+                              {"i32": d}, {"i32": splits}, {"i32": hq * d}]}
+            if len(when) > 1:
+                merge["when"] = when
+            launches.append(merge)
+    impl = {"launches": launches}
+    if scratch:
+        impl["scratch"] = scratch
+    return {"params": iface, "impl": impl}
+
+
+def last_row_op(row_bytes: int) -> dict:
+    """Interface [src, dst, cu_seqlens]: the last row of every sequence of a ragged batch."""
+    return {"params": ["in buffer<bf16>", "out buffer<bf16>", "in buffer<i32>"], "impl": {"launches": [{
+        "module": "misc", "entry": "kern_last_row", "block": [128, 1, 1], "grid": ["seqs", 1, 1],
+        "params": ["in buffer<bf16>", "out buffer<bf16>", "in buffer<i32>", "i32", "i32"],
+        "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"i32": I32_MAX}, {"i32": row_bytes}]}]}}
+
+
+def argmax_op(vocab: int, dtype: str = "bf16", parts: int = 32, rows_var: str = "seqs") -> dict:
+    """Interface [logits, tokens out]."""
+    return {"params": [f"in buffer<{dtype}>", "out buffer<i64>"], "impl": {
+        "scratch": {"pv": {"dtype": "f32", "shape": [rows_var, parts]}, "pi": {"dtype": "i32", "shape": [rows_var, parts]}},
+        "launches": [
+            {"module": "sampling", "entry": f"kern_argmax_partial_{dtype}", "block": [256, 1, 1], "grid": [rows_var, parts, 1],
+             "params": [f"in buffer<{dtype}>", "out buffer<f32>", "out buffer<i32>", "i32", "i32", "i32"],
+             "args": [{"param": 0}, {"scratch": "pv"}, {"scratch": "pi"}, {"i32": I32_MAX}, {"i32": vocab}, {"i32": vocab}]},
+            {"module": "sampling", "entry": "kern_argmax_final_i64", "block": [32, 1, 1], "grid": [rows_var, 1, 1],
+             "params": ["in buffer<f32>", "in buffer<i32>", "out buffer<i64>", "i32", "i32"],
+             "args": [{"scratch": "pv"}, {"scratch": "pi"}, {"param": 1}, {"i32": I32_MAX}, {"i32": parts}]}]}}
+
+
+def sample_op(vocab: int, dtype: str = "bf16") -> dict:
+    """Interface [logits, tokens out, temperature, top_k, top_p, min_p, seed, seq_lens (draw offset)]."""
+    return {"params": [f"in buffer<{dtype}>", "out buffer<i64>", "in buffer<f32>", "in buffer<i32>", "in buffer<f32>",
+                       "in buffer<f32>", "in buffer<i64>", "in buffer<i32>"],
+            "impl": {"scratch": {"probs": {"dtype": "f32", "shape": ["seqs", vocab]}},
+                     "launches": [{"module": "sampling", "entry": f"kern_sample_{dtype}", "block": [1024, 1, 1],
+                                   "grid": ["seqs", 1, 1],
+                                   "params": [f"in buffer<{dtype}>", "out buffer<f32>", "out buffer<i64>", "in buffer<f32>",
+                                              "in buffer<i32>", "in buffer<f32>", "in buffer<f32>", "in buffer<i64>",
+                                              "in buffer<i32>", "i32", "i32", "i32"],
+                                   "args": [{"param": 0}, {"scratch": "probs"}, {"param": 1}, {"param": 2}, {"param": 3},
+                                            {"param": 4}, {"param": 5}, {"param": 6}, {"param": 7}, {"i32": I32_MAX},
+                                            {"i32": vocab}, {"i32": vocab}]}]}}
+
+
+def rope_table_op(max_pos: int, rot: int, theta: float) -> dict:
+    """Interface [cos, sin]: the `once` program's table of angles."""
+    return {"params": ["out buffer<f32>", "out buffer<f32>"], "impl": {"launches": [{
+        "module": "attn_prep", "entry": "kern_rope_table_f32", "block": [256, 1, 1],
+        "grid": [min(1024, -(-max_pos * (rot // 2) // 256)), 1, 1],
+        "params": ["out buffer<f32>", "out buffer<f32>", "i32", "i32", "i64"],
+        "args": [{"param": 0}, {"param": 1}, {"i32": max_pos}, {"i32": rot}, {"i64": f64_bits(theta)}]}]}}

@@ -105,9 +105,18 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tens
     kv_map = k.tensor_map_2d(view, min(page_size, TK), 64)
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
     entry = f"kern_attn_{'prefill' if prefill else 'decode'}_paged_d{d}"
-    k.launch("attn_paged", entry, (hk * nblk, n_seqs, splits), (160,),
+    grid = (hk * nblk, n_seqs, splits)
+    work = count = None
+    if prefill and cu_q is not None:
+        items = (q.shape[0] + toks_per_blk - 1) // toks_per_blk + n_seqs
+        work = torch.empty(2 * items, dtype=torch.int32, device=q.device)
+        count = torch.empty(1, dtype=torch.int32, device=q.device)
+        k.launch("attn_paged", "kern_attn_plan", (1,), (256,),
+                 [ptr(cu_q), i32(n_seqs), i32(toks_per_blk), ptr(work), ptr(count), i32(items)])
+        grid = (hk, items, 1)
+    k.launch("attn_paged", entry, grid, (160,),
              [kv_map, ptr(q), ptr(out), ptr(ws_o), ptr(ws_ml), ptr(block_table), ptr(seq_lens),
-              ptr(cu_q), i32(n_seqs), i32(hq), i32(hk), i32(q.stride(0)), i32(out.stride(0)),
+              ptr(cu_q), ptr(work), ptr(count), i32(n_seqs), i32(hq), i32(hk), i32(q.stride(0)), i32(out.stride(0)),
               i32(block_table.shape[1]), i32(page_size), i32(rows_per_seq), i32(splits), i32(pages),
               f32(scale * 1.4426950408889634), ptr(k.err_word())],
              shared_mem=_attn_smem(d))

@@ -1,0 +1,178 @@
+"""``kern_b200.Runtime``: the Python face of the native executor.
+
+Mirrors the reference's Python binding (crates/kern-py/src/lib.rs:47-245): construct from a manifest,
+a kernels directory and a checkpoint; ``run`` / ``issue`` programs by name with a var assignment;
+``region(name)`` views of runtime memory as torch tensors; ``offer`` / ``connect`` for rank groups;
+``bind_host`` / ``enqueue_after`` for engines that own the states (vLLM / SGLang style hosts).
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from . import _native
+from .models.common import KERNELS_DIR
+
+_NP = {"bf16": np.uint16, "f16": np.float16, "f32": np.float32, "fp8e4m3": np.uint8, "fp8e8m0": np.uint8, "i8": np.int8,
+       "i32": np.int32, "u32": np.uint32, "i64": np.int64, "u64": np.uint64, "u8": np.uint8}
+_TORCH = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32, "i8": torch.int8, "i32": torch.int32,
+          "i64": torch.int64, "u8": torch.uint8, "fp8e4m3": torch.uint8, "fp8e8m0": torch.uint8, "u32": torch.int32,
+          "u64": torch.int64}
+
+
+class _CudaView:
+    """Minimal ``__cuda_array_interface__`` carrier so torch can view runtime memory without a copy."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+def manifest_text(manifest) -> str:
+    if isinstance(manifest, dict):
+        return json.dumps(manifest)
+    if isinstance(manifest, Path) or (isinstance(manifest, str) and not manifest.lstrip().startswith("{")):
+        return Path(manifest).read_text()
+    return manifest
+
+
+def verify(manifest, strict_multicast: bool = False):
+    """-> (native manifest | None, [diagnostics])."""
+    return _native.verify(manifest_text(manifest), strict_multicast)
+
+
+class Runtime:
+    def __init__(self, manifest, kernels: str | Path | None = None, weights=None, gpu: int = 0,
+                 topology: dict[str, tuple[int, int]] | None = None, tokens: int = 0, slots: int = 0,
+                 memory_fraction: float = 0.9, stream: int | None = None):
+        if not _native.cuda_available():
+            raise RuntimeError("kern_b200.Runtime needs a CUDA device; use kern_b200.cpu.CpuRuntime on a machine without one")
+        text = manifest_text(manifest)
+        self.gpu = gpu
+        with torch.cuda.device(gpu):
+            torch.zeros(1, device="cuda")   # the primary context the runtime shares with torch
+            self._stream = torch.cuda.Stream(device=gpu) if stream is None else None
+            raw = self._stream.cuda_stream if stream is None else stream
+            self._rt = _native.Runtime(text, str(kernels or KERNELS_DIR), gpu, dict(topology or {}), tokens, slots,
+                                       memory_fraction, raw)
+        self.doc = json.loads(self._rt.manifest_json())
+        pj = self._rt.protocol_json()
+        self.protocol = json.loads(pj) if pj else None
+        self.stream = raw
+        if weights is not None:
+            self.load_weights(weights)
+
+    # ---- load ----
+    def load_weights(self, weights) -> None:
+        if isinstance(weights, (str, Path)):
+            p = Path(weights)
+            paths = sorted(str(x) for x in p.glob("*.safetensors")) if p.is_dir() else [str(p)]
+        else:
+            paths = [str(x) for x in weights]
+        if not paths:
+            raise FileNotFoundError(f"no safetensors files under {weights}")
+        self._rt.load_weights(paths)
+
+    def once(self) -> None:
+        """Run every `once` program (after every peer is connected)."""
+        self._rt.run_once_programs()
+
+    # ---- memory ----
+    def region(self, name: str) -> tuple[int, int]:
+        return self._rt.region(name)
+
+    def tensor(self, name: str) -> torch.Tensor:
+        """Zero-copy torch view of a buffer (declared dtype and var-max shape) or a state (bytes)."""
+        ptr, nbytes = self._rt.region(name)
+        b = self.doc["buffers"].get(name)
+        if b is None:
+            return torch.as_tensor(_CudaView(ptr, (nbytes,), "|u1"), device=f"cuda:{self.gpu}")
+        shape = [d if isinstance(d, int) else self.doc["vars"][d]["max"] for d in b["shape"]]
+        dt = b["dtype"]
+        es = np.dtype(_NP[dt]).itemsize
+        raw = torch.as_tensor(_CudaView(ptr, (nbytes,), "|u1"), device=f"cuda:{self.gpu}")
+        return raw.view(_TORCH[dt]).view(shape) if nbytes == es * int(np.prod(shape)) else raw
+
+    def write(self, name: str, data, offset: int = 0) -> None:
+        """Host -> device on the runtime's stream. ``data``: pinned torch tensor (no staging copy), any
+        torch CPU tensor, numpy array or bytes."""
+        if isinstance(data, torch.Tensor):
+            assert data.device.type == "cpu" and data.is_contiguous()
+            self._rt.write_input_ptr(name, data.data_ptr(), data.numel() * data.element_size(), offset)
+        else:
+            self._rt.write_input(name, np.ascontiguousarray(data) if not isinstance(data, (bytes, bytearray)) else data, offset)
+
+    def read(self, name: str, count: int | None = None, offset: int = 0, out: torch.Tensor | None = None):
+        """Device -> host of an output (or any buffer); synchronises the runtime's stream."""
+        b = self.doc["buffers"][name]
+        dt = b["dtype"]
+        es = np.dtype(_NP[dt]).itemsize
+        if out is not None:
+            self._rt.read_output_ptr(name, out.data_ptr(), out.numel() * out.element_size(), offset)
+            return out
+        total = self._rt.region(name)[1] // es
+        n = total if count is None else count
+        raw = self._rt.read_output(name, n * es, offset)
+        return np.frombuffer(raw, dtype=_NP[dt]).copy()
+
+    # ---- execution ----
+    def issue(self, program: str, vars: dict[str, int], eager: bool = False) -> int:
+        return self._rt.issue(program, vars, eager)
+
+    def run(self, program: str, vars: dict[str, int]) -> int:
+        return self._rt.run(program, vars)
+
+    def enqueue_after(self, program: str, vars: dict[str, int], stream: int) -> int:
+        return self._rt.enqueue_after(program, vars, stream)
+
+    def synchronize(self) -> None:
+        self._rt.synchronize()
+
+    def check_error(self) -> None:
+        for f in (self.protocol or {}).get("fills", []):
+            if f["fill"] == "error":
+                code = int(self.read(f["name"], 1)[0])
+                if code:
+                    raise RuntimeError(f"device error word `{f['name']}` = {code}")
+
+    # ---- pool support ----
+    def zero_slot(self, slot: int) -> None:
+        self._rt.zero_slot(slot)
+
+    def run_copies(self, copies: dict) -> None:
+        """Execute a pool copy plan (half pages are copied whole: the tail rows are dead to the holder)."""
+        if copies["pages"]:
+            self._rt.copy_pages(list(copies["pages"]))
+        if copies["slot"] is not None:
+            self._rt.copy_slot(*copies["slot"])
+
+    # ---- groups ----
+    def rank(self, group: str) -> int:
+        return self._rt.rank(group)
+
+    def offer(self) -> dict[str, bytes]:
+        return dict(self._rt.export_handles())
+
+    def connect(self, group: str, members: list[dict[str, bytes]]) -> None:
+        self._rt.connect(group, members)
+
+    # ---- hosted ----
+    @property
+    def awaits_host(self) -> bool:
+        return self._rt.awaits_host
+
+    def bind_host(self, regions: dict[str, tuple[int, str, list[int], list[int]]]) -> None:
+        self._rt.bind_host(regions)
+
+    # ---- facts ----
+    page_unit = property(lambda self: self._rt.page_unit)
+    pages = property(lambda self: self._rt.pages)
+    slots = property(lambda self: self._rt.slots)
+    launches_total = property(lambda self: self._rt.launches_total)
+    graphs = property(lambda self: self._rt.graphs)
+
+    def banner(self) -> str:
+        return self._rt.banner()
