@@ -394,29 +394,44 @@ KERN_ATTN_ENTRY(kern_attn_prefill_paged_d64, 64, true)
 KERN_ATTN_ENTRY(kern_attn_prefill_paged_d128, 128, true)
 KERN_ATTN_ENTRY(kern_attn_prefill_paged_d256, 256, true)
 
-// Work list for ragged prefill: one (sequence, query block) pair per block of `toks_per_blk` new rows,
-// so the attention grid is sized by the rows of the call and not by sequences x the longest one.
+// Work lists for a ragged call: one (sequence, query block) pair per block of new rows, so the
+// attention grids are sized by the rows of the call and not by sequences x the longest one.
+// Sequences with at most `small_rows` new rows (decode rows and speculative rounds riding in a ragged
+// batch) go to list d in blocks of `tpb_d` tokens for the token-parallel kernel, where four warps share
+// each KV tile; the rest go to list p in blocks of `tpb_p` tokens for the row-parallel causal kernel.
 // One CTA; the plan is the same for every layer of a step.
-extern "C" __global__ void kern_attn_plan(const int* cu_q, int seqs, int toks_per_blk, int* work,
-                                          int* work_count, int max_items) {
+extern "C" __global__ void kern_attn_plan(const int* cu_q, int seqs, int tpb_p, int tpb_d, int small_rows,
+                                          int* work_p, int* count_p, int max_p, int* work_d,
+                                          int* count_d, int max_d) {
   pdl_wait();
-  __shared__ int base[1025];
+  __shared__ int base_p[1025], base_d[1025];
   if (threadIdx.x == 0) {
-    int n = 0;
+    int np = 0, nd = 0;
     for (int s = 0; s < seqs && s < 1024; ++s) {
-      base[s] = n;
+      base_p[s] = np;
+      base_d[s] = nd;
       const int r = cu_q[s + 1] - cu_q[s];
-      n += r > 0 ? (r + toks_per_blk - 1) / toks_per_blk : 0;
+      if (r <= 0) continue;
+      if (r <= small_rows) nd += (r + tpb_d - 1) / tpb_d;
+      else np += (r + tpb_p - 1) / tpb_p;
     }
-    base[seqs < 1024 ? seqs : 1024] = n;
-    *work_count = n < max_items ? n : max_items;
+    const int e = seqs < 1024 ? seqs : 1024;
+    base_p[e] = np;
+    base_d[e] = nd;
+    *count_p = np < max_p ? np : max_p;
+    *count_d = nd < max_d ? nd : max_d;
   }
   __syncthreads();
-  for (int s = threadIdx.x; s < seqs && s < 1024; s += blockDim.x)
-    for (int i = base[s]; i < base[s + 1] && i < max_items; ++i) {
-      work[2 * i] = s;
-      work[2 * i + 1] = i - base[s];
+  for (int s = threadIdx.x; s < seqs && s < 1024; s += blockDim.x) {
+    for (int i = base_p[s]; i < base_p[s + 1] && i < max_p; ++i) {
+      work_p[2 * i] = s;
+      work_p[2 * i + 1] = i - base_p[s];
     }
+    for (int i = base_d[s]; i < base_d[s + 1] && i < max_d; ++i) {
+      work_d[2 * i] = s;
+      work_d[2 * i + 1] = i - base_d[s];
+    }
+  }
 }
 
 // Merge split-KV partials: out[token][head][:] = sum_s O_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m)

@@ -115,9 +115,9 @@ def _attention(prefill):
             max_pages, page, rows_per_seq, splits, pool_pages, scale_log2, err):
         d = kv._head_dim
         pool = kv.view(torch.bfloat16).view(-1, 2, hk, page, d)
-        n_seqs = g[1] if not prefill else None
-        if prefill:
-            n_seqs = int(kv._vars_seqs)
+        n_seqs = int(kv._vars_seqs)
+        # a work list means a ragged call, whose sequences are split between the two kernels by rows
+        small = max(1, 16 // (hq // hk)) if isinstance(work, torch.Tensor) else None
         grp = hq // hk
         scale = scale_log2 / 1.4426950408889634
         tb = table.view(-1, max_pages)
@@ -129,6 +129,8 @@ def _attention(prefill):
                 r0, r1 = s * rows_per_seq, (s + 1) * rows_per_seq
             R = r1 - r0
             if R <= 0 or L <= 0:
+                continue
+            if small is not None and isinstance(cu_q, torch.Tensor) and ((R <= small) == prefill):
                 continue
             npg = -(-L // page)
             pages = tb[s, :npg].long()

@@ -212,24 +212,36 @@ def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, 
              "in buffer<i32>", "in buffer<i32>", "out buffer<i32>"]
     lp = list(_ATTN_LP)
     lp[7], lp[8], lp[9] = "in buffer<i32>", "in buffer<i32>", "in buffer<i32>"
-    args = [_kv_map(d, page_size, 1), {"param": 0}, {"param": 2}, {"i64": 0}, {"i64": 0}, {"param": 3}, {"param": 4},
-            {"param": 5}, {"param": 6}, {"param": 7}, {"i32": I32_MAX}, {"i32": hq}, {"i32": hk}, {"i32": q_stride},
-            {"i32": hq * d}, {"i32": table_width}, {"i32": page_size}, {"i32": 1}, {"i32": 1}, {"i32": I32_MAX},
-            {"f32": (d ** -0.5) * 1.4426950408889634}, {"param": 8}]
-    return {"params": iface, "impl": {"launches": [{
-        "module": "attn_paged", "entry": f"kern_attn_prefill_paged_d{d}", "block": [160, 1, 1],
-        "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1], "shared_mem": attn_smem(d),
-        "params": lp, "args": args}]}}
+    iface += ["in buffer<i32>", "in buffer<i32>"]     # the second work list (few-row sequences) and its count
+
+    def args(work: int, count: int) -> list:
+        return [_kv_map(d, page_size, 1), {"param": 0}, {"param": 2}, {"i64": 0}, {"i64": 0}, {"param": 3}, {"param": 4},
+                {"param": 5}, {"param": work}, {"param": count}, {"i32": I32_MAX}, {"i32": hq}, {"i32": hk},
+                {"i32": q_stride}, {"i32": hq * d}, {"i32": table_width}, {"i32": page_size}, {"i32": 1}, {"i32": 1},
+                {"i32": I32_MAX}, {"f32": (d ** -0.5) * 1.4426950408889634}, {"param": 8}]
+
+    # many-row sequences: row-parallel causal kernel; few-row sequences (decode rows riding in the ragged
+    # call): token-parallel kernel, so their KV streams at full bandwidth
+    return {"params": iface, "impl": {"launches": [
+        {"module": "attn_paged", "entry": f"kern_attn_prefill_paged_d{d}", "block": [160, 1, 1],
+         "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1], "shared_mem": attn_smem(d),
+         "params": lp, "args": args(6, 7)},
+        {"module": "attn_paged", "entry": f"kern_attn_decode_paged_d{d}", "block": [160, 1, 1],
+         "grid": [hk, "seqs", 1], "shared_mem": attn_smem(d), "params": lp, "args": args(9, 10)}]}}
 
 
 def attn_plan_op(hq: int, hk: int, seqs_max: int) -> dict:
     """Interface [cu_seqlens, work, work_count, seqs, max_items]; the attention grid's (sequence, block)
     work list. A call passes ``{"var": "seqs"}`` and ``attn_plan_items(...)``."""
-    tpb = 64 // (hq // hk)
-    return {"params": ["in buffer<i32>", "out buffer<i32>", "out buffer<i32>", "i32", "i32"], "impl": {"launches": [{
-        "module": "attn_paged", "entry": "kern_attn_plan", "block": [256, 1, 1], "grid": [1, 1, 1],
-        "params": ["in buffer<i32>", "i32", "i32", "out buffer<i32>", "out buffer<i32>", "i32"],
-        "args": [{"param": 0}, {"param": 3}, {"i32": tpb}, {"param": 1}, {"param": 2}, {"param": 4}]}]}}
+    g = hq // hk
+    tpb, tpd = 64 // g, max(1, 16 // g)
+    return {"params": ["in buffer<i32>", "out buffer<i32>", "out buffer<i32>", "i32", "i32", "out buffer<i32>", "out buffer<i32>"],
+            "impl": {"launches": [{
+                "module": "attn_paged", "entry": "kern_attn_plan", "block": [256, 1, 1], "grid": [1, 1, 1],
+                "params": ["in buffer<i32>", "i32", "i32", "i32", "i32", "out buffer<i32>", "out buffer<i32>", "i32",
+                           "out buffer<i32>", "out buffer<i32>", "i32"],
+                "args": [{"param": 0}, {"param": 3}, {"i32": tpb}, {"i32": tpd}, {"i32": tpd}, {"param": 1}, {"param": 2},
+                         {"param": 4}, {"param": 5}, {"param": 6}, {"param": 3}]}]}}
 
 
 def attn_plan_items(hq: int, hk: int) -> dict:

@@ -134,6 +134,8 @@ def build_manifest(cfg: DenseConfig) -> dict:
     bufs["logits"] = {"dtype": "bf16", "shape": ["seqs", cfg.vocab], "kind": "workspace"}
     bufs["work"] = {"dtype": "i32", "shape": [2 * (-(-T // max(1, 64 // (hq // hk))) + S)], "kind": "workspace"}
     bufs["work_count"] = {"dtype": "i32", "shape": [1], "kind": "workspace"}
+    bufs["work_d"] = {"dtype": "i32", "shape": [2 * S], "kind": "workspace"}
+    bufs["work_d_count"] = {"dtype": "i32", "shape": [1], "kind": "workspace"}
     bufs["rope_cos"] = {"dtype": "f32", "shape": [cfg.max_context, d // 2], "kind": "carry"}
     bufs["rope_sin"] = {"dtype": "f32", "shape": [cfg.max_context, d // 2], "kind": "carry"}
     if cfg.sampling:
@@ -194,7 +196,7 @@ def build_manifest(cfg: DenseConfig) -> dict:
         if prefill:
             calls.append({"op": "attn_prefill", "label": lbl + "attn",
                           "args": [B("qkv"), kv, B("attn"), B("block_table"), B("seq_lens"), B("cu_seqlens"), B("work"),
-                                   B("work_count"), err]})
+                                   B("work_count"), err, B("work_d"), B("work_d_count")]})
         else:
             calls.append({"op": "attn_decode", "label": lbl + "attn",
                           "args": [B("qkv"), kv, B("attn"), B("block_table"), B("seq_lens"), err]})
@@ -221,7 +223,8 @@ def build_manifest(cfg: DenseConfig) -> dict:
 
     prefill = [{"op": "embed", "label": "embed", "args": [B("token_ids"), B("w.embed"), B("x"), err]},
                {"op": "attn_plan", "label": "plan", "args": [B("cu_seqlens"), B("work"), B("work_count"), {"var": "seqs"},
-                                                              {"expr": C.attn_plan_items(hq, hk)}]}]
+                                                              {"expr": C.attn_plan_items(hq, hk)}, B("work_d"),
+                                                              B("work_d_count")]}]
     decode = [{"op": "embed", "label": "embed", "args": [B("token_ids"), B("w.embed"), B("x"), err]}]
     for i in range(cfg.layers):
         prefill += layer(i, True)
@@ -244,6 +247,24 @@ def build_manifest(cfg: DenseConfig) -> dict:
             "decode": {"batch": {"groups": S, "rows": 1}, "graph": True, "calls": decode},
         },
     }
+
+
+def load_random_weights(rt, cfg: DenseConfig, seed: int = 0, std: float = 0.02) -> None:
+    """Fill a runtime's weight buffers with the synthetic checkpoint, generated tensor by tensor on the
+    runtime's own device (no file, no host copy): the benchmark's random-init weights."""
+    shapes = weight_names(cfg)
+    order = {n: i for i, n in enumerate(shapes)}
+
+    def provider(name: str) -> torch.Tensor:
+        dev = rt.tensor(next(iter(rt.doc["buffers"]))).device
+        g = torch.Generator(device=dev).manual_seed(seed * 1000003 + order[name])
+        if name.endswith("norm.weight"):
+            t = 1.0 + 0.1 * torch.randn(shapes[name], generator=g, device=dev)
+        else:
+            t = std * torch.randn(shapes[name], generator=g, device=dev)
+        return t.to(torch.bfloat16)
+
+    rt.load_tensors(provider)
 
 
 # ---- PyTorch fp32 oracle ---------------------------------------------------------------------------

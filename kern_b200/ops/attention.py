@@ -110,9 +110,10 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tens
     if prefill and cu_q is not None:
         items = (q.shape[0] + toks_per_blk - 1) // toks_per_blk + n_seqs
         work = torch.empty(2 * items, dtype=torch.int32, device=q.device)
-        count = torch.empty(1, dtype=torch.int32, device=q.device)
+        count = torch.zeros(2, dtype=torch.int32, device=q.device)
         k.launch("attn_paged", "kern_attn_plan", (1,), (256,),
-                 [ptr(cu_q), i32(n_seqs), i32(toks_per_blk), ptr(work), ptr(count), i32(items)])
+                 [ptr(cu_q), i32(n_seqs), i32(toks_per_blk), i32(max(1, 16 // g)), i32(0), ptr(work), ptr(count),
+                  i32(items), ptr(work), ptr(count[1:]), i32(0)])
         grid = (hk, items, 1)
     k.launch("attn_paged", entry, grid, (160,),
              [kv_map, ptr(q), ptr(out), ptr(ws_o), ptr(ws_ml), ptr(block_table), ptr(seq_lens),

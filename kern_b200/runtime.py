@@ -76,6 +76,37 @@ class Runtime:
             raise FileNotFoundError(f"no safetensors files under {weights}")
         self._rt.load_weights(paths)
 
+    def load_tensors(self, provider) -> None:
+        """Bind the weights from tensors already on the device: ``provider(name)`` returns the checkpoint
+        tensor of that name (device-to-device copies by segment, the same `bind` rules as a file load)."""
+        ranks = lambda g: self._rt.rank(g)
+        pick = lambda t: t if isinstance(t, str) else t["tensors"][ranks(t["group"])]
+        rng = lambda r, whole: (0, whole) if r is None else (tuple(r) if isinstance(r, list) else tuple(r["ranges"][ranks(r["group"])]))
+        for name, b in self.doc["buffers"].items():
+            if b["kind"] not in ("weight", "source") or b.get("placement") == "host":
+                continue
+            dst = self.tensor(name).view(-1)
+            at = 0
+            for seg in b["bind"]:
+                t = provider(pick(seg["tensor"]))
+                t2 = t.reshape(t.shape[0], -1) if t.dim() > 1 else t.reshape(-1, 1)
+                if "interleave" in seg:
+                    u = provider(pick(seg["interleave"]["with"])).reshape(t2.shape)
+                    n = seg["interleave"]["rows"]
+                    part = torch.stack([t2.view(-1, n, t2.shape[1]), u.view(-1, n, t2.shape[1])], 1).reshape(-1)
+                    del u
+                else:
+                    r, c = rng(seg.get("rows"), t2.shape[0]), rng(seg.get("cols"), t2.shape[1])
+                    part = t2[r[0]:r[1], c[0]:c[1]].reshape(-1)
+                if at + part.numel() > dst.numel():
+                    raise ValueError(f"buffer `{name}`: bound tensors hold more than the buffer")
+                dst[at:at + part.numel()] = part.to(dst.dtype)
+                at += part.numel()
+                del t, t2, part
+            if at != dst.numel():
+                raise ValueError(f"buffer `{name}`: bound tensors hold {at} elements, the buffer {dst.numel()}")
+        torch.cuda.synchronize(self.gpu)
+
     def once(self) -> None:
         """Run every `once` program (after every peer is connected)."""
         self._rt.run_once_programs()
