@@ -66,6 +66,7 @@ def main():
     ap.add_argument("--concurrency", type=int, default=256)
     ap.add_argument("--layers", type=int, default=36, help="for quick functional checks only; the headline is 36")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--profile", action="store_true", help="after the timed region, run one more step with per-call timing and print the cost by op to stderr")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -137,7 +138,7 @@ def main():
             last[i] = t[0]
     rt.check_error()
 
-    def one_step():
+    def one_step(timed=False):
         # requests that have produced all their tokens finish; new ones take their places and are prefilled in
         # the same call as everyone else's decode rows
         fresh, rows = {}, 0
@@ -151,7 +152,7 @@ def main():
                 fresh[j] = p
                 rows += len(p)
         batch = [(seqs[i], fresh.get(i) or [last[i]]) for i in range(conc)]
-        toks = eng.step(batch)
+        toks = eng.step(batch, timed=timed)
         for i, t in enumerate(toks):
             last[i] = t[0]
             seqs[i].age += 1
@@ -187,6 +188,16 @@ def main():
     step_ms = [evs[k].elapsed_time(evs[k + 1]) for k in range(steps)]
     dev_s = sum(step_ms) / 1e3
     rt.check_error()
+    if args.profile and rank == 0:
+        rows = one_step(timed=True)
+        by_op = {}
+        for label, op, ms, n in eng.last_times:
+            e = by_op.setdefault(op, [0.0, 0, 0])
+            e[0] += ms; e[1] += n; e[2] += 1
+        total = sum(v[0] for v in by_op.values())
+        print(f"# cost by op of one step ({rows} prompt rows + {conc} decode rows), eager, total {total:.2f} ms", file=sys.stderr)
+        for op, (ms, n, calls) in sorted(by_op.items(), key=lambda kv: -kv[1][0]):
+            print(f"#   {op:14s} {ms:8.3f} ms  {100 * ms / total:5.1f}%  calls {calls:4d}  launches {n}", file=sys.stderr)
 
     if world > 1:
         t = torch.tensor([dev_s, wall], device="cuda")

@@ -87,6 +87,11 @@ void bind_runtime(py::module_& m) {
         r.synchronize();
         return n;
       })
+      .def("issue_timed", [](Runtime& r, const std::string& program, const VarMap& vars) {
+        std::vector<std::tuple<std::string, std::string, float, size_t>> out;
+        for (auto& c : r.issue_timed(program, vars)) out.emplace_back(c.label, c.op, c.ms, c.launches);
+        return out;
+      })
       .def("is_captured", &Runtime::is_captured)
       .def("enqueue_after", &Runtime::enqueue_after)
       .def("zero_slot", &Runtime::zero_slot)

@@ -427,6 +427,34 @@ size_t Runtime::enqueue_after(const std::string& program, const VarMap& vars, ui
   return n;
 }
 
+std::vector<Runtime::CallTime> Runtime::issue_timed(const std::string& program, const VarMap& vars) {
+  if (!compiled_) throw std::runtime_error("the manifest's host states have not been bound yet");
+  auto it = programs_.find(program);
+  if (it == programs_.end()) throw std::runtime_error("no program named `" + program + "`");
+  const CompiledProgram& p = it->second;
+  const Program& src = m_.programs.at(program);
+  dev_->make_current();
+  std::vector<CUevent> evs;
+  std::vector<CallTime> out;
+  auto mark = [&] { CUevent e = dev_->event_create(true); dev_->event_record(e, stream_); evs.push_back(e); };
+  mark();
+  size_t call = (size_t)-1;
+  for (auto& l : p.launches) {
+    if (l.call_index != call) {
+      if (call != (size_t)-1) mark();
+      call = l.call_index;
+      out.push_back({l.label, src.calls[call].op, 0.f, 0});
+    }
+    out.back().launches += launch_one(l, vars, stream_);
+  }
+  mark();
+  dev_->stream_sync(stream_);
+  for (size_t i = 0; i + 1 < evs.size() && i < out.size(); ++i) out[i].ms = dev_->event_ms(evs[i], evs[i + 1]);
+  for (auto e : evs) Cuda::get().cuEventDestroy_(e);
+  for (auto& c : out) launches_total_ += c.launches;
+  return out;
+}
+
 void Runtime::run_once_programs() {
   for (auto& kv : m_.programs)
     if (kv.second.once) issue(kv.first, m_.vars_at_max(), true);

@@ -118,6 +118,14 @@ class Runtime {
   // eager or captured according to the program and `eager`; returns the number of kernel launches issued
   // (a graph replay counts the launches its graph holds)
   size_t issue(const std::string& program, const VarMap& vars, bool eager = false);
+  // One eager run with a CUDA event between calls: (call label, op, milliseconds) per call, in order.
+  // Serialises the lanes (everything on the main stream); for cost-by-op reports, not for serving.
+  struct CallTime {
+    std::string label, op;
+    float ms = 0;
+    size_t launches = 0;
+  };
+  std::vector<CallTime> issue_timed(const std::string& program, const VarMap& vars);
   bool is_captured(const std::string& program, const VarMap& vars) const;
   size_t graphs() const { return graphs_.size(); }
   uint64_t launches_total() const { return launches_total_; }

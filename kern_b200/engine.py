@@ -97,15 +97,20 @@ class Engine:
                 return f
         raise ValueError(f"no program takes {groups} sequences of rows {sorted(set(rows_each))}")
 
-    def step(self, batch: list[tuple[Sequence, list[int]]], eager: bool = False, read: bool = True):
+    def step(self, batch: list[tuple[Sequence, list[int]]], eager: bool = False, read: bool = True, timed: bool = False,
+             pad: int = 0):
         """Feed each sequence its new tokens; returns, per sequence, the tokens the call emitted for it
         (one for a plain step, up to ``count`` for a speculative round), or None when ``read`` is off
         or the program emits nothing."""
-        b = len(batch)
+        real = len(batch)
         rows_each = [len(t) for _, t in batch]
-        total = sum(rows_each)
-        if b == 0 or total == 0:
+        if real == 0 or sum(rows_each) == 0:
             return []
+        # `pad` dead sequences of the same row count bring a fixed-shape call up to a bucket: token 0 at
+        # position 0, slot -1 (nothing appended), context 0 (nothing attended); their outputs are dropped
+        rows_each += [rows_each[0]] * pad
+        b = real + pad
+        total = sum(rows_each)
         if total > self.rows_max or b > self.groups_max:
             raise ValueError(f"call of {b} sequences / {total} rows exceeds the manifest's {self.groups_max} / {self.rows_max}")
         fw = self.forward_for(b, rows_each)
@@ -123,10 +128,15 @@ class Engine:
             seq_len[i] = s.length + n
             at += n
             cu[i + 1] = at
+        for i in range(real, b):
+            n = rows_each[i]
+            tok[at:at + n], pos[at:at + n], slot[at:at + n], seq_len[i] = 0, 0, -1, 0
+            at += n
+            cu[i + 1] = at
         longest = int(seq_len.max())
         for f in self.fills.get("token", []):
             if f["axis"] == "groups":
-                self._write(f["name"], f["dtype"], np.array([t[0] for _, t in batch], np.int64))
+                self._write(f["name"], f["dtype"], np.array([t[0] for _, t in batch] + [0] * pad, np.int64))
             else:
                 self._write(f["name"], f["dtype"], tok)
         cols = {"position": pos, "slot": slot, "seq_len": seq_len, "valid": np.ones(total, np.int64)}
@@ -136,7 +146,7 @@ class Engine:
         for f in self.fills.get("cu_seqlens", []):
             self._write(f["name"], f["dtype"], cu)
         if "temperature" in self.fills:
-            sm = [s.sampling for s, _ in batch]
+            sm = [s.sampling for s, _ in batch] + [Sampling()] * pad
             for kind, vals in (("temperature", [x.temperature for x in sm]), ("top_k", [x.top_k for x in sm]),
                                ("top_p", [x.top_p for x in sm]), ("min_p", [x.min_p for x in sm]), ("seed", [x.seed for x in sm])):
                 f = self.fills[kind][0]
@@ -156,7 +166,11 @@ class Engine:
             vars_[self.p["ranks"]["var"]] = total
         if self.p.get("context"):
             vars_[self.p["context"]["var"]] = longest
-        launches = self.rt.issue(fw["name"], vars_, eager)
+        if timed:     # cost by call, eagerly, with an event between calls
+            self.last_times = self.rt.issue_timed(fw["name"], vars_)
+            launches = sum(t[3] for t in self.last_times)
+        else:
+            launches = self.rt.issue(fw["name"], vars_, eager)
         for s, new in batch:
             s.length += len(new)
             s.tokens.extend(new)
@@ -164,7 +178,7 @@ class Engine:
         self.last_launches = launches
         if not read or fw["emits"] is None:
             return None
-        return self.read_tokens(fw, b)
+        return self.read_tokens(fw, b)[:real]
 
     def read_tokens(self, fw, b: int):
         ef = next(f for f in self.p["fills"] if f["name"] == fw["emits"])

@@ -1,0 +1,161 @@
+"""Micro-benchmarks of the hand-written ops with roofline fractions.
+
+    python -m kern_b200.ops.bench_ops gemm --m 4096 --n 4096 --k 4096 [--epilogue store] [--bn 256]
+    python -m kern_b200.ops.bench_ops attn_decode --seqs 256 --ctx 2432 [--hq 32 --hk 8 --d 128 --page 64]
+    python -m kern_b200.ops.bench_ops attn_prefill --seqs 4 --rows 2048 --prefix 0
+    python -m kern_b200.ops.bench_ops norm --rows 4096 --n 4096
+
+Timing: CUDA events on the launching stream, warm-up first, a buffer larger than L2 written between
+timed iterations, synchronize on both sides. The roofline denominators are the measured copy bandwidth
+and bf16 GEMM throughput of this machine's GPUs when ``MEASURED_PEAKS.json`` is present at the repository
+root ("of measured"), otherwise 6.65 TB/s and 1.59 PFLOP/s ("of fallback").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+
+def peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "of measured"
+    return 6.65e12, 1.59e15, "of fallback"
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush.fill_(1)
+
+
+def timeit(fn, iters=10, warmup=3, flush=True):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def report(name, ms, flops=0.0, nbytes=0.0, **extra):
+    bw, fl, tag = peaks()
+    out = {"op": name, "ms_p50": round(ms[0], 4), "ms_min": round(ms[1], 4), **extra}
+    if flops:
+        out["tflops"] = round(flops / ms[0] / 1e9, 1)
+        out["frac_of_gemm_peak"] = f"{flops / (ms[0] * 1e-3) / fl:.3f} {tag}"
+    if nbytes:
+        out["gbs"] = round(nbytes / ms[0] / 1e6, 1)
+        out["frac_of_copy_bw"] = f"{nbytes / (ms[0] * 1e-3) / bw:.3f} {tag}"
+    print(json.dumps(out))
+    return out
+
+
+def bench_gemm(a):
+    from .gemm import gemm
+    from .launcher import Kernels
+
+    x = (torch.randn(a.m, a.k, device="cuda")).to(torch.bfloat16)
+    w = (torch.randn(a.n, a.k, device="cuda") * 0.1).to(torch.bfloat16)
+    cols = a.n // 2 if a.epilogue == "swiglu" else a.n
+    out = torch.zeros(a.m, cols, device="cuda", dtype=torch.float32 if a.epilogue == "f32" else torch.bfloat16)
+    ms = timeit(lambda: gemm(x, w, out=out, epilogue=a.epilogue, bn=a.bn), a.iters)
+    Kernels.get().check_error()
+    nbytes = 2 * (a.m * a.k + a.n * a.k) + out.numel() * out.element_size()
+    report("gemm_bf16_tn", ms, flops=2.0 * a.m * a.n * a.k, nbytes=nbytes, m=a.m, n=a.n, k=a.k, epilogue=a.epilogue, bn=a.bn)
+    if a.compare:
+        y = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+        ms2 = timeit(lambda: torch.matmul(x, w.t(), out=y), a.iters)
+        report("torch.matmul (cuBLAS, comparison only)", ms2, flops=2.0 * a.m * a.n * a.k)
+
+
+def _cache(seqs, ctx, hk, d, page):
+    per = (ctx + page - 1) // page
+    pool = torch.randn(seqs * per + 1, 2, hk, page, d, device="cuda").to(torch.bfloat16)
+    table = (torch.randperm(seqs * per, device="cuda").to(torch.int32) + 1).view(seqs, per).contiguous()
+    return pool, table
+
+
+def bench_attn_decode(a):
+    from .attention import paged_attention
+    from .launcher import Kernels
+
+    pool, table = _cache(a.seqs, a.ctx, a.hk, a.d, a.page)
+    q = torch.randn(a.seqs * a.rows, a.hq * a.d, device="cuda").to(torch.bfloat16)
+    lens = torch.full((a.seqs,), a.ctx, dtype=torch.int32, device="cuda")
+    out = torch.empty_like(q)
+    ms = timeit(lambda: paged_attention(q, pool, table, lens, a.hq, out=out, rows_per_seq=a.rows, splits=a.splits), a.iters)
+    Kernels.get().check_error()
+    kv_bytes = a.seqs * a.ctx * 2 * a.hk * a.d * 2
+    report("attn_decode_paged", ms, nbytes=kv_bytes + 2 * q.numel() * 2, seqs=a.seqs, ctx=a.ctx, rows=a.rows, splits=a.splits,
+           kv_gb=round(kv_bytes / 1e9, 3))
+
+
+def bench_attn_prefill(a):
+    from .attention import paged_attention
+    from .launcher import Kernels
+
+    ctx = a.prefix + a.rows
+    pool, table = _cache(a.seqs, ctx, a.hk, a.d, a.page)
+    q = torch.randn(a.seqs * a.rows, a.hq * a.d, device="cuda").to(torch.bfloat16)
+    lens = torch.full((a.seqs,), ctx, dtype=torch.int32, device="cuda")
+    cu = (torch.arange(a.seqs + 1, device="cuda") * a.rows).to(torch.int32)
+    out = torch.empty_like(q)
+    ms = timeit(lambda: paged_attention(q, pool, table, lens, a.hq, out=out, prefill=True, cu_q=cu, max_rows=a.rows), a.iters)
+    Kernels.get().check_error()
+    # causal: row r of a chunk sees prefix + r + 1 keys
+    keys = a.rows * a.prefix + a.rows * (a.rows + 1) / 2
+    report("attn_prefill_paged", ms, flops=4.0 * a.seqs * a.hq * a.d * keys, seqs=a.seqs, rows=a.rows, prefix=a.prefix)
+
+
+def bench_norm(a):
+    from .basic import rms_norm
+
+    x = torch.randn(a.rows, a.n, device="cuda").to(torch.bfloat16)
+    w = torch.randn(a.n, device="cuda").to(torch.bfloat16)
+    y = torch.empty_like(x)
+    ms = timeit(lambda: rms_norm(x, w, out=y), a.iters)
+    report("rms_norm", ms, nbytes=2 * x.numel() * 2, rows=a.rows, n=a.n)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="op", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=4096); g.add_argument("--n", type=int, default=4096); g.add_argument("--k", type=int, default=4096)
+    g.add_argument("--epilogue", default="store"); g.add_argument("--bn", type=int, default=None); g.add_argument("--compare", action="store_true")
+    d = sub.add_parser("attn_decode")
+    p = sub.add_parser("attn_prefill")
+    for s in (d, p):
+        s.add_argument("--seqs", type=int, default=64); s.add_argument("--hq", type=int, default=32); s.add_argument("--hk", type=int, default=8)
+        s.add_argument("--d", type=int, default=128); s.add_argument("--page", type=int, default=64); s.add_argument("--rows", type=int, default=1)
+    d.add_argument("--ctx", type=int, default=2432); d.add_argument("--splits", type=int, default=None)
+    p.add_argument("--prefix", type=int, default=0)
+    n = sub.add_parser("norm")
+    n.add_argument("--rows", type=int, default=4096); n.add_argument("--n", type=int, default=4096)
+    for s in (g, d, p, n):
+        s.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args(argv)
+    {"gemm": bench_gemm, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "norm": bench_norm}[a.op](a)
+
+
+if __name__ == "__main__":
+    main()

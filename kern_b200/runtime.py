@@ -153,6 +153,10 @@ class Runtime:
     def issue(self, program: str, vars: dict[str, int], eager: bool = False) -> int:
         return self._rt.issue(program, vars, eager)
 
+    def issue_timed(self, program: str, vars: dict[str, int]):
+        """One eager run with an event between calls: [(label, op, ms, launches)] in call order."""
+        return self._rt.issue_timed(program, vars)
+
     def run(self, program: str, vars: dict[str, int]) -> int:
         return self._rt.run(program, vars)
 

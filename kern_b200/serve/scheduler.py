@@ -1,0 +1,293 @@
+"""Continuous batching over one engine (one rank, or the head's view of a rank group).
+
+Each `step()`:
+  1. admits waiting requests while the pool can hold their worst case (prompt + max_tokens): a prefix
+     lookup first — a hit restores the kept pages (whole pages shared, a half page and the state slot
+     copied) and only the rest of the prompt is computed; when the pool is full, kept prefixes are
+     evicted until the request fits or nothing is left to evict;
+  2. builds one call: prompt rows of the admitted / still-prefilling requests up to the chunk budget
+     (prefill first), plus one decode row (or one speculative round) for every running request;
+     a pure-decode call is padded up to a bucket so captured graphs are reused;
+  3. hands tokens back, finishes requests (stop token, length), and keeps their prefix: pure-KV models at
+     the last page boundary, stateful models at the exact end (`retire`, no copy).
+
+Reference: crates/kern-serve/src/scheduler.rs:122 (buckets), :552-861 (admit), :867-967 (keep / finish),
+:985-1062 (prefill / step), :1067-1116 (stats line).
+"""
+from __future__ import annotations
+
+import logging
+import time
+from collections import deque
+from dataclasses import dataclass, field
+
+from .. import _native
+from ..engine import Engine, Sampling, Sequence
+
+log = logging.getLogger("kern.scheduler")
+
+BUCKETS = [1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512, 640, 768, 1024]
+
+
+def bucket_for(n: int, limit: int) -> int:
+    for b in BUCKETS:
+        if n <= b <= limit:
+            return b
+    return min(max(n, 1), limit)
+
+
+@dataclass
+class Request:
+    id: str
+    prompt: list[int]
+    max_tokens: int = 16
+    sampling: Sampling = field(default_factory=Sampling)
+    stop_ids: tuple[int, ...] = ()
+    history_tokens: int | None = None     # prompt length up to the last turn boundary (where a stateful model snapshots)
+    arrival: float = field(default_factory=time.monotonic)
+    # filled by the scheduler
+    seq: Sequence | None = None
+    fed: int = 0                # prompt tokens already in the states
+    cached: int = 0             # of which came from the prefix cache
+    out: list[int] = field(default_factory=list)
+    first_token_at: float | None = None
+    finished: str | None = None  # "stop" | "length" | "abort"
+    token_times: list[float] = field(default_factory=list)
+
+
+@dataclass
+class Stats:
+    steps: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    prefix_hits: int = 0
+    prefix_hit_tokens: int = 0
+    prefix_queries: int = 0
+    evictions: int = 0
+    accepted: int = 0
+    proposed: int = 0
+    step_seconds: float = 0.0
+    denied: int = 0
+
+
+class Scheduler:
+    def __init__(self, engine: Engine, chunk: int | None = None, max_seqs: int | None = None, prefix_cache: bool = True,
+                 rows: int | None = None, stats_every: float = 5.0):
+        self.eng = engine
+        self.pool = engine.pool
+        self.chunk = min(chunk or engine.rows_max, engine.rows_max)
+        row_shapes = sorted(f["rows"] for f in engine.forwards if f["rows"] != "var")
+        self.rows = rows if rows is not None else (row_shapes[-1] if row_shapes else 1)   # widest declared round
+        self.round = next((f for f in engine.forwards if f["rows"] == self.rows and self.rows > 1), None)
+        step_groups = max((f["groups"] for f in engine.forwards if f["rows"] != "var"), default=engine.groups_max)
+        self.max_seqs = min(max_seqs or step_groups, engine.groups_max)
+        self.prefix = _native.Prefix(self.pool.unit) if prefix_cache else None
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+        self.done: list[Request] = []
+        self.stats = Stats()
+        self._last_stats = time.monotonic()
+        self._stats_every = stats_every
+        self._last_counts = (0, 0)
+
+    # ---- the three calls of the Scheduler interface: submit / step / metrics ----
+    def submit(self, req: Request) -> None:
+        need = len(req.prompt) + req.max_tokens
+        if self.pool.pages_for(need) > self.pool.total_pages:
+            req.finished = "abort"
+            self.done.append(req)
+            raise ValueError(f"request {req.id} needs {need} tokens, more than the pool holds")
+        self.waiting.append(req)
+
+    def abort(self, req_id: str) -> bool:
+        for q in (self.waiting, self.running):
+            for r in list(q):
+                if r.id == req_id:
+                    q.remove(r)
+                    if r.seq is not None:
+                        self.eng.close(r.seq)
+                        r.seq = None
+                    r.finished = "abort"
+                    self.done.append(r)
+                    return True
+        return False
+
+    def idle(self) -> bool:
+        return not self.waiting and not self.running
+
+    def metrics(self) -> dict:
+        p = self.pool
+        return {"kv_used_blocks": p.total_pages - p.free_pages, "kv_total_blocks": p.total_pages,
+                "num_running_reqs": len(self.running), "num_waiting_reqs": len(self.waiting),
+                "spec_decode": {"accepted": self.stats.accepted, "proposed": self.stats.proposed},
+                "prefix_cache": {"queries": self.stats.prefix_queries, "hits": self.stats.prefix_hits,
+                                 "hit_tokens": self.stats.prefix_hit_tokens, "entries": len(self.prefix) if self.prefix is not None else 0}}
+
+    # ---- admission ----
+    def _make_room(self, pages: int, slot: bool) -> bool:
+        """Evict kept prefixes until the ask fits; allocation and 'is there room' stay one action: the caller
+        retries the lease itself."""
+        while not self.pool.room(pages, slot):
+            if self.prefix is None or len(self.prefix) == 0:
+                return False
+            self.prefix.evict()
+            self.stats.evictions += 1
+        return True
+
+    def _admit_one(self, req: Request) -> bool:
+        need = len(req.prompt) + req.max_tokens + (self.rows if self.round else 0)
+        hit = None
+        if self.prefix is not None and len(req.prompt) > 1:
+            self.stats.prefix_queries += 1
+            # at least one prompt token must be computed so the call has a row to emit from
+            hit = self.prefix.lookup(req.prompt, len(req.prompt) - 1)
+        for attempt in range(2):
+            try:
+                if hit is not None:
+                    length, ckpt = hit
+                    lease, copies = self.pool.restore(ckpt, length, need)
+                    self.eng.rt.run_copies(copies)
+                    if lease.slot >= 0 and copies["slot"] is None:
+                        self.eng.rt.zero_slot(lease.slot)
+                    req.seq = Sequence(lease=lease, length=length, sampling=req.sampling, tokens=list(req.prompt[:length]))
+                    req.fed = req.cached = length
+                    self.stats.prefix_hits += 1
+                    self.stats.prefix_hit_tokens += length
+                else:
+                    req.seq = self.eng.open(need, req.sampling)
+                return True
+            except _native.Denied as e:
+                why = e.args[1] if len(e.args) > 1 else "busy"
+                if why != "busy" or attempt == 1:
+                    self.stats.denied += 1
+                    return False
+                shared = (hit[0] // self.pool.unit) if hit is not None else 0
+                if not self._make_room(self.pool.pages_for(need) - shared, True):
+                    self.stats.denied += 1
+                    return False
+        return False
+
+    def _admit(self) -> None:
+        while self.waiting and len(self.running) < self.max_seqs:
+            if not self._admit_one(self.waiting[0]):
+                break
+            self.running.append(self.waiting.popleft())
+
+    # ---- keeping prefixes ----
+    def _keep(self, req: Request) -> None:
+        """A finished request leaves its tokens' state behind for the next turn of the conversation."""
+        seq = req.seq
+        req.seq = None
+        if seq is None:
+            return
+        if self.prefix is None or seq.length < 1:
+            self.eng.close(seq)
+            return
+        tokens = seq.tokens[:seq.length]
+        stateful = seq.lease.slot >= 0
+        # pure KV: keep whole pages only (usable at any page boundary, nothing to copy);
+        # stateful: the state is "exactly after these tokens", kept at the exact end by retiring the lease
+        length = seq.length if stateful else (seq.length // self.pool.unit) * self.pool.unit
+        if length == 0:
+            self.eng.close(seq)
+            return
+        ckpt = self.pool.retire(seq.lease, length)
+        self.prefix.insert(tokens, ckpt, stateful, length)
+
+    def _finish(self, req: Request, why: str) -> None:
+        req.finished = why
+        self.running.remove(req)
+        self._keep(req)
+        self.done.append(req)
+
+    # ---- one step ----
+    def step(self) -> list[tuple[Request, list[int]]]:
+        """Run one call; returns (request, new tokens) for every request that produced tokens."""
+        t0 = time.monotonic()
+        self._admit()
+        if not self.running:
+            return []
+        batch, kinds = [], []
+        budget = self.chunk
+        decoding = [r for r in self.running if r.fed >= len(r.prompt)]
+        prefilling = [r for r in self.running if r.fed < len(r.prompt)]
+        rows_decode = self.rows if self.round else 1
+        budget -= len(decoding) * rows_decode
+        for r in prefilling:                       # prefill first: oldest request gets the budget
+            if budget <= 0:
+                break
+            n = min(budget, len(r.prompt) - r.fed)
+            batch.append((r.seq, r.prompt[r.fed:r.fed + n]))
+            kinds.append((r, "prefill", n))
+            budget -= n
+        use_round = self.round is not None and not batch       # a round is a fixed-shape call of its own
+        for r in decoding:
+            last = r.out[-1]
+            batch.append((r.seq, [last] * (self.rows if use_round else 1)))
+            kinds.append((r, "decode", 1))
+        if not batch:
+            return []
+        pad = 0
+        if not prefilling or not any(k[1] == "prefill" for k in kinds):
+            # fixed-shape call: pad to a bucket with dead rows so captured graphs are reused
+            want = bucket_for(len(batch), self.max_seqs)
+            pad = want - len(batch)
+        toks = self.eng.step(batch, pad=pad)
+        now = time.monotonic()
+        emitted = []
+        for (r, kind, n), got in zip(kinds, toks or [[]] * len(kinds)):
+            if kind == "prefill":
+                r.fed += n
+                self.stats.prefill_tokens += n
+                if r.fed < len(r.prompt):
+                    continue                       # the chunk's emitted token is not the prompt's next token yet
+                new = got[:1]
+            else:
+                new = got
+                self.stats.decode_tokens += len(new)
+                if use_round:
+                    self.stats.proposed += self.rows - 1
+                    self.stats.accepted += max(0, len(new) - 1)
+            if r.first_token_at is None and new:
+                r.first_token_at = now
+            taken = []
+            for t in new:
+                r.out.append(int(t))
+                r.token_times.append(now)
+                taken.append(int(t))
+                if int(t) in r.stop_ids:
+                    self._finish(r, "stop")
+                    break
+                if len(r.out) >= r.max_tokens:
+                    self._finish(r, "length")
+                    break
+            if use_round and r.finished is None and r.seq is not None:
+                # a round fed `rows` positions; only the accepted ones stay (paged KV slot = position: no copy)
+                r.seq.length -= self.rows - len(new)
+                del r.seq.tokens[r.seq.length:]
+            emitted.append((r, taken))
+        self.stats.steps += 1
+        self.stats.step_seconds += time.monotonic() - t0
+        self._maybe_log()
+        return emitted
+
+    def run_until_idle(self, max_steps: int = 1 << 30) -> None:
+        n = 0
+        while not self.idle() and n < max_steps:
+            self.step()
+            n += 1
+
+    def _maybe_log(self) -> None:
+        now = time.monotonic()
+        if now - self._last_stats < self._stats_every:
+            return
+        s = self.stats
+        dt = now - self._last_stats
+        steps = s.steps - self._last_counts[0]
+        toks = s.decode_tokens - self._last_counts[1]
+        p = self.pool
+        log.info("stats running=%d waiting=%d kv=%.1f%% steps=%d step_ms=%.2f tok_s=%.1f accept=%.1f%% prefix_hits=%d evictions=%d",
+                 len(self.running), len(self.waiting), 100.0 * (p.total_pages - p.free_pages) / max(1, p.total_pages), steps,
+                 1e3 * s.step_seconds / max(1, s.steps), toks / dt, 100.0 * s.accepted / max(1, s.proposed), s.prefix_hits, s.evictions)
+        self._last_stats = now
+        self._last_counts = (s.steps, s.decode_tokens)
