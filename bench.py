@@ -66,6 +66,8 @@ def main():
     ap.add_argument("--concurrency", type=int, default=256)
     ap.add_argument("--layers", type=int, default=36, help="for quick functional checks only; the headline is 36")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"],
+                    help="N > 1: tensor parallel over one replicated batch (default) or data-parallel replicas")
     ap.add_argument("--profile", action="store_true", help="after the timed region, run one more step with per-call timing and print the cost by op to stderr")
     args = ap.parse_args()
 
@@ -91,16 +93,27 @@ def main():
     from kern_b200.models import dense
     from kern_b200.runtime import Runtime
 
-    conc = args.concurrency // world          # data-parallel replicas split the concurrent requests
+    tp = world > 1 and args.parallelism == "tp"
+    # tensor parallel: every rank is fed the whole batch; data parallel: replicas split the concurrent requests
+    conc = args.concurrency if tp else args.concurrency // world
     out_len, p_lo, p_hi = 256, 512, 4096
     cfg = dense.DenseConfig(name="dense-8b", layers=args.layers, max_seqs=max(conc, 8), max_tokens=p_hi + conc + 64,
-                            max_context=p_hi + out_len + 64, page_size=64)
+                            max_context=p_hi + out_len + 64, page_size=64, tp=world if tp else 1)
     torch.cuda.set_device(local)
-    rt = Runtime(dense.build_manifest(cfg), gpu=local, memory_fraction=0.92)
-    dense.load_random_weights(rt, cfg, seed=args.seed)
-    rt.once()
+    if tp:
+        from kern_b200.models import dense_tp
+        from kern_b200.parallel import group
+
+        doc = dense_tp.build_manifest_tp(cfg)
+        rt = Runtime(doc, gpu=local, memory_fraction=0.90, topology=group.topology(doc["topology"]["groups"], rank, world))
+        dense.load_random_weights(rt, cfg, seed=args.seed)
+        group.start(rt)
+    else:
+        rt = Runtime(dense.build_manifest(cfg), gpu=local, memory_fraction=0.92)
+        dense.load_random_weights(rt, cfg, seed=args.seed)
+        rt.once()
     eng = Engine(rt)
-    rng = np.random.default_rng(args.seed + rank)
+    rng = np.random.default_rng(args.seed + (0 if tp else rank))   # tensor-parallel ranks replay the same requests
 
     def new_prompt():
         return rng.integers(0, cfg.vocab, int(rng.integers(p_lo, p_hi + 1))).tolist()
@@ -203,7 +216,7 @@ def main():
         t = torch.tensor([dev_s, wall], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_s, wall = float(t[0]), float(t[1])
-    total_tokens = conc * world * steps
+    total_tokens = conc * (1 if tp else world) * steps
     value = total_tokens / dev_s
     e2e = total_tokens / wall
     if rank == 0:
@@ -215,8 +228,8 @@ def main():
             "dtype": "bf16", "data": "synthetic (uniform-random token ids, random-init N(0,0.02) bf16 weights)",
             "config": {"model": "dense GQA 8B-class: 36L hidden 4096 32Q/8KV hd128 SwiGLU 12288 vocab 151936"
                        if args.layers == 36 else f"REDUCED {args.layers}-layer functional check (not a headline number)",
-                       "global_batch": conc * world, "seq_len": f"prompts {p_lo}-{p_hi} uniform, {out_len} outputs",
-                       "parallelism": f"dp{world}" if world > 1 else "tp1",
+                       "global_batch": conc * (1 if tp else world), "seq_len": f"prompts {p_lo}-{p_hi} uniform, {out_len} outputs",
+                       "parallelism": (f"tp{world}" if tp else f"dp{world}") if world > 1 else "tp1",
                        "step": "steady-state engine iteration: 1 finished request replaced (whole prompt prefilled) + decode rows, every live sequence emits a token",
                        "l2": "inputs larger than L2 (weights 15 GB + paged KV of all live sequences read every step)",
                        "mean_prompt_rows_per_step": round(prompt_rows / steps, 1)},

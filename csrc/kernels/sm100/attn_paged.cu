@@ -3,7 +3,7 @@
 //     64-token KV tile between them, optional split-KV over grid.z with a merge kernel), and
 //   * causal chunked prefill (each math warp owns 16 query rows of a 64-row block and walks the
 //     KV tiles up to its causal limit; earlier chunks / a cached prefix are simply more pages).
-// KV tiles are fetched by a producer warp with 2-D TMA boxes (128-byte swizzle, no multicast)
+// KV tiles are fetched by a producer warp with 2-D TMA boxes (128-byte swizzle, single-CTA destination)
 // into a ring of stages guarded by bounded mbarrier waits; the math is bf16 mma.sync with f32
 // online softmax. The kernel is bandwidth-bound in decode (the KV cache is read exactly once) —
 // the roofline it is measured against is HBM, not the tensor cores.

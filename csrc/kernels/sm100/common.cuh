@@ -1,5 +1,5 @@
 // Shared device-side helpers for the sm_100a kernels: PTX wrappers for mbarrier, TMA
-// (cp.async.bulk.tensor, never with cluster multicast), tcgen05 (TMEM alloc, MMA, commit, ld),
+// (cp.async.bulk.tensor into this CTA's own shared memory only), tcgen05 (TMEM alloc, MMA, commit, ld),
 // bounded waits with a sticky error word, and small numeric utilities.
 //
 // Every wait in this tree is bounded: a wait that runs out records a code in the launch's
@@ -72,7 +72,7 @@ KERN_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_f
   return false;
 }
 
-// ---- TMA (tiled bulk tensor copies; no multicast anywhere) ------------------------------------
+// ---- TMA (tiled bulk tensor copies, each into the issuing CTA only) -------------------------------
 KERN_DEVICE void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }

@@ -15,8 +15,9 @@
 // fastest, so CTAs running at the same time share W tiles through L2.
 //
 // Epilogues: 0 bf16 store; 1 f32 store; 2 bf16 store of acc + R (R may alias C: the in-place
-// residual add, beta = 1); 3 SwiGLU over weights interleaved 16 gate rows / 16 up rows:
-// out[m, n/2] = silu(gate) * up, ldc counts output columns.
+// residual add, beta = 1); 3 SwiGLU over W = [gate rows ; up rows] (N = 2 x intermediate): each tile
+// stages BN/2 gate rows and the matching BN/2 up rows, out[m, n/2] = silu(gate) * up, ldc counts
+// output columns. The W descriptor's box is BN/2 rows for this epilogue.
 //
 // Every mbarrier wait is bounded; a wait that runs out sets *err and the CTA unwinds.
 #include "common.cuh"
@@ -106,7 +107,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
           uint8_t* sb = sa + Cfg::kStageBytesA;
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
           tma_load_2d(sa, tma_a, kb * BK, m_blk * BM, &full_bar[stage]);
-          tma_load_2d(sb, tma_b, kb * BK, n_blk * BN, &full_bar[stage]);
+          if constexpr (EPI == 3) {
+            // W = [gate rows ; up rows]: this tile's B rows are BN/2 gate rows then the matching BN/2 up rows
+            tma_load_2d(sb, tma_b, kb * BK, n_blk * (BN / 2), &full_bar[stage]);
+            tma_load_2d(sb + (BN / 2) * BK * 2, tma_b, kb * BK, N / 2 + n_blk * (BN / 2), &full_bar[stage]);
+          } else {
+            tma_load_2d(sb, tma_b, kb * BK, n_blk * BN, &full_bar[stage]);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -167,6 +174,33 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
       tc_fence_after();
       const int row = m_blk * BM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      if constexpr (EPI == 3) {
+        // SwiGLU: accumulator columns [0, BN/2) are gate, [BN/2, BN) the matching up columns
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(t_row + c * 32, g);
+          tmem_ld_32x32(t_row + BN / 2 + c * 32, u);
+          tmem_ld_wait();
+          const int col = n_blk * (BN / 2) + c * 32;   // output column
+          if (row < M && col < N / 2) {
+            __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(Cv) + (size_t)row * ldc + col;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col + v * 8 < N / 2) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  f[j] = silu(__uint_as_float(g[v * 8 + j])) * __uint_as_float(u[v * 8 + j]);
+                uint4 o;
+                o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+                o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+                *reinterpret_cast<uint4*>(C + v * 8) = o;
+              }
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -210,24 +244,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
                 *reinterpret_cast<float4*>(C + v * 4) = o;
               }
             }
-          } else {  // EPI == 3: SwiGLU, 16 gate columns then 16 up columns
-            if (col < N) {
-              __nv_bfloat16* C =
-                  reinterpret_cast<__nv_bfloat16*>(Cv) + (size_t)row * ldc + (col >> 1);
-              float f[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                f[j] = silu(__uint_as_float(r[j])) * __uint_as_float(r[16 + j]);
-              uint4 o0, o1;
-              o0.x = pack_bf16x2(f[0], f[1]);   o0.y = pack_bf16x2(f[2], f[3]);
-              o0.z = pack_bf16x2(f[4], f[5]);   o0.w = pack_bf16x2(f[6], f[7]);
-              o1.x = pack_bf16x2(f[8], f[9]);   o1.y = pack_bf16x2(f[10], f[11]);
-              o1.z = pack_bf16x2(f[12], f[13]); o1.w = pack_bf16x2(f[14], f[15]);
-              *reinterpret_cast<uint4*>(C) = o0;
-              *reinterpret_cast<uint4*>(C + 8) = o1;
-            }
           }
         }
+      }
       }
       tc_fence_before();
       __syncwarp();

@@ -70,8 +70,7 @@ def _gemm(epi):
         av = torch.as_strided(a, (m, k), (a_stride(a, k), 1))
         acc = _f(av) @ _f(w[: n * k].view(n, k)).t()
         if epi == "swiglu":
-            t = acc.view(m, n // 32, 2, 16)
-            acc = (torch.nn.functional.silu(t[:, :, 0]) * t[:, :, 1]).reshape(m, n // 2)
+            acc = torch.nn.functional.silu(acc[:, : n // 2]) * acc[:, n // 2:]
         cv = torch.as_strided(c, (m, acc.shape[1]), (ldc, 1))
         if epi == "acc":
             acc = acc + _f(torch.as_strided(r, (m, n), (ldc, 1)))

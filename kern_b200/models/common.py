@@ -110,7 +110,7 @@ def gemm_op(n: int, k: int, *, epilogue: str = "store", rows_var: str = "tokens"
     """C[rows, n] = A[rows, k] · W[n, k]ᵀ through the tcgen05 GEMM, one launch per `when` range.
 
     Interface: [a, w, c, rows, err]. epilogue store | acc (c += …, c is inout) | f32 | swiglu
-    (c is [rows, n/2] over weights interleaved 16 gate / 16 up rows)."""
+    (c is [rows, n/2] over weights stacked [gate rows ; up rows])."""
     lda = k if lda is None else lda
     out_cols = n // 2 if epilogue == "swiglu" else n
     ldc = out_cols if ldc is None else ldc
@@ -135,7 +135,8 @@ def gemm_op(n: int, k: int, *, epilogue: str = "store", rows_var: str = "tokens"
                     "param": 0, "dtype": "bf16", "dims": [k, 0], "strides": [lda * 2], "box": [BK, BM],
                     "swizzle": 128, "l2_promotion": 256}}]}},
                 {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
-                    "param": 1, "dtype": "bf16", "dims": [k, n], "strides": [k * 2], "box": [BK, bn],
+                    "param": 1, "dtype": "bf16", "dims": [k, n], "strides": [k * 2],
+                    "box": [BK, bn // 2 if epilogue == "swiglu" else bn],
                     "swizzle": 128, "l2_promotion": 256}}]}},
                 {"param": 2}, {"param": 2 if epilogue == "acc" else 0}, {"param": 3}, {"i32": n}, {"i32": k},
                 {"i32": ldc}, {"param": 4}],
@@ -350,3 +351,58 @@ def rope_table_op(max_pos: int, rot: int, theta: float) -> dict:
         "grid": [min(1024, -(-max_pos * (rot // 2) // 256)), 1, 1],
         "params": ["out buffer<f32>", "out buffer<f32>", "i32", "i32", "i64"],
         "args": [{"param": 0}, {"param": 1}, {"i32": max_pos}, {"i32": rot}, {"i64": f64_bits(theta)}]}]}}
+
+
+# ---- tensor-parallel ops ---------------------------------------------------------------------------
+TP_GRID = 592                      # most CTAs of the fused all-reduce (4 per SM) = columns of its flag arrays
+TP_ONESHOT_ROWS = 64               # up to this many rows every rank reduces everything itself
+
+
+def tp_slot_rows(rows_max: int, nranks: int, grid: int = TP_GRID) -> int:
+    """Rows one staging slot must hold: all rows in one-shot mode, a rank's dealt share in two-shot."""
+    per_cta = -(-rows_max // grid)
+    return max(TP_ONESHOT_ROWS, -(-per_cta // nranks) * grid)
+
+
+def tp_allreduce_norm_op(hidden: int, eps: float, nranks: int, rows_max: int, group: str = "tp",
+                         plus_one: bool = False, timeout_ns: int = 2_000_000_000) -> dict:
+    """x += sum over the group of `partial`; xn = rmsnorm(x) * w — one kernel over NVLink peer memory.
+    Interface [partial, x, x_peers, xn, w, comm, comm_peers, flags, flag_peers, epochs, err, rows]."""
+    slot_rows = tp_slot_rows(rows_max, nranks)
+    iface = ["in buffer<bf16>", "inout buffer<bf16>", "in buffer<u64>", "out buffer<bf16>", "in buffer<bf16>",
+             "inout buffer<bf16>", "in buffer<u64>", "inout buffer<u32>", "in buffer<u64>", "inout buffer<u32>",
+             "out buffer<i32>", "i32"]
+    lp = iface[:11] + ["i32", "i32", "i32", "i32", "i32", "f32", "i32", "i32", "i64", "i32"]
+    launches = []
+    # few rows: one-shot on a grid no larger than the rows (every CTA of the grid exchanges flags);
+    # many rows: two-shot on the full grid
+    for mode, grid, lo, hi in ((0, 16, 1, min(16, rows_max)), (0, TP_ONESHOT_ROWS, 17, min(TP_ONESHOT_ROWS, rows_max)),
+                               (1, TP_GRID, TP_ONESHOT_ROWS + 1, rows_max)):
+        if lo > hi:
+            continue
+        when = {"var": "tokens"}
+        if lo > 1:
+            when["min"] = lo
+        if hi < rows_max:
+            when["max"] = hi
+        launch = {"module": "tp_allreduce_norm", "entry": "kern_tp_allreduce_residual_norm", "block": [256, 1, 1],
+                  "grid": [grid, 1, 1], "shared_mem": hidden * 4, "params": lp,
+                  "args": [{"param": i} for i in range(11)] + [{"rank": group}, {"i32": nranks}, {"param": 11}, {"i32": hidden},
+                                                                {"i32": slot_rows}, {"f32": eps}, {"i32": int(plus_one)},
+                                                                {"i32": mode}, {"i64": timeout_ns}, {"i32": TP_GRID}]}
+        if len(when) > 1:
+            launch["when"] = when
+        launches.append(launch)
+    return {"params": iface, "impl": {"launches": launches}}
+
+
+def tp_buffers(hidden: int, nranks: int, rows_max: int, group: str = "tp") -> dict:
+    """Exported staging / flag buffers of the fused all-reduce and their peer address tables."""
+    slot_rows = tp_slot_rows(rows_max, nranks)
+    return {
+        "tp.comm": {"dtype": "bf16", "shape": [2, nranks, slot_rows, hidden], "kind": "carry", "export": True},
+        "tp.comm_peers": {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": "tp.comm", "group": group},
+        "tp.flags": {"dtype": "u32", "shape": [2, nranks, TP_GRID], "kind": "carry", "export": True},
+        "tp.flags_peers": {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": "tp.flags", "group": group},
+        "tp.epochs": {"dtype": "u32", "shape": [TP_GRID], "kind": "carry"},
+    }

@@ -2,7 +2,7 @@
 PyTorch fp32 oracle of the same architecture.
 
 The generator is the only place that knows the model: which kernels a layer calls, how the
-checkpoint's tensors concatenate into fused weights (q|k|v stacked, gate/up interleaved for the
+checkpoint's tensors concatenate into fused weights (q|k|v stacked, gate then up stacked for the
 SwiGLU epilogue), which tables are derived at load. The engine sees a manifest.
 Programs: ``load`` (once: rope tables), ``prefill`` (ragged rows over up to ``seqs`` sequences: prompt
 chunks and decode rows mixed, split by ``cu_seqlens``), ``decode`` (one row per sequence, replayed as a
@@ -157,7 +157,7 @@ def build_manifest(cfg: DenseConfig) -> dict:
                                                    {"tensor": p + "self_attn.v_proj.weight"}])
         weight(f"w.l{i}.o", (h, cfg.q_dim), [{"tensor": p + "self_attn.o_proj.weight"}])
         weight(f"w.l{i}.ln2", (h,), [{"tensor": p + "post_attention_layernorm.weight"}])
-        weight(f"w.l{i}.gu", (2 * inter, h), [{"tensor": p + "mlp.gate_proj.weight", "interleave": {"with": p + "mlp.up_proj.weight", "rows": 16}}])
+        weight(f"w.l{i}.gu", (2 * inter, h), [{"tensor": p + "mlp.gate_proj.weight"}, {"tensor": p + "mlp.up_proj.weight"}])
         weight(f"w.l{i}.down", (h, inter), [{"tensor": p + "mlp.down_proj.weight"}])
         if cfg.qk_norm:
             weight(f"w.l{i}.qn", (d,), [{"tensor": p + "self_attn.q_norm.weight"}])

@@ -32,13 +32,10 @@ def pick_bn(m: int, n: int, sms: int, epilogue: str = "store") -> int:
     return choices[-1]
 
 
-def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, rows: int = 16) -> torch.Tensor:
-    """Weights for the SwiGLU epilogue: ``rows`` gate rows, then ``rows`` up rows, repeating."""
-    i, k = gate.shape
-    assert up.shape == gate.shape and i % rows == 0
-    g = gate.reshape(i // rows, rows, k)
-    u = up.reshape(i // rows, rows, k)
-    return torch.stack([g, u], dim=1).reshape(2 * i, k).contiguous()
+def stack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Weights for the SwiGLU epilogue: all gate rows, then all up rows."""
+    assert up.shape == gate.shape
+    return torch.cat([gate, up], 0).contiguous()
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *,
@@ -47,7 +44,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *,
     """``a[M,K]`` bf16 row-major (row stride free), ``w[N,K]`` bf16; returns ``out``.
 
     epilogue: ``store`` (bf16), ``f32``, ``acc`` (bf16 ``out = a·wᵀ + residual``; residual defaults
-    to ``out`` itself), ``swiglu`` (``out[M, N/2] = silu(gate)·up`` over interleaved weights).
+    to ``out`` itself), ``swiglu`` (``out[M, N/2] = silu(gate)·up`` over weights stacked [gate; up]).
     ``m`` runs only the first m rows (the tensor maps are made for the whole buffer, so a decode
     step with fewer rows reuses them).
     """
@@ -55,7 +52,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *,
     assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1]
     M = a.shape[0] if m is None else m
     N, K = w.shape
-    assert K % 8 == 0 and N % 8 == 0
+    assert K % 8 == 0 and N % (16 if epilogue == "swiglu" else 8) == 0
     k = Kernels.get(a.device)
     out_cols = N // 2 if epilogue == "swiglu" else N
     if out is None:
@@ -71,7 +68,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *,
     if bn is None:
         bn = pick_bn(M, N, k.sm_count, epilogue)
     tma_a = k.tensor_map_2d(a, BM, BK)
-    tma_b = k.tensor_map_2d(w, bn, BK)
+    tma_b = k.tensor_map_2d(w, bn // 2 if epilogue == "swiglu" else bn, BK)
     tiles = ((M + BM - 1) // BM) * ((N + bn - 1) // bn)
     grid = min(tiles, k.sm_count)
     entry = f"kern_gemm_bf16_tn{_EPI[epilogue]}_n{bn}"
@@ -91,8 +88,6 @@ def gemm_reference(a: torch.Tensor, w: torch.Tensor, epilogue: str = "store",
     if epilogue == "acc":
         return (acc + residual.float()).to(torch.bfloat16)
     if epilogue == "swiglu":
-        m, n = acc.shape
-        t = acc.reshape(m, n // 32, 2, 16)
-        g, u = t[:, :, 0], t[:, :, 1]
-        return (torch.nn.functional.silu(g) * u).reshape(m, n // 2).to(torch.bfloat16)
+        n = acc.shape[1]
+        return (torch.nn.functional.silu(acc[:, : n // 2]) * acc[:, n // 2:]).to(torch.bfloat16)
     return acc.to(torch.bfloat16)

@@ -1,0 +1,54 @@
+"""Tensor parallelism over NVLink peer memory: the fused all-reduce + residual + RMSNorm kernel and the
+tensor-parallel decoder, as one process per GPU; plus the bounded wait of the peer barrier on one GPU
+(a flag that nothing sets makes the wait run out and the kernel report which rank is missing)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_peer_barrier_wait_runs_out_and_names_the_missing_rank(cuda):
+    from kern_b200.ops.launcher import Kernels, i32, i64, ptr
+    import struct
+
+    k = Kernels.get(cuda)
+    flags = torch.zeros(8, dtype=torch.int32, device=cuda)
+    epoch = torch.zeros(1, dtype=torch.int32, device=cuda)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    # a "group" of 3 whose other two members never launch: every flag pointer is this rank's own array, so
+    # rank 0's own arrival shows up and ranks 1 and 2 never do
+    peers = torch.tensor([flags.data_ptr()] * 3, dtype=torch.int64, device=cuda)
+    k.launch("tp_allreduce_norm", "kern_peer_barrier", (1,), (32,),
+             [ptr(flags), ptr(peers), ptr(epoch), ptr(err), i32(0), i32(3), i64(2_000_000)])   # 2 ms
+    torch.cuda.synchronize()
+    assert int(err.item()) in (201, 202)
+    assert int(epoch.item()) == 1 and int(flags[0].item()) == 1
+    # the context is still usable and a complete group passes
+    err.zero_()
+    peers1 = torch.tensor([flags.data_ptr()], dtype=torch.int64, device=cuda)
+    k.launch("tp_allreduce_norm", "kern_peer_barrier", (1,), (32,),
+             [ptr(flags), ptr(peers1), ptr(epoch), ptr(err), i32(0), i32(1), i64(2_000_000)])
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0 and int(epoch.item()) == 2
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tp_allreduce_and_model(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29500 + world), "-m", "kern_b200.parallel.tp_check", "--rows", "1", "8", "64", "65", "300", "1000"]
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
+    assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
+    ar = next(l for l in lines if l["check"] == "allreduce_residual_norm")
+    assert all(r["ok"] for r in ar["results"]) and len(ar["results"]) == 12
+    model = next(l for l in lines if l["check"] == "tp_model")
+    assert model["ok"], model
