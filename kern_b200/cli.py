@@ -1,0 +1,335 @@
+"""The `kern` command: verify / cut / kernels / run / test / bench / workload / server.
+
+    python -m kern_b200 verify model/manifest.json
+    python -m kern_b200 cut model/manifest.json --at 40,80 --out stages/
+    python -m kern_b200 run --manifest m.json --weights ckpt/ --prompt-ids 1,2,3 --steps 16 [--cpu]
+    python -m kern_b200 test A.json B.json --weights ckpt/ [--cpu]        (exit 0 PASS / 1 FAIL / 2 INCONCLUSIVE)
+    python -m kern_b200 bench --manifest m.json --weights ckpt/ [--workload w.toml]
+    python -m kern_b200 server --manifest m.json --weights ckpt/ --port 8000
+
+Flags override the `[targets.<name>]` of a `kern.toml` found by walking up from the working directory
+(`gpu`, `capacity`, `[targets.x]{manifest,reference,kernels,weights,tokenizer}`, `[test]`, `[run]`).
+Reference: crates/kern-run/src/bin/kern.rs:32-333, crates/kern-run/src/config.rs:40-159.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+import time
+import tomllib
+from pathlib import Path
+
+
+# ---- kern.toml ---------------------------------------------------------------------------------------
+_TOP = {"gpu", "capacity", "targets", "kernels", "test", "run"}
+_TARGET = {"manifest", "reference", "kernels", "weights", "tokenizer"}
+
+
+def find_config(start: Path | None = None) -> tuple[Path | None, dict]:
+    d = (start or Path.cwd()).resolve()
+    for p in [d, *d.parents]:
+        f = p / "kern.toml"
+        if f.exists():
+            cfg = tomllib.loads(f.read_text())
+            unknown = set(cfg) - _TOP
+            if unknown:
+                raise SystemExit(f"{f}: unknown field(s) {sorted(unknown)}")
+            for name, t in cfg.get("targets", {}).items():
+                bad = set(t) - _TARGET
+                if bad:
+                    raise SystemExit(f"{f}: target `{name}`: unknown field(s) {sorted(bad)}")
+            return f, cfg
+    return None, {}
+
+
+def resolve(args, cfg_path, cfg) -> None:
+    """flag > target > default."""
+    t = cfg.get("targets", {}).get(getattr(args, "target", None) or "", {})
+    base = cfg_path.parent if cfg_path else Path.cwd()
+    for key in ("manifest", "weights", "kernels", "tokenizer"):
+        if getattr(args, key, None) is None and key in t:
+            setattr(args, key, str(base / t[key]))
+    if getattr(args, "gpu", None) is None:
+        args.gpu = cfg.get("gpu", 0)
+    if getattr(args, "capacity", None) is None:
+        args.capacity = cfg.get("capacity", 0)
+
+
+def make_runtime(args, manifest=None):
+    manifest = manifest or args.manifest
+    if args.cpu:
+        from .cpu import CpuRuntime
+
+        rt = CpuRuntime(manifest, weights=_weights_path(args.weights), tokens=args.capacity or 4096, slots=getattr(args, "max_seqs", 0) or 0)
+    else:
+        from .runtime import Runtime
+
+        rt = Runtime(manifest, kernels=args.kernels, weights=args.weights, gpu=args.gpu, tokens=args.capacity or 0,
+                     slots=getattr(args, "max_seqs", 0) or 0)
+    rt.once()
+    return rt
+
+
+def _weights_path(w):
+    if w is None:
+        return None
+    p = Path(w)
+    if p.is_dir():
+        files = sorted(p.glob("*.safetensors"))
+        if len(files) != 1:
+            from .models.common import read_safetensors
+
+            out = {}
+            for f in files:
+                out.update(read_safetensors(f))
+            return out
+        return files[0]
+    return p
+
+
+# ---- subcommands --------------------------------------------------------------------------------------
+def cmd_verify(args) -> int:
+    from . import _native
+
+    text = Path(args.manifest).read_text()
+    t0 = time.perf_counter()
+    m, errs = _native.verify(text)
+    ms = (time.perf_counter() - t0) * 1e3
+    if m is None:
+        print(f"{args.manifest}: {len(errs)} problem(s)")
+        for e in errs:
+            print("  -", e)
+        return 1
+    print(f"{args.manifest}: verified in {ms:.2f} ms (model `{m.model}`)")
+    try:
+        p = json.loads(m.protocol())
+    except ValueError:
+        try:
+            p = json.loads(m.self_hosted().protocol(sampled=False))
+            print("  (hosted or stage manifest: checked without a token output)")
+        except ValueError as e:
+            print(f"  no serving protocol: {e}")
+            return 0
+    print(f"  rows: `{p['rows']['var']}` <= {p['rows']['max']}   groups: `{p['groups']['var']}` <= {p['groups']['max']}"
+          + (f"   ranks: `{p['ranks']['var']}`" if p.get("ranks") else "") + (f"   context: `{p['context']['var']}`" if p.get("context") else ""))
+    for f in p["fills"]:
+        ax = f["axis"] if isinstance(f["axis"], str) else f"[{f['axis']['fixed']}]"
+        print(f"  fill {f['fill']:12s} {f['name']}  {f['dtype']} over {ax}" + (f" x{f['width']}" if f["width"] != 1 else ""))
+    for t in p["page_tables"]:
+        print(f"  page table {t['name']} [{p['groups']['var']}, {t['width']}] -> {t['state']} (page of {t['stride']})")
+    for t in p["line_tables"]:
+        print(f"  line table {t['name']} lines={t['lines']} -> {t['state']}")
+    for f in p["forwards"]:
+        print(f"  forward {f['name']}: up to {f['groups']} groups x {f['rows']} rows" + (f", emits {f['emits']}" if f["emits"] else "")
+              + (f" (count {f['count']})" if f["count"] else "") + (", graph" if f["graph"] else ""))
+    for name in p["once"]:
+        print(f"  once {name}")
+    for name in p["derive"]:
+        print(f"  derive {name}")
+    return 0
+
+
+def cmd_cut(args) -> int:
+    from . import _native
+
+    m, errs = _native.verify(Path(args.manifest).read_text())
+    if m is None:
+        print("\n".join(errs))
+        return 1
+    try:
+        stages = m.cut([int(x) for x in args.at.split(",")])
+    except ValueError as e:
+        print(e)
+        return 1
+    out = Path(args.out)
+    out.mkdir(parents=True, exist_ok=True)
+    whole = json.loads(m.to_json())
+    for i, s in enumerate(stages):
+        doc = json.loads(s.to_json())
+        (out / f"stage{i}.json").write_text(s.to_json())
+        regions = lambda d, st: len({a.get("offset", 0) for p in d["programs"].values() for c in p["calls"] for a in c["args"] if a.get("state") == st})
+        use = ", ".join(f"{st} {regions(doc, st)}/{regions(whole, st)}" for st in doc["states"])
+        print(f"stage {i}: {sum(len(p['calls']) for p in doc['programs'].values())} calls, {len(doc['buffers'])} buffers, states [{use}]")
+    return 0
+
+
+def cmd_kernels(args) -> int:
+    from .models.common import kernel_index
+
+    for name, e in sorted(kernel_index().items()):
+        print(f"{e['sha256']}  {e['source']}")
+    return 0
+
+
+def _prompt_ids(args, tok=None):
+    if args.prompt_ids:
+        return [int(x) for x in args.prompt_ids.split(",")]
+    from .serve.server import ByteTokenizer, HFTokenizer
+
+    tok = HFTokenizer(args.tokenizer) if args.tokenizer else ByteTokenizer()
+    return tok.encode(args.prompt or "hello")
+
+
+def cmd_run(args) -> int:
+    from .engine import Engine, Sampling
+
+    rt = make_runtime(args)
+    if hasattr(rt, "banner"):
+        print(rt.banner(), file=sys.stderr)
+    eng = Engine(rt)
+    prompt = _prompt_ids(args)
+    t0 = time.perf_counter()
+    toks = eng.generate(prompt, args.steps, chunk=args.chunk, sampling=Sampling(temperature=args.temperature, seed=args.seed))
+    dt = time.perf_counter() - t0
+    print(json.dumps({"prompt_tokens": len(prompt), "tokens": toks, "seconds": round(dt, 4), "tok_s": round(len(toks) / dt, 1)}))
+    return 0
+
+
+def cmd_test(args) -> int:
+    from .testing.abtest import EngineSide, run_test
+
+    a = EngineSide(make_runtime(args, args.a))
+    b = EngineSide(make_runtime(args, args.b))
+    rep = run_test(a, b, seed=args.seed, prompts=args.prompts, decode_steps=args.decode_steps, logit_kl=args.logit_kl, chunk=args.chunk)
+    print(rep.text())
+    return rep.exit_code
+
+
+def load_workload(path: str | None) -> dict:
+    """Workload TOML: samples (12..256), seed, [[sweep]] of groups x (rows | chunk) x context with weights."""
+    if path is None:
+        return {"samples": 12, "seed": 0, "sweep": [{"groups": 1, "rows": 1, "context": 256, "weight": 1.0},
+                                                     {"groups": 1, "chunk": 256, "context": 256, "weight": 1.0}]}
+    w = tomllib.loads(Path(path).read_text())
+    unknown = set(w) - {"samples", "seed", "sweep"}
+    if unknown:
+        raise SystemExit(f"{path}: unknown field(s) {sorted(unknown)}")
+    if not 12 <= w.get("samples", 12) <= 256:
+        raise SystemExit(f"{path}: samples must be 12..=256")
+    return {"samples": w.get("samples", 12), "seed": w.get("seed", 0), "sweep": w.get("sweep", [])}
+
+
+def cmd_bench(args) -> int:
+    """Each sweep point: contexts built once, then `samples` timed calls of the forward program (device-synchronised
+    wall time per call; graph programs replay their captured graph); min / p10 / p50 / p90 / max / cv."""
+    from .engine import Engine
+
+    rt = make_runtime(args)
+    eng = Engine(rt)
+    wl = load_workload(args.workload)
+    import numpy as np
+
+    rng = np.random.default_rng(wl["seed"])
+    report = {"version": 5, "points": []}
+    for pt in wl["sweep"]:
+        g, ctx = int(pt.get("groups", 1)), int(pt.get("context", 64))
+        rows = min(int(pt.get("chunk", pt.get("rows", 1))), eng.rows_max // max(1, g))
+        longest = min((t["width"] * t["stride"] for t in eng.page_tables), default=ctx)
+        ctx = max(rows, min(ctx, longest))          # a context the manifest's page-table row can hold
+        seqs = [eng.open(ctx) for _ in range(g)]
+        if ctx > rows:
+            pre = ctx - rows
+            for i in range(0, pre, eng.rows_max // max(1, g)):
+                n = min(eng.rows_max // max(1, g), pre - i)
+                eng.step([(s, rng.integers(1, 200, n).tolist()) for s in seqs])
+        times = []
+        for k in range(4 + wl["samples"]):                       # WARMUP = 4
+            batch = [(s, rng.integers(1, 200, rows).tolist()) for s in seqs]
+            rt.synchronize()
+            t0 = time.perf_counter()
+            eng.step(batch)
+            rt.synchronize()
+            if k >= 4:
+                times.append((time.perf_counter() - t0) * 1e3)
+            for s in seqs:                                       # rewind: every sample runs at the same context
+                s.length -= rows                                 # (a paged slot is its position: the rows are overwritten)
+                del s.tokens[-rows:]
+        for s in seqs:
+            eng.close(s)
+        times.sort()
+        q = lambda f: times[min(len(times) - 1, int(f * len(times)))]
+        point = {"groups": g, "rows": rows, "context": ctx, "weight": pt.get("weight", 1.0), "min_ms": times[0], "p10_ms": q(0.1),
+                 "p50_ms": q(0.5), "p90_ms": q(0.9), "max_ms": times[-1], "cv": statistics.pstdev(times) / max(1e-9, statistics.mean(times))}
+        report["points"].append(point)
+        print(json.dumps(point))
+    if args.out:
+        Path(args.out).write_text(json.dumps(report, indent=1))
+    return 0
+
+
+def cmd_workload(args) -> int:
+    """steps.parquet of a served run -> a weighted bench workload (buckets of groups x rows x context)."""
+    import pyarrow.parquet as pq
+
+    t = pq.read_table(args.steps).to_pydict()
+    buckets: dict[tuple, float] = {}
+    for g, r, c, ms in zip(t["groups"], t["rows"], t["context"], t.get("device_ms", [1.0] * len(t["groups"]))):
+        key = (int(g), int(r), 1 << max(0, int(c) - 1).bit_length())
+        buckets[key] = buckets.get(key, 0.0) + float(ms)
+    total = sum(buckets.values()) or 1.0
+    lines = [f"samples = {args.samples}", "seed = 0", ""]
+    for (g, r, c), w in sorted(buckets.items(), key=lambda kv: -kv[1]):
+        lines += ["[[sweep]]", f"groups = {g}", (f"rows = {r}" if r <= 16 else f"chunk = {r}"), f"context = {c}", f"weight = {w / total:.4f}", ""]
+    Path(args.out).write_text("\n".join(lines))
+    print(f"{len(buckets)} sweep points -> {args.out}")
+    return 0
+
+
+def cmd_server(args) -> int:
+    import logging
+
+    from .engine import Engine
+    from .serve.scheduler import Scheduler
+    from .serve.server import ByteTokenizer, HFTokenizer, Server
+    from .utils.logline import setup_logging
+
+    setup_logging()
+    rt = make_runtime(args)
+    sched = Scheduler(Engine(rt), chunk=args.chunk, max_seqs=args.max_seqs or None, rows=args.rows)
+    tok = HFTokenizer(args.tokenizer) if args.tokenizer else ByteTokenizer()
+    srv = Server(sched, tok, model_name=rt.doc["model"], host=args.host, port=args.port)
+    logging.getLogger("kern.serve").info("listening host=%s port=%d model=%s", args.host, srv.port, rt.doc["model"])
+    srv.serve_forever()
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="kern", description="manifest-driven inference engine for B200")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    def common(p, manifest=True):
+        if manifest:
+            p.add_argument("--manifest")
+        p.add_argument("--target", help="a [targets.<name>] of kern.toml")
+        p.add_argument("--weights"); p.add_argument("--kernels"); p.add_argument("--tokenizer")
+        p.add_argument("--gpu", type=int); p.add_argument("--capacity", type=int, help="token capacity of the paged states")
+        p.add_argument("--cpu", action="store_true", help="run on the host-memory executor instead of a GPU")
+        p.add_argument("--chunk", type=int); p.add_argument("--max-seqs", type=int, default=0)
+
+    v = sub.add_parser("verify"); v.add_argument("manifest")
+    c = sub.add_parser("cut"); c.add_argument("manifest"); c.add_argument("--at", required=True); c.add_argument("--out", required=True)
+    sub.add_parser("kernels")
+    r = sub.add_parser("run"); common(r)
+    r.add_argument("--prompt"); r.add_argument("--prompt-ids"); r.add_argument("--steps", type=int, default=16)
+    r.add_argument("--temperature", type=float, default=0.0); r.add_argument("--seed", type=int, default=0)
+    t = sub.add_parser("test"); t.add_argument("a"); t.add_argument("b"); common(t, manifest=False)
+    t.add_argument("--seed", type=int, default=0); t.add_argument("--prompts", type=int, default=4)
+    t.add_argument("--decode-steps", type=int, default=8); t.add_argument("--logit-kl", type=float, default=0.01)
+    b = sub.add_parser("bench"); common(b); b.add_argument("--workload"); b.add_argument("--out")
+    w = sub.add_parser("workload"); w.add_argument("steps"); w.add_argument("--out", required=True); w.add_argument("--samples", type=int, default=32)
+    s = sub.add_parser("server"); common(s)
+    s.add_argument("--host", default="127.0.0.1"); s.add_argument("--port", type=int, default=8000); s.add_argument("--rows", type=int)
+    args = ap.parse_args(argv)
+    if args.cmd in ("run", "test", "bench", "server"):
+        path, cfg = find_config()
+        resolve(args, path, cfg)
+        if args.cmd != "test" and not args.manifest:
+            ap.error("--manifest (or a --target of kern.toml) is required")
+    return {"verify": cmd_verify, "cut": cmd_cut, "kernels": cmd_kernels, "run": cmd_run, "test": cmd_test, "bench": cmd_bench,
+            "workload": cmd_workload, "server": cmd_server}[args.cmd](args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,74 @@
+"""`kern` subcommands on the CPU executor: verify (prints the protocol), cut, run, test (A/B verdicts), bench."""
+import dataclasses
+import json
+
+import pytest
+
+from kern_b200 import cli
+from kern_b200.models import common, dense
+
+
+@pytest.fixture(scope="module")
+def pkg(tmp_path_factory):
+    d = tmp_path_factory.mktemp("pkg")
+    cfg = dense.TOY
+    (d / "manifest.json").write_text(json.dumps(dense.build_manifest(cfg)))
+    common.write_safetensors(d / "model.safetensors", dense.random_weights(cfg, seed=0, std=0.05))
+    return d, cfg
+
+
+def test_verify_prints_protocol_and_rejects(pkg, capsys, tmp_path):
+    d, _ = pkg
+    assert cli.main(["verify", str(d / "manifest.json")]) == 0
+    out = capsys.readouterr().out
+    assert "forward decode: up to 4 groups x 1 rows, emits next_token, graph" in out and "fill token" in out and "once load" in out
+    bad = json.loads((d / "manifest.json").read_text())
+    bad["vars"]["tokens"]["max"] = 0
+    (tmp_path / "bad.json").write_text(json.dumps(bad))
+    assert cli.main(["verify", str(tmp_path / "bad.json")]) == 1
+    assert "max must be >= 1" in capsys.readouterr().out
+
+
+def test_run_and_cut(pkg, capsys, tmp_path):
+    d, cfg = pkg
+    assert cli.main(["run", "--cpu", "--manifest", str(d / "manifest.json"), "--weights", str(d), "--prompt-ids", "5,6,7,8", "--steps", "4"]) == 0
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert len(line["tokens"]) == 4
+    # per-layer KV states: a cut between the layers leaves each stage its own
+    n_layer0 = next(i for i, c in enumerate(json.loads((d / "manifest.json").read_text())["programs"]["decode"]["calls"]) if c.get("label") == "l1.ln1")
+    rc = cli.main(["cut", str(d / "manifest.json"), "--at", str(n_layer0), "--out", str(tmp_path / "stages")])
+    out = capsys.readouterr().out
+    # the toy's prefill and decode programs differ in length before the cut point, so this cut may be refused;
+    # either way the command must answer, never crash
+    assert rc in (0, 1) and ("stage 0" in out or "cannot cut" in out)
+
+
+def test_ab_test_verdicts(pkg, capsys, tmp_path):
+    d, cfg = pkg
+    a = d / "manifest.json"
+    assert cli.main(["test", str(a), str(a), "--cpu", "--weights", str(d), "--prompts", "2", "--decode-steps", "3"]) == 0
+    assert "PASS: bit-identical" in capsys.readouterr().out
+    # B: another launch geometry for the norm (an implementation change with identical values)
+    doc = json.loads(a.read_text())
+    doc["ops"]["norm"]["impl"]["launches"][0]["block"] = [128, 1, 1]
+    (tmp_path / "b.json").write_text(json.dumps(doc))
+    assert cli.main(["test", str(a), str(tmp_path / "b.json"), "--cpu", "--weights", str(d), "--prompts", "2", "--decode-steps", "3"]) == 0
+    out = capsys.readouterr().out
+    assert "diff op norm: impl" in out and "PASS" in out
+    # B: a different epsilon in the final norm changes the function -> not bit-identical; tiny eps stays within KL
+    doc2 = json.loads(a.read_text())
+    for l in doc2["ops"]["norm_last"]["impl"]["launches"]:
+        l["args"][7] = {"f32": 0.5}
+    (tmp_path / "c.json").write_text(json.dumps(doc2))
+    rc = cli.main(["test", str(a), str(tmp_path / "c.json"), "--cpu", "--weights", str(d), "--prompts", "2", "--decode-steps", "3"])
+    out = capsys.readouterr().out
+    assert "diff op norm_last: impl" in out and rc in (1, 2) or "logit evidence" in out
+
+
+def test_bench_and_kernels(pkg, capsys):
+    d, _ = pkg
+    assert cli.main(["bench", "--cpu", "--manifest", str(d / "manifest.json"), "--weights", str(d), "--capacity", "1024"]) == 0
+    pts = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert len(pts) == 2 and all(p["p50_ms"] > 0 and p["min_ms"] <= p["p50_ms"] <= p["max_ms"] for p in pts)
+    assert cli.main(["kernels"]) == 0
+    assert "gemm_bf16.cubin" in capsys.readouterr().out
