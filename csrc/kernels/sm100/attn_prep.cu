@@ -18,7 +18,7 @@ extern "C" __global__ void __launch_bounds__(128)
                              const long long* slots, const float* cos_tab, const float* sin_tab,
                              const __nv_bfloat16* q_norm, const __nv_bfloat16* k_norm, int tokens,
                              int hq, int hk, int d, int rot, int page_size, float eps,
-                             int norm_plus_one, long long kv_slots, int max_pos, int* err) {
+                             int norm_plus_one, long long kv_slots, int max_pos, int row_stride, int* err) {
   extern __shared__ float rows[];  // [4][d]
   pdl_wait();
   const int t = blockIdx.x;
@@ -38,7 +38,7 @@ extern "C" __global__ void __launch_bounds__(128)
   const int half = rot >> 1;
   const float* cs = cos_tab + (size_t)pos * half;
   const float* sn = sin_tab + (size_t)pos * half;
-  __nv_bfloat16* base = qkv + (size_t)t * (hq + 2 * hk) * d;
+  __nv_bfloat16* base = qkv + (size_t)t * row_stride;   // a row may carry more than q|k|v (an output gate)
   const long long page = slot >= 0 ? slot / page_size : 0;
   const int off = slot >= 0 ? (int)(slot % page_size) : 0;
   const size_t page_elems = (size_t)2 * hk * page_size * d;

@@ -82,10 +82,10 @@ def a_stride(a, k):
     return getattr(a, "_row_stride", k)
 
 
-def k_rope_append(g, qkv, kv, positions, slots, cos, sin, qn, kn, tokens, hq, hk, d, rot, page, eps, plus_one, kv_slots, max_pos, err):
+def k_rope_append(g, qkv, kv, positions, slots, cos, sin, qn, kn, tokens, hq, hk, d, rot, page, eps, plus_one, kv_slots, max_pos, row_stride, err):
     t = g[0]
     half = rot // 2
-    rows = qkv[: t * (hq + 2 * hk) * d].view(t, hq + 2 * hk, d)
+    rows = qkv[: t * row_stride].view(t, row_stride)[:, : (hq + 2 * hk) * d].unflatten(1, (hq + 2 * hk, d))
     pos = positions[:t].long().clamp(0, max_pos - 1)
     c, s = cos.view(-1, half)[pos][:, None], sin.view(-1, half)[pos][:, None]
     pool = kv.view(torch.bfloat16).view(-1, 2, hk, page, d)
@@ -194,6 +194,63 @@ def k_silu_mul(g, x, out, tokens, d):
     out[: t * d] = (torch.nn.functional.silu(xv[:, :d]) * xv[:, d:]).reshape(-1).to(out.dtype)
 
 
+def k_sigmoid_mul(g, x, gate, out, tokens, d, xs, gs):
+    t = g[0]
+    xv = _f(torch.as_strided(x, (t, d), (xs, 1), x.storage_offset()))
+    gv = _f(torch.as_strided(gate, (t, d), (gs, 1), gate.storage_offset()))
+    res = (xv * torch.sigmoid(gv)).to(out.dtype)
+    out[: t * d] = res.reshape(-1)
+
+
+def _rows_of(cu, s):
+    return (int(cu[s]), int(cu[s + 1])) if isinstance(cu, torch.Tensor) else (s, s + 1)
+
+
+def k_gdn_conv(g, x, y, state, lines, cu, w, bias, seqs, conv_dim, width, x_stride, line_bytes):
+    from .ops import gdn as G
+
+    wt = _f(w[: conv_dim * width].view(conv_dim, width))
+    for s in range(g[0]):
+        r0, r1 = _rows_of(cu, s)
+        if r1 <= r0:
+            continue
+        ln = int(lines[s])
+        win = state[ln * line_bytes: ln * line_bytes + (width - 1) * conv_dim * 2].view(torch.bfloat16).view(width - 1, conv_dim)
+        hist = _f(win) if ln > 0 else torch.zeros(width - 1, conv_dim)
+        xs = _f(torch.as_strided(x, (r1 - r0, conv_dim), (x_stride, 1), x.storage_offset() + r0 * x_stride))
+        out, new = G.conv_ref(xs, hist, wt, _f(bias[:conv_dim]) if isinstance(bias, torch.Tensor) else None)
+        y[r0 * conv_dim: r1 * conv_dim] = out.to(torch.bfloat16).reshape(-1)
+        if ln > 0:
+            win.copy_(new.to(torch.bfloat16))
+
+
+def _gdn_rule(dim):
+    def run(g, qkv, zba, out, state, lines, cu, A_log, dt_bias, norm_w, seqs, hk, hv, zba_stride, z_off, b_off, a_off,
+            line_bytes, s_off, eps):
+        from .ops import gdn as G
+
+        conv_dim = 2 * hk * dim + hv * dim
+        for s in range(g[1]):
+            r0, r1 = _rows_of(cu, s)
+            n = r1 - r0
+            if n <= 0:
+                continue
+            ln = int(lines[s])
+            Sb = state[ln * line_bytes + s_off: ln * line_bytes + s_off + hv * dim * dim * 4].view(torch.float32).view(hv, dim, dim)
+            S0 = Sb.clone() if ln > 0 else torch.zeros(hv, dim, dim)
+            rows = _f(qkv[r0 * conv_dim: r1 * conv_dim].view(n, conv_dim))
+            zr = _f(torch.as_strided(zba, (n, a_off + hv), (zba_stride, 1), zba.storage_offset() + r0 * zba_stride))
+            q = rows[:, :hk * dim].view(n, hk, dim)
+            k = rows[:, hk * dim:2 * hk * dim].view(n, hk, dim)
+            v = rows[:, 2 * hk * dim:].view(n, hv, dim)
+            o, S1 = G.rule_ref(q, k, v, zr[:, z_off:z_off + hv * dim].reshape(n, hv, dim), zr[:, b_off:b_off + hv],
+                               zr[:, a_off:a_off + hv], S0, A_log[:hv], dt_bias[:hv], norm_w[:dim], eps)
+            out[r0 * hv * dim: r1 * hv * dim] = o.to(torch.bfloat16).reshape(-1)
+            if ln > 0:
+                Sb.copy_(S1)
+    return run
+
+
 def k_copy_rows(g, src, dst, idx, rows, row_bytes, ss, ds):
     r = g[0]
     s8, d8 = src.view(torch.uint8), dst.view(torch.uint8)
@@ -215,7 +272,9 @@ CPU_KERNELS = {
     "kern_attn_plan": k_noop, "kern_attn_merge_splits": k_noop,
     "kern_last_row": k_last_row, "kern_argmax_partial_bf16": k_argmax_partial, "kern_argmax_partial_f32": k_argmax_partial,
     "kern_argmax_final_i64": k_argmax_final, "kern_sample_bf16": k_sample, "kern_sample_f32": k_sample,
-    "kern_silu_mul_bf16": k_silu_mul, "kern_copy_rows": k_copy_rows,
+    "kern_silu_mul_bf16": k_silu_mul, "kern_copy_rows": k_copy_rows, "kern_sigmoid_mul_bf16": k_sigmoid_mul,
+    "kern_gdn_conv_bf16": k_gdn_conv, "kern_gdn_rule_k128_v128": _gdn_rule(128), "kern_gdn_rule_k64_v64": _gdn_rule(64),
+    "kern_gdn_rule_k32_v32": _gdn_rule(32),
     "kern_fill_f32": k_fill, "kern_fill_i32": k_fill, "kern_fill_i64": k_fill, "kern_fill_u8": k_fill,
 }
 for _bn in (256, 128, 64, 32):

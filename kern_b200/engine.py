@@ -161,6 +161,12 @@ class Engine:
                 m = min(len(ids), w)
                 rows[i, :m] = np.asarray(ids[:m], np.int32) // per if per > 1 else ids[:m]
             self._write(t["name"], "i32", rows.reshape(-1))
+        for t in self.p.get("line_tables", []):
+            # [lines, groups(, w)]: line 0 of a sequence is its own state slot; the rest stay null (0)
+            rows = np.zeros((t["lines"], b, t["width"]), np.int32)
+            for i, (s, _) in enumerate(batch):
+                rows[0, i, 0] = max(0, s.lease.slot)
+            self._write(t["name"], "i32", rows.reshape(-1))
         vars_ = {self.p["rows"]["var"]: total, self.p["groups"]["var"]: b}
         if self.p.get("ranks"):
             vars_[self.p["ranks"]["var"]] = total

@@ -169,7 +169,7 @@ def embedding_op(hidden: int, vocab: int, ids_dtype: str = "i64") -> dict:
 
 
 def rope_append_op(hq: int, hk: int, d: int, rot: int, page_size: int, max_pos: int, eps: float,
-                   qk_norm: bool, norm_plus_one: bool = False) -> dict:
+                   qk_norm: bool, norm_plus_one: bool = False, row_stride: int | None = None) -> dict:
     """Interface [qkv, kv state, positions, slots, cos, sin, (q_norm, k_norm,) err]."""
     iface = ["inout buffer<bf16>", "inout state", "in buffer<i64>", "in buffer<i64>", "in buffer<f32>", "in buffer<f32>"]
     lp = list(iface)
@@ -182,9 +182,10 @@ def rope_append_op(hq: int, hk: int, d: int, rot: int, page_size: int, max_pos: 
         lp += ["i64", "i64"]
         args += [{"i64": 0}, {"i64": 0}]
     iface.append("out buffer<i32>")
-    lp += ["i32"] * 6 + ["f32", "i32", "i64", "i32", "out buffer<i32>"]
+    lp += ["i32"] * 6 + ["f32", "i32", "i64", "i32", "i32", "out buffer<i32>"]
     args += [{"i32": I32_MAX}, {"i32": hq}, {"i32": hk}, {"i32": d}, {"i32": rot}, {"i32": page_size}, {"f32": eps},
-             {"i32": int(norm_plus_one)}, {"i64": I64_MAX}, {"i32": max_pos}, {"param": len(iface) - 1}]
+             {"i32": int(norm_plus_one)}, {"i64": I64_MAX}, {"i32": max_pos},
+             {"i32": row_stride or (hq + 2 * hk) * d}, {"param": len(iface) - 1}]
     return {"params": iface, "impl": {"launches": [{
         "module": "attn_prep", "entry": "kern_rope_kv_append_bf16", "block": [128, 1, 1], "grid": ["tokens", 1, 1],
         "shared_mem": 4 * d * 4, "params": lp, "args": args}]}}
@@ -406,3 +407,70 @@ def tp_buffers(hidden: int, nranks: int, rows_max: int, group: str = "tp") -> di
         "tp.flags_peers": {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": "tp.flags", "group": group},
         "tp.epochs": {"dtype": "u32", "shape": [TP_GRID], "kind": "carry"},
     }
+
+
+# ---- gated DeltaNet (hybrid decoders) ----------------------------------------------------------------
+def gdn_line_bytes(hk: int, hv: int, dk: int, dv: int, width: int = 4) -> tuple[int, int]:
+    """(bytes of one per-sequence state line, offset of the recurrent matrix in it)."""
+    conv = (width - 1) * (2 * hk * dk + hv * dv) * 2
+    s_off = (conv + 255) // 256 * 256
+    return s_off + hv * dv * dk * 4, s_off
+
+
+def gdn_conv_op(conv_dim: int, width: int, x_stride: int, line_bytes: int, ragged: bool) -> dict:
+    """Causal conv + SiLU over the first `conv_dim` channels of a row, window kept in the state line.
+    Interface [x, y, state, lines, (cu_seqlens,) w]."""
+    iface = ["in buffer<bf16>", "out buffer<bf16>", "inout state", "in buffer<i32>"]
+    lp = list(iface)
+    args = [{"param": i} for i in range(4)]
+    if ragged:
+        iface.append("in buffer<i32>")
+        lp.append("in buffer<i32>")
+        args.append({"param": 4})
+    else:
+        lp.append("i64")
+        args.append({"i64": 0})
+    iface.append("in buffer<bf16>")
+    w_at = len(iface) - 1
+    lp += ["in buffer<bf16>", "i64", "i32", "i32", "i32", "i32", "i64"]
+    args += [{"param": w_at}, {"i64": 0}, {"i32": I32_MAX}, {"i32": conv_dim}, {"i32": width}, {"i32": x_stride},
+             {"i64": line_bytes}]
+    return {"params": iface, "impl": {"launches": [{
+        "module": "gdn", "entry": "kern_gdn_conv_bf16", "block": [256, 1, 1], "grid": ["seqs", -(-conv_dim // 256), 1],
+        "params": lp, "args": args}]}}
+
+
+def gdn_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_off: int, eps: float,
+                ragged: bool) -> dict:
+    """Gated delta rule + gated RMSNorm. Interface [qkv, zba, out, state, lines, (cu_seqlens,) A_log, dt_bias, norm_w].
+    `zba` points at the z|b|a columns of the projection's row."""
+    iface = ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "inout state", "in buffer<i32>"]
+    lp = list(iface)
+    args = [{"param": i} for i in range(5)]
+    if ragged:
+        iface.append("in buffer<i32>")
+        lp.append("in buffer<i32>")
+        args.append({"param": 5})
+    else:
+        lp.append("i64")
+        args.append({"i64": 0})
+    at = len(iface)
+    iface += ["in buffer<f32>", "in buffer<f32>", "in buffer<bf16>"]
+    lp += ["in buffer<f32>", "in buffer<f32>", "in buffer<bf16>"] + ["i32"] * 7 + ["i64", "i64", "f32"]
+    args += [{"param": at}, {"param": at + 1}, {"param": at + 2}, {"i32": I32_MAX}, {"i32": hk}, {"i32": hv},
+             {"i32": zba_stride}, {"i32": 0}, {"i32": hv * dim}, {"i32": hv * dim + hv}, {"i64": line_bytes},
+             {"i64": s_off}, {"f32": eps}]
+    smem = (dim * (dim + 256 // dim) + 2 * dim + dim) * 4
+    return {"params": iface, "impl": {"launches": [{
+        "module": "gdn", "entry": f"kern_gdn_rule_k{dim}_v{dim}", "block": [256, 1, 1], "grid": [hv, "seqs", 1],
+        "shared_mem": smem, "params": lp, "args": args}]}}
+
+
+def sigmoid_mul_op(d: int, x_stride: int, gate_stride: int) -> dict:
+    """out[t, :d] = x[t, :d] * sigmoid(gate[t, :d]). Interface [x, gate, out]."""
+    return {"params": ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>"], "impl": {"launches": [{
+        "module": "norm_embed", "entry": "kern_sigmoid_mul_bf16", "block": [256, 1, 1],
+        "grid": ["tokens", max(1, -(-d // 256)), 1],
+        "params": ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "i32", "i32", "i32", "i32"],
+        "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"i32": I32_MAX}, {"i32": d}, {"i32": x_stride},
+                 {"i32": gate_stride}]}]}}

@@ -35,14 +35,14 @@ def rope_kv_append(qkv: torch.Tensor, pool: torch.Tensor, positions: torch.Tenso
     k = Kernels.get(qkv.device)
     t = qkv.shape[0] if tokens is None else tokens
     pages, two, hk_, page_size, d_ = pool.shape
-    assert two == 2 and hk_ == hk and d_ == d and qkv.shape[1] == (hq + 2 * hk) * d and d % 8 == 0
+    assert two == 2 and hk_ == hk and d_ == d and qkv.shape[1] >= (hq + 2 * hk) * d and d % 8 == 0 and qkv.stride(1) == 1
     assert positions.dtype == torch.int64 and slots.dtype == torch.int64
     rot = d if rot is None else rot
     assert cos.shape[1] == rot // 2
     k.launch("attn_prep", "kern_rope_kv_append_bf16", (t,), (128,),
              [ptr(qkv), ptr(pool), ptr(positions), ptr(slots), ptr(cos), ptr(sin), ptr(q_norm),
               ptr(k_norm), i32(t), i32(hq), i32(hk), i32(d), i32(rot), i32(page_size), f32(eps),
-              i32(int(norm_plus_one)), i64(pages * page_size), i32(cos.shape[0]), ptr(k.err_word())],
+              i32(int(norm_plus_one)), i64(pages * page_size), i32(cos.shape[0]), i32(qkv.stride(0)), ptr(k.err_word())],
              shared_mem=4 * d * 4)
 
 

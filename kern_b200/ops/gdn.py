@@ -1,0 +1,79 @@
+"""Gated DeltaNet: wrappers for the causal conv and the gated delta rule kernels, and their PyTorch
+fp32 statement (the oracle the GPU tests and the CPU executor use).
+
+State line of one sequence for one layer: ``[(width-1) x conv_dim bf16 | HV x DV x DK f32]``; line 0 is null.
+Reference counterpart of the decode step: tools/kernels-src/gdn_decode.cu:90, :171.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .launcher import Kernels, f32, i32, i64, ptr
+
+NULL = 0
+
+
+def line_bytes(hk: int, hv: int, dk: int, dv: int, width: int = 4) -> tuple[int, int]:
+    """(bytes of one state line, byte offset of S inside it); S starts 256-byte aligned."""
+    conv = (width - 1) * (2 * hk * dk + hv * dv) * 2
+    s_off = (conv + 255) // 256 * 256
+    return s_off + hv * dv * dk * 4, s_off
+
+
+def rule_smem(dk: int, dv: int) -> int:
+    return (dv * (dk + 256 // dv) + 2 * dk + dv) * 4
+
+
+def conv(x, y, state, lines, cu_q, w, bias, seqs, conv_dim, width, line_b):
+    k = Kernels.get(x.device)
+    k.launch("gdn", "kern_gdn_conv_bf16", (seqs, (conv_dim + 255) // 256), (256,),
+             [ptr(x), ptr(y), ptr(state), ptr(lines), ptr(cu_q), ptr(w), ptr(bias), i32(seqs), i32(conv_dim),
+              i32(width), i32(x.stride(0)), i64(line_b)])
+    return y
+
+
+def rule(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv, z_off, b_off, a_off,
+         line_b, s_off, eps=1e-6):
+    k = Kernels.get(qkv.device)
+    assert dk == dv and dk in (32, 64, 128)
+    k.launch("gdn", f"kern_gdn_rule_k{dk}_v{dv}", (hv, seqs), (256,),
+             [ptr(qkv), ptr(zba), ptr(out), ptr(state), ptr(lines), ptr(cu_q), ptr(A_log), ptr(dt_bias), ptr(norm_w),
+              i32(seqs), i32(hk), i32(hv), i32(zba.stride(0)), i32(z_off), i32(b_off), i32(a_off), i64(line_b),
+              i64(s_off), f32(eps)], shared_mem=rule_smem(dk, dv))
+    return out
+
+
+# ---- fp32 statement ------------------------------------------------------------------------------------
+def conv_ref(x, window, w, bias=None):
+    """x: [T, C] f32 rows of one sequence, window: [width-1, C] (history, oldest first), w: [C, width].
+    Returns (silu(conv) [T, C], new window)."""
+    width = w.shape[1]
+    full = torch.cat([window.float(), x.float()], 0)                      # [T + width - 1, C]
+    y = sum(full[j:j + x.shape[0]] * w[:, j].float() for j in range(width))
+    if bias is not None:
+        y = y + bias.float()
+    return F.silu(y), full[full.shape[0] - (width - 1):].clone()
+
+
+def rule_ref(q, k, v, z, b, a, S, A_log, dt_bias, norm_w, eps=1e-6):
+    """One sequence: q,k [T, HK, DK]; v,z [T, HV, DV]; b,a [T, HV]; S [HV, DV, DK] f32 (updated copy returned)."""
+    T, hk, dk = q.shape
+    hv, dv = v.shape[1], v.shape[2]
+    rep = hv // hk
+    q = q.float() * torch.rsqrt(q.float().pow(2).sum(-1, keepdim=True) + 1e-6)
+    k = k.float() * torch.rsqrt(k.float().pow(2).sum(-1, keepdim=True) + 1e-6)
+    q = (q / dk ** 0.5).repeat_interleave(rep, 1)
+    k = k.repeat_interleave(rep, 1)
+    g = -torch.exp(A_log.float()) * F.softplus(a.float() + dt_bias.float())          # [T, HV]
+    beta = torch.sigmoid(b.float()).to(torch.bfloat16).float()
+    S = S.float().clone()
+    out = torch.empty(T, hv, dv, dtype=torch.float32, device=q.device)
+    for t in range(T):
+        S = S * torch.exp(g[t])[:, None, None]
+        sk = torch.einsum("hvk,hk->hv", S, k[t])
+        u = (v[t].float() - sk) * beta[t][:, None]
+        S = S + u[:, :, None] * k[t][:, None, :]
+        out[t] = torch.einsum("hvk,hk->hv", S, q[t])
+    y = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float() * F.silu(z.float())
+    return y, S

@@ -82,13 +82,20 @@ class Runtime:
         ranks = lambda g: self._rt.rank(g)
         pick = lambda t: t if isinstance(t, str) else t["tensors"][ranks(t["group"])]
         rng = lambda r, whole: (0, whole) if r is None else (tuple(r) if isinstance(r, list) else tuple(r["ranges"][ranks(r["group"])]))
+        last = [None, None]          # consecutive segments of one tensor (row ranges) fetch it once
+
+        def fetch(n):
+            if last[0] != n:
+                last[0], last[1] = n, provider(n)
+            return last[1]
+
         for name, b in self.doc["buffers"].items():
             if b["kind"] not in ("weight", "source") or b.get("placement") == "host":
                 continue
             dst = self.tensor(name).view(-1)
             at = 0
             for seg in b["bind"]:
-                t = provider(pick(seg["tensor"]))
+                t = fetch(pick(seg["tensor"]))
                 t2 = t.reshape(t.shape[0], -1) if t.dim() > 1 else t.reshape(-1, 1)
                 if "interleave" in seg:
                     u = provider(pick(seg["interleave"]["with"])).reshape(t2.shape)

@@ -1,0 +1,98 @@
+"""Gated DeltaNet kernels (causal conv + SiLU, gated delta rule) against the PyTorch fp32 statement:
+ragged prefill chunks, then decode rows continuing from the stored state, with a padding (null-line) row."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def bf(x):
+    return x.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("hk,hv,d", [(2, 4, 32), (2, 6, 64), (4, 12, 128)])
+def test_gdn_prefill_then_decode(cuda, hk, hv, d):
+    from kern_b200.ops import gdn
+    from kern_b200.ops.launcher import Kernels
+
+    torch.manual_seed(hk * 100 + d)
+    width, dk, dv = 4, d, d
+    conv_dim = 2 * hk * dk + hv * dv
+    zba_dim = hv * dv + 2 * hv
+    x_stride = conv_dim + zba_dim
+    lb, s_off = gdn.line_bytes(hk, hv, dk, dv, width)
+    lens = [13, 1, 40]
+    seqs = len(lens)
+    lines_n = 6
+    state = torch.zeros(lines_n, lb, dtype=torch.uint8, device=cuda)
+    lines = torch.tensor([3, 1, 5], dtype=torch.int32, device=cuda)
+    w = bf(torch.randn(conv_dim, width, device=cuda) * 0.5)
+    bias = bf(torch.randn(conv_dim, device=cuda) * 0.1)
+    A_log = torch.randn(hv, device=cuda) * 0.5
+    dt_bias = torch.randn(hv, device=cuda) * 0.5
+    norm_w = bf(1 + 0.1 * torch.randn(dv, device=cuda))
+
+    ref_win = [torch.zeros(width - 1, conv_dim, device=cuda) for _ in lens]
+    ref_S = [torch.zeros(hv, dv, dk, device=cuda) for _ in lens]
+
+    def run(rows_per_seq, decode):
+        T = sum(rows_per_seq)
+        x = bf(torch.randn(T, x_stride, device=cuda))
+        cu = torch.tensor([0] + list(torch.tensor(rows_per_seq).cumsum(0)), dtype=torch.int32, device=cuda)
+        y = torch.empty(T, conv_dim, dtype=torch.bfloat16, device=cuda)
+        out = torch.empty(T, hv * dv, dtype=torch.bfloat16, device=cuda)
+        cu_arg = None if decode else cu
+        gdn.conv(x, y, state, lines, cu_arg, w, bias, seqs, conv_dim, width, lb)
+        zba = x[:, conv_dim:]
+        gdn.rule(y, zba, out, state, lines, cu_arg, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv,
+                 0, hv * dv, hv * dv + hv, lb, s_off)
+        torch.cuda.synchronize()
+        Kernels.get(cuda).check_error()
+        for s, n in enumerate(rows_per_seq):
+            r0 = int(cu[s])
+            xs = x[r0:r0 + n].float()
+            yr, ref_win[s] = gdn.conv_ref(xs[:, :conv_dim], ref_win[s], w, bias)
+            torch.testing.assert_close(y[r0:r0 + n].float(), yr, rtol=2e-2, atol=2e-2)
+            yb = y[r0:r0 + n].float()          # the rule kernel reads the bf16 conv output
+            q = yb[:, :hk * dk].view(n, hk, dk)
+            k = yb[:, hk * dk:2 * hk * dk].view(n, hk, dk)
+            v = yb[:, 2 * hk * dk:].view(n, hv, dv)
+            z = xs[:, conv_dim:conv_dim + hv * dv].view(n, hv, dv)
+            b = xs[:, conv_dim + hv * dv:conv_dim + hv * dv + hv]
+            a = xs[:, conv_dim + hv * dv + hv:]
+            o, ref_S[s] = gdn.rule_ref(q, k, v, z, b, a, ref_S[s], A_log, dt_bias, norm_w)
+            torch.testing.assert_close(out[r0:r0 + n].float().view(n, hv, dv), o, rtol=3e-2, atol=3e-2)
+            ln = int(lines[s])
+            S_dev = state[ln, s_off:].view(torch.float32).view(hv, dv, dk)
+            torch.testing.assert_close(S_dev, ref_S[s], rtol=1e-3, atol=1e-3)
+            win_dev = state[ln, :(width - 1) * conv_dim * 2].view(torch.bfloat16).view(width - 1, conv_dim)
+            torch.testing.assert_close(win_dev.float(), bf(ref_win[s]).float(), rtol=0, atol=0)
+
+    run(lens, decode=False)
+    for _ in range(3):
+        run([1, 1, 1], decode=True)
+    # untouched lines (0 = null, 2, 4) stayed zero
+    for ln in (0, 2, 4):
+        assert int(state[ln].count_nonzero()) == 0
+
+
+def test_gdn_null_line_is_read_as_zero_and_never_written(cuda):
+    from kern_b200.ops import gdn
+
+    hk, hv, d, width = 2, 4, 64, 4
+    conv_dim = 2 * hk * d + hv * d
+    lb, s_off = gdn.line_bytes(hk, hv, d, d, width)
+    state = torch.full((2, lb), 0x3c, dtype=torch.uint8, device=cuda)      # garbage in the null line
+    lines = torch.zeros(2, dtype=torch.int32, device=cuda)
+    x = bf(torch.randn(2, conv_dim + hv * d + 2 * hv, device=cuda))
+    y = torch.empty(2, conv_dim, dtype=torch.bfloat16, device=cuda)
+    out = torch.empty(2, hv * d, dtype=torch.bfloat16, device=cuda)
+    w = bf(torch.randn(conv_dim, width, device=cuda))
+    gdn.conv(x, y, state, lines, None, w, None, 2, conv_dim, width, lb)
+    gdn.rule(y, x[:, conv_dim:], out, state, lines, None, torch.zeros(hv, device=cuda), torch.zeros(hv, device=cuda),
+             bf(torch.ones(d, device=cuda)), 2, hk, hv, d, d, 0, hv * d, hv * d + hv, lb, s_off)
+    torch.cuda.synchronize()
+    assert bool((state == 0x3c).all())
+    yr, _ = gdn.conv_ref(x[:1, :conv_dim].float(), torch.zeros(width - 1, conv_dim, device=cuda), w)
+    torch.testing.assert_close(y[:1].float(), yr, rtol=2e-2, atol=2e-2)
+    assert bool(torch.isfinite(out.float()).all())
