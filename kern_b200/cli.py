@@ -59,6 +59,23 @@ def resolve(args, cfg_path, cfg) -> None:
 
 def make_runtime(args, manifest=None):
     manifest = manifest or args.manifest
+    model = getattr(args, "model", None)
+    if model and not manifest:
+        from .models import registry
+
+        over = {k: getattr(args, k, None) or None for k in ("layers", "max_tokens", "max_seqs", "max_context")}
+        cfg, build, load, make = registry.resolve(model, **over)
+        if args.cpu:
+            from .cpu import CpuRuntime
+
+            rt = CpuRuntime(build(cfg), weights=make(cfg), tokens=args.capacity or 4096, slots=cfg.max_seqs)
+        else:
+            from .runtime import Runtime
+
+            rt = Runtime(build(cfg), kernels=args.kernels, gpu=args.gpu, tokens=args.capacity or 0, slots=cfg.max_seqs)
+            load(rt, cfg)
+        rt.once()
+        return rt
     if args.cpu:
         from .cpu import CpuRuntime
 
@@ -307,6 +324,8 @@ def main(argv=None) -> int:
         p.add_argument("--gpu", type=int); p.add_argument("--capacity", type=int, help="token capacity of the paged states")
         p.add_argument("--cpu", action="store_true", help="run on the host-memory executor instead of a GPU")
         p.add_argument("--chunk", type=int); p.add_argument("--max-seqs", type=int, default=0)
+        p.add_argument("--model", help="a built-in model family with random-init weights instead of --manifest/--weights")
+        p.add_argument("--layers", type=int); p.add_argument("--max-tokens", type=int); p.add_argument("--max-context", type=int)
 
     v = sub.add_parser("verify"); v.add_argument("manifest")
     c = sub.add_parser("cut"); c.add_argument("manifest"); c.add_argument("--at", required=True); c.add_argument("--out", required=True)
@@ -325,8 +344,8 @@ def main(argv=None) -> int:
     if args.cmd in ("run", "test", "bench", "server"):
         path, cfg = find_config()
         resolve(args, path, cfg)
-        if args.cmd != "test" and not args.manifest:
-            ap.error("--manifest (or a --target of kern.toml) is required")
+        if args.cmd != "test" and not args.manifest and not getattr(args, "model", None):
+            ap.error("--manifest, --model or a --target of kern.toml is required")
     return {"verify": cmd_verify, "cut": cmd_cut, "kernels": cmd_kernels, "run": cmd_run, "test": cmd_test, "bench": cmd_bench,
             "workload": cmd_workload, "server": cmd_server}[args.cmd](args)
 

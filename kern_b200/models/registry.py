@@ -1,0 +1,28 @@
+"""Model families by name: ``name -> (config, manifest builder, synthetic-weights loader)``.
+
+``kern run|bench|server --model NAME`` builds the manifest in memory and fills the weights with the family's
+random-init checkpoint on the device (no files), which is how the benchmarks run without a network."""
+from __future__ import annotations
+
+import dataclasses
+
+
+def families() -> dict:
+    from . import dense, hybrid
+
+    out = {}
+    for cfg in (dense.TOY, dense.TINY, dense.DENSE_8B):
+        out[cfg.name] = (cfg, dense.build_manifest, dense.load_random_weights, dense.random_weights)
+    for cfg in (hybrid.TOY_HYBRID, hybrid.TINY_HYBRID, hybrid.HYBRID_27B):
+        out[cfg.name] = (cfg, hybrid.build_manifest, hybrid.load_random_weights, hybrid.random_weights)
+    return out
+
+
+def resolve(name: str, **overrides):
+    """-> (config with overrides applied, builder, device loader, host weights maker)."""
+    fam = families()
+    if name not in fam:
+        raise KeyError(f"unknown model `{name}`; known: {', '.join(sorted(fam))}")
+    cfg, build, load, make = fam[name]
+    overrides = {k: v for k, v in overrides.items() if v is not None}
+    return dataclasses.replace(cfg, **overrides), build, load, make
