@@ -8,8 +8,8 @@
 //   q = l2norm(q) / sqrt(DK);  k = l2norm(k);  g = -exp(A_log[hv]) * softplus(a + dt_bias[hv]);  beta = sigmoid(b)
 //   S *= exp(g);  u = (v - S k) * beta;  S += u k^T;  o = S q;  y = rmsnorm(o) * w * silu(z)
 // Reference counterpart: tools/kernels-src/gdn_decode.cu:90 (conv), :171 (step) — decode only; the
-// reference takes chunked prefill as a mined kernel. Here one kernel body serves both: the state tile
-// lives in shared memory for the whole chunk of a sequence, tokens are walked in order.
+// reference takes chunked prefill as a mined kernel. Here one kernel body serves both: a CTA keeps its
+// sixteen state rows in registers for the whole chunk of a sequence and walks the tokens in order.
 #include "common.cuh"
 
 using namespace kern;
@@ -49,115 +49,145 @@ extern "C" __global__ void __launch_bounds__(256)
 
 // ---- gated delta rule ---------------------------------------------------------------------------------
 // qkv: conv output [tokens][conv_dim] laid out [q: HK*DK | k: HK*DK | v: HV*DV]
-// zba: [tokens][zba_stride] with z at z_off (HV*DV), b at b_off (HV), a at a_off (HV)   (bf16)
-// out: [tokens][HV*DV] bf16.  A_log, dt_bias: f32 [HV].  norm_w: bf16 [DV].
-// grid [HV, seqs], block 256, dyn smem = (DV * (DK + 256 / DV) + 2 * DK + DV) * 4 bytes.
-// 256 / DV threads share a value row, each taking every (256 / DV)-th key column.
+// zba: [tokens][zba_stride] with b at b_off (HV), a at a_off (HV)   (bf16)
+// o_raw: [tokens][HV*DV] f32, the un-normalised output S q (kern_gdn_gate_norm_bf16 finishes it).
+// A_log, dt_bias: f32 [HV].
+//
+// Every value row of S has its own recurrence (u[v] = beta (v[v] - S[v,:] k); S[v,:] += u[v] k), so a head is
+// split over DV / 16 CTAs of 16 rows each: grid [HV * DV/16, seqs], block 256. Sixteen lanes share a row, each
+// keeping DK/16 state elements in registers for the whole chunk of the sequence: the token loop touches no
+// shared-memory state and has no block barrier, only two 16-lane shuffle reductions per token. Tokens are
+// staged 32 at a time: q and k are loaded, l2-normalised (one warp per token) and parked in shared memory
+// together with v, the decay and beta of those tokens.
+constexpr int GDN_ROWS = 16;   // value rows per CTA
+constexpr int GDN_TB = 32;     // tokens per staged batch
+
 template <int DK, int DV>
-__device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, __nv_bfloat16* out, uint8_t* state,
+__device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, float* o_raw, uint8_t* state,
                                          const int* lines, const int* cu_q, const float* A_log, const float* dt_bias,
-                                         const __nv_bfloat16* norm_w, int seqs, int hk, int hv, int zba_stride, int z_off,
-                                         int b_off, int a_off, long long line_bytes, long long s_offset, float eps) {
-  extern __shared__ float sm[];
-  constexpr int TPR = 256 / DV;       // threads per value row
-  constexpr int KPT = DK / TPR;       // k elements per thread (interleaved: k = j * TPR + part)
-  constexpr int LD = DK + TPR;        // row stride = TPR mod 32 banks: a warp's 32 (row, part) pairs hit 32 banks
-  float* S = sm;                      // [DV][LD]
-  float* qs = S + DV * LD;            // [DK]
-  float* ks = qs + DK;               // [DK]
-  float* os = ks + DK;               // [DV] output before the norm
-  __shared__ float red[32];
-  const int h = blockIdx.x, s = blockIdx.y;
+                                         int seqs, int hk, int hv, int zba_stride, int b_off, int a_off,
+                                         long long line_bytes, long long s_offset) {
+  constexpr int TPR = 256 / GDN_ROWS;   // 16 lanes per value row
+  constexpr int KPT = DK / TPR;         // state elements per thread (k = j * TPR + part)
+  static_assert(KPT >= 1 && DV % GDN_ROWS == 0, "shape");
+  __shared__ float qs[GDN_TB][DK];
+  __shared__ float ks[GDN_TB][DK];
+  __shared__ float vs[GDN_TB][GDN_ROWS];
+  __shared__ float decays[GDN_TB];
+  __shared__ float betas[GDN_TB];
+  constexpr int PARTS = DV / GDN_ROWS;
+  const int h = blockIdx.x / PARTS, row0 = (blockIdx.x % PARTS) * GDN_ROWS, s = blockIdx.y;
   if (s >= seqs) return;
   const int line = lines[s];
   const int r0 = cu_q ? cu_q[s] : s, r1 = cu_q ? cu_q[s + 1] : s + 1;
   if (r1 <= r0) return;
   const int kh = h / (hv / hk);
   const int conv_dim = 2 * hk * DK + hv * DV;
-  float* Sg = reinterpret_cast<float*>(state + (size_t)line * line_bytes + s_offset) + (size_t)h * DV * DK;
-  const int tid = threadIdx.x;
-  for (int i = tid; i < DV * DK; i += 256) S[(i / DK) * LD + (i % DK)] = line > 0 ? Sg[i] : 0.f;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int vrow = tid / TPR, kpart = tid % TPR;
+  float* Sg = reinterpret_cast<float*>(state + (size_t)line * line_bytes + s_offset) +
+              ((size_t)h * DV + row0 + vrow) * DK;
+  float S[KPT];
+#pragma unroll
+  for (int j = 0; j < KPT; ++j) S[j] = line > 0 ? Sg[j * TPR + kpart] : 0.f;
   const float a_neg = -__expf(A_log[h]);
   const float dtb = dt_bias[h];
-  const int warp = tid >> 5, lane = tid & 31;
-  __syncthreads();
-  for (int r = r0; r < r1; ++r) {
-    const __nv_bfloat16* row = qkv + (size_t)r * conv_dim;
-    // q, k with l2 norm (all threads cooperate: DK <= 256)
-    float qv = 0.f, kv = 0.f;
-    if (tid < DK) {
-      qv = __bfloat162float(row[kh * DK + tid]);
-      kv = __bfloat162float(row[hk * DK + kh * DK + tid]);
-    }
-    float q2 = warp_sum(qv * qv), k2 = warp_sum(kv * kv);
-    if (lane == 0) { red[warp] = q2; red[8 + warp] = k2; }
-    __syncthreads();
-    float qn = 0.f, kn = 0.f;
-    for (int i = 0; i < 8; ++i) { qn += red[i]; kn += red[8 + i]; }
-    if (tid < DK) {
-      qs[tid] = qv * rsqrtf(qn + 1e-6f) * rsqrtf((float)DK);
-      ks[tid] = kv * rsqrtf(kn + 1e-6f);
-    }
-    const float av = __bfloat162float(zba[(size_t)r * zba_stride + a_off + h]) + dtb;
-    const float sp = av > 20.f ? av : log1pf(__expf(av));
-    const float decay = __expf(a_neg * sp);
-    const float bb = __bfloat162float(zba[(size_t)r * zba_stride + b_off + h]);
-    const float beta = __bfloat162float(__float2bfloat16(1.f / (1.f + __expf(-bb))));
-    const float vv = __bfloat162float(row[2 * hk * DK + h * DV + vrow]);
-    __syncthreads();
-    // S *= decay; sk = S k (this thread's part of its row)
-    float* Srow = S + vrow * LD + kpart;
-    float sk = 0.f;
-#pragma unroll 8
-    for (int j = 0; j < KPT; ++j) {
-      const float sv = Srow[j * TPR] * decay;
-      Srow[j * TPR] = sv;
-      sk += sv * ks[j * TPR + kpart];
-    }
+  for (int base = r0; base < r1; base += GDN_TB) {
+    const int nb = min(GDN_TB, r1 - base);
+    __syncthreads();   // the previous batch has been consumed
+    for (int t = warp; t < nb; t += 8) {
+      const __nv_bfloat16* row = qkv + (size_t)(base + t) * conv_dim;
+      float qv[(DK + 31) / 32], kv[(DK + 31) / 32];
+      float q2 = 0.f, k2 = 0.f;
 #pragma unroll
-    for (int o = TPR / 2; o > 0; o >>= 1) sk += __shfl_xor_sync(0xffffffffu, sk, o);
-    const float u = (vv - sk) * beta;
-    float oq = 0.f;
-#pragma unroll 8
-    for (int j = 0; j < KPT; ++j) {
-      const float sv = Srow[j * TPR] + u * ks[j * TPR + kpart];
-      Srow[j * TPR] = sv;
-      oq += sv * qs[j * TPR + kpart];
-    }
+      for (int i = 0; i < (DK + 31) / 32; ++i) {
+        const int c = i * 32 + lane;
+        qv[i] = c < DK ? __bfloat162float(row[kh * DK + c]) : 0.f;
+        kv[i] = c < DK ? __bfloat162float(row[hk * DK + kh * DK + c]) : 0.f;
+        q2 += qv[i] * qv[i];
+        k2 += kv[i] * kv[i];
+      }
+      q2 = warp_sum(q2);
+      k2 = warp_sum(k2);
+      const float qi = rsqrtf(q2 + 1e-6f) * rsqrtf((float)DK), ki = rsqrtf(k2 + 1e-6f);
 #pragma unroll
-    for (int o = TPR / 2; o > 0; o >>= 1) oq += __shfl_xor_sync(0xffffffffu, oq, o);
-    if (kpart == 0) os[vrow] = oq;
-    __syncthreads();
-    // gated RMSNorm over DV: y = o * rsqrt(mean(o^2) + eps) * w * silu(z)
-    float ov = tid < DV ? os[tid] : 0.f;
-    float o2 = warp_sum(ov * ov);
-    if (lane == 0) red[16 + warp] = o2;
-    __syncthreads();
-    float on = 0.f;
-    for (int i = 0; i < 8; ++i) on += red[16 + i];
-    if (tid < DV) {
-      const float z = __bfloat162float(zba[(size_t)r * zba_stride + z_off + h * DV + tid]);
-      const float y = ov * rsqrtf(on / (float)DV + eps) * __bfloat162float(norm_w[tid]) * silu(z);
-      out[(size_t)r * hv * DV + h * DV + tid] = __float2bfloat16(y);
+      for (int i = 0; i < (DK + 31) / 32; ++i) {
+        const int c = i * 32 + lane;
+        if (c < DK) { qs[t][c] = qv[i] * qi; ks[t][c] = kv[i] * ki; }
+      }
+      if (lane < GDN_ROWS) vs[t][lane] = __bfloat162float(row[2 * hk * DK + h * DV + row0 + lane]);
+      if (lane == 16) {
+        const float av = __bfloat162float(zba[(size_t)(base + t) * zba_stride + a_off + h]) + dtb;
+        const float sp = av > 20.f ? av : log1pf(__expf(av));
+        decays[t] = __expf(a_neg * sp);
+      }
+      if (lane == 17) {
+        const float bb = __bfloat162float(zba[(size_t)(base + t) * zba_stride + b_off + h]);
+        betas[t] = __bfloat162float(__float2bfloat16(1.f / (1.f + __expf(-bb))));
+      }
     }
     __syncthreads();
+    for (int t = 0; t < nb; ++t) {
+      const float decay = decays[t], beta = betas[t], vv = vs[t][vrow];
+      float kr[KPT];
+      float sk = 0.f;
+#pragma unroll
+      for (int j = 0; j < KPT; ++j) {
+        kr[j] = ks[t][j * TPR + kpart];
+        S[j] *= decay;
+        sk += S[j] * kr[j];
+      }
+#pragma unroll
+      for (int o = TPR / 2; o > 0; o >>= 1) sk += __shfl_xor_sync(0xffffffffu, sk, o);
+      const float u = (vv - sk) * beta;
+      float oq = 0.f;
+#pragma unroll
+      for (int j = 0; j < KPT; ++j) {
+        S[j] += u * kr[j];
+        oq += S[j] * qs[t][j * TPR + kpart];
+      }
+#pragma unroll
+      for (int o = TPR / 2; o > 0; o >>= 1) oq += __shfl_xor_sync(0xffffffffu, oq, o);
+      if (kpart == 0) o_raw[(size_t)(base + t) * hv * DV + h * DV + row0 + vrow] = oq;
+    }
   }
-  if (line > 0)
-    for (int i = tid; i < DV * DK; i += 256) Sg[i] = S[(i / DK) * LD + (i % DK)];
+  if (line > 0) {
+#pragma unroll
+    for (int j = 0; j < KPT; ++j) Sg[j * TPR + kpart] = S[j];
+  }
 }
 
-#define KERN_GDN_ENTRY(name, DK, DV)                                                                                  \
-  extern "C" __global__ void __launch_bounds__(256)                                                                   \
-      name(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, __nv_bfloat16* out, uint8_t* state, const int* lines,  \
-           const int* cu_q, const float* A_log, const float* dt_bias, const __nv_bfloat16* norm_w, int seqs, int hk,  \
-           int hv, int zba_stride, int z_off, int b_off, int a_off, long long line_bytes, long long s_offset,         \
-           float eps) {                                                                                               \
-    pdl_wait();                                                                                                       \
-    gdn_body<DK, DV>(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv, zba_stride, z_off,       \
-                     b_off, a_off, line_bytes, s_offset, eps);                                                        \
+#define KERN_GDN_ENTRY(name, DK, DV)                                                                                   \
+  extern "C" __global__ void __launch_bounds__(256)                                                                    \
+      name(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, float* o_raw, uint8_t* state, const int* lines,         \
+           const int* cu_q, const float* A_log, const float* dt_bias, int seqs, int hk, int hv, int zba_stride,        \
+           int b_off, int a_off, long long line_bytes, long long s_offset) {                                           \
+    pdl_wait();                                                                                                        \
+    gdn_body<DK, DV>(qkv, zba, o_raw, state, lines, cu_q, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off, a_off,      \
+                     line_bytes, s_offset);                                                                            \
   }
 
 KERN_GDN_ENTRY(kern_gdn_rule_k128_v128, 128, 128)
 KERN_GDN_ENTRY(kern_gdn_rule_k64_v64, 64, 64)
 KERN_GDN_ENTRY(kern_gdn_rule_k32_v32, 32, 32)
+
+// y = rmsnorm(o) * w * silu(z) per (token, value head): grid [tokens, HV], block 128 (dv <= 128 * 8).
+extern "C" __global__ void __launch_bounds__(128)
+    kern_gdn_gate_norm_bf16(const float* o_raw, const __nv_bfloat16* zba, __nv_bfloat16* out, const __nv_bfloat16* norm_w,
+                            int tokens, int hv, int dv, int zba_stride, int z_off, float eps) {
+  pdl_wait();
+  __shared__ float red[4];
+  const int t = blockIdx.x, h = blockIdx.y;
+  if (t >= tokens) return;
+  const float* o = o_raw + ((size_t)t * hv + h) * dv;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dv; i += 128) ss += o[i] * o[i];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  const float inv = rsqrtf((red[0] + red[1] + red[2] + red[3]) / (float)dv + eps);
+  for (int i = threadIdx.x; i < dv; i += 128) {
+    const float z = __bfloat162float(zba[(size_t)t * zba_stride + z_off + h * dv + i]);
+    out[((size_t)t * hv + h) * dv + i] = __float2bfloat16(o[i] * inv * __bfloat162float(norm_w[i]) * silu(z));
+  }
+}

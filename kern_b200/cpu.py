@@ -225,8 +225,7 @@ def k_gdn_conv(g, x, y, state, lines, cu, w, bias, seqs, conv_dim, width, x_stri
 
 
 def _gdn_rule(dim):
-    def run(g, qkv, zba, out, state, lines, cu, A_log, dt_bias, norm_w, seqs, hk, hv, zba_stride, z_off, b_off, a_off,
-            line_bytes, s_off, eps):
+    def run(g, qkv, zba, o_raw, state, lines, cu, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off, a_off, line_bytes, s_off):
         from .ops import gdn as G
 
         conv_dim = 2 * hk * dim + hv * dim
@@ -243,12 +242,21 @@ def _gdn_rule(dim):
             q = rows[:, :hk * dim].view(n, hk, dim)
             k = rows[:, hk * dim:2 * hk * dim].view(n, hk, dim)
             v = rows[:, 2 * hk * dim:].view(n, hv, dim)
-            o, S1 = G.rule_ref(q, k, v, zr[:, z_off:z_off + hv * dim].reshape(n, hv, dim), zr[:, b_off:b_off + hv],
-                               zr[:, a_off:a_off + hv], S0, A_log[:hv], dt_bias[:hv], norm_w[:dim], eps)
-            out[r0 * hv * dim: r1 * hv * dim] = o.to(torch.bfloat16).reshape(-1)
+            o, S1 = G.rule_ref(q, k, v, None, zr[:, b_off:b_off + hv], zr[:, a_off:a_off + hv], S0, A_log[:hv], dt_bias[:hv],
+                               None, normalize=False)
+            o_raw[r0 * hv * dim: r1 * hv * dim] = o.reshape(-1)
             if ln > 0:
                 Sb.copy_(S1)
     return run
+
+
+def k_gdn_gate_norm(g, o_raw, zba, out, norm_w, tokens, hv, dv, zba_stride, z_off, eps):
+    from .ops import gdn as G
+
+    t = g[0]
+    o = o_raw[: t * hv * dv].view(t, hv, dv)
+    z = _f(torch.as_strided(zba, (t, hv * dv), (zba_stride, 1), zba.storage_offset() + z_off)).view(t, hv, dv)
+    out[: t * hv * dv] = G.gate_norm_ref(o, z, norm_w[:dv], eps).to(torch.bfloat16).reshape(-1)
 
 
 def k_copy_rows(g, src, dst, idx, rows, row_bytes, ss, ds):
@@ -274,7 +282,7 @@ CPU_KERNELS = {
     "kern_argmax_final_i64": k_argmax_final, "kern_sample_bf16": k_sample, "kern_sample_f32": k_sample,
     "kern_silu_mul_bf16": k_silu_mul, "kern_copy_rows": k_copy_rows, "kern_sigmoid_mul_bf16": k_sigmoid_mul,
     "kern_gdn_conv_bf16": k_gdn_conv, "kern_gdn_rule_k128_v128": _gdn_rule(128), "kern_gdn_rule_k64_v64": _gdn_rule(64),
-    "kern_gdn_rule_k32_v32": _gdn_rule(32),
+    "kern_gdn_rule_k32_v32": _gdn_rule(32), "kern_gdn_gate_norm_bf16": k_gdn_gate_norm,
     "kern_fill_f32": k_fill, "kern_fill_i32": k_fill, "kern_fill_i64": k_fill, "kern_fill_u8": k_fill,
 }
 for _bn in (256, 128, 64, 32):

@@ -15,19 +15,13 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from . import _native
+from . import _native, fills
 
 _NP = {"i32": np.int32, "i64": np.int64, "f32": np.float32}
 _TT = {"i32": torch.int32, "i64": torch.int64, "f32": torch.float32}
 
 
-@dataclass
-class Sampling:
-    temperature: float = 0.0
-    top_k: int = 0
-    top_p: float = 1.0
-    min_p: float = 0.0
-    seed: int = 0
+Sampling = fills.Sampling
 
 
 @dataclass
@@ -87,91 +81,23 @@ class Engine:
         self.h2d_bytes += len(values) * t.element_size()
 
     def forward_for(self, groups: int, rows_each: list[int]):
-        r0 = rows_each[0]
-        if all(r == r0 for r in rows_each):
-            for f in self.forwards:
-                if f["rows"] == r0 and groups <= f["groups"]:
-                    return f
-        for f in self.forwards:
-            if f["rows"] == "var" and groups <= f["groups"]:
-                return f
-        raise ValueError(f"no program takes {groups} sequences of rows {sorted(set(rows_each))}")
+        return fills.forward_for(self.p, groups, rows_each)
 
     def step(self, batch: list[tuple[Sequence, list[int]]], eager: bool = False, read: bool = True, timed: bool = False,
              pad: int = 0):
         """Feed each sequence its new tokens; returns, per sequence, the tokens the call emitted for it
         (one for a plain step, up to ``count`` for a speculative round), or None when ``read`` is off
-        or the program emits nothing."""
+        or the program emits nothing. ``pad`` dead sequences bring a fixed-shape call up to a bucket."""
         real = len(batch)
-        rows_each = [len(t) for _, t in batch]
-        if real == 0 or sum(rows_each) == 0:
+        if real == 0 or sum(len(t) for _, t in batch) == 0:
             return []
-        # `pad` dead sequences of the same row count bring a fixed-shape call up to a bucket: token 0 at
-        # position 0, slot -1 (nothing appended), context 0 (nothing attended); their outputs are dropped
-        rows_each += [rows_each[0]] * pad
-        b = real + pad
-        total = sum(rows_each)
-        if total > self.rows_max or b > self.groups_max:
-            raise ValueError(f"call of {b} sequences / {total} rows exceeds the manifest's {self.groups_max} / {self.rows_max}")
-        fw = self.forward_for(b, rows_each)
-        tok = np.empty(total, np.int64)
-        pos = np.empty(total, np.int64)
-        slot = np.empty(total, np.int64)
-        seq_len = np.empty(b, np.int64)
-        cu = np.zeros(b + 1, np.int64)
-        at = 0
-        for i, (s, new) in enumerate(batch):
-            n = len(new)
-            tok[at:at + n] = new
-            pos[at:at + n] = np.arange(s.length, s.length + n)
-            slot[at:at + n] = s.lease.slots_of(s.length, s.length + n)
-            seq_len[i] = s.length + n
-            at += n
-            cu[i + 1] = at
-        for i in range(real, b):
-            n = rows_each[i]
-            tok[at:at + n], pos[at:at + n], slot[at:at + n], seq_len[i] = 0, 0, -1, 0
-            at += n
-            cu[i + 1] = at
-        longest = int(seq_len.max())
-        for f in self.fills.get("token", []):
-            if f["axis"] == "groups":
-                self._write(f["name"], f["dtype"], np.array([t[0] for _, t in batch] + [0] * pad, np.int64))
-            else:
-                self._write(f["name"], f["dtype"], tok)
-        cols = {"position": pos, "slot": slot, "seq_len": seq_len, "valid": np.ones(total, np.int64)}
-        for kind, col in cols.items():
-            for f in self.fills.get(kind, []):
-                self._write(f["name"], f["dtype"], col)
-        for f in self.fills.get("cu_seqlens", []):
-            self._write(f["name"], f["dtype"], cu)
-        if "temperature" in self.fills:
-            sm = [s.sampling for s, _ in batch] + [Sampling()] * pad
-            for kind, vals in (("temperature", [x.temperature for x in sm]), ("top_k", [x.top_k for x in sm]),
-                               ("top_p", [x.top_p for x in sm]), ("min_p", [x.min_p for x in sm]), ("seed", [x.seed for x in sm])):
-                f = self.fills[kind][0]
-                self._write(f["name"], f["dtype"], np.array(vals))
-        for t in self.page_tables:
-            w = t["width"]
-            per = t["stride"] // self.unit           # pool pages per table entry
-            rows = np.zeros((b, w), np.int32)
-            for i, (s, _) in enumerate(batch):
-                pg = s.lease.pages
-                ids = pg[::per] if per > 1 else pg
-                m = min(len(ids), w)
-                rows[i, :m] = np.asarray(ids[:m], np.int32) // per if per > 1 else ids[:m]
-            self._write(t["name"], "i32", rows.reshape(-1))
-        for t in self.p.get("line_tables", []):
-            # [lines, groups(, w)]: line 0 of a sequence is its own state slot; the rest stay null (0)
-            rows = np.zeros((t["lines"], b, t["width"]), np.int32)
-            for i, (s, _) in enumerate(batch):
-                rows[0, i, 0] = max(0, s.lease.slot)
-            self._write(t["name"], "i32", rows.reshape(-1))
-        vars_ = {self.p["rows"]["var"]: total, self.p["groups"]["var"]: b}
-        if self.p.get("ranks"):
-            vars_[self.p["ranks"]["var"]] = total
-        if self.p.get("context"):
-            vars_[self.p["context"]["var"]] = longest
+        entries = [fills.Entry(length=s.length, new=new, pages=s.lease.pages, slot=s.lease.slot,
+                               slots=s.lease.slots_of(s.length, s.length + len(new)), sampling=s.sampling)
+                   for s, new in batch]
+        call = fills.build(self.p, self.unit, entries, pad)
+        for name, (dtype, col) in call.columns.items():
+            self._write(name, dtype, col)
+        fw, vars_, b = call.forward, call.vars, call.groups
         if timed:     # cost by call, eagerly, with an event between calls
             self.last_times = self.rt.issue_timed(fw["name"], vars_)
             launches = sum(t[3] for t in self.last_times)

@@ -442,28 +442,28 @@ def gdn_conv_op(conv_dim: int, width: int, x_stride: int, line_bytes: int, ragge
 
 def gdn_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_off: int, eps: float,
                 ragged: bool) -> dict:
-    """Gated delta rule + gated RMSNorm. Interface [qkv, zba, out, state, lines, (cu_seqlens,) A_log, dt_bias, norm_w].
-    `zba` points at the z|b|a columns of the projection's row."""
+    """Gated delta rule (value rows split over CTAs) + gated RMSNorm.
+    Interface [qkv, zba, out, state, lines, (cu_seqlens,) A_log, dt_bias, norm_w]; `zba` points at the z|b|a columns
+    of the projection's row."""
     iface = ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "inout state", "in buffer<i32>"]
-    lp = list(iface)
-    args = [{"param": i} for i in range(5)]
     if ragged:
         iface.append("in buffer<i32>")
-        lp.append("in buffer<i32>")
-        args.append({"param": 5})
-    else:
-        lp.append("i64")
-        args.append({"i64": 0})
     at = len(iface)
     iface += ["in buffer<f32>", "in buffer<f32>", "in buffer<bf16>"]
-    lp += ["in buffer<f32>", "in buffer<f32>", "in buffer<bf16>"] + ["i32"] * 7 + ["i64", "i64", "f32"]
-    args += [{"param": at}, {"param": at + 1}, {"param": at + 2}, {"i32": I32_MAX}, {"i32": hk}, {"i32": hv},
-             {"i32": zba_stride}, {"i32": 0}, {"i32": hv * dim}, {"i32": hv * dim + hv}, {"i64": line_bytes},
-             {"i64": s_off}, {"f32": eps}]
-    smem = (dim * (dim + 256 // dim) + 2 * dim + dim) * 4
-    return {"params": iface, "impl": {"launches": [{
-        "module": "gdn", "entry": f"kern_gdn_rule_k{dim}_v{dim}", "block": [256, 1, 1], "grid": [hv, "seqs", 1],
-        "shared_mem": smem, "params": lp, "args": args}]}}
+    lp = ["in buffer<bf16>", "in buffer<bf16>", "out buffer<f32>", "inout state", "in buffer<i32>",
+          "in buffer<i32>" if ragged else "i64", "in buffer<f32>", "in buffer<f32>"] + ["i32"] * 6 + ["i64", "i64"]
+    args = [{"param": 0}, {"param": 1}, {"scratch": "o_raw"}, {"param": 3}, {"param": 4},
+            {"param": 5} if ragged else {"i64": 0}, {"param": at}, {"param": at + 1}, {"i32": I32_MAX}, {"i32": hk},
+            {"i32": hv}, {"i32": zba_stride}, {"i32": hv * dim}, {"i32": hv * dim + hv}, {"i64": line_bytes}, {"i64": s_off}]
+    rule = {"module": "gdn", "entry": f"kern_gdn_rule_k{dim}_v{dim}", "block": [256, 1, 1],
+            "grid": [hv * (dim // 16), "seqs", 1], "params": lp, "args": args}
+    norm = {"module": "gdn", "entry": "kern_gdn_gate_norm_bf16", "block": [128, 1, 1], "grid": ["tokens", hv, 1],
+            "params": ["in buffer<f32>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<bf16>", "i32", "i32", "i32", "i32",
+                       "i32", "f32"],
+            "args": [{"scratch": "o_raw"}, {"param": 1}, {"param": 2}, {"param": at + 2}, {"i32": I32_MAX}, {"i32": hv},
+                     {"i32": dim}, {"i32": zba_stride}, {"i32": 0}, {"f32": eps}]}
+    return {"params": iface, "impl": {"launches": [rule, norm],
+                                      "scratch": {"o_raw": {"dtype": "f32", "shape": ["tokens", hv * dim]}}}}
 
 
 def sigmoid_mul_op(d: int, x_stride: int, gate_stride: int) -> dict:

@@ -21,26 +21,20 @@ def line_bytes(hk: int, hv: int, dk: int, dv: int, width: int = 4) -> tuple[int,
     return s_off + hv * dv * dk * 4, s_off
 
 
-def rule_smem(dk: int, dv: int) -> int:
-    return (dv * (dk + 256 // dv) + 2 * dk + dv) * 4
-
-
-def conv(x, y, state, lines, cu_q, w, bias, seqs, conv_dim, width, line_b):
-    k = Kernels.get(x.device)
-    k.launch("gdn", "kern_gdn_conv_bf16", (seqs, (conv_dim + 255) // 256), (256,),
-             [ptr(x), ptr(y), ptr(state), ptr(lines), ptr(cu_q), ptr(w), ptr(bias), i32(seqs), i32(conv_dim),
-              i32(width), i32(x.stride(0)), i64(line_b)])
-    return y
-
-
 def rule(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv, z_off, b_off, a_off,
-         line_b, s_off, eps=1e-6):
+         line_b, s_off, eps=1e-6, o_raw=None):
+    """Gated delta rule (value rows split over CTAs, state in registers) then the gated RMSNorm."""
     k = Kernels.get(qkv.device)
     assert dk == dv and dk in (32, 64, 128)
-    k.launch("gdn", f"kern_gdn_rule_k{dk}_v{dv}", (hv, seqs), (256,),
-             [ptr(qkv), ptr(zba), ptr(out), ptr(state), ptr(lines), ptr(cu_q), ptr(A_log), ptr(dt_bias), ptr(norm_w),
-              i32(seqs), i32(hk), i32(hv), i32(zba.stride(0)), i32(z_off), i32(b_off), i32(a_off), i64(line_b),
-              i64(s_off), f32(eps)], shared_mem=rule_smem(dk, dv))
+    tokens = out.shape[0]
+    if o_raw is None:
+        o_raw = torch.empty(tokens, hv * dv, dtype=torch.float32, device=qkv.device)
+    k.launch("gdn", f"kern_gdn_rule_k{dk}_v{dv}", (hv * (dv // 16), seqs), (256,),
+             [ptr(qkv), ptr(zba), ptr(o_raw), ptr(state), ptr(lines), ptr(cu_q), ptr(A_log), ptr(dt_bias),
+              i32(seqs), i32(hk), i32(hv), i32(zba.stride(0)), i32(b_off), i32(a_off), i64(line_b), i64(s_off)])
+    k.launch("gdn", "kern_gdn_gate_norm_bf16", (tokens, hv), (128,),
+             [ptr(o_raw), ptr(zba), ptr(out), ptr(norm_w), i32(tokens), i32(hv), i32(dv), i32(zba.stride(0)),
+              i32(z_off), f32(eps)])
     return out
 
 
@@ -56,7 +50,7 @@ def conv_ref(x, window, w, bias=None):
     return F.silu(y), full[full.shape[0] - (width - 1):].clone()
 
 
-def rule_ref(q, k, v, z, b, a, S, A_log, dt_bias, norm_w, eps=1e-6):
+def rule_ref(q, k, v, z, b, a, S, A_log, dt_bias, norm_w, eps=1e-6, normalize=True):
     """One sequence: q,k [T, HK, DK]; v,z [T, HV, DV]; b,a [T, HV]; S [HV, DV, DK] f32 (updated copy returned)."""
     T, hk, dk = q.shape
     hv, dv = v.shape[1], v.shape[2]
@@ -75,5 +69,11 @@ def rule_ref(q, k, v, z, b, a, S, A_log, dt_bias, norm_w, eps=1e-6):
         u = (v[t].float() - sk) * beta[t][:, None]
         S = S + u[:, :, None] * k[t][:, None, :]
         out[t] = torch.einsum("hvk,hk->hv", S, q[t])
-    y = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float() * F.silu(z.float())
-    return y, S
+    if not normalize:
+        return out, S
+    return gate_norm_ref(out, z, norm_w, eps), S
+
+
+def gate_norm_ref(o, z, norm_w, eps=1e-6):
+    o = o.float()
+    return o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float() * F.silu(z.float())
