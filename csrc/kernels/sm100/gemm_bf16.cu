@@ -38,10 +38,14 @@ struct GemmCfg {
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 256;
 };
 
-template <int BN, int EPI>
+// GROUPED: the M tiles come from a device table of int4 {expert, first row, rows (<= BM), -} built by the MoE
+// planner (`tile_count` of them); A rows are the expert-sorted activations, B is a 3-D map [K, N, experts].
+// A tile's load may run into the next expert's rows; the epilogue stores only the tile's own rows.
+template <int BN, int EPI, bool GROUPED = false>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
                                           void* Cv, const void* Rv,
-                                          int M, int N, int K, int ldc, int* err) {
+                                          int M, int N, int K, int ldc, int* err,
+                                          const int* tile_table = nullptr, const int* tile_count = nullptr) {
   using Cfg = GemmCfg<BN>;
   constexpr int kStages = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -57,9 +61,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_m = (M + BM - 1) / BM;
   const int num_n = (N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -87,6 +89,19 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
     tma_prefetch_desc(tma_b);
   }
   pdl_wait();  // everything above touched only this CTA's own state and the descriptors
+  const int num_m = GROUPED ? *tile_count : (M + BM - 1) / BM;
+  const int num_tiles = num_m * num_n;
+  // tile t -> (first row, row bound, n block, expert)
+  auto tile_of = [&](int t, int& row0, int& row_end, int& n_blk, int& expert) {
+    const int mt = t % num_m;
+    n_blk = t / num_m;
+    if constexpr (GROUPED) {
+      const int4 e = reinterpret_cast<const int4*>(tile_table)[mt];
+      expert = e.x; row0 = e.y; row_end = min(M, e.y + e.z);
+    } else {
+      expert = 0; row0 = mt * BM; row_end = M;
+    }
+  };
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -95,7 +110,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int m_blk = t % num_m, n_blk = t / num_m;
+        int row0, row_end, n_blk, expert;
+        tile_of(t, row0, row_end, n_blk, expert);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
             set_error(err, ERR_WAIT_EMPTY);
@@ -106,13 +122,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
           uint8_t* sa = tiles + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kStageBytesA;
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          tma_load_2d(sa, tma_a, kb * BK, m_blk * BM, &full_bar[stage]);
+          tma_load_2d(sa, tma_a, kb * BK, row0, &full_bar[stage]);
+          auto load_b = [&](uint8_t* dst, int n_row) {
+            if constexpr (GROUPED) tma_load_3d(dst, tma_b, kb * BK, n_row, expert, &full_bar[stage]);
+            else tma_load_2d(dst, tma_b, kb * BK, n_row, &full_bar[stage]);
+          };
           if constexpr (EPI == 3) {
             // W = [gate rows ; up rows]: this tile's B rows are BN/2 gate rows then the matching BN/2 up rows
-            tma_load_2d(sb, tma_b, kb * BK, n_blk * (BN / 2), &full_bar[stage]);
-            tma_load_2d(sb + (BN / 2) * BK * 2, tma_b, kb * BK, N / 2 + n_blk * (BN / 2), &full_bar[stage]);
+            load_b(sb, n_blk * (BN / 2));
+            load_b(sb + (BN / 2) * BK * 2, N / 2 + n_blk * (BN / 2));
           } else {
-            tma_load_2d(sb, tma_b, kb * BK, n_blk * BN, &full_bar[stage]);
+            load_b(sb, n_blk * BN);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -165,14 +185,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      const int m_blk = t % num_m, n_blk = t / num_m;
+      int row0, row_end, n_blk, expert;
+      tile_of(t, row0, row_end, n_blk, expert);
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) {
         set_error(err, ERR_WAIT_TMEM_FULL);
         *abort_flag = 1;
         break;
       }
       tc_fence_after();
-      const int row = m_blk * BM + quarter * 32 + lane;
+      const int row = row0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       if constexpr (EPI == 3) {
         // SwiGLU: accumulator columns [0, BN/2) are gate, [BN/2, BN) the matching up columns
@@ -183,7 +204,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
           tmem_ld_32x32(t_row + BN / 2 + c * 32, u);
           tmem_ld_wait();
           const int col = n_blk * (BN / 2) + c * 32;   // output column
-          if (row < M && col < N / 2) {
+          if (row < row_end && col < N / 2) {
             __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(Cv) + (size_t)row * ldc + col;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -207,7 +228,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
         const int col = n_blk * BN + c * 32;
-        if (row < M) {
+        if (row < row_end) {
           if constexpr (EPI == 0 || EPI == 2) {
             __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(Cv) + (size_t)row * ldc + col;
             const __nv_bfloat16* R =
@@ -273,6 +294,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
 
 }  // namespace kern
 
+#ifndef KERN_GEMM_NO_ENTRIES
 #define KERN_GEMM_ENTRY(name, BN, EPI)                                                        \
   extern "C" __global__ void __launch_bounds__(192, 1)                                        \
       name(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, \
@@ -294,3 +316,4 @@ KERN_GEMM_ENTRY(kern_gemm_bf16_tn_acc_n32, 32, 2)
 KERN_GEMM_ENTRY(kern_gemm_bf16_tn_swiglu_n256, 256, 3)
 KERN_GEMM_ENTRY(kern_gemm_bf16_tn_swiglu_n128, 128, 3)
 KERN_GEMM_ENTRY(kern_gemm_bf16_tn_swiglu_n64, 64, 3)
+#endif  // KERN_GEMM_NO_ENTRIES

@@ -1,0 +1,195 @@
+// Mixture-of-experts routing and the routed (grouped) tcgen05 GEMM.
+//
+//   kern_moe_route_f32      router scores -> top-k expert ids and weights per token (sigmoid or softmax scoring,
+//                           optional selection bias, renormalise, scale)
+//   kern_moe_plan           counts per expert -> row offsets, the permuted row of every (token, choice), and the
+//                           M-tile table the grouped GEMM walks; experts outside [e_lo, e_hi) belong to another rank
+//   kern_moe_gather_bf16    x_perm[perm[t, j]] = x[t]
+//   kern_moe_gemm_*         C_perm = A_perm . W[expert]^T over the tile table (store / SwiGLU epilogues)
+//   kern_moe_combine_bf16   out[t] = (acc ? out[t] : 0) + sum_j w[t, j] * y_perm[perm[t, j]]  (+ shared[t])
+//
+// Reference counterparts: tools/kernels-src/topk_row.cu:21 (top-k per row); the routed batched GEMMs the reference
+// takes as prebuilt blobs (kernel_index/trtllm_bmm_*.toml) are written here on the same tcgen05 body as the dense GEMM.
+#define KERN_GEMM_NO_ENTRIES
+#include "gemm_bf16.cu"
+
+using namespace kern;
+
+// One warp per token; E <= 1024. mode 0: sigmoid scores, mode 1: softmax over all experts.
+// Selection uses score + bias (bias may be null); the weight is the unbiased score. renorm: weights sum to 1.
+extern "C" __global__ void __launch_bounds__(128)
+    kern_moe_route_f32(const float* logits, const float* bias, int* topk_ids, float* topk_w, int tokens, int experts,
+                       int k, int mode, int renorm, float scale, int ld) {
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= tokens) return;
+  constexpr int PER = 32;   // up to 1024 experts
+  float sc[PER], sel[PER];
+  const float* row = logits + (size_t)t * ld;
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = i * 32 + lane;
+    sc[i] = e < experts ? row[e] : -INFINITY;
+    mx = fmaxf(mx, sc[i]);
+  }
+  if (mode == 1) {
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = i * 32 + lane;
+      sc[i] = e < experts ? __expf(sc[i] - mx) : 0.f;
+      sum += sc[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) sc[i] /= sum;
+  } else {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) sc[i] = 1.f / (1.f + __expf(-sc[i]));
+  }
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = i * 32 + lane;
+    sel[i] = e < experts ? sc[i] + (bias ? bias[e] : 0.f) : -INFINITY;
+  }
+  float wsum = 0.f;
+  float my_w = 0.f;
+  int my_id = 0;
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = i * 32 + lane;
+      if (sel[i] > best) { best = sel[i]; bi = e; }   // lowest index wins ties within a lane (ascending scan)
+    }
+    // warp arg-max, ties -> lowest expert id
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    float w = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i)
+      if (i * 32 + lane == bi) { w = sc[i]; sel[i] = -INFINITY; }
+    w = warp_sum(w);
+    wsum += w;
+    if (lane == j) { my_w = w; my_id = bi; }
+  }
+  if (lane < k) {
+    const float w = renorm ? my_w / (wsum + 1e-20f) : my_w;
+    topk_ids[(size_t)t * k + lane] = my_id;
+    topk_w[(size_t)t * k + lane] = w * scale;
+  }
+}
+
+// Single CTA (block 1024). entries = tokens * k. Outputs:
+//   perm[entries]      permuted row of each (token, choice), -1 when the expert is not local
+//   offsets[E_local+1] first permuted row of every local expert
+//   tiles[int4]        {local expert, first row, rows, 0} per M tile of `bm` rows; tile_count[0] = how many
+//   rows_out[0]        total permuted rows
+extern "C" __global__ void __launch_bounds__(1024)
+    kern_moe_plan(const int* topk_ids, int* perm, int* offsets, int* tiles, int* tile_count, int* rows_out, int entries,
+                  int e_lo, int e_hi, int bm, int max_tiles, int* err) {
+  pdl_wait();
+  extern __shared__ int sm[];          // counts[E_local] | cursor[E_local]
+  const int el = e_hi - e_lo;
+  int* counts = sm;
+  int* cursor = sm + el;
+  for (int i = threadIdx.x; i < el; i += blockDim.x) counts[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int e = topk_ids[i];
+    if (e >= e_lo && e < e_hi) atomicAdd(&counts[e - e_lo], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, nt = 0;
+    for (int e = 0; e < el; ++e) {
+      offsets[e] = at;
+      cursor[e] = at;
+      for (int m0 = 0; m0 < counts[e]; m0 += bm) {
+        if (nt < max_tiles) {
+          reinterpret_cast<int4*>(tiles)[nt] = make_int4(e, at + m0, min(bm, counts[e] - m0), 0);
+          ++nt;
+        } else {
+          set_error(err, ERR_BOUNDS);
+        }
+      }
+      at += counts[e];
+    }
+    offsets[el] = at;
+    tile_count[0] = nt;
+    rows_out[0] = at;
+  }
+  __syncthreads();
+  // stable placement: entries of one expert keep token order, so a run is reproducible bit for bit
+  for (int e = threadIdx.x; e < el; e += blockDim.x) {
+    if (counts[e] == 0) continue;
+    int at = cursor[e];
+    for (int i = 0; i < entries; ++i)
+      if (topk_ids[i] == e + e_lo) perm[i] = at++;
+  }
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int e = topk_ids[i];
+    if (e < e_lo || e >= e_hi) perm[i] = -1;
+  }
+}
+
+// grid = entries (tokens * k), block 128; 16-byte vectors.
+extern "C" __global__ void __launch_bounds__(128)
+    kern_moe_gather_bf16(const __nv_bfloat16* x, const int* perm, __nv_bfloat16* x_perm, int entries, int k, int hidden) {
+  pdl_wait();
+  const int i = blockIdx.x;
+  if (i >= entries) return;
+  const int r = perm[i];
+  if (r < 0) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(i / k) * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(x_perm + (size_t)r * hidden);
+  for (int v = threadIdx.x; v < hidden / 8; v += 128) dst[v] = src[v];
+}
+
+// grid = tokens, block 128. out may alias shared (read before write per element).
+extern "C" __global__ void __launch_bounds__(128)
+    kern_moe_combine_bf16(const __nv_bfloat16* y_perm, const int* perm, const float* topk_w, const __nv_bfloat16* shared,
+                          __nv_bfloat16* out, int tokens, int k, int hidden, int accumulate) {
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (t >= tokens) return;
+  for (int v = threadIdx.x; v < hidden / 8; v += 128) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    auto add = [&](uint4 p, float w) {
+      float2 a = unpack_bf16x2(p.x), b = unpack_bf16x2(p.y), c = unpack_bf16x2(p.z), d = unpack_bf16x2(p.w);
+      acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * b.x; acc[3] += w * b.y;
+      acc[4] += w * c.x; acc[5] += w * c.y; acc[6] += w * d.x; acc[7] += w * d.y;
+    };
+    if (accumulate) add(reinterpret_cast<const uint4*>(out + (size_t)t * hidden)[v], 1.f);
+    if (shared) add(reinterpret_cast<const uint4*>(shared + (size_t)t * hidden)[v], 1.f);
+    for (int j = 0; j < k; ++j) {
+      const int r = perm[(size_t)t * k + j];
+      if (r >= 0) add(reinterpret_cast<const uint4*>(y_perm + (size_t)r * hidden)[v], topk_w[(size_t)t * k + j]);
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out + (size_t)t * hidden)[v] = o;
+  }
+}
+
+#define KERN_MOE_GEMM_ENTRY(name, BN, EPI)                                                                        \
+  extern "C" __global__ void __launch_bounds__(192, 1)                                                            \
+      name(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, void* C,          \
+           const int* tiles, const int* tile_count, int M, int N, int K, int ldc, int* err) {                      \
+    kern::gemm_body<BN, EPI, true>(&tma_a, &tma_b, C, nullptr, M, N, K, ldc, err, tiles, tile_count);              \
+  }
+
+KERN_MOE_GEMM_ENTRY(kern_moe_gemm_bf16_n256, 256, 0)
+KERN_MOE_GEMM_ENTRY(kern_moe_gemm_bf16_n128, 128, 0)
+KERN_MOE_GEMM_ENTRY(kern_moe_gemm_bf16_n64, 64, 0)
+KERN_MOE_GEMM_ENTRY(kern_moe_gemm_bf16_swiglu_n256, 256, 3)
+KERN_MOE_GEMM_ENTRY(kern_moe_gemm_bf16_swiglu_n128, 128, 3)
+KERN_MOE_GEMM_ENTRY(kern_moe_gemm_bf16_swiglu_n64, 64, 3)

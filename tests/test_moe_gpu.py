@@ -1,0 +1,85 @@
+"""MoE routing, planning, routed tcgen05 GEMMs and combine against the PyTorch fp32 statement."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def bf(x):
+    return x.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("mode,bias", [("sigmoid", False), ("sigmoid", True), ("softmax", False)])
+@pytest.mark.parametrize("t,e,k", [(1, 8, 2), (37, 64, 6), (300, 384, 8)])
+def test_route(cuda, t, e, k, mode, bias):
+    from kern_b200.ops import moe
+
+    torch.manual_seed(t + e)
+    logits = torch.randn(t, e, device=cuda) * 2
+    b = torch.randn(e, device=cuda) * 0.5 if bias else None
+    ids, w = moe.route(logits, k, b, mode, True, 2.5)
+    rid, rw = moe.route_reference(logits, k, b, mode, True, 2.5)
+    torch.cuda.synchronize()
+    assert torch.equal(ids.sort(-1).values, rid.sort(-1).values)
+    order, rorder = ids.argsort(-1), rid.argsort(-1)
+    torch.testing.assert_close(torch.gather(w, 1, order), torch.gather(rw, 1, rorder), rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("t,e,k,e_lo,e_n", [(5, 8, 2, 0, 8), (200, 32, 4, 8, 16), (1000, 16, 2, 0, 16)])
+def test_plan_is_a_stable_partition(cuda, t, e, k, e_lo, e_n):
+    from kern_b200.ops import moe
+    from kern_b200.ops.launcher import Kernels
+
+    torch.manual_seed(1)
+    ids = torch.stack([torch.randperm(e, device=cuda)[:k] for _ in range(t)]).int()
+    pl = moe.plan(ids, e_n, e_lo)
+    torch.cuda.synchronize()
+    Kernels.get(cuda).check_error()
+    flat, perm = ids.flatten().cpu(), pl["perm"].cpu()
+    offsets = pl["offsets"].cpu()
+    local = (flat >= e_lo) & (flat < e_lo + e_n)
+    assert bool((perm[~local] == -1).all())
+    assert sorted(perm[local].tolist()) == list(range(int(local.sum())))
+    assert int(pl["rows"]) == int(local.sum())
+    for x in range(e_n):
+        mine = perm[flat == x + e_lo]
+        assert mine.tolist() == list(range(int(offsets[x]), int(offsets[x + 1])))     # token order kept
+    n = int(pl["tile_count"])
+    covered = []
+    for ex, r0, nr, _ in pl["tiles"][:n].cpu().tolist():
+        assert 0 < nr <= 128 and int(offsets[ex]) <= r0 and r0 + nr <= int(offsets[ex + 1])
+        covered += list(range(r0, r0 + nr))
+    assert covered == list(range(int(local.sum())))
+
+
+@pytest.mark.parametrize("t,h,inter,e,k", [(3, 256, 128, 8, 2), (150, 512, 256, 16, 4), (700, 1024, 512, 32, 8)])
+def test_moe_layer(cuda, t, h, inter, e, k):
+    from kern_b200.ops import moe
+    from kern_b200.ops.launcher import Kernels
+
+    torch.manual_seed(t)
+    x = bf(torch.randn(t, h, device=cuda))
+    wr = bf(torch.randn(e, h, device=cuda) * 0.1)
+    w1 = bf(torch.randn(e, 2 * inter, h, device=cuda) * h ** -0.5)
+    w2 = bf(torch.randn(e, h, inter, device=cuda) * inter ** -0.5)
+    shared = bf(torch.randn(t, h, device=cuda))
+    got = moe.moe_layer(x, wr, w1, w2, k, scale=1.5, shared=shared)
+    torch.cuda.synchronize()
+    Kernels.get(cuda).check_error()
+    ref = moe.moe_reference(x, wr, w1, w2, k, scale=1.5, shared=shared)
+    torch.testing.assert_close(got.float(), ref, rtol=3e-2, atol=3e-2)
+
+
+def test_moe_expert_parallel_shares_sum_to_the_whole(cuda):
+    from kern_b200.ops import moe
+
+    torch.manual_seed(9)
+    t, h, inter, e, k = 90, 256, 128, 16, 4
+    x = bf(torch.randn(t, h, device=cuda))
+    wr = bf(torch.randn(e, h, device=cuda) * 0.1)
+    w1 = bf(torch.randn(e, 2 * inter, h, device=cuda) * h ** -0.5)
+    w2 = bf(torch.randn(e, h, inter, device=cuda) * inter ** -0.5)
+    whole = moe.moe_reference(x, wr, w1, w2, k)
+    parts = sum(moe.moe_layer(x, wr, w1[lo:lo + 4].contiguous(), w2[lo:lo + 4].contiguous(), k, e_lo=lo).float()
+                for lo in range(0, e, 4))
+    torch.testing.assert_close(parts, whole, rtol=4e-2, atol=4e-2)
