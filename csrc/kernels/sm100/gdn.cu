@@ -17,34 +17,83 @@ using namespace kern;
 // ---- causal conv (width <= 4) + SiLU ----------------------------------------------------------------
 // x: [tokens][x_stride] (the q|k|v channels are the first conv_dim of a row), y: [tokens][conv_dim]
 // w: [conv_dim][width] bf16, bias optional. cu_q: [seqs+1] row starts (nullptr: one row per sequence).
-// grid [seqs, ceil(conv_dim / 256)], block 256: a thread owns one channel and walks its sequence's rows.
+// Every output row depends on at most width-1 earlier inputs, so rows are independent: grid
+// [ceil(rows / 16), ceil(conv_dim / 256)], block 256; a thread owns one channel and walks 16 consecutive rows,
+// carrying the last inputs in registers and re-seeding them from the state window at a sequence's first row.
+// The window itself is advanced afterwards by kern_gdn_conv_state (a separate launch: rows of one sequence may sit
+// in several CTAs, and none of them may see the window half-updated).
+constexpr int CONV_ROWS = 16;
+
 extern "C" __global__ void __launch_bounds__(256)
-    kern_gdn_conv_bf16(const __nv_bfloat16* x, __nv_bfloat16* y, uint8_t* state, const int* lines, const int* cu_q,
-                       const __nv_bfloat16* w, const __nv_bfloat16* bias, int seqs, int conv_dim, int width, int x_stride,
-                       long long line_bytes) {
+    kern_gdn_conv_bf16(const __nv_bfloat16* x, __nv_bfloat16* y, const uint8_t* state, const int* lines, const int* cu_q,
+                       const __nv_bfloat16* w, const __nv_bfloat16* bias, int seqs, int rows, int conv_dim, int width,
+                       int x_stride, long long line_bytes) {
+  pdl_wait();
+  const int c = blockIdx.y * 256 + threadIdx.x;
+  const int total = cu_q ? min(rows, cu_q[seqs]) : min(rows, seqs);
+  const int ra = blockIdx.x * CONV_ROWS, rb = min(total, ra + CONV_ROWS);
+  if (c >= conv_dim || ra >= rb) return;
+  float wt[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < width; ++j) wt[j] = __bfloat162float(w[(size_t)c * width + j]);
+  const float bs = bias ? __bfloat162float(bias[c]) : 0.f;
+  // the sequence of row ra: the last s with cu_q[s] <= ra
+  int s = ra;
+  if (cu_q) {
+    int lo = 0, hi = seqs - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (cu_q[mid] <= ra) lo = mid; else hi = mid - 1;
+    }
+    s = lo;
+  }
+  int r0 = cu_q ? cu_q[s] : s, r1 = cu_q ? cu_q[s + 1] : s + 1;
+  float hist[3] = {0.f, 0.f, 0.f};     // inputs r-3, r-2, r-1 (only the last width-1 matter)
+  auto seed = [&](int r) {
+    const int line = lines[s];
+    const __nv_bfloat16* win = reinterpret_cast<const __nv_bfloat16*>(state + (size_t)line * line_bytes);
+    for (int d = 1; d <= width - 1; ++d) {
+      const int rr = r - d;
+      float v;
+      if (rr >= r0) v = __bfloat162float(x[(size_t)rr * x_stride + c]);
+      else v = line > 0 ? __bfloat162float(win[(size_t)(width - 1 - (r0 - rr)) * conv_dim + c]) : 0.f;
+      hist[3 - d] = v;
+    }
+  };
+  seed(ra);
+  for (int r = ra; r < rb; ++r) {
+    while (r >= r1) {     // next sequence (empty ones are skipped)
+      ++s;
+      r0 = cu_q ? cu_q[s] : s;
+      r1 = cu_q ? cu_q[s + 1] : s + 1;
+      if (r < r1) seed(r);
+    }
+    const float cur = __bfloat162float(x[(size_t)r * x_stride + c]);
+    float acc = bs + wt[width - 1] * cur;
+    for (int j = 0; j < width - 1; ++j) acc += wt[j] * hist[3 - (width - 1) + j];
+    y[(size_t)r * conv_dim + c] = __float2bfloat16(silu(acc));
+    hist[0] = hist[1]; hist[1] = hist[2]; hist[2] = cur;
+  }
+}
+
+// window' = the last width-1 inputs of (window ++ this call's rows). grid [seqs, ceil(conv_dim / 256)], block 256.
+extern "C" __global__ void __launch_bounds__(256)
+    kern_gdn_conv_state(const __nv_bfloat16* x, uint8_t* state, const int* lines, const int* cu_q, int seqs, int conv_dim,
+                        int width, int x_stride, long long line_bytes) {
   pdl_wait();
   const int s = blockIdx.x;
   const int c = blockIdx.y * 256 + threadIdx.x;
   if (s >= seqs || c >= conv_dim) return;
   const int line = lines[s];
   const int r0 = cu_q ? cu_q[s] : s, r1 = cu_q ? cu_q[s + 1] : s + 1;
-  if (r1 <= r0) return;
-  __nv_bfloat16* win = reinterpret_cast<__nv_bfloat16*>(state + (size_t)line * line_bytes);   // [(width-1)][conv_dim]
-  float hist[3] = {0.f, 0.f, 0.f};
-  for (int j = 0; j < width - 1; ++j) hist[j] = line > 0 ? __bfloat162float(win[(size_t)j * conv_dim + c]) : 0.f;
-  float wt[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int j = 0; j < width; ++j) wt[j] = __bfloat162float(w[(size_t)c * width + j]);
-  const float bs = bias ? __bfloat162float(bias[c]) : 0.f;
-  for (int r = r0; r < r1; ++r) {
-    const float cur = __bfloat162float(x[(size_t)r * x_stride + c]);
-    float acc = bs + wt[width - 1] * cur;
-    for (int j = 0; j < width - 1; ++j) acc += wt[j] * hist[j];
-    y[(size_t)r * conv_dim + c] = __float2bfloat16(silu(acc));
-    for (int j = 0; j + 1 < width - 1; ++j) hist[j] = hist[j + 1];
-    if (width > 1) hist[width - 2] = cur;
+  const int n = r1 - r0, keep = width - 1;
+  if (line <= 0 || n <= 0) return;
+  __nv_bfloat16* win = reinterpret_cast<__nv_bfloat16*>(state + (size_t)line * line_bytes);
+  __nv_bfloat16 nw[3];
+  for (int j = 0; j < keep; ++j) {
+    const int src = n + j - keep;      // index into this call's rows; negative: still in the old window
+    nw[j] = src >= 0 ? x[(size_t)(r0 + src) * x_stride + c] : win[(size_t)(keep + src) * conv_dim + c];
   }
-  if (line > 0)
-    for (int j = 0; j < width - 1; ++j) win[(size_t)j * conv_dim + c] = __float2bfloat16(hist[j]);
+  for (int j = 0; j < keep; ++j) win[(size_t)j * conv_dim + c] = nw[j];
 }
 
 // ---- gated delta rule ---------------------------------------------------------------------------------

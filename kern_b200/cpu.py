@@ -206,22 +206,35 @@ def _rows_of(cu, s):
     return (int(cu[s]), int(cu[s + 1])) if isinstance(cu, torch.Tensor) else (s, s + 1)
 
 
-def k_gdn_conv(g, x, y, state, lines, cu, w, bias, seqs, conv_dim, width, x_stride, line_bytes):
+def _gdn_window(state, line, line_bytes, width, conv_dim):
+    return state[line * line_bytes: line * line_bytes + (width - 1) * conv_dim * 2].view(torch.bfloat16).view(width - 1, conv_dim)
+
+
+def k_gdn_conv(g, x, y, state, lines, cu, w, bias, seqs, rows, conv_dim, width, x_stride, line_bytes):
     from .ops import gdn as G
 
     wt = _f(w[: conv_dim * width].view(conv_dim, width))
-    for s in range(g[0]):
+    for s in range(seqs):
         r0, r1 = _rows_of(cu, s)
         if r1 <= r0:
             continue
         ln = int(lines[s])
-        win = state[ln * line_bytes: ln * line_bytes + (width - 1) * conv_dim * 2].view(torch.bfloat16).view(width - 1, conv_dim)
-        hist = _f(win) if ln > 0 else torch.zeros(width - 1, conv_dim)
+        hist = _f(_gdn_window(state, ln, line_bytes, width, conv_dim)) if ln > 0 else torch.zeros(width - 1, conv_dim)
         xs = _f(torch.as_strided(x, (r1 - r0, conv_dim), (x_stride, 1), x.storage_offset() + r0 * x_stride))
-        out, new = G.conv_ref(xs, hist, wt, _f(bias[:conv_dim]) if isinstance(bias, torch.Tensor) else None)
+        out, _ = G.conv_ref(xs, hist, wt, _f(bias[:conv_dim]) if isinstance(bias, torch.Tensor) else None)
         y[r0 * conv_dim: r1 * conv_dim] = out.to(torch.bfloat16).reshape(-1)
-        if ln > 0:
-            win.copy_(new.to(torch.bfloat16))
+
+
+def k_gdn_conv_state(g, x, state, lines, cu, seqs, conv_dim, width, x_stride, line_bytes):
+    for s in range(g[0]):
+        r0, r1 = _rows_of(cu, s)
+        ln = int(lines[s])
+        if r1 <= r0 or ln <= 0:
+            continue
+        win = _gdn_window(state, ln, line_bytes, width, conv_dim)
+        xs = torch.as_strided(x, (r1 - r0, conv_dim), (x_stride, 1), x.storage_offset() + r0 * x_stride)
+        full = torch.cat([win.clone(), xs], 0)
+        win.copy_(full[full.shape[0] - (width - 1):])
 
 
 def _gdn_rule(dim):
@@ -281,7 +294,7 @@ CPU_KERNELS = {
     "kern_last_row": k_last_row, "kern_argmax_partial_bf16": k_argmax_partial, "kern_argmax_partial_f32": k_argmax_partial,
     "kern_argmax_final_i64": k_argmax_final, "kern_sample_bf16": k_sample, "kern_sample_f32": k_sample,
     "kern_silu_mul_bf16": k_silu_mul, "kern_copy_rows": k_copy_rows, "kern_sigmoid_mul_bf16": k_sigmoid_mul,
-    "kern_gdn_conv_bf16": k_gdn_conv, "kern_gdn_rule_k128_v128": _gdn_rule(128), "kern_gdn_rule_k64_v64": _gdn_rule(64),
+    "kern_gdn_conv_bf16": k_gdn_conv, "kern_gdn_conv_state": k_gdn_conv_state, "kern_gdn_rule_k128_v128": _gdn_rule(128), "kern_gdn_rule_k64_v64": _gdn_rule(64),
     "kern_gdn_rule_k32_v32": _gdn_rule(32), "kern_gdn_gate_norm_bf16": k_gdn_gate_norm,
     "kern_fill_f32": k_fill, "kern_fill_i32": k_fill, "kern_fill_i64": k_fill, "kern_fill_u8": k_fill,
 }

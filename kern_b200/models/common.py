@@ -418,26 +418,26 @@ def gdn_line_bytes(hk: int, hv: int, dk: int, dv: int, width: int = 4) -> tuple[
 
 
 def gdn_conv_op(conv_dim: int, width: int, x_stride: int, line_bytes: int, ragged: bool) -> dict:
-    """Causal conv + SiLU over the first `conv_dim` channels of a row, window kept in the state line.
-    Interface [x, y, state, lines, (cu_seqlens,) w]."""
+    """Causal conv + SiLU over the first `conv_dim` channels of a row (row-parallel), then the windows kept in the
+    state lines advance. Interface [x, y, state, lines, (cu_seqlens,) w, seqs, rows]."""
     iface = ["in buffer<bf16>", "out buffer<bf16>", "inout state", "in buffer<i32>"]
-    lp = list(iface)
-    args = [{"param": i} for i in range(4)]
     if ragged:
         iface.append("in buffer<i32>")
-        lp.append("in buffer<i32>")
-        args.append({"param": 4})
-    else:
-        lp.append("i64")
-        args.append({"i64": 0})
-    iface.append("in buffer<bf16>")
-    w_at = len(iface) - 1
-    lp += ["in buffer<bf16>", "i64", "i32", "i32", "i32", "i32", "i64"]
-    args += [{"param": w_at}, {"i64": 0}, {"i32": I32_MAX}, {"i32": conv_dim}, {"i32": width}, {"i32": x_stride},
-             {"i64": line_bytes}]
-    return {"params": iface, "impl": {"launches": [{
-        "module": "gdn", "entry": "kern_gdn_conv_bf16", "block": [256, 1, 1], "grid": ["seqs", -(-conv_dim // 256), 1],
-        "params": lp, "args": args}]}}
+    iface += ["in buffer<bf16>", "i32", "i32"]
+    w_at = len(iface) - 3
+    cu_t, cu_a = ("in buffer<i32>", {"param": 4}) if ragged else ("i64", {"i64": 0})
+    conv = {"module": "gdn", "entry": "kern_gdn_conv_bf16", "block": [256, 1, 1],
+            "grid": [{"ceil_div": ["tokens", 16]}, -(-conv_dim // 256), 1],
+            "params": ["in buffer<bf16>", "out buffer<bf16>", "in state", "in buffer<i32>", cu_t, "in buffer<bf16>", "i64",
+                       "i32", "i32", "i32", "i32", "i32", "i64"],
+            "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"param": 3}, cu_a, {"param": w_at}, {"i64": 0},
+                     {"param": w_at + 1}, {"param": w_at + 2}, {"i32": conv_dim}, {"i32": width}, {"i32": x_stride},
+                     {"i64": line_bytes}]}
+    upd = {"module": "gdn", "entry": "kern_gdn_conv_state", "block": [256, 1, 1], "grid": ["seqs", -(-conv_dim // 256), 1],
+           "params": ["in buffer<bf16>", "inout state", "in buffer<i32>", cu_t, "i32", "i32", "i32", "i32", "i64"],
+           "args": [{"param": 0}, {"param": 2}, {"param": 3}, cu_a, {"i32": I32_MAX}, {"i32": conv_dim}, {"i32": width},
+                    {"i32": x_stride}, {"i64": line_bytes}]}
+    return {"params": iface, "impl": {"launches": [conv, upd]}}
 
 
 def gdn_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_off: int, eps: float,

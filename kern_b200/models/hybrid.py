@@ -289,7 +289,7 @@ def build_manifest(cfg: HybridConfig) -> dict:
         calls = [
             {"op": "norm", "label": lbl + "ln1", "args": [B("x"), B(f"w.l{i}.ln1"), B("xn")]},
             {"op": "gdn_in", "label": lbl + "gdn_in", "args": [B("xn"), B(f"w.l{i}.gin"), B("gin"), {"var": "tokens"}, err]},
-            {"op": "gdn_conv" + sfx, "label": lbl + "conv", "args": [B("gin"), B("gconv"), st, B("lines"), *cu, B(f"w.l{i}.conv")]},
+            {"op": "gdn_conv" + sfx, "label": lbl + "conv", "args": [B("gin"), B("gconv"), st, B("lines"), *cu, B(f"w.l{i}.conv"), {"var": "seqs"}, {"var": "tokens"}]},
             {"op": "gdn_rule" + sfx, "label": lbl + "rule",
              "args": [B("gconv"), B("gin", cfg.conv_dim * 2), B("gout"), st, B("lines"), *cu, B(f"w.l{i}.alog"),
                       B(f"w.l{i}.dtb"), B(f"w.l{i}.gnorm")]},

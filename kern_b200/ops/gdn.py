@@ -21,6 +21,18 @@ def line_bytes(hk: int, hv: int, dk: int, dv: int, width: int = 4) -> tuple[int,
     return s_off + hv * dv * dk * 4, s_off
 
 
+def conv(x, y, state, lines, cu_q, w, bias, seqs, conv_dim, width, line_b, rows=None):
+    """Causal conv + SiLU over the rows of the call (row-parallel), then the state windows advance."""
+    k = Kernels.get(x.device)
+    rows = x.shape[0] if rows is None else rows
+    k.launch("gdn", "kern_gdn_conv_bf16", ((rows + 15) // 16, (conv_dim + 255) // 256), (256,),
+             [ptr(x), ptr(y), ptr(state), ptr(lines), ptr(cu_q), ptr(w), ptr(bias), i32(seqs), i32(rows), i32(conv_dim),
+              i32(width), i32(x.stride(0)), i64(line_b)])
+    k.launch("gdn", "kern_gdn_conv_state", (seqs, (conv_dim + 255) // 256), (256,),
+             [ptr(x), ptr(state), ptr(lines), ptr(cu_q), i32(seqs), i32(conv_dim), i32(width), i32(x.stride(0)), i64(line_b)])
+    return y
+
+
 def rule(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv, z_off, b_off, a_off,
          line_b, s_off, eps=1e-6, o_raw=None):
     """Gated delta rule (value rows split over CTAs, state in registers) then the gated RMSNorm."""

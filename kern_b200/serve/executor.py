@@ -91,7 +91,10 @@ def serve_rank(head: tuple[str, int], rank: int, world: int, make_runtime, watch
     ex = Executor(rt)
     log.info("rank ready rank=%d pages=%d slots=%d", rank, rt.pages, rt.slots)
     while True:
-        order = wire.recv(sock)
+        try:
+            order = wire.recv(sock)
+        except (ConnectionError, OSError):      # the head went away: same as a clean close
+            return
         if order is None:
             return
         try:

@@ -93,3 +93,36 @@ def test_chunked_prefill_equals_whole(tiny):
     lb = rt.tensor("logits")[0].float()
     assert a[0] == b[0]
     assert torch.allclose(la, lb, atol=0.06, rtol=0.05)
+
+
+@pytest.mark.parametrize("lined", [False, True])
+def test_integer_model_served_on_gpu_equals_twin(cuda, lined):
+    """The exact integer model through the native runtime, CUDA graphs, prefix cache and state slots."""
+    import random
+
+    from kern_b200.engine import Engine
+    from kern_b200.models import toy_int
+    from kern_b200.runtime import Runtime
+    from kern_b200.serve.scheduler import Request, Scheduler
+
+    rt = Runtime(toy_int.build_manifest(lined), tokens=16 * 40, slots=12 if lined else 0)
+    sch = Scheduler(Engine(rt), chunk=24, max_seqs=4)
+    rng = random.Random(3)
+    base = [rng.randrange(256) for _ in range(70)]
+    waves = [[[rng.randrange(256) for _ in range(rng.randint(1, 60))] for _ in range(6)] + [base[:50]],
+             [base[:50] + [1, 2, 3], base[:33], base]]
+    reqs = []
+    for wave in waves:
+        new = [Request(id=str(len(reqs) + i), prompt=p, max_tokens=10, stop_ids=(toy_int.EOS,)) for i, p in enumerate(wave)]
+        reqs += new
+        for r in new:
+            sch.submit(r)
+        for _ in range(2000):
+            if sch.idle():
+                break
+            sch.step()
+        assert sch.idle()
+    rt.check_error()
+    for r in reqs:
+        assert [t for t in r.out if t != toy_int.EOS] == toy_int.generate(r.prompt, 10, lined), r.id
+    assert rt.graphs >= 1
