@@ -18,20 +18,19 @@ using namespace kern;
 // x: [tokens][x_stride] (the q|k|v channels are the first conv_dim of a row), y: [tokens][conv_dim]
 // w: [conv_dim][width] bf16, bias optional. cu_q: [seqs+1] row starts (nullptr: one row per sequence).
 // Every output row depends on at most width-1 earlier inputs, so rows are independent: grid
-// [ceil(rows / 16), ceil(conv_dim / 256)], block 256; a thread owns one channel and walks 16 consecutive rows,
+// [ceil(rows / rpc), ceil(conv_dim / 256)], block 256; a thread owns one channel and walks rpc consecutive rows
+// (16 for prefill chunks, 1 for decode rows),
 // carrying the last inputs in registers and re-seeding them from the state window at a sequence's first row.
 // The window itself is advanced afterwards by kern_gdn_conv_state (a separate launch: rows of one sequence may sit
 // in several CTAs, and none of them may see the window half-updated).
-constexpr int CONV_ROWS = 16;
-
 extern "C" __global__ void __launch_bounds__(256)
     kern_gdn_conv_bf16(const __nv_bfloat16* x, __nv_bfloat16* y, const uint8_t* state, const int* lines, const int* cu_q,
                        const __nv_bfloat16* w, const __nv_bfloat16* bias, int seqs, int rows, int conv_dim, int width,
-                       int x_stride, long long line_bytes) {
+                       int x_stride, long long line_bytes, int rpc) {
   pdl_wait();
   const int c = blockIdx.y * 256 + threadIdx.x;
   const int total = cu_q ? min(rows, cu_q[seqs]) : min(rows, seqs);
-  const int ra = blockIdx.x * CONV_ROWS, rb = min(total, ra + CONV_ROWS);
+  const int ra = blockIdx.x * rpc, rb = min(total, ra + rpc);
   if (c >= conv_dim || ra >= rb) return;
   float wt[4] = {0.f, 0.f, 0.f, 0.f};
   for (int j = 0; j < width; ++j) wt[j] = __bfloat162float(w[(size_t)c * width + j]);

@@ -210,7 +210,7 @@ def _gdn_window(state, line, line_bytes, width, conv_dim):
     return state[line * line_bytes: line * line_bytes + (width - 1) * conv_dim * 2].view(torch.bfloat16).view(width - 1, conv_dim)
 
 
-def k_gdn_conv(g, x, y, state, lines, cu, w, bias, seqs, rows, conv_dim, width, x_stride, line_bytes):
+def k_gdn_conv(g, x, y, state, lines, cu, w, bias, seqs, rows, conv_dim, width, x_stride, line_bytes, rpc):
     from .ops import gdn as G
 
     wt = _f(w[: conv_dim * width].view(conv_dim, width))

@@ -427,12 +427,12 @@ def gdn_conv_op(conv_dim: int, width: int, x_stride: int, line_bytes: int, ragge
     w_at = len(iface) - 3
     cu_t, cu_a = ("in buffer<i32>", {"param": 4}) if ragged else ("i64", {"i64": 0})
     conv = {"module": "gdn", "entry": "kern_gdn_conv_bf16", "block": [256, 1, 1],
-            "grid": [{"ceil_div": ["tokens", 16]}, -(-conv_dim // 256), 1],
+            "grid": [{"ceil_div": ["tokens", 16]} if ragged else "tokens", -(-conv_dim // 256), 1],
             "params": ["in buffer<bf16>", "out buffer<bf16>", "in state", "in buffer<i32>", cu_t, "in buffer<bf16>", "i64",
-                       "i32", "i32", "i32", "i32", "i32", "i64"],
+                       "i32", "i32", "i32", "i32", "i32", "i64", "i32"],
             "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"param": 3}, cu_a, {"param": w_at}, {"i64": 0},
                      {"param": w_at + 1}, {"param": w_at + 2}, {"i32": conv_dim}, {"i32": width}, {"i32": x_stride},
-                     {"i64": line_bytes}]}
+                     {"i64": line_bytes}, {"i32": 16 if ragged else 1}]}
     upd = {"module": "gdn", "entry": "kern_gdn_conv_state", "block": [256, 1, 1], "grid": ["seqs", -(-conv_dim // 256), 1],
            "params": ["in buffer<bf16>", "inout state", "in buffer<i32>", cu_t, "i32", "i32", "i32", "i32", "i64"],
            "args": [{"param": 0}, {"param": 2}, {"param": 3}, cu_a, {"i32": I32_MAX}, {"i32": conv_dim}, {"i32": width},

@@ -25,9 +25,10 @@ def conv(x, y, state, lines, cu_q, w, bias, seqs, conv_dim, width, line_b, rows=
     """Causal conv + SiLU over the rows of the call (row-parallel), then the state windows advance."""
     k = Kernels.get(x.device)
     rows = x.shape[0] if rows is None else rows
-    k.launch("gdn", "kern_gdn_conv_bf16", ((rows + 15) // 16, (conv_dim + 255) // 256), (256,),
+    rpc = 16 if cu_q is not None else 1
+    k.launch("gdn", "kern_gdn_conv_bf16", ((rows + rpc - 1) // rpc, (conv_dim + 255) // 256), (256,),
              [ptr(x), ptr(y), ptr(state), ptr(lines), ptr(cu_q), ptr(w), ptr(bias), i32(seqs), i32(rows), i32(conv_dim),
-              i32(width), i32(x.stride(0)), i64(line_b)])
+              i32(width), i32(x.stride(0)), i64(line_b), i32(rpc)])
     k.launch("gdn", "kern_gdn_conv_state", (seqs, (conv_dim + 255) // 256), (256,),
              [ptr(x), ptr(state), ptr(lines), ptr(cu_q), i32(seqs), i32(conv_dim), i32(width), i32(x.stride(0)), i64(line_b)])
     return y
