@@ -38,6 +38,15 @@ struct GemmCfg {
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 256;
 };
 
+// EPI 4 (tensor-parallel partial sums): instead of storing C, every row of the tile is pushed over NVLink into the
+// staging slot of the rank that will reduce it (the row dealing of the fused all-reduce kernel: row = j + i G,
+// owner = i % nranks, dense index (i / nranks) G + j, parity from that kernel's epoch of column j).
+struct ScatterArgs {
+  const unsigned long long* comm_peers = nullptr;   // every rank's staging buffer, mapped here
+  const uint32_t* epochs = nullptr;                 // the all-reduce kernel's per-column epochs (read only)
+  int rank = 0, nranks = 1, grid = 1, slot_rows = 0;
+};
+
 // GROUPED: the M tiles come from a device table of int4 {expert, first row, rows (<= BM), -} built by the MoE
 // planner (`tile_count` of them); A rows are the expert-sorted activations, B is a 3-D map [K, N, experts].
 // A tile's load may run into the next expert's rows; the epilogue stores only the tile's own rows.
@@ -45,7 +54,8 @@ template <int BN, int EPI, bool GROUPED = false>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
                                           void* Cv, const void* Rv,
                                           int M, int N, int K, int ldc, int* err,
-                                          const int* tile_table = nullptr, const int* tile_count = nullptr) {
+                                          const int* tile_table = nullptr, const int* tile_count = nullptr,
+                                          ScatterArgs sc = ScatterArgs()) {
   using Cfg = GemmCfg<BN>;
   constexpr int kStages = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -229,7 +239,29 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         tmem_ld_wait();
         const int col = n_blk * BN + c * 32;
         if (row < row_end) {
-          if constexpr (EPI == 0 || EPI == 2) {
+          if constexpr (EPI == 4) {
+            const int j = row % sc.grid, i = row / sc.grid;
+            const int owner = i % sc.nranks, idx = (i / sc.nranks) * sc.grid + j;
+            if (idx >= sc.slot_rows) {
+              set_error(err, ERR_BOUNDS);
+            } else {
+              const uint32_t parity = (sc.epochs[j] + 1) & 1;
+              const size_t slot_elems = (size_t)sc.slot_rows * N;
+              __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(sc.comm_peers[owner]) +
+                                 parity * ((size_t)sc.nranks * slot_elems) + sc.rank * slot_elems + (size_t)idx * N + col;
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                if (col + v * 8 < N) {
+                  uint4 o;
+                  o.x = pack_bf16x2(__uint_as_float(r[v * 8]), __uint_as_float(r[v * 8 + 1]));
+                  o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                  o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                  o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                  *reinterpret_cast<uint4*>(C + v * 8) = o;
+                }
+              }
+            }
+          } else if constexpr (EPI == 0 || EPI == 2) {
             __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(Cv) + (size_t)row * ldc + col;
             const __nv_bfloat16* R =
                 reinterpret_cast<const __nv_bfloat16*>(Rv) + (size_t)row * ldc + col;
@@ -277,6 +309,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
   }
 
   // ---------------- teardown ----------------
+  if constexpr (EPI == 4) __threadfence_system();   // the pushed rows are on their way before the kernel is done
   pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();

@@ -13,6 +13,8 @@
 //   mode 1 (two-shot, many rows): rows are dealt to owners inside each CTA; push each partial row to its
 //          owner only, the owner reduces (+ residual) and pushes the new x row to every peer, then every
 //          rank normalises all of its CTA's rows locally. Link bytes: 2 (N-1)/N of the message.
+//   mode 2 (fused with the GEMM): as mode 1, but the partial rows were pushed to their owners by the epilogue of
+//          the tensor-parallel GEMM launched just before (tp_gemm.cu); `partial` is not read.
 //
 // Reference counterpart: tools/kernels-src/peer_allreduce.cu:196-334 (one-shot Lamport and two-shot
 // f32 all-reduce; its authors list the fused residual + RMSNorm tail and bf16 partials as not done) and
@@ -83,8 +85,8 @@ extern "C" __global__ void __launch_bounds__(kThreads)
   const size_t parity_elems = (size_t)nranks * slot_elems;
   const int my_rows = rows > j ? (rows - j + G - 1) / G : 0;   // rows j, j+G, ... of this CTA
 
-  // ---- phase 1: push partial rows ----
-  for (int i = 0; i < my_rows; ++i) {
+  // ---- phase 1: push partial rows (mode 2: the GEMM before this kernel already did, tile by tile) ----
+  for (int i = 0; i < (mode == 2 ? 0 : my_rows); ++i) {
     const int row = j + i * G;
     const uint4* src = reinterpret_cast<const uint4*>(partial + (size_t)row * hidden);
     if (mode == 0) {
@@ -122,7 +124,7 @@ extern "C" __global__ void __launch_bounds__(kThreads)
     for (int i = 0; i < my_rows; ++i) {
       const int row = j + i * G;
       int idx = row;
-      if (mode == 1) {
+      if (mode >= 1) {
         if (i % nranks != rank) continue;   // not my row to reduce
         idx = (i / nranks) * G + j;
       }
@@ -147,7 +149,7 @@ extern "C" __global__ void __launch_bounds__(kThreads)
       }
     }
   }
-  if (mode == 1) {
+  if (mode >= 1) {
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x < nranks)
@@ -170,7 +172,7 @@ extern "C" __global__ void __launch_bounds__(kThreads)
     float ss = 0.f;
     for (int v = threadIdx.x; v < nv; v += kThreads) {
       float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      add8(f, mode == 1 ? ld_volatile16(xr + v) : xr[v]);
+      add8(f, mode >= 1 ? ld_volatile16(xr + v) : xr[v]);
 #pragma unroll
       for (int e = 0; e < 8; ++e) { rowbuf[v * 8 + e] = f[e]; ss += f[e] * f[e]; }
     }

@@ -366,8 +366,9 @@ def tp_slot_rows(rows_max: int, nranks: int, grid: int = TP_GRID) -> int:
 
 
 def tp_allreduce_norm_op(hidden: int, eps: float, nranks: int, rows_max: int, group: str = "tp",
-                         plus_one: bool = False, timeout_ns: int = 2_000_000_000) -> dict:
+                         plus_one: bool = False, timeout_ns: int = 2_000_000_000, fused_gemm: bool = False) -> dict:
     """x += sum over the group of `partial`; xn = rmsnorm(x) * w — one kernel over NVLink peer memory.
+    `fused_gemm`: above TP_ONESHOT_ROWS rows the partials were already pushed by tp_gemm_reduce_op's epilogue.
     Interface [partial, x, x_peers, xn, w, comm, comm_peers, flags, flag_peers, epochs, err, rows]."""
     slot_rows = tp_slot_rows(rows_max, nranks)
     iface = ["in buffer<bf16>", "inout buffer<bf16>", "in buffer<u64>", "out buffer<bf16>", "in buffer<bf16>",
@@ -378,7 +379,7 @@ def tp_allreduce_norm_op(hidden: int, eps: float, nranks: int, rows_max: int, gr
     # few rows: one-shot on a grid no larger than the rows (every CTA of the grid exchanges flags);
     # many rows: two-shot on the full grid
     for mode, grid, lo, hi in ((0, 16, 1, min(16, rows_max)), (0, TP_ONESHOT_ROWS, 17, min(TP_ONESHOT_ROWS, rows_max)),
-                               (1, TP_GRID, TP_ONESHOT_ROWS + 1, rows_max)):
+                               (2 if fused_gemm else 1, TP_GRID, TP_ONESHOT_ROWS + 1, rows_max)):
         if lo > hi:
             continue
         when = {"var": "tokens"}
@@ -394,6 +395,44 @@ def tp_allreduce_norm_op(hidden: int, eps: float, nranks: int, rows_max: int, gr
         if len(when) > 1:
             launch["when"] = when
         launches.append(launch)
+    return {"params": iface, "impl": {"launches": launches}}
+
+
+def tp_gemm_reduce_op(n: int, k: int, nranks: int, rows_max: int, group: str = "tp") -> dict:
+    """A tensor-parallel partial GEMM feeding the fused all-reduce. Up to TP_ONESHOT_ROWS rows it stores the partial
+    (the one-shot all-reduce pushes it); above, its epilogue pushes every row over NVLink straight into the reducing
+    rank's staging slot, and the all-reduce runs in mode 2 (reduce + residual + norm + gather only).
+    Interface [a, w, part, comm_peers, epochs, rows, err]."""
+    slot_rows = tp_slot_rows(rows_max, nranks)
+    iface = ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<u64>", "in buffer<u32>", "i32", "out buffer<i32>"]
+    a_map = {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+        "param": 0, "dtype": "bf16", "dims": [k, 0], "strides": [k * 2], "box": [BK, BM], "swizzle": 128, "l2_promotion": 256}}]}}
+    b_map = lambda bn: {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+        "param": 1, "dtype": "bf16", "dims": [k, n], "strides": [k * 2], "box": [BK, bn], "swizzle": 128, "l2_promotion": 256}}]}}
+    launches = []
+    small = min(TP_ONESHOT_ROWS, rows_max)
+    for bn, lo, hi in gemm_ranges(n, small):
+        when = {"var": "tokens", "max": hi}
+        if lo > 1:
+            when["min"] = lo
+        launches.append({"module": "gemm_bf16", "entry": f"kern_gemm_bf16_tn_n{bn}", "block": [192, 1, 1], "grid": [SMS, 1, 1],
+                         "shared_mem": gemm_smem(bn), "when": when,
+                         "params": ["bytes<128>", "bytes<128>", "out buffer<bf16>", "i64", "i32", "i32", "i32", "i32", "out buffer<i32>"],
+                         "args": [a_map, b_map(bn), {"param": 2}, {"i64": 0}, {"param": 5}, {"i32": n}, {"i32": k}, {"i32": n},
+                                  {"param": 6}]})
+    for bn, lo, hi in gemm_ranges(n, rows_max):
+        lo = max(lo, small + 1)
+        if lo > hi:
+            continue
+        when = {"var": "tokens", "min": lo}
+        if hi < rows_max:
+            when["max"] = hi
+        launches.append({"module": "tp_gemm", "entry": f"kern_tp_gemm_scatter_bf16_n{bn}", "block": [192, 1, 1], "grid": [SMS, 1, 1],
+                         "shared_mem": gemm_smem(bn), "when": when,
+                         "params": ["bytes<128>", "bytes<128>", "i32", "i32", "i32", "out buffer<i32>", "in buffer<u64>",
+                                    "in buffer<u32>", "i32", "i32", "i32", "i32"],
+                         "args": [a_map, b_map(bn), {"param": 5}, {"i32": n}, {"i32": k}, {"param": 6}, {"param": 3}, {"param": 4},
+                                  {"rank": group}, {"i32": nranks}, {"i32": TP_GRID}, {"i32": slot_rows}]})
     return {"params": iface, "impl": {"launches": launches}}
 
 

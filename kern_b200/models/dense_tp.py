@@ -13,7 +13,9 @@ from . import common as C
 from .dense import DenseConfig
 
 
-def build_manifest_tp(cfg: DenseConfig) -> dict:
+def build_manifest_tp(cfg: DenseConfig, fused: bool = True) -> dict:
+    """`fused`: the o/down projections push their partial rows to the reducing rank from the GEMM epilogue
+    (GEMM + reduce-scatter in one kernel); off, they store the partial and the all-reduce kernel pushes it."""
     n = cfg.tp
     assert n >= 2 and cfg.heads % n == 0 and cfg.kv_heads % n == 0 and cfg.intermediate % (16 * n) == 0
     h, d = cfg.hidden, cfg.head_dim
@@ -73,9 +75,10 @@ def build_manifest_tp(cfg: DenseConfig) -> dict:
     ops["embed"] = C.embedding_op(h, cfg.vocab)
     ops["norm"] = C.rms_norm_op(h, cfg.eps)
     ops["qkv_proj"] = C.gemm_op(qkv_dim, h, rows_max=T)
-    ops["o_proj"] = C.gemm_op(h, qd, rows_max=T)                       # partial sums: reduced by the fused all-reduce
+    # partial sums: pushed to the reducing rank by the GEMM epilogue, finished by the fused all-reduce
+    ops["o_proj"] = C.tp_gemm_reduce_op(h, qd, n, T) if fused else C.gemm_op(h, qd, rows_max=T)
     ops["gate_up"] = C.gemm_op(2 * inter, h, epilogue="swiglu", rows_max=T)
-    ops["down_proj"] = C.gemm_op(h, inter, rows_max=T)
+    ops["down_proj"] = C.tp_gemm_reduce_op(h, inter, n, T) if fused else C.gemm_op(h, inter, rows_max=T)
     ops["lm_head"] = C.gemm_op(cfg.vocab, h, rows_var="seqs", rows_max=S)
     ops["rope_append"] = C.rope_append_op(hq, hk, d, d, cfg.page_size, cfg.max_context, cfg.eps, cfg.qk_norm)
     ops["attn_plan"] = C.attn_plan_op(hq, hk, S)
@@ -84,7 +87,7 @@ def build_manifest_tp(cfg: DenseConfig) -> dict:
     ops["last_row"] = C.last_row_op(h * 2)
     ops["rope_table"] = C.rope_table_op(cfg.max_context, d, cfg.rope_theta)
     ops["pick"] = C.argmax_op(cfg.vocab)
-    ops["allreduce_norm"] = C.tp_allreduce_norm_op(h, cfg.eps, n, T)
+    ops["allreduce_norm"] = C.tp_allreduce_norm_op(h, cfg.eps, n, T, fused_gemm=fused)
 
     B = lambda name: {"buf": name}
     err = B("error")
@@ -93,6 +96,8 @@ def build_manifest_tp(cfg: DenseConfig) -> dict:
         return {"op": "allreduce_norm", "label": label,
                 "args": [B("part"), B("x"), B("x_peers"), B("xn"), B(w), B("tp.comm"), B("tp.comm_peers"), B("tp.flags"),
                          B("tp.flags_peers"), B("tp.epochs"), err, {"var": "tokens"}]}
+
+    push = [B("tp.comm_peers"), B("tp.epochs")] if fused else []
 
     def layer(i: int, prefill: bool) -> list[dict]:
         kv = {"state": f"kv.l{i}"}
@@ -113,10 +118,10 @@ def build_manifest_tp(cfg: DenseConfig) -> dict:
                           "args": [B("qkv"), kv, B("attn"), B("block_table"), B("seq_lens"), err]})
         nxt = f"w.l{i + 1}.ln1" if i + 1 < cfg.layers else "w.norm"
         calls += [
-            {"op": "o_proj", "label": lbl + "o", "args": [B("attn"), B(f"w.l{i}.o"), B("part"), {"var": "tokens"}, err]},
+            {"op": "o_proj", "label": lbl + "o", "args": [B("attn"), B(f"w.l{i}.o"), B("part"), *push, {"var": "tokens"}, err]},
             ar(lbl + "ar_attn", f"w.l{i}.ln2"),
             {"op": "gate_up", "label": lbl + "gate_up", "args": [B("xn"), B(f"w.l{i}.gu"), B("act"), {"var": "tokens"}, err]},
-            {"op": "down_proj", "label": lbl + "down", "args": [B("act"), B(f"w.l{i}.down"), B("part"), {"var": "tokens"}, err]},
+            {"op": "down_proj", "label": lbl + "down", "args": [B("act"), B(f"w.l{i}.down"), B("part"), *push, {"var": "tokens"}, err]},
             ar(lbl + "ar_mlp", nxt),       # leaves the next layer's normed input (or the final norm) in xn
         ]
         return calls
@@ -137,7 +142,7 @@ def build_manifest_tp(cfg: DenseConfig) -> dict:
     prefill += [{"op": "last_row", "label": "last_row", "args": [B("xn"), B("last"), B("cu_seqlens")]}] + head("last")
     decode += head("xn")
 
-    mods = ["norm_embed", "gemm_bf16", "attn_prep", "attn_paged", "misc", "sampling", "tp_allreduce_norm"]
+    mods = ["norm_embed", "gemm_bf16", "attn_prep", "attn_paged", "misc", "sampling", "tp_allreduce_norm"] + (["tp_gemm"] if fused else [])
     return {
         "schema_version": 7,
         "model": f"{cfg.name}-tp{n}",

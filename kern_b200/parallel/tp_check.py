@@ -77,7 +77,7 @@ def allreduce_manifest(hidden, world, rows_max):
                          "step_graph": {"batch": {"groups": 1, "rows": "tokens"}, "graph": True, "calls": [call]}}}
 
 
-def check_model(rank, world):
+def check_model(rank, world, fused=True):
     from ..engine import Engine
     from ..models import dense, dense_tp
     from ..runtime import Runtime
@@ -87,7 +87,7 @@ def check_model(rank, world):
                             head_dim=64, intermediate=512 * world // 2, rope_theta=10000.0, page_size=16, max_tokens=256, max_seqs=8,
                             max_context=256, tp=world)
     weights = dense.random_weights(cfg, seed=0, std=0.05)
-    doc = dense_tp.build_manifest_tp(cfg)
+    doc = dense_tp.build_manifest_tp(cfg, fused=fused)
     rt = Runtime(doc, gpu=torch.cuda.current_device(), topology=group.topology(doc["topology"]["groups"], rank, world),
                  tokens=cfg.page_size * 64)
     rt.load_tensors(lambda name: weights[name].cuda())
@@ -141,6 +141,7 @@ def main(argv=None):
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--skip-model", action="store_true")
+    ap.add_argument("--unfused", action="store_true", help="the model check without the GEMM + reduce-scatter fusion")
     args = ap.parse_args(argv)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
@@ -162,10 +163,10 @@ def main(argv=None):
         if rank == 0:
             print(json.dumps({"check": "allreduce_time", "hidden": args.hidden, "world": world, "results": t}))
     if not args.skip_model:
-        m = check_model(rank, world)
+        m = check_model(rank, world, fused=not args.unfused)
         ok &= m["ok"]
         if rank == 0:
-            print(json.dumps({"check": "tp_model", "world": world, **m}))
+            print(json.dumps({"check": "tp_model", "world": world, "fused_gemm_reduce_scatter": not args.unfused, **m}))
     flag = torch.tensor([int(ok)], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()
