@@ -203,10 +203,18 @@ class Scheduler:
     # ---- one step ----
     def step(self) -> list[tuple[Request, list[int]]]:
         """Run one call; returns (request, new tokens) for every request that produced tokens."""
+        plan = self.plan()
+        if plan is None:
+            return []
+        return self.finish(plan, self.eng.step(plan["batch"], pad=plan["pad"]))
+
+    def plan(self) -> dict | None:
+        """Admit, then decide this step's call: {batch, kinds, pad, round}. None when there is nothing to run.
+        A tier that runs several schedulers in lockstep plans each, issues all calls at once, then finishes each."""
         t0 = time.monotonic()
         self._admit()
         if not self.running:
-            return []
+            return None
         batch, kinds = [], []
         budget = self.chunk
         decoding = [r for r in self.running if r.fed >= len(r.prompt)]
@@ -226,13 +234,17 @@ class Scheduler:
             batch.append((r.seq, [last] * (self.rows if use_round else 1)))
             kinds.append((r, "decode", 1))
         if not batch:
-            return []
+            return None
         pad = 0
         if not prefilling or not any(k[1] == "prefill" for k in kinds):
             # fixed-shape call: pad to a bucket with dead rows so captured graphs are reused
             want = bucket_for(len(batch), self.max_seqs)
             pad = want - len(batch)
-        toks = self.eng.step(batch, pad=pad)
+        return {"batch": batch, "kinds": kinds, "pad": pad, "round": use_round, "t0": t0}
+
+    def finish(self, plan: dict, toks) -> list[tuple[Request, list[int]]]:
+        """Account for the tokens the planned call emitted."""
+        kinds, use_round, t0 = plan["kinds"], plan["round"], plan["t0"]
         now = time.monotonic()
         emitted = []
         for (r, kind, n), got in zip(kinds, toks or [[]] * len(kinds)):

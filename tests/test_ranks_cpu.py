@@ -171,3 +171,50 @@ def test_a_rank_that_cannot_start_fails_the_head_fast():
 
     with pytest.raises(RuntimeError, match="rank 1 could not start"):
         executor.spawn_threads(2, maker, {"tp": 2}, timeout=20)
+
+
+def test_dp_tier_places_by_prefix_then_backlog_and_answers_exactly():
+    import random
+
+    from kern_b200.models import toy_int
+    from kern_b200.serve.dp import DpTier
+
+    doc = toy_int.build_manifest(False)
+
+    def maker(q):
+        def make():
+            rt = CpuRuntime(doc, tokens=16 * 40)
+            rt.offer = lambda: {}
+            rt.connect = lambda g, offers: None
+            return rt
+        return make
+
+    ex, _ = executor.spawn_threads(4, maker, {"tp": 1}, timeout=20)
+    probe = CpuRuntime(doc, tokens=16)
+    tier = DpTier(ex, probe.protocol, ex.hellos[0]["unit"], tp=1, chunk=32, max_seqs=3, patience=2)
+    rng = random.Random(0)
+    base = [rng.randrange(256) for _ in range(64)]
+    first = Request(id="a", prompt=base[:48], max_tokens=5, stop_ids=(toy_int.EOS,))
+    home = tier.submit(first)
+    while not tier.idle():
+        tier.step()
+    # a prompt sharing the prefix goes where the prefix lives; strangers spread over the least loaded replicas
+    again = Request(id="b", prompt=base[:48] + [3, 4, 5], max_tokens=5, stop_ids=(toy_int.EOS,))
+    assert tier.submit(again) == home
+    others = [Request(id=f"o{i}", prompt=[rng.randrange(256) for _ in range(20)], max_tokens=5, stop_ids=(toy_int.EOS,)) for i in range(6)]
+    spots = [tier.submit(r) for r in others]
+    assert len(set(spots)) == 4 and max(spots.count(g) for g in range(4)) <= 2
+    # patience: when the home replica is far busier than the rest, the hit is given up
+    for i in range(4):
+        tier.scheds[home].submit(Request(id=f"x{i}", prompt=[1, 2, 3], max_tokens=2))
+    late = Request(id="c", prompt=base[:48] + [9], max_tokens=5, stop_ids=(toy_int.EOS,))
+    assert tier.submit(late) != home
+    for _ in range(500):
+        if tier.idle():
+            break
+        tier.step()
+    assert tier.idle()
+    for r in [first, again, late] + others:
+        assert [t for t in r.out if t != toy_int.EOS] == toy_int.generate(r.prompt, 5), r.id
+    assert tier.scheds[home].stats.prefix_hits >= 1
+    ex.close()
