@@ -208,7 +208,10 @@ std::vector<Manifest> cut_manifest(const Manifest& m, const std::vector<size_t>&
     for (size_t i = 0; i < at.back() && i < p.calls.size(); ++i)
       for (auto& a : accesses(m, p.calls[i])) {
         auto bi = m.buffers.find(*a.buf);
-        if (a.writes && bi != m.buffers.end() && (bi->second.kind == BufferKind::Output || bi->second.kind == BufferKind::Carry))
+        // the error word is every stage's own: each keeps it as its output and the head reads them all
+        const bool error_word = bi != m.buffers.end() && bi->second.fill && *bi->second.fill == Fill::Error;
+        if (a.writes && !error_word && bi != m.buffers.end() &&
+            (bi->second.kind == BufferKind::Output || bi->second.kind == BufferKind::Carry))
           errs.push_back("program `" + *d.first + "` call " + std::to_string(i) + " writes " + kind_name(bi->second.kind) +
                          " buffer `" + *a.buf + "` before the last stage; a pipeline's outputs come from its last stage");
       }
