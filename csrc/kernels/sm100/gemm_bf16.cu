@@ -231,6 +231,63 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
             }
           }
         }
+      } else if constexpr (EPI == 4) {
+        // Rows go to the rank that reduces them. A lane first works out where its own row lands (once per tile);
+        // then, 64 columns at a time, the warp parks its 32 x 64 block in shared memory and writes it out four rows
+        // per instruction, eight lanes per row: every peer store covers a whole 128-byte line.
+        uint8_t* stage = smem + kStages * Cfg::kStageBytes + 512 + quarter * (32 * 144 + 256);
+        unsigned long long* rowptr = reinterpret_cast<unsigned long long*>(stage + 32 * 144);
+        {
+          unsigned long long dst = 0;
+          if (row < row_end) {
+            const int j = row % sc.grid, i = row / sc.grid;
+            const int owner = i % sc.nranks, idx = (i / sc.nranks) * sc.grid + j;
+            if (idx >= sc.slot_rows) {
+              set_error(err, ERR_BOUNDS);
+            } else {
+              const uint32_t parity = (sc.epochs[j] + 1) & 1;
+              const size_t slot_elems = (size_t)sc.slot_rows * N;
+              dst = sc.comm_peers[owner] +
+                    2ull * (parity * ((size_t)sc.nranks * slot_elems) + sc.rank * slot_elems + (size_t)idx * N);
+            }
+          }
+          rowptr[lane] = dst;
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_row + c * 64, r0);
+          tmem_ld_32x32(t_row + c * 64 + 32, r1);
+          tmem_ld_wait();
+          uint4* mine = reinterpret_cast<uint4*>(stage + lane * 144);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r0[v * 8]), __uint_as_float(r0[v * 8 + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r0[v * 8 + 2]), __uint_as_float(r0[v * 8 + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r0[v * 8 + 4]), __uint_as_float(r0[v * 8 + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r0[v * 8 + 6]), __uint_as_float(r0[v * 8 + 7]));
+            mine[v] = o;
+            o.x = pack_bf16x2(__uint_as_float(r1[v * 8]), __uint_as_float(r1[v * 8 + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r1[v * 8 + 2]), __uint_as_float(r1[v * 8 + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r1[v * 8 + 4]), __uint_as_float(r1[v * 8 + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r1[v * 8 + 6]), __uint_as_float(r1[v * 8 + 7]));
+            mine[4 + v] = o;
+          }
+          __syncwarp();
+          const int col = n_blk * BN + c * 64 + (lane & 7) * 8;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3);
+            const unsigned long long dst = rowptr[rr];
+            if (dst != 0 && col < N) {
+              const uint4 val = *reinterpret_cast<const uint4*>(stage + rr * 144 + (lane & 7) * 16);
+              *reinterpret_cast<uint4*>(dst + 2ull * col) = val;
+            }
+          }
+          __syncwarp();
+        }
       } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -239,29 +296,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         tmem_ld_wait();
         const int col = n_blk * BN + c * 32;
         if (row < row_end) {
-          if constexpr (EPI == 4) {
-            const int j = row % sc.grid, i = row / sc.grid;
-            const int owner = i % sc.nranks, idx = (i / sc.nranks) * sc.grid + j;
-            if (idx >= sc.slot_rows) {
-              set_error(err, ERR_BOUNDS);
-            } else {
-              const uint32_t parity = (sc.epochs[j] + 1) & 1;
-              const size_t slot_elems = (size_t)sc.slot_rows * N;
-              __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(sc.comm_peers[owner]) +
-                                 parity * ((size_t)sc.nranks * slot_elems) + sc.rank * slot_elems + (size_t)idx * N + col;
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                if (col + v * 8 < N) {
-                  uint4 o;
-                  o.x = pack_bf16x2(__uint_as_float(r[v * 8]), __uint_as_float(r[v * 8 + 1]));
-                  o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-                  o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-                  o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-                  *reinterpret_cast<uint4*>(C + v * 8) = o;
-                }
-              }
-            }
-          } else if constexpr (EPI == 0 || EPI == 2) {
+          if constexpr (EPI == 0 || EPI == 2) {
             __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(Cv) + (size_t)row * ldc + col;
             const __nv_bfloat16* R =
                 reinterpret_cast<const __nv_bfloat16*>(Rv) + (size_t)row * ldc + col;

@@ -428,7 +428,7 @@ def tp_gemm_reduce_op(n: int, k: int, nranks: int, rows_max: int, group: str = "
         if hi < rows_max:
             when["max"] = hi
         launches.append({"module": "tp_gemm", "entry": f"kern_tp_gemm_scatter_bf16_n{bn}", "block": [192, 1, 1], "grid": [SMS, 1, 1],
-                         "shared_mem": gemm_smem(bn), "when": when,
+                         "shared_mem": gemm_smem(bn) + 20480, "when": when,     # + the epilogue's row staging
                          "params": ["bytes<128>", "bytes<128>", "i32", "i32", "i32", "out buffer<i32>", "in buffer<u64>",
                                     "in buffer<u32>", "i32", "i32", "i32", "i32"],
                          "args": [a_map, b_map(bn), {"param": 5}, {"i32": n}, {"i32": k}, {"param": 6}, {"param": 3}, {"param": 4},
