@@ -304,13 +304,17 @@ def build_manifest(cfg: HybridConfig) -> dict:
             {"op": "pick", "label": "argmax", "args": [B("logits"), B("next_token")]},
         ]
 
-    prefill = [{"op": "embed", "label": "embed", "args": [B("token_ids"), B("w.embed"), B("x"), err]},
-               {"op": "attn_plan", "label": "plan", "args": [B("cu_seqlens"), B("work"), B("work_count"), {"var": "seqs"},
-                                                              {"expr": C.attn_plan_items(hq, hk)}, B("work_d"),
-                                                              B("work_d_count")]}]
+    prefill = [{"op": "embed", "label": "embed", "args": [B("token_ids"), B("w.embed"), B("x"), err]}]
+    # the attention work lists are planned right before the first attention layer, so a pipeline stage made only of
+    # linear-attention layers ahead of it neither receives nor forwards them
+    plan = {"op": "attn_plan", "label": f"l{fulls[0]}.plan",
+            "args": [B("cu_seqlens"), B("work"), B("work_count"), {"var": "seqs"}, {"expr": C.attn_plan_items(hq, hk)},
+                     B("work_d"), B("work_d_count")]}
     decode = [{"op": "embed", "label": "embed", "args": [B("token_ids"), B("w.embed"), B("x"), err]}]
     for i in range(cfg.layers):
         layer = full_layer if cfg.is_full(i) else gdn_layer
+        if i == fulls[0]:
+            prefill.append(plan)
         prefill += layer(i, True)
         decode += layer(i, False)
     prefill += [{"op": "last_row", "label": "last_row", "args": [B("x"), B("last"), B("cu_seqlens")]}] + head("last")
