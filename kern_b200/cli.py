@@ -280,7 +280,7 @@ def cmd_workload(args) -> int:
     """steps.parquet of a served run -> a weighted bench workload (buckets of groups x rows x context)."""
     import pyarrow.parquet as pq
 
-    t = pq.read_table(args.steps).to_pydict()
+    t = pq.ParquetFile(args.steps).read().to_pydict()      # the file alone: no partition columns from its path
     buckets: dict[tuple, float] = {}
     for g, r, c, ms in zip(t["groups"], t["rows"], t["context"], t.get("device_ms", [1.0] * len(t["groups"]))):
         key = (int(g), int(r), 1 << max(0, int(c) - 1).bit_length())

@@ -1,0 +1,164 @@
+"""Step and kernel traces as Parquet, NVML counters, and the hooks that feed them.
+
+Files: ``<dir>/date=YYYY-MM-DD/rank=<q>/HHMMSS.{steps,kernels,counters}.parquet`` (zstd). A file holds what was
+recorded since the last rotate; ``rotate()`` closes the open batch (a quarter-hour timer or ``POST /kern/trace/rotate``).
+
+  steps     seq, t_ns, program, groups, rows, context, graph, device_us, host_us, launches
+  kernels   seq, call, label, op, start_us, end_us, launches          (per labelled call of a timed step)
+  counters  t_ns, sm_mhz, mem_mhz, gpu_util, mem_util, power_w        (read-only NVML samples)
+
+Timing is by CUDA events on the runtime's stream (device time) — a software-timestamp path that needs no profiler
+attached. ``kern workload`` turns steps.parquet into a weighted bench workload.
+Reference counterpart: crates/kern-trace/src/lib.rs:154-204 (schemas), :286-390 (Recorder),
+crates/kern-runtime/src/trace.rs:226-283 (folding launches into steps), crates/kern-runtime/src/counters.rs:93-214.
+"""
+from __future__ import annotations
+
+import threading
+import time
+from datetime import datetime, timezone
+from pathlib import Path
+
+STEP_FIELDS = ("seq", "t_ns", "program", "groups", "rows", "context", "graph", "device_us", "host_us", "launches")
+KERNEL_FIELDS = ("seq", "call", "label", "op", "start_us", "end_us", "launches")
+COUNTER_FIELDS = ("t_ns", "sm_mhz", "mem_mhz", "gpu_util", "mem_util", "power_w")
+
+
+def shape_of(groups: int, rows: int) -> str:
+    """The shape class a step is counted under: decode (one row per sequence), round (a few), prefill (many)."""
+    per = rows / max(1, groups)
+    return "decode" if per <= 1 else ("round" if per <= 16 else "prefill")
+
+
+class Recorder:
+    def __init__(self, directory: str | Path, rank: int = 0, clock=time.time_ns):
+        self.dir, self.rank, self.clock = Path(directory), rank, clock
+        self._lock = threading.Lock()
+        self._rows = {"steps": [], "kernels": [], "counters": []}
+        self.seq = 0
+        self.dropped = 0
+        self.written: list[Path] = []
+
+    # ---- feeding ----
+    def step(self, program: str, groups: int, rows: int, context: int, graph: bool, device_us: float, host_us: float,
+             launches: int, calls=None) -> int:
+        """One runtime call. `calls`: [(label, op, ms, launches)] of a timed (eager, per-call events) step."""
+        with self._lock:
+            self.seq += 1
+            seq = self.seq
+            self._rows["steps"].append((seq, self.clock(), program, groups, rows, context, bool(graph), float(device_us),
+                                        float(host_us), int(launches)))
+            at = 0.0
+            for i, (label, op, ms, n) in enumerate(calls or []):
+                self._rows["kernels"].append((seq, i, label or "", op, at, at + ms * 1e3, int(n)))
+                at += ms * 1e3
+        return seq
+
+    def counters(self, sm_mhz: int, mem_mhz: int, gpu_util: int, mem_util: int, power_w: float) -> None:
+        with self._lock:
+            self._rows["counters"].append((self.clock(), sm_mhz, mem_mhz, gpu_util, mem_util, power_w))
+
+    # ---- files ----
+    def _path(self, kind: str, now: datetime) -> Path:
+        d = self.dir / f"date={now:%Y-%m-%d}" / f"rank={self.rank}"
+        d.mkdir(parents=True, exist_ok=True)
+        return d / f"{now:%H%M%S}.{kind}.parquet"
+
+    def rotate(self) -> list[Path]:
+        """Write what is buffered and start afresh; returns the files written."""
+        import pyarrow as pa
+        import pyarrow.parquet as pq
+
+        with self._lock:
+            rows, self._rows = self._rows, {"steps": [], "kernels": [], "counters": []}
+        now = datetime.now(timezone.utc)
+        out = []
+        for kind, fields in (("steps", STEP_FIELDS), ("kernels", KERNEL_FIELDS), ("counters", COUNTER_FIELDS)):
+            if not rows[kind]:
+                continue
+            cols = list(zip(*rows[kind]))
+            table = pa.table({f: list(c) for f, c in zip(fields, cols)})
+            path = self._path(kind, now)
+            n = 0
+            while path.exists():          # two rotates inside one second
+                n += 1
+                path = path.with_name(f"{now:%H%M%S}-{n}.{kind}.parquet")
+            pq.write_table(table, path, compression="zstd", compression_level=3, use_dictionary=["program", "label", "op"]
+                           if kind != "counters" else False)
+            out.append(path)
+        self.written += out
+        return out
+
+    close = rotate
+
+
+class Counters(threading.Thread):
+    """Samples NVML (read only: clocks, utilisation, power) into a recorder every `period` seconds."""
+
+    def __init__(self, recorder: Recorder, gpu: int = 0, period: float = 0.2, nvml=None):
+        super().__init__(name="kern-counters", daemon=True)
+        self.rec, self.gpu, self.period = recorder, gpu, max(0.00005, period)
+        self._halt = threading.Event()
+        self.nvml = nvml
+
+    def run(self) -> None:
+        nv = self.nvml
+        if nv is None:
+            import pynvml as nv
+        nv.nvmlInit()
+        h = nv.nvmlDeviceGetHandleByIndex(self.gpu)
+        while not self._halt.wait(self.period):
+            try:
+                u = nv.nvmlDeviceGetUtilizationRates(h)
+                self.rec.counters(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_MEM),
+                                  u.gpu, u.memory, nv.nvmlDeviceGetPowerUsage(h) / 1000.0)
+            except Exception:
+                self.rec.dropped += 1
+
+    def stop(self) -> None:
+        self._halt.set()
+
+
+class TracedEngine:
+    """Wraps an engine: every step is recorded (device time by CUDA events on the runtime's stream when there is a
+    GPU, host time always); every `sample_every`-th step runs eagerly with per-call events so kernels.parquet gets
+    the cost by call."""
+
+    def __init__(self, engine, recorder: Recorder, sample_every: int = 0):
+        self.eng, self.rec, self.sample_every = engine, recorder, sample_every
+        self._n = 0
+
+    def __getattr__(self, name):
+        return getattr(self.eng, name)
+
+    def step(self, batch, **kw):
+        self._n += 1
+        timed = bool(self.sample_every) and self._n % self.sample_every == 0 and hasattr(self.eng.rt, "issue_timed")
+        groups = len(batch) + kw.get("pad", 0)
+        rows = sum(len(t) for _, t in batch) + kw.get("pad", 0) * (len(batch[0][1]) if batch else 0)
+        context = max((s.length + len(t) for s, t in batch), default=0)
+        ev = None
+        try:
+            import torch
+            if torch.cuda.is_available() and hasattr(self.eng.rt, "stream"):
+                st = torch.cuda.ExternalStream(self.eng.rt.stream)
+                ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), st)
+                ev[0].record(st)
+        except Exception:
+            ev = None
+        t0 = time.perf_counter()
+        out = self.eng.step(batch, timed=timed, **kw) if timed else self.eng.step(batch, **kw)
+        host_us = (time.perf_counter() - t0) * 1e6
+        device_us = 0.0
+        if ev is not None:
+            ev[1].record(ev[2])
+            ev[1].synchronize()
+            device_us = ev[0].elapsed_time(ev[1]) * 1e3
+        fw = self.eng.forward_for(groups, [len(t) for _, t in batch] + [len(batch[0][1])] * kw.get("pad", 0))
+        self.rec.step(fw["name"], groups, rows, context, bool(fw.get("graph")) and not timed, device_us, host_us,
+                      getattr(self.eng, "last_launches", 0), getattr(self.eng, "last_times", None) if timed else None)
+        return out
+
+
+def prometheus_lines(recorder: Recorder, steps_by: dict | None = None) -> list[str]:
+    return ["# TYPE kern_trace_dropped_records_total counter", f"kern_trace_dropped_records_total {recorder.dropped}"]
