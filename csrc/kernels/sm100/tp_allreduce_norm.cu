@@ -215,3 +215,120 @@ extern "C" __global__ void kern_peer_barrier(uint32_t* flags, const unsigned lon
     if (!wait_flag(flags + threadIdx.x, epoch, timeout_ns)) set_error(err, ERR_WAIT_PEER + threadIdx.x);
   }
 }
+
+// ---- one-shot all-reduce without flags (few rows: decode steps) ------------------------------------------------
+// The payload is its own arrival signal: every 16-bit word of a staging buffer starts as the poison 0x8000 (bf16 -0.0),
+// senders never store that value (a partial that is exactly -0.0 travels as +0.0, the same number), so a receiver just
+// polls the vector it needs until none of its eight words is poison. No flag write, no second round trip.
+// Three staging buffers rotate by the CTA's epoch: a call writes stage e % 3, reads it, and re-poisons its rows of
+// stage (e + 2) % 3 — the one the previous call used, which no peer writes again before it has consumed this call's
+// rows. grid = rows (CTA j owns row j, on every rank), block 256, dyn smem = hidden * 4.
+//   lamport : [3 stages][nranks slots][slot_rows][hidden] bf16 on every rank (exported, poisoned by a `once` fill)
+// Reference counterpart: tools/kernels-src/peer_allreduce.cu:196-259 (f32 payload, -0.0 poison, three stages).
+namespace {
+constexpr uint32_t kPoison2 = 0x80008000u;
+KERN_DEVICE bool has_poison(uint4 v) {
+  auto p = [](uint32_t w) { return (w & 0xffffu) == 0x8000u || (w >> 16) == 0x8000u; };
+  return p(v.x) || p(v.y) || p(v.z) || p(v.w);
+}
+KERN_DEVICE uint32_t scrub2(uint32_t w) {   // -0.0 -> +0.0 in either half
+  if ((w & 0xffffu) == 0x8000u) w &= 0xffff0000u;
+  if ((w >> 16) == 0x8000u) w &= 0x0000ffffu;
+  return w;
+}
+}  // namespace
+
+extern "C" __global__ void __launch_bounds__(kThreads)
+    kern_tp_allreduce_lamport(const __nv_bfloat16* partial, __nv_bfloat16* x, __nv_bfloat16* xn, const __nv_bfloat16* w,
+                              __nv_bfloat16* lamport, const unsigned long long* lamport_peers, uint32_t* epochs, int* err,
+                              int rank, int nranks, int rows, int hidden, int slot_rows, float eps, int plus_one,
+                              long long timeout_ns) {
+  extern __shared__ float rowbuf[];
+  __shared__ float red[32];
+  __shared__ int failed;
+  pdl_wait();
+  const int row = blockIdx.x;
+  if (row >= rows) return;
+  if (row >= slot_rows) { if (threadIdx.x == 0) set_error(err, ERR_BOUNDS); return; }
+  const int nv = hidden / 8;
+  if (threadIdx.x == 0) failed = 0;
+  const uint32_t epoch = epochs[row] + 1;
+  __syncthreads();
+  if (threadIdx.x == 0) epochs[row] = epoch;
+  const size_t slot_elems = (size_t)slot_rows * hidden;
+  const size_t stage_elems = (size_t)nranks * slot_elems;
+  const uint32_t stage = epoch % 3, clear = (epoch + 2) % 3;
+
+  // push my row into my slot of this stage on every rank (mine included)
+  const uint4* src = reinterpret_cast<const uint4*>(partial + (size_t)row * hidden);
+  for (int v = threadIdx.x; v < nv; v += kThreads) {
+    uint4 d = src[v];
+    d.x = scrub2(d.x); d.y = scrub2(d.y); d.z = scrub2(d.z); d.w = scrub2(d.w);
+    for (int p = 0; p < nranks; ++p) {
+      __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(lamport_peers[p]) + stage * stage_elems + rank * slot_elems;
+      reinterpret_cast<uint4*>(base + (size_t)row * hidden)[v] = d;
+    }
+  }
+  // re-poison my row of the stage used two calls from now
+  for (int r = 0; r < nranks; ++r) {
+    uint4* c = reinterpret_cast<uint4*>(lamport + clear * stage_elems + r * slot_elems + (size_t)row * hidden);
+    for (int v = threadIdx.x; v < nv; v += kThreads) c[v] = make_uint4(kPoison2, kPoison2, kPoison2, kPoison2);
+  }
+  // gather: poll each rank's vector until it is whole, sum in rank order, add the residual
+  const __nv_bfloat16* mine = lamport + stage * stage_elems;
+  uint4* xr = reinterpret_cast<uint4*>(x + (size_t)row * hidden);
+  float ss = 0.f;
+  const uint64_t t0 = globaltimer_ns();
+  for (int v = threadIdx.x; v < nv; v += kThreads) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    bool ok = true;
+    for (int r = 0; r < nranks && ok; ++r) {
+      const uint4* p = reinterpret_cast<const uint4*>(mine + r * slot_elems + (size_t)row * hidden) + v;
+      uint4 d = ld_volatile16(p);
+      while (has_poison(d)) {
+        if ((long long)(globaltimer_ns() - t0) > timeout_ns) {
+          set_error(err, ERR_WAIT_PEER + r);
+          failed = 1;
+          ok = false;
+          break;
+        }
+        d = ld_volatile16(p);
+      }
+      if (ok) add8(acc, d);
+    }
+    if (!ok) break;
+    uint4 s = pack8(acc);
+    float tot[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    add8(tot, s);
+    add8(tot, xr[v]);
+    const uint4 out = pack8(tot);
+    xr[v] = out;
+    float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    add8(f, out);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { rowbuf[v * 8 + e] = f[e]; ss += f[e] * f[e]; }
+  }
+  __syncthreads();
+  if (failed) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < kThreads / 32 ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  const float inv = rsqrtf(red[0] / (float)hidden + eps);
+  uint4* yr = reinterpret_cast<uint4*>(xn + (size_t)row * hidden);
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  for (int v = threadIdx.x; v < nv; v += kThreads) {
+    float ww[8] = {0, 0, 0, 0, 0, 0, 0, 0}, o[8];
+    add8(ww, wv[v]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = rowbuf[v * 8 + e] * inv * (plus_one ? ww[e] + 1.f : ww[e]);
+    yr[v] = pack8(o);
+  }
+  pdl_launch_dependents();
+}

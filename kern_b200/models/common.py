@@ -366,9 +366,12 @@ def tp_slot_rows(rows_max: int, nranks: int, grid: int = TP_GRID) -> int:
 
 
 def tp_allreduce_norm_op(hidden: int, eps: float, nranks: int, rows_max: int, group: str = "tp",
-                         plus_one: bool = False, timeout_ns: int = 2_000_000_000, fused_gemm: bool = False) -> dict:
+                         plus_one: bool = False, timeout_ns: int = 2_000_000_000, fused_gemm: bool = False,
+                         lamport: bool = False) -> dict:
     """x += sum over the group of `partial`; xn = rmsnorm(x) * w — one kernel over NVLink peer memory.
     `fused_gemm`: above TP_ONESHOT_ROWS rows the partials were already pushed by tp_gemm_reduce_op's epilogue.
+    `lamport`: up to TP_ONESHOT_ROWS rows use the flagless one-shot; the interface grows by [lamport, lamport_peers,
+    lamport_epochs] (buffers of `tp_buffers(..., lamport=True)`, poisoned once by `tp_lamport_init_op`).
     Interface [partial, x, x_peers, xn, w, comm, comm_peers, flags, flag_peers, epochs, err, rows]."""
     slot_rows = tp_slot_rows(rows_max, nranks)
     iface = ["in buffer<bf16>", "inout buffer<bf16>", "in buffer<u64>", "out buffer<bf16>", "in buffer<bf16>",
@@ -378,8 +381,27 @@ def tp_allreduce_norm_op(hidden: int, eps: float, nranks: int, rows_max: int, gr
     launches = []
     # few rows: one-shot on a grid no larger than the rows (every CTA of the grid exchanges flags);
     # many rows: two-shot on the full grid
+    if lamport:
+        # few rows: the flagless one-shot (payload is its own arrival signal), one CTA per row
+        iface += ["inout buffer<bf16>", "in buffer<u64>", "inout buffer<u32>"]
+        when = {"var": "tokens"}
+        if rows_max > TP_ONESHOT_ROWS:
+            when["max"] = TP_ONESHOT_ROWS
+        launch = {"module": "tp_allreduce_norm", "entry": "kern_tp_allreduce_lamport", "block": [256, 1, 1],
+                  "grid": ["tokens", 1, 1], "shared_mem": hidden * 4,
+                  "params": ["in buffer<bf16>", "inout buffer<bf16>", "out buffer<bf16>", "in buffer<bf16>", "inout buffer<bf16>",
+                             "in buffer<u64>", "inout buffer<u32>", "out buffer<i32>", "i32", "i32", "i32", "i32", "i32", "f32",
+                             "i32", "i64"],
+                  "args": [{"param": 0}, {"param": 1}, {"param": 3}, {"param": 4}, {"param": 12}, {"param": 13}, {"param": 14},
+                           {"param": 10}, {"rank": group}, {"i32": nranks}, {"param": 11}, {"i32": hidden},
+                           {"i32": TP_ONESHOT_ROWS}, {"f32": eps}, {"i32": int(plus_one)}, {"i64": timeout_ns}]}
+        if len(when) > 1:
+            launch["when"] = when
+        launches.append(launch)
     for mode, grid, lo, hi in ((0, 16, 1, min(16, rows_max)), (0, TP_ONESHOT_ROWS, 17, min(TP_ONESHOT_ROWS, rows_max)),
                                (2 if fused_gemm else 1, TP_GRID, TP_ONESHOT_ROWS + 1, rows_max)):
+        if lamport and mode == 0:
+            continue
         if lo > hi:
             continue
         when = {"var": "tokens"}
@@ -436,10 +458,23 @@ def tp_gemm_reduce_op(n: int, k: int, nranks: int, rows_max: int, group: str = "
     return {"params": iface, "impl": {"launches": launches}}
 
 
-def tp_buffers(hidden: int, nranks: int, rows_max: int, group: str = "tp") -> dict:
+def tp_lamport_init_op(hidden: int, nranks: int) -> dict:
+    """Poison the three Lamport stages (every 16-bit word 0x8000). Interface [lamport]."""
+    n_words = 3 * nranks * TP_ONESHOT_ROWS * hidden // 2
+    return {"params": ["out buffer<bf16>"], "impl": {"launches": [{
+        "module": "misc", "entry": "kern_fill_i32", "block": [256, 1, 1], "grid": [1184, 1, 1],
+        "params": ["out buffer<bf16>", "i64", "i32"], "args": [{"param": 0}, {"i64": n_words}, {"i32": -2147450880}]}]}}
+
+
+def tp_buffers(hidden: int, nranks: int, rows_max: int, group: str = "tp", lamport: bool = False) -> dict:
     """Exported staging / flag buffers of the fused all-reduce and their peer address tables."""
     slot_rows = tp_slot_rows(rows_max, nranks)
-    return {
+    extra = {}
+    if lamport:
+        extra = {"tp.lamport": {"dtype": "bf16", "shape": [3, nranks, TP_ONESHOT_ROWS, hidden], "kind": "carry", "export": True},
+                 "tp.lamport_peers": {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": "tp.lamport", "group": group},
+                 "tp.lamport_epochs": {"dtype": "u32", "shape": [TP_ONESHOT_ROWS], "kind": "carry"}}
+    return {**extra,
         "tp.comm": {"dtype": "bf16", "shape": [2, nranks, slot_rows, hidden], "kind": "carry", "export": True},
         "tp.comm_peers": {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": "tp.comm", "group": group},
         "tp.flags": {"dtype": "u32", "shape": [2, nranks, TP_GRID], "kind": "carry", "export": True},

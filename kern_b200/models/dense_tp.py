@@ -13,9 +13,10 @@ from . import common as C
 from .dense import DenseConfig
 
 
-def build_manifest_tp(cfg: DenseConfig, fused: bool = True) -> dict:
+def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True) -> dict:
     """`fused`: the o/down projections push their partial rows to the reducing rank from the GEMM epilogue
-    (GEMM + reduce-scatter in one kernel); off, they store the partial and the all-reduce kernel pushes it."""
+    (GEMM + reduce-scatter in one kernel); off, they store the partial and the all-reduce kernel pushes it.
+    `lamport`: decode-sized calls use the flagless one-shot all-reduce."""
     n = cfg.tp
     assert n >= 2 and cfg.heads % n == 0 and cfg.kv_heads % n == 0 and cfg.intermediate % (16 * n) == 0
     h, d = cfg.hidden, cfg.head_dim
@@ -45,7 +46,7 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True) -> dict:
     bufs["work_d_count"] = {"dtype": "i32", "shape": [1], "kind": "workspace"}
     bufs["rope_cos"] = {"dtype": "f32", "shape": [cfg.max_context, d // 2], "kind": "carry"}
     bufs["rope_sin"] = {"dtype": "f32", "shape": [cfg.max_context, d // 2], "kind": "carry"}
-    bufs.update(C.tp_buffers(h, n, T))
+    bufs.update(C.tp_buffers(h, n, T, lamport=lamport))
 
     def ranked(width: int) -> dict:
         return {"group": "tp", "ranges": [[r * width, (r + 1) * width] for r in range(n)]}
@@ -87,7 +88,9 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True) -> dict:
     ops["last_row"] = C.last_row_op(h * 2)
     ops["rope_table"] = C.rope_table_op(cfg.max_context, d, cfg.rope_theta)
     ops["pick"] = C.argmax_op(cfg.vocab)
-    ops["allreduce_norm"] = C.tp_allreduce_norm_op(h, cfg.eps, n, T, fused_gemm=fused)
+    if lamport:
+        ops["lamport_init"] = C.tp_lamport_init_op(h, n)
+    ops["allreduce_norm"] = C.tp_allreduce_norm_op(h, cfg.eps, n, T, fused_gemm=fused, lamport=lamport)
 
     B = lambda name: {"buf": name}
     err = B("error")
@@ -95,7 +98,8 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True) -> dict:
     def ar(label: str, w: str) -> dict:
         return {"op": "allreduce_norm", "label": label,
                 "args": [B("part"), B("x"), B("x_peers"), B("xn"), B(w), B("tp.comm"), B("tp.comm_peers"), B("tp.flags"),
-                         B("tp.flags_peers"), B("tp.epochs"), err, {"var": "tokens"}]}
+                         B("tp.flags_peers"), B("tp.epochs"), err, {"var": "tokens"}] +
+                        ([B("tp.lamport"), B("tp.lamport_peers"), B("tp.lamport_epochs")] if lamport else [])}
 
     push = [B("tp.comm_peers"), B("tp.epochs")] if fused else []
 
@@ -153,7 +157,8 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True) -> dict:
         "modules": C.modules_for(mods),
         "ops": ops,
         "programs": {
-            "load": {"once": True, "calls": [{"op": "rope_table", "args": [B("rope_cos"), B("rope_sin")]}]},
+            "load": {"once": True, "calls": [{"op": "rope_table", "args": [B("rope_cos"), B("rope_sin")]}] +
+                     ([{"op": "lamport_init", "args": [B("tp.lamport")]}] if lamport else [])},
             "prefill": {"batch": {"groups": S, "rows": "tokens"}, "calls": prefill},
             "decode": {"batch": {"groups": S, "rows": 1}, "graph": True, "calls": decode},
         },

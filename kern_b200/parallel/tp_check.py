@@ -53,7 +53,7 @@ def check_allreduce(rt, rank, world, rows_list, hidden, iters_graph=3):
     return results
 
 
-def allreduce_manifest(hidden, world, rows_max):
+def allreduce_manifest(hidden, world, rows_max, lamport=False):
     from ..models import common as C
 
     bufs = {"part": {"dtype": "bf16", "shape": ["tokens", hidden], "kind": "input"},
@@ -62,16 +62,19 @@ def allreduce_manifest(hidden, world, rows_max):
             "xn": {"dtype": "bf16", "shape": ["tokens", hidden], "kind": "output"},
             "w": {"dtype": "bf16", "shape": [hidden], "kind": "input"},
             "error": {"dtype": "i32", "shape": [1], "kind": "output"}}
-    bufs.update(C.tp_buffers(hidden, world, rows_max))
+    bufs.update(C.tp_buffers(hidden, world, rows_max, lamport=lamport))
     B = lambda n: {"buf": n}
     call = {"op": "allreduce_norm", "args": [B("part"), B("x"), B("x_peers"), B("xn"), B("w"), B("tp.comm"), B("tp.comm_peers"),
-                                             B("tp.flags"), B("tp.flags_peers"), B("tp.epochs"), B("error"), {"var": "tokens"}]}
+                                             B("tp.flags"), B("tp.flags_peers"), B("tp.epochs"), B("error"), {"var": "tokens"}] +
+            ([B("tp.lamport"), B("tp.lamport_peers"), B("tp.lamport_epochs")] if lamport else [])}
     return {"schema_version": 7, "model": "tp-allreduce-check",
             "vars": {"tokens": {"max": rows_max, "axis": "rows"}},
             "topology": {"groups": {"tp": world}}, "states": {}, "buffers": bufs,
-            "modules": C.modules_for(["tp_allreduce_norm"]),
-            "ops": {"allreduce_norm": C.tp_allreduce_norm_op(hidden, 1e-6, world, rows_max)},
+            "modules": C.modules_for(["tp_allreduce_norm"] + (["misc"] if lamport else [])),
+            "ops": {"allreduce_norm": C.tp_allreduce_norm_op(hidden, 1e-6, world, rows_max, lamport=lamport),
+                    **({"lamport_init": C.tp_lamport_init_op(hidden, world)} if lamport else {})},
             "programs": {"step": {"calls": [call]},
+                         **({"init": {"once": True, "calls": [{"op": "lamport_init", "args": [B("tp.lamport")]}]}} if lamport else {}),
                          # sixteen back-to-back calls in one graph: the per-call device time without launch gaps
                          "burst16": {"batch": {"groups": 1, "rows": "tokens"}, "graph": True, "calls": [call] * 16},
                          "step_graph": {"batch": {"groups": 1, "rows": "tokens"}, "graph": True, "calls": [call]}}}
@@ -141,6 +144,7 @@ def main(argv=None):
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--skip-model", action="store_true")
+    ap.add_argument("--no-lamport", action="store_true", help="decode-sized all-reduce through flags instead of the flagless one-shot")
     ap.add_argument("--unfused", action="store_true", help="the model check without the GEMM + reduce-scatter fusion")
     args = ap.parse_args(argv)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -151,7 +155,8 @@ def main(argv=None):
     from . import group
 
     rows_max = max(args.rows + [4096 if args.time else 1])
-    rt = Runtime(allreduce_manifest(args.hidden, world, rows_max), gpu=local, topology={"tp": (rank, world)})
+    rt = Runtime(allreduce_manifest(args.hidden, world, rows_max, lamport=not args.no_lamport), gpu=local,
+                 topology={"tp": (rank, world)})
     group.start(rt)
     ok = True
     res = check_allreduce(rt, rank, world, args.rows, args.hidden)
@@ -161,7 +166,8 @@ def main(argv=None):
     if args.time:
         t = time_allreduce(rt, world, [1, 8, 16, 32, 64, 256, 1024, 4096])
         if rank == 0:
-            print(json.dumps({"check": "allreduce_time", "hidden": args.hidden, "world": world, "results": t}))
+            print(json.dumps({"check": "allreduce_time", "hidden": args.hidden, "world": world, "lamport": not args.no_lamport,
+                              "results": t}))
     if not args.skip_model:
         m = check_model(rank, world, fused=not args.unfused)
         ok &= m["ok"]
