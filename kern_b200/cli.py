@@ -204,6 +204,24 @@ def cmd_run(args) -> int:
     return 0
 
 
+def cmd_e2e(args) -> int:
+    """`kern test e2e-logits record --manifest M --out REC` writes a recording; `kern test e2e-logits --manifest M REC`
+    judges this engine against it (exit 0 / 1)."""
+    from .testing import e2e
+    from .testing.abtest import EngineSide
+
+    side = EngineSide(make_runtime(args))
+    if args.record:
+        vocab = max((b.get("domain", {}).get("max", 0) for b in side.doc["buffers"].values() if b.get("fill") == "token"), default=255) + 1
+        qs = e2e.plan(args.seed, args.prompts, vocab, max_tokens=args.decode_steps)
+        e2e.record(side, qs, source=side.doc["model"], chunk=args.chunk or 256).save(args.out)
+        print(f"recorded {len(qs)} questions -> {args.out}")
+        return 0
+    text, code = e2e.summary(e2e.judge(e2e.Recording.load(args.recording), side, kl_limit=args.logit_kl, chunk=args.chunk or 256))
+    print(text)
+    return code
+
+
 def cmd_test(args) -> int:
     from .testing.abtest import EngineSide, run_test
 
@@ -336,18 +354,22 @@ def main(argv=None) -> int:
     t = sub.add_parser("test"); t.add_argument("a"); t.add_argument("b"); common(t, manifest=False)
     t.add_argument("--seed", type=int, default=0); t.add_argument("--prompts", type=int, default=4)
     t.add_argument("--decode-steps", type=int, default=8); t.add_argument("--logit-kl", type=float, default=0.01)
+    e = sub.add_parser("e2e-logits", help="record an engine's answers, or judge an engine against a recording")
+    common(e); e.add_argument("recording", nargs="?"); e.add_argument("--record", action="store_true"); e.add_argument("--out")
+    e.add_argument("--seed", type=int, default=0); e.add_argument("--prompts", type=int, default=8)
+    e.add_argument("--decode-steps", type=int, default=16); e.add_argument("--logit-kl", type=float, default=0.01)
     b = sub.add_parser("bench"); common(b); b.add_argument("--workload"); b.add_argument("--out")
     w = sub.add_parser("workload"); w.add_argument("steps"); w.add_argument("--out", required=True); w.add_argument("--samples", type=int, default=32)
     s = sub.add_parser("server"); common(s)
     s.add_argument("--host", default="127.0.0.1"); s.add_argument("--port", type=int, default=8000); s.add_argument("--rows", type=int)
     args = ap.parse_args(argv)
-    if args.cmd in ("run", "test", "bench", "server"):
+    if args.cmd in ("run", "test", "bench", "server", "e2e-logits"):
         path, cfg = find_config()
         resolve(args, path, cfg)
         if args.cmd != "test" and not args.manifest and not getattr(args, "model", None):
             ap.error("--manifest, --model or a --target of kern.toml is required")
     return {"verify": cmd_verify, "cut": cmd_cut, "kernels": cmd_kernels, "run": cmd_run, "test": cmd_test, "bench": cmd_bench,
-            "workload": cmd_workload, "server": cmd_server}[args.cmd](args)
+            "workload": cmd_workload, "server": cmd_server, "e2e-logits": cmd_e2e}[args.cmd](args)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,39 @@
+"""e2e-logits: record on one engine, judge the same model (passes) and a perturbed one (fails)."""
+import numpy as np
+
+from kern_b200.cpu import CpuRuntime
+from kern_b200.models import dense
+from kern_b200.testing import e2e
+from kern_b200.testing.abtest import EngineSide
+
+
+def side(weights):
+    rt = CpuRuntime(dense.build_manifest(dense.TOY), weights=weights, tokens=16 * 24)
+    rt.once()
+    return EngineSide(rt)
+
+
+def test_record_save_load_judge(tmp_path):
+    cfg = dense.TOY
+    w = dense.random_weights(cfg, seed=5, std=0.08)
+    qs = e2e.plan(seed=1, count=3, vocab=cfg.vocab, lengths=(5, 30), max_tokens=6)
+    assert [q.id for q in qs] == ["q0", "q1", "q2"] and e2e.plan(1, 3, cfg.vocab, (5, 30), 6)[1].prompt == qs[1].prompt
+    rec = e2e.record(side(w), qs, source="toy@cpu")
+    path = tmp_path / "rec.parquet"
+    rec.save(path)
+    back = e2e.Recording.load(path)
+    assert back.source == "toy@cpu" and [r["output"] for r in back.rows] == [r["output"] for r in rec.rows]
+    assert all(len(r["top_ids"]) == 6 and len(r["top_ids"][0]) == e2e.TOP and r["noise"] == 0.0 for r in back.rows)
+    text, code = e2e.summary(e2e.judge(back, side(w)))
+    assert code == 0 and "PASS: 3/3" in text
+    w2 = dict(w)
+    w2["lm_head.weight"] = (w["lm_head.weight"].float() + 0.2 * (np.random.default_rng(0).standard_normal(w["lm_head.weight"].shape)).astype(np.float32)).to(w["lm_head.weight"].dtype)
+    text, code = e2e.summary(e2e.judge(back, side(w2)))
+    assert code == 1 and "FAIL" in text
+
+
+def test_kl_top_is_zero_on_itself_and_positive_off():
+    row = np.random.default_rng(0).standard_normal(300).astype(np.float32)
+    ids, lp = e2e.top_of(row)
+    assert ids[0] == int(row.argmax()) and abs(e2e.kl_top(ids, lp, row)) < 1e-9
+    assert e2e.kl_top(ids, lp, row[::-1].copy()) > 0.1
