@@ -335,7 +335,7 @@ class CpuRuntime:
         for b in self.doc["buffers"].values():
             dom = b.get("domain") or {}
             st = self.doc["states"].get(dom.get("index_into", ""))
-            if st and st.get("bytes_per_token") and "fill" not in b:
+            if st and (st.get("bytes_per_token") or st.get("host")) and "fill" not in b:
                 self.page_unit = math.lcm(self.page_unit, dom.get("stride", 1))
         self.pages = max(1, tokens // self.page_unit)
         self.slots = slots
@@ -383,6 +383,25 @@ class CpuRuntime:
         for pname, p in self.doc["programs"].items():
             if p.get("derive"):
                 self.issue(pname, {k: v["max"] for k, v in self.doc["vars"].items()})
+
+    # ---- hosted ----
+    @property
+    def awaits_host(self) -> bool:
+        return any(s.get("host") and self.states[n].numel() == 0 for n, s in self.doc["states"].items())
+
+    def bind_host_tensors(self, tensors: dict) -> None:
+        """Host-owned states: the engine's own (CPU) tensors become the states, shared, not copied."""
+        for name, t in tensors.items():
+            decl = self.doc["states"].get(name, {}).get("host")
+            if decl is None:
+                raise ValueError(f"`{name}` is not a host state of this manifest")
+            if list(t.shape[1:]) != decl["shape"][1:] or list(t.stride()) != decl["strides"]:
+                raise ValueError(f"host state `{name}`: tensor {list(t.shape)}/{list(t.stride())} is not the declared "
+                                 f"{decl['shape']}/{decl['strides']}")
+            self.states[name] = t.view(-1).view(torch.uint8)
+        missing = [n for n, s in self.doc["states"].items() if s.get("host") and n not in tensors]
+        if missing:
+            raise ValueError(f"host state `{missing[0]}` was not bound")
 
     def _pick(self, t):
         return t if isinstance(t, str) else t["tensors"][self.rank(t["group"])]

@@ -110,7 +110,9 @@ def random_weights(cfg: DenseConfig, seed: int = 0, device: str = "cpu", std: fl
     return out
 
 
-def build_manifest(cfg: DenseConfig) -> dict:
+def build_manifest(cfg: DenseConfig, hosted: bool = False) -> dict:
+    """`hosted`: the manifest a host engine (vLLM / SGLang style) drives: KV states are the host's tensors, `prefill` /
+    `decode` end at `hidden` (final-norm rows), and a `head` program turns the rows copied into `head_in` into `logits`."""
     h, d, hq, hk = cfg.hidden, cfg.head_dim, cfg.heads, cfg.kv_heads
     T, S, W = cfg.max_tokens, cfg.max_seqs, cfg.table_width
     inter = cfg.intermediate
@@ -229,10 +231,33 @@ def build_manifest(cfg: DenseConfig) -> dict:
     for i in range(cfg.layers):
         prefill += layer(i, True)
         decode += layer(i, False)
-    prefill += [{"op": "last_row", "label": "last_row", "args": [B("x"), B("last"), B("cu_seqlens")]}] + head("last")
-    decode += head("x")
+    programs = {"load": {"once": True, "calls": [{"op": "rope_table", "args": [B("rope_cos"), B("rope_sin")]}]}}
+    if hosted:
+        from ..hosted import kv_shape
 
-    mods = ["norm_embed", "gemm_bf16", "attn_prep", "attn_paged", "misc", "sampling"]
+        shape, strides = kv_shape(hk, cfg.page_size, d)
+        for name in states:
+            states[name] = {"host": {"dtype": "bf16", "shape": shape, "strides": strides}}   # sized by the host
+        for name in ("last", "last_n", "next_token"):
+            bufs.pop(name)
+        bufs["hidden"] = {"dtype": "bf16", "shape": ["tokens", h], "kind": "output"}
+        bufs["head_in"] = {"dtype": "bf16", "shape": ["tokens", h], "kind": "input"}
+        bufs["logits"] = {"dtype": "bf16", "shape": ["tokens", cfg.vocab], "kind": "output"}
+        ops.pop("norm_last"); ops.pop("last_row"); ops.pop("pick")
+        ops["lm_head"] = C.gemm_op(cfg.vocab, h, rows_max=T)
+        final = [{"op": "norm", "label": "final_norm", "args": [B("x"), B("w.norm"), B("hidden")]}]
+        programs.update({
+            "prefill": {"batch": {"groups": S, "rows": "tokens"}, "calls": prefill + final},
+            "decode": {"batch": {"groups": S, "rows": 1}, "graph": True, "calls": decode + final},
+            "head": {"calls": [{"op": "lm_head", "label": "lm_head",
+                                "args": [B("head_in"), B("w.head"), B("logits"), {"var": "tokens"}, err]}]}})
+    else:
+        prefill += [{"op": "last_row", "label": "last_row", "args": [B("x"), B("last"), B("cu_seqlens")]}] + head("last")
+        decode += head("x")
+        programs.update({"prefill": {"batch": {"groups": S, "rows": "tokens"}, "calls": prefill},
+                         "decode": {"batch": {"groups": S, "rows": 1}, "graph": True, "calls": decode}})
+
+    mods = ["norm_embed", "gemm_bf16", "attn_prep", "attn_paged"] + ([] if hosted else ["misc", "sampling"])
     return {
         "schema_version": 7,
         "model": cfg.name,
@@ -241,11 +266,7 @@ def build_manifest(cfg: DenseConfig) -> dict:
         "buffers": bufs,
         "modules": C.modules_for(mods),
         "ops": ops,
-        "programs": {
-            "load": {"once": True, "calls": [{"op": "rope_table", "args": [B("rope_cos"), B("rope_sin")]}]},
-            "prefill": {"batch": {"groups": S, "rows": "tokens"}, "calls": prefill},
-            "decode": {"batch": {"groups": S, "rows": 1}, "graph": True, "calls": decode},
-        },
+        "programs": programs,
     }
 
 
