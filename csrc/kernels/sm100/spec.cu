@@ -98,3 +98,17 @@ extern "C" __global__ void kern_spec_accept(const long long* drafts, const long 
     }
   }
 }
+
+// dst[i] = src[i * stride + column]: one row of every sequence's block (a draft-chain step's token, position, slot).
+extern "C" __global__ void kern_spec_column_i64(const long long* src, long long* dst, int seqs, int stride, int column) {
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < seqs) dst[i] = src[(size_t)i * stride + column];
+}
+
+// out[i] = max(0, lens[i] - delta) for live sequences (lens[i] > 0), else 0: the context a chain step attends to.
+extern "C" __global__ void kern_spec_lens(const int* lens, int* out, int seqs, int delta) {
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < seqs) out[i] = lens[i] > 0 ? max(0, lens[i] - delta) : 0;
+}

@@ -98,10 +98,14 @@ def serve_rank(head: tuple[str, int], rank: int, world: int, make_runtime, watch
         if order is None:
             return
         try:
-            wire.send(sock, ex.run(order))
+            answer = ex.run(order)
         except Exception as e:     # the head decides what a failed step means; the rank stays in its loop
             log.exception("order failed rank=%d", rank)
-            wire.send(sock, {"tokens": [], "counts": [], "landed": [], "error": -1, "why": f"{type(e).__name__}: {e}"})
+            answer = {"tokens": [], "counts": [], "landed": [], "error": -1, "why": f"{type(e).__name__}: {e}"}
+        try:
+            wire.send(sock, answer)
+        except (ConnectionError, OSError):
+            return
 
 
 class Executors:
