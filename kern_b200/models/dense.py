@@ -316,6 +316,11 @@ class DenseOracle:
         a, b = xf[..., :half], xf[..., half:]
         return torch.cat([a * cos - b * sin, b * cos + a * sin], -1).to(self.dtype)
 
+    def mlp(self, i: int, xn: torch.Tensor) -> torch.Tensor:
+        w, p = self.w, f"model.layers.{i}."
+        act = torch.nn.functional.silu((xn @ w[p + "mlp.gate_proj.weight"].t()).float()) * (xn @ w[p + "mlp.up_proj.weight"].t()).float()
+        return act.to(self.dtype) @ w[p + "mlp.down_proj.weight"].t()
+
     @torch.no_grad()
     def forward(self, tokens, cache) -> torch.Tensor:
         cfg, w = self.cfg, self.w
@@ -346,8 +351,7 @@ class DenseOracle:
             o = torch.einsum("hrl,lhd->rhd", torch.softmax(s, -1), vv).reshape(n, cfg.q_dim).to(self.dtype)
             x = x + o @ w[p + "self_attn.o_proj.weight"].t()
             xn = self._norm(x, w[p + "post_attention_layernorm.weight"])
-            act = torch.nn.functional.silu((xn @ w[p + "mlp.gate_proj.weight"].t()).float()) * (xn @ w[p + "mlp.up_proj.weight"].t()).float()
-            x = x + act.to(self.dtype) @ w[p + "mlp.down_proj.weight"].t()
+            x = x + self.mlp(i, xn)
         xn = self._norm(x, w["model.norm.weight"])
         head = w["model.embed_tokens.weight"] if cfg.tie_embeddings else w["lm_head.weight"]
         return (xn @ head.t()).float()

@@ -1,0 +1,284 @@
+"""Mixture-of-experts decoder (GQA attention + routed SwiGLU experts, the Qwen3-MoE / DeepSeek-style MLP): manifest
+generator, synthetic checkpoint, oracle, and the CPU statements of the MoE kernels.
+
+A layer's MLP is: router GEMM (f32 logits) -> top-k routing -> plan (expert-sorted rows + the M-tile table) -> gather
+-> routed GEMM with SwiGLU epilogue -> routed GEMM -> weighted combine accumulated into the residual. Under expert
+parallelism a rank keeps experts [e_lo, e_hi) and computes its share of every token; the shares meet in the
+tensor-parallel all-reduce.
+Reference shape: the routed batched GEMMs and routing tables of kernel_index/trtllm_bmm_*.toml, tools/kernels-src/topk_row.cu.
+"""
+from __future__ import annotations
+
+import dataclasses
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from . import common as C
+from . import dense
+
+
+@dataclass
+class MoeConfig(dense.DenseConfig):
+    experts: int = 128
+    top_k: int = 8
+    moe_intermediate: int = 768
+    scoring: str = "softmax"          # softmax | sigmoid
+    routed_scale: float = 1.0
+
+
+TOY_MOE = MoeConfig(name="toy-moe", vocab=256, hidden=64, layers=2, heads=4, kv_heads=2, head_dim=16, intermediate=128,
+                    rope_theta=10000.0, page_size=16, max_tokens=64, max_seqs=4, max_context=64, experts=8, top_k=2,
+                    moe_intermediate=32)
+TINY_MOE = MoeConfig(name="tiny-moe", vocab=512, hidden=256, layers=2, heads=4, kv_heads=2, head_dim=64, intermediate=512,
+                     rope_theta=10000.0, page_size=16, max_tokens=256, max_seqs=8, max_context=256, experts=16, top_k=4,
+                     moe_intermediate=128)
+MOE_30B = MoeConfig(name="moe-30b-a3b", vocab=151936, hidden=2048, layers=48, heads=32, kv_heads=4, head_dim=128,
+                    intermediate=6144, qk_norm=True, experts=128, top_k=8, moe_intermediate=768)
+
+
+def weight_names(cfg: MoeConfig) -> dict[str, tuple[int, ...]]:
+    out = {n: s for n, s in dense.weight_names(cfg).items() if ".mlp." not in n}
+    h, I = cfg.hidden, cfg.moe_intermediate
+    for i in range(cfg.layers):
+        p = f"model.layers.{i}.mlp."
+        out[p + "gate.weight"] = (cfg.experts, h)
+        for e in range(cfg.experts):
+            out[p + f"experts.{e}.gate_proj.weight"] = (I, h)
+            out[p + f"experts.{e}.up_proj.weight"] = (I, h)
+            out[p + f"experts.{e}.down_proj.weight"] = (h, I)
+    return out
+
+
+def random_weights(cfg: MoeConfig, seed: int = 0, device: str = "cpu", std: float = 0.02) -> dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(seed)
+    out = {}
+    for name, shape in weight_names(cfg).items():
+        if name.endswith("norm.weight"):
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g, device=device)
+        elif name.endswith("mlp.gate.weight"):
+            t = 10 * std * torch.randn(shape, generator=g, device=device)       # a router with opinions
+        else:
+            t = std * torch.randn(shape, generator=g, device=device)
+        out[name] = t.to(torch.bfloat16)
+    return out
+
+
+def load_random_weights(rt, cfg: MoeConfig, seed: int = 0, std: float = 0.02) -> None:
+    shapes = weight_names(cfg)
+    order = {n: i for i, n in enumerate(shapes)}
+
+    def provider(name: str) -> torch.Tensor:
+        dev = rt.tensor(next(iter(rt.doc["buffers"]))).device
+        g = torch.Generator(device=dev).manual_seed(seed * 1000003 + order[name])
+        scale = 1.0 if name.endswith("norm.weight") else (10 * std if name.endswith("mlp.gate.weight") else std)
+        t = torch.randn(shapes[name], generator=g, device=dev) * (0.1 if name.endswith("norm.weight") else scale)
+        return ((1.0 + t) if name.endswith("norm.weight") else t).to(torch.bfloat16)
+
+    rt.load_tensors(provider)
+
+
+def _moe_ops(cfg: MoeConfig, e_lo: int, e_n: int) -> dict:
+    h, I, E, k, T = cfg.hidden, cfg.moe_intermediate, cfg.experts, cfg.top_k, cfg.max_tokens
+    max_tiles = T * k // C.BM + e_n
+    L = lambda module, entry, block, grid, lp, args, **kw: {"module": module, "entry": entry, "block": block, "grid": grid,
+                                                            "params": lp, "args": args, **kw}
+    ops = {}
+    ops["moe_router"] = C.gemm_op(E, h, epilogue="f32", rows_max=T)
+    ops["moe_route"] = {"params": ["in buffer<f32>", "out buffer<i32>", "out buffer<f32>"], "impl": {"launches": [L(
+        "moe", "kern_moe_route_f32", [128, 1, 1], [{"ceil_div": ["tokens", 4]}, 1, 1],
+        ["in buffer<f32>", "i64", "out buffer<i32>", "out buffer<f32>", "i32", "i32", "i32", "i32", "i32", "f32", "i32"],
+        [{"param": 0}, {"i64": 0}, {"param": 1}, {"param": 2}, {"i32": C.I32_MAX}, {"i32": E}, {"i32": k},
+         {"i32": 1 if cfg.scoring == "softmax" else 0}, {"i32": 1}, {"f32": cfg.routed_scale}, {"i32": E}])]}}
+    # `tokens` bounds the entries through the grid-free loop: the kernel is told tokens * k by the `entries` arg
+    ops["moe_plan"] = {"params": ["in buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>",
+                                  "out buffer<i32>", "i32", "out buffer<i32>"], "impl": {"launches": [L(
+        "moe", "kern_moe_plan", [1024, 1, 1], [1, 1, 1],
+        ["in buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "i32",
+         "i32", "i32", "i32", "i32", "out buffer<i32>"],
+        [{"param": 0}, {"param": 1}, {"param": 2}, {"param": 3}, {"param": 4}, {"param": 5}, {"param": 6}, {"i32": e_lo},
+         {"i32": e_lo + e_n}, {"i32": C.BM}, {"i32": max_tiles}, {"param": 7}], shared_mem=2 * e_n * 4)]}}
+    ops["moe_gather"] = {"params": ["in buffer<bf16>", "in buffer<i32>", "out buffer<bf16>", "i32"], "impl": {"launches": [L(
+        "moe", "kern_moe_gather_bf16", [128, 1, 1], [{"mul": ["tokens", k]}, 1, 1],
+        ["in buffer<bf16>", "in buffer<i32>", "out buffer<bf16>", "i32", "i32", "i32"],
+        [{"param": 0}, {"param": 1}, {"param": 2}, {"param": 3}, {"i32": k}, {"i32": h}])]}}
+
+    def routed(n, kk, epi):
+        bn = 128 if n >= 128 else 64
+        out_cols = n // 2 if epi == "swiglu" else n
+        a_map = {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+            "param": 0, "dtype": "bf16", "dims": [kk, 0], "strides": [kk * 2], "box": [C.BK, C.BM], "swizzle": 128, "l2_promotion": 256}}]}}
+        b_map = {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+            "param": 1, "dtype": "bf16", "dims": [kk, n, e_n], "strides": [kk * 2, n * kk * 2],
+            "box": [C.BK, bn // 2 if epi == "swiglu" else bn, 1], "swizzle": 128, "l2_promotion": 256}}]}}
+        return {"params": ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "i32",
+                           "out buffer<i32>"], "impl": {"launches": [L(
+            "moe", f"kern_moe_gemm_bf16{'_swiglu' if epi == 'swiglu' else ''}_n{bn}", [192, 1, 1], [C.SMS, 1, 1],
+            ["bytes<128>", "bytes<128>", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "i32", "i32", "i32", "i32",
+             "out buffer<i32>"],
+            [a_map, b_map, {"param": 2}, {"param": 3}, {"param": 4}, {"param": 5}, {"i32": n}, {"i32": kk}, {"i32": out_cols},
+             {"param": 6}], shared_mem=C.gemm_smem(bn))]}}
+
+    ops["moe_fc1"] = routed(2 * I, h, "swiglu")
+    ops["moe_fc2"] = routed(h, I, "store")
+    ops["moe_combine"] = {"params": ["in buffer<bf16>", "in buffer<i32>", "in buffer<f32>", "inout buffer<bf16>"], "impl": {"launches": [L(
+        "moe", "kern_moe_combine_bf16", [128, 1, 1], ["tokens", 1, 1],
+        ["in buffer<bf16>", "in buffer<i32>", "in buffer<f32>", "i64", "inout buffer<bf16>", "i32", "i32", "i32", "i32"],
+        [{"param": 0}, {"param": 1}, {"param": 2}, {"i64": 0}, {"param": 3}, {"i32": C.I32_MAX}, {"i32": k}, {"i32": h}, {"i32": 1}])]}}
+    return ops
+
+
+def build_manifest(cfg: MoeConfig) -> dict:
+    """The dense decoder's manifest with every layer's MLP replaced by the routed experts."""
+    doc = dense.build_manifest(cfg)
+    doc["model"] = cfg.name
+    bufs, ops = doc["buffers"], doc["ops"]
+    h, I, E, k, T = cfg.hidden, cfg.moe_intermediate, cfg.experts, cfg.top_k, cfg.max_tokens
+    for name in ("gate_up", "down_proj"):
+        ops.pop(name)
+    bufs.pop("act")
+    ops.update(_moe_ops(cfg, 0, E))
+    max_tiles = T * k // C.BM + E
+    bufs["moe.logits"] = {"dtype": "f32", "shape": ["tokens", E], "kind": "workspace"}
+    bufs["moe.ids"] = {"dtype": "i32", "shape": ["tokens", k], "kind": "workspace"}
+    bufs["moe.w"] = {"dtype": "f32", "shape": ["tokens", k], "kind": "workspace"}
+    bufs["moe.perm"] = {"dtype": "i32", "shape": ["tokens", k], "kind": "workspace"}
+    bufs["moe.offsets"] = {"dtype": "i32", "shape": [E + 1], "kind": "workspace"}
+    bufs["moe.tiles"] = {"dtype": "i32", "shape": [max_tiles, 4], "kind": "workspace"}
+    bufs["moe.tile_count"] = {"dtype": "i32", "shape": [1], "kind": "workspace"}
+    bufs["moe.rows"] = {"dtype": "i32", "shape": [1], "kind": "workspace"}
+    bufs["moe.x"] = {"dtype": "bf16", "shape": ["tokens", k, h], "kind": "workspace"}
+    bufs["moe.act"] = {"dtype": "bf16", "shape": ["tokens", k, I], "kind": "workspace"}
+    bufs["moe.y"] = {"dtype": "bf16", "shape": ["tokens", k, h], "kind": "workspace"}
+    B = lambda n: {"buf": n}
+    err = B("error")
+    for i in range(cfg.layers):
+        p = f"model.layers.{i}.mlp."
+        for name in (f"w.l{i}.gu", f"w.l{i}.down"):
+            bufs.pop(name)
+        bufs[f"w.l{i}.router"] = {"dtype": "bf16", "shape": [E, h], "kind": "weight", "bind": [{"tensor": p + "gate.weight"}]}
+        bufs[f"w.l{i}.w1"] = {"dtype": "bf16", "shape": [E, 2 * I, h], "kind": "weight",
+                              "bind": [{"tensor": p + f"experts.{e}.{n}_proj.weight"} for e in range(E) for n in ("gate", "up")]}
+        bufs[f"w.l{i}.w2"] = {"dtype": "bf16", "shape": [E, h, I], "kind": "weight",
+                              "bind": [{"tensor": p + f"experts.{e}.down_proj.weight"} for e in range(E)]}
+
+    def moe_calls(i: int) -> list[dict]:
+        l = f"l{i}."
+        return [
+            {"op": "moe_router", "label": l + "router", "args": [B("xn"), B(f"w.l{i}.router"), B("moe.logits"), {"var": "tokens"}, err]},
+            {"op": "moe_route", "label": l + "route", "args": [B("moe.logits"), B("moe.ids"), B("moe.w")]},
+            {"op": "moe_plan", "label": l + "plan", "args": [B("moe.ids"), B("moe.perm"), B("moe.offsets"), B("moe.tiles"),
+                                                             B("moe.tile_count"), B("moe.rows"), {"expr": {"mul": ["tokens", k]}}, err]},
+            {"op": "moe_gather", "label": l + "gather", "args": [B("xn"), B("moe.perm"), B("moe.x"), {"expr": {"mul": ["tokens", k]}}]},
+            {"op": "moe_fc1", "label": l + "fc1", "args": [B("moe.x"), B(f"w.l{i}.w1"), B("moe.act"), B("moe.tiles"), B("moe.tile_count"),
+                                                           {"expr": {"mul": ["tokens", k]}}, err]},
+            {"op": "moe_fc2", "label": l + "fc2", "args": [B("moe.act"), B(f"w.l{i}.w2"), B("moe.y"), B("moe.tiles"), B("moe.tile_count"),
+                                                           {"expr": {"mul": ["tokens", k]}}, err]},
+            {"op": "moe_combine", "label": l + "combine", "args": [B("moe.y"), B("moe.perm"), B("moe.w"), B("x")]},
+        ]
+
+    for prog in ("prefill", "decode"):
+        out = []
+        for c in doc["programs"][prog]["calls"]:
+            lbl = c.get("label", "")
+            if lbl.endswith(".gate_up"):
+                out += moe_calls(int(lbl[1:lbl.index(".")]))
+            elif lbl.endswith(".down"):
+                continue
+            else:
+                out.append(c)
+        doc["programs"][prog]["calls"] = out
+    doc["modules"] = C.modules_for(["norm_embed", "gemm_bf16", "attn_prep", "attn_paged", "misc", "sampling", "moe"])
+    return doc
+
+
+class MoeOracle(dense.DenseOracle):
+    """The dense oracle with the routed MLP (fp32)."""
+
+    def mlp(self, i: int, xn: torch.Tensor) -> torch.Tensor:
+        cfg, w, p = self.cfg, self.w, f"model.layers.{i}.mlp."
+        logits = xn.float() @ w[p + "gate.weight"].float().t()
+        s = torch.softmax(logits, -1) if cfg.scoring == "softmax" else torch.sigmoid(logits)
+        wt, ids = torch.topk(s, cfg.top_k, dim=-1)
+        wt = wt / wt.sum(-1, keepdim=True) * cfg.routed_scale
+        out = torch.zeros_like(xn, dtype=torch.float32)
+        for e in range(cfg.experts):
+            tok, j = torch.nonzero(ids == e, as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            x = xn[tok].float()
+            a = F.silu(x @ w[p + f"experts.{e}.gate_proj.weight"].float().t()) * (x @ w[p + f"experts.{e}.up_proj.weight"].float().t())
+            out.index_add_(0, tok, (a @ w[p + f"experts.{e}.down_proj.weight"].float().t()) * wt[tok, j][:, None])
+        return out.to(self.dtype)
+
+
+# ---- CPU statements ------------------------------------------------------------------------------------
+def _register_cpu() -> None:
+    from .. import cpu
+    from ..ops import moe as M
+
+    def route(g, logits, bias, ids, wts, tokens, experts, k, mode, renorm, scale, ld):
+        t = ids.numel() // k if tokens >= C.I32_MAX else tokens
+        t = min(t, g[0] * 4)
+        i, w = M.route_reference(logits[: t * ld].view(t, ld)[:, :experts], k, bias if isinstance(bias, torch.Tensor) else None,
+                                 "softmax" if mode == 1 else "sigmoid", bool(renorm), scale)
+        ids[: t * k] = i.reshape(-1)
+        wts[: t * k] = w.reshape(-1).float()
+
+    def plan(g, ids, perm, offsets, tiles, tile_count, rows_out, entries, e_lo, e_hi, bm, max_tiles, err):
+        flat = ids[:entries]
+        at, nt = 0, 0
+        tl = tiles.view(-1, 4)
+        for e in range(e_lo, e_hi):
+            mine = torch.nonzero(flat == e).flatten()
+            offsets[e - e_lo] = at
+            perm[mine] = torch.arange(at, at + mine.numel(), dtype=perm.dtype)
+            for m0 in range(0, mine.numel(), bm):
+                tl[nt] = torch.tensor([e - e_lo, at + m0, min(bm, mine.numel() - m0), 0], dtype=tl.dtype)
+                nt += 1
+            at += mine.numel()
+        offsets[e_hi - e_lo] = at
+        perm[:entries][(flat < e_lo) | (flat >= e_hi)] = -1
+        tile_count[0], rows_out[0] = nt, at
+
+    def gather(g, x, perm, xp, entries, k, hidden):
+        for i in range(entries):
+            r = int(perm[i])
+            if r >= 0:
+                xp[r * hidden:(r + 1) * hidden] = x[(i // k) * hidden:(i // k + 1) * hidden]
+
+    def gemm(epi):
+        def run(g, a, w, c, tiles, tile_count, M_, N, K, ldc, err):
+            A = a._row_stride if hasattr(a, "_row_stride") else K
+            tl = tiles.view(-1, 4)
+            wv = w.view(torch.bfloat16) if w.dtype != torch.bfloat16 else w
+            for t in range(int(tile_count[0])):
+                e, r0, nr, _ = (int(v) for v in tl[t])
+                rows = cpu._f(a[r0 * K:(r0 + nr) * K].view(nr, K))
+                We = cpu._f(wv[e * N * K:(e + 1) * N * K].view(N, K))
+                acc = rows @ We.t()
+                if epi == "swiglu":
+                    acc = F.silu(acc[:, : N // 2]) * acc[:, N // 2:]
+                c[r0 * ldc:(r0 + nr) * ldc] = acc.to(torch.bfloat16).reshape(-1)
+        return run
+
+    def combine(g, y, perm, wts, shared, out, tokens, k, hidden, accumulate):
+        for t in range(g[0]):
+            acc = cpu._f(out[t * hidden:(t + 1) * hidden]).clone() if accumulate else torch.zeros(hidden)
+            for j in range(k):
+                r = int(perm[t * k + j])
+                if r >= 0:
+                    acc += float(wts[t * k + j]) * cpu._f(y[r * hidden:(r + 1) * hidden])
+            out[t * hidden:(t + 1) * hidden] = acc.to(out.dtype)
+
+    cpu.register("kern_moe_route_f32", route)
+    cpu.register("kern_moe_plan", plan)
+    cpu.register("kern_moe_gather_bf16", gather)
+    cpu.register("kern_moe_combine_bf16", combine)
+    for bn in (256, 128, 64):
+        cpu.register(f"kern_moe_gemm_bf16_n{bn}", gemm("store"))
+        cpu.register(f"kern_moe_gemm_bf16_swiglu_n{bn}", gemm("swiglu"))
+
+
+_register_cpu()

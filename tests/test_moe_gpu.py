@@ -83,3 +83,34 @@ def test_moe_expert_parallel_shares_sum_to_the_whole(cuda):
     parts = sum(moe.moe_layer(x, wr, w1[lo:lo + 4].contiguous(), w2[lo:lo + 4].contiguous(), k, e_lo=lo).float()
                 for lo in range(0, e, 4))
     torch.testing.assert_close(parts, whole, rtol=4e-2, atol=4e-2)
+
+
+def test_moe_decoder_end_to_end(cuda):
+    """The MoE decoder's manifest on the native runtime: prefill + graph-replayed decode against the fp32 oracle."""
+    from kern_b200.engine import Engine
+    from kern_b200.models import moe
+    from kern_b200.runtime import Runtime
+
+    cfg = moe.TINY_MOE
+    w = moe.random_weights(cfg, seed=1, std=0.05)
+    rt = Runtime(moe.build_manifest(cfg), tokens=cfg.page_size * 64)
+    rt.load_tensors(lambda name: w[name].cuda())
+    rt.once()
+    eng, oracle = Engine(rt), moe.MoeOracle(cfg, w, device="cuda")
+    torch.manual_seed(0)
+    prompts = [torch.randint(1, cfg.vocab, (n,)).tolist() for n in (150, 9)]
+    seqs = [eng.open(200) for _ in prompts]
+    caches = [oracle.new_cache() for _ in prompts]
+    first = eng.step(list(zip(seqs, prompts)))
+    logits = rt.tensor("logits")[:2].float()
+    diffs = [(logits[i] - oracle.forward(p, c)[-1]).abs() for i, (p, c) in enumerate(zip(prompts, caches))]
+    toks = [f[0] for f in first]
+    for _ in range(4):
+        refs = [oracle.forward([t], c)[-1] for t, c in zip(toks, caches)]
+        nxt = eng.step([(s, [t]) for s, t in zip(seqs, toks)])
+        logits = rt.tensor("logits")[:2].float()
+        diffs += [(logits[i] - refs[i]).abs() for i in range(2)]
+        toks = [n[0] for n in nxt]
+    rt.check_error()
+    assert max(float(d.max()) for d in diffs) < 0.3 and max(float(d.mean()) for d in diffs) < 0.05
+    assert rt.graphs >= 1
