@@ -86,10 +86,10 @@ def _moe_ops(cfg: MoeConfig, e_lo: int, e_n: int) -> dict:
                                                             "params": lp, "args": args, **kw}
     ops = {}
     ops["moe_router"] = C.gemm_op(E, h, epilogue="f32", rows_max=T)
-    ops["moe_route"] = {"params": ["in buffer<f32>", "out buffer<i32>", "out buffer<f32>"], "impl": {"launches": [L(
+    ops["moe_route"] = {"params": ["in buffer<f32>", "out buffer<i32>", "out buffer<f32>", "i32"], "impl": {"launches": [L(
         "moe", "kern_moe_route_f32", [128, 1, 1], [{"ceil_div": ["tokens", 4]}, 1, 1],
         ["in buffer<f32>", "i64", "out buffer<i32>", "out buffer<f32>", "i32", "i32", "i32", "i32", "i32", "f32", "i32"],
-        [{"param": 0}, {"i64": 0}, {"param": 1}, {"param": 2}, {"i32": C.I32_MAX}, {"i32": E}, {"i32": k},
+        [{"param": 0}, {"i64": 0}, {"param": 1}, {"param": 2}, {"param": 3}, {"i32": E}, {"i32": k},
          {"i32": 1 if cfg.scoring == "softmax" else 0}, {"i32": 1}, {"f32": cfg.routed_scale}, {"i32": E}])]}}
     # `tokens` bounds the entries through the grid-free loop: the kernel is told tokens * k by the `entries` arg
     ops["moe_plan"] = {"params": ["in buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>",
@@ -167,7 +167,7 @@ def build_manifest(cfg: MoeConfig) -> dict:
         l = f"l{i}."
         return [
             {"op": "moe_router", "label": l + "router", "args": [B("xn"), B(f"w.l{i}.router"), B("moe.logits"), {"var": "tokens"}, err]},
-            {"op": "moe_route", "label": l + "route", "args": [B("moe.logits"), B("moe.ids"), B("moe.w")]},
+            {"op": "moe_route", "label": l + "route", "args": [B("moe.logits"), B("moe.ids"), B("moe.w"), {"var": "tokens"}]},
             {"op": "moe_plan", "label": l + "plan", "args": [B("moe.ids"), B("moe.perm"), B("moe.offsets"), B("moe.tiles"),
                                                              B("moe.tile_count"), B("moe.rows"), {"expr": {"mul": ["tokens", k]}}, err]},
             {"op": "moe_gather", "label": l + "gather", "args": [B("xn"), B("moe.perm"), B("moe.x"), {"expr": {"mul": ["tokens", k]}}]},
@@ -219,8 +219,7 @@ def _register_cpu() -> None:
     from ..ops import moe as M
 
     def route(g, logits, bias, ids, wts, tokens, experts, k, mode, renorm, scale, ld):
-        t = ids.numel() // k if tokens >= C.I32_MAX else tokens
-        t = min(t, g[0] * 4)
+        t = tokens
         i, w = M.route_reference(logits[: t * ld].view(t, ld)[:, :experts], k, bias if isinstance(bias, torch.Tensor) else None,
                                  "softmax" if mode == 1 else "sigmoid", bool(renorm), scale)
         ids[: t * k] = i.reshape(-1)

@@ -113,15 +113,16 @@ def build_manifest(target: dense.DenseConfig, draft: dense.DenseConfig | None = 
     def small(entry, lp, args, grid, block=(128, 1, 1), module="spec"):
         return {"module": module, "entry": entry, "block": list(block), "grid": grid, "params": lp, "args": args}
 
-    ops["column"] = {"params": ["in buffer<i64>", "out buffer<i64>", "i32"], "impl": {"launches": [small(
+    # these three run a thread per sequence in blocks of 128: the real sequence count is an argument (interface: [.., n, seqs])
+    ops["column"] = {"params": ["in buffer<i64>", "out buffer<i64>", "i32", "i32"], "impl": {"launches": [small(
         "kern_spec_column_i64", ["in buffer<i64>", "out buffer<i64>", "i32", "i32", "i32"],
-        [{"param": 0}, {"param": 1}, {"i32": C.I32_MAX}, {"i32": R}, {"param": 2}], [{"ceil_div": ["seqs", 128]}, 1, 1])]}}
-    ops["lens"] = {"params": ["in buffer<i32>", "out buffer<i32>", "i32"], "impl": {"launches": [small(
+        [{"param": 0}, {"param": 1}, {"param": 3}, {"i32": R}, {"param": 2}], [{"ceil_div": ["seqs", 128]}, 1, 1])]}}
+    ops["lens"] = {"params": ["in buffer<i32>", "out buffer<i32>", "i32", "i32"], "impl": {"launches": [small(
         "kern_spec_lens", ["in buffer<i32>", "out buffer<i32>", "i32", "i32"],
-        [{"param": 0}, {"param": 1}, {"i32": C.I32_MAX}, {"param": 2}], [{"ceil_div": ["seqs", 128]}, 1, 1])]}}
-    ops["chain"] = {"params": ["in buffer<i64>", "inout buffer<i64>", "i32"], "impl": {"launches": [small(
+        [{"param": 0}, {"param": 1}, {"param": 3}, {"param": 2}], [{"ceil_div": ["seqs", 128]}, 1, 1])]}}
+    ops["chain"] = {"params": ["in buffer<i64>", "inout buffer<i64>", "i32", "i32"], "impl": {"launches": [small(
         "kern_spec_chain", ["in buffer<i64>", "inout buffer<i64>", "i32", "i32", "i32"],
-        [{"param": 0}, {"param": 1}, {"i32": C.I32_MAX}, {"param": 2}, {"i32": R}], [{"ceil_div": ["seqs", 128]}, 1, 1])]}}
+        [{"param": 0}, {"param": 1}, {"param": 3}, {"param": 2}, {"i32": R}], [{"ceil_div": ["seqs", 128]}, 1, 1])]}}
     ops["splice"] = {"params": ["in buffer<i64>", "in buffer<i64>", "out buffer<i64>"], "impl": {"launches": [small(
         "kern_spec_splice", ["in buffer<i64>", "in buffer<i64>", "out buffer<i64>", "i32", "i32", "i32", "i64"],
         [{"param": 0}, {"param": 1}, {"param": 2}, {"i32": C.I32_MAX}, {"i32": R}, {"i32": R}, {"i64": 0}], ["seqs", 1, 1],
@@ -154,21 +155,21 @@ def build_manifest(target: dense.DenseConfig, draft: dense.DenseConfig | None = 
     ops["zero_i64"] = {"params": ["out buffer<i64>"], "impl": {"launches": [small(
         "kern_fill_i64", ["out buffer<i64>", "i64", "i64"], [{"param": 0}, {"i64": S * R}, {"i64": 0}], [8, 1, 1],
         block=(256, 1, 1), module="misc")]}}
-    calls = [{"op": "column", "label": "anchor", "args": [B("token_ids"), B("anchor"), {"i32": 0}]},
+    calls = [{"op": "column", "label": "anchor", "args": [B("token_ids"), B("anchor"), {"i32": 0}, {"var": "seqs"}]},
              {"op": "zero_i64", "label": "drafts0", "args": [B("drafts")]}]
     for j in range(R):
         src = B("anchor") if j == 0 else None
         if j == 0:
-            calls.append({"op": "column", "label": f"c{j}.tok", "args": [B("token_ids"), B("c.tok"), {"i32": 0}]})
+            calls.append({"op": "column", "label": f"c{j}.tok", "args": [B("token_ids"), B("c.tok"), {"i32": 0}, {"var": "seqs"}]})
         else:
-            calls.append({"op": "column", "label": f"c{j}.tok", "args": [B("drafts"), B("c.tok"), {"i32": j - 1}]})
-        calls += [{"op": "column", "label": f"c{j}.pos", "args": [B("positions"), B("c.pos"), {"i32": j}]},
-                  {"op": "column", "label": f"c{j}.slot", "args": [B("slot_mapping"), B("c.slot"), {"i32": j}]},
-                  {"op": "lens", "label": f"c{j}.lens", "args": [B("seq_lens"), B("c.lens"), {"i32": R - 1 - j}]}]
+            calls.append({"op": "column", "label": f"c{j}.tok", "args": [B("drafts"), B("c.tok"), {"i32": j - 1}, {"var": "seqs"}]})
+        calls += [{"op": "column", "label": f"c{j}.pos", "args": [B("positions"), B("c.pos"), {"i32": j}, {"var": "seqs"}]},
+                  {"op": "column", "label": f"c{j}.slot", "args": [B("slot_mapping"), B("c.slot"), {"i32": j}, {"var": "seqs"}]},
+                  {"op": "lens", "label": f"c{j}.lens", "args": [B("seq_lens"), B("c.lens"), {"i32": R - 1 - j}, {"var": "seqs"}]}]
         for c in copy.deepcopy(step):
             c["label"] = f"c{j}." + c.get("label", c["op"])
             calls.append(c)
-        calls.append({"op": "chain", "label": f"c{j}.keep", "args": [B("d.next_token"), B("drafts"), {"i32": j}]})
+        calls.append({"op": "chain", "label": f"c{j}.keep", "args": [B("d.next_token"), B("drafts"), {"i32": j}, {"var": "seqs"}]})
     calls.append({"op": "splice", "label": "splice", "args": [B("anchor"), B("drafts"), B("ids")]})
     # verify: the target's decode step over R rows per sequence
     verify = []
@@ -213,19 +214,15 @@ def _register_cpu() -> None:
     from .. import cpu
 
     def column(g, src, dst, seqs, stride, col):
-        n = cpu_seqs(dst, seqs)
-        dst[:n] = src[: n * stride].view(n, stride)[:, col]
-
-    def cpu_seqs(buf, seqs):
-        return min(buf.numel(), seqs) if seqs < C.I32_MAX else int(getattr(buf, "_n", buf.numel()))
+        dst[:seqs] = src[: seqs * stride].view(seqs, stride)[:, col]
 
     def lens(g, src, out, seqs, delta):
-        n = out.numel()
+        n = seqs
         v = src[:n]
         out[:n] = ((v > 0) * (v - delta).clamp(min=0)).to(out.dtype)
 
     def chain(g, nxt, drafts, seqs, col, stride):
-        n = nxt.numel()
+        n = seqs
         drafts[: n * stride].view(n, stride)[:, col] = nxt[:n]
 
     def splice(g, anchor, drafts, ids, seqs, block, dstride, mask):
