@@ -50,12 +50,15 @@ struct ScatterArgs {
 // GROUPED: the M tiles come from a device table of int4 {expert, first row, rows (<= BM), -} built by the MoE
 // planner (`tile_count` of them); A rows are the expert-sorted activations, B is a 3-D map [K, N, experts].
 // A tile's load may run into the next expert's rows; the epilogue stores only the tile's own rows.
-template <int BN, int EPI, bool GROUPED = false>
+// FP8: A and B hold e4m3 bytes (a swizzle row is 128 elements, the instruction is kind::f8f6f4 with K = 32), the
+// accumulator is scaled by *scale_a * *scale_b (per-tensor scales) before the epilogue's conversion.
+template <int BN, int EPI, bool GROUPED = false, bool FP8 = false>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
                                           void* Cv, const void* Rv,
                                           int M, int N, int K, int ldc, int* err,
                                           const int* tile_table = nullptr, const int* tile_count = nullptr,
-                                          ScatterArgs sc = ScatterArgs()) {
+                                          ScatterArgs sc = ScatterArgs(), const float* scale_a = nullptr,
+                                          const float* scale_b = nullptr) {
   using Cfg = GemmCfg<BN>;
   constexpr int kStages = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -72,7 +75,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_n = (N + BN - 1) / BN;
-  const int num_kb = (K + BK - 1) / BK;
+  constexpr int BKE = FP8 ? 2 * BK : BK;   // elements of one 128-byte swizzle row
+  const int num_kb = (K + BKE - 1) / BKE;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -132,10 +136,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
           uint8_t* sa = tiles + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kStageBytesA;
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          tma_load_2d(sa, tma_a, kb * BK, row0, &full_bar[stage]);
+          tma_load_2d(sa, tma_a, kb * BKE, row0, &full_bar[stage]);
           auto load_b = [&](uint8_t* dst, int n_row) {
-            if constexpr (GROUPED) tma_load_3d(dst, tma_b, kb * BK, n_row, expert, &full_bar[stage]);
-            else tma_load_2d(dst, tma_b, kb * BK, n_row, &full_bar[stage]);
+            if constexpr (GROUPED) tma_load_3d(dst, tma_b, kb * BKE, n_row, expert, &full_bar[stage]);
+            else tma_load_2d(dst, tma_b, kb * BKE, n_row, &full_bar[stage]);
           };
           if constexpr (EPI == 3) {
             // W = [gate rows ; up rows]: this tile's B rows are BN/2 gate rows then the matching BN/2 up rows
@@ -151,7 +155,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      // e4m3 is format 0 of kind::f8f6f4, bf16 format 1 of kind::f16: the descriptors differ only in those fields
+      constexpr uint32_t idesc = FP8 ? ((1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24))
+                                     : umma_idesc_bf16(BM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -177,8 +183,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
           const uint32_t sb = sa + Cfg::kStageBytesA;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            umma_bf16(d_tmem, umma_desc_sw128(sa + k * 32), umma_desc_sw128(sb + k * 32), idesc,
-                      (kb | k) != 0);
+            if constexpr (FP8)
+              umma_f8f6f4(d_tmem, umma_desc_sw128(sa + k * 32), umma_desc_sw128(sb + k * 32), idesc, (kb | k) != 0);
+            else
+              umma_bf16(d_tmem, umma_desc_sw128(sa + k * 32), umma_desc_sw128(sb + k * 32), idesc, (kb | k) != 0);
           }
           tc_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -192,6 +200,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
   } else {
     // ---------------- epilogue warps 2..5 ----------------
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are this warp's
+    const float out_scale = FP8 ? scale_a[0] * scale_b[0] : 1.f;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
@@ -305,7 +314,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
               if (col + v * 8 < N) {
                 float f[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]) * out_scale;
                 if constexpr (EPI == 2) {
                   uint4 old = *reinterpret_cast<const uint4*>(R + v * 8);
                   float2 a = unpack_bf16x2(old.x), b = unpack_bf16x2(old.y),

@@ -87,6 +87,37 @@ def bench_gemm(a):
         report("torch.matmul (cuBLAS, comparison only)", ms2, flops=2.0 * a.m * a.n * a.k)
 
 
+def bench_gemm_fp8(a):
+    from . import gemm_fp8 as F8
+    from .launcher import Kernels
+
+    x = (torch.randn(a.m, a.k, device="cuda")).to(torch.bfloat16)
+    w = (torch.randn(a.n, a.k, device="cuda") * 0.1).to(torch.bfloat16)
+    xq, sx = F8.quantize(x)
+    wq, sw = F8.quantize(w)
+    out = torch.zeros(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: F8.gemm_fp8(xq, wq, sx, sw, out=out, bn=a.bn), a.iters)
+    Kernels.get().check_error()
+    report("gemm_e4m3_tn", ms, flops=2.0 * a.m * a.n * a.k, nbytes=a.m * a.k + a.n * a.k + out.numel() * 2, m=a.m, n=a.n, k=a.k, bn=a.bn)
+
+
+def bench_moe(a):
+    """One MoE layer's routed part (plan, gather, two routed GEMMs, combine) at a decode- or prefill-sized batch."""
+    from . import moe as M
+    from .launcher import Kernels
+
+    x = torch.randn(a.tokens, a.hidden, device="cuda").to(torch.bfloat16)
+    wr = (torch.randn(a.experts, a.hidden, device="cuda") * 0.1).to(torch.bfloat16)
+    w1 = (torch.randn(a.experts, 2 * a.inter, a.hidden, device="cuda") * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(a.experts, a.hidden, a.inter, device="cuda") * 0.02).to(torch.bfloat16)
+    ms = timeit(lambda: M.moe_layer(x, wr, w1, w2, a.top_k), a.iters)
+    Kernels.get().check_error()
+    flops = 2.0 * a.tokens * a.top_k * 3 * a.hidden * a.inter
+    touched = min(a.experts, a.tokens * a.top_k)
+    report("moe_layer_bf16", ms, flops=flops, nbytes=touched * 3 * a.hidden * a.inter * 2.0, tokens=a.tokens, experts=a.experts,
+           top_k=a.top_k, hidden=a.hidden, inter=a.inter)
+
+
 def _cache(seqs, ctx, hk, d, page):
     per = (ctx + page - 1) // page
     pool = torch.randn(seqs * per + 1, 2, hk, page, d, device="cuda").to(torch.bfloat16)
@@ -142,6 +173,12 @@ def main(argv=None):
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=4096); g.add_argument("--n", type=int, default=4096); g.add_argument("--k", type=int, default=4096)
     g.add_argument("--epilogue", default="store"); g.add_argument("--bn", type=int, default=None); g.add_argument("--compare", action="store_true")
+    g8 = sub.add_parser("gemm_fp8")
+    g8.add_argument("--m", type=int, default=4096); g8.add_argument("--n", type=int, default=4096); g8.add_argument("--k", type=int, default=4096)
+    g8.add_argument("--bn", type=int, default=None)
+    mo = sub.add_parser("moe")
+    mo.add_argument("--tokens", type=int, default=2048); mo.add_argument("--experts", type=int, default=128); mo.add_argument("--top-k", type=int, default=8)
+    mo.add_argument("--hidden", type=int, default=2048); mo.add_argument("--inter", type=int, default=768)
     d = sub.add_parser("attn_decode")
     p = sub.add_parser("attn_prefill")
     for s in (d, p):
@@ -151,10 +188,10 @@ def main(argv=None):
     p.add_argument("--prefix", type=int, default=0)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=4096); n.add_argument("--n", type=int, default=4096)
-    for s in (g, d, p, n):
+    for s in (g, d, p, n, g8, mo):
         s.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "norm": bench_norm}[a.op](a)
+    {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "moe": bench_moe, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "norm": bench_norm}[a.op](a)
 
 
 if __name__ == "__main__":

@@ -58,3 +58,28 @@ def test_gemm_partial_rows_and_strided_a(cuda):
     ref = gemm_reference(a[:100], w)
     torch.testing.assert_close(out[:100].float(), ref.float(), rtol=2e-2, atol=3e-2)
     assert float(out[100:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (77, 384, 512), (300, 1024, 1024), (2048, 4096, 4096)])
+def test_gemm_fp8_e4m3(cuda, m, n, k):
+    """kind::f8f6f4 GEMM against fp32 math on the same quantised operands, and the quantiser against torch's cast."""
+    from kern_b200.ops import gemm_fp8 as F8
+    from kern_b200.ops.launcher import Kernels
+
+    torch.manual_seed(m + n)
+    a = (torch.randn(m, k, device=cuda) * 2).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=cuda) * 0.5).to(torch.bfloat16)
+    aq, sa = F8.quantize(a)
+    wq, sw = F8.quantize(w)
+    torch.cuda.synchronize()
+    assert abs(float(sa) - float(a.float().abs().max()) / 448) < 1e-6
+    ref_q = (a.float() / sa).to(torch.float8_e4m3fn).view(torch.uint8)
+    assert (aq != ref_q).float().mean() < 1e-3          # identical but for ties in rounding
+    out = F8.gemm_fp8(aq, wq, sa, sw)
+    torch.cuda.synchronize()
+    Kernels.get(cuda).check_error()
+    ref = F8.dequant(aq, sa) @ F8.dequant(wq, sw).t()
+    torch.testing.assert_close(out.float(), ref, rtol=1.6e-2, atol=1e-2 * float(ref.abs().max()))
+    res = torch.randn(m, n, device=cuda).to(torch.bfloat16)
+    out2 = F8.gemm_fp8(aq, wq, sa, sw, residual=res, out=torch.empty_like(res))
+    torch.testing.assert_close(out2.float(), ref + res.float(), rtol=1.6e-2, atol=1e-2 * float(ref.abs().max()))
