@@ -63,6 +63,7 @@ class Stats:
     prefix_hits: int = 0
     prefix_hit_tokens: int = 0
     prefix_queries: int = 0
+    pooled_hit_tokens: int = 0
     evictions: int = 0
     accepted: int = 0
     proposed: int = 0
@@ -72,8 +73,11 @@ class Stats:
 
 class Scheduler:
     def __init__(self, engine: Engine, chunk: int | None = None, max_seqs: int | None = None, prefix_cache: bool = True,
-                 rows: int | None = None, stats_every: float = 5.0):
+                 rows: int | None = None, stats_every: float = 5.0, pooled=None):
+        """`pooled`: a `PooledCache` (a tier shared with other engines, or an SSD arena) consulted after the local
+        prefix cache at admission and fed when requests finish."""
         self.eng = engine
+        self.pooled = pooled
         self.pool = engine.pool
         self.chunk = min(chunk or engine.rows_max, engine.rows_max)
         row_shapes = sorted(f["rows"] for f in engine.forwards if f["rows"] != "var")
@@ -155,6 +159,14 @@ class Scheduler:
                     self.stats.prefix_hit_tokens += length
                 else:
                     req.seq = self.eng.open(need, req.sampling)
+                if self.pooled is not None and len(req.prompt) > 1:
+                    have = req.seq.length
+                    got = self.pooled.fetch(req.prompt, have, list(req.seq.lease.pages), len(req.prompt) - 1)
+                    if got > have:
+                        req.seq.length = got
+                        req.seq.tokens = list(req.prompt[:got])
+                        req.fed = req.cached = got
+                        self.stats.pooled_hit_tokens += got - have
                 return True
             except _native.Denied as e:
                 why = e.args[1] if len(e.args) > 1 else "busy"
@@ -191,6 +203,8 @@ class Scheduler:
         if length == 0:
             self.eng.close(seq)
             return
+        if self.pooled is not None and not stateful:
+            self.pooled.put(tokens[:length], list(seq.lease.pages))
         ckpt = self.pool.retire(seq.lease, length)
         self.prefix.insert(tokens, ckpt, stateful, length)
 
