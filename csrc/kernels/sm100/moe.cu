@@ -127,16 +127,11 @@ extern "C" __global__ void __launch_bounds__(1024)
     rows_out[0] = at;
   }
   __syncthreads();
-  // stable placement: entries of one expert keep token order, so a run is reproducible bit for bit
-  for (int e = threadIdx.x; e < el; e += blockDim.x) {
-    if (counts[e] == 0) continue;
-    int at = cursor[e];
-    for (int i = 0; i < entries; ++i)
-      if (topk_ids[i] == e + e_lo) perm[i] = at++;
-  }
+  // placement: an entry takes the next free row of its expert. The order inside an expert is whatever the atomics
+  // give; every output row depends only on its own input row and the expert's weights, so the result's bits do not.
   for (int i = threadIdx.x; i < entries; i += blockDim.x) {
     const int e = topk_ids[i];
-    if (e < e_lo || e >= e_hi) perm[i] = -1;
+    perm[i] = (e >= e_lo && e < e_hi) ? atomicAdd(&cursor[e - e_lo], 1) : -1;
   }
 }
 
