@@ -78,6 +78,19 @@ def _gemm(epi):
     return run
 
 
+def _gemv(epi):
+    def run(g, a, w, c, r, m, n, k, lda, ldc, err):
+        av = torch.as_strided(a, (m, k), (lda, 1), a.storage_offset())
+        acc = _f(av) @ _f(w[: n * k].view(n, k)).t()
+        if epi == "swiglu":
+            acc = torch.nn.functional.silu(acc[:, : n // 2]) * acc[:, n // 2:]
+        cv = torch.as_strided(c, (m, acc.shape[1]), (ldc, 1), c.storage_offset())
+        if epi == "acc":
+            acc = acc + _f(torch.as_strided(r, (m, n), (ldc, 1), r.storage_offset()))
+        cv.copy_(acc.to(c.dtype))
+    return run
+
+
 def a_stride(a, k):
     return getattr(a, "_row_stride", k)
 
@@ -301,6 +314,8 @@ CPU_KERNELS = {
 for _bn in (256, 128, 64, 32):
     for _epi, _sfx in (("store", ""), ("acc", "_acc"), ("f32", "_f32"), ("swiglu", "_swiglu")):
         CPU_KERNELS[f"kern_gemm_bf16_tn{_sfx}_n{_bn}"] = _gemm(_epi)
+        for _mt in (1, 2, 4, 8):
+            CPU_KERNELS[f"kern_gemv_bf16_tn{_sfx}_m{_mt}"] = _gemv(_epi)
 for _d in (16, 32, 64, 128, 256):
     CPU_KERNELS[f"kern_attn_prefill_paged_d{_d}"] = _attention(True)
     CPU_KERNELS[f"kern_attn_decode_paged_d{_d}"] = _attention(False)

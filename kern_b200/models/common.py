@@ -37,6 +37,9 @@ def kernel_index() -> dict:
 
 def modules_for(names) -> dict:
     idx = kernel_index()
+    names = list(names)
+    if "gemm_bf16" in names and "gemv_bf16" not in names:
+        names.append("gemv_bf16")          # every gemm_op carries the weight-streaming launches for a handful of rows
     return {n: {"source": idx[n]["source"], "sha256": idx[n]["sha256"], "multicast": False} for n in names}
 
 
@@ -82,6 +85,9 @@ def f64_bits(v: float) -> int:
 
 
 # ---- op builders: one place that knows each kernel's launch ABI ------------------------------------
+GEMV_ROWS = 8
+
+
 def gemm_smem(bn: int) -> int:
     return 1024 + GEMM_STAGES[bn] * (BM * BK * 2 + bn * BK * 2) + 256
 
@@ -121,7 +127,28 @@ def gemm_op(n: int, k: int, *, epilogue: str = "store", rows_var: str = "tokens"
     lparams = ["bytes<128>", "bytes<128>", f"{cdir} buffer<{cdt}>", "in buffer<bf16>", "i32", "i32", "i32", "i32",
                "out buffer<i32>"]
     launches = []
+    # a handful of rows: the weight-streaming kernel (one launch per row-count class), above it the tensor-core tiles
+    for mt, lo in ((1, 1), (2, 2), (4, 3), (8, 5)):
+        hi = min(mt, rows_max)
+        if lo > hi:
+            continue
+        when = {"var": rows_var}
+        if lo > 1:
+            when["min"] = lo
+        if hi < rows_max:
+            when["max"] = hi
+        launch = {"module": "gemv_bf16", "entry": f"kern_gemv_bf16_tn{suffix}_m{mt}", "block": [256, 1, 1], "grid": [4 * SMS, 1, 1],
+                  "params": ["in buffer<bf16>", "in buffer<bf16>", f"{cdir} buffer<{cdt}>", "in buffer<bf16>" if epilogue == "acc" else "i64",
+                             "i32", "i32", "i32", "i32", "i32", "out buffer<i32>"],
+                  "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"param": 2} if epilogue == "acc" else {"i64": 0}, {"param": 3},
+                           {"i32": n}, {"i32": k}, {"i32": lda}, {"i32": ldc}, {"param": 4}]}
+        if len(when) > 1:
+            launch["when"] = when
+        launches.append(launch)
     for bn, lo, hi in gemm_ranges(n, rows_max):
+        lo = max(lo, GEMV_ROWS + 1)
+        if lo > hi:
+            continue
         when = {"var": rows_var}
         if lo > 1:
             when["min"] = lo

@@ -83,3 +83,25 @@ def test_gemm_fp8_e4m3(cuda, m, n, k):
     res = torch.randn(m, n, device=cuda).to(torch.bfloat16)
     out2 = F8.gemm_fp8(aq, wq, sa, sw, residual=res, out=torch.empty_like(res))
     torch.testing.assert_close(out2.float(), ref + res.float(), rtol=1.6e-2, atol=1e-2 * float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("epilogue", ["store", "f32", "acc", "swiglu"])
+@pytest.mark.parametrize("m,n,k", [(1, 256, 128), (2, 1000, 448), (3, 4096, 4096), (5, 776, 1024), (8, 6144, 2048)])
+def test_gemv_small_rows(cuda, epilogue, m, n, k):
+    """A handful of rows take the weight-streaming kernel; same results as the fp32 statement."""
+    from kern_b200.ops.gemm import GEMV_ROWS, gemm, gemm_reference
+    from kern_b200.ops.launcher import Kernels
+
+    assert m <= GEMV_ROWS
+    if epilogue == "swiglu" and n % 16:
+        n = n // 16 * 16
+    torch.manual_seed(m * 7 + n)
+    a = torch.randn(m + 3, k + 64, device=cuda).to(torch.bfloat16)[:m, :k]          # a strided view: lda != k
+    w = (torch.randn(n, k, device=cuda) * k ** -0.5).to(torch.bfloat16)
+    res = torch.randn(m, n, device=cuda).to(torch.bfloat16) if epilogue == "acc" else None
+    out = res.clone() if res is not None else None
+    got = gemm(a, w, out=out, epilogue=epilogue)
+    torch.cuda.synchronize()
+    Kernels.get(cuda).check_error()
+    ref = gemm_reference(a, w, epilogue, res)
+    torch.testing.assert_close(got.float(), ref.float(), rtol=1.6e-2, atol=1.6e-2)
