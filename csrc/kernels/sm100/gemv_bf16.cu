@@ -3,8 +3,9 @@
 // would leave most of the machine idle and most of the tile empty at these sizes. The op is bandwidth-bound: the
 // roofline is the weight bytes over the copy bandwidth.
 //
-// A warp owns four weight rows at a time (so A is fetched once per four outputs), each lane strides over the K vectors,
-// partial sums are reduced with shuffles at the end. Persistent grid: warps take row groups round-robin.
+// A CTA owns four weight rows at a time (so A is fetched once per four outputs); its 256 threads stride over the K
+// vectors of those rows, partial sums meet through shuffles and shared memory. Persistent grid: CTAs take row groups
+// round-robin, eight or so resident per SM, so tens of kilobytes of loads are in flight on every SM.
 // Epilogues as in the tensor-core GEMM: 0 store bf16, 1 store f32, 2 accumulate into a bf16 residual, 3 SwiGLU over
 // weights stacked [gate rows ; up rows] (two gate rows and their two up rows per group).
 // (The reference calls a library GEMM for every shape; this kernel has no counterpart there.)
@@ -17,14 +18,13 @@ namespace {
 template <int MT, int EPI>
 __device__ __forceinline__ void gemv_body(const __nv_bfloat16* A, const __nv_bfloat16* W, void* Cv, const void* Rv, int M,
                                           int N, int K, int lda, int ldc) {
-  constexpr int R = 4;                       // weight rows per warp per group
+  constexpr int R = 4;                       // weight rows per CTA per group
+  __shared__ float part[8][MT * R];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int warps = gridDim.x * (blockDim.x >> 5);
-  const int gw = blockIdx.x * (blockDim.x >> 5) + warp;
   const int kv = K >> 3;
   const int half = N >> 1;
   const int groups = EPI == 3 ? (half + 1) / 2 : (N + R - 1) / R;
-  for (int g = gw; g < groups; g += warps) {
+  for (int g = blockIdx.x; g < groups; g += gridDim.x) {
     int rows[R];
     if constexpr (EPI == 3) {
       rows[0] = 2 * g; rows[1] = 2 * g + 1; rows[2] = half + 2 * g; rows[3] = half + 2 * g + 1;
@@ -42,8 +42,9 @@ __device__ __forceinline__ void gemv_body(const __nv_bfloat16* A, const __nv_bfl
     const uint4* w1 = reinterpret_cast<const uint4*>(W + (size_t)rows[1] * K);
     const uint4* w2 = reinterpret_cast<const uint4*>(W + (size_t)rows[2] * K);
     const uint4* w3 = reinterpret_cast<const uint4*>(W + (size_t)rows[3] * K);
+    // the whole CTA strides over the K vectors of its four rows: 256 x 4 x 16 bytes in flight per pass
 #pragma unroll 2
-    for (int v = lane; v < kv; v += 32) {
+    for (int v = threadIdx.x; v < kv; v += 256) {
       uint4 wv[R];
       wv[0] = __ldcs(w0 + v); wv[1] = __ldcs(w1 + v); wv[2] = __ldcs(w2 + v); wv[3] = __ldcs(w3 + v);   // streamed once
       float wf[R][8];
@@ -68,32 +69,45 @@ __device__ __forceinline__ void gemv_body(const __nv_bfloat16* A, const __nv_bfl
 #pragma unroll
     for (int m = 0; m < MT; ++m)
 #pragma unroll
-      for (int r = 0; r < R; ++r) acc[m][r] = warp_sum(acc[m][r]);
-    if (lane == 0) {
+      for (int r = 0; r < R; ++r) {
+        const float s = warp_sum(acc[m][r]);
+        if (lane == 0) part[warp][m * R + r] = s;
+      }
+    __syncthreads();
+    if (threadIdx.x < MT * R) {
+      const int m = threadIdx.x / R, r = threadIdx.x % R;
+      float s = 0.f;
 #pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        if (m >= M) break;
+      for (int w = 0; w < 8; ++w) s += part[w][threadIdx.x];
+      part[0][threadIdx.x] = s;            // column threadIdx.x is only read by this thread above
+      (void)m; (void)r;
+    }
+    __syncthreads();
+    if (threadIdx.x < MT * R) {
+      const int m = threadIdx.x / R, r = threadIdx.x % R;
+      if (m < M) {
         if constexpr (EPI == 3) {
-          __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(Cv) + (size_t)m * ldc;
-          C[2 * g] = __float2bfloat16(silu(acc[m][0]) * acc[m][2]);
-          if (2 * g + 1 < half) C[2 * g + 1] = __float2bfloat16(silu(acc[m][1]) * acc[m][3]);
+          // outputs 2g (r = 0) and 2g + 1 (r = 1): gate in columns 0..1, up in 2..3
+          if (r < 2 && 2 * g + r < half)
+            reinterpret_cast<__nv_bfloat16*>(Cv)[(size_t)m * ldc + 2 * g + r] =
+                __float2bfloat16(silu(part[0][m * R + r]) * part[0][m * R + 2 + r]);
         } else {
-#pragma unroll
-          for (int r = 0; r < R; ++r) {
-            const int n = g * R + r;
-            if (n >= N) break;
+          const int n = g * R + r;
+          if (n < N) {
+            const float v = part[0][threadIdx.x];
             if constexpr (EPI == 1) {
-              reinterpret_cast<float*>(Cv)[(size_t)m * ldc + n] = acc[m][r];
+              reinterpret_cast<float*>(Cv)[(size_t)m * ldc + n] = v;
             } else if constexpr (EPI == 2) {
               const float res = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(Rv)[(size_t)m * ldc + n]);
-              reinterpret_cast<__nv_bfloat16*>(Cv)[(size_t)m * ldc + n] = __float2bfloat16(acc[m][r] + res);
+              reinterpret_cast<__nv_bfloat16*>(Cv)[(size_t)m * ldc + n] = __float2bfloat16(v + res);
             } else {
-              reinterpret_cast<__nv_bfloat16*>(Cv)[(size_t)m * ldc + n] = __float2bfloat16(acc[m][r]);
+              reinterpret_cast<__nv_bfloat16*>(Cv)[(size_t)m * ldc + n] = __float2bfloat16(v);
             }
           }
         }
       }
     }
+    __syncthreads();     // `part` is reused by the next group
   }
 }
 

@@ -137,7 +137,7 @@ def gemm_op(n: int, k: int, *, epilogue: str = "store", rows_var: str = "tokens"
             when["min"] = lo
         if hi < rows_max:
             when["max"] = hi
-        launch = {"module": "gemv_bf16", "entry": f"kern_gemv_bf16_tn{suffix}_m{mt}", "block": [256, 1, 1], "grid": [4 * SMS, 1, 1],
+        launch = {"module": "gemv_bf16", "entry": f"kern_gemv_bf16_tn{suffix}_m{mt}", "block": [256, 1, 1], "grid": [8 * SMS, 1, 1],
                   "params": ["in buffer<bf16>", "in buffer<bf16>", f"{cdir} buffer<{cdt}>", "in buffer<bf16>" if epilogue == "acc" else "i64",
                              "i32", "i32", "i32", "i32", "i32", "out buffer<i32>"],
                   "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"param": 2} if epilogue == "acc" else {"i64": 0}, {"param": 3},
