@@ -121,9 +121,14 @@ KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a) {
   // query token r (0-based among this step's R rows) sits at position L - R + r
   const int last_pos = L - R + tok_lo + tok_n - 1;
   const int ntiles_all = last_pos / TK + 1;
+  // `splits` packs three numbers: bits 0-7 the KV splits of this launch, bits 8-15 the first partial slot it writes,
+  // bits 16-31 the partial slots per (row, head) in the workspace (0: same as the splits). A context-parallel rank
+  // writes its partials into its own run of slots of a workspace that holds every rank's; one merge covers them all.
+  const int nsplit = a.splits & 0xff, split_base = (a.splits >> 8) & 0xff;
+  const int split_total = (a.splits >> 16) ? (a.splits >> 16) : nsplit;
   int tile_lo = 0, tile_hi = ntiles_all;
-  if (a.splits > 1) {
-    const int per = (ntiles_all + a.splits - 1) / a.splits;
+  if (nsplit > 1) {
+    const int per = (ntiles_all + nsplit - 1) / nsplit;
     tile_lo = split * per;
     tile_hi = min(ntiles_all, tile_lo + per);
     if (tile_hi < tile_lo) tile_hi = tile_lo;
@@ -336,11 +341,11 @@ KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a) {
         acc += mo[(w * 16 + r) * D + c] * f;
       }
       const int tk = row0_tok + tok_lo + r / G, head = kvh * G + r % G;
-      if (a.splits == 1) {
+      if (split_total == 1) {
         a.out[(size_t)tk * a.out_stride + (size_t)head * D + c] =
             __float2bfloat16(l > 0.f ? acc / l : 0.f);
       } else {
-        const size_t base = ((size_t)tk * a.hq + head) * a.splits + split;
+        const size_t base = ((size_t)tk * a.hq + head) * split_total + split_base + split;
         a.ws_o[base * D + c] = acc;
         if (c == 0) {
           a.ws_ml[base * 2] = m;

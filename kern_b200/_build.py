@@ -14,6 +14,7 @@ from __future__ import annotations
 import fcntl
 import hashlib
 import json
+import re
 import os
 import subprocess
 import sys
@@ -65,7 +66,9 @@ def build_kernels(force: bool = False, verbose: bool = False) -> dict[str, dict]
     jobs = []
     for src in kernel_sources():
         out = KOUT / (src.stem + ".cubin")
-        if force or _newer([src, *headers], out):
+        # a source that includes another kernel source (the GEMM body shared by several modules) depends on it too
+        included = [KSRC / m for m in re.findall(r'#include\s+"([\w.]+\.cu)"', src.read_text())]
+        if force or _newer([src, *headers, *included], out):
             jobs.append((src, out))
 
     def one(job):
@@ -139,7 +142,7 @@ def build_host_libs(force: bool = False) -> list[Path]:
     outs = []
     for src in sorted(HSRC.glob("*.cu")):
         out = PKG / ("lib" + src.stem + ".so")
-        if force or _newer([src, *KSRC.glob("*.cuh")], out):
+        if force or _newer([src, *HSRC.glob("*.h"), *KSRC.glob("*.cuh"), *KSRC.glob("*.cu")], out):   # host sources include kernel sources
             _run([NVCC, *ARCH, "-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC",
                   "-I", str(KSRC), "-o", str(out), str(src), "-lcudart"])
         outs.append(out)

@@ -65,8 +65,13 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tens
                     prefill: bool = False, cu_q: torch.Tensor | None = None, rows_per_seq: int = 1,
                     max_rows: int | None = None, seqs: int | None = None, splits: int | None = None,
                     max_len: int | None = None, scale: float | None = None,
-                    workspace: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
+                    workspace: tuple[torch.Tensor, torch.Tensor] | None = None,
+                    partial: tuple[int, int] | None = None) -> torch.Tensor:
     """Attention of this step's query rows over each sequence's paged context.
+
+    ``partial=(base, total)`` (decode only): write un-normalised partials into slots ``base .. base+splits-1`` of a
+    workspace with ``total`` slots per (row, head) and skip the merge — a context-parallel rank's share;
+    ``merge_partials`` finishes once every share is in.
 
     ``q``: 2-D bf16 view whose row t holds the ``hq`` query heads of token t (a column slice of the
     fused qkv buffer works: the row stride is free). ``seq_lens[s]`` counts the context *including*
@@ -94,13 +99,16 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tens
     elif splits is None:
         splits = pick_splits(hk * nblk * n_seqs, max_len, k.sm_count)
     ws_o = ws_ml = None
-    if splits > 1:
+    total = splits if partial is None else partial[1]
+    if partial is not None:
+        assert not prefill and workspace is not None and partial[0] + splits <= total < 65536 and partial[0] < 256
+    if total > 1:
         if workspace is not None:
             ws_o, ws_ml = workspace
         else:
-            ws_o = torch.empty(q.shape[0] * hq * splits * d, dtype=torch.float32, device=q.device)
-            ws_ml = torch.empty(q.shape[0] * hq * splits * 2, dtype=torch.float32, device=q.device)
-        assert ws_o.numel() >= q.shape[0] * hq * splits * d
+            ws_o = torch.empty(q.shape[0] * hq * total * d, dtype=torch.float32, device=q.device)
+            ws_ml = torch.empty(q.shape[0] * hq * total * 2, dtype=torch.float32, device=q.device)
+        assert ws_o.numel() >= q.shape[0] * hq * total * d
     view = pool.view(pages * 2 * hk * page_size, d)
     kv_map = k.tensor_map_2d(view, min(page_size, TK), 64)
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
@@ -118,14 +126,29 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tens
     k.launch("attn_paged", entry, grid, (160,),
              [kv_map, ptr(q), ptr(out), ptr(ws_o), ptr(ws_ml), ptr(block_table), ptr(seq_lens),
               ptr(cu_q), ptr(work), ptr(count), i32(n_seqs), i32(hq), i32(hk), i32(q.stride(0)), i32(out.stride(0)),
-              i32(block_table.shape[1]), i32(page_size), i32(rows_per_seq), i32(splits), i32(pages),
+              i32(block_table.shape[1]), i32(page_size), i32(rows_per_seq),
+              i32(splits if partial is None else splits | (partial[0] << 8) | (total << 16)), i32(pages),
               f32(scale * 1.4426950408889634), ptr(k.err_word())],
              shared_mem=_attn_smem(d))
-    if splits > 1:
-        rows = q.shape[0] * hq
-        k.launch("attn_paged", "kern_attn_merge_splits", (rows,), (min(256, d),),
-                 [ptr(ws_o), ptr(ws_ml), ptr(out), i32(rows), i32(hq), i32(d), i32(splits),
-                  i32(out.stride(0))])
+    if splits > 1 and partial is None:
+        merge_partials(ws_o, ws_ml, out, q.shape[0], hq, d, splits)
+    return out
+
+
+def new_partials(rows: int, hq: int, d: int, total: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """A workspace of `total` partial slots per (row, head), every slot neutral (m = -inf, l = 0): a rank whose share
+    of a sequence is empty leaves its slots as they are."""
+    ws_o = torch.zeros(rows * hq * total * d, dtype=torch.float32, device=device)
+    ws_ml = torch.zeros(rows * hq * total, 2, dtype=torch.float32, device=device)
+    ws_ml[:, 0] = float("-inf")
+    return ws_o, ws_ml.view(-1)
+
+
+def merge_partials(ws_o, ws_ml, out, rows: int, hq: int, d: int, total: int) -> torch.Tensor:
+    k = Kernels.get(out.device)
+    n = rows * hq
+    k.launch("attn_paged", "kern_attn_merge_splits", (n,), (min(256, d),),
+             [ptr(ws_o), ptr(ws_ml), ptr(out), i32(n), i32(hq), i32(d), i32(total), i32(out.stride(0))])
     return out
 
 

@@ -203,3 +203,42 @@ def test_rope_kv_append(cuda, hq, hk, d, rot, qk_norm):
         pg, off = s // page_size, s % page_size
         torch.testing.assert_close(pool[pg, 0, :, off].float(), k_ref[i], rtol=2e-2, atol=2e-2)
         assert torch.equal(pool[pg, 1, :, off], v0[i])
+
+
+@pytest.mark.parametrize("width", [2, 4])
+def test_decode_attention_context_parallel_partials(cuda, width):
+    """Positions dealt round-robin over `width` ranks (rank m holds p with p % width == m): every rank's partial over
+    its own pages, written into its run of slots of one workspace, merged once, equals attention over the whole context."""
+    from kern_b200.ops import attention as A
+
+    torch.manual_seed(11)
+    hq, hk, d, page = 16, 4, 128, 16
+    lens = [1, 3, 64, 65, 300, 777]
+    seqs = len(lens)
+    q = bf(torch.randn(seqs, hq * d, device=cuda))
+    ks = [bf(torch.randn(l, hk, d, device=cuda)) for l in lens]
+    vs = [bf(torch.randn(l, hk, d, device=cuda)) for l in lens]
+    splits = 2
+    ws = A.new_partials(seqs, hq, d, width * splits, cuda)
+    out = torch.empty(seqs, hq * d, dtype=torch.bfloat16, device=cuda)
+    for m in range(width):
+        local = [len(range(m, l, width)) for l in lens]
+        pages_needed = sum(-(-n // page) for n in local) + 1
+        pool = torch.zeros(pages_needed, 2, hk, page, d, dtype=torch.bfloat16, device=cuda)
+        table = torch.zeros(seqs, max(1, max(-(-n // page) for n in local)), dtype=torch.int32, device=cuda)
+        nxt = 1
+        for s, l in enumerate(lens):
+            kk, vv = ks[s][m::width], vs[s][m::width]
+            for p in range(-(-local[s] // page)):
+                table[s, p] = nxt
+                lo, hi = p * page, min(local[s], (p + 1) * page)
+                pool[nxt, 0, :, : hi - lo] = kk[lo:hi].transpose(0, 1)
+                pool[nxt, 1, :, : hi - lo] = vv[lo:hi].transpose(0, 1)
+                nxt += 1
+        A.paged_attention(q, pool, table, torch.tensor(local, dtype=torch.int32, device=cuda), hq, out=out, splits=splits,
+                          workspace=ws, partial=(m * splits, width * splits))
+    A.merge_partials(ws[0], ws[1], out, seqs, hq, d, width * splits)
+    check_err(cuda)
+    for s, l in enumerate(lens):
+        ref = A.attention_reference(q[s:s + 1].view(1, hq, d), ks[s], vs[s], torch.tensor([l - 1], device=cuda))
+        torch.testing.assert_close(out[s:s + 1].float(), ref, rtol=2e-2, atol=2e-2)
