@@ -1,4 +1,4 @@
-// C[M, N] = A[M, K] . W[N, K]^T for a handful of rows (up to 16) (decode steps of a few sequences): the weights are read once,
+// C[M, N] = A[M, K] . W[N, K]^T for a handful of rows (decode steps of a few sequences): the weights are read once,
 // straight from HBM with 16-byte loads, and every one of the 148 SMs streams its share — a 128-row tensor-core tile
 // would leave most of the machine idle and most of the tile empty at these sizes. The op is bandwidth-bound: the
 // roofline is the weight bytes over the copy bandwidth.
@@ -135,4 +135,3 @@ KERN_GEMV_FAMILY(1)
 KERN_GEMV_FAMILY(2)
 KERN_GEMV_FAMILY(4)
 KERN_GEMV_FAMILY(8)
-KERN_GEMV_FAMILY(16)

@@ -314,7 +314,7 @@ CPU_KERNELS = {
 for _bn in (256, 128, 64, 32):
     for _epi, _sfx in (("store", ""), ("acc", "_acc"), ("f32", "_f32"), ("swiglu", "_swiglu")):
         CPU_KERNELS[f"kern_gemm_bf16_tn{_sfx}_n{_bn}"] = _gemm(_epi)
-        for _mt in (1, 2, 4, 8, 16):
+        for _mt in (1, 2, 4, 8):
             CPU_KERNELS[f"kern_gemv_bf16_tn{_sfx}_m{_mt}"] = _gemv(_epi)
 for _d in (16, 32, 64, 128, 256):
     CPU_KERNELS[f"kern_attn_prefill_paged_d{_d}"] = _attention(True)

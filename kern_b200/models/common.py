@@ -85,7 +85,7 @@ def f64_bits(v: float) -> int:
 
 
 # ---- op builders: one place that knows each kernel's launch ABI ------------------------------------
-GEMV_ROWS = 16
+GEMV_ROWS = 4
 
 
 def gemm_smem(bn: int) -> int:
@@ -128,7 +128,7 @@ def gemm_op(n: int, k: int, *, epilogue: str = "store", rows_var: str = "tokens"
                "out buffer<i32>"]
     launches = []
     # a handful of rows: the weight-streaming kernel (one launch per row-count class), above it the tensor-core tiles
-    for mt, lo in ((1, 1), (2, 2), (4, 3), (8, 5), (16, 9)):
+    for mt, lo in ((1, 1), (2, 2), (4, 3)):
         hi = min(mt, rows_max)
         if lo > hi:
             continue

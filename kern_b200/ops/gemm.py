@@ -38,7 +38,8 @@ def stack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.cat([gate, up], 0).contiguous()
 
 
-GEMV_ROWS = 16       # up to this many rows the weight-streaming kernel runs instead of the tensor-core tiles
+GEMV_ROWS = 4        # up to this many rows the weight-streaming kernel runs instead of the tensor-core tiles
+                     # (measured: at 16 rows the activations' L1 traffic makes it 2-3x slower than the tiles)
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *,
@@ -70,7 +71,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *,
         return out
     if bn is None and M <= GEMV_ROWS and w.is_contiguous():
         # a handful of rows: stream the weights once on every SM instead of filling one 128-row tile
-        mt = next(t for t in (1, 2, 4, 8, 16) if M <= t)
+        mt = next(t for t in (1, 2, 4, 8) if M <= t)
         k.launch("gemv_bf16", f"kern_gemv_bf16_tn{_EPI[epilogue]}_m{mt}", (k.sm_count * 8,), (256,),
                  [ptr(a), ptr(w), ptr(out), ptr(residual), i32(M), i32(N), i32(K), i32(a.stride(0)), i32(out.stride(0)), ptr(k.err_word())], pdl=pdl)
         return out

@@ -86,7 +86,7 @@ def test_gemm_fp8_e4m3(cuda, m, n, k):
 
 
 @pytest.mark.parametrize("epilogue", ["store", "f32", "acc", "swiglu"])
-@pytest.mark.parametrize("m,n,k", [(1, 256, 128), (2, 1000, 448), (3, 4096, 4096), (5, 776, 1024), (8, 6144, 2048), (13, 512, 1024), (16, 4096, 2048)])
+@pytest.mark.parametrize("m,n,k", [(1, 256, 128), (2, 1000, 448), (3, 4096, 4096), (4, 776, 1024)])
 def test_gemv_small_rows(cuda, epilogue, m, n, k):
     """A handful of rows take the weight-streaming kernel; same results as the fp32 statement."""
     from kern_b200.ops.gemm import GEMV_ROWS, gemm, gemm_reference
