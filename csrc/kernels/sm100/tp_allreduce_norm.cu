@@ -332,3 +332,53 @@ extern "C" __global__ void __launch_bounds__(kThreads)
   }
   pdl_launch_dependents();
 }
+
+// ---- all-gather over peer memory -------------------------------------------------------------------------------
+// Every rank contributes `bytes` bytes (a multiple of 16); afterwards y on every rank holds the nranks blocks in rank
+// order. Each CTA j moves its slice of the local block into slot [parity][rank] of every peer's staging buffer, raises
+// its epoch flag on every peer, waits (bounded) for every peer's flag of the same CTA, then copies its slice of all
+// slots out to y. Parity double-buffering lets the next call start while a slow peer still reads this one.
+//   sym   : [2 parities][nranks][slot_bytes] on every rank (exported);   flags: [nranks][flag_stride] u32 (exported)
+// grid G <= flag_stride (the same on every rank), block 256.
+// Reference counterpart: tools/kernels-src/peer_collective.cu:128 (LL-style all-gather with per-CTA epochs).
+extern "C" __global__ void __launch_bounds__(kThreads)
+    kern_peer_allgather(const uint8_t* x, uint8_t* y, uint8_t* sym, const unsigned long long* sym_peers, uint32_t* flags,
+                        const unsigned long long* flag_peers, uint32_t* epochs, int* err, int rank, int nranks,
+                        long long bytes, long long slot_bytes, long long timeout_ns, int flag_stride) {
+  __shared__ int failed;
+  pdl_wait();
+  const int j = blockIdx.x, G = gridDim.x;
+  if (threadIdx.x == 0) failed = 0;
+  const uint32_t epoch = epochs[j] + 1;
+  __syncthreads();
+  if (threadIdx.x == 0) epochs[j] = epoch;
+  if (bytes > slot_bytes || (bytes & 15)) {
+    if (threadIdx.x == 0) set_error(err, ERR_BOUNDS);
+    return;
+  }
+  const long long parity_off = (long long)(epoch & 1) * nranks * slot_bytes;
+  const long long nvec = bytes / 16;
+  const long long per = (nvec + G - 1) / G, lo = j * per, hi = lo + per < nvec ? lo + per : nvec;
+  const uint4* src = reinterpret_cast<const uint4*>(x);
+  for (int p = 0; p < nranks; ++p) {
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sym_peers[p]) + parity_off + (long long)rank * slot_bytes);
+    for (long long v = lo + threadIdx.x; v < hi; v += kThreads) dst[v] = src[v];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < nranks) {
+    st_release_sys(reinterpret_cast<uint32_t*>(flag_peers[threadIdx.x]) + (size_t)rank * flag_stride + j, epoch);
+    if (!wait_flag(flags + (size_t)threadIdx.x * flag_stride + j, epoch, timeout_ns)) {
+      set_error(err, ERR_WAIT_PEER + threadIdx.x);
+      failed = 1;
+    }
+  }
+  __syncthreads();
+  if (failed) return;
+  for (int r = 0; r < nranks; ++r) {
+    const uint4* s = reinterpret_cast<const uint4*>(sym + parity_off + (long long)r * slot_bytes);
+    uint4* d = reinterpret_cast<uint4*>(y + (long long)r * bytes);
+    for (long long v = lo + threadIdx.x; v < hi; v += kThreads) d[v] = ld_volatile16(s + v);
+  }
+  pdl_launch_dependents();
+}

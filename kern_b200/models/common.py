@@ -485,6 +485,28 @@ def tp_gemm_reduce_op(n: int, k: int, nranks: int, rows_max: int, group: str = "
     return {"params": iface, "impl": {"launches": launches}}
 
 
+AG_GRID = 64
+
+
+def tp_allgather_op(nranks: int, slot_bytes: int, group: str = "tp", timeout_ns: int = 2_000_000_000) -> dict:
+    """All-gather of one block per rank over peer memory. Interface [x, y, sym, sym_peers, flags, flag_peers, epochs, err, bytes]."""
+    iface = ["in buffer<u8>", "out buffer<u8>", "inout buffer<u8>", "in buffer<u64>", "inout buffer<u32>", "in buffer<u64>",
+             "inout buffer<u32>", "out buffer<i32>", "i64"]
+    return {"params": iface, "impl": {"launches": [{
+        "module": "tp_allreduce_norm", "entry": "kern_peer_allgather", "block": [256, 1, 1], "grid": [AG_GRID, 1, 1],
+        "params": iface[:8] + ["i32", "i32", "i64", "i64", "i64", "i32"],
+        "args": [{"param": i} for i in range(8)] + [{"rank": group}, {"i32": nranks}, {"param": 8}, {"i64": slot_bytes},
+                                                     {"i64": timeout_ns}, {"i32": AG_GRID}]}]}}
+
+
+def tp_allgather_buffers(nranks: int, slot_bytes: int, group: str = "tp") -> dict:
+    return {"ag.sym": {"dtype": "u8", "shape": [2, nranks, slot_bytes], "kind": "carry", "export": True},
+            "ag.sym_peers": {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": "ag.sym", "group": group},
+            "ag.flags": {"dtype": "u32", "shape": [nranks, AG_GRID], "kind": "carry", "export": True},
+            "ag.flags_peers": {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": "ag.flags", "group": group},
+            "ag.epochs": {"dtype": "u32", "shape": [AG_GRID], "kind": "carry"}}
+
+
 def tp_lamport_init_op(hidden: int, nranks: int) -> dict:
     """Poison the three Lamport stages (every 16-bit word 0x8000). Interface [lamport]."""
     n_words = 3 * nranks * TP_ONESHOT_ROWS * hidden // 2

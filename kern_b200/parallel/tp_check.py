@@ -80,6 +80,62 @@ def allreduce_manifest(hidden, world, rows_max, lamport=False):
                          "step_graph": {"batch": {"groups": 1, "rows": "tokens"}, "graph": True, "calls": [call]}}}
 
 
+def allgather_manifest(world, slot_bytes):
+    from ..models import common as C
+
+    bufs = {"x": {"dtype": "u8", "shape": [slot_bytes], "kind": "input"},
+            "y": {"dtype": "u8", "shape": [world, slot_bytes], "kind": "output"},
+            "error": {"dtype": "i32", "shape": [1], "kind": "output"}}
+    bufs.update(C.tp_allgather_buffers(world, slot_bytes))
+    B = lambda n: {"buf": n}
+    call = {"op": "allgather", "args": [B("x"), B("y"), B("ag.sym"), B("ag.sym_peers"), B("ag.flags"), B("ag.flags_peers"),
+                                        B("ag.epochs"), B("error"), {"var": "bytes"}]}
+    return {"schema_version": 7, "model": "tp-allgather-check", "vars": {"bytes": {"max": slot_bytes}},
+            "topology": {"groups": {"tp": world}}, "states": {}, "buffers": bufs,
+            "modules": C.modules_for(["tp_allreduce_norm"]), "ops": {"allgather": C.tp_allgather_op(world, slot_bytes)},
+            "programs": {"step": {"calls": [call]}, "burst16": {"calls": [call] * 16}}}
+
+
+def check_allgather(rank, world, local, sizes=(16, 4096, 1 << 20), time_it=False):
+    from ..runtime import Runtime
+    from . import group
+
+    slot = max(sizes)
+    rt = Runtime(allgather_manifest(world, slot), gpu=local, topology={"tp": (rank, world)})
+    group.start(rt)
+    out = []
+    for n in sizes:
+        for rep in range(3):                 # parities alternate; the third call reuses the first one's buffer
+            x = ((torch.arange(n, device="cuda") * 7 + rank * 31 + rep) % 251).to(torch.uint8)
+            rt.tensor("x")[:n] = x
+            torch.cuda.synchronize()
+            dist.barrier()
+            rt.run("step", {"bytes": n})
+            rt.check_error()
+            y = rt.tensor("y").view(-1)[: world * n].view(world, n)
+            want = torch.stack([((torch.arange(n, device="cuda") * 7 + r * 31 + rep) % 251).to(torch.uint8) for r in range(world)])
+            out.append({"bytes": n, "rep": rep, "ok": bool(torch.equal(y, want))})
+            dist.barrier()
+    times = []
+    if time_it:
+        stream = torch.cuda.ExternalStream(rt.stream)
+        for n in sizes:
+            for _ in range(3):
+                rt.run("burst16", {"bytes": n})
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record(stream)
+            for _ in range(20):
+                rt.issue("burst16", {"bytes": n})
+            b.record(stream)
+            rt.synchronize()
+            t = torch.tensor([a.elapsed_time(b) / 320 * 1e3], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times.append({"bytes_per_rank": n, "us_max_over_ranks": round(float(t), 2)})
+    return out, times
+
+
 def check_model(rank, world, fused=True):
     from ..engine import Engine
     from ..models import dense, dense_tp
@@ -168,6 +224,10 @@ def main(argv=None):
         if rank == 0:
             print(json.dumps({"check": "allreduce_time", "hidden": args.hidden, "world": world, "lamport": not args.no_lamport,
                               "results": t}))
+    ag, ag_t = check_allgather(rank, world, local, time_it=args.time)
+    ok &= all(r["ok"] for r in ag)
+    if rank == 0:
+        print(json.dumps({"check": "allgather", "world": world, "ok": all(r["ok"] for r in ag), "times": ag_t}))
     if not args.skip_model:
         m = check_model(rank, world, fused=not args.unfused)
         ok &= m["ok"]
