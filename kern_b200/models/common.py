@@ -93,21 +93,37 @@ def gemm_smem(bn: int) -> int:
 
 
 def gemm_ranges(n: int, var_max: int, tiles=(256, 128, 64), sms: int = SMS):
-    """`when` ranges of the row count: the widest N tile that still gives every SM a tile."""
-    # 256-wide tiles once they fill every SM; 128-wide from half the SMs on (a narrower tile feeds the
-    # tensor cores worse than a partly idle grid does); 64-wide below that, where the op is weight-bound
-    fill = {256: 1.0, 128: 0.5}
+    """`when` ranges of the row count -> N tile.
+
+    Up to two M tiles (256 rows) the op is bound by streaming the weights, and what matters is how evenly the tiles
+    cover the SMs: the tile width with the least `waves x width` (work of the slowest SM) wins, narrow tiles included.
+    Beyond that it is tensor-core bound: the widest tile that still gives every SM a tile (256 once they fill every SM,
+    128 from half the SMs on — a narrower tile feeds the tensor cores worse than a partly idle grid does)."""
+    def cost(bn, m_tiles):
+        t = m_tiles * -(-n // bn)
+        return -(-t // sms) * bn * (1 + 8 / bn)      # a narrow tile pays more per byte (fewer bytes in flight, more tile turns)
+
     out, hi = [], var_max
+    fill = {256: 1.0, 128: 0.5}
     for i, bn in enumerate(tiles):
         ncols = -(-n // bn)
-        need_m_tiles = -(-int(sms * fill.get(bn, 1.0)) // ncols)   # M tiles needed for that fill
+        need_m_tiles = -(-int(sms * fill.get(bn, 1.0)) // ncols)
         lo = 1 if i == len(tiles) - 1 else (need_m_tiles - 1) * BM + 1
-        lo = max(1, lo)
+        lo = max(2 * BM + 1, lo)
         if lo <= hi:
             out.append((bn, lo, hi))
             hi = lo - 1
-        if hi < 1:
+        if hi <= 2 * BM:
             break
+    for m_tiles in (2, 1):
+        lo, top = (m_tiles - 1) * BM + 1, min(m_tiles * BM, var_max)
+        if lo > top:
+            continue
+        best = min(tiles, key=lambda bn: (cost(bn, m_tiles), -bn))
+        if out and out[-1][0] == best and out[-1][1] == top + 1:
+            out[-1] = (best, lo, out[-1][2])
+        else:
+            out.append((best, lo, top))
     return out
 
 
@@ -145,7 +161,8 @@ def gemm_op(n: int, k: int, *, epilogue: str = "store", rows_var: str = "tokens"
         if len(when) > 1:
             launch["when"] = when
         launches.append(launch)
-    for bn, lo, hi in gemm_ranges(n, rows_max):
+    tiles = (256, 128, 64, 32) if epilogue in ("store", "acc") else (256, 128, 64)
+    for bn, lo, hi in gemm_ranges(n, rows_max, tiles):
         lo = max(lo, GEMV_ROWS + 1)
         if lo > hi:
             continue
