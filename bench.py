@@ -70,8 +70,9 @@ def main():
                     help="N > 1: data-parallel replicas, the concurrency split between them (default: the higher "
                          "tok/s per box for a model that fits one GPU), or tensor parallel over one replicated batch "
                          "(lower latency per token)")
-    ap.add_argument("--tp-fused", action="store_true",
-                    help="tensor parallel with the GEMM + reduce-scatter fusion (epilogue pushes partial rows over NVLink)")
+    ap.add_argument("--tp-unfused", action="store_true",
+                    help="tensor parallel without the GEMM + reduce-scatter fusion (the all-reduce kernel pushes the partials "
+                         "instead of the GEMM epilogue; A/B)")
     ap.add_argument("--profile", action="store_true", help="after the timed region, run one more step with per-call timing and print the cost by op to stderr")
     args = ap.parse_args()
 
@@ -108,7 +109,7 @@ def main():
         from kern_b200.models import dense_tp
         from kern_b200.parallel import group
 
-        doc = dense_tp.build_manifest_tp(cfg, fused=args.tp_fused)
+        doc = dense_tp.build_manifest_tp(cfg, fused=not args.tp_unfused)
         rt = Runtime(doc, gpu=local, memory_fraction=0.90, topology=group.topology(doc["topology"]["groups"], rank, world))
         dense.load_random_weights(rt, cfg, seed=args.seed)
         group.start(rt)
