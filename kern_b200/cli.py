@@ -251,11 +251,59 @@ def cmd_bench(args) -> int:
     wall time per call; graph programs replay their captured graph); min / p10 / p50 / p90 / max / cv."""
     from .engine import Engine
 
-    rt = make_runtime(args)
-    eng = Engine(rt)
     wl = load_workload(args.workload)
+    if getattr(args, "candidate", None):
+        return bench_candidate(args, wl)
+    rt = make_runtime(args)
+    report = bench_points(rt, wl, by_op=getattr(args, "by_op", False))
+    if args.out:
+        Path(args.out).write_text(json.dumps(report, indent=1))
+    return 0
+
+
+def bench_candidate(args, wl) -> int:
+    """`--candidate FILE`: the candidate's ops are spliced over the manifest's (same interfaces), both are held to the
+    same answers (the A/B test's verdict must be PASS), both are priced on the workload, and every sweep point says
+    which implementation it would pick (the faster one when the gap exceeds both sides' spread)."""
+    from . import _native
+    from .testing.abtest import EngineSide, run_test
+
+    base_text = Path(args.manifest).read_text()
+    m, errs = _native.verify(base_text)
+    if m is None:
+        print("\n".join(errs))
+        return 1
+    try:
+        spliced = m.splice(Path(args.candidate).read_text())
+    except ValueError as e:
+        print(e)
+        return 1
+    cand_text = spliced.to_json()
+    a, b = make_runtime(args, base_text), make_runtime(args, cand_text)
+    verdict = run_test(EngineSide(a), EngineSide(b), seed=wl["seed"], prompts=2, decode_steps=4, logit_kl=0.01, chunk=args.chunk or 256)
+    print(f"held to outputs: {verdict.verdict}")
+    if verdict.exit_code == 1:
+        print(verdict.text())
+        return 1
+    ra, rb = bench_points(a, wl, quiet=True), bench_points(b, wl, quiet=True)
+    picks = []
+    for pa, pb in zip(ra["points"], rb["points"]):
+        gap = pa["p50_ms"] - pb["p50_ms"]
+        noise = max(pa["p90_ms"] - pa["p10_ms"], pb["p90_ms"] - pb["p10_ms"])
+        pick = "candidate" if gap > noise else ("base" if -gap > noise else "either")
+        picks.append({"groups": pa["groups"], "rows": pa["rows"], "context": pa["context"], "base_ms": pa["p50_ms"],
+                      "candidate_ms": pb["p50_ms"], "pick": pick})
+        print(json.dumps(picks[-1]))
+    if args.out:
+        Path(args.out).write_text(json.dumps({"version": 5, "held": verdict.verdict, "picks": picks}, indent=1))
+    return 0
+
+
+def bench_points(rt, wl, by_op: bool = False, quiet: bool = False) -> dict:
+    from .engine import Engine
     import numpy as np
 
+    eng = Engine(rt)
     rng = np.random.default_rng(wl["seed"])
     report = {"version": 5, "points": []}
     for pt in wl["sweep"]:
@@ -287,11 +335,26 @@ def cmd_bench(args) -> int:
         q = lambda f: times[min(len(times) - 1, int(f * len(times)))]
         point = {"groups": g, "rows": rows, "context": ctx, "weight": pt.get("weight", 1.0), "min_ms": times[0], "p10_ms": q(0.1),
                  "p50_ms": q(0.5), "p90_ms": q(0.9), "max_ms": times[-1], "cv": statistics.pstdev(times) / max(1e-9, statistics.mean(times))}
+        if by_op and hasattr(rt, "issue_timed"):
+            # one more call of the same shape, eagerly, with an event between calls: the cost by op
+            seqs2 = [eng.open(ctx) for _ in range(g)]
+            if ctx > rows:
+                pre = ctx - rows
+                for i in range(0, pre, eng.rows_max // max(1, g)):
+                    n = min(eng.rows_max // max(1, g), pre - i)
+                    eng.step([(s, rng.integers(1, 200, n).tolist()) for s in seqs2])
+            eng.step([(s, rng.integers(1, 200, rows).tolist()) for s in seqs2], timed=True)
+            cost: dict[str, float] = {}
+            for label, op, ms, _n in eng.last_times:
+                cost[op] = cost.get(op, 0.0) + ms
+            total = sum(cost.values()) or 1.0
+            point["by_op"] = {op: round(ms / total, 4) for op, ms in sorted(cost.items(), key=lambda kv: -kv[1])}
+            for s in seqs2:
+                eng.close(s)
         report["points"].append(point)
-        print(json.dumps(point))
-    if args.out:
-        Path(args.out).write_text(json.dumps(report, indent=1))
-    return 0
+        if not quiet:
+            print(json.dumps(point))
+    return report
 
 
 def cmd_workload(args) -> int:
@@ -359,6 +422,8 @@ def main(argv=None) -> int:
     e.add_argument("--seed", type=int, default=0); e.add_argument("--prompts", type=int, default=8)
     e.add_argument("--decode-steps", type=int, default=16); e.add_argument("--logit-kl", type=float, default=0.01)
     b = sub.add_parser("bench"); common(b); b.add_argument("--workload"); b.add_argument("--out")
+    b.add_argument("--by-op", action="store_true", help="add each point's cost by op (one eager call with an event between calls)")
+    b.add_argument("--candidate", help="a candidate (modules + ops) to splice over the manifest and price against it")
     w = sub.add_parser("workload"); w.add_argument("steps"); w.add_argument("--out", required=True); w.add_argument("--samples", type=int, default=32)
     s = sub.add_parser("server"); common(s)
     s.add_argument("--host", default="127.0.0.1"); s.add_argument("--port", type=int, default=8000); s.add_argument("--rows", type=int)

@@ -72,3 +72,28 @@ def test_bench_and_kernels(pkg, capsys):
     assert len(pts) == 2 and all(p["p50_ms"] > 0 and p["min_ms"] <= p["p50_ms"] <= p["max_ms"] for p in pts)
     assert cli.main(["kernels"]) == 0
     assert "gemm_bf16.cubin" in capsys.readouterr().out
+
+
+def test_bench_candidate_splices_and_picks(tmp_path, capsys):
+    """`kern bench --candidate`: an op implementation from another manifest is spliced in, held to the same answers, priced."""
+    import json
+
+    from kern_b200.cli import main
+    from kern_b200.models import common, dense
+
+    cfg = dense.TOY
+    doc = dense.build_manifest(cfg)
+    mpath, wpath = tmp_path / "m.json", tmp_path / "w.safetensors"
+    mpath.write_text(json.dumps(doc))
+    common.write_safetensors(wpath, dense.random_weights(cfg, seed=1, std=0.08))
+    # the candidate: the same norm op (another implementation would go here), interface unchanged
+    cand = {"modules": {"norm_embed": doc["modules"]["norm_embed"]}, "ops": {"norm": doc["ops"]["norm"]}}
+    cpath = tmp_path / "cand.json"
+    cpath.write_text(json.dumps(cand))
+    out = tmp_path / "picks.json"
+    assert main(["bench", "--cpu", "--manifest", str(mpath), "--weights", str(wpath), "--candidate", str(cpath), "--out", str(out)]) == 0
+    got = json.loads(out.read_text())
+    assert got["held"] == "PASS" and len(got["picks"]) == 2 and all(p["pick"] in ("base", "candidate", "either") for p in got["picks"])
+    bad = dict(cand, ops={"norm": {**doc["ops"]["norm"], "params": doc["ops"]["norm"]["params"][:2]}})
+    cpath.write_text(json.dumps(bad))
+    assert main(["bench", "--cpu", "--manifest", str(mpath), "--weights", str(wpath), "--candidate", str(cpath)]) == 1
