@@ -94,8 +94,10 @@ extern "C" __global__ void __launch_bounds__(128)
 //   rows_out[0]        total permuted rows
 extern "C" __global__ void __launch_bounds__(1024)
     kern_moe_plan(const int* topk_ids, int* perm, int* offsets, int* tiles, int* tile_count, int* rows_out, int entries,
-                  int e_lo, int e_hi, int bm, int max_tiles, int* err) {
+                  int e_lo, int e_hi, int bm, int max_tiles, int* err, int rank, int per_rank) {
   pdl_wait();
+  e_lo += rank * per_rank;      // expert parallel: rank r keeps experts [e_lo + r * per_rank, e_hi + r * per_rank)
+  e_hi += rank * per_rank;
   extern __shared__ int sm[];          // counts[E_local] | cursor[E_local]
   const int el = e_hi - e_lo;
   int* counts = sm;

@@ -79,7 +79,9 @@ def load_random_weights(rt, cfg: MoeConfig, seed: int = 0, std: float = 0.02) ->
     rt.load_tensors(provider)
 
 
-def _moe_ops(cfg: MoeConfig, e_lo: int, e_n: int) -> dict:
+def _moe_ops(cfg: MoeConfig, e_lo: int, e_n: int, ep_group: str | None = None, accumulate: bool = True) -> dict:
+    """`ep_group`: the rank of that group shifts the expert range by e_n per rank (expert parallel). `accumulate`: the
+    combine adds into its output (a residual) instead of overwriting it (a partial sum for an all-reduce)."""
     h, I, E, k, T = cfg.hidden, cfg.moe_intermediate, cfg.experts, cfg.top_k, cfg.max_tokens
     max_tiles = T * k // C.BM + e_n
     L = lambda module, entry, block, grid, lp, args, **kw: {"module": module, "entry": entry, "block": block, "grid": grid,
@@ -96,9 +98,10 @@ def _moe_ops(cfg: MoeConfig, e_lo: int, e_n: int) -> dict:
                                   "out buffer<i32>", "i32", "out buffer<i32>"], "impl": {"launches": [L(
         "moe", "kern_moe_plan", [1024, 1, 1], [1, 1, 1],
         ["in buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "i32",
-         "i32", "i32", "i32", "i32", "out buffer<i32>"],
+         "i32", "i32", "i32", "i32", "out buffer<i32>", "i32", "i32"],
         [{"param": 0}, {"param": 1}, {"param": 2}, {"param": 3}, {"param": 4}, {"param": 5}, {"param": 6}, {"i32": e_lo},
-         {"i32": e_lo + e_n}, {"i32": C.BM}, {"i32": max_tiles}, {"param": 7}], shared_mem=2 * e_n * 4)]}}
+         {"i32": e_lo + e_n}, {"i32": C.BM}, {"i32": max_tiles}, {"param": 7},
+         {"rank": ep_group} if ep_group else {"i32": 0}, {"i32": e_n if ep_group else 0}], shared_mem=2 * e_n * 4)]}}
     ops["moe_gather"] = {"params": ["in buffer<bf16>", "in buffer<i32>", "out buffer<bf16>", "i32"], "impl": {"launches": [L(
         "moe", "kern_moe_gather_bf16", [128, 1, 1], [{"mul": ["tokens", k]}, 1, 1],
         ["in buffer<bf16>", "in buffer<i32>", "out buffer<bf16>", "i32", "i32", "i32"],
@@ -122,10 +125,13 @@ def _moe_ops(cfg: MoeConfig, e_lo: int, e_n: int) -> dict:
 
     ops["moe_fc1"] = routed(2 * I, h, "swiglu")
     ops["moe_fc2"] = routed(h, I, "store")
-    ops["moe_combine"] = {"params": ["in buffer<bf16>", "in buffer<i32>", "in buffer<f32>", "inout buffer<bf16>"], "impl": {"launches": [L(
+    ops["moe_combine"] = {"params": ["in buffer<bf16>", "in buffer<i32>", "in buffer<f32>",
+                                     ("inout" if accumulate else "out") + " buffer<bf16>"], "impl": {"launches": [L(
         "moe", "kern_moe_combine_bf16", [128, 1, 1], ["tokens", 1, 1],
-        ["in buffer<bf16>", "in buffer<i32>", "in buffer<f32>", "i64", "inout buffer<bf16>", "i32", "i32", "i32", "i32"],
-        [{"param": 0}, {"param": 1}, {"param": 2}, {"i64": 0}, {"param": 3}, {"i32": C.I32_MAX}, {"i32": k}, {"i32": h}, {"i32": 1}])]}}
+        ["in buffer<bf16>", "in buffer<i32>", "in buffer<f32>", "i64", ("inout" if accumulate else "out") + " buffer<bf16>",
+         "i32", "i32", "i32", "i32"],
+        [{"param": 0}, {"param": 1}, {"param": 2}, {"i64": 0}, {"param": 3}, {"i32": C.I32_MAX}, {"i32": k}, {"i32": h},
+         {"i32": int(accumulate)}])]}}
     return ops
 
 
@@ -225,7 +231,8 @@ def _register_cpu() -> None:
         ids[: t * k] = i.reshape(-1)
         wts[: t * k] = w.reshape(-1).float()
 
-    def plan(g, ids, perm, offsets, tiles, tile_count, rows_out, entries, e_lo, e_hi, bm, max_tiles, err):
+    def plan(g, ids, perm, offsets, tiles, tile_count, rows_out, entries, e_lo, e_hi, bm, max_tiles, err, rank, per_rank):
+        e_lo, e_hi = e_lo + rank * per_rank, e_hi + rank * per_rank
         flat = ids[:entries]
         at, nt = 0, 0
         tl = tiles.view(-1, 4)

@@ -52,7 +52,7 @@ def plan(ids: torch.Tensor, experts_local: int, e_lo: int = 0):
            "rows": torch.zeros(1, dtype=torch.int32, device=dev), "max_tiles": mt}
     kn.launch("moe", "kern_moe_plan", (1,), (1024,),
               [ptr(ids), ptr(out["perm"]), ptr(out["offsets"]), ptr(out["tiles"]), ptr(out["tile_count"]), ptr(out["rows"]),
-               i32(entries), i32(e_lo), i32(e_lo + experts_local), i32(BM), i32(mt), ptr(kn.err_word())],
+               i32(entries), i32(e_lo), i32(e_lo + experts_local), i32(BM), i32(mt), ptr(kn.err_word()), i32(0), i32(0)],
               shared_mem=2 * experts_local * 4)
     return out
 

@@ -174,6 +174,45 @@ def check_model(rank, world, fused=True):
     return {"model_max_logit_diff": round(worst, 4), "ok": worst < 0.12, "graphs": rt.graphs}
 
 
+def check_moe(rank, world):
+    """Expert-parallel MoE decoder (attention by heads, experts by ranges) against the one-GPU fp32 oracle."""
+    import dataclasses
+
+    from ..engine import Engine
+    from ..models import moe, moe_ep
+    from ..runtime import Runtime
+    from . import group
+
+    cfg = dataclasses.replace(moe.TINY_MOE, name="tiny-moe-ep", heads=8, kv_heads=max(2, world), experts=16, top_k=4, tp=world)
+    weights = moe.random_weights(cfg, seed=0, std=0.05)
+    doc = moe_ep.build_manifest_ep(cfg)
+    rt = Runtime(doc, gpu=torch.cuda.current_device(), topology=group.topology(doc["topology"]["groups"], rank, world),
+                 tokens=cfg.page_size * 64)
+    rt.load_tensors(lambda name: weights[name].cuda())
+    group.start(rt)
+    eng = Engine(rt)
+    oracle = moe.MoeOracle(cfg, weights, device="cuda")
+    torch.manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (37, 5, 80)]
+    seqs = [eng.open(120) for _ in prompts]
+    caches = [oracle.new_cache() for _ in prompts]
+    first = eng.step(list(zip(seqs, prompts)))
+    diffs = []
+    logits = rt.tensor("logits")[:3].float()
+    for i, (p, c) in enumerate(zip(prompts, caches)):
+        diffs.append((logits[i] - oracle.forward(p, c)[-1]).abs())
+    toks = [f[0] for f in first]
+    for _ in range(4):
+        refs = [oracle.forward([t], c)[-1] for t, c in zip(toks, caches)]
+        nxt = eng.step([(s, [t]) for s, t in zip(seqs, toks)])
+        logits = rt.tensor("logits")[:3].float()
+        diffs += [(logits[i] - refs[i]).abs() for i in range(3)]
+        toks = [n[0] for n in nxt]
+    rt.check_error()
+    worst, mean = max(float(d.max()) for d in diffs), max(float(d.mean()) for d in diffs)
+    return {"moe_max_logit_diff": round(worst, 4), "moe_mean_logit_diff": round(mean, 4), "ok": worst < 0.3 and mean < 0.05}
+
+
 def time_allreduce(rt, world, rows_list, iters=20):
     out = []
     stream = torch.cuda.ExternalStream(rt.stream)
@@ -201,6 +240,7 @@ def main(argv=None):
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--skip-model", action="store_true")
     ap.add_argument("--no-lamport", action="store_true", help="decode-sized all-reduce through flags instead of the flagless one-shot")
+    ap.add_argument("--moe", action="store_true", help="also check the expert-parallel MoE decoder")
     ap.add_argument("--unfused", action="store_true", help="the model check without the GEMM + reduce-scatter fusion")
     args = ap.parse_args(argv)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -233,6 +273,11 @@ def main(argv=None):
         ok &= m["ok"]
         if rank == 0:
             print(json.dumps({"check": "tp_model", "world": world, "fused_gemm_reduce_scatter": not args.unfused, **m}))
+    if args.moe:
+        e = check_moe(rank, world)
+        ok &= e["ok"]
+        if rank == 0:
+            print(json.dumps({"check": "ep_moe_model", "world": world, **e}))
     flag = torch.tensor([int(ok)], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()
