@@ -523,6 +523,12 @@ class CpuRuntime:
                         vals.append(next(iter(la.values())))
                 entry = l["entry"]
                 fn = CPU_KERNELS.get(entry)
+                if fn is None:          # model families register their kernels' statements when imported
+                    import importlib
+
+                    for mod in ("toy_int", "spec", "moe"):
+                        importlib.import_module(f"kern_b200.models.{mod}")
+                    fn = CPU_KERNELS.get(entry)
                 if fn is None:
                     raise NotImplementedError(f"no CPU statement of `{entry}` is registered")
                 grid = [_eval(g, vars) for g in l.get("grid", [1, 1, 1])]

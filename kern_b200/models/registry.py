@@ -17,6 +17,11 @@ def families() -> dict:
         out[cfg.name] = (cfg, hybrid.build_manifest, hybrid.load_random_weights, hybrid.random_weights)
     for cfg in (moe.TOY_MOE, moe.TINY_MOE, moe.MOE_30B):
         out[cfg.name] = (cfg, moe.build_manifest, moe.load_random_weights, moe.random_weights)
+    from . import toy_int
+
+    for lined in (False, True):
+        name = "toy-int-stateful" if lined else "toy-int"
+        out[name] = (lined, lambda lined: toy_int.build_manifest(lined), lambda rt, cfg: None, lambda cfg: None)
     return out
 
 
@@ -27,4 +32,6 @@ def resolve(name: str, **overrides):
         raise KeyError(f"unknown model `{name}`; known: {', '.join(sorted(fam))}")
     cfg, build, load, make = fam[name]
     overrides = {k: v for k, v in overrides.items() if v is not None}
+    if not dataclasses.is_dataclass(cfg):
+        return cfg, build, load, make          # a family without a config object (the integer model)
     return dataclasses.replace(cfg, **overrides), build, load, make

@@ -72,5 +72,21 @@ class DpTier:
 
     def metrics(self) -> dict:
         ms = [s.metrics() for s in self.scheds]
-        return {"replicas": ms, "num_running_reqs": sum(m["num_running_reqs"] for m in ms),
-                "num_waiting_reqs": sum(m["num_waiting_reqs"] for m in ms)}
+        tot = lambda k: sum(m[k] for m in ms)
+        return {"replicas": ms, "num_running_reqs": tot("num_running_reqs"), "num_waiting_reqs": tot("num_waiting_reqs"),
+                "kv_used_blocks": tot("kv_used_blocks"), "kv_total_blocks": tot("kv_total_blocks"),
+                "spec_decode": {k: sum(m["spec_decode"][k] for m in ms) for k in ("accepted", "proposed")},
+                "prefix_cache": {k: sum(m["prefix_cache"][k] for m in ms) for k in ("queries", "hits", "hit_tokens", "entries")}}
+
+    @property
+    def stats(self):
+        """The replicas' counters summed (what the metrics endpoint reports for the tier)."""
+        import dataclasses
+
+        from .scheduler import Stats
+
+        out = Stats()
+        for s in self.scheds:
+            for f in dataclasses.fields(Stats):
+                setattr(out, f.name, getattr(out, f.name) + getattr(s.stats, f.name))
+        return out

@@ -1,0 +1,33 @@
+"""Rank *processes* (spawned, host-memory runtimes) behind the head: a data-parallel tier of the exact integer model
+answers exactly; a rank process that is killed ends the serving loop's connection (fail fast is observable)."""
+import random
+
+import pytest
+
+from kern_b200.models import toy_int
+from kern_b200.serve import launch
+from kern_b200.serve.scheduler import Request
+
+
+@pytest.mark.timeout(120)
+def test_two_rank_processes_serve_exactly():
+    spec = {"manifest": toy_int.build_manifest(False), "cpu": True, "tokens": 16 * 30}
+    sched, ex, procs = launch.launch(spec, world=2, tp=1, chunk=32, max_seqs=2, timeout=60)
+    ex.watch.on_lost = lambda who: None          # the test ends the ranks itself
+    try:
+        rng = random.Random(2)
+        reqs = [Request(id=f"r{i}", prompt=[rng.randrange(256) for _ in range(rng.randint(3, 50))], max_tokens=5,
+                        stop_ids=(toy_int.EOS,)) for i in range(6)]
+        spots = [sched.submit(r) for r in reqs]
+        assert set(spots) == {0, 1}
+        for _ in range(400):
+            if sched.idle():
+                break
+            sched.step()
+        assert sched.idle()
+        for r in reqs:
+            assert [t for t in r.out if t != toy_int.EOS] == toy_int.generate(r.prompt, 5)
+        assert sched.stats.decode_tokens > 0 and sched.metrics()["kv_total_blocks"] == 2 * 30
+    finally:
+        launch.shutdown(ex, procs)
+    assert all(not p.is_alive() for p in procs)
