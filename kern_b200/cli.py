@@ -384,9 +384,36 @@ def cmd_server(args) -> int:
     from .utils.logline import setup_logging
 
     setup_logging()
+    tok = HFTokenizer(args.tokenizer) if args.tokenizer else ByteTokenizer()
+    if args.world > 1:
+        # rank processes (one per GPU) behind this head: one tensor-parallel group, or a data-parallel tier of them
+        from .serve import launch
+
+        if args.model:
+            from .models import registry
+
+            cfg, build, _load, make = registry.resolve(args.model)
+            if args.tp > 1:
+                import dataclasses
+
+                from .models import dense_tp
+
+                doc = dense_tp.build_manifest_tp(dataclasses.replace(cfg, tp=args.tp))
+            else:
+                doc = build(cfg)
+        else:
+            doc = json.loads(Path(args.manifest).read_text())
+        spec = {"manifest": doc, "weights": args.weights, "model": args.model, "cpu": args.cpu, "tokens": args.capacity or 0,
+                "slots": args.max_seqs or 0}
+        sched, ex, procs = launch.launch(spec, world=args.world, tp=args.tp, chunk=args.chunk, max_seqs=args.max_seqs or None)
+        srv = Server(sched, tok, model_name=doc["model"], host=args.host, port=args.port)
+        try:
+            srv.serve_forever()
+        finally:
+            launch.shutdown(ex, procs)
+        return 0
     rt = make_runtime(args)
     sched = Scheduler(Engine(rt), chunk=args.chunk, max_seqs=args.max_seqs or None, rows=args.rows)
-    tok = HFTokenizer(args.tokenizer) if args.tokenizer else ByteTokenizer()
     srv = Server(sched, tok, model_name=rt.doc["model"], host=args.host, port=args.port)
     logging.getLogger("kern.serve").info("listening host=%s port=%d model=%s", args.host, srv.port, rt.doc["model"])
     srv.serve_forever()
@@ -427,6 +454,8 @@ def main(argv=None) -> int:
     w = sub.add_parser("workload"); w.add_argument("steps"); w.add_argument("--out", required=True); w.add_argument("--samples", type=int, default=32)
     s = sub.add_parser("server"); common(s)
     s.add_argument("--host", default="127.0.0.1"); s.add_argument("--port", type=int, default=8000); s.add_argument("--rows", type=int)
+    s.add_argument("--world", type=int, default=1, help="rank processes (one per GPU)")
+    s.add_argument("--tp", type=int, default=1, help="ranks per tensor-parallel group; world / tp groups form a data-parallel tier")
     args = ap.parse_args(argv)
     if args.cmd in ("run", "test", "bench", "server", "e2e-logits"):
         path, cfg = find_config()
