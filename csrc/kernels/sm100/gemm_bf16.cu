@@ -27,12 +27,18 @@ namespace kern {
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 
-template <int BN>
+// MT2: the CTA's tile is 256 rows tall (two 128-row MMAs per K step sharing one B tile). Per FLOP the stage carries a
+// third less data from L2 (A 32 KB + B 32 KB per 256x256x64 against 16 + 32 per 128x256x64), which is what bounds the
+// 128-row tile at large sizes. The two accumulators fill all 512 TMEM columns, so the epilogue is not overlapped with
+// the next tile's MMAs (its loads still are).
+template <int BN, bool MT2 = false>
 struct GemmCfg {
-  static constexpr int kStageBytesA = BM * BK * 2;
+  static constexpr int kRows = MT2 ? 2 * BM : BM;
+  static constexpr int kStageBytesA = kRows * BK * 2;
   static constexpr int kStageBytesB = BN * BK * 2;
   static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kStages = MT2 ? 3 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  static constexpr int kAccs = MT2 ? 1 : 2;              // accumulator sets in TMEM
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   // 1024 B of slack for alignment + stages + barriers
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 256;
@@ -52,15 +58,17 @@ struct ScatterArgs {
 // A tile's load may run into the next expert's rows; the epilogue stores only the tile's own rows.
 // FP8: A and B hold e4m3 bytes (a swizzle row is 128 elements, the instruction is kind::f8f6f4 with K = 32), the
 // accumulator is scaled by *scale_a * *scale_b (per-tensor scales) before the epilogue's conversion.
-template <int BN, int EPI, bool GROUPED = false, bool FP8 = false>
+template <int BN, int EPI, bool GROUPED = false, bool FP8 = false, bool MT2 = false>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
                                           void* Cv, const void* Rv,
                                           int M, int N, int K, int ldc, int* err,
                                           const int* tile_table = nullptr, const int* tile_count = nullptr,
                                           ScatterArgs sc = ScatterArgs(), const float* scale_a = nullptr,
                                           const float* scale_b = nullptr) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, MT2>;
   constexpr int kStages = Cfg::kStages;
+  constexpr int BMT = Cfg::kRows;
+  static_assert(!(MT2 && (GROUPED || EPI == 4 || BN != 256)), "the 256-row tile exists for the plain 256-wide GEMM");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -103,7 +111,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
     tma_prefetch_desc(tma_b);
   }
   pdl_wait();  // everything above touched only this CTA's own state and the descriptors
-  const int num_m = GROUPED ? *tile_count : (M + BM - 1) / BM;
+  const int num_m = GROUPED ? *tile_count : (M + BMT - 1) / BMT;
   const int num_tiles = num_m * num_n;
   // tile t -> (first row, row bound, n block, expert)
   auto tile_of = [&](int t, int& row0, int& row_end, int& n_blk, int& expert) {
@@ -113,7 +121,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
       const int4 e = reinterpret_cast<const int4*>(tile_table)[mt];
       expert = e.x; row0 = e.y; row_end = min(M, e.y + e.z);
     } else {
-      expert = 0; row0 = mt * BM; row_end = M;
+      expert = 0; row0 = mt * BMT; row_end = M;
     }
   };
 
@@ -187,13 +195,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
               umma_f8f6f4(d_tmem, umma_desc_sw128(sa + k * 32), umma_desc_sw128(sb + k * 32), idesc, (kb | k) != 0);
             else
               umma_bf16(d_tmem, umma_desc_sw128(sa + k * 32), umma_desc_sw128(sb + k * 32), idesc, (kb | k) != 0);
+            if constexpr (MT2)      // rows 128..255 of the tile: the A sub-tile 16 KB further on, the next BN TMEM columns
+              umma_bf16(d_tmem + BN, umma_desc_sw128(sa + BM * BK * 2 + k * 32), umma_desc_sw128(sb + k * 32), idesc,
+                        (kb | k) != 0);
           }
           tc_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         tc_commit(&tfull_bar[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        if (++acc == Cfg::kAccs) { acc = 0; acc_phase ^= 1; }
       }
     }
     __syncwarp();
@@ -212,8 +223,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         break;
       }
       tc_fence_after();
-      const int row = row0 + quarter * 32 + lane;
-      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int hh = 0; hh < (MT2 ? 2 : 1); ++hh) {     // the 256-row tile drains its two 128-row accumulators in turn
+      const int row = row0 + hh * BM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (MT2 ? hh : acc) * BN;
       if constexpr (EPI == 3) {
         // SwiGLU: accumulator columns [0, BN/2) are gate, [BN/2, BN) the matching up columns
 #pragma unroll 1
@@ -345,10 +358,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         }
       }
       }
+      }   // hh
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (++acc == Cfg::kAccs) { acc = 0; acc_phase ^= 1; }
     }
   }
 
@@ -379,6 +393,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
     kern::gemm_body<BN, EPI>(&tma_a, &tma_b, C, R, M, N, K, ldc, err);                        \
   }
 
+#define KERN_GEMM_ENTRY_M256(name, EPI)                                                       \
+  extern "C" __global__ void __launch_bounds__(192, 1)                                        \
+      name(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, \
+           void* C, const void* R, int M, int N, int K, int ldc, int* err) {                  \
+    kern::gemm_body<256, EPI, false, false, true>(&tma_a, &tma_b, C, R, M, N, K, ldc, err);   \
+  }
+
+KERN_GEMM_ENTRY_M256(kern_gemm_bf16_tn_m256_n256, 0)
+KERN_GEMM_ENTRY_M256(kern_gemm_bf16_tn_acc_m256_n256, 2)
+KERN_GEMM_ENTRY_M256(kern_gemm_bf16_tn_swiglu_m256_n256, 3)
 KERN_GEMM_ENTRY(kern_gemm_bf16_tn_n256, 256, 0)
 KERN_GEMM_ENTRY(kern_gemm_bf16_tn_n128, 128, 0)
 KERN_GEMM_ENTRY(kern_gemm_bf16_tn_n64, 64, 0)

@@ -77,10 +77,10 @@ def bench_gemm(a):
     w = (torch.randn(a.n, a.k, device="cuda") * 0.1).to(torch.bfloat16)
     cols = a.n // 2 if a.epilogue == "swiglu" else a.n
     out = torch.zeros(a.m, cols, device="cuda", dtype=torch.float32 if a.epilogue == "f32" else torch.bfloat16)
-    ms = timeit(lambda: gemm(x, w, out=out, epilogue=a.epilogue, bn=a.bn), a.iters)
+    ms = timeit(lambda: gemm(x, w, out=out, epilogue=a.epilogue, bn=a.bn, bm=a.bm), a.iters)
     Kernels.get().check_error()
     nbytes = 2 * (a.m * a.k + a.n * a.k) + out.numel() * out.element_size()
-    report("gemm_bf16_tn", ms, flops=2.0 * a.m * a.n * a.k, nbytes=nbytes, m=a.m, n=a.n, k=a.k, epilogue=a.epilogue, bn=a.bn)
+    report("gemm_bf16_tn", ms, flops=2.0 * a.m * a.n * a.k, nbytes=nbytes, m=a.m, n=a.n, k=a.k, epilogue=a.epilogue, bn=a.bn, bm=a.bm)
     if a.compare:
         y = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
         ms2 = timeit(lambda: torch.matmul(x, w.t(), out=y), a.iters)
@@ -116,6 +116,38 @@ def bench_moe(a):
     touched = min(a.experts, a.tokens * a.top_k)
     report("moe_layer_bf16", ms, flops=flops, nbytes=touched * 3 * a.hidden * a.inter * 2.0, tokens=a.tokens, experts=a.experts,
            top_k=a.top_k, hidden=a.hidden, inter=a.inter)
+
+
+def bench_gdn(a):
+    """Gated DeltaNet decode step (conv + rule + gated norm) for `seqs` sequences, or a prefill chunk of `rows` rows of one."""
+    from . import gdn as G
+    from .launcher import Kernels
+
+    hk, hv, d, width = a.hk, a.hv, a.d, 4
+    conv_dim = 2 * hk * d + hv * d
+    x_stride = conv_dim + hv * d + 2 * hv
+    lb, s_off = G.line_bytes(hk, hv, d, d, width)
+    seqs, rows = (a.seqs, a.seqs) if a.rows == 1 else (1, a.rows)
+    state = torch.zeros(seqs + 1, lb, dtype=torch.uint8, device="cuda")
+    lines = torch.arange(1, seqs + 1, dtype=torch.int32, device="cuda")
+    cu = None if a.rows == 1 else torch.tensor([0, rows], dtype=torch.int32, device="cuda")
+    x = torch.randn(rows, x_stride, device="cuda").to(torch.bfloat16)
+    y = torch.empty(rows, conv_dim, dtype=torch.bfloat16, device="cuda")
+    out = torch.empty(rows, hv * d, dtype=torch.bfloat16, device="cuda")
+    w = (torch.randn(conv_dim, width, device="cuda") * 0.3).to(torch.bfloat16)
+    A_log, dtb = torch.zeros(hv, device="cuda"), torch.zeros(hv, device="cuda")
+    nw = torch.ones(d, device="cuda").to(torch.bfloat16)
+    o_raw = torch.empty(rows, hv * d, dtype=torch.float32, device="cuda")
+
+    def step():
+        G.conv(x, y, state, lines, cu, w, None, seqs, conv_dim, width, lb)
+        G.rule(y, x[:, conv_dim:], out, state, lines, cu, A_log, dtb, nw, seqs, hk, hv, d, d, 0, hv * d, hv * d + hv, lb, s_off,
+               o_raw=o_raw)
+
+    ms = timeit(step, a.iters)
+    Kernels.get().check_error()
+    nbytes = 2.0 * seqs * hv * d * d * 4 if a.rows == 1 else 0.0      # the recurrent state is read and written once per step
+    report("gdn_step" if a.rows == 1 else "gdn_prefill_chunk", ms, nbytes=nbytes, seqs=seqs, rows=rows, hk=hk, hv=hv, d=d)
 
 
 def _cache(seqs, ctx, hk, d, page):
@@ -173,12 +205,16 @@ def main(argv=None):
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=4096); g.add_argument("--n", type=int, default=4096); g.add_argument("--k", type=int, default=4096)
     g.add_argument("--epilogue", default="store"); g.add_argument("--bn", type=int, default=None); g.add_argument("--compare", action="store_true")
+    g.add_argument("--bm", type=int, default=None, help="128 or 256 rows per tile (default: chosen by shape)")
     g8 = sub.add_parser("gemm_fp8")
     g8.add_argument("--m", type=int, default=4096); g8.add_argument("--n", type=int, default=4096); g8.add_argument("--k", type=int, default=4096)
     g8.add_argument("--bn", type=int, default=None)
     mo = sub.add_parser("moe")
     mo.add_argument("--tokens", type=int, default=2048); mo.add_argument("--experts", type=int, default=128); mo.add_argument("--top-k", type=int, default=8)
     mo.add_argument("--hidden", type=int, default=2048); mo.add_argument("--inter", type=int, default=768)
+    gd = sub.add_parser("gdn")
+    gd.add_argument("--seqs", type=int, default=64); gd.add_argument("--rows", type=int, default=1)
+    gd.add_argument("--hk", type=int, default=16); gd.add_argument("--hv", type=int, default=48); gd.add_argument("--d", type=int, default=128)
     d = sub.add_parser("attn_decode")
     p = sub.add_parser("attn_prefill")
     for s in (d, p):
@@ -188,10 +224,10 @@ def main(argv=None):
     p.add_argument("--prefix", type=int, default=0)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=4096); n.add_argument("--n", type=int, default=4096)
-    for s in (g, d, p, n, g8, mo):
+    for s in (g, d, p, n, g8, mo, gd):
         s.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "moe": bench_moe, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "norm": bench_norm}[a.op](a)
+    {"gemm": bench_gemm, "gdn": bench_gdn, "gemm_fp8": bench_gemm_fp8, "moe": bench_moe, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "norm": bench_norm}[a.op](a)
 
 
 if __name__ == "__main__":

@@ -34,6 +34,22 @@ def pick_bn(m: int, n: int, sms: int, epilogue: str = "store") -> int:
     return choices[-1]
 
 
+def pick_bm(m: int, n: int, bn: int, sms: int, epilogue: str = "store") -> int:
+    """256-row tiles (a third less L2 traffic per FLOP) once they still fill the machine evenly; else 128."""
+    if bn != 256 or epilogue not in ("store", "acc", "swiglu") or not M256_ENABLED:
+        return 128
+    t256 = ((m + 255) // 256) * ((n + 255) // 256)
+    t128 = ((m + 127) // 128) * ((n + 255) // 256)
+    # time ~ waves x tile work; a 256-row tile is two 128-row tiles of work done M256_GAIN times faster
+    cost256 = -(-t256 // sms) * 2.0 / M256_GAIN
+    cost128 = -(-t128 // sms) * 1.0
+    return 256 if cost256 < cost128 else 128
+
+
+M256_ENABLED = True
+M256_GAIN = 1.10          # measured speed of the 256-row tile over two 128-row tiles at large sizes
+
+
 def stack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """Weights for the SwiGLU epilogue: all gate rows, then all up rows."""
     assert up.shape == gate.shape
@@ -46,7 +62,7 @@ GEMV_ROWS = 4        # up to this many rows the weight-streaming kernel runs ins
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *,
          epilogue: str = "store", residual: torch.Tensor | None = None, bn: int | None = None,
-         m: int | None = None, pdl: bool = False) -> torch.Tensor:
+         m: int | None = None, pdl: bool = False, bm: int | None = None) -> torch.Tensor:
     """``a[M,K]`` bf16 row-major (row stride free), ``w[N,K]`` bf16; returns ``out``.
 
     epilogue: ``store`` (bf16), ``f32``, ``acc`` (bf16 ``out = a·wᵀ + residual``; residual defaults
@@ -79,11 +95,14 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *,
         return out
     if bn is None:
         bn = pick_bn(M, N, k.sm_count, epilogue)
-    tma_a = k.tensor_map_2d(a, BM, BK)
+    if bm is None:
+        bm = pick_bm(M, N, bn, k.sm_count, epilogue)
+    assert bm in (128, 256) and (bm == 128 or (bn == 256 and epilogue in ("store", "acc", "swiglu")))
+    tma_a = k.tensor_map_2d(a, bm, BK)
     tma_b = k.tensor_map_2d(w, bn // 2 if epilogue == "swiglu" else bn, BK)
-    tiles = ((M + BM - 1) // BM) * ((N + bn - 1) // bn)
+    tiles = ((M + bm - 1) // bm) * ((N + bn - 1) // bn)
     grid = min(tiles, k.sm_count)
-    entry = f"kern_gemm_bf16_tn{_EPI[epilogue]}_n{bn}"
+    entry = f"kern_gemm_bf16_tn{_EPI[epilogue]}{'_m256' if bm == 256 else ''}_n{bn}"
     k.launch("gemm_bf16", entry, (grid,), (192,),
              [tma_a, tma_b, ptr(out), ptr(residual), i32(M), i32(N), i32(K), i32(out.stride(0)),
               ptr(k.err_word())],

@@ -105,3 +105,21 @@ def test_gemv_small_rows(cuda, epilogue, m, n, k):
     Kernels.get(cuda).check_error()
     ref = gemm_reference(a, w, epilogue, res)
     torch.testing.assert_close(got.float(), ref.float(), rtol=1.6e-2, atol=1.6e-2)
+
+
+@pytest.mark.parametrize("epilogue", ["store", "acc", "swiglu"])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 512, 320), (1000, 1024, 1024), (2049, 4096, 2048)])
+def test_gemm_256_row_tiles(cuda, epilogue, m, n, k):
+    """The 256-row tile (two MMAs per K step sharing one B tile, both accumulators in TMEM) against the fp32 statement."""
+    from kern_b200.ops.gemm import gemm, gemm_reference
+    from kern_b200.ops.launcher import Kernels
+
+    torch.manual_seed(m + n + k)
+    a = torch.randn(m, k, device=cuda).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=cuda) * k ** -0.5).to(torch.bfloat16)
+    res = torch.randn(m, n, device=cuda).to(torch.bfloat16) if epilogue == "acc" else None
+    out = res.clone() if res is not None else None
+    got = gemm(a, w, out=out, epilogue=epilogue, bn=256, bm=256)
+    torch.cuda.synchronize()
+    Kernels.get(cuda).check_error()
+    torch.testing.assert_close(got.float(), gemm_reference(a, w, epilogue, res).float(), rtol=1.6e-2, atol=1.6e-2)
