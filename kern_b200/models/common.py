@@ -127,6 +127,27 @@ def gemm_ranges(n: int, var_max: int, tiles=(256, 128, 64), sms: int = SMS):
     return out
 
 
+M256_GAIN = 0.0      # speed of a 256-row tile over two 128-row tiles at large sizes (0: the 256-row tiles are not used)
+
+
+def m256_split(n: int, lo: int, hi: int, sms: int = SMS):
+    """Sub-ranges of [lo, hi] rows by tile height: 256 where `waves x tile work` is smaller than with 128-row tiles."""
+    ncols = -(-n // 256)
+    out = []
+    r = lo
+    while r <= hi:
+        top = min(hi, -(-r // BM) * BM)            # rows up to the next multiple of 128 share their tile counts
+        c256 = -(-(-(-top // 256) * ncols) // sms) * 2.0 / M256_GAIN
+        c128 = -(-(-(-top // BM) * ncols) // sms) * 1.0
+        bm = 256 if c256 < c128 else BM
+        if out and out[-1][0] == bm:
+            out[-1] = (bm, out[-1][1], top)
+        else:
+            out.append((bm, r, top))
+        r = top + 1
+    return out
+
+
 def gemm_op(n: int, k: int, *, epilogue: str = "store", rows_var: str = "tokens", rows_max: int,
             lda: int | None = None, ldc: int | None = None) -> dict:
     """C[rows, n] = A[rows, k] · W[n, k]ᵀ through the tcgen05 GEMM, one launch per `when` range.
@@ -162,7 +183,13 @@ def gemm_op(n: int, k: int, *, epilogue: str = "store", rows_var: str = "tokens"
             launch["when"] = when
         launches.append(launch)
     tiles = (256, 128, 64, 32) if epilogue in ("store", "acc") else (256, 128, 64)
+    ranges = []
     for bn, lo, hi in gemm_ranges(n, rows_max, tiles):
+        if bn == 256 and epilogue in ("store", "acc", "swiglu") and M256_GAIN:
+            ranges += [(bn, bm, a, b) for bm, a, b in m256_split(n, lo, hi)]
+        else:
+            ranges.append((bn, BM, lo, hi))
+    for bn, bm, lo, hi in ranges:
         lo = max(lo, GEMV_ROWS + 1)
         if lo > hi:
             continue
@@ -172,11 +199,11 @@ def gemm_op(n: int, k: int, *, epilogue: str = "store", rows_var: str = "tokens"
         if hi < rows_max:
             when["max"] = hi
         launch = {
-            "module": "gemm_bf16", "entry": f"kern_gemm_bf16_tn{suffix}_n{bn}", "params": lparams,
+            "module": "gemm_bf16", "entry": f"kern_gemm_bf16_tn{suffix}{'_m256' if bm == 256 else ''}_n{bn}", "params": lparams,
             "block": [192, 1, 1], "grid": [SMS, 1, 1], "shared_mem": gemm_smem(bn),
             "args": [
                 {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
-                    "param": 0, "dtype": "bf16", "dims": [k, 0], "strides": [lda * 2], "box": [BK, BM],
+                    "param": 0, "dtype": "bf16", "dims": [k, 0], "strides": [lda * 2], "box": [BK, bm],
                     "swizzle": 128, "l2_promotion": 256}}]}},
                 {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
                     "param": 1, "dtype": "bf16", "dims": [k, n], "strides": [k * 2],
