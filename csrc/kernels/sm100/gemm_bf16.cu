@@ -46,7 +46,7 @@ struct GemmCfg {
 
 // EPI 4 (tensor-parallel partial sums): instead of storing C, every row of the tile is pushed over NVLink into the
 // staging slot of the rank that will reduce it (the row dealing of the fused all-reduce kernel: row = j + i G,
-// owner = i % nranks, dense index (i / nranks) G + j, parity from that kernel's epoch of column j).
+// owner = (i + j) % nranks, dense index (i / nranks) G + j, parity from that kernel's epoch of column j).
 struct ScatterArgs {
   const unsigned long long* comm_peers = nullptr;   // every rank's staging buffer, mapped here
   const uint32_t* epochs = nullptr;                 // the all-reduce kernel's per-column epochs (read only)
@@ -263,7 +263,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
           unsigned long long dst = 0;
           if (row < row_end) {
             const int j = row % sc.grid, i = row / sc.grid;
-            const int owner = i % sc.nranks, idx = (i / sc.nranks) * sc.grid + j;
+            const int owner = (i + j) % sc.nranks, idx = (i / sc.nranks) * sc.grid + j;
             if (idx >= sc.slot_rows) {
               set_error(err, ERR_BOUNDS);
             } else {

@@ -10,7 +10,7 @@
 //
 //   mode 0 (one-shot, few rows): push my partial rows into my slot on every peer, wait for everyone's,
 //          then every rank reduces every row itself in rank order (all ranks produce identical bytes).
-//   mode 1 (two-shot, many rows): rows are dealt to owners inside each CTA; push each partial row to its
+//   mode 1 (two-shot, many rows): rows are dealt to owners inside each CTA (row j + i G belongs to rank (i + j) % N); push each partial row to its
 //          owner only, the owner reduces (+ residual) and pushes the new x row to every peer, then every
 //          rank normalises all of its CTA's rows locally. Link bytes: 2 (N-1)/N of the message.
 //   mode 2 (fused with the GEMM): as mode 1, but the partial rows were pushed to their owners by the epilogue of
@@ -98,7 +98,7 @@ extern "C" __global__ void __launch_bounds__(kThreads)
         for (int v = threadIdx.x; v < nv; v += kThreads) dst[v] = src[v];
       }
     } else {
-      const int owner = i % nranks;
+      const int owner = (i + j) % nranks;   // rotated by the CTA so a few rows per CTA still spread over every rank
       const int idx = (i / nranks) * G + j;   // dense index among the owner's rows
       if (idx >= slot_rows) { if (threadIdx.x == 0) set_error(err, ERR_BOUNDS); continue; }
       __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(comm_peers[owner]) + parity * parity_elems + rank * slot_elems;
@@ -125,7 +125,7 @@ extern "C" __global__ void __launch_bounds__(kThreads)
       const int row = j + i * G;
       int idx = row;
       if (mode >= 1) {
-        if (i % nranks != rank) continue;   // not my row to reduce
+        if ((i + j) % nranks != rank) continue;   // not my row to reduce
         idx = (i / nranks) * G + j;
       }
       if (idx >= slot_rows) continue;
