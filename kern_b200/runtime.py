@@ -158,7 +158,33 @@ class Runtime:
 
     # ---- execution ----
     def issue(self, program: str, vars: dict[str, int], eager: bool = False) -> int:
-        return self._rt.issue(program, vars, eager)
+        rec = getattr(self, "_recorder", None)
+        if rec is None:
+            return self._rt.issue(program, vars, eager)
+        import time
+
+        t0 = time.perf_counter()
+        n = self._rt.issue(program, vars, eager)
+        p = self.protocol or {}
+        rows = vars.get((p.get("rows") or {}).get("var"), 0)
+        groups = vars.get((p.get("groups") or {}).get("var"), 0)
+        ctx = vars.get((p.get("context") or {}).get("var"), 0) if p.get("context") else 0
+        graph = bool(self.doc["programs"][program].get("graph")) and not eager
+        rec.step(program, groups, rows, ctx, graph, 0.0, (time.perf_counter() - t0) * 1e6, n)
+        return n
+
+    def record(self, directory, rank: int = 0):
+        """Start recording every issued step into Parquet traces under `directory` (see `kern_b200.trace`); returns the
+        recorder (`rotate()` writes what is buffered, `record(None)` stops)."""
+        if directory is None:
+            rec, self._recorder = getattr(self, "_recorder", None), None
+            if rec is not None:
+                rec.rotate()
+            return None
+        from .trace import Recorder
+
+        self._recorder = Recorder(directory, rank)
+        return self._recorder
 
     def issue_timed(self, program: str, vars: dict[str, int]):
         """One eager run with an event between calls: [(label, op, ms, launches)] in call order."""
