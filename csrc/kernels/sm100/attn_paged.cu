@@ -45,11 +45,13 @@ KERN_DEVICE uint32_t kv_off(int tok, int chunk) {
   return (uint32_t)(cb * (TK * 128) + tok * 128 + ((c ^ (tok & 7)) << 4));
 }
 
-template <int D>
+// Prefill with head_dim <= 128 runs a two-stage ring so that two CTAs (eight math warps) fit one SM: the row-parallel
+// kernel is bound by mma.sync issue, not by the depth of its KV ring; decode keeps the deep ring (it is bandwidth-bound).
+template <int D, bool PREFILL = false>
 struct AttnCfg {
   static constexpr int kTileBytes = TK * D * 2;         // one of K or V
   static constexpr int kStageBytes = 2 * kTileBytes;    // K then V
-  static constexpr int kStages = D >= 256 ? 3 : 4;
+  static constexpr int kStages = (PREFILL && D <= 128) ? 2 : (D >= 256 ? 3 : 4);
   static constexpr int kQStride = D + 8;                // padded bf16 row of the q tile
   static constexpr int kQBytes = 64 * kQStride * 2;
   static constexpr int kSmem = 1024 + kStages * kStageBytes + kQBytes + 256;
@@ -73,7 +75,7 @@ struct AttnArgs {
 // PREFILL = false: decode/verify (warps split tokens); true: causal prefill (warps split rows)
 template <int D, bool PREFILL>
 KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a) {
-  using Cfg = AttnCfg<D>;
+  using Cfg = AttnCfg<D, PREFILL>;
   constexpr int kStages = Cfg::kStages;
   constexpr int NT = PREFILL ? 8 : 2;        // 8-token n-tiles of S per warp per KV tile
   constexpr int ROWS = PREFILL ? 64 : 16;    // query rows per CTA
@@ -379,7 +381,7 @@ KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a) {
 using namespace kern;
 
 #define KERN_ATTN_ENTRY(name, D, PREFILL)                                                        \
-  extern "C" __global__ void __launch_bounds__(160, 1)                                           \
+  extern "C" __global__ void __launch_bounds__(160, (PREFILL && D <= 128) ? 2 : 1)               \
       name(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* q,                   \
            __nv_bfloat16* out, float* ws_o, float* ws_ml, const int* block_table,                \
            const int* seq_lens, const int* cu_q, const int* work, const int* work_count,         \

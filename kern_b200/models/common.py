@@ -262,8 +262,9 @@ def rope_append_op(hq: int, hk: int, d: int, rot: int, page_size: int, max_pos: 
         "shared_mem": 4 * d * 4, "params": lp, "args": args}]}}
 
 
-def attn_smem(d: int) -> int:
-    return 1024 + (3 if d >= 256 else 4) * (2 * 64 * d * 2) + 64 * (d + 8) * 2 + 256
+def attn_smem(d: int, prefill: bool = False) -> int:
+    stages = 2 if (prefill and d <= 128) else (3 if d >= 256 else 4)
+    return 1024 + stages * (2 * 64 * d * 2) + 64 * (d + 8) * 2 + 256
 
 
 _ATTN_LP = ["bytes<128>", "in buffer<bf16>", "out buffer<bf16>", "i64", "i64", "in buffer<i32>", "in buffer<i32>",
@@ -297,7 +298,7 @@ def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, 
     # call): token-parallel kernel, so their KV streams at full bandwidth
     return {"params": iface, "impl": {"launches": [
         {"module": "attn_paged", "entry": f"kern_attn_prefill_paged_d{d}", "block": [160, 1, 1],
-         "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1], "shared_mem": attn_smem(d),
+         "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1], "shared_mem": attn_smem(d, prefill=True),
          "params": lp, "args": args(6, 7)},
         {"module": "attn_paged", "entry": f"kern_attn_decode_paged_d{d}", "block": [160, 1, 1],
          "grid": [hk, "seqs", 1], "shared_mem": attn_smem(d), "params": lp, "args": args(9, 10)}]}}

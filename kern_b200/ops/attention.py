@@ -46,8 +46,8 @@ def rope_kv_append(qkv: torch.Tensor, pool: torch.Tensor, positions: torch.Tenso
              shared_mem=4 * d * 4)
 
 
-def _attn_smem(d: int) -> int:
-    stages = 3 if d >= 256 else 4
+def _attn_smem(d: int, prefill: bool = False) -> int:
+    stages = 2 if (prefill and d <= 128) else (3 if d >= 256 else 4)
     return 1024 + stages * (2 * TK * d * 2) + 64 * (d + 8) * 2 + 256
 
 
@@ -129,7 +129,7 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tens
               i32(block_table.shape[1]), i32(page_size), i32(rows_per_seq),
               i32(splits if partial is None else splits | (partial[0] << 8) | (total << 16)), i32(pages),
               f32(scale * 1.4426950408889634), ptr(k.err_word())],
-             shared_mem=_attn_smem(d))
+             shared_mem=_attn_smem(d, prefill))
     if splits > 1 and partial is None:
         merge_partials(ws_o, ws_ml, out, q.shape[0], hq, d, splits)
     return out
