@@ -97,3 +97,14 @@ def test_bench_candidate_splices_and_picks(tmp_path, capsys):
     bad = dict(cand, ops={"norm": {**doc["ops"]["norm"], "params": doc["ops"]["norm"]["params"][:2]}})
     cpath.write_text(json.dumps(bad))
     assert main(["bench", "--cpu", "--manifest", str(mpath), "--weights", str(wpath), "--candidate", str(cpath)]) == 1
+
+
+def test_pick_fewest_ranges_within_noise():
+    from kern_b200.testing.pick import Point, gaps, pick
+
+    pts = [Point(1, {"gemv": 1.0, "tile": 3.0}), Point(4, {"gemv": 1.2, "tile": 2.9}), Point(8, {"gemv": 2.5, "tile": 2.6}, noise=0.2),
+           Point(16, {"gemv": 9.0, "tile": 2.7}), Point(256, {"gemv": 99.0, "tile": 3.0})]
+    got = pick(pts)
+    assert got == [("gemv", 1, 8), ("tile", 9, 256)]            # the tie at 8 (within noise) extends the first range
+    assert gaps(got, 512) == [(257, 512)] and gaps(got, 256) == []
+    assert pick([Point(5, {"a": 1.0, "b": 1.05}, noise=0.1), Point(9, {"a": 2.0, "b": 1.0})]) == [("b", 1, 9)]
