@@ -108,21 +108,24 @@ extern "C" __global__ void __launch_bounds__(256)
 // staged 32 at a time: q and k are loaded, l2-normalised (one warp per token) and parked in shared memory
 // together with v, the decay and beta of those tokens.
 constexpr int GDN_ROWS = 16;   // value rows per CTA
-constexpr int GDN_TB = 32;     // tokens per staged batch
+constexpr int GDN_TB = 32;     // most tokens per staged batch
 
 template <int DK, int DV>
 __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, float* o_raw, uint8_t* state,
                                          const int* lines, const int* cu_q, const float* A_log, const float* dt_bias,
                                          int seqs, int hk, int hv, int zba_stride, int b_off, int a_off,
-                                         long long line_bytes, long long s_offset) {
+                                         long long line_bytes, long long s_offset, int tb) {
   constexpr int TPR = 256 / GDN_ROWS;   // 16 lanes per value row
   constexpr int KPT = DK / TPR;         // state elements per thread (k = j * TPR + part)
   static_assert(KPT >= 1 && DV % GDN_ROWS == 0, "shape");
-  __shared__ float qs[GDN_TB][DK];
-  __shared__ float ks[GDN_TB][DK];
-  __shared__ float vs[GDN_TB][GDN_ROWS];
-  __shared__ float decays[GDN_TB];
-  __shared__ float betas[GDN_TB];
+  // staging for `tb` tokens (dynamic shared memory: (2 DK + GDN_ROWS + 2) * 4 bytes per token) — a decode launch stages
+  // one token and leaves the SM's shared memory to more resident CTAs
+  extern __shared__ float gdn_sm[];
+  float (*qs)[DK] = reinterpret_cast<float (*)[DK]>(gdn_sm);
+  float (*ks)[DK] = reinterpret_cast<float (*)[DK]>(gdn_sm + (size_t)tb * DK);
+  float (*vs)[GDN_ROWS] = reinterpret_cast<float (*)[GDN_ROWS]>(gdn_sm + (size_t)2 * tb * DK);
+  float* decays = gdn_sm + (size_t)tb * (2 * DK + GDN_ROWS);
+  float* betas = decays + tb;
   constexpr int PARTS = DV / GDN_ROWS;
   const int h = blockIdx.x / PARTS, row0 = (blockIdx.x % PARTS) * GDN_ROWS, s = blockIdx.y;
   if (s >= seqs) return;
@@ -140,8 +143,8 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
   for (int j = 0; j < KPT; ++j) S[j] = line > 0 ? Sg[j * TPR + kpart] : 0.f;
   const float a_neg = -__expf(A_log[h]);
   const float dtb = dt_bias[h];
-  for (int base = r0; base < r1; base += GDN_TB) {
-    const int nb = min(GDN_TB, r1 - base);
+  for (int base = r0; base < r1; base += tb) {
+    const int nb = min(tb, r1 - base);
     __syncthreads();   // the previous batch has been consumed
     for (int t = warp; t < nb; t += 8) {
       const __nv_bfloat16* row = qkv + (size_t)(base + t) * conv_dim;
@@ -209,10 +212,10 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
   extern "C" __global__ void __launch_bounds__(256)                                                                    \
       name(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, float* o_raw, uint8_t* state, const int* lines,         \
            const int* cu_q, const float* A_log, const float* dt_bias, int seqs, int hk, int hv, int zba_stride,        \
-           int b_off, int a_off, long long line_bytes, long long s_offset) {                                           \
+           int b_off, int a_off, long long line_bytes, long long s_offset, int tb) {                                   \
     pdl_wait();                                                                                                        \
     gdn_body<DK, DV>(qkv, zba, o_raw, state, lines, cu_q, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off, a_off,      \
-                     line_bytes, s_offset);                                                                            \
+                     line_bytes, s_offset, tb < 1 ? 1 : (tb > GDN_TB ? GDN_TB : tb));                                  \
   }
 
 KERN_GDN_ENTRY(kern_gdn_rule_k128_v128, 128, 128)

@@ -251,7 +251,7 @@ def k_gdn_conv_state(g, x, state, lines, cu, seqs, conv_dim, width, x_stride, li
 
 
 def _gdn_rule(dim):
-    def run(g, qkv, zba, o_raw, state, lines, cu, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off, a_off, line_bytes, s_off):
+    def run(g, qkv, zba, o_raw, state, lines, cu, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off, a_off, line_bytes, s_off, tb):
         from .ops import gdn as G
 
         conv_dim = 2 * hk * dim + hv * dim

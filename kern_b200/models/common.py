@@ -617,14 +617,16 @@ def gdn_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_
     if ragged:
         iface.append("in buffer<i32>")
     at = len(iface)
+    tb = 32 if ragged else 1          # tokens staged per pass
     iface += ["in buffer<f32>", "in buffer<f32>", "in buffer<bf16>"]
     lp = ["in buffer<bf16>", "in buffer<bf16>", "out buffer<f32>", "inout state", "in buffer<i32>",
-          "in buffer<i32>" if ragged else "i64", "in buffer<f32>", "in buffer<f32>"] + ["i32"] * 6 + ["i64", "i64"]
+          "in buffer<i32>" if ragged else "i64", "in buffer<f32>", "in buffer<f32>"] + ["i32"] * 6 + ["i64", "i64", "i32"]
     args = [{"param": 0}, {"param": 1}, {"scratch": "o_raw"}, {"param": 3}, {"param": 4},
             {"param": 5} if ragged else {"i64": 0}, {"param": at}, {"param": at + 1}, {"i32": I32_MAX}, {"i32": hk},
-            {"i32": hv}, {"i32": zba_stride}, {"i32": hv * dim}, {"i32": hv * dim + hv}, {"i64": line_bytes}, {"i64": s_off}]
+            {"i32": hv}, {"i32": zba_stride}, {"i32": hv * dim}, {"i32": hv * dim + hv}, {"i64": line_bytes}, {"i64": s_off},
+            {"i32": tb}]
     rule = {"module": "gdn", "entry": f"kern_gdn_rule_k{dim}_v{dim}", "block": [256, 1, 1],
-            "grid": [hv * (dim // 16), "seqs", 1], "params": lp, "args": args}
+            "grid": [hv * (dim // 16), "seqs", 1], "shared_mem": tb * (2 * dim + 16 + 2) * 4, "params": lp, "args": args}
     norm = {"module": "gdn", "entry": "kern_gdn_gate_norm_bf16", "block": [128, 1, 1], "grid": ["tokens", hv, 1],
             "params": ["in buffer<f32>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<bf16>", "i32", "i32", "i32", "i32",
                        "i32", "f32"],
