@@ -119,7 +119,7 @@ def gemm_ranges(n: int, var_max: int, tiles=(256, 128, 64), sms: int = SMS):
         lo, top = (m_tiles - 1) * BM + 1, min(m_tiles * BM, var_max)
         if lo > top:
             continue
-        best = min(tiles, key=lambda bn: (cost(bn, m_tiles), -bn))
+        best = min([t for t in tiles if t >= 64], key=lambda bn: (cost(bn, m_tiles), -bn))   # 32-wide tiles measured slower here
         if out and out[-1][0] == best and out[-1][1] == top + 1:
             out[-1] = (best, lo, out[-1][2])
         else:

@@ -27,7 +27,7 @@ def pick_bn(m: int, n: int, sms: int, epilogue: str = "store") -> int:
     num_m = (m + BM - 1) // BM
     choices = _TILES[epilogue]
     if num_m <= 2:       # weight-bound: the width with the least waves x width, i.e. the most even cover of the SMs
-        return min(choices, key=lambda bn: (-(-(num_m * ((n + bn - 1) // bn)) // sms) * bn * (1 + 8 / bn), -bn))
+        return min([c for c in choices if c >= 64], key=lambda bn: (-(-(num_m * ((n + bn - 1) // bn)) // sms) * bn * (1 + 8 / bn), -bn))
     for bn in choices:
         if num_m * ((n + bn - 1) // bn) >= sms:
             return bn
