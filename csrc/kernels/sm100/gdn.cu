@@ -110,7 +110,7 @@ extern "C" __global__ void __launch_bounds__(256)
 constexpr int GDN_ROWS = 16;   // value rows per CTA
 constexpr int GDN_TB = 32;     // most tokens per staged batch
 
-template <int DK, int DV, int PT>     // PT: tokens a warp stages per batch (4: 32-token batches of a prefill chunk; 1: decode rows)
+template <int DK, int DV>
 __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, float* o_raw, uint8_t* state,
                                          const int* lines, const int* cu_q, const float* A_log, const float* dt_bias,
                                          int seqs, int hk, int hv, int zba_stride, int b_off, int a_off,
@@ -143,61 +143,40 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
   for (int j = 0; j < KPT; ++j) S[j] = line > 0 ? Sg[j * TPR + kpart] : 0.f;
   const float a_neg = -__expf(A_log[h]);
   const float dtb = dt_bias[h];
-  // Staging is software-pipelined: the raw q, k, v, a, b of batch n+1 are fetched into registers before batch n is
-  // computed (each warp stages tokens warp, warp+8, ...: up to four of a 32-token batch), so the global loads run under
-  // the token loop; normalising them and parking them in shared memory happens after that loop, between two barriers.
-  constexpr int QN = (DK + 31) / 32;       // q / k elements per lane of a staged token
-  float pq[PT][QN], pk[PT][QN], pv[PT], pab[PT];
-  auto fetch = [&](int base, int nb) {
-#pragma unroll
-    for (int u = 0; u < PT; ++u) {
-      const int t = warp + u * 8;
-      if (t < nb) {
-        const __nv_bfloat16* row = qkv + (size_t)(base + t) * conv_dim;
-#pragma unroll
-        for (int i = 0; i < QN; ++i) {
-          const int c = i * 32 + lane;
-          pq[u][i] = c < DK ? __bfloat162float(row[kh * DK + c]) : 0.f;
-          pk[u][i] = c < DK ? __bfloat162float(row[hk * DK + kh * DK + c]) : 0.f;
-        }
-        pv[u] = lane < GDN_ROWS ? __bfloat162float(row[2 * hk * DK + h * DV + row0 + lane]) : 0.f;
-        pab[u] = lane == 16 ? __bfloat162float(zba[(size_t)(base + t) * zba_stride + a_off + h])
-                            : (lane == 17 ? __bfloat162float(zba[(size_t)(base + t) * zba_stride + b_off + h]) : 0.f);
-      }
-    }
-  };
-  auto park = [&](int nb) {
-#pragma unroll
-    for (int u = 0; u < PT; ++u) {
-      const int t = warp + u * 8;
-      if (t < nb) {
-        float q2 = 0.f, k2 = 0.f;
-#pragma unroll
-        for (int i = 0; i < QN; ++i) { q2 += pq[u][i] * pq[u][i]; k2 += pk[u][i] * pk[u][i]; }
-        q2 = warp_sum(q2);
-        k2 = warp_sum(k2);
-        const float qi = rsqrtf(q2 + 1e-6f) * rsqrtf((float)DK), ki = rsqrtf(k2 + 1e-6f);
-#pragma unroll
-        for (int i = 0; i < QN; ++i) {
-          const int c = i * 32 + lane;
-          if (c < DK) { qs[t][c] = pq[u][i] * qi; ks[t][c] = pk[u][i] * ki; }
-        }
-        if (lane < GDN_ROWS) vs[t][lane] = pv[u];
-        if (lane == 16) {
-          const float av = pab[u] + dtb;
-          const float sp = av > 20.f ? av : log1pf(__expf(av));
-          decays[t] = __expf(a_neg * sp);
-        }
-        if (lane == 17) betas[t] = __bfloat162float(__float2bfloat16(1.f / (1.f + __expf(-pab[u]))));
-      }
-    }
-  };
-  fetch(r0, min(tb, r1 - r0));
   for (int base = r0; base < r1; base += tb) {
     const int nb = min(tb, r1 - base);
     __syncthreads();   // the previous batch has been consumed
-    park(nb);
-    if (base + tb < r1) fetch(base + tb, min(tb, r1 - base - tb));   // in flight while this batch is computed
+    for (int t = warp; t < nb; t += 8) {
+      const __nv_bfloat16* row = qkv + (size_t)(base + t) * conv_dim;
+      float qv[(DK + 31) / 32], kv[(DK + 31) / 32];
+      float q2 = 0.f, k2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < (DK + 31) / 32; ++i) {
+        const int c = i * 32 + lane;
+        qv[i] = c < DK ? __bfloat162float(row[kh * DK + c]) : 0.f;
+        kv[i] = c < DK ? __bfloat162float(row[hk * DK + kh * DK + c]) : 0.f;
+        q2 += qv[i] * qv[i];
+        k2 += kv[i] * kv[i];
+      }
+      q2 = warp_sum(q2);
+      k2 = warp_sum(k2);
+      const float qi = rsqrtf(q2 + 1e-6f) * rsqrtf((float)DK), ki = rsqrtf(k2 + 1e-6f);
+#pragma unroll
+      for (int i = 0; i < (DK + 31) / 32; ++i) {
+        const int c = i * 32 + lane;
+        if (c < DK) { qs[t][c] = qv[i] * qi; ks[t][c] = kv[i] * ki; }
+      }
+      if (lane < GDN_ROWS) vs[t][lane] = __bfloat162float(row[2 * hk * DK + h * DV + row0 + lane]);
+      if (lane == 16) {
+        const float av = __bfloat162float(zba[(size_t)(base + t) * zba_stride + a_off + h]) + dtb;
+        const float sp = av > 20.f ? av : log1pf(__expf(av));
+        decays[t] = __expf(a_neg * sp);
+      }
+      if (lane == 17) {
+        const float bb = __bfloat162float(zba[(size_t)(base + t) * zba_stride + b_off + h]);
+        betas[t] = __bfloat162float(__float2bfloat16(1.f / (1.f + __expf(-bb))));
+      }
+    }
     __syncthreads();
     for (int t = 0; t < nb; ++t) {
       const float decay = decays[t], beta = betas[t], vv = vs[t][vrow];
@@ -229,23 +208,19 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
   }
 }
 
-#define KERN_GDN_ENTRY(name, DK, DV, PT)                                                                                 \
+#define KERN_GDN_ENTRY(name, DK, DV)                                                                                   \
   extern "C" __global__ void __launch_bounds__(256)                                                                    \
       name(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, float* o_raw, uint8_t* state, const int* lines,         \
            const int* cu_q, const float* A_log, const float* dt_bias, int seqs, int hk, int hv, int zba_stride,        \
            int b_off, int a_off, long long line_bytes, long long s_offset, int tb) {                                   \
     pdl_wait();                                                                                                        \
-    gdn_body<DK, DV, PT>(qkv, zba, o_raw, state, lines, cu_q, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off, a_off,  \
-                         line_bytes, s_offset, tb < 1 ? 1 : (tb > 8 * PT ? 8 * PT : tb));                              \
+    gdn_body<DK, DV>(qkv, zba, o_raw, state, lines, cu_q, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off, a_off,      \
+                     line_bytes, s_offset, tb < 1 ? 1 : (tb > GDN_TB ? GDN_TB : tb));                                  \
   }
 
-KERN_GDN_ENTRY(kern_gdn_rule_k128_v128, 128, 128, 4)
-KERN_GDN_ENTRY(kern_gdn_rule_k64_v64, 64, 64, 4)
-KERN_GDN_ENTRY(kern_gdn_rule_k32_v32, 32, 32, 4)
-// decode rows: one staged token per pass, no prefetch registers to speak of, so more CTAs stay resident
-KERN_GDN_ENTRY(kern_gdn_rule_dec_k128_v128, 128, 128, 1)
-KERN_GDN_ENTRY(kern_gdn_rule_dec_k64_v64, 64, 64, 1)
-KERN_GDN_ENTRY(kern_gdn_rule_dec_k32_v32, 32, 32, 1)
+KERN_GDN_ENTRY(kern_gdn_rule_k128_v128, 128, 128)
+KERN_GDN_ENTRY(kern_gdn_rule_k64_v64, 64, 64)
+KERN_GDN_ENTRY(kern_gdn_rule_k32_v32, 32, 32)
 
 // y = rmsnorm(o) * w * silu(z) per (token, value head): grid [tokens, HV], block 128 (dv <= 128 * 8).
 extern "C" __global__ void __launch_bounds__(128)

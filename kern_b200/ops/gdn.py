@@ -47,7 +47,7 @@ def rule(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv
     if o_raw is None:
         o_raw = torch.empty(tokens, hv * dv, dtype=torch.float32, device=qkv.device)
     tb = 1 if cu_q is None else 32          # tokens staged per pass: a decode row needs one
-    k.launch("gdn", f"kern_gdn_rule_{'dec_' if cu_q is None else ''}k{dk}_v{dv}", (hv * (dv // 16), seqs), (256,),
+    k.launch("gdn", f"kern_gdn_rule_k{dk}_v{dv}", (hv * (dv // 16), seqs), (256,),
              [ptr(qkv), ptr(zba), ptr(o_raw), ptr(state), ptr(lines), ptr(cu_q), ptr(A_log), ptr(dt_bias),
               i32(seqs), i32(hk), i32(hv), i32(zba.stride(0)), i32(b_off), i32(a_off), i64(line_b), i64(s_off), i32(tb)],
              shared_mem=rule_smem(dk, tb))
