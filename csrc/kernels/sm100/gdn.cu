@@ -116,16 +116,15 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
                                          int seqs, int hk, int hv, int zba_stride, int b_off, int a_off,
                                          long long line_bytes, long long s_offset, int tb) {
   constexpr int TPR = 256 / GDN_ROWS;   // 16 lanes per value row
-  constexpr int KPT = DK / TPR;         // state elements per thread (k = j * TPR + part)
+  constexpr int KPT = DK / TPR;         // state elements per thread: k = part * KPT + j, contiguous
   static_assert(KPT >= 1 && DV % GDN_ROWS == 0, "shape");
-  // staging for `tb` tokens (dynamic shared memory: (2 DK + GDN_ROWS + 2) * 4 bytes per token) — a decode launch stages
-  // one token and leaves the SM's shared memory to more resident CTAs
-  extern __shared__ float gdn_sm[];
+  // staging for `tb` tokens (dynamic shared memory: (2 DK + GDN_ROWS + 4) * 4 bytes per token) — a decode launch stages
+  // one token and leaves the SM's shared memory to more resident CTAs.  meta[t] = {decay, beta, k.q, -}
+  extern __shared__ __align__(16) float gdn_sm[];
   float (*qs)[DK] = reinterpret_cast<float (*)[DK]>(gdn_sm);
   float (*ks)[DK] = reinterpret_cast<float (*)[DK]>(gdn_sm + (size_t)tb * DK);
-  float (*vs)[GDN_ROWS] = reinterpret_cast<float (*)[GDN_ROWS]>(gdn_sm + (size_t)2 * tb * DK);
-  float* decays = gdn_sm + (size_t)tb * (2 * DK + GDN_ROWS);
-  float* betas = decays + tb;
+  float4* meta = reinterpret_cast<float4*>(gdn_sm + (size_t)2 * tb * DK);
+  float (*vs)[GDN_ROWS] = reinterpret_cast<float (*)[GDN_ROWS]>(gdn_sm + (size_t)tb * (2 * DK + 4));
   constexpr int PARTS = DV / GDN_ROWS;
   const int h = blockIdx.x / PARTS, row0 = (blockIdx.x % PARTS) * GDN_ROWS, s = blockIdx.y;
   if (s >= seqs) return;
@@ -137,74 +136,94 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int vrow = tid / TPR, kpart = tid % TPR;
   float* Sg = reinterpret_cast<float*>(state + (size_t)line * line_bytes + s_offset) +
-              ((size_t)h * DV + row0 + vrow) * DK;
+              ((size_t)h * DV + row0 + vrow) * DK + kpart * KPT;
   float S[KPT];
 #pragma unroll
-  for (int j = 0; j < KPT; ++j) S[j] = line > 0 ? Sg[j * TPR + kpart] : 0.f;
+  for (int j = 0; j < KPT; ++j) S[j] = line > 0 ? Sg[j] : 0.f;
   const float a_neg = -__expf(A_log[h]);
   const float dtb = dt_bias[h];
+  constexpr int QN = (DK + 31) / 32;
   for (int base = r0; base < r1; base += tb) {
     const int nb = min(tb, r1 - base);
     __syncthreads();   // the previous batch has been consumed
-    for (int t = warp; t < nb; t += 8) {
-      const __nv_bfloat16* row = qkv + (size_t)(base + t) * conv_dim;
-      float qv[(DK + 31) / 32], kv[(DK + 31) / 32];
-      float q2 = 0.f, k2 = 0.f;
+    // a warp stages tokens warp, warp + 8, ...: all their loads are issued first, then each is normalised and parked
+    float pq[GDN_TB / 8][QN], pk[GDN_TB / 8][QN];
 #pragma unroll
-      for (int i = 0; i < (DK + 31) / 32; ++i) {
-        const int c = i * 32 + lane;
-        qv[i] = c < DK ? __bfloat162float(row[kh * DK + c]) : 0.f;
-        kv[i] = c < DK ? __bfloat162float(row[hk * DK + kh * DK + c]) : 0.f;
-        q2 += qv[i] * qv[i];
-        k2 += kv[i] * kv[i];
-      }
-      q2 = warp_sum(q2);
-      k2 = warp_sum(k2);
-      const float qi = rsqrtf(q2 + 1e-6f) * rsqrtf((float)DK), ki = rsqrtf(k2 + 1e-6f);
+    for (int u = 0; u < GDN_TB / 8; ++u) {
+      const int t = warp + u * 8;
+      if (t < nb) {
+        const __nv_bfloat16* row = qkv + (size_t)(base + t) * conv_dim;
 #pragma unroll
-      for (int i = 0; i < (DK + 31) / 32; ++i) {
-        const int c = i * 32 + lane;
-        if (c < DK) { qs[t][c] = qv[i] * qi; ks[t][c] = kv[i] * ki; }
+        for (int i = 0; i < QN; ++i) {
+          const int c = i * 32 + lane;
+          pq[u][i] = c < DK ? __bfloat162float(row[kh * DK + c]) : 0.f;
+          pk[u][i] = c < DK ? __bfloat162float(row[hk * DK + kh * DK + c]) : 0.f;
+        }
       }
-      if (lane < GDN_ROWS) vs[t][lane] = __bfloat162float(row[2 * hk * DK + h * DV + row0 + lane]);
-      if (lane == 16) {
-        const float av = __bfloat162float(zba[(size_t)(base + t) * zba_stride + a_off + h]) + dtb;
-        const float sp = av > 20.f ? av : log1pf(__expf(av));
-        decays[t] = __expf(a_neg * sp);
-      }
-      if (lane == 17) {
-        const float bb = __bfloat162float(zba[(size_t)(base + t) * zba_stride + b_off + h]);
-        betas[t] = __bfloat162float(__float2bfloat16(1.f / (1.f + __expf(-bb))));
+    }
+#pragma unroll
+    for (int u = 0; u < GDN_TB / 8; ++u) {
+      const int t = warp + u * 8;
+      if (t < nb) {
+        const __nv_bfloat16* row = qkv + (size_t)(base + t) * conv_dim;
+        float q2 = 0.f, k2 = 0.f, qk = 0.f;
+#pragma unroll
+        for (int i = 0; i < QN; ++i) { q2 += pq[u][i] * pq[u][i]; k2 += pk[u][i] * pk[u][i]; qk += pq[u][i] * pk[u][i]; }
+        q2 = warp_sum(q2);
+        k2 = warp_sum(k2);
+        qk = warp_sum(qk);
+        const float qi = rsqrtf(q2 + 1e-6f) * rsqrtf((float)DK), ki = rsqrtf(k2 + 1e-6f);
+#pragma unroll
+        for (int i = 0; i < QN; ++i) {
+          const int c = i * 32 + lane;
+          if (c < DK) { qs[t][c] = pq[u][i] * qi; ks[t][c] = pk[u][i] * ki; }
+        }
+        if (lane < GDN_ROWS) vs[t][lane] = __bfloat162float(row[2 * hk * DK + h * DV + row0 + lane]);
+        if (lane == 16) {
+          const float av = __bfloat162float(zba[(size_t)(base + t) * zba_stride + a_off + h]) + dtb;
+          const float sp = av > 20.f ? av : log1pf(__expf(av));
+          const float bb = __bfloat162float(zba[(size_t)(base + t) * zba_stride + b_off + h]);
+          meta[t] = make_float4(__expf(a_neg * sp), __bfloat162float(__float2bfloat16(1.f / (1.f + __expf(-bb)))),
+                                qk * qi * ki, 0.f);
+        }
       }
     }
     __syncthreads();
     for (int t = 0; t < nb; ++t) {
-      const float decay = decays[t], beta = betas[t], vv = vs[t][vrow];
-      float kr[KPT];
-      float sk = 0.f;
+      const float4 m = meta[t];            // decay, beta, k.q
+      const float vv = vs[t][vrow];
+      float kr[KPT], qr[KPT];
+      if constexpr (KPT % 4 == 0) {
 #pragma unroll
-      for (int j = 0; j < KPT; ++j) {
-        kr[j] = ks[t][j * TPR + kpart];
-        S[j] *= decay;
-        sk += S[j] * kr[j];
+        for (int j = 0; j < KPT / 4; ++j) {
+          const float4 k4 = reinterpret_cast<const float4*>(&ks[t][kpart * KPT])[j];
+          const float4 q4 = reinterpret_cast<const float4*>(&qs[t][kpart * KPT])[j];
+          kr[4 * j] = k4.x; kr[4 * j + 1] = k4.y; kr[4 * j + 2] = k4.z; kr[4 * j + 3] = k4.w;
+          qr[4 * j] = q4.x; qr[4 * j + 1] = q4.y; qr[4 * j + 2] = q4.z; qr[4 * j + 3] = q4.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < KPT; ++j) { kr[j] = ks[t][kpart * KPT + j]; qr[j] = qs[t][kpart * KPT + j]; }
       }
+      // both products run on the state *before* this token: S_t q = decay (S_{t-1} q) + u (k.q), so one round of
+      // shuffles carries the two sums instead of two rounds in sequence
+      float sa = 0.f, sb = 0.f;
 #pragma unroll
-      for (int o = TPR / 2; o > 0; o >>= 1) sk += __shfl_xor_sync(0xffffffffu, sk, o);
-      const float u = (vv - sk) * beta;
-      float oq = 0.f;
+      for (int j = 0; j < KPT; ++j) { sa += S[j] * kr[j]; sb += S[j] * qr[j]; }
 #pragma unroll
-      for (int j = 0; j < KPT; ++j) {
-        S[j] += u * kr[j];
-        oq += S[j] * qs[t][j * TPR + kpart];
+      for (int o = TPR / 2; o > 0; o >>= 1) {
+        sa += __shfl_xor_sync(0xffffffffu, sa, o);
+        sb += __shfl_xor_sync(0xffffffffu, sb, o);
       }
+      const float u = (vv - m.x * sa) * m.y;
 #pragma unroll
-      for (int o = TPR / 2; o > 0; o >>= 1) oq += __shfl_xor_sync(0xffffffffu, oq, o);
-      if (kpart == 0) o_raw[(size_t)(base + t) * hv * DV + h * DV + row0 + vrow] = oq;
+      for (int j = 0; j < KPT; ++j) S[j] = m.x * S[j] + u * kr[j];
+      if (kpart == 0) o_raw[(size_t)(base + t) * hv * DV + h * DV + row0 + vrow] = m.x * sb + u * m.z;
     }
   }
   if (line > 0) {
 #pragma unroll
-    for (int j = 0; j < KPT; ++j) Sg[j * TPR + kpart] = S[j];
+    for (int j = 0; j < KPT; ++j) Sg[j] = S[j];
   }
 }
 

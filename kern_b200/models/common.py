@@ -626,7 +626,7 @@ def gdn_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_
             {"i32": hv}, {"i32": zba_stride}, {"i32": hv * dim}, {"i32": hv * dim + hv}, {"i64": line_bytes}, {"i64": s_off},
             {"i32": tb}]
     rule = {"module": "gdn", "entry": f"kern_gdn_rule_k{dim}_v{dim}", "block": [256, 1, 1],
-            "grid": [hv * (dim // 16), "seqs", 1], "shared_mem": tb * (2 * dim + 16 + 2) * 4, "params": lp, "args": args}
+            "grid": [hv * (dim // 16), "seqs", 1], "shared_mem": tb * (2 * dim + 16 + 4) * 4, "params": lp, "args": args}
     norm = {"module": "gdn", "entry": "kern_gdn_gate_norm_bf16", "block": [128, 1, 1], "grid": ["tokens", hv, 1],
             "params": ["in buffer<f32>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<bf16>", "i32", "i32", "i32", "i32",
                        "i32", "f32"],

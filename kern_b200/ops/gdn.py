@@ -22,7 +22,7 @@ def line_bytes(hk: int, hv: int, dk: int, dv: int, width: int = 4) -> tuple[int,
 
 
 def rule_smem(dk: int, tb: int) -> int:
-    return tb * (2 * dk + 16 + 2) * 4
+    return tb * (2 * dk + 16 + 4) * 4
 
 
 def conv(x, y, state, lines, cu_q, w, bias, seqs, conv_dim, width, line_b, rows=None):
