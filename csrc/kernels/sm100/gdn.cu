@@ -116,7 +116,10 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
                                          int seqs, int hk, int hv, int zba_stride, int b_off, int a_off,
                                          long long line_bytes, long long s_offset, int tb) {
   constexpr int TPR = 256 / GDN_ROWS;   // 16 lanes per value row
-  constexpr int KPT = DK / TPR;         // state elements per thread: k = part * KPT + j, contiguous
+  constexpr int KPT = DK / TPR;         // state elements per thread, in 16-byte groups: group g of a thread is keys
+                                        // g * 4 TPR + part * 4 .. + 3, so a row's 16 lanes read 256 contiguous bytes per access
+  constexpr int VEC = KPT % 4 == 0 ? 4 : KPT;      // elements per group (DK = 32: one 8-byte group)
+  constexpr int NG = KPT / VEC;
   static_assert(KPT >= 1 && DV % GDN_ROWS == 0, "shape");
   // staging for `tb` tokens (dynamic shared memory: (2 DK + GDN_ROWS + 4) * 4 bytes per token) — a decode launch stages
   // one token and leaves the SM's shared memory to more resident CTAs.  meta[t] = {decay, beta, k.q, -}
@@ -136,10 +139,19 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int vrow = tid / TPR, kpart = tid % TPR;
   float* Sg = reinterpret_cast<float*>(state + (size_t)line * line_bytes + s_offset) +
-              ((size_t)h * DV + row0 + vrow) * DK + kpart * KPT;
+              ((size_t)h * DV + row0 + vrow) * DK;
+  auto kidx = [&](int j) { return (j / VEC) * (VEC * TPR) + kpart * VEC + (j % VEC); };
   float S[KPT];
+  if constexpr (VEC == 4) {
 #pragma unroll
-  for (int j = 0; j < KPT; ++j) S[j] = line > 0 ? Sg[j] : 0.f;
+    for (int g = 0; g < NG; ++g) {
+      const float4 v = line > 0 ? *reinterpret_cast<const float4*>(Sg + g * 4 * TPR + kpart * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      S[4 * g] = v.x; S[4 * g + 1] = v.y; S[4 * g + 2] = v.z; S[4 * g + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < KPT; ++j) S[j] = line > 0 ? Sg[kidx(j)] : 0.f;
+  }
   const float a_neg = -__expf(A_log[h]);
   const float dtb = dt_bias[h];
   constexpr int QN = (DK + 31) / 32;
@@ -193,17 +205,17 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
       const float4 m = meta[t];            // decay, beta, k.q
       const float vv = vs[t][vrow];
       float kr[KPT], qr[KPT];
-      if constexpr (KPT % 4 == 0) {
+      if constexpr (VEC == 4) {
 #pragma unroll
-        for (int j = 0; j < KPT / 4; ++j) {
-          const float4 k4 = reinterpret_cast<const float4*>(&ks[t][kpart * KPT])[j];
-          const float4 q4 = reinterpret_cast<const float4*>(&qs[t][kpart * KPT])[j];
+        for (int j = 0; j < NG; ++j) {
+          const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][j * 4 * TPR + kpart * 4]);
+          const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][j * 4 * TPR + kpart * 4]);
           kr[4 * j] = k4.x; kr[4 * j + 1] = k4.y; kr[4 * j + 2] = k4.z; kr[4 * j + 3] = k4.w;
           qr[4 * j] = q4.x; qr[4 * j + 1] = q4.y; qr[4 * j + 2] = q4.z; qr[4 * j + 3] = q4.w;
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < KPT; ++j) { kr[j] = ks[t][kpart * KPT + j]; qr[j] = qs[t][kpart * KPT + j]; }
+        for (int j = 0; j < KPT; ++j) { kr[j] = ks[t][kidx(j)]; qr[j] = qs[t][kidx(j)]; }
       }
       // both products run on the state *before* this token: S_t q = decay (S_{t-1} q) + u (k.q), so one round of
       // shuffles carries the two sums instead of two rounds in sequence
@@ -222,8 +234,14 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
     }
   }
   if (line > 0) {
+    if constexpr (VEC == 4) {
 #pragma unroll
-    for (int j = 0; j < KPT; ++j) Sg[j] = S[j];
+      for (int g = 0; g < NG; ++g)
+        *reinterpret_cast<float4*>(Sg + g * 4 * TPR + kpart * 4) = make_float4(S[4 * g], S[4 * g + 1], S[4 * g + 2], S[4 * g + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < KPT; ++j) Sg[kidx(j)] = S[j];
+    }
   }
 }
 
