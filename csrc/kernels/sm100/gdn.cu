@@ -107,29 +107,29 @@ extern "C" __global__ void __launch_bounds__(256)
 // shared-memory state and has no block barrier, only two 16-lane shuffle reductions per token. Tokens are
 // staged 32 at a time: q and k are loaded, l2-normalised (one warp per token) and parked in shared memory
 // together with v, the decay and beta of those tokens.
-constexpr int GDN_ROWS = 16;   // value rows per CTA
 constexpr int GDN_TB = 32;     // most tokens per staged batch
 
-template <int DK, int DV>
+template <int DK, int DV, int ROWS>   // ROWS value rows per CTA: 16 for decode rows (many CTAs, bandwidth), 64 for prefill chunks
+                                      // (the per-token overhead — staged q/k reads, shuffles — is paid once per 64 rows)
 __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, float* o_raw, uint8_t* state,
                                          const int* lines, const int* cu_q, const float* A_log, const float* dt_bias,
                                          int seqs, int hk, int hv, int zba_stride, int b_off, int a_off,
                                          long long line_bytes, long long s_offset, int tb) {
-  constexpr int TPR = 256 / GDN_ROWS;   // 16 lanes per value row
+  constexpr int TPR = 256 / ROWS;       // lanes per value row
   constexpr int KPT = DK / TPR;         // state elements per thread, in 16-byte groups: group g of a thread is keys
                                         // g * 4 TPR + part * 4 .. + 3, so a row's 16 lanes read 256 contiguous bytes per access
   constexpr int VEC = KPT % 4 == 0 ? 4 : KPT;      // elements per group (DK = 32: one 8-byte group)
   constexpr int NG = KPT / VEC;
-  static_assert(KPT >= 1 && DV % GDN_ROWS == 0, "shape");
-  // staging for `tb` tokens (dynamic shared memory: (2 DK + GDN_ROWS + 4) * 4 bytes per token) — a decode launch stages
+  static_assert(KPT >= 1 && DV % ROWS == 0 && TPR <= 32, "shape");
+  // staging for `tb` tokens (dynamic shared memory: (2 DK + ROWS + 4) * 4 bytes per token) — a decode launch stages
   // one token and leaves the SM's shared memory to more resident CTAs.  meta[t] = {decay, beta, k.q, -}
   extern __shared__ __align__(16) float gdn_sm[];
   float (*qs)[DK] = reinterpret_cast<float (*)[DK]>(gdn_sm);
   float (*ks)[DK] = reinterpret_cast<float (*)[DK]>(gdn_sm + (size_t)tb * DK);
   float4* meta = reinterpret_cast<float4*>(gdn_sm + (size_t)2 * tb * DK);
-  float (*vs)[GDN_ROWS] = reinterpret_cast<float (*)[GDN_ROWS]>(gdn_sm + (size_t)tb * (2 * DK + 4));
-  constexpr int PARTS = DV / GDN_ROWS;
-  const int h = blockIdx.x / PARTS, row0 = (blockIdx.x % PARTS) * GDN_ROWS, s = blockIdx.y;
+  float (*vs)[ROWS] = reinterpret_cast<float (*)[ROWS]>(gdn_sm + (size_t)tb * (2 * DK + 4));
+  constexpr int PARTS = DV / ROWS;
+  const int h = blockIdx.x / PARTS, row0 = (blockIdx.x % PARTS) * ROWS, s = blockIdx.y;
   if (s >= seqs) return;
   const int line = lines[s];
   const int r0 = cu_q ? cu_q[s] : s, r1 = cu_q ? cu_q[s + 1] : s + 1;
@@ -190,8 +190,8 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
           const int c = i * 32 + lane;
           if (c < DK) { qs[t][c] = pq[u][i] * qi; ks[t][c] = pk[u][i] * ki; }
         }
-        if (lane < GDN_ROWS) vs[t][lane] = __bfloat162float(row[2 * hk * DK + h * DV + row0 + lane]);
-        if (lane == 16) {
+        for (int r = lane; r < ROWS; r += 32) vs[t][r] = __bfloat162float(row[2 * hk * DK + h * DV + row0 + r]);
+        if (lane == 31) {
           const float av = __bfloat162float(zba[(size_t)(base + t) * zba_stride + a_off + h]) + dtb;
           const float sp = av > 20.f ? av : log1pf(__expf(av));
           const float bb = __bfloat162float(zba[(size_t)(base + t) * zba_stride + b_off + h]);
@@ -245,19 +245,24 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
   }
 }
 
-#define KERN_GDN_ENTRY(name, DK, DV)                                                                                   \
+#define KERN_GDN_ENTRY(name, DK, DV, ROWS)                                                                             \
   extern "C" __global__ void __launch_bounds__(256)                                                                    \
       name(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, float* o_raw, uint8_t* state, const int* lines,         \
            const int* cu_q, const float* A_log, const float* dt_bias, int seqs, int hk, int hv, int zba_stride,        \
            int b_off, int a_off, long long line_bytes, long long s_offset, int tb) {                                   \
     pdl_wait();                                                                                                        \
-    gdn_body<DK, DV>(qkv, zba, o_raw, state, lines, cu_q, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off, a_off,      \
-                     line_bytes, s_offset, tb < 1 ? 1 : (tb > GDN_TB ? GDN_TB : tb));                                  \
+    gdn_body<DK, DV, ROWS>(qkv, zba, o_raw, state, lines, cu_q, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off,       \
+                           a_off, line_bytes, s_offset, tb < 1 ? 1 : (tb > GDN_TB ? GDN_TB : tb));                     \
   }
 
-KERN_GDN_ENTRY(kern_gdn_rule_k128_v128, 128, 128)
-KERN_GDN_ENTRY(kern_gdn_rule_k64_v64, 64, 64)
-KERN_GDN_ENTRY(kern_gdn_rule_k32_v32, 32, 32)
+// prefill chunks: grid [HV * DV / rows, seqs] with rows = min(64, DV)
+KERN_GDN_ENTRY(kern_gdn_rule_k128_v128, 128, 128, 64)
+KERN_GDN_ENTRY(kern_gdn_rule_k64_v64, 64, 64, 64)
+KERN_GDN_ENTRY(kern_gdn_rule_k32_v32, 32, 32, 32)
+// decode rows: grid [HV * DV / 16, seqs]
+KERN_GDN_ENTRY(kern_gdn_rule_dec_k128_v128, 128, 128, 16)
+KERN_GDN_ENTRY(kern_gdn_rule_dec_k64_v64, 64, 64, 16)
+KERN_GDN_ENTRY(kern_gdn_rule_dec_k32_v32, 32, 32, 16)
 
 // y = rmsnorm(o) * w * silu(z) per (token, value head): grid [tokens, HV], block 128 (dv <= 128 * 8).
 extern "C" __global__ void __launch_bounds__(128)

@@ -309,6 +309,7 @@ CPU_KERNELS = {
     "kern_silu_mul_bf16": k_silu_mul, "kern_copy_rows": k_copy_rows, "kern_sigmoid_mul_bf16": k_sigmoid_mul,
     "kern_gdn_conv_bf16": k_gdn_conv, "kern_gdn_conv_state": k_gdn_conv_state, "kern_gdn_rule_k128_v128": _gdn_rule(128), "kern_gdn_rule_k64_v64": _gdn_rule(64),
     "kern_gdn_rule_k32_v32": _gdn_rule(32), "kern_gdn_gate_norm_bf16": k_gdn_gate_norm,
+    "kern_gdn_rule_dec_k128_v128": _gdn_rule(128), "kern_gdn_rule_dec_k64_v64": _gdn_rule(64), "kern_gdn_rule_dec_k32_v32": _gdn_rule(32),
     "kern_fill_f32": k_fill, "kern_fill_i32": k_fill, "kern_fill_i64": k_fill, "kern_fill_u8": k_fill,
 }
 for _bn in (256, 128, 64, 32):

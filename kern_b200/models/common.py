@@ -625,8 +625,10 @@ def gdn_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_
             {"param": 5} if ragged else {"i64": 0}, {"param": at}, {"param": at + 1}, {"i32": I32_MAX}, {"i32": hk},
             {"i32": hv}, {"i32": zba_stride}, {"i32": hv * dim}, {"i32": hv * dim + hv}, {"i64": line_bytes}, {"i64": s_off},
             {"i32": tb}]
-    rule = {"module": "gdn", "entry": f"kern_gdn_rule_k{dim}_v{dim}", "block": [256, 1, 1],
-            "grid": [hv * (dim // 16), "seqs", 1], "shared_mem": tb * (2 * dim + 16 + 4) * 4, "params": lp, "args": args}
+    rows_cta = min(64, dim) if ragged else 16          # value rows per CTA (prefill chunks amortise per-token overhead)
+    rule = {"module": "gdn", "entry": f"kern_gdn_rule_{'' if ragged else 'dec_'}k{dim}_v{dim}", "block": [256, 1, 1],
+            "grid": [hv * (dim // rows_cta), "seqs", 1], "shared_mem": tb * (2 * dim + rows_cta + 4) * 4, "params": lp,
+            "args": args}
     norm = {"module": "gdn", "entry": "kern_gdn_gate_norm_bf16", "block": [128, 1, 1], "grid": ["tokens", hv, 1],
             "params": ["in buffer<f32>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<bf16>", "i32", "i32", "i32", "i32",
                        "i32", "f32"],

@@ -21,8 +21,13 @@ def line_bytes(hk: int, hv: int, dk: int, dv: int, width: int = 4) -> tuple[int,
     return s_off + hv * dv * dk * 4, s_off
 
 
-def rule_smem(dk: int, tb: int) -> int:
-    return tb * (2 * dk + 16 + 4) * 4
+def rule_rows(dv: int, decode: bool) -> int:
+    """Value rows per CTA: 16 for decode rows, min(64, dv) for prefill chunks."""
+    return 16 if decode else min(64, dv)
+
+
+def rule_smem(dk: int, tb: int, rows: int = 16) -> int:
+    return tb * (2 * dk + rows + 4) * 4
 
 
 def conv(x, y, state, lines, cu_q, w, bias, seqs, conv_dim, width, line_b, rows=None):
@@ -47,10 +52,11 @@ def rule(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv
     if o_raw is None:
         o_raw = torch.empty(tokens, hv * dv, dtype=torch.float32, device=qkv.device)
     tb = 1 if cu_q is None else 32          # tokens staged per pass: a decode row needs one
-    k.launch("gdn", f"kern_gdn_rule_k{dk}_v{dv}", (hv * (dv // 16), seqs), (256,),
+    rows_cta = rule_rows(dv, cu_q is None)
+    k.launch("gdn", f"kern_gdn_rule_{'dec_' if cu_q is None else ''}k{dk}_v{dv}", (hv * (dv // rows_cta), seqs), (256,),
              [ptr(qkv), ptr(zba), ptr(o_raw), ptr(state), ptr(lines), ptr(cu_q), ptr(A_log), ptr(dt_bias),
               i32(seqs), i32(hk), i32(hv), i32(zba.stride(0)), i32(b_off), i32(a_off), i64(line_b), i64(s_off), i32(tb)],
-             shared_mem=rule_smem(dk, tb))
+             shared_mem=rule_smem(dk, tb, rows_cta))
     k.launch("gdn", "kern_gdn_gate_norm_bf16", (tokens, hv), (128,),
              [ptr(o_raw), ptr(zba), ptr(out), ptr(norm_w), i32(tokens), i32(hv), i32(dv), i32(zba.stride(0)),
               i32(z_off), f32(eps)])
