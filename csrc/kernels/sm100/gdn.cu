@@ -109,8 +109,9 @@ extern "C" __global__ void __launch_bounds__(256)
 // together with v, the decay and beta of those tokens.
 constexpr int GDN_TB = 32;     // most tokens per staged batch
 
-template <int DK, int DV, int ROWS>   // ROWS value rows per CTA: 16 for decode rows (many CTAs, bandwidth), 64 for prefill chunks
-                                      // (the per-token overhead — staged q/k reads, shuffles — is paid once per 64 rows)
+template <int DK, int DV, int ROWS>   // ROWS value rows per CTA. 16 everywhere: 64 rows per CTA pay the staged q/k reads and
+                                      // the shuffles once per 64 rows, but leave 96 CTAs of 8 warps on 148 SMs and measured
+                                      // slower (1.44 ms against 1.27 ms per 2048-row chunk)
 __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, float* o_raw, uint8_t* state,
                                          const int* lines, const int* cu_q, const float* A_log, const float* dt_bias,
                                          int seqs, int hk, int hv, int zba_stride, int b_off, int a_off,
@@ -255,11 +256,11 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
                            a_off, line_bytes, s_offset, tb < 1 ? 1 : (tb > GDN_TB ? GDN_TB : tb));                     \
   }
 
-// prefill chunks: grid [HV * DV / rows, seqs] with rows = min(64, DV)
-KERN_GDN_ENTRY(kern_gdn_rule_k128_v128, 128, 128, 64)
-KERN_GDN_ENTRY(kern_gdn_rule_k64_v64, 64, 64, 64)
-KERN_GDN_ENTRY(kern_gdn_rule_k32_v32, 32, 32, 32)
-// decode rows: grid [HV * DV / 16, seqs]
+// prefill chunks (ragged rows per sequence): grid [HV * DV / 16, seqs]
+KERN_GDN_ENTRY(kern_gdn_rule_k128_v128, 128, 128, 16)
+KERN_GDN_ENTRY(kern_gdn_rule_k64_v64, 64, 64, 16)
+KERN_GDN_ENTRY(kern_gdn_rule_k32_v32, 32, 32, 16)
+// one row per sequence, unfused (the fused decode step is kern_gdn_step_*): grid [HV * DV / 16, seqs]
 KERN_GDN_ENTRY(kern_gdn_rule_dec_k128_v128, 128, 128, 16)
 KERN_GDN_ENTRY(kern_gdn_rule_dec_k64_v64, 64, 64, 16)
 KERN_GDN_ENTRY(kern_gdn_rule_dec_k32_v32, 32, 32, 16)
@@ -284,3 +285,163 @@ extern "C" __global__ void __launch_bounds__(128)
     out[((size_t)t * hv + h) * dv + i] = __float2bfloat16(o[i] * inv * __bfloat162float(norm_w[i]) * silu(z));
   }
 }
+
+// ---- fused decode step -------------------------------------------------------------------------------------------
+// One new token per sequence: a CTA owns one (sequence, value head) pair. The head's whole [DV, DK] f32 state comes in
+// with bulk copies (one mbarrier; 64 KB in flight per CTA, three CTAs per SM) while the warps normalise q and k and
+// fetch v and the gates; the rule then runs out of shared memory, the new state goes straight from registers to
+// global memory, and the gated RMSNorm of the head's output closes the same launch. The step is bandwidth-bound: the
+// roofline is two passes over the state at the copy bandwidth.
+// Reference: tools/kernels-src/gdn_decode.cu:171 (kern_gdn_step_bf16: same fusion, one state tile per CTA).
+template <int DK, int DV>
+__device__ __forceinline__ void gdn_step_body(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, __nv_bfloat16* out,
+                                              uint8_t* state, const int* lines, const float* A_log, const float* dt_bias,
+                                              const __nv_bfloat16* norm_w, int seqs, int hk, int hv, int zba_stride,
+                                              int z_off, int b_off, int a_off, long long line_bytes, long long s_offset,
+                                              float eps) {
+  constexpr int TPR = DK >= 64 ? 16 : DK / 4;   // lanes per value row; each holds DK / TPR keys in 16-byte groups
+  constexpr int KPT = DK / TPR;
+  constexpr int NG = KPT / 4;
+  constexpr int RPP = 256 / TPR;                // value rows per pass
+  constexpr int PASSES = DV / RPP;
+  static_assert(KPT % 4 == 0 && DV % RPP == 0 && PASSES >= 1, "shape");
+  constexpr uint32_t STATE_BYTES = DV * DK * 4;
+  constexpr uint32_t PIECE = STATE_BYTES < 16384 ? STATE_BYTES : 16384;
+  extern __shared__ __align__(128) float gdn_sm[];
+  float* Ssm = gdn_sm;                          // [DV][DK]
+  float* qs = Ssm + DV * DK;
+  float* ks = qs + DK;
+  float* vs = ks + DK;
+  float* os = vs + DV;
+  float* red = os + DV;                         // 8 partial sums + {decay, beta, k.q}
+  uint64_t* bar = reinterpret_cast<uint64_t*>(red + 16);
+  const int h = blockIdx.x, s = blockIdx.y;
+  if (s >= seqs) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int line = lines[s];
+  uint8_t* Sg8 = state + (size_t)line * line_bytes + s_offset + (size_t)h * STATE_BYTES;
+  if (tid == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+    if (line > 0) {
+      mbar_expect_tx(bar, STATE_BYTES);
+      for (uint32_t off = 0; off < STATE_BYTES; off += PIECE)
+        bulk_load_1d(reinterpret_cast<uint8_t*>(Ssm) + off, Sg8 + off, PIECE, bar);
+    }
+  }
+  const int kh = h / (hv / hk);
+  const int conv_dim = 2 * hk * DK + hv * DV;
+  const __nv_bfloat16* row = qkv + (size_t)s * conv_dim;
+  if (warp == 0) {
+    constexpr int QN = (DK + 31) / 32;
+    float pq[QN], pk[QN];
+    float q2 = 0.f, k2 = 0.f, qk = 0.f;
+#pragma unroll
+    for (int i = 0; i < QN; ++i) {
+      const int c = i * 32 + lane;
+      pq[i] = c < DK ? __bfloat162float(row[kh * DK + c]) : 0.f;
+      pk[i] = c < DK ? __bfloat162float(row[hk * DK + kh * DK + c]) : 0.f;
+      q2 += pq[i] * pq[i]; k2 += pk[i] * pk[i]; qk += pq[i] * pk[i];
+    }
+    q2 = warp_sum(q2); k2 = warp_sum(k2); qk = warp_sum(qk);
+    const float qi = rsqrtf(q2 + 1e-6f) * rsqrtf((float)DK), ki = rsqrtf(k2 + 1e-6f);
+#pragma unroll
+    for (int i = 0; i < QN; ++i) {
+      const int c = i * 32 + lane;
+      if (c < DK) { qs[c] = pq[i] * qi; ks[c] = pk[i] * ki; }
+    }
+    if (lane == 0) red[10] = qk * qi * ki;
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const float av = __bfloat162float(zba[(size_t)s * zba_stride + a_off + h]) + dt_bias[h];
+      const float sp = av > 20.f ? av : log1pf(__expf(av));
+      const float bb = __bfloat162float(zba[(size_t)s * zba_stride + b_off + h]);
+      red[8] = __expf(-__expf(A_log[h]) * sp);
+      red[9] = __bfloat162float(__float2bfloat16(1.f / (1.f + __expf(-bb))));
+    }
+  } else {
+    for (int r = tid - 64; r < DV; r += 192) vs[r] = __bfloat162float(row[2 * hk * DK + h * DV + r]);
+  }
+  __syncthreads();                              // q, k, v, gates parked; the barrier's init is visible
+  bool have = line > 0;
+  if (have) {
+    // every copy reads this GPU's own memory and completes; the limit only keeps a broken launch from spinning, and
+    // a CTA that gave up reads the state with plain loads instead (same values), so no result depends on the limit
+    bool ok = false;
+    for (uint32_t i = 0; i < (1u << 22) && !ok; ++i) ok = mbar_try_wait(bar, 0) != 0;
+    if (!__syncthreads_and(ok ? 1 : 0)) {
+      const float4* src = reinterpret_cast<const float4*>(Sg8);
+      for (int i = tid; i < (int)(STATE_BYTES / 16); i += 256) reinterpret_cast<float4*>(Ssm)[i] = src[i];
+      __syncthreads();
+    }
+  }
+  const float decay = red[8], beta = red[9], kq = red[10];
+  const int vrow = tid / TPR, kpart = tid % TPR;
+  float kr[KPT], qr[KPT];
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    const float4 k4 = *reinterpret_cast<const float4*>(ks + g * 4 * TPR + kpart * 4);
+    const float4 q4 = *reinterpret_cast<const float4*>(qs + g * 4 * TPR + kpart * 4);
+    kr[4 * g] = k4.x; kr[4 * g + 1] = k4.y; kr[4 * g + 2] = k4.z; kr[4 * g + 3] = k4.w;
+    qr[4 * g] = q4.x; qr[4 * g + 1] = q4.y; qr[4 * g + 2] = q4.z; qr[4 * g + 3] = q4.w;
+  }
+#pragma unroll
+  for (int p = 0; p < PASSES; ++p) {
+    const int r = p * RPP + vrow;
+    float S[KPT];
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+      const float4 v = have ? *reinterpret_cast<const float4*>(Ssm + (size_t)r * DK + g * 4 * TPR + kpart * 4)
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+      S[4 * g] = v.x; S[4 * g + 1] = v.y; S[4 * g + 2] = v.z; S[4 * g + 3] = v.w;
+    }
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int j = 0; j < KPT; ++j) { sa += S[j] * kr[j]; sb += S[j] * qr[j]; }
+#pragma unroll
+    for (int o = TPR / 2; o > 0; o >>= 1) {
+      sa += __shfl_xor_sync(0xffffffffu, sa, o);
+      sb += __shfl_xor_sync(0xffffffffu, sb, o);
+    }
+    const float u = (vs[r] - decay * sa) * beta;
+    if (have) {
+      float* dst = reinterpret_cast<float*>(Sg8) + (size_t)r * DK;
+#pragma unroll
+      for (int g = 0; g < NG; ++g)
+        *reinterpret_cast<float4*>(dst + g * 4 * TPR + kpart * 4) =
+            make_float4(decay * S[4 * g] + u * kr[4 * g], decay * S[4 * g + 1] + u * kr[4 * g + 1],
+                        decay * S[4 * g + 2] + u * kr[4 * g + 2], decay * S[4 * g + 3] + u * kr[4 * g + 3]);
+    }
+    if (kpart == 0) os[r] = decay * sb + u * kq;
+  }
+  __syncthreads();
+  // gated RMSNorm over the head's DV outputs
+  float ss = 0.f;
+  for (int i = tid; i < DV; i += 256) ss += os[i] * os[i];
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += red[w];
+  const float inv = rsqrtf(tot / (float)DV + eps);
+  for (int i = tid; i < DV; i += 256) {
+    const float z = __bfloat162float(zba[(size_t)s * zba_stride + z_off + h * DV + i]);
+    out[((size_t)s * hv + h) * DV + i] = __float2bfloat16(os[i] * inv * __bfloat162float(norm_w[i]) * silu(z));
+  }
+}
+
+#define KERN_GDN_STEP_ENTRY(name, DK, DV)                                                                              \
+  extern "C" __global__ void __launch_bounds__(256)                                                                    \
+      name(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, __nv_bfloat16* out, uint8_t* state, const int* lines,   \
+           const float* A_log, const float* dt_bias, const __nv_bfloat16* norm_w, int seqs, int hk, int hv,            \
+           int zba_stride, int z_off, int b_off, int a_off, long long line_bytes, long long s_offset, float eps) {     \
+    pdl_wait();                                                                                                        \
+    gdn_step_body<DK, DV>(qkv, zba, out, state, lines, A_log, dt_bias, norm_w, seqs, hk, hv, zba_stride, z_off, b_off,  \
+                          a_off, line_bytes, s_offset, eps);                                                           \
+  }
+
+// grid [HV, seqs], block 256, dynamic shared memory DV * DK * 4 + (2 DK + 2 DV + 16) * 4 + 16 bytes
+KERN_GDN_STEP_ENTRY(kern_gdn_step_k128_v128, 128, 128)
+KERN_GDN_STEP_ENTRY(kern_gdn_step_k64_v64, 64, 64)
+KERN_GDN_STEP_ENTRY(kern_gdn_step_k32_v32, 32, 32)

@@ -276,6 +276,19 @@ def _gdn_rule(dim):
     return run
 
 
+def _gdn_step(dim):
+    rule = _gdn_rule(dim)
+
+    def run(g, qkv, zba, out, state, lines, A_log, dt_bias, norm_w, seqs, hk, hv, zba_stride, z_off, b_off, a_off,
+            line_bytes, s_off, eps):
+        n = g[1]
+        o_raw = torch.zeros(n * hv * dim, dtype=torch.float32)
+        rule((hv, n, 1), qkv, zba, o_raw, state, lines, 0, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off, a_off,
+             line_bytes, s_off, 1)
+        k_gdn_gate_norm((n, hv, 1), o_raw, zba, out, norm_w, n, hv, dim, zba_stride, z_off, eps)
+    return run
+
+
 def k_gdn_gate_norm(g, o_raw, zba, out, norm_w, tokens, hv, dv, zba_stride, z_off, eps):
     from .ops import gdn as G
 
@@ -309,6 +322,7 @@ CPU_KERNELS = {
     "kern_silu_mul_bf16": k_silu_mul, "kern_copy_rows": k_copy_rows, "kern_sigmoid_mul_bf16": k_sigmoid_mul,
     "kern_gdn_conv_bf16": k_gdn_conv, "kern_gdn_conv_state": k_gdn_conv_state, "kern_gdn_rule_k128_v128": _gdn_rule(128), "kern_gdn_rule_k64_v64": _gdn_rule(64),
     "kern_gdn_rule_k32_v32": _gdn_rule(32), "kern_gdn_gate_norm_bf16": k_gdn_gate_norm,
+    "kern_gdn_step_k128_v128": _gdn_step(128), "kern_gdn_step_k64_v64": _gdn_step(64), "kern_gdn_step_k32_v32": _gdn_step(32),
     "kern_gdn_rule_dec_k128_v128": _gdn_rule(128), "kern_gdn_rule_dec_k64_v64": _gdn_rule(64), "kern_gdn_rule_dec_k32_v32": _gdn_rule(32),
     "kern_fill_f32": k_fill, "kern_fill_i32": k_fill, "kern_fill_i64": k_fill, "kern_fill_u8": k_fill,
 }

@@ -614,8 +614,18 @@ def gdn_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_
     Interface [qkv, zba, out, state, lines, (cu_seqlens,) A_log, dt_bias, norm_w]; `zba` points at the z|b|a columns
     of the projection's row."""
     iface = ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "inout state", "in buffer<i32>"]
-    if ragged:
-        iface.append("in buffer<i32>")
+    if not ragged:
+        # one row per sequence: the fused step (state by bulk copy, rule, gated norm) in one launch
+        iface += ["in buffer<f32>", "in buffer<f32>", "in buffer<bf16>"]
+        step = {"module": "gdn", "entry": f"kern_gdn_step_k{dim}_v{dim}", "block": [256, 1, 1], "grid": [hv, "seqs", 1],
+                "shared_mem": dim * dim * 4 + (4 * dim + 16) * 4 + 16,
+                "params": ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "inout state", "in buffer<i32>",
+                           "in buffer<f32>", "in buffer<f32>", "in buffer<bf16>"] + ["i32"] * 7 + ["i64", "i64", "f32"],
+                "args": [{"param": i} for i in range(8)] + [
+                    {"i32": I32_MAX}, {"i32": hk}, {"i32": hv}, {"i32": zba_stride}, {"i32": 0}, {"i32": hv * dim},
+                    {"i32": hv * dim + hv}, {"i64": line_bytes}, {"i64": s_off}, {"f32": eps}]}
+        return {"params": iface, "impl": {"launches": [step]}}
+    iface.append("in buffer<i32>")
     at = len(iface)
     tb = 32 if ragged else 1          # tokens staged per pass
     iface += ["in buffer<f32>", "in buffer<f32>", "in buffer<bf16>"]
@@ -625,7 +635,7 @@ def gdn_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_
             {"param": 5} if ragged else {"i64": 0}, {"param": at}, {"param": at + 1}, {"i32": I32_MAX}, {"i32": hk},
             {"i32": hv}, {"i32": zba_stride}, {"i32": hv * dim}, {"i32": hv * dim + hv}, {"i64": line_bytes}, {"i64": s_off},
             {"i32": tb}]
-    rows_cta = min(64, dim) if ragged else 16          # value rows per CTA (prefill chunks amortise per-token overhead)
+    rows_cta = 16          # value rows per CTA
     rule = {"module": "gdn", "entry": f"kern_gdn_rule_{'' if ragged else 'dec_'}k{dim}_v{dim}", "block": [256, 1, 1],
             "grid": [hv * (dim // rows_cta), "seqs", 1], "shared_mem": tb * (2 * dim + rows_cta + 4) * 4, "params": lp,
             "args": args}

@@ -141,8 +141,11 @@ def bench_gdn(a):
 
     def step():
         G.conv(x, y, state, lines, cu, w, None, seqs, conv_dim, width, lb)
-        G.rule(y, x[:, conv_dim:], out, state, lines, cu, A_log, dtb, nw, seqs, hk, hv, d, d, 0, hv * d, hv * d + hv, lb, s_off,
-               o_raw=o_raw)
+        if a.rows == 1 and not a.unfused:
+            G.step(y, x[:, conv_dim:], out, state, lines, A_log, dtb, nw, seqs, hk, hv, d, d, 0, hv * d, hv * d + hv, lb, s_off)
+        else:
+            G.rule(y, x[:, conv_dim:], out, state, lines, cu, A_log, dtb, nw, seqs, hk, hv, d, d, 0, hv * d, hv * d + hv, lb,
+                   s_off, o_raw=o_raw)
 
     ms = timeit(step, a.iters)
     Kernels.get().check_error()
@@ -215,6 +218,7 @@ def main(argv=None):
     gd = sub.add_parser("gdn")
     gd.add_argument("--seqs", type=int, default=64); gd.add_argument("--rows", type=int, default=1)
     gd.add_argument("--hk", type=int, default=16); gd.add_argument("--hv", type=int, default=48); gd.add_argument("--d", type=int, default=128)
+    gd.add_argument("--unfused", action="store_true", help="decode rows through the two-launch rule + norm instead of the fused step")
     d = sub.add_parser("attn_decode")
     p = sub.add_parser("attn_prefill")
     for s in (d, p):

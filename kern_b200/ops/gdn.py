@@ -22,8 +22,8 @@ def line_bytes(hk: int, hv: int, dk: int, dv: int, width: int = 4) -> tuple[int,
 
 
 def rule_rows(dv: int, decode: bool) -> int:
-    """Value rows per CTA: 16 for decode rows, min(64, dv) for prefill chunks."""
-    return 16 if decode else min(64, dv)
+    """Value rows per CTA (64 per CTA measured slower for prefill chunks: too few CTAs for 148 SMs)."""
+    return 16
 
 
 def rule_smem(dk: int, tb: int, rows: int = 16) -> int:
@@ -60,6 +60,23 @@ def rule(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv
     k.launch("gdn", "kern_gdn_gate_norm_bf16", (tokens, hv), (128,),
              [ptr(o_raw), ptr(zba), ptr(out), ptr(norm_w), i32(tokens), i32(hv), i32(dv), i32(zba.stride(0)),
               i32(z_off), f32(eps)])
+    return out
+
+
+def step_smem(dk: int, dv: int) -> int:
+    return dv * dk * 4 + (2 * dk + 2 * dv + 16) * 4 + 16
+
+
+def step(qkv, zba, out, state, lines, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv, z_off, b_off, a_off, line_b, s_off,
+         eps=1e-6):
+    """Fused decode step (one row per sequence): the head's state by bulk copy into shared memory, the rule, the new
+    state straight to global memory, and the gated RMSNorm, in one launch of [HV, seqs] CTAs."""
+    k = Kernels.get(qkv.device)
+    assert dk == dv and dk in (32, 64, 128)
+    k.launch("gdn", f"kern_gdn_step_k{dk}_v{dv}", (hv, seqs), (256,),
+             [ptr(qkv), ptr(zba), ptr(out), ptr(state), ptr(lines), ptr(A_log), ptr(dt_bias), ptr(norm_w), i32(seqs),
+              i32(hk), i32(hv), i32(zba.stride(0)), i32(z_off), i32(b_off), i32(a_off), i64(line_b), i64(s_off), f32(eps)],
+             shared_mem=step_smem(dk, dv))
     return out
 
 

@@ -35,7 +35,7 @@ def test_gdn_prefill_then_decode(cuda, hk, hv, d):
     ref_win = [torch.zeros(width - 1, conv_dim, device=cuda) for _ in lens]
     ref_S = [torch.zeros(hv, dv, dk, device=cuda) for _ in lens]
 
-    def run(rows_per_seq, decode):
+    def run(rows_per_seq, decode, fused=False):
         T = sum(rows_per_seq)
         x = bf(torch.randn(T, x_stride, device=cuda))
         cu = torch.tensor([0] + list(torch.tensor(rows_per_seq).cumsum(0)), dtype=torch.int32, device=cuda)
@@ -44,8 +44,12 @@ def test_gdn_prefill_then_decode(cuda, hk, hv, d):
         cu_arg = None if decode else cu
         gdn.conv(x, y, state, lines, cu_arg, w, bias, seqs, conv_dim, width, lb)
         zba = x[:, conv_dim:]
-        gdn.rule(y, zba, out, state, lines, cu_arg, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv,
-                 0, hv * dv, hv * dv + hv, lb, s_off)
+        if fused:
+            gdn.step(y, zba, out, state, lines, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv,
+                     0, hv * dv, hv * dv + hv, lb, s_off)
+        else:
+            gdn.rule(y, zba, out, state, lines, cu_arg, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv,
+                     0, hv * dv, hv * dv + hv, lb, s_off)
         torch.cuda.synchronize()
         Kernels.get(cuda).check_error()
         for s, n in enumerate(rows_per_seq):
@@ -69,8 +73,8 @@ def test_gdn_prefill_then_decode(cuda, hk, hv, d):
             torch.testing.assert_close(win_dev.float(), bf(ref_win[s]).float(), rtol=0, atol=0)
 
     run(lens, decode=False)
-    for _ in range(3):
-        run([1, 1, 1], decode=True)
+    for i in range(4):
+        run([1, 1, 1], decode=True, fused=i % 2 == 0)      # the fused step and the two-launch form continue each other
     # untouched lines (0 = null, 2, 4) stayed zero
     for ln in (0, 2, 4):
         assert int(state[ln].count_nonzero()) == 0
@@ -91,8 +95,12 @@ def test_gdn_null_line_is_read_as_zero_and_never_written(cuda):
     gdn.conv(x, y, state, lines, None, w, None, 2, conv_dim, width, lb)
     gdn.rule(y, x[:, conv_dim:], out, state, lines, None, torch.zeros(hv, device=cuda), torch.zeros(hv, device=cuda),
              bf(torch.ones(d, device=cuda)), 2, hk, hv, d, d, 0, hv * d, hv * d + hv, lb, s_off)
+    out2 = torch.empty_like(out)
+    gdn.step(y, x[:, conv_dim:], out2, state, lines, torch.zeros(hv, device=cuda), torch.zeros(hv, device=cuda),
+             bf(torch.ones(d, device=cuda)), 2, hk, hv, d, d, 0, hv * d, hv * d + hv, lb, s_off)
     torch.cuda.synchronize()
     assert bool((state == 0x3c).all())
+    torch.testing.assert_close(out2.float(), out.float(), rtol=2e-2, atol=2e-2)
     yr, _ = gdn.conv_ref(x[:1, :conv_dim].float(), torch.zeros(width - 1, conv_dim, device=cuda), w)
     torch.testing.assert_close(y[:1].float(), yr, rtol=2e-2, atol=2e-2)
     assert bool(torch.isfinite(out.float()).all())
