@@ -119,3 +119,59 @@ def rule_ref(q, k, v, z, b, a, S, A_log, dt_bias, norm_w, eps=1e-6, normalize=Tr
 def gate_norm_ref(o, z, norm_w, eps=1e-6):
     o = o.float()
     return o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float() * F.silu(z.float())
+
+
+# ---- chunked (WY) form of the rule: the statement of the two prefill kernels --------------------------------
+CHUNK = 64
+
+
+def chunk_prep_ref(q, k, v, b, a, A_log, dt_bias):
+    """Per chunk of 64 tokens of one sequence, everything that does not depend on the carried state.
+    q,k [T, HK, D]; v [T, HV, D]; b,a [T, HV]. Returns W, Qg, Kd, Ut [T, HV, D], M [T, HV, 64], gC [T, HV]:
+      g   = inclusive cumulative log decay inside the chunk
+      L   = beta_i exp(g_i - g_j) (k_i.k_j) for j < i;   T = (I + L)^-1
+      W   = T (beta exp(g) K);  Ut = T (beta V);  Qg = exp(g) q;  Kd = exp(g_last - g) k
+      M   = exp(g_i - g_j) (q_i.k_j) for j <= i;  gC = exp(g_last)
+    so that with the chunk's incoming state S0:  U = Ut - W S0^T,  O = Qg S0^T + M U,  S1 = gC S0 + U^T Kd."""
+    T_, hk, d = q.shape
+    hv = v.shape[1]
+    rep = hv // hk
+    qn = q.float() * torch.rsqrt(q.float().pow(2).sum(-1, keepdim=True) + 1e-6) / d ** 0.5
+    kn = k.float() * torch.rsqrt(k.float().pow(2).sum(-1, keepdim=True) + 1e-6)
+    qn, kn = qn.repeat_interleave(rep, 1), kn.repeat_interleave(rep, 1)          # [T, HV, D]
+    ga = -torch.exp(A_log.float()) * F.softplus(a.float() + dt_bias.float())     # [T, HV] log decay
+    beta = torch.sigmoid(b.float()).to(torch.bfloat16).float()
+    W, Qg, Kd, Ut = (torch.zeros(T_, hv, d, device=q.device) for _ in range(4))
+    M = torch.zeros(T_, hv, CHUNK, device=q.device)
+    gC = torch.zeros(T_, hv, device=q.device)
+    for c0 in range(0, T_, CHUNK):
+        n = min(CHUNK, T_ - c0)
+        sl = slice(c0, c0 + n)
+        g = ga[sl].cumsum(0)                                                      # [n, HV]
+        kk = torch.einsum("ihd,jhd->hij", kn[sl], kn[sl])
+        qk = torch.einsum("ihd,jhd->hij", qn[sl], kn[sl])
+        e = torch.exp((g.t()[:, :, None] - g.t()[:, None, :]).clamp(max=0.0))     # [HV, i, j]; only j <= i is used
+        low = torch.tril(torch.ones(n, n, device=q.device), -1)
+        L = beta[sl].t()[:, :, None] * e * kk * low
+        Tm = torch.linalg.inv(torch.eye(n, device=q.device) + L)                  # unit lower triangular
+        W[sl] = torch.einsum("hij,jhd->ihd", Tm, (beta[sl] * torch.exp(g))[:, :, None] * kn[sl])
+        Ut[sl] = torch.einsum("hij,jhd->ihd", Tm, beta[sl][:, :, None] * v[sl].float())
+        Qg[sl] = torch.exp(g)[:, :, None] * qn[sl]
+        Kd[sl] = torch.exp(g[-1][None] - g)[:, :, None] * kn[sl]
+        M[sl, :, :n] = (e * qk * torch.tril(torch.ones(n, n, device=q.device))).permute(1, 0, 2)
+        gC[sl] = torch.exp(g[-1])[None]
+    return W, Qg, Kd, Ut, M, gC
+
+
+def chunk_rule_ref(W, Qg, Kd, Ut, M, gC, S):
+    """The state-dependent half: one pass over the chunks of one sequence. S [HV, DV, DK] f32. Returns (o [T, HV, DV], S)."""
+    T_, hv, d = W.shape
+    S = S.float().clone()
+    out = torch.empty(T_, hv, d, dtype=torch.float32, device=W.device)
+    for c0 in range(0, T_, CHUNK):
+        n = min(CHUNK, T_ - c0)
+        sl = slice(c0, c0 + n)
+        U = Ut[sl] - torch.einsum("ihk,hvk->ihv", W[sl], S)
+        out[sl] = torch.einsum("ihk,hvk->ihv", Qg[sl], S) + torch.einsum("ihj,jhv->ihv", M[sl, :, :n], U)
+        S = gC[c0][:, None, None] * S + torch.einsum("ihv,ihk->hvk", U, Kd[sl])
+    return out, S
