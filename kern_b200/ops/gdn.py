@@ -80,6 +80,42 @@ def step(qkv, zba, out, state, lines, A_log, dt_bias, norm_w, seqs, hk, hv, dk, 
     return out
 
 
+CHUNK_PREP_SMEM = (2 * 64 * 132 + 64 * 68 + 2 * 64) * 4
+CHUNK_RULE_SMEM = (64 * 132 * 3 + 64 * 136 + 64 * 68 + 2 * 64 * 72) * 4
+
+
+def chunk_scratch(tokens: int, hv: int, device) -> dict:
+    """Scratch of the chunked rule: W, Qg, Kd, Ut [tokens, HV, 128], M [tokens, HV, 64], gC [tokens, HV], all f32."""
+    big = lambda: torch.empty(tokens, hv, 128, dtype=torch.float32, device=device)
+    return {"W": big(), "Qg": big(), "Kd": big(), "Ut": big(),
+            "M": torch.empty(tokens, hv, 64, dtype=torch.float32, device=device),
+            "gC": torch.empty(tokens, hv, dtype=torch.float32, device=device)}
+
+
+def rule_chunked(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv, z_off, b_off, a_off,
+                 line_b, s_off, eps=1e-6, o_raw=None, scratch=None):
+    """Prefill rows through the chunked (WY) form: a parallel launch over (64-token chunk, head) prepares the
+    state-independent factors on the tensor cores, a second launch walks the chunks with the state on chip, then the
+    gated RMSNorm. dk = dv = 128 only."""
+    k = Kernels.get(qkv.device)
+    assert dk == dv == 128 and cu_q is not None
+    tokens = out.shape[0]
+    if o_raw is None:
+        o_raw = torch.empty(tokens, hv * dv, dtype=torch.float32, device=qkv.device)
+    sc = scratch if scratch is not None else chunk_scratch(tokens, hv, qkv.device)
+    k.launch("gdn_chunk", "kern_gdn_chunk_prep_k128_v128", ((tokens + 63) // 64 + seqs, hv), (256,),
+             [ptr(qkv), ptr(zba), ptr(cu_q), ptr(A_log), ptr(dt_bias), ptr(sc["W"]), ptr(sc["Qg"]), ptr(sc["Kd"]),
+              ptr(sc["Ut"]), ptr(sc["M"]), ptr(sc["gC"]), i32(seqs), i32(hk), i32(hv), i32(zba.stride(0)), i32(b_off),
+              i32(a_off)], shared_mem=CHUNK_PREP_SMEM)
+    k.launch("gdn_chunk", "kern_gdn_chunk_rule_k128_v128", (hv * 2, seqs), (256,),
+             [ptr(sc["W"]), ptr(sc["Qg"]), ptr(sc["Kd"]), ptr(sc["Ut"]), ptr(sc["M"]), ptr(sc["gC"]), ptr(o_raw), ptr(state),
+              ptr(lines), ptr(cu_q), i32(seqs), i32(hv), i64(line_b), i64(s_off)], shared_mem=CHUNK_RULE_SMEM)
+    k.launch("gdn", "kern_gdn_gate_norm_bf16", (tokens, hv), (128,),
+             [ptr(o_raw), ptr(zba), ptr(out), ptr(norm_w), i32(tokens), i32(hv), i32(dv), i32(zba.stride(0)),
+              i32(z_off), f32(eps)])
+    return out
+
+
 # ---- fp32 statement ------------------------------------------------------------------------------------
 def conv_ref(x, window, w, bias=None):
     """x: [T, C] f32 rows of one sequence, window: [width-1, C] (history, oldest first), w: [C, width].

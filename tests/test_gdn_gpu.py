@@ -104,3 +104,50 @@ def test_gdn_null_line_is_read_as_zero_and_never_written(cuda):
     yr, _ = gdn.conv_ref(x[:1, :conv_dim].float(), torch.zeros(width - 1, conv_dim, device=cuda), w)
     torch.testing.assert_close(y[:1].float(), yr, rtol=2e-2, atol=2e-2)
     assert bool(torch.isfinite(out.float()).all())
+
+
+def test_gdn_chunked_prefill_matches_the_statement(cuda):
+    """The chunked (WY) prefill path against the sequential fp32 statement: ragged lengths around the 64-token chunk,
+    a non-zero incoming state, then the sequential kernel continues from the state the chunked one left."""
+    from kern_b200.ops import gdn
+    from kern_b200.ops.launcher import Kernels
+
+    torch.manual_seed(7)
+    hk, hv, d, width = 2, 6, 128, 4
+    conv_dim = 2 * hk * d + hv * d
+    x_stride = conv_dim + hv * d + 2 * hv
+    lb, s_off = gdn.line_bytes(hk, hv, d, d, width)
+    lens = [200, 64, 1, 65]
+    seqs = len(lens)
+    state = torch.zeros(seqs + 2, lb, dtype=torch.uint8, device=cuda)
+    lines = torch.tensor([2, 4, 1, 5], dtype=torch.int32, device=cuda)
+    S0 = [torch.randn(hv, d, d, device=cuda) * 0.2 for _ in lens]
+    for s, ln in enumerate(lines.tolist()):
+        state[ln, s_off:].view(torch.float32).view(hv, d, d).copy_(S0[s])
+    A_log = torch.randn(hv, device=cuda) * 0.5
+    dt_bias = torch.randn(hv, device=cuda) * 0.5
+    norm_w = bf(1 + 0.1 * torch.randn(d, device=cuda))
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=cuda)
+    x = bf(torch.randn(T, x_stride, device=cuda))
+    y = x[:, :conv_dim].contiguous()            # the rule reads post-conv rows; any bf16 rows serve here
+    out = torch.empty(T, hv * d, dtype=torch.bfloat16, device=cuda)
+    gdn.rule_chunked(y, x[:, conv_dim:], out, state, lines, cu, A_log, dt_bias, norm_w, seqs, hk, hv, d, d,
+                     0, hv * d, hv * d + hv, lb, s_off)
+    torch.cuda.synchronize()
+    Kernels.get(cuda).check_error()
+    for s, n in enumerate(lens):
+        r0 = int(cu[s])
+        yb, xs = y[r0:r0 + n].float(), x[r0:r0 + n].float()
+        q = yb[:, :hk * d].view(n, hk, d)
+        k = yb[:, hk * d:2 * hk * d].view(n, hk, d)
+        v = yb[:, 2 * hk * d:].view(n, hv, d)
+        z = xs[:, conv_dim:conv_dim + hv * d].view(n, hv, d)
+        b = xs[:, conv_dim + hv * d:conv_dim + hv * d + hv]
+        a = xs[:, conv_dim + hv * d + hv:]
+        o, S1 = gdn.rule_ref(q, k, v, z, b, a, S0[s], A_log, dt_bias, norm_w)
+        torch.testing.assert_close(out[r0:r0 + n].float().view(n, hv, d), o, rtol=3e-2, atol=3e-2)
+        S_dev = state[int(lines[s]), s_off:].view(torch.float32).view(hv, d, d)
+        # tf32 products (10-bit mantissa operands, f32 accumulation) against the all-f32 statement
+        torch.testing.assert_close(S_dev, S1, rtol=5e-3, atol=5e-3)
+    assert int(state[0].count_nonzero()) == 0 and int(state[3].count_nonzero()) == 0
