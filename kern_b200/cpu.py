@@ -289,6 +289,45 @@ def _gdn_step(dim):
     return run
 
 
+def k_gdn_chunk_prep(g, qkv, zba, cu, A_log, dt_bias, Wg, Qg, Kg, Ug, Mg, Gg, seqs, hk, hv, zba_stride, b_off, a_off):
+    from .ops import gdn as G
+
+    dim = 128
+    conv_dim = 2 * hk * dim + hv * dim
+    for s in range(seqs):
+        r0, r1 = _rows_of(cu, s)
+        n = r1 - r0
+        if n <= 0:
+            continue
+        rows = _f(qkv[r0 * conv_dim: r1 * conv_dim].view(n, conv_dim))
+        zr = _f(torch.as_strided(zba, (n, a_off + hv), (zba_stride, 1), zba.storage_offset() + r0 * zba_stride))
+        q = rows[:, :hk * dim].view(n, hk, dim)
+        k = rows[:, hk * dim:2 * hk * dim].view(n, hk, dim)
+        v = rows[:, 2 * hk * dim:].view(n, hv, dim)
+        parts = G.chunk_prep_ref(q, k, v, zr[:, b_off:b_off + hv], zr[:, a_off:a_off + hv], A_log[:hv], dt_bias[:hv])
+        for dst, src, w in zip((Wg, Qg, Kg, Ug, Mg, Gg), parts, (dim, dim, dim, dim, 64, 1)):
+            dst[r0 * hv * w: r1 * hv * w] = src.reshape(-1)
+
+
+def k_gdn_chunk_rule(g, Wg, Qg, Kg, Ug, Mg, Gg, o_raw, state, lines, cu, seqs, hv, line_bytes, s_off):
+    from .ops import gdn as G
+
+    dim = 128
+    for s in range(seqs):
+        r0, r1 = _rows_of(cu, s)
+        n = r1 - r0
+        if n <= 0:
+            continue
+        ln = int(lines[s])
+        Sb = state[ln * line_bytes + s_off: ln * line_bytes + s_off + hv * dim * dim * 4].view(torch.float32).view(hv, dim, dim)
+        S0 = Sb.clone() if ln > 0 else torch.zeros(hv, dim, dim)
+        cut = lambda t, w: t[r0 * hv * w: r1 * hv * w].view(n, hv, w) if w > 1 else t[r0 * hv: r1 * hv].view(n, hv)
+        o, S1 = G.chunk_rule_ref(cut(Wg, dim), cut(Qg, dim), cut(Kg, dim), cut(Ug, dim), cut(Mg, 64), cut(Gg, 1), S0)
+        o_raw[r0 * hv * dim: r1 * hv * dim] = o.reshape(-1)
+        if ln > 0:
+            Sb.copy_(S1)
+
+
 def k_gdn_gate_norm(g, o_raw, zba, out, norm_w, tokens, hv, dv, zba_stride, z_off, eps):
     from .ops import gdn as G
 
@@ -323,6 +362,7 @@ CPU_KERNELS = {
     "kern_gdn_conv_bf16": k_gdn_conv, "kern_gdn_conv_state": k_gdn_conv_state, "kern_gdn_rule_k128_v128": _gdn_rule(128), "kern_gdn_rule_k64_v64": _gdn_rule(64),
     "kern_gdn_rule_k32_v32": _gdn_rule(32), "kern_gdn_gate_norm_bf16": k_gdn_gate_norm,
     "kern_gdn_step_k128_v128": _gdn_step(128), "kern_gdn_step_k64_v64": _gdn_step(64), "kern_gdn_step_k32_v32": _gdn_step(32),
+    "kern_gdn_chunk_prep_k128_v128": k_gdn_chunk_prep, "kern_gdn_chunk_rule_k128_v128": k_gdn_chunk_rule,
     "kern_gdn_rule_dec_k128_v128": _gdn_rule(128), "kern_gdn_rule_dec_k64_v64": _gdn_rule(64), "kern_gdn_rule_dec_k32_v32": _gdn_rule(32),
     "kern_fill_f32": k_fill, "kern_fill_i32": k_fill, "kern_fill_i64": k_fill, "kern_fill_u8": k_fill,
 }

@@ -609,10 +609,11 @@ def gdn_conv_op(conv_dim: int, width: int, x_stride: int, line_bytes: int, ragge
 
 
 def gdn_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_off: int, eps: float,
-                ragged: bool) -> dict:
+                ragged: bool, chunked: bool = True) -> dict:
     """Gated delta rule (value rows split over CTAs) + gated RMSNorm.
-    Interface [qkv, zba, out, state, lines, (cu_seqlens,) A_log, dt_bias, norm_w]; `zba` points at the z|b|a columns
-    of the projection's row."""
+    Interface [qkv, zba, out, state, lines, A_log, dt_bias, norm_w] for one row per sequence (the fused step), or
+    [qkv, zba, out, state, lines, cu_seqlens, A_log, dt_bias, norm_w, seqs] for ragged rows; `zba` points at the z|b|a
+    columns of the projection's row. Ragged rows of 128-wide heads take the chunked (WY) pair of launches."""
     iface = ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "inout state", "in buffer<i32>"]
     if not ragged:
         # one row per sequence: the fused step (state by bulk copy, rule, gated norm) in one launch
@@ -628,22 +629,46 @@ def gdn_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_
     iface.append("in buffer<i32>")
     at = len(iface)
     tb = 32 if ragged else 1          # tokens staged per pass
-    iface += ["in buffer<f32>", "in buffer<f32>", "in buffer<bf16>"]
+    iface += ["in buffer<f32>", "in buffer<f32>", "in buffer<bf16>", "i32"]      # ..., A_log, dt_bias, norm_w, seqs
     lp = ["in buffer<bf16>", "in buffer<bf16>", "out buffer<f32>", "inout state", "in buffer<i32>",
           "in buffer<i32>" if ragged else "i64", "in buffer<f32>", "in buffer<f32>"] + ["i32"] * 6 + ["i64", "i64", "i32"]
     args = [{"param": 0}, {"param": 1}, {"scratch": "o_raw"}, {"param": 3}, {"param": 4},
-            {"param": 5} if ragged else {"i64": 0}, {"param": at}, {"param": at + 1}, {"i32": I32_MAX}, {"i32": hk},
+            {"param": 5} if ragged else {"i64": 0}, {"param": at}, {"param": at + 1}, {"param": at + 3}, {"i32": hk},
             {"i32": hv}, {"i32": zba_stride}, {"i32": hv * dim}, {"i32": hv * dim + hv}, {"i64": line_bytes}, {"i64": s_off},
             {"i32": tb}]
-    rows_cta = 16          # value rows per CTA
-    rule = {"module": "gdn", "entry": f"kern_gdn_rule_{'' if ragged else 'dec_'}k{dim}_v{dim}", "block": [256, 1, 1],
-            "grid": [hv * (dim // rows_cta), "seqs", 1], "shared_mem": tb * (2 * dim + rows_cta + 4) * 4, "params": lp,
-            "args": args}
     norm = {"module": "gdn", "entry": "kern_gdn_gate_norm_bf16", "block": [128, 1, 1], "grid": ["tokens", hv, 1],
             "params": ["in buffer<f32>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<bf16>", "i32", "i32", "i32", "i32",
                        "i32", "f32"],
             "args": [{"scratch": "o_raw"}, {"param": 1}, {"param": 2}, {"param": at + 2}, {"i32": I32_MAX}, {"i32": hv},
                      {"i32": dim}, {"i32": zba_stride}, {"i32": 0}, {"f32": eps}]}
+    if chunked and dim == 128:
+        # prefill rows in the chunked (WY) form: factors per (64-token chunk, head) on the tensor cores, then one pass
+        # over the chunks with the state on chip
+        names = ["gw", "gq", "gk", "gu", "gm", "gc"]
+        sc = [{"scratch": n} for n in names]
+        prep = {"module": "gdn_chunk", "entry": "kern_gdn_chunk_prep_k128_v128", "block": [256, 1, 1],
+                "grid": [{"add": [{"ceil_div": ["tokens", 64]}, "seqs"]}, hv, 1],
+                "shared_mem": (2 * 64 * 132 + 64 * 68 + 2 * 64) * 4,
+                "params": ["in buffer<bf16>", "in buffer<bf16>", "in buffer<i32>", "in buffer<f32>", "in buffer<f32>"] +
+                          ["out buffer<f32>"] * 6 + ["i32"] * 6,
+                "args": [{"param": 0}, {"param": 1}, {"param": 5}, {"param": at}, {"param": at + 1}, *sc,
+                         {"param": at + 3}, {"i32": hk}, {"i32": hv}, {"i32": zba_stride}, {"i32": hv * dim},
+                         {"i32": hv * dim + hv}]}
+        walk = {"module": "gdn_chunk", "entry": "kern_gdn_chunk_rule_k128_v128", "block": [256, 1, 1],
+                "grid": [hv * 2, "seqs", 1], "shared_mem": (64 * 132 * 3 + 64 * 136 + 64 * 68 + 2 * 64 * 72) * 4,
+                "params": ["in buffer<f32>"] * 6 + ["out buffer<f32>", "inout state", "in buffer<i32>", "in buffer<i32>",
+                                                    "i32", "i32", "i64", "i64"],
+                "args": [*sc, {"scratch": "o_raw"}, {"param": 3}, {"param": 4}, {"param": 5}, {"param": at + 3}, {"i32": hv},
+                         {"i64": line_bytes}, {"i64": s_off}]}
+        scratch = {n: {"dtype": "f32", "shape": ["tokens", hv * 128]} for n in names[:4]}
+        scratch["gm"] = {"dtype": "f32", "shape": ["tokens", hv * 64]}
+        scratch["gc"] = {"dtype": "f32", "shape": ["tokens", hv]}
+        scratch["o_raw"] = {"dtype": "f32", "shape": ["tokens", hv * dim]}
+        return {"params": iface, "impl": {"launches": [prep, walk, norm], "scratch": scratch}}
+    rows_cta = 16          # value rows per CTA
+    rule = {"module": "gdn", "entry": f"kern_gdn_rule_{'' if ragged else 'dec_'}k{dim}_v{dim}", "block": [256, 1, 1],
+            "grid": [hv * (dim // rows_cta), "seqs", 1], "shared_mem": tb * (2 * dim + rows_cta + 4) * 4, "params": lp,
+            "args": args}
     return {"params": iface, "impl": {"launches": [rule, norm],
                                       "scratch": {"o_raw": {"dtype": "f32", "shape": ["tokens", hv * dim]}}}}
 

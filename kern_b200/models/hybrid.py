@@ -90,6 +90,10 @@ TOY_HYBRID = HybridConfig(name="toy-hybrid", vocab=256, hidden=64, layers=4, ful
 TINY_HYBRID = HybridConfig(name="tiny-hybrid", vocab=512, hidden=256, layers=4, full_every=2, heads=4, kv_heads=2,
                            head_dim=64, rot_dim=32, gdn_k_heads=2, gdn_v_heads=4, gdn_dim=64, intermediate=512,
                            rope_theta=10000.0, page_size=16, max_tokens=256, max_seqs=8, max_context=256)
+# GDN heads of 128, the size whose prefill runs through the chunked (WY) kernels
+TINY_HYBRID_K128 = HybridConfig(name="tiny-hybrid-k128", vocab=512, hidden=256, layers=2, full_every=2, heads=4, kv_heads=2,
+                                head_dim=64, rot_dim=32, gdn_k_heads=2, gdn_v_heads=4, gdn_dim=128, intermediate=512,
+                                rope_theta=10000.0, page_size=16, max_tokens=256, max_seqs=8, max_context=256)
 HYBRID_27B = HybridConfig(name="hybrid-27b")
 
 
@@ -292,7 +296,7 @@ def build_manifest(cfg: HybridConfig) -> dict:
             {"op": "gdn_conv" + sfx, "label": lbl + "conv", "args": [B("gin"), B("gconv"), st, B("lines"), *cu, B(f"w.l{i}.conv"), {"var": "seqs"}, {"var": "tokens"}]},
             {"op": "gdn_rule" + sfx, "label": lbl + "rule",
              "args": [B("gconv"), B("gin", cfg.conv_dim * 2), B("gout"), st, B("lines"), *cu, B(f"w.l{i}.alog"),
-                      B(f"w.l{i}.dtb"), B(f"w.l{i}.gnorm")]},
+                      B(f"w.l{i}.dtb"), B(f"w.l{i}.gnorm"), *([{"var": "seqs"}] if prefill else [])]},
             {"op": "gdn_out", "label": lbl + "gdn_out", "args": [B("gout"), B(f"w.l{i}.gout"), B("x"), {"var": "tokens"}, err]},
         ]
         return calls + mlp(i, lbl)
@@ -320,6 +324,8 @@ def build_manifest(cfg: HybridConfig) -> dict:
     prefill += [{"op": "last_row", "label": "last_row", "args": [B("x"), B("last"), B("cu_seqlens")]}] + head("last")
     decode += head("x")
     mods = ["norm_embed", "gemm_bf16", "attn_prep", "attn_paged", "misc", "sampling", "gdn"]
+    if gd == 128:
+        mods.append("gdn_chunk")      # prefill rows of 128-wide heads run the chunked (WY) kernels
     return {
         "schema_version": 7, "model": cfg.name,
         "vars": {"tokens": {"max": T, "axis": "rows"}, "seqs": {"max": S, "axis": "groups"}},

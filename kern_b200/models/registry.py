@@ -13,7 +13,7 @@ def families() -> dict:
     out = {}
     for cfg in (dense.TOY, dense.TINY, dense.DENSE_8B):
         out[cfg.name] = (cfg, dense.build_manifest, dense.load_random_weights, dense.random_weights)
-    for cfg in (hybrid.TOY_HYBRID, hybrid.TINY_HYBRID, hybrid.HYBRID_27B):
+    for cfg in (hybrid.TOY_HYBRID, hybrid.TINY_HYBRID, hybrid.TINY_HYBRID_K128, hybrid.HYBRID_27B):
         out[cfg.name] = (cfg, hybrid.build_manifest, hybrid.load_random_weights, hybrid.random_weights)
     for cfg in (moe.TOY_MOE, moe.TINY_MOE, moe.MOE_30B):
         out[cfg.name] = (cfg, moe.build_manifest, moe.load_random_weights, moe.random_weights)

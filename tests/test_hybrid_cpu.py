@@ -51,6 +51,29 @@ def test_prefill_and_decode_match_oracle():
     assert worst < 0.12, worst
 
 
+def test_chunked_rule_statement_through_the_manifest():
+    """GDN heads of 128: the prefill program runs the chunked (WY) pair of launches; prompts longer than one 64-token
+    chunk, then decode steps through the fused step, against the oracle's token-by-token rule."""
+    cfg, w, rt, eng, oracle = make(hybrid.TINY_HYBRID_K128)
+    entries = {l["entry"] for op in hybrid.build_manifest(cfg)["ops"].values() for l in op.get("impl", {}).get("launches", [])}
+    assert {"kern_gdn_chunk_prep_k128_v128", "kern_gdn_chunk_rule_k128_v128", "kern_gdn_step_k128_v128"} <= entries
+    torch.manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (150, 5)]
+    seqs = [eng.open(160), eng.open(16)]
+    caches = [oracle.new_cache() for _ in prompts]
+    first = eng.step(list(zip(seqs, prompts)))
+    logits = rt.tensor("logits")[:2].float()
+    worst = max(float((logits[i] - oracle.forward(p, c)[-1]).abs().max()) for i, (p, c) in enumerate(zip(prompts, caches)))
+    toks = [f[0] for f in first]
+    for _ in range(2):
+        refs = [oracle.forward([t], c)[-1] for t, c in zip(toks, caches)]
+        nxt = eng.step([(s, [t]) for s, t in zip(seqs, toks)])
+        logits = rt.tensor("logits")[:2].float()
+        worst = max(worst, max(float((logits[i] - refs[i]).abs().max()) for i in range(2)))
+        toks = [n[0] for n in nxt]
+    assert worst < 0.2, worst
+
+
 def test_chunked_prefill_equals_one_shot():
     cfg, w, rt, eng, oracle = make()
     torch.manual_seed(1)

@@ -75,3 +75,42 @@ def test_hybrid_chunked_prefill_equals_one_shot(tiny):
     assert one == two
     eng.close(a)
     eng.close(b)
+
+
+def test_hybrid_k128_chunked_prefill_and_fused_step(cuda):
+    """GDN heads of 128: prefill through the chunked (WY) kernels (prompts longer than one 64-token chunk), decode
+    through the fused step, against the fp32 oracle's token-by-token rule."""
+    from kern_b200.engine import Engine
+    from kern_b200.models import hybrid
+    from kern_b200.runtime import Runtime
+
+    cfg = hybrid.TINY_HYBRID_K128
+    weights = hybrid.random_weights(cfg, seed=0, std=0.05)
+    rt = Runtime(hybrid.build_manifest(cfg), tokens=cfg.page_size * 64, slots=8)
+    rt.load_tensors(lambda name: weights[name].cuda())
+    rt.once()
+    eng = Engine(rt)
+    oracle = hybrid.HybridOracle(cfg, weights, device="cuda")
+    torch.manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (150, 5, 64)]
+    seqs = [eng.open(200) for _ in prompts]
+    caches = [oracle.new_cache() for _ in prompts]
+    first = eng.step(list(zip(seqs, prompts)))
+    logits = rt.tensor("logits")[:3].float()
+    worst, means = 0.0, []
+    for i, (p, c) in enumerate(zip(prompts, caches)):
+        diff = (logits[i] - oracle.forward(p, c)[-1]).abs()
+        worst = max(worst, float(diff.max()))
+        means.append(float(diff.mean()))
+    toks = [f[0] for f in first]
+    for _ in range(4):
+        refs = [oracle.forward([t], c)[-1] for t, c in zip(toks, caches)]
+        nxt = eng.step([(s, [t]) for s, t in zip(seqs, toks)])
+        logits = rt.tensor("logits")[:3].float()
+        for i in range(3):
+            diff = (logits[i] - refs[i]).abs()
+            worst = max(worst, float(diff.max()))
+            means.append(float(diff.mean()))
+        toks = [n[0] for n in nxt]
+    rt.check_error()
+    assert worst < 0.35 and max(means) < 0.06, (worst, max(means))
