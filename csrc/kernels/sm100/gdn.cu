@@ -18,8 +18,8 @@ using namespace kern;
 // x: [tokens][x_stride] (the q|k|v channels are the first conv_dim of a row), y: [tokens][conv_dim]
 // w: [conv_dim][width] bf16, bias optional. cu_q: [seqs+1] row starts (nullptr: one row per sequence).
 // Every output row depends on at most width-1 earlier inputs, so rows are independent: grid
-// [ceil(rows / rpc), ceil(conv_dim / 256)], block 256; a thread owns one channel and walks rpc consecutive rows
-// (16 for prefill chunks, 1 for decode rows),
+// [ceil(rows / rpc), ceil(conv_dim / 1024)], block 256; a thread owns four adjacent channels (8-byte loads and stores;
+// conv_dim is a multiple of 4) and walks rpc consecutive rows (16 for prefill chunks, 1 for decode rows),
 // carrying the last inputs in registers and re-seeding them from the state window at a sequence's first row.
 // The window itself is advanced afterwards by kern_gdn_conv_state (a separate launch: rows of one sequence may sit
 // in several CTAs, and none of them may see the window half-updated).
@@ -28,13 +28,22 @@ extern "C" __global__ void __launch_bounds__(256)
                        const __nv_bfloat16* w, const __nv_bfloat16* bias, int seqs, int rows, int conv_dim, int width,
                        int x_stride, long long line_bytes, int rpc) {
   pdl_wait();
-  const int c = blockIdx.y * 256 + threadIdx.x;
+  const int c = (blockIdx.y * 256 + threadIdx.x) * 4;
   const int total = cu_q ? min(rows, cu_q[seqs]) : min(rows, seqs);
   const int ra = blockIdx.x * rpc, rb = min(total, ra + rpc);
   if (c >= conv_dim || ra >= rb) return;
-  float wt[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int j = 0; j < width; ++j) wt[j] = __bfloat162float(w[(size_t)c * width + j]);
-  const float bs = bias ? __bfloat162float(bias[c]) : 0.f;
+  auto load4 = [](const __nv_bfloat16* p, float (&o)[4]) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+    o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+  };
+  float wt[4][4];      // [channel][tap], right-aligned: tap 3 multiplies the current row, tap 2 the row before, ...
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) wt[i][j] = j >= 4 - width ? __bfloat162float(w[(size_t)(c + i) * width + j - (4 - width)]) : 0.f;
+  float bs[4] = {0.f, 0.f, 0.f, 0.f};
+  if (bias) load4(bias + c, bs);
   // the sequence of row ra: the last s with cu_q[s] <= ra
   int s = ra;
   if (cu_q) {
@@ -46,16 +55,23 @@ extern "C" __global__ void __launch_bounds__(256)
     s = lo;
   }
   int r0 = cu_q ? cu_q[s] : s, r1 = cu_q ? cu_q[s + 1] : s + 1;
-  float hist[3] = {0.f, 0.f, 0.f};     // inputs r-3, r-2, r-1 (only the last width-1 matter)
+  float hist[3][4];     // inputs r-3, r-2, r-1 (only the last width-1 matter)
+#pragma unroll
+  for (int d = 0; d < 3; ++d)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) hist[d][i] = 0.f;
   auto seed = [&](int r) {
     const int line = lines[s];
     const __nv_bfloat16* win = reinterpret_cast<const __nv_bfloat16*>(state + (size_t)line * line_bytes);
-    for (int d = 1; d <= width - 1; ++d) {
+#pragma unroll
+    for (int d = 1; d <= 3; ++d) {
+      if (d > width - 1) continue;
       const int rr = r - d;
-      float v;
-      if (rr >= r0) v = __bfloat162float(x[(size_t)rr * x_stride + c]);
-      else v = line > 0 ? __bfloat162float(win[(size_t)(width - 1 - (r0 - rr)) * conv_dim + c]) : 0.f;
-      hist[3 - d] = v;
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (rr >= r0) load4(x + (size_t)rr * x_stride + c, v);
+      else if (line > 0) load4(win + (size_t)(width - 1 - (r0 - rr)) * conv_dim + c, v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) hist[3 - d][i] = v[i];
     }
   };
   seed(ra);
@@ -66,11 +82,15 @@ extern "C" __global__ void __launch_bounds__(256)
       r1 = cu_q ? cu_q[s + 1] : s + 1;
       if (r < r1) seed(r);
     }
-    const float cur = __bfloat162float(x[(size_t)r * x_stride + c]);
-    float acc = bs + wt[width - 1] * cur;
-    for (int j = 0; j < width - 1; ++j) acc += wt[j] * hist[3 - (width - 1) + j];
-    y[(size_t)r * conv_dim + c] = __float2bfloat16(silu(acc));
-    hist[0] = hist[1]; hist[1] = hist[2]; hist[2] = cur;
+    float cur[4], o[4];
+    load4(x + (size_t)r * x_stride + c, cur);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float acc = bs[i] + wt[i][3] * cur[i] + wt[i][2] * hist[2][i] + wt[i][1] * hist[1][i] + wt[i][0] * hist[0][i];
+      o[i] = silu(acc);
+      hist[0][i] = hist[1][i]; hist[1][i] = hist[2][i]; hist[2][i] = cur[i];
+    }
+    *reinterpret_cast<uint2*>(y + (size_t)r * conv_dim + c) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
   }
 }
 
@@ -265,24 +285,40 @@ KERN_GDN_ENTRY(kern_gdn_rule_dec_k128_v128, 128, 128, 16)
 KERN_GDN_ENTRY(kern_gdn_rule_dec_k64_v64, 64, 64, 16)
 KERN_GDN_ENTRY(kern_gdn_rule_dec_k32_v32, 32, 32, 16)
 
-// y = rmsnorm(o) * w * silu(z) per (token, value head): grid [tokens, HV], block 128 (dv <= 128 * 8).
+// y = rmsnorm(o) * w * silu(z) per (token, value head): a warp per row of dv values (dv a multiple of 32, at most
+// 256), grid [ceil(HV / 4), tokens], block 128.
 extern "C" __global__ void __launch_bounds__(128)
     kern_gdn_gate_norm_bf16(const float* o_raw, const __nv_bfloat16* zba, __nv_bfloat16* out, const __nv_bfloat16* norm_w,
                             int tokens, int hv, int dv, int zba_stride, int z_off, float eps) {
   pdl_wait();
-  __shared__ float red[4];
-  const int t = blockIdx.x, h = blockIdx.y;
-  if (t >= tokens) return;
+  const int t = blockIdx.y, h = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= tokens || h >= hv) return;
   const float* o = o_raw + ((size_t)t * hv + h) * dv;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < dv; i += 128) ss += o[i] * o[i];
-  ss = warp_sum(ss);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  const float inv = rsqrtf((red[0] + red[1] + red[2] + red[3]) / (float)dv + eps);
-  for (int i = threadIdx.x; i < dv; i += 128) {
-    const float z = __bfloat162float(zba[(size_t)t * zba_stride + z_off + h * dv + i]);
-    out[((size_t)t * hv + h) * dv + i] = __float2bfloat16(o[i] * inv * __bfloat162float(norm_w[i]) * silu(z));
+  const __nv_bfloat16* z = zba + (size_t)t * zba_stride + z_off + h * dv;
+  __nv_bfloat16* y = out + ((size_t)t * hv + h) * dv;
+  if (dv == 128) {      // 16-byte loads of o, 8-byte loads of z and the weight
+    const float4 v = *reinterpret_cast<const float4*>(o + lane * 4);
+    const uint2 zu = *reinterpret_cast<const uint2*>(z + lane * 4);
+    const uint2 wu = *reinterpret_cast<const uint2*>(norm_w + lane * 4);
+    const float inv = rsqrtf(warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w) / 128.f + eps);
+    const float2 z01 = unpack_bf16x2(zu.x), z23 = unpack_bf16x2(zu.y), w01 = unpack_bf16x2(wu.x), w23 = unpack_bf16x2(wu.y);
+    *reinterpret_cast<uint2*>(y + lane * 4) =
+        make_uint2(pack_bf16x2(v.x * inv * w01.x * silu(z01.x), v.y * inv * w01.y * silu(z01.y)),
+                   pack_bf16x2(v.z * inv * w23.x * silu(z23.x), v.w * inv * w23.y * silu(z23.y)));
+    return;
+  }
+  float ov[8], ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = i * 32 + lane;
+    ov[i] = c < dv ? o[c] : 0.f;
+    ss += ov[i] * ov[i];
+  }
+  const float inv = rsqrtf(warp_sum(ss) / (float)dv + eps);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = i * 32 + lane;
+    if (c < dv) y[c] = __float2bfloat16(ov[i] * inv * __bfloat162float(norm_w[c]) * silu(__bfloat162float(z[c])));
   }
 }
 

@@ -118,6 +118,39 @@ void Runtime::compile_call(CompiledProgram& out, const std::string& pname, const
       }
     };
 
+    if (l.is_extern && parse_nccl_extern(l.entry, &cl.coll, &cl.elem)) {
+      // [send, recv, count, rank]: count in elements per rank (the block an all-gather sends and a reduce-scatter
+      // receives; per peer for an all-to-all); the rank arg names the group whose communicator carries the call
+      if (largs.size() != 4) throw std::runtime_error(where + ": a collective built-in takes [send, recv, count, rank]");
+      auto ptr_of = [&](size_t j, uint64_t* extent) {
+        if (largs[j].kind == LaunchArg::Scratch) { auto& s = scratch_.at(c.op).at(largs[j].name); *extent = s.bytes; return s.ptr; }
+        if (largs[j].kind != LaunchArg::Param) throw std::runtime_error(where + ": collective operand " + std::to_string(j) + " must be a buffer");
+        const Arg& a = c.args.at(largs[j].param);
+        if (a.kind != Arg::Buf && a.kind != Arg::StateK) throw std::runtime_error(where + ": collective operand " + std::to_string(j) + " must be a buffer");
+        *extent = arg_extent(a);
+        return arg_pointer(a);
+      };
+      cl.ext = ExternKind::Nccl;
+      cl.a_ptr = ptr_of(0, &cl.a_rows);
+      cl.c_ptr = ptr_of(1, &cl.w_rows);
+      const LaunchArg& cnt = largs[2];
+      if (cnt.kind == LaunchArg::I32 || cnt.kind == LaunchArg::I64) cl.m = const_expr((uint64_t)cnt.i);
+      else if (cnt.kind == LaunchArg::Param) {
+        const Arg& a = c.args.at(cnt.param);
+        if (a.kind == Arg::Var) cl.m = var_expr(a.name);
+        else if (a.kind == Arg::ExprK) cl.m = a.expr;
+        else if (a.kind == Arg::I32 || a.kind == Arg::I64) cl.m = const_expr((uint64_t)a.i);
+        else throw std::runtime_error(where + ": collective count must be an integer");
+      } else throw std::runtime_error(where + ": collective count must be an integer");
+      cl.n = const_expr(0); cl.k = const_expr(0);
+      const LaunchArg& rk = largs[3];
+      if (rk.kind == LaunchArg::Rank) cl.group = rk.name;
+      else if (rk.kind == LaunchArg::Param && c.args.at(rk.param).kind == Arg::Rank) cl.group = c.args.at(rk.param).name;
+      else throw std::runtime_error(where + ": the last arg of a collective built-in is `{rank: <group>}`");
+      if (!topo_.count(cl.group)) throw std::runtime_error(where + ": collective over unknown group `" + cl.group + "`");
+      out.launches.push_back(std::move(cl));
+      continue;
+    }
     if (l.is_extern) {
       static const std::pair<const char*, ExternKind> kinds[] = {{"extern:cublaslt_bf16_tn", ExternKind::GemmBf16},
                                                                   {"extern:cublaslt_bf16_tn_acc", ExternKind::GemmBf16Acc},
@@ -297,12 +330,65 @@ size_t Runtime::launch_gemm(const CompiledLaunch& l, const VarMap& vars, CUstrea
   return 1;
 }
 
+// One collective on the issuing stream (NCCL calls are capturable, so graph programs may hold them).
+size_t Runtime::launch_nccl(const CompiledLaunch& l, const VarMap& vars, CUstream s) {
+  std::string why;
+  auto cnt = l.m.eval(vars, &why);
+  if (!cnt) throw std::runtime_error("collective count of `" + l.label + "`: " + why);
+  const uint64_t n = *cnt;
+  if (n == 0) return 0;
+  const uint64_t world = topo_.at(l.group).size, eb = nccl_elem_bytes(l.elem);
+  if (world == 1) {      // a group of one: every collective is a copy, and no communicator exists
+    if (l.a_rows < n * eb || l.w_rows < n * eb) throw std::runtime_error("collective `" + l.label + "`: buffers smaller than the count");
+    if (l.a_ptr != l.c_ptr) dev_->d2d(l.c_ptr, l.a_ptr, n * eb, s);
+    return 1;
+  }
+  auto it = nccl_comms_.find(l.group);
+  if (it == nccl_comms_.end()) throw std::runtime_error("nccl group `" + l.group + "` not joined: connect() it before the first issue");
+  uint64_t ins = n, outs = n;
+  switch (l.coll) {
+    case NcclColl::AllReduce: break;
+    case NcclColl::AllGather: outs = n * world; break;
+    case NcclColl::ReduceScatter: ins = n * world; break;
+    case NcclColl::AllToAll: ins = outs = n * world; break;
+  }
+  if (l.a_rows < ins * eb || l.w_rows < outs * eb)
+    throw std::runtime_error("collective `" + l.label + "`: " + std::to_string(n) + " elements per rank need " + std::to_string(ins * eb) +
+                             " B to send and " + std::to_string(outs * eb) + " B to receive; the buffers hold " +
+                             std::to_string(l.a_rows) + " B and " + std::to_string(l.w_rows) + " B");
+  NcclApi& api = NcclApi::get();
+  const void* src = reinterpret_cast<const void*>(l.a_ptr);
+  void* dst = reinterpret_cast<void*>(l.c_ptr);
+  void* comm = it->second;
+  const int dt = (int)l.elem;
+  switch (l.coll) {
+    case NcclColl::AllReduce: api.check(api.AllReduce(src, dst, n, dt, 0, comm, s), "all-reduce"); break;
+    case NcclColl::AllGather: api.check(api.AllGather(src, dst, n, dt, comm, s), "all-gather"); break;
+    case NcclColl::ReduceScatter: api.check(api.ReduceScatter(src, dst, n, dt, 0, comm, s), "reduce-scatter"); break;
+    case NcclColl::AllToAll: {
+      // block p of `send` to peer p, peer p's block into block p of `recv`
+      api.check(api.GroupStart(), "group start");
+      int rc = 0;
+      for (uint64_t p = 0; p < world && rc == 0; ++p) {
+        rc = api.Send(static_cast<const uint8_t*>(src) + p * n * eb, n, dt, (int)p, comm, s);
+        if (rc == 0) rc = api.Recv(static_cast<uint8_t*>(dst) + p * n * eb, n, dt, (int)p, comm, s);
+      }
+      const int end = api.GroupEnd();
+      api.check(rc, "send/recv");
+      api.check(end, "group end");
+      break;
+    }
+  }
+  return 1;
+}
+
 size_t Runtime::launch_one(const CompiledLaunch& l, const VarMap& vars, CUstream s) {
   if (l.when) {
     auto it = vars.find(l.when->var);
     if (it == vars.end()) throw std::runtime_error("`when` reads var `" + l.when->var + "`, which the call did not set");
     if (!l.when->holds(it->second)) return 0;
   }
+  if (l.ext == ExternKind::Nccl) return launch_nccl(l, vars, s);
   if (l.ext != ExternKind::None) return launch_gemm(l, vars, s);
   LaunchDims d;
   for (int i = 0; i < 3; ++i) {
@@ -497,6 +583,25 @@ std::map<std::string, std::string> Runtime::export_handles() {
     auto r = region(name);
     out[name] = dev_->ipc_export(r.first);
   }
+  // member 0 of every group with `extern:nccl_*` launches creates the communicator's id and offers it
+  for (auto& grp : nccl_groups()) {
+    if (topo_.at(grp).index != 0) continue;
+    auto it = nccl_ids_.find(grp);
+    if (it == nccl_ids_.end()) {
+      NcclUniqueId id;
+      NcclApi::get().check(NcclApi::get().GetUniqueId(&id), "unique id");
+      it = nccl_ids_.emplace(grp, id).first;
+    }
+    out["nccl_id." + grp] = std::string(it->second.internal, sizeof it->second.internal);
+  }
+  return out;
+}
+
+std::set<std::string> Runtime::nccl_groups() const {
+  std::set<std::string> out;
+  for (auto& p : programs_)
+    for (auto& l : p.second.launches)
+      if (l.ext == ExternKind::Nccl && topo_.at(l.group).size > 1) out.insert(l.group);
   return out;
 }
 
@@ -519,11 +624,24 @@ void Runtime::connect(const std::string& group, const std::vector<std::map<std::
     dev_->stream_sync(stream_);
     imported_[kv.first] = addrs;
   }
+  if (nccl_groups().count(group) && !nccl_comms_.count(group)) {
+    // every member calls this with the same offers: member 0's id joins them into one communicator
+    auto h = members.at(0).find("nccl_id." + group);
+    if (h == members[0].end() || h->second.size() != sizeof(NcclUniqueId))
+      throw std::runtime_error("member 0 of `" + group + "` did not offer the communicator id `nccl_id." + group + "`");
+    NcclUniqueId id;
+    std::memcpy(id.internal, h->second.data(), sizeof id.internal);
+    dev_->make_current();
+    void* comm = nullptr;
+    NcclApi::get().check(NcclApi::get().CommInitRank(&comm, (int)g->second.size, id, (int)g->second.index), "communicator join");
+    nccl_comms_[group] = comm;
+  }
 }
 
 bool Runtime::peers_connected() const {
   for (auto& kv : m_.buffers)
     if (kv.second.kind == BufferKind::Peer && !imported_.count(kv.first)) return false;
+  for (auto& grp : nccl_groups()) if (!nccl_comms_.count(grp)) return false;
   return true;
 }
 

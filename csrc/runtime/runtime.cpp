@@ -78,6 +78,7 @@ Runtime::~Runtime() {
     Cuda::get().cuStreamSynchronize_(stream_);
     for (auto& g : graphs_) dev_->graph_destroy(g.second.exec);
     for (auto p : imported_ptrs_) dev_->ipc_close(p);
+    for (auto& kv : nccl_comms_) NcclApi::get().CommDestroy(kv.second);
     for (auto& kv : buffers_) if (!kv.second.borrowed && !kv.second.host) dev_->free(kv.second.ptr);
     for (auto& kv : buffers_) if (!kv.second.borrowed && kv.second.host) dev_->host_free(reinterpret_cast<void*>(kv.second.ptr));
     for (auto& kv : states_) if (!kv.second.borrowed) dev_->free(kv.second.ptr);

@@ -11,12 +11,14 @@
 #include <map>
 #include <memory>
 #include <optional>
+#include <set>
 #include <string>
 #include <vector>
 
 #include "../manifest/protocol.hpp"
 #include "../manifest/types.hpp"
 #include "device.hpp"
+#include "nccl_api.hpp"
 #include "safetensors.hpp"
 
 namespace kern {
@@ -55,7 +57,7 @@ struct CompiledArg {
   std::vector<Patch> patches;
 };
 
-enum class ExternKind { None, GemmBf16, GemmBf16Acc, GemmBf16F32 };
+enum class ExternKind { None, GemmBf16, GemmBf16Acc, GemmBf16F32, Nccl };
 
 struct CompiledLaunch {
   std::string label;           // op name / call label for traces
@@ -77,6 +79,10 @@ struct CompiledLaunch {
   uint64_t a_rows = 0, w_rows = 0;
   Expr m, n, k;
   std::optional<Expr> ldc, lda;
+  // extern collective: send = a_ptr (a_rows bytes behind it), recv = c_ptr (w_rows bytes), count = m (elements per rank)
+  NcclColl coll = NcclColl::AllReduce;
+  NcclElem elem = NcclElem::F32;
+  std::string group;
 };
 
 struct CompiledProgram {
@@ -141,6 +147,7 @@ class Runtime {
   // handles of every member of `group` in member order -> fills each peer buffer of that group
   void connect(const std::string& group, const std::vector<std::map<std::string, std::string>>& members);
   bool peers_connected() const;
+  std::set<std::string> nccl_groups() const;     // groups named by `extern:nccl_*` launches: each needs connect() first
 
   // ---- hosted mode ----
   bool awaits_host() const;
@@ -170,6 +177,8 @@ class Runtime {
   std::map<std::string, std::map<std::string, Allocation>> scratch_;   // op -> scratch name -> allocation
   std::map<std::string, std::vector<uint64_t>> imported_;             // peer buffer -> mapped addresses
   std::vector<uint64_t> imported_ptrs_;
+  std::map<std::string, void*> nccl_comms_;      // group -> communicator of the `extern:nccl_*` launches
+  std::map<std::string, NcclUniqueId> nccl_ids_;  // ids this rank (index 0 of the group) created and offers
   uint64_t page_unit_ = 1, pages_ = 0, slots_ = 0;
   uint64_t err_word_ = 0;
   bool weights_loaded_ = false;
@@ -201,6 +210,7 @@ class Runtime {
   size_t enqueue(const CompiledProgram& p, const VarMap& vars);
   size_t launch_one(const CompiledLaunch& l, const VarMap& vars, CUstream s);
   size_t launch_gemm(const CompiledLaunch& l, const VarMap& vars, CUstream s);
+  size_t launch_nccl(const CompiledLaunch& l, const VarMap& vars, CUstream s);
   void ensure_staging(size_t bytes);
   void upload(uint64_t dst, const uint8_t* src, size_t bytes);
   void upload_2d(uint64_t dst, size_t dst_pitch, const uint8_t* src, size_t src_pitch, size_t width, size_t rows);

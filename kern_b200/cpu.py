@@ -285,7 +285,7 @@ def _gdn_step(dim):
         o_raw = torch.zeros(n * hv * dim, dtype=torch.float32)
         rule((hv, n, 1), qkv, zba, o_raw, state, lines, 0, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off, a_off,
              line_bytes, s_off, 1)
-        k_gdn_gate_norm((n, hv, 1), o_raw, zba, out, norm_w, n, hv, dim, zba_stride, z_off, eps)
+        k_gdn_gate_norm(((hv + 3) // 4, n, 1), o_raw, zba, out, norm_w, n, hv, dim, zba_stride, z_off, eps)
     return run
 
 
@@ -331,7 +331,7 @@ def k_gdn_chunk_rule(g, Wg, Qg, Kg, Ug, Mg, Gg, o_raw, state, lines, cu, seqs, h
 def k_gdn_gate_norm(g, o_raw, zba, out, norm_w, tokens, hv, dv, zba_stride, z_off, eps):
     from .ops import gdn as G
 
-    t = g[0]
+    t = g[1]
     o = o_raw[: t * hv * dv].view(t, hv, dv)
     z = _f(torch.as_strided(zba, (t, hv * dv), (zba_stride, 1), zba.storage_offset() + z_off)).view(t, hv, dv)
     out[: t * hv * dv] = G.gate_norm_ref(o, z, norm_w[:dv], eps).to(torch.bfloat16).reshape(-1)
@@ -577,6 +577,11 @@ class CpuRuntime:
                     else:
                         vals.append(next(iter(la.values())))
                 entry = l["entry"]
+                if entry.startswith("extern:nccl_"):
+                    grp = largs[3].get("rank") or call["args"][largs[3]["param"]]["rank"]
+                    self._collective(entry, vals[0], vals[1], int(vals[2]), grp)
+                    n += 1
+                    continue
                 fn = CPU_KERNELS.get(entry)
                 if fn is None:          # model families register their kernels' statements when imported
                     import importlib
@@ -595,6 +600,54 @@ class CpuRuntime:
         return n
 
     run = issue
+
+    def _collective(self, entry: str, send, recv, count: int, group: str) -> None:
+        """`extern:nccl_<coll>_<elem>` with [send, recv, count, rank]: count elements per rank (per peer for an
+        all-to-all). A group of one is a copy; larger groups go through the process's `torch.distributed` default
+        group (gloo on CPU), whose world must be the group.  Reference: crates/kern-runtime/src/nccl.rs:190."""
+        coll, elem = entry[len("extern:nccl_"):].split("_")
+        dt = {"f32": torch.float32, "bf16": torch.bfloat16, "i32": torch.int32, "u8": torch.uint8}[elem]
+        world = self.topology.get(group, (0, 1))[1]
+        ins = count * (world if coll in ("reducescatter", "alltoall") else 1)
+        outs = count * (world if coll in ("allgather", "alltoall") else 1)
+        src, dst = send.view(dt)[:ins], recv.view(dt)[:outs]
+        if src.numel() < ins or dst.numel() < outs:
+            raise ValueError(f"{entry}: {count} elements per rank need {ins} to send and {outs} to receive")
+        if count == 0:
+            return
+        if world == 1:
+            dst.copy_(src)
+            return
+        import torch.distributed as dist
+
+        if not dist.is_initialized() or dist.get_world_size() != world:
+            raise RuntimeError(f"{entry}: group `{group}` of {world} needs torch.distributed initialised with that world")
+        wide = src.float() if dt in (torch.bfloat16,) and coll in ("allreduce", "reducescatter") else src.clone()
+        if coll == "allreduce":
+            dist.all_reduce(wide)
+            dst.copy_(wide.to(dt))
+        elif coll == "allgather":
+            parts = [torch.empty_like(wide) for _ in range(world)]
+            dist.all_gather(parts, wide)
+            dst.copy_(torch.cat(parts))
+        elif coll == "reducescatter":
+            dist.all_reduce(wide)
+            r = self.rank(group)
+            dst.copy_(wide[r * count:(r + 1) * count].to(dt))
+        else:
+            outp = [torch.empty(count, dtype=dt) for _ in range(world)]
+            dist.all_to_all(outp, list(wide.split(count))) if dist.get_backend() != "gloo" else self._a2a_gloo(outp, wide, count, world, group)
+            dst.copy_(torch.cat(outp))
+
+    def _a2a_gloo(self, outp, wide, count, world, group):
+        """gloo has no all-to-all: every rank gathers all blocks and keeps the ones addressed to it."""
+        import torch.distributed as dist
+
+        parts = [torch.empty_like(wide) for _ in range(world)]
+        dist.all_gather(parts, wide)
+        r = self.rank(group)
+        for p in range(world):
+            outp[p].copy_(parts[p][r * count:(r + 1) * count])
 
     def _pack(self, pack, cargs, opname):
         """A pack holding one tensor map stands for the tensor it describes (row stride and head dim kept)."""

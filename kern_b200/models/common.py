@@ -595,7 +595,7 @@ def gdn_conv_op(conv_dim: int, width: int, x_stride: int, line_bytes: int, ragge
     w_at = len(iface) - 3
     cu_t, cu_a = ("in buffer<i32>", {"param": 4}) if ragged else ("i64", {"i64": 0})
     conv = {"module": "gdn", "entry": "kern_gdn_conv_bf16", "block": [256, 1, 1],
-            "grid": [{"ceil_div": ["tokens", 16]} if ragged else "tokens", -(-conv_dim // 256), 1],
+            "grid": [{"ceil_div": ["tokens", 16]} if ragged else "tokens", -(-conv_dim // 1024), 1],
             "params": ["in buffer<bf16>", "out buffer<bf16>", "in state", "in buffer<i32>", cu_t, "in buffer<bf16>", "i64",
                        "i32", "i32", "i32", "i32", "i32", "i64", "i32"],
             "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"param": 3}, cu_a, {"param": w_at}, {"i64": 0},
@@ -636,7 +636,7 @@ def gdn_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_
             {"param": 5} if ragged else {"i64": 0}, {"param": at}, {"param": at + 1}, {"param": at + 3}, {"i32": hk},
             {"i32": hv}, {"i32": zba_stride}, {"i32": hv * dim}, {"i32": hv * dim + hv}, {"i64": line_bytes}, {"i64": s_off},
             {"i32": tb}]
-    norm = {"module": "gdn", "entry": "kern_gdn_gate_norm_bf16", "block": [128, 1, 1], "grid": ["tokens", hv, 1],
+    norm = {"module": "gdn", "entry": "kern_gdn_gate_norm_bf16", "block": [128, 1, 1], "grid": [-(-hv // 4), "tokens", 1],
             "params": ["in buffer<f32>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<bf16>", "i32", "i32", "i32", "i32",
                        "i32", "f32"],
             "args": [{"scratch": "o_raw"}, {"param": 1}, {"param": 2}, {"param": at + 2}, {"i32": I32_MAX}, {"i32": hv},

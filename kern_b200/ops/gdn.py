@@ -35,7 +35,7 @@ def conv(x, y, state, lines, cu_q, w, bias, seqs, conv_dim, width, line_b, rows=
     k = Kernels.get(x.device)
     rows = x.shape[0] if rows is None else rows
     rpc = 16 if cu_q is not None else 1
-    k.launch("gdn", "kern_gdn_conv_bf16", ((rows + rpc - 1) // rpc, (conv_dim + 255) // 256), (256,),
+    k.launch("gdn", "kern_gdn_conv_bf16", ((rows + rpc - 1) // rpc, (conv_dim + 1023) // 1024), (256,),
              [ptr(x), ptr(y), ptr(state), ptr(lines), ptr(cu_q), ptr(w), ptr(bias), i32(seqs), i32(rows), i32(conv_dim),
               i32(width), i32(x.stride(0)), i64(line_b), i32(rpc)])
     k.launch("gdn", "kern_gdn_conv_state", (seqs, (conv_dim + 255) // 256), (256,),
@@ -57,7 +57,7 @@ def rule(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv
              [ptr(qkv), ptr(zba), ptr(o_raw), ptr(state), ptr(lines), ptr(cu_q), ptr(A_log), ptr(dt_bias),
               i32(seqs), i32(hk), i32(hv), i32(zba.stride(0)), i32(b_off), i32(a_off), i64(line_b), i64(s_off), i32(tb)],
              shared_mem=rule_smem(dk, tb, rows_cta))
-    k.launch("gdn", "kern_gdn_gate_norm_bf16", (tokens, hv), (128,),
+    k.launch("gdn", "kern_gdn_gate_norm_bf16", ((hv + 3) // 4, tokens), (128,),
              [ptr(o_raw), ptr(zba), ptr(out), ptr(norm_w), i32(tokens), i32(hv), i32(dv), i32(zba.stride(0)),
               i32(z_off), f32(eps)])
     return out
@@ -110,7 +110,7 @@ def rule_chunked(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs
     k.launch("gdn_chunk", "kern_gdn_chunk_rule_k128_v128", (hv * 2, seqs), (256,),
              [ptr(sc["W"]), ptr(sc["Qg"]), ptr(sc["Kd"]), ptr(sc["Ut"]), ptr(sc["M"]), ptr(sc["gC"]), ptr(o_raw), ptr(state),
               ptr(lines), ptr(cu_q), i32(seqs), i32(hv), i64(line_b), i64(s_off)], shared_mem=CHUNK_RULE_SMEM)
-    k.launch("gdn", "kern_gdn_gate_norm_bf16", (tokens, hv), (128,),
+    k.launch("gdn", "kern_gdn_gate_norm_bf16", ((hv + 3) // 4, tokens), (128,),
              [ptr(o_raw), ptr(zba), ptr(out), ptr(norm_w), i32(tokens), i32(hv), i32(dv), i32(zba.stride(0)),
               i32(z_off), f32(eps)])
     return out

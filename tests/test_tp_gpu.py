@@ -52,3 +52,25 @@ def test_tp_allreduce_and_model(world):
     assert all(r["ok"] for r in ar["results"]) and len(ar["results"]) == 12
     model = next(l for l in lines if l["check"] == "tp_model")
     assert model["ok"], model
+
+
+def test_collective_externs_group_of_one(cuda):
+    """`extern:nccl_*` launches on one rank: no communicator, every collective is a device copy (eager and captured)."""
+    from kern_b200.parallel import coll_check
+
+    assert coll_check.main(["--sizes", "1", "1000"]) == 0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_collective_externs(world):
+    """All-reduce, all-gather, reduce-scatter and all-to-all built-ins over NCCL, one process per GPU; the communicator
+    id travels in rank 0's offer."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29520 + world), "-m", "kern_b200.parallel.coll_check"]
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
+    line = next(json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))
+    assert line["world"] == world and all(r["ok"] for r in line["results"]), line
