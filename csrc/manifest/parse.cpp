@@ -27,14 +27,14 @@ struct Rd {
   const Json& j;
   std::string path;
   Ctx& cx;
-  std::set<std::string> seen;
+  std::vector<const char*> seen;      // keys asked for (string literals): a handful per object
   bool ok;
   Rd(const Json& j_, std::string p, Ctx& c) : j(j_), path(std::move(p)), cx(c), ok(j_.is_obj()) {
     if (!ok) cx.err(path, "expected an object");
   }
   const Json* opt(const char* k) {
     if (!ok) return nullptr;
-    seen.insert(k);
+    seen.push_back(k);
     const Json* v = j.find(k);
     return (v && v->is_null()) ? nullptr : v;
   }
@@ -47,7 +47,8 @@ struct Rd {
   void done() {
     if (!ok) return;
     for (auto& kv : j.obj)
-      if (!seen.count(kv.first)) cx.err(path, "unknown field `" + kv.first + "`");
+      if (std::none_of(seen.begin(), seen.end(), [&](const char* k) { return kv.first == k; }))
+        cx.err(path, "unknown field `" + kv.first + "`");
   }
   bool u64(const Json& v, const std::string& p, uint64_t& out) {
     const Json* n = cx.num(v);

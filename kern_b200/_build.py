@@ -137,6 +137,18 @@ def build_native(force: bool = False) -> Path:
     return out
 
 
+def build_cli(force: bool = False) -> Path:
+    """The native `kern` binary (verify / cut / print): the manifest library and a main, nothing else."""
+    out = PKG / "bin" / "kern"
+    srcs = [CSRC / "cli" / "kern_main.cpp", *sorted((CSRC / "manifest").glob("*.cpp"))]
+    headers = [p for p in (CSRC / "manifest").glob("*.hpp")] + [p for p in (CSRC / "common").glob("*.hpp")]
+    if not force and not _newer([*srcs, *headers], out):
+        return out
+    out.parent.mkdir(exist_ok=True)
+    _run([CXX, "-O2", "-std=c++17", "-Wall", "-Wno-unused-function", "-I", str(CSRC), "-o", str(out), *map(str, srcs)])
+    return out
+
+
 def build_host_libs(force: bool = False) -> list[Path]:
     """Shared libraries with host code compiled by nvcc (C entry points reached through ctypes)."""
     outs = []
@@ -156,6 +168,7 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
         try:
             build_kernels(force, verbose)
             build_native(force)
+            build_cli(force)
             build_host_libs(force)
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)

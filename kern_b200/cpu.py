@@ -663,3 +663,53 @@ class CpuRuntime:
                 holder._vars_seqs = self._vars.get(self.protocol["groups"]["var"], 1) if self.protocol else 1
                 return holder
         return pack
+
+
+# ---- block-draft helpers and the state advance (statements: ops/draft.py) ------------------------------------------
+def _k_topk(g, logits, ids, vals, n, row_stride, k):
+    from .ops import draft as D
+
+    rows = g[0]
+    x = torch.as_strided(logits, (rows, n), (row_stride, 1), logits.storage_offset())
+    i, v = D.topk_ref(x, k)
+    ids[: rows * k] = i.reshape(-1)
+    vals[: rows * k] = v.reshape(-1)
+
+
+def _k_mask_row0(g, dst, src, rows, rows_per_seq, cols):
+    from .ops import draft as D
+
+    r = g[0]
+    dst[: r * cols] = D.mask_row0_ref(src[: r * cols].view(r, cols), rows_per_seq).reshape(-1)
+
+
+def _k_conv_shift(g, lines, line_stride, state, accepted, seqs, line_bytes, tok_bytes):
+    from .ops import draft as D
+
+    n = g[0]
+    D.conv_shift_ref(torch.as_strided(lines, (n, line_stride), (line_stride, 1), lines.storage_offset()), state, accepted,
+                     line_bytes, tok_bytes)
+
+
+def _k_dflash_conv(g, x, delta, base, tokens, dim, groups, delta_stride, side):
+    from .ops import draft as D
+
+    T = min(tokens, g[0] * 8)
+    d = torch.as_strided(delta, (T, 4 * groups), (delta_stride, 1), delta.storage_offset())
+    x[: T * dim] = D.dflash_conv_ref(x[: T * dim].view(T, dim), d, base, groups, side).reshape(-1)
+
+
+def _k_dflash_select(g, cand, unary, hidden_r, succ, pred, pred_anchor, out, steps, rank, hr_stride, rows_per_seq):
+    from .ops import draft as D
+
+    seqs = g[0]
+    rows = seqs * rows_per_seq
+    res = D.dflash_select_ref(cand[: rows * 16].view(rows, 16), unary[: rows * 16].view(rows, 16),
+                              torch.as_strided(hidden_r, (rows, rank), (hr_stride, 1), hidden_r.storage_offset()),
+                              succ[: rows * 16 * rank].view(rows, 16, rank), pred[: rows * 16 * rank].view(rows, 16, rank),
+                              pred_anchor[: seqs * rank].view(seqs, rank), steps, rows_per_seq)
+    out[: seqs * steps] = res.reshape(-1)
+
+
+CPU_KERNELS.update({"kern_topk_bf16": _k_topk, "kern_mask_row0_bf16": _k_mask_row0, "kern_conv_shift": _k_conv_shift,
+                    "kern_dflash_conv_bf16": _k_dflash_conv, "kern_dflash_select": _k_dflash_select})

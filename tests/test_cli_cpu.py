@@ -108,3 +108,32 @@ def test_pick_fewest_ranges_within_noise():
     assert got == [("gemv", 1, 8), ("tile", 9, 256)]            # the tie at 8 (within noise) extends the first range
     assert gaps(got, 512) == [(257, 512)] and gaps(got, 256) == []
     assert pick([Point(5, {"a": 1.0, "b": 1.05}, noise=0.1), Point(9, {"a": 2.0, "b": 1.0})]) == [("b", 1, 9)]
+
+
+def test_native_kern_binary_verifies_and_cuts(tmp_path):
+    """The C++ `kern` binary (manifest library + main, no Python or CUDA behind it): verify with the protocol, a
+    diagnostic for a broken manifest, and cut into stage files."""
+    import json
+    import subprocess
+    from kern_b200 import _build
+    from kern_b200.models import dense
+
+    exe = _build.build_cli()
+    doc = dense.build_manifest(dense.TINY)
+    good = tmp_path / "m.json"
+    good.write_text(json.dumps(doc))
+    p = subprocess.run([str(exe), "verify", str(good), "--protocol", "--greedy"], capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0 and p.stdout.startswith("ok:") and '"page_tables"' in p.stdout, p.stdout[:500]
+    bad = dict(doc, surprise=1)
+    (tmp_path / "bad.json").write_text(json.dumps(bad))
+    p = subprocess.run([str(exe), "verify", str(tmp_path / "bad.json")], capture_output=True, text=True, timeout=60)
+    assert p.returncode == 1 and "surprise" in p.stdout
+    calls = len(doc["programs"]["prefill"]["calls"])
+    (tmp_path / "st").mkdir()
+    p = subprocess.run([str(exe), "cut", str(good), "--at", str(calls // 2), "--out", str(tmp_path / "st")],
+                       capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0, p.stdout
+    from kern_b200.runtime import verify
+    for i in range(2):
+        m, diags = verify(json.loads((tmp_path / "st" / f"stage{i}.json").read_text()))
+        assert m is not None, diags[:3]

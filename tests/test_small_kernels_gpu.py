@@ -110,3 +110,67 @@ def test_hold_times_out_with_an_error_status_and_mark_publishes(cuda):
     k.launch("signals", "kern_lanes_join", (1,), (32,), [ptr(out), ptr(tot), i32(3)])
     torch.cuda.synchronize()
     assert float(tot) == 6.0
+
+
+def test_topk_rows_against_torch(cuda):
+    from kern_b200.ops import draft as D
+
+    torch.manual_seed(0)
+    x = torch.randn(5, 30011, device=cuda).to(torch.bfloat16)
+    x[1, 100] = x[1, 20000] = 9.0            # a tie at the top: the smaller index first
+    ids, vals = D.topk(x, 16)
+    torch.cuda.synchronize()
+    rid, rv = D.topk_ref(x, 16)
+    assert torch.equal(vals, rv) and torch.equal(ids, rid)
+    assert ids[1, 0].item() == 100 and ids[1, 1].item() == 20000
+    small = torch.randn(2, 10, device=cuda).to(torch.bfloat16)      # fewer columns than k: the tail is (-1, -inf)
+    ids, vals = D.topk(small, 16)
+    assert (ids[:, 10:] == -1).all() and torch.isinf(vals[:, 10:]).all()
+    assert torch.equal(ids[:, :10], D.topk_ref(small, 10)[0])
+
+
+def test_mask_row0_and_conv_shift(cuda):
+    from kern_b200.ops import draft as D
+
+    torch.manual_seed(1)
+    src = torch.randn(12, 96, device=cuda).to(torch.bfloat16)
+    assert torch.equal(D.mask_row0(src, 4), D.mask_row0_ref(src, 4))
+    line_bytes, tok_bytes, lines_n = 9 * 256, 256, 6
+    state = torch.randint(0, 255, (lines_n, line_bytes), dtype=torch.uint8, device=cuda)
+    want = state.clone()
+    lines = torch.tensor([[1, 2, 3, 1], [4, 4, 4, 4], [0, 0, 0, 0], [5, 5, 5, 5]], dtype=torch.int32, device=cuda)
+    accepted = torch.tensor([3, 1, 4, 4], dtype=torch.int32, device=cuda)      # a = 2, 0 (no-op), 3 on the null line, 3
+    D.conv_shift(lines, state, accepted, line_bytes, tok_bytes)
+    torch.cuda.synchronize()
+    D.conv_shift_ref(lines.cpu(), want, accepted.cpu(), line_bytes, tok_bytes)
+    assert torch.equal(state, want)
+
+
+def test_dflash_conv_and_select(cuda):
+    from kern_b200.ops import draft as D
+
+    torch.manual_seed(2)
+    T, dim, groups = 21, 640, 40
+    x = torch.randn(T, dim, device=cuda).to(torch.bfloat16)
+    delta = (torch.randn(T, 4 * groups + 8, device=cuda) * 0.3).to(torch.bfloat16)
+    base = torch.randn(2, 2, dim, device=cuda).to(torch.bfloat16)
+    for side in (0, 1):
+        want = D.dflash_conv_ref(x, delta[:, :4 * groups], base, groups, side)
+        got = D.dflash_conv(x.clone(), delta, base, groups, side)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    seqs, rps, steps, rank = 3, 8, 7, 256
+    rows = seqs * rps
+    cand = torch.randint(0, 50000, (rows, 16), device=cuda)
+    unary = torch.randn(rows, 16, device=cuda)
+    hidden_r = torch.randn(rows, rank + 32, device=cuda).to(torch.bfloat16)
+    succ = torch.randn(rows, 16, rank, device=cuda).to(torch.bfloat16)
+    pred = torch.randn(rows, 16, rank, device=cuda).to(torch.bfloat16)
+    anchor = torch.randn(seqs, rank, device=cuda).to(torch.bfloat16)
+    got = D.dflash_select(cand, unary, hidden_r, succ, pred, anchor, steps, rps)
+    torch.cuda.synchronize()
+    want = D.dflash_select_ref(cand, unary, hidden_r, succ, pred, anchor, steps, rps)
+    # a different summation order can flip a near-tie between two candidates; every later step then walks another path
+    agree = (got == want).float().mean().item()
+    assert agree > 0.8, agree
+    assert torch.equal(got[:, 0], want[:, 0])
