@@ -348,9 +348,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
 #pragma unroll
             for (int v = 0; v < 8; ++v) {
               if (col + v * 4 < N) {
-                float4 o = make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
-                                       __uint_as_float(r[v * 4 + 2]),
-                                       __uint_as_float(r[v * 4 + 3]));
+                float4 o = make_float4(__uint_as_float(r[v * 4]) * out_scale, __uint_as_float(r[v * 4 + 1]) * out_scale,
+                                       __uint_as_float(r[v * 4 + 2]) * out_scale,
+                                       __uint_as_float(r[v * 4 + 3]) * out_scale);
                 *reinterpret_cast<float4*>(C + v * 4) = o;
               }
             }

@@ -21,6 +21,9 @@ using namespace kern;
 KERN_FP8_GEMM_ENTRY(kern_gemm_e4m3_tn_n256, 256, 0)
 KERN_FP8_GEMM_ENTRY(kern_gemm_e4m3_tn_n128, 128, 0)
 KERN_FP8_GEMM_ENTRY(kern_gemm_e4m3_tn_n64, 64, 0)
+KERN_FP8_GEMM_ENTRY(kern_gemm_e4m3_tn_f32_n256, 256, 1)
+KERN_FP8_GEMM_ENTRY(kern_gemm_e4m3_tn_f32_n128, 128, 1)
+KERN_FP8_GEMM_ENTRY(kern_gemm_e4m3_tn_f32_n64, 64, 1)
 KERN_FP8_GEMM_ENTRY(kern_gemm_e4m3_tn_acc_n256, 256, 2)
 KERN_FP8_GEMM_ENTRY(kern_gemm_e4m3_tn_acc_n128, 128, 2)
 

@@ -154,11 +154,18 @@ void Runtime::compile_call(CompiledProgram& out, const std::string& pname, const
     if (l.is_extern) {
       static const std::pair<const char*, ExternKind> kinds[] = {{"extern:cublaslt_bf16_tn", ExternKind::GemmBf16},
                                                                   {"extern:cublaslt_bf16_tn_acc", ExternKind::GemmBf16Acc},
-                                                                  {"extern:cublas_bf16_tn_f32", ExternKind::GemmBf16F32}};
+                                                                  {"extern:cublas_bf16_tn_f32", ExternKind::GemmBf16F32},
+                                                                  {"extern:cublaslt_fp8_tn", ExternKind::GemmFp8},
+                                                                  {"extern:cublaslt_fp8_tn_f32", ExternKind::GemmFp8F32}};
       for (auto& k : kinds) if (l.entry == k.first) cl.ext = k.second;
       if (cl.ext == ExternKind::None)
         throw std::runtime_error(where + ": built-in `" + l.entry + "` is not provided by this runtime");
-      if (largs.size() < 6 || largs.size() > 8) throw std::runtime_error(where + ": a GEMM built-in takes [a, w, c, m, n, k] plus optional row strides");
+      const bool fp8 = cl.ext == ExternKind::GemmFp8 || cl.ext == ExternKind::GemmFp8F32;
+      // e4m3 operands with per-tensor device scales: [a, w, c, a_scale, w_scale, m, n, k] plus an optional C row stride
+      const size_t so = fp8 ? 2 : 0;
+      if (fp8 ? (largs.size() < 8 || largs.size() > 9) : (largs.size() < 6 || largs.size() > 8))
+        throw std::runtime_error(where + (fp8 ? ": an fp8 GEMM built-in takes [a, w, c, a_scale, w_scale, m, n, k] plus an optional C row stride"
+                                              : ": a GEMM built-in takes [a, w, c, m, n, k] plus optional row strides"));
       auto ptr_of = [&](size_t j, uint64_t* extent) {
         if (largs[j].kind == LaunchArg::Scratch) { auto& s = scratch_.at(c.op).at(largs[j].name); if (extent) *extent = s.bytes; return s.ptr; }
         if (largs[j].kind != LaunchArg::Param) throw std::runtime_error(where + ": GEMM operand " + std::to_string(j) + " must be a buffer");
@@ -180,12 +187,20 @@ void Runtime::compile_call(CompiledProgram& out, const std::string& pname, const
       cl.a_ptr = ptr_of(0, &a_ext);
       cl.w_ptr = ptr_of(1, &w_ext);
       cl.c_ptr = ptr_of(2, nullptr);
-      cl.m = expr_of(3); cl.n = expr_of(4); cl.k = expr_of(5);
-      if (largs.size() >= 7) cl.ldc = expr_of(6);
-      if (largs.size() >= 8) cl.lda = expr_of(7);
+      if (fp8) { cl.sa_ptr = ptr_of(3, nullptr); cl.sw_ptr = ptr_of(4, nullptr); }
+      cl.m = expr_of(3 + so); cl.n = expr_of(4 + so); cl.k = expr_of(5 + so);
+      if (largs.size() >= 7 + so) cl.ldc = expr_of(6 + so);
+      if (!fp8 && largs.size() >= 8) cl.lda = expr_of(7);
       cl.a_rows = a_ext;   // bytes available behind the pointers: row counts follow at launch
       cl.w_rows = w_ext;
-      if (!gemm_fns_.size()) {
+      if (fp8 && !gemm_fns_.count("kern_gemm_e4m3_tn_n128")) {
+        for (const char* epi : {"", "_f32"})
+          for (int bn : {256, 128, 64}) {
+            const std::string e = std::string("kern_gemm_e4m3_tn") + epi + "_n" + std::to_string(bn);
+            gemm_fns_[e] = dev_->function(builtin_gemm8_, e);
+          }
+      }
+      if (!fp8 && !gemm_fns_.count("kern_gemm_bf16_tn_n128")) {
         for (const char* epi : {"", "_acc", "_f32"})
           for (int bn : {256, 128, 64, 32}) {
             if (bn == 32 && std::string(epi) == "_f32") continue;
@@ -292,6 +307,36 @@ size_t Runtime::launch_gemm(const CompiledLaunch& l, const VarMap& vars, CUstrea
   const uint64_t m = ev(l.m), n = ev(l.n), k = ev(l.k);
   if (m == 0 || n == 0) return 0;
   const uint64_t ldc = l.ldc ? ev(*l.ldc) : n, lda = l.lda ? ev(*l.lda) : k;
+  if (l.ext == ExternKind::GemmFp8 || l.ext == ExternKind::GemmFp8F32) {
+    // one byte per element, 128-element K boxes; the tile width as the bf16 picker would choose it (no 32-wide tile)
+    const bool f32o = l.ext == ExternKind::GemmFp8F32;
+    const uint64_t tiles_m = (m + 127) / 128;
+    const int bn = tiles_m * ((n + 255) / 256) >= (uint64_t)dev_->sm_count() ? 256 : (n >= 128 ? 128 : 64);
+    if (k % 16) throw std::runtime_error("fp8 GEMM `" + l.label + "`: k must be a multiple of 16");
+    auto tmap8 = [&](uint64_t ptr, uint64_t ld, uint64_t avail_bytes, uint64_t box_rows) {
+      TensorMapSpec sp;
+      sp.dtype = 0;      // CU_TENSOR_MAP_DATA_TYPE_UINT8
+      sp.dims = {k, std::max<uint64_t>(1, avail_bytes / ld)};
+      sp.strides = {ld};
+      sp.box = {128, (uint32_t)box_rows};
+      sp.swizzle = 128;
+      sp.l2_promotion = 256;
+      return dev_->encode_tensor_map(ptr, sp);
+    };
+    alignas(64) std::array<uint8_t, 128> ta = tmap8(l.a_ptr, k, l.a_rows, 128);
+    alignas(64) std::array<uint8_t, 128> tb = tmap8(l.w_ptr, k, std::min<uint64_t>(l.w_rows, n * k), bn);
+    CUfunction fn = gemm_fns_.at(std::string("kern_gemm_e4m3_tn") + (f32o ? "_f32" : "") + "_n" + std::to_string(bn));
+    uint64_t c = l.c_ptr, r = 0, sa = l.sa_ptr, sw = l.sw_ptr, err = err_word_;
+    int mi = (int)m, ni = (int)n, ki = (int)k, ldci = (int)ldc;
+    void* params[] = {ta.data(), tb.data(), &c, &r, &sa, &sw, &mi, &ni, &ki, &ldci, &err};
+    LaunchDims d;
+    d.grid[0] = (unsigned)std::min<uint64_t>(tiles_m * ((n + bn - 1) / bn), dev_->sm_count());
+    d.block[0] = 192;
+    const int stages = bn == 256 ? 4 : (bn == 128 ? 6 : 8);
+    d.shared_mem = 1024 + stages * (128 * 128 + bn * 128) + 256;
+    dev_->launch(fn, d, s, params);
+    return 1;
+  }
   const bool f32 = l.ext == ExternKind::GemmBf16F32;
   const GemmPick pk = pick_gemm_tile(m, n, dev_->sm_count(), !f32);
   // descriptors cover everything behind the pointers, so one encoding serves every row count

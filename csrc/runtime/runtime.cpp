@@ -121,6 +121,10 @@ void Runtime::load_modules() {
     const std::string path = kernels_dir_ + "/gemm_bf16.cubin";
     builtin_gemm_ = dev_->load_module(read_file(path));
   }
+  bool needs_gemm8 = false;
+  for (auto& okv : m_.ops)
+    for (auto& l : okv.second.launches) needs_gemm8 |= l.is_extern && l.entry.rfind("extern:cublaslt_fp8", 0) == 0;
+  if (needs_gemm8) builtin_gemm8_ = dev_->load_module(read_file(kernels_dir_ + "/gemm_fp8.cubin"));
   // a multi-rank manifest runs only modules declared free of cluster-multicast copies
   bool multi = false;
   for (auto& kv : topo_) multi |= kv.second.size >= 2;

@@ -57,7 +57,7 @@ struct CompiledArg {
   std::vector<Patch> patches;
 };
 
-enum class ExternKind { None, GemmBf16, GemmBf16Acc, GemmBf16F32, Nccl };
+enum class ExternKind { None, GemmBf16, GemmBf16Acc, GemmBf16F32, GemmFp8, GemmFp8F32, Nccl };
 
 struct CompiledLaunch {
   std::string label;           // op name / call label for traces
@@ -79,6 +79,7 @@ struct CompiledLaunch {
   uint64_t a_rows = 0, w_rows = 0;
   Expr m, n, k;
   std::optional<Expr> ldc, lda;
+  uint64_t sa_ptr = 0, sw_ptr = 0;   // per-tensor f32 scales of an fp8 GEMM (device words)
   // extern collective: send = a_ptr (a_rows bytes behind it), recv = c_ptr (w_rows bytes), count = m (elements per rank)
   NcclColl coll = NcclColl::AllReduce;
   NcclElem elem = NcclElem::F32;
@@ -171,6 +172,7 @@ class Runtime {
 
   std::map<std::string, CUmodule> modules_;
   CUmodule builtin_gemm_ = nullptr;
+  CUmodule builtin_gemm8_ = nullptr;     // e4m3 GEMMs behind `extern:cublaslt_fp8_tn[_f32]`
   std::map<std::string, CUfunction> gemm_fns_;
   std::map<std::string, Allocation> buffers_;
   std::map<std::string, StateAlloc> states_;

@@ -713,3 +713,31 @@ def _k_dflash_select(g, cand, unary, hidden_r, succ, pred, pred_anchor, out, ste
 
 CPU_KERNELS.update({"kern_topk_bf16": _k_topk, "kern_mask_row0_bf16": _k_mask_row0, "kern_conv_shift": _k_conv_shift,
                     "kern_dflash_conv_bf16": _k_dflash_conv, "kern_dflash_select": _k_dflash_select})
+
+
+# ---- the runtime's GEMM built-ins: C[m, n] = A[m, k] . W[n, k]^T ------------------------------------------------------
+def _extern_gemm(acc: bool, f32_out: bool, fp8: bool):
+    def run(g, a, w, c, *rest):
+        if fp8:
+            sa, sw, m, n, k = rest[:5]
+            A = a[: m * k].view(torch.float8_e4m3fn).float().view(m, k) * float(sa[0])
+            W = w[: n * k].view(torch.float8_e4m3fn).float().view(n, k) * float(sw[0])
+            ldc = rest[5] if len(rest) > 5 else n
+        else:
+            m, n, k = rest[:3]
+            ldc = rest[3] if len(rest) > 3 else n
+            lda = rest[4] if len(rest) > 4 else k
+            A = _f(torch.as_strided(a, (m, k), (lda, 1), a.storage_offset()))
+            W = _f(w[: n * k].view(n, k))
+        out = A @ W.t()
+        C = torch.as_strided(c, (m, n), (ldc, 1), c.storage_offset())
+        if acc:
+            out = out + C.float()
+        C.copy_(out if f32_out else out.to(torch.bfloat16))
+    return run
+
+
+CPU_KERNELS.update({
+    "extern:cublaslt_bf16_tn": _extern_gemm(False, False, False), "extern:cublaslt_bf16_tn_acc": _extern_gemm(True, False, False),
+    "extern:cublas_bf16_tn_f32": _extern_gemm(False, True, False), "extern:cublaslt_fp8_tn": _extern_gemm(False, False, True),
+    "extern:cublaslt_fp8_tn_f32": _extern_gemm(False, True, True)})

@@ -123,3 +123,15 @@ def test_gemm_256_row_tiles(cuda, epilogue, m, n, k):
     torch.cuda.synchronize()
     Kernels.get(cuda).check_error()
     torch.testing.assert_close(got.float(), gemm_reference(a, w, epilogue, res).float(), rtol=1.6e-2, atol=1.6e-2)
+
+
+def test_extern_gemm_builtins_gpu(cuda):
+    """The GEMM built-ins a package may name (`extern:cublaslt_*`) on a GPU: served by the runtime's own tcgen05
+    kernels (bf16 and e4m3 with device scales)."""
+    from kern_b200.runtime import Runtime
+    from kern_b200.testing.extern_gemm import check, manifest
+
+    rt = Runtime(manifest(512, 384, 512))
+    for m in (1, 200, 512):
+        check(rt, "cuda", m, 384, 512)
+    rt.check_error()
