@@ -78,6 +78,9 @@ void bind_runtime(py::module_& m) {
         r.synchronize();
       })
       .def("run_once_programs", &Runtime::run_once_programs)
+      .def("issue_range", [](Runtime& r, const std::string& program, const VarMap& vars, size_t lo, size_t hi) {
+        return r.issue_range(program, vars, lo, hi);
+      })
       .def("issue", [](Runtime& r, const std::string& program, const VarMap& vars, bool eager) {
         return r.issue(program, vars, eager);
       }, py::arg("program"), py::arg("vars"), py::arg("eager") = false)

@@ -558,6 +558,20 @@ size_t Runtime::enqueue_after(const std::string& program, const VarMap& vars, ui
   return n;
 }
 
+// Calls [lo, hi) of a program, eagerly and in order on the main stream (lanes are not forked): the harness behind
+// activation probes, which read what a call wrote before the next range overwrites it.
+size_t Runtime::issue_range(const std::string& program, const VarMap& vars, size_t lo, size_t hi) {
+  if (!compiled_) throw std::runtime_error("the manifest's host states have not been bound yet");
+  auto it = programs_.find(program);
+  if (it == programs_.end()) throw std::runtime_error("no program named `" + program + "`");
+  dev_->make_current();
+  size_t n = 0;
+  for (auto& l : it->second.launches)
+    if (l.call_index >= lo && l.call_index < hi) n += launch_one(l, vars, stream_);
+  launches_total_ += n;
+  return n;
+}
+
 std::vector<Runtime::CallTime> Runtime::issue_timed(const std::string& program, const VarMap& vars) {
   if (!compiled_) throw std::runtime_error("the manifest's host states have not been bound yet");
   auto it = programs_.find(program);

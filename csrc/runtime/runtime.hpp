@@ -132,6 +132,7 @@ class Runtime {
     float ms = 0;
     size_t launches = 0;
   };
+  size_t issue_range(const std::string& program, const VarMap& vars, size_t lo, size_t hi);
   std::vector<CallTime> issue_timed(const std::string& program, const VarMap& vars);
   bool is_captured(const std::string& program, const VarMap& vars) const;
   size_t graphs() const { return graphs_.size(); }

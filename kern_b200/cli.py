@@ -196,6 +196,10 @@ def cmd_run(args) -> int:
     if hasattr(rt, "banner"):
         print(rt.banner(), file=sys.stderr)
     eng = Engine(rt)
+    if getattr(args, "probe_dir", None):
+        from .testing.probe import Probe
+
+        eng.probe = Probe(args.probe_dir, args.probe_labels or "")
     prompt = _prompt_ids(args)
     t0 = time.perf_counter()
     toks = eng.generate(prompt, args.steps, chunk=args.chunk, sampling=Sampling(temperature=args.temperature, seed=args.seed))
@@ -441,6 +445,8 @@ def main(argv=None) -> int:
     r = sub.add_parser("run"); common(r)
     r.add_argument("--prompt"); r.add_argument("--prompt-ids"); r.add_argument("--steps", type=int, default=16)
     r.add_argument("--temperature", type=float, default=0.0); r.add_argument("--seed", type=int, default=0)
+    r.add_argument("--probe-dir", help="dump what the calls named by --probe-labels wrote, step by step, into this directory")
+    r.add_argument("--probe-labels", help="comma-separated call labels (or label suffixes), e.g. l0.attn_out,head")
     t = sub.add_parser("test"); t.add_argument("a"); t.add_argument("b"); common(t, manifest=False)
     t.add_argument("--seed", type=int, default=0); t.add_argument("--prompts", type=int, default=4)
     t.add_argument("--decode-steps", type=int, default=8); t.add_argument("--logit-kl", type=float, default=0.01)

@@ -552,11 +552,14 @@ class CpuRuntime:
             return self.rank(a["rank"])
         return next(iter(a.values()))
 
-    def issue(self, program: str, vars: dict[str, int], eager: bool = False) -> int:
+    def issue_range(self, program: str, vars: dict[str, int], lo: int, hi: int) -> int:
+        return self.issue(program, vars, calls=(lo, hi))
+
+    def issue(self, program: str, vars: dict[str, int], eager: bool = False, calls: tuple[int, int] | None = None) -> int:
         self._vars = dict(vars)
         p = self.doc["programs"][program]
         n = 0
-        for call in p["calls"]:
+        for call in (p["calls"] if calls is None else p["calls"][calls[0]:calls[1]]):
             op = self.doc["ops"][call["op"]]
             cargs = [self._resolve_call_arg(a, pt) for a, pt in zip(call["args"], op["params"])]
             for l in op["impl"]["launches"]:

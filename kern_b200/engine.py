@@ -36,6 +36,7 @@ class Sequence:
 class Engine:
     def __init__(self, rt, pool: "_native.Pool | None" = None):
         self.rt = rt
+        self.probe = None      # a testing.probe.Probe: steps run call range by call range and dump activations
         p = rt.protocol
         if p is None:
             raise ValueError("the manifest has no serving protocol (no program declares a `batch`)")
@@ -101,6 +102,8 @@ class Engine:
         if timed:     # cost by call, eagerly, with an event between calls
             self.last_times = self.rt.issue_timed(fw["name"], vars_)
             launches = sum(t[3] for t in self.last_times)
+        elif self.probe is not None:     # call range by call range, dumping what the asked-for calls wrote
+            launches = self.probe.run(self.rt, fw["name"], vars_, f"step{self.steps:04d}")
         else:
             launches = self.rt.issue(fw["name"], vars_, eager)
         for s, new in batch:

@@ -173,6 +173,10 @@ class Runtime:
         rec.step(program, groups, rows, ctx, graph, 0.0, (time.perf_counter() - t0) * 1e6, n)
         return n
 
+    def issue_range(self, program: str, vars: dict[str, int], lo: int, hi: int) -> int:
+        """Calls [lo, hi) of `program`, eagerly and in order (what activation probes step a program with)."""
+        return self._rt.issue_range(program, vars, lo, hi)
+
     def record(self, directory, rank: int = 0):
         """Start recording every issued step into Parquet traces under `directory` (see `kern_b200.trace`); returns the
         recorder (`rotate()` writes what is buffered, `record(None)` stops)."""

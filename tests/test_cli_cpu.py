@@ -137,3 +137,25 @@ def test_native_kern_binary_verifies_and_cuts(tmp_path):
     for i in range(2):
         m, diags = verify(json.loads((tmp_path / "st" / f"stage{i}.json").read_text()))
         assert m is not None, diags[:3]
+
+
+def test_run_with_activation_probes(tmp_path, capsys):
+    """`kern run --probe-dir`: the program runs call range by call range and the asked-for calls' outputs land as
+    tensors; the generated tokens are the ones an unprobed run gives."""
+    import json
+    import torch
+    from kern_b200 import cli
+
+    base = ["run", "--model", "toy", "--cpu", "--prompt-ids", "1,2,3,4,5", "--steps", "3"]
+    assert cli.main(base) == 0
+    plain = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["tokens"]
+    d = tmp_path / "probes"
+    assert cli.main(base + ["--probe-dir", str(d), "--probe-labels", "l0.ln1,head"]) == 0
+    probed = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["tokens"]
+    assert probed == plain
+    index = json.loads((d / "index.json").read_text())
+    labels = {e["label"] for e in index}
+    assert "l0.ln1" in labels and any(l.endswith("head") for l in labels), labels
+    first = next(e for e in index if e["label"] == "l0.ln1")
+    t = torch.load(d / first["file"])
+    assert list(t.shape) == first["shape"] and t.shape[0] == 5 and bool(torch.isfinite(t.float()).all())
