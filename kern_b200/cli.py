@@ -172,6 +172,25 @@ def cmd_cut(args) -> int:
     return 0
 
 
+def cmd_schema(args) -> int:
+    from . import schema
+
+    if args.validate:
+        errs = schema.validate(json.loads(Path(args.validate).read_text()))
+        for e in errs:
+            print("error:", e)
+        return 1 if errs else 0
+    if args.write:
+        print(schema.write_golden())
+        return 0
+    if args.check:
+        ok = schema.check_golden()
+        print("schema/manifest-v7.schema.json is " + ("up to date" if ok else "STALE: run `python -m kern_b200 schema --write` and commit the diff"))
+        return 0 if ok else 1
+    sys.stdout.write(schema.text())
+    return 0
+
+
 def cmd_kernels(args) -> int:
     from .models.common import kernel_index
 
@@ -442,6 +461,10 @@ def main(argv=None) -> int:
     v = sub.add_parser("verify"); v.add_argument("manifest")
     c = sub.add_parser("cut"); c.add_argument("manifest"); c.add_argument("--at", required=True); c.add_argument("--out", required=True)
     sub.add_parser("kernels")
+    sc = sub.add_parser("schema", help="the JSON Schema of the manifest wire format")
+    sc.add_argument("--check", action="store_true", help="compare with the committed schema/manifest-v7.schema.json; exit 1 on a difference")
+    sc.add_argument("--write", action="store_true", help="rewrite the committed file")
+    sc.add_argument("--validate", help="a manifest to check against the schema (shape only; `verify` does the rest)")
     r = sub.add_parser("run"); common(r)
     r.add_argument("--prompt"); r.add_argument("--prompt-ids"); r.add_argument("--steps", type=int, default=16)
     r.add_argument("--temperature", type=float, default=0.0); r.add_argument("--seed", type=int, default=0)
@@ -468,7 +491,7 @@ def main(argv=None) -> int:
         resolve(args, path, cfg)
         if args.cmd != "test" and not args.manifest and not getattr(args, "model", None):
             ap.error("--manifest, --model or a --target of kern.toml is required")
-    return {"verify": cmd_verify, "cut": cmd_cut, "kernels": cmd_kernels, "run": cmd_run, "test": cmd_test, "bench": cmd_bench,
+    return {"verify": cmd_verify, "cut": cmd_cut, "kernels": cmd_kernels, "schema": cmd_schema, "run": cmd_run, "test": cmd_test, "bench": cmd_bench,
             "workload": cmd_workload, "server": cmd_server, "e2e-logits": cmd_e2e}[args.cmd](args)
 
 
