@@ -464,3 +464,89 @@ extern "C" __global__ void kern_attn_merge_splits(const float* ws_o, const float
     out[(size_t)tk * out_stride + (size_t)head * d + c] = __float2bfloat16(l > 0.f ? acc / l : 0.f);
   }
 }
+
+// Merge the partials of a context-parallel group after an all-gather: rank r's compact workspace ([rows * hq][splits]
+// slots, as a launch with `partial = (0, splits)` writes it) sits at ws + r * rows * splits slots. Same arithmetic as
+// above over ranks * splits slots. grid = tokens * hq, block = D threads (<= 256).
+extern "C" __global__ void kern_attn_merge_ranks(const float* ws_o, const float* ws_ml, __nv_bfloat16* out, int rows, int hq,
+                                                 int d, int splits, int ranks, int out_stride) {
+  pdl_wait();
+  const int row = blockIdx.x;  // token * hq + head
+  if (row >= rows) return;
+  const int tk = row / hq, head = row % hq;
+  float m = -INFINITY;
+  for (int r = 0; r < ranks; ++r)
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, ws_ml[(((size_t)r * rows + row) * splits + s) * 2]);
+  const float m_use = m == -INFINITY ? 0.f : m;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float l = 0.f, acc = 0.f;
+    for (int r = 0; r < ranks; ++r)
+      for (int s = 0; s < splits; ++s) {
+        const size_t b = ((size_t)r * rows + row) * splits + s;
+        const float f = exp2f(ws_ml[b * 2] - m_use);
+        l += ws_ml[b * 2 + 1] * f;
+        acc += ws_o[b * d + c] * f;
+      }
+    out[(size_t)tk * out_stride + (size_t)head * d + c] = __float2bfloat16(l > 0.f ? acc / l : 0.f);
+  }
+}
+
+// Context parallel by position: position p of a sequence lives on member p % world at local index p / world, so a
+// sequence of L positions has ceil((L - rank) / world) of them here. grid = ceil(seqs / 256), block 256.
+extern "C" __global__ void kern_dcp_local_lens(const int* seq_lens, int* local_lens, int seqs, int rank, int world) {
+  pdl_wait();
+  const int s = blockIdx.x * 256 + threadIdx.x;
+  if (s >= seqs) return;
+  const int L = seq_lens[s];
+  local_lens[s] = L > rank ? (L - rank + world - 1) / world : 0;
+}
+
+
+// Start of a context-parallel decode attention: the local length of every sequence, and every partial slot of the
+// call set neutral (m = -inf, l = 0) so that a member whose share of a sequence is empty contributes nothing.
+// grid = seqs, block 128; slots = heads * splits partial slots per sequence row.
+extern "C" __global__ void __launch_bounds__(128)
+    kern_dcp_prepare(const int* seq_lens, int* local_lens, float* ws_ml, int seqs, int rank, int world, int slots) {
+  pdl_wait();
+  const int s = blockIdx.x;
+  if (s >= seqs) return;
+  if (threadIdx.x == 0) {
+    const int L = seq_lens[s];
+    local_lens[s] = L > rank ? (L - rank + world - 1) / world : 0;
+  }
+  for (int i = threadIdx.x; i < slots; i += 128)
+    *reinterpret_cast<float2*>(ws_ml + ((size_t)s * slots + i) * 2) = make_float2(-INFINITY, 0.f);
+}
+
+// Deal the rows of a paged KV pool to a member of a by-position group: local index li of sequence s on member `rank`
+// is position li * world + rank. Copies K and V rows (all kv heads) from the source pool (the whole context, this
+// GPU's) into the destination pool (the member's, possibly another GPU's memory mapped here: plain 16-byte stores).
+// KV layout of both: [page][k|v][kv_head][page_size][head_dim] bf16. grid [ceil(max local rows / 4), seqs], block 128:
+// a warp per row. Tables: [seqs][width] page ids; src_lens = whole lengths.
+// Reference counterpart: crates/kern-runtime/src/push.rs:398-434 (push_rows), :494 (the gather kernel).
+extern "C" __global__ void __launch_bounds__(128)
+    kern_deal_rows_bf16(const __nv_bfloat16* src, __nv_bfloat16* dst, const int* src_table, const int* dst_table,
+                        const int* src_lens, int seqs, int src_width, int dst_width, int hk, int d, int page_size, int rank,
+                        int world, int first_pos, int* err) {
+  pdl_wait();
+  const int s = blockIdx.y;
+  if (s >= seqs) return;
+  const int li = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  const int L = src_lens[s];
+  const long long pos = (long long)li * world + rank;
+  if (pos >= L || pos < first_pos) return;      // first_pos: rows below it were dealt by an earlier call
+  const int sp = (int)(pos / page_size), so = (int)(pos % page_size), dp = li / page_size, dof = li % page_size;
+  if (sp >= src_width || dp >= dst_width) {
+    if (lane == 0) set_error(err, ERR_BOUNDS);
+    return;
+  }
+  const size_t page_elems = (size_t)2 * hk * page_size * d;
+  const __nv_bfloat16* sb = src + (size_t)src_table[(size_t)s * src_width + sp] * page_elems + (size_t)so * d;
+  __nv_bfloat16* db = dst + (size_t)dst_table[(size_t)s * dst_width + dp] * page_elems + (size_t)dof * d;
+  const int vecs = d / 8;
+  for (int i = lane; i < 2 * hk * vecs; i += 32) {
+    const int blk = i / vecs, v = i % vecs;      // blk = (k|v) * hk + head
+    reinterpret_cast<uint4*>(db + (size_t)blk * page_size * d)[v] =
+        reinterpret_cast<const uint4*>(sb + (size_t)blk * page_size * d)[v];
+  }
+}

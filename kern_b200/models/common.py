@@ -304,6 +304,45 @@ def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, 
          "grid": [hk, "seqs", 1], "shared_mem": attn_smem(d), "params": lp, "args": args(9, 10)}]}}
 
 
+def attn_decode_dcp_op(hq: int, hk: int, d: int, page_size: int, table_width: int, q_stride: int, world: int,
+                       group: str = "dcp", splits: int = 4) -> dict:
+    """Decode attention of a member of a by-position (context-parallel) group: positions are dealt round-robin, the
+    member attends over its own pages and leaves un-normalised partials, the group all-gathers them and every member
+    merges (log-sum-exp) to the same rows.
+    Interface [q(kv) buffer, kv state, out, block_table, seq_lens (whole lengths), err, count_o, count_ml, rows_hq, seqs]:
+    the call passes `hq * splits * d`, `hq * splits * 2` and `hq` times `seqs` and `seqs` itself."""
+    iface = ["in buffer<bf16>", "in state", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "out buffer<i32>",
+             "i64", "i64", "i32", "i32"]
+    scratch = {"local_lens": {"dtype": "i32", "shape": ["seqs"]},
+               "ws_o": {"dtype": "f32", "shape": ["seqs", hq * splits * d]}, "ws_ml": {"dtype": "f32", "shape": ["seqs", hq * splits * 2]},
+               "all_o": {"dtype": "f32", "shape": ["seqs", world * hq * splits * d]},
+               "all_ml": {"dtype": "f32", "shape": ["seqs", world * hq * splits * 2]}}
+    prepare = {"module": "attn_paged", "entry": "kern_dcp_prepare", "block": [128, 1, 1], "grid": ["seqs", 1, 1],
+               "params": ["in buffer<i32>", "out buffer<i32>", "out buffer<f32>", "i32", "i32", "i32", "i32"],
+               "args": [{"param": 4}, {"scratch": "local_lens"}, {"scratch": "ws_ml"}, {"param": 9}, {"rank": group},
+                        {"i32": world}, {"i32": hq * splits}]}
+    lp = list(_ATTN_LP)
+    lp[3], lp[4] = "out buffer<f32>", "inout buffer<f32>"
+    lp[6] = "in buffer<i32>"
+    g = hq // hk
+    nblk = -(-1 // max(1, 16 // g))
+    attn = {"module": "attn_paged", "entry": f"kern_attn_decode_paged_d{d}", "block": [160, 1, 1],
+            "grid": [hk * nblk, "seqs", splits], "shared_mem": attn_smem(d), "params": lp,
+            "args": [_kv_map(d, page_size, 1), {"param": 0}, {"param": 2}, {"scratch": "ws_o"}, {"scratch": "ws_ml"}, {"param": 3},
+                     {"scratch": "local_lens"}, {"i64": 0}, {"i64": 0}, {"i64": 0}, {"i32": I32_MAX}, {"i32": hq}, {"i32": hk},
+                     {"i32": q_stride}, {"i32": hq * d}, {"i32": table_width}, {"i32": page_size}, {"i32": 1},
+                     {"i32": splits | (splits << 16)}, {"i32": I32_MAX}, {"f32": (d ** -0.5) * 1.4426950408889634}, {"param": 5}]}
+    gather = lambda src, dst, cnt: {"entry": "extern:nccl_allgather_f32", "params": ["in buffer<f32>", "out buffer<f32>", "i64", "i32"],
+                                    "args": [{"scratch": src}, {"scratch": dst}, {"param": cnt}, {"rank": group}]}
+    merge = {"module": "attn_paged", "entry": "kern_attn_merge_ranks", "block": [min(256, d), 1, 1],
+             "grid": [{"mul": ["seqs", hq]}, 1, 1],
+             "params": ["in buffer<f32>", "in buffer<f32>", "out buffer<bf16>", "i32", "i32", "i32", "i32", "i32", "i32"],
+             "args": [{"scratch": "all_o"}, {"scratch": "all_ml"}, {"param": 2}, {"param": 8}, {"i32": hq}, {"i32": d},
+                      {"i32": splits}, {"i32": world}, {"i32": hq * d}]}
+    return {"params": iface, "impl": {"launches": [prepare, attn, gather("ws_o", "all_o", 6), gather("ws_ml", "all_ml", 7), merge],
+                                      "scratch": scratch}}
+
+
 def attn_plan_op(hq: int, hk: int, seqs_max: int) -> dict:
     """Interface [cu_seqlens, work, work_count, seqs, max_items]; the attention grid's (sequence, block)
     work list. A call passes ``{"var": "seqs"}`` and ``attn_plan_items(...)``."""

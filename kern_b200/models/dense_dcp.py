@@ -1,0 +1,46 @@
+"""The dense decoder as a member of a decode context-parallel group: weights and the batch are replicated, the KV of
+every sequence is dealt over the members by position (position p on member p % w at local index p / w), and the decode
+attention is partial attention over the member's own pages + an all-gather of the partials + one merge.
+
+The manifest is the one-GPU decoder with its `decode` program kept, `prefill` dropped (a context-parallel group only
+decodes: the context arrives dealt from a prefill tier, `ops/attention.deal_rows`), and `attn_decode` replaced. The
+host fills positions and whole sequence lengths as always; the slot of a new token is its local slot on the owning
+member and -1 elsewhere (nothing appended).
+Reference: docs/pool.md:199-211 (`shard: by position`), crates/kern-pool/src/deal.rs:26 (Interleave).
+"""
+from __future__ import annotations
+
+from . import common as C
+from . import dense
+
+
+def build_manifest_dcp(cfg: dense.DenseConfig, world: int, splits: int = 4, group: str = "dcp") -> dict:
+    doc = dense.build_manifest(cfg)
+    hq, hk, d = cfg.heads, cfg.kv_heads, cfg.head_dim
+    doc["model"] = f"{doc['model']}-dcp{world}"
+    doc["topology"] = {"groups": {group: world}}
+    doc["programs"].pop("prefill")
+    for name in ("attn_prefill", "attn_plan", "last_row"):
+        doc["ops"].pop(name, None)
+    for name in ("work", "work_count", "work_d", "work_d_count", "cu_seqlens", "last"):
+        doc["buffers"].pop(name, None)
+    launched = {l.get("module") for op in doc["ops"].values() for l in op["impl"]["launches"]}
+    for name in [m for m in doc["modules"] if m not in launched]:
+        doc["modules"].pop(name)          # modules only the dropped ops used
+    for st in doc["states"].values():
+        st["shard"] = {"by": "position", "group": group}
+    doc["ops"]["attn_decode"] = C.attn_decode_dcp_op(hq, hk, d, cfg.page_size, cfg.table_width, cfg.qkv_dim, world, group, splits)
+    extra = [{"expr": {"mul": ["seqs", hq * splits * d]}}, {"expr": {"mul": ["seqs", hq * splits * 2]}},
+             {"expr": {"mul": ["seqs", hq]}}, {"var": "seqs"}]
+    for call in doc["programs"]["decode"]["calls"]:
+        if call["op"] == "attn_decode":
+            call["args"] = call["args"] + extra
+    return doc
+
+
+def dealt_slot(position: int, pages: list[int], page_size: int, rank: int, world: int) -> int:
+    """The KV slot of `position` on member `rank` (its pages hold its local positions), or -1 on the other members."""
+    if position % world != rank:
+        return -1
+    li = position // world
+    return pages[li // page_size] * page_size + li % page_size

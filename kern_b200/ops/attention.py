@@ -152,6 +152,41 @@ def merge_partials(ws_o, ws_ml, out, rows: int, hq: int, d: int, total: int) -> 
     return out
 
 
+def merge_rank_partials(ws_o, ws_ml, out, rows: int, hq: int, d: int, splits: int, ranks: int) -> torch.Tensor:
+    """Merge the all-gathered compact workspaces of a context-parallel group: `ws_o` is [ranks][rows * hq][splits][d],
+    `ws_ml` [ranks][rows * hq][splits][2], each rank's part written by a decode launch with ``partial=(0, splits)``."""
+    k = Kernels.get(out.device)
+    n = rows * hq
+    k.launch("attn_paged", "kern_attn_merge_ranks", (n,), (min(256, d),),
+             [ptr(ws_o), ptr(ws_ml), ptr(out), i32(n), i32(hq), i32(d), i32(splits), i32(ranks), i32(out.stride(0))])
+    return out
+
+
+def dcp_local_lens(seq_lens: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Positions of each sequence that live on member `rank` of a by-position group of `world`."""
+    out = torch.empty_like(seq_lens)
+    n = seq_lens.numel()
+    Kernels.get(seq_lens.device).launch("attn_paged", "kern_dcp_local_lens", ((n + 255) // 256,), (256,),
+                                        [ptr(seq_lens), ptr(out), i32(n), i32(rank), i32(world)])
+    return out
+
+
+def deal_rows(src_kv: torch.Tensor, dst_kv: torch.Tensor, src_table: torch.Tensor, dst_table: torch.Tensor,
+              src_lens: torch.Tensor, hk: int, d: int, page_size: int, rank: int, world: int, first_pos: int = 0) -> None:
+    """Copy the KV rows of positions p = li * world + rank (p >= first_pos) of every sequence from a pool holding the
+    whole context into member `rank`'s pool at local index li. Pools: [page][k|v][kv_head][page_size][d] bf16 (any
+    dtype view of the same bytes); `dst_kv` may be another GPU's mapped memory."""
+    k = Kernels.get(src_kv.device)
+    seqs = src_lens.numel()
+    max_local = (int(src_lens.max()) + world - 1) // world
+    if max_local <= 0:
+        return
+    k.launch("attn_paged", "kern_deal_rows_bf16", ((max_local + 3) // 4, seqs), (128,),
+             [ptr(src_kv), ptr(dst_kv), ptr(src_table), ptr(dst_table), ptr(src_lens), i32(seqs), i32(src_table.shape[1]),
+              i32(dst_table.shape[1]), i32(hk), i32(d), i32(page_size), i32(rank), i32(world), i32(first_pos),
+              ptr(k.err_word())])
+
+
 # ---- PyTorch fp32 references ---------------------------------------------------------------------
 def rope_reference(x: torch.Tensor, positions: torch.Tensor, rot: int, theta: float) -> torch.Tensor:
     """x [tokens, heads, d] -> rotate-half RoPE over the first ``rot`` dims, fp32 math."""

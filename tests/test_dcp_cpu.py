@@ -1,0 +1,32 @@
+"""Decode context parallelism, the parts that need no GPU: the member manifest verifies and projects its by-position
+shards, and the host's dealing of a new token's slot agrees with the pool library's `deal`."""
+import json
+
+from kern_b200.models import dense, dense_dcp
+from kern_b200.runtime import verify
+
+
+def test_member_manifest_verifies_and_projects_shards():
+    doc = dense_dcp.build_manifest_dcp(dense.TINY, 4)
+    m, diags = verify(doc)
+    assert m is not None, diags
+    p = json.loads(m.protocol(sampled=False))
+    assert p["shards"], p.keys()
+    assert "prefill" not in doc["programs"]
+    entries = [l["entry"] for l in doc["ops"]["attn_decode"]["impl"]["launches"]]
+    assert entries == ["kern_dcp_prepare", "kern_attn_decode_paged_d64", "extern:nccl_allgather_f32", "extern:nccl_allgather_f32",
+                       "kern_attn_merge_ranks"]
+    from kern_b200 import schema
+    assert schema.validate(doc) == []
+
+
+def test_dealt_slot_follows_position_modulo_world():
+    page = 16
+    pages = [7, 9, 4]
+    for world in (2, 4):
+        for rank in range(world):
+            owned = [p for p in range(90) if dense_dcp.dealt_slot(p, pages, page, rank, world) >= 0]
+            assert owned == [p for p in range(90) if p % world == rank]
+            for p in owned:
+                li = p // world
+                assert dense_dcp.dealt_slot(p, pages, page, rank, world) == pages[li // page] * page + li % page

@@ -74,3 +74,24 @@ def test_collective_externs(world):
     assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
     line = next(json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))
     assert line["world"] == world and all(r["ok"] for r in line["results"]), line
+
+
+def test_decode_context_parallel_one_rank(cuda):
+    """The dealt-position path with a group of one: local lengths, partial slots, merge over ranks."""
+    from kern_b200.parallel import dcp_check
+
+    assert dcp_check.main(["--lens", "1", "65", "300", "--model"]) == 0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_decode_context_parallel(world):
+    """Positions dealt over the ranks, per-rank partial attention, all-gather over NVLink, one merge."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29540 + world), "-m", "kern_b200.parallel.dcp_check", "--model"]
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
+    lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 2 and all(l["ok"] and l["world"] == world for l in lines), lines
