@@ -697,6 +697,23 @@ void Runtime::connect(const std::string& group, const std::vector<std::map<std::
   }
 }
 
+std::string Runtime::export_region(const std::string& name) { return dev_->ipc_export(region(name).first); }
+
+uint64_t Runtime::import_region(const std::string& handle) {
+  const uint64_t p = dev_->ipc_import(handle);
+  imported_ptrs_.push_back(p);
+  return p;
+}
+
+void Runtime::push_unit(const std::string& state, uint64_t dst_base, int64_t src_unit, int64_t dst_unit) {
+  auto it = states_.find(state);
+  if (it == states_.end()) throw std::runtime_error("no state named `" + state + "`");
+  const auto& st = it->second;
+  if (src_unit < 0 || (uint64_t)src_unit >= st.units || dst_unit < 0)
+    throw std::runtime_error("push of `" + state + "` names a unit outside the pool");
+  dev_->d2d(dst_base + (uint64_t)dst_unit * st.unit_bytes, st.ptr + (uint64_t)src_unit * st.unit_bytes, st.unit_bytes, stream_);
+}
+
 bool Runtime::peers_connected() const {
   for (auto& kv : m_.buffers)
     if (kv.second.kind == BufferKind::Peer && !imported_.count(kv.first)) return false;

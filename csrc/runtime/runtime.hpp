@@ -149,6 +149,11 @@ class Runtime {
   // handles of every member of `group` in member order -> fills each peer buffer of that group
   void connect(const std::string& group, const std::vector<std::map<std::string, std::string>>& members);
   bool peers_connected() const;
+  // Another process's pool, for pushing pages and slots into it (prefill tier -> decode tier): the owner exports the
+  // region of a state, the pusher maps it and copies whole units (a page of a paged state, a slot of a per-sequence one).
+  std::string export_region(const std::string& name);
+  uint64_t import_region(const std::string& handle);
+  void push_unit(const std::string& state, uint64_t dst_base, int64_t src_unit, int64_t dst_unit);
   std::set<std::string> nccl_groups() const;     // groups named by `extern:nccl_*` launches: each needs connect() first
 
   // ---- hosted mode ----

@@ -222,6 +222,25 @@ class Runtime:
             self._rt.copy_slot(*copies["slot"])
 
     # ---- groups ----
+    # ---- another process's pool (prefill tier -> decode tier) ----
+    def export_states(self) -> dict[str, bytes]:
+        """A handle per state of this runtime's pools, for a process that will push pages and slots into them."""
+        return {name: self._rt.export_region(name) for name in self.doc["states"]}
+
+    def map_pool(self, handles: dict[str, bytes]) -> dict[str, int]:
+        """Map another process's exported states; the result goes to `push`."""
+        return {name: self._rt.import_region(h) for name, h in handles.items()}
+
+    def push(self, mapped: dict[str, int], plan: dict) -> None:
+        """Run a push plan (`serve.pd.moves`): whole pages of every paged state, the slot of every per-sequence one,
+        from this runtime's pools into the mapped ones, on this runtime's stream (one device copy per unit)."""
+        for name, s in self.doc["states"].items():
+            if s.get("bytes_per_token"):
+                for a, b in plan["pages"]:
+                    self._rt.push_unit(name, mapped[name], a, b)
+            elif s.get("bytes_per_seq") and plan.get("slot") is not None:
+                self._rt.push_unit(name, mapped[name], plan["slot"][0], plan["slot"][1])
+
     def rank(self, group: str) -> int:
         return self._rt.rank(group)
 

@@ -95,3 +95,18 @@ def test_decode_context_parallel(world):
     assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
     lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
     assert len(lines) == 2 and all(l["ok"] and l["world"] == world for l in lines), lines
+
+
+@pytest.mark.parametrize("lined", [False, True])
+def test_prefill_decode_two_gpu_processes(lined):
+    """A prefill process and a decode process on two GPUs: seats reserved, pages and the state slot pushed into the
+    decode tier's exported pools by device copies, tokens equal to the exact model's twin."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(29560 + int(lined)), "-m", "kern_b200.parallel.pd_check"] + (["--lined"] if lined else [])
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
+    line = next(json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))
+    assert line["ok"] and line["busy_seen"], line
