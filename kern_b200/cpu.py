@@ -153,6 +153,26 @@ def _attention(prefill):
             posn = torch.arange(L - R, L)
             mask = torch.arange(L)[None, :] <= posn[:, None]
             sc = sc.masked_fill(~mask[None], float("-inf"))
+            if (splits >> 16) and isinstance(ws_o, torch.Tensor):
+                # context-parallel partial mode: un-normalised (o, m, l) in the log2 domain into the first of this
+                # launch's slots, the other slots neutral; a merge over every member's slots finishes
+                nsplit, base, total = splits & 0xff, (splits >> 8) & 0xff, splits >> 16
+                s2 = sc * 1.4426950408889634                                      # [hq, R, L]
+                m = s2.max(-1).values                                             # [hq, R]
+                pr = torch.exp2(s2 - m[..., None])
+                l = pr.sum(-1)
+                o = torch.einsum("hrl,lhd->rhd", pr, vv.repeat_interleave(grp, 1))   # [R, hq, d]
+                wo = ws_o.view(-1, d)
+                wml = ws_ml.view(-1, 2)
+                for r in range(R):
+                    for hh in range(hq):
+                        at = ((r0 + r) * hq + hh) * total + base
+                        wo[at] = o[r, hh]
+                        wml[at, 0], wml[at, 1] = m[hh, r], l[hh, r]
+                        for x in range(1, nsplit):
+                            wo[at + x] = 0
+                            wml[at + x, 0], wml[at + x, 1] = float("-inf"), 0.0
+                continue
             o = torch.einsum("hrl,lhd->rhd", torch.softmax(sc, -1), vv.repeat_interleave(grp, 1))
             torch.as_strided(out, (R, hq * d), (out_stride, 1), out.storage_offset() + r0 * out_stride).copy_(o.reshape(R, hq * d).to(out.dtype))
     return run
@@ -744,3 +764,46 @@ CPU_KERNELS.update({
     "extern:cublaslt_bf16_tn": _extern_gemm(False, False, False), "extern:cublaslt_bf16_tn_acc": _extern_gemm(True, False, False),
     "extern:cublas_bf16_tn_f32": _extern_gemm(False, True, False), "extern:cublaslt_fp8_tn": _extern_gemm(False, False, True),
     "extern:cublaslt_fp8_tn_f32": _extern_gemm(False, True, True)})
+
+
+# ---- decode context parallelism (statements of attn_paged.cu's dealing and merging kernels) -------------------------
+def _k_dcp_local_lens(g, seq_lens, local_lens, seqs, rank, world):
+    L = seq_lens[:seqs].long()
+    local_lens[:seqs] = torch.where(L > rank, (L - rank + world - 1) // world, torch.zeros_like(L)).to(local_lens.dtype)
+
+
+def _k_dcp_prepare(g, seq_lens, local_lens, ws_ml, seqs, rank, world, slots):
+    n = g[0]
+    _k_dcp_local_lens(g, seq_lens, local_lens, n, rank, world)
+    w = ws_ml[: n * slots * 2].view(-1, 2)
+    w[:, 0], w[:, 1] = float("-inf"), 0.0
+
+
+def _k_attn_merge_ranks(g, ws_o, ws_ml, out, rows, hq, d, splits, ranks, out_stride):
+    n = g[0]                                     # rows * hq as launched
+    o = ws_o[: ranks * n * splits * d].view(ranks, n, splits, d).permute(1, 0, 2, 3).reshape(n, ranks * splits, d)
+    ml = ws_ml[: ranks * n * splits * 2].view(ranks, n, splits, 2).permute(1, 0, 2, 3).reshape(n, ranks * splits, 2)
+    m = ml[..., 0].max(-1, keepdim=True).values
+    m = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+    f = torch.exp2(ml[..., 0] - m)
+    l = (ml[..., 1] * f).sum(-1)
+    acc = (o * f[..., None]).sum(1)
+    res = torch.where(l[:, None] > 0, acc / l[:, None].clamp_min(1e-38), torch.zeros_like(acc))
+    tokens = n // hq
+    torch.as_strided(out, (tokens, hq * d), (out_stride, 1), out.storage_offset()).copy_(res.view(tokens, hq * d).to(out.dtype))
+
+
+def _k_deal_rows(g, src, dst, src_table, dst_table, src_lens, seqs, src_width, dst_width, hk, d, page, rank, world, first_pos, err):
+    sp = src.view(torch.bfloat16).view(-1, 2, hk, page, d)
+    dp = dst.view(torch.bfloat16).view(-1, 2, hk, page, d)
+    st, dt = src_table.view(-1, src_width), dst_table.view(-1, dst_width)
+    for s in range(g[1]):
+        for pos in range(rank, int(src_lens[s]), world):
+            if pos < first_pos:
+                continue
+            li = pos // world
+            dp[int(dt[s, li // page]), :, :, li % page] = sp[int(st[s, pos // page]), :, :, pos % page]
+
+
+CPU_KERNELS.update({"kern_dcp_local_lens": _k_dcp_local_lens, "kern_dcp_prepare": _k_dcp_prepare,
+                    "kern_attn_merge_ranks": _k_attn_merge_ranks, "kern_deal_rows_bf16": _k_deal_rows})

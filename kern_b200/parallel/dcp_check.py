@@ -18,7 +18,7 @@ import torch
 import torch.distributed as dist
 
 
-def check_model(rank: int, world: int, local: int, steps: int = 6) -> dict:
+def check_model(rank: int, world: int, local: int, steps: int = 6, cpu: bool = False) -> dict:
     """The dense decoder as a context-parallel decode group: every rank prefills the prompts on a whole-context
     runtime of its own (the stand-in for a prefill tier), deals the KV rows to its member pool, and the group decodes;
     logits are compared step by step with the whole-context runtime decoding the same tokens."""
@@ -30,18 +30,28 @@ def check_model(rank: int, world: int, local: int, steps: int = 6) -> dict:
     from . import group
 
     cfg = dense.TINY
-    dev = torch.device(f"cuda:{local}")
+    dev = torch.device("cpu" if cpu else f"cuda:{local}")
     weights = dense.random_weights(cfg, seed=0, std=0.05)
-    full = Runtime(dense.build_manifest(cfg), gpu=local, tokens=cfg.page_size * 64, slots=8)
-    full.load_tensors(lambda name: weights[name].to(dev))
-    full.once()
-    eng = Engine(full)
-    rt = Runtime(dense_dcp.build_manifest_dcp(cfg, world), gpu=local, topology={"dcp": (rank, world)}, tokens=cfg.page_size * 64, slots=8)
-    rt.load_tensors(lambda name: weights[name].to(dev))
-    if world > 1:
-        group.start(rt)
-    else:
+    if cpu:       # gloo ranks and the host-memory executor: the same manifests, PyTorch statements per kernel
+        from ..cpu import CPU_KERNELS, CpuRuntime
+
+        full = CpuRuntime(dense.build_manifest(cfg), weights=weights, tokens=cfg.page_size * 64)
+        rt = CpuRuntime(dense_dcp.build_manifest_dcp(cfg, world), weights=weights, tokens=cfg.page_size * 64,
+                        topology={"dcp": (rank, world)})
+        full.once()
         rt.once()
+    else:
+        full = Runtime(dense.build_manifest(cfg), gpu=local, tokens=cfg.page_size * 64, slots=8)
+        full.load_tensors(lambda name: weights[name].to(dev))
+        full.once()
+        rt = Runtime(dense_dcp.build_manifest_dcp(cfg, world), gpu=local, topology={"dcp": (rank, world)},
+                     tokens=cfg.page_size * 64, slots=8)
+        rt.load_tensors(lambda name: weights[name].to(dev))
+        if world > 1:
+            group.start(rt)
+        else:
+            rt.once()
+    eng = Engine(full)
     member = Engine(rt)          # its fills and readers; pages are assigned by hand below
     g = torch.Generator().manual_seed(3)
     prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (45, 3, 130, 17)]
@@ -62,11 +72,17 @@ def check_model(rank: int, world: int, local: int, steps: int = 6) -> dict:
         src_table[i, : len(pg)] = torch.tensor(pg, dtype=torch.int32)
         dst_table[i, : len(local_pages[i])] = torch.tensor(local_pages[i], dtype=torch.int32)
     lens = torch.tensor([len(p) for p in prompts], dtype=torch.int32, device=dev)
-    full.synchronize()
     for i in range(cfg.layers):
-        A.deal_rows(full.tensor(f"kv.l{i}"), rt.tensor(f"kv.l{i}"), src_table, dst_table, lens, cfg.kv_heads, cfg.head_dim, page,
-                    rank, world)
-    torch.cuda.synchronize()
+        if cpu:
+            CPU_KERNELS["kern_deal_rows_bf16"]((1, len(prompts), 1), full.states[f"kv.l{i}"], rt.states[f"kv.l{i}"], src_table,
+                                               dst_table, lens, len(prompts), W, W, cfg.kv_heads, cfg.head_dim, page, rank,
+                                               world, 0, None)
+        else:
+            full.synchronize()
+            A.deal_rows(full.tensor(f"kv.l{i}"), rt.tensor(f"kv.l{i}"), src_table, dst_table, lens, cfg.kv_heads, cfg.head_dim,
+                        page, rank, world)
+    if not cpu:
+        torch.cuda.synchronize()
     worst, agree, length = 0.0, 0, [len(p) for p in prompts]
     for _ in range(steps):
         ref_next = eng.step([(s, [t]) for s, t in zip(seqs, toks)])
@@ -79,7 +95,8 @@ def check_model(rank: int, world: int, local: int, steps: int = 6) -> dict:
             member._write(name, dtype, col)
         rt.issue(call.forward["name"], call.vars)
         got_next = member.read_tokens(call.forward, call.groups)[: len(prompts)]
-        rt.check_error()
+        if not cpu:
+            rt.check_error()
         logits = rt.tensor("logits")[: len(prompts)].float()
         worst = max(worst, float((logits - ref_logits).abs().max()))
         agree += sum(int(a[0] == b[0]) for a, b in zip(got_next, ref_next))
@@ -95,8 +112,23 @@ def main(argv=None) -> int:
     ap.add_argument("--lens", type=int, nargs="+", default=[1, 3, 64, 65, 300, 777, 4099])
     ap.add_argument("--splits", type=int, default=2)
     ap.add_argument("--time", action="store_true")
+    ap.add_argument("--cpu", action="store_true", help="gloo ranks and the host-memory executor (the model check only)")
     a = ap.parse_args(argv)
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    if a.cpu:
+        if world > 1:
+            dist.init_process_group("gloo")
+        ml = check_model(rank, world, local, cpu=True)
+        okm = torch.tensor([int(ml["ok"])])
+        if world > 1:
+            dist.all_reduce(okm, op=dist.ReduceOp.MIN)
+        ml["ok"] = bool(okm.item())
+        if rank == 0:
+            print(json.dumps(dict(ml, backend="gloo")), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return 0 if ml["ok"] else 1
     torch.cuda.set_device(local)
     dev = torch.device(f"cuda:{local}")
     if world > 1:

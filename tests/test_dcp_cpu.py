@@ -30,3 +30,19 @@ def test_dealt_slot_follows_position_modulo_world():
             for p in owned:
                 li = p // world
                 assert dense_dcp.dealt_slot(p, pages, page, rank, world) == pages[li // page] * page + li % page
+
+
+def test_dense_decoder_as_a_two_rank_decode_group_over_gloo():
+    """Two CPU ranks: each prefills on a whole-context runtime, deals its KV rows into its member pool, and the group
+    decodes through partial attention + all-gather + merge; logits equal the whole-context decoder's."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29657", "-m", "kern_b200.parallel.dcp_check", "--cpu"]
+    p = subprocess.run(cmd, cwd=root, env=dict(os.environ, PYTHONPATH=root), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, (p.stdout[-2000:], p.stderr[-2000:])
+    line = next(json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))
+    assert line["ok"] and line["world"] == 2 and line["tokens_agree"] == line["of"], line
