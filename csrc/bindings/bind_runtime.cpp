@@ -117,5 +117,6 @@ void bind_runtime(py::module_& m) {
       .def("export_region", [](Runtime& r, const std::string& name) { return py::bytes(r.export_region(name)); })
       .def("import_region", [](Runtime& r, py::bytes h) { return r.import_region(std::string(h)); })
       .def("push_unit", &Runtime::push_unit)
+      .def("push_bytes", &Runtime::push_bytes)
       .def("bind_host", &Runtime::bind_host);
 }

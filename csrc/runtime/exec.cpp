@@ -714,6 +714,12 @@ void Runtime::push_unit(const std::string& state, uint64_t dst_base, int64_t src
   dev_->d2d(dst_base + (uint64_t)dst_unit * st.unit_bytes, st.ptr + (uint64_t)src_unit * st.unit_bytes, st.unit_bytes, stream_);
 }
 
+void Runtime::push_bytes(const std::string& name, uint64_t dst_base, uint64_t nbytes) {
+  auto r = region(name);
+  if (nbytes > r.second) throw std::runtime_error("push of `" + name + "`: " + std::to_string(nbytes) + " bytes asked, the region holds " + std::to_string(r.second));
+  if (nbytes) dev_->d2d(dst_base, r.first, nbytes, stream_);
+}
+
 bool Runtime::peers_connected() const {
   for (auto& kv : m_.buffers)
     if (kv.second.kind == BufferKind::Peer && !imported_.count(kv.first)) return false;

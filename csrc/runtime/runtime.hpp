@@ -154,6 +154,7 @@ class Runtime {
   std::string export_region(const std::string& name);
   uint64_t import_region(const std::string& handle);
   void push_unit(const std::string& state, uint64_t dst_base, int64_t src_unit, int64_t dst_unit);
+  void push_bytes(const std::string& name, uint64_t dst_base, uint64_t nbytes);   // the first nbytes of a buffer (a crossing workspace into the next stage's landing buffer)
   std::set<std::string> nccl_groups() const;     // groups named by `extern:nccl_*` launches: each needs connect() first
 
   // ---- hosted mode ----

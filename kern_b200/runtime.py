@@ -241,6 +241,14 @@ class Runtime:
             elif s.get("bytes_per_seq") and plan.get("slot") is not None:
                 self._rt.push_unit(name, mapped[name], plan["slot"][0], plan["slot"][1])
 
+    def export_buffers(self, names) -> dict[str, bytes]:
+        """Handles of buffers another process will write (a pipeline stage's landing buffers)."""
+        return {n: self._rt.export_region(n) for n in names}
+
+    def push_bytes(self, name: str, dst_ptr: int, nbytes: int) -> None:
+        """The first `nbytes` of buffer `name` into mapped memory of another process, on this runtime's stream."""
+        self._rt.push_bytes(name, dst_ptr, nbytes)
+
     def rank(self, group: str) -> int:
         return self._rt.rank(group)
 

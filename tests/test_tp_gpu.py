@@ -110,3 +110,18 @@ def test_prefill_decode_two_gpu_processes(lined):
     assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
     line = next(json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))
     assert line["ok"] and line["busy_seen"], line
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_pipeline_with_a_process_per_stage(world):
+    """`cut` stage manifests on their own GPUs and processes; crossing workspaces pushed into the next stage's exported
+    landing buffers; tokens equal the uncut model's."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29570 + world), "-m", "kern_b200.parallel.pp_check"]
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
+    line = next(json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))
+    assert line["ok"] and line["stages"] == world and line["crossing_bytes"] > 0, line
