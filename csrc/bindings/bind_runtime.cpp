@@ -12,7 +12,7 @@ void bind_runtime(py::module_& m) {
   py::class_<Runtime, std::shared_ptr<Runtime>>(m, "Runtime")
       .def(py::init([](const std::string& manifest_text, const std::string& kernels_dir, int gpu,
                        std::map<std::string, std::pair<uint64_t, uint64_t>> topology, uint64_t tokens, uint64_t slots,
-                       double memory_fraction, uint64_t stream) {
+                       double memory_fraction, uint64_t stream, bool guard_bands) {
              Errors errs;
              Manifest mf = parse_manifest_text(manifest_text, errs);
              if (errs.empty()) errs = verify_manifest(mf);
@@ -27,11 +27,12 @@ void bind_runtime(py::module_& m) {
              cap.tokens = tokens;
              cap.slots = slots;
              cap.memory_fraction = memory_fraction;
+             cap.guard_bands = guard_bands;
              return std::make_shared<Runtime>(std::move(mf), kernels_dir, gpu, std::move(topo), cap, stream);
            }),
            py::arg("manifest"), py::arg("kernels"), py::arg("gpu") = 0,
            py::arg("topology") = std::map<std::string, std::pair<uint64_t, uint64_t>>(), py::arg("tokens") = 0,
-           py::arg("slots") = 0, py::arg("memory_fraction") = 0.9, py::arg("stream") = 0)
+           py::arg("slots") = 0, py::arg("memory_fraction") = 0.9, py::arg("stream") = 0, py::arg("guard_bands") = false)
       .def("manifest_json", [](Runtime& r) { return manifest_to_json(r.manifest()).dump(1); })
       .def("protocol_json", [](Runtime& r) -> py::object {
         if (!r.protocol()) return py::none();
@@ -114,6 +115,7 @@ void bind_runtime(py::module_& m) {
         }
         r.connect(group, ms);
       })
+      .def("check_guards", &Runtime::check_guards)
       .def("export_region", [](Runtime& r, const std::string& name) { return py::bytes(r.export_region(name)); })
       .def("import_region", [](Runtime& r, py::bytes h) { return r.import_region(std::string(h)); })
       .def("push_unit", &Runtime::push_unit)

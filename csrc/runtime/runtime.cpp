@@ -79,11 +79,11 @@ Runtime::~Runtime() {
     for (auto& g : graphs_) dev_->graph_destroy(g.second.exec);
     for (auto p : imported_ptrs_) dev_->ipc_close(p);
     for (auto& kv : nccl_comms_) NcclApi::get().CommDestroy(kv.second);
-    for (auto& kv : buffers_) if (!kv.second.borrowed && !kv.second.host) dev_->free(kv.second.ptr);
+    for (auto& kv : buffers_) if (!kv.second.borrowed && !kv.second.host) dev_->free(kv.second.ptr - guard_);
     for (auto& kv : buffers_) if (!kv.second.borrowed && kv.second.host) dev_->host_free(reinterpret_cast<void*>(kv.second.ptr));
-    for (auto& kv : states_) if (!kv.second.borrowed) dev_->free(kv.second.ptr);
-    for (auto& o : scratch_) for (auto& kv : o.second) dev_->free(kv.second.ptr);
-    if (err_word_) dev_->free(err_word_);
+    for (auto& kv : states_) if (!kv.second.borrowed) dev_->free(kv.second.ptr - guard_);
+    for (auto& o : scratch_) for (auto& kv : o.second) dev_->free(kv.second.ptr - guard_);
+    if (err_word_) dev_->free(err_word_ - guard_);
     if (staging_) dev_->host_free(staging_);
     for (auto s : lane_streams_) Cuda::get().cuStreamDestroy_(s);
     for (auto e : lane_events_) Cuda::get().cuEventDestroy_(e);
@@ -146,12 +146,22 @@ void Runtime::allocate() {
     auto st = m_.states.find(*b.domain->index_into);
     if (st != m_.states.end() && st->second.is_paged()) page_unit_ = lcm64(page_unit_, std::max<uint64_t>(1, b.domain->stride));
   }
-  auto zero_alloc = [&](uint64_t bytes) {
-    uint64_t p = dev_->alloc(bytes);
-    dev_->memset8(p, 0, bytes ? bytes : 16, stream_);
-    return p;
+  bool multi = false;
+  for (auto& kv : topo_) multi |= kv.second.size >= 2;
+  guard_ = cap_.guard_bands && !multi ? 256 : 0;      // exported handles name an allocation's base: no bands on 2+ ranks
+  auto zero_alloc = [&](uint64_t bytes, const std::string& name) {
+    const uint64_t pay = (bytes ? bytes : 16);
+    const uint64_t padded = (pay + 255) / 256 * 256;      // the trailing band starts 256-byte aligned, right after the payload's last line
+    uint64_t p = dev_->alloc(padded + 2 * guard_);
+    if (guard_) {
+      dev_->memset8(p, 0xA5, guard_, stream_);
+      dev_->memset8(p + guard_ + pay, 0xA5, padded - pay + guard_, stream_);
+      guards_.push_back({name, p, pay});
+    }
+    dev_->memset8(p + guard_, 0, pay, stream_);
+    return p + guard_;
   };
-  err_word_ = zero_alloc(256);
+  err_word_ = zero_alloc(256, "error word");
   for (auto& kv : m_.buffers) {
     const Buffer& b = kv.second;
     auto bytes = b.bytes(vmax);
@@ -163,7 +173,7 @@ void Runtime::allocate() {
       a.host = true;
       a.ptr = reinterpret_cast<uint64_t>(dev_->host_alloc(a.bytes));
     } else {
-      a.ptr = zero_alloc(a.bytes);
+      a.ptr = zero_alloc(a.bytes, kv.first);
     }
     buffers_[kv.first] = a;
   }
@@ -176,7 +186,7 @@ void Runtime::allocate() {
       if (!bytes) throw std::runtime_error("op `" + okv.first + "` scratch `" + skv.first + "`: size overflows");
       Allocation a;
       a.bytes = *bytes;
-      a.ptr = zero_alloc(a.bytes);
+      a.ptr = zero_alloc(a.bytes, okv.first + "." + skv.first);
       scratch_[okv.first][skv.first] = a;
     }
   // states: per-sequence and fixed first, then the paged ones share what is asked for (or what is left)
@@ -191,10 +201,10 @@ void Runtime::allocate() {
       a.unit_bytes = s.bytes_per_seq;
       a.units = slots_ + 1;
       a.bytes = a.unit_bytes * a.units;
-      a.ptr = zero_alloc(a.bytes);
+      a.ptr = zero_alloc(a.bytes, kv.first);
     } else if (s.bytes) {
       a.bytes = s.bytes;
-      a.ptr = zero_alloc(a.bytes);
+      a.ptr = zero_alloc(a.bytes, kv.first);
     } else {
       a.paged = true;
       token_bytes += s.bytes_per_token;
@@ -219,9 +229,29 @@ void Runtime::allocate() {
       a.unit_bytes = kv.second.bytes_per_token * page_unit_;
       a.units = pages_;
       a.bytes = a.unit_bytes * a.units;
-      a.ptr = zero_alloc(a.bytes);
+      a.ptr = zero_alloc(a.bytes, kv.first);
     }
   }
+}
+
+std::vector<std::string> Runtime::check_guards() {
+  std::vector<std::string> bad;
+  if (!guard_) return bad;
+  dev_->make_current();
+  dev_->stream_sync(stream_);
+  std::vector<uint8_t> band(2 * guard_ + 256);
+  for (auto& g : guards_) {
+    const uint64_t padded = (g.bytes + 255) / 256 * 256, tail = padded - g.bytes + guard_;
+    dev_->d2h(band.data(), g.base, guard_, stream_);
+    dev_->d2h(band.data() + guard_, g.base + guard_ + g.bytes, tail, stream_);
+    dev_->stream_sync(stream_);
+    bool before = true, after = true;
+    for (uint64_t i = 0; i < guard_; ++i) before &= band[i] == 0xA5;
+    for (uint64_t i = 0; i < tail; ++i) after &= band[guard_ + i] == 0xA5;
+    if (!before) bad.push_back(g.name + " (before)");
+    if (!after) bad.push_back(g.name + " (after)");
+  }
+  return bad;
 }
 
 bool Runtime::awaits_host() const {

@@ -27,6 +27,8 @@ struct Capacity {
   uint64_t tokens = 0;     // token capacity of the paged states (0: fit what the device has left)
   uint64_t slots = 0;      // per-sequence state slots (excluding the null line)
   double memory_fraction = 0.9;   // of free device memory the paged states may take when tokens == 0
+  bool guard_bands = false;       // test mode: a 256-byte canary band before and after every device allocation of the
+                                  // runtime (buffers, scratch, states), checked by check_guards(); one rank only
 };
 
 struct GroupRank {
@@ -148,6 +150,9 @@ class Runtime {
   std::map<std::string, std::string> export_handles();
   // handles of every member of `group` in member order -> fills each peer buffer of that group
   void connect(const std::string& group, const std::vector<std::map<std::string, std::string>>& members);
+  // Names of the allocations whose canary bands no longer hold their pattern ("x (after)", "op.scratch (before)"); empty
+  // when guard bands are off. Synchronises the stream.
+  std::vector<std::string> check_guards();
   bool peers_connected() const;
   // Another process's pool, for pushing pages and slots into it (prefill tier -> decode tier): the owner exports the
   // region of a state, the pusher maps it and copies whole units (a page of a paged state, a slot of a per-sequence one).
@@ -186,6 +191,9 @@ class Runtime {
   std::map<std::string, std::map<std::string, Allocation>> scratch_;   // op -> scratch name -> allocation
   std::map<std::string, std::vector<uint64_t>> imported_;             // peer buffer -> mapped addresses
   std::vector<uint64_t> imported_ptrs_;
+  struct Guard { std::string name; uint64_t base, bytes; };     // base = start of the leading band; bytes = payload size
+  std::vector<Guard> guards_;
+  uint64_t guard_ = 0;                                            // band size in bytes (0: off)
   std::map<std::string, void*> nccl_comms_;      // group -> communicator of the `extern:nccl_*` launches
   std::map<std::string, NcclUniqueId> nccl_ids_;  // ids this rank (index 0 of the group) created and offers
   uint64_t page_unit_ = 1, pages_ = 0, slots_ = 0;

@@ -47,7 +47,7 @@ def verify(manifest, strict_multicast: bool = False):
 class Runtime:
     def __init__(self, manifest, kernels: str | Path | None = None, weights=None, gpu: int = 0,
                  topology: dict[str, tuple[int, int]] | None = None, tokens: int = 0, slots: int = 0,
-                 memory_fraction: float = 0.9, stream: int | None = None):
+                 memory_fraction: float = 0.9, stream: int | None = None, guard_bands: bool = False):
         if not _native.cuda_available():
             raise RuntimeError("kern_b200.Runtime needs a CUDA device; use kern_b200.cpu.CpuRuntime on a machine without one")
         text = manifest_text(manifest)
@@ -57,7 +57,7 @@ class Runtime:
             self._stream = torch.cuda.Stream(device=gpu) if stream is None else None
             raw = self._stream.cuda_stream if stream is None else stream
             self._rt = _native.Runtime(text, str(kernels or KERNELS_DIR), gpu, dict(topology or {}), tokens, slots,
-                                       memory_fraction, raw)
+                                       memory_fraction, raw, guard_bands)
         self.doc = json.loads(self._rt.manifest_json())
         pj = self._rt.protocol_json()
         self.protocol = json.loads(pj) if pj else None
@@ -248,6 +248,11 @@ class Runtime:
     def push_bytes(self, name: str, dst_ptr: int, nbytes: int) -> None:
         """The first `nbytes` of buffer `name` into mapped memory of another process, on this runtime's stream."""
         self._rt.push_bytes(name, dst_ptr, nbytes)
+
+    def check_guards(self) -> list[str]:
+        """With `guard_bands=True` (test mode): the allocations whose canary bands were written over since load —
+        "name (before)" / "name (after)" — the sign of a kernel that wrote outside its buffer without faulting."""
+        return list(self._rt.check_guards())
 
     def rank(self, group: str) -> int:
         return self._rt.rank(group)

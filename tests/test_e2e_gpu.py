@@ -126,3 +126,29 @@ def test_integer_model_served_on_gpu_equals_twin(cuda, lined):
     for r in reqs:
         assert [t for t in r.out if t != toy_int.EOS] == toy_int.generate(r.prompt, 10, lined), r.id
     assert rt.graphs >= 1
+
+
+def test_guard_bands_stay_clean_and_report_an_overrun(cuda):
+    """Test mode: canary bands around every device allocation. A whole prefill + decode of the tiny decoder leaves them
+    intact; a byte written past the end of a workspace (from the host, inside the runtime's own allocation) is named."""
+    from kern_b200.engine import Engine
+    from kern_b200.models import dense
+    from kern_b200.runtime import Runtime, _CudaView
+
+    cfg = dense.TINY
+    weights = dense.random_weights(cfg, seed=0, std=0.05)
+    rt = Runtime(dense.build_manifest(cfg), tokens=cfg.page_size * 32, slots=4, guard_bands=True)
+    rt.load_tensors(lambda name: weights[name].cuda())
+    rt.once()
+    eng = Engine(rt)
+    s = eng.open(64)
+    tok = eng.step([(s, list(range(1, 40)))])[0][0]
+    for _ in range(4):
+        tok = eng.step([(s, [tok])])[0][0]
+    rt.check_error()
+    assert rt.check_guards() == []
+    ptr, nbytes = rt.region("xn")
+    past = torch.as_tensor(_CudaView(ptr + nbytes, (1,), "|u1"), device="cuda:0")     # first byte of the trailing band
+    past.fill_(7)
+    torch.cuda.synchronize()
+    assert rt.check_guards() == ["xn (after)"]
