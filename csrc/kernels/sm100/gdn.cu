@@ -329,12 +329,15 @@ extern "C" __global__ void __launch_bounds__(128)
 // global memory, and the gated RMSNorm of the head's output closes the same launch. The step is bandwidth-bound: the
 // roofline is two passes over the state at the copy bandwidth.
 // Reference: tools/kernels-src/gdn_decode.cu:171 (kern_gdn_step_bf16: same fusion, one state tile per CTA).
-template <int DK, int DV>
+// KDA = true: the decay is per key channel (Kimi Delta Attention): S[v, k] <- dec[k] S[v, k] before the delta update,
+// dec[k] = exp(-exp(A_log[h]) softplus(gk[t, h, k] + dt_bias[h, k])); `gk` rows of HV * DK bf16 replace the scalar gate
+// column `a` (dt_bias then holds HV * DK values).
+template <int DK, int DV, bool KDA = false>
 __device__ __forceinline__ void gdn_step_body(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, __nv_bfloat16* out,
                                               uint8_t* state, const int* lines, const float* A_log, const float* dt_bias,
                                               const __nv_bfloat16* norm_w, int seqs, int hk, int hv, int zba_stride,
                                               int z_off, int b_off, int a_off, long long line_bytes, long long s_offset,
-                                              float eps) {
+                                              float eps, const __nv_bfloat16* gk = nullptr, int gk_stride = 0) {
   constexpr int TPR = DK >= 64 ? 16 : DK / 4;   // lanes per value row; each holds DK / TPR keys in 16-byte groups
   constexpr int KPT = DK / TPR;
   constexpr int NG = KPT / 4;
@@ -351,6 +354,7 @@ __device__ __forceinline__ void gdn_step_body(const __nv_bfloat16* qkv, const __
   float* os = vs + DV;
   float* red = os + DV;                         // 8 partial sums + {decay, beta, k.q}
   uint64_t* bar = reinterpret_cast<uint64_t*>(red + 16);
+  float* dec = reinterpret_cast<float*>(bar + 2);      // KDA: per-key decay [DK]
   const int h = blockIdx.x, s = blockIdx.y;
   if (s >= seqs) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -395,6 +399,13 @@ __device__ __forceinline__ void gdn_step_body(const __nv_bfloat16* qkv, const __
       red[8] = __expf(-__expf(A_log[h]) * sp);
       red[9] = __bfloat162float(__float2bfloat16(1.f / (1.f + __expf(-bb))));
     }
+    if constexpr (KDA) {
+      const float a_neg = -__expf(A_log[h]);
+      for (int c = lane; c < DK; c += 32) {
+        const float x = __bfloat162float(gk[(size_t)s * gk_stride + h * DK + c]) + dt_bias[h * DK + c];
+        dec[c] = __expf(a_neg * (x > 20.f ? x : log1pf(__expf(x))));
+      }
+    }
   } else {
     for (int r = tid - 64; r < DV; r += 192) vs[r] = __bfloat162float(row[2 * hk * DK + h * DV + r]);
   }
@@ -411,16 +422,23 @@ __device__ __forceinline__ void gdn_step_body(const __nv_bfloat16* qkv, const __
       __syncthreads();
     }
   }
-  const float decay = red[8], beta = red[9], kq = red[10];
+  const float decay = KDA ? 1.f : red[8], beta = red[9], kq = red[10];
   const int vrow = tid / TPR, kpart = tid % TPR;
-  float kr[KPT], qr[KPT];
+  float kr[KPT], qr[KPT], dr[KPT];
 #pragma unroll
   for (int g = 0; g < NG; ++g) {
     const float4 k4 = *reinterpret_cast<const float4*>(ks + g * 4 * TPR + kpart * 4);
     const float4 q4 = *reinterpret_cast<const float4*>(qs + g * 4 * TPR + kpart * 4);
     kr[4 * g] = k4.x; kr[4 * g + 1] = k4.y; kr[4 * g + 2] = k4.z; kr[4 * g + 3] = k4.w;
     qr[4 * g] = q4.x; qr[4 * g + 1] = q4.y; qr[4 * g + 2] = q4.z; qr[4 * g + 3] = q4.w;
+    if constexpr (KDA) {
+      const float4 d4 = *reinterpret_cast<const float4*>(dec + g * 4 * TPR + kpart * 4);
+      dr[4 * g] = d4.x; dr[4 * g + 1] = d4.y; dr[4 * g + 2] = d4.z; dr[4 * g + 3] = d4.w;
+    } else {
+      dr[4 * g] = dr[4 * g + 1] = dr[4 * g + 2] = dr[4 * g + 3] = red[8];
+    }
   }
+  (void)decay;
 #pragma unroll
   for (int p = 0; p < PASSES; ++p) {
     const int r = p * RPP + vrow;
@@ -431,6 +449,9 @@ __device__ __forceinline__ void gdn_step_body(const __nv_bfloat16* qkv, const __
                             : make_float4(0.f, 0.f, 0.f, 0.f);
       S[4 * g] = v.x; S[4 * g + 1] = v.y; S[4 * g + 2] = v.z; S[4 * g + 3] = v.w;
     }
+    // the decayed state first (a scalar per head, or a value per key channel), then both products on it
+#pragma unroll
+    for (int j = 0; j < KPT; ++j) S[j] *= dr[j];
     float sa = 0.f, sb = 0.f;
 #pragma unroll
     for (int j = 0; j < KPT; ++j) { sa += S[j] * kr[j]; sb += S[j] * qr[j]; }
@@ -439,16 +460,16 @@ __device__ __forceinline__ void gdn_step_body(const __nv_bfloat16* qkv, const __
       sa += __shfl_xor_sync(0xffffffffu, sa, o);
       sb += __shfl_xor_sync(0xffffffffu, sb, o);
     }
-    const float u = (vs[r] - decay * sa) * beta;
+    const float u = (vs[r] - sa) * beta;
     if (have) {
       float* dst = reinterpret_cast<float*>(Sg8) + (size_t)r * DK;
 #pragma unroll
       for (int g = 0; g < NG; ++g)
         *reinterpret_cast<float4*>(dst + g * 4 * TPR + kpart * 4) =
-            make_float4(decay * S[4 * g] + u * kr[4 * g], decay * S[4 * g + 1] + u * kr[4 * g + 1],
-                        decay * S[4 * g + 2] + u * kr[4 * g + 2], decay * S[4 * g + 3] + u * kr[4 * g + 3]);
+            make_float4(S[4 * g] + u * kr[4 * g], S[4 * g + 1] + u * kr[4 * g + 1], S[4 * g + 2] + u * kr[4 * g + 2],
+                        S[4 * g + 3] + u * kr[4 * g + 3]);
     }
-    if (kpart == 0) os[r] = decay * sb + u * kq;
+    if (kpart == 0) os[r] = sb + u * kq;
   }
   __syncthreads();
   // gated RMSNorm over the head's DV outputs
@@ -477,7 +498,21 @@ __device__ __forceinline__ void gdn_step_body(const __nv_bfloat16* qkv, const __
                           a_off, line_bytes, s_offset, eps);                                                           \
   }
 
-// grid [HV, seqs], block 256, dynamic shared memory DV * DK * 4 + (2 DK + 2 DV + 16) * 4 + 16 bytes
+#define KERN_KDA_STEP_ENTRY(name, DK, DV)                                                                               \
+  extern "C" __global__ void __launch_bounds__(256)                                                                    \
+      name(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, __nv_bfloat16* out, uint8_t* state, const int* lines,   \
+           const float* A_log, const float* dt_bias, const __nv_bfloat16* norm_w, const __nv_bfloat16* gk, int seqs,   \
+           int hk, int hv, int zba_stride, int z_off, int b_off, int gk_stride, long long line_bytes,                  \
+           long long s_offset, float eps) {                                                                            \
+    pdl_wait();                                                                                                        \
+    gdn_step_body<DK, DV, true>(qkv, zba, out, state, lines, A_log, dt_bias, norm_w, seqs, hk, hv, zba_stride, z_off,   \
+                                b_off, 0, line_bytes, s_offset, eps, gk, gk_stride);                                   \
+  }
+
+// grid [HV, seqs], block 256, dynamic shared memory DV * DK * 4 + (2 DK + 2 DV + 16) * 4 + 16 bytes (+ DK * 4 for KDA)
 KERN_GDN_STEP_ENTRY(kern_gdn_step_k128_v128, 128, 128)
 KERN_GDN_STEP_ENTRY(kern_gdn_step_k64_v64, 64, 64)
 KERN_GDN_STEP_ENTRY(kern_gdn_step_k32_v32, 32, 32)
+// per-key decay (Kimi Delta Attention) decode step: `gk` [tokens, HV * DK] bf16 gate rows, dt_bias [HV * DK]
+KERN_KDA_STEP_ENTRY(kern_kda_step_k128_v128, 128, 128)
+KERN_KDA_STEP_ENTRY(kern_kda_step_k64_v64, 64, 64)

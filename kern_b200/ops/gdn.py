@@ -80,6 +80,19 @@ def step(qkv, zba, out, state, lines, A_log, dt_bias, norm_w, seqs, hk, hv, dk, 
     return out
 
 
+def kda_step(qkv, zba, gk, out, state, lines, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv, z_off, b_off, line_b, s_off,
+             eps=1e-6):
+    """Fused decode step with a decay per key channel (Kimi Delta Attention): `gk` [tokens, HV * DK] bf16 gate rows,
+    `dt_bias` [HV * DK]; everything else as `step`."""
+    k = Kernels.get(qkv.device)
+    assert dk == dv and dk in (64, 128)
+    k.launch("gdn", f"kern_kda_step_k{dk}_v{dv}", (hv, seqs), (256,),
+             [ptr(qkv), ptr(zba), ptr(out), ptr(state), ptr(lines), ptr(A_log), ptr(dt_bias), ptr(norm_w), ptr(gk), i32(seqs),
+              i32(hk), i32(hv), i32(zba.stride(0)), i32(z_off), i32(b_off), i32(gk.stride(0)), i64(line_b), i64(s_off), f32(eps)],
+             shared_mem=step_smem(dk, dv) + dk * 4)
+    return out
+
+
 CHUNK_PREP_SMEM = (2 * 64 * 132 + 64 * 68 + 2 * 64) * 4
 CHUNK_RULE_SMEM = (64 * 132 * 3 + 64 * 136 + 64 * 68 + 2 * 64 * 72) * 4
 
@@ -211,3 +224,25 @@ def chunk_rule_ref(W, Qg, Kd, Ut, M, gC, S):
         out[sl] = torch.einsum("ihk,hvk->ihv", Qg[sl], S) + torch.einsum("ihj,jhv->ihv", M[sl, :, :n], U)
         S = gC[c0][:, None, None] * S + torch.einsum("ihv,ihk->hvk", U, Kd[sl])
     return out, S
+
+
+def kda_rule_ref(q, k, v, z, b, gk, S, A_log, dt_bias, norm_w, eps=1e-6):
+    """The delta rule with a decay per key channel, one sequence: gk [T, HV, DK] gate rows, dt_bias [HV, DK];
+    S[h, v, k] <- dec[h, k] S[h, v, k], then the delta update and the read-out as in `rule_ref`."""
+    T, hk, dk = q.shape
+    hv = v.shape[1]
+    rep = hv // hk
+    q = q.float() * torch.rsqrt(q.float().pow(2).sum(-1, keepdim=True) + 1e-6)
+    k = k.float() * torch.rsqrt(k.float().pow(2).sum(-1, keepdim=True) + 1e-6)
+    q = (q / dk ** 0.5).repeat_interleave(rep, 1)
+    k = k.repeat_interleave(rep, 1)
+    dec = torch.exp(-torch.exp(A_log.float())[None, :, None] * F.softplus(gk.float() + dt_bias.float()[None]))      # [T, HV, DK]
+    beta = torch.sigmoid(b.float()).to(torch.bfloat16).float()
+    S = S.float().clone()
+    out = torch.empty(T, hv, v.shape[2], dtype=torch.float32, device=q.device)
+    for t in range(T):
+        S = S * dec[t][:, None, :]
+        u = (v[t].float() - torch.einsum("hvk,hk->hv", S, k[t])) * beta[t][:, None]
+        S = S + u[:, :, None] * k[t][:, None, :]
+        out[t] = torch.einsum("hvk,hk->hv", S, q[t])
+    return gate_norm_ref(out, z, norm_w, eps), S

@@ -151,3 +151,46 @@ def test_gdn_chunked_prefill_matches_the_statement(cuda):
         # tf32 products (10-bit mantissa operands, f32 accumulation) against the all-f32 statement
         torch.testing.assert_close(S_dev, S1, rtol=5e-3, atol=5e-3)
     assert int(state[0].count_nonzero()) == 0 and int(state[3].count_nonzero()) == 0
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_kda_decode_step_per_key_decay(cuda, d):
+    """The fused decode step with a decay per key channel against its fp32 statement, three steps in a row from a
+    non-zero state, one padding (null-line) row."""
+    from kern_b200.ops import gdn
+    from kern_b200.ops.launcher import Kernels
+
+    torch.manual_seed(3 + d)
+    hk, hv, width = 2, 6, 4
+    conv_dim = 2 * hk * d + hv * d
+    zb = hv * d + hv
+    lb, s_off = gdn.line_bytes(hk, hv, d, d, width)
+    seqs = 3
+    state = torch.zeros(5, lb, dtype=torch.uint8, device=cuda)
+    lines = torch.tensor([2, 0, 4], dtype=torch.int32, device=cuda)
+    S = [torch.randn(hv, d, d, device=cuda) * 0.2 if ln > 0 else torch.zeros(hv, d, d, device=cuda) for ln in lines.tolist()]
+    for i, ln in enumerate(lines.tolist()):
+        if ln > 0:
+            state[ln, s_off:].view(torch.float32).view(hv, d, d).copy_(S[i])
+    A_log = torch.randn(hv, device=cuda) * 0.5
+    dt_bias = torch.randn(hv * d, device=cuda) * 0.5
+    norm_w = bf(1 + 0.1 * torch.randn(d, device=cuda))
+    for _ in range(3):
+        y = bf(torch.randn(seqs, conv_dim, device=cuda))
+        zba = bf(torch.randn(seqs, zb, device=cuda))
+        gk = bf(torch.randn(seqs, hv * d, device=cuda))
+        out = torch.empty(seqs, hv * d, dtype=torch.bfloat16, device=cuda)
+        gdn.kda_step(y, zba, gk, out, state, lines, A_log, dt_bias, norm_w, seqs, hk, hv, d, d, 0, hv * d, lb, s_off)
+        torch.cuda.synchronize()
+        Kernels.get(cuda).check_error()
+        for i in range(seqs):
+            yf = y[i:i + 1].float()
+            q, k, v = yf[:, :hk * d].view(1, hk, d), yf[:, hk * d:2 * hk * d].view(1, hk, d), yf[:, 2 * hk * d:].view(1, hv, d)
+            z = zba[i:i + 1, :hv * d].float().view(1, hv, d)
+            b = zba[i:i + 1, hv * d:hv * d + hv].float()
+            o, S1 = gdn.kda_rule_ref(q, k, v, z, b, gk[i:i + 1].float().view(1, hv, d), S[i], A_log, dt_bias.view(hv, d), norm_w)
+            torch.testing.assert_close(out[i:i + 1].float().view(1, hv, d), o, rtol=3e-2, atol=3e-2)
+            if int(lines[i]) > 0:
+                S[i] = S1
+                torch.testing.assert_close(state[int(lines[i]), s_off:].view(torch.float32).view(hv, d, d), S1, rtol=1e-3, atol=1e-3)
+    assert int(state[0].count_nonzero()) == 0
