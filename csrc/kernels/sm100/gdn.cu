@@ -129,13 +129,14 @@ extern "C" __global__ void __launch_bounds__(256)
 // together with v, the decay and beta of those tokens.
 constexpr int GDN_TB = 32;     // most tokens per staged batch
 
-template <int DK, int DV, int ROWS>   // ROWS value rows per CTA. 16 everywhere: 64 rows per CTA pay the staged q/k reads and
+template <int DK, int DV, int ROWS, bool KDA = false>   // ROWS value rows per CTA. 16 everywhere: 64 rows per CTA pay the staged q/k reads and
                                       // the shuffles once per 64 rows, but leave 96 CTAs of 8 warps on 148 SMs and measured
                                       // slower (1.44 ms against 1.27 ms per 2048-row chunk)
 __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, float* o_raw, uint8_t* state,
                                          const int* lines, const int* cu_q, const float* A_log, const float* dt_bias,
                                          int seqs, int hk, int hv, int zba_stride, int b_off, int a_off,
-                                         long long line_bytes, long long s_offset, int tb) {
+                                         long long line_bytes, long long s_offset, int tb,
+                                         const __nv_bfloat16* gk = nullptr, int gk_stride = 0) {
   constexpr int TPR = 256 / ROWS;       // lanes per value row
   constexpr int KPT = DK / TPR;         // state elements per thread, in 16-byte groups: group g of a thread is keys
                                         // g * 4 TPR + part * 4 .. + 3, so a row's 16 lanes read 256 contiguous bytes per access
@@ -149,6 +150,7 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
   float (*ks)[DK] = reinterpret_cast<float (*)[DK]>(gdn_sm + (size_t)tb * DK);
   float4* meta = reinterpret_cast<float4*>(gdn_sm + (size_t)2 * tb * DK);
   float (*vs)[ROWS] = reinterpret_cast<float (*)[ROWS]>(gdn_sm + (size_t)tb * (2 * DK + 4));
+  float (*ds)[DK] = reinterpret_cast<float (*)[DK]>(gdn_sm + (size_t)tb * (2 * DK + 4 + ROWS));     // KDA: decay per key
   constexpr int PARTS = DV / ROWS;
   const int h = blockIdx.x / PARTS, row0 = (blockIdx.x % PARTS) * ROWS, s = blockIdx.y;
   if (s >= seqs) return;
@@ -209,7 +211,14 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
 #pragma unroll
         for (int i = 0; i < QN; ++i) {
           const int c = i * 32 + lane;
-          if (c < DK) { qs[t][c] = pq[u][i] * qi; ks[t][c] = pk[u][i] * ki; }
+          if (c < DK) {
+            qs[t][c] = pq[u][i] * qi;
+            ks[t][c] = pk[u][i] * ki;
+            if constexpr (KDA) {
+              const float x = __bfloat162float(gk[(size_t)(base + t) * gk_stride + h * DK + c]) + dt_bias[h * DK + c];
+              ds[t][c] = __expf(a_neg * (x > 20.f ? x : log1pf(__expf(x))));
+            }
+          }
         }
         for (int r = lane; r < ROWS; r += 32) vs[t][r] = __bfloat162float(row[2 * hk * DK + h * DV + row0 + r]);
         if (lane == 31) {
@@ -240,6 +249,19 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
       }
       // both products run on the state *before* this token: S_t q = decay (S_{t-1} q) + u (k.q), so one round of
       // shuffles carries the two sums instead of two rounds in sequence
+      if constexpr (KDA) {      // decay per key channel, applied before both products
+        if constexpr (VEC == 4) {
+#pragma unroll
+          for (int j = 0; j < NG; ++j) {
+            const float4 d4 = *reinterpret_cast<const float4*>(&ds[t][j * 4 * TPR + kpart * 4]);
+            S[4 * j] *= d4.x; S[4 * j + 1] *= d4.y; S[4 * j + 2] *= d4.z; S[4 * j + 3] *= d4.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < KPT; ++j) S[j] *= ds[t][kidx(j)];
+        }
+      }
+      const float dcy = KDA ? 1.f : m.x;
       float sa = 0.f, sb = 0.f;
 #pragma unroll
       for (int j = 0; j < KPT; ++j) { sa += S[j] * kr[j]; sb += S[j] * qr[j]; }
@@ -248,10 +270,10 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
         sa += __shfl_xor_sync(0xffffffffu, sa, o);
         sb += __shfl_xor_sync(0xffffffffu, sb, o);
       }
-      const float u = (vv - m.x * sa) * m.y;
+      const float u = (vv - dcy * sa) * m.y;
 #pragma unroll
-      for (int j = 0; j < KPT; ++j) S[j] = m.x * S[j] + u * kr[j];
-      if (kpart == 0) o_raw[(size_t)(base + t) * hv * DV + h * DV + row0 + vrow] = m.x * sb + u * m.z;
+      for (int j = 0; j < KPT; ++j) S[j] = dcy * S[j] + u * kr[j];
+      if (kpart == 0) o_raw[(size_t)(base + t) * hv * DV + h * DV + row0 + vrow] = dcy * sb + u * m.z;
     }
   }
   if (line > 0) {
@@ -276,10 +298,23 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
                            a_off, line_bytes, s_offset, tb < 1 ? 1 : (tb > GDN_TB ? GDN_TB : tb));                     \
   }
 
+#define KERN_KDA_ENTRY(name, DK, DV, ROWS)                                                                             \
+  extern "C" __global__ void __launch_bounds__(256)                                                                    \
+      name(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, float* o_raw, uint8_t* state, const int* lines,         \
+           const int* cu_q, const float* A_log, const float* dt_bias, const __nv_bfloat16* gk, int seqs, int hk,       \
+           int hv, int zba_stride, int b_off, int gk_stride, long long line_bytes, long long s_offset, int tb) {       \
+    pdl_wait();                                                                                                        \
+    gdn_body<DK, DV, ROWS, true>(qkv, zba, o_raw, state, lines, cu_q, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off,  \
+                                 0, line_bytes, s_offset, tb < 1 ? 1 : (tb > GDN_TB ? GDN_TB : tb), gk, gk_stride);    \
+  }
+
 // prefill chunks (ragged rows per sequence): grid [HV * DV / 16, seqs]
 KERN_GDN_ENTRY(kern_gdn_rule_k128_v128, 128, 128, 16)
 KERN_GDN_ENTRY(kern_gdn_rule_k64_v64, 64, 64, 16)
 KERN_GDN_ENTRY(kern_gdn_rule_k32_v32, 32, 32, 16)
+// decay per key channel (Kimi Delta Attention), ragged rows; dynamic shared memory (3 DK + ROWS + 4) * 4 bytes per staged token
+KERN_KDA_ENTRY(kern_kda_rule_k128_v128, 128, 128, 16)
+KERN_KDA_ENTRY(kern_kda_rule_k64_v64, 64, 64, 16)
 // one row per sequence, unfused (the fused decode step is kern_gdn_step_*): grid [HV * DV / 16, seqs]
 KERN_GDN_ENTRY(kern_gdn_rule_dec_k128_v128, 128, 128, 16)
 KERN_GDN_ENTRY(kern_gdn_rule_dec_k64_v64, 64, 64, 16)

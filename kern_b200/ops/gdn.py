@@ -93,6 +93,25 @@ def kda_step(qkv, zba, gk, out, state, lines, A_log, dt_bias, norm_w, seqs, hk, 
     return out
 
 
+def kda_rule(qkv, zba, gk, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv, z_off, b_off, line_b, s_off,
+             eps=1e-6):
+    """Ragged rows (prefill chunks, speculative rows) of the per-key-decay rule, token by token with the state in
+    registers, then the gated RMSNorm."""
+    k = Kernels.get(qkv.device)
+    assert dk == dv and dk in (64, 128) and cu_q is not None
+    tokens = out.shape[0]
+    o_raw = torch.empty(tokens, hv * dv, dtype=torch.float32, device=qkv.device)
+    tb = 32
+    k.launch("gdn", f"kern_kda_rule_k{dk}_v{dv}", (hv * (dv // 16), seqs), (256,),
+             [ptr(qkv), ptr(zba), ptr(o_raw), ptr(state), ptr(lines), ptr(cu_q), ptr(A_log), ptr(dt_bias), ptr(gk), i32(seqs),
+              i32(hk), i32(hv), i32(zba.stride(0)), i32(b_off), i32(gk.stride(0)), i64(line_b), i64(s_off), i32(tb)],
+             shared_mem=tb * (3 * dk + 16 + 4) * 4)
+    k.launch("gdn", "kern_gdn_gate_norm_bf16", ((hv + 3) // 4, tokens), (128,),
+             [ptr(o_raw), ptr(zba), ptr(out), ptr(norm_w), i32(tokens), i32(hv), i32(dv), i32(zba.stride(0)),
+              i32(z_off), f32(eps)])
+    return out
+
+
 CHUNK_PREP_SMEM = (2 * 64 * 132 + 64 * 68 + 2 * 64) * 4
 CHUNK_RULE_SMEM = (64 * 132 * 3 + 64 * 136 + 64 * 68 + 2 * 64 * 72) * 4
 

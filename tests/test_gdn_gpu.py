@@ -175,6 +175,28 @@ def test_kda_decode_step_per_key_decay(cuda, d):
     A_log = torch.randn(hv, device=cuda) * 0.5
     dt_bias = torch.randn(hv * d, device=cuda) * 0.5
     norm_w = bf(1 + 0.1 * torch.randn(d, device=cuda))
+    # ragged rows first (the token-by-token kernel), then single-row steps continue from the state it left
+    lens = [37, 5, 1]
+    T = sum(lens)
+    cu = torch.tensor([0, 37, 42, 43], dtype=torch.int32, device=cuda)
+    y = bf(torch.randn(T, conv_dim, device=cuda))
+    zba = bf(torch.randn(T, zb, device=cuda))
+    gk = bf(torch.randn(T, hv * d, device=cuda))
+    out = torch.empty(T, hv * d, dtype=torch.bfloat16, device=cuda)
+    gdn.kda_rule(y, zba, gk, out, state, lines, cu, A_log, dt_bias, norm_w, seqs, hk, hv, d, d, 0, hv * d, lb, s_off)
+    torch.cuda.synchronize()
+    Kernels.get(cuda).check_error()
+    for i, n in enumerate(lens):
+        r0 = int(cu[i])
+        yf = y[r0:r0 + n].float()
+        q, k, v = yf[:, :hk * d].view(n, hk, d), yf[:, hk * d:2 * hk * d].view(n, hk, d), yf[:, 2 * hk * d:].view(n, hv, d)
+        z = zba[r0:r0 + n, :hv * d].float().view(n, hv, d)
+        b = zba[r0:r0 + n, hv * d:hv * d + hv].float()
+        o, S1 = gdn.kda_rule_ref(q, k, v, z, b, gk[r0:r0 + n].float().view(n, hv, d), S[i], A_log, dt_bias.view(hv, d), norm_w)
+        torch.testing.assert_close(out[r0:r0 + n].float().view(n, hv, d), o, rtol=3e-2, atol=3e-2)
+        if int(lines[i]) > 0:
+            S[i] = S1
+            torch.testing.assert_close(state[int(lines[i]), s_off:].view(torch.float32).view(hv, d, d), S1, rtol=1e-3, atol=1e-3)
     for _ in range(3):
         y = bf(torch.randn(seqs, conv_dim, device=cuda))
         zba = bf(torch.randn(seqs, zb, device=cuda))
