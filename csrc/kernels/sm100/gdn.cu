@@ -331,7 +331,8 @@ extern "C" __global__ void __launch_bounds__(128)
   const float* o = o_raw + ((size_t)t * hv + h) * dv;
   const __nv_bfloat16* z = zba + (size_t)t * zba_stride + z_off + h * dv;
   __nv_bfloat16* y = out + ((size_t)t * hv + h) * dv;
-  if (dv == 128) {      // 16-byte loads of o, 8-byte loads of z and the weight
+  if (dv == 128 && (zba_stride & 3) == 0 && (z_off & 3) == 0) {      // 16-byte loads of o, 8-byte loads of z and the weight
+                                                                      // (rows of z must then start 8-byte aligned)
     const float4 v = *reinterpret_cast<const float4*>(o + lane * 4);
     const uint2 zu = *reinterpret_cast<const uint2*>(z + lane * 4);
     const uint2 wu = *reinterpret_cast<const uint2*>(norm_w + lane * 4);

@@ -65,14 +65,18 @@ def make_runtime(args, manifest=None):
 
         over = {k: getattr(args, k, None) or None for k in ("layers", "max_tokens", "max_seqs", "max_context")}
         cfg, build, load, make = registry.resolve(model, **over)
+        doc = build(cfg)
+        # state slots only for models with per-sequence state: a lease that holds a slot makes its checkpoints usable
+        # at their exact length only, which would cost a slot-free model most of its prefix-cache hits
+        slots = (getattr(cfg, "max_seqs", 0) or 8) if any(s.get("bytes_per_seq") for s in doc["states"].values()) else 0
         if args.cpu:
             from .cpu import CpuRuntime
 
-            rt = CpuRuntime(build(cfg), weights=make(cfg), tokens=args.capacity or 4096, slots=cfg.max_seqs)
+            rt = CpuRuntime(doc, weights=make(cfg), tokens=args.capacity or 4096, slots=slots)
         else:
             from .runtime import Runtime
 
-            rt = Runtime(build(cfg), kernels=args.kernels, gpu=args.gpu, tokens=args.capacity or 0, slots=cfg.max_seqs)
+            rt = Runtime(doc, kernels=args.kernels, gpu=args.gpu, tokens=args.capacity or 0, slots=slots)
             load(rt, cfg)
         rt.once()
         return rt
@@ -189,6 +193,37 @@ def cmd_schema(args) -> int:
         return 0 if ok else 1
     sys.stdout.write(schema.text())
     return 0
+
+
+def cmd_gate(args) -> int:
+    """The serving scenarios (`testing/gate.py`) against a model target; fresh engines come from the same flags."""
+    from .engine import Engine
+    from .testing.gate import Gate
+
+    first = make_runtime(args)
+    p = first.protocol
+    page = first.page_unit
+    vocab = args.vocab or 256
+    for b in first.doc["buffers"].values():
+        if b.get("fill") == "token" and "domain" in b and "max" in b["domain"]:
+            vocab = int(b["domain"]["max"]) + 1
+    capacity = args.capacity or page * 24
+    spare = [first]
+
+    def make(tokens):
+        if spare and tokens == capacity:
+            return Engine(spare.pop())
+        ns = argparse.Namespace(**vars(args))
+        ns.capacity = tokens
+        return Engine(make_runtime(ns))
+
+    args.capacity = capacity
+    results = Gate(make, vocab, page, capacity, seed=args.seed).run(args.only.split(",") if args.only else None)
+    for r in results:
+        print(r.line())
+    bad = [r for r in results if not r.ok]
+    print(f"{len(results) - len(bad)} of {len(results)} scenarios pass" + (f" (protocol rows {p['rows']['max']}, page {page})" if p else ""))
+    return 1 if bad else 0
 
 
 def cmd_kernels(args) -> int:
@@ -461,6 +496,9 @@ def main(argv=None) -> int:
     v = sub.add_parser("verify"); v.add_argument("manifest")
     c = sub.add_parser("cut"); c.add_argument("manifest"); c.add_argument("--at", required=True); c.add_argument("--out", required=True)
     sub.add_parser("kernels")
+    gt = sub.add_parser("gate", help="the serving scenarios every model target must pass"); common(gt)
+    gt.add_argument("--only", help="comma-separated scenario names"); gt.add_argument("--seed", type=int, default=0)
+    gt.add_argument("--vocab", type=int, help="token id range when the manifest declares no domain")
     sc = sub.add_parser("schema", help="the JSON Schema of the manifest wire format")
     sc.add_argument("--check", action="store_true", help="compare with the committed schema/manifest-v7.schema.json; exit 1 on a difference")
     sc.add_argument("--write", action="store_true", help="rewrite the committed file")
@@ -491,7 +529,7 @@ def main(argv=None) -> int:
         resolve(args, path, cfg)
         if args.cmd != "test" and not args.manifest and not getattr(args, "model", None):
             ap.error("--manifest, --model or a --target of kern.toml is required")
-    return {"verify": cmd_verify, "cut": cmd_cut, "kernels": cmd_kernels, "schema": cmd_schema, "run": cmd_run, "test": cmd_test, "bench": cmd_bench,
+    return {"verify": cmd_verify, "cut": cmd_cut, "kernels": cmd_kernels, "schema": cmd_schema, "gate": cmd_gate, "run": cmd_run, "test": cmd_test, "bench": cmd_bench,
             "workload": cmd_workload, "server": cmd_server, "e2e-logits": cmd_e2e}[args.cmd](args)
 
 

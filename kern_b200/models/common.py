@@ -627,6 +627,7 @@ def gdn_line_bytes(hk: int, hv: int, dk: int, dv: int, width: int = 4) -> tuple[
 def gdn_conv_op(conv_dim: int, width: int, x_stride: int, line_bytes: int, ragged: bool) -> dict:
     """Causal conv + SiLU over the first `conv_dim` channels of a row (row-parallel), then the windows kept in the
     state lines advance. Interface [x, y, state, lines, (cu_seqlens,) w, seqs, rows]."""
+    assert conv_dim % 4 == 0 and x_stride % 4 == 0, "the conv kernel moves four channels (8 bytes) per thread"
     iface = ["in buffer<bf16>", "out buffer<bf16>", "inout state", "in buffer<i32>"]
     if ragged:
         iface.append("in buffer<i32>")

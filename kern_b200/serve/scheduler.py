@@ -208,6 +208,18 @@ class Scheduler:
         ckpt = self.pool.retire(seq.lease, length)
         self.prefix.insert(tokens, ckpt, stateful, length)
 
+    def _snapshot(self, req: Request) -> None:
+        """Keep the states of a running request at its turn boundary: whole pages join the shared chain, the half page
+        and the state slot are copied to the checkpoint (`Pool.checkpoint`); the request goes on with its lease. A
+        later prompt that shares the history restores from here — a checkpoint that holds a slot is usable at its
+        exact length only, so without this a stateful model would hit the cache only at the very end of a sequence."""
+        try:
+            ckpt, copies = self.pool.checkpoint(req.seq.lease, req.fed)
+        except _native.Denied:
+            return                                  # no room for the copy: go on without a snapshot
+        self.eng.rt.run_copies(copies)
+        self.prefix.insert(req.prompt[:req.fed], ckpt, True, req.fed)
+
     def _finish(self, req: Request, why: str) -> None:
         req.finished = why
         self.running.remove(req)
@@ -239,6 +251,9 @@ class Scheduler:
             if budget <= 0:
                 break
             n = min(budget, len(r.prompt) - r.fed)
+            h = r.history_tokens
+            if h is not None and r.seq.lease.slot >= 0 and r.fed < h < len(r.prompt):
+                n = min(n, h - r.fed)      # a chunk ends at the turn boundary, where the per-sequence state is snapshotted
             batch.append((r.seq, r.prompt[r.fed:r.fed + n]))
             kinds.append((r, "prefill", n))
             budget -= n
@@ -266,6 +281,8 @@ class Scheduler:
                 r.fed += n
                 self.stats.prefill_tokens += n
                 if r.fed < len(r.prompt):
+                    if self.prefix is not None and r.history_tokens == r.fed and r.seq.lease.slot >= 0:
+                        self._snapshot(r)          # a stateful model's state exactly after the previous turns
                     continue                       # the chunk's emitted token is not the prompt's next token yet
                 new = got[:1]
             else:
