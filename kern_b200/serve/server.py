@@ -197,8 +197,21 @@ def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None):
             if not chat and self.path != "/v1/completions":
                 return self._json(404, {"error": {"message": f"no route {self.path}"}})
             try:
+                history = None
                 if chat:
-                    prompt = tokenizer.chat(body["messages"])
+                    msgs = body["messages"]
+                    prompt = tokenizer.chat(msgs)
+                    # the turn boundary: the rendering of everything before the last message is a prefix of the whole
+                    # prompt when the template is prefix-stable; a model with per-sequence state snapshots it there
+                    if len(msgs) > 1:
+                        try:
+                            head = tokenizer.chat(msgs[:-1])
+                            n = 0
+                            while n < min(len(head), len(prompt)) and head[n] == prompt[n]:
+                                n += 1
+                            history = n if 0 < n < len(prompt) else None
+                        except Exception:
+                            history = None
                 else:
                     p = body.get("prompt", "")
                     prompt = list(p) if isinstance(p, list) and p and isinstance(p[0], int) else tokenizer.encode(p if isinstance(p, str) else p[0])
@@ -210,7 +223,7 @@ def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None):
                 stop = tuple(body.get("stop_token_ids") or ()) + (() if body.get("ignore_eos") else
                                                                   ((tokenizer.eos_token_id,) if tokenizer.eos_token_id is not None else ()))
                 req = Request(id="cmpl-" + uuid.uuid4().hex[:16], prompt=prompt, max_tokens=int(body.get("max_tokens", 16)),
-                              sampling=sampling, stop_ids=stop)
+                              sampling=sampling, stop_ids=stop, history_tokens=history)
             except (KeyError, ValueError, TypeError) as e:
                 return self._json(400, {"error": {"message": f"bad request: {e}"}})
             q = driver.submit(req)
