@@ -524,7 +524,7 @@ def main(argv=None) -> int:
     s.add_argument("--world", type=int, default=1, help="rank processes (one per GPU)")
     s.add_argument("--tp", type=int, default=1, help="ranks per tensor-parallel group; world / tp groups form a data-parallel tier")
     args = ap.parse_args(argv)
-    if args.cmd in ("run", "test", "bench", "server", "e2e-logits"):
+    if args.cmd in ("run", "test", "bench", "server", "e2e-logits", "gate"):
         path, cfg = find_config()
         resolve(args, path, cfg)
         if args.cmd != "test" and not args.manifest and not getattr(args, "model", None):
