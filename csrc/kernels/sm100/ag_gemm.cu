@@ -1,0 +1,29 @@
+// All-gather fused into the tensor-core GEMM (sequence-parallel prefill inside a tensor-parallel group):
+//   C[T, N] = G[T, K] . W[N, K]^T, where rank r produced rows [r T/n, (r+1) T/n) of G and the rest is pulled from the
+// peers' buffers by the same kernel while the tiles of the local rows are already running. See AgArgs in
+// gemm_bf16.cu for the protocol. A cross-rank barrier (kern_peer_barrier) must precede the launch — every rank's slice
+// is complete before anyone pulls it — and G alternates between two buffers from call to call, so a rank that runs
+// ahead never overwrites rows a peer is still pulling. grid = the SM count in every launch, block 256.
+// Reference: docs/multi-gpu.md:495-528 (all-gather + GEMM per layer as two steps: nccl_allgather_bf16, then the GEMM).
+#define KERN_GEMM_NO_ENTRIES
+#include "gemm_bf16.cu"
+
+#define KERN_AG_GEMM_ENTRY(name, BN)                                                                                 \
+  extern "C" __global__ void __launch_bounds__(256, 1)                                                               \
+      name(const __grid_constant__ CUtensorMap tma_g, const __grid_constant__ CUtensorMap tma_b, void* C, int M,      \
+           int N, int K, int ldc, int* err, const unsigned long long* peers, uint32_t* flags, uint32_t* epochs,       \
+           int rank, int nranks, int max_blocks) {                                                                   \
+    kern::AgArgs ag;                                                                                                 \
+    ag.peers = peers; ag.flags = flags; ag.epochs = epochs; ag.rank = rank; ag.nranks = nranks;                      \
+    ag.max_blocks = max_blocks;                                                                                      \
+    if (M % (nranks * kern::BM) != 0 || (M + kern::BM - 1) / kern::BM > max_blocks) {                                \
+      /* a rank's slice must be whole 128-row blocks, and every block needs its counter */                          \
+      if (threadIdx.x == 0 && blockIdx.x == 0) kern::set_error(err, kern::ERR_BOUNDS);                               \
+      return;                                                                                                        \
+    }                                                                                                                \
+    kern::gemm_body<BN, 0, false, false, false, true>(&tma_g, &tma_b, C, nullptr, M, N, K, ldc, err, nullptr,        \
+                                                      nullptr, kern::ScatterArgs(), nullptr, nullptr, ag);           \
+  }
+
+KERN_AG_GEMM_ENTRY(kern_ag_gemm_bf16_tn_n256, 256)
+KERN_AG_GEMM_ENTRY(kern_ag_gemm_bf16_tn_n128, 128)

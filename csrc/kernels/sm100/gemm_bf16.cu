@@ -53,22 +53,40 @@ struct ScatterArgs {
   int rank = 0, nranks = 1, grid = 1, slot_rows = 0;
 };
 
+// AG (all-gather fused into the GEMM): A is a row-sharded activation, rows [r T/n, (r+1) T/n) produced on rank r. Every
+// rank keeps a buffer G of all T rows at the same offsets; its own slice is written by the producing op, and this
+// kernel pulls the other slices out of the peers' G (plain 16-byte loads over NVLink, two extra warps per CTA, every
+// CTA a share of every 128-row block) while the tensor-core warps already multiply the rows that are here: the tile
+// order starts with this rank's own blocks and walks the peers' in the order they are pulled. A block's arrival is a
+// counter (every CTA adds one when its share is in place); the TMA producer waits for it — with a limit — before the
+// first load of a tile from that block. Counters only grow: launch e of a grid of g CTAs brings each to e g, so
+// nothing is reset and captured graphs replay; the grid size must therefore be the same in every launch.
+KERN_DEVICE int num_m_of(int M, int nranks) { return (M / nranks + BM - 1) / BM; }
+
+struct AgArgs {
+  const unsigned long long* peers = nullptr;   // G of every rank, mapped here (this rank's own included)
+  uint32_t* flags = nullptr;                   // [max_blocks] arrival counters (local)
+  uint32_t* epochs = nullptr;                  // [grid] launches seen by each CTA (local)
+  int rank = 0, nranks = 1, max_blocks = 0;
+};
+
 // GROUPED: the M tiles come from a device table of int4 {expert, first row, rows (<= BM), -} built by the MoE
 // planner (`tile_count` of them); A rows are the expert-sorted activations, B is a 3-D map [K, N, experts].
 // A tile's load may run into the next expert's rows; the epilogue stores only the tile's own rows.
 // FP8: A and B hold e4m3 bytes (a swizzle row is 128 elements, the instruction is kind::f8f6f4 with K = 32), the
 // accumulator is scaled by *scale_a * *scale_b (per-tensor scales) before the epilogue's conversion.
-template <int BN, int EPI, bool GROUPED = false, bool FP8 = false, bool MT2 = false>
+template <int BN, int EPI, bool GROUPED = false, bool FP8 = false, bool MT2 = false, bool AG = false>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
                                           void* Cv, const void* Rv,
                                           int M, int N, int K, int ldc, int* err,
                                           const int* tile_table = nullptr, const int* tile_count = nullptr,
                                           ScatterArgs sc = ScatterArgs(), const float* scale_a = nullptr,
-                                          const float* scale_b = nullptr) {
+                                          const float* scale_b = nullptr, AgArgs ag = AgArgs()) {
   using Cfg = GemmCfg<BN, MT2>;
   constexpr int kStages = Cfg::kStages;
   constexpr int BMT = Cfg::kRows;
   static_assert(!(MT2 && (GROUPED || EPI == 4 || BN != 256)), "the 256-row tile exists for the plain 256-wide GEMM");
+  static_assert(!(AG && (GROUPED || FP8 || MT2)), "the all-gather form exists for the plain bf16 GEMM");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -114,9 +132,20 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
   const int num_m = GROUPED ? *tile_count : (M + BMT - 1) / BMT;
   const int num_tiles = num_m * num_n;
   // tile t -> (first row, row bound, n block, expert)
+  // AG: blocks per rank, this rank's first block, and the counter value that says "every CTA's share of the block is in"
+  const int ag_bpr = AG ? num_m_of(M, ag.nranks) : 0;
+  uint32_t ag_want = 0;
+  if constexpr (AG) {
+    ag_want = (ag.epochs[blockIdx.x] + 1u) * gridDim.x;
+    __syncthreads();      // every thread has read this CTA's launch count before the gather warps can write the next one
+  }
   auto tile_of = [&](int t, int& row0, int& row_end, int& n_blk, int& expert) {
-    const int mt = t % num_m;
+    int mt = t % num_m;
     n_blk = t / num_m;
+    if constexpr (AG) {      // n fast inside a block of rows, this rank's own blocks first
+      mt = (t / num_n + ag.rank * ag_bpr) % num_m;
+      n_blk = t % num_n;
+    }
     if constexpr (GROUPED) {
       const int4 e = reinterpret_cast<const int4*>(tile_table)[mt];
       expert = e.x; row0 = e.y; row_end = min(M, e.y + e.z);
@@ -134,6 +163,22 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int row0, row_end, n_blk, expert;
         tile_of(t, row0, row_end, n_blk, expert);
+        if constexpr (AG) {
+          const int blk = row0 / BM;
+          if (blk / ag_bpr != ag.rank) {       // a peer's rows: wait until every CTA has put its share of the block here
+            bool here = false;
+            for (uint32_t i = 0; i < (1u << 22) && !here; ++i) {
+              here = ld_acquire_sys(ag.flags + blk) >= ag_want;
+              if (!here) { if ((i & 0xff) == 0xff && *abort_flag != 0) break; __nanosleep(100); }
+            }
+            if (!here) {
+              set_error(err, ERR_WAIT_PEER + blk / ag_bpr);
+              *abort_flag = 1;
+              break;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");   // the rows were written by ordinary stores; TMA reads them next
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
             set_error(err, ERR_WAIT_EMPTY);
@@ -208,6 +253,36 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
       }
     }
     __syncwarp();
+  } else if (warp >= 6) {
+    // ---------------- gather warps 6..7 (AG only): pull the peers' rows into this rank's G ----------------
+    if constexpr (AG) {
+      const int gt = threadIdx.x - 192;                      // 0..63
+      uint8_t* mine = reinterpret_cast<uint8_t*>(ag.peers[ag.rank]);
+      // blocks nobody gathers in this launch (own rows, blocks past the last row) arrive at once: every counter moves
+      // by the grid size in every launch, whatever the row count
+      for (int b = gt; b < ag.max_blocks; b += 64) {
+        const bool remote = b < num_m && b / ag_bpr != ag.rank;
+        if (!remote) atomicAdd(ag.flags + b, 1u);
+      }
+      for (int i = ag_bpr; i < num_m; ++i) {                 // the order the tiles will want them
+        const int b = (i + ag.rank * ag_bpr) % num_m;
+        const int rows = min(BM, M - b * BM);
+        const size_t off = (size_t)b * BM * K * 2, vecs = (size_t)rows * K * 2 / 16;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(ag.peers[b / ag_bpr]) + off;
+        uint8_t* dst = mine + off;
+        for (size_t v = (size_t)blockIdx.x * 64 + gt; v < vecs; v += (size_t)gridDim.x * 64) {
+          uint4 x;
+          asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w) : "l"(src + v * 16) : "memory");
+          *reinterpret_cast<uint4*>(dst + v * 16) = x;
+        }
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");
+        asm volatile("bar.sync 1, 64;" ::: "memory");          // both gather warps are done with this block
+        if (gt == 0) atomicAdd(ag.flags + b, 1u);
+      }
+      if (gt == 0) ag.epochs[blockIdx.x] = ag_want / gridDim.x;
+    }
   } else {
     // ---------------- epilogue warps 2..5 ----------------
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are this warp's

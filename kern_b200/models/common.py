@@ -218,6 +218,49 @@ def gemm_op(n: int, k: int, *, epilogue: str = "store", rows_var: str = "tokens"
     return {"params": iface, "impl": {"launches": launches}}
 
 
+AG_MAX_BLOCKS = 128      # 128-row blocks the fused all-gather GEMM keeps counters for (16 384 rows)
+
+
+def ag_gemm_buffers(rows_max: int, k: int, nranks: int, group: str = "tp") -> dict:
+    """Buffers of the all-gather fused into the GEMM: `ag.g` holds all rows (this rank writes its slice, the kernel
+    pulls the rest), the barrier's flags, and the arrival counters."""
+    return {"ag.g": {"dtype": "bf16", "shape": [rows_max, k], "kind": "carry", "export": True},
+            "ag.g_peers": {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": "ag.g", "group": group},
+            "ag.bar": {"dtype": "u32", "shape": [32], "kind": "carry", "export": True},
+            "ag.bar_peers": {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": "ag.bar", "group": group},
+            "ag.bar_epoch": {"dtype": "u32", "shape": [1], "kind": "carry"},
+            "ag.blocks": {"dtype": "u32", "shape": [AG_MAX_BLOCKS], "kind": "carry"},
+            "ag.cta_epochs": {"dtype": "u32", "shape": [SMS], "kind": "carry"}}
+
+
+def ag_gemm_op(n: int, k: int, nranks: int, group: str = "tp", bn: int = 256, timeout_ns: int = 2_000_000_000,
+               closing_barrier: bool = True) -> dict:
+    """C[rows, n] = G[rows, k] . W[n, k]^T with the all-gather of G's row slices inside the GEMM kernel.
+    Interface [g, g_peers, w, c, bar, bar_peers, bar_epoch, blocks, cta_epochs, err, rows]. A cross-rank barrier runs
+    first (every slice is complete before anyone pulls it); `closing_barrier` adds one after the GEMM so that the
+    same `g` can be rewritten by the next call (a caller that alternates two buffers drops it)."""
+    iface = ["inout buffer<bf16>", "in buffer<u64>", "in buffer<bf16>", "out buffer<bf16>", "inout buffer<u32>", "in buffer<u64>",
+             "inout buffer<u32>", "inout buffer<u32>", "inout buffer<u32>", "out buffer<i32>", "i32"]
+    barrier = {"module": "tp_allreduce_norm", "entry": "kern_peer_barrier", "block": [32, 1, 1], "grid": [1, 1, 1],
+               "params": ["inout buffer<u32>", "in buffer<u64>", "inout buffer<u32>", "out buffer<i32>", "i32", "i32", "i64"],
+               "args": [{"param": 4}, {"param": 5}, {"param": 6}, {"param": 9}, {"rank": group}, {"i32": nranks},
+                        {"i64": timeout_ns}]}
+    gemm = {"module": "ag_gemm", "entry": f"kern_ag_gemm_bf16_tn_n{bn}", "block": [256, 1, 1], "grid": [SMS, 1, 1],
+            "shared_mem": gemm_smem(bn),
+            "params": ["bytes<128>", "bytes<128>", "out buffer<bf16>", "i32", "i32", "i32", "i32", "out buffer<i32>",
+                       "in buffer<u64>", "inout buffer<u32>", "inout buffer<u32>", "i32", "i32", "i32"],
+            "args": [
+                {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+                    "param": 0, "dtype": "bf16", "dims": [k, 0], "strides": [k * 2], "box": [BK, BM], "swizzle": 128,
+                    "l2_promotion": 256}}]}},
+                {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+                    "param": 2, "dtype": "bf16", "dims": [k, n], "strides": [k * 2], "box": [BK, bn], "swizzle": 128,
+                    "l2_promotion": 256}}]}},
+                {"param": 3}, {"param": 10}, {"i32": n}, {"i32": k}, {"i32": n}, {"param": 9}, {"param": 1}, {"param": 7},
+                {"param": 8}, {"rank": group}, {"i32": nranks}, {"i32": AG_MAX_BLOCKS}]}
+    return {"params": iface, "impl": {"launches": [barrier, gemm] + ([dict(barrier)] if closing_barrier else [])}}
+
+
 def rms_norm_op(n: int, eps: float, plus_one: bool = False, rows_var: str = "tokens") -> dict:
     """Interface [x, w, y]; one row per CTA."""
     entry = "kern_rms_norm_bf16" if n <= 8192 else "kern_rms_norm_wide_bf16"

@@ -125,3 +125,26 @@ def test_pipeline_with_a_process_per_stage(world):
     assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
     line = next(json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))
     assert line["ok"] and line["stages"] == world and line["crossing_bytes"] > 0, line
+
+
+def test_allgather_gemm_one_rank(cuda):
+    """The all-gather GEMM with a group of one: no rows to pull, every counter still moves by the grid size per launch
+    (row counts change between launches, then a captured replay)."""
+    from kern_b200.parallel import ag_gemm_check
+
+    assert ag_gemm_check.main(["--rows", "128", "512", "256", "--n", "512", "--k", "1024"]) == 0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_allgather_gemm_fused(world):
+    """Rows sharded over the ranks; one kernel pulls the peers' slices over NVLink while the tensor cores run the local
+    ones; the product equals the GEMM over all rows (whatever was not pulled would be NaN)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29580 + world), "-m", "kern_b200.parallel.ag_gemm_check"]
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
+    line = next(json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))
+    assert line["world"] == world and all(r["ok"] for r in line["results"]), line
