@@ -180,6 +180,25 @@ def bench_attn_decode(a):
            kv_gb=round(kv_bytes / 1e9, 3))
 
 
+def bench_mla_decode(a):
+    """Absorbed latent-attention decode: `seqs` sequences of `ctx` latent rows, `heads` heads on this GPU."""
+    from . import mla
+    from .launcher import Kernels
+
+    page = a.page
+    pages_per = -(-a.ctx // page)
+    cache = (torch.randn(a.seqs * pages_per + 1, page, mla.DQK, device="cuda") * 0.3).to(torch.bfloat16)
+    table = (torch.arange(a.seqs * pages_per, device="cuda", dtype=torch.int32) + 1).view(a.seqs, pages_per)
+    q = (torch.randn(a.seqs, a.heads * mla.DQK, device="cuda") * 0.3).to(torch.bfloat16)
+    lens = torch.full((a.seqs,), a.ctx, dtype=torch.int32, device="cuda")
+    out = torch.empty(a.seqs, a.heads * mla.DV, dtype=torch.bfloat16, device="cuda")
+    ms = timeit(lambda: mla.mla_decode(q, cache, table, lens, a.heads, splits=a.splits, out=out), a.iters)
+    Kernels.get().check_error()
+    lat_bytes = a.seqs * a.ctx * mla.DQK * 2
+    report("mla_decode", ms, nbytes=lat_bytes, flops=2.0 * a.seqs * a.heads * a.ctx * (mla.DQK + mla.DV), seqs=a.seqs, ctx=a.ctx,
+           heads=a.heads, splits=a.splits, latent_gb=round(lat_bytes / 1e9, 3))
+
+
 def bench_attn_prefill(a):
     from .attention import paged_attention
     from .launcher import Kernels
@@ -232,12 +251,16 @@ def main(argv=None):
         s.add_argument("--d", type=int, default=128); s.add_argument("--page", type=int, default=64); s.add_argument("--rows", type=int, default=1)
     d.add_argument("--ctx", type=int, default=2432); d.add_argument("--splits", type=int, default=None)
     p.add_argument("--prefix", type=int, default=0)
+    ml = sub.add_parser("mla_decode")
+    ml.add_argument("--seqs", type=int, default=64); ml.add_argument("--ctx", type=int, default=8192)
+    ml.add_argument("--heads", type=int, default=16); ml.add_argument("--page", type=int, default=64)
+    ml.add_argument("--splits", type=int, default=None)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=4096); n.add_argument("--n", type=int, default=4096)
-    for s in (g, d, p, n, g8, mo, gd):
+    for s in (g, d, p, n, g8, mo, gd, ml):
         s.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "gdn": bench_gdn, "gemm_fp8": bench_gemm_fp8, "moe": bench_moe, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "norm": bench_norm}[a.op](a)
+    {"gemm": bench_gemm, "gdn": bench_gdn, "gemm_fp8": bench_gemm_fp8, "moe": bench_moe, "attn_decode": bench_attn_decode, "mla_decode": bench_mla_decode, "attn_prefill": bench_attn_prefill, "norm": bench_norm}[a.op](a)
 
 
 if __name__ == "__main__":

@@ -50,8 +50,7 @@ def main(argv=None) -> int:
 
     rows_max = max(a.rows) * world
     rt = Runtime(manifest(world, rows_max, a.n, a.k), gpu=local, topology={"tp": (rank, world)})
-    if world > 1:
-        group.start(rt)
+    group.start(rt)          # a group of one still fills its peer tables (with its own addresses)
     g = torch.Generator().manual_seed(9)
     w = (torch.randn(a.n, a.k, generator=g) * 0.05).to(torch.bfloat16).to(dev)
     rt.tensor("w").copy_(w)

@@ -44,12 +44,16 @@ def connect(rt, pg=None) -> None:
     groups = rt.doc.get("topology", {}).get("groups", {})
     if not groups:
         return
+    if not dist.is_initialized():
+        # one process: every group has one member, whose peer tables hold its own addresses (a kernel that walks
+        # the table must not find a null pointer there)
+        for g in groups:
+            rt.connect(g, [rt.offer()])
+        return
     rank, world = dist.get_rank(pg), dist.get_world_size(pg)
     offers = [None] * world
     dist.all_gather_object(offers, rt.offer(), group=pg)
     for g in groups:
-        if groups[g] < 2:
-            continue
         rt.connect(g, [offers[r] for r in members_of(groups, g, rank, world)])
 
 

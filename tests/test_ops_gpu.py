@@ -242,3 +242,33 @@ def test_decode_attention_context_parallel_partials(cuda, width):
     for s, l in enumerate(lens):
         ref = A.attention_reference(q[s:s + 1].view(1, hq, d), ks[s], vs[s], torch.tensor([l - 1], device=cuda))
         torch.testing.assert_close(out[s:s + 1].float(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("heads,splits", [(16, 1), (16, 4), (40, None), (128, 2)])
+def test_mla_absorbed_decode(cuda, heads, splits):
+    """Latent attention decode (keys = 576-wide latent rows, values = their first 512 columns, one shared cache):
+    ragged context lengths over paged latents against the fp32 statement; head counts that are not a multiple of the
+    16-head CTA tile; one split, fixed splits and the automatic choice."""
+    from kern_b200.ops import mla
+
+    torch.manual_seed(heads)
+    page = 32
+    lens = [1, 63, 64, 65, 300, 1000]
+    seqs = len(lens)
+    lat = [bf(torch.randn(l, mla.DQK, device=cuda) * 0.5) for l in lens]
+    pages_needed = sum(-(-l // page) for l in lens) + 1
+    cache = torch.zeros(pages_needed, page, mla.DQK, dtype=torch.bfloat16, device=cuda)
+    table = torch.zeros(seqs, max(-(-l // page) for l in lens), dtype=torch.int32, device=cuda)
+    nxt = 1
+    for s, l in enumerate(lens):
+        for p in range(-(-l // page)):
+            table[s, p] = nxt
+            lo, hi = p * page, min(l, (p + 1) * page)
+            cache[nxt, : hi - lo] = lat[s][lo:hi]
+            nxt += 1
+    q = bf(torch.randn(seqs, heads * mla.DQK, device=cuda) * 0.5)
+    out = mla.mla_decode(q, cache, table, torch.tensor(lens, dtype=torch.int32, device=cuda), heads, splits=splits)
+    check_err(cuda)
+    for s in range(seqs):
+        ref = mla.mla_decode_ref(q[s].view(heads, mla.DQK), lat[s], heads)
+        torch.testing.assert_close(out[s].float().view(heads, mla.DV), ref, rtol=2e-2, atol=2e-2)
