@@ -6,10 +6,11 @@
 //   cache  paged latent rows [page][page_size][576] bf16, one "kv head"
 //   out    [seqs, H, 512] bf16 (the caller applies W_UV / o_proj), or split partials (o, m, l) for the usual merge
 //
-// A CTA owns 16 heads of one sequence (one m16 tile) and one KV split. Four math warps: for S = Q K^T each takes 16 of
+// A CTA owns 16 heads of one sequence (one m16 tile) and one KV split. Eight math warps: for S = Q K^T each takes 8 of
 // the tile's 64 tokens; the probabilities go through shared memory (all warps use the tile's common row maximum), and
-// for O += P V each warp owns 128 of the 512 value columns — a warp's accumulator is 16 x 128, not 16 x 512. A fifth
-// warp feeds a two-stage ring of 72 KB tiles by TMA (nine 64-column boxes per tile, 128-byte swizzle).
+// for O += P V each warp owns 64 of the 512 value columns — a warp's accumulator is 16 x 64, not 16 x 512. A ninth
+// warp feeds a two-stage ring of 72 KB tiles by TMA (nine 64-column boxes per tile, 128-byte swizzle). (Four math
+// warps of 16 tokens / 128 columns measured 4.1 us per tile: too few warps to hide the ldmatrix -> mma chains.)
 // With 16 heads per rank (tensor parallel 8) a tile is read once per sequence; with more heads the CTAs of a sequence
 // share the tile through L2. One row per sequence (decode); verify rows of a speculative round are not handled here.
 // Reference: the reference takes this kernel from a CuTe-DSL build (MLA decode, sm100) and the context form from a
@@ -23,6 +24,7 @@ namespace {
 constexpr int TKM = 64;                  // tokens per tile
 constexpr int DQK = 576, DVV = 512;
 constexpr int HM = 16;                   // heads per CTA
+constexpr int MW = 8;                    // math warps: each 64 / MW tokens of a tile for S, 512 / MW value columns for O
 constexpr int kTileBytes = TKM * DQK * 2;
 constexpr int kStagesM = 2;
 constexpr int kQStride = DQK + 8, kPStride = TKM + 8;
@@ -43,15 +45,15 @@ KERN_DEVICE uint32_t lat_off(int tok, int chunk) {
   const int cb = chunk >> 3, c = chunk & 7;
   return (uint32_t)(cb * (TKM * 128) + tok * 128 + ((c ^ (tok & 7)) << 4));
 }
-KERN_DEVICE void math_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+KERN_DEVICE void math_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 }  // namespace
 
-// grid [ceil(H / 16), seqs, splits], block 160, dynamic shared memory MLA_SMEM bytes.
+// grid [ceil(H / 16), seqs, splits], block 288, dynamic shared memory MLA_SMEM bytes.
 // `splits` packs (launch splits | first slot << 8 | slots per (row, head) << 16) as the GQA decode kernel does.
-constexpr int MLA_SMEM = 1024 + kStagesM * kTileBytes + kQBytes + kPBytes + 2 * 4 * HM * 4 + 128;
+constexpr int MLA_SMEM = 1024 + kStagesM * kTileBytes + kQBytes + kPBytes + 2 * MW * HM * 4 + 128;
 
-extern "C" __global__ void __launch_bounds__(160, 1)
+extern "C" __global__ void __launch_bounds__(288, 1)
     kern_mla_decode_bf16(const __grid_constant__ CUtensorMap lat_map, const __nv_bfloat16* q, __nv_bfloat16* out, float* ws_o,
                          float* ws_ml, const int* block_table, const int* seq_lens, int seqs, int heads, int q_stride,
                          int out_stride, int max_pages, int page_size, int splits, int pool_pages, float scale_log2, int* err) {
@@ -60,9 +62,9 @@ extern "C" __global__ void __launch_bounds__(160, 1)
   uint8_t* stages = smem;
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem + kStagesM * kTileBytes);
   __nv_bfloat16* ps = reinterpret_cast<__nv_bfloat16*>(smem + kStagesM * kTileBytes + kQBytes);
-  float* sm_m = reinterpret_cast<float*>(smem + kStagesM * kTileBytes + kQBytes + kPBytes);      // [4][16] tile maxima per warp
-  float* sm_l = sm_m + 4 * HM;                                                                   // [4][16] row sums per warp
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sm_l + 4 * HM);
+  float* sm_m = reinterpret_cast<float*>(smem + kStagesM * kTileBytes + kQBytes + kPBytes);      // [MW][16] tile maxima per warp
+  float* sm_l = sm_m + MW * HM;                                                                  // [MW][16] row sums per warp
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sm_l + MW * HM);
   uint64_t* empty_bar = full_bar + kStagesM;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kStagesM);
 
@@ -71,7 +73,7 @@ extern "C" __global__ void __launch_bounds__(160, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStagesM; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 4);
+      mbar_init(&empty_bar[s], MW);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -104,7 +106,7 @@ extern "C" __global__ void __launch_bounds__(160, 1)
   }
   __syncthreads();
 
-  if (warp == 4) {
+  if (warp == MW) {
     // ---------------- producer ----------------
     if (lane == 0) {
       const int box_rows = page_size < TKM ? page_size : TKM;
@@ -142,16 +144,16 @@ extern "C" __global__ void __launch_bounds__(160, 1)
     }
   }
 
-  float o[16][4];                       // this warp's 16 heads x 128 value columns
+  float o[8][4];                        // this warp's 16 heads x 64 value columns
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 #pragma unroll
-  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-  if (warp < 4) {
+  if (warp < MW) {
     const int rA = lane >> 2, rB = rA + 8;
     const uint32_t q_addr = smem_u32(qs) + (((lane & 7) + ((lane >> 3) & 1) * 8) * kQStride + (lane >> 4) * 8) * 2;
     const uint32_t p_addr = smem_u32(ps) + (((lane & 7) + ((lane >> 3) & 1) * 8) * kPStride + (lane >> 4) * 8) * 2;
-    const int wtok = warp * 16;         // this warp's tokens inside a tile (for S)
+    const int wtok = warp * 8;          // this warp's tokens inside a tile (for S)
     int stage = 0;
     uint32_t phase = 0;
     bool live = true;
@@ -164,9 +166,8 @@ extern "C" __global__ void __launch_bounds__(160, 1)
       // the four warps meet at two barriers per tile, so a warp that gave up keeps walking (without touching the ring)
       const uint32_t sk = smem_u32(stages + stage * kTileBytes);
       const int tok0 = (tile_lo + t) * TKM;
-      float s[2][4];
-#pragma unroll
-      for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      float s[1][4];
+      s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
       if (live) {
 #pragma unroll 2
         for (int kk = 0; kk < DQK / 16; kk += 2) {
@@ -174,7 +175,7 @@ extern "C" __global__ void __launch_bounds__(160, 1)
           ldsm4(q_addr + kk * 32, qa[0][0], qa[0][1], qa[0][2], qa[0][3]);
           ldsm4(q_addr + kk * 32 + 32, qa[1][0], qa[1][1], qa[1][2], qa[1][3]);
 #pragma unroll
-          for (int n = 0; n < 2; ++n) {
+          for (int n = 0; n < 1; ++n) {
             const int tok = wtok + n * 8 + (lane & 7);
             uint32_t b0, b1, b2, b3;
             ldsm4(sk + lat_off(tok, kk * 2 + (lane >> 3)), b0, b1, b2, b3);
@@ -185,7 +186,7 @@ extern "C" __global__ void __launch_bounds__(160, 1)
       }
       float mxA = -INFINITY, mxB = -INFINITY;
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
+      for (int n = 0; n < 1; ++n) {
         const int j = tok0 + wtok + n * 8 + 2 * (lane & 3);
         s[n][0] = (live && j < L) ? s[n][0] * scale_log2 : -INFINITY;
         s[n][1] = (live && j + 1 < L) ? s[n][1] * scale_log2 : -INFINITY;
@@ -202,7 +203,7 @@ extern "C" __global__ void __launch_bounds__(160, 1)
       math_bar();                       // every warp's tile maxima are in
       float tA = -INFINITY, tB = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) { tA = fmaxf(tA, sm_m[w * HM + rA]); tB = fmaxf(tB, sm_m[w * HM + rB]); }
+      for (int w = 0; w < MW; ++w) { tA = fmaxf(tA, sm_m[w * HM + rA]); tB = fmaxf(tB, sm_m[w * HM + rB]); }
       const float mA = fmaxf(m_run[0], tA), mB = fmaxf(m_run[1], tB);
       const float mA_use = mA == -INFINITY ? 0.f : mA, mB_use = mB == -INFINITY ? 0.f : mB;
       const float cA = exp2f(m_run[0] - mA_use), cB = exp2f(m_run[1] - mB_use);
@@ -210,7 +211,7 @@ extern "C" __global__ void __launch_bounds__(160, 1)
       m_run[1] = mB;
       float sumA = 0.f, sumB = 0.f;
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
+      for (int n = 0; n < 1; ++n) {
         const float p0 = exp2f(s[n][0] - mA_use), p1 = exp2f(s[n][1] - mA_use);
         const float p2 = exp2f(s[n][2] - mB_use), p3 = exp2f(s[n][3] - mB_use);
         sumA += p0 + p1;
@@ -222,19 +223,19 @@ extern "C" __global__ void __launch_bounds__(160, 1)
       l_run[0] = l_run[0] * cA + sumA;
       l_run[1] = l_run[1] * cB + sumB;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) { o[i][0] *= cA; o[i][1] *= cA; o[i][2] *= cB; o[i][3] *= cB; }
+      for (int i = 0; i < 8; ++i) { o[i][0] *= cA; o[i][1] *= cA; o[i][2] *= cB; o[i][3] *= cB; }
       math_bar();                       // the tile's probabilities are in shared memory
       if (live) {
-        // O[:, 128 warp ..] += P V, V = the tile's first 512 columns
+        // O[:, 64 warp ..] += P V, V = the tile's first 512 columns
 #pragma unroll
         for (int ks = 0; ks < TKM / 16; ++ks) {
           uint32_t a0, a1, a2, a3;
           ldsm4(p_addr + ks * 32, a0, a1, a2, a3);
           const int tok = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
-          for (int dn = 0; dn < 8; ++dn) {
+          for (int dn = 0; dn < 4; ++dn) {
             uint32_t b0, b1, b2, b3;
-            ldsm4_t(sk + lat_off(tok, warp * 16 + dn * 2 + (lane >> 4)), b0, b1, b2, b3);
+            ldsm4_t(sk + lat_off(tok, warp * 8 + dn * 2 + (lane >> 4)), b0, b1, b2, b3);
             mma16816(o[dn * 2], a0, a1, a2, a3, b0, b1);
             mma16816(o[dn * 2 + 1], a0, a1, a2, a3, b2, b3);
           }
@@ -253,12 +254,12 @@ extern "C" __global__ void __launch_bounds__(160, 1)
     math_bar();
     float lA = 0.f, lB = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) { lA += sm_l[w * HM + rA]; lB += sm_l[w * HM + rB]; }
+    for (int w = 0; w < MW; ++w) { lA += sm_l[w * HM + rA]; lB += sm_l[w * HM + rB]; }
     if (split_total == 1) {
       const float iA = lA > 0.f ? 1.f / lA : 0.f, iB = lB > 0.f ? 1.f / lB : 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int c = warp * 128 + i * 8 + 2 * (lane & 3);
+      for (int i = 0; i < 8; ++i) {
+        const int c = warp * 64 + i * 8 + 2 * (lane & 3);
         if (rA < valid_rows)
           *reinterpret_cast<uint32_t*>(out + (size_t)seq * out_stride + (size_t)(head0 + rA) * DVV + c) = pack_bf16x2(o[i][0] * iA, o[i][1] * iA);
         if (rB < valid_rows)
@@ -271,8 +272,8 @@ extern "C" __global__ void __launch_bounds__(160, 1)
         if (r >= valid_rows) continue;
         const size_t base = ((size_t)seq * heads + head0 + r) * split_total + split_base + split;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int c = warp * 128 + i * 8 + 2 * (lane & 3);
+        for (int i = 0; i < 8; ++i) {
+          const int c = warp * 64 + i * 8 + 2 * (lane & 3);
           *reinterpret_cast<float2*>(ws_o + base * DVV + c) = make_float2(o[i][2 * hh], o[i][2 * hh + 1]);
         }
         if (warp == 0 && (lane & 3) == 0) {

@@ -11,7 +11,7 @@ from .attention import merge_partials
 from .launcher import Kernels, f32, i32, ptr
 
 DQK, DV, HEADS_PER_CTA = 576, 512, 16
-SMEM = 1024 + 2 * 64 * DQK * 2 + 16 * (DQK + 8) * 2 + 16 * 72 * 2 + 2 * 4 * 16 * 4 + 128
+SMEM = 1024 + 2 * 64 * DQK * 2 + 16 * (DQK + 8) * 2 + 16 * 72 * 2 + 2 * 8 * 16 * 4 + 128
 
 
 def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor, heads: int,
@@ -28,14 +28,14 @@ def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, 
     blocks = -(-heads // HEADS_PER_CTA)
     if splits is None:      # enough CTAs for the machine, never more than one per 64-token tile
         longest = int(seq_lens.max()) if seqs else 1
-        splits = max(1, min(32, -(-longest // 64), -(-k.sm_count // max(1, seqs * blocks))))
+        splits = max(1, min(128, -(-longest // 128), -(-2 * k.sm_count // max(1, seqs * blocks))))
     scale = (192 ** -0.5) if scale is None else scale
     lat = k.tensor_map_2d(cache.view(pages * page_size, DQK), min(page_size, 64), 64)
     ws_o = ws_ml = None
     if splits > 1:
         ws_o = torch.empty(seqs * heads * splits * DV, dtype=torch.float32, device=q.device)
         ws_ml = torch.empty(seqs * heads * splits * 2, dtype=torch.float32, device=q.device)
-    k.launch("mla_decode", "kern_mla_decode_bf16", (blocks, seqs, splits), (160,),
+    k.launch("mla_decode", "kern_mla_decode_bf16", (blocks, seqs, splits), (288,),
              [lat, ptr(q), ptr(out), ptr(ws_o), ptr(ws_ml), ptr(block_table), ptr(seq_lens), i32(seqs), i32(heads), i32(q.stride(0)),
               i32(out.stride(0)), i32(block_table.shape[1]), i32(page_size), i32(splits), i32(pages), f32(scale * 1.4426950408889634),
               ptr(k.err_word())], shared_mem=SMEM)
