@@ -28,7 +28,7 @@ def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, 
     blocks = -(-heads // HEADS_PER_CTA)
     if splits is None:      # enough CTAs for the machine, never more than one per 64-token tile
         longest = block_table.shape[1] * page_size      # the table's reach: no device read on the launch path
-        splits = max(1, min(128, -(-longest // 128), -(-2 * k.sm_count // max(1, seqs * blocks))))
+        splits = max(1, min(128, -(-longest // 256), -(-k.sm_count // max(1, seqs * blocks))))
     scale = (192 ** -0.5) if scale is None else scale
     lat = k.tensor_map_2d(cache.view(pages * page_size, DQK), min(page_size, 64), 64)
     ws_o = ws_ml = None
