@@ -6,11 +6,13 @@
 //   cache  paged latent rows [page][page_size][576] bf16, one "kv head"
 //   out    [seqs, H, 512] bf16 (the caller applies W_UV / o_proj), or split partials (o, m, l) for the usual merge
 //
-// A CTA owns 16 heads of one sequence (one m16 tile) and one KV split. Eight math warps: for S = Q K^T each takes 8 of
-// the tile's 64 tokens; the probabilities go through shared memory (all warps use the tile's common row maximum), and
-// for O += P V each warp owns 64 of the 512 value columns — a warp's accumulator is 16 x 64, not 16 x 512. A ninth
-// warp feeds a two-stage ring of 72 KB tiles by TMA (nine 64-column boxes per tile, 128-byte swizzle). (Four math
-// warps of 16 tokens / 128 columns measured 4.1 us per tile: too few warps to hide the ldmatrix -> mma chains.)
+// A CTA owns 16 heads of one sequence (one m16 tile) and one KV split. MW math warps, a tile of 8 MW tokens: for
+// S = Q K^T each warp takes 8 of the tile's tokens; the probabilities go through shared memory (all warps use the tile's
+// common row maximum), and for O += P V each warp owns 512 / MW of the value columns — a warp's accumulator is
+// 16 x 128, not 16 x 512. One more warp feeds the ring of tiles by TMA (nine 64-column boxes per tile, 128-byte
+// swizzle). MW = 4: 32-token tiles (36 KB) in a four-stage ring; 64-token tiles fit only two stages beside the 18 KB of
+// queries, which left one tile in flight while the other was consumed (0.56 of the copy bandwidth; four or eight math
+// warps made no difference there).
 // With 16 heads per rank (tensor parallel 8) a tile is read once per sequence; with more heads the CTAs of a sequence
 // share the tile through L2. One row per sequence (decode); verify rows of a speculative round are not handled here.
 // Reference: the reference takes this kernel from a CuTe-DSL build (MLA decode, sm100) and the context form from a
@@ -21,12 +23,13 @@ using namespace kern;
 
 namespace {
 
-constexpr int TKM = 64;                  // tokens per tile
+constexpr int MW = 4;                    // math warps: each 8 tokens of a tile for S, 512 / MW value columns for O
+constexpr int TKM = 8 * MW;              // tokens per tile
 constexpr int DQK = 576, DVV = 512;
 constexpr int HM = 16;                   // heads per CTA
-constexpr int MW = 8;                    // math warps: each 64 / MW tokens of a tile for S, 512 / MW value columns for O
 constexpr int kTileBytes = TKM * DQK * 2;
-constexpr int kStagesM = 2;
+constexpr int kStagesM = MW == 4 ? 4 : 2;    // 32-token tiles (36 KB) four deep, or 64-token tiles two deep
+constexpr int ON = DVV / MW / 8;             // 8-column accumulator tiles per warp
 constexpr int kQStride = DQK + 8, kPStride = TKM + 8;
 constexpr int kQBytes = HM * kQStride * 2, kPBytes = HM * kPStride * 2;
 
@@ -45,15 +48,15 @@ KERN_DEVICE uint32_t lat_off(int tok, int chunk) {
   const int cb = chunk >> 3, c = chunk & 7;
   return (uint32_t)(cb * (TKM * 128) + tok * 128 + ((c ^ (tok & 7)) << 4));
 }
-KERN_DEVICE void math_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+KERN_DEVICE void math_bar() { asm volatile("bar.sync 1, %0;" ::"n"(MW * 32) : "memory"); }
 
 }  // namespace
 
-// grid [ceil(H / 16), seqs, splits], block 288, dynamic shared memory MLA_SMEM bytes.
+// grid [ceil(H / 16), seqs, splits], block 32 MW + 32, dynamic shared memory MLA_SMEM bytes.
 // `splits` packs (launch splits | first slot << 8 | slots per (row, head) << 16) as the GQA decode kernel does.
 constexpr int MLA_SMEM = 1024 + kStagesM * kTileBytes + kQBytes + kPBytes + 2 * MW * HM * 4 + 128;
 
-extern "C" __global__ void __launch_bounds__(288, 1)
+extern "C" __global__ void __launch_bounds__(MW * 32 + 32, 1)
     kern_mla_decode_bf16(const __grid_constant__ CUtensorMap lat_map, const __nv_bfloat16* q, __nv_bfloat16* out, float* ws_o,
                          float* ws_ml, const int* block_table, const int* seq_lens, int seqs, int heads, int q_stride,
                          int out_stride, int max_pages, int page_size, int splits, int pool_pages, float scale_log2, int* err) {
@@ -144,10 +147,10 @@ extern "C" __global__ void __launch_bounds__(288, 1)
     }
   }
 
-  float o[8][4];                        // this warp's 16 heads x 64 value columns
+  float o[ON][4];                       // this warp's 16 heads x (512 / MW) value columns
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 #pragma unroll
-  for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int i = 0; i < ON; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
   if (warp < MW) {
     const int rA = lane >> 2, rB = rA + 8;
@@ -223,19 +226,19 @@ extern "C" __global__ void __launch_bounds__(288, 1)
       l_run[0] = l_run[0] * cA + sumA;
       l_run[1] = l_run[1] * cB + sumB;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { o[i][0] *= cA; o[i][1] *= cA; o[i][2] *= cB; o[i][3] *= cB; }
+      for (int i = 0; i < ON; ++i) { o[i][0] *= cA; o[i][1] *= cA; o[i][2] *= cB; o[i][3] *= cB; }
       math_bar();                       // the tile's probabilities are in shared memory
       if (live) {
-        // O[:, 64 warp ..] += P V, V = the tile's first 512 columns
+        // O[:, (512 / MW) warp ..] += P V, V = the tile's first 512 columns
 #pragma unroll
         for (int ks = 0; ks < TKM / 16; ++ks) {
           uint32_t a0, a1, a2, a3;
           ldsm4(p_addr + ks * 32, a0, a1, a2, a3);
           const int tok = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
-          for (int dn = 0; dn < 4; ++dn) {
+          for (int dn = 0; dn < ON / 2; ++dn) {
             uint32_t b0, b1, b2, b3;
-            ldsm4_t(sk + lat_off(tok, warp * 8 + dn * 2 + (lane >> 4)), b0, b1, b2, b3);
+            ldsm4_t(sk + lat_off(tok, warp * ON + dn * 2 + (lane >> 4)), b0, b1, b2, b3);
             mma16816(o[dn * 2], a0, a1, a2, a3, b0, b1);
             mma16816(o[dn * 2 + 1], a0, a1, a2, a3, b2, b3);
           }
@@ -258,8 +261,8 @@ extern "C" __global__ void __launch_bounds__(288, 1)
     if (split_total == 1) {
       const float iA = lA > 0.f ? 1.f / lA : 0.f, iB = lB > 0.f ? 1.f / lB : 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int c = warp * 64 + i * 8 + 2 * (lane & 3);
+      for (int i = 0; i < ON; ++i) {
+        const int c = warp * (DVV / MW) + i * 8 + 2 * (lane & 3);
         if (rA < valid_rows)
           *reinterpret_cast<uint32_t*>(out + (size_t)seq * out_stride + (size_t)(head0 + rA) * DVV + c) = pack_bf16x2(o[i][0] * iA, o[i][1] * iA);
         if (rB < valid_rows)
@@ -272,8 +275,8 @@ extern "C" __global__ void __launch_bounds__(288, 1)
         if (r >= valid_rows) continue;
         const size_t base = ((size_t)seq * heads + head0 + r) * split_total + split_base + split;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int c = warp * 64 + i * 8 + 2 * (lane & 3);
+        for (int i = 0; i < ON; ++i) {
+          const int c = warp * (DVV / MW) + i * 8 + 2 * (lane & 3);
           *reinterpret_cast<float2*>(ws_o + base * DVV + c) = make_float2(o[i][2 * hh], o[i][2 * hh + 1]);
         }
         if (warp == 0 && (lane & 3) == 0) {

@@ -11,7 +11,8 @@ from .attention import merge_partials
 from .launcher import Kernels, f32, i32, ptr
 
 DQK, DV, HEADS_PER_CTA = 576, 512, 16
-SMEM = 1024 + 2 * 64 * DQK * 2 + 16 * (DQK + 8) * 2 + 16 * 72 * 2 + 2 * 8 * 16 * 4 + 128
+MATH_WARPS, TILE, STAGES = 4, 32, 4
+SMEM = 1024 + STAGES * TILE * DQK * 2 + 16 * (DQK + 8) * 2 + 16 * (TILE + 8) * 2 + 2 * MATH_WARPS * 16 * 4 + 128
 
 
 def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor, heads: int,
@@ -22,7 +23,7 @@ def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, 
     seqs = q.shape[0]
     pages, page_size, w = cache.shape
     assert w == DQK and cache.dtype == torch.bfloat16 and q.dtype == torch.bfloat16 and q.shape[1] == heads * DQK
-    assert 64 % min(page_size, 64) == 0
+    assert page_size % TILE == 0 or TILE % page_size == 0
     if out is None:
         out = torch.empty(seqs, heads * DV, dtype=torch.bfloat16, device=q.device)
     blocks = -(-heads // HEADS_PER_CTA)
@@ -30,12 +31,12 @@ def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, 
         longest = block_table.shape[1] * page_size      # the table's reach: no device read on the launch path
         splits = max(1, min(128, -(-longest // 256), -(-k.sm_count // max(1, seqs * blocks))))
     scale = (192 ** -0.5) if scale is None else scale
-    lat = k.tensor_map_2d(cache.view(pages * page_size, DQK), min(page_size, 64), 64)
+    lat = k.tensor_map_2d(cache.view(pages * page_size, DQK), min(page_size, TILE), 64)
     ws_o = ws_ml = None
     if splits > 1:
         ws_o = torch.empty(seqs * heads * splits * DV, dtype=torch.float32, device=q.device)
         ws_ml = torch.empty(seqs * heads * splits * 2, dtype=torch.float32, device=q.device)
-    k.launch("mla_decode", "kern_mla_decode_bf16", (blocks, seqs, splits), (288,),
+    k.launch("mla_decode", "kern_mla_decode_bf16", (blocks, seqs, splits), (MATH_WARPS * 32 + 32,),
              [lat, ptr(q), ptr(out), ptr(ws_o), ptr(ws_ml), ptr(block_table), ptr(seq_lens), i32(seqs), i32(heads), i32(q.stride(0)),
               i32(out.stride(0)), i32(block_table.shape[1]), i32(page_size), i32(splits), i32(pages), f32(scale * 1.4426950408889634),
               ptr(k.err_word())], shared_mem=SMEM)
