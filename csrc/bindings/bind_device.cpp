@@ -4,6 +4,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include "../runtime/cupti_trace.hpp"
 #include "../runtime/device.hpp"
 
 namespace py = pybind11;
@@ -31,6 +32,38 @@ struct PyGraph {
 
 void bind_device(py::module_& m) {
   m.def("cuda_available", [] { return Cuda::available(); });
+  // kernel activity tracing (CUPTI by dlopen): start / collect / stop; records are
+  // (name, start_ns, end_ns, stream, (gx, gy, gz), (bx, by, bz), registers, shared_bytes)
+  m.def("cupti_available", [] {
+    std::string why;
+    const bool ok = CuptiTrace::get().available(&why);
+    return py::make_tuple(ok, why);
+  });
+  m.def("cupti_start", [] { CuptiTrace::get().start(); });
+  auto to_py = [](const std::vector<KernelRecord>& recs) {
+    py::list out;
+    for (auto& r : recs)
+      out.append(py::make_tuple(r.name, r.start_ns, r.end_ns, r.stream, py::make_tuple(r.grid[0], r.grid[1], r.grid[2]),
+                                py::make_tuple(r.block[0], r.block[1], r.block[2]), r.registers, r.shared_bytes));
+    return out;
+  };
+  m.def("cupti_collect", [to_py] {
+    std::vector<KernelRecord> recs;
+    {
+      py::gil_scoped_release rel;
+      recs = CuptiTrace::get().collect();
+    }
+    return to_py(recs);
+  });
+  m.def("cupti_stop", [to_py] {
+    std::vector<KernelRecord> recs;
+    {
+      py::gil_scoped_release rel;
+      recs = CuptiTrace::get().stop();
+    }
+    return to_py(recs);
+  });
+  m.def("cupti_dropped", [] { return CuptiTrace::get().dropped(); });
 
   py::class_<PyModule>(m, "Module");
   py::class_<PyFunction>(m, "Function").def_readonly("name", &PyFunction::name);

@@ -162,3 +162,67 @@ class TracedEngine:
 
 def prometheus_lines(recorder: Recorder, steps_by: dict | None = None) -> list[str]:
     return ["# TYPE kern_trace_dropped_records_total counter", f"kern_trace_dropped_records_total {recorder.dropped}"]
+
+
+# ---- kernel activity through CUPTI --------------------------------------------------------------------------------------
+class KernelTrace:
+    """Every kernel this process launches while the trace is on, with its device start and end (CUPTI activity records,
+    `csrc/runtime/cupti_trace.hpp`): no events around launches, graph replays included.
+
+        with KernelTrace() as kt:
+            engine.step(...)
+            torch.cuda.synchronize()
+        for name, stats in kt.by_kernel().items(): ...
+
+    Reference counterpart: crates/kern-runtime/src/trace.rs:171-283 (launch tags and folding into steps)."""
+
+    FIELDS = ("name", "start_ns", "end_ns", "stream", "grid", "block", "registers", "shared_bytes")
+
+    def __init__(self):
+        from . import _native
+
+        self._n = _native
+        ok, why = _native.cupti_available()
+        if not ok:
+            raise RuntimeError(f"kernel tracing is unavailable: {why}")
+        self.records: list[dict] = []
+
+    def __enter__(self):
+        self._n.cupti_start()
+        return self
+
+    def collect(self) -> list[dict]:
+        """Records since the last collect (synchronise the streams first); also appended to `self.records`."""
+        new = [dict(zip(self.FIELDS, r)) for r in self._n.cupti_collect()]
+        self.records += new
+        return new
+
+    def __exit__(self, *exc):
+        self.records += [dict(zip(self.FIELDS, r)) for r in self._n.cupti_stop()]
+        return False
+
+    def by_kernel(self) -> dict[str, dict]:
+        """name -> {launches, total_us, mean_us, max_us}, longest total first."""
+        out: dict[str, dict] = {}
+        for r in self.records:
+            d = out.setdefault(r["name"], {"launches": 0, "total_us": 0.0, "max_us": 0.0})
+            us = (r["end_ns"] - r["start_ns"]) / 1e3
+            d["launches"] += 1
+            d["total_us"] += us
+            d["max_us"] = max(d["max_us"], us)
+        for d in out.values():
+            d["mean_us"] = d["total_us"] / d["launches"]
+        return dict(sorted(out.items(), key=lambda kv: -kv[1]["total_us"]))
+
+    def write(self, path) -> None:
+        """The raw records as Parquet (zstd): name, start_ns, end_ns, stream, grid/block extents, registers, shared_bytes."""
+        import pyarrow as pa
+        import pyarrow.parquet as pq
+
+        cols = {"name": [r["name"] for r in self.records], "start_ns": [r["start_ns"] for r in self.records],
+                "end_ns": [r["end_ns"] for r in self.records], "stream": [r["stream"] for r in self.records],
+                "registers": [r["registers"] for r in self.records], "shared_bytes": [r["shared_bytes"] for r in self.records]}
+        for i, ax in enumerate("xyz"):
+            cols["grid_" + ax] = [r["grid"][i] for r in self.records]
+            cols["block_" + ax] = [r["block"][i] for r in self.records]
+        pq.write_table(pa.table(cols), str(path), compression="zstd")

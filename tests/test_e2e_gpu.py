@@ -152,3 +152,31 @@ def test_guard_bands_stay_clean_and_report_an_overrun(cuda):
     past.fill_(7)
     torch.cuda.synchronize()
     assert rt.check_guards() == ["xn (after)"]
+
+
+def test_kernel_activity_trace_names_our_kernels(tiny, tmp_path):
+    """CUPTI activity records of a prefill and a few graph-replayed decode steps: our entry points by name, positive
+    durations, launch shapes; folded by kernel and written as Parquet."""
+    import pyarrow.parquet as pq
+    from kern_b200.engine import Engine
+    from kern_b200.trace import KernelTrace
+
+    cfg, weights, rt = tiny
+    eng = Engine(rt)
+    s = eng.open(64)
+    with KernelTrace() as kt:
+        tok = eng.step([(s, list(range(1, 30)))])[0][0]
+        for _ in range(3):
+            tok = eng.step([(s, [tok])])[0][0]
+        torch.cuda.synchronize()
+        first = kt.collect()
+    eng.close(s)
+    assert first and len(kt.records) >= len(first)
+    names = {r["name"] for r in kt.records}
+    assert any(n.startswith("kern_rms_norm") or n.startswith("kern_fused_add_rms_norm") for n in names), sorted(names)[:20]
+    assert any(n.startswith("kern_gemm_bf16") or n.startswith("kern_gemv_bf16") for n in names)
+    assert all(r["end_ns"] > r["start_ns"] and r["block"][0] >= 1 for r in kt.records)
+    top = kt.by_kernel()
+    assert sum(d["launches"] for d in top.values()) == len(kt.records)
+    kt.write(tmp_path / "kernels.parquet")
+    assert pq.ParquetFile(tmp_path / "kernels.parquet").read().num_rows == len(kt.records)
