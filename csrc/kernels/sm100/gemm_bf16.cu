@@ -270,11 +270,23 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         const size_t off = (size_t)b * BM * K * 2, vecs = (size_t)rows * K * 2 / 16;
         const uint8_t* src = reinterpret_cast<const uint8_t*>(ag.peers[b / ag_bpr]) + off;
         uint8_t* dst = mine + off;
-        for (size_t v = (size_t)blockIdx.x * 64 + gt; v < vecs; v += (size_t)gridDim.x * 64) {
-          uint4 x;
-          asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                       : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w) : "l"(src + v * 16) : "memory");
-          *reinterpret_cast<uint4*>(dst + v * 16) = x;
+        // eight loads in flight per thread before the first store: a peer load takes a couple of microseconds, and
+        // one at a time they would add up to the whole transfer
+        const size_t stride = (size_t)gridDim.x * 64;
+        for (size_t v0 = (size_t)blockIdx.x * 64 + gt; v0 < vecs; v0 += stride * 8) {
+          uint4 x[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const size_t v = v0 + u * stride;
+            if (v < vecs)
+              asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(x[u].x), "=r"(x[u].y), "=r"(x[u].z), "=r"(x[u].w) : "l"(src + v * 16));
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const size_t v = v0 + u * stride;
+            if (v < vecs) *reinterpret_cast<uint4*>(dst + v * 16) = x[u];
+          }
         }
         __threadfence();
         asm volatile("fence.proxy.async;" ::: "memory");
