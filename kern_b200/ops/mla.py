@@ -11,7 +11,7 @@ from .attention import merge_partials
 from .launcher import Kernels, f32, i32, ptr
 
 DQK, DV, HEADS_PER_CTA = 576, 512, 16
-MATH_WARPS, TILE, STAGES = 4, 32, 4
+MATH_WARPS, TILE, STAGES = 8, 64, 2
 SMEM = 1024 + STAGES * TILE * DQK * 2 + 16 * (DQK + 8) * 2 + 16 * (TILE + 8) * 2 + 2 * MATH_WARPS * 16 * 4 + 128
 
 
@@ -29,7 +29,7 @@ def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, 
     blocks = -(-heads // HEADS_PER_CTA)
     if splits is None:      # enough CTAs for the machine, never more than one per 64-token tile
         longest = block_table.shape[1] * page_size      # the table's reach: no device read on the launch path
-        splits = max(1, min(128, -(-longest // 256), -(-k.sm_count // max(1, seqs * blocks))))
+        splits = max(1, min(128, -(-longest // 256), k.sm_count // max(1, seqs * blocks)))      # never more CTAs than SMs
     scale = (192 ** -0.5) if scale is None else scale
     lat = k.tensor_map_2d(cache.view(pages * page_size, DQK), min(page_size, TILE), 64)
     ws_o = ws_ml = None
