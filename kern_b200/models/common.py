@@ -221,10 +221,14 @@ def gemm_op(n: int, k: int, *, epilogue: str = "store", rows_var: str = "tokens"
 AG_MAX_BLOCKS = 128      # 128-row blocks the fused all-gather GEMM keeps counters for (16 384 rows)
 
 
-def ag_gemm_buffers(rows_max: int, k: int, nranks: int, group: str = "tp") -> dict:
+def ag_gemm_buffers(rows_max: int, k: int, nranks: int, group: str = "tp", alternate: bool = False) -> dict:
     """Buffers of the all-gather fused into the GEMM: `ag.g` holds all rows (this rank writes its slice, the kernel
-    pulls the rest), the barrier's flags, and the arrival counters."""
-    return {"ag.g": {"dtype": "bf16", "shape": [rows_max, k], "kind": "carry", "export": True},
+    pulls the rest), the barrier's flags, and the arrival counters. `alternate`: a second row buffer `ag.g1`, for
+    callers that switch buffers from call to call and so need no barrier after the GEMM."""
+    second = {"ag.g1": {"dtype": "bf16", "shape": [rows_max, k], "kind": "carry", "export": True},
+              "ag.g1_peers": {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": "ag.g1", "group": group}} if alternate else {}
+    return {**second,
+            "ag.g": {"dtype": "bf16", "shape": [rows_max, k], "kind": "carry", "export": True},
             "ag.g_peers": {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": "ag.g", "group": group},
             "ag.bar": {"dtype": "u32", "shape": [32], "kind": "carry", "export": True},
             "ag.bar_peers": {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": "ag.bar", "group": group},

@@ -22,15 +22,21 @@ def manifest(world: int, rows_max: int, n: int, k: int) -> dict:
     bufs = {"w": {"dtype": "bf16", "shape": [n, k], "kind": "input"},
             "c": {"dtype": "bf16", "shape": ["rows", n], "kind": "output"},
             "error": {"dtype": "i32", "shape": [1], "kind": "output"}}
-    bufs.update(C.ag_gemm_buffers(rows_max, k, world))
+    bufs.update(C.ag_gemm_buffers(rows_max, k, world, alternate=True))
     B = lambda name: {"buf": name}
-    call = {"op": "ag_gemm", "args": [B("ag.g"), B("ag.g_peers"), B("w"), B("c"), B("ag.bar"), B("ag.bar_peers"), B("ag.bar_epoch"),
-                                      B("ag.blocks"), B("ag.cta_epochs"), B("error"), {"var": "rows"}]}
+    args = lambda g: [B(g), B(g + "_peers"), B("w"), B("c"), B("ag.bar"), B("ag.bar_peers"), B("ag.bar_epoch"),
+                      B("ag.blocks"), B("ag.cta_epochs"), B("error"), {"var": "rows"}]
+    call = {"op": "ag_gemm", "args": args("ag.g")}
+    # the layout a decoder uses: consecutive calls switch between two row buffers, and the barrier that opens call k + 1
+    # is what tells everyone that call k's pulls are over, so nothing follows the GEMM
+    pair = [{"op": "ag_gemm_open", "args": args("ag.g")}, {"op": "ag_gemm_open", "args": args("ag.g1")}]
     return {"schema_version": 7, "model": "ag-gemm-check", "vars": {"rows": {"max": rows_max, "axis": "rows"}},
             "topology": {"groups": {"tp": world}}, "states": {}, "buffers": bufs,
-            "modules": C.modules_for(["ag_gemm", "tp_allreduce_norm"]), "ops": {"ag_gemm": C.ag_gemm_op(n, k, world)},
+            "modules": C.modules_for(["ag_gemm", "tp_allreduce_norm"]),
+            "ops": {"ag_gemm": C.ag_gemm_op(n, k, world), "ag_gemm_open": C.ag_gemm_op(n, k, world, closing_barrier=False)},
             "programs": {"step": {"calls": [call]},
-                         "step_graph": {"batch": {"groups": 1, "rows": "rows"}, "graph": True, "calls": [call]}}}
+                         "step_graph": {"batch": {"groups": 1, "rows": "rows"}, "graph": True, "calls": [call]},
+                         "pair_graph": {"batch": {"groups": 1, "rows": "rows"}, "graph": True, "calls": pair * 2}}}
 
 
 def main(argv=None) -> int:
@@ -56,12 +62,16 @@ def main(argv=None) -> int:
     rt.tensor("w").copy_(w)
     G = rt.tensor("ag.g")
     results = []
-    for it, tr in enumerate(a.rows + a.rows[:2]):
-        program = "step_graph" if it >= len(a.rows) else "step"
+    G1 = rt.tensor("ag.g1")
+    for it, tr in enumerate(a.rows + a.rows[:2] + a.rows[:1]):
+        program = "step" if it < len(a.rows) else ("step_graph" if it < len(a.rows) + 2 else "pair_graph")
         T = tr * world
         slices = [(torch.randn(tr, a.k, generator=torch.Generator().manual_seed(100 * it + r)) * 0.5).to(torch.bfloat16) for r in range(world)]
         G[:T].fill_(float("nan"))                              # what is not pulled stays NaN and poisons the product
         G[rank * tr:(rank + 1) * tr].copy_(slices[rank].to(dev))
+        if program == "pair_graph":
+            G1[:T].fill_(float("nan"))
+            G1[rank * tr:(rank + 1) * tr].copy_(slices[rank].to(dev))
         torch.cuda.synchronize()
         rt.run(program, {"rows": T})
         rt.check_error()
@@ -87,6 +97,13 @@ def main(argv=None) -> int:
             def fused():
                 rt.issue("step_graph", {"rows": T})
 
+            G1 = rt.tensor("ag.g1")
+            G1[rank * tr:(rank + 1) * tr].copy_(mine)
+            torch.cuda.synchronize()
+
+            def alternating():          # four GEMMs per replay, two row buffers, no closing barrier
+                rt.issue("pair_graph", {"rows": T})
+
             full = torch.empty(T, a.k, dtype=torch.bfloat16, device=dev)
             out = torch.empty(T, a.n, dtype=torch.bfloat16, device=dev)
 
@@ -98,7 +115,8 @@ def main(argv=None) -> int:
                 GM.gemm(full, w, out=out)
 
             row = {"rows_per_rank": tr}
-            for name, fn, st in (("fused_us", fused, stream), ("allgather_then_gemm_us", two_step, torch.cuda.current_stream())):
+            for name, fn, st, per in (("fused_us", fused, stream, 1), ("fused_alternating_us", alternating, stream, 4),
+                                      ("allgather_then_gemm_us", two_step, torch.cuda.current_stream(), 1)):
                 for _ in range(3):
                     fn()
                 torch.cuda.synchronize()
@@ -110,7 +128,7 @@ def main(argv=None) -> int:
                     fn()
                 e1.record(st)
                 torch.cuda.synchronize()
-                t = torch.tensor([e0.elapsed_time(e1) / 20 * 1e3], device=dev)
+                t = torch.tensor([e0.elapsed_time(e1) / 20 / per * 1e3], device=dev)
                 if world > 1:
                     dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 row[name] = round(float(t), 1)
