@@ -190,3 +190,59 @@ KERN_MOE_GEMM_ENTRY(kern_moe_gemm_bf16_n64, 64, 0)
 KERN_MOE_GEMM_ENTRY(kern_moe_gemm_bf16_swiglu_n256, 256, 3)
 KERN_MOE_GEMM_ENTRY(kern_moe_gemm_bf16_swiglu_n128, 128, 3)
 KERN_MOE_GEMM_ENTRY(kern_moe_gemm_bf16_swiglu_n64, 64, 3)
+
+// ---- expert parallel over sharded tokens: dispatch by pull, combine by push -------------------------------------------
+// Tokens live on their home rank (rows_per_rank each, token t = home * rows_per_rank + local row); every rank knows
+// every token's expert choices (an all-gather of the ids) and plans over all of them, keeping the entries of its own
+// experts. The gather below IS the dispatch: it reads exactly the rows this rank's experts need, straight out of the
+// home ranks' exported activation buffers (16-byte peer loads, several in flight per thread). After the grouped GEMMs,
+// the return kernel pushes every result row into slot (local row, choice) of the home rank's exported return buffer
+// (plain 16-byte peer stores; a slot has exactly one writer), and the home rank's combine weighs its k slots.
+// Barriers (kern_peer_barrier) stand before the pull and after the push.
+// Reference counterpart: docs/roadmap.md:13-16,63 (all-to-all / all-gather -> FC1 -> FC2 -> finalize -> reduce-scatter).
+
+// grid = entries (tokens * k), block 128.
+extern "C" __global__ void __launch_bounds__(128)
+    kern_moe_gather_peers_bf16(const unsigned long long* x_peers, const int* perm, __nv_bfloat16* x_perm, int entries, int k,
+                               int hidden, int rows_per_rank) {
+  pdl_wait();
+  const int i = blockIdx.x;
+  if (i >= entries) return;
+  const int r = perm[i];
+  if (r < 0) return;
+  const int t = i / k;
+  const uint8_t* src = reinterpret_cast<const uint8_t*>(x_peers[t / rows_per_rank]) + (size_t)(t % rows_per_rank) * hidden * 2;
+  uint4* dst = reinterpret_cast<uint4*>(x_perm + (size_t)r * hidden);
+  const int vecs = hidden / 8;
+  for (int v0 = threadIdx.x; v0 < vecs; v0 += 128 * 4) {
+    uint4 x[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * 128;
+      if (v < vecs)
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(x[u].x), "=r"(x[u].y), "=r"(x[u].z), "=r"(x[u].w) : "l"(src + (size_t)v * 16));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * 128;
+      if (v < vecs) dst[v] = x[u];
+    }
+  }
+}
+
+// grid = entries, block 128: y_perm[perm[i]] -> ret of the home rank, slot (local row, choice).
+extern "C" __global__ void __launch_bounds__(128)
+    kern_moe_return_bf16(const __nv_bfloat16* y_perm, const int* perm, const unsigned long long* ret_peers, int entries, int k,
+                         int hidden, int rows_per_rank) {
+  pdl_wait();
+  const int i = blockIdx.x;
+  if (i >= entries) return;
+  const int r = perm[i];
+  if (r < 0) return;
+  const int t = i / k, j = i % k;
+  uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(ret_peers[t / rows_per_rank]) +
+                                        ((size_t)(t % rows_per_rank) * k + j) * hidden * 2);
+  const uint4* src = reinterpret_cast<const uint4*>(y_perm + (size_t)r * hidden);
+  for (int v = threadIdx.x; v < hidden / 8; v += 128) dst[v] = src[v];
+}

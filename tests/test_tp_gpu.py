@@ -148,3 +148,26 @@ def test_allgather_gemm_fused(world):
     assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
     line = next(json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))
     assert line["world"] == world and all(r["ok"] for r in line["results"]), line
+
+
+def test_expert_parallel_all_to_all_one_rank(cuda):
+    """The sharded-token expert-parallel layer with a group of one: dispatch and return go through the peer tables
+    (which hold this rank's own addresses)."""
+    from kern_b200.parallel import ep_check
+
+    assert ep_check.main(["--rows", "8", "130"]) == 0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_all_to_all(world):
+    """Tokens and experts sharded over the ranks: ids all-gathered, rows pulled from their home ranks by the gather that
+    feeds the grouped GEMMs, results pushed back into per-(token, choice) slots; equals the dense mixture."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29600 + world), "-m", "kern_b200.parallel.ep_check"]
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
+    line = next(json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))
+    assert line["world"] == world and all(r["ok"] for r in line["results"]), line
