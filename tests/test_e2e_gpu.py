@@ -164,6 +164,12 @@ def test_kernel_activity_trace_names_our_kernels(tiny, tmp_path):
     cfg, weights, rt = tiny
     eng = Engine(rt)
     s = eng.open(64)
+    try:
+        probe = KernelTrace()
+        probe.__enter__()
+        probe.__exit__(None, None, None)
+    except RuntimeError as e:      # no CUPTI on this machine, or another tool holds it
+        pytest.skip(f"kernel activity tracing is not available here: {e}")
     with KernelTrace() as kt:
         tok = eng.step([(s, list(range(1, 30)))])[0][0]
         for _ in range(3):
