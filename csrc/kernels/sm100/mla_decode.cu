@@ -10,8 +10,10 @@
 // S = Q K^T each warp takes 8 of the tile's tokens; the probabilities go through shared memory (all warps use the tile's
 // common row maximum), and for O += P V each warp owns 512 / MW of the value columns — a warp's accumulator is
 // 16 x 64, not 16 x 512. One more warp feeds the ring of tiles by TMA (nine 64-column boxes per tile, 128-byte
-// swizzle). MW = 8: 64-token tiles (72 KB) in a two-stage ring. MW = 4 (32-token tiles, four stages) measured slower
-// (0.20 ms against 0.17 ms for 64 sequences of 8192 rows): the deeper ring does not pay for twice the barriers per token.
+// swizzle). Tiles of 48 tokens (54 KB) in a three-stage ring: six of the eight warps score (8 tokens each), all
+// eight own 64 value columns. 64-token tiles fit only two stages beside the 18 KB of queries (one tile in flight while
+// the other is consumed: 0.56 of the copy bandwidth); 32-token tiles four deep measured slower than that (twice the
+// barriers per token).
 // With 16 heads per rank (tensor parallel 8) a tile is read once per sequence; with more heads the CTAs of a sequence
 // share the tile through L2. One row per sequence (decode); verify rows of a speculative round are not handled here.
 // Reference: the reference takes this kernel from a CuTe-DSL build (MLA decode, sm100) and the context form from a
@@ -22,12 +24,13 @@ using namespace kern;
 
 namespace {
 
-constexpr int MW = 8;                    // math warps: each 8 tokens of a tile for S, 512 / MW value columns for O
-constexpr int TKM = 8 * MW;              // tokens per tile
+constexpr int MW = 8;                    // math warps: 512 / MW value columns each for O
+constexpr int TKM = 48;                  // tokens per tile
+constexpr int SW = TKM / 8;              // warps that take part in S = Q K^T, 8 tokens of the tile each
 constexpr int DQK = 576, DVV = 512;
 constexpr int HM = 16;                   // heads per CTA
 constexpr int kTileBytes = TKM * DQK * 2;
-constexpr int kStagesM = MW == 4 ? 4 : 2;    // 32-token tiles (36 KB) four deep, or 64-token tiles two deep
+constexpr int kStagesM = TKM == 48 ? 3 : 2;   // 48-token tiles (54 KB) three deep, or 64-token tiles two deep
 constexpr int ON = DVV / MW / 8;             // 8-column accumulator tiles per warp
 constexpr int kQStride = DQK + 8, kPStride = TKM + 8;
 constexpr int kQBytes = HM * kQStride * 2, kPBytes = HM * kPStride * 2;
@@ -111,7 +114,8 @@ extern "C" __global__ void __launch_bounds__(MW * 32 + 32, 1)
   if (warp == MW) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      const int box_rows = page_size < TKM ? page_size : TKM;
+      // a box never crosses a page: 16-row boxes for the 48-token tile, whole tiles (or pages) otherwise
+      const int box_rows = TKM % 32 != 0 ? 16 : (page_size < TKM ? page_size : TKM);
       const int boxes = TKM / box_rows;
       int stage = 0;
       uint32_t phase = 0;
@@ -170,7 +174,8 @@ extern "C" __global__ void __launch_bounds__(MW * 32 + 32, 1)
       const int tok0 = (tile_lo + t) * TKM;
       float s[1][4];
       s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
-      if (live) {
+      const bool scoring = live && warp < SW;
+      if (scoring) {
 #pragma unroll 2
         for (int kk = 0; kk < DQK / 16; kk += 2) {
           uint32_t qa[2][4];
@@ -190,10 +195,10 @@ extern "C" __global__ void __launch_bounds__(MW * 32 + 32, 1)
 #pragma unroll
       for (int n = 0; n < 1; ++n) {
         const int j = tok0 + wtok + n * 8 + 2 * (lane & 3);
-        s[n][0] = (live && j < L) ? s[n][0] * scale_log2 : -INFINITY;
-        s[n][1] = (live && j + 1 < L) ? s[n][1] * scale_log2 : -INFINITY;
-        s[n][2] = (live && j < L) ? s[n][2] * scale_log2 : -INFINITY;
-        s[n][3] = (live && j + 1 < L) ? s[n][3] * scale_log2 : -INFINITY;
+        s[n][0] = (scoring && j < L) ? s[n][0] * scale_log2 : -INFINITY;
+        s[n][1] = (scoring && j + 1 < L) ? s[n][1] * scale_log2 : -INFINITY;
+        s[n][2] = (scoring && j < L) ? s[n][2] * scale_log2 : -INFINITY;
+        s[n][3] = (scoring && j + 1 < L) ? s[n][3] * scale_log2 : -INFINITY;
         mxA = fmaxf(mxA, fmaxf(s[n][0], s[n][1]));
         mxB = fmaxf(mxB, fmaxf(s[n][2], s[n][3]));
       }
@@ -201,11 +206,11 @@ extern "C" __global__ void __launch_bounds__(MW * 32 + 32, 1)
       mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
       mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
       mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
-      if ((lane & 3) == 0) { sm_m[warp * HM + rA] = mxA; sm_m[warp * HM + rB] = mxB; }
-      math_bar();                       // every warp's tile maxima are in
+      if (warp < SW && (lane & 3) == 0) { sm_m[warp * HM + rA] = mxA; sm_m[warp * HM + rB] = mxB; }
+      math_bar();                       // every scoring warp's tile maxima are in
       float tA = -INFINITY, tB = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < MW; ++w) { tA = fmaxf(tA, sm_m[w * HM + rA]); tB = fmaxf(tB, sm_m[w * HM + rB]); }
+      for (int w = 0; w < SW; ++w) { tA = fmaxf(tA, sm_m[w * HM + rA]); tB = fmaxf(tB, sm_m[w * HM + rB]); }
       const float mA = fmaxf(m_run[0], tA), mB = fmaxf(m_run[1], tB);
       const float mA_use = mA == -INFINITY ? 0.f : mA, mB_use = mB == -INFINITY ? 0.f : mB;
       const float cA = exp2f(m_run[0] - mA_use), cB = exp2f(m_run[1] - mB_use);
@@ -219,8 +224,10 @@ extern "C" __global__ void __launch_bounds__(MW * 32 + 32, 1)
         sumA += p0 + p1;
         sumB += p2 + p3;
         const int col = wtok + n * 8 + 2 * (lane & 3);
-        *reinterpret_cast<uint32_t*>(ps + rA * kPStride + col) = pack_bf16x2(p0, p1);
-        *reinterpret_cast<uint32_t*>(ps + rB * kPStride + col) = pack_bf16x2(p2, p3);
+        if (warp < SW) {
+          *reinterpret_cast<uint32_t*>(ps + rA * kPStride + col) = pack_bf16x2(p0, p1);
+          *reinterpret_cast<uint32_t*>(ps + rB * kPStride + col) = pack_bf16x2(p2, p3);
+        }
       }
       l_run[0] = l_run[0] * cA + sumA;
       l_run[1] = l_run[1] * cB + sumB;

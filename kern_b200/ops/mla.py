@@ -11,7 +11,7 @@ from .attention import merge_partials
 from .launcher import Kernels, f32, i32, ptr
 
 DQK, DV, HEADS_PER_CTA = 576, 512, 16
-MATH_WARPS, TILE, STAGES = 8, 64, 2
+MATH_WARPS, TILE, STAGES = 8, 48, 3
 SMEM = 1024 + STAGES * TILE * DQK * 2 + 16 * (DQK + 8) * 2 + 16 * (TILE + 8) * 2 + 2 * MATH_WARPS * 16 * 4 + 128
 
 
@@ -23,7 +23,8 @@ def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, 
     seqs = q.shape[0]
     pages, page_size, w = cache.shape
     assert w == DQK and cache.dtype == torch.bfloat16 and q.dtype == torch.bfloat16 and q.shape[1] == heads * DQK
-    assert page_size % TILE == 0 or TILE % page_size == 0
+    BOX = 16 if TILE % 32 else None      # rows of a TMA box: never across a page
+    assert page_size % (BOX or 1) == 0 and (BOX or page_size % TILE == 0 or TILE % page_size == 0)
     if out is None:
         out = torch.empty(seqs, heads * DV, dtype=torch.bfloat16, device=q.device)
     blocks = -(-heads // HEADS_PER_CTA)
@@ -31,7 +32,7 @@ def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, 
         longest = block_table.shape[1] * page_size      # the table's reach: no device read on the launch path
         splits = max(1, min(128, -(-longest // 256), k.sm_count // max(1, seqs * blocks)))      # never more CTAs than SMs
     scale = (192 ** -0.5) if scale is None else scale
-    lat = k.tensor_map_2d(cache.view(pages * page_size, DQK), min(page_size, TILE), 64)
+    lat = k.tensor_map_2d(cache.view(pages * page_size, DQK), BOX or min(page_size, TILE), 64)
     ws_o = ws_ml = None
     if splits > 1:
         ws_o = torch.empty(seqs * heads * splits * DV, dtype=torch.float32, device=q.device)
