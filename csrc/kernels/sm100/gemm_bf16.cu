@@ -264,34 +264,45 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         const bool remote = b < num_m && b / ag_bpr != ag.rank;
         if (!remote) atomicAdd(ag.flags + b, 1u);
       }
-      for (int i = ag_bpr; i < num_m; ++i) {                 // the order the tiles will want them
-        const int b = (i + ag.rank * ag_bpr) % num_m;
-        const int rows = min(BM, M - b * BM);
-        const size_t off = (size_t)b * BM * K * 2, vecs = (size_t)rows * K * 2 / 16;
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(ag.peers[b / ag_bpr]) + off;
-        uint8_t* dst = mine + off;
-        // eight loads in flight per thread before the first store: a peer load takes a couple of microseconds, and
-        // one at a time they would add up to the whole transfer
-        const size_t stride = (size_t)gridDim.x * 64;
-        for (size_t v0 = (size_t)blockIdx.x * 64 + gt; v0 < vecs; v0 += stride * 8) {
-          uint4 x[8];
+      // The peers' blocks in the order the tiles will want them, cut into units of eight 16-byte vectors per thread.
+      // The loads of unit u + 1 are issued before the stores of unit u: a peer load takes a couple of microseconds,
+      // and one at a time (or one block at a time) the round trips would add up to the whole transfer.
+      const size_t vecs = (size_t)BM * K * 2 / 16, stride = (size_t)gridDim.x * 64, span = stride * 8;
+      const int nb = (int)((vecs + span - 1) / span);                    // units per block
+      const int units = (num_m - ag_bpr) * nb;
+      auto block_of = [&](int u) { return (ag_bpr + u / nb + ag.rank * ag_bpr) % num_m; };
+      auto load = [&](int u, uint4 (&x)[8]) {
+        const int b = block_of(u);
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(ag.peers[b / ag_bpr]) + (size_t)b * BM * K * 2;
+        const size_t v0 = (size_t)(u % nb) * span + (size_t)blockIdx.x * 64 + gt;
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const size_t v = v0 + u * stride;
-            if (v < vecs)
-              asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                           : "=r"(x[u].x), "=r"(x[u].y), "=r"(x[u].z), "=r"(x[u].w) : "l"(src + v * 16));
-          }
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const size_t v = v0 + u * stride;
-            if (v < vecs) *reinterpret_cast<uint4*>(dst + v * 16) = x[u];
-          }
+        for (int q = 0; q < 8; ++q) {
+          const size_t v = v0 + q * stride;
+          if (v < vecs)
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(x[q].x), "=r"(x[q].y), "=r"(x[q].z), "=r"(x[q].w) : "l"(src + v * 16));
         }
-        __threadfence();
-        asm volatile("fence.proxy.async;" ::: "memory");
-        asm volatile("bar.sync 1, 64;" ::: "memory");          // both gather warps are done with this block
-        if (gt == 0) atomicAdd(ag.flags + b, 1u);
+      };
+      uint4 xa[8], xb[8];
+      if (units > 0) load(0, xa);
+      for (int u = 0; u < units; ++u) {
+        if (u + 1 < units) load(u + 1, xb);
+        const int b = block_of(u);
+        uint8_t* dst = mine + (size_t)b * BM * K * 2;
+        const size_t v0 = (size_t)(u % nb) * span + (size_t)blockIdx.x * 64 + gt;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const size_t v = v0 + q * stride;
+          if (v < vecs) *reinterpret_cast<uint4*>(dst + v * 16) = xa[q];
+        }
+        if (u % nb == nb - 1) {                                          // this CTA's share of block b is in place
+          __threadfence();
+          asm volatile("fence.proxy.async;" ::: "memory");
+          asm volatile("bar.sync 1, 64;" ::: "memory");                  // both gather warps are done with it
+          if (gt == 0) atomicAdd(ag.flags + b, 1u);
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) xa[q] = xb[q];
       }
       if (gt == 0) ag.epochs[blockIdx.x] = ag_want / gridDim.x;
     }
