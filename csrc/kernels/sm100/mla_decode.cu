@@ -10,10 +10,10 @@
 // S = Q K^T each warp takes 8 of the tile's tokens; the probabilities go through shared memory (all warps use the tile's
 // common row maximum), and for O += P V each warp owns 512 / MW of the value columns — a warp's accumulator is
 // 16 x 64, not 16 x 512. One more warp feeds the ring of tiles by TMA (nine 64-column boxes per tile, 128-byte
-// swizzle). Tiles of 48 tokens (54 KB) in a three-stage ring: six of the eight warps score (8 tokens each), all
-// eight own 64 value columns. 64-token tiles fit only two stages beside the 18 KB of queries (one tile in flight while
-// the other is consumed: 0.56 of the copy bandwidth); 32-token tiles four deep measured slower than that (twice the
-// barriers per token).
+// swizzle). Tiles of 64 tokens (72 KB) in a two-stage ring, all eight warps score. Measured alternatives, both slower
+// than this (0.167 ms for 64 sequences of 8192 rows): 48-token tiles three deep with six scoring warps (0.196 ms) and
+// 32-token tiles four deep with four warps (0.203 ms) — more barriers and row-maximum exchanges per token cost more
+// than the deeper ring gains.
 // With 16 heads per rank (tensor parallel 8) a tile is read once per sequence; with more heads the CTAs of a sequence
 // share the tile through L2. One row per sequence (decode); verify rows of a speculative round are not handled here.
 // Reference: the reference takes this kernel from a CuTe-DSL build (MLA decode, sm100) and the context form from a
@@ -25,7 +25,7 @@ using namespace kern;
 namespace {
 
 constexpr int MW = 8;                    // math warps: 512 / MW value columns each for O
-constexpr int TKM = 48;                  // tokens per tile
+constexpr int TKM = 64;                  // tokens per tile
 constexpr int SW = TKM / 8;              // warps that take part in S = Q K^T, 8 tokens of the tile each
 constexpr int DQK = 576, DVV = 512;
 constexpr int HM = 16;                   // heads per CTA

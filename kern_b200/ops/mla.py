@@ -11,7 +11,7 @@ from .attention import merge_partials
 from .launcher import Kernels, f32, i32, ptr
 
 DQK, DV, HEADS_PER_CTA = 576, 512, 16
-MATH_WARPS, TILE, STAGES = 8, 48, 3
+MATH_WARPS, TILE, STAGES = 8, 64, 2
 SMEM = 1024 + STAGES * TILE * DQK * 2 + 16 * (DQK + 8) * 2 + 16 * (TILE + 8) * 2 + 2 * MATH_WARPS * 16 * 4 + 128
 
 
