@@ -94,6 +94,61 @@ extern "C" __global__ void __launch_bounds__(256)
   }
 }
 
+// One row per sequence (decode): the conv of the row and the shift of its window in ONE launch — a thread owns four
+// channels of one sequence, so it reads its own window, writes y, and then writes the shifted window; nobody else
+// touches those bytes. grid [seqs, ceil(conv_dim / 1024)], block 256. Row s belongs to sequence s.
+extern "C" __global__ void __launch_bounds__(256)
+    kern_gdn_conv_step_bf16(const __nv_bfloat16* x, __nv_bfloat16* y, uint8_t* state, const int* lines, const __nv_bfloat16* w,
+                            const __nv_bfloat16* bias, int seqs, int conv_dim, int width, int x_stride, long long line_bytes) {
+  pdl_wait();
+  const int s = blockIdx.x;
+  const int c = (blockIdx.y * 256 + threadIdx.x) * 4;
+  if (s >= seqs || c >= conv_dim) return;
+  auto load4 = [](const __nv_bfloat16* p, float (&o)[4]) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+    o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+  };
+  const int line = lines[s], keep = width - 1;
+  __nv_bfloat16* win = reinterpret_cast<__nv_bfloat16*>(state + (size_t)line * line_bytes);
+  float hist[3][4];        // right-aligned: hist[2] is the previous row
+  uint2 raw[3];
+#pragma unroll
+  for (int d = 0; d < 3; ++d) {
+    raw[d] = make_uint2(0u, 0u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) hist[d][i] = 0.f;
+  }
+#pragma unroll
+  for (int d = 0; d < 3; ++d) {
+    if (d < 3 - keep || line <= 0) continue;                    // window row d - (3 - keep)
+    raw[d] = *reinterpret_cast<const uint2*>(win + (size_t)(d - (3 - keep)) * conv_dim + c);
+    const float2 a = unpack_bf16x2(raw[d].x), b = unpack_bf16x2(raw[d].y);
+    hist[d][0] = a.x; hist[d][1] = a.y; hist[d][2] = b.x; hist[d][3] = b.y;
+  }
+  float cur[4], bs[4] = {0.f, 0.f, 0.f, 0.f}, o[4];
+  const uint2 xr = *reinterpret_cast<const uint2*>(x + (size_t)s * x_stride + c);
+  load4(x + (size_t)s * x_stride + c, cur);
+  if (bias) load4(bias + c, bs);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float wt[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) wt[j] = j >= 4 - width ? __bfloat162float(w[(size_t)(c + i) * width + j - (4 - width)]) : 0.f;
+    o[i] = silu(bs[i] + wt[3] * cur[i] + wt[2] * hist[2][i] + wt[1] * hist[1][i] + wt[0] * hist[0][i]);
+  }
+  *reinterpret_cast<uint2*>(y + (size_t)s * conv_dim + c) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+  if (line > 0) {
+    // new window = old rows 1 .. keep-1, then this row
+#pragma unroll
+    for (int d = 0; d < 3; ++d) {
+      if (d < 3 - keep) continue;
+      const int j = d - (3 - keep);                                // window row j takes old row j + 1, the last one x
+      *reinterpret_cast<uint2*>(win + (size_t)j * conv_dim + c) = d == 2 ? xr : raw[d + 1];
+    }
+  }
+}
+
 // window' = the last width-1 inputs of (window ++ this call's rows). grid [seqs, ceil(conv_dim / 256)], block 256.
 extern "C" __global__ void __launch_bounds__(256)
     kern_gdn_conv_state(const __nv_bfloat16* x, uint8_t* state, const int* lines, const int* cu_q, int seqs, int conv_dim,

@@ -270,6 +270,12 @@ def k_gdn_conv_state(g, x, state, lines, cu, seqs, conv_dim, width, x_stride, li
         win.copy_(full[full.shape[0] - (width - 1):])
 
 
+def k_gdn_conv_step(g, x, y, state, lines, w, bias, seqs, conv_dim, width, x_stride, line_bytes):
+    n = g[0]
+    k_gdn_conv((n, 1, 1), x, y, state, lines, 0, w, bias, n, n, conv_dim, width, x_stride, line_bytes, 1)
+    k_gdn_conv_state((n, 1, 1), x, state, lines, 0, n, conv_dim, width, x_stride, line_bytes)
+
+
 def _gdn_rule(dim):
     def run(g, qkv, zba, o_raw, state, lines, cu, A_log, dt_bias, seqs, hk, hv, zba_stride, b_off, a_off, line_bytes, s_off, tb):
         from .ops import gdn as G
@@ -382,6 +388,7 @@ CPU_KERNELS = {
     "kern_gdn_conv_bf16": k_gdn_conv, "kern_gdn_conv_state": k_gdn_conv_state, "kern_gdn_rule_k128_v128": _gdn_rule(128), "kern_gdn_rule_k64_v64": _gdn_rule(64),
     "kern_gdn_rule_k32_v32": _gdn_rule(32), "kern_gdn_gate_norm_bf16": k_gdn_gate_norm,
     "kern_gdn_step_k128_v128": _gdn_step(128), "kern_gdn_step_k64_v64": _gdn_step(64), "kern_gdn_step_k32_v32": _gdn_step(32),
+    "kern_gdn_conv_step_bf16": k_gdn_conv_step,
     "kern_gdn_chunk_prep_k128_v128": k_gdn_chunk_prep, "kern_gdn_chunk_rule_k128_v128": k_gdn_chunk_rule,
     "kern_gdn_rule_dec_k128_v128": _gdn_rule(128), "kern_gdn_rule_dec_k64_v64": _gdn_rule(64), "kern_gdn_rule_dec_k32_v32": _gdn_rule(32),
     "kern_fill_f32": k_fill, "kern_fill_i32": k_fill, "kern_fill_i64": k_fill, "kern_fill_u8": k_fill,

@@ -680,6 +680,13 @@ def gdn_conv_op(conv_dim: int, width: int, x_stride: int, line_bytes: int, ragge
         iface.append("in buffer<i32>")
     iface += ["in buffer<bf16>", "i32", "i32"]
     w_at = len(iface) - 3
+    if not ragged:      # one row per sequence: the conv and the window shift in one launch
+        step = {"module": "gdn", "entry": "kern_gdn_conv_step_bf16", "block": [256, 1, 1], "grid": ["seqs", -(-conv_dim // 1024), 1],
+                "params": ["in buffer<bf16>", "out buffer<bf16>", "inout state", "in buffer<i32>", "in buffer<bf16>", "i64", "i32",
+                           "i32", "i32", "i32", "i64"],
+                "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"param": 3}, {"param": w_at}, {"i64": 0}, {"param": w_at + 1},
+                         {"i32": conv_dim}, {"i32": width}, {"i32": x_stride}, {"i64": line_bytes}]}
+        return {"params": iface, "impl": {"launches": [step]}}
     cu_t, cu_a = ("in buffer<i32>", {"param": 4}) if ragged else ("i64", {"i64": 0})
     conv = {"module": "gdn", "entry": "kern_gdn_conv_bf16", "block": [256, 1, 1],
             "grid": [{"ceil_div": ["tokens", 16]} if ragged else "tokens", -(-conv_dim // 1024), 1],

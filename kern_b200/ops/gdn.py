@@ -35,7 +35,12 @@ def conv(x, y, state, lines, cu_q, w, bias, seqs, conv_dim, width, line_b, rows=
     k = Kernels.get(x.device)
     rows = x.shape[0] if rows is None else rows
     assert conv_dim % 4 == 0 and x.stride(0) % 4 == 0, "the conv kernel moves four channels (8 bytes) per thread"
-    rpc = 16 if cu_q is not None else 1
+    if cu_q is None:      # one row per sequence: conv and window shift in one launch
+        k.launch("gdn", "kern_gdn_conv_step_bf16", (seqs, (conv_dim + 1023) // 1024), (256,),
+                 [ptr(x), ptr(y), ptr(state), ptr(lines), ptr(w), ptr(bias), i32(seqs), i32(conv_dim), i32(width),
+                  i32(x.stride(0)), i64(line_b)])
+        return y
+    rpc = 16
     k.launch("gdn", "kern_gdn_conv_bf16", ((rows + rpc - 1) // rpc, (conv_dim + 1023) // 1024), (256,),
              [ptr(x), ptr(y), ptr(state), ptr(lines), ptr(cu_q), ptr(w), ptr(bias), i32(seqs), i32(rows), i32(conv_dim),
               i32(width), i32(x.stride(0)), i64(line_b), i32(rpc)])
