@@ -50,9 +50,12 @@ def main(argv=None) -> int:
 
     warm = Request(id="w", prompt=rng.integers(1, vocab, min(a.tokens, 3 * a.chunk)).tolist(), max_tokens=2)
     ttft(warm)                                   # graphs, tensor maps, allocator
-    cold = Request(id="a", prompt=prompt, max_tokens=2)
+    # a turn boundary one page before the end: where a model with per-sequence state snapshots it
+    page = rt.page_unit
+    hist = max(page, (a.tokens - 2) // page * page)
+    cold = Request(id="a", prompt=prompt, max_tokens=2, history_tokens=hist)
     t_cold = ttft(cold)
-    again = Request(id="b", prompt=prompt, max_tokens=2)
+    again = Request(id="b", prompt=prompt, max_tokens=2, history_tokens=hist)
     t_hit = ttft(again)
     print(json.dumps({"model": a.model, "prompt_tokens": a.tokens, "chunk": a.chunk, "ttft_cold_ms": round(t_cold * 1e3, 1),
                       "ttft_repeat_ms": round(t_hit * 1e3, 1), "cached_tokens": again.cached,
