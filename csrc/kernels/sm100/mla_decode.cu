@@ -61,7 +61,8 @@ constexpr int MLA_SMEM = 1024 + kStagesM * kTileBytes + kQBytes + kPBytes + 2 * 
 extern "C" __global__ void __launch_bounds__(MW * 32 + 32, 1)
     kern_mla_decode_bf16(const __grid_constant__ CUtensorMap lat_map, const __nv_bfloat16* q, __nv_bfloat16* out, float* ws_o,
                          float* ws_ml, const int* block_table, const int* seq_lens, int seqs, int heads, int q_stride,
-                         int out_stride, int max_pages, int page_size, int splits, int pool_pages, float scale_log2, int* err) {
+                         int out_stride, int max_pages, int page_size, int splits, int pool_pages, float scale_log2, int* err,
+                         const int* row_seq) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stages = smem;
@@ -88,6 +89,7 @@ extern "C" __global__ void __launch_bounds__(MW * 32 + 32, 1)
   pdl_wait();
   if (seq >= seqs) return;
   const int L = seq_lens[seq];
+  const int trow = row_seq != nullptr ? row_seq[seq] : seq;      // the block-table row: prefill rows share their sequence's
   const int valid_rows = min(HM, heads - head0);
   const int nsplit = splits & 0xff, split_base = (splits >> 8) & 0xff;
   const int split_total = (splits >> 16) ? (splits >> 16) : nsplit;
@@ -133,7 +135,7 @@ extern "C" __global__ void __launch_bounds__(MW * 32 + 32, 1)
           int page = 0, in_page = 0;
           const int pidx = tok / page_size;
           if (tok < L && pidx < max_pages) {
-            page = block_table[(size_t)seq * max_pages + pidx];
+            page = block_table[(size_t)trow * max_pages + pidx];
             in_page = tok % page_size;
           }
           if (page < 0 || page >= pool_pages) {
@@ -293,4 +295,68 @@ extern "C" __global__ void __launch_bounds__(MW * 32 + 32, 1)
     }
   }
   pdl_launch_dependents();
+}
+
+// ---- the steps around the attention of a latent-attention layer ----------------------------------------------------
+// kern_mla_rope_append_bf16: grid = tokens, block 128. Per token: RMS-norm of the 512 compressed columns (weight w),
+// rotation of the 64 positional key columns, both written as one 576-wide row of the paged latent cache at `slots[t]`;
+// and the rotation, in place, of the last 64 columns of every head's 576-wide query. The rotation pairs column i with
+// i + 32 (half-split), angles from the [max_pos, 32] tables.
+extern "C" __global__ void __launch_bounds__(128)
+    kern_mla_rope_append_bf16(const __nv_bfloat16* lat, __nv_bfloat16* q, __nv_bfloat16* cache, const long long* positions,
+                              const long long* slots, const float* cos_tab, const float* sin_tab, const __nv_bfloat16* w,
+                              int tokens, int heads, int lat_stride, int q_stride, float eps, long long kv_slots, int max_pos,
+                              int* err) {
+  __shared__ float red[4];
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (t >= tokens) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  long long pos = positions[t], slot = slots[t];
+  if (pos < 0 || pos >= max_pos) { set_error(err, ERR_BOUNDS); pos = 0; }
+  if (slot >= kv_slots) { set_error(err, ERR_BOUNDS); slot = -1; }
+  const float* cs = cos_tab + (size_t)pos * 32;
+  const float* sn = sin_tab + (size_t)pos * 32;
+  const __nv_bfloat16* src = lat + (size_t)t * lat_stride;
+  // the compressed part: four columns per thread
+  float v[4], ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[j] = __bfloat162float(src[threadIdx.x * 4 + j]);
+    ss += v[j] * v[j];
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  const float inv = rsqrtf((red[0] + red[1] + red[2] + red[3]) / 512.f + eps);
+  if (slot >= 0) {
+    __nv_bfloat16* dst = cache + (size_t)slot * DQK;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      dst[threadIdx.x * 4 + j] = __float2bfloat16(v[j] * inv * __bfloat162float(w[threadIdx.x * 4 + j]));
+    if (threadIdx.x < 32) {
+      const float a = __bfloat162float(src[512 + threadIdx.x]), b = __bfloat162float(src[544 + threadIdx.x]);
+      dst[512 + threadIdx.x] = __float2bfloat16(a * cs[threadIdx.x] - b * sn[threadIdx.x]);
+      dst[544 + threadIdx.x] = __float2bfloat16(b * cs[threadIdx.x] + a * sn[threadIdx.x]);
+    }
+  }
+  for (int h = warp; h < heads; h += 4) {
+    __nv_bfloat16* qp = q + (size_t)t * q_stride + (size_t)h * DQK + 512;
+    const float a = __bfloat162float(qp[lane]), b = __bfloat162float(qp[32 + lane]);
+    qp[lane] = __float2bfloat16(a * cs[lane] - b * sn[lane]);
+    qp[32 + lane] = __float2bfloat16(b * cs[lane] + a * sn[lane]);
+  }
+}
+
+// kern_mla_rows: grid = ceil(tokens / 128), block 128. Turns a ragged call into one attention row per token:
+// row_seq[t] = the sequence of row t, row_len[t] = positions[t] + 1 (the causal reach of the row).
+extern "C" __global__ void __launch_bounds__(128)
+    kern_mla_rows(const long long* positions, const int* cu_q, int seqs, int tokens, int* row_seq, int* row_len) {
+  pdl_wait();
+  const int t = blockIdx.x * 128 + threadIdx.x;
+  if (t >= tokens) return;
+  int s = 0;
+  while (s + 1 < seqs && t >= cu_q[s + 1]) ++s;
+  row_seq[t] = s;
+  row_len[t] = t < cu_q[seqs] ? (int)positions[t] + 1 : 0;
 }

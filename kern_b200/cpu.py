@@ -814,3 +814,108 @@ def _k_deal_rows(g, src, dst, src_table, dst_table, src_lens, seqs, src_width, d
 
 CPU_KERNELS.update({"kern_dcp_local_lens": _k_dcp_local_lens, "kern_dcp_prepare": _k_dcp_prepare,
                     "kern_attn_merge_ranks": _k_attn_merge_ranks, "kern_deal_rows_bf16": _k_deal_rows})
+
+
+# ---- per-key-decay delta rule and latent attention (statements: ops/gdn.py kda_rule_ref, ops/mla.py) ---------------
+def _kda_rule(dim):
+    def run(g, qkv, zba, o_raw, state, lines, cu, A_log, dt_bias, gk, seqs, hk, hv, zba_stride, b_off, gk_stride, line_bytes,
+            s_off, tb):
+        from .ops import gdn as G
+
+        conv_dim = 2 * hk * dim + hv * dim
+        for s in range(g[1]):
+            r0, r1 = _rows_of(cu, s)
+            n = r1 - r0
+            if n <= 0:
+                continue
+            ln = int(lines[s])
+            Sb = state[ln * line_bytes + s_off: ln * line_bytes + s_off + hv * dim * dim * 4].view(torch.float32).view(hv, dim, dim)
+            S0 = Sb.clone() if ln > 0 else torch.zeros(hv, dim, dim)
+            rows = _f(qkv[r0 * conv_dim: r1 * conv_dim].view(n, conv_dim))
+            b = _f(torch.as_strided(zba, (n, hv), (zba_stride, 1), zba.storage_offset() + r0 * zba_stride + b_off))
+            gate = _f(torch.as_strided(gk, (n, hv * dim), (gk_stride, 1), gk.storage_offset() + r0 * gk_stride)).view(n, hv, dim)
+            q = rows[:, :hk * dim].view(n, hk, dim)
+            k = rows[:, hk * dim:2 * hk * dim].view(n, hk, dim)
+            v = rows[:, 2 * hk * dim:].view(n, hv, dim)
+            hvd = hv * dim
+            T, rep = n, hv // hk
+            qn = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6) / dim ** 0.5
+            kn = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+            qn, kn = qn.repeat_interleave(rep, 1), kn.repeat_interleave(rep, 1)
+            dec = torch.exp(-torch.exp(A_log[:hv].float())[None, :, None] *
+                            torch.nn.functional.softplus(gate + dt_bias[:hvd].float().view(1, hv, dim)))
+            beta = _f(torch.sigmoid(b).to(torch.bfloat16))
+            S = S0.float().clone()
+            o = torch.empty(T, hv, dim)
+            for t in range(T):
+                S = S * dec[t][:, None, :]
+                u = (v[t] - torch.einsum("hvk,hk->hv", S, kn[t])) * beta[t][:, None]
+                S = S + u[:, :, None] * kn[t][:, None, :]
+                o[t] = torch.einsum("hvk,hk->hv", S, qn[t])
+            o_raw[r0 * hvd: r1 * hvd] = o.reshape(-1)
+            if ln > 0:
+                Sb.copy_(S)
+    return run
+
+
+def _kda_step(dim):
+    rule = _kda_rule(dim)
+
+    def run(g, qkv, zba, out, state, lines, A_log, dt_bias, norm_w, gk, seqs, hk, hv, zba_stride, z_off, b_off, gk_stride,
+            line_bytes, s_off, eps):
+        n = g[1]
+        o_raw = torch.zeros(n * hv * dim, dtype=torch.float32)
+        rule((hv, n, 1), qkv, zba, o_raw, state, lines, 0, A_log, dt_bias, gk, seqs, hk, hv, zba_stride, b_off, gk_stride,
+             line_bytes, s_off, 1)
+        k_gdn_gate_norm(((hv + 3) // 4, n, 1), o_raw, zba, out, norm_w, n, hv, dim, zba_stride, z_off, eps)
+    return run
+
+
+def _k_mla_rope_append(g, lat, q, cache, positions, slots, cos, sin, w, tokens, heads, lat_stride, q_stride, eps, kv_slots,
+                       max_pos, err):
+    t = g[0]
+    pos = positions[:t].long().clamp(0, max_pos - 1)
+    c, s = cos.view(-1, 32)[pos], sin.view(-1, 32)[pos]
+    rows = _f(torch.as_strided(lat, (t, 576), (lat_stride, 1), lat.storage_offset()))
+    comp = rows[:, :512]
+    comp = comp * torch.rsqrt(comp.pow(2).mean(-1, keepdim=True) + eps) * _f(w[:512])
+    a, b = rows[:, 512:544], rows[:, 544:]
+    new = torch.cat([comp, a * c - b * s, b * c + a * s], -1).to(torch.bfloat16)
+    sl = slots[:t].long()
+    ok = sl >= 0
+    cache.view(torch.bfloat16).view(-1, 576)[sl[ok]] = new[ok]
+    qv = torch.as_strided(q, (t, heads, 576), (q_stride, 576, 1), q.storage_offset())
+    qa, qb = _f(qv[..., 512:544]), _f(qv[..., 544:])
+    qv[..., 512:544] = (qa * c[:, None] - qb * s[:, None]).to(torch.bfloat16)
+    qv[..., 544:] = (qb * c[:, None] + qa * s[:, None]).to(torch.bfloat16)
+
+
+def _k_mla_rows(g, positions, cu, seqs, tokens, row_seq, row_len):
+    row_seq[:tokens] = 0
+    row_len[:tokens] = 0
+    for s in range(seqs):
+        r0, r1 = int(cu[s]), int(cu[s + 1])
+        row_seq[r0:r1] = s
+        row_len[r0:r1] = (positions[r0:r1] + 1).to(torch.int32)
+
+
+def _k_mla_decode(g, kv, q, out, ws_o, ws_ml, table, lens, seqs, heads, q_stride, out_stride, max_pages, page, splits,
+                  pool_pages, scale_log2, err, row_seq):
+    pool = kv.view(torch.bfloat16).view(-1, page, 576)
+    tb = table.view(-1, max_pages)
+    scale = scale_log2 / 1.4426950408889634
+    for r in range(g[1]):
+        L = int(lens[r])
+        if L <= 0:
+            continue
+        trow = int(row_seq[r]) if isinstance(row_seq, torch.Tensor) else r
+        lat = _f(pool[tb[trow, : -(-L // page)].long()]).reshape(-1, 576)[:L]
+        qq = _f(torch.as_strided(q, (heads, 576), (576, 1), q.storage_offset() + r * q_stride))
+        p = torch.softmax((qq @ lat.t()) * scale, -1)
+        torch.as_strided(out, (heads * 512,), (1,), out.storage_offset() + r * out_stride).copy_((p @ lat[:, :512]).reshape(-1).to(out.dtype))
+
+
+CPU_KERNELS.update({"kern_kda_rule_k128_v128": _kda_rule(128), "kern_kda_rule_k64_v64": _kda_rule(64),
+                    "kern_kda_step_k128_v128": _kda_step(128), "kern_kda_step_k64_v64": _kda_step(64),
+                    "kern_mla_rope_append_bf16": _k_mla_rope_append, "kern_mla_rows": _k_mla_rows,
+                    "kern_mla_decode_bf16": _k_mla_decode})

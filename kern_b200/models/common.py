@@ -265,14 +265,14 @@ def ag_gemm_op(n: int, k: int, nranks: int, group: str = "tp", bn: int = 256, ti
     return {"params": iface, "impl": {"launches": [barrier, gemm] + ([dict(barrier)] if closing_barrier else [])}}
 
 
-def rms_norm_op(n: int, eps: float, plus_one: bool = False, rows_var: str = "tokens") -> dict:
-    """Interface [x, w, y]; one row per CTA."""
+def rms_norm_op(n: int, eps: float, plus_one: bool = False, rows_var: str = "tokens", x_stride: int | None = None) -> dict:
+    """Interface [x, w, y]; one row per CTA. `x_stride`: elements between rows of x when they are columns of wider rows."""
     entry = "kern_rms_norm_bf16" if n <= 8192 else "kern_rms_norm_wide_bf16"
     return {"params": ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>"],
             "impl": {"launches": [{
                 "module": "norm_embed", "entry": entry, "block": [256, 1, 1], "grid": [rows_var, 1, 1],
                 "params": ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "i32", "i32", "i32", "i32", "f32", "i32"],
-                "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"i32": I32_MAX}, {"i32": n}, {"i32": n}, {"i32": n},
+                "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"i32": I32_MAX}, {"i32": n}, {"i32": x_stride or n}, {"i32": n},
                          {"f32": eps}, {"i32": int(plus_one)}]}]}}
 
 
@@ -775,3 +775,86 @@ def sigmoid_mul_op(d: int, x_stride: int, gate_stride: int) -> dict:
         "params": ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "i32", "i32", "i32", "i32"],
         "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"i32": I32_MAX}, {"i32": d}, {"i32": x_stride},
                  {"i32": gate_stride}]}]}}
+
+
+# ---- per-key-decay delta rule (Kimi Delta Attention) and latent attention ---------------------------------------
+def kda_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_off: int, eps: float, ragged: bool) -> dict:
+    """Delta rule with a decay per key channel + gated RMSNorm. `zba` points at the z|b columns of the projection's
+    row and `gk` at its hv * dim gate columns (same row stride).
+    Interface [qkv, zba, gk, out, state, lines, A_log, dt_bias, norm_w] for one row per sequence (the fused step), or
+    [qkv, zba, gk, out, state, lines, cu_seqlens, A_log, dt_bias, norm_w, seqs] for ragged rows (token by token)."""
+    assert dim in (64, 128)
+    iface = ["in buffer<bf16>", "in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "inout state", "in buffer<i32>"]
+    if not ragged:
+        iface += ["in buffer<f32>", "in buffer<f32>", "in buffer<bf16>"]
+        step = {"module": "gdn", "entry": f"kern_kda_step_k{dim}_v{dim}", "block": [256, 1, 1], "grid": [hv, "seqs", 1],
+                "shared_mem": dim * dim * 4 + (4 * dim + 16) * 4 + 16 + dim * 4,
+                "params": ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "inout state", "in buffer<i32>",
+                           "in buffer<f32>", "in buffer<f32>", "in buffer<bf16>", "in buffer<bf16>"] + ["i32"] * 7 +
+                          ["i64", "i64", "f32"],
+                "args": [{"param": 0}, {"param": 1}, {"param": 3}, {"param": 4}, {"param": 5}, {"param": 6}, {"param": 7},
+                         {"param": 8}, {"param": 2}, {"i32": I32_MAX}, {"i32": hk}, {"i32": hv}, {"i32": zba_stride}, {"i32": 0},
+                         {"i32": hv * dim}, {"i32": zba_stride}, {"i64": line_bytes}, {"i64": s_off}, {"f32": eps}]}
+        return {"params": iface, "impl": {"launches": [step]}}
+    iface += ["in buffer<i32>", "in buffer<f32>", "in buffer<f32>", "in buffer<bf16>", "i32"]
+    tb = 32
+    rule = {"module": "gdn", "entry": f"kern_kda_rule_k{dim}_v{dim}", "block": [256, 1, 1], "grid": [hv * (dim // 16), "seqs", 1],
+            "shared_mem": tb * (3 * dim + 16 + 4) * 4,
+            "params": ["in buffer<bf16>", "in buffer<bf16>", "out buffer<f32>", "inout state", "in buffer<i32>", "in buffer<i32>",
+                       "in buffer<f32>", "in buffer<f32>", "in buffer<bf16>"] + ["i32"] * 6 + ["i64", "i64", "i32"],
+            "args": [{"param": 0}, {"param": 1}, {"scratch": "o_raw"}, {"param": 4}, {"param": 5}, {"param": 6}, {"param": 7},
+                     {"param": 8}, {"param": 2}, {"param": 10}, {"i32": hk}, {"i32": hv}, {"i32": zba_stride}, {"i32": hv * dim},
+                     {"i32": zba_stride}, {"i64": line_bytes}, {"i64": s_off}, {"i32": tb}]}
+    norm = {"module": "gdn", "entry": "kern_gdn_gate_norm_bf16", "block": [128, 1, 1], "grid": [-(-hv // 4), "tokens", 1],
+            "params": ["in buffer<f32>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<bf16>", "i32", "i32", "i32", "i32",
+                       "i32", "f32"],
+            "args": [{"scratch": "o_raw"}, {"param": 1}, {"param": 3}, {"param": 9}, {"i32": I32_MAX}, {"i32": hv},
+                     {"i32": dim}, {"i32": zba_stride}, {"i32": 0}, {"f32": eps}]}
+    return {"params": iface, "impl": {"launches": [rule, norm],
+                                      "scratch": {"o_raw": {"dtype": "f32", "shape": ["tokens", hv * dim]}}}}
+
+
+MLA_DQK, MLA_DV = 576, 512
+MLA_SMEM = 1024 + 2 * 64 * MLA_DQK * 2 + 16 * (MLA_DQK + 8) * 2 + 16 * (64 + 8) * 2 + 2 * 8 * 16 * 4 + 128
+
+
+def mla_rope_append_op(heads: int, lat_stride: int, eps: float, max_pos: int) -> dict:
+    """Latent row of a token (RMS-normed 512 compressed columns + rotated 64 positional ones) into the paged latent
+    cache, and the rotation of the positional 64 columns of every head's query, in place.
+    Interface [latent columns of the projection's row, q, latent state, positions, slots, cos, sin, norm weight, err]."""
+    iface = ["in buffer<bf16>", "inout buffer<bf16>", "inout state", "in buffer<i64>", "in buffer<i64>", "in buffer<f32>",
+             "in buffer<f32>", "in buffer<bf16>", "out buffer<i32>"]
+    return {"params": iface, "impl": {"launches": [{
+        "module": "mla_decode", "entry": "kern_mla_rope_append_bf16", "block": [128, 1, 1], "grid": ["tokens", 1, 1],
+        "params": iface[:8] + ["i32", "i32", "i32", "i32", "f32", "i64", "i32", "out buffer<i32>"],
+        "args": [{"param": i} for i in range(8)] + [{"i32": I32_MAX}, {"i32": heads}, {"i32": lat_stride},
+                                                     {"i32": heads * MLA_DQK}, {"f32": eps}, {"i64": I64_MAX}, {"i32": max_pos},
+                                                     {"param": 8}]}]}}
+
+
+def mla_rows_op() -> dict:
+    """One attention row per token of a ragged call. Interface [positions, cu_seqlens, row_seq, row_len, seqs, tokens]."""
+    iface = ["in buffer<i64>", "in buffer<i32>", "out buffer<i32>", "out buffer<i32>", "i32", "i32"]
+    return {"params": iface, "impl": {"launches": [{
+        "module": "mla_decode", "entry": "kern_mla_rows", "block": [128, 1, 1], "grid": [{"ceil_div": ["tokens", 128]}, 1, 1],
+        "params": ["in buffer<i64>", "in buffer<i32>", "i32", "i32", "out buffer<i32>", "out buffer<i32>"],
+        "args": [{"param": 0}, {"param": 1}, {"param": 4}, {"param": 5}, {"param": 2}, {"param": 3}]}]}}
+
+
+def mla_attn_op(heads: int, page_size: int, table_width: int, ragged: bool, head_width: int = 192) -> dict:
+    """Absorbed latent attention: every head attends over the shared 576-wide latent rows, values their first 512
+    columns. One row per sequence: interface [q, latent state, out, block_table, seq_lens, err]; ragged rows bring
+    [.., row_len, err, row_seq] — a row reads its sequence's table row and attends over its own causal reach."""
+    assert page_size % 64 == 0 or 64 % page_size == 0
+    iface = ["in buffer<bf16>", "in state", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "out buffer<i32>"]
+    if ragged:
+        iface.append("in buffer<i32>")
+    lp = ["bytes<128>", "in buffer<bf16>", "out buffer<bf16>", "i64", "i64", "in buffer<i32>", "in buffer<i32>"] + ["i32"] * 8 + \
+         ["f32", "out buffer<i32>", "in buffer<i32>" if ragged else "i64"]
+    args = [_kv_map(MLA_DQK, page_size, 1), {"param": 0}, {"param": 2}, {"i64": 0}, {"i64": 0}, {"param": 3}, {"param": 4},
+            {"i32": I32_MAX}, {"i32": heads}, {"i32": heads * MLA_DQK}, {"i32": heads * MLA_DV}, {"i32": table_width},
+            {"i32": page_size}, {"i32": 1}, {"i32": I32_MAX}, {"f32": (head_width ** -0.5) * 1.4426950408889634}, {"param": 5},
+            {"param": 6} if ragged else {"i64": 0}]
+    return {"params": iface, "impl": {"launches": [{
+        "module": "mla_decode", "entry": "kern_mla_decode_bf16", "block": [288, 1, 1],
+        "grid": [-(-heads // 16), "tokens" if ragged else "seqs", 1], "shared_mem": MLA_SMEM, "params": lp, "args": args}]}}

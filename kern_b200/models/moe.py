@@ -139,6 +139,13 @@ def build_manifest(cfg: MoeConfig) -> dict:
     """The dense decoder's manifest with every layer's MLP replaced by the routed experts."""
     doc = dense.build_manifest(cfg)
     doc["model"] = cfg.name
+    return moeify(doc, cfg, ["norm_embed", "gemm_bf16", "attn_prep", "attn_paged", "misc", "sampling", "moe"])
+
+
+def moeify(doc: dict, cfg, modules: list[str]) -> dict:
+    """Replace the dense MLP of every layer of `doc` by routed experts. The document follows the decoder builders'
+    naming: calls labelled `l<i>.gate_up` / `l<i>.down`, weights `w.l<i>.gu` / `w.l<i>.down`, rows `xn` -> `x`.
+    `cfg` brings hidden, layers, max_tokens, experts, top_k, moe_intermediate, scoring and routed_scale."""
     bufs, ops = doc["buffers"], doc["ops"]
     h, I, E, k, T = cfg.hidden, cfg.moe_intermediate, cfg.experts, cfg.top_k, cfg.max_tokens
     for name in ("gate_up", "down_proj"):
@@ -195,7 +202,7 @@ def build_manifest(cfg: MoeConfig) -> dict:
             else:
                 out.append(c)
         doc["programs"][prog]["calls"] = out
-    doc["modules"] = C.modules_for(["norm_embed", "gemm_bf16", "attn_prep", "attn_paged", "misc", "sampling", "moe"])
+    doc["modules"] = C.modules_for(modules)
     return doc
 
 

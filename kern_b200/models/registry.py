@@ -8,7 +8,7 @@ import dataclasses
 
 
 def families() -> dict:
-    from . import dense, hybrid, moe
+    from . import dense, hybrid, latent, moe
 
     out = {}
     for cfg in (dense.TOY, dense.TINY, dense.DENSE_8B):
@@ -17,6 +17,9 @@ def families() -> dict:
         out[cfg.name] = (cfg, hybrid.build_manifest, hybrid.load_random_weights, hybrid.random_weights)
     for cfg in (moe.TOY_MOE, moe.TINY_MOE, moe.MOE_30B):
         out[cfg.name] = (cfg, moe.build_manifest, moe.load_random_weights, moe.random_weights)
+    for cfg in (latent.TINY_LATENT, latent.TINY_LATENT_MOE, latent.LATENT_48B):
+        out[cfg.name] = (cfg, latent.build_manifest, latent.load_random_weights,
+                         lambda cfg, **kw: latent.folded(cfg, latent.random_weights(cfg, **kw)))
     from . import toy_int
 
     for lined in (False, True):

@@ -16,9 +16,11 @@ SMEM = 1024 + STAGES * TILE * DQK * 2 + 16 * (DQK + 8) * 2 + 16 * (TILE + 8) * 2
 
 
 def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor, heads: int,
-               scale: float | None = None, splits: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+               scale: float | None = None, splits: int | None = None, out: torch.Tensor | None = None,
+               row_seq: torch.Tensor | None = None) -> torch.Tensor:
     """q [seqs, heads * 576] bf16; cache [pages, page_size, 576] bf16; block_table [seqs, max_pages] i32; seq_lens [seqs]
-    i32 -> out [seqs, heads * 512] bf16. `scale` defaults to 1 / sqrt(192) (the un-absorbed head width: 128 + 64)."""
+    i32 -> out [seqs, heads * 512] bf16. With `row_seq` [rows] i32 a row of q is not a sequence of its own: it reads
+    block-table row row_seq[r] and attends over seq_lens[r] positions (prefill rows: their position + 1). `scale` defaults to 1 / sqrt(192) (the un-absorbed head width: 128 + 64)."""
     k = Kernels.get(q.device)
     seqs = q.shape[0]
     pages, page_size, w = cache.shape
@@ -40,7 +42,7 @@ def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, 
     k.launch("mla_decode", "kern_mla_decode_bf16", (blocks, seqs, splits), (MATH_WARPS * 32 + 32,),
              [lat, ptr(q), ptr(out), ptr(ws_o), ptr(ws_ml), ptr(block_table), ptr(seq_lens), i32(seqs), i32(heads), i32(q.stride(0)),
               i32(out.stride(0)), i32(block_table.shape[1]), i32(page_size), i32(splits), i32(pages), f32(scale * 1.4426950408889634),
-              ptr(k.err_word())], shared_mem=SMEM)
+              ptr(k.err_word()), ptr(row_seq)], shared_mem=SMEM)
     if splits > 1:
         merge_partials(ws_o, ws_ml, out, seqs, heads, DV, splits)
     return out

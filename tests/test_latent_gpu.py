@@ -1,0 +1,68 @@
+"""Latent-attention hybrid (KDA + absorbed MLA, dense and routed MLP) end to end on a GPU against the PyTorch fp32
+oracle over the un-folded checkpoint, and the last latent layer's attention rows on their own."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def build(cfg):
+    from kern_b200.models import latent
+    from kern_b200.runtime import Runtime
+
+    weights = latent.random_weights(cfg, seed=0, std=0.05)
+    fold = latent.folded(cfg, weights)
+    rt = Runtime(latent.build_manifest(cfg), tokens=cfg.page_size * 64, slots=8)
+    rt.load_tensors(lambda name: fold[name].cuda())
+    rt.once()
+    return weights, rt
+
+
+@pytest.mark.parametrize("name", ["tiny-latent", "tiny-latent-moe"])
+def test_latent_prefill_decode_and_graph(cuda, name):
+    from kern_b200.engine import Engine
+    from kern_b200.models import latent
+    from test_latent_cpu import last_latent_attention_error
+
+    cfg = {c.name: c for c in (latent.TINY_LATENT, latent.TINY_LATENT_MOE)}[name]
+    weights, rt = build(cfg)
+    eng = Engine(rt)
+    oracle = latent.LatentOracle(cfg, weights, device="cuda")
+    torch.manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (45, 3, 130)]
+    seqs = [eng.open(160) for _ in prompts]
+    caches = [oracle.new_cache() for _ in prompts]
+    first = eng.step(list(zip(seqs, prompts)))
+    logits = rt.tensor("logits")[:3].float()
+    errs = [(logits[i] - oracle.forward(p, c)[-1]).abs() for i, (p, c) in enumerate(zip(prompts, caches))]
+    assert last_latent_attention_error(cfg, rt, oracle, prompts[0], caches[0]) < 0.03
+    toks = [f[0] for f in first]
+    for _ in range(6):      # decode replays one CUDA graph; the recurrent state advances in place
+        refs = [oracle.forward([t], c)[-1] for t, c in zip(toks, caches)]
+        nxt = eng.step([(s, [t]) for s, t in zip(seqs, toks)])
+        logits = rt.tensor("logits")[:3].float()
+        errs += [(logits[i] - refs[i]).abs() for i in range(3)]
+        toks = [n[0] for n in nxt]
+    rt.check_error()
+    errs = torch.stack(errs)
+    assert float(errs.mean()) < 0.04 and float(errs.max()) < 0.6, (float(errs.mean()), float(errs.max()))
+    assert rt.graphs >= 1
+
+
+def test_latent_chunked_prefill_equals_one_shot(cuda):
+    from kern_b200.engine import Engine
+    from kern_b200.models import latent
+
+    cfg = latent.TINY_LATENT
+    weights, rt = build(cfg)
+    eng = Engine(rt)
+    torch.manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab, (150,)).tolist()
+    a = eng.open(160)
+    one = eng.step([(a, prompt)])[0][0]
+    whole = rt.tensor("logits")[0].float().clone()
+    b = eng.open(160)
+    eng.step([(b, prompt[:70])])
+    two = eng.step([(b, prompt[70:])])[0][0]
+    assert float((whole - rt.tensor("logits")[0].float()).abs().max()) < 0.08 and one == two
+    rt.check_error()
