@@ -911,6 +911,7 @@ def _k_mla_decode(g, kv, q, out, ws_o, ws_ml, table, lens, seqs, heads, q_stride
         trow = int(row_seq[r]) if isinstance(row_seq, torch.Tensor) else r
         lat = _f(pool[tb[trow, : -(-L // page)].long()]).reshape(-1, 576)[:L]
         qq = _f(torch.as_strided(q, (heads, 576), (576, 1), q.storage_offset() + r * q_stride))
+        # a split launch is followed by the merge; here the first writes the finished rows and the merge is a no-op
         p = torch.softmax((qq @ lat.t()) * scale, -1)
         torch.as_strided(out, (heads * 512,), (1,), out.storage_offset() + r * out_stride).copy_((p @ lat[:, :512]).reshape(-1).to(out.dtype))
 

@@ -841,20 +841,59 @@ def mla_rows_op() -> dict:
         "args": [{"param": 0}, {"param": 1}, {"param": 4}, {"param": 5}, {"param": 2}, {"param": 3}]}]}}
 
 
-def mla_attn_op(heads: int, page_size: int, table_width: int, ragged: bool, head_width: int = 192) -> dict:
+def mla_attn_op(heads: int, page_size: int, table_width: int, ragged: bool, head_width: int = 192, seqs_max: int = 0,
+                sms: int = SMS) -> dict:
     """Absorbed latent attention: every head attends over the shared 576-wide latent rows, values their first 512
-    columns. One row per sequence: interface [q, latent state, out, block_table, seq_lens, err]; ragged rows bring
-    [.., row_len, err, row_seq] — a row reads its sequence's table row and attends over its own causal reach."""
+    columns. One row per sequence: interface [q, latent state, out, block_table, seq_lens, err], the context split over
+    CTAs by `when` ranges of the batch (partials merged by a second launch) so that a few long sequences still fill
+    the machine; ragged rows bring [.., row_len, err, row_seq] — a row reads its sequence's table row and attends over
+    its own causal reach."""
     assert page_size % 64 == 0 or 64 % page_size == 0
     iface = ["in buffer<bf16>", "in state", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "out buffer<i32>"]
     if ragged:
         iface.append("in buffer<i32>")
-    lp = ["bytes<128>", "in buffer<bf16>", "out buffer<bf16>", "i64", "i64", "in buffer<i32>", "in buffer<i32>"] + ["i32"] * 8 + \
-         ["f32", "out buffer<i32>", "in buffer<i32>" if ragged else "i64"]
-    args = [_kv_map(MLA_DQK, page_size, 1), {"param": 0}, {"param": 2}, {"i64": 0}, {"i64": 0}, {"param": 3}, {"param": 4},
-            {"i32": I32_MAX}, {"i32": heads}, {"i32": heads * MLA_DQK}, {"i32": heads * MLA_DV}, {"i32": table_width},
-            {"i32": page_size}, {"i32": 1}, {"i32": I32_MAX}, {"f32": (head_width ** -0.5) * 1.4426950408889634}, {"param": 5},
-            {"param": 6} if ragged else {"i64": 0}]
-    return {"params": iface, "impl": {"launches": [{
-        "module": "mla_decode", "entry": "kern_mla_decode_bf16", "block": [288, 1, 1],
-        "grid": [-(-heads // 16), "tokens" if ragged else "seqs", 1], "shared_mem": MLA_SMEM, "params": lp, "args": args}]}}
+    blocks = -(-heads // 16)
+    ranges, hi = [], seqs_max
+    if ragged or not seqs_max:
+        ranges = [(1, 1, seqs_max)]
+    else:
+        for splits in (1, 2, 4, 8, 16, 32):
+            lo = 1 if splits == 32 else max(1, -(-sms // (blocks * splits)))
+            if lo <= hi:
+                ranges.append((splits, lo, hi))
+                hi = lo - 1
+            if hi < 1:
+                break
+    max_splits = max(s for s, _, _ in ranges)
+    launches = []
+    for splits, lo, hi in ranges:
+        when = {"var": "seqs"}
+        if lo > 1:
+            when["min"] = lo
+        if seqs_max and hi < seqs_max:
+            when["max"] = hi
+        part = splits > 1
+        lp = ["bytes<128>", "in buffer<bf16>", "out buffer<bf16>", "out buffer<f32>" if part else "i64",
+              "out buffer<f32>" if part else "i64", "in buffer<i32>", "in buffer<i32>"] + ["i32"] * 8 + \
+             ["f32", "out buffer<i32>", "in buffer<i32>" if ragged else "i64"]
+        ws = [{"scratch": "ws_o"}, {"scratch": "ws_ml"}] if part else [{"i64": 0}, {"i64": 0}]
+        args = [_kv_map(MLA_DQK, page_size, 1), {"param": 0}, {"param": 2}, *ws, {"param": 3}, {"param": 4},
+                {"i32": I32_MAX}, {"i32": heads}, {"i32": heads * MLA_DQK}, {"i32": heads * MLA_DV}, {"i32": table_width},
+                {"i32": page_size}, {"i32": splits}, {"i32": I32_MAX}, {"f32": (head_width ** -0.5) * 1.4426950408889634},
+                {"param": 5}, {"param": 6} if ragged else {"i64": 0}]
+        launch = {"module": "mla_decode", "entry": "kern_mla_decode_bf16", "block": [288, 1, 1],
+                  "grid": [blocks, "tokens" if ragged else "seqs", splits], "shared_mem": MLA_SMEM, "params": lp, "args": args}
+        merge = {"module": "attn_paged", "entry": "kern_attn_merge_splits", "block": [256, 1, 1],
+                 "grid": [{"mul": ["tokens", heads]}, 1, 1],
+                 "params": ["in buffer<f32>", "in buffer<f32>", "out buffer<bf16>", "i32", "i32", "i32", "i32", "i32"],
+                 "args": [{"scratch": "ws_o"}, {"scratch": "ws_ml"}, {"param": 2}, {"i32": I32_MAX}, {"i32": heads},
+                          {"i32": MLA_DV}, {"i32": splits}, {"i32": heads * MLA_DV}]}
+        for l in ([launch, merge] if part else [launch]):
+            if len(when) > 1:
+                l["when"] = when
+            launches.append(l)
+    impl = {"launches": launches}
+    if max_splits > 1:
+        impl["scratch"] = {"ws_o": {"dtype": "f32", "shape": ["tokens", heads * max_splits * MLA_DV]},
+                           "ws_ml": {"dtype": "f32", "shape": ["tokens", heads * max_splits * 2]}}
+    return {"params": iface, "impl": impl}

@@ -270,7 +270,7 @@ def build_manifest(cfg: LatentConfig) -> dict:
     ops["mla_rope"] = C.mla_rope_append_op(H, cfg.qa_dim, cfg.eps, cfg.max_context)
     ops["mla_rows"] = C.mla_rows_op()
     ops["mla_attn_p"] = C.mla_attn_op(H, cfg.page_size, W, ragged=True)
-    ops["mla_attn_d"] = C.mla_attn_op(H, cfg.page_size, W, ragged=False)
+    ops["mla_attn_d"] = C.mla_attn_op(H, cfg.page_size, W, ragged=False, seqs_max=S)
     ops["kda_in"] = C.gemm_op(cfg.kda_in_dim, h, rows_max=T)
     ops["kda_out"] = C.gemm_op(h, cfg.kda_v_dim, epilogue="acc", rows_max=T)
     for ragged, sfx in ((True, "_p"), (False, "_d")):
@@ -345,7 +345,7 @@ def build_manifest(cfg: LatentConfig) -> dict:
         decode += layer(i, False)
     prefill += [{"op": "last_row", "label": "last_row", "args": [B("x"), B("last"), B("cu_seqlens")]}] + head("last")
     decode += head("x")
-    mods = ["norm_embed", "gemm_bf16", "attn_prep", "mla_decode", "misc", "sampling", "gdn"]
+    mods = ["norm_embed", "gemm_bf16", "attn_prep", "attn_paged", "mla_decode", "misc", "sampling", "gdn"]
     doc = {
         "schema_version": 7, "model": cfg.name,
         "vars": {"tokens": {"max": T, "axis": "rows"}, "seqs": {"max": S, "axis": "groups"}},
