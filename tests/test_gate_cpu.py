@@ -5,7 +5,7 @@ import pytest
 from kern_b200 import cli
 
 
-@pytest.mark.parametrize("model", ["toy", "toy-int-stateful"])
+@pytest.mark.parametrize("model", ["toy", "toy-int-stateful", "tiny-latent"])
 def test_gate_passes(model, capsys):
     assert cli.main(["gate", "--model", model, "--cpu"]) == 0
     out = capsys.readouterr().out

@@ -35,7 +35,17 @@ def test_latent_prefill_decode_and_graph(cuda, name):
     first = eng.step(list(zip(seqs, prompts)))
     logits = rt.tensor("logits")[:3].float()
     errs = [(logits[i] - oracle.forward(p, c)[-1]).abs() for i, (p, c) in enumerate(zip(prompts, caches))]
-    assert last_latent_attention_error(cfg, rt, oracle, prompts[0], caches[0]) < 0.03
+    # the last latent layer's attention alone: against the oracle's latent rows (which differ from the runtime's own
+    # by the rounding of three layers), and against the same call through the host-memory statement of every kernel
+    assert last_latent_attention_error(cfg, rt, oracle, prompts[0], caches[0]) < 0.1
+    from kern_b200.cpu import CpuRuntime
+    host = CpuRuntime(latent.build_manifest(cfg), weights=latent.folded(cfg, weights), tokens=cfg.page_size * 64, slots=8)
+    host.once()
+    heng = Engine(host)
+    heng.step(list(zip([heng.open(160) for _ in prompts], prompts)))
+    n = sum(len(p) for p in prompts)
+    a, b = rt.tensor("attn")[:n].float().cpu(), host.tensor("attn")[:n].float()
+    assert float((a - b).abs().max() / b.abs().max()) < 0.02
     toks = [f[0] for f in first]
     for _ in range(6):      # decode replays one CUDA graph; the recurrent state advances in place
         refs = [oracle.forward([t], c)[-1] for t, c in zip(toks, caches)]

@@ -5,7 +5,7 @@ import torch
 
 from kern_b200.cpu import CpuRuntime
 from kern_b200.engine import Engine
-from kern_b200.models import dense, hybrid
+from kern_b200.models import dense, hybrid, latent
 from kern_b200.serve import pp
 from kern_b200.serve.scheduler import Request, Scheduler
 
@@ -51,6 +51,27 @@ def test_hybrid_pipeline_four_stages_with_state_slots():
     w = hybrid.random_weights(cfg, seed=4, std=0.08)
     pipe, single, docs = make(cfg, hybrid.build_manifest, w, 4, slots=5)
     assert sorted(s for d in docs for s in d["states"]) == sorted(["gdn.l0", "gdn.l1", "gdn.l2", "kv.l3"])
+    torch.manual_seed(1)
+    prompt = torch.randint(1, cfg.vocab, (22,)).tolist()
+    res = []
+    for eng in (single, pipe):
+        s = eng.open(40)
+        t = eng.step([(s, prompt[:10])])
+        t = eng.step([(s, prompt[10:])])[0]
+        out = [t[0]]
+        for _ in range(4):
+            out.append(eng.step([(s, [out[-1]])])[0][0])
+        res.append(out)
+    assert res[0] == res[1]
+
+
+def test_latent_moe_pipeline_two_stages():
+    """KDA + latent attention + routed experts cut in two: the row plan of the latent layers (`row_seq`, `row_len`)
+    is made on the stage of the first latent layer and crosses the cut with the activations."""
+    cfg = latent.TINY_LATENT
+    w = latent.folded(cfg, latent.random_weights(cfg, seed=4, std=0.05))
+    pipe, single, docs = make(cfg, latent.build_manifest, w, 2, slots=5)
+    assert sorted(s for d in docs for s in d["states"]) == sorted(["kda.l0", "kv.l1", "kda.l2", "kv.l3"])
     torch.manual_seed(1)
     prompt = torch.randint(1, cfg.vocab, (22,)).tolist()
     res = []
