@@ -138,6 +138,8 @@ def _random(name, shape, dtype, g, device, std):
         t = torch.randn(shape, generator=g, device=device)
     elif name.endswith("conv1d.weight"):
         t = 0.3 * torch.randn(shape, generator=g, device=device)
+    elif name.endswith("mlp.gate.weight"):
+        t = 10 * std * torch.randn(shape, generator=g, device=device)       # a router with opinions
     else:
         t = std * torch.randn(shape, generator=g, device=device)
     return t.to(torch.bfloat16 if dtype == "bf16" else torch.float32)
