@@ -81,6 +81,64 @@ KERN_DEVICE bool chunk_of(const int* cu_q, int seqs, int slot, int& r0, int& nva
 
 }  // namespace
 
+// T = (I + L)^-1, then W = T Ks and Ut = T Qs to scratch (Ks holds beta-scaled decayed keys, Qs beta v); shared by
+// the scalar-decay and the per-key-decay preparation.
+KERN_DEVICE void solve_and_project(float (*Ls)[LDL], float (*Ks)[LDK], float (*Qs)[LDK], float* Wg, float* Ug, int r0,
+                                   int nvalid, int hv, int h) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  // T = (I + L)^-1 by forward substitution: thread j owns column j (row t needs rows < t of the same column only);
+  // the row of L is a broadcast read, two accumulators halve the dependent chain
+  float Tc[CH];
+  if (tid < CH) {
+#pragma unroll
+    for (int t = 0; t < CH; ++t) {
+      float a0 = t == tid ? 1.f : 0.f, a1 = 0.f;
+#pragma unroll
+      for (int i4 = 0; i4 < t / 4; ++i4) {
+        const float4 l = *reinterpret_cast<const float4*>(&Ls[t][4 * i4]);
+        a0 -= l.x * Tc[4 * i4];
+        a1 -= l.y * Tc[4 * i4 + 1];
+        a0 -= l.z * Tc[4 * i4 + 2];
+        a1 -= l.w * Tc[4 * i4 + 3];
+      }
+#pragma unroll
+      for (int i = (t / 4) * 4; i < t; ++i) a0 -= Ls[t][i] * Tc[i];
+      Tc[t] = a0 + a1;
+    }
+  }
+  __syncthreads();      // every column is done reading L
+  if (tid < CH) {
+#pragma unroll
+    for (int t = 0; t < CH; ++t) Ls[t][tid] = tf32r(Tc[t]);
+  }
+  __syncthreads();
+
+  // W = T (beta exp(g) K), Ut = T (beta V): warp -> rows 16 mb .., columns 64 nh ..; T is lower triangular, so the
+  // products stop at the diagonal block
+  {
+    const int mb = warp & 3, nh = warp >> 2;
+    float w[8][4], u[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { w[i][j] = 0.f; u[i][j] = 0.f; }
+    auto a_at = [&](int m, int k) { return __float_as_uint(Ls[16 * mb + m][k]); };
+    warp_mma<8>(w, 2 * (mb + 1), a_at, [&](int k, int n) { return __float_as_uint(Ks[k][64 * nh + n]); });
+    warp_mma<8>(u, 2 * (mb + 1), a_at, [&](int k, int n) { return __float_as_uint(Qs[k][64 * nh + n]); });
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int i = 16 * mb + g + 8 * hh, col = 64 * nh + 8 * nt + 2 * t4;
+        if (i < nvalid) {
+          const size_t at = ((size_t)(r0 + i) * hv + h) * DD + col;
+          *reinterpret_cast<float2*>(Wg + at) = make_float2(tf32r(w[nt][2 * hh]), tf32r(w[nt][2 * hh + 1]));
+          *reinterpret_cast<float2*>(Ug + at) = make_float2(tf32r(u[nt][2 * hh]), tf32r(u[nt][2 * hh + 1]));
+        }
+      }
+  }
+}
+
 // grid [ceil(tokens / 64) + seqs, HV], block 256, dynamic shared memory PREP_SMEM bytes.
 // Scratch: W, Qg, Kd, Ut [tokens, HV, 128] f32; M [tokens, HV, 64] f32; gC [tokens, HV] f32.
 constexpr int PREP_SMEM = (2 * CH * LDK + CH * LDL + 2 * CH) * 4;
@@ -234,57 +292,221 @@ extern "C" __global__ void __launch_bounds__(256, 2)
   }
   if (tid < nvalid) Gg[(size_t)(r0 + tid) * hv + h] = __expf(g_last);
 
-  // T = (I + L)^-1 by forward substitution: thread j owns column j (row t needs rows < t of the same column only);
-  // the row of L is a broadcast read, two accumulators halve the dependent chain
-  float Tc[CH];
-  if (tid < CH) {
+  solve_and_project(Ls, Ks, Qs, Wg, Ug, r0, nvalid, hv, h);
+}
+
+// ---- per-key decay (Kimi Delta Attention) ---------------------------------------------------------------------------
+// The same factors with g a vector over the keys: G[t][k] the inclusive running sum of log2 decay inside the chunk.
+//   L[i,j] = beta_i sum_k k_i[k] k_j[k] 2^(G_i[k] - G_j[k])  (j < i)      M[i,j] = sum_k q_i[k] k_j[k] 2^(G_i[k] - G_j[k])  (j <= i)
+//   W = T (beta 2^G K)     Qg = 2^G q     Kd = 2^(G_last - G) k     Dg = 2^G_last (a vector)
+// The pairwise sums are not matrix products (the weight depends on i, j and k), and k / 2^G overflows under strong
+// decay, so they run on the CUDA cores with every exponent <= 0: tokens fall in four groups of 16; for j in an earlier
+// group than i,   2^(G_i - G_j) = 2^(G_i - R_a) . 2^(R_a - R_b') . 2^(R_b' - G_j)
+// (R_a: the sum just before group a of i; R_b': the sum at the end of j's group) — the last factor is folded into a
+// copy of the keys once (Km), the middle one is a 3-row table, the first costs one exp2 per (i, k); pairs inside a
+// group take 2^(G_i - G_j) directly. A thread owns rows {bi + 16 a} x columns {bj + 16 b}: ten live pairs each.
+// grid [ceil(tokens / 64) + seqs, HV], block 256, dynamic shared memory KDA_PREP_SMEM bytes.
+constexpr int KDA_PREP_SMEM = (4 * CH * LDK + CH * LDL + CH + 3 * DD) * 4;
+
+extern "C" __global__ void __launch_bounds__(256, 1)
+    kern_kda_chunk_prep_k128_v128(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, const __nv_bfloat16* gk, const int* cu_q,
+                                  const float* A_log, const float* dt_bias, float* Wg, float* Qg, float* Kg, float* Ug,
+                                  float* Mg, float* Dg, int seqs, int hk, int hv, int zba_stride, int b_off, int gk_stride) {
+  pdl_wait();
+  extern __shared__ __align__(16) float sm[];
+  float (*Ks)[LDK] = reinterpret_cast<float (*)[LDK]>(sm);                    // k, later beta 2^G k
+  float (*Qs)[LDK] = reinterpret_cast<float (*)[LDK]>(sm + CH * LDK);         // q, later beta v
+  float (*Gs)[LDK] = reinterpret_cast<float (*)[LDK]>(sm + 2 * CH * LDK);     // log2 decay, then its running sum
+  float (*Km)[LDK] = reinterpret_cast<float (*)[LDK]>(sm + 3 * CH * LDK);     // k 2^(R' - G)
+  float (*Ls)[LDL] = reinterpret_cast<float (*)[LDL]>(sm + 4 * CH * LDK);     // L, later T
+  float* bs = sm + 4 * CH * LDK + CH * LDL;                                   // beta
+  float (*Dt)[DD] = reinterpret_cast<float (*)[DD]>(bs + CH);                 // 2^(R_2 - R_1), 2^(R_3 - R_1), 2^(R_3 - R_2)
+  int r0, nvalid;
+  if (!chunk_of(cu_q, seqs, blockIdx.x, r0, nvalid)) return;
+  const int h = blockIdx.y, kh = h / (hv / hk);
+  const int conv_dim = 2 * hk * DD + hv * DD;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  uint4 vreg[4];
+  {
+    const float a2 = -__expf(A_log[h]) * 1.4426950408889634f;
 #pragma unroll
-    for (int t = 0; t < CH; ++t) {
-      float a0 = t == tid ? 1.f : 0.f, a1 = 0.f;
+    for (int i = 0; i < 4; ++i) {
+      const int p = tid + 256 * i, tok = p >> 4, c8 = p & 15;
+      const bool ok = tok < nvalid;
+      vreg[i] = ok ? *reinterpret_cast<const uint4*>(qkv + (size_t)(r0 + tok) * conv_dim + 2 * hk * DD + h * DD + c8 * 8)
+                   : make_uint4(0u, 0u, 0u, 0u);
+      const uint4 gr = ok ? *reinterpret_cast<const uint4*>(gk + (size_t)(r0 + tok) * gk_stride + h * DD + c8 * 8)
+                          : make_uint4(0u, 0u, 0u, 0u);
+      const float2 g01 = unpack_bf16x2(gr.x), g23 = unpack_bf16x2(gr.y), g45 = unpack_bf16x2(gr.z), g67 = unpack_bf16x2(gr.w);
+      const float gv[8] = {g01.x, g01.y, g23.x, g23.y, g45.x, g45.y, g67.x, g67.y};
 #pragma unroll
-      for (int i4 = 0; i4 < t / 4; ++i4) {
-        const float4 l = *reinterpret_cast<const float4*>(&Ls[t][4 * i4]);
-        a0 -= l.x * Tc[4 * i4];
-        a1 -= l.y * Tc[4 * i4 + 1];
-        a0 -= l.z * Tc[4 * i4 + 2];
-        a1 -= l.w * Tc[4 * i4 + 3];
+      for (int e = 0; e < 8; ++e) {
+        const float x = gv[e] + dt_bias[h * DD + c8 * 8 + e];
+        Gs[tok][c8 * 8 + e] = ok ? a2 * (x > 20.f ? x : log1pf(__expf(x))) : 0.f;      // padding rows decay nothing
       }
+    }
+    uint2 rq[8], rk[8];
 #pragma unroll
-      for (int i = (t / 4) * 4; i < t; ++i) a0 -= Ls[t][i] * Tc[i];
-      Tc[t] = a0 + a1;
+    for (int u = 0; u < 8; ++u) {
+      const int tok = warp + 8 * u;
+      const __nv_bfloat16* row = qkv + (size_t)(r0 + tok) * conv_dim;
+      rq[u] = tok < nvalid ? *reinterpret_cast<const uint2*>(row + kh * DD + lane * 4) : make_uint2(0u, 0u);
+      rk[u] = tok < nvalid ? *reinterpret_cast<const uint2*>(row + hk * DD + kh * DD + lane * 4) : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int tok = warp + 8 * u;
+      const float2 q01 = unpack_bf16x2(rq[u].x), q23 = unpack_bf16x2(rq[u].y);
+      const float2 k01 = unpack_bf16x2(rk[u].x), k23 = unpack_bf16x2(rk[u].y);
+      float q2 = q01.x * q01.x + q01.y * q01.y + q23.x * q23.x + q23.y * q23.y;
+      float k2 = k01.x * k01.x + k01.y * k01.y + k23.x * k23.x + k23.y * k23.y;
+      q2 = warp_sum(q2);
+      k2 = warp_sum(k2);
+      const float qi = rsqrtf(q2 + 1e-6f) * rsqrtf((float)DD), ki = rsqrtf(k2 + 1e-6f);
+      *reinterpret_cast<float4*>(&Qs[tok][lane * 4]) = make_float4(q01.x * qi, q01.y * qi, q23.x * qi, q23.y * qi);
+      *reinterpret_cast<float4*>(&Ks[tok][lane * 4]) = make_float4(k01.x * ki, k01.y * ki, k23.x * ki, k23.y * ki);
+      if (lane == 0) {
+        float be = 0.f;
+        if (tok < nvalid) {
+          const float bb = __bfloat162float(zba[(size_t)(r0 + tok) * zba_stride + b_off + h]);
+          be = __bfloat162float(__float2bfloat16(1.f / (1.f + __expf(-bb))));
+        }
+        bs[tok] = be;
+      }
     }
   }
-  __syncthreads();      // every column is done reading L
-  if (tid < CH) {
+  __syncthreads();
+  if (tid < DD) {      // running sum over the 64 tokens, one key column per thread
+    float run = 0.f;
+#pragma unroll 8
+    for (int t = 0; t < CH; ++t) {
+      run += Gs[t][tid];
+      Gs[t][tid] = run;
+    }
+  }
+  __syncthreads();
+  // Km and the group-to-group table
 #pragma unroll
-    for (int t = 0; t < CH; ++t) Ls[t][tid] = tf32r(Tc[t]);
+  for (int i = 0; i < 8; ++i) {
+    const int p = tid + 256 * i, tok = p >> 5, c4 = (p & 31) * 4;
+    const int gend = (tok | 15);      // last token of tok's group
+    const float4 gj = *reinterpret_cast<const float4*>(&Gs[tok][c4]), ge = *reinterpret_cast<const float4*>(&Gs[gend][c4]);
+    const float4 kj = *reinterpret_cast<const float4*>(&Ks[tok][c4]);
+    *reinterpret_cast<float4*>(&Km[tok][c4]) = make_float4(kj.x * exp2f(ge.x - gj.x), kj.y * exp2f(ge.y - gj.y),
+                                                           kj.z * exp2f(ge.z - gj.z), kj.w * exp2f(ge.w - gj.w));
+  }
+  for (int p = tid; p < 3 * DD; p += 256) {
+    const int which = p / DD, k = p % DD;
+    const int hi = which == 0 ? 31 : 47, lo = which == 2 ? 31 : 15;      // R_2 - R_1, R_3 - R_1, R_3 - R_2
+    Dt[which][k] = exp2f(Gs[hi][k] - Gs[lo][k]);
   }
   __syncthreads();
 
-  // W = T (beta exp(g) K), Ut = T (beta V): warp -> rows 16 mb .., columns 64 nh ..; T is lower triangular, so the
-  // products stop at the diagonal block
   {
-    const int mb = warp & 3, nh = warp >> 2;
-    float w[8][4], u[8][4];
+    const int bi = tid >> 4, bj = tid & 15;
+    float Ao[6], Po[6], Ai[4], Pi[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int x = 0; x < 6; ++x) { Ao[x] = 0.f; Po[x] = 0.f; }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { w[i][j] = 0.f; u[i][j] = 0.f; }
-    auto a_at = [&](int m, int k) { return __float_as_uint(Ls[16 * mb + m][k]); };
-    warp_mma<8>(w, 2 * (mb + 1), a_at, [&](int k, int n) { return __float_as_uint(Ks[k][64 * nh + n]); });
-    warp_mma<8>(u, 2 * (mb + 1), a_at, [&](int k, int n) { return __float_as_uint(Qs[k][64 * nh + n]); });
+    for (int x = 0; x < 4; ++x) { Ai[x] = 0.f; Pi[x] = 0.f; }
+    auto dot = [](const float4& a, const float4& b) { return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; };
+    auto mul = [](const float4& a, const float4& b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); };
+    auto ex2 = [](const float4& a, const float4& b) {      // 2^min(a - b, 0)
+      return make_float4(exp2f(fminf(a.x - b.x, 0.f)), exp2f(fminf(a.y - b.y, 0.f)), exp2f(fminf(a.z - b.z, 0.f)),
+                         exp2f(fminf(a.w - b.w, 0.f)));
+    };
+#pragma unroll 1
+    for (int k = 0; k < DD; k += 4) {
+      float4 ki[4], qi[4], gi[4];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const int i = 16 * mb + g + 8 * hh, col = 64 * nh + 8 * nt + 2 * t4;
-        if (i < nvalid) {
-          const size_t at = ((size_t)(r0 + i) * hv + h) * DD + col;
-          *reinterpret_cast<float2*>(Wg + at) = make_float2(tf32r(w[nt][2 * hh]), tf32r(w[nt][2 * hh + 1]));
-          *reinterpret_cast<float2*>(Ug + at) = make_float2(tf32r(u[nt][2 * hh]), tf32r(u[nt][2 * hh + 1]));
-        }
+      for (int a = 0; a < 4; ++a) {
+        ki[a] = *reinterpret_cast<const float4*>(&Ks[bi + 16 * a][k]);
+        qi[a] = *reinterpret_cast<const float4*>(&Qs[bi + 16 * a][k]);
+        gi[a] = *reinterpret_cast<const float4*>(&Gs[bi + 16 * a][k]);
       }
+      // pairs inside a group
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const float4 kj = *reinterpret_cast<const float4*>(&Ks[bj + 16 * a][k]);
+        const float4 gj = *reinterpret_cast<const float4*>(&Gs[bj + 16 * a][k]);
+        const float4 t = mul(kj, ex2(gi[a], gj));
+        Ai[a] += dot(ki[a], t);
+        Pi[a] += dot(qi[a], t);
+      }
+      // pairs across groups: rows of group a >= 1 against columns of groups b < a
+      float4 km[3], kp[4], qp[4];
+#pragma unroll
+      for (int b = 0; b < 3; ++b) km[b] = *reinterpret_cast<const float4*>(&Km[bj + 16 * b][k]);
+#pragma unroll
+      for (int a = 1; a < 4; ++a) {
+        const float4 e1 = ex2(gi[a], *reinterpret_cast<const float4*>(&Gs[16 * a - 1][k]));
+        kp[a] = mul(ki[a], e1);
+        qp[a] = mul(qi[a], e1);
+      }
+      const float4 d21 = *reinterpret_cast<const float4*>(&Dt[0][k]), d31 = *reinterpret_cast<const float4*>(&Dt[1][k]),
+                   d32 = *reinterpret_cast<const float4*>(&Dt[2][k]);
+      const float4 t20 = mul(km[0], d21), t30 = mul(km[0], d31), t31 = mul(km[1], d32);
+      Ao[0] += dot(kp[1], km[0]); Po[0] += dot(qp[1], km[0]);      // (1, 0)
+      Ao[1] += dot(kp[2], t20);   Po[1] += dot(qp[2], t20);        // (2, 0)
+      Ao[2] += dot(kp[2], km[1]); Po[2] += dot(qp[2], km[1]);      // (2, 1)
+      Ao[3] += dot(kp[3], t30);   Po[3] += dot(qp[3], t30);        // (3, 0)
+      Ao[4] += dot(kp[3], t31);   Po[4] += dot(qp[3], t31);        // (3, 1)
+      Ao[5] += dot(kp[3], km[2]); Po[5] += dot(qp[3], km[2]);      // (3, 2)
+    }
+    // scatter: L strictly below the diagonal (times beta_i), M on and below it, zeros above
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const int i = bi + 16 * a;
+      const float be = bs[i];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int j = bj + 16 * b;
+        float lv = 0.f, mv = 0.f;
+        if (b == a) {
+          lv = bj < bi ? Ai[a] : 0.f;
+          mv = bj <= bi ? Pi[a] : 0.f;
+        } else if (b < a) {
+          const int x = a == 1 ? 0 : (a == 2 ? 1 + b : 3 + b);
+          lv = Ao[x];
+          mv = Po[x];
+        }
+        Ls[i][j] = be * lv;
+        if (i < nvalid) Mg[((size_t)(r0 + i) * hv + h) * CH + j] = tf32r(mv);
+      }
+    }
   }
+  __syncthreads();      // L complete; raw q and k are no longer needed
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int p = tid + 256 * i, tok = p >> 4, c0 = (p & 15) * 8;
+    const float be = bs[tok];
+    const float2 v01 = unpack_bf16x2(vreg[i].x), v23 = unpack_bf16x2(vreg[i].y), v45 = unpack_bf16x2(vreg[i].z),
+                 v67 = unpack_bf16x2(vreg[i].w);
+    const float vv[8] = {v01.x, v01.y, v23.x, v23.y, v45.x, v45.y, v67.x, v67.y};
+    float qo[8], ko[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float q = Qs[tok][c0 + e], k = Ks[tok][c0 + e], gt = Gs[tok][c0 + e];
+      const float eg = exp2f(gt), ed = exp2f(Gs[CH - 1][c0 + e] - gt);
+      qo[e] = tf32r(eg * q);
+      ko[e] = tf32r(ed * k);
+      Ks[tok][c0 + e] = tf32r(be * eg * k);
+      Qs[tok][c0 + e] = tf32r(be * vv[e]);
+    }
+    if (tok < nvalid) {
+      float* qd = Qg + ((size_t)(r0 + tok) * hv + h) * DD + c0;
+      float* kd = Kg + ((size_t)(r0 + tok) * hv + h) * DD + c0;
+      *reinterpret_cast<float4*>(qd) = make_float4(qo[0], qo[1], qo[2], qo[3]);
+      *reinterpret_cast<float4*>(qd + 4) = make_float4(qo[4], qo[5], qo[6], qo[7]);
+      *reinterpret_cast<float4*>(kd) = make_float4(ko[0], ko[1], ko[2], ko[3]);
+      *reinterpret_cast<float4*>(kd + 4) = make_float4(ko[4], ko[5], ko[6], ko[7]);
+    }
+  }
+  if (tid < DD) Dg[((size_t)r0 * hv + h) * DD + tid] = exp2f(Gs[CH - 1][tid]);
+  // the elementwise pass reads Gs[CH - 1] while the last row's own elements are rewritten only in Ks / Qs: no hazard
+  solve_and_project(Ls, Ks, Qs, Wg, Ug, r0, nvalid, hv, h);
 }
 
 // grid [HV * 2, seqs], block 256, dynamic shared memory RULE_SMEM bytes. A CTA owns 64 value rows of one head.
@@ -292,10 +514,12 @@ extern "C" __global__ void __launch_bounds__(256, 2)
 // 4..7 compute the outputs. Two block barriers per chunk; every operand buffer is refilled right after its product.
 constexpr int RULE_SMEM = (CH * LDK * 3 + CH * LDN + CH * LDL + 2 * CH * LDU) * 4;
 
-extern "C" __global__ void __launch_bounds__(256, 1)
-    kern_gdn_chunk_rule_k128_v128(const float* Wg, const float* Qg, const float* Kg, const float* Ug, const float* Mg,
-                                  const float* Gg, float* o_raw, uint8_t* state, const int* lines, const int* cu_q, int seqs,
-                                  int hv, long long line_bytes, long long s_offset) {
+// KDA: the state's decay over a chunk is a vector over the keys, Gg [.., HV, 128] read at the chunk's first token.
+template <bool KDA>
+__device__ __forceinline__ void chunk_rule_body(const float* Wg, const float* Qg, const float* Kg, const float* Ug,
+                                                const float* Mg, const float* Gg, float* o_raw, uint8_t* state,
+                                                const int* lines, const int* cu_q, int seqs, int hv, long long line_bytes,
+                                                long long s_offset) {
   pdl_wait();
   extern __shared__ __align__(16) float sm[];
   float (*Ss)[LDK] = reinterpret_cast<float (*)[LDK]>(sm);                                  // state rows (tf32), B[k][n] = Ss[n][k]
@@ -367,8 +591,16 @@ extern "C" __global__ void __launch_bounds__(256, 1)
 
   for (int c = 0; c < nch; ++c) {
     const int r0 = q0 + c * CH, nv = min(CH, q1 - r0);
-    const float gC = Gg[(size_t)r0 * hv + h];
+    const float gC = KDA ? 1.f : Gg[(size_t)r0 * hv + h];
     const int wl = warp & 3;
+    float2 dk[16];
+    if constexpr (KDA) {
+      if (warp < 4) {
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt)
+          dk[nt] = *reinterpret_cast<const float2*>(Gg + ((size_t)r0 * hv + h) * DD + 8 * nt + 2 * t4);
+      }
+    }
     float acc[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
@@ -400,7 +632,7 @@ extern "C" __global__ void __launch_bounds__(256, 1)
 #pragma unroll
       for (int nt = 0; nt < 16; ++nt)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) S[nt][j] *= gC;
+        for (int j = 0; j < 4; ++j) S[nt][j] *= KDA ? ((j & 1) ? dk[nt].y : dk[nt].x) : gC;
       warp_mma<16>(S, CH / 8, [&](int m, int k) { return __float_as_uint(Us[k][16 * wl + m]); },
                    [&](int k, int n) { return __float_as_uint(Kc[k][n]); });
 #pragma unroll
@@ -436,4 +668,20 @@ extern "C" __global__ void __launch_bounds__(256, 1)
         *reinterpret_cast<float2*>(Sgl + (size_t)(16 * warp + g + 8 * hh) * DD + 8 * nt + 2 * t4) =
             make_float2(S[nt][2 * hh], S[nt][2 * hh + 1]);
   }
+}
+
+extern "C" __global__ void __launch_bounds__(256, 1)
+    kern_gdn_chunk_rule_k128_v128(const float* Wg, const float* Qg, const float* Kg, const float* Ug, const float* Mg,
+                                  const float* Gg, float* o_raw, uint8_t* state, const int* lines, const int* cu_q, int seqs,
+                                  int hv, long long line_bytes, long long s_offset) {
+  chunk_rule_body<false>(Wg, Qg, Kg, Ug, Mg, Gg, o_raw, state, lines, cu_q, seqs, hv, line_bytes, s_offset);
+}
+
+// The per-key-decay rule (Kimi Delta Attention): same walk, `Dg` [tokens, HV, 128] holds at a chunk's first token the
+// decay of every key over the chunk.
+extern "C" __global__ void __launch_bounds__(256, 1)
+    kern_kda_chunk_rule_k128_v128(const float* Wg, const float* Qg, const float* Kg, const float* Ug, const float* Mg,
+                                  const float* Dg, float* o_raw, uint8_t* state, const int* lines, const int* cu_q, int seqs,
+                                  int hv, long long line_bytes, long long s_offset) {
+  chunk_rule_body<true>(Wg, Qg, Kg, Ug, Mg, Dg, o_raw, state, lines, cu_q, seqs, hv, line_bytes, s_offset);
 }

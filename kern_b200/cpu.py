@@ -920,3 +920,46 @@ CPU_KERNELS.update({"kern_kda_rule_k128_v128": _kda_rule(128), "kern_kda_rule_k6
                     "kern_kda_step_k128_v128": _kda_step(128), "kern_kda_step_k64_v64": _kda_step(64),
                     "kern_mla_rope_append_bf16": _k_mla_rope_append, "kern_mla_rows": _k_mla_rows,
                     "kern_mla_decode_bf16": _k_mla_decode})
+
+
+def _k_kda_chunk_prep(g, qkv, zba, gk, cu, A_log, dt_bias, Wg, Qg, Kg, Ug, Mg, Dg, seqs, hk, hv, zba_stride, b_off, gk_stride):
+    from .ops import gdn as G
+
+    dim = 128
+    conv_dim = 2 * hk * dim + hv * dim
+    for s in range(seqs):
+        r0, r1 = _rows_of(cu, s)
+        n = r1 - r0
+        if n <= 0:
+            continue
+        rows = _f(qkv[r0 * conv_dim: r1 * conv_dim].view(n, conv_dim))
+        b = _f(torch.as_strided(zba, (n, hv), (zba_stride, 1), zba.storage_offset() + r0 * zba_stride + b_off))
+        gate = _f(torch.as_strided(gk, (n, hv * dim), (gk_stride, 1), gk.storage_offset() + r0 * gk_stride)).view(n, hv, dim)
+        q = rows[:, :hk * dim].view(n, hk, dim)
+        k = rows[:, hk * dim:2 * hk * dim].view(n, hk, dim)
+        v = rows[:, 2 * hk * dim:].view(n, hv, dim)
+        parts = G.kda_chunk_prep_ref(q, k, v, b, gate, A_log[:hv], dt_bias[:hv * dim].view(hv, dim))
+        for dst, src, w in zip((Wg, Qg, Kg, Ug, Mg, Dg), parts, (dim, dim, dim, dim, 64, dim)):
+            dst[r0 * hv * w: r1 * hv * w] = src.reshape(-1)
+
+
+def _k_kda_chunk_rule(g, Wg, Qg, Kg, Ug, Mg, Dg, o_raw, state, lines, cu, seqs, hv, line_bytes, s_off):
+    from .ops import gdn as G
+
+    dim = 128
+    for s in range(seqs):
+        r0, r1 = _rows_of(cu, s)
+        n = r1 - r0
+        if n <= 0:
+            continue
+        ln = int(lines[s])
+        Sb = state[ln * line_bytes + s_off: ln * line_bytes + s_off + hv * dim * dim * 4].view(torch.float32).view(hv, dim, dim)
+        S0 = Sb.clone() if ln > 0 else torch.zeros(hv, dim, dim)
+        cut = lambda t, w: t[r0 * hv * w: r1 * hv * w].view(n, hv, w)
+        o, S1 = G.chunk_rule_ref(cut(Wg, dim), cut(Qg, dim), cut(Kg, dim), cut(Ug, dim), cut(Mg, 64), cut(Dg, dim), S0)
+        o_raw[r0 * hv * dim: r1 * hv * dim] = o.reshape(-1)
+        if ln > 0:
+            Sb.copy_(S1)
+
+
+CPU_KERNELS.update({"kern_kda_chunk_prep_k128_v128": _k_kda_chunk_prep, "kern_kda_chunk_rule_k128_v128": _k_kda_chunk_rule})

@@ -778,11 +778,13 @@ def sigmoid_mul_op(d: int, x_stride: int, gate_stride: int) -> dict:
 
 
 # ---- per-key-decay delta rule (Kimi Delta Attention) and latent attention ---------------------------------------
-def kda_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_off: int, eps: float, ragged: bool) -> dict:
+def kda_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_off: int, eps: float, ragged: bool,
+                chunked: bool = True) -> dict:
     """Delta rule with a decay per key channel + gated RMSNorm. `zba` points at the z|b columns of the projection's
     row and `gk` at its hv * dim gate columns (same row stride).
     Interface [qkv, zba, gk, out, state, lines, A_log, dt_bias, norm_w] for one row per sequence (the fused step), or
-    [qkv, zba, gk, out, state, lines, cu_seqlens, A_log, dt_bias, norm_w, seqs] for ragged rows (token by token)."""
+    [qkv, zba, gk, out, state, lines, cu_seqlens, A_log, dt_bias, norm_w, seqs] for ragged rows (heads of 128 in the
+    chunked form, others token by token)."""
     assert dim in (64, 128)
     iface = ["in buffer<bf16>", "in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "inout state", "in buffer<i32>"]
     if not ragged:
@@ -810,6 +812,28 @@ def kda_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_
                        "i32", "f32"],
             "args": [{"scratch": "o_raw"}, {"param": 1}, {"param": 3}, {"param": 9}, {"i32": I32_MAX}, {"i32": hv},
                      {"i32": dim}, {"i32": zba_stride}, {"i32": 0}, {"f32": eps}]}
+    if chunked and dim == 128:
+        # prefill rows in the chunked (WY) form: pairwise sums with a weight per key on the CUDA cores, the solve and the
+        # products with the state on the tensor cores, one pass over the chunks with the state on chip
+        names = ["gw", "gq", "gk", "gu", "gm", "gd"]
+        sc = [{"scratch": n} for n in names]
+        prep = {"module": "gdn_chunk", "entry": "kern_kda_chunk_prep_k128_v128", "block": [256, 1, 1],
+                "grid": [{"add": [{"ceil_div": ["tokens", 64]}, "seqs"]}, hv, 1],
+                "shared_mem": (4 * 64 * 132 + 64 * 68 + 64 + 3 * 128) * 4,
+                "params": ["in buffer<bf16>", "in buffer<bf16>", "in buffer<bf16>", "in buffer<i32>", "in buffer<f32>",
+                           "in buffer<f32>"] + ["out buffer<f32>"] * 6 + ["i32"] * 6,
+                "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"param": 6}, {"param": 7}, {"param": 8}, *sc,
+                         {"param": 10}, {"i32": hk}, {"i32": hv}, {"i32": zba_stride}, {"i32": hv * dim}, {"i32": zba_stride}]}
+        walk = {"module": "gdn_chunk", "entry": "kern_kda_chunk_rule_k128_v128", "block": [256, 1, 1],
+                "grid": [hv * 2, "seqs", 1], "shared_mem": (64 * 132 * 3 + 64 * 136 + 64 * 68 + 2 * 64 * 72) * 4,
+                "params": ["in buffer<f32>"] * 6 + ["out buffer<f32>", "inout state", "in buffer<i32>", "in buffer<i32>",
+                                                    "i32", "i32", "i64", "i64"],
+                "args": [*sc, {"scratch": "o_raw"}, {"param": 4}, {"param": 5}, {"param": 6}, {"param": 10}, {"i32": hv},
+                         {"i64": line_bytes}, {"i64": s_off}]}
+        scratch = {n: {"dtype": "f32", "shape": ["tokens", hv * 128]} for n in names}
+        scratch["gm"] = {"dtype": "f32", "shape": ["tokens", hv * 64]}
+        scratch["o_raw"] = {"dtype": "f32", "shape": ["tokens", hv * dim]}
+        return {"params": iface, "impl": {"launches": [prep, walk, norm], "scratch": scratch}}
     return {"params": iface, "impl": {"launches": [rule, norm],
                                       "scratch": {"o_raw": {"dtype": "f32", "shape": ["tokens", hv * dim]}}}}
 

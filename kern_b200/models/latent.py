@@ -81,6 +81,10 @@ class LatentConfig:
 TINY_LATENT = LatentConfig(name="tiny-latent", vocab=512, hidden=256, layers=4, full_every=2, heads=4, q_lora=64,
                            kda_k_heads=2, kda_v_heads=8, kda_dim=64, intermediate=512, page_size=16, max_tokens=256,
                            max_seqs=8, max_context=256)
+# KDA heads of 128, the size whose prefill runs through the chunked (WY) kernels
+TINY_LATENT_K128 = LatentConfig(name="tiny-latent-k128", vocab=512, hidden=256, layers=2, full_every=2, heads=4, q_lora=64,
+                                kda_k_heads=2, kda_v_heads=8, kda_dim=128, intermediate=512, page_size=16, max_tokens=256,
+                                max_seqs=8, max_context=256)
 TINY_LATENT_MOE = LatentConfig(name="tiny-latent-moe", vocab=512, hidden=256, layers=2, full_every=2, heads=4, q_lora=64,
                                kda_k_heads=2, kda_v_heads=8, kda_dim=64, intermediate=512, experts=16, top_k=4,
                                moe_intermediate=128, page_size=16, max_tokens=256, max_seqs=8, max_context=256)
@@ -348,6 +352,8 @@ def build_manifest(cfg: LatentConfig) -> dict:
     prefill += [{"op": "last_row", "label": "last_row", "args": [B("x"), B("last"), B("cu_seqlens")]}] + head("last")
     decode += head("x")
     mods = ["norm_embed", "gemm_bf16", "attn_prep", "attn_paged", "mla_decode", "misc", "sampling", "gdn"]
+    if gd == 128:
+        mods.append("gdn_chunk")      # prefill rows of 128-wide heads run the chunked (WY) kernels
     doc = {
         "schema_version": 7, "model": cfg.name,
         "vars": {"tokens": {"max": T, "axis": "rows"}, "seqs": {"max": S, "axis": "groups"}},

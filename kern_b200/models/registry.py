@@ -17,7 +17,7 @@ def families() -> dict:
         out[cfg.name] = (cfg, hybrid.build_manifest, hybrid.load_random_weights, hybrid.random_weights)
     for cfg in (moe.TOY_MOE, moe.TINY_MOE, moe.MOE_30B):
         out[cfg.name] = (cfg, moe.build_manifest, moe.load_random_weights, moe.random_weights)
-    for cfg in (latent.TINY_LATENT, latent.TINY_LATENT_MOE, latent.LATENT_48B):
+    for cfg in (latent.TINY_LATENT, latent.TINY_LATENT_K128, latent.TINY_LATENT_MOE, latent.LATENT_48B):
         out[cfg.name] = (cfg, latent.build_manifest, latent.load_random_weights,
                          lambda cfg, **kw: latent.folded(cfg, latent.random_weights(cfg, **kw)))
     from . import toy_int

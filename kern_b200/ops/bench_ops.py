@@ -139,11 +139,21 @@ def bench_gdn(a):
     nw = torch.ones(d, device="cuda").to(torch.bfloat16)
     o_raw = torch.empty(rows, hv * d, dtype=torch.float32, device="cuda")
 
-    scratch = G.chunk_scratch(rows, hv, "cuda") if a.rows > 1 and a.chunked else None
+    scratch = G.chunk_scratch(rows, hv, "cuda", kda=a.kda) if a.rows > 1 and a.chunked else None
+    if a.kda:      # the per-key-decay rule: gate rows beside z | b in the projection's row
+        A_log, dtb = torch.zeros(hv, device="cuda"), torch.zeros(hv * d, device="cuda")
+        gk = torch.randn(rows, hv * d, device="cuda").to(torch.bfloat16)
 
     def step():
         G.conv(x, y, state, lines, cu, w, None, seqs, conv_dim, width, lb)
-        if a.rows > 1 and a.chunked:
+        if a.kda and a.rows > 1 and a.chunked:
+            G.kda_rule_chunked(y, x[:, conv_dim:], gk, out, state, lines, cu, A_log, dtb, nw, seqs, hk, hv, d, d, 0, hv * d, lb,
+                               s_off, o_raw=o_raw, scratch=scratch)
+        elif a.kda and a.rows > 1:
+            G.kda_rule(y, x[:, conv_dim:], gk, out, state, lines, cu, A_log, dtb, nw, seqs, hk, hv, d, d, 0, hv * d, lb, s_off)
+        elif a.kda:
+            G.kda_step(y, x[:, conv_dim:], gk, out, state, lines, A_log, dtb, nw, seqs, hk, hv, d, d, 0, hv * d, lb, s_off)
+        elif a.rows > 1 and a.chunked:
             G.rule_chunked(y, x[:, conv_dim:], out, state, lines, cu, A_log, dtb, nw, seqs, hk, hv, d, d, 0, hv * d,
                            hv * d + hv, lb, s_off, o_raw=o_raw, scratch=scratch)
         elif a.rows == 1 and not a.unfused:
@@ -155,7 +165,7 @@ def bench_gdn(a):
     ms = timeit(step, a.iters)
     Kernels.get().check_error()
     nbytes = 2.0 * seqs * hv * d * d * 4 if a.rows == 1 else 0.0      # the recurrent state is read and written once per step
-    report("gdn_step" if a.rows == 1 else ("gdn_prefill_chunked" if a.chunked else "gdn_prefill_chunk"), ms, nbytes=nbytes, seqs=seqs, rows=rows, hk=hk, hv=hv, d=d)
+    report(("kda_" if a.kda else "") + ("gdn_step" if a.rows == 1 else ("gdn_prefill_chunked" if a.chunked else "gdn_prefill_chunk")), ms, nbytes=nbytes, seqs=seqs, rows=rows, hk=hk, hv=hv, d=d)
 
 
 def _cache(seqs, ctx, hk, d, page):
@@ -242,6 +252,7 @@ def main(argv=None):
     gd = sub.add_parser("gdn")
     gd.add_argument("--seqs", type=int, default=64); gd.add_argument("--rows", type=int, default=1)
     gd.add_argument("--hk", type=int, default=16); gd.add_argument("--hv", type=int, default=48); gd.add_argument("--d", type=int, default=128)
+    gd.add_argument("--kda", action="store_true", help="a decay per key channel (Kimi Delta Attention)")
     gd.add_argument("--chunked", action="store_true", help="prefill rows through the chunked (WY) kernels")
     gd.add_argument("--unfused", action="store_true", help="decode rows through the two-launch rule + norm instead of the fused step")
     d = sub.add_parser("attn_decode")

@@ -122,12 +122,13 @@ CHUNK_PREP_SMEM = (2 * 64 * 132 + 64 * 68 + 2 * 64) * 4
 CHUNK_RULE_SMEM = (64 * 132 * 3 + 64 * 136 + 64 * 68 + 2 * 64 * 72) * 4
 
 
-def chunk_scratch(tokens: int, hv: int, device) -> dict:
-    """Scratch of the chunked rule: W, Qg, Kd, Ut [tokens, HV, 128], M [tokens, HV, 64], gC [tokens, HV], all f32."""
+def chunk_scratch(tokens: int, hv: int, device, kda: bool = False) -> dict:
+    """Scratch of the chunked rule: W, Qg, Kd, Ut [tokens, HV, 128], M [tokens, HV, 64], gC [tokens, HV], all f32
+    (`kda`: gC is [tokens, HV, 128], the decay of every key over a chunk at the chunk's first token)."""
     big = lambda: torch.empty(tokens, hv, 128, dtype=torch.float32, device=device)
     return {"W": big(), "Qg": big(), "Kd": big(), "Ut": big(),
             "M": torch.empty(tokens, hv, 64, dtype=torch.float32, device=device),
-            "gC": torch.empty(tokens, hv, dtype=torch.float32, device=device)}
+            "gC": big() if kda else torch.empty(tokens, hv, dtype=torch.float32, device=device)}
 
 
 def rule_chunked(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv, z_off, b_off, a_off,
@@ -146,6 +147,33 @@ def rule_chunked(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs
               ptr(sc["Ut"]), ptr(sc["M"]), ptr(sc["gC"]), i32(seqs), i32(hk), i32(hv), i32(zba.stride(0)), i32(b_off),
               i32(a_off)], shared_mem=CHUNK_PREP_SMEM)
     k.launch("gdn_chunk", "kern_gdn_chunk_rule_k128_v128", (hv * 2, seqs), (256,),
+             [ptr(sc["W"]), ptr(sc["Qg"]), ptr(sc["Kd"]), ptr(sc["Ut"]), ptr(sc["M"]), ptr(sc["gC"]), ptr(o_raw), ptr(state),
+              ptr(lines), ptr(cu_q), i32(seqs), i32(hv), i64(line_b), i64(s_off)], shared_mem=CHUNK_RULE_SMEM)
+    k.launch("gdn", "kern_gdn_gate_norm_bf16", ((hv + 3) // 4, tokens), (128,),
+             [ptr(o_raw), ptr(zba), ptr(out), ptr(norm_w), i32(tokens), i32(hv), i32(dv), i32(zba.stride(0)),
+              i32(z_off), f32(eps)])
+    return out
+
+
+KDA_CHUNK_PREP_SMEM = (4 * 64 * 132 + 64 * 68 + 64 + 3 * 128) * 4
+
+
+def kda_rule_chunked(qkv, zba, gk, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv, z_off, b_off, line_b,
+                     s_off, eps=1e-6, o_raw=None, scratch=None):
+    """Prefill rows of the per-key-decay rule through the chunked (WY) form: the pairwise sums of a chunk carry a
+    weight per (i, j, key) and run on the CUDA cores with every exponent <= 0, the triangular solve and the products
+    with the state on the tensor cores; `scratch["gC"]` is [tokens, HV, 128] here (a decay per key). dk = dv = 128."""
+    k = Kernels.get(qkv.device)
+    assert dk == dv == 128 and cu_q is not None and gk.stride(0) % 8 == 0 and gk.data_ptr() % 16 == 0
+    tokens = out.shape[0]
+    if o_raw is None:
+        o_raw = torch.empty(tokens, hv * dv, dtype=torch.float32, device=qkv.device)
+    sc = scratch if scratch is not None else chunk_scratch(tokens, hv, qkv.device, kda=True)
+    k.launch("gdn_chunk", "kern_kda_chunk_prep_k128_v128", ((tokens + 63) // 64 + seqs, hv), (256,),
+             [ptr(qkv), ptr(zba), ptr(gk), ptr(cu_q), ptr(A_log), ptr(dt_bias), ptr(sc["W"]), ptr(sc["Qg"]), ptr(sc["Kd"]),
+              ptr(sc["Ut"]), ptr(sc["M"]), ptr(sc["gC"]), i32(seqs), i32(hk), i32(hv), i32(zba.stride(0)), i32(b_off),
+              i32(gk.stride(0))], shared_mem=KDA_CHUNK_PREP_SMEM)
+    k.launch("gdn_chunk", "kern_kda_chunk_rule_k128_v128", (hv * 2, seqs), (256,),
              [ptr(sc["W"]), ptr(sc["Qg"]), ptr(sc["Kd"]), ptr(sc["Ut"]), ptr(sc["M"]), ptr(sc["gC"]), ptr(o_raw), ptr(state),
               ptr(lines), ptr(cu_q), i32(seqs), i32(hv), i64(line_b), i64(s_off)], shared_mem=CHUNK_RULE_SMEM)
     k.launch("gdn", "kern_gdn_gate_norm_bf16", ((hv + 3) // 4, tokens), (128,),
@@ -247,7 +275,8 @@ def chunk_rule_ref(W, Qg, Kd, Ut, M, gC, S):
         sl = slice(c0, c0 + n)
         U = Ut[sl] - torch.einsum("ihk,hvk->ihv", W[sl], S)
         out[sl] = torch.einsum("ihk,hvk->ihv", Qg[sl], S) + torch.einsum("ihj,jhv->ihv", M[sl, :, :n], U)
-        S = gC[c0][:, None, None] * S + torch.einsum("ihv,ihk->hvk", U, Kd[sl])
+        dec = gC[c0][:, None, None] if gC.dim() == 2 else gC[c0][:, None, :]      # a scalar per head, or a vector over keys
+        S = dec * S + torch.einsum("ihv,ihk->hvk", U, Kd[sl])
     return out, S
 
 
@@ -271,3 +300,35 @@ def kda_rule_ref(q, k, v, z, b, gk, S, A_log, dt_bias, norm_w, eps=1e-6):
         S = S + u[:, :, None] * k[t][:, None, :]
         out[t] = torch.einsum("hvk,hk->hv", S, q[t])
     return gate_norm_ref(out, z, norm_w, eps), S
+
+
+def kda_chunk_prep_ref(q, k, v, b, gk, A_log, dt_bias):
+    """`chunk_prep_ref` with a decay per key: gk [T, HV, D] gate rows, dt_bias [HV, D]; G the inclusive running sum of
+    the log decay per key inside the chunk, and the pairwise weights exp(G_i - G_j) sit inside the sums over keys.
+    Returns W, Qg, Kd, Ut [T, HV, D], M [T, HV, 64], D [T, HV, D] (exp(G_last) on every row of the chunk)."""
+    T_, hk, d = q.shape
+    hv = v.shape[1]
+    rep = hv // hk
+    qn = q.float() * torch.rsqrt(q.float().pow(2).sum(-1, keepdim=True) + 1e-6) / d ** 0.5
+    kn = k.float() * torch.rsqrt(k.float().pow(2).sum(-1, keepdim=True) + 1e-6)
+    qn, kn = qn.repeat_interleave(rep, 1), kn.repeat_interleave(rep, 1)          # [T, HV, D]
+    ga = -torch.exp(A_log.float())[None, :, None] * F.softplus(gk.float() + dt_bias.float()[None])      # [T, HV, D]
+    beta = torch.sigmoid(b.float()).to(torch.bfloat16).float()
+    W, Qg, Kd, Ut, Dv = (torch.zeros(T_, hv, d, device=q.device) for _ in range(5))
+    M = torch.zeros(T_, hv, CHUNK, device=q.device)
+    for c0 in range(0, T_, CHUNK):
+        n = min(CHUNK, T_ - c0)
+        sl = slice(c0, c0 + n)
+        G = ga[sl].cumsum(0)                                                       # [n, HV, D]
+        e = torch.exp((G[:, None] - G[None, :]).clamp(max=0.0))                    # [i, j, HV, D]
+        kk = torch.einsum("ihd,jhd,ijhd->hij", kn[sl], kn[sl], e)
+        qk = torch.einsum("ihd,jhd,ijhd->hij", qn[sl], kn[sl], e)
+        L = beta[sl].t()[:, :, None] * kk * torch.tril(torch.ones(n, n, device=q.device), -1)
+        Tm = torch.linalg.inv(torch.eye(n, device=q.device) + L)
+        W[sl] = torch.einsum("hij,jhd->ihd", Tm, beta[sl][:, :, None] * torch.exp(G) * kn[sl])
+        Ut[sl] = torch.einsum("hij,jhd->ihd", Tm, beta[sl][:, :, None] * v[sl].float())
+        Qg[sl] = torch.exp(G) * qn[sl]
+        Kd[sl] = torch.exp(G[-1][None] - G) * kn[sl]
+        M[sl, :, :n] = (qk * torch.tril(torch.ones(n, n, device=q.device))).permute(1, 0, 2)
+        Dv[sl] = torch.exp(G[-1])[None]
+    return W, Qg, Kd, Ut, M, Dv

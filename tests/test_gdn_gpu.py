@@ -216,3 +216,47 @@ def test_kda_decode_step_per_key_decay(cuda, d):
                 S[i] = S1
                 torch.testing.assert_close(state[int(lines[i]), s_off:].view(torch.float32).view(hv, d, d), S1, rtol=1e-3, atol=1e-3)
     assert int(state[0].count_nonzero()) == 0
+
+
+def test_kda_chunked_prefill_matches_the_statement(cuda):
+    """The chunked (WY) form of the per-key-decay rule against its token-by-token fp32 statement: sequences of several
+    chunks with ragged tails, a null-line row, strong and weak decays, from non-zero states."""
+    from kern_b200.ops import gdn
+    from kern_b200.ops.launcher import Kernels
+
+    torch.manual_seed(11)
+    hk, hv, d, width = 2, 6, 128, 4
+    conv_dim = 2 * hk * d + hv * d
+    zb = hv * d + hv + 2                      # z | b | pad: the gate rows start 16-byte aligned
+    lb, s_off = gdn.line_bytes(hk, hv, d, d, width)
+    lens = [150, 64, 5, 70]
+    seqs, T = len(lens), sum(lens)
+    state = torch.zeros(6, lb, dtype=torch.uint8, device=cuda)
+    lines = torch.tensor([2, 4, 0, 5], dtype=torch.int32, device=cuda)
+    S = [torch.randn(hv, d, d, device=cuda) * 0.2 if ln > 0 else torch.zeros(hv, d, d, device=cuda) for ln in lines.tolist()]
+    for i, ln in enumerate(lines.tolist()):
+        if ln > 0:
+            state[ln, s_off:].view(torch.float32).view(hv, d, d).copy_(S[i])
+    A_log = torch.log(torch.empty(hv, device=cuda).uniform_(0.05, 4.0))      # from almost no decay to e^-12 per token
+    dt_bias = torch.randn(hv * d, device=cuda)
+    norm_w = bf(1 + 0.1 * torch.randn(d, device=cuda))
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32, device=cuda)
+    y = bf(torch.randn(T, conv_dim, device=cuda))
+    row = bf(torch.randn(T, zb + hv * d, device=cuda))
+    zba, gk = row[:, :zb], row[:, zb:]
+    out = torch.empty(T, hv * d, dtype=torch.bfloat16, device=cuda)
+    gdn.kda_rule_chunked(y, zba, gk, out, state, lines, cu, A_log, dt_bias, norm_w, seqs, hk, hv, d, d, 0, hv * d, lb, s_off)
+    torch.cuda.synchronize()
+    Kernels.get(cuda).check_error()
+    for i, n in enumerate(lens):
+        r0 = int(cu[i])
+        yf = y[r0:r0 + n].float()
+        q, k, v = yf[:, :hk * d].view(n, hk, d), yf[:, hk * d:2 * hk * d].view(n, hk, d), yf[:, 2 * hk * d:].view(n, hv, d)
+        z = zba[r0:r0 + n, :hv * d].float().view(n, hv, d)
+        b = zba[r0:r0 + n, hv * d:hv * d + hv].float()
+        o, S1 = gdn.kda_rule_ref(q, k, v, z, b, gk[r0:r0 + n].float().view(n, hv, d), S[i], A_log, dt_bias.view(hv, d), norm_w)
+        torch.testing.assert_close(out[r0:r0 + n].float().view(n, hv, d), o, rtol=3e-2, atol=3e-2)
+        if int(lines[i]) > 0:
+            # tf32 products against the all-f32 statement
+            torch.testing.assert_close(state[int(lines[i]), s_off:].view(torch.float32).view(hv, d, d), S1, rtol=5e-3, atol=5e-3)
+    assert int(state[0].count_nonzero()) == 0 and int(state[3].count_nonzero()) == 0

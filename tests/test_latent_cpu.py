@@ -17,7 +17,7 @@ def make(cfg, slots=6):
 
 
 def test_manifests_verify():
-    for cfg in (latent.TINY_LATENT, latent.TINY_LATENT_MOE, latent.LATENT_48B):
+    for cfg in (latent.TINY_LATENT, latent.TINY_LATENT_K128, latent.TINY_LATENT_MOE, latent.LATENT_48B):
         m, diags = verify(latent.build_manifest(cfg))
         assert m is not None, diags[:5]
 
@@ -41,12 +41,12 @@ def test_absorbed_projections_equal_the_factors():
     assert torch.allclose(want, got, rtol=2e-2, atol=3.0), float((want - got).abs().max())
 
 
-@pytest.mark.parametrize("cfg", [latent.TINY_LATENT, latent.TINY_LATENT_MOE], ids=lambda c: c.name)
+@pytest.mark.parametrize("cfg", [latent.TINY_LATENT, latent.TINY_LATENT_K128, latent.TINY_LATENT_MOE], ids=lambda c: c.name)
 def test_prefill_and_decode_match_oracle(cfg):
     w, rt, eng, oracle = make(cfg)
     torch.manual_seed(0)
-    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 3, 37)]
-    seqs = [eng.open(48) for _ in prompts]
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 3, 37 if cfg.kda_dim == 64 else 100)]
+    seqs = [eng.open(112) for _ in prompts]
     caches = [oracle.new_cache() for _ in prompts]
     first = eng.step(list(zip(seqs, prompts)))
     logits = rt.tensor("logits")[:3].float()
