@@ -18,13 +18,13 @@ def build(cfg):
     return weights, rt
 
 
-@pytest.mark.parametrize("name", ["tiny-latent", "tiny-latent-moe"])
+@pytest.mark.parametrize("name", ["tiny-latent", "tiny-latent-k128", "tiny-latent-moe"])
 def test_latent_prefill_decode_and_graph(cuda, name):
     from kern_b200.engine import Engine
     from kern_b200.models import latent
     from test_latent_cpu import last_latent_attention_error
 
-    cfg = {c.name: c for c in (latent.TINY_LATENT, latent.TINY_LATENT_MOE)}[name]
+    cfg = {c.name: c for c in (latent.TINY_LATENT, latent.TINY_LATENT_K128, latent.TINY_LATENT_MOE)}[name]
     weights, rt = build(cfg)
     eng = Engine(rt)
     oracle = latent.LatentOracle(cfg, weights, device="cuda")
