@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import sys
 import os
 
 import numpy as np
@@ -81,6 +82,9 @@ def main(argv=None) -> int:
                 rt.write(name, np.ascontiguousarray(col.astype(np_of[dtype])))
         if rank > 0:
             dist.recv(torch.zeros(1, device=dev), src=rank - 1)         # the previous stage's push has landed
+            # the receive is only enqueued on torch's stream; the runtime issues on its own stream, so the host waits
+            # for the signal itself before it launches (a graph replay is otherwise quick enough to overtake it)
+            torch.cuda.current_stream().synchronize()
         rt.issue(call.program, {k: v for k, v in call.vars.items() if k in stages[rank]["vars"]})
         if rank + 1 < world:
             vmax = {k: v["max"] for k, v in stages[rank + 1]["vars"].items()}
@@ -97,6 +101,9 @@ def main(argv=None) -> int:
             ef = next(f for f in proto["fills"] if f["name"] == call.forward["emits"])
             got = np.asarray(rt.read(ef["name"], call.groups * ef["width"])).reshape(call.groups, ef["width"])[:, 0]
             want = [t[0] for t in oracle.step(list(zip(oseqs, feed)))]
+            if got.tolist() != want and ok:
+                print(json.dumps({"check": "pipeline_process_per_stage", "first_mismatch_call": it, "got": got.tolist(),
+                                  "want": want}), file=sys.stderr, flush=True)
             ok = ok and got.tolist() == want
             toks = torch.tensor(want, dtype=torch.int64, device=dev)
         dist.broadcast(toks, src=world - 1)
