@@ -302,13 +302,13 @@ extern "C" __global__ void __launch_bounds__(256, 2)
 // The pairwise sums are not matrix products (the weight depends on i, j and k), and k / 2^G overflows under strong
 // decay, so they run on the CUDA cores with every exponent <= 0: tokens fall in four groups of 16; for j in an earlier
 // group than i,   2^(G_i - G_j) = 2^(G_i - R_a) . 2^(R_a - R_b') . 2^(R_b' - G_j)
-// (R_a: the sum just before group a of i; R_b': the sum at the end of j's group) — the last factor is folded into a
-// copy of the keys once (Km), the middle one is a 3-row table, the first costs one exp2 per (i, k); pairs inside a
+// (R_a: the sum just before group a of i; R_b': the sum at the end of j's group) — the last factor is folded into the
+// keys as they are loaded, the middle one is a 3-row table, the first costs one exp2 per (i, k); pairs inside a
 // group take 2^(G_i - G_j) directly. A thread owns rows {bi + 16 a} x columns {bj + 16 b}: ten live pairs each.
 // grid [ceil(tokens / 64) + seqs, HV], block 256, dynamic shared memory KDA_PREP_SMEM bytes.
-constexpr int KDA_PREP_SMEM = (4 * CH * LDK + CH * LDL + CH + 3 * DD) * 4;
+constexpr int KDA_PREP_SMEM = (3 * CH * LDK + CH + 3 * DD) * 4;      // 103 KB: two CTAs per SM
 
-extern "C" __global__ void __launch_bounds__(256, 1)
+extern "C" __global__ void __launch_bounds__(256, 2)
     kern_kda_chunk_prep_k128_v128(const __nv_bfloat16* qkv, const __nv_bfloat16* zba, const __nv_bfloat16* gk, const int* cu_q,
                                   const float* A_log, const float* dt_bias, float* Wg, float* Qg, float* Kg, float* Ug,
                                   float* Mg, float* Dg, int seqs, int hk, int hv, int zba_stride, int b_off, int gk_stride) {
@@ -317,9 +317,8 @@ extern "C" __global__ void __launch_bounds__(256, 1)
   float (*Ks)[LDK] = reinterpret_cast<float (*)[LDK]>(sm);                    // k, later beta 2^G k
   float (*Qs)[LDK] = reinterpret_cast<float (*)[LDK]>(sm + CH * LDK);         // q, later beta v
   float (*Gs)[LDK] = reinterpret_cast<float (*)[LDK]>(sm + 2 * CH * LDK);     // log2 decay, then its running sum
-  float (*Km)[LDK] = reinterpret_cast<float (*)[LDK]>(sm + 3 * CH * LDK);     // k 2^(R' - G)
-  float (*Ls)[LDL] = reinterpret_cast<float (*)[LDL]>(sm + 4 * CH * LDK);     // L, later T
-  float* bs = sm + 4 * CH * LDK + CH * LDL;                                   // beta
+  float (*Ls)[LDL] = reinterpret_cast<float (*)[LDL]>(sm + 2 * CH * LDK);     // L, later T: over Gs, once Gs has been used
+  float* bs = sm + 3 * CH * LDK;                                              // beta
   float (*Dt)[DD] = reinterpret_cast<float (*)[DD]>(bs + CH);                 // 2^(R_2 - R_1), 2^(R_3 - R_1), 2^(R_3 - R_2)
   int r0, nvalid;
   if (!chunk_of(cu_q, seqs, blockIdx.x, r0, nvalid)) return;
@@ -386,16 +385,7 @@ extern "C" __global__ void __launch_bounds__(256, 1)
     }
   }
   __syncthreads();
-  // Km and the group-to-group table
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int p = tid + 256 * i, tok = p >> 5, c4 = (p & 31) * 4;
-    const int gend = (tok | 15);      // last token of tok's group
-    const float4 gj = *reinterpret_cast<const float4*>(&Gs[tok][c4]), ge = *reinterpret_cast<const float4*>(&Gs[gend][c4]);
-    const float4 kj = *reinterpret_cast<const float4*>(&Ks[tok][c4]);
-    *reinterpret_cast<float4*>(&Km[tok][c4]) = make_float4(kj.x * exp2f(ge.x - gj.x), kj.y * exp2f(ge.y - gj.y),
-                                                           kj.z * exp2f(ge.z - gj.z), kj.w * exp2f(ge.w - gj.w));
-  }
+  // the group-to-group table
   for (int p = tid; p < 3 * DD; p += 256) {
     const int which = p / DD, k = p % DD;
     const int hi = which == 0 ? 31 : 47, lo = which == 2 ? 31 : 15;      // R_2 - R_1, R_3 - R_1, R_3 - R_2
@@ -425,7 +415,10 @@ extern "C" __global__ void __launch_bounds__(256, 1)
         qi[a] = *reinterpret_cast<const float4*>(&Qs[bi + 16 * a][k]);
         gi[a] = *reinterpret_cast<const float4*>(&Gs[bi + 16 * a][k]);
       }
-      // pairs inside a group
+      // pairs inside a group; the same column loads give the folded keys km[b] = k_j 2^(R_b' - G_j) of groups 0..2
+      float4 km[3], kp[4], qp[4], rr[4];
+#pragma unroll
+      for (int a = 1; a < 4; ++a) rr[a] = *reinterpret_cast<const float4*>(&Gs[16 * a - 1][k]);      // R_a = R_(a-1)'
 #pragma unroll
       for (int a = 0; a < 4; ++a) {
         const float4 kj = *reinterpret_cast<const float4*>(&Ks[bj + 16 * a][k]);
@@ -433,14 +426,12 @@ extern "C" __global__ void __launch_bounds__(256, 1)
         const float4 t = mul(kj, ex2(gi[a], gj));
         Ai[a] += dot(ki[a], t);
         Pi[a] += dot(qi[a], t);
+        if (a < 3) km[a] = mul(kj, ex2(rr[a + 1], gj));
       }
       // pairs across groups: rows of group a >= 1 against columns of groups b < a
-      float4 km[3], kp[4], qp[4];
-#pragma unroll
-      for (int b = 0; b < 3; ++b) km[b] = *reinterpret_cast<const float4*>(&Km[bj + 16 * b][k]);
 #pragma unroll
       for (int a = 1; a < 4; ++a) {
-        const float4 e1 = ex2(gi[a], *reinterpret_cast<const float4*>(&Gs[16 * a - 1][k]));
+        const float4 e1 = ex2(gi[a], rr[a]);
         kp[a] = mul(ki[a], e1);
         qp[a] = mul(qi[a], e1);
       }
@@ -454,6 +445,35 @@ extern "C" __global__ void __launch_bounds__(256, 1)
       Ao[4] += dot(kp[3], t31);   Po[4] += dot(qp[3], t31);        // (3, 1)
       Ao[5] += dot(kp[3], km[2]); Po[5] += dot(qp[3], km[2]);      // (3, 2)
     }
+    __syncthreads();      // every pairwise sum is in registers: raw q, k and the running sums are read once more below
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int p = tid + 256 * i, tok = p >> 4, c0 = (p & 15) * 8;
+      const float be = bs[tok];
+      const float2 v01 = unpack_bf16x2(vreg[i].x), v23 = unpack_bf16x2(vreg[i].y), v45 = unpack_bf16x2(vreg[i].z),
+                   v67 = unpack_bf16x2(vreg[i].w);
+      const float vv[8] = {v01.x, v01.y, v23.x, v23.y, v45.x, v45.y, v67.x, v67.y};
+      float qo[8], ko[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float q = Qs[tok][c0 + e], k = Ks[tok][c0 + e], gt = Gs[tok][c0 + e];
+        const float eg = exp2f(gt), ed = exp2f(Gs[CH - 1][c0 + e] - gt);
+        qo[e] = tf32r(eg * q);
+        ko[e] = tf32r(ed * k);
+        Ks[tok][c0 + e] = tf32r(be * eg * k);
+        Qs[tok][c0 + e] = tf32r(be * vv[e]);
+      }
+      if (tok < nvalid) {
+        float* qd = Qg + ((size_t)(r0 + tok) * hv + h) * DD + c0;
+        float* kd = Kg + ((size_t)(r0 + tok) * hv + h) * DD + c0;
+        *reinterpret_cast<float4*>(qd) = make_float4(qo[0], qo[1], qo[2], qo[3]);
+        *reinterpret_cast<float4*>(qd + 4) = make_float4(qo[4], qo[5], qo[6], qo[7]);
+        *reinterpret_cast<float4*>(kd) = make_float4(ko[0], ko[1], ko[2], ko[3]);
+        *reinterpret_cast<float4*>(kd + 4) = make_float4(ko[4], ko[5], ko[6], ko[7]);
+      }
+    }
+    if (tid < DD) Dg[((size_t)r0 * hv + h) * DD + tid] = exp2f(Gs[CH - 1][tid]);
+    __syncthreads();      // the running sums are used up: L takes their place
     // scatter: L strictly below the diagonal (times beta_i), M on and below it, zeros above
 #pragma unroll
     for (int a = 0; a < 4; ++a) {
@@ -476,36 +496,7 @@ extern "C" __global__ void __launch_bounds__(256, 1)
       }
     }
   }
-  __syncthreads();      // L complete; raw q and k are no longer needed
-
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int p = tid + 256 * i, tok = p >> 4, c0 = (p & 15) * 8;
-    const float be = bs[tok];
-    const float2 v01 = unpack_bf16x2(vreg[i].x), v23 = unpack_bf16x2(vreg[i].y), v45 = unpack_bf16x2(vreg[i].z),
-                 v67 = unpack_bf16x2(vreg[i].w);
-    const float vv[8] = {v01.x, v01.y, v23.x, v23.y, v45.x, v45.y, v67.x, v67.y};
-    float qo[8], ko[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float q = Qs[tok][c0 + e], k = Ks[tok][c0 + e], gt = Gs[tok][c0 + e];
-      const float eg = exp2f(gt), ed = exp2f(Gs[CH - 1][c0 + e] - gt);
-      qo[e] = tf32r(eg * q);
-      ko[e] = tf32r(ed * k);
-      Ks[tok][c0 + e] = tf32r(be * eg * k);
-      Qs[tok][c0 + e] = tf32r(be * vv[e]);
-    }
-    if (tok < nvalid) {
-      float* qd = Qg + ((size_t)(r0 + tok) * hv + h) * DD + c0;
-      float* kd = Kg + ((size_t)(r0 + tok) * hv + h) * DD + c0;
-      *reinterpret_cast<float4*>(qd) = make_float4(qo[0], qo[1], qo[2], qo[3]);
-      *reinterpret_cast<float4*>(qd + 4) = make_float4(qo[4], qo[5], qo[6], qo[7]);
-      *reinterpret_cast<float4*>(kd) = make_float4(ko[0], ko[1], ko[2], ko[3]);
-      *reinterpret_cast<float4*>(kd + 4) = make_float4(ko[4], ko[5], ko[6], ko[7]);
-    }
-  }
-  if (tid < DD) Dg[((size_t)r0 * hv + h) * DD + tid] = exp2f(Gs[CH - 1][tid]);
-  // the elementwise pass reads Gs[CH - 1] while the last row's own elements are rewritten only in Ks / Qs: no hazard
+  __syncthreads();      // L complete
   solve_and_project(Ls, Ks, Qs, Wg, Ug, r0, nvalid, hv, h);
 }
 

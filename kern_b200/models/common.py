@@ -819,7 +819,7 @@ def kda_rule_op(hk: int, hv: int, dim: int, zba_stride: int, line_bytes: int, s_
         sc = [{"scratch": n} for n in names]
         prep = {"module": "gdn_chunk", "entry": "kern_kda_chunk_prep_k128_v128", "block": [256, 1, 1],
                 "grid": [{"add": [{"ceil_div": ["tokens", 64]}, "seqs"]}, hv, 1],
-                "shared_mem": (4 * 64 * 132 + 64 * 68 + 64 + 3 * 128) * 4,
+                "shared_mem": (3 * 64 * 132 + 64 + 3 * 128) * 4,
                 "params": ["in buffer<bf16>", "in buffer<bf16>", "in buffer<bf16>", "in buffer<i32>", "in buffer<f32>",
                            "in buffer<f32>"] + ["out buffer<f32>"] * 6 + ["i32"] * 6,
                 "args": [{"param": 0}, {"param": 1}, {"param": 2}, {"param": 6}, {"param": 7}, {"param": 8}, *sc,

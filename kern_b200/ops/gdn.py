@@ -155,7 +155,7 @@ def rule_chunked(qkv, zba, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs
     return out
 
 
-KDA_CHUNK_PREP_SMEM = (4 * 64 * 132 + 64 * 68 + 64 + 3 * 128) * 4
+KDA_CHUNK_PREP_SMEM = (3 * 64 * 132 + 64 + 3 * 128) * 4
 
 
 def kda_rule_chunked(qkv, zba, gk, out, state, lines, cu_q, A_log, dt_bias, norm_w, seqs, hk, hv, dk, dv, z_off, b_off, line_b,
