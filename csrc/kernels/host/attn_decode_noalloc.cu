@@ -8,6 +8,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "../sm100/attn_paged.cu"
 
@@ -24,6 +25,7 @@ struct DeviceSetup {
   float* scratch = nullptr;   // device address of g_noalloc_scratch on that device
 };
 DeviceSetup g_setup[kMaxDevices];
+std::mutex g_setup_mutex;   // first calls from several host threads take turns
 thread_local char g_last_error[256] = "";
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -47,6 +49,7 @@ int smem_for(int d) { return 1024 + (d >= 256 ? 3 : 4) * (2 * 64 * d * 2) + 64 *
 // kernels need its device address.
 int setup_device(int dev) {
   if (dev < 0 || dev >= kMaxDevices) return fail(KERN_NOALLOC_BAD_ARGUMENT, "device index is outside 0..63%s");
+  std::lock_guard<std::mutex> lock(g_setup_mutex);
   if (g_setup[dev].ready) return KERN_NOALLOC_OK;
   void* p = nullptr;
   cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
@@ -113,7 +116,9 @@ extern "C" int kern_attn_decode_split_noalloc(const void* q, const void* kv_pool
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(KERN_NOALLOC_CUDA_ERROR, "cuTensorMapEncodeTiled rejected the kv pool geometry%s");
   }
-  // the statistics of splits that no CTA writes (an empty sequence) must read as "nothing here"
+  // The statistics of splits that no CTA writes (an empty sequence) must read as "nothing here". A (row, head) is
+  // written by every split or by none, so a cleared pair (max 0, sum 0) is never mixed with live ones: the merge
+  // sees sum 0 over all splits and writes a zero row, as the allocating path does from its (-inf, 0) pairs.
   e = cudaMemsetAsync(ws_ml, 0, stat_rows * 2 * sizeof(float), stream);
   if (e != cudaSuccess) return fail(KERN_NOALLOC_CUDA_ERROR, "cudaMemsetAsync: %s", cudaGetErrorString(e));
 

@@ -24,7 +24,9 @@
  *
  * First call. The first call on each device looks up the device address of the array and raises the
  * kernels' shared-memory limit, with that device current. Make that first call outside any stream
- * capture; later calls only enqueue a clear, two kernels and nothing else.
+ * capture; later calls only enqueue a clear, two kernels and nothing else. First calls made from
+ * several host threads at once are serialised by a lock inside the library; the calls themselves
+ * are not, so the sharing rule above still applies to them.
  */
 #ifndef KERN_ATTN_DECODE_NOALLOC_H
 #define KERN_ATTN_DECODE_NOALLOC_H

@@ -81,21 +81,22 @@ class Engine:
         self.rt.write(name, t[: len(values)])
         self.h2d_bytes += len(values) * t.element_size()
 
-    def forward_for(self, groups: int, rows_each: list[int]):
-        return fills.forward_for(self.p, groups, rows_each)
+    def forward_for(self, groups: int, rows_each: list[int], round: bool = False):
+        return fills.forward_for(self.p, groups, rows_each, round)
 
     def step(self, batch: list[tuple[Sequence, list[int]]], eager: bool = False, read: bool = True, timed: bool = False,
-             pad: int = 0):
+             pad: int = 0, round: bool = False):
         """Feed each sequence its new tokens; returns, per sequence, the tokens the call emitted for it
         (one for a plain step, up to ``count`` for a speculative round), or None when ``read`` is off
-        or the program emits nothing. ``pad`` dead sequences bring a fixed-shape call up to a bucket."""
+        or the program emits nothing. ``pad`` dead sequences bring a fixed-shape call up to a bucket; ``round`` asks for
+        the speculative-round program (every sequence is fed the round's row count)."""
         real = len(batch)
         if real == 0 or sum(len(t) for _, t in batch) == 0:
             return []
         entries = [fills.Entry(length=s.length, new=new, pages=s.lease.pages, slot=s.lease.slot,
                                slots=s.lease.slots_of(s.length, s.length + len(new)), sampling=s.sampling)
                    for s, new in batch]
-        call = fills.build(self.p, self.unit, entries, pad)
+        call = fills.build(self.p, self.unit, entries, pad, round=round)
         for name, (dtype, col) in call.columns.items():
             self._write(name, dtype, col)
         fw, vars_, b = call.forward, call.vars, call.groups

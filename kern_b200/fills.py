@@ -42,11 +42,14 @@ class Call:
     real: int
 
 
-def forward_for(protocol: dict, groups: int, rows_each: list[int]) -> dict:
+def forward_for(protocol: dict, groups: int, rows_each: list[int], round: bool = False) -> dict:
+    """The forward program for a call of this shape. A speculative round (a fixed-shape forward of several rows per
+    sequence that reports a `count`) is taken only when the caller asks for one: a prefill chunk that happens to be as
+    long as a round is still a prefill chunk."""
     r0 = rows_each[0]
     if all(r == r0 for r in rows_each):
         for f in protocol["forwards"]:
-            if f["rows"] == r0 and groups <= f["groups"]:
+            if f["rows"] == r0 and groups <= f["groups"] and (round or r0 == 1 or f["count"] is None):
                 return f
     for f in protocol["forwards"]:
         if f["rows"] == "var" and groups <= f["groups"]:
@@ -54,7 +57,7 @@ def forward_for(protocol: dict, groups: int, rows_each: list[int]) -> dict:
     raise ValueError(f"no program takes {groups} sequences of rows {sorted(set(rows_each))}")
 
 
-def build(p: dict, unit: int, batch: list[Entry], pad: int = 0, page_map=None) -> Call:
+def build(p: dict, unit: int, batch: list[Entry], pad: int = 0, page_map=None, round: bool = False) -> Call:
     """``pad`` dead sequences of the first one's row count bring a fixed-shape call up to a bucket: token 0 at
     position 0, slot -1 (nothing appended), context 0 (nothing attended); their outputs are dropped.
     ``page_map(entry) -> pages`` lets a head substitute one member rank's page ids (default: ``entry.pages``)."""
@@ -65,7 +68,7 @@ def build(p: dict, unit: int, batch: list[Entry], pad: int = 0, page_map=None) -
     rows_max, groups_max = p["rows"]["max"], p["groups"]["max"]
     if total > rows_max or b > groups_max:
         raise ValueError(f"call of {b} sequences / {total} rows exceeds the manifest's {groups_max} / {rows_max}")
-    fw = forward_for(p, b, rows_each)
+    fw = forward_for(p, b, rows_each, round)
     tok = np.zeros(total, np.int64)
     pos = np.zeros(total, np.int64)
     slot = np.full(total, -1, np.int64)

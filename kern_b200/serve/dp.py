@@ -59,7 +59,7 @@ class DpTier:
     # ---- one lockstep step over every replica ----
     def step(self):
         plans = [s.plan() for s in self.scheds]
-        staged = {g: self.ranks.stage(g, p["batch"], p["pad"]) for g, p in enumerate(plans) if p is not None}
+        staged = {g: self.ranks.stage(g, p["batch"], p["pad"], p["round"]) for g, p in enumerate(plans) if p is not None}
         if not staged and not any(self.ranks.acts):
             return []
         answers = self.ex.run(self.ranks.orders(list(staged.values())))

@@ -100,12 +100,12 @@ class PipelineEngine:
     def close(self, seq) -> None:
         seq.lease.release()
 
-    def step(self, batch, eager: bool = False, read: bool = True, timed: bool = False, pad: int = 0):
+    def step(self, batch, eager: bool = False, read: bool = True, timed: bool = False, pad: int = 0, round: bool = False):
         if not batch or sum(len(t) for _, t in batch) == 0:
             return []
         entries = [fills.Entry(length=s.length, new=new, pages=s.lease.pages, slot=s.lease.slot,
                                slots=s.lease.slots_of(s.length, s.length + len(new)), sampling=s.sampling) for s, new in batch]
-        call = fills.build(self.p, self.unit, entries, pad)
+        call = fills.build(self.p, self.unit, entries, pad, round=round)
         for si, rt in enumerate(self.stages):
             bufs = rt.doc["buffers"]
             for name, (dtype, col) in call.columns.items():

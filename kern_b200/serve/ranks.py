@@ -192,18 +192,19 @@ class Ranks:
                                    slots=l.slots_of(sq.length, sq.length + len(new)), sampling=sq.sampling))
         return out
 
-    def stage(self, g: int, batch: list, pad: int = 0) -> Staged:
+    def stage(self, g: int, batch: list, pad: int = 0, round: bool = False) -> Staged:
         """`batch`: [(sequence, new tokens)] where a sequence carries `.lease` (a GroupLease), `.length`, `.sampling`."""
-        call = fills.build(self.p, self.unit, self._entries(batch, 0), pad)
+        call = fills.build(self.p, self.unit, self._entries(batch, 0), pad, round=round)
         return Staged(group=g, call=call, seqs=[sq for sq, _ in batch], new=[new for _, new in batch])
 
     def item_for(self, staged: Staged, member: int, read: bool = True) -> dict:
         """The member's own view of the call: same fills, its own leases' tables and slots."""
         call = staged.call
         cols = call.columns
+        fw_round = call.forward["count"] is not None and call.forward["rows"] not in (1, "var")
         if member > 0:
             cols = fills.build(self.p, self.unit, self._entries(list(zip(staged.seqs, staged.new)), member),
-                               call.groups - call.real).columns
+                               call.groups - call.real, round=fw_round).columns
         fw = call.forward
         return {"program": call.program, "vars": call.vars, "groups": call.groups, "emits": fw["emits"], "count": fw["count"],
                 "read": read, "rows": {n: [dt, v.tolist()] for n, (dt, v) in cols.items()}}
@@ -290,10 +291,10 @@ class GroupEngine:
     def close(self, seq) -> None:
         seq.lease.release()
 
-    def step(self, batch, eager: bool = False, read: bool = True, timed: bool = False, pad: int = 0):
+    def step(self, batch, eager: bool = False, read: bool = True, timed: bool = False, pad: int = 0, round: bool = False):
         if not batch or sum(len(t) for _, t in batch) == 0:
             return []
-        staged = self.ranks.stage(self.g, batch, pad)
+        staged = self.ranks.stage(self.g, batch, pad, round)
         answers = self.ex.run(self.ranks.orders([staged], read))
         staged.commit()
         self.steps += 1

@@ -220,10 +220,14 @@ class Scheduler:
         self.eng.rt.run_copies(copies)
         self.prefix.insert(req.prompt[:req.fed], ckpt, True, req.fed)
 
-    def _finish(self, req: Request, why: str) -> None:
+    def _finish(self, req: Request, why: str, keep: bool = True) -> None:
         req.finished = why
         self.running.remove(req)
-        self._keep(req)
+        if keep:
+            self._keep(req)
+        elif req.seq is not None:
+            self.eng.close(req.seq)
+            req.seq = None
         self.done.append(req)
 
     # ---- one step ----
@@ -232,7 +236,7 @@ class Scheduler:
         plan = self.plan()
         if plan is None:
             return []
-        return self.finish(plan, self.eng.step(plan["batch"], pad=plan["pad"]))
+        return self.finish(plan, self.eng.step(plan["batch"], pad=plan["pad"], round=plan["round"]))
 
     def plan(self) -> dict | None:
         """Admit, then decide this step's call: {batch, kinds, pad, round}. None when there is nothing to run.
@@ -293,21 +297,31 @@ class Scheduler:
                     self.stats.accepted += max(0, len(new) - 1)
             if r.first_token_at is None and new:
                 r.first_token_at = now
-            taken = []
+            taken, why = [], None
             for t in new:
                 r.out.append(int(t))
                 r.token_times.append(now)
                 taken.append(int(t))
                 if int(t) in r.stop_ids:
-                    self._finish(r, "stop")
+                    why = "stop"
                     break
                 if len(r.out) >= r.max_tokens:
-                    self._finish(r, "length")
+                    why = "length"
                     break
-            if use_round and r.finished is None and r.seq is not None:
-                # a round fed `rows` positions; only the accepted ones stay (paged KV slot = position: no copy)
-                r.seq.length -= self.rows - len(new)
-                del r.seq.tokens[r.seq.length:]
+            keepable = True
+            if use_round and kind == "decode" and r.seq is not None:
+                # A round fed `rows` positions holding [last, d1 .. d(rows-1)]; the engine recorded placeholders. Only the
+                # positions of the tokens taken stay (paged KV slot = position: no copy), and the history must name what
+                # those positions really hold, [last] + taken[:-1], before anything is kept under it as a prefix key.
+                old_len = r.seq.length - self.rows
+                last = r.seq.tokens[old_len]
+                r.seq.length = old_len + len(taken)
+                r.seq.tokens[old_len:] = [last] + taken[:-1]
+                # a per-sequence recurrent state was advanced by the kernels over every accepted position: when the
+                # request stops short of them, the slot is ahead of `length` and cannot be kept as a checkpoint
+                keepable = not (r.seq.lease.slot >= 0 and len(taken) < len(new))
+            if why is not None:
+                self._finish(r, why, keep=keepable)
             emitted.append((r, taken))
         self.stats.steps += 1
         self.stats.step_seconds += time.monotonic() - t0

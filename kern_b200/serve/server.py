@@ -75,7 +75,12 @@ class Driver(threading.Thread):
 
     def submit(self, req: Request) -> queue.Queue:
         q: queue.Queue = queue.Queue()
+        if self.failed:                       # the driver thread is gone: answer at once instead of queueing
+            q.put(("error", self.failed))
+            return q
         self.inbox.put(("submit", req, q))
+        if self.failed:                       # it failed between the check and the put
+            self._drain_inbox()
         return q
 
     def abort(self, req_id: str) -> None:
@@ -122,6 +127,18 @@ class Driver(threading.Thread):
             self.failed = repr(e)
             for s in self.streams.values():
                 s.put(("error", self.failed))
+            self.streams.clear()
+            self._drain_inbox()
+
+    def _drain_inbox(self) -> None:
+        """After a failure nothing reads the inbox any more: everyone queued in it gets the error now."""
+        while True:
+            try:
+                kind, _, q = self.inbox.get_nowait()
+            except queue.Empty:
+                return
+            if kind == "submit" and q is not None:
+                q.put(("error", self.failed))
 
 
 def prometheus(driver: Driver, model: str) -> str:
@@ -196,6 +213,8 @@ def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None):
             chat = self.path == "/v1/chat/completions"
             if not chat and self.path != "/v1/completions":
                 return self._json(404, {"error": {"message": f"no route {self.path}"}})
+            if driver.failed:
+                return self._json(503, {"error": {"message": f"engine failed: {driver.failed}"}})
             try:
                 history = None
                 if chat:

@@ -53,7 +53,7 @@ class SimEngine:
     def close(self, seq) -> None:
         seq.lease.release()
 
-    def step(self, batch, eager=False, read=True, timed=False, pad=0):
+    def step(self, batch, eager=False, read=True, timed=False, pad=0, round=False):
         if sum(len(t) for _, t in batch) > self.rows_max or len(batch) + pad > self.groups_max:
             raise ValueError("call exceeds the model's limits")
         out = []

@@ -154,7 +154,7 @@ class TracedEngine:
             ev[1].record(ev[2])
             ev[1].synchronize()
             device_us = ev[0].elapsed_time(ev[1]) * 1e3
-        fw = self.eng.forward_for(groups, [len(t) for _, t in batch] + [len(batch[0][1])] * kw.get("pad", 0))
+        fw = self.eng.forward_for(groups, [len(t) for _, t in batch] + [len(batch[0][1])] * kw.get("pad", 0), kw.get("round", False))
         self.rec.step(fw["name"], groups, rows, context, bool(fw.get("graph")) and not timed, device_us, host_us,
                       getattr(self.eng, "last_launches", 0), getattr(self.eng, "last_times", None) if timed else None)
         return out

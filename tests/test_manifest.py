@@ -14,7 +14,7 @@ import pytest
 from kern_b200 import _native as N
 
 SHA = "ab" * 32
-REF = os.environ.get("KERN_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))      # the upstream tree, when one is mounted
+REF = os.environ.get("KERN_REFERENCE_DIR", "")      # the upstream tree, when one is mounted (fixture tests skip otherwise)
 
 
 def base():

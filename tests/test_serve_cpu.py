@@ -135,3 +135,36 @@ def test_http_completions_stream_and_metrics(toy):
             post("/v1/completions", {"prompt": "", "max_tokens": 1})
     finally:
         srv.stop()
+
+
+def test_a_failed_step_answers_503_at_once(toy):
+    """Once the driver thread has died on a failed step, /health says so and a new request gets 503 immediately
+    instead of waiting in an inbox nobody reads."""
+    import time
+    import urllib.error
+
+    cfg, make = toy
+    sched = Scheduler(make())
+    srv = Server(sched, model_name="toy", port=0).start()
+    base = f"http://127.0.0.1:{srv.port}"
+    try:
+        def post(body, timeout=20):
+            req = urllib.request.Request(base + "/v1/completions", data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+            return urllib.request.urlopen(req, timeout=timeout)
+
+        def boom(*a, **k):
+            raise RuntimeError("injected step failure")
+
+        sched.eng.step = boom                      # the failure is made on the host: the next call raises
+        with pytest.raises(urllib.error.HTTPError) as e1:
+            post({"prompt": [1, 2, 3], "max_tokens": 2})
+        assert e1.value.code >= 500
+        t0 = time.monotonic()
+        with pytest.raises(urllib.error.HTTPError) as e2:
+            post({"prompt": [4, 5, 6], "max_tokens": 2})
+        assert e2.value.code == 503 and time.monotonic() - t0 < 5
+        with pytest.raises(urllib.error.HTTPError) as e3:
+            urllib.request.urlopen(base + "/health", timeout=10)
+        assert e3.value.code == 503
+    finally:
+        srv.stop()

@@ -27,6 +27,5 @@ def test_the_simulator_notices_a_wrong_page():
     eng.mem[b.lease.pages[0]] = dict(eng.mem[a.lease.pages[0]])        # the bug: b's first page now holds a's tokens
     got = eng.step([(b, [5])])[0][0]
     from kern_b200.models import toy_int
-    assert got != toy_int.generate(list(range(100, 120)) + [5], 1)[0:1] or True
     want = toy_int.next_of(sum(toy_int.slot_sum(t, p) for p, t in enumerate(list(range(100, 120)) + [5])) & toy_int.M)
     assert got != want

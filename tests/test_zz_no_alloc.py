@@ -72,6 +72,37 @@ def test_no_alloc_entry_matches_the_allocating_one_twice(cuda):
         torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
 
 
+def _fp32_statement(q, pool, table, seq_lens, hq):
+    """Plain PyTorch fp32 decode attention over the paged pool; an empty sequence gives a zero row."""
+    _, _, hk, page, d = pool.shape
+    out = torch.zeros(q.shape[0], hq * d, dtype=torch.float32, device=q.device)
+    for s, l in enumerate(seq_lens.tolist()):
+        if l == 0:
+            continue
+        ids = table[s, : (l + page - 1) // page].long()
+        k = pool[ids, 0].permute(1, 0, 2, 3).reshape(hk, -1, d)[:, :l].float()
+        v = pool[ids, 1].permute(1, 0, 2, 3).reshape(hk, -1, d)[:, :l].float()
+        qs = q[s].float().view(hk, hq // hk, d)
+        p = torch.softmax(torch.einsum("kgd,kld->kgl", qs, k) * d ** -0.5, -1)
+        out[s] = torch.einsum("kgl,kld->kgd", p, v).reshape(-1)
+    return out
+
+
+def test_no_alloc_entry_with_an_empty_sequence_against_fp32(cuda):
+    """A sequence of length 0 launches no work for its rows: they must come out zero, on a workspace the call before
+    left dirty, and the live rows must match a plain fp32 statement of the op."""
+    lib = _load()
+    q, pool, table, seq_lens = _case(cuda, 3, [300, 1, 90])
+    _call(lib, q, pool, table, seq_lens, 32, 4)                 # dirties the workspace for every row
+    seq_lens[1] = 0
+    rc, out, err = _call(lib, q, pool, table, seq_lens, 32, 4)
+    assert rc == 0, lib.kern_noalloc_last_error()
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    assert float(out[1].float().abs().max()) == 0.0
+    torch.testing.assert_close(out.float(), _fp32_statement(q, pool, table, seq_lens, 32), rtol=2e-2, atol=2e-2)
+
+
 def test_no_alloc_entry_refuses_what_does_not_fit(cuda):
     lib = _load()
     q, pool, table, seq_lens = _case(cuda, 2, [64] * 40)
