@@ -1,22 +1,28 @@
-"""Headline benchmark: output tokens/s of the serving engine at fixed concurrency, dense GQA 8B-class
-decoder (36 layers, hidden 4096, 32 Q / 8 KV heads of 128, SwiGLU 12288, vocab 151936, bf16 random
-init), 256 concurrent requests with prompts of 512-4096 uniform-random token ids and 256 greedy
-output tokens each.
+"""Headline benchmark: output tokens/s of the serving engine at fixed concurrency.
 
-A step is one iteration of the engine in steady state at that concurrency: every one of the 256
-sequences produces a token — one request has just finished and its replacement's whole prompt is
-prefilled in the same call as the 255 decode rows (ragged batch through the manifest's `prefill`
-program). Inputs of each step are written from pinned host memory and the step's tokens are read back
-to the host, through the package's public API (kern_b200.Runtime + kern_b200.Engine).
+Config (b), the default: dense GQA 8B-class decoder (36 layers, hidden 4096, 32 Q / 8 KV heads of 128, SwiGLU 12288,
+vocab 151936, bf16 random init), 256 concurrent requests with prompts of 512-4096 uniform-random token ids and 256
+greedy output tokens each; N GPUs = tensor parallel over N ranks (sequence-parallel prefill rows, fused
+GEMM + reduce-scatter and all-gather + GEMM kernels over NVLink peer memory).
 
-    python bench.py --gpus 1 --steps 16 --warmup 3
-    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+The timed loop is the serving loop a user of the package runs: `kern_b200.serve.scheduler.Scheduler.step()` over a
+`kern_b200.Engine` over a `kern_b200.Runtime` — admission, leases, prefix cache bookkeeping, bucketing, chunk budget,
+the host-to-device copy of the step's inputs from pinned memory and the device-to-host read of its tokens are all
+inside it. The system is held in steady state: 256 requests are live at staggered ages, so in every step one request
+finishes and its replacement (submitted the moment the slot frees) is admitted and its whole prompt prefilled in the same
+call as the other 255 requests' decode rows; every live sequence emits one token per step.
 
-Prints one JSON line (rank 0). `--impl reference` reports why the reference cannot run here.
+    python bench.py [--gpus 1] [--steps 256] [--warmup 3] [--config b]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+
+Prints one JSON line (rank 0). TTFT of a request = host clock from its submission to its first token being on the host;
+TPOT = gap between consecutive tokens of a request (both p50 over the requests / tokens of the timed region).
+`--impl reference` runs what of the reference can run on this machine (see baseline/README.md) or says why not.
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import subprocess
@@ -27,6 +33,7 @@ import time
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 PUBLISHED_TOK_S = None   # the reference publishes no B200 number for this config (BASELINE.json `published` is empty)
+METRIC = "output tok/s per box at fixed concurrency; p50 TTFT & TPOT"
 
 
 def clocks_sampler(gpu: int, stop: threading.Event, out: list):
@@ -57,37 +64,49 @@ def summarize_clocks(samples):
             "reasons": sorted(reasons)}
 
 
+def pct(sorted_vals, q):
+    if not sorted_vals:
+        return None
+    return sorted_vals[min(len(sorted_vals) - 1, int(q * len(sorted_vals)))]
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--steps", type=int, default=256, help="timed steps (256 = every live sequence turns over once)")
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="b", choices=["b", "toy"],
+                    help="b: dense GQA 8B-class at concurrency 256 (the headline); toy: the reference's own toy-paged package "
+                         "(its manifest and cubin) served by this engine, the workload of the reference arm")
     ap.add_argument("--concurrency", type=int, default=256)
     ap.add_argument("--layers", type=int, default=36, help="for quick functional checks only; the headline is 36")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--parallelism", default="dp", choices=["tp", "dp"],
-                    help="N > 1: data-parallel replicas, the concurrency split between them (default: the higher "
-                         "tok/s per box for a model that fits one GPU), or tensor parallel over one replicated batch "
-                         "(lower latency per token)")
-    ap.add_argument("--tp-unfused", action="store_true",
-                    help="tensor parallel without the GEMM + reduce-scatter fusion (the all-reduce kernel pushes the partials "
-                         "instead of the GEMM epilogue; A/B)")
+    ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"],
+                    help="N > 1: tensor parallel over one batch (the configuration the metric names; default), or "
+                         "data-parallel replicas with the concurrency split between them (reported for comparison only)")
+    ap.add_argument("--tp-layout", default="sp", choices=["sp", "fused", "unfused"],
+                    help="tensor-parallel ragged program: sequence-parallel rows with GEMM + reduce-scatter and all-gather + GEMM "
+                         "kernels (default); replicated rows with the GEMM epilogue pushing partials to the all-reduce; or "
+                         "replicated rows with a plain GEMM and the all-reduce kernel pushing them (A/B)")
     ap.add_argument("--profile", action="store_true", help="after the timed region, run one more step with per-call timing and print the cost by op to stderr")
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a Rust workspace (maturin wheel) and no Rust toolchain is installed; its kernels are "
-                          "prebuilt sm_103a cubins fetched from Hugging Face, which this box cannot reach"}))
-        return 0
+        from baseline import reference_arm
 
+        return reference_arm.main(args)
+    if args.config == "toy":
+        from kern_b200.testing import bench_toy
+
+        return bench_toy.main(args)
     import numpy as np
     import torch
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")      # NCCL only carries the handshake and the final max over ranks
     if world > 1:
         import torch.distributed as dist
         torch.cuda.set_device(local)
@@ -97,19 +116,20 @@ def main():
     from kern_b200.engine import Engine
     from kern_b200.models import dense
     from kern_b200.runtime import Runtime
+    from kern_b200.serve.scheduler import Request, Scheduler
 
     tp = world > 1 and args.parallelism == "tp"
     # tensor parallel: every rank is fed the whole batch; data parallel: replicas split the concurrent requests
-    conc = args.concurrency if tp else args.concurrency // world
+    conc = args.concurrency if (tp or world == 1) else args.concurrency // world
     out_len, p_lo, p_hi = 256, 512, 4096
     cfg = dense.DenseConfig(name="dense-8b", layers=args.layers, max_seqs=max(conc, 8), max_tokens=p_hi + conc + 64,
-                            max_context=p_hi + out_len + 64, page_size=64, tp=world if tp else 1)
+                            max_context=p_hi + 2 * out_len + 64, page_size=64, tp=world if tp else 1)
     torch.cuda.set_device(local)
     if tp:
         from kern_b200.models import dense_tp
         from kern_b200.parallel import group
 
-        doc = dense_tp.build_manifest_tp(cfg, fused=not args.tp_unfused)
+        doc = dense_tp.build_manifest_tp(cfg, fused=args.tp_layout != "unfused", sp=args.tp_layout == "sp")
         rt = Runtime(doc, gpu=local, memory_fraction=0.90, topology=group.topology(doc["topology"]["groups"], rank, world))
         dense.load_random_weights(rt, cfg, seed=args.seed)
         group.start(rt)
@@ -118,63 +138,44 @@ def main():
         dense.load_random_weights(rt, cfg, seed=args.seed)
         rt.once()
     eng = Engine(rt)
+    sch = Scheduler(eng, chunk=eng.rows_max, max_seqs=conc, prefix_cache=True, stats_every=1e9)
     rng = np.random.default_rng(args.seed + (0 if tp else rank))   # tensor-parallel ranks replay the same requests
+    issued = [0]
 
-    def new_prompt():
-        return rng.integers(0, cfg.vocab, int(rng.integers(p_lo, p_hi + 1))).tolist()
+    def new_request(max_tokens: int) -> Request:
+        issued[0] += 1
+        prompt = rng.integers(0, cfg.vocab, int(rng.integers(p_lo, p_hi + 1))).tolist()
+        return Request(id=f"r{issued[0]}", prompt=prompt, max_tokens=max_tokens)
 
-    # ---- bring the engine to steady state: `conc` live sequences at staggered ages ----
-    seqs, last = [], []
+    # ---- bring the engine to steady state (untimed): `conc` live requests whose remaining lengths are 1..conc ----
     t0 = time.perf_counter()
-    prefill_tokens = 0
-    pending = []
-    start_ages = rng.permutation([(i * out_len) // conc for i in range(conc)])   # evenly spread: steady state
-    for i in range(conc):
-        p = new_prompt()
-        s = eng.open(len(p) + out_len + 8)
-        s.age = int(start_ages[i])                 # tokens it has produced so far in its life
-        pending.append((s, p))
-        if sum(len(q) for _, q in pending) + p_hi > cfg.max_tokens - conc or i == conc - 1:
-            toks = eng.step(pending)
-            prefill_tokens += sum(len(q) for _, q in pending)
-            for (s2, _), t in zip(pending, toks):
-                seqs.append(s2)
-                last.append(t[0])
-            pending = []
+    first = [new_request(2 * out_len) for _ in range(conc)]     # room in the lease for the tokens made while the others prefill
+    for r in first:
+        sch.submit(r)
+    prefill_tokens = sum(len(r.prompt) for r in first)
+    while any(r.fed < len(r.prompt) for r in first):
+        sch.step()
     rt.synchronize()
     prefill_s = time.perf_counter() - t0
-    # advance every sequence by its age so contexts look like a running server's
-    ages = [s.age for s in seqs]
-    for k in range(max(ages) if ages else 0):
-        live = [(s, [last[i]]) for i, s in enumerate(seqs) if k < ages[i]]
-        if not live:
-            break
-        # (decode program; untimed)
-        idx = [i for i, s in enumerate(seqs) if k < ages[i]]
-        toks = eng.step(live, eager=True)     # every batch size once: not worth a graph each
-        for i, t in zip(idx, toks):
-            last[i] = t[0]
+    remaining = rng.permutation(conc) + 1                        # one request ends in every step from here on
+    for r, left in zip(first, remaining):
+        r.max_tokens = len(r.out) + max(1, int(left) * out_len // conc)
     rt.check_error()
 
-    def one_step(timed=False):
-        # requests that have produced all their tokens finish; new ones take their places and are prefilled in
-        # the same call as everyone else's decode rows
-        fresh, rows = {}, 0
-        for j in range(conc):
-            if seqs[j].age >= out_len:
-                eng.close(seqs[j])
-                p = new_prompt()
-                s = eng.open(len(p) + out_len + 8)
-                s.age = 0
-                seqs[j] = s
-                fresh[j] = p
-                rows += len(p)
-        batch = [(seqs[i], fresh.get(i) or [last[i]]) for i in range(conc)]
-        toks = eng.step(batch, timed=timed)
-        for i, t in enumerate(toks):
-            last[i] = t[0]
-            seqs[i].age += 1
-        return rows
+    live = {r.id: r for r in first}
+    finished_in_region: list[Request] = []
+
+    def one_step() -> int:
+        """One scheduler step; every request that ends is replaced at once (closed loop). Returns the prompt rows fed."""
+        before = sch.stats.prefill_tokens
+        for r, _ in sch.step():
+            if r.finished:
+                live.pop(r.id, None)
+                finished_in_region.append(r)
+                nr = new_request(out_len)
+                live[nr.id] = nr
+                sch.submit(nr)
+        return sch.stats.prefill_tokens - before
 
     for _ in range(warmup):
         one_step()
@@ -190,6 +191,8 @@ def main():
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     h2d0, d2h0, launches = eng.h2d_bytes, eng.d2h_bytes, 0
     prompt_rows = 0
+    finished_in_region.clear()
+    region_t0 = time.monotonic()
     wall0 = time.perf_counter()
     evs[0].record(stream)
     for k in range(steps):
@@ -199,6 +202,7 @@ def main():
     rt.synchronize()
     torch.cuda.synchronize()
     wall = time.perf_counter() - wall0
+    region_t1 = time.monotonic()
     stop.set()
     th.join(timeout=2)
     if world > 1:
@@ -206,40 +210,60 @@ def main():
     step_ms = [evs[k].elapsed_time(evs[k + 1]) for k in range(steps)]
     dev_s = sum(step_ms) / 1e3
     rt.check_error()
-    if args.profile and rank == 0:
-        rows = one_step(timed=True)
+    if args.profile:          # every rank runs the extra step (the ranks wait for one another); rank 0 prints
+        eng_step = eng.step
+        eng.step = lambda batch, **kw: eng_step(batch, timed=True, **{k: v for k, v in kw.items() if k != "timed"})
+        rows = one_step()
+        eng.step = eng_step
         by_op = {}
         for label, op, ms, n in eng.last_times:
             e = by_op.setdefault(op, [0.0, 0, 0])
             e[0] += ms; e[1] += n; e[2] += 1
         total = sum(v[0] for v in by_op.values())
-        print(f"# cost by op of one step ({rows} prompt rows + {conc} decode rows), eager, total {total:.2f} ms", file=sys.stderr)
-        for op, (ms, n, calls) in sorted(by_op.items(), key=lambda kv: -kv[1][0]):
-            print(f"#   {op:14s} {ms:8.3f} ms  {100 * ms / total:5.1f}%  calls {calls:4d}  launches {n}", file=sys.stderr)
+        if rank == 0:
+            print(f"# cost by op of one step ({rows} prompt rows + {conc} decode rows), eager, total {total:.2f} ms", file=sys.stderr)
+            for op, (ms, n, calls) in sorted(by_op.items(), key=lambda kv: -kv[1][0]):
+                print(f"#   {op:14s} {ms:8.3f} ms  {100 * ms / total:5.1f}%  calls {calls:4d}  launches {n}", file=sys.stderr)
+
+    # per-request latencies of the timed region (host clock: they include the copies both ways and the scheduler)
+    reqs = list(live.values()) + finished_in_region
+    ttft = sorted(1e3 * (r.first_token_at - r.arrival) for r in reqs
+                  if r.first_token_at is not None and region_t0 <= r.arrival and r.first_token_at <= region_t1)
+    gaps = sorted(1e3 * (b - a) for r in reqs for a, b in zip(r.token_times, r.token_times[1:]) if a >= region_t0 and b <= region_t1)
 
     if world > 1:
         t = torch.tensor([dev_s, wall], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_s, wall = float(t[0]), float(t[1])
-    total_tokens = conc * (1 if tp else world) * steps
+    replicas = 1 if (tp or world == 1) else world
+    total_tokens = conc * replicas * steps
     value = total_tokens / dev_s
     e2e = total_tokens / wall
     if rank == 0:
         sm = sorted(step_ms)
         line = {
-            "metric": "output tok/s per box at fixed concurrency; p50 TTFT & TPOT", "value": round(value, 1), "unit": "tok/s",
+            "metric": METRIC, "value": round(value, 1), "unit": "tok/s",
             "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": round(dev_s / steps * 1e3, 3),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": (value / PUBLISHED_TOK_S) if PUBLISHED_TOK_S else None,
             "dtype": "bf16", "data": "synthetic (uniform-random token ids, random-init N(0,0.02) bf16 weights)",
             "config": {"model": "dense GQA 8B-class: 36L hidden 4096 32Q/8KV hd128 SwiGLU 12288 vocab 151936"
                        if args.layers == 36 else f"REDUCED {args.layers}-layer functional check (not a headline number)",
-                       "global_batch": conc * (1 if tp else world), "seq_len": f"prompts {p_lo}-{p_hi} uniform, {out_len} outputs",
+                       "global_batch": conc * replicas, "seq_len": f"prompts {p_lo}-{p_hi} uniform, {out_len} outputs",
                        "parallelism": (f"tp{world}" if tp else f"dp{world}") if world > 1 else "tp1",
-                       "step": "steady-state engine iteration: 1 finished request replaced (whole prompt prefilled) + decode rows, every live sequence emits a token",
+                       "tp_layout": args.tp_layout if tp else None,
+                       "step": "steady-state scheduler step: 1 finished request replaced (whole prompt prefilled) + decode rows, every live sequence emits a token",
                        "l2": "inputs larger than L2 (weights 15 GB + paged KV of all live sequences read every step)",
                        "mean_prompt_rows_per_step": round(prompt_rows / steps, 1)},
-            "tpot_ms_p50": round(sm[len(sm) // 2], 3), "ttft_ms_p50": round(sm[len(sm) // 2], 3),
-            "ttft_note": "a new request's prompt is prefilled inside the step it is admitted in, so its first token arrives one step after admission",
+            "step_ms": {"p10": round(pct(sm, 0.10), 3), "p50": round(pct(sm, 0.50), 3), "p90": round(pct(sm, 0.90), 3),
+                        "min": round(sm[0], 3), "max": round(sm[-1], 3),
+                        "sha1": hashlib.sha1(",".join(f"{x:.3f}" for x in step_ms).encode()).hexdigest()[:16],
+                        "first": [round(x, 3) for x in step_ms[:8]]},
+            "ttft_ms_p50": round(pct(ttft, 0.5), 3) if ttft else None, "ttft_ms_p90": round(pct(ttft, 0.9), 3) if ttft else None,
+            "ttft_requests": len(ttft),
+            "tpot_ms_p50": round(pct(gaps, 0.5), 3) if gaps else None, "tpot_ms_p90": round(pct(gaps, 0.9), 3) if gaps else None,
+            "latency_note": "TTFT: submission (the moment a slot frees) to first token on the host; TPOT: gap between a request's "
+                            "consecutive tokens on the host; rank 0's clock",
+            "timed_region_s": round(wall, 3),
             "prefill_tok_s_warmup_wallclock": round(prefill_tokens / prefill_s, 1),
             "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": (eng.h2d_bytes - h2d0) // steps,
                     "d2h_bytes_per_step": (eng.d2h_bytes - d2h0) // steps},

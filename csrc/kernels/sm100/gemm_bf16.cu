@@ -47,9 +47,15 @@ struct GemmCfg {
 // EPI 4 (tensor-parallel partial sums): instead of storing C, every row of the tile is pushed over NVLink into the
 // staging slot of the rank that will reduce it (the row dealing of the fused all-reduce kernel: row = j + i G,
 // owner = (i + j) % nranks, dense index (i / nranks) G + j, parity from that kernel's epoch of column j).
+//
+// Sequence-parallel form (grid == 0): rows are owned in sub-blocks of kSpRows, sub-block s by rank s % nranks at dense
+// index (s / nranks) kSpRows + row % kSpRows; the parity comes from the one epoch word of kern_sp_reduce_norm, which
+// reduces the owner's rows only (a reduce-scatter: nothing is sent back). An epilogue warp's 32 rows are one sub-block,
+// so they land as 32 consecutive rows of one owner's slot.
+constexpr int kSpRows = 32;
 struct ScatterArgs {
   const unsigned long long* comm_peers = nullptr;   // every rank's staging buffer, mapped here
-  const uint32_t* epochs = nullptr;                 // the all-reduce kernel's per-column epochs (read only)
+  const uint32_t* epochs = nullptr;                 // the reducing kernel's epochs (read only)
   int rank = 0, nranks = 1, grid = 1, slot_rows = 0;
 };
 
@@ -63,11 +69,23 @@ struct ScatterArgs {
 // nothing is reset and captured graphs replay; the grid size must therefore be the same in every launch.
 KERN_DEVICE int num_m_of(int M, int nranks) { return (M / nranks + BM - 1) / BM; }
 
+//
+// Sequence-parallel form (`ready` set): G's rows are owned in sub-blocks of kSpRows (sub-block s by rank s % nranks, the
+// layout kern_sp_reduce_norm leaves), so every 128-row block holds rows of up to four owners and none is local: the
+// gather warps first wait (bounded) until every peer's `ready` word has reached this rank's own epoch, i.e. the peer's
+// rows of this call are final, then pull each block's foreign rows in block order while the tiles of the blocks
+// already here run. No barrier kernel before or after: the reduce kernel of the next call lines the ranks up again
+// before anyone rewrites a row.
+constexpr int kGatherWarps = 4;
+constexpr int kAgWindow = 8;     // 128-row blocks per window of the tile order
 struct AgArgs {
   const unsigned long long* peers = nullptr;   // G of every rank, mapped here (this rank's own included)
   uint32_t* flags = nullptr;                   // [max_blocks] arrival counters (local)
   uint32_t* epochs = nullptr;                  // [grid] launches seen by each CTA (local)
   int rank = 0, nranks = 1, max_blocks = 0;
+  const uint32_t* ready = nullptr;             // sequence-parallel: [nranks] epochs at which each rank's rows were final
+  const uint32_t* epoch_word = nullptr;        //   and this rank's own epoch
+  long long timeout_ns = 2000000000ll;
 };
 
 // GROUPED: the M tiles come from a device table of int4 {expert, first row, rows (<= BM), -} built by the MoE
@@ -133,7 +151,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
   const int num_tiles = num_m * num_n;
   // tile t -> (first row, row bound, n block, expert)
   // AG: blocks per rank, this rank's first block, and the counter value that says "every CTA's share of the block is in"
-  const int ag_bpr = AG ? num_m_of(M, ag.nranks) : 0;
+  const int ag_bpr = AG ? (ag.ready != nullptr ? 0 : num_m_of(M, ag.nranks)) : 0;
+  // the block this rank's tile order and pulls start from: its own rows (contiguous slices), or a rank-dependent
+  // offset so that the ranks pull from different owners at any one time (sequence-parallel sub-blocks)
+  const int ag_first = AG ? (ag_bpr ? ag.rank * ag_bpr : (int)(((long long)ag.rank * num_m) / ag.nranks)) : 0;
   uint32_t ag_want = 0;
   if constexpr (AG) {
     ag_want = (ag.epochs[blockIdx.x] + 1u) * gridDim.x;
@@ -142,9 +163,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
   auto tile_of = [&](int t, int& row0, int& row_end, int& n_blk, int& expert) {
     int mt = t % num_m;
     n_blk = t / num_m;
-    if constexpr (AG) {      // n fast inside a block of rows, this rank's own blocks first
-      mt = (t / num_n + ag.rank * ag_bpr) % num_m;
-      n_blk = t % num_n;
+    if constexpr (AG) {
+      // Blocks in the order they arrive (this rank's first block first), kAgWindow of them at a time with the row
+      // blocks fastest inside a window: CTAs that run together then share a few W tiles through L2 (with the columns
+      // fastest every wave would stream the whole of W), and no tile waits for a block far down the pull order.
+      const int per_win = kAgWindow * num_n;
+      const int w = t / per_win, r = t - w * per_win;
+      const int m0 = w * kAgWindow, wm = min(kAgWindow, num_m - m0);
+      mt = (m0 + r % wm + ag_first) % num_m;
+      n_blk = r / wm;
     }
     if constexpr (GROUPED) {
       const int4 e = reinterpret_cast<const int4*>(tile_table)[mt];
@@ -165,14 +192,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         tile_of(t, row0, row_end, n_blk, expert);
         if constexpr (AG) {
           const int blk = row0 / BM;
-          if (blk / ag_bpr != ag.rank) {       // a peer's rows: wait until every CTA has put its share of the block here
+          if (ag_bpr == 0 || blk / ag_bpr != ag.rank) {       // a peer's rows: wait until every CTA has put its share of the block here
             bool here = false;
             for (uint32_t i = 0; i < (1u << 22) && !here; ++i) {
               here = ld_acquire_sys(ag.flags + blk) >= ag_want;
               if (!here) { if ((i & 0xff) == 0xff && *abort_flag != 0) break; __nanosleep(100); }
             }
             if (!here) {
-              set_error(err, ERR_WAIT_PEER + blk / ag_bpr);
+              set_error(err, ERR_WAIT_PEER + (ag_bpr ? blk / ag_bpr : ag.nranks));
               *abort_flag = 1;
               break;
             }
@@ -254,55 +281,99 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
     }
     __syncwarp();
   } else if (warp >= 6) {
-    // ---------------- gather warps 6..7 (AG only): pull the peers' rows into this rank's G ----------------
+    // ---------------- gather warps 6.. (AG only): pull the peers' rows into this rank's G ----------------
     if constexpr (AG) {
-      const int gt = threadIdx.x - 192;                      // 0..63
+      constexpr int GT = kGatherWarps * 32;
+      const int gt = threadIdx.x - 192;                      // 0..GT-1
       uint8_t* mine = reinterpret_cast<uint8_t*>(ag.peers[ag.rank]);
+      const bool sp = ag.ready != nullptr;
+      if (sp) {
+        // every peer's rows of this call are final once its `ready` word has reached this rank's own epoch
+        const uint32_t e = *reinterpret_cast<const volatile uint32_t*>(ag.epoch_word);
+        if (gt < ag.nranks && gt != ag.rank) {
+          const uint64_t t0 = globaltimer_ns();
+          while ((int32_t)(ld_acquire_sys(ag.ready + gt) - e) < 0) {
+            if (*abort_flag != 0) break;
+            if ((long long)(globaltimer_ns() - t0) > ag.timeout_ns) {
+              set_error(err, ERR_WAIT_PEER + gt);
+              *abort_flag = 1;
+              break;
+            }
+            __nanosleep(40);
+          }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(GT) : "memory");
+      }
       // blocks nobody gathers in this launch (own rows, blocks past the last row) arrive at once: every counter moves
       // by the grid size in every launch, whatever the row count
-      for (int b = gt; b < ag.max_blocks; b += 64) {
-        const bool remote = b < num_m && b / ag_bpr != ag.rank;
+      for (int b = gt; b < ag.max_blocks; b += GT) {
+        const bool remote = b < num_m && (sp || b / ag_bpr != ag.rank);
         if (!remote) atomicAdd(ag.flags + b, 1u);
       }
-      // The peers' blocks in the order the tiles will want them, cut into units of eight 16-byte vectors per thread.
-      // The loads of unit u + 1 are issued before the stores of unit u: a peer load takes a couple of microseconds,
-      // and one at a time (or one block at a time) the round trips would add up to the whole transfer.
-      const size_t vecs = (size_t)BM * K * 2 / 16, stride = (size_t)gridDim.x * 64, span = stride * 8;
-      const int nb = (int)((vecs + span - 1) / span);                    // units per block
-      const int units = (num_m - ag_bpr) * nb;
-      auto block_of = [&](int u) { return (ag_bpr + u / nb + ag.rank * ag_bpr) % num_m; };
-      auto load = [&](int u, uint4 (&x)[8]) {
-        const int b = block_of(u);
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(ag.peers[b / ag_bpr]) + (size_t)b * BM * K * 2;
-        const size_t v0 = (size_t)(u % nb) * span + (size_t)blockIdx.x * 64 + gt;
+      // The blocks to pull, in the order the tiles will want them, form one run of 16-byte vectors that is cut into units
+      // of eight vectors per thread over the whole grid (a unit usually spans two or three blocks). The loads of unit
+      // u + 1 are issued before the stores of unit u, so a thread keeps up to sixteen peer loads in flight: a peer load
+      // takes a few microseconds, and the link is only busy while about latency x bandwidth bytes are outstanding.
+      // A block's counter moves once every unit that touches the block has been stored.
+      const size_t row_vecs = (size_t)K * 2 / 16;
+      const size_t vecs = (size_t)BM * row_vecs, stride = (size_t)gridDim.x * GT, span = stride * 8;
+      const int pull_blocks = sp ? num_m : num_m - ag_bpr;
+      const size_t total = (size_t)pull_blocks * vecs;
+      const int units = (*abort_flag != 0) ? 0 : (int)((total + span - 1) / span);
+      auto block_at = [&](int i) { return ((sp ? 0 : ag_bpr) + i + ag_first) % num_m; };   // i-th block in pull order
+      // where vector v of block b comes from (null: it is this rank's own, or past the last row)
+      auto source = [&](int b, size_t v) -> const uint8_t* {
+        if (!sp) return reinterpret_cast<const uint8_t*>(ag.peers[b / ag_bpr]) + (size_t)b * BM * K * 2 + v * 16;
+        const int row = b * BM + (int)(v / row_vecs);
+        const int owner = (row / kSpRows) % ag.nranks;
+        if (row >= M || owner == ag.rank) return nullptr;
+        return reinterpret_cast<const uint8_t*>(ag.peers[owner]) + (size_t)b * BM * K * 2 + v * 16;
+      };
+      auto load = [&](int u, uint4 (&x)[8], uint32_t& have) {
+        const size_t l0 = (size_t)u * span + (size_t)blockIdx.x * GT + gt;
+        have = 0;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-          const size_t v = v0 + q * stride;
-          if (v < vecs)
-            asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(x[q].x), "=r"(x[q].y), "=r"(x[q].z), "=r"(x[q].w) : "l"(src + v * 16));
+          const size_t l = l0 + q * stride;
+          if (l < total) {
+            const int i = (int)(l / vecs);
+            const uint8_t* src = source(block_at(i), l - (size_t)i * vecs);
+            if (src != nullptr) {
+              have |= 1u << q;
+              asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(x[q].x), "=r"(x[q].y), "=r"(x[q].z), "=r"(x[q].w) : "l"(src));
+            }
+          }
         }
       };
       uint4 xa[8], xb[8];
-      if (units > 0) load(0, xa);
+      uint32_t ha = 0, hb = 0;
+      int signalled = 0;                                                   // blocks (in pull order) whose counter has moved
+      if (units > 0) load(0, xa, ha);
       for (int u = 0; u < units; ++u) {
-        if (u + 1 < units) load(u + 1, xb);
-        const int b = block_of(u);
-        uint8_t* dst = mine + (size_t)b * BM * K * 2;
-        const size_t v0 = (size_t)(u % nb) * span + (size_t)blockIdx.x * 64 + gt;
+        if (u + 1 < units) load(u + 1, xb, hb);
+        const size_t l0 = (size_t)u * span + (size_t)blockIdx.x * GT + gt;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-          const size_t v = v0 + q * stride;
-          if (v < vecs) *reinterpret_cast<uint4*>(dst + v * 16) = xa[q];
+          if (ha & (1u << q)) {
+            const size_t l = l0 + q * stride;
+            const int i = (int)(l / vecs);
+            *reinterpret_cast<uint4*>(mine + (size_t)block_at(i) * BM * K * 2 + (l - (size_t)i * vecs) * 16) = xa[q];
+          }
         }
-        if (u % nb == nb - 1) {                                          // this CTA's share of block b is in place
+        const size_t covered = (size_t)(u + 1) * span;
+        const int complete = covered >= total ? pull_blocks : (int)(covered / vecs);
+        if (complete > signalled) {                                        // this CTA's share of these blocks is in place
           __threadfence();
           asm volatile("fence.proxy.async;" ::: "memory");
-          asm volatile("bar.sync 1, 64;" ::: "memory");                  // both gather warps are done with it
-          if (gt == 0) atomicAdd(ag.flags + b, 1u);
+          asm volatile("bar.sync 1, %0;" ::"n"(GT) : "memory");          // all gather warps are done with them
+          if (gt == 0)
+            for (int i = signalled; i < complete; ++i) atomicAdd(ag.flags + block_at(i), 1u);
+          signalled = complete;
         }
 #pragma unroll
         for (int q = 0; q < 8; ++q) xa[q] = xb[q];
+        ha = hb;
       }
       if (gt == 0) ag.epochs[blockIdx.x] = ag_want / gridDim.x;
     }
@@ -360,8 +431,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         {
           unsigned long long dst = 0;
           if (row < row_end) {
-            const int j = row % sc.grid, i = row / sc.grid;
-            const int owner = (i + j) % sc.nranks, idx = (i / sc.nranks) * sc.grid + j;
+            int j, owner, idx;
+            if (sc.grid == 0) {          // sequence-parallel: sub-blocks of kSpRows rows, one epoch word
+              const int sb = row / kSpRows;
+              j = 0; owner = sb % sc.nranks; idx = (sb / sc.nranks) * kSpRows + row % kSpRows;
+            } else {
+              j = row % sc.grid;
+              const int i = row / sc.grid;
+              owner = (i + j) % sc.nranks; idx = (i / sc.nranks) * sc.grid + j;
+            }
             if (idx >= sc.slot_rows) {
               set_error(err, ERR_BOUNDS);
             } else {

@@ -55,6 +55,8 @@ class Engine:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.steps = 0
+        self._pad: Sequence | None = None     # a page (and a state slot) no sequence owns, leased on the first padded call
+        self._pad_denied = False
 
     # ---- sequences ----
     def open(self, tokens_capacity: int, sampling: Sampling | None = None) -> Sequence:
@@ -66,6 +68,25 @@ class Engine:
 
     def close(self, seq: Sequence) -> None:
         seq.lease.release()
+
+    @property
+    def pad_pages(self) -> int:
+        """Pages held by the pad lease (0 until a call was padded)."""
+        return len(self._pad.lease.pages) if self._pad is not None else 0
+
+    def _pad_entry(self, rows: int):
+        """The entry padding rows write to: a lease of its own, taken once. When the pool has no page to spare the
+        call falls back to dead rows (slot -1, context 0), which only this package's own kernels are built to skip."""
+        if self._pad is None and not self._pad_denied:
+            widest = max([f["rows"] for f in self.forwards if f["rows"] != "var"] + [rows])
+            try:
+                self._pad = self.open(widest)
+            except _native.Denied:
+                self._pad_denied = True
+        if self._pad is None:
+            return None
+        l = self._pad.lease
+        return fills.Entry(length=0, new=[0] * rows, pages=l.pages, slot=l.slot, slots=l.slots_of(0, rows))
 
     # ---- one call ----
     def _buf(self, name: str, dtype: str, n: int) -> torch.Tensor:
@@ -96,7 +117,8 @@ class Engine:
         entries = [fills.Entry(length=s.length, new=new, pages=s.lease.pages, slot=s.lease.slot,
                                slots=s.lease.slots_of(s.length, s.length + len(new)), sampling=s.sampling)
                    for s, new in batch]
-        call = fills.build(self.p, self.unit, entries, pad, round=round)
+        call = fills.build(self.p, self.unit, entries, pad, round=round,
+                           pad_entry=self._pad_entry(len(batch[0][1])) if pad > 0 else None)
         for name, (dtype, col) in call.columns.items():
             self._write(name, dtype, col)
         fw, vars_, b = call.forward, call.vars, call.groups

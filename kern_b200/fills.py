@@ -57,9 +57,13 @@ def forward_for(protocol: dict, groups: int, rows_each: list[int], round: bool =
     raise ValueError(f"no program takes {groups} sequences of rows {sorted(set(rows_each))}")
 
 
-def build(p: dict, unit: int, batch: list[Entry], pad: int = 0, page_map=None, round: bool = False) -> Call:
-    """``pad`` dead sequences of the first one's row count bring a fixed-shape call up to a bucket: token 0 at
-    position 0, slot -1 (nothing appended), context 0 (nothing attended); their outputs are dropped.
+def build(p: dict, unit: int, batch: list[Entry], pad: int = 0, page_map=None, round: bool = False,
+          pad_entry: Entry | None = None) -> Call:
+    """``pad`` extra sequences of the first one's row count bring a fixed-shape call up to a bucket; their outputs are
+    dropped. With ``pad_entry`` (a page and a state slot no sequence owns) they are ordinary rows that write there:
+    token 0 at positions 0.., the pad page's slots, a context of their own rows — the package format's convention
+    (crates/kern-serve/src/ranks.rs:301-355, scheduler.rs:35-38), which kernels written for it rely on. Without one
+    they are dead rows: slot -1 (nothing appended), context 0 (nothing attended), which this package's own kernels skip.
     ``page_map(entry) -> pages`` lets a head substitute one member rank's page ids (default: ``entry.pages``)."""
     real = len(batch)
     rows_each = [len(e.new) for e in batch] + [len(batch[0].new)] * pad
@@ -85,7 +89,13 @@ def build(p: dict, unit: int, batch: list[Entry], pad: int = 0, page_map=None, r
         at += n
         cu[i + 1] = at
     for i in range(real, b):
-        at += rows_each[i]
+        n = rows_each[i]
+        if pad_entry is not None:
+            pos[at:at + n] = np.arange(n)
+            if pad_entry.slots is not None:
+                slot[at:at + n] = pad_entry.slots[:n]
+            seq_len[i] = n
+        at += n
         cu[i + 1] = at
     fills: dict[str, list] = {}
     for f in p["fills"]:
@@ -113,12 +123,19 @@ def build(p: dict, unit: int, batch: list[Entry], pad: int = 0, page_map=None, r
             ids = pg[::per] if per > 1 else pg
             m = min(len(ids), w)
             rows[i, :m] = np.asarray(ids[:m], np.int32) // per if per > 1 else ids[:m]
+        if pad_entry is not None and b > real:
+            pg = page_map(pad_entry) if page_map else pad_entry.pages
+            ids = pg[::per] if per > 1 else pg
+            m = min(len(ids), w)
+            rows[real:, :m] = np.asarray(ids[:m], np.int32) // per if per > 1 else ids[:m]
         cols[t["name"]] = ("i32", rows.reshape(-1))
     for t in p.get("line_tables", []):
         # [lines, groups(, w)]: line 0 of a sequence is its own state slot; the rest stay null (0)
         rows = np.zeros((t["lines"], b, t["width"]), np.int32)
         for i, e in enumerate(batch):
             rows[0, i, 0] = max(0, e.slot)
+        if pad_entry is not None:
+            rows[0, real:, 0] = max(0, pad_entry.slot)
         cols[t["name"]] = ("i32", rows.reshape(-1))
     vars_ = {p["rows"]["var"]: total, p["groups"]["var"]: b}
     if p.get("ranks"):

@@ -249,7 +249,7 @@ def ag_gemm_op(n: int, k: int, nranks: int, group: str = "tp", bn: int = 256, ti
                "params": ["inout buffer<u32>", "in buffer<u64>", "inout buffer<u32>", "out buffer<i32>", "i32", "i32", "i64"],
                "args": [{"param": 4}, {"param": 5}, {"param": 6}, {"param": 9}, {"rank": group}, {"i32": nranks},
                         {"i64": timeout_ns}]}
-    gemm = {"module": "ag_gemm", "entry": f"kern_ag_gemm_bf16_tn_n{bn}", "block": [256, 1, 1], "grid": [SMS, 1, 1],
+    gemm = {"module": "ag_gemm", "entry": f"kern_ag_gemm_bf16_tn_n{bn}", "block": [320, 1, 1], "grid": [SMS, 1, 1],
             "shared_mem": gemm_smem(bn),
             "params": ["bytes<128>", "bytes<128>", "out buffer<bf16>", "i32", "i32", "i32", "i32", "out buffer<i32>",
                        "in buffer<u64>", "inout buffer<u32>", "inout buffer<u32>", "i32", "i32", "i32"],
@@ -614,6 +614,127 @@ def tp_gemm_reduce_op(n: int, k: int, nranks: int, rows_max: int, group: str = "
                          "args": [a_map, b_map(bn), {"param": 5}, {"i32": n}, {"i32": k}, {"param": 6}, {"param": 3}, {"param": 4},
                                   {"rank": group}, {"i32": nranks}, {"i32": TP_GRID}, {"i32": slot_rows}]})
     return {"params": iface, "impl": {"launches": launches}}
+
+
+# ---- sequence-parallel layout inside a tensor-parallel group -----------------------------------------
+SP_SUB = 32                        # rows per ownership sub-block: sub-block s belongs to rank s % nranks
+SP_GRID = 2 * SMS                  # CTAs of the reduce + norm kernel
+SP_FLAG_STRIDE = 32                # words per row of `sp.flags`
+
+
+def sp_slot_rows(rows_max: int, nranks: int) -> int:
+    """Rows one staging slot holds: a rank's share of the sub-blocks of the largest call."""
+    return -(-(-(-rows_max // SP_SUB)) // nranks) * SP_SUB
+
+
+def sp_buffers(hidden: int, nranks: int, rows_max: int, group: str = "tp") -> dict:
+    """Exported buffers of the sequence-parallel path: staging slots the peers' GEMM epilogues push into, the
+    all-gather buffer `sp.g` of normed rows, the two rows of epoch flags, and the local counters."""
+    peer = lambda of: {"dtype": "u64", "shape": [nranks], "kind": "peer", "of": of, "group": group}
+    return {
+        "sp.comm": {"dtype": "bf16", "shape": [2, nranks, sp_slot_rows(rows_max, nranks), hidden], "kind": "carry", "export": True},
+        "sp.comm_peers": peer("sp.comm"),
+        "sp.flags": {"dtype": "u32", "shape": [2, SP_FLAG_STRIDE], "kind": "carry", "export": True},
+        "sp.flags_peers": peer("sp.flags"),
+        "sp.state": {"dtype": "u32", "shape": [2], "kind": "carry"},
+        "sp.g": {"dtype": "bf16", "shape": [rows_max, hidden], "kind": "carry", "export": True},
+        "sp.g_peers": peer("sp.g"),
+        "sp.blocks": {"dtype": "u32", "shape": [AG_MAX_BLOCKS], "kind": "carry"},
+        "sp.cta_epochs": {"dtype": "u32", "shape": [SMS], "kind": "carry"},
+    }
+
+
+def _when(var: str, lo: int, hi: int, var_max: int) -> dict | None:
+    w = {"var": var}
+    if lo > 1:
+        w["min"] = lo
+    if hi < var_max:
+        w["max"] = hi
+    return w if len(w) > 1 else None
+
+
+def sp_gemm_scatter_op(n: int, k: int, nranks: int, rows_max: int, group: str = "tp") -> dict:
+    """A tensor-parallel partial GEMM whose epilogue is the push half of a reduce-scatter: every row of every tile goes
+    from TMEM over NVLink into its owner's staging slot (sub-block ownership). `sp_reduce_norm_op` finishes it.
+    Interface [a, w, comm_peers, state, rows, err]."""
+    slot_rows = sp_slot_rows(rows_max, nranks)
+    iface = ["in buffer<bf16>", "in buffer<bf16>", "in buffer<u64>", "in buffer<u32>", "i32", "out buffer<i32>"]
+    a_map = {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+        "param": 0, "dtype": "bf16", "dims": [k, 0], "strides": [k * 2], "box": [BK, BM], "swizzle": 128, "l2_promotion": 256}}]}}
+    b_map = lambda bn: {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+        "param": 1, "dtype": "bf16", "dims": [k, n], "strides": [k * 2], "box": [BK, bn], "swizzle": 128, "l2_promotion": 256}}]}}
+    launches = []
+    for bn, lo, hi in gemm_ranges(n, rows_max):
+        launch = {"module": "tp_gemm", "entry": f"kern_tp_gemm_scatter_bf16_n{bn}", "block": [192, 1, 1], "grid": [SMS, 1, 1],
+                  "shared_mem": gemm_smem(bn) + 20480,     # + the epilogue's row staging
+                  "params": ["bytes<128>", "bytes<128>", "i32", "i32", "i32", "out buffer<i32>", "in buffer<u64>",
+                             "in buffer<u32>", "i32", "i32", "i32", "i32"],
+                  "args": [a_map, b_map(bn), {"param": 4}, {"i32": n}, {"i32": k}, {"param": 5}, {"param": 2}, {"param": 3},
+                           {"rank": group}, {"i32": nranks}, {"i32": 0}, {"i32": slot_rows}]}
+        w = _when("tokens", lo, hi, rows_max)
+        if w:
+            launch["when"] = w
+        launches.append(launch)
+    return {"params": iface, "impl": {"launches": launches}}
+
+
+def sp_reduce_norm_op(hidden: int, eps: float, nranks: int, rows_max: int, group: str = "tp", plus_one: bool = False,
+                      timeout_ns: int = 2_000_000_000) -> dict:
+    """On the rows this rank owns: x += sum of the partials the peers pushed; g = rmsnorm(x) * w. One kernel; it also
+    lines the ranks up (bounded waits on epoch flags). Interface [x, g, w, comm, flags, flags_peers, state, err, rows]."""
+    iface = ["inout buffer<bf16>", "inout buffer<bf16>", "in buffer<bf16>", "inout buffer<bf16>", "inout buffer<u32>",
+             "in buffer<u64>", "inout buffer<u32>", "out buffer<i32>", "i32"]      # comm is inout: the peers write it
+    return {"params": iface, "impl": {"launches": [{
+        "module": "tp_sp", "entry": "kern_sp_reduce_norm", "block": [256, 1, 1], "grid": [SP_GRID, 1, 1],
+        "params": iface[:8] + ["i32", "i32", "i32", "i32", "i32", "f32", "i32", "i64"],
+        "args": [{"param": i} for i in range(8)] + [{"rank": group}, {"i32": nranks}, {"param": 8}, {"i32": hidden},
+                                                     {"i32": sp_slot_rows(rows_max, nranks)}, {"f32": eps}, {"i32": int(plus_one)},
+                                                     {"i64": timeout_ns}]}]}}
+
+
+def sp_ag_gemm_op(n: int, k: int, nranks: int, rows_max: int, group: str = "tp", epilogue: str = "store",
+                  timeout_ns: int = 2_000_000_000) -> dict:
+    """C[rows, n] = G[rows, k] . W[n, k]^T where G's rows sit on their owners (sub-block ownership): the kernel's gather
+    warps pull the foreign rows of each 128-row block over NVLink while the tensor-core warps run the blocks already
+    here. `epilogue`: store | swiglu (c is [rows, n/2] over weights stacked [gate rows ; up rows]).
+    Interface [g, g_peers, w, c, blocks, cta_epochs, ready, state, err, rows]; `ready` is row 1 of `sp.flags`."""
+    out_cols = n // 2 if epilogue == "swiglu" else n
+    suffix = {"store": "", "swiglu": "_swiglu"}[epilogue]
+    iface = ["inout buffer<bf16>", "in buffer<u64>", "in buffer<bf16>", "out buffer<bf16>", "inout buffer<u32>",
+             "inout buffer<u32>", "in buffer<u32>", "in buffer<u32>", "out buffer<i32>", "i32"]
+    launches = []
+    for bn, lo, hi in gemm_ranges(n, rows_max, (256, 128, 64)):
+        launch = {"module": "ag_gemm", "entry": f"kern_ag_gemm_sp_bf16_tn{suffix}_n{bn}", "block": [320, 1, 1],
+                  "grid": [SMS, 1, 1], "shared_mem": gemm_smem(bn),
+                  "params": ["bytes<128>", "bytes<128>", "out buffer<bf16>", "i32", "i32", "i32", "i32", "out buffer<i32>",
+                             "in buffer<u64>", "inout buffer<u32>", "inout buffer<u32>", "in buffer<u32>", "in buffer<u32>",
+                             "i32", "i32", "i32", "i64"],
+                  "args": [
+                      {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+                          "param": 0, "dtype": "bf16", "dims": [k, 0], "strides": [k * 2], "box": [BK, BM], "swizzle": 128,
+                          "l2_promotion": 256}}]}},
+                      {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+                          "param": 2, "dtype": "bf16", "dims": [k, n], "strides": [k * 2],
+                          "box": [BK, bn // 2 if epilogue == "swiglu" else bn], "swizzle": 128, "l2_promotion": 256}}]}},
+                      {"param": 3}, {"param": 9}, {"i32": n}, {"i32": k}, {"i32": out_cols}, {"param": 8}, {"param": 1},
+                      {"param": 4}, {"param": 5}, {"param": 6}, {"param": 7}, {"rank": group}, {"i32": nranks},
+                      {"i32": AG_MAX_BLOCKS}, {"i64": timeout_ns}]}
+        w = _when("tokens", lo, hi, rows_max)
+        if w:
+            launch["when"] = w
+        launches.append(launch)
+    return {"params": iface, "impl": {"launches": launches}}
+
+
+def sp_last_rows_op(hidden: int, nranks: int, group: str = "tp", timeout_ns: int = 2_000_000_000) -> dict:
+    """last[i] = the final row of sequence i, fetched from the rank that owns it. Interface
+    [g_peers, last, cu_seqlens, flags, state, err, seqs]."""
+    iface = ["in buffer<u64>", "out buffer<bf16>", "in buffer<i32>", "in buffer<u32>", "in buffer<u32>", "out buffer<i32>", "i32"]
+    return {"params": iface, "impl": {"launches": [{
+        "module": "tp_sp", "entry": "kern_sp_last_rows", "block": [256, 1, 1], "grid": ["seqs", 1, 1],
+        "params": iface[:6] + ["i32", "i32", "i32", "i32", "i64"],
+        "args": [{"param": i} for i in range(6)] + [{"rank": group}, {"i32": nranks}, {"param": 6}, {"i32": hidden},
+                                                     {"i64": timeout_ns}]}]}}
 
 
 AG_GRID = 64

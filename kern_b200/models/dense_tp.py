@@ -6,6 +6,14 @@ sums that the fused peer all-reduce + residual + RMSNorm kernel turns into the n
 every rank (no NCCL on the path). Weights bind by rank-selected row / column ranges of the same
 checkpoint tensors (`bind` with `{group, ranges}`: crates/kern-manifest/src/types.rs:481-541).
 The batch is replicated: every rank of the group is fed the same rows.
+
+`sp=True` gives the ragged `prefill` program the sequence-parallel layout (reference: docs/multi-gpu.md:495-528 does it
+with NCCL reduce-scatter / all-gather between library GEMMs): attention still runs on all rows by heads, but the
+residual stream and the norms live on the rows a rank owns (32-row sub-blocks dealt round-robin). The o / down
+projections end in the scatter epilogue (GEMM + reduce-scatter in one kernel: partial rows go from TMEM straight into
+the owner's staging slot), `kern_sp_reduce_norm` adds, norms and leaves the owner's rows in `sp.g`, and the QKV /
+gate-up GEMMs pull the other owners' rows while their own tiles run (all-gather + GEMM in one kernel). The fixed-shape
+`decode` program keeps the replicated layout and the flagless one-shot all-reduce: a handful of rows is latency-bound.
 """
 from __future__ import annotations
 
@@ -13,7 +21,7 @@ from . import common as C
 from .dense import DenseConfig
 
 
-def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True) -> dict:
+def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True, sp: bool = False) -> dict:
     """`fused`: the o/down projections push their partial rows to the reducing rank from the GEMM epilogue
     (GEMM + reduce-scatter in one kernel); off, they store the partial and the all-reduce kernel pushes it.
     `lamport`: decode-sized calls use the flagless one-shot all-reduce."""
@@ -47,6 +55,8 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True
     bufs["rope_cos"] = {"dtype": "f32", "shape": [cfg.max_context, d // 2], "kind": "carry"}
     bufs["rope_sin"] = {"dtype": "f32", "shape": [cfg.max_context, d // 2], "kind": "carry"}
     bufs.update(C.tp_buffers(h, n, T, lamport=lamport))
+    if sp:
+        bufs.update(C.sp_buffers(h, n, T))
 
     def ranked(width: int) -> dict:
         return {"group": "tp", "ranges": [[r * width, (r + 1) * width] for r in range(n)]}
@@ -91,9 +101,18 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True
     if lamport:
         ops["lamport_init"] = C.tp_lamport_init_op(h, n)
     ops["allreduce_norm"] = C.tp_allreduce_norm_op(h, cfg.eps, n, T, fused_gemm=fused, lamport=lamport)
+    if sp:
+        ops["sp_o_proj"] = C.sp_gemm_scatter_op(h, qd, n, T)
+        ops["sp_down_proj"] = C.sp_gemm_scatter_op(h, inter, n, T)
+        ops["sp_reduce_norm"] = C.sp_reduce_norm_op(h, cfg.eps, n, T)
+        ops["sp_qkv_proj"] = C.sp_ag_gemm_op(qkv_dim, h, n, T)
+        ops["sp_gate_up"] = C.sp_ag_gemm_op(2 * inter, h, n, T, epilogue="swiglu")
+        ops["sp_last_rows"] = C.sp_last_rows_op(h, n)
+        ops.pop("last_row")
 
-    B = lambda name: {"buf": name}
+    B = lambda name, off=0: ({"buf": name, "offset": off} if off else {"buf": name})
     err = B("error")
+    sp_ready = B("sp.flags", C.SP_FLAG_STRIDE * 4)      # row 1 of the flags: "this rank's rows are final"
 
     def ar(label: str, w: str) -> dict:
         return {"op": "allreduce_norm", "label": label,
@@ -102,6 +121,40 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True
                         ([B("tp.lamport"), B("tp.lamport_peers"), B("tp.lamport_epochs")] if lamport else [])}
 
     push = [B("tp.comm_peers"), B("tp.epochs")] if fused else []
+
+    def sp_layer(i: int) -> list[dict]:
+        """One layer of the sequence-parallel prefill program; `sp.g` holds the layer's normed input (all rows in layer
+        0, where every rank normed them itself; the owners' rows afterwards)."""
+        kv = {"state": f"kv.l{i}"}
+        lbl = f"l{i}."
+        rope_args = [B("qkv"), kv, B("positions"), B("slot_mapping"), B("rope_cos"), B("rope_sin")]
+        if cfg.qk_norm:
+            rope_args += [B(f"w.l{i}.qn"), B(f"w.l{i}.kn")]
+        ag_tail = [B("sp.blocks"), B("sp.cta_epochs"), sp_ready, B("sp.state"), err, {"var": "tokens"}]
+
+        def reduce(label: str, w: str) -> dict:
+            return {"op": "sp_reduce_norm", "label": label,
+                    "args": [B("x"), B("sp.g"), B(w), B("sp.comm"), B("sp.flags"), B("sp.flags_peers"), B("sp.state"), err,
+                             {"var": "tokens"}]}
+
+        qkv = ({"op": "qkv_proj", "label": lbl + "qkv", "args": [B("sp.g"), B(f"w.l{i}.qkv"), B("qkv"), {"var": "tokens"}, err]}
+               if i == 0 else
+               {"op": "sp_qkv_proj", "label": lbl + "qkv", "args": [B("sp.g"), B("sp.g_peers"), B(f"w.l{i}.qkv"), B("qkv"), *ag_tail]})
+        nxt = f"w.l{i + 1}.ln1" if i + 1 < cfg.layers else "w.norm"
+        return [
+            qkv,
+            {"op": "rope_append", "label": lbl + "rope", "args": rope_args + [err]},
+            {"op": "attn_prefill", "label": lbl + "attn",
+             "args": [B("qkv"), kv, B("attn"), B("block_table"), B("seq_lens"), B("cu_seqlens"), B("work"),
+                      B("work_count"), err, B("work_d"), B("work_d_count")]},
+            {"op": "sp_o_proj", "label": lbl + "o",
+             "args": [B("attn"), B(f"w.l{i}.o"), B("sp.comm_peers"), B("sp.state"), {"var": "tokens"}, err]},
+            reduce(lbl + "rs_attn", f"w.l{i}.ln2"),
+            {"op": "sp_gate_up", "label": lbl + "gate_up", "args": [B("sp.g"), B("sp.g_peers"), B(f"w.l{i}.gu"), B("act"), *ag_tail]},
+            {"op": "sp_down_proj", "label": lbl + "down",
+             "args": [B("act"), B(f"w.l{i}.down"), B("sp.comm_peers"), B("sp.state"), {"var": "tokens"}, err]},
+            reduce(lbl + "rs_mlp", nxt),       # leaves the next layer's normed input (or the final norm) on its owners
+        ]
 
     def layer(i: int, prefill: bool) -> list[dict]:
         kv = {"state": f"kv.l{i}"}
@@ -140,13 +193,21 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True
                         "args": [B("cu_seqlens"), B("work"), B("work_count"), {"var": "seqs"}, {"expr": C.attn_plan_items(hq, hk)},
                                  B("work_d"), B("work_d_count")]}]
     decode = list(start)
+    if sp:
+        prefill[1] = {"op": "norm", "label": "l0.ln1", "args": [B("x"), B("w.l0.ln1"), B("sp.g")]}
     for i in range(cfg.layers):
-        prefill += layer(i, True)
+        prefill += sp_layer(i) if sp else layer(i, True)
         decode += layer(i, False)
-    prefill += [{"op": "last_row", "label": "last_row", "args": [B("xn"), B("last"), B("cu_seqlens")]}] + head("last")
+    if sp:
+        prefill += [{"op": "sp_last_rows", "label": "last_row",
+                     "args": [B("sp.g_peers"), B("last"), B("cu_seqlens"), B("sp.flags"), B("sp.state"), err, {"var": "seqs"}]}]
+    else:
+        prefill += [{"op": "last_row", "label": "last_row", "args": [B("xn"), B("last"), B("cu_seqlens")]}]
+    prefill += head("last")
     decode += head("xn")
 
-    mods = ["norm_embed", "gemm_bf16", "attn_prep", "attn_paged", "misc", "sampling", "tp_allreduce_norm"] + (["tp_gemm"] if fused else [])
+    mods = (["norm_embed", "gemm_bf16", "attn_prep", "attn_paged", "misc", "sampling", "tp_allreduce_norm"] +
+            (["tp_gemm"] if fused or sp else []) + (["tp_sp", "ag_gemm"] if sp else []))
     return {
         "schema_version": 7,
         "model": f"{cfg.name}-tp{n}",

@@ -61,7 +61,10 @@ def generate(ids: list[int], max_tokens: int, lined: bool = False) -> list[int]:
 
 
 def build_manifest(lined: bool = False, page_size: int = 16, max_tokens: int = 128, max_seqs: int = 8,
-                   max_context: int = 256, name: str | None = None) -> dict:
+                   max_context: int = 256, name: str | None = None, per_sequence_prefill: bool = False) -> dict:
+    """`per_sequence_prefill` (paged form only): the ragged program takes one sequence per call and only appends — it
+    emits nothing, and the first step is fed the prompt's last token — the shape of the reference's paged packages
+    (tools/toy/gen.py:107-113)."""
     W = -(-max_context // page_size)
     B = lambda n: {"buf": n}
     bufs = {
@@ -136,10 +139,16 @@ def build_manifest(lined: bool = False, page_size: int = 16, max_tokens: int = 1
                     "args": pa + ([B("cu_seqlens")] if prefill else []) + [B("next_token")]})
         return out
 
+    prefill = {"batch": {"groups": max_seqs, "rows": "tokens"}, "calls": calls(True)}
+    if per_sequence_prefill:
+        assert not lined
+        prefill = {"batch": {"groups": 1, "rows": "tokens"}, "calls": calls(True)[:1]}
+        ops.pop("predict_p")
+        bufs.pop("cu_seqlens")
     return {"schema_version": 7, "model": name or ("toy-int-stateful" if lined else "toy-int-paged"),
             "vars": {"tokens": {"max": max_tokens, "axis": "rows"}, "seqs": {"max": max_seqs, "axis": "groups"}},
             "states": states, "buffers": bufs, "modules": C.modules_for(["toy_int"]), "ops": ops,
-            "programs": {"prefill": {"batch": {"groups": max_seqs, "rows": "tokens"}, "calls": calls(True)},
+            "programs": {"prefill": prefill,
                          "decode": {"batch": {"groups": max_seqs, "rows": 1}, "graph": True, "calls": calls(False)}}}
 
 

@@ -136,26 +136,28 @@ def check_allgather(rank, world, local, sizes=(16, 4096, 1 << 20), time_it=False
     return out, times
 
 
-def check_model(rank, world, fused=True):
+def check_model(rank, world, fused=True, sp=False):
+    """`sp`: the ragged program in the sequence-parallel layout (scatter epilogue, reduce + norm on own rows, all-gather
+    GEMM), with calls of several 128-row blocks, a ragged tail, and a second ragged call after decode steps."""
     from ..engine import Engine
     from ..models import dense, dense_tp
     from ..runtime import Runtime
     from . import group
 
     cfg = dense.DenseConfig(name="tiny-tp", vocab=512, hidden=256, layers=2, heads=8, kv_heads=max(2, world),
-                            head_dim=64, intermediate=512 * world // 2, rope_theta=10000.0, page_size=16, max_tokens=256, max_seqs=8,
-                            max_context=256, tp=world)
+                            head_dim=64, intermediate=512 * world // 2, rope_theta=10000.0, page_size=16,
+                            max_tokens=640 if sp else 256, max_seqs=8, max_context=512 if sp else 256, tp=world)
     weights = dense.random_weights(cfg, seed=0, std=0.05)
-    doc = dense_tp.build_manifest_tp(cfg, fused=fused)
+    doc = dense_tp.build_manifest_tp(cfg, fused=fused, sp=sp)
     rt = Runtime(doc, gpu=torch.cuda.current_device(), topology=group.topology(doc["topology"]["groups"], rank, world),
-                 tokens=cfg.page_size * 64)
+                 tokens=cfg.page_size * (160 if sp else 64))
     rt.load_tensors(lambda name: weights[name].cuda())
     group.start(rt)
     eng = Engine(rt)
     oracle = dense.DenseOracle(cfg, weights, device="cuda")
     torch.manual_seed(0)
-    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (37, 5, 80)]
-    seqs = [eng.open(120) for _ in prompts]
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in ((300, 5, 181) if sp else (37, 5, 80))]
+    seqs = [eng.open(len(p) + 40) for p in prompts]
     caches = [oracle.new_cache() for _ in prompts]
     first = eng.step(list(zip(seqs, prompts)))
     worst = 0.0
@@ -170,8 +172,22 @@ def check_model(rank, world, fused=True):
         for i in range(3):
             worst = max(worst, float((logits[i] - refs[i]).abs().max()))
         toks = [n[0] for n in nxt]
+    if sp:
+        # a second and a third ragged call (the staging parity alternates): new sequences next to decode rows of the old
+        for lens in ((70, 33), (129,)):
+            more = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in lens]
+            new_seqs = [eng.open(len(p) + 8) for p in more]
+            new_caches = [oracle.new_cache() for _ in more]
+            refs = [oracle.forward([t], c)[-1] for t, c in zip(toks, caches)] + [oracle.forward(p, c)[-1] for p, c in zip(more, new_caches)]
+            nxt = eng.step([(s_, [t]) for s_, t in zip(seqs, toks)] + list(zip(new_seqs, more)))
+            logits = rt.tensor("logits")[:len(refs)].float()
+            for i, r in enumerate(refs):
+                worst = max(worst, float((logits[i] - r).abs().max()))
+            toks = [n[0] for n in nxt[:3]]
+            for s_ in new_seqs:
+                eng.close(s_)
     rt.check_error()
-    return {"model_max_logit_diff": round(worst, 4), "ok": worst < 0.12, "graphs": rt.graphs}
+    return {"model_max_logit_diff": round(worst, 4), "ok": worst < 0.12, "graphs": rt.graphs, "sp": sp}
 
 
 def check_moe(rank, world):
@@ -242,6 +258,8 @@ def main(argv=None):
     ap.add_argument("--no-lamport", action="store_true", help="decode-sized all-reduce through flags instead of the flagless one-shot")
     ap.add_argument("--moe", action="store_true", help="also check the expert-parallel MoE decoder")
     ap.add_argument("--unfused", action="store_true", help="the model check without the GEMM + reduce-scatter fusion")
+    ap.add_argument("--sp", action="store_true", help="also check the decoder with the sequence-parallel ragged program")
+    ap.add_argument("--only-sp", action="store_true", help="run the sequence-parallel decoder check alone")
     args = ap.parse_args(argv)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
@@ -250,6 +268,15 @@ def main(argv=None):
     from ..runtime import Runtime
     from . import group
 
+    if args.only_sp:
+        from . import group as _g   # noqa: F401
+        m = check_model(rank, world, sp=True)
+        if rank == 0:
+            print(json.dumps({"check": "tp_model_sp", "world": world, **m}))
+        flag = torch.tensor([int(m["ok"])], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        dist.destroy_process_group()
+        return 0 if int(flag) else 1
     rows_max = max(args.rows + [4096 if args.time else 1])
     rt = Runtime(allreduce_manifest(args.hidden, world, rows_max, lamport=not args.no_lamport), gpu=local,
                  topology={"tp": (rank, world)})
@@ -273,6 +300,11 @@ def main(argv=None):
         ok &= m["ok"]
         if rank == 0:
             print(json.dumps({"check": "tp_model", "world": world, "fused_gemm_reduce_scatter": not args.unfused, **m}))
+    if args.sp and not args.skip_model:
+        m = check_model(rank, world, sp=True)
+        ok &= m["ok"]
+        if rank == 0:
+            print(json.dumps({"check": "tp_model_sp", "world": world, **m}))
     if args.moe:
         e = check_moe(rank, world)
         ok &= e["ok"]

@@ -85,6 +85,13 @@ class Scheduler:
         self.round = next((f for f in engine.forwards if f["rows"] == self.rows and self.rows > 1), None)
         step_groups = max((f["groups"] for f in engine.forwards if f["rows"] != "var"), default=engine.groups_max)
         self.max_seqs = min(max_seqs or step_groups, engine.groups_max)
+        # The ragged (prefill) program of a package may take fewer sequences per call than a step does (one, in packages
+        # whose prefill is a per-sequence program), and may emit nothing (the prompt's last token is then fed by the
+        # first step, as the reference's paged packages do: tools/toy/gen.py:107-113, crates/kern-serve/src/scheduler.rs:985-1062).
+        ragged = next((f for f in engine.forwards if f["rows"] == "var"), None)
+        self.ragged_groups = ragged["groups"] if ragged else 0
+        self.prefill_emits = ragged is None or ragged["emits"] is not None
+        self.split = ragged is not None and self.ragged_groups < self.max_seqs
         self.prefix = _native.Prefix(self.pool.unit) if prefix_cache else None
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
@@ -231,11 +238,18 @@ class Scheduler:
         self.done.append(req)
 
     # ---- one step ----
+    def _target(self, r: Request) -> int:
+        """Prompt tokens the ragged program is fed: all of them, or all but the last when it emits nothing."""
+        return len(r.prompt) - (0 if self.prefill_emits else 1)
+
     def step(self) -> list[tuple[Request, list[int]]]:
-        """Run one call; returns (request, new tokens) for every request that produced tokens."""
+        """Run one step (one call; several when the ragged program takes fewer sequences than the step holds);
+        returns (request, new tokens) for every request that produced tokens."""
         plan = self.plan()
         if plan is None:
             return []
+        for pre in plan.get("pre", []):
+            pre["toks"] = self.eng.step(pre["batch"])
         return self.finish(plan, self.eng.step(plan["batch"], pad=plan["pad"], round=plan["round"]))
 
     def plan(self) -> dict | None:
@@ -247,47 +261,66 @@ class Scheduler:
             return None
         batch, kinds = [], []
         budget = self.chunk
-        decoding = [r for r in self.running if r.fed >= len(r.prompt)]
-        prefilling = [r for r in self.running if r.fed < len(r.prompt)]
+        decoding = [r for r in self.running if r.fed >= self._target(r)]
+        prefilling = [r for r in self.running if r.fed < self._target(r)]
         rows_decode = self.rows if self.round else 1
-        budget -= len(decoding) * rows_decode
+        if not self.split:
+            budget -= len(decoding) * rows_decode
+        pre: list[dict] = []
         for r in prefilling:                       # prefill first: oldest request gets the budget
             if budget <= 0:
                 break
-            n = min(budget, len(r.prompt) - r.fed)
+            n = min(budget, self._target(r) - r.fed)
             h = r.history_tokens
             if h is not None and r.seq.lease.slot >= 0 and r.fed < h < len(r.prompt):
                 n = min(n, h - r.fed)      # a chunk ends at the turn boundary, where the per-sequence state is snapshotted
-            batch.append((r.seq, r.prompt[r.fed:r.fed + n]))
-            kinds.append((r, "prefill", n))
+            if self.split:
+                # calls of their own, as many sequences each as the ragged program takes
+                if not pre or len(pre[-1]["batch"]) >= self.ragged_groups or \
+                        sum(k[2] for k in pre[-1]["kinds"]) + n > self.eng.rows_max:
+                    pre.append({"batch": [], "kinds": []})
+                pre[-1]["batch"].append((r.seq, r.prompt[r.fed:r.fed + n]))
+                pre[-1]["kinds"].append((r, "prefill", n))
+            else:
+                batch.append((r.seq, r.prompt[r.fed:r.fed + n]))
+                kinds.append((r, "prefill", n))
             budget -= n
         use_round = self.round is not None and not batch       # a round is a fixed-shape call of its own
         for r in decoding:
-            last = r.out[-1]
+            last = r.out[-1] if r.out else r.prompt[-1]       # a prefill that emits nothing leaves the last prompt token to the step
             batch.append((r.seq, [last] * (self.rows if use_round else 1)))
             kinds.append((r, "decode", 1))
+        if not batch and pre:
+            last_pre = pre.pop()                   # nothing decodes yet: the last ragged call is the step's main call
+            batch, kinds = last_pre["batch"], last_pre["kinds"]
         if not batch:
             return None
         pad = 0
-        if not prefilling or not any(k[1] == "prefill" for k in kinds):
+        if not any(k[1] == "prefill" for k in kinds):
             # fixed-shape call: pad to a bucket with dead rows so captured graphs are reused
             want = bucket_for(len(batch), self.max_seqs)
             pad = want - len(batch)
-        return {"batch": batch, "kinds": kinds, "pad": pad, "round": use_round, "t0": t0}
+        return {"batch": batch, "kinds": kinds, "pad": pad, "round": use_round, "t0": t0, "pre": pre}
 
     def finish(self, plan: dict, toks) -> list[tuple[Request, list[int]]]:
         """Account for the tokens the planned call emitted."""
-        kinds, use_round, t0 = plan["kinds"], plan["round"], plan["t0"]
+        kinds, use_round, t0 = list(plan["kinds"]), plan["round"], plan["t0"]
+        toks = list(toks or [[]] * len(kinds))
+        for pre in reversed(plan.get("pre", [])):          # the ragged calls that ran before the main one
+            kinds = list(pre["kinds"]) + kinds
+            toks = list(pre.get("toks") or [[]] * len(pre["kinds"])) + toks
         now = time.monotonic()
         emitted = []
-        for (r, kind, n), got in zip(kinds, toks or [[]] * len(kinds)):
+        for (r, kind, n), got in zip(kinds, toks):
             if kind == "prefill":
                 r.fed += n
                 self.stats.prefill_tokens += n
-                if r.fed < len(r.prompt):
+                if r.fed < self._target(r):
                     if self.prefix is not None and r.history_tokens == r.fed and r.seq.lease.slot >= 0:
                         self._snapshot(r)          # a stateful model's state exactly after the previous turns
                     continue                       # the chunk's emitted token is not the prompt's next token yet
+                if not self.prefill_emits:
+                    continue                       # the first step feeds the prompt's last token and emits
                 new = got[:1]
             else:
                 new = got

@@ -61,3 +61,29 @@ def test_eviction_under_pressure_keeps_answers_exact(lined):
     for r in reqs:
         assert [t for t in r.out if t != toy_int.EOS] == toy_int.generate(r.prompt, 8, lined)
     assert sch.stats.evictions >= 1
+
+
+def test_per_sequence_prefill_that_emits_nothing():
+    """A package whose ragged program takes one sequence per call and emits nothing (the reference's paged shape): the
+    scheduler runs a ragged call per admitted prompt, holds back the prompt's last token for the first step, and every
+    emitted token still equals the twin's — with chunking, several requests at once and a prefix-cache hit."""
+    doc = toy_int.build_manifest(False, per_sequence_prefill=True)
+    m, diags = verify(doc)
+    assert m is not None, diags
+    rt = CpuRuntime(doc, tokens=16 * 40)
+    sch = Scheduler(Engine(rt), chunk=24, max_seqs=4)
+    assert sch.split and not sch.prefill_emits
+    rng = random.Random(5)
+    prompts = [[rng.randrange(256) for _ in range(n)] for n in (1, 7, 30, 53, 16, 17)]
+    reqs = [Request(id=str(i), prompt=p, max_tokens=6, stop_ids=(toy_int.EOS,)) for i, p in enumerate(prompts)]
+    for r in reqs:
+        sch.submit(r)
+    sch.run_until_idle(500)
+    assert sch.idle()
+    for r in reqs:
+        want = toy_int.generate(r.prompt, 6)
+        assert r.out[:len(want)] == want and len(r.out) in (len(want), len(want) + 1), (r.id, r.out, want)
+    again = Request(id="again", prompt=prompts[3] + reqs[3].out[:2], max_tokens=3, stop_ids=(toy_int.EOS,))
+    sch.submit(again)
+    sch.run_until_idle(100)
+    assert again.cached >= 48 and again.out[:3][:len(toy_int.generate(again.prompt, 3))] == toy_int.generate(again.prompt, 3)
