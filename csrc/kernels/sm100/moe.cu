@@ -92,9 +92,12 @@ extern "C" __global__ void __launch_bounds__(128)
 //   offsets[E_local+1] first permuted row of every local expert
 //   tiles[int4]        {local expert, first row, rows, 0} per M tile of `bm` rows; tile_count[0] = how many
 //   rows_out[0]        total permuted rows
-extern "C" __global__ void __launch_bounds__(1024)
-    kern_moe_plan(const int* topk_ids, int* perm, int* offsets, int* tiles, int* tile_count, int* rows_out, int entries,
-                  int e_lo, int e_hi, int bm, int max_tiles, int* err, int rank, int per_rank) {
+//
+// `align`: every expert's first row is rounded up to a multiple of it (the block-scaled GEMM wants its 128-row tiles on
+// 128-row boundaries of the sorted buffer: the scale atoms are 128 rows tall); rows_out then counts the gaps too.
+__device__ __forceinline__ void moe_plan_body(const int* topk_ids, int* perm, int* offsets, int* tiles, int* tile_count,
+                                              int* rows_out, int entries, int e_lo, int e_hi, int bm, int max_tiles, int* err,
+                                              int rank, int per_rank, int align) {
   pdl_wait();
   e_lo += rank * per_rank;      // expert parallel: rank r keeps experts [e_lo + r * per_rank, e_hi + r * per_rank)
   e_hi += rank * per_rank;
@@ -112,6 +115,7 @@ extern "C" __global__ void __launch_bounds__(1024)
   if (threadIdx.x == 0) {
     int at = 0, nt = 0;
     for (int e = 0; e < el; ++e) {
+      if (align > 1 && counts[e] > 0) at = (at + align - 1) / align * align;
       offsets[e] = at;
       cursor[e] = at;
       for (int m0 = 0; m0 < counts[e]; m0 += bm) {
@@ -135,6 +139,17 @@ extern "C" __global__ void __launch_bounds__(1024)
     const int e = topk_ids[i];
     perm[i] = (e >= e_lo && e < e_hi) ? atomicAdd(&cursor[e - e_lo], 1) : -1;
   }
+}
+
+extern "C" __global__ void __launch_bounds__(1024)
+    kern_moe_plan(const int* topk_ids, int* perm, int* offsets, int* tiles, int* tile_count, int* rows_out, int entries,
+                  int e_lo, int e_hi, int bm, int max_tiles, int* err, int rank, int per_rank) {
+  moe_plan_body(topk_ids, perm, offsets, tiles, tile_count, rows_out, entries, e_lo, e_hi, bm, max_tiles, err, rank, per_rank, 1);
+}
+extern "C" __global__ void __launch_bounds__(1024)
+    kern_moe_plan_aligned(const int* topk_ids, int* perm, int* offsets, int* tiles, int* tile_count, int* rows_out,
+                          int entries, int e_lo, int e_hi, int bm, int max_tiles, int* err, int rank, int per_rank) {
+  moe_plan_body(topk_ids, perm, offsets, tiles, tile_count, rows_out, entries, e_lo, e_hi, bm, max_tiles, err, rank, per_rank, bm);
 }
 
 // grid = entries (tokens * k), block 128; 16-byte vectors.

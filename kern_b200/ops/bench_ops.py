@@ -118,6 +118,61 @@ def bench_moe(a):
            top_k=a.top_k, hidden=a.hidden, inter=a.inter)
 
 
+def bench_gemm_mx(a):
+    """Block-scaled GEMM (MXFP8 x MXFP8 or MXFP8 x MXFP4) on random codes and scales near 1."""
+    from . import gemm_mx as G
+    from .launcher import Kernels
+
+    aq = torch.randint(0, 256, (a.m, a.k), device="cuda", dtype=torch.uint8) & 0x77        # finite e4m3 codes of small magnitude
+    wq = torch.randint(0, 256, (a.n, a.k // 2 if a.fp4 else a.k), device="cuda", dtype=torch.uint8)
+    if not a.fp4:
+        wq &= 0x77
+    sfa = torch.randint(125, 130, (G.atom_bytes(a.m, a.k),), device="cuda", dtype=torch.uint8)
+    sfw = torch.randint(125, 130, (G.atom_bytes(a.n, a.k),), device="cuda", dtype=torch.uint8)
+    out = torch.zeros(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: G.gemm_mx(aq, sfa, wq, sfw, a.fp4, out=out, bn=a.bn or 256), a.iters)
+    Kernels.get().check_error()
+    report("gemm_mxfp8_mxfp4_tn" if a.fp4 else "gemm_mxfp8_tn", ms, flops=2.0 * a.m * a.n * a.k,
+           nbytes=aq.numel() + wq.numel() + out.numel() * 2, m=a.m, n=a.n, k=a.k, bn=a.bn or 256)
+
+
+def bench_moe_mx(a):
+    """The two routed expert GEMMs with MXFP4 weights and MXFP8 activations over a planned batch: `tokens` tokens choose
+    `top_k` of `experts_total` experts uniformly, this rank holds the first `experts` of them (expert parallel); FC1 with the
+    SwiGLU + MXFP8 epilogue, FC2 to bf16. Random codes: the time does not depend on the values."""
+    from . import gemm_mx as G
+    from . import moe as M
+    from .launcher import Kernels
+
+    dev = "cuda"
+    ids = torch.stack([torch.randperm(a.experts_total, device=dev)[:a.top_k] for _ in range(a.tokens)]).int()
+    pl = M.plan(ids, a.experts, 0, aligned=True)
+    rows = pl["rows_bound"]
+    torch.cuda.synchronize()
+    live = int(pl["rows"].item())
+    xq = torch.randint(0, 256, (rows, a.hidden), device=dev, dtype=torch.uint8) & 0x77
+    sfx = torch.randint(125, 130, (G.atom_bytes(rows, a.hidden),), device=dev, dtype=torch.uint8)
+    w1 = torch.randint(0, 256, (a.experts, 2 * a.inter, a.hidden // 2), device=dev, dtype=torch.uint8)
+    sf1 = torch.randint(125, 130, (a.experts, G.atom_bytes(2 * a.inter, a.hidden)), device=dev, dtype=torch.uint8)
+    w2 = torch.randint(0, 256, (a.experts, a.hidden, a.inter // 2), device=dev, dtype=torch.uint8)
+    sf2 = torch.randint(125, 130, (a.experts, G.atom_bytes(a.hidden, a.inter)), device=dev, dtype=torch.uint8)
+    state = {}
+
+    def fc1():
+        state["act"] = M.grouped_gemm_mx(xq, sfx, w1, sf1, pl, swiglu_mxfp8=True, bn=a.bn or 256)
+
+    fc1()
+    act_q, sf_act = state["act"]
+    ms1 = timeit(fc1, a.iters)
+    ms2 = timeit(lambda: M.grouped_gemm_mx(act_q, sf_act, w2, sf2, pl, bn=a.bn or 256), a.iters)
+    Kernels.get().check_error()
+    real = sum(min(live, live) for _ in range(1))
+    report("moe_fc1_mxfp8_mxfp4_swiglu_mxfp8", ms1, flops=2.0 * real * 2 * a.inter * a.hidden,
+           nbytes=w1.numel() + real * a.hidden + real * a.inter, rows=real, experts=a.experts, hidden=a.hidden, inter=a.inter)
+    report("moe_fc2_mxfp8_mxfp4_bf16", ms2, flops=2.0 * real * a.inter * a.hidden,
+           nbytes=w2.numel() + real * a.inter + real * a.hidden * 2, rows=real, experts=a.experts, hidden=a.hidden, inter=a.inter)
+
+
 def bench_gdn(a):
     """Gated DeltaNet decode step (conv + rule + gated norm) for `seqs` sequences, or a prefill chunk of `rows` rows of one."""
     from . import gdn as G
@@ -246,6 +301,13 @@ def main(argv=None):
     g8 = sub.add_parser("gemm_fp8")
     g8.add_argument("--m", type=int, default=4096); g8.add_argument("--n", type=int, default=4096); g8.add_argument("--k", type=int, default=4096)
     g8.add_argument("--bn", type=int, default=None)
+    gx = sub.add_parser("gemm_mx")
+    gx.add_argument("--m", type=int, default=4096); gx.add_argument("--n", type=int, default=4096); gx.add_argument("--k", type=int, default=4096)
+    gx.add_argument("--bn", type=int, default=None); gx.add_argument("--fp4", action="store_true", help="MXFP4 weights (packed e2m1)")
+    mx = sub.add_parser("moe_mx")
+    mx.add_argument("--tokens", type=int, default=16384); mx.add_argument("--experts-total", type=int, default=384)
+    mx.add_argument("--experts", type=int, default=96, help="experts held by this rank"); mx.add_argument("--top-k", type=int, default=8)
+    mx.add_argument("--hidden", type=int, default=7168); mx.add_argument("--inter", type=int, default=2048); mx.add_argument("--bn", type=int, default=None)
     mo = sub.add_parser("moe")
     mo.add_argument("--tokens", type=int, default=2048); mo.add_argument("--experts", type=int, default=128); mo.add_argument("--top-k", type=int, default=8)
     mo.add_argument("--hidden", type=int, default=2048); mo.add_argument("--inter", type=int, default=768)
@@ -268,10 +330,10 @@ def main(argv=None):
     ml.add_argument("--splits", type=int, default=None)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=4096); n.add_argument("--n", type=int, default=4096)
-    for s in (g, d, p, n, g8, mo, gd, ml):
+    for s in (g, d, p, n, g8, mo, gd, ml, gx, mx):
         s.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "gdn": bench_gdn, "gemm_fp8": bench_gemm_fp8, "moe": bench_moe, "attn_decode": bench_attn_decode, "mla_decode": bench_mla_decode, "attn_prefill": bench_attn_prefill, "norm": bench_norm}[a.op](a)
+    {"gemm": bench_gemm, "gemm_mx": bench_gemm_mx, "moe_mx": bench_moe_mx, "gdn": bench_gdn, "gemm_fp8": bench_gemm_fp8, "moe": bench_moe, "attn_decode": bench_attn_decode, "mla_decode": bench_mla_decode, "attn_prefill": bench_attn_prefill, "norm": bench_norm}[a.op](a)
 
 
 if __name__ == "__main__":

@@ -39,8 +39,9 @@ def max_tiles(entries: int, experts: int) -> int:
     return entries // BM + experts
 
 
-def plan(ids: torch.Tensor, experts_local: int, e_lo: int = 0):
-    """-> dict(perm [T*k], offsets [E+1], tiles [max,4], tile_count [1], rows [1])."""
+def plan(ids: torch.Tensor, experts_local: int, e_lo: int = 0, aligned: bool = False):
+    """-> dict(perm [T*k], offsets [E+1], tiles [max,4], tile_count [1], rows [1]). `aligned`: every expert's rows start
+    on a 128-row boundary of the sorted buffer (what the block-scaled GEMM needs); `rows_bound` is then the buffer size."""
     kn = Kernels.get(ids.device)
     entries = ids.numel()
     dev = ids.device
@@ -49,8 +50,9 @@ def plan(ids: torch.Tensor, experts_local: int, e_lo: int = 0):
            "offsets": torch.empty(experts_local + 1, dtype=torch.int32, device=dev),
            "tiles": torch.zeros(mt, 4, dtype=torch.int32, device=dev),
            "tile_count": torch.zeros(1, dtype=torch.int32, device=dev),
-           "rows": torch.zeros(1, dtype=torch.int32, device=dev), "max_tiles": mt}
-    kn.launch("moe", "kern_moe_plan", (1,), (1024,),
+           "rows": torch.zeros(1, dtype=torch.int32, device=dev), "max_tiles": mt,
+           "rows_bound": (-(-entries // BM) + experts_local) * BM if aligned else entries}
+    kn.launch("moe", "kern_moe_plan_aligned" if aligned else "kern_moe_plan", (1,), (1024,),
               [ptr(ids), ptr(out["perm"]), ptr(out["offsets"]), ptr(out["tiles"]), ptr(out["tile_count"]), ptr(out["rows"]),
                i32(entries), i32(e_lo), i32(e_lo + experts_local), i32(BM), i32(mt), ptr(kn.err_word()), i32(0), i32(0)],
               shared_mem=2 * experts_local * 4)
@@ -130,5 +132,106 @@ def moe_reference(x, w_router, w1, w2, k, bias=None, mode="sigmoid", scale=1.0, 
         h = xf[tok] @ w1[e].float().t()
         act = (F.silu(h[:, :inter]) * h[:, inter:]).to(torch.bfloat16).float()
         y = (act @ w2[e].float().t()).to(torch.bfloat16).float()
+        out.index_add_(0, tok, y * wts[tok, j][:, None])
+    return out
+
+
+# ---- block-scaled experts: MXFP8 activations x MXFP4 weights ------------------------------------------------------
+def prepare_expert_weights_mx(w1: torch.Tensor, w2: torch.Tensor):
+    """bf16/fp32 expert weights -> what the block-scaled layer reads: w1 [E, 2I, H] (gate rows then up rows) is
+    re-ordered into groups of 128 rows = 64 gate rows + the matching 64 up rows, both are quantised to MXFP4 (packed
+    nibbles) with their scales as atoms per expert. Returns (w1_q [E, 2I, H/2], sf1 [E, atoms], w2_q [E, H, I/2], sf2)."""
+    from . import gemm_mx as G
+
+    e, two_i, h = w1.shape
+    inter = two_i // 2
+    assert inter % 64 == 0
+    gate, up = w1[:, :inter].reshape(e, inter // 64, 64, h), w1[:, inter:].reshape(e, inter // 64, 64, h)
+    w1i = torch.cat([gate, up], 2).reshape(e, two_i, h)
+    q1, s1, q2, s2 = [], [], [], []
+    for x in range(e):
+        q, sf = G.quantize_mxfp4_torch(w1i[x])
+        q1.append(q); s1.append(G.sf_to_atoms(sf))
+        q, sf = G.quantize_mxfp4_torch(w2[x])
+        q2.append(q); s2.append(G.sf_to_atoms(sf))
+    return torch.stack(q1), torch.stack(s1), torch.stack(q2), torch.stack(s2)
+
+
+def gather_quant_mx(x: torch.Tensor, perm: torch.Tensor, k: int, rows_bound: int):
+    """Expert-sorted MXFP8 activations (+ scale atoms) straight from the bf16 rows."""
+    from . import gemm_mx as G
+
+    kn = Kernels.get(x.device)
+    t, h = x.shape
+    q = torch.zeros(rows_bound, h, dtype=torch.uint8, device=x.device)
+    sf = torch.full((G.atom_bytes(rows_bound, h),), 0x7F, dtype=torch.uint8, device=x.device)
+    kn.launch("gemm_mx", "kern_moe_gather_quant_mxfp8", (t * k,), (128,), [ptr(x), ptr(perm), ptr(q), ptr(sf), i32(t * k), i32(k), i32(h)])
+    return q, sf
+
+
+def grouped_gemm_mx(a_q, sfa, w_q, sfw, pl: dict, swiglu_mxfp8: bool = False, bn: int = 256):
+    """Routed block-scaled GEMM over the planner's (aligned) tile table. a_q [rows, K] e4m3, w_q [E, N, K/2] packed e2m1,
+    scales as atoms (sfw per expert). Store form -> bf16 [rows, N]; `swiglu_mxfp8` -> (e4m3 [rows, N/2], its scale atoms)."""
+    from . import gemm_mx as G
+    from .launcher import i64
+
+    kn = Kernels.get(a_q.device)
+    rows, k = a_q.shape
+    e, n, half = w_q.shape
+    assert half * 2 == k and k % G.BK == 0 and n % bn == 0 and w_q.is_contiguous() and sfw.is_contiguous()
+    tma_a = kn.tensor_map_2d(a_q, G.BM, G.BK)
+    tma_b = kn.dev.encode_tensor_map(w_q.data_ptr(), G.TM_16U4_ALIGN16B, [k, n, e], [half, n * half], [G.BK, bn, 1], 128, 256, False)
+    stages = 4 if bn == 256 else 6
+    smem = 1024 + stages * (G.BM * G.BK + bn * G.BK + (2048 if bn == 256 else 1024)) + 256
+    if swiglu_mxfp8:
+        out = torch.zeros(rows, n // 2, dtype=torch.uint8, device=a_q.device)
+        sf_out = torch.full((G.atom_bytes(rows, n // 2),), 0x7F, dtype=torch.uint8, device=a_q.device)
+        entry = f"kern_moe_gemm_mxfp8_mxfp4_swiglu_mxfp8_n{bn}"
+    else:
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=a_q.device)
+        sf_out = None
+        entry = f"kern_moe_gemm_mxfp8_mxfp4_n{bn}"
+    kn.launch("gemm_mx", entry, (kn.sm_count,), (192,),
+              [tma_a, tma_b, ptr(sfa), ptr(sfw), ptr(out), i32(rows), i32(n), i32(k), i32(out.stride(0)), ptr(kn.err_word()),
+               ptr(pl["tiles"]), ptr(pl["tile_count"]), i64(sfw.stride(0)), ptr(sf_out)], shared_mem=smem)
+    return (out, sf_out) if swiglu_mxfp8 else out
+
+
+def moe_layer_mx(x, w_router, w1_q, sf1, w2_q, sf2, k, bias=None, mode="sigmoid", scale=1.0, e_lo=0, shared=None, bn=256):
+    """The routed layer with MXFP4 expert weights and MXFP8 activations: route (bf16 router) -> aligned plan ->
+    gather + quantise -> FC1 (SwiGLU, MXFP8 out) -> FC2 (bf16 out) -> weighted combine."""
+    from .gemm import gemm
+
+    logits = gemm(x, w_router, epilogue="f32")
+    ids, wts = route(logits, k, bias, mode, True, scale)
+    pl = plan(ids, w1_q.shape[0], e_lo, aligned=True)
+    xq, sfx = gather_quant_mx(x, pl["perm"], k, pl["rows_bound"])
+    act_q, sf_act = grouped_gemm_mx(xq, sfx, w1_q, sf1, pl, swiglu_mxfp8=True, bn=bn)
+    yp = grouped_gemm_mx(act_q, sf_act, w2_q, sf2, pl, bn=bn)
+    out = torch.empty_like(x)
+    return combine(yp, pl["perm"], wts, out, shared)
+
+
+def moe_reference_mx(x, w_router, w1, w2, k, bias=None, mode="sigmoid", scale=1.0, e_lo=0, shared=None):
+    """fp32 statement of the block-scaled layer: the same quantisation points (activations to MXFP8 before each expert
+    GEMM, weights to MXFP4), everything else in fp32. w1 / w2 are the unquantised weights in checkpoint order."""
+    from . import gemm_mx as G
+
+    xf = x.float()
+    logits = xf @ w_router.float().t()
+    ids, wts = route_reference(logits, k, bias, mode, True, scale)
+    out = torch.zeros_like(xf) if shared is None else shared.float().clone()
+    inter = w1.shape[1] // 2
+    xq = G.dequant_mxfp8(*G.quantize_mxfp8_torch(xf))
+    for e in range(w1.shape[0]):
+        tok, j = torch.nonzero(ids == e + e_lo, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        w1d = G.dequant_mxfp4(*G.quantize_mxfp4_torch(w1[e].float()))
+        w2d = G.dequant_mxfp4(*G.quantize_mxfp4_torch(w2[e].float()))
+        h = xq[tok] @ w1d.t()
+        act = F.silu(h[:, :inter]) * h[:, inter:]
+        act = G.dequant_mxfp8(*G.quantize_mxfp8_torch(act))
+        y = (act @ w2d.t()).to(torch.bfloat16).float()
         out.index_add_(0, tok, y * wts[tok, j][:, None])
     return out

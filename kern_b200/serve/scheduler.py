@@ -285,7 +285,7 @@ class Scheduler:
                 batch.append((r.seq, r.prompt[r.fed:r.fed + n]))
                 kinds.append((r, "prefill", n))
             budget -= n
-        use_round = self.round is not None and not batch       # a round is a fixed-shape call of its own
+        use_round = self.round is not None and not batch and bool(decoding)     # a round is a fixed-shape call of its own
         for r in decoding:
             last = r.out[-1] if r.out else r.prompt[-1]       # a prefill that emits nothing leaves the last prompt token to the step
             batch.append((r.seq, [last] * (self.rows if use_round else 1)))

@@ -19,8 +19,29 @@ def available() -> bool:
     return (PKG / "toy-paged.json").exists()
 
 
+def oracle():
+    """The reference's own statement of the toy arithmetic (tools/toy/model.py), loaded from the installed copy."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("kern_ref_toy_model", ROOT / "baseline" / "_ref" / "tools" / "toy" / "model.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def check_against_oracle(reqs, doc: dict, limit: int) -> int:
+    """Requests whose served tokens equal the oracle's greedy continuation (up to its end-of-sequence)."""
+    model = oracle()
+    ok = 0
+    for r in reqs:
+        want = model.generate(r.prompt, limit, doc)
+        got = [t for t in r.out[:limit]]
+        ok += got[:len(want)] == want and (len(want) == limit or (len(got) > len(want) and got[len(want)] == model.EOS))
+    return ok
+
+
 def run(concurrency: int = 256, requests: int | None = None, out_len: int = 256, seed: int = 0, gpu: int = 0,
-        target: str = "toy-paged") -> dict:
+        target: str = "toy-paged", verify: int = 6) -> dict:
     import numpy as np
 
     from ..engine import Engine
@@ -53,12 +74,14 @@ def run(concurrency: int = 256, requests: int | None = None, out_len: int = 256,
     wall = time.monotonic() - t0
     rt.check_error()
     tokens = sum(len(r.out) for r in reqs)
+    checked = reqs[:: max(1, len(reqs) // verify)][:verify] if verify else []
+    exact = check_against_oracle(checked, rt.doc, out_len) if checked else 0
     ttft = sorted(r.first_token_at - t0 for r in reqs)
     gaps = sorted(b - a for r in reqs for a, b in zip(r.token_times, r.token_times[1:]))
     return {"output_tok_s": tokens / wall, "tokens": tokens, "wall_s": wall, "requests": requests, "concurrency": concurrency,
             "steps": sch.stats.steps - steps0, "gpu_launches": rt.launches_total - launches0,
             "ttft_ms_p50_all_submitted_at_t0": 1e3 * ttft[len(ttft) // 2], "tpot_ms_p50": 1e3 * gaps[len(gaps) // 2],
-            "prefix_hit_tokens": sch.stats.prefix_hit_tokens}
+            "prefix_hit_tokens": sch.stats.prefix_hit_tokens, "oracle_checked": len(checked), "oracle_exact": exact}
 
 
 def main(args) -> int:
@@ -74,5 +97,6 @@ def main(args) -> int:
                    "concurrency": conc, "requests": res["requests"], "seq_len": "prompts 512-2048 uniform, 256 outputs"},
         "ttft_ms_p50_all_submitted_at_t0": round(res["ttft_ms_p50_all_submitted_at_t0"], 2),
         "tpot_ms_p50": round(res["tpot_ms_p50"], 3), "wall_s": round(res["wall_s"], 2), "steps": res["steps"],
-        "gpu_launches": res["gpu_launches"]}))
+        "gpu_launches": res["gpu_launches"],
+        "exact_vs_reference_oracle": f"{res['oracle_exact']}/{res['oracle_checked']} sampled requests equal tools/toy/model.py token for token"}))
     return 0
