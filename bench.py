@@ -85,10 +85,11 @@ def main():
     ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"],
                     help="N > 1: tensor parallel over one batch (the configuration the metric names; default), or "
                          "data-parallel replicas with the concurrency split between them (reported for comparison only)")
-    ap.add_argument("--tp-layout", default="sp", choices=["sp", "fused", "unfused"],
-                    help="tensor-parallel ragged program: sequence-parallel rows with GEMM + reduce-scatter and all-gather + GEMM "
-                         "kernels (default); replicated rows with the GEMM epilogue pushing partials to the all-reduce; or "
-                         "replicated rows with a plain GEMM and the all-reduce kernel pushing them (A/B)")
+    ap.add_argument("--tp-layout", default="sp", choices=["sp", "sp-pull", "fused", "unfused"],
+                    help="tensor-parallel ragged program: sequence-parallel rows (GEMM + reduce-scatter epilogue, reduce + norm on "
+                         "own rows, normed rows pushed to every rank; default), the same with the all-gather pulled inside the next "
+                         "GEMM, replicated rows with the GEMM epilogue pushing partials to the all-reduce, or replicated rows with a "
+                         "plain GEMM and the all-reduce kernel pushing them (A/B)")
     ap.add_argument("--profile", action="store_true", help="after the timed region, run one more step with per-call timing and print the cost by op to stderr")
     args = ap.parse_args()
 
@@ -129,7 +130,8 @@ def main():
         from kern_b200.models import dense_tp
         from kern_b200.parallel import group
 
-        doc = dense_tp.build_manifest_tp(cfg, fused=args.tp_layout != "unfused", sp=args.tp_layout == "sp")
+        doc = dense_tp.build_manifest_tp(cfg, fused=args.tp_layout != "unfused", sp=args.tp_layout.startswith("sp"),
+                                         sp_push=args.tp_layout == "sp")
         rt = Runtime(doc, gpu=local, memory_fraction=0.90, topology=group.topology(doc["topology"]["groups"], rank, world))
         dense.load_random_weights(rt, cfg, seed=args.seed)
         group.start(rt)

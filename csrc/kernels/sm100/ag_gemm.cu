@@ -37,10 +37,11 @@ KERN_AG_GEMM_ENTRY(kern_ag_gemm_bf16_tn_n128, 128)
       name(const __grid_constant__ CUtensorMap tma_g, const __grid_constant__ CUtensorMap tma_b, void* C, int M,      \
            int N, int K, int ldc, int* err, const unsigned long long* peers, uint32_t* flags, uint32_t* epochs,       \
            const uint32_t* ready, const uint32_t* epoch_word, int rank, int nranks, int max_blocks,                   \
-           long long timeout_ns) {                                                                                   \
+           long long timeout_ns, int pushed) {                                                                       \
     kern::AgArgs ag;                                                                                                 \
     ag.peers = peers; ag.flags = flags; ag.epochs = epochs; ag.rank = rank; ag.nranks = nranks;                      \
     ag.max_blocks = max_blocks; ag.ready = ready; ag.epoch_word = epoch_word; ag.timeout_ns = timeout_ns;            \
+    ag.pushed = pushed;                                                                                              \
     if ((M + kern::BM - 1) / kern::BM > max_blocks) { /* every block needs its counter */                            \
       if (threadIdx.x == 0 && blockIdx.x == 0) kern::set_error(err, kern::ERR_BOUNDS);                               \
       return;                                                                                                        \

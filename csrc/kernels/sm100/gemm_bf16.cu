@@ -85,6 +85,7 @@ struct AgArgs {
   int rank = 0, nranks = 1, max_blocks = 0;
   const uint32_t* ready = nullptr;             // sequence-parallel: [nranks] epochs at which each rank's rows were final
   const uint32_t* epoch_word = nullptr;        //   and this rank's own epoch
+  int pushed = 0;                              //   1: the owners pushed their rows here already; only wait for the flags
   long long timeout_ns = 2000000000ll;
 };
 
@@ -307,7 +308,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
       // blocks nobody gathers in this launch (own rows, blocks past the last row) arrive at once: every counter moves
       // by the grid size in every launch, whatever the row count
       for (int b = gt; b < ag.max_blocks; b += GT) {
-        const bool remote = b < num_m && (sp || b / ag_bpr != ag.rank);
+        const bool remote = b < num_m && !ag.pushed && (sp || b / ag_bpr != ag.rank);
         if (!remote) atomicAdd(ag.flags + b, 1u);
       }
       // The blocks to pull, in the order the tiles will want them, form one run of 16-byte vectors that is cut into units
@@ -317,7 +318,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
       // A block's counter moves once every unit that touches the block has been stored.
       const size_t row_vecs = (size_t)K * 2 / 16;
       const size_t vecs = (size_t)BM * row_vecs, stride = (size_t)gridDim.x * GT, span = stride * 8;
-      const int pull_blocks = sp ? num_m : num_m - ag_bpr;
+      const int pull_blocks = ag.pushed ? 0 : (sp ? num_m : num_m - ag_bpr);
       const size_t total = (size_t)pull_blocks * vecs;
       const int units = (*abort_flag != 0) ? 0 : (int)((total + span - 1) / span);
       auto block_at = [&](int i) { return ((sp ? 0 : ag_bpr) + i + ag_first) % num_m; };   // i-th block in pull order

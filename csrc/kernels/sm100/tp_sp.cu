@@ -7,9 +7,12 @@
 // (tp_gemm.cu, grid = 0 form). This kernel, on the owner:
 //   x[row] += sum over ranks of slot[r][idx]        (fp32 sum, one rounding)
 //   g[row]  = rmsnorm(x[row]) * w                   (g: the all-gather buffer the next GEMM pulls from)
-// and nothing is sent back: the QKV / gate-up GEMM that follows pulls the rows it needs out of every owner's g while
-// its own tiles run (ag_gemm.cu, `_sp` entries). Per layer and rank the link carries (n-1)/n of the message once in
-// each direction, and the norm / residual work is 1/n of the replicated layout's.
+// The all-gather half comes in two forms. Pull (g_peers null): nothing is sent back, the QKV / gate-up GEMM that follows
+// pulls the rows it needs out of every owner's g while its own tiles run (ag_gemm.cu, `_sp` entries). Push (g_peers set):
+// the owner writes each normed row straight into every rank's g — posted stores keep the link far busier than loads
+// issued from the SMs do — and the following GEMM only waits for the owners' "rows final" flags. Either way the link
+// carries (n-1)/n of the message once in each direction per layer, and the norm / residual work is 1/n of the
+// replicated layout's.
 //
 // Synchronisation, all by epoch words that only grow (captured graphs replay without host help):
 //   flags[0][r]  "rank r has launched this call's reduce kernel": written by r on every peer at kernel start — r's GEMM
@@ -64,7 +67,8 @@ KERN_DEVICE bool wait_epoch(const uint32_t* flag, uint32_t epoch, long long time
 extern "C" __global__ void __launch_bounds__(kThreads)
     kern_sp_reduce_norm(__nv_bfloat16* x, __nv_bfloat16* g, const __nv_bfloat16* w, const __nv_bfloat16* comm,
                         uint32_t* flags, const unsigned long long* flag_peers, uint32_t* state, int* err, int rank,
-                        int nranks, int rows, int hidden, int slot_rows, float eps, int plus_one, long long timeout_ns) {
+                        int nranks, int rows, int hidden, int slot_rows, float eps, int plus_one, long long timeout_ns,
+                        const unsigned long long* g_peers) {
   __shared__ int failed;
   pdl_wait();
   if (threadIdx.x == 0) failed = (err != nullptr && *reinterpret_cast<volatile int*>(err) != 0) ? 1 : 0;
@@ -137,7 +141,15 @@ extern "C" __global__ void __launch_bounds__(kThreads)
         add8(ww, wv[v]);
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] = f[e] * inv * (plus_one ? ww[e] + 1.f : ww[e]);
-        yr[v] = pack8(o);
+        const uint4 out = pack8(o);
+        if (g_peers == nullptr) {
+          yr[v] = out;
+        } else {
+          // push form of the all-gather: the owner writes its normed row into every rank's g (posted peer stores, a whole
+          // 512-byte run per warp instruction); the GEMM that follows only waits for the owners' flags
+          for (int p = 0; p < nranks; ++p)
+            reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g_peers[(p + rank) % nranks]) + (size_t)row * hidden)[v] = out;
+        }
       }
     }
   }

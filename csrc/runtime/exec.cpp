@@ -156,11 +156,13 @@ void Runtime::compile_call(CompiledProgram& out, const std::string& pname, const
                                                                   {"extern:cublaslt_bf16_tn_acc", ExternKind::GemmBf16Acc},
                                                                   {"extern:cublas_bf16_tn_f32", ExternKind::GemmBf16F32},
                                                                   {"extern:cublaslt_fp8_tn", ExternKind::GemmFp8},
-                                                                  {"extern:cublaslt_fp8_tn_f32", ExternKind::GemmFp8F32}};
+                                                                  {"extern:cublaslt_fp8_tn_f32", ExternKind::GemmFp8F32},
+                                                                  {"extern:cublaslt_mxfp8_tn", ExternKind::GemmMxfp8}};
       for (auto& k : kinds) if (l.entry == k.first) cl.ext = k.second;
       if (cl.ext == ExternKind::None)
         throw std::runtime_error(where + ": built-in `" + l.entry + "` is not provided by this runtime");
-      const bool fp8 = cl.ext == ExternKind::GemmFp8 || cl.ext == ExternKind::GemmFp8F32;
+      const bool mx = cl.ext == ExternKind::GemmMxfp8;     // same argument list as fp8; the scales are UE8M0 atoms
+      const bool fp8 = cl.ext == ExternKind::GemmFp8 || cl.ext == ExternKind::GemmFp8F32 || mx;
       // e4m3 operands with per-tensor device scales: [a, w, c, a_scale, w_scale, m, n, k] plus an optional C row stride
       const size_t so = fp8 ? 2 : 0;
       if (fp8 ? (largs.size() < 8 || largs.size() > 9) : (largs.size() < 6 || largs.size() > 8))
@@ -193,7 +195,13 @@ void Runtime::compile_call(CompiledProgram& out, const std::string& pname, const
       if (!fp8 && largs.size() >= 8) cl.lda = expr_of(7);
       cl.a_rows = a_ext;   // bytes available behind the pointers: row counts follow at launch
       cl.w_rows = w_ext;
-      if (fp8 && !gemm_fns_.count("kern_gemm_e4m3_tn_n128")) {
+      if (mx && !gemm_fns_.count("kern_gemm_mxfp8_tn_n128")) {
+        for (int bn : {256, 128}) {
+          const std::string e = "kern_gemm_mxfp8_tn_n" + std::to_string(bn);
+          gemm_fns_[e] = dev_->function(builtin_gemm_mx_, e);
+        }
+      }
+      if (fp8 && !mx && !gemm_fns_.count("kern_gemm_e4m3_tn_n128")) {
         for (const char* epi : {"", "_f32"})
           for (int bn : {256, 128, 64}) {
             const std::string e = std::string("kern_gemm_e4m3_tn") + epi + "_n" + std::to_string(bn);
@@ -307,6 +315,36 @@ size_t Runtime::launch_gemm(const CompiledLaunch& l, const VarMap& vars, CUstrea
   const uint64_t m = ev(l.m), n = ev(l.n), k = ev(l.k);
   if (m == 0 || n == 0) return 0;
   const uint64_t ldc = l.ldc ? ev(*l.ldc) : n, lda = l.lda ? ev(*l.lda) : k;
+  if (l.ext == ExternKind::GemmMxfp8) {
+    // MXFP8 x MXFP8 -> bf16: e4m3 bytes, one UE8M0 scale per 32 elements of K in 128 x 4 atoms of 512 bytes (atom
+    // (r / 128, b / 4) at 512 (r / 128 * ceil(k / 128) + b / 4), entry (r % 32) 16 + (r % 128 / 32) 4 + b % 4): the layout
+    // the reference's library call takes (crates/kern-runtime/src/cublas.rs:395-400), which is what tcgen05.cp wants.
+    if (k % 128) throw std::runtime_error("mxfp8 GEMM `" + l.label + "`: k must be a multiple of 128 (one stage of the block-scaled kernel)");
+    const uint64_t tiles_m = (m + 127) / 128;
+    const int bn = (n % 256 == 0 && tiles_m * (n / 256) >= (uint64_t)dev_->sm_count() / 2) ? 256 : 128;
+    auto tmap8 = [&](uint64_t ptr, uint64_t avail_bytes, uint64_t box_rows) {
+      TensorMapSpec sp;
+      sp.dtype = 0;
+      sp.dims = {k, std::max<uint64_t>(1, avail_bytes / k)};
+      sp.strides = {k};
+      sp.box = {128, (uint32_t)box_rows};
+      sp.swizzle = 128;
+      sp.l2_promotion = 256;
+      return dev_->encode_tensor_map(ptr, sp);
+    };
+    alignas(64) std::array<uint8_t, 128> ta = tmap8(l.a_ptr, l.a_rows, 128);
+    alignas(64) std::array<uint8_t, 128> tb = tmap8(l.w_ptr, std::min<uint64_t>(l.w_rows, n * k), bn);
+    CUfunction fn = gemm_fns_.at("kern_gemm_mxfp8_tn_n" + std::to_string(bn));
+    uint64_t c = l.c_ptr, sa = l.sa_ptr, sw = l.sw_ptr, err = err_word_;
+    int mi = (int)m, ni = (int)n, ki = (int)k, ldci = (int)ldc;
+    void* params[] = {ta.data(), tb.data(), &sa, &sw, &c, &mi, &ni, &ki, &ldci, &err};
+    LaunchDims d;
+    d.grid[0] = (unsigned)std::min<uint64_t>(tiles_m * ((n + bn - 1) / bn), dev_->sm_count());
+    d.block[0] = 192;
+    d.shared_mem = 1024 + (bn == 256 ? 4 : 6) * (128 * 128 + bn * 128 + (bn == 256 ? 2048 : 1024)) + 256;
+    dev_->launch(fn, d, s, params);
+    return 1;
+  }
   if (l.ext == ExternKind::GemmFp8 || l.ext == ExternKind::GemmFp8F32) {
     // one byte per element, 128-element K boxes; the tile width as the bf16 picker would choose it (no 32-wide tile)
     const bool f32o = l.ext == ExternKind::GemmFp8F32;

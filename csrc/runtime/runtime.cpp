@@ -1,6 +1,9 @@
 // Runtime: load, allocation, weights (see runtime.hpp). Compilation and execution live in exec.cpp.
 #include "runtime.hpp"
 
+#include <cstdio>
+#include <cstdlib>
+
 #include <dirent.h>
 
 #include <fstream>
@@ -100,6 +103,15 @@ uint64_t Runtime::rank(const std::string& group) const {
   return it->second.index;
 }
 
+// The built-in modules (the kernels behind the `extern:` vocabulary) sit beside the package's own cubins, or, for a
+// package that brings only its own, in the directory KERN_B200_KERNELS names (the in-tree kernels).
+std::string Runtime::builtin_path(const std::string& file) const {
+  const std::string here = kernels_dir_ + "/" + file;
+  if (FILE* f = std::fopen(here.c_str(), "rb")) { std::fclose(f); return here; }
+  if (const char* dir = std::getenv("KERN_B200_KERNELS")) return std::string(dir) + "/" + file;
+  return here;
+}
+
 // Modules are found by the hash of their bytes: file names are labels. Every *.cubin under the
 // kernels directory is hashed once; a manifest module resolves to the file with its sha256.
 void Runtime::load_modules() {
@@ -117,14 +129,15 @@ void Runtime::load_modules() {
   for (auto& okv : m_.ops)
     for (auto& l : okv.second.launches)
       needs_gemm |= l.is_extern && (l.entry.rfind("extern:cublaslt_bf16", 0) == 0 || l.entry.rfind("extern:cublas_bf16", 0) == 0);
-  if (needs_gemm) {
-    const std::string path = kernels_dir_ + "/gemm_bf16.cubin";
-    builtin_gemm_ = dev_->load_module(read_file(path));
-  }
-  bool needs_gemm8 = false;
+  if (needs_gemm) builtin_gemm_ = dev_->load_module(read_file(builtin_path("gemm_bf16.cubin")));
+  bool needs_gemm8 = false, needs_mx = false;
   for (auto& okv : m_.ops)
-    for (auto& l : okv.second.launches) needs_gemm8 |= l.is_extern && l.entry.rfind("extern:cublaslt_fp8", 0) == 0;
-  if (needs_gemm8) builtin_gemm8_ = dev_->load_module(read_file(kernels_dir_ + "/gemm_fp8.cubin"));
+    for (auto& l : okv.second.launches) {
+      needs_gemm8 |= l.is_extern && l.entry.rfind("extern:cublaslt_fp8", 0) == 0;
+      needs_mx |= l.is_extern && l.entry == "extern:cublaslt_mxfp8_tn";
+    }
+  if (needs_gemm8) builtin_gemm8_ = dev_->load_module(read_file(builtin_path("gemm_fp8.cubin")));
+  if (needs_mx) builtin_gemm_mx_ = dev_->load_module(read_file(builtin_path("gemm_mx.cubin")));
   // a multi-rank manifest runs only modules declared free of cluster-multicast copies
   bool multi = false;
   for (auto& kv : topo_) multi |= kv.second.size >= 2;

@@ -59,7 +59,7 @@ struct CompiledArg {
   std::vector<Patch> patches;
 };
 
-enum class ExternKind { None, GemmBf16, GemmBf16Acc, GemmBf16F32, GemmFp8, GemmFp8F32, Nccl };
+enum class ExternKind { None, GemmBf16, GemmBf16Acc, GemmBf16F32, GemmFp8, GemmFp8F32, GemmMxfp8, Nccl };
 
 struct CompiledLaunch {
   std::string label;           // op name / call label for traces
@@ -185,6 +185,8 @@ class Runtime {
   std::map<std::string, CUmodule> modules_;
   CUmodule builtin_gemm_ = nullptr;
   CUmodule builtin_gemm8_ = nullptr;     // e4m3 GEMMs behind `extern:cublaslt_fp8_tn[_f32]`
+  CUmodule builtin_gemm_mx_ = nullptr;   // block-scaled GEMM behind `extern:cublaslt_mxfp8_tn`
+  std::string builtin_path(const std::string& file) const;
   std::map<std::string, CUfunction> gemm_fns_;
   std::map<std::string, Allocation> buffers_;
   std::map<std::string, StateAlloc> states_;

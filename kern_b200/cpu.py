@@ -767,7 +767,18 @@ def _extern_gemm(acc: bool, f32_out: bool, fp8: bool):
     return run
 
 
+def _extern_gemm_mx(g, a, w, c, sa, sw, m, n, k, ldc=None):
+    """`extern:cublaslt_mxfp8_tn`: e4m3 operands, UE8M0 scales per 32 elements of K in 128 x 4 atoms."""
+    from .ops import gemm_mx as G
+
+    A = G.dequant_mxfp8(a[: m * k].view(m, k), G.atoms_to_sf(sa[: G.atom_bytes(m, k)], m, k))
+    W = G.dequant_mxfp8(w[: n * k].view(n, k), G.atoms_to_sf(sw[: G.atom_bytes(n, k)], n, k))
+    C = torch.as_strided(c, (m, n), (ldc or n, 1), c.storage_offset())
+    C.copy_((A @ W.t()).to(torch.bfloat16))
+
+
 CPU_KERNELS.update({
+    "extern:cublaslt_mxfp8_tn": _extern_gemm_mx,
     "extern:cublaslt_bf16_tn": _extern_gemm(False, False, False), "extern:cublaslt_bf16_tn_acc": _extern_gemm(True, False, False),
     "extern:cublas_bf16_tn_f32": _extern_gemm(False, True, False), "extern:cublaslt_fp8_tn": _extern_gemm(False, False, True),
     "extern:cublaslt_fp8_tn_f32": _extern_gemm(False, True, True)})

@@ -679,24 +679,27 @@ def sp_gemm_scatter_op(n: int, k: int, nranks: int, rows_max: int, group: str = 
 
 
 def sp_reduce_norm_op(hidden: int, eps: float, nranks: int, rows_max: int, group: str = "tp", plus_one: bool = False,
-                      timeout_ns: int = 2_000_000_000) -> dict:
+                      timeout_ns: int = 2_000_000_000, push: bool = True) -> dict:
     """On the rows this rank owns: x += sum of the partials the peers pushed; g = rmsnorm(x) * w. One kernel; it also
-    lines the ranks up (bounded waits on epoch flags). Interface [x, g, w, comm, flags, flags_peers, state, err, rows]."""
+    lines the ranks up (bounded waits on epoch flags). `push`: the normed rows go straight into every rank's g (the
+    all-gather as posted peer stores); off, they stay here and the next GEMM pulls them.
+    Interface [x, g, w, comm, flags, flags_peers, state, err, rows, g_peers]."""
     iface = ["inout buffer<bf16>", "inout buffer<bf16>", "in buffer<bf16>", "inout buffer<bf16>", "inout buffer<u32>",
-             "in buffer<u64>", "inout buffer<u32>", "out buffer<i32>", "i32"]      # comm is inout: the peers write it
+             "in buffer<u64>", "inout buffer<u32>", "out buffer<i32>", "i32", "in buffer<u64>"]      # comm is inout: the peers write it
     return {"params": iface, "impl": {"launches": [{
         "module": "tp_sp", "entry": "kern_sp_reduce_norm", "block": [256, 1, 1], "grid": [SP_GRID, 1, 1],
-        "params": iface[:8] + ["i32", "i32", "i32", "i32", "i32", "f32", "i32", "i64"],
+        "params": iface[:8] + ["i32", "i32", "i32", "i32", "i32", "f32", "i32", "i64", "in buffer<u64>" if push else "i64"],
         "args": [{"param": i} for i in range(8)] + [{"rank": group}, {"i32": nranks}, {"param": 8}, {"i32": hidden},
                                                      {"i32": sp_slot_rows(rows_max, nranks)}, {"f32": eps}, {"i32": int(plus_one)},
-                                                     {"i64": timeout_ns}]}]}}
+                                                     {"i64": timeout_ns}, {"param": 9} if push else {"i64": 0}]}]}}
 
 
 def sp_ag_gemm_op(n: int, k: int, nranks: int, rows_max: int, group: str = "tp", epilogue: str = "store",
-                  timeout_ns: int = 2_000_000_000) -> dict:
+                  timeout_ns: int = 2_000_000_000, pushed: bool = True) -> dict:
     """C[rows, n] = G[rows, k] . W[n, k]^T where G's rows sit on their owners (sub-block ownership): the kernel's gather
     warps pull the foreign rows of each 128-row block over NVLink while the tensor-core warps run the blocks already
-    here. `epilogue`: store | swiglu (c is [rows, n/2] over weights stacked [gate rows ; up rows]).
+    here (`pushed`: the owners wrote them here already, the kernel only waits for their flags).
+    `epilogue`: store | swiglu (c is [rows, n/2] over weights stacked [gate rows ; up rows]).
     Interface [g, g_peers, w, c, blocks, cta_epochs, ready, state, err, rows]; `ready` is row 1 of `sp.flags`."""
     out_cols = n // 2 if epilogue == "swiglu" else n
     suffix = {"store": "", "swiglu": "_swiglu"}[epilogue]
@@ -708,7 +711,7 @@ def sp_ag_gemm_op(n: int, k: int, nranks: int, rows_max: int, group: str = "tp",
                   "grid": [SMS, 1, 1], "shared_mem": gemm_smem(bn),
                   "params": ["bytes<128>", "bytes<128>", "out buffer<bf16>", "i32", "i32", "i32", "i32", "out buffer<i32>",
                              "in buffer<u64>", "inout buffer<u32>", "inout buffer<u32>", "in buffer<u32>", "in buffer<u32>",
-                             "i32", "i32", "i32", "i64"],
+                             "i32", "i32", "i32", "i64", "i32"],
                   "args": [
                       {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
                           "param": 0, "dtype": "bf16", "dims": [k, 0], "strides": [k * 2], "box": [BK, BM], "swizzle": 128,
@@ -718,7 +721,7 @@ def sp_ag_gemm_op(n: int, k: int, nranks: int, rows_max: int, group: str = "tp",
                           "box": [BK, bn // 2 if epilogue == "swiglu" else bn], "swizzle": 128, "l2_promotion": 256}}]}},
                       {"param": 3}, {"param": 9}, {"i32": n}, {"i32": k}, {"i32": out_cols}, {"param": 8}, {"param": 1},
                       {"param": 4}, {"param": 5}, {"param": 6}, {"param": 7}, {"rank": group}, {"i32": nranks},
-                      {"i32": AG_MAX_BLOCKS}, {"i64": timeout_ns}]}
+                      {"i32": AG_MAX_BLOCKS}, {"i64": timeout_ns}, {"i32": int(pushed)}]}
         w = _when("tokens", lo, hi, rows_max)
         if w:
             launch["when"] = w

@@ -21,7 +21,7 @@ from . import common as C
 from .dense import DenseConfig
 
 
-def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True, sp: bool = False) -> dict:
+def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True, sp: bool = False, sp_push: bool = True) -> dict:
     """`fused`: the o/down projections push their partial rows to the reducing rank from the GEMM epilogue
     (GEMM + reduce-scatter in one kernel); off, they store the partial and the all-reduce kernel pushes it.
     `lamport`: decode-sized calls use the flagless one-shot all-reduce."""
@@ -104,9 +104,9 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True
     if sp:
         ops["sp_o_proj"] = C.sp_gemm_scatter_op(h, qd, n, T)
         ops["sp_down_proj"] = C.sp_gemm_scatter_op(h, inter, n, T)
-        ops["sp_reduce_norm"] = C.sp_reduce_norm_op(h, cfg.eps, n, T)
-        ops["sp_qkv_proj"] = C.sp_ag_gemm_op(qkv_dim, h, n, T)
-        ops["sp_gate_up"] = C.sp_ag_gemm_op(2 * inter, h, n, T, epilogue="swiglu")
+        ops["sp_reduce_norm"] = C.sp_reduce_norm_op(h, cfg.eps, n, T, push=sp_push)
+        ops["sp_qkv_proj"] = C.sp_ag_gemm_op(qkv_dim, h, n, T, pushed=sp_push)
+        ops["sp_gate_up"] = C.sp_ag_gemm_op(2 * inter, h, n, T, epilogue="swiglu", pushed=sp_push)
         ops["sp_last_rows"] = C.sp_last_rows_op(h, n)
         ops.pop("last_row")
 
@@ -135,7 +135,7 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True
         def reduce(label: str, w: str) -> dict:
             return {"op": "sp_reduce_norm", "label": label,
                     "args": [B("x"), B("sp.g"), B(w), B("sp.comm"), B("sp.flags"), B("sp.flags_peers"), B("sp.state"), err,
-                             {"var": "tokens"}]}
+                             {"var": "tokens"}, B("sp.g_peers")]}
 
         qkv = ({"op": "qkv_proj", "label": lbl + "qkv", "args": [B("sp.g"), B(f"w.l{i}.qkv"), B("qkv"), {"var": "tokens"}, err]}
                if i == 0 else

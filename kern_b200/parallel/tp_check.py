@@ -136,7 +136,7 @@ def check_allgather(rank, world, local, sizes=(16, 4096, 1 << 20), time_it=False
     return out, times
 
 
-def check_model(rank, world, fused=True, sp=False):
+def check_model(rank, world, fused=True, sp=False, sp_push=True):
     """`sp`: the ragged program in the sequence-parallel layout (scatter epilogue, reduce + norm on own rows, all-gather
     GEMM), with calls of several 128-row blocks, a ragged tail, and a second ragged call after decode steps."""
     from ..engine import Engine
@@ -148,7 +148,7 @@ def check_model(rank, world, fused=True, sp=False):
                             head_dim=64, intermediate=512 * world // 2, rope_theta=10000.0, page_size=16,
                             max_tokens=640 if sp else 256, max_seqs=8, max_context=512 if sp else 256, tp=world)
     weights = dense.random_weights(cfg, seed=0, std=0.05)
-    doc = dense_tp.build_manifest_tp(cfg, fused=fused, sp=sp)
+    doc = dense_tp.build_manifest_tp(cfg, fused=fused, sp=sp, sp_push=sp_push)
     rt = Runtime(doc, gpu=torch.cuda.current_device(), topology=group.topology(doc["topology"]["groups"], rank, world),
                  tokens=cfg.page_size * (160 if sp else 64))
     rt.load_tensors(lambda name: weights[name].cuda())
@@ -270,10 +270,13 @@ def main(argv=None):
 
     if args.only_sp:
         from . import group as _g   # noqa: F401
-        m = check_model(rank, world, sp=True)
-        if rank == 0:
-            print(json.dumps({"check": "tp_model_sp", "world": world, **m}))
-        flag = torch.tensor([int(m["ok"])], device="cuda")
+        ok_all = True
+        for push in (True, False):
+            m = check_model(rank, world, sp=True, sp_push=push)
+            ok_all &= m["ok"]
+            if rank == 0:
+                print(json.dumps({"check": "tp_model_sp", "world": world, "all_gather": "push" if push else "pull", **m}))
+        flag = torch.tensor([int(ok_all)], device="cuda")
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         dist.destroy_process_group()
         return 0 if int(flag) else 1

@@ -13,8 +13,12 @@ from pathlib import Path
 import numpy as np
 import torch
 
+import os
+
 from . import _native
 from .models.common import KERNELS_DIR
+
+os.environ.setdefault("KERN_B200_KERNELS", str(KERNELS_DIR))     # where a foreign package's `extern:` built-ins are found
 
 _NP = {"bf16": np.uint16, "f16": np.float16, "f32": np.float32, "fp8e4m3": np.uint8, "fp8e8m0": np.uint8, "i8": np.int8,
        "i32": np.int32, "u32": np.uint32, "i64": np.int64, "u64": np.uint64, "u8": np.uint8}

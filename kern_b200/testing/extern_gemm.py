@@ -1,11 +1,13 @@
 """A manifest whose ops are the runtime's GEMM built-ins (`extern:cublaslt_bf16_tn[_acc]`, `extern:cublas_bf16_tn_f32`,
-`extern:cublaslt_fp8_tn[_f32]`) — the vocabulary a package written against the reference's runtime names; here the
+`extern:cublaslt_fp8_tn[_f32]`, `extern:cublaslt_mxfp8_tn`) — the vocabulary a package written against the reference's runtime names; here the
 runtime's own tcgen05 kernels serve it. Used by the tests and as an example of the arg forms.
 Reference: crates/kern-runtime/src/compile.rs:174-183 (arg forms), cublas.rs:78 / :329 / :387."""
 from __future__ import annotations
 
 
 def manifest(m_max: int, n: int, k: int) -> dict:
+    from ..ops.gemm_mx import atom_bytes
+
     buf = lambda dt, shape, kind="workspace": {"dtype": dt, "shape": shape, "kind": kind}
     B = lambda name: {"buf": name}
     g6 = ["in buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "i32", "i32", "i32"]
@@ -17,7 +19,9 @@ def manifest(m_max: int, n: int, k: int) -> dict:
                     "c32": buf("f32", [m_max, n], "output"),
                     "a8": buf("u8", [m_max, k], "input"), "w8": buf("u8", [n, k], "input"),
                     "sa": buf("f32", [1], "input"), "sw": buf("f32", [1], "input"),
-                    "c8": buf("bf16", [m_max, n], "output"), "c8f": buf("f32", [m_max, n], "output")},
+                    "c8": buf("bf16", [m_max, n], "output"), "c8f": buf("f32", [m_max, n], "output"),
+                    "sfa": buf("u8", [atom_bytes(m_max, k)], "input"), "sfw": buf("u8", [atom_bytes(n, k)], "input"),
+                    "cmx": buf("bf16", [m_max, n], "output")},
         "ops": {
             "mm": {"params": g6, "impl": ext("extern:cublaslt_bf16_tn")},
             "mm_acc": {"params": ["in buffer<bf16>", "in buffer<bf16>", "inout buffer<bf16>", "i32", "i32", "i32"],
@@ -28,6 +32,8 @@ def manifest(m_max: int, n: int, k: int) -> dict:
                                "i32", "i32", "i32"], "impl": ext("extern:cublaslt_fp8_tn")},
             "mm8_f32": {"params": ["in buffer<u8>", "in buffer<u8>", "out buffer<f32>", "in buffer<f32>", "in buffer<f32>",
                                    "i32", "i32", "i32"], "impl": ext("extern:cublaslt_fp8_tn_f32")},
+            "mmx": {"params": ["in buffer<u8>", "in buffer<u8>", "out buffer<bf16>", "in buffer<u8>", "in buffer<u8>",
+                               "i32", "i32", "i32"], "impl": ext("extern:cublaslt_mxfp8_tn")},
         },
         "programs": {"step": {"calls": [
             {"op": "mm", "args": [B("a"), B("w"), B("c"), {"var": "m"}, {"i32": n}, {"i32": k}]},
@@ -36,6 +42,7 @@ def manifest(m_max: int, n: int, k: int) -> dict:
             {"op": "mm_f32", "args": [B("a"), B("w"), B("c32"), {"var": "m"}, {"i32": n}, {"i32": k}]},
             {"op": "mm8", "args": [B("a8"), B("w8"), B("c8"), B("sa"), B("sw"), {"var": "m"}, {"i32": n}, {"i32": k}]},
             {"op": "mm8_f32", "args": [B("a8"), B("w8"), B("c8f"), B("sa"), B("sw"), {"var": "m"}, {"i32": n}, {"i32": k}]},
+            {"op": "mmx", "args": [B("a8"), B("w8"), B("cmx"), B("sfa"), B("sfw"), {"var": "m"}, {"i32": n}, {"i32": k}]},
         ]}}}
 
 
@@ -49,7 +56,12 @@ def check(rt, device: str, m: int, n: int, k: int) -> None:
     a8 = (torch.randn(m, k, device=device)).to(torch.float8_e4m3fn)
     w8 = (torch.randn(n, k, device=device)).to(torch.float8_e4m3fn)
     sa, sw = torch.tensor([0.5], device=device), torch.tensor([0.25], device=device)
-    for name, t in (("a", a), ("w", w), ("a8", a8.view(torch.uint8)), ("w8", w8.view(torch.uint8)), ("sa", sa), ("sw", sw)):
+    from ..ops import gemm_mx as G
+
+    sfa = torch.randint(124, 131, (m, k // 32), dtype=torch.uint8, device=device)
+    sfw = torch.randint(124, 131, (n, k // 32), dtype=torch.uint8, device=device)
+    for name, t in (("a", a), ("w", w), ("a8", a8.view(torch.uint8)), ("w8", w8.view(torch.uint8)), ("sa", sa), ("sw", sw),
+                    ("sfa", G.sf_to_atoms(sfa)), ("sfw", G.sf_to_atoms(sfw))):
         rt.tensor(name).view(-1)[: t.numel()] = t.reshape(-1)
     rt.run("step", {"m": m})
     rt.synchronize() if hasattr(rt, "synchronize") else None
@@ -61,3 +73,5 @@ def check(rt, device: str, m: int, n: int, k: int) -> None:
     torch.testing.assert_close(get("c32"), ref, rtol=1e-3, atol=1e-3)
     torch.testing.assert_close(get("c8"), ref8, rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(get("c8f"), ref8, rtol=1e-3, atol=1e-3)
+    refx = G.dequant_mxfp8(a8.view(torch.uint8), sfa) @ G.dequant_mxfp8(w8.view(torch.uint8), sfw).t()
+    torch.testing.assert_close(get("cmx"), refx, rtol=2e-2, atol=2e-2 * float(refx.abs().max()))
