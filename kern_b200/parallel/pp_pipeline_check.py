@@ -57,7 +57,7 @@ def main(argv=None) -> int:
         cfg = dense.DenseConfig(name=a.model, max_seqs=8, max_tokens=a.chunk, max_context=a.prompt + 64, page_size=64)
         if a.layers:
             cfg = dataclasses.replace(cfg, layers=a.layers)
-        tokens = a.prompt + 4096
+        tokens = a.prompt + 4 * a.chunk + 1024
     else:
         cfg = dataclasses.replace(dense.TINY if not a.cpu else dense.TOY, layers=2 * world, name="tiny-deep")
         tokens = cfg.page_size * 64
@@ -103,6 +103,7 @@ def main(argv=None) -> int:
                 prompt = torch.randint(0, cfg.vocab, (a.prompt,), generator=g).tolist()
                 warm = pipe.open(a.chunk * 2 + 8)
                 pipe.prefill(warm, prompt[: a.chunk * 2], a.chunk)          # warm-up: two chunks through every stage
+                warm.lease.release()
                 seq = pipe.open(a.prompt + 8)
                 t0 = time.perf_counter()
                 tok = pipe.prefill(seq, prompt, a.chunk)

@@ -207,6 +207,65 @@ class Runtime:
     def synchronize(self) -> None:
         self._rt.synchronize()
 
+    # ---- stream-ordered signals between the device and the host (or another stream, stage or process) ----
+    def _signals(self):
+        from .ops.launcher import Kernels
+
+        return Kernels.get(torch.device(f"cuda:{self.gpu}"))
+
+    def mark(self) -> "Mark":
+        """Enqueue a mark: once everything issued so far on the runtime's stream has run, the device writes the mark's
+        sequence number into a pinned host word; `Mark.wait()` is the host's side (a deadline, no stream
+        synchronisation). Reference: crates/kern-runtime/src/exec.rs:67-97."""
+        import struct
+
+        from .ops.launcher import ptr
+
+        m = getattr(self, "_mark_word", None)
+        if m is None:
+            m = self._mark_word = torch.zeros(1, dtype=torch.int64, pin_memory=True)
+            self._mark_seq = 0
+        self._mark_seq += 1
+        self._signals().launch("signals", "kern_mark", (1,), (32,), [ptr(m), struct.pack("<Q", self._mark_seq)], stream=self.stream)
+        return Mark(m, self._mark_seq)
+
+    def gate(self) -> "Gate":
+        """A counter in pinned host memory that the host (or a peer's copy) advances and `hold` waits on."""
+        return Gate(torch.zeros(1, dtype=torch.int64, pin_memory=True))
+
+    def hold(self, gate: "Gate", want: int, timeout_s: float = 60.0, code: int = 901) -> None:
+        """Enqueue a wait on the runtime's stream: what is issued after it runs once `gate` has been opened `want` times.
+        The wait is bounded: after `timeout_s` it sets the error word to `code` and lets the stream go on
+        (the host sees the error at its next `check_error`). Reference: exec.rs:103-113, 135-164."""
+        import struct
+
+        from .ops.launcher import i32, i64, ptr
+
+        err = self._rt.region(self._error_name())[0] if self._error_name() else 0
+        self._signals().launch("signals", "kern_hold", (1,), (32,),
+                               [ptr(gate.word), struct.pack("<Q", want), i64(int(timeout_s * 1e9)), struct.pack("<Q", err), i32(code)],
+                               stream=self.stream)
+
+    def _error_name(self):
+        for f in (self.protocol or {}).get("fills", []):
+            if f["fill"] == "error":
+                return f["name"]
+        return "error" if "error" in self.doc["buffers"] else None
+
+    def fetch(self, name: str, count: int | None = None) -> "Fetch":
+        """Start reading an output into a pinned buffer of the runtime's pool, behind what is issued so far; the result
+        is taken with `Fetch.get()`, which waits on a mark, not on the stream (later work may already be queued).
+        Reference: exec.rs:257-277."""
+        b = self.doc["buffers"][name]
+        src = self.tensor(name).view(-1)
+        n = src.numel() if count is None else count
+        pool = self.__dict__.setdefault("_fetch_pool", {})
+        free = pool.setdefault((name, n), [])
+        dst = free.pop() if free else torch.empty(n, dtype=src.dtype, pin_memory=True)
+        with torch.cuda.stream(torch.cuda.ExternalStream(self.stream, device=f"cuda:{self.gpu}")):
+            dst.copy_(src[:n], non_blocking=True)
+        return Fetch(dst, self.mark(), free, b["dtype"])
+
     def check_error(self) -> None:
         for f in (self.protocol or {}).get("fills", []):
             if f["fill"] == "error":
@@ -284,3 +343,46 @@ class Runtime:
 
     def banner(self) -> str:
         return self._rt.banner()
+
+
+class Mark:
+    """A point of the runtime's stream the host can wait for without synchronising the stream."""
+
+    def __init__(self, word: torch.Tensor, seq: int):
+        self.word, self.seq = word, seq
+
+    def done(self) -> bool:
+        return int(self.word[0]) >= self.seq
+
+    def wait(self, timeout_s: float = 60.0) -> None:
+        import time
+
+        deadline = time.monotonic() + timeout_s
+        while not self.done():
+            if time.monotonic() > deadline:
+                raise TimeoutError(f"mark {self.seq} did not land within {timeout_s:.0f} s (the device reached {int(self.word[0])})")
+            time.sleep(0.00005)
+
+
+class Gate:
+    def __init__(self, word: torch.Tensor):
+        self.word = word
+
+    def open(self, n: int = 1) -> None:
+        """Advance the count the device-side `hold` polls (a plain host store to pinned memory)."""
+        self.word[0] += n
+
+    @property
+    def count(self) -> int:
+        return int(self.word[0])
+
+
+class Fetch:
+    def __init__(self, buf: torch.Tensor, mark: Mark, free: list, dtype: str):
+        self.buf, self.mark, self._free, self.dtype = buf, mark, free, dtype
+
+    def get(self, timeout_s: float = 60.0) -> np.ndarray:
+        self.mark.wait(timeout_s)
+        out = self.buf.numpy().copy() if self.dtype != "bf16" else self.buf.view(torch.int16).numpy().copy()
+        self._free.append(self.buf)
+        return out

@@ -185,8 +185,46 @@ class Stage:
                 self.sends[j] = [dist.isend(self.outgoing[n][j][:sizes[n]], dst=self._peer(self.rank + 1), group=self.data_pg) for n in self.leave]
         self.items += 1
         if self.rank == self.world - 1 and item.emits is not None:
-            return self._tokens(item)
+            return self._tokens_later(item) if st.cuda else self._tokens(item)
         return None
+
+    def _tokens_later(self, item: Item):
+        """GPU: copy the item's outputs to pinned memory behind its kernels and hand back something to wait on — the
+        host goes on to the next item at once (a read that waited here would hold the whole pipeline to one item)."""
+        n = item.groups * item.width
+        slot = self._pinned[item.k % len(self._pinned)] if getattr(self, "_pinned", None) else None
+        if slot is None:
+            self._pinned = [{} for _ in range(8)]
+            slot = self._pinned[item.k % 8]
+        with self.st.on(self.st.compute):
+            out = {}
+            for name in [item.emits] + ([item.count] if item.count else []):
+                src = self.rt.tensor(name).view(-1)
+                dst = slot.get(name)
+                if dst is None or dst.numel() < src.numel():
+                    dst = slot[name] = torch.empty(src.numel(), dtype=src.dtype, pin_memory=True)
+                m = n if name == item.emits else item.groups
+                dst[:m].copy_(src[:m], non_blocking=True)
+                out[name] = dst
+            ev = torch.cuda.Event()
+            ev.record(self.st.compute)
+        return _Pending(item, ev, out)
+
+    def finish(self, pending) -> list:
+        """Wait (with the deadline) for a pending read and decode it."""
+        if not isinstance(pending, _Pending):
+            return pending
+        deadline = time.monotonic() + self.timeout
+        while not pending.event.query():
+            if time.monotonic() > deadline:
+                raise StageTimeout(f"stage {self.rank}: item {pending.item.k} did not finish within {self.timeout:.0f} s")
+            time.sleep(0.0002)
+        item = pending.item
+        toks = pending.out[item.emits][: item.groups * item.width].numpy().reshape(item.groups, item.width)
+        if item.count is not None:
+            cnt = pending.out[item.count][: item.groups].numpy()
+            return [toks[i, : int(cnt[i])].tolist() for i in range(item.real)]
+        return [toks[i, :1].tolist() for i in range(item.real)]
 
     def _peer(self, stage: int) -> int:
         return dist.get_global_rank(self.data_pg, stage) if self.data_pg is not None else stage
@@ -220,6 +258,13 @@ class Stage:
             self._sync(f"stage {self.rank}: drain")
             self.st.send.synchronize()
             self.st.recv.synchronize()
+
+
+@dataclass
+class _Pending:
+    item: Item
+    event: object
+    out: dict
 
 
 def _timedelta(seconds: float):
@@ -330,18 +375,60 @@ class Pipeline:
 
     # -- every stage but the head --
     def serve(self) -> int:
-        """Run announced items until the head says stop; returns how many."""
+        """Run announced items until the head says stop; returns how many. Announcements arrive on a listener thread
+        and (on the last stage) reports leave on a reporter thread, so the loop below only ever issues device work."""
+        import queue
+        import threading
+
+        items: queue.Queue = queue.Queue()
+        outbox: queue.Queue = queue.Queue()
+        failure: list = []
+
+        def listen():
+            try:
+                while True:
+                    it = self._hear()
+                    items.put(it)
+                    if it.stop:
+                        return
+            except Exception as e:      # noqa: BLE001
+                failure.append(e)
+                items.put(Item(k=-1, program="", vars={}, columns={}, stop=True))
+
+        def report():
+            try:
+                while True:
+                    got = outbox.get()
+                    if got is None:
+                        return
+                    item, pending = got
+                    self._report(item, self.stage.finish(pending) if pending is not None else [])
+            except Exception as e:      # noqa: BLE001
+                failure.append(e)
+
+        threading.Thread(target=listen, daemon=True, name="kern-pp-listen").start()
+        last = self.rank == self.world - 1
+        reporter = None
+        if last:
+            reporter = threading.Thread(target=report, daemon=True, name="kern-pp-report")
+            reporter.start()
         n = 0
         while True:
-            item = self._hear()
+            item = items.get()
+            if failure:
+                raise failure[0]
             if item.stop:
                 self.stage.drain()
-                if self.rank == self.world - 1:
+                if last:
+                    outbox.put(None)
+                    reporter.join(timeout=self.timeout)
+                    if failure:
+                        raise failure[0]
                     self._report(Item(k=-1, program="", vars={}, columns={}), [])        # lets the head's listener go
                 return n
-            toks = self.stage.run(item)
-            if self.rank == self.world - 1:
-                self._report(item, toks or [])
+            pending = self.stage.run(item)
+            if last:
+                outbox.put((item, pending))
             n += 1
 
     # -- the head --
@@ -361,7 +448,7 @@ class Pipeline:
             self._announce(item)
         toks = self.stage.run(item)
         if self.world == 1:
-            self._report(item, toks or [])
+            self._report(item, self.stage.finish(toks) if toks is not None else [])
             self.reported = self.k + 1
         for s, new in batch:
             s.length += len(new)

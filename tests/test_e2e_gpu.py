@@ -186,3 +186,40 @@ def test_kernel_activity_trace_names_our_kernels(tiny, tmp_path):
     assert sum(d["launches"] for d in top.values()) == len(kt.records)
     kt.write(tmp_path / "kernels.parquet")
     assert pq.ParquetFile(tmp_path / "kernels.parquet").read().num_rows == len(kt.records)
+
+
+def test_mark_gate_hold_and_fetch(cuda):
+    """The runtime's stream-ordered signals: a program issued behind a `hold` does not run until the host opens the
+    gate; a `mark` tells the host when the stream got there without a stream synchronisation; `fetch` reads an output
+    behind the work issued so far; and a gate nobody opens makes the hold give up after its limit with an error code,
+    leaving the context usable."""
+    import time
+
+    from kern_b200.models import toy_int
+    from kern_b200.runtime import Runtime
+    from kern_b200.engine import Engine
+
+    rt = Runtime(toy_int.build_manifest(False), tokens=16 * 40)
+    eng = Engine(rt)
+    seq = eng.open(64)
+    prompt = list(range(3, 20))
+    gate = rt.gate()
+    rt.hold(gate, 1, timeout_s=20.0)
+    toks = eng.step([(seq, prompt)], read=False)           # queued behind the hold
+    m = rt.mark()
+    time.sleep(0.05)
+    assert not m.done()                                    # the stream is parked on the gate
+    f = rt.fetch("next_token", 1)
+    gate.open()
+    m.wait(10.0)
+    assert int(f.get(10.0)[0]) == toy_int.generate(prompt, 1)[0]
+    rt.check_error()
+    # a gate nobody opens: the hold gives up after 5 ms, sets the error word and the stream goes on
+    rt.hold(rt.gate(), 1, timeout_s=0.005, code=777)
+    rt.mark().wait(10.0)
+    with pytest.raises(RuntimeError, match="777"):
+        rt.check_error()
+    rt.tensor("error").zero_()
+    torch.cuda.synchronize()
+    eng.step([(seq, [5])])
+    rt.check_error()
