@@ -1,0 +1,370 @@
+// Causal prefill attention over the paged KV cache on the 5th-generation tensor cores (head_dim 128).
+//
+// One CTA = one (sequence, block of query rows, KV head): 128 query rows (128 / G tokens x the G query heads that
+// share the KV head), walked over KV tiles of 128 tokens up to the block's causal limit:
+//
+//   warp 0      TMA producer: K and V tiles of the paged cache (2-D boxes per page, 128-byte swizzle) into a ring
+//   warp 1      issues the MMAs from one thread:  S = Q K^T   (128 x 128 x D, accumulator in TMEM, two S buffers)
+//                                                 O += P V    (128 x D x 128, accumulator in TMEM)
+//   warps 2..5  softmax, one thread per query row: read its row of S out of TMEM (tcgen05.ld), running maximum,
+//               exponentials, row sum, and P as bf16 into shared memory (the A operand of the second MMA);
+//               at the end read O, divide by the row sum and store
+//
+// S(j + 1) = Q K^T is issued before P(j) V, so the tensor cores work on the next tile's scores while the softmax
+// warps are busy with this tile's. O is rescaled lazily: a row's reference maximum moves only when the running
+// maximum has grown by more than 8 (a factor 256, harmless in f32), so most tiles need no pass over O at all.
+// V is consumed straight from its [token][d] tile as an MN-major B operand: no transpose anywhere.
+// Every mbarrier wait is bounded; a wait that runs out sets *err, the CTA drains and frees its TMEM.
+//
+// Layouts as in attn_paged.cu (q rows inside the fused qkv buffer; kv pool [pages][2][hk][page][d] behind one 2-D
+// tensor map with 64-column boxes; block_table, seq_lens, cu_q, the planner's work list).
+// The reference takes prefill attention as a prebuilt trtllm-gen FMHA blob (kernel_index/trtllm_fmha_*.toml); it has no
+// source counterpart.
+#include "common.cuh"
+
+namespace kern {
+
+constexpr int FM = 128;   // query rows per CTA
+constexpr int FN = 128;   // tokens per KV tile
+
+// Shared-memory descriptor of an MN-major operand tile written by TMA with the 128-byte swizzle: rows are K (tokens),
+// each 128 bytes = 64 MN elements; 8 rows form a 1024-byte swizzle atom; the next 64 MN elements are `mn_block_bytes`
+// further on.
+KERN_DEVICE uint64_t umma_desc_sw128_mn(uint32_t smem_addr, uint32_t mn_block_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFF) << 16;   // leading byte offset: next block of 64 along MN
+  d |= (uint64_t)(1024 >> 4) << 32;                        // stride byte offset: next 8 rows along K
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;                                  // SWIZZLE_128B
+  return d;
+}
+
+KERN_DEVICE void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+KERN_DEVICE void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <int D>
+struct FmhaCfg {
+  static constexpr int kQBytes = FM * D * 2;              // D / 64 column blocks of [128 rows][128 bytes]
+  static constexpr int kPBytes = FM * FN * 2;             // two blocks of 64 tokens
+  static constexpr int kTileBytes = FN * D * 2;           // K or V
+  static constexpr int kStages = 2;
+  static constexpr int kSmem = 1024 + kQBytes + kPBytes + kStages * 2 * kTileBytes + 256;
+  static constexpr int kTmemCols = 512;                   // S0 | S1 | O
+};
+
+struct FmhaArgs {
+  const __nv_bfloat16* q;
+  __nv_bfloat16* out;
+  const int* block_table;
+  const int* seq_lens;
+  const int* cu_q;
+  const int* work;
+  const int* work_count;
+  int* err;
+  int hq, hk, q_stride, out_stride, max_pages, page_size, pool_pages;
+  float scale_log2;
+};
+
+template <int D>
+KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a) {
+  using Cfg = FmhaCfg<D>;
+  constexpr int kStages = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* p_s = q_s + Cfg::kQBytes;
+  uint8_t* kv_s = p_s + Cfg::kPBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + kStages * 2 * Cfg::kTileBytes);
+  uint64_t* kv_full = bars;                  // [stages]  TMA -> MMA
+  uint64_t* kv_empty = bars + kStages;       // [stages]  P V done with the stage
+  uint64_t* s_full = kv_empty + kStages;     // [2]       S buffer written
+  uint64_t* s_empty = s_full + 2;            // [2]       softmax has read the S buffer (128 arrivals)
+  uint64_t* p_full = s_empty + 2;            // [1]       P in shared memory (128 arrivals)
+  uint64_t* p_empty = p_full + 1;            // [1]       P V has consumed P (and O is quiet)
+  uint64_t* o_full = p_empty + 1;            // [1]       last P V done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = a.hq / a.hk;
+  if ((int)blockIdx.y >= *a.work_count) return;          // uniform per CTA, before any barrier or allocation
+  const int seq = a.work[2 * blockIdx.y], blk = a.work[2 * blockIdx.y + 1];
+  const int kvh = blockIdx.x;
+  const int L = a.seq_lens[seq];
+  const int row0_tok = a.cu_q[seq];
+  const int R = a.cu_q[seq + 1] - row0_tok;
+  const int toks_per_blk = FM / G;
+  const int tok_lo = blk * toks_per_blk;
+  if (tok_lo >= R || L <= 0) return;
+  const int tok_n = min(toks_per_blk, R - tok_lo);
+  const int valid_rows = tok_n * G;
+  const int last_pos = L - R + tok_lo + tok_n - 1;
+  const int ntiles = last_pos / FN + 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 128); }
+    mbar_init(p_full, 128);
+    mbar_init(p_empty, 1);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(kv_map);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  // ---- Q tile -> shared memory in the K-major 128-byte-swizzled layout the MMA reads (all warps) ----
+  for (int i = threadIdx.x; i < FM * (D / 8); i += blockDim.x) {
+    const int r = i / (D / 8), c = i % (D / 8);            // row, 16-byte chunk
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < valid_rows) {
+      const int tk = tok_lo + r / G, g = r % G;
+      v = *reinterpret_cast<const uint4*>(a.q + (size_t)(row0_tok + tk) * a.q_stride + (size_t)(kvh * G + g) * D + c * 8);
+    }
+    const int cb = c >> 3, cc = c & 7;
+    *reinterpret_cast<uint4*>(q_s + cb * (FM * 128) + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+  }
+  fence_proxy_async();        // generic-proxy stores above are read by the tensor core's async proxy
+  __syncthreads();
+
+  if (warp == 0) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      const int box_rows = a.page_size < 64 ? a.page_size : 64;
+      const int boxes = FN / box_rows;
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = 0; t < ntiles; ++t) {
+        if (!mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag)) {
+          set_error(a.err, ERR_WAIT_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        uint8_t* sk = kv_s + stage * 2 * Cfg::kTileBytes;
+        uint8_t* sv = sk + Cfg::kTileBytes;
+        mbar_expect_tx(&kv_full[stage], 2 * Cfg::kTileBytes);
+        for (int b = 0; b < boxes; ++b) {
+          const int tok = t * FN + b * box_rows;
+          int page = 0, in_page = 0;
+          const int pidx = tok / a.page_size;
+          if (tok < L && pidx < a.max_pages) {
+            page = a.block_table[(size_t)seq * a.max_pages + pidx];
+            in_page = tok % a.page_size;
+          }
+          if (page < 0 || page >= a.pool_pages) {
+            set_error(a.err, ERR_BOUNDS);
+            page = 0;
+          }
+          const int krow = ((page * 2 + 0) * a.hk + kvh) * a.page_size + in_page;
+          const int vrow = ((page * 2 + 1) * a.hk + kvh) * a.page_size + in_page;
+#pragma unroll
+          for (int cb = 0; cb < D / 64; ++cb) {
+            tma_load_2d(sk + cb * (FN * 128) + b * box_rows * 128, kv_map, cb * 64, krow, &kv_full[stage]);
+            tma_load_2d(sv + cb * (FN * 128) + b * box_rows * 128, kv_map, cb * 64, vrow, &kv_full[stage]);
+          }
+        }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(FM, FN);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(FM, D) | (1u << 16);      // B (= V) is MN-major
+      const uint32_t o_tmem = tmem_base + 2 * FN;
+      bool ok = true;
+      auto issue_qk = [&](int j) {
+        const int stage = j % kStages;
+        if (!mbar_wait(&kv_full[stage], (j / kStages) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
+        if (!mbar_wait(&s_empty[j & 1], ((j >> 1) & 1) ^ 1, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_EMPTY); return false; }
+        tc_fence_after();
+        const uint32_t sq = smem_u32(q_s), sk = smem_u32(kv_s + stage * 2 * Cfg::kTileBytes);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16(tmem_base + (j & 1) * FN, umma_desc_sw128(sq + (k >> 2) * (FM * 128) + (k & 3) * 32),
+                    umma_desc_sw128(sk + (k >> 2) * (FN * 128) + (k & 3) * 32), idesc_qk, k != 0);
+        tc_commit(&s_full[j & 1]);
+        return true;
+      };
+      auto issue_pv = [&](int j) {
+        const int stage = j % kStages;
+        if (!mbar_wait(p_full, j & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
+        tc_fence_after();
+        const uint32_t sp = smem_u32(p_s), sv = smem_u32(kv_s + stage * 2 * Cfg::kTileBytes + Cfg::kTileBytes);
+#pragma unroll
+        for (int k = 0; k < FN / 16; ++k)
+          umma_bf16(o_tmem, umma_desc_sw128(sp + (k >> 2) * (FM * 128) + (k & 3) * 32),
+                    umma_desc_sw128_mn(sv + k * 16 * 128, FN * 128), idesc_pv, (j | k) != 0);
+        tc_commit(&kv_empty[stage]);        // K and V of the stage are free
+        tc_commit(p_empty);                 // P is consumed and O is quiet until the next P V
+        if (j == ntiles - 1) tc_commit(o_full);
+        return true;
+      };
+      ok = issue_qk(0);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        if (j + 1 < ntiles) ok = issue_qk(j + 1);     // next tile's scores first: they overlap this tile's softmax
+        if (ok) ok = issue_pv(j);
+      }
+      if (!ok) *abort_flag = 1;
+    }
+    __syncwarp();
+  } else {
+    // ---------------- softmax warps 2..5: one thread per query row ----------------
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                           // row of the tile = TMEM lane
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int pos = row < valid_rows ? (L - R + tok_lo + row / G) : -1;       // last token this row may attend to
+    float m_ref = -INFINITY, l_run = 0.f;                          // reference maximum (lazy) and row sum
+    bool ok = true;
+    for (int j = 0; j < ntiles && ok; ++j) {
+      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_FULL); *abort_flag = 1; ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_tmem = tmem_base + lane_addr + (j & 1) * FN;
+      const int tok0 = j * FN;
+      const bool diag = tok0 + FN - 1 > pos;                        // some column of the tile is above this row's limit
+      // pass 1: the row maximum of the tile
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < FN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_tmem + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (!diag || tok0 + c * 32 + i <= pos) mx = fmaxf(mx, __uint_as_float(r[i]));
+      }
+      mx *= a.scale_log2;
+      // lazy reference maximum: move it (and rescale O and l) only when the running maximum outgrew it by 2^8
+      float alpha = 1.f;
+      bool moved = false;
+      if (mx > m_ref + 8.f) {
+        alpha = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
+        m_ref = mx;
+        moved = true;
+      }
+      // P and O may be touched once P(j-1) V is done
+      if (j > 0 && !mbar_wait(p_empty, (j - 1) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_EMPTY); *abort_flag = 1; ok = false; break; }
+      tc_fence_after();
+      if (moved && j > 0) {
+        const uint32_t o_tmem = tmem_base + lane_addr + 2 * FN;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(o_tmem + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_32x32(o_tmem + c * 32, r);
+        }
+        tmem_st_wait();
+      }
+      l_run *= alpha;
+      // pass 2: exponentials -> P (bf16, K-major swizzled, the A operand of P V), row sum
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < FN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_tmem + c * 32, r);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int t = tok0 + c * 32 + 2 * i;
+          const float p0 = (!diag || t <= pos) ? exp2f(__uint_as_float(r[2 * i]) * a.scale_log2 - m_use) : 0.f;
+          const float p1 = (!diag || t + 1 <= pos) ? exp2f(__uint_as_float(r[2 * i + 1]) * a.scale_log2 - m_use) : 0.f;
+          sum += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        // 32 tokens = four 16-byte chunks of this row: chunks 4c .. 4c+3 of 16, block (4c) >> 3
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = c * 4 + q, cb = chunk >> 3, cc = chunk & 7;
+          *reinterpret_cast<uint4*>(p_s + cb * (FM * 128) + row * 128 + ((cc ^ (row & 7)) << 4)) =
+              make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+        }
+      }
+      l_run += sum;
+      tc_fence_before();
+      fence_proxy_async();
+      mbar_arrive(&s_empty[j & 1]);
+      mbar_arrive(p_full);
+    }
+    // ---- epilogue: O / l -> out ----
+    if (ok && !mbar_wait(o_full, 0, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_FULL); *abort_flag = 1; ok = false; }
+    if (ok) {
+      tc_fence_after();
+      const uint32_t o_tmem = tmem_base + lane_addr + 2 * FN;
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* dst = nullptr;
+      if (row < valid_rows) {
+        const int tk = row0_tok + tok_lo + row / G, head = kvh * G + row % G;
+        dst = a.out + (size_t)tk * a.out_stride + (size_t)head * D;
+      }
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(o_tmem + c * 32, r);
+        tmem_ld_wait();
+        if (dst != nullptr) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[v * 8]) * inv, __uint_as_float(r[v * 8 + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * inv, __uint_as_float(r[v * 8 + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * inv, __uint_as_float(r[v * 8 + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * inv, __uint_as_float(r[v * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o;
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0 && threadIdx.x == 0) {
+    const uint64_t t0 = globaltimer_ns();       // let copies in flight land before the shared memory goes away
+    while (globaltimer_ns() - t0 < 2000000ull) { __nanosleep(1000); }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+}  // namespace kern
+
+using namespace kern;
+
+extern "C" __global__ void __launch_bounds__(192, 1)
+    kern_attn_fmha_prefill_d128(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* q, __nv_bfloat16* out,
+                                const int* block_table, const int* seq_lens, const int* cu_q, const int* work,
+                                const int* work_count, int hq, int hk, int q_stride, int out_stride, int max_pages,
+                                int page_size, int pool_pages, float scale_log2, int* err) {
+  FmhaArgs a{q, out, block_table, seq_lens, cu_q, work, work_count, err, hq, hk, q_stride, out_stride, max_pages, page_size,
+             pool_pages, scale_log2};
+  fmha_body<128>(&kv_map, a);
+}

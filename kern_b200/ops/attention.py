@@ -135,6 +135,38 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tens
     return out
 
 
+def fmha_prefill(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor, hq: int,
+                 cu_q: torch.Tensor, *, out: torch.Tensor | None = None, seqs: int | None = None,
+                 scale: float | None = None) -> torch.Tensor:
+    """Causal prefill attention of a ragged call on the tcgen05 kernel (csrc/kernels/sm100/attn_fmha.cu): head_dim 128,
+    128 query rows per CTA (128 / group tokens x the group's heads), S and O in TMEM. Same operands as
+    ``paged_attention(..., prefill=True, cu_q=...)``."""
+    k = Kernels.get(q.device)
+    pages, _, hk, page_size, d = pool.shape
+    assert d == 128, "the tcgen05 prefill kernel is built for head_dim 128"
+    assert page_size >= 8 and (page_size <= 64 and 64 % page_size == 0 or page_size % 64 == 0)
+    g = hq // hk
+    assert hq % hk == 0 and 128 % g == 0
+    n_seqs = block_table.shape[0] if seqs is None else seqs
+    if out is None:
+        out = torch.empty(q.shape[0], hq * d, dtype=torch.bfloat16, device=q.device)
+    tpb = 128 // g
+    items = (q.shape[0] + tpb - 1) // tpb + n_seqs
+    work = torch.empty(2 * items, dtype=torch.int32, device=q.device)
+    count = torch.zeros(2, dtype=torch.int32, device=q.device)
+    k.launch("attn_paged", "kern_attn_plan", (1,), (256,),
+             [ptr(cu_q), i32(n_seqs), i32(tpb), i32(1), i32(0), ptr(work), ptr(count), i32(items), ptr(work), ptr(count[1:]), i32(0)])
+    view = pool.view(pages * 2 * hk * page_size, d)
+    kv_map = k.tensor_map_2d(view, min(page_size, 64), 64)
+    scale = (1.0 / math.sqrt(d)) if scale is None else scale
+    smem = 1024 + 128 * d * 2 + 128 * 128 * 2 + 2 * 2 * (128 * d * 2) + 256
+    k.launch("attn_fmha", "kern_attn_fmha_prefill_d128", (hk, items, 1), (192,),
+             [kv_map, ptr(q), ptr(out), ptr(block_table), ptr(seq_lens), ptr(cu_q), ptr(work), ptr(count), i32(hq), i32(hk),
+              i32(q.stride(0)), i32(out.stride(0)), i32(block_table.shape[1]), i32(page_size), i32(pages),
+              f32(scale * 1.4426950408889634), ptr(k.err_word())], shared_mem=smem)
+    return out
+
+
 def new_partials(rows: int, hq: int, d: int, total: int, device) -> tuple[torch.Tensor, torch.Tensor]:
     """A workspace of `total` partial slots per (row, head), every slot neutral (m = -inf, l = 0): a rank whose share
     of a sequence is empty leaves its slots as they are."""

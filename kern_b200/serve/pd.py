@@ -139,6 +139,10 @@ class Decoder:
         seat = self.seats.pop(req, None)
         if seat is not None:
             self.eng.close(seat.seq)
+        # an ask that was answered Busy and is still queued dies with its request: granted later, its seat would belong
+        # to nobody (the prefill side has already forgotten the request)
+        if any(a["req"] == req for a in self.waiting):
+            self.waiting = deque(a for a in self.waiting if a["req"] != req)
         out = []
         while self.waiting:                       # whoever waited longest gets the room first
             got = self._grant(self.waiting[0])
