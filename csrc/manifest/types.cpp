@@ -276,7 +276,7 @@ uint64_t TensorMapDecl::bits() const {
 }
 int TensorMapDecl::cu_dtype() const {
   static const std::pair<const char*, int> t[] = {{"u8", 0}, {"u16", 1}, {"u32", 2}, {"i32", 3}, {"u64", 4},
-      {"i64", 5}, {"f16", 6}, {"f32", 7}, {"bf16", 9}, {"tf32", 11}, {"u4", 13}, {"u4packed", 13}};
+      {"i64", 5}, {"f16", 6}, {"f32", 7}, {"bf16", 9}, {"tf32", 11}, {"u4", 14}, {"u4packed", 13}};   // u4: 16U4_ALIGN16B (16 nibbles per 16-byte chunk in shared memory), u4packed: 16U4_ALIGN8B
   for (auto& p : t) if (dtype == p.first) return p.second;
   return -1;
 }
@@ -298,6 +298,12 @@ Errors TensorMapDecl::check() const {
       e.push_back("strides[" + std::to_string(i) + "] = " + std::to_string(strides[i]) + " is not a positive multiple of 16");
       break;
     }
+  if (dtype == "u4") {       // the unpacking type: whole 128-nibble boxes, 32-byte strides
+    if (!box.empty() && box[0] != 128) e.push_back("box[0] of a `u4` map must be 128 nibbles");
+    if (dims[0] % 128) e.push_back("dims[0] of a `u4` map must be a multiple of 128 nibbles");
+    for (size_t i = 0; i < strides.size(); ++i)
+      if (strides[i] % 32) { e.push_back("strides of a `u4` map must be multiples of 32 bytes"); break; }
+  }
   const uint64_t b = bits();
   if ((dims[0] * b) % 128) e.push_back("dims[0] = " + std::to_string(dims[0]) + " elements is not a multiple of 16 bytes");
   if (!box.empty()) {

@@ -26,6 +26,7 @@ class MoeConfig(dense.DenseConfig):
     moe_intermediate: int = 768
     scoring: str = "softmax"          # softmax | sigmoid
     routed_scale: float = 1.0
+    mx_experts: bool = False          # expert weights MXFP4 (e2m1 + UE8M0 per 32), expert activations MXFP8
 
 
 TOY_MOE = MoeConfig(name="toy-moe", vocab=256, hidden=64, layers=2, heads=4, kv_heads=2, head_dim=16, intermediate=128,
@@ -135,6 +136,52 @@ def _moe_ops(cfg: MoeConfig, e_lo: int, e_n: int, ep_group: str | None = None, a
     return ops
 
 
+def mx_rows_bound(tokens: int, k: int, experts: int) -> int:
+    """Rows of the expert-sorted buffers when every expert's rows start on a 128-row boundary."""
+    return (-(-tokens * k // C.BM) + experts) * C.BM
+
+
+def _moe_mx_ops(cfg: MoeConfig, e_n: int) -> dict:
+    """The block-scaled form of the routed experts (csrc/kernels/sm100/gemm_mx.cu): aligned plan, gather fused with the
+    MXFP8 quantiser, FC1 = MXFP8 x MXFP4 with the SwiGLU + MXFP8 epilogue, FC2 = MXFP8 x MXFP4 -> bf16."""
+    from ..ops.gemm_mx import atom_bytes
+
+    h, I, k, T = cfg.hidden, cfg.moe_intermediate, cfg.top_k, cfg.max_tokens
+    rows = mx_rows_bound(T, k, e_n)
+    L = lambda module, entry, block, grid, lp, args, **kw: {"module": module, "entry": entry, "block": block, "grid": grid,
+                                                            "params": lp, "args": args, **kw}
+    ops = {}
+    ops["moe_gather_q"] = {"params": ["in buffer<bf16>", "in buffer<i32>", "out buffer<u8>", "out buffer<u8>", "i32"], "impl": {"launches": [L(
+        "gemm_mx", "kern_moe_gather_quant_mxfp8", [128, 1, 1], [{"mul": ["tokens", k]}, 1, 1],
+        ["in buffer<bf16>", "in buffer<i32>", "out buffer<u8>", "out buffer<u8>", "i32", "i32", "i32"],
+        [{"param": 0}, {"param": 1}, {"param": 2}, {"param": 3}, {"param": 4}, {"i32": k}, {"i32": h}])]}}
+
+    def routed(n, kk, swiglu):
+        bn = 256 if n % 256 == 0 else 128
+        a_map = {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+            "param": 0, "dtype": "u8", "dims": [kk, 0], "strides": [kk], "box": [128, C.BM], "swizzle": 128, "l2_promotion": 256}}]}}
+        b_map = {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+            "param": 1, "dtype": "u4", "dims": [kk, n, e_n], "strides": [kk // 2, n * kk // 2],
+            "box": [128, bn, 1], "swizzle": 128, "l2_promotion": 256}}]}}
+        out_t = "out buffer<u8>" if swiglu else "out buffer<bf16>"
+        iface = ["in buffer<u8>", "in buffer<u8>", "in buffer<u8>", "in buffer<u8>", out_t, "in buffer<i32>", "in buffer<i32>",
+                 "out buffer<i32>"] + (["out buffer<u8>"] if swiglu else [])
+        stages = 4 if bn == 256 else 6
+        smem = 1024 + stages * (128 * 128 + bn * 128 + (2048 if bn == 256 else 1024)) + 256
+        entry = f"kern_moe_gemm_mxfp8_mxfp4{'_swiglu_mxfp8' if swiglu else ''}_n{bn}"
+        return {"params": iface, "impl": {"launches": [L(
+            "gemm_mx", entry, [192, 1, 1], [C.SMS, 1, 1],
+            ["bytes<128>", "bytes<128>", "in buffer<u8>", "in buffer<u8>", out_t, "i32", "i32", "i32", "i32", "out buffer<i32>",
+             "in buffer<i32>", "in buffer<i32>", "i64", "out buffer<u8>" if swiglu else "i64"],
+            [a_map, b_map, {"param": 2}, {"param": 3}, {"param": 4}, {"i32": rows}, {"i32": n}, {"i32": kk},
+             {"i32": n // 2 if swiglu else n}, {"param": 7}, {"param": 5}, {"param": 6}, {"i64": atom_bytes(n, kk)},
+             {"param": 8} if swiglu else {"i64": 0}], shared_mem=smem)]}}
+
+    ops["moe_fc1"] = routed(2 * I, h, True)
+    ops["moe_fc2"] = routed(h, I, False)
+    return ops
+
+
 def build_manifest(cfg: MoeConfig) -> dict:
     """The dense decoder's manifest with every layer's MLP replaced by the routed experts."""
     doc = dense.build_manifest(cfg)
@@ -148,11 +195,20 @@ def moeify(doc: dict, cfg, modules: list[str]) -> dict:
     `cfg` brings hidden, layers, max_tokens, experts, top_k, moe_intermediate, scoring and routed_scale."""
     bufs, ops = doc["buffers"], doc["ops"]
     h, I, E, k, T = cfg.hidden, cfg.moe_intermediate, cfg.experts, cfg.top_k, cfg.max_tokens
+    mx = bool(getattr(cfg, "mx_experts", False))
     for name in ("gate_up", "down_proj"):
         ops.pop(name)
     bufs.pop("act")
     ops.update(_moe_ops(cfg, 0, E))
     max_tiles = T * k // C.BM + E
+    if mx:
+        from ..ops.gemm_mx import atom_bytes
+
+        assert h % 128 == 0 and I % 128 == 0, "block-scaled experts need hidden and intermediate multiples of 128"
+        ops.update(_moe_mx_ops(cfg, E))
+        ops["moe_plan"]["impl"]["launches"][0]["entry"] = "kern_moe_plan_aligned"
+        ops.pop("moe_gather")
+        rows = mx_rows_bound(T, k, E)
     bufs["moe.logits"] = {"dtype": "f32", "shape": ["tokens", E], "kind": "workspace"}
     bufs["moe.ids"] = {"dtype": "i32", "shape": ["tokens", k], "kind": "workspace"}
     bufs["moe.w"] = {"dtype": "f32", "shape": ["tokens", k], "kind": "workspace"}
@@ -161,9 +217,16 @@ def moeify(doc: dict, cfg, modules: list[str]) -> dict:
     bufs["moe.tiles"] = {"dtype": "i32", "shape": [max_tiles, 4], "kind": "workspace"}
     bufs["moe.tile_count"] = {"dtype": "i32", "shape": [1], "kind": "workspace"}
     bufs["moe.rows"] = {"dtype": "i32", "shape": [1], "kind": "workspace"}
-    bufs["moe.x"] = {"dtype": "bf16", "shape": ["tokens", k, h], "kind": "workspace"}
-    bufs["moe.act"] = {"dtype": "bf16", "shape": ["tokens", k, I], "kind": "workspace"}
-    bufs["moe.y"] = {"dtype": "bf16", "shape": ["tokens", k, h], "kind": "workspace"}
+    if mx:
+        bufs["moe.x"] = {"dtype": "u8", "shape": [rows, h], "kind": "workspace"}
+        bufs["moe.sfx"] = {"dtype": "u8", "shape": [atom_bytes(rows, h)], "kind": "workspace"}
+        bufs["moe.act"] = {"dtype": "u8", "shape": [rows, I], "kind": "workspace"}
+        bufs["moe.sfact"] = {"dtype": "u8", "shape": [atom_bytes(rows, I)], "kind": "workspace"}
+        bufs["moe.y"] = {"dtype": "bf16", "shape": [rows, h], "kind": "workspace"}
+    else:
+        bufs["moe.x"] = {"dtype": "bf16", "shape": ["tokens", k, h], "kind": "workspace"}
+        bufs["moe.act"] = {"dtype": "bf16", "shape": ["tokens", k, I], "kind": "workspace"}
+        bufs["moe.y"] = {"dtype": "bf16", "shape": ["tokens", k, h], "kind": "workspace"}
     B = lambda n: {"buf": n}
     err = B("error")
     for i in range(cfg.layers):
@@ -171,6 +234,14 @@ def moeify(doc: dict, cfg, modules: list[str]) -> dict:
         for name in (f"w.l{i}.gu", f"w.l{i}.down"):
             bufs.pop(name)
         bufs[f"w.l{i}.router"] = {"dtype": "bf16", "shape": [E, h], "kind": "weight", "bind": [{"tensor": p + "gate.weight"}]}
+        if mx:
+            # the packed form of a block-scaled checkpoint: nibbles and scale atoms per layer, experts stacked
+            # (`mx_checkpoint` writes it from bf16 expert weights)
+            bufs[f"w.l{i}.w1"] = {"dtype": "u8", "shape": [E, 2 * I, h // 2], "kind": "weight", "bind": [{"tensor": p + "experts.w1_mxfp4"}]}
+            bufs[f"w.l{i}.sf1"] = {"dtype": "u8", "shape": [E, atom_bytes(2 * I, h)], "kind": "weight", "bind": [{"tensor": p + "experts.w1_scales"}]}
+            bufs[f"w.l{i}.w2"] = {"dtype": "u8", "shape": [E, h, I // 2], "kind": "weight", "bind": [{"tensor": p + "experts.w2_mxfp4"}]}
+            bufs[f"w.l{i}.sf2"] = {"dtype": "u8", "shape": [E, atom_bytes(h, I)], "kind": "weight", "bind": [{"tensor": p + "experts.w2_scales"}]}
+            continue
         bufs[f"w.l{i}.w1"] = {"dtype": "bf16", "shape": [E, 2 * I, h], "kind": "weight",
                               "bind": [{"tensor": p + f"experts.{e}.{n}_proj.weight"} for e in range(E) for n in ("gate", "up")]}
         bufs[f"w.l{i}.w2"] = {"dtype": "bf16", "shape": [E, h, I], "kind": "weight",
@@ -178,6 +249,20 @@ def moeify(doc: dict, cfg, modules: list[str]) -> dict:
 
     def moe_calls(i: int) -> list[dict]:
         l = f"l{i}."
+        if mx:
+            return [
+                {"op": "moe_router", "label": l + "router", "args": [B("xn"), B(f"w.l{i}.router"), B("moe.logits"), {"var": "tokens"}, err]},
+                {"op": "moe_route", "label": l + "route", "args": [B("moe.logits"), B("moe.ids"), B("moe.w"), {"var": "tokens"}]},
+                {"op": "moe_plan", "label": l + "plan", "args": [B("moe.ids"), B("moe.perm"), B("moe.offsets"), B("moe.tiles"),
+                                                                 B("moe.tile_count"), B("moe.rows"), {"expr": {"mul": ["tokens", k]}}, err]},
+                {"op": "moe_gather_q", "label": l + "gather", "args": [B("xn"), B("moe.perm"), B("moe.x"), B("moe.sfx"),
+                                                                       {"expr": {"mul": ["tokens", k]}}]},
+                {"op": "moe_fc1", "label": l + "fc1", "args": [B("moe.x"), B(f"w.l{i}.w1"), B("moe.sfx"), B(f"w.l{i}.sf1"), B("moe.act"),
+                                                               B("moe.tiles"), B("moe.tile_count"), err, B("moe.sfact")]},
+                {"op": "moe_fc2", "label": l + "fc2", "args": [B("moe.act"), B(f"w.l{i}.w2"), B("moe.sfact"), B(f"w.l{i}.sf2"), B("moe.y"),
+                                                               B("moe.tiles"), B("moe.tile_count"), err]},
+                {"op": "moe_combine", "label": l + "combine", "args": [B("moe.y"), B("moe.perm"), B("moe.w"), B("x")]},
+            ]
         return [
             {"op": "moe_router", "label": l + "router", "args": [B("xn"), B(f"w.l{i}.router"), B("moe.logits"), {"var": "tokens"}, err]},
             {"op": "moe_route", "label": l + "route", "args": [B("moe.logits"), B("moe.ids"), B("moe.w"), {"var": "tokens"}]},
@@ -202,8 +287,23 @@ def moeify(doc: dict, cfg, modules: list[str]) -> dict:
             else:
                 out.append(c)
         doc["programs"][prog]["calls"] = out
-    doc["modules"] = C.modules_for(modules)
+    doc["modules"] = C.modules_for(list(modules) + (["gemm_mx"] if mx else []))
     return doc
+
+
+def mx_checkpoint(cfg: MoeConfig, weights: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """A bf16 checkpoint -> the block-scaled one a `mx_experts` manifest binds: every layer's expert weights quantised to
+    MXFP4 (gate/up rows interleaved in groups of 64, nibbles packed, scale atoms per expert), everything else kept."""
+    from ..ops import moe as M
+
+    out = {k: v for k, v in weights.items() if ".mlp.experts." not in k}
+    for i in range(cfg.layers):
+        p = f"model.layers.{i}.mlp.experts."
+        w1 = torch.stack([torch.cat([weights[p + f"{e}.gate_proj.weight"], weights[p + f"{e}.up_proj.weight"]], 0) for e in range(cfg.experts)])
+        w2 = torch.stack([weights[p + f"{e}.down_proj.weight"] for e in range(cfg.experts)])
+        q1, s1, q2, s2 = M.prepare_expert_weights_mx(w1, w2)
+        out[p + "w1_mxfp4"], out[p + "w1_scales"], out[p + "w2_mxfp4"], out[p + "w2_scales"] = q1, s1, q2, s2
+    return out
 
 
 class MoeOracle(dense.DenseOracle):
@@ -285,8 +385,70 @@ def _register_cpu() -> None:
                     acc += float(wts[t * k + j]) * cpu._f(y[r * hidden:(r + 1) * hidden])
             out[t * hidden:(t + 1) * hidden] = acc.to(out.dtype)
 
+    def plan_aligned(g, ids, perm, offsets, tiles, tile_count, rows_out, entries, e_lo, e_hi, bm, max_tiles, err, rank, per_rank):
+        e_lo, e_hi = e_lo + rank * per_rank, e_hi + rank * per_rank
+        flat = ids[:entries]
+        at, nt = 0, 0
+        tl = tiles.view(-1, 4)
+        for e in range(e_lo, e_hi):
+            mine = torch.nonzero(flat == e).flatten()
+            if mine.numel():
+                at = -(-at // bm) * bm
+            offsets[e - e_lo] = at
+            perm[mine] = torch.arange(at, at + mine.numel(), dtype=perm.dtype)
+            for m0 in range(0, mine.numel(), bm):
+                tl[nt] = torch.tensor([e - e_lo, at + m0, min(bm, mine.numel() - m0), 0], dtype=tl.dtype)
+                nt += 1
+            at += mine.numel()
+        offsets[e_hi - e_lo] = at
+        perm[:entries][(flat < e_lo) | (flat >= e_hi)] = -1
+        tile_count[0], rows_out[0] = nt, at
+
+    def gather_q(g, x, perm, q, sf, entries, k, hidden):
+        from ..ops import gemm_mx as G
+
+        rows_bound = q.numel() // hidden
+        sfm = G.atoms_to_sf(sf, rows_bound, hidden).clone()
+        qv = q.view(rows_bound, hidden)
+        for i in range(entries):
+            r = int(perm[i])
+            if r >= 0:
+                qq, ss = G.quantize_mxfp8_torch(cpu._f(x[(i // k) * hidden:(i // k + 1) * hidden]).view(1, hidden))
+                qv[r] = qq[0]
+                sfm[r] = ss[0]
+        sf.copy_(G.sf_to_atoms(sfm)[: sf.numel()])
+
+    def gemm_mx(swiglu):
+        def run(g, a, w, sfa, sfw, c, M_, N, K, ldc, err, tiles, tile_count, sfw_expert_bytes, sf_out):
+            from ..ops import gemm_mx as G
+
+            tl = tiles.view(-1, 4)
+            A = G.dequant_mxfp8(a[: M_ * K].view(M_, K), G.atoms_to_sf(sfa[: G.atom_bytes(M_, K)], M_, K))
+            out_sf = G.atoms_to_sf(sf_out, M_, N // 2).clone() if swiglu else None
+            for t in range(int(tile_count[0])):
+                e, r0, nr, _ = (int(v) for v in tl[t])
+                We = G.dequant_mxfp4(w[e * N * K // 2:(e + 1) * N * K // 2].view(N, K // 2),
+                                     G.atoms_to_sf(sfw[e * sfw_expert_bytes:(e + 1) * sfw_expert_bytes], N, K))
+                acc = A[r0:r0 + nr] @ We.t()
+                if swiglu:       # W rows: groups of 128 = 64 gate rows + the matching 64 up rows
+                    acc = acc.view(nr, N // 128, 2, 64)
+                    act = (F.silu(acc[:, :, 0]) * acc[:, :, 1]).reshape(nr, N // 2)
+                    qq, ss = G.quantize_mxfp8_torch(act)
+                    c.view(-1, ldc)[r0:r0 + nr] = qq
+                    out_sf[r0:r0 + nr] = ss
+                else:
+                    c.view(-1, ldc)[r0:r0 + nr] = acc.to(torch.bfloat16)
+            if swiglu:
+                sf_out.copy_(G.sf_to_atoms(out_sf)[: sf_out.numel()])
+        return run
+
     cpu.register("kern_moe_route_f32", route)
     cpu.register("kern_moe_plan", plan)
+    cpu.register("kern_moe_plan_aligned", plan_aligned)
+    cpu.register("kern_moe_gather_quant_mxfp8", gather_q)
+    for bn in (256, 128):
+        cpu.register(f"kern_moe_gemm_mxfp8_mxfp4_n{bn}", gemm_mx(False))
+        cpu.register(f"kern_moe_gemm_mxfp8_mxfp4_swiglu_mxfp8_n{bn}", gemm_mx(True))
     cpu.register("kern_moe_gather_bf16", gather)
     cpu.register("kern_moe_combine_bf16", combine)
     for bn in (256, 128, 64):

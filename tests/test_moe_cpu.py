@@ -34,3 +34,36 @@ def test_prefill_and_decode_match_oracle():
         worst = max([worst] + [float((logits[i] - refs[i]).abs().max()) for i in range(2)])
         toks = [n[0] for n in nxt]
     assert worst < 0.15, worst
+
+
+def test_block_scaled_experts_manifest_on_the_cpu_executor():
+    """`mx_experts`: MXFP4 expert weights and MXFP8 expert activations. The manifest verifies, binds the packed checkpoint
+    (`mx_checkpoint`), and on the host-memory executor the decoder's logits stay close to the bf16-expert oracle's (the
+    quantisation is the only difference)."""
+    import dataclasses
+
+    import torch
+
+    from kern_b200.cpu import CpuRuntime
+    from kern_b200.engine import Engine
+    from kern_b200.models import moe
+    from kern_b200.runtime import verify
+
+    cfg = dataclasses.replace(moe.TINY_MOE, name="tiny-moe-mx", mx_experts=True, moe_intermediate=128, layers=1, experts=8, top_k=2)
+    doc = moe.build_manifest(cfg)
+    m, diags = verify(doc)
+    assert m is not None, diags[:5]
+    w = moe.random_weights(cfg, seed=3, std=0.05)
+    rt = CpuRuntime(doc, weights=moe.mx_checkpoint(cfg, w), tokens=cfg.page_size * 16)
+    rt.once()
+    eng = Engine(rt)
+    oracle = moe.MoeOracle(cfg, w)
+    torch.manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (21,)).tolist()
+    seq = eng.open(40)
+    eng.step([(seq, prompt)])
+    logits = rt.tensor("logits")[:1].float()
+    ref = oracle.forward(prompt, oracle.new_cache())[-1]
+    err = float((logits[0] - ref).abs().max())
+    assert err < 0.35 * float(ref.abs().max()) + 0.05, (err, float(ref.abs().max()))
+    assert int(logits[0].argmax()) == int(ref.argmax()) or err < 0.1

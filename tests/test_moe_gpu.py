@@ -114,3 +114,39 @@ def test_moe_decoder_end_to_end(cuda):
     rt.check_error()
     assert max(float(d.max()) for d in diffs) < 0.3 and max(float(d.mean()) for d in diffs) < 0.05
     assert rt.graphs >= 1
+
+
+def test_moe_decoder_with_block_scaled_experts(cuda):
+    """The `mx_experts` decoder on the GPU (MXFP4 expert weights through the TMA unpacking type, MXFP8 activations, scales
+    through TMEM) against the same manifest on the host-memory executor, which states every kernel in PyTorch."""
+    import dataclasses
+
+    from kern_b200.cpu import CpuRuntime
+    from kern_b200.engine import Engine
+    from kern_b200.models import moe
+    from kern_b200.runtime import Runtime
+
+    cfg = dataclasses.replace(moe.TINY_MOE, name="tiny-moe-mx", mx_experts=True, moe_intermediate=128, experts=8, top_k=2)
+    doc = moe.build_manifest(cfg)
+    w = moe.mx_checkpoint(cfg, moe.random_weights(cfg, seed=3, std=0.05))
+    rt = Runtime(doc, tokens=cfg.page_size * 32)
+    rt.load_tensors(lambda name: w[name].cuda())
+    rt.once()
+    ref_rt = CpuRuntime(doc, weights=w, tokens=cfg.page_size * 32)
+    ref_rt.once()
+    eng, ref = Engine(rt), Engine(ref_rt)
+    torch.manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (37, 5)]
+    seqs, rseqs = [eng.open(60) for _ in prompts], [ref.open(60) for _ in prompts]
+    a = eng.step(list(zip(seqs, prompts)))
+    b = ref.step(list(zip(rseqs, prompts)))
+    rt.check_error()
+    got, want = rt.tensor("logits")[:2].float().cpu(), ref_rt.tensor("logits")[:2].float()
+    assert float((got - want).abs().max()) < 0.08 * float(want.abs().max()) + 0.02
+    for _ in range(3):
+        toks = [t[0] for t in b]
+        a = eng.step([(s, [t]) for s, t in zip(seqs, toks)])
+        b = ref.step([(s, [t]) for s, t in zip(rseqs, toks)])
+        rt.check_error()
+        got, want = rt.tensor("logits")[:2].float().cpu(), ref_rt.tensor("logits")[:2].float()
+        assert float((got - want).abs().max()) < 0.08 * float(want.abs().max()) + 0.02
