@@ -43,6 +43,19 @@ def modules_for(names) -> dict:
     return {n: {"source": idx[n]["source"], "sha256": idx[n]["sha256"], "multicast": False} for n in names}
 
 
+def ensure_modules(doc: dict) -> dict:
+    """Add the built-in modules that some launch of `doc` names and `doc["modules"]` lacks."""
+    idx = None
+    for op in doc["ops"].values():
+        for l in op.get("impl", {}).get("launches", []):
+            m = l.get("module")
+            if m and m not in doc["modules"]:
+                idx = idx or kernel_index()
+                if m in idx:
+                    doc["modules"][m] = {"source": idx[m]["source"], "sha256": idx[m]["sha256"], "multicast": False}
+    return doc
+
+
 def write_safetensors(path, tensors: dict[str, torch.Tensor], metadata: dict | None = None) -> None:
     """8-byte little-endian header length, JSON header padded to 8 bytes, raw little-endian data."""
     header, blobs, off = {}, [], 0
@@ -324,11 +337,20 @@ def _kv_map(d: int, page_size: int, state_param: int) -> dict:
         "swizzle": 128, "l2_promotion": 256}}]}}
 
 
+def fmha_prefill(hq: int, hk: int, d: int) -> bool:
+    """Whether the many-row list of a ragged call goes to the tcgen05 kernel (attn_fmha.cu): head_dim 128 and a group
+    size that divides its 128-row tile. `KERN_B200_FMHA=0` keeps the mma.sync kernel (A/B)."""
+    import os
+
+    return d == 128 and 128 % (hq // hk) == 0 and os.environ.get("KERN_B200_FMHA", "1") != "0"
+
+
 def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, q_stride: int) -> dict:
     """Ragged causal attention over the paged context.
     Interface [q(kv) buffer, kv state, out, block_table, seq_lens, cu_seqlens, work, work_count, err]."""
     g = hq // hk
-    tpb = 64 // g
+    fmha = fmha_prefill(hq, hk, d)
+    tpb = (128 if fmha else 64) // g
     iface = ["in buffer<bf16>", "in state", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "in buffer<i32>",
              "in buffer<i32>", "in buffer<i32>", "out buffer<i32>"]
     lp = list(_ATTN_LP)
@@ -341,12 +363,23 @@ def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, 
                 {"i32": q_stride}, {"i32": hq * d}, {"i32": table_width}, {"i32": page_size}, {"i32": 1}, {"i32": 1},
                 {"i32": I32_MAX}, {"f32": (d ** -0.5) * 1.4426950408889634}, {"param": 8}]
 
-    # many-row sequences: row-parallel causal kernel; few-row sequences (decode rows riding in the ragged
-    # call): token-parallel kernel, so their KV streams at full bandwidth
+    # many-row sequences: row-parallel causal kernel (on the 5th-generation tensor cores for head_dim 128); few-row
+    # sequences (decode rows riding in the ragged call): token-parallel kernel, so their KV streams at full bandwidth
+    if fmha:
+        many = {"module": "attn_fmha", "entry": "kern_attn_fmha_prefill_d128", "block": [192, 1, 1],
+                "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1],
+                "shared_mem": 1024 + 128 * d * 2 + 128 * 128 * 2 + 2 * 2 * (128 * d * 2) + 256,
+                "params": ["bytes<128>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "in buffer<i32>",
+                           "in buffer<i32>", "in buffer<i32>"] + ["i32"] * 7 + ["f32", "out buffer<i32>"],
+                "args": [_kv_map(d, page_size, 1), {"param": 0}, {"param": 2}, {"param": 3}, {"param": 4}, {"param": 5}, {"param": 6},
+                         {"param": 7}, {"i32": hq}, {"i32": hk}, {"i32": q_stride}, {"i32": hq * d}, {"i32": table_width},
+                         {"i32": page_size}, {"i32": I32_MAX}, {"f32": (d ** -0.5) * 1.4426950408889634}, {"param": 8}]}
+    else:
+        many = {"module": "attn_paged", "entry": f"kern_attn_prefill_paged_d{d}", "block": [160, 1, 1],
+                "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1], "shared_mem": attn_smem(d, prefill=True),
+                "params": lp, "args": args(6, 7)}
     return {"params": iface, "impl": {"launches": [
-        {"module": "attn_paged", "entry": f"kern_attn_prefill_paged_d{d}", "block": [160, 1, 1],
-         "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1], "shared_mem": attn_smem(d, prefill=True),
-         "params": lp, "args": args(6, 7)},
+        many,
         {"module": "attn_paged", "entry": f"kern_attn_decode_paged_d{d}", "block": [160, 1, 1],
          "grid": [hk, "seqs", 1], "shared_mem": attn_smem(d), "params": lp, "args": args(9, 10)}]}}
 
@@ -390,11 +423,12 @@ def attn_decode_dcp_op(hq: int, hk: int, d: int, page_size: int, table_width: in
                                       "scratch": scratch}}
 
 
-def attn_plan_op(hq: int, hk: int, seqs_max: int) -> dict:
+def attn_plan_op(hq: int, hk: int, seqs_max: int, d: int = 0) -> dict:
     """Interface [cu_seqlens, work, work_count, seqs, max_items]; the attention grid's (sequence, block)
-    work list. A call passes ``{"var": "seqs"}`` and ``attn_plan_items(...)``."""
+    work list. A call passes ``{"var": "seqs"}`` and ``attn_plan_items(...)``. `d`: the head_dim, which decides the
+    block of the many-row list (the tcgen05 kernel's tile is 128 rows)."""
     g = hq // hk
-    tpb, tpd = 64 // g, max(1, 16 // g)
+    tpb, tpd = (128 if fmha_prefill(hq, hk, d) else 64) // g, max(1, 16 // g)
     return {"params": ["in buffer<i32>", "out buffer<i32>", "out buffer<i32>", "i32", "i32", "out buffer<i32>", "out buffer<i32>"],
             "impl": {"launches": [{
                 "module": "attn_paged", "entry": "kern_attn_plan", "block": [256, 1, 1], "grid": [1, 1, 1],

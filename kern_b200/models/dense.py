@@ -174,7 +174,7 @@ def build_manifest(cfg: DenseConfig, hosted: bool = False) -> dict:
     ops["down_proj"] = C.gemm_op(h, inter, epilogue="acc", rows_max=T)
     ops["lm_head"] = C.gemm_op(cfg.vocab, h, rows_var="seqs", rows_max=S)
     ops["rope_append"] = C.rope_append_op(hq, hk, d, d, cfg.page_size, cfg.max_context, cfg.eps, cfg.qk_norm)
-    ops["attn_plan"] = C.attn_plan_op(hq, hk, S)
+    ops["attn_plan"] = C.attn_plan_op(hq, hk, S, d)
     ops["attn_prefill"] = C.attn_prefill_op(hq, hk, d, cfg.page_size, W, cfg.qkv_dim)
     ops["attn_decode"] = C.attn_decode_op(hq, hk, d, cfg.page_size, W, cfg.qkv_dim, S)
     ops["last_row"] = C.last_row_op(h * 2)
@@ -258,7 +258,7 @@ def build_manifest(cfg: DenseConfig, hosted: bool = False) -> dict:
                          "decode": {"batch": {"groups": S, "rows": 1}, "graph": True, "calls": decode}})
 
     mods = ["norm_embed", "gemm_bf16", "attn_prep", "attn_paged"] + ([] if hosted else ["misc", "sampling"])
-    return {
+    return C.ensure_modules({
         "schema_version": 7,
         "model": cfg.name,
         "vars": {"tokens": {"max": T, "axis": "rows"}, "seqs": {"max": S, "axis": "groups"}},
@@ -267,7 +267,7 @@ def build_manifest(cfg: DenseConfig, hosted: bool = False) -> dict:
         "modules": C.modules_for(mods),
         "ops": ops,
         "programs": programs,
-    }
+    })
 
 
 def load_random_weights(rt, cfg: DenseConfig, seed: int = 0, std: float = 0.02) -> None:

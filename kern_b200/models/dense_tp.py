@@ -92,7 +92,7 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True
     ops["down_proj"] = C.tp_gemm_reduce_op(h, inter, n, T) if fused else C.gemm_op(h, inter, rows_max=T)
     ops["lm_head"] = C.gemm_op(cfg.vocab, h, rows_var="seqs", rows_max=S)
     ops["rope_append"] = C.rope_append_op(hq, hk, d, d, cfg.page_size, cfg.max_context, cfg.eps, cfg.qk_norm)
-    ops["attn_plan"] = C.attn_plan_op(hq, hk, S)
+    ops["attn_plan"] = C.attn_plan_op(hq, hk, S, d)
     ops["attn_prefill"] = C.attn_prefill_op(hq, hk, d, cfg.page_size, W, qkv_dim)
     ops["attn_decode"] = C.attn_decode_op(hq, hk, d, cfg.page_size, W, qkv_dim, S)
     ops["last_row"] = C.last_row_op(h * 2)
@@ -208,7 +208,7 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True
 
     mods = (["norm_embed", "gemm_bf16", "attn_prep", "attn_paged", "misc", "sampling", "tp_allreduce_norm"] +
             (["tp_gemm"] if fused or sp else []) + (["tp_sp", "ag_gemm"] if sp else []))
-    return {
+    return C.ensure_modules({
         "schema_version": 7,
         "model": f"{cfg.name}-tp{n}",
         "vars": {"tokens": {"max": T, "axis": "rows"}, "seqs": {"max": S, "axis": "groups"}},
@@ -223,4 +223,4 @@ def build_manifest_tp(cfg: DenseConfig, fused: bool = True, lamport: bool = True
             "prefill": {"batch": {"groups": S, "rows": "tokens"}, "calls": prefill},
             "decode": {"batch": {"groups": S, "rows": 1}, "graph": True, "calls": decode},
         },
-    }
+    })

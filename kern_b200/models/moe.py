@@ -288,7 +288,7 @@ def moeify(doc: dict, cfg, modules: list[str]) -> dict:
                 out.append(c)
         doc["programs"][prog]["calls"] = out
     doc["modules"] = C.modules_for(list(modules) + (["gemm_mx"] if mx else []))
-    return doc
+    return C.ensure_modules(doc)
 
 
 def mx_checkpoint(cfg: MoeConfig, weights: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
