@@ -398,6 +398,14 @@ for _bn in (256, 128, 64, 32):
         CPU_KERNELS[f"kern_gemm_bf16_tn{_sfx}_n{_bn}"] = _gemm(_epi)
         for _mt in (1, 2, 4, 8):
             CPU_KERNELS[f"kern_gemv_bf16_tn{_sfx}_m{_mt}"] = _gemv(_epi)
+def _attention_fmha(g, kv, q, out, table, seq_lens, cu_q, work, work_count, hq, hk, q_stride, out_stride, max_pages, page,
+                    pool_pages, scale_log2, err):
+    """The tcgen05 prefill kernel's statement: the same arithmetic as the row-parallel kernel's."""
+    _attention(True)(g, kv, q, out, 0, 0, table, seq_lens, cu_q, work, work_count, 0, hq, hk, q_stride, out_stride, max_pages,
+                     page, 1, 1, pool_pages, scale_log2, err)
+
+
+CPU_KERNELS["kern_attn_fmha_prefill_d128"] = _attention_fmha
 for _d in (16, 32, 64, 128, 256):
     CPU_KERNELS[f"kern_attn_prefill_paged_d{_d}"] = _attention(True)
     CPU_KERNELS[f"kern_attn_decode_paged_d{_d}"] = _attention(False)

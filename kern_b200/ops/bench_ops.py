@@ -274,11 +274,17 @@ def bench_attn_prefill(a):
     lens = torch.full((a.seqs,), ctx, dtype=torch.int32, device="cuda")
     cu = (torch.arange(a.seqs + 1, device="cuda") * a.rows).to(torch.int32)
     out = torch.empty_like(q)
-    ms = timeit(lambda: paged_attention(q, pool, table, lens, a.hq, out=out, prefill=True, cu_q=cu, max_rows=a.rows), a.iters)
+    if a.fmha:
+        from .attention import fmha_prefill
+
+        ms = timeit(lambda: fmha_prefill(q, pool, table, lens, a.hq, cu, out=out), a.iters)
+    else:
+        ms = timeit(lambda: paged_attention(q, pool, table, lens, a.hq, out=out, prefill=True, cu_q=cu, max_rows=a.rows), a.iters)
     Kernels.get().check_error()
     # causal: row r of a chunk sees prefix + r + 1 keys
     keys = a.rows * a.prefix + a.rows * (a.rows + 1) / 2
-    report("attn_prefill_paged", ms, flops=4.0 * a.seqs * a.hq * a.d * keys, seqs=a.seqs, rows=a.rows, prefix=a.prefix)
+    report("attn_fmha_prefill_tcgen05" if a.fmha else "attn_prefill_paged", ms, flops=4.0 * a.seqs * a.hq * a.d * keys, seqs=a.seqs,
+           rows=a.rows, prefix=a.prefix)
 
 
 def bench_norm(a):
@@ -324,6 +330,7 @@ def main(argv=None):
         s.add_argument("--d", type=int, default=128); s.add_argument("--page", type=int, default=64); s.add_argument("--rows", type=int, default=1)
     d.add_argument("--ctx", type=int, default=2432); d.add_argument("--splits", type=int, default=None)
     p.add_argument("--prefix", type=int, default=0)
+    p.add_argument("--fmha", action="store_true", help="the tcgen05 kernel (head_dim 128) instead of the mma.sync one")
     ml = sub.add_parser("mla_decode")
     ml.add_argument("--seqs", type=int, default=64); ml.add_argument("--ctx", type=int, default=8192)
     ml.add_argument("--heads", type=int, default=16); ml.add_argument("--page", type=int, default=64)

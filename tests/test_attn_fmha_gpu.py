@@ -54,3 +54,44 @@ def test_fmha_prefill_matches_fp32(cuda, hq, hk, page_size, new, prefix):
         pos = torch.arange(prefix[s], lens[s], device=cuda)
         ref = A.attention_reference(qs, ks[s], vs[s], pos)
         torch.testing.assert_close(out[lo:hi].float(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_dense_decoder_with_head_dim_128_uses_the_tcgen05_prefill_kernel(cuda, monkeypatch):
+    """A small dense decoder with head_dim 128 through the runtime and the engine: ragged calls that mix prompt chunks
+    (the tcgen05 kernel's list) with decode rows (the token-parallel kernel's list), against the fp32 oracle."""
+    import dataclasses
+
+    from kern_b200.engine import Engine
+    from kern_b200.models import dense
+    from kern_b200.runtime import Runtime
+
+    monkeypatch.setenv("KERN_B200_FMHA", "1")
+    cfg = dataclasses.replace(dense.TINY, name="tiny-d128", head_dim=128, heads=8, kv_heads=2, hidden=256, max_tokens=512,
+                              max_context=512, page_size=64)
+    doc = dense.build_manifest(cfg)
+    assert doc["ops"]["attn_prefill"]["impl"]["launches"][0]["entry"] == "kern_attn_fmha_prefill_d128"
+    w = dense.random_weights(cfg, seed=0, std=0.05)
+    rt = Runtime(doc, tokens=cfg.page_size * 40)
+    rt.load_tensors(lambda name: w[name].cuda())
+    rt.once()
+    eng = Engine(rt)
+    oracle = dense.DenseOracle(cfg, w, device="cuda")
+    torch.manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (200, 3, 70)]
+    seqs = [eng.open(len(p) + 200) for p in prompts]
+    caches = [oracle.new_cache() for _ in prompts]
+    first = eng.step(list(zip(seqs, prompts)))
+    rt.check_error()
+    logits = rt.tensor("logits")[:3].float()
+    for i, (p, c) in enumerate(zip(prompts, caches)):
+        assert float((logits[i] - oracle.forward(p, c)[-1]).abs().max()) < 0.12
+    # a mixed call: two sequences decode one row each while the third is fed a 150-token chunk
+    toks = [f[0] for f in first]
+    chunk = torch.randint(0, cfg.vocab, (150,)).tolist()
+    feeds = [[toks[0]], [toks[1]], chunk]
+    refs = [oracle.forward(f, c)[-1] for f, c in zip(feeds, caches)]
+    eng.step(list(zip(seqs, feeds)))
+    rt.check_error()
+    logits = rt.tensor("logits")[:3].float()
+    for i in range(3):
+        assert float((logits[i] - refs[i]).abs().max()) < 0.12
