@@ -85,13 +85,16 @@ def main():
     ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"],
                     help="N > 1: tensor parallel over one batch (the configuration the metric names; default), or "
                          "data-parallel replicas with the concurrency split between them (reported for comparison only)")
-    ap.add_argument("--tp-layout", default="sp", choices=["sp", "sp-pull", "fused", "unfused"],
+    ap.add_argument("--tp-layout", default=None, choices=["sp", "sp-pull", "fused", "unfused"],
                     help="tensor-parallel ragged program: sequence-parallel rows (GEMM + reduce-scatter epilogue, reduce + norm on "
-                         "own rows, normed rows pushed to every rank; default), the same with the all-gather pulled inside the next "
+                         "own rows, normed rows pushed to every rank; default up to 4 GPUs, the sizes it has been measured at; "
+                         "8 GPUs default to `fused`), the same with the all-gather pulled inside the next "
                          "GEMM, replicated rows with the GEMM epilogue pushing partials to the all-reduce, or replicated rows with a "
                          "plain GEMM and the all-reduce kernel pushing them (A/B)")
     ap.add_argument("--profile", action="store_true", help="after the timed region, run one more step with per-call timing and print the cost by op to stderr")
     args = ap.parse_args()
+    if args.tp_layout is None:
+        args.tp_layout = "sp" if args.gpus <= 4 else "fused"
 
     if args.impl == "reference":
         from baseline import reference_arm

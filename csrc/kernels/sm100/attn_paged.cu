@@ -47,11 +47,12 @@ KERN_DEVICE uint32_t kv_off(int tok, int chunk) {
 
 // Prefill with head_dim <= 128 runs a two-stage ring so that two CTAs (eight math warps) fit one SM: the row-parallel
 // kernel is bound by mma.sync issue, not by the depth of its KV ring; decode keeps the deep ring (it is bandwidth-bound).
-template <int D, bool PREFILL = false>
+// ST > 0 fixes the depth of the ring (the ragged entry runs both kernels' CTAs side by side at two stages each).
+template <int D, bool PREFILL = false, int ST = 0>
 struct AttnCfg {
   static constexpr int kTileBytes = TK * D * 2;         // one of K or V
   static constexpr int kStageBytes = 2 * kTileBytes;    // K then V
-  static constexpr int kStages = (PREFILL && D <= 128) ? 2 : (D >= 256 ? 3 : 4);
+  static constexpr int kStages = ST > 0 ? ST : ((PREFILL && D <= 128) ? 2 : (D >= 256 ? 3 : 4));
   static constexpr int kQStride = D + 8;                // padded bf16 row of the q tile
   static constexpr int kQBytes = 64 * kQStride * 2;
   static constexpr int kSmem = 1024 + kStages * kStageBytes + kQBytes + 256;
@@ -73,9 +74,10 @@ struct AttnArgs {
 };
 
 // PREFILL = false: decode/verify (warps split tokens); true: causal prefill (warps split rows)
-template <int D, bool PREFILL>
-KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a) {
-  using Cfg = AttnCfg<D, PREFILL>;
+// `y`: the CTA's index into the work list (or its sequence), blockIdx.y unless the caller maps it
+template <int D, bool PREFILL, int ST = 0>
+KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a, const int y) {
+  using Cfg = AttnCfg<D, PREFILL, ST>;
   constexpr int kStages = Cfg::kStages;
   constexpr int NT = PREFILL ? 8 : 2;        // 8-token n-tiles of S per warp per KV tile
   constexpr int ROWS = PREFILL ? 64 : 16;    // query rows per CTA
@@ -90,11 +92,11 @@ KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = a.hq / a.hk;
-  int seq = blockIdx.y, blk = blockIdx.x / a.hk;
+  int seq = y, blk = blockIdx.x / a.hk;
   if (a.work != nullptr) {
-    if ((int)blockIdx.y >= *a.work_count) return;   // uniform per CTA, before any barrier
-    seq = a.work[2 * blockIdx.y];
-    blk = a.work[2 * blockIdx.y + 1];
+    if (y >= *a.work_count) return;   // uniform per CTA, before any barrier
+    seq = a.work[2 * y];
+    blk = a.work[2 * y + 1];
   }
   const int L = a.seq_lens[seq];
   const int row0_tok = a.cu_q ? a.cu_q[seq] : seq * a.rows_per_seq;
@@ -391,7 +393,7 @@ using namespace kern;
     AttnArgs a{q, out, ws_o, ws_ml, block_table, seq_lens, cu_q, work, work_count, err, seqs, hq, \
                hk, q_stride,                                                                     \
                out_stride, max_pages, page_size, rows_per_seq, splits, pool_pages, scale_log2};  \
-    attn_body<D, PREFILL>(&kv_map, a);                                                           \
+    attn_body<D, PREFILL>(&kv_map, a, (int)blockIdx.y);                                          \
   }
 
 KERN_ATTN_ENTRY(kern_attn_decode_paged_d64, 64, false)
@@ -400,6 +402,32 @@ KERN_ATTN_ENTRY(kern_attn_decode_paged_d256, 256, false)
 KERN_ATTN_ENTRY(kern_attn_prefill_paged_d64, 64, true)
 KERN_ATTN_ENTRY(kern_attn_prefill_paged_d128, 128, true)
 KERN_ATTN_ENTRY(kern_attn_prefill_paged_d256, 256, true)
+
+// Both lists of a ragged call in one launch (head_dim <= 128): CTAs of the row-parallel causal kernel (list p, bound by
+// tensor-core issue) and of the token-parallel kernel (list d, bound by the KV stream) alternate in launch order while
+// both lists last, two CTAs per SM with a two-stage ring each, so the decode rows' KV streams while the prompt rows'
+// tiles compute. grid = (hk, at least count_p + count_d).
+#define KERN_ATTN_RAGGED_ENTRY(name, D)                                                          \
+  extern "C" __global__ void __launch_bounds__(160, 2)                                           \
+      name(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* q,                   \
+           __nv_bfloat16* out, const int* block_table, const int* seq_lens, const int* cu_q,     \
+           const int* work_p, const int* count_p, const int* work_d, const int* count_d,         \
+           int hq, int hk, int q_stride, int out_stride, int max_pages, int page_size,           \
+           int pool_pages, float scale_log2, int* err) {                                         \
+    const int np = *count_p, nd = *count_d, m = np < nd ? np : nd;                               \
+    const int y = blockIdx.y;                                                                    \
+    if (y >= np + nd) return;                                                                    \
+    const bool is_p = y < 2 * m ? !(y & 1) : np > nd;                                            \
+    const int idx = y < 2 * m ? (y >> 1) : y - m;                                                \
+    AttnArgs a{q, out, nullptr, nullptr, block_table, seq_lens, cu_q, is_p ? work_p : work_d,    \
+               is_p ? count_p : count_d, err, 0x7fffffff, hq, hk, q_stride, out_stride,          \
+               max_pages, page_size, 1, 1, pool_pages, scale_log2};                              \
+    if (is_p) attn_body<D, true, 2>(&kv_map, a, idx);                                            \
+    else attn_body<D, false, 2>(&kv_map, a, idx);                                                \
+  }
+
+KERN_ATTN_RAGGED_ENTRY(kern_attn_ragged_paged_d64, 64)
+KERN_ATTN_RAGGED_ENTRY(kern_attn_ragged_paged_d128, 128)
 
 // Work lists for a ragged call: one (sequence, query block) pair per block of new rows, so the
 // attention grids are sized by the rows of the call and not by sequences x the longest one.

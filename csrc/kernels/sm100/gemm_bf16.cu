@@ -89,23 +89,47 @@ struct AgArgs {
   long long timeout_ns = 2000000000ll;
 };
 
+// EP (expert parallel over sharded tokens; both forms are GROUPED):
+//   EP == 1, dispatch fused into the routed GEMM: the A operand is the expert-sorted activation buffer `xg`, and the
+//     rows are not there yet when the kernel starts. Row r of xg is token src_tok[r] (a global index: home rank =
+//     token / rows_per_rank; -1: padding), and the gather warps of the AG form pull every row straight out of its home
+//     rank's exported activation buffer (16-byte peer loads over NVLink, local rows through the same code) while the
+//     tensor-core warps already multiply the 128-row blocks that have arrived; the arrival counters and the producer's
+//     bounded wait are the AG form's. Needs the aligned plan (every tile starts on a 128-row boundary of xg).
+//   EPI == 5, combine fused into the routed GEMM's epilogue: row r of the result, times its routing weight row_w[r],
+//     is added into the f32 accumulator row of its token on the token's home rank (red.add.v4.f32 over NVLink, local
+//     tokens the same way); the top-k weighted reduction happens in those adds. When the last CTA of the grid is
+//     done it publishes this rank's epoch into every rank's `done` words; the home rank's finalize kernel waits for
+//     all of them before it reads (and clears) its accumulator.
+struct EpArgs {
+  const unsigned long long* x_peers = nullptr;    // dispatch: every rank's activation buffer [rows_per_rank, K]
+  __nv_bfloat16* xg = nullptr;                    //           this rank's expert-sorted rows (the A operand)
+  const int* src_tok = nullptr;                   // both: global token of each expert-sorted row, -1 for padding
+  const float* row_w = nullptr;                   // combine: routing weight of each expert-sorted row
+  const unsigned long long* acc_peers = nullptr;  //          every rank's f32 accumulator [rows_per_rank, N]
+  const unsigned long long* done_peers = nullptr; //          every rank's done words [nranks]
+  uint32_t* state = nullptr;                      //          {CTAs finished, epoch} (local)
+  int rows_per_rank = 1, rank = 0, nranks = 1;
+};
+
 // GROUPED: the M tiles come from a device table of int4 {expert, first row, rows (<= BM), -} built by the MoE
 // planner (`tile_count` of them); A rows are the expert-sorted activations, B is a 3-D map [K, N, experts].
 // A tile's load may run into the next expert's rows; the epilogue stores only the tile's own rows.
 // FP8: A and B hold e4m3 bytes (a swizzle row is 128 elements, the instruction is kind::f8f6f4 with K = 32), the
 // accumulator is scaled by *scale_a * *scale_b (per-tensor scales) before the epilogue's conversion.
-template <int BN, int EPI, bool GROUPED = false, bool FP8 = false, bool MT2 = false, bool AG = false>
+template <int BN, int EPI, bool GROUPED = false, bool FP8 = false, bool MT2 = false, bool AG = false, int EP = 0>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
                                           void* Cv, const void* Rv,
                                           int M, int N, int K, int ldc, int* err,
                                           const int* tile_table = nullptr, const int* tile_count = nullptr,
                                           ScatterArgs sc = ScatterArgs(), const float* scale_a = nullptr,
-                                          const float* scale_b = nullptr, AgArgs ag = AgArgs()) {
+                                          const float* scale_b = nullptr, AgArgs ag = AgArgs(), EpArgs ep = EpArgs()) {
   using Cfg = GemmCfg<BN, MT2>;
   constexpr int kStages = Cfg::kStages;
   constexpr int BMT = Cfg::kRows;
   static_assert(!(MT2 && (GROUPED || EPI == 4 || BN != 256)), "the 256-row tile exists for the plain 256-wide GEMM");
-  static_assert(!(AG && (GROUPED || FP8 || MT2)), "the all-gather form exists for the plain bf16 GEMM");
+  static_assert(!(AG && (FP8 || MT2)) && (!(AG && GROUPED) || EP == 1), "the all-gather form exists for the plain bf16 GEMM");
+  static_assert((EP != 1 || (AG && GROUPED)) && (EPI != 5 || GROUPED), "the expert-parallel forms are routed GEMMs");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -152,10 +176,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
   const int num_tiles = num_m * num_n;
   // tile t -> (first row, row bound, n block, expert)
   // AG: blocks per rank, this rank's first block, and the counter value that says "every CTA's share of the block is in"
-  const int ag_bpr = AG ? (ag.ready != nullptr ? 0 : num_m_of(M, ag.nranks)) : 0;
+  const int ag_bpr = AG ? ((EP == 1 || ag.ready != nullptr) ? 0 : num_m_of(M, ag.nranks)) : 0;
   // the block this rank's tile order and pulls start from: its own rows (contiguous slices), or a rank-dependent
   // offset so that the ranks pull from different owners at any one time (sequence-parallel sub-blocks)
   const int ag_first = AG ? (ag_bpr ? ag.rank * ag_bpr : (int)(((long long)ag.rank * num_m) / ag.nranks)) : 0;
+  const int bpr_div = ag_bpr ? ag_bpr : 1;     // divisor where the blocks-per-rank form of the expression is not taken
   uint32_t ag_want = 0;
   if constexpr (AG) {
     ag_want = (ag.epochs[blockIdx.x] + 1u) * gridDim.x;
@@ -193,14 +218,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         tile_of(t, row0, row_end, n_blk, expert);
         if constexpr (AG) {
           const int blk = row0 / BM;
-          if (ag_bpr == 0 || blk / ag_bpr != ag.rank) {       // a peer's rows: wait until every CTA has put its share of the block here
+          if (ag_bpr == 0 || blk / bpr_div != ag.rank) {       // a peer's rows: wait until every CTA has put its share of the block here
             bool here = false;
             for (uint32_t i = 0; i < (1u << 22) && !here; ++i) {
               here = ld_acquire_sys(ag.flags + blk) >= ag_want;
               if (!here) { if ((i & 0xff) == 0xff && *abort_flag != 0) break; __nanosleep(100); }
             }
             if (!here) {
-              set_error(err, ERR_WAIT_PEER + (ag_bpr ? blk / ag_bpr : ag.nranks));
+              set_error(err, ERR_WAIT_PEER + (ag_bpr ? blk / bpr_div : ag.nranks));
               *abort_flag = 1;
               break;
             }
@@ -286,8 +311,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
     if constexpr (AG) {
       constexpr int GT = kGatherWarps * 32;
       const int gt = threadIdx.x - 192;                      // 0..GT-1
-      uint8_t* mine = reinterpret_cast<uint8_t*>(ag.peers[ag.rank]);
-      const bool sp = ag.ready != nullptr;
+      uint8_t* mine = EP == 1 ? reinterpret_cast<uint8_t*>(ep.xg) : reinterpret_cast<uint8_t*>(ag.peers[ag.rank]);
+      const bool sp = EP != 1 && ag.ready != nullptr;
+      constexpr bool epd = EP == 1;
       if (sp) {
         // every peer's rows of this call are final once its `ready` word has reached this rank's own epoch
         const uint32_t e = *reinterpret_cast<const volatile uint32_t*>(ag.epoch_word);
@@ -308,7 +334,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
       // blocks nobody gathers in this launch (own rows, blocks past the last row) arrive at once: every counter moves
       // by the grid size in every launch, whatever the row count
       for (int b = gt; b < ag.max_blocks; b += GT) {
-        const bool remote = b < num_m && !ag.pushed && (sp || b / ag_bpr != ag.rank);
+        const bool remote = b < num_m && !ag.pushed && (sp || epd || b / bpr_div != ag.rank);
         if (!remote) atomicAdd(ag.flags + b, 1u);
       }
       // The blocks to pull, in the order the tiles will want them, form one run of 16-byte vectors that is cut into units
@@ -318,13 +344,19 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
       // A block's counter moves once every unit that touches the block has been stored.
       const size_t row_vecs = (size_t)K * 2 / 16;
       const size_t vecs = (size_t)BM * row_vecs, stride = (size_t)gridDim.x * GT, span = stride * 8;
-      const int pull_blocks = ag.pushed ? 0 : (sp ? num_m : num_m - ag_bpr);
+      const int pull_blocks = ag.pushed ? 0 : ((sp || epd) ? num_m : num_m - ag_bpr);
       const size_t total = (size_t)pull_blocks * vecs;
       const int units = (*abort_flag != 0) ? 0 : (int)((total + span - 1) / span);
-      auto block_at = [&](int i) { return ((sp ? 0 : ag_bpr) + i + ag_first) % num_m; };   // i-th block in pull order
+      auto block_at = [&](int i) { return (((sp || epd) ? 0 : ag_bpr) + i + ag_first) % num_m; };   // i-th block in pull order
       // where vector v of block b comes from (null: it is this rank's own, or past the last row)
       auto source = [&](int b, size_t v) -> const uint8_t* {
-        if (!sp) return reinterpret_cast<const uint8_t*>(ag.peers[b / ag_bpr]) + (size_t)b * BM * K * 2 + v * 16;
+        if constexpr (epd) {        // row r of the sorted buffer is token src_tok[r] on its home rank
+          const int tok = ep.src_tok[b * BM + (int)(v / row_vecs)];
+          if (tok < 0) return nullptr;
+          return reinterpret_cast<const uint8_t*>(ep.x_peers[tok / ep.rows_per_rank]) +
+                 ((size_t)(tok % ep.rows_per_rank) * row_vecs + v % row_vecs) * 16;
+        }
+        if (!sp) return reinterpret_cast<const uint8_t*>(ag.peers[b / bpr_div]) + (size_t)b * BM * K * 2 + v * 16;
         const int row = b * BM + (int)(v / row_vecs);
         const int owner = (row / kSpRows) % ag.nranks;
         if (row >= M || owner == ag.rank) return nullptr;
@@ -487,6 +519,33 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
           }
           __syncwarp();
         }
+      } else if constexpr (EPI == 5) {
+        // combine: this row, times its routing weight, is added into its token's accumulator on the home rank
+        float* dst = nullptr;
+        float wr = 0.f;
+        if (row < row_end) {
+          const int tok = ep.src_tok[row];
+          if (tok >= 0) {
+            wr = ep.row_w[row];
+            dst = reinterpret_cast<float*>(ep.acc_peers[tok / ep.rows_per_rank]) + (size_t)(tok % ep.rows_per_rank) * N;
+          }
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          const int col = n_blk * BN + c * 32;
+          if (dst != nullptr) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              if (col + v * 4 < N)
+                asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + col + v * 4),
+                             "f"(__uint_as_float(r[v * 4]) * wr), "f"(__uint_as_float(r[v * 4 + 1]) * wr),
+                             "f"(__uint_as_float(r[v * 4 + 2]) * wr), "f"(__uint_as_float(r[v * 4 + 3]) * wr)
+                             : "memory");
+          }
+        }
       } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -544,10 +603,23 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
   }
 
   // ---------------- teardown ----------------
-  if constexpr (EPI == 4) __threadfence_system();   // the pushed rows are on their way before the kernel is done
+  if constexpr (EPI == 4 || EPI == 5) __threadfence_system();   // the pushed rows are on their way before the kernel is done
   pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
+  if constexpr (EPI == 5) {
+    // the last CTA to get here publishes this rank's epoch: every add of this launch is ordered before it
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      if (atomicAdd(ep.state, 1u) == gridDim.x - 1) {
+        ep.state[0] = 0;
+        const uint32_t e = ep.state[1] + 1;
+        ep.state[1] = e;
+        __threadfence_system();
+        for (int r = 0; r < ep.nranks; ++r) st_release_sys(reinterpret_cast<uint32_t*>(ep.done_peers[r]) + ep.rank, e);
+      }
+    }
+  }
   if (*abort_flag != 0 && threadIdx.x == 0) {
     // give loads that were in flight time to land before the CTA (and its shared memory) retires
     const uint64_t t0 = globaltimer_ns();

@@ -405,7 +405,17 @@ def _attention_fmha(g, kv, q, out, table, seq_lens, cu_q, work, work_count, hq, 
                      page, 1, 1, pool_pages, scale_log2, err)
 
 
+def _attention_ragged(g, kv, q, out, table, seq_lens, cu_q, work_p, count_p, work_d, count_d, hq, hk, q_stride, out_stride,
+                      max_pages, page, pool_pages, scale_log2, err):
+    """Both work lists of a ragged call in one launch: the row-parallel and the token-parallel kernel's statements."""
+    for prefill, work, count in ((True, work_p, count_p), (False, work_d, count_d)):
+        _attention(prefill)(g, kv, q, out, 0, 0, table, seq_lens, cu_q, work, count, 0, hq, hk, q_stride, out_stride,
+                            max_pages, page, 1, 1, pool_pages, scale_log2, err)
+
+
 CPU_KERNELS["kern_attn_fmha_prefill_d128"] = _attention_fmha
+for _d in (64, 128):
+    CPU_KERNELS[f"kern_attn_ragged_paged_d{_d}"] = _attention_ragged
 for _d in (16, 32, 64, 128, 256):
     CPU_KERNELS[f"kern_attn_prefill_paged_d{_d}"] = _attention(True)
     CPU_KERNELS[f"kern_attn_decode_paged_d{_d}"] = _attention(False)

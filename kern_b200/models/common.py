@@ -347,6 +347,14 @@ def fmha_prefill(hq: int, hk: int, d: int) -> bool:
     return d == 128 and 128 % (hq // hk) == 0 and os.environ.get("KERN_B200_FMHA", "0") == "1"
 
 
+def attn_ragged(d: int) -> bool:
+    """Whether a ragged call's two work lists run as one launch (head_dim 64 or 128; `KERN_B200_ATTN_RAGGED=0` keeps
+    the two launches, for A/B)."""
+    import os
+
+    return d in (64, 128) and os.environ.get("KERN_B200_ATTN_RAGGED", "1") != "0"
+
+
 def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, q_stride: int) -> dict:
     """Ragged causal attention over the paged context.
     Interface [q(kv) buffer, kv state, out, block_table, seq_lens, cu_seqlens, work, work_count, err]."""
@@ -376,6 +384,18 @@ def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, 
                 "args": [_kv_map(d, page_size, 1), {"param": 0}, {"param": 2}, {"param": 3}, {"param": 4}, {"param": 5}, {"param": 6},
                          {"param": 7}, {"i32": hq}, {"i32": hk}, {"i32": q_stride}, {"i32": hq * d}, {"i32": table_width},
                          {"i32": page_size}, {"i32": I32_MAX}, {"f32": (d ** -0.5) * 1.4426950408889634}, {"param": 8}]}
+    elif attn_ragged(d):
+        # both lists in one launch: the two kernels' CTAs alternate, two per SM, so the decode rows' KV streams under
+        # the prompt rows' tensor-core work (a sequence is on one list only, so the grid bound is unchanged)
+        return {"params": iface, "impl": {"launches": [{
+            "module": "attn_paged", "entry": f"kern_attn_ragged_paged_d{d}", "block": [160, 1, 1],
+            "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1], "shared_mem": attn_smem(d, prefill=True),
+            "params": ["bytes<128>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "in buffer<i32>",
+                       "in buffer<i32>", "in buffer<i32>", "in buffer<i32>", "in buffer<i32>"] + ["i32"] * 7 + ["f32", "out buffer<i32>"],
+            "args": [_kv_map(d, page_size, 1), {"param": 0}, {"param": 2}, {"param": 3}, {"param": 4}, {"param": 5}, {"param": 6},
+                     {"param": 7}, {"param": 9}, {"param": 10}, {"i32": hq}, {"i32": hk}, {"i32": q_stride}, {"i32": hq * d},
+                     {"i32": table_width}, {"i32": page_size}, {"i32": I32_MAX}, {"f32": (d ** -0.5) * 1.4426950408889634},
+                     {"param": 8}]}]}}
     else:
         many = {"module": "attn_paged", "entry": f"kern_attn_prefill_paged_d{d}", "block": [160, 1, 1],
                 "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1], "shared_mem": attn_smem(d, prefill=True),

@@ -6,6 +6,8 @@ Reference shape: docs/roadmap.md:13-16 (EP decode as gather, local experts, redu
 """
 from __future__ import annotations
 
+import dataclasses
+
 from . import common as C
 from . import dense_tp
 from .moe import MoeConfig, _moe_ops
@@ -77,4 +79,168 @@ def build_manifest_ep(cfg: MoeConfig, lamport: bool = True) -> dict:
         doc["programs"][prog]["calls"] = out
     mods = list(doc["modules"]) + ["moe"]
     doc["modules"] = C.modules_for([m for m in mods if m != "gemv_bf16"])
+    return doc
+
+
+# ---- expert parallel over sharded tokens: every rank runs its own sequences (attention data-parallel), experts by ranges ----
+
+def ep_fused_buffers(world: int, rows_max: int, hidden: int, inter: int, e_n: int, k: int, x: str, group: str = "ep") -> dict:
+    """Buffers of the fused dispatch / combine kernels (`moe.cu`, `kern_ep_*`). `x`: the name of the activation buffer
+    the experts read (exported here, with its peer table `<x>_peers`); `rows_max`: tokens per rank."""
+    T = rows_max * world
+    max_tiles = T * k // C.BM + e_n
+    max_rows = max_tiles * C.BM                  # every expert's rows start on a 128-row boundary
+    buf = lambda dt, shape, kind="workspace", **kw: {"dtype": dt, "shape": shape, "kind": kind, **kw}
+    peer = lambda of: {"dtype": "u64", "shape": [world], "kind": "peer", "of": of, "group": group}
+    return {
+        x + "_peers": peer(x),
+        "ep.ids_all": buf("i32", [T, k], "carry", export=True), "ep.ids_peers": peer("ep.ids_all"),
+        "ep.w_all": buf("f32", [T, k], "carry", export=True), "ep.w_peers": peer("ep.w_all"),
+        "ep.ready": buf("u32", [world], "carry", export=True), "ep.ready_peers": peer("ep.ready"),
+        "ep.pub_epoch": buf("u32", [1], "carry"),
+        "ep.acc": buf("f32", [rows_max, hidden], "carry", export=True), "ep.acc_peers": peer("ep.acc"),
+        "ep.done": buf("u32", [world], "carry", export=True), "ep.done_peers": peer("ep.done"),
+        "ep.state": buf("u32", [2], "carry"), "ep.blocks": buf("u32", [max_tiles], "carry"),
+        "ep.cta_epochs": buf("u32", [C.SMS], "carry"),
+        "ep.perm": buf("i32", [T, k]), "ep.offsets": buf("i32", [e_n + 1]), "ep.tiles": buf("i32", [max_tiles, 4]),
+        "ep.tile_count": buf("i32", [1]), "ep.n_rows": buf("i32", [1]), "ep.src_tok": buf("i32", [max_rows]),
+        "ep.row_w": buf("f32", [max_rows]),
+        "ep.xp": buf("bf16", [max_rows, hidden], "carry"), "ep.act": buf("bf16", [max_rows, inter]),
+    }
+
+
+def ep_fused_ops(world: int, rows_max: int, hidden: int, inter: int, e_n: int, k: int, rows_var: str, group: str = "ep",
+                 accumulate: bool = False, timeout_ns: int = 2_000_000_000) -> dict:
+    """The five ops of a fused expert-parallel layer. Interfaces:
+    ep_publish [ids, w, ids_peers, w_peers, ready_peers, pub_epoch, rows];
+    ep_plan [ids_all, w_all, perm, offsets, tiles, tile_count, n_rows, src_tok, row_w, ready, pub_epoch, err];
+    ep_fc1 [xp, w1, act, tiles, tile_count, x_peers, src_tok, blocks, cta_epochs, err];
+    ep_fc2 [act, w2, tiles, tile_count, acc_peers, src_tok, row_w, state, done_peers, err];
+    ep_finalize [acc, out, done, state, err] (`accumulate`: out += the experts' sum, else out = it)."""
+    T = rows_max * world
+    max_tiles = T * k // C.BM + e_n
+    max_rows = max_tiles * C.BM
+    L = lambda module, entry, block, grid, lp, args, **kw: {"module": module, "entry": entry, "block": block, "grid": grid,
+                                                            "params": lp, "args": args, **kw}
+    P = lambda i: {"param": i}
+    rank = {"rank": group}
+    ops = {}
+    ops["ep_publish"] = {"params": ["in buffer<i32>", "in buffer<f32>", "in buffer<u64>", "in buffer<u64>", "in buffer<u64>",
+                                    "inout buffer<u32>", "i32"], "impl": {"launches": [L(
+        "moe", "kern_ep_publish", [1024, 1, 1], [1, 1, 1],
+        ["in buffer<i32>", "in buffer<f32>", "in buffer<u64>", "in buffer<u64>", "in buffer<u64>", "inout buffer<u32>", "i32", "i32",
+         "i32", "i32", "i32"],
+        [P(0), P(1), P(2), P(3), P(4), P(5), P(6), {"i32": rows_max}, {"i32": k}, rank, {"i32": world}])]}}
+    # the tables and flag words the peers write into are `inout` here: their writers are other ranks' kernels
+    ops["ep_plan"] = {"params": ["inout buffer<i32>", "inout buffer<f32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>",
+                                 "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<f32>", "inout buffer<u32>",
+                                 "in buffer<u32>", "out buffer<i32>"], "impl": {"launches": [L(
+        "moe", "kern_moe_plan_ep", [1024, 1, 1], [1, 1, 1],
+        ["inout buffer<i32>", "inout buffer<f32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>",
+         "out buffer<i32>", "out buffer<i32>", "out buffer<f32>", "inout buffer<u32>", "in buffer<u32>"] + ["i32"] * 6 +
+        ["out buffer<i32>", "i32", "i32", "i64"],
+        [P(i) for i in range(11)] + [{"i32": T * k}, {"i32": k}, {"i32": e_n}, {"i32": C.BM}, {"i32": max_tiles}, {"i32": max_rows},
+                                     P(11), rank, {"i32": world}, {"i64": timeout_ns}], shared_mem=2 * e_n * 4)]}}
+
+    def maps(kk, n, swiglu, bn):
+        a_map = {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+            "param": 0, "dtype": "bf16", "dims": [kk, 0], "strides": [kk * 2], "box": [C.BK, C.BM], "swizzle": 128, "l2_promotion": 256}}]}}
+        b_map = {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+            "param": 1, "dtype": "bf16", "dims": [kk, n, e_n], "strides": [kk * 2, n * kk * 2],
+            "box": [C.BK, bn // 2 if swiglu else bn, 1], "swizzle": 128, "l2_promotion": 256}}]}}
+        return a_map, b_map
+
+    bn1 = 128 if 2 * inter >= 128 else 64
+    a1, b1 = maps(hidden, 2 * inter, True, bn1)
+    ops["ep_fc1"] = {"params": ["inout buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>",
+                                "in buffer<u64>", "in buffer<i32>", "inout buffer<u32>", "inout buffer<u32>", "out buffer<i32>"],
+                     "impl": {"launches": [L(
+        "moe", f"kern_ep_fc1_bf16_swiglu_n{bn1}", [320, 1, 1], [C.SMS, 1, 1],
+        ["bytes<128>", "bytes<128>", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "i32", "i32", "i32", "i32",
+         "out buffer<i32>", "in buffer<u64>", "inout buffer<bf16>", "in buffer<i32>", "inout buffer<u32>", "inout buffer<u32>",
+         "i32", "i32", "i32", "i32"],
+        [a1, b1, P(2), P(3), P(4), {"i32": max_rows}, {"i32": 2 * inter}, {"i32": hidden}, {"i32": inter}, P(9), P(5), P(0), P(6),
+         P(7), P(8), {"i32": rows_max}, {"i32": max_tiles}, rank, {"i32": world}], shared_mem=C.gemm_smem(bn1))]}}
+    bn2 = 128 if hidden >= 128 else 64
+    a2, b2 = maps(inter, hidden, False, bn2)
+    ops["ep_fc2"] = {"params": ["in buffer<bf16>", "in buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "in buffer<u64>",
+                                "in buffer<i32>", "in buffer<f32>", "inout buffer<u32>", "in buffer<u64>", "out buffer<i32>"],
+                     "impl": {"launches": [L(
+        "moe", f"kern_ep_fc2_bf16_combine_n{bn2}", [192, 1, 1], [C.SMS, 1, 1],
+        ["bytes<128>", "bytes<128>", "in buffer<i32>", "in buffer<i32>", "i32", "i32", "i32", "out buffer<i32>", "in buffer<u64>",
+         "in buffer<i32>", "in buffer<f32>", "inout buffer<u32>", "in buffer<u64>", "i32", "i32", "i32"],
+        [a2, b2, P(2), P(3), {"i32": max_rows}, {"i32": hidden}, {"i32": inter}, P(9), P(4), P(5), P(6), P(7), P(8),
+         {"i32": rows_max}, rank, {"i32": world}], shared_mem=C.gemm_smem(bn2))]}}
+    odir = "inout" if accumulate else "out"
+    ops["ep_finalize"] = {"params": ["inout buffer<f32>", f"{odir} buffer<bf16>", "inout buffer<u32>", "in buffer<u32>",
+                                     "out buffer<i32>"], "impl": {"launches": [L(
+        "moe", "kern_ep_finalize", [128, 1, 1], [rows_var, 1, 1],
+        ["inout buffer<f32>", f"{odir} buffer<bf16>", "i64", "inout buffer<u32>", "in buffer<u32>", "out buffer<i32>", "i32", "i32",
+         "i32", "i64", "i32"],
+        [P(0), P(1), {"i64": 0}, P(2), P(3), P(4), {"i32": C.I32_MAX}, {"i32": hidden}, {"i32": world}, {"i64": timeout_ns},
+         {"i32": int(accumulate)}])]}}
+    return ops
+
+
+def ep_fused_calls(ids: str, w: str, x: str, w1: str, w2: str, out: str, rows_var: str, label: str = "") -> list[dict]:
+    """The five calls of one fused layer: routing of this rank's rows in `ids` / `w`, activations in the exported `x`,
+    this rank's expert weights `w1` / `w2`, the experts' weighted sum into `out`."""
+    B = lambda n: {"buf": n}
+    err = B("error")
+    return [
+        {"op": "ep_publish", "label": label + "publish", "args": [B(ids), B(w), B("ep.ids_peers"), B("ep.w_peers"),
+                                                                  B("ep.ready_peers"), B("ep.pub_epoch"), {"var": rows_var}]},
+        {"op": "ep_plan", "label": label + "plan", "args": [B("ep.ids_all"), B("ep.w_all"), B("ep.perm"), B("ep.offsets"),
+                                                            B("ep.tiles"), B("ep.tile_count"), B("ep.n_rows"), B("ep.src_tok"),
+                                                            B("ep.row_w"), B("ep.ready"), B("ep.pub_epoch"), err]},
+        {"op": "ep_fc1", "label": label + "fc1", "args": [B("ep.xp"), B(w1), B("ep.act"), B("ep.tiles"), B("ep.tile_count"),
+                                                          B(x + "_peers"), B("ep.src_tok"), B("ep.blocks"), B("ep.cta_epochs"), err]},
+        {"op": "ep_fc2", "label": label + "fc2", "args": [B("ep.act"), B(w2), B("ep.tiles"), B("ep.tile_count"), B("ep.acc_peers"),
+                                                          B("ep.src_tok"), B("ep.row_w"), B("ep.state"), B("ep.done_peers"), err]},
+        {"op": "ep_finalize", "label": label + "finalize", "args": [B("ep.acc"), B(out), B("ep.done"), B("ep.state"), err]},
+    ]
+
+
+def build_manifest_ep_sharded(cfg: MoeConfig, world: int) -> dict:
+    """The MoE decoder with tokens sharded over an expert-parallel group: every rank serves its own sequences (attention,
+    norms, router and head are whole on every rank: data parallel), rank r keeps experts [r E/n, (r+1) E/n), and every
+    routed layer is the fused pair of kernels — dispatch inside FC1, combine inside FC2. The ranks step in lockstep: a
+    layer's kernels wait for every rank's publish and done words. `cfg.max_tokens` is the rows per rank."""
+    from . import moe
+
+    assert world >= 1 and cfg.experts % world == 0
+    doc = moe.build_manifest(dataclasses.replace(cfg, mx_experts=False) if getattr(cfg, "mx_experts", False) else cfg)
+    doc["model"] = f"{cfg.name}-ep{world}-sharded"
+    doc.setdefault("topology", {}).setdefault("groups", {})["ep"] = world
+    bufs, ops = doc["buffers"], doc["ops"]
+    h, I, E, k, T = cfg.hidden, cfg.moe_intermediate, cfg.experts, cfg.top_k, cfg.max_tokens
+    el = E // world
+    for name in ("moe_plan", "moe_gather", "moe_fc1", "moe_fc2", "moe_combine"):
+        ops.pop(name)
+    for name in ("moe.perm", "moe.offsets", "moe.tiles", "moe.tile_count", "moe.rows", "moe.x", "moe.act", "moe.y"):
+        bufs.pop(name)
+    bufs["xn"]["export"] = True
+    bufs.update(ep_fused_buffers(world, T, h, I, el, k, "xn"))
+    ops.update(ep_fused_ops(world, T, h, I, el, k, "tokens", accumulate=True))
+    ranked = lambda fmt: {"group": "ep", "tensors": [fmt(r) for r in range(world)]}
+    for i in range(cfg.layers):
+        p = f"model.layers.{i}.mlp."
+        bufs[f"w.l{i}.w1"] = {"dtype": "bf16", "shape": [el, 2 * I, h], "kind": "weight",
+                              "bind": [{"tensor": ranked(lambda r, j=j, part=part: p + f"experts.{r * el + j}.{part}_proj.weight")}
+                                       for j in range(el) for part in ("gate", "up")]}
+        bufs[f"w.l{i}.w2"] = {"dtype": "bf16", "shape": [el, h, I], "kind": "weight",
+                              "bind": [{"tensor": ranked(lambda r, j=j: p + f"experts.{r * el + j}.down_proj.weight")} for j in range(el)]}
+    drop = (".plan", ".gather", ".fc1", ".fc2")
+    for prog in doc["programs"].values():
+        out = []
+        for c in prog["calls"]:
+            lbl = c.get("label", "")
+            if lbl.endswith(drop):
+                continue
+            if lbl.endswith(".combine"):
+                i = int(lbl[1:lbl.index(".")])
+                out += ep_fused_calls("moe.ids", "moe.w", "xn", f"w.l{i}.w1", f"w.l{i}.w2", "x", "tokens", label=f"l{i}.ep_")
+            else:
+                out.append(c)
+        prog["calls"] = out
     return doc

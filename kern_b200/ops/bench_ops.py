@@ -287,6 +287,27 @@ def bench_attn_prefill(a):
            rows=a.rows, prefix=a.prefix)
 
 
+def bench_attn_ragged(a):
+    """One serving step's attention: a prompt chunk of `rows` rows plus `seqs` decode rows over `ctx` tokens each, as
+    one launch (both kernels' CTAs side by side) or as the two launches one after the other (`--two-launches`)."""
+    from .attention import ragged_attention
+    from .launcher import Kernels
+
+    per = (max(a.ctx, a.rows) + a.page - 1) // a.page
+    n = a.seqs + 1
+    pool = torch.randn(n * per + 1, 2, a.hk, a.page, a.d, device="cuda").to(torch.bfloat16)
+    table = (torch.randperm(n * per, device="cuda").to(torch.int32) + 1).view(n, per).contiguous()
+    q = torch.randn(a.rows + a.seqs, a.hq * a.d, device="cuda").to(torch.bfloat16)
+    lens = torch.tensor([a.rows] + [a.ctx] * a.seqs, dtype=torch.int32, device="cuda")
+    cu = torch.tensor([0] + [a.rows + i for i in range(a.seqs + 1)], dtype=torch.int32, device="cuda")
+    out = torch.empty_like(q)
+    ms = timeit(lambda: ragged_attention(q, pool, table, lens, a.hq, cu, out=out, one_launch=not a.two_launches), a.iters)
+    Kernels.get().check_error()
+    kv_bytes = a.seqs * a.ctx * 2 * a.hk * a.d * 2
+    report("attn_ragged_two_launches" if a.two_launches else "attn_ragged_one_launch", ms, nbytes=kv_bytes,
+           flops=4.0 * a.hq * a.d * a.rows * (a.rows + 1) / 2, prompt_rows=a.rows, decode_seqs=a.seqs, ctx=a.ctx)
+
+
 def bench_norm(a):
     from .basic import rms_norm
 
@@ -331,16 +352,20 @@ def main(argv=None):
     d.add_argument("--ctx", type=int, default=2432); d.add_argument("--splits", type=int, default=None)
     p.add_argument("--prefix", type=int, default=0)
     p.add_argument("--fmha", action="store_true", help="the tcgen05 kernel (head_dim 128) instead of the mma.sync one")
+    rg = sub.add_parser("attn_ragged")
+    rg.add_argument("--seqs", type=int, default=256); rg.add_argument("--hq", type=int, default=32); rg.add_argument("--hk", type=int, default=8)
+    rg.add_argument("--d", type=int, default=128); rg.add_argument("--page", type=int, default=64); rg.add_argument("--rows", type=int, default=2304)
+    rg.add_argument("--ctx", type=int, default=2432); rg.add_argument("--two-launches", action="store_true")
     ml = sub.add_parser("mla_decode")
     ml.add_argument("--seqs", type=int, default=64); ml.add_argument("--ctx", type=int, default=8192)
     ml.add_argument("--heads", type=int, default=16); ml.add_argument("--page", type=int, default=64)
     ml.add_argument("--splits", type=int, default=None)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=4096); n.add_argument("--n", type=int, default=4096)
-    for s in (g, d, p, n, g8, mo, gd, ml, gx, mx):
+    for s in (g, d, p, n, g8, mo, gd, ml, gx, mx, rg):
         s.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "gemm_mx": bench_gemm_mx, "moe_mx": bench_moe_mx, "gdn": bench_gdn, "gemm_fp8": bench_gemm_fp8, "moe": bench_moe, "attn_decode": bench_attn_decode, "mla_decode": bench_mla_decode, "attn_prefill": bench_attn_prefill, "norm": bench_norm}[a.op](a)
+    {"gemm": bench_gemm, "gemm_mx": bench_gemm_mx, "moe_mx": bench_moe_mx, "gdn": bench_gdn, "gemm_fp8": bench_gemm_fp8, "moe": bench_moe, "attn_decode": bench_attn_decode, "mla_decode": bench_mla_decode, "attn_prefill": bench_attn_prefill, "attn_ragged": bench_attn_ragged, "norm": bench_norm}[a.op](a)
 
 
 if __name__ == "__main__":

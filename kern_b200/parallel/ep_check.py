@@ -116,6 +116,73 @@ def manifest(world: int, rows_max: int, hidden: int, inter: int, experts: int, k
                          "step_graph": {"batch": {"groups": 1, "rows": "rows"}, "graph": True, "calls": calls}}}
 
 
+def manifest_fused(world: int, rows_max: int, hidden: int, inter: int, experts: int, k: int) -> dict:
+    """The same layer with the dispatch inside FC1 and the combine inside FC2 (`moe.cu`, the `kern_ep_*` entries): five
+    launches, no barrier kernel, no NCCL call. `rows_max`: tokens per rank."""
+    from ..models import common as C
+    from ..models import moe_ep
+
+    assert experts % world == 0 and hidden % 8 == 0
+    e_n = experts // world
+    buf = lambda dt, shape, kind="workspace", **kw: {"dtype": dt, "shape": shape, "kind": kind, **kw}
+    bufs = {
+        "ep.x": buf("bf16", [rows_max, hidden], "inout", export=True),
+        "ids": buf("i32", ["rows", k], "input"), "w": buf("f32", ["rows", k], "input"),
+        "w1": buf("bf16", [e_n, 2 * inter, hidden], "input"), "w2": buf("bf16", [e_n, hidden, inter], "input"),
+        "out": buf("bf16", ["rows", hidden], "output"), "error": buf("i32", [1], "output"),
+        **moe_ep.ep_fused_buffers(world, rows_max, hidden, inter, e_n, k, "ep.x"),
+    }
+    ops = moe_ep.ep_fused_ops(world, rows_max, hidden, inter, e_n, k, "rows")
+    calls = moe_ep.ep_fused_calls("ids", "w", "ep.x", "w1", "w2", "out", "rows")
+    return {"schema_version": 7, "model": "ep-fused-check", "vars": {"rows": {"max": rows_max, "axis": "rows"}},
+            "topology": {"groups": {"ep": world}}, "states": {}, "buffers": bufs,
+            "modules": C.modules_for(["moe"]), "ops": ops,
+            "programs": {"step": {"calls": calls},
+                         "step_graph": {"batch": {"groups": 1, "rows": "rows"}, "graph": True, "calls": calls}}}
+
+
+def check_model(rank: int, world: int, dev) -> dict:
+    """The MoE decoder with tokens sharded over the group (`models/moe_ep.py::build_manifest_ep_sharded`): every rank
+    serves its own prompts, the routed layers are the fused kernels; logits against the one-GPU fp32 oracle."""
+    import dataclasses
+
+    from ..engine import Engine
+    from ..models import moe, moe_ep
+    from ..runtime import Runtime
+    from . import group
+
+    cfg = dataclasses.replace(moe.TINY_MOE, name="tiny-moe-eps", experts=16, top_k=4)
+    weights = moe.random_weights(cfg, seed=0, std=0.05)
+    doc = moe_ep.build_manifest_ep_sharded(cfg, world)
+    rt = Runtime(doc, gpu=dev.index, topology=group.topology(doc["topology"]["groups"], rank, world), tokens=cfg.page_size * 64)
+    rt.load_tensors(lambda name: weights[name].to(dev))
+    group.start(rt)
+    eng = Engine(rt)
+    oracle = moe.MoeOracle(cfg, weights, device="cuda")
+    g = torch.Generator().manual_seed(100 + rank)                       # every rank has its own traffic
+    prompts = [torch.randint(0, cfg.vocab, (int(n),), generator=g).tolist() for n in torch.randint(3, 90, (3,), generator=g)]
+    seqs = [eng.open(140) for _ in prompts]
+    caches = [oracle.new_cache() for _ in prompts]
+    first = eng.step(list(zip(seqs, prompts)))
+    diffs = []
+    logits = rt.tensor("logits")[:3].float()
+    for i, (p, c) in enumerate(zip(prompts, caches)):
+        diffs.append((logits[i] - oracle.forward(p, c)[-1]).abs())
+    toks = [f[0] for f in first]
+    for _ in range(4):                                                   # the same number of steps on every rank
+        refs = [oracle.forward([t], c)[-1] for t, c in zip(toks, caches)]
+        nxt = eng.step([(s, [t]) for s, t in zip(seqs, toks)])
+        logits = rt.tensor("logits")[:3].float()
+        diffs += [(logits[i] - refs[i]).abs() for i in range(3)]
+        toks = [n[0] for n in nxt]
+    rt.check_error()
+    worst, mean = max(float(d.max()) for d in diffs), max(float(d.mean()) for d in diffs)
+    ok = torch.tensor([int(worst < 0.3 and mean < 0.05)], device=dev)
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return {"max_logit_diff": round(worst, 4), "mean_logit_diff": round(mean, 4), "graphs": rt.graphs, "ok": bool(ok.item())}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--rows", type=int, nargs="+", default=[8, 200, 64], help="tokens per rank")
@@ -124,6 +191,8 @@ def main(argv=None) -> int:
     ap.add_argument("--experts", type=int, default=16)
     ap.add_argument("--top-k", type=int, default=4)
     ap.add_argument("--time", action="store_true")
+    ap.add_argument("--fused", action="store_true", help="dispatch inside FC1, combine inside FC2 (five launches per layer)")
+    ap.add_argument("--model", action="store_true", help="also run the MoE decoder with sharded tokens and fused routed layers")
     a = ap.parse_args(argv)
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -136,7 +205,7 @@ def main(argv=None) -> int:
     h, I, E, k = a.hidden, a.inter, a.experts, a.top_k
     e_n = E // world
     rows_max = max(a.rows)
-    rt = Runtime(manifest(world, rows_max, h, I, E, k), gpu=local, topology={"ep": (rank, world)})
+    rt = Runtime((manifest_fused if a.fused else manifest)(world, rows_max, h, I, E, k), gpu=local, topology={"ep": (rank, world)})
     group.start(rt)
     g = torch.Generator().manual_seed(21)
     w1 = (torch.randn(E, 2 * I, h, generator=g) * 0.05).to(torch.bfloat16)       # [gate rows ; up rows] per expert
@@ -154,8 +223,9 @@ def main(argv=None) -> int:
         rt.tensor("ep.x")[:tr].copy_(xs[rank].to(dev))
         rt.tensor("ids").view(-1)[: tr * k].copy_(ids[rank].reshape(-1).to(dev))
         rt.tensor("w").view(-1)[: tr * k].copy_(ws[rank].reshape(-1).to(dev))
-        rt.tensor("iota").view(-1)[: tr * k].copy_(torch.arange(tr * k, dtype=torch.int32, device=dev))
-        rt.tensor("ep.ret").fill_(float("nan"))        # a slot nobody returns to would poison the sum
+        if not a.fused:
+            rt.tensor("iota").view(-1)[: tr * k].copy_(torch.arange(tr * k, dtype=torch.int32, device=dev))
+            rt.tensor("ep.ret").fill_(float("nan"))        # a slot nobody returns to would poison the sum
         torch.cuda.synchronize()
         rt.run(program, {"rows": tr})
         rt.check_error()
@@ -174,7 +244,7 @@ def main(argv=None) -> int:
         if world > 1:
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         results.append({"rows_per_rank": tr, "program": program, "max_abs_err": round(err, 4), "ok": bool(ok.item())})
-    line = {"check": "expert_parallel_all_to_all", "world": world, "experts": E, "top_k": k, "hidden": h, "results": results}
+    line = {"check": "expert_parallel_fused" if a.fused else "expert_parallel_all_to_all", "world": world, "experts": E, "top_k": k, "hidden": h, "results": results}
     if a.time:
         stream = torch.cuda.ExternalStream(rt.stream)
         times = []
@@ -198,6 +268,10 @@ def main(argv=None) -> int:
         line["times"] = times
     if rank == 0:
         print(json.dumps(line), flush=True)
+    if a.model:
+        m = check_model(rank, world, dev)
+        if rank == 0:
+            print(json.dumps({"check": "expert_parallel_sharded_decoder", "world": world, **m}), flush=True)
     allok = all(r["ok"] for r in results)
     if world > 1:
         dist.barrier()

@@ -169,6 +169,36 @@ def test_prefill_attention_ragged_with_prefix(cuda, hq, hk, d, page_size):
         torch.testing.assert_close(out[lo:hi].float(), ref, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("hq,hk,d,page_size", [(32, 8, 128, 64), (8, 2, 64, 16), (4, 4, 128, 128)])
+@pytest.mark.parametrize("one_launch", [True, False])
+def test_ragged_attention_both_lists(cuda, hq, hk, d, page_size, one_launch):
+    """Prompt chunks and decode rows in one call: the one-launch form (both kernels' CTAs side by side) and the
+    two-launch form against the fp32 statement, with more decode sequences than prompt blocks and the reverse."""
+    from kern_b200.ops import attention as A
+
+    torch.manual_seed(16)
+    g = hq // hk
+    small = max(1, 16 // g)
+    for new, prefix in (([300, 1, 1, small, 70, 1, 1, 1, 1, 1, 1, 1], [0, 500, 63, 200, 64, 1, 127, 128, 129, 900, 31, 5]),
+                        ([1, 257, 130, 5, 64], [40, 300, 0, 17, 64])):
+        lens = [n + p for n, p in zip(new, prefix)]
+        seqs = len(lens)
+        pool, table, ks, vs = _build_cache(cuda, seqs, lens, hk, d, page_size)
+        cu = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=cuda)
+        total = int(cu[-1])
+        wide = bf(torch.randn(total, (hq + 2 * hk) * d, device=cuda))
+        q = wide[:, : hq * d]
+        seq_lens = torch.tensor(lens, dtype=torch.int32, device=cuda)
+        out = A.ragged_attention(q, pool, table, seq_lens, hq, cu, one_launch=one_launch)
+        check_err(cuda)
+        for s in range(seqs):
+            lo, hi = int(cu[s]), int(cu[s + 1])
+            qs = q[lo:hi].reshape(hi - lo, hq, d)
+            pos = torch.arange(prefix[s], lens[s], device=cuda)
+            ref = A.attention_reference(qs, ks[s], vs[s], pos)
+            torch.testing.assert_close(out[lo:hi].float(), ref, rtol=2e-2, atol=2e-2)
+
+
 @pytest.mark.parametrize("hq,hk,d,rot,qk_norm", [(32, 8, 128, 128, False), (24, 4, 256, 64, True), (4, 2, 64, 64, True)])
 def test_rope_kv_append(cuda, hq, hk, d, rot, qk_norm):
     from kern_b200.ops import attention as A
