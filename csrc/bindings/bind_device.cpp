@@ -139,7 +139,7 @@ void bind_device(py::module_& m) {
       .def("free", &Device::free)
       .def("mem_info", &Device::mem_info)
       .def("ipc_export", [](Device& d, uint64_t p) { return py::bytes(d.ipc_export(p)); })
-      .def("ipc_import", [](Device& d, py::bytes h) { return d.ipc_import(h); })
+      .def("ipc_import", [](Device& d, py::bytes h) { return d.ipc_import(h, nullptr); })
       .def("ipc_close", &Device::ipc_close)
       .def("stream_create", [](Device& d) { return (uint64_t)d.stream_create(); })
       .def("stream_sync", [](Device& d, uint64_t s) {

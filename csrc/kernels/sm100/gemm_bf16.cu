@@ -96,20 +96,22 @@ struct AgArgs {
 //     rank's exported activation buffer (16-byte peer loads over NVLink, local rows through the same code) while the
 //     tensor-core warps already multiply the 128-row blocks that have arrived; the arrival counters and the producer's
 //     bounded wait are the AG form's. Needs the aligned plan (every tile starts on a 128-row boundary of xg).
-//   EPI == 5, combine fused into the routed GEMM's epilogue: row r of the result, times its routing weight row_w[r],
-//     is added into the f32 accumulator row of its token on the token's home rank (red.add.v4.f32 over NVLink, local
-//     tokens the same way); the top-k weighted reduction happens in those adds. When the last CTA of the grid is
-//     done it publishes this rank's epoch into every rank's `done` words; the home rank's finalize kernel waits for
-//     all of them before it reads (and clears) its accumulator.
+//   EPI == 5, combine fused into the routed GEMM's epilogue: row r of the result goes from TMEM straight into slot
+//     (token, choice) of the return buffer on the token's home rank (bf16, whole 128-byte lines over NVLink through the
+//     same shared-memory staging as EPI 4; a slot has exactly one writer, local tokens take the same path). When the
+//     last CTA of the grid is done it publishes this rank's epoch into every rank's `done` words; the home rank's
+//     finalize kernel waits for all of them and then forms the top-k weighted sum of its k slots. (Adding weighted f32
+//     rows into an accumulator on the home rank with red.add instead was measured first: 16-byte reductions over
+//     NVLink made the routed layer 25-45 % slower than the un-fused chain.)
 struct EpArgs {
   const unsigned long long* x_peers = nullptr;    // dispatch: every rank's activation buffer [rows_per_rank, K]
   __nv_bfloat16* xg = nullptr;                    //           this rank's expert-sorted rows (the A operand)
   const int* src_tok = nullptr;                   // both: global token of each expert-sorted row, -1 for padding
-  const float* row_w = nullptr;                   // combine: routing weight of each expert-sorted row
-  const unsigned long long* acc_peers = nullptr;  //          every rank's f32 accumulator [rows_per_rank, N]
+  const int* row_choice = nullptr;                // combine: which of its token's k choices each expert-sorted row is
+  const unsigned long long* ret_peers = nullptr;  //          every rank's return buffer [rows_per_rank, k, N] bf16
   const unsigned long long* done_peers = nullptr; //          every rank's done words [nranks]
   uint32_t* state = nullptr;                      //          {CTAs finished, epoch} (local)
-  int rows_per_rank = 1, rank = 0, nranks = 1;
+  int rows_per_rank = 1, rank = 0, nranks = 1, k = 1;
 };
 
 // GROUPED: the M tiles come from a device table of int4 {expert, first row, rows (<= BM), -} built by the MoE
@@ -333,10 +335,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
       }
       // blocks nobody gathers in this launch (own rows, blocks past the last row) arrive at once: every counter moves
       // by the grid size in every launch, whatever the row count
-      for (int b = gt; b < ag.max_blocks; b += GT) {
-        const bool remote = b < num_m && !ag.pushed && (sp || epd || b / bpr_div != ag.rank);
-        if (!remote) atomicAdd(ag.flags + b, 1u);
-      }
+      auto arrive_unpulled = [&]() {
+        for (int b = gt; b < ag.max_blocks; b += GT) {
+          const bool remote = b < num_m && !ag.pushed && (sp || epd || b / bpr_div != ag.rank);
+          if (!remote) atomicAdd(ag.flags + b, 1u);
+        }
+      };
+      // (the routed form has a counter per possible tile and nobody waits for the unused ones in this launch: its
+      // bookkeeping adds run after the pulls, off the path of the first tiles)
+      if constexpr (!epd) arrive_unpulled();
       // The blocks to pull, in the order the tiles will want them, form one run of 16-byte vectors that is cut into units
       // of eight vectors per thread over the whole grid (a unit usually spans two or three blocks). The loads of unit
       // u + 1 are issued before the stores of unit u, so a thread keeps up to sixteen peer loads in flight: a peer load
@@ -408,6 +415,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         for (int q = 0; q < 8; ++q) xa[q] = xb[q];
         ha = hb;
       }
+      if constexpr (epd) arrive_unpulled();
       if (gt == 0) ag.epochs[blockIdx.x] = ag_want / gridDim.x;
     }
   } else {
@@ -455,7 +463,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
             }
           }
         }
-      } else if constexpr (EPI == 4) {
+      } else if constexpr (EPI == 4 || EPI == 5) {
         // Rows go to the rank that reduces them. A lane first works out where its own row lands (once per tile);
         // then, 64 columns at a time, the warp parks its 32 x 64 block in shared memory and writes it out four rows
         // per instruction, eight lanes per row: every peer store covers a whole 128-byte line.
@@ -463,7 +471,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         unsigned long long* rowptr = reinterpret_cast<unsigned long long*>(stage + 32 * 144);
         {
           unsigned long long dst = 0;
-          if (row < row_end) {
+          if constexpr (EPI == 5) {
+            // the row's slot (token, choice) in the return buffer of the token's home rank
+            if (row < row_end) {
+              const int tok = ep.src_tok[row];
+              if (tok >= 0)
+                dst = ep.ret_peers[tok / ep.rows_per_rank] +
+                      2ull * (((size_t)(tok % ep.rows_per_rank) * ep.k + ep.row_choice[row]) * (size_t)N);
+            }
+          } else if (row < row_end) {
             int j, owner, idx;
             if (sc.grid == 0) {          // sequence-parallel: sub-blocks of kSpRows rows, one epoch word
               const int sb = row / kSpRows;
@@ -518,33 +534,6 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
             }
           }
           __syncwarp();
-        }
-      } else if constexpr (EPI == 5) {
-        // combine: this row, times its routing weight, is added into its token's accumulator on the home rank
-        float* dst = nullptr;
-        float wr = 0.f;
-        if (row < row_end) {
-          const int tok = ep.src_tok[row];
-          if (tok >= 0) {
-            wr = ep.row_w[row];
-            dst = reinterpret_cast<float*>(ep.acc_peers[tok / ep.rows_per_rank]) + (size_t)(tok % ep.rows_per_rank) * N;
-          }
-        }
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + c * 32, r);
-          tmem_ld_wait();
-          const int col = n_blk * BN + c * 32;
-          if (dst != nullptr) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v)
-              if (col + v * 4 < N)
-                asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + col + v * 4),
-                             "f"(__uint_as_float(r[v * 4]) * wr), "f"(__uint_as_float(r[v * 4 + 1]) * wr),
-                             "f"(__uint_as_float(r[v * 4 + 2]) * wr), "f"(__uint_as_float(r[v * 4 + 3]) * wr)
-                             : "memory");
-          }
         }
       } else {
 #pragma unroll 1

@@ -97,10 +97,10 @@ extern "C" __global__ void __launch_bounds__(128)
 // 128-row boundaries of the sorted buffer: the scale atoms are 128 rows tall); rows_out then counts the gaps too.
 __device__ __forceinline__ void moe_plan_body(const int* topk_ids, int* perm, int* offsets, int* tiles, int* tile_count,
                                               int* rows_out, int entries, int e_lo, int e_hi, int bm, int max_tiles, int* err,
-                                              int rank, int per_rank, int align, int k = 1, const float* topk_w = nullptr,
-                                              int* src_tok = nullptr, float* row_w = nullptr, int max_rows = 0) {
+                                              int rank, int per_rank, int align, int k = 1, int* src_tok = nullptr,
+                                              int* row_choice = nullptr, int max_rows = 0) {
   pdl_wait();
-  // the inverse of perm for the expert-parallel kernels: the token and routing weight of every sorted row, -1 in the gaps
+  // the inverse of perm for the expert-parallel kernels: the token and the choice of every sorted row, -1 in the gaps
   if (src_tok != nullptr)
     for (int i = threadIdx.x; i < max_rows; i += blockDim.x) src_tok[i] = -1;
   e_lo += rank * per_rank;      // expert parallel: rank r keeps experts [e_lo + r * per_rank, e_hi + r * per_rank)
@@ -146,7 +146,7 @@ __device__ __forceinline__ void moe_plan_body(const int* topk_ids, int* perm, in
     if (src_tok != nullptr && r >= 0) {
       if (r < max_rows) {
         src_tok[r] = i / k;
-        row_w[r] = topk_w[i];
+        row_choice[r] = i % k;
       } else {
         set_error(err, ERR_BOUNDS);
       }
@@ -277,35 +277,30 @@ extern "C" __global__ void __launch_bounds__(128)
 
 // ---- expert parallel over sharded tokens, fused: dispatch inside FC1, combine inside FC2 ------------------------------
 // Per layer and rank, five launches and no barrier kernel, no NCCL call:
-//   kern_ep_publish      this rank's expert ids and routing weights into every rank's table (peer stores), then its epoch
-//                        into every rank's `ids_ready` words
+//   kern_ep_publish      this rank's expert ids into every rank's table (peer stores), then its epoch into every rank's
+//                        `ids_ready` words
 //   kern_moe_plan_ep     waits (bounded) until every rank's ids of this epoch are here, then plans over all tokens for
-//                        this rank's experts: tile table on 128-row boundaries, token and weight of every sorted row
+//                        this rank's experts: tile table on 128-row boundaries, token and choice of every sorted row
 //   kern_ep_fc1_*        routed GEMM + SwiGLU whose gather warps pull the rows out of the home ranks while tiles run (EP 1)
-//   kern_ep_fc2_*        routed GEMM whose epilogue adds weight x row into the token's accumulator on its home rank
-//                        and publishes `done` when the grid has finished (EPI 5)
-//   kern_ep_finalize     waits (bounded) for every rank's `done`, writes the accumulator out as bf16 (plus an optional
-//                        shared-expert / residual term) and clears it for the next layer
-// Hazards are closed by the two flag rounds: a rank rewrites its activations, ids or accumulator only after its finalize,
-// which has seen every peer's FC2 — and therefore its plan and its pulls — finished; a peer adds into an accumulator only
-// after its plan has seen the home rank's publish, which is after the home rank's previous finalize in stream order.
+//   kern_ep_fc2_*        routed GEMM whose epilogue stores every result row into its (token, choice) slot on the token's
+//                        home rank and publishes `done` when the grid has finished (EPI 5)
+//   kern_ep_finalize     waits (bounded) for every rank's `done`, then out[t] = sum_j w[t, j] * slot[t, j] (plus an optional
+//                        shared-expert / residual term): the top-k weighted reduction, on the home rank
+// Hazards are closed by the two flag rounds: a rank rewrites its activations or ids only after its finalize, which has
+// seen every peer's FC2 - and therefore its plan and its pulls - finished; a peer writes a slot only after its plan has
+// seen the home rank's publish, which is after the home rank's previous finalize (the slots' reader) in stream order.
 // Reference: docs/roadmap.md:13-16 (one-launch routed layer), docs/runtime.md:201-202, crates/kern-runtime/src/nccl.rs:238-256
 // (the all-to-all the reference's un-fused path uses).
 
 // One CTA. grid = 1, block 1024.
 extern "C" __global__ void __launch_bounds__(1024)
-    kern_ep_publish(const int* ids, const float* w, const unsigned long long* ids_peers, const unsigned long long* w_peers,
-                    const unsigned long long* ready_peers, uint32_t* epoch, int tokens, int rows_per_rank, int k, int rank,
-                    int nranks) {
+    kern_ep_publish(const int* ids, const unsigned long long* ids_peers, const unsigned long long* ready_peers,
+                    uint32_t* epoch, int tokens, int rows_per_rank, int k, int rank, int nranks) {
   pdl_wait();
   const int n = rows_per_rank * k, have = tokens * k;
   for (int r = 0; r < nranks; ++r) {
     int* di = reinterpret_cast<int*>(ids_peers[r]) + (size_t)rank * n;
-    float* dw = reinterpret_cast<float*>(w_peers[r]) + (size_t)rank * n;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      di[i] = i < have ? ids[i] : -1;          // rows this rank does not have this step route nowhere
-      dw[i] = i < have ? w[i] : 0.f;
-    }
+    for (int i = threadIdx.x; i < n; i += blockDim.x) di[i] = i < have ? ids[i] : -1;   // rows not in this step route nowhere
   }
   __threadfence_system();
   __syncthreads();
@@ -317,10 +312,9 @@ extern "C" __global__ void __launch_bounds__(1024)
 }
 
 extern "C" __global__ void __launch_bounds__(1024)
-    kern_moe_plan_ep(const int* ids_all, const float* w_all, int* perm, int* offsets, int* tiles, int* tile_count,
-                     int* rows_out, int* src_tok, float* row_w, const uint32_t* ready, const uint32_t* epoch, int entries,
-                     int k, int e_n, int bm, int max_tiles, int max_rows, int* err, int rank, int nranks,
-                     long long timeout_ns) {
+    kern_moe_plan_ep(const int* ids_all, int* perm, int* offsets, int* tiles, int* tile_count, int* rows_out, int* src_tok,
+                     int* row_choice, const uint32_t* ready, const uint32_t* epoch, int entries, int k, int e_n, int bm,
+                     int max_tiles, int max_rows, int* err, int rank, int nranks, long long timeout_ns) {
   __shared__ int failed;
   if (threadIdx.x == 0) failed = 0;
   __syncthreads();
@@ -342,7 +336,7 @@ extern "C" __global__ void __launch_bounds__(1024)
     return;
   }
   moe_plan_body(ids_all, perm, offsets, tiles, tile_count, rows_out, entries, 0, e_n, bm, max_tiles, err, rank, e_n, bm, k,
-                w_all, src_tok, row_w, max_rows);
+                src_tok, row_choice, max_rows);
 }
 
 #define KERN_EP_FC1_ENTRY(name, BN)                                                                                    \
@@ -369,23 +363,25 @@ KERN_EP_FC1_ENTRY(kern_ep_fc1_bf16_swiglu_n64, 64)
 #define KERN_EP_FC2_ENTRY(name, BN)                                                                                    \
   extern "C" __global__ void __launch_bounds__(192, 1)                                                                 \
       name(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const int* tiles,      \
-           const int* tile_count, int M, int N, int K, int* err, const unsigned long long* acc_peers,                   \
-           const int* src_tok, const float* row_w, uint32_t* state, const unsigned long long* done_peers,               \
-           int rows_per_rank, int rank, int nranks) {                                                                  \
+           const int* tile_count, int M, int N, int K, int* err, const unsigned long long* ret_peers,                   \
+           const int* src_tok, const int* row_choice, uint32_t* state, const unsigned long long* done_peers,            \
+           int rows_per_rank, int k, int rank, int nranks) {                                                           \
     kern::EpArgs ep;                                                                                                   \
-    ep.acc_peers = acc_peers; ep.src_tok = src_tok; ep.row_w = row_w; ep.state = state; ep.done_peers = done_peers;    \
-    ep.rows_per_rank = rows_per_rank; ep.rank = rank; ep.nranks = nranks;                                              \
+    ep.ret_peers = ret_peers; ep.src_tok = src_tok; ep.row_choice = row_choice; ep.state = state;                      \
+    ep.done_peers = done_peers; ep.rows_per_rank = rows_per_rank; ep.k = k; ep.rank = rank; ep.nranks = nranks;        \
     kern::gemm_body<BN, 5, true>(&tma_a, &tma_b, nullptr, nullptr, M, N, K, N, err, tiles, tile_count,                 \
                                  kern::ScatterArgs(), nullptr, nullptr, kern::AgArgs(), ep);                          \
   }
 
+KERN_EP_FC2_ENTRY(kern_ep_fc2_bf16_combine_n256, 256)
 KERN_EP_FC2_ENTRY(kern_ep_fc2_bf16_combine_n128, 128)
 KERN_EP_FC2_ENTRY(kern_ep_fc2_bf16_combine_n64, 64)
 
-// grid = this rank's tokens, block 128. out[t] = acc[t] (+ out[t] when accumulate) (+ extra[t]); acc[t] = 0.
+// grid = this rank's tokens, block 128. out[t] = sum_j w[t, j] * ret[t, j] (+ out[t] when accumulate) (+ extra[t]).
 extern "C" __global__ void __launch_bounds__(128)
-    kern_ep_finalize(float* acc, __nv_bfloat16* out, const __nv_bfloat16* extra, const uint32_t* done, const uint32_t* state,
-                     int* err, int tokens, int hidden, int nranks, long long timeout_ns, int accumulate) {
+    kern_ep_finalize(const __nv_bfloat16* ret, const float* topk_w, __nv_bfloat16* out, const __nv_bfloat16* extra,
+                     const uint32_t* done, const uint32_t* state, int* err, int tokens, int k, int hidden, int nranks,
+                     long long timeout_ns, int accumulate) {
   pdl_wait();
   __shared__ int failed;
   if (threadIdx.x == 0) failed = 0;
@@ -406,22 +402,25 @@ extern "C" __global__ void __launch_bounds__(128)
   if (failed) return;
   const int t = blockIdx.x;
   if (t >= tokens) return;
-  float4* a = reinterpret_cast<float4*>(acc + (size_t)t * hidden);
-  for (int v = threadIdx.x; v < hidden / 4; v += 128) {
-    float4 x;
-    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w) : "l"(a + v));
-    a[v] = make_float4(0.f, 0.f, 0.f, 0.f);
-    uint2* o = reinterpret_cast<uint2*>(out + (size_t)t * hidden) + v;
-    if (accumulate) {
-      const uint2 old = *o;
-      const float2 p = unpack_bf16x2(old.x), q = unpack_bf16x2(old.y);
-      x.x += p.x; x.y += p.y; x.z += q.x; x.w += q.y;
+  for (int v = threadIdx.x; v < hidden / 8; v += 128) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    auto add = [&](uint4 p, float w) {
+      float2 a = unpack_bf16x2(p.x), b = unpack_bf16x2(p.y), c = unpack_bf16x2(p.z), d = unpack_bf16x2(p.w);
+      acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * b.x; acc[3] += w * b.y;
+      acc[4] += w * c.x; acc[5] += w * c.y; acc[6] += w * d.x; acc[7] += w * d.y;
+    };
+    if (accumulate) add(reinterpret_cast<const uint4*>(out + (size_t)t * hidden)[v], 1.f);
+    if (extra != nullptr) add(reinterpret_cast<const uint4*>(extra + (size_t)t * hidden)[v], 1.f);
+    for (int j = 0; j < k; ++j) {
+      // the slots were written by other GPUs: read them past this SM's L1
+      uint4 p;
+      const uint4* src = reinterpret_cast<const uint4*>(ret + ((size_t)t * k + j) * hidden) + v;
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(p.x), "=r"(p.y), "=r"(p.z), "=r"(p.w) : "l"(src));
+      add(p, topk_w[(size_t)t * k + j]);
     }
-    if (extra != nullptr) {
-      const uint2 ex = reinterpret_cast<const uint2*>(extra + (size_t)t * hidden)[v];
-      const float2 p = unpack_bf16x2(ex.x), q = unpack_bf16x2(ex.y);
-      x.x += p.x; x.y += p.y; x.z += q.x; x.w += q.y;
-    }
-    *o = make_uint2(pack_bf16x2(x.x, x.y), pack_bf16x2(x.z, x.w));
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out + (size_t)t * hidden)[v] = o;
   }
 }

@@ -289,16 +289,26 @@ class Device {
   }
   // Legacy IPC handles for cuMemAlloc memory (64 bytes); the simplest carrier between the
   // one-process-per-GPU ranks of one box.
-  std::string ipc_export(uint64_t p) {
+  // `offset`: where the exported region starts inside its allocation (a handle names the whole allocation; a runtime
+  // with guard bands keeps its payload behind the first band). It travels as eight more bytes after the handle.
+  std::string ipc_export(uint64_t p, uint64_t offset = 0) {
     CUipcMemHandle h;
     KERN_CU(cuIpcGetMemHandle_(&h, (CUdeviceptr)p));
-    return std::string(reinterpret_cast<const char*>(&h), sizeof(h));
+    std::string out(reinterpret_cast<const char*>(&h), sizeof(h));
+    if (offset) out.append(reinterpret_cast<const char*>(&offset), sizeof(offset));
+    return out;
   }
-  uint64_t ipc_import(const std::string& handle) {
+  // The mapped allocation's base; `offset_out` receives the region's offset inside it.
+  uint64_t ipc_import(const std::string& handle, uint64_t* offset_out = nullptr) {
     make_current();
-    if (handle.size() != sizeof(CUipcMemHandle)) throw std::runtime_error("IPC handle must be 64 bytes");
+    if (handle.size() != sizeof(CUipcMemHandle) && handle.size() != sizeof(CUipcMemHandle) + 8)
+      throw std::runtime_error("IPC handle must be 64 bytes (72 with a region offset)");
     CUipcMemHandle h;
     std::memcpy(&h, handle.data(), sizeof(h));
+    uint64_t off = 0;
+    if (handle.size() > sizeof(h)) std::memcpy(&off, handle.data() + sizeof(h), 8);
+    if (off && !offset_out) throw std::runtime_error("this IPC handle carries a region offset the caller does not take");
+    if (offset_out) *offset_out = off;
     CUdeviceptr p = 0;
     KERN_CU(cuIpcOpenMemHandle_(&p, h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS));
     return (uint64_t)p;

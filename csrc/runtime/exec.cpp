@@ -678,7 +678,7 @@ std::map<std::string, std::string> Runtime::export_handles() {
   for (auto& kv : m_.buffers) if (kv.second.kind == BufferKind::Peer && kv.second.of) wanted.insert(*kv.second.of);
   for (auto& name : wanted) {
     auto r = region(name);
-    out[name] = dev_->ipc_export(r.first);
+    out[name] = dev_->ipc_export(r.first, guard_);
   }
   // member 0 of every group with `extern:nccl_*` launches creates the communicator's id and offers it
   for (auto& grp : nccl_groups()) {
@@ -714,8 +714,10 @@ void Runtime::connect(const std::string& group, const std::vector<std::map<std::
       if (r == g->second.index) { addrs[r] = region(*b.of).first; continue; }
       auto h = members[r].find(*b.of);
       if (h == members[r].end()) throw std::runtime_error("member " + std::to_string(r) + " of `" + group + "` did not offer `" + *b.of + "`");
-      addrs[r] = dev_->ipc_import(h->second);
-      imported_ptrs_.push_back(addrs[r]);
+      uint64_t off = 0;
+      const uint64_t base = dev_->ipc_import(h->second, &off);
+      imported_ptrs_.push_back(base);
+      addrs[r] = base + off;
     }
     dev_->h2d(buffers_.at(kv.first).ptr, addrs.data(), addrs.size() * 8, stream_);
     dev_->stream_sync(stream_);
@@ -735,12 +737,13 @@ void Runtime::connect(const std::string& group, const std::vector<std::map<std::
   }
 }
 
-std::string Runtime::export_region(const std::string& name) { return dev_->ipc_export(region(name).first); }
+std::string Runtime::export_region(const std::string& name) { return dev_->ipc_export(region(name).first, guard_); }
 
 uint64_t Runtime::import_region(const std::string& handle) {
-  const uint64_t p = dev_->ipc_import(handle);
+  uint64_t off = 0;
+  const uint64_t p = dev_->ipc_import(handle, &off);
   imported_ptrs_.push_back(p);
-  return p;
+  return p + off;
 }
 
 void Runtime::push_unit(const std::string& state, uint64_t dst_base, int64_t src_unit, int64_t dst_unit) {

@@ -159,9 +159,7 @@ void Runtime::allocate() {
     auto st = m_.states.find(*b.domain->index_into);
     if (st != m_.states.end() && st->second.is_paged()) page_unit_ = lcm64(page_unit_, std::max<uint64_t>(1, b.domain->stride));
   }
-  bool multi = false;
-  for (auto& kv : topo_) multi |= kv.second.size >= 2;
-  guard_ = cap_.guard_bands && !multi ? 256 : 0;      // exported handles name an allocation's base: no bands on 2+ ranks
+  guard_ = cap_.guard_bands ? 256 : 0;      // an exported handle carries the band's size as the region's offset
   auto zero_alloc = [&](uint64_t bytes, const std::string& name) {
     const uint64_t pay = (bytes ? bytes : 16);
     const uint64_t padded = (pay + 255) / 256 * 256;      // the trailing band starts 256-byte aligned, right after the payload's last line

@@ -28,7 +28,8 @@ struct Capacity {
   uint64_t slots = 0;      // per-sequence state slots (excluding the null line)
   double memory_fraction = 0.9;   // of free device memory the paged states may take when tokens == 0
   bool guard_bands = false;       // test mode: a 256-byte canary band before and after every device allocation of the
-                                  // runtime (buffers, scratch, states), checked by check_guards(); one rank only
+                                  // runtime (buffers, scratch, states), checked by check_guards(); exported regions
+                                  // carry the band's size in their handle, so peers' writes are covered too
 };
 
 struct GroupRank {

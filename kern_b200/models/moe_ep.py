@@ -95,16 +95,15 @@ def ep_fused_buffers(world: int, rows_max: int, hidden: int, inter: int, e_n: in
     return {
         x + "_peers": peer(x),
         "ep.ids_all": buf("i32", [T, k], "carry", export=True), "ep.ids_peers": peer("ep.ids_all"),
-        "ep.w_all": buf("f32", [T, k], "carry", export=True), "ep.w_peers": peer("ep.w_all"),
         "ep.ready": buf("u32", [world], "carry", export=True), "ep.ready_peers": peer("ep.ready"),
         "ep.pub_epoch": buf("u32", [1], "carry"),
-        "ep.acc": buf("f32", [rows_max, hidden], "carry", export=True), "ep.acc_peers": peer("ep.acc"),
+        "ep.ret": buf("bf16", [rows_max, k, hidden], "carry", export=True), "ep.ret_peers": peer("ep.ret"),
         "ep.done": buf("u32", [world], "carry", export=True), "ep.done_peers": peer("ep.done"),
         "ep.state": buf("u32", [2], "carry"), "ep.blocks": buf("u32", [max_tiles], "carry"),
         "ep.cta_epochs": buf("u32", [C.SMS], "carry"),
         "ep.perm": buf("i32", [T, k]), "ep.offsets": buf("i32", [e_n + 1]), "ep.tiles": buf("i32", [max_tiles, 4]),
         "ep.tile_count": buf("i32", [1]), "ep.n_rows": buf("i32", [1]), "ep.src_tok": buf("i32", [max_rows]),
-        "ep.row_w": buf("f32", [max_rows]),
+        "ep.row_choice": buf("i32", [max_rows]),
         "ep.xp": buf("bf16", [max_rows, hidden], "carry"), "ep.act": buf("bf16", [max_rows, inter]),
     }
 
@@ -112,11 +111,11 @@ def ep_fused_buffers(world: int, rows_max: int, hidden: int, inter: int, e_n: in
 def ep_fused_ops(world: int, rows_max: int, hidden: int, inter: int, e_n: int, k: int, rows_var: str, group: str = "ep",
                  accumulate: bool = False, timeout_ns: int = 2_000_000_000) -> dict:
     """The five ops of a fused expert-parallel layer. Interfaces:
-    ep_publish [ids, w, ids_peers, w_peers, ready_peers, pub_epoch, rows];
-    ep_plan [ids_all, w_all, perm, offsets, tiles, tile_count, n_rows, src_tok, row_w, ready, pub_epoch, err];
+    ep_publish [ids, ids_peers, ready_peers, pub_epoch, rows];
+    ep_plan [ids_all, perm, offsets, tiles, tile_count, n_rows, src_tok, row_choice, ready, pub_epoch, err];
     ep_fc1 [xp, w1, act, tiles, tile_count, x_peers, src_tok, blocks, cta_epochs, err];
-    ep_fc2 [act, w2, tiles, tile_count, acc_peers, src_tok, row_w, state, done_peers, err];
-    ep_finalize [acc, out, done, state, err] (`accumulate`: out += the experts' sum, else out = it)."""
+    ep_fc2 [act, w2, tiles, tile_count, ret_peers, src_tok, row_choice, state, done_peers, err];
+    ep_finalize [ret, w, out, done, state, err] (`accumulate`: out += the experts' weighted sum, else out = it)."""
     T = rows_max * world
     max_tiles = T * k // C.BM + e_n
     max_rows = max_tiles * C.BM
@@ -125,22 +124,21 @@ def ep_fused_ops(world: int, rows_max: int, hidden: int, inter: int, e_n: int, k
     P = lambda i: {"param": i}
     rank = {"rank": group}
     ops = {}
-    ops["ep_publish"] = {"params": ["in buffer<i32>", "in buffer<f32>", "in buffer<u64>", "in buffer<u64>", "in buffer<u64>",
-                                    "inout buffer<u32>", "i32"], "impl": {"launches": [L(
+    ops["ep_publish"] = {"params": ["in buffer<i32>", "in buffer<u64>", "in buffer<u64>", "inout buffer<u32>", "i32"],
+                         "impl": {"launches": [L(
         "moe", "kern_ep_publish", [1024, 1, 1], [1, 1, 1],
-        ["in buffer<i32>", "in buffer<f32>", "in buffer<u64>", "in buffer<u64>", "in buffer<u64>", "inout buffer<u32>", "i32", "i32",
-         "i32", "i32", "i32"],
-        [P(0), P(1), P(2), P(3), P(4), P(5), P(6), {"i32": rows_max}, {"i32": k}, rank, {"i32": world}])]}}
-    # the tables and flag words the peers write into are `inout` here: their writers are other ranks' kernels
-    ops["ep_plan"] = {"params": ["inout buffer<i32>", "inout buffer<f32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>",
-                                 "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<f32>", "inout buffer<u32>",
-                                 "in buffer<u32>", "out buffer<i32>"], "impl": {"launches": [L(
+        ["in buffer<i32>", "in buffer<u64>", "in buffer<u64>", "inout buffer<u32>", "i32", "i32", "i32", "i32", "i32"],
+        [P(0), P(1), P(2), P(3), P(4), {"i32": rows_max}, {"i32": k}, rank, {"i32": world}])]}}
+    # the table and flag words the peers write into are `inout` here: their writers are other ranks' kernels
+    ops["ep_plan"] = {"params": ["inout buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>",
+                                 "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "inout buffer<u32>", "in buffer<u32>",
+                                 "out buffer<i32>"], "impl": {"launches": [L(
         "moe", "kern_moe_plan_ep", [1024, 1, 1], [1, 1, 1],
-        ["inout buffer<i32>", "inout buffer<f32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>",
-         "out buffer<i32>", "out buffer<i32>", "out buffer<f32>", "inout buffer<u32>", "in buffer<u32>"] + ["i32"] * 6 +
+        ["inout buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>", "out buffer<i32>",
+         "out buffer<i32>", "out buffer<i32>", "inout buffer<u32>", "in buffer<u32>"] + ["i32"] * 6 +
         ["out buffer<i32>", "i32", "i32", "i64"],
-        [P(i) for i in range(11)] + [{"i32": T * k}, {"i32": k}, {"i32": e_n}, {"i32": C.BM}, {"i32": max_tiles}, {"i32": max_rows},
-                                     P(11), rank, {"i32": world}, {"i64": timeout_ns}], shared_mem=2 * e_n * 4)]}}
+        [P(i) for i in range(10)] + [{"i32": T * k}, {"i32": k}, {"i32": e_n}, {"i32": C.BM}, {"i32": max_tiles}, {"i32": max_rows},
+                                     P(10), rank, {"i32": world}, {"i64": timeout_ns}], shared_mem=2 * e_n * 4)]}}
 
     def maps(kk, n, swiglu, bn):
         a_map = {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
@@ -164,21 +162,22 @@ def ep_fused_ops(world: int, rows_max: int, hidden: int, inter: int, e_n: int, k
     bn2 = 128 if hidden >= 128 else 64
     a2, b2 = maps(inter, hidden, False, bn2)
     ops["ep_fc2"] = {"params": ["in buffer<bf16>", "in buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "in buffer<u64>",
-                                "in buffer<i32>", "in buffer<f32>", "inout buffer<u32>", "in buffer<u64>", "out buffer<i32>"],
+                                "in buffer<i32>", "in buffer<i32>", "inout buffer<u32>", "in buffer<u64>", "out buffer<i32>"],
                      "impl": {"launches": [L(
         "moe", f"kern_ep_fc2_bf16_combine_n{bn2}", [192, 1, 1], [C.SMS, 1, 1],
         ["bytes<128>", "bytes<128>", "in buffer<i32>", "in buffer<i32>", "i32", "i32", "i32", "out buffer<i32>", "in buffer<u64>",
-         "in buffer<i32>", "in buffer<f32>", "inout buffer<u32>", "in buffer<u64>", "i32", "i32", "i32"],
+         "in buffer<i32>", "in buffer<i32>", "inout buffer<u32>", "in buffer<u64>", "i32", "i32", "i32", "i32"],
         [a2, b2, P(2), P(3), {"i32": max_rows}, {"i32": hidden}, {"i32": inter}, P(9), P(4), P(5), P(6), P(7), P(8),
-         {"i32": rows_max}, rank, {"i32": world}], shared_mem=C.gemm_smem(bn2))]}}
+         {"i32": rows_max}, {"i32": k}, rank, {"i32": world}],
+        shared_mem=C.gemm_smem(bn2) + 20480)]}}     # + the epilogue's row staging
     odir = "inout" if accumulate else "out"
-    ops["ep_finalize"] = {"params": ["inout buffer<f32>", f"{odir} buffer<bf16>", "inout buffer<u32>", "in buffer<u32>",
-                                     "out buffer<i32>"], "impl": {"launches": [L(
+    ops["ep_finalize"] = {"params": ["inout buffer<bf16>", "in buffer<f32>", f"{odir} buffer<bf16>", "inout buffer<u32>",
+                                     "in buffer<u32>", "out buffer<i32>"], "impl": {"launches": [L(
         "moe", "kern_ep_finalize", [128, 1, 1], [rows_var, 1, 1],
-        ["inout buffer<f32>", f"{odir} buffer<bf16>", "i64", "inout buffer<u32>", "in buffer<u32>", "out buffer<i32>", "i32", "i32",
-         "i32", "i64", "i32"],
-        [P(0), P(1), {"i64": 0}, P(2), P(3), P(4), {"i32": C.I32_MAX}, {"i32": hidden}, {"i32": world}, {"i64": timeout_ns},
-         {"i32": int(accumulate)}])]}}
+        ["inout buffer<bf16>", "in buffer<f32>", f"{odir} buffer<bf16>", "i64", "inout buffer<u32>", "in buffer<u32>",
+         "out buffer<i32>", "i32", "i32", "i32", "i32", "i64", "i32"],
+        [P(0), P(1), P(2), {"i64": 0}, P(3), P(4), P(5), {"i32": C.I32_MAX}, {"i32": k}, {"i32": hidden}, {"i32": world},
+         {"i64": timeout_ns}, {"i32": int(accumulate)}])]}}
     return ops
 
 
@@ -188,16 +187,16 @@ def ep_fused_calls(ids: str, w: str, x: str, w1: str, w2: str, out: str, rows_va
     B = lambda n: {"buf": n}
     err = B("error")
     return [
-        {"op": "ep_publish", "label": label + "publish", "args": [B(ids), B(w), B("ep.ids_peers"), B("ep.w_peers"),
-                                                                  B("ep.ready_peers"), B("ep.pub_epoch"), {"var": rows_var}]},
-        {"op": "ep_plan", "label": label + "plan", "args": [B("ep.ids_all"), B("ep.w_all"), B("ep.perm"), B("ep.offsets"),
-                                                            B("ep.tiles"), B("ep.tile_count"), B("ep.n_rows"), B("ep.src_tok"),
-                                                            B("ep.row_w"), B("ep.ready"), B("ep.pub_epoch"), err]},
+        {"op": "ep_publish", "label": label + "publish", "args": [B(ids), B("ep.ids_peers"), B("ep.ready_peers"), B("ep.pub_epoch"),
+                                                                  {"var": rows_var}]},
+        {"op": "ep_plan", "label": label + "plan", "args": [B("ep.ids_all"), B("ep.perm"), B("ep.offsets"), B("ep.tiles"),
+                                                            B("ep.tile_count"), B("ep.n_rows"), B("ep.src_tok"), B("ep.row_choice"),
+                                                            B("ep.ready"), B("ep.pub_epoch"), err]},
         {"op": "ep_fc1", "label": label + "fc1", "args": [B("ep.xp"), B(w1), B("ep.act"), B("ep.tiles"), B("ep.tile_count"),
                                                           B(x + "_peers"), B("ep.src_tok"), B("ep.blocks"), B("ep.cta_epochs"), err]},
-        {"op": "ep_fc2", "label": label + "fc2", "args": [B("ep.act"), B(w2), B("ep.tiles"), B("ep.tile_count"), B("ep.acc_peers"),
-                                                          B("ep.src_tok"), B("ep.row_w"), B("ep.state"), B("ep.done_peers"), err]},
-        {"op": "ep_finalize", "label": label + "finalize", "args": [B("ep.acc"), B(out), B("ep.done"), B("ep.state"), err]},
+        {"op": "ep_fc2", "label": label + "fc2", "args": [B("ep.act"), B(w2), B("ep.tiles"), B("ep.tile_count"), B("ep.ret_peers"),
+                                                          B("ep.src_tok"), B("ep.row_choice"), B("ep.state"), B("ep.done_peers"), err]},
+        {"op": "ep_finalize", "label": label + "finalize", "args": [B("ep.ret"), B(w), B(out), B("ep.done"), B("ep.state"), err]},
     ]
 
 

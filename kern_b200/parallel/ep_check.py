@@ -205,7 +205,8 @@ def main(argv=None) -> int:
     h, I, E, k = a.hidden, a.inter, a.experts, a.top_k
     e_n = E // world
     rows_max = max(a.rows)
-    rt = Runtime((manifest_fused if a.fused else manifest)(world, rows_max, h, I, E, k), gpu=local, topology={"ep": (rank, world)})
+    rt = Runtime((manifest_fused if a.fused else manifest)(world, rows_max, h, I, E, k), gpu=local, topology={"ep": (rank, world)},
+                 guard_bands=True)      # canary bands around every allocation: the peers' adds and stores land in this rank's memory
     group.start(rt)
     g = torch.Generator().manual_seed(21)
     w1 = (torch.randn(E, 2 * I, h, generator=g) * 0.05).to(torch.bfloat16)       # [gate rows ; up rows] per expert
@@ -244,6 +245,10 @@ def main(argv=None) -> int:
         if world > 1:
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         results.append({"rows_per_rank": tr, "program": program, "max_abs_err": round(err, 4), "ok": bool(ok.item())})
+    if world > 1:
+        dist.barrier()
+    bad = rt.check_guards()
+    results.append({"guard_bands_overwritten": bad, "ok": not bad})
     line = {"check": "expert_parallel_fused" if a.fused else "expert_parallel_all_to_all", "world": world, "experts": E, "top_k": k, "hidden": h, "results": results}
     if a.time:
         stream = torch.cuda.ExternalStream(rt.stream)
@@ -266,6 +271,19 @@ def main(argv=None) -> int:
             times.append({"rows_per_rank": tr, "layer_us_max_over_ranks": round(float(t), 1)})
         rt.check_error()
         line["times"] = times
+        # cost by call of the largest size: eager, an event between calls, median of 5 (waits for peers included)
+        tr = max(a.rows)
+        samples = []
+        for _ in range(6):
+            if world > 1:
+                dist.barrier()
+            samples.append(rt.issue_timed("step", {"rows": tr}))
+        rt.check_error()
+        by = {}
+        for smp in samples[1:]:
+            for label, op, ms, _ in smp:
+                by.setdefault(label, []).append(ms * 1e3)
+        line["by_call_us"] = {"rows_per_rank": tr, **{l: round(sorted(v)[len(v) // 2], 1) for l, v in by.items()}}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if a.model:

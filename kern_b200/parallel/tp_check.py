@@ -149,8 +149,10 @@ def check_model(rank, world, fused=True, sp=False, sp_push=True):
                             max_tokens=640 if sp else 256, max_seqs=8, max_context=512 if sp else 256, tp=world)
     weights = dense.random_weights(cfg, seed=0, std=0.05)
     doc = dense_tp.build_manifest_tp(cfg, fused=fused, sp=sp, sp_push=sp_push)
+    # canary bands around every allocation, the exported ones included: the scatter epilogues and the pushes of the
+    # peers write into this rank's memory, and a write past a region's end would land in its band
     rt = Runtime(doc, gpu=torch.cuda.current_device(), topology=group.topology(doc["topology"]["groups"], rank, world),
-                 tokens=cfg.page_size * (160 if sp else 64))
+                 tokens=cfg.page_size * (160 if sp else 64), guard_bands=True)
     rt.load_tensors(lambda name: weights[name].cuda())
     group.start(rt)
     eng = Engine(rt)
@@ -187,7 +189,10 @@ def check_model(rank, world, fused=True, sp=False, sp_push=True):
             for s_ in new_seqs:
                 eng.close(s_)
     rt.check_error()
-    return {"model_max_logit_diff": round(worst, 4), "ok": worst < 0.12, "graphs": rt.graphs, "sp": sp}
+    torch.distributed.barrier() if world > 1 else None      # every rank's writes into this rank's memory are done
+    bad = rt.check_guards()
+    return {"model_max_logit_diff": round(worst, 4), "ok": worst < 0.12 and not bad, "graphs": rt.graphs, "sp": sp,
+            "guard_bands_overwritten": bad}
 
 
 def check_moe(rank, world):

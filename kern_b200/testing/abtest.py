@@ -265,6 +265,114 @@ class EngineSide:
         return out
 
 
+# ---- span-local replay ---------------------------------------------------------------------------------
+def read_set(doc: dict, program: str, calls: list[int]) -> set[str]:
+    """Buffers the given calls of a program read, by the ops' declared directions."""
+    out = set()
+    for k in calls:
+        c = doc["programs"][program]["calls"][k]
+        for arg, p in zip(c["args"], doc["ops"][c["op"]]["params"]):
+            if "buf" in arg and (p.startswith("in ") or p.startswith("inout ")):
+                out.add(arg["buf"])
+    return out
+
+
+def _buffer_bytes(doc: dict, name: str) -> tuple:
+    b = doc["buffers"].get(name)
+    return None if b is None else (b["dtype"], tuple(b["shape"]))
+
+
+class SpanTap:
+    """An engine probe (``Engine.probe``) that runs a program in call ranges around its changed spans.
+
+    Recording side (A): before each span it keeps images of the buffers the span reads — on both sides — and after the
+    span the buffers it writes. Replaying side (B): it runs its own calls up to the span, puts A's images of the same
+    step into the buffers its span reads, runs only the span, and compares what the span wrote with what A's span
+    wrote. A difference is then pinned to the span that made it, from identical inputs, instead of being read off the
+    end of a free run where earlier differences have piled up. Paged / per-sequence states are not imaged: along
+    forced tokens they differ only where an earlier span's outputs already did, which that span's line shows.
+    Reference: crates/kern-test/src/harness.rs:46-220 (frontier snapshots), replay.rs."""
+
+    def __init__(self, mine: dict, other: dict, spans_by_program: dict, side: str, store: dict, results: list | None = None):
+        self.doc, self.other, self.side, self.store = mine, other, side, store
+        self.results = results if results is not None else []
+        self.spans = {p: [sp for sp in ss if sp["a"] and sp["b"]] for p, ss in spans_by_program.items()}
+        self.step = 0
+
+    def _shared(self, names) -> list[str]:
+        return sorted(n for n in names if _buffer_bytes(self.doc, n) is not None and
+                      _buffer_bytes(self.doc, n) == _buffer_bytes(self.other, n))
+
+    @staticmethod
+    def _image(rt, names) -> dict:
+        import torch
+
+        if hasattr(rt, "synchronize"):
+            rt.synchronize()
+        return {n: rt.tensor(n).contiguous().view(-1).view(torch.uint8).cpu().clone() for n in names}
+
+    def run(self, rt, program: str, vars: dict, tag: str) -> int:
+        import torch
+
+        calls = self.doc["programs"][program]["calls"]
+        key_step = (program, tuple(sorted(vars.items())), self.step)
+        self.step += 1
+        lo, n = 0, 0
+        for k, sp in enumerate(self.spans.get(program, [])):
+            mine = sp["a"] if self.side == "a" else sp["b"]
+            theirs_doc_calls = sp["b"] if self.side == "a" else sp["a"]
+            first, last = mine[0], mine[-1] + 1
+            reads = self._shared(read_set(self.doc, program, mine) | read_set(self.other, program, theirs_doc_calls))
+            writes = self._shared(write_set(self.doc, program, mine) & write_set(self.other, program, theirs_doc_calls))
+            n += rt.issue_range(program, vars, lo, first)
+            key = key_step + (k,)
+            if self.side == "a":
+                self.store[key] = {"in": self._image(rt, reads)}
+                n += rt.issue_range(program, vars, first, last)
+                self.store[key]["out"] = self._image(rt, writes)
+            else:
+                rec = self.store.get(key)
+                if rec is None:
+                    self.results.append({"program": program, "span": k, "step": key_step[2], "skipped": "A recorded no such step"})
+                    n += rt.issue_range(program, vars, first, last)
+                else:
+                    if hasattr(rt, "synchronize"):
+                        rt.synchronize()
+                    for name, img in rec["in"].items():
+                        t = rt.tensor(name)
+                        t.view(-1).view(torch.uint8).copy_(img.to(t.device))
+                    n += rt.issue_range(program, vars, first, last)
+                    got = self._image(rt, writes)
+                    for name in writes:
+                        c = compare_bytes(self.doc["buffers"][name]["dtype"], rec["out"][name].numpy().tobytes(), got[name].numpy().tobytes())
+                        self.results.append({"program": program, "span": k, "step": key_step[2], "buffer": name,
+                                             "identical": c.identical, "value_identical": c.value_identical,
+                                             "differing": c.n_diff, "max_abs": c.max_abs, "max_ulp": c.max_ulp})
+            lo = last
+        n += rt.issue_range(program, vars, lo, len(calls))
+        return n
+
+
+def replay_spans(side_a: "EngineSide", side_b: "EngineSide", work: list[list[int]], forced: list[list[int]], chunk: int) -> list[dict]:
+    """Run the workload on A recording span images, then on B (teacher-forced along `forced`, A's tokens) replaying
+    every changed span from A's images. Returns one line per (program, span, step, buffer)."""
+    sp = spans(side_a.doc, side_b.doc)
+    if not any(x["a"] and x["b"] for ss in sp.values() for x in ss):
+        return []
+    store, results = {}, []
+    side_a.eng.probe = SpanTap(side_a.doc, side_b.doc, sp, "a", store)
+    try:
+        side_a.forced_run(work, forced, chunk)
+    finally:
+        side_a.eng.probe = None
+    side_b.eng.probe = SpanTap(side_b.doc, side_a.doc, sp, "b", store, results)
+    try:
+        side_b.forced_run(work, forced, chunk)
+    finally:
+        side_b.eng.probe = None
+    return results
+
+
 # ---- report ------------------------------------------------------------------------------------------
 @dataclass
 class Report:
@@ -338,6 +446,19 @@ def run_test(side_a: EngineSide, side_b: EngineSide, seed: int = 0, prompts: int
                 f"min_top{TOP}_overlap={min(s['top_overlap'] for s in stats)}")
         rep.add(f"noise max_kl={max(s['kl'] for s in noise):.3e}")
         rep.facts["max_kl"] = worst["kl"]
+    # REPLAY: every changed span of B from A's images of the same step
+    span_lines = replay_spans(side_a, side_b, work, out_a, chunk) if any(sp.values()) else []
+    rep.facts["span_replay"] = span_lines
+    by_span: dict = {}
+    for l in span_lines:
+        if "buffer" in l:
+            by_span.setdefault((l["program"], l["span"]), []).append(l)
+    for (prog, k), ls in sorted(by_span.items()):
+        worst_l = max(ls, key=lambda l: (not l["value_identical"], l["max_abs"]))
+        how = "bit-identical" if all(l["identical"] for l in ls) else (
+            "value-identical" if all(l["value_identical"] for l in ls) else
+            f"differs: {worst_l['buffer']} max_abs={worst_l['max_abs']:.3e} max_ulp={worst_l['max_ulp']} at step {worst_l['step']}")
+        rep.add(f"replay program {prog} span {k}: {len(ls)} comparisons from A's images, {how}")
     bit_identical = have_logits and all(np.array_equal(x, y) for x, y in zip(rows_a, forced_b))
     rep.add(f"perf A prefill {perf_a['prefill_s'] * 1e3:.2f} ms decode {perf_a['decode_s'] * 1e3:.2f} ms | "
             f"B prefill {perf_b['prefill_s'] * 1e3:.2f} ms decode {perf_b['decode_s'] * 1e3:.2f} ms")

@@ -55,6 +55,9 @@ def test_ab_test_verdicts(pkg, capsys, tmp_path):
     assert cli.main(["test", str(a), str(tmp_path / "b.json"), "--cpu", "--weights", str(d), "--prompts", "2", "--decode-steps", "3"]) == 0
     out = capsys.readouterr().out
     assert "diff op norm: impl" in out and "PASS" in out
+    # every changed span was replayed on B from A's images of the same step, and wrote the same bytes
+    replays = [l for l in out.splitlines() if l.startswith("replay program")]
+    assert replays and all("bit-identical" in l for l in replays)
     # B: a different epsilon in the final norm changes the function -> not bit-identical; tiny eps stays within KL
     doc2 = json.loads(a.read_text())
     for l in doc2["ops"]["norm_last"]["impl"]["launches"]:
@@ -63,6 +66,9 @@ def test_ab_test_verdicts(pkg, capsys, tmp_path):
     rc = cli.main(["test", str(a), str(tmp_path / "c.json"), "--cpu", "--weights", str(d), "--prompts", "2", "--decode-steps", "3"])
     out = capsys.readouterr().out
     assert "diff op norm_last: impl" in out and rc in (1, 2) or "logit evidence" in out
+    # the replay pins the difference to the span that holds the changed op, from identical inputs
+    replays = [l for l in out.splitlines() if l.startswith("replay program")]
+    assert replays and all("differs: " in l for l in replays)
 
 
 def test_bench_and_kernels(pkg, capsys):

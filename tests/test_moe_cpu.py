@@ -1,4 +1,5 @@
 """The MoE decoder's manifest through the CPU executor against the fp32 oracle."""
+import pytest
 import torch
 
 from kern_b200.cpu import CpuRuntime
@@ -67,3 +68,33 @@ def test_block_scaled_experts_manifest_on_the_cpu_executor():
     err = float((logits[0] - ref).abs().max())
     assert err < 0.35 * float(ref.abs().max()) + 0.05, (err, float(ref.abs().max()))
     assert int(logits[0].argmax()) == int(ref.argmax()) or err < 0.1
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_fused_expert_parallel_manifests_verify(world):
+    """The fused dispatch / combine layer and the decoder over sharded tokens are valid manifests at every group size:
+    five launches per routed layer, none of them a barrier kernel or a library collective."""
+    import dataclasses
+    import json
+
+    from kern_b200 import _native
+    from kern_b200.models import moe, moe_ep
+    from kern_b200.parallel import ep_check
+
+    doc = ep_check.manifest_fused(world, 64, 1024, 512, 16, 4)
+    m, errs = _native.verify(json.dumps(doc))
+    assert m is not None, errs
+    entries = [l["entry"] for c in doc["programs"]["step"]["calls"] for l in doc["ops"][c["op"]]["impl"]["launches"]]
+    assert entries == ["kern_ep_publish", "kern_moe_plan_ep", "kern_ep_fc1_bf16_swiglu_n128", "kern_ep_fc2_bf16_combine_n128",
+                       "kern_ep_finalize"]
+    cfg = dataclasses.replace(moe.TINY_MOE, experts=16, top_k=4)
+    doc = moe_ep.build_manifest_ep_sharded(cfg, world)
+    m, errs = _native.verify(json.dumps(doc))
+    assert m is not None, errs
+    used = {c["op"] for p in doc["programs"].values() for c in p["calls"]}
+    assert {"ep_publish", "ep_plan", "ep_fc1", "ep_fc2", "ep_finalize"} <= used
+    assert not any(l["entry"].startswith("extern:nccl") or l["entry"] == "kern_peer_barrier"
+                   for o in used for l in doc["ops"][o]["impl"]["launches"])
+    # every rank binds its own range of experts
+    w1 = doc["buffers"]["w.l0.w1"]
+    assert w1["shape"][0] == 16 // world and len(w1["bind"][0]["tensor"]["tensors"]) == world
