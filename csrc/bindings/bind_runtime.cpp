@@ -8,7 +8,23 @@
 namespace py = pybind11;
 using namespace kern;
 
+static py::list copies_to_py(const std::vector<RowsCopy>& cs) {
+  py::list out;
+  for (auto& c : cs) out.append(py::make_tuple(c.src, c.dst, c.width, c.src_pitch, c.dst_pitch, c.rows));
+  return out;
+}
+
 void bind_runtime(py::module_& m) {
+  // push shapes (push.hpp): tuples (src, dst, width, src_pitch, dst_pitch, rows), byte offsets
+  m.def("dealt_copies", [](const std::vector<std::tuple<int64_t, int64_t, int64_t, int64_t>>& runs, uint64_t row) {
+    std::vector<pool::RowRun> rr;
+    for (auto& r : runs) rr.push_back({std::get<0>(r), std::get<1>(r), std::get<2>(r), std::get<3>(r)});
+    return copies_to_py(dealt_copies(rr, row));
+  }, "runs (src_row, src_stride, dst_row, rows) of a deal as strided copies of `row`-byte rows, pieces of at most 64 KiB");
+  m.def("split_copies", [](const std::vector<std::pair<uint64_t, uint64_t>>& segments, uint64_t of, uint64_t lines, uint64_t part) {
+    return copies_to_py(Split(segments, of).copies(lines, part));
+  }, "member `part`'s share of a slot of `lines` lines whose rows are sharded by heads over `of` members");
+  m.def("split_line", [](const std::vector<std::pair<uint64_t, uint64_t>>& segments, uint64_t of) { return Split(segments, of).line(); });
   py::class_<Runtime, std::shared_ptr<Runtime>>(m, "Runtime")
       .def(py::init([](const std::string& manifest_text, const std::string& kernels_dir, int gpu,
                        std::map<std::string, std::pair<uint64_t, uint64_t>> topology, uint64_t tokens, uint64_t slots,
@@ -120,5 +136,11 @@ void bind_runtime(py::module_& m) {
       .def("import_region", [](Runtime& r, py::bytes h) { return r.import_region(std::string(h)); })
       .def("push_unit", &Runtime::push_unit)
       .def("push_bytes", &Runtime::push_bytes)
+      .def("push_copies", [](Runtime& r, const std::string& state, uint64_t src_off, uint64_t dst_base, uint64_t dst_bytes,
+                             const std::vector<std::tuple<uint64_t, uint64_t, uint64_t, uint64_t, uint64_t, uint64_t>>& copies) {
+        std::vector<RowsCopy> cs;
+        for (auto& c : copies) cs.push_back({std::get<0>(c), std::get<1>(c), std::get<2>(c), std::get<3>(c), std::get<4>(c), std::get<5>(c)});
+        r.push_copies(state, src_off, dst_base, dst_bytes, cs);
+      })
       .def("bind_host", &Runtime::bind_host);
 }

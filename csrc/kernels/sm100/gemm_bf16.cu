@@ -185,7 +185,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
   const int bpr_div = ag_bpr ? ag_bpr : 1;     // divisor where the blocks-per-rank form of the expression is not taken
   uint32_t ag_want = 0;
   if constexpr (AG) {
-    ag_want = (ag.epochs[blockIdx.x] + 1u) * gridDim.x;
+    // the routed form counts rows (every launch adds BM to each counter), the others the CTAs that have put their share in
+    ag_want = (ag.epochs[blockIdx.x] + 1u) * (EP == 1 ? (uint32_t)BM : gridDim.x);
     __syncthreads();      // every thread has read this CTA's launch count before the gather warps can write the next one
   }
   auto tile_of = [&](int t, int& row0, int& row_end, int& n_blk, int& expert) {
@@ -313,9 +314,49 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
     if constexpr (AG) {
       constexpr int GT = kGatherWarps * 32;
       const int gt = threadIdx.x - 192;                      // 0..GT-1
-      uint8_t* mine = EP == 1 ? reinterpret_cast<uint8_t*>(ep.xg) : reinterpret_cast<uint8_t*>(ag.peers[ag.rank]);
-      const bool sp = EP != 1 && ag.ready != nullptr;
-      constexpr bool epd = EP == 1;
+      if constexpr (EP == 1) {
+        // Routed form: a warp per row. Row r of the sorted buffer is token src_tok[r] on its home rank; the warp copies
+        // its K * 2 bytes (eight 16-byte loads in flight per lane, the next eight issued before the stores of the last),
+        // and then adds one to the row's block counter; padding rows count at once. A block is ready at BM arrivals.
+        const int gw = blockIdx.x * kGatherWarps + (warp - 6), GW = gridDim.x * kGatherWarps;
+        const int row_vecs = K * 2 / 16, total_rows = num_m * BM;
+        for (int b = num_m + gw * 32 + lane; b < ag.max_blocks; b += GW * 32) atomicAdd(ag.flags + b, (uint32_t)BM);   // unused this launch
+        auto ld8 = [&](const uint8_t* src, int v0, uint4 (&x)[8]) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int v = v0 + q * 32;
+            if (v < row_vecs)
+              asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(x[q].x), "=r"(x[q].y), "=r"(x[q].z), "=r"(x[q].w) : "l"(src + (size_t)v * 16));
+          }
+        };
+        for (int r = gw; r < total_rows && *abort_flag == 0; r += GW) {
+          const int tok = ep.src_tok[r];
+          if (tok >= 0) {
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(ep.x_peers[tok / ep.rows_per_rank]) +
+                                 (size_t)(tok % ep.rows_per_rank) * row_vecs * 16;
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(ep.xg) + (size_t)r * row_vecs * 16);
+            uint4 xa[8], xb[8];
+            ld8(src, lane, xa);
+            for (int v0 = lane; v0 < row_vecs; v0 += 256) {
+              if (v0 + 256 < row_vecs) ld8(src, v0 + 256, xb);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                if (v0 + q * 32 < row_vecs) dst[v0 + q * 32] = xa[q];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) xa[q] = xb[q];
+            }
+            __threadfence();
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+          __syncwarp();
+          if (lane == 0) atomicAdd(ag.flags + (r >> 7), 1u);
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(GT) : "memory");
+        if (gt == 0) ag.epochs[blockIdx.x] = ag_want / BM;
+      } else {
+      uint8_t* mine = reinterpret_cast<uint8_t*>(ag.peers[ag.rank]);
+      const bool sp = ag.ready != nullptr;
       if (sp) {
         // every peer's rows of this call are final once its `ready` word has reached this rank's own epoch
         const uint32_t e = *reinterpret_cast<const volatile uint32_t*>(ag.epoch_word);
@@ -335,15 +376,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
       }
       // blocks nobody gathers in this launch (own rows, blocks past the last row) arrive at once: every counter moves
       // by the grid size in every launch, whatever the row count
-      auto arrive_unpulled = [&]() {
-        for (int b = gt; b < ag.max_blocks; b += GT) {
-          const bool remote = b < num_m && !ag.pushed && (sp || epd || b / bpr_div != ag.rank);
-          if (!remote) atomicAdd(ag.flags + b, 1u);
-        }
-      };
-      // (the routed form has a counter per possible tile and nobody waits for the unused ones in this launch: its
-      // bookkeeping adds run after the pulls, off the path of the first tiles)
-      if constexpr (!epd) arrive_unpulled();
+      for (int b = gt; b < ag.max_blocks; b += GT) {
+        const bool remote = b < num_m && !ag.pushed && (sp || b / bpr_div != ag.rank);
+        if (!remote) atomicAdd(ag.flags + b, 1u);
+      }
       // The blocks to pull, in the order the tiles will want them, form one run of 16-byte vectors that is cut into units
       // of eight vectors per thread over the whole grid (a unit usually spans two or three blocks). The loads of unit
       // u + 1 are issued before the stores of unit u, so a thread keeps up to sixteen peer loads in flight: a peer load
@@ -351,18 +387,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
       // A block's counter moves once every unit that touches the block has been stored.
       const size_t row_vecs = (size_t)K * 2 / 16;
       const size_t vecs = (size_t)BM * row_vecs, stride = (size_t)gridDim.x * GT, span = stride * 8;
-      const int pull_blocks = ag.pushed ? 0 : ((sp || epd) ? num_m : num_m - ag_bpr);
+      const int pull_blocks = ag.pushed ? 0 : (sp ? num_m : num_m - ag_bpr);
       const size_t total = (size_t)pull_blocks * vecs;
       const int units = (*abort_flag != 0) ? 0 : (int)((total + span - 1) / span);
-      auto block_at = [&](int i) { return (((sp || epd) ? 0 : ag_bpr) + i + ag_first) % num_m; };   // i-th block in pull order
+      auto block_at = [&](int i) { return ((sp ? 0 : ag_bpr) + i + ag_first) % num_m; };   // i-th block in pull order
       // where vector v of block b comes from (null: it is this rank's own, or past the last row)
       auto source = [&](int b, size_t v) -> const uint8_t* {
-        if constexpr (epd) {        // row r of the sorted buffer is token src_tok[r] on its home rank
-          const int tok = ep.src_tok[b * BM + (int)(v / row_vecs)];
-          if (tok < 0) return nullptr;
-          return reinterpret_cast<const uint8_t*>(ep.x_peers[tok / ep.rows_per_rank]) +
-                 ((size_t)(tok % ep.rows_per_rank) * row_vecs + v % row_vecs) * 16;
-        }
         if (!sp) return reinterpret_cast<const uint8_t*>(ag.peers[b / bpr_div]) + (size_t)b * BM * K * 2 + v * 16;
         const int row = b * BM + (int)(v / row_vecs);
         const int owner = (row / kSpRows) % ag.nranks;
@@ -415,8 +445,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
         for (int q = 0; q < 8; ++q) xa[q] = xb[q];
         ha = hb;
       }
-      if constexpr (epd) arrive_unpulled();
       if (gt == 0) ag.epochs[blockIdx.x] = ag_want / gridDim.x;
+      }   // !EP
     }
   } else {
     // ---------------- epilogue warps 2..5 ----------------

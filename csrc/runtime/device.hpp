@@ -206,6 +206,17 @@ class Device {
   void h2d(uint64_t dst, const void* src, size_t n, CUstream s) { KERN_CU(cuMemcpyHtoDAsync_((CUdeviceptr)dst, src, n, s)); }
   void d2h(void* dst, uint64_t src, size_t n, CUstream s) { KERN_CU(cuMemcpyDtoHAsync_(dst, (CUdeviceptr)src, n, s)); }
   void d2d(uint64_t dst, uint64_t src, size_t n, CUstream s) { KERN_CU(cuMemcpyDtoDAsync_((CUdeviceptr)dst, (CUdeviceptr)src, n, s)); }
+  // `rows` rows of `width` bytes, device to device (either side may be mapped peer memory), rows `pitch` bytes apart
+  void copy_2d(uint64_t dst, uint64_t dst_pitch, uint64_t src, uint64_t src_pitch, uint64_t width, uint64_t rows, CUstream s) {
+    if (rows == 0 || width == 0) return;
+    if (rows == 1 || (dst_pitch == width && src_pitch == width)) { d2d(dst, src, width * rows, s); return; }
+    CUDA_MEMCPY2D c;
+    std::memset(&c, 0, sizeof(c));
+    c.srcMemoryType = CU_MEMORYTYPE_DEVICE; c.srcDevice = (CUdeviceptr)src; c.srcPitch = src_pitch;
+    c.dstMemoryType = CU_MEMORYTYPE_DEVICE; c.dstDevice = (CUdeviceptr)dst; c.dstPitch = dst_pitch;
+    c.WidthInBytes = width; c.Height = rows;
+    KERN_CU(cuMemcpy2DAsync_(&c, s));
+  }
   void* host_alloc(size_t bytes) {
     void* p = nullptr;
     KERN_CU(cuMemHostAlloc_(&p, bytes ? bytes : 16, CU_MEMHOSTALLOC_PORTABLE));

@@ -755,6 +755,22 @@ void Runtime::push_unit(const std::string& state, uint64_t dst_base, int64_t src
   dev_->d2d(dst_base + (uint64_t)dst_unit * st.unit_bytes, st.ptr + (uint64_t)src_unit * st.unit_bytes, st.unit_bytes, stream_);
 }
 
+void Runtime::push_copies(const std::string& state, uint64_t src_off, uint64_t dst_base, uint64_t dst_bytes, const std::vector<RowsCopy>& copies) {
+  auto it = states_.find(state);
+  if (it == states_.end()) throw std::runtime_error("no state named `" + state + "`");
+  const auto& st = it->second;
+  const uint64_t have = st.units * st.unit_bytes;
+  for (const auto& c : copies) {
+    if (c.rows == 0 || c.width == 0) continue;
+    const uint64_t src_end = src_off + c.src + (c.rows - 1) * c.src_pitch + c.width;
+    const uint64_t dst_end = c.dst + (c.rows - 1) * c.dst_pitch + c.width;
+    if (src_end > have || dst_end > dst_bytes)
+      throw std::runtime_error("push of `" + state + "`: a copy ends at byte " + std::to_string(src_end) + " of " + std::to_string(have) +
+                               " here, " + std::to_string(dst_end) + " of " + std::to_string(dst_bytes) + " there");
+  }
+  for (const auto& c : copies) dev_->copy_2d(dst_base + c.dst, c.dst_pitch, st.ptr + src_off + c.src, c.src_pitch, c.width, c.rows, stream_);
+}
+
 void Runtime::push_bytes(const std::string& name, uint64_t dst_base, uint64_t nbytes) {
   auto r = region(name);
   if (nbytes > r.second) throw std::runtime_error("push of `" + name + "`: " + std::to_string(nbytes) + " bytes asked, the region holds " + std::to_string(r.second));

@@ -18,6 +18,7 @@
 #include "../manifest/protocol.hpp"
 #include "../manifest/types.hpp"
 #include "device.hpp"
+#include "push.hpp"
 #include "nccl_api.hpp"
 #include "safetensors.hpp"
 
@@ -160,6 +161,9 @@ class Runtime {
   std::string export_region(const std::string& name);
   uint64_t import_region(const std::string& handle);
   void push_unit(const std::string& state, uint64_t dst_base, int64_t src_unit, int64_t dst_unit);
+  // strided copies (push.hpp: dealt rows, slot parts) from this runtime's `state`, starting `src_off` bytes in, into mapped
+  // memory at `dst_base`; every copy is checked against the state's bytes here and `dst_bytes` there
+  void push_copies(const std::string& state, uint64_t src_off, uint64_t dst_base, uint64_t dst_bytes, const std::vector<RowsCopy>& copies);
   void push_bytes(const std::string& name, uint64_t dst_base, uint64_t nbytes);   // the first nbytes of a buffer (a crossing workspace into the next stage's landing buffer)
   std::set<std::string> nccl_groups() const;     // groups named by `extern:nccl_*` launches: each needs connect() first
 

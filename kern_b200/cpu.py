@@ -582,6 +582,54 @@ class CpuRuntime:
                 a, b = copies["slot"]
                 st[b * n:(b + 1) * n] = st[a * n:(a + 1) * n].clone()
 
+    # ---- another runtime's pools (prefill tier -> decode tier), in host memory: a "mapped pool" is the other runtime's tensor ----
+    def export_states(self) -> dict:
+        return dict(self.states)
+
+    def map_pool(self, handles: dict) -> dict:
+        return dict(handles)
+
+    def state_bytes(self) -> dict[str, int]:
+        return {n: int(t.numel()) for n, t in self.states.items()}
+
+    def _unit_bytes(self, name: str) -> int:
+        s = self.doc["states"][name]
+        return s["bytes_per_token"] * self.page_unit if s.get("bytes_per_token") else s.get("bytes_per_seq", 0)
+
+    def push_state_unit(self, state: str, dst, src_unit: int, dst_unit: int) -> None:
+        n = self._unit_bytes(state)
+        dst[dst_unit * n:(dst_unit + 1) * n] = self.states[state][src_unit * n:(src_unit + 1) * n]
+
+    def push(self, mapped: dict, plan: dict) -> None:
+        for name, s in self.doc["states"].items():
+            if s.get("bytes_per_token"):
+                for a, b in plan["pages"]:
+                    self.push_state_unit(name, mapped[name], a, b)
+            elif s.get("bytes_per_seq") and plan.get("slot") is not None:
+                self.push_state_unit(name, mapped[name], plan["slot"][0], plan["slot"][1])
+
+    def _push_copies(self, state: str, src_off: int, dst, dst_off: int, dst_bytes: int, copies) -> int:
+        src = self.states[state]
+        for (s0, d0, width, sp, dp, rows) in copies:
+            if rows and (src_off + s0 + (rows - 1) * sp + width > src.numel() or d0 + (rows - 1) * dp + width > dst_bytes):
+                raise ValueError(f"push of `{state}`: a copy runs past the end of one side")
+            for r in range(rows):
+                a, b = src_off + s0 + r * sp, dst_off + d0 + r * dp
+                dst[b:b + width] = src[a:a + width]
+        return len(copies)
+
+    def push_rows(self, state: str, dst, dst_bytes: int, runs, row_bytes: int) -> int:
+        return self._push_copies(state, 0, dst, 0, dst_bytes, _native.dealt_copies([tuple(r) for r in runs], row_bytes))
+
+    def push_slot_part(self, state: str, dst, dst_bytes: int, from_slot: int, into_slot: int, segments, of: int, part: int) -> int:
+        mine = int(self.doc["states"][state]["bytes_per_seq"])
+        line = _native.split_line(list(segments), of)
+        if mine % line or mine % of:
+            raise ValueError(f"state `{state}`: a slot of {mine} bytes is not whole lines of {line} bytes over {of} members")
+        theirs = mine // of
+        return self._push_copies(state, from_slot * mine, dst, into_slot * theirs, dst_bytes - into_slot * theirs,
+                                 _native.split_copies(list(segments), of, mine // line, part))
+
     # ---- execution ----
     def _resolve_call_arg(self, a, ptype):
         if "buf" in a:

@@ -304,6 +304,35 @@ class Runtime:
             elif s.get("bytes_per_seq") and plan.get("slot") is not None:
                 self._rt.push_unit(name, mapped[name], plan["slot"][0], plan["slot"][1])
 
+    def state_bytes(self) -> dict[str, int]:
+        """Bytes of every state's pool as allocated here (what a peer that maps them checks its copies against)."""
+        return {name: int(self._rt.region(name)[1]) for name in self.doc["states"]}
+
+    def push_state_unit(self, state: str, dst_ptr: int, src_unit: int, dst_unit: int) -> None:
+        """One page or slot of `state` into the same-shaped mapped pool at `dst_ptr`."""
+        self._rt.push_unit(state, dst_ptr, src_unit, dst_unit)
+
+    def push_rows(self, state: str, dst_ptr: int, dst_bytes: int, runs, row_bytes: int) -> int:
+        """The dealt rows of a paged state (runs of `kern_pool.deal`: source rows a group width apart, destination rows
+        contiguous) into a mapped pool, as strided copies of at most 64 KiB. Reference: crates/kern-runtime/src/push.rs:400-434."""
+        copies = _native.dealt_copies([tuple(r) for r in runs], row_bytes)
+        self._rt.push_copies(state, 0, dst_ptr, dst_bytes, copies)
+        return len(copies)
+
+    def push_slot_part(self, state: str, dst_ptr: int, dst_bytes: int, from_slot: int, into_slot: int, segments, of: int,
+                       part: int) -> int:
+        """Member `part`'s columns of slot `from_slot` of a per-sequence state into slot `into_slot` of a mapped pool whose
+        slots are 1/`of` the size (a decode group that shards the state by heads). `segments`: what a line of the slot
+        holds, (rows, width bytes) each. Reference: crates/kern-runtime/src/push.rs:365-398."""
+        mine = int(self.doc["states"][state]["bytes_per_seq"])
+        line = _native.split_line(list(segments), of)
+        if mine % line or mine % of:
+            raise ValueError(f"state `{state}`: a slot of {mine} bytes is not whole lines of {line} bytes over {of} members")
+        theirs = mine // of
+        copies = _native.split_copies(list(segments), of, mine // line, part)
+        self._rt.push_copies(state, from_slot * mine, dst_ptr + into_slot * theirs, dst_bytes - into_slot * theirs, copies)
+        return len(copies)
+
     def export_buffers(self, names) -> dict[str, bytes]:
         """Handles of buffers another process will write (a pipeline stage's landing buffers)."""
         return {n: self._rt.export_region(n) for n in names}

@@ -62,6 +62,78 @@ def moves(src_pages: list[int], seat: dict, length: int, unit: int, src_slot: in
             "slot": [src_slot, seat["slot"]] if src_slot >= 0 and seat.get("slot", -1) >= 0 else None}
 
 
+def group_moves(src_pages: list[int], seats: list[dict], length: int, unit: int, src_slot: int = -1, *,
+                by_position: bool = False, splits: dict | None = None, d_unit: int | None = None) -> list[dict]:
+    """The copies of one request into the seats of a decode *group* (one seat per rank), a move per (state kind, rank):
+
+    * ``by_position`` (decode context parallelism): rank m of w holds positions p = m (mod w) at local position p // w,
+      so its paged states take the dealt rows — ``{"kind": "rows", "rank": m, "runs": [...]}`` with the runs of
+      `kern_pool.deal` over this lease's pages and the seat's pages; every rank takes the whole state slot.
+    * otherwise (tensor parallel by heads): paged states are sharded by the manifests themselves (each rank's pool holds
+      its heads of every position; the prefill side is built with the same sharding, or pushes whole pages when the
+      bytes per token agree), and a per-sequence state named in ``splits`` — ``{state: [(rows, width), ...]}``, the
+      generator's knowledge of what a line of the slot holds — goes by parts:
+      ``{"kind": "part", "rank": m, "state": name, "from": slot, "into": slot, "segments": [...], "of": w, "part": m}``.
+    Whole pages / whole slots are ``{"kind": "pages", ...}`` / ``{"kind": "slot", ...}`` as in `moves`.
+    Reference: crates/kern-serve/src/pd/mod.rs:225-329 (Move::Rows / Part / Slot)."""
+    w = len(seats)
+    out: list[dict] = []
+    for m, seat in enumerate(seats):
+        if by_position:
+            runs = _native.deal(list(src_pages), unit, list(seat["pages"]), d_unit or unit, w, m, length)
+            out.append({"kind": "rows", "rank": m, "runs": [list(r) for r in runs]})
+        else:
+            n = -(-length // unit)
+            if n > len(src_pages) or n > len(seat["pages"]):
+                raise ValueError(f"{length} tokens need {n} pages; the lease has {len(src_pages)}, rank {m}'s seat {len(seat['pages'])}")
+            out.append({"kind": "pages", "rank": m, "pages": [[src_pages[i], seat["pages"][i]] for i in range(n)]})
+        if src_slot >= 0 and seat.get("slot", -1) >= 0:
+            parted = set()
+            for name, segments in (splits or {}).items():
+                out.append({"kind": "part", "rank": m, "state": name, "from": src_slot, "into": seat["slot"],
+                            "segments": [list(x) for x in segments], "of": w, "part": m})
+                parted.add(name)
+            out.append({"kind": "slot", "rank": m, "slot": [src_slot, seat["slot"]], "except": sorted(parted)})
+    return out
+
+
+class Mirrors:
+    """A prefill runtime's view of a decode group: every rank's pools mapped once (they are fixed from the rank's load
+    for as long as it serves), and the moves of `group_moves` run into them as copies on the prefill runtime's stream,
+    behind the call that wrote the prompt's last rows. `sizes[rank][state]` are the mapped states' bytes (each rank
+    says them with its handles), against which every strided copy is checked before it is issued.
+    Reference: crates/kern-serve/src/pd/mirror.rs:17-61."""
+
+    def __init__(self, rt, handles: list[dict], sizes: list[dict]):
+        self.rt = rt
+        self.mapped = [rt.map_pool(h) for h in handles]
+        self.sizes = sizes
+
+    def push(self, plan: list[dict]) -> int:
+        """Issue every move; returns how many device copies were enqueued."""
+        rt, doc, n = self.rt, self.rt.doc, 0
+        for mv in plan:
+            to, size = self.mapped[mv["rank"]], self.sizes[mv["rank"]]
+            if mv["kind"] == "rows":
+                for name, s in doc["states"].items():
+                    if s.get("bytes_per_token") and name in to:
+                        n += rt.push_rows(name, to[name], size[name], mv["runs"], s["bytes_per_token"])
+            elif mv["kind"] == "pages":
+                rt.push(to, {"pages": mv["pages"], "slot": None})
+                n += len(mv["pages"])
+            elif mv["kind"] == "part":
+                n += rt.push_slot_part(mv["state"], to[mv["state"]], size[mv["state"]], mv["from"], mv["into"],
+                                       [tuple(x) for x in mv["segments"]], mv["of"], mv["part"])
+            elif mv["kind"] == "slot":
+                for name, s in doc["states"].items():
+                    if s.get("bytes_per_seq") and name in to and name not in mv.get("except", ()):
+                        rt.push_state_unit(name, to[name], mv["slot"][0], mv["slot"][1])
+                        n += 1
+            else:
+                raise ValueError(f"unknown move {mv['kind']!r}")
+        return n
+
+
 # ---- D side ------------------------------------------------------------------------------------------------
 @dataclass
 class _Seat:

@@ -223,3 +223,50 @@ def test_mark_gate_hold_and_fetch(cuda):
     torch.cuda.synchronize()
     eng.step([(seq, [5])])
     rt.check_error()
+
+
+@pytest.mark.gpu
+def test_push_dealt_rows_and_slot_parts_between_two_runtimes(cuda):
+    """`Runtime.push_rows` / `push_slot_part` as strided device copies: a prefill runtime's paged rows dealt over a
+    two-member decode group by position, and its state slot sharded by heads, land where the plan says (the decode
+    side's pools are plain device pointers here: both runtimes live in this process)."""
+    from kern_b200.models import toy_int
+    from kern_b200.runtime import Runtime
+    from kern_b200.serve import pd
+
+    doc = toy_int.build_manifest(lined=True)
+    p_rt = Runtime(doc, tokens=16 * 8, slots=4)
+    ranks = [Runtime(doc, tokens=16 * 8, slots=4) for _ in range(2)]
+    unit = p_rt.page_unit if hasattr(p_rt, "page_unit") else 16
+    paged = [n for n, s in doc["states"].items() if s.get("bytes_per_token")]
+    slotted = [n for n, s in doc["states"].items() if s.get("bytes_per_seq")]
+    torch.manual_seed(3)
+    for n in paged + slotted:
+        t = p_rt.tensor(n)
+        t.copy_(torch.randint(0, 256, t.shape, device=cuda, dtype=torch.uint8))
+    length, src_pages, src_slot = unit * 2 + 5, [3, 1, 6], 2
+    seats = [{"pages": [2, 5], "slot": 1}, {"pages": [4, 0], "slot": 3}]
+    mirrors = pd.Mirrors.__new__(pd.Mirrors)
+    mirrors.rt, mirrors.mapped, mirrors.sizes = p_rt, [{n: r.region(n)[0] for n in doc["states"]} for r in ranks], [r.state_bytes() for r in ranks]
+    assert mirrors.push(pd.group_moves(src_pages, seats, length, unit, src_slot, by_position=True)) > 0
+    p_rt.synchronize()
+    for name in paged:
+        row = doc["states"][name]["bytes_per_token"]
+        src_t = p_rt.tensor(name)
+        for m, (rt, seat) in enumerate(zip(ranks, seats)):
+            dst_t = rt.tensor(name)
+            for j, pos in enumerate(range(m, length, 2)):
+                s0 = (src_pages[pos // unit] * unit + pos % unit) * row
+                d0 = (seat["pages"][j // unit] * unit + j % unit) * row
+                assert torch.equal(dst_t[d0:d0 + row], src_t[s0:s0 + row]), (name, m, pos)
+    name = slotted[0]
+    nb = doc["states"][name]["bytes_per_seq"]
+    halves = [torch.zeros(4 * nb // 2, dtype=torch.uint8, device=cuda) for _ in range(2)]
+    for m in range(2):
+        p_rt.push_slot_part(name, halves[m].data_ptr(), halves[m].numel(), src_slot, 3, [(2, nb // 2)], 2, m)
+    p_rt.synchronize()
+    whole = p_rt.tensor(name)[src_slot * nb:(src_slot + 1) * nb].view(2, 2, nb // 4)
+    for m in range(2):
+        assert torch.equal(halves[m][3 * nb // 2:4 * nb // 2].view(2, nb // 4), whole[:, m])
+    with pytest.raises(RuntimeError):
+        p_rt.push_rows(paged[0], ranks[0].region(paged[0])[0], 64, [(0, 2, 0, 4)], doc["states"][paged[0]]["bytes_per_token"])

@@ -99,3 +99,84 @@ def test_refuse_and_abort_and_two_choices():
     t.report(2, {"seqs": 50, "free_pages": 1, "total_pages": 100})
     picks = [t.pick() for _ in range(200)]
     assert picks.count(1) > 100 and t.pick(busy={0, 1, 2}) is None and t.pick(busy={0, 2}) == 1
+
+
+def test_dealt_rows_and_slot_parts_as_copies():
+    """The shapes of a push that is not whole pages or slots: a deal's runs cut into strided copies of at most 64 KiB,
+    and a slot sharded by heads as one strided copy per row of each segment; over all members the parts tile the slot."""
+    from kern_b200 import _native as n
+
+    runs = n.deal([3, 4, 5], 16, [7, 8], 16, 4, 1, 40)          # positions 1, 5, 9, ... of 40, member 1 of 4
+    assert runs == [(3 * 16 + 1, 4, 7 * 16, 10)]
+    assert n.dealt_copies(runs, 1024) == [((3 * 16 + 1) * 1024, 7 * 16 * 1024, 1024, 4096, 1024, 10)]
+    big = n.dealt_copies([(0, 2, 0, 100)], 4096)                # 16 rows of 4 KiB per 64 KiB piece
+    assert [c[5] for c in big] == [16] * 6 + [4] and big[1][0] == 16 * 2 * 4096 and big[1][1] == 16 * 4096
+    assert n.dealt_copies([(0, 2, 0, 3)], 1 << 20)[0][5] == 1   # a row above the piece size travels alone
+    segs, of, lines = [(1, 64 * 4), (3, 16 * 4)], 4, 2          # a [heads=4, 64] block and a 3-tap window of [heads=4, 16]
+    line = n.split_line(segs, of)
+    assert line == 256 + 192
+    covered, dst_seen = set(), {}
+    for part in range(of):
+        for (s0, d0, w, sp, dp, rows) in n.split_copies(segs, of, lines, part):
+            assert sp == line and dp == line // of and rows == lines
+            for r in range(rows):
+                src = range(s0 + r * sp, s0 + r * sp + w)
+                assert not covered & set(src)
+                covered |= set(src)
+                for i, b in enumerate(src):
+                    dst_seen[(part, d0 + r * dp + i)] = b
+    assert covered == set(range(line * lines))                  # the members' sources tile the slot
+    for part in range(of):                                      # and each member's destinations tile its own slot
+        assert sorted(d for (p, d) in dst_seen if p == part) == list(range(line * lines // of))
+    with pytest.raises(ValueError):
+        n.split_copies([(1, 10)], 4, 1, 0)                      # a width the members do not divide
+
+
+def test_mirrors_push_dealt_rows_and_parts_between_host_runtimes():
+    """A prefill runtime pushing one request into a two-rank decode group held in host memory: by position (each rank
+    gets every second row of the paged state, the slot whole) and by heads (each rank gets its columns of the slot)."""
+    import torch
+
+    from kern_b200.cpu import CpuRuntime
+    from kern_b200.models import toy_int
+
+    doc = toy_int.build_manifest(lined=True)
+    p_rt = CpuRuntime(doc, tokens=16 * 8, slots=4)
+    ranks = [CpuRuntime(doc, tokens=16 * 8, slots=4) for _ in range(2)]
+    unit = p_rt.page_unit
+    paged = [n for n, s in doc["states"].items() if s.get("bytes_per_token")]
+    slotted = [n for n, s in doc["states"].items() if s.get("bytes_per_seq")]
+    assert paged and slotted
+    g = torch.Generator().manual_seed(1)
+    for n in paged + slotted:
+        p_rt.states[n].copy_(torch.randint(0, 256, p_rt.states[n].shape, generator=g, dtype=torch.uint8))
+    length, src_pages, src_slot = unit * 2 + 5, [3, 1, 6], 2
+    mirrors = pd.Mirrors(p_rt, [r.export_states() for r in ranks], [r.state_bytes() for r in ranks])
+    seats = [{"pages": [2, 5], "slot": 1}, {"pages": [4, 0], "slot": 3}]
+    # by position
+    n_copies = mirrors.push(pd.group_moves(src_pages, seats, length, unit, src_slot, by_position=True))
+    assert n_copies > 0
+    for name in paged:
+        row = doc["states"][name]["bytes_per_token"]
+        for m, (rt, seat) in enumerate(zip(ranks, seats)):
+            for j, pos in enumerate(range(m, length, 2)):
+                src = (src_pages[pos // unit] * unit + pos % unit) * row
+                dst = (seat["pages"][j // unit] * unit + j % unit) * row
+                assert torch.equal(rt.states[name][dst:dst + row], p_rt.states[name][src:src + row]), (name, m, pos)
+    for name in slotted:
+        nb = doc["states"][name]["bytes_per_seq"]
+        for rt, seat in zip(ranks, seats):
+            assert torch.equal(rt.states[name][seat["slot"] * nb:(seat["slot"] + 1) * nb], p_rt.states[name][src_slot * nb:(src_slot + 1) * nb])
+    # by heads: a group whose slots are half the size takes its columns of every row
+    name = slotted[0]
+    nb = doc["states"][name]["bytes_per_seq"]
+    assert nb % 4 == 0
+    segs = [(2, nb // 2)]                                        # two rows per line, each split over the two members
+    halves = [torch.zeros(4 * nb // 2, dtype=torch.uint8) for _ in range(2)]
+    for m in range(2):
+        p_rt.push_slot_part(name, halves[m], halves[m].numel(), src_slot, 3, segs, 2, m)
+    whole = p_rt.states[name][src_slot * nb:(src_slot + 1) * nb].view(2, 2, nb // 4)      # [row, member, bytes]
+    for m in range(2):
+        assert torch.equal(halves[m][3 * nb // 2:4 * nb // 2].view(2, nb // 4), whole[:, m])
+    with pytest.raises(ValueError):
+        p_rt.push_rows(paged[0], ranks[0].states[paged[0]], 64, [(0, 2, 0, 4)], doc["states"][paged[0]]["bytes_per_token"])
