@@ -357,6 +357,7 @@ extern "C" __global__ void __launch_bounds__(1024)
                                                         tile_count, kern::ScatterArgs(), nullptr, nullptr, ag, ep);    \
   }
 
+KERN_EP_FC1_ENTRY(kern_ep_fc1_bf16_swiglu_n256, 256)
 KERN_EP_FC1_ENTRY(kern_ep_fc1_bf16_swiglu_n128, 128)
 KERN_EP_FC1_ENTRY(kern_ep_fc1_bf16_swiglu_n64, 64)
 

@@ -73,16 +73,6 @@ namespace kern {
   X(cuGraphExecDestroy)             \
   X(cuGraphGetNodes)                \
   X(cuTensorMapEncodeTiled)         \
-  X(cuMemCreate)                    \
-  X(cuMemRelease)                   \
-  X(cuMemAddressReserve)            \
-  X(cuMemAddressFree)               \
-  X(cuMemMap)                       \
-  X(cuMemUnmap)                     \
-  X(cuMemSetAccess)                 \
-  X(cuMemGetAllocationGranularity)  \
-  X(cuMemExportToShareableHandle)   \
-  X(cuMemImportFromShareableHandle) \
   X(cuIpcGetMemHandle)              \
   X(cuIpcOpenMemHandle)             \
   X(cuIpcCloseMemHandle)            \

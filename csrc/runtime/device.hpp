@@ -224,82 +224,8 @@ class Device {
   }
   void host_free(void* p) { if (p) Cuda::get().cuMemFreeHost_(p); }
 
-  // One physical VMM allocation mapped at one reserved range (pooled states, exported buffers).
-  struct Vmm {
-    uint64_t va = 0;
-    size_t bytes = 0;
-    CUmemGenericAllocationHandle handle = 0;
-  };
-  size_t vmm_granularity() {
-    CUmemAllocationProp prop;
-    std::memset(&prop, 0, sizeof(prop));
-    prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
-    prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
-    prop.location.id = gpu_;
-    size_t g = 0;
-    KERN_CU(cuMemGetAllocationGranularity_(&g, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
-    return g;
-  }
-  Vmm alloc_vmm(size_t bytes, bool shareable) {
-    make_current();
-    CUmemAllocationProp prop;
-    std::memset(&prop, 0, sizeof(prop));
-    prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
-    prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
-    prop.location.id = gpu_;
-    if (shareable) prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
-    size_t g = 0;
-    KERN_CU(cuMemGetAllocationGranularity_(&g, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
-    Vmm v;
-    v.bytes = ((bytes ? bytes : 1) + g - 1) / g * g;
-    KERN_CU(cuMemCreate_(&v.handle, v.bytes, &prop, 0));
-    CUdeviceptr va = 0;
-    KERN_CU(cuMemAddressReserve_(&va, v.bytes, g, 0, 0));
-    KERN_CU(cuMemMap_(va, v.bytes, 0, v.handle, 0));
-    CUmemAccessDesc acc;
-    std::memset(&acc, 0, sizeof(acc));
-    acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
-    acc.location.id = gpu_;
-    acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
-    KERN_CU(cuMemSetAccess_(va, v.bytes, &acc, 1));
-    v.va = (uint64_t)va;
-    return v;
-  }
-  int export_fd(const Vmm& v) {
-    int fd = -1;
-    KERN_CU(cuMemExportToShareableHandle_(&fd, v.handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
-    return fd;
-  }
-  // Map an allocation another process exported (its file descriptor already received here).
-  Vmm import_fd(int fd, size_t bytes) {
-    make_current();
-    Vmm v;
-    v.bytes = bytes;
-    KERN_CU(cuMemImportFromShareableHandle_(&v.handle, (void*)(uintptr_t)fd,
-                                            CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
-    CUdeviceptr va = 0;
-    KERN_CU(cuMemAddressReserve_(&va, bytes, vmm_granularity(), 0, 0));
-    KERN_CU(cuMemMap_(va, bytes, 0, v.handle, 0));
-    CUmemAccessDesc acc;
-    std::memset(&acc, 0, sizeof(acc));
-    acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
-    acc.location.id = gpu_;
-    acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
-    KERN_CU(cuMemSetAccess_(va, bytes, &acc, 1));
-    v.va = (uint64_t)va;
-    return v;
-  }
-  void free_vmm(Vmm& v) {
-    auto& cu = Cuda::get();
-    if (v.va) {
-      cu.cuMemUnmap_((CUdeviceptr)v.va, v.bytes);
-      cu.cuMemAddressFree_((CUdeviceptr)v.va, v.bytes);
-    }
-    if (v.handle) cu.cuMemRelease_(v.handle);
-    v = Vmm{};
-  }
-  // Legacy IPC handles for cuMemAlloc memory (64 bytes); the simplest carrier between the
-  // one-process-per-GPU ranks of one box.
+  // IPC handles for cuMemAlloc memory (64 bytes): the carrier between the one-process-per-GPU ranks of one box.
+  // Every state and exported buffer is one cuMemAlloc; there is no cuMemCreate / cuMemMap pool.
   // `offset`: where the exported region starts inside its allocation (a handle names the whole allocation; a runtime
   // with guard bands keeps its payload behind the first band). It travels as eight more bytes after the handle.
   std::string ipc_export(uint64_t p, uint64_t offset = 0) {

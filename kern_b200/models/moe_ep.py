@@ -84,6 +84,9 @@ def build_manifest_ep(cfg: MoeConfig, lamport: bool = True) -> dict:
 
 # ---- expert parallel over sharded tokens: every rank runs its own sequences (attention data-parallel), experts by ranges ----
 
+EP_WIDE_FROM = 192      # rows of this rank from which the routed GEMMs take 256-wide tiles
+
+
 def ep_fused_buffers(world: int, rows_max: int, hidden: int, inter: int, e_n: int, k: int, x: str, group: str = "ep") -> dict:
     """Buffers of the fused dispatch / combine kernels (`moe.cu`, `kern_ep_*`). `x`: the name of the activation buffer
     the experts read (exported here, with its peer table `<x>_peers`); `rows_max`: tokens per rank."""
@@ -109,7 +112,7 @@ def ep_fused_buffers(world: int, rows_max: int, hidden: int, inter: int, e_n: in
 
 
 def ep_fused_ops(world: int, rows_max: int, hidden: int, inter: int, e_n: int, k: int, rows_var: str, group: str = "ep",
-                 accumulate: bool = False, timeout_ns: int = 2_000_000_000) -> dict:
+                 accumulate: bool = False, timeout_ns: int = 2_000_000_000, bn: int | None = None) -> dict:
     """The five ops of a fused expert-parallel layer. Interfaces:
     ep_publish [ids, ids_peers, ready_peers, pub_epoch, rows];
     ep_plan [ids_all, perm, offsets, tiles, tile_count, n_rows, src_tok, row_choice, ready, pub_epoch, err];
@@ -148,28 +151,48 @@ def ep_fused_ops(world: int, rows_max: int, hidden: int, inter: int, e_n: int, k
             "box": [C.BK, bn // 2 if swiglu else bn, 1], "swizzle": 128, "l2_promotion": 256}}]}}
         return a_map, b_map
 
-    bn1 = 128 if 2 * inter >= 128 else 64
-    a1, b1 = maps(hidden, 2 * inter, True, bn1)
+    # 128-wide tiles keep every SM streaming expert weights at decode sizes; 256-wide tiles are the faster tensor-core
+    # shape once every expert has several row tiles (measured at 2 ranks, hidden 7168 / intermediate 2048: 758 against
+    # 1002 us per layer at 1024 tokens per rank). `bn` fixes one width; None picks by this rank's row count.
+    def widths(n: int) -> list[tuple[int, dict | None]]:
+        small = 128 if n >= 128 else 64
+        if bn is not None:
+            return [(min(bn, small) if bn < 256 or n < 256 else 256, None)]
+        if n < 256 or rows_max <= EP_WIDE_FROM:
+            return [(small, None)]
+        return [(small, {"var": rows_var, "max": EP_WIDE_FROM}), (256, {"var": rows_var, "min": EP_WIDE_FROM + 1})]
+
+    def with_when(launch: dict, when: dict | None) -> dict:
+        if when is not None:
+            launch["when"] = when
+        return launch
+
+    fc1 = []
+    for bn1, when in widths(2 * inter):
+        a1, b1 = maps(hidden, 2 * inter, True, bn1)
+        fc1.append(with_when(L(
+            "moe", f"kern_ep_fc1_bf16_swiglu_n{bn1}", [320, 1, 1], [C.SMS, 1, 1],
+            ["bytes<128>", "bytes<128>", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "i32", "i32", "i32", "i32",
+             "out buffer<i32>", "in buffer<u64>", "inout buffer<bf16>", "in buffer<i32>", "inout buffer<u32>", "inout buffer<u32>",
+             "i32", "i32", "i32", "i32"],
+            [a1, b1, P(2), P(3), P(4), {"i32": max_rows}, {"i32": 2 * inter}, {"i32": hidden}, {"i32": inter}, P(9), P(5), P(0), P(6),
+             P(7), P(8), {"i32": rows_max}, {"i32": max_tiles}, rank, {"i32": world}], shared_mem=C.gemm_smem(bn1)), when))
     ops["ep_fc1"] = {"params": ["inout buffer<bf16>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>",
                                 "in buffer<u64>", "in buffer<i32>", "inout buffer<u32>", "inout buffer<u32>", "out buffer<i32>"],
-                     "impl": {"launches": [L(
-        "moe", f"kern_ep_fc1_bf16_swiglu_n{bn1}", [320, 1, 1], [C.SMS, 1, 1],
-        ["bytes<128>", "bytes<128>", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "i32", "i32", "i32", "i32",
-         "out buffer<i32>", "in buffer<u64>", "inout buffer<bf16>", "in buffer<i32>", "inout buffer<u32>", "inout buffer<u32>",
-         "i32", "i32", "i32", "i32"],
-        [a1, b1, P(2), P(3), P(4), {"i32": max_rows}, {"i32": 2 * inter}, {"i32": hidden}, {"i32": inter}, P(9), P(5), P(0), P(6),
-         P(7), P(8), {"i32": rows_max}, {"i32": max_tiles}, rank, {"i32": world}], shared_mem=C.gemm_smem(bn1))]}}
-    bn2 = 128 if hidden >= 128 else 64
-    a2, b2 = maps(inter, hidden, False, bn2)
+                     "impl": {"launches": fc1}}
+    fc2 = []
+    for bn2, when in widths(hidden):
+        a2, b2 = maps(inter, hidden, False, bn2)
+        fc2.append(with_when(L(
+            "moe", f"kern_ep_fc2_bf16_combine_n{bn2}", [192, 1, 1], [C.SMS, 1, 1],
+            ["bytes<128>", "bytes<128>", "in buffer<i32>", "in buffer<i32>", "i32", "i32", "i32", "out buffer<i32>", "in buffer<u64>",
+             "in buffer<i32>", "in buffer<i32>", "inout buffer<u32>", "in buffer<u64>", "i32", "i32", "i32", "i32"],
+            [a2, b2, P(2), P(3), {"i32": max_rows}, {"i32": hidden}, {"i32": inter}, P(9), P(4), P(5), P(6), P(7), P(8),
+             {"i32": rows_max}, {"i32": k}, rank, {"i32": world}],
+            shared_mem=C.gemm_smem(bn2) + 20480), when))     # + the epilogue's row staging
     ops["ep_fc2"] = {"params": ["in buffer<bf16>", "in buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "in buffer<u64>",
                                 "in buffer<i32>", "in buffer<i32>", "inout buffer<u32>", "in buffer<u64>", "out buffer<i32>"],
-                     "impl": {"launches": [L(
-        "moe", f"kern_ep_fc2_bf16_combine_n{bn2}", [192, 1, 1], [C.SMS, 1, 1],
-        ["bytes<128>", "bytes<128>", "in buffer<i32>", "in buffer<i32>", "i32", "i32", "i32", "out buffer<i32>", "in buffer<u64>",
-         "in buffer<i32>", "in buffer<i32>", "inout buffer<u32>", "in buffer<u64>", "i32", "i32", "i32", "i32"],
-        [a2, b2, P(2), P(3), {"i32": max_rows}, {"i32": hidden}, {"i32": inter}, P(9), P(4), P(5), P(6), P(7), P(8),
-         {"i32": rows_max}, {"i32": k}, rank, {"i32": world}],
-        shared_mem=C.gemm_smem(bn2) + 20480)]}}     # + the epilogue's row staging
+                     "impl": {"launches": fc2}}
     odir = "inout" if accumulate else "out"
     ops["ep_finalize"] = {"params": ["inout buffer<bf16>", "in buffer<f32>", f"{odir} buffer<bf16>", "inout buffer<u32>",
                                      "in buffer<u32>", "out buffer<i32>"], "impl": {"launches": [L(

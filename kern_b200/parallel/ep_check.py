@@ -116,7 +116,7 @@ def manifest(world: int, rows_max: int, hidden: int, inter: int, experts: int, k
                          "step_graph": {"batch": {"groups": 1, "rows": "rows"}, "graph": True, "calls": calls}}}
 
 
-def manifest_fused(world: int, rows_max: int, hidden: int, inter: int, experts: int, k: int) -> dict:
+def manifest_fused(world: int, rows_max: int, hidden: int, inter: int, experts: int, k: int, bn: int | None = None) -> dict:
     """The same layer with the dispatch inside FC1 and the combine inside FC2 (`moe.cu`, the `kern_ep_*` entries): five
     launches, no barrier kernel, no NCCL call. `rows_max`: tokens per rank."""
     from ..models import common as C
@@ -132,7 +132,7 @@ def manifest_fused(world: int, rows_max: int, hidden: int, inter: int, experts: 
         "out": buf("bf16", ["rows", hidden], "output"), "error": buf("i32", [1], "output"),
         **moe_ep.ep_fused_buffers(world, rows_max, hidden, inter, e_n, k, "ep.x"),
     }
-    ops = moe_ep.ep_fused_ops(world, rows_max, hidden, inter, e_n, k, "rows")
+    ops = moe_ep.ep_fused_ops(world, rows_max, hidden, inter, e_n, k, "rows", bn=bn)
     calls = moe_ep.ep_fused_calls("ids", "w", "ep.x", "w1", "w2", "out", "rows")
     return {"schema_version": 7, "model": "ep-fused-check", "vars": {"rows": {"max": rows_max, "axis": "rows"}},
             "topology": {"groups": {"ep": world}}, "states": {}, "buffers": bufs,
@@ -192,6 +192,7 @@ def main(argv=None) -> int:
     ap.add_argument("--top-k", type=int, default=4)
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--fused", action="store_true", help="dispatch inside FC1, combine inside FC2 (five launches per layer)")
+    ap.add_argument("--bn", type=int, default=None, choices=[64, 128, 256], help="tile width of the fused routed GEMMs (default: by row count)")
     ap.add_argument("--model", action="store_true", help="also run the MoE decoder with sharded tokens and fused routed layers")
     a = ap.parse_args(argv)
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
@@ -205,7 +206,8 @@ def main(argv=None) -> int:
     h, I, E, k = a.hidden, a.inter, a.experts, a.top_k
     e_n = E // world
     rows_max = max(a.rows)
-    rt = Runtime((manifest_fused if a.fused else manifest)(world, rows_max, h, I, E, k), gpu=local, topology={"ep": (rank, world)},
+    doc = manifest_fused(world, rows_max, h, I, E, k, bn=a.bn) if a.fused else manifest(world, rows_max, h, I, E, k)
+    rt = Runtime(doc, gpu=local, topology={"ep": (rank, world)},
                  guard_bands=True)      # canary bands around every allocation: the peers' adds and stores land in this rank's memory
     group.start(rt)
     g = torch.Generator().manual_seed(21)

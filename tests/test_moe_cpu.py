@@ -87,6 +87,15 @@ def test_fused_expert_parallel_manifests_verify(world):
     entries = [l["entry"] for c in doc["programs"]["step"]["calls"] for l in doc["ops"][c["op"]]["impl"]["launches"]]
     assert entries == ["kern_ep_publish", "kern_moe_plan_ep", "kern_ep_fc1_bf16_swiglu_n128", "kern_ep_fc2_bf16_combine_n128",
                        "kern_ep_finalize"]
+    # from 193 rows of a rank on, the routed GEMMs switch to 256-wide tiles: one launch of each runs, whatever the count
+    wide = ep_check.manifest_fused(world, 1024, 1024, 512, 16, 4)
+    m, errs = _native.verify(json.dumps(wide))
+    assert m is not None, errs
+    for op, small, big in (("ep_fc1", "kern_ep_fc1_bf16_swiglu_n128", "kern_ep_fc1_bf16_swiglu_n256"),
+                           ("ep_fc2", "kern_ep_fc2_bf16_combine_n128", "kern_ep_fc2_bf16_combine_n256")):
+        ls = wide["ops"][op]["impl"]["launches"]
+        assert [l["entry"] for l in ls] == [small, big]
+        assert ls[0]["when"] == {"var": "rows", "max": 192} and ls[1]["when"] == {"var": "rows", "min": 193}
     cfg = dataclasses.replace(moe.TINY_MOE, experts=16, top_k=4)
     doc = moe_ep.build_manifest_ep_sharded(cfg, world)
     m, errs = _native.verify(json.dumps(doc))
