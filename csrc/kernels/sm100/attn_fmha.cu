@@ -14,7 +14,8 @@
 // warps are busy with this tile's. O is rescaled lazily: a row's reference maximum moves only when the running
 // maximum has grown by more than 8 (a factor 256, harmless in f32), so most tiles need no pass over O at all.
 // V is consumed straight from its [token][d] tile as an MN-major B operand: no transpose anywhere.
-// Every mbarrier wait is bounded; a wait that runs out sets *err, the CTA drains and frees its TMEM.
+// Every mbarrier wait is bounded by wall-clock time (2 s); a wait that runs out sets *err with the code of the wait
+// that gave up, the CTA drains and frees its TMEM.
 //
 // Layouts as in attn_paged.cu (q rows inside the fused qkv buffer; kv pool [pages][2][hk][page][d] behind one 2-D
 // tensor map with 64-column boxes; block_table, seq_lens, cu_q, the planner's work list).
@@ -99,6 +100,7 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = a.hq / a.hk;
   if ((int)blockIdx.y >= *a.work_count) return;          // uniform per CTA, before any barrier or allocation
+  if (*reinterpret_cast<volatile int*>(a.err) != 0) return;   // an earlier CTA (or kernel) gave up: the call is lost, do not wait again
   const int seq = a.work[2 * blockIdx.y], blk = a.work[2 * blockIdx.y + 1];
   const int kvh = blockIdx.x;
   const int L = a.seq_lens[seq];
@@ -154,7 +156,7 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a) {
       int stage = 0;
       uint32_t phase = 0;
       for (int t = 0; t < ntiles; ++t) {
-        if (!mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag)) {
+        if (!mbar_wait_ns(&kv_empty[stage], phase ^ 1, abort_flag)) {
           set_error(a.err, ERR_WAIT_EMPTY);
           *abort_flag = 1;
           break;
@@ -194,8 +196,8 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a) {
       bool ok = true;
       auto issue_qk = [&](int j) {
         const int stage = j % kStages;
-        if (!mbar_wait(&kv_full[stage], (j / kStages) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
-        if (!mbar_wait(&s_empty[j & 1], ((j >> 1) & 1) ^ 1, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_EMPTY); return false; }
+        if (!mbar_wait_ns(&kv_full[stage], (j / kStages) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
+        if (!mbar_wait_ns(&s_empty[j & 1], ((j >> 1) & 1) ^ 1, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_EMPTY); return false; }
         tc_fence_after();
         const uint32_t sq = smem_u32(q_s), sk = smem_u32(kv_s + stage * 2 * Cfg::kTileBytes);
 #pragma unroll
@@ -207,7 +209,7 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a) {
       };
       auto issue_pv = [&](int j) {
         const int stage = j % kStages;
-        if (!mbar_wait(p_full, j & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
+        if (!mbar_wait_ns(p_full, j & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
         tc_fence_after();
         const uint32_t sp = smem_u32(p_s), sv = smem_u32(kv_s + stage * 2 * Cfg::kTileBytes + Cfg::kTileBytes);
 #pragma unroll
@@ -236,7 +238,7 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a) {
     float m_ref = -INFINITY, l_run = 0.f;                          // reference maximum (lazy) and row sum
     bool ok = true;
     for (int j = 0; j < ntiles && ok; ++j) {
-      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_FULL); *abort_flag = 1; ok = false; break; }
+      if (!mbar_wait_ns(&s_full[j & 1], (j >> 1) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_FULL); *abort_flag = 1; ok = false; break; }
       tc_fence_after();
       const uint32_t s_tmem = tmem_base + lane_addr + (j & 1) * FN;
       const int tok0 = j * FN;
@@ -262,7 +264,7 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a) {
         moved = true;
       }
       // P and O may be touched once P(j-1) V is done
-      if (j > 0 && !mbar_wait(p_empty, (j - 1) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_EMPTY); *abort_flag = 1; ok = false; break; }
+      if (j > 0 && !mbar_wait_ns(p_empty, (j - 1) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_EMPTY); *abort_flag = 1; ok = false; break; }
       tc_fence_after();
       if (moved && j > 0) {
         const uint32_t o_tmem = tmem_base + lane_addr + 2 * FN;
@@ -310,7 +312,7 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a) {
       mbar_arrive(p_full);
     }
     // ---- epilogue: O / l -> out ----
-    if (ok && !mbar_wait(o_full, 0, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_FULL); *abort_flag = 1; ok = false; }
+    if (ok && !mbar_wait_ns(o_full, 0, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_FULL); *abort_flag = 1; ok = false; }
     if (ok) {
       tc_fence_after();
       const uint32_t o_tmem = tmem_base + lane_addr + 2 * FN;

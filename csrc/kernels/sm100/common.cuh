@@ -72,6 +72,21 @@ KERN_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_f
   return false;
 }
 
+// The same wait bounded by wall-clock time instead of a poll count (a poll's own duration is up to the hardware, so a
+// count of polls can be minutes): gives up `limit_ns` after its first miss.
+KERN_DEVICE uint64_t globaltimer_ns();
+KERN_DEVICE bool mbar_wait_ns(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint64_t limit_ns = 2000000000ull) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 0x3f) == 0x3f) {
+      if (*abort_flag != 0) return false;
+      if (globaltimer_ns() - t0 > limit_ns) return false;
+    }
+  }
+}
+
 // ---- TMA (tiled bulk tensor copies, each into the issuing CTA only) -------------------------------
 KERN_DEVICE void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
