@@ -76,8 +76,10 @@ def main():
     ap.add_argument("--steps", type=int, default=256, help="timed steps (256 = every live sequence turns over once)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="b", choices=["b", "toy"],
-                    help="b: dense GQA 8B-class at concurrency 256 (the headline); toy: the reference's own toy-paged package "
+    ap.add_argument("--config", default="b", choices=["b", "c", "d", "toy"],
+                    help="b: dense GQA 8B-class at concurrency 256 (the headline); c: the hybrid 27B-class decoder under agent-style "
+                         "traffic on one GPU; d: decode of a routed-experts decoder with the experts sharded over the GPUs "
+                         "(fused dispatch / combine); toy: the reference's own toy-paged package "
                          "(its manifest and cubin) served by this engine, the workload of the reference arm")
     ap.add_argument("--concurrency", type=int, default=256)
     ap.add_argument("--layers", type=int, default=36, help="for quick functional checks only; the headline is 36")
@@ -104,6 +106,14 @@ def main():
         from kern_b200.testing import bench_toy
 
         return bench_toy.main(args)
+    if args.config == "c":
+        from kern_b200.testing import bench_agent
+
+        return bench_agent.main(args)
+    if args.config == "d":
+        from kern_b200.testing import bench_ep
+
+        return bench_ep.main(args)
     import numpy as np
     import torch
 

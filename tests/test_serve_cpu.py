@@ -168,3 +168,37 @@ def test_a_failed_step_answers_503_at_once(toy):
         assert e3.value.code == 503
     finally:
         srv.stop()
+
+
+def test_agent_traffic_replay_reuses_prefixes_and_is_exact(toy):
+    """Agent-style sessions (shared family prefix, growing conversation, a new suffix per turn) replayed in a closed
+    loop: every request is served, most prompt tokens come from the prefix cache from the second turn on, and the
+    answers equal the same requests served alone."""
+    from kern_b200.testing import agent_traffic as T
+
+    cfg, make = toy
+    sessions = T.generate(seed=5, sessions=6, turns=3, prefix=(16, 28), suffix=(2, 4), output=(2, 4), vocab=cfg.vocab,
+                          families=2, shared=0.5)      # the toy's context is 64 tokens: 28 + 3 x (4 + 4) fits
+    a, b = sessions[0], sessions[2]
+    assert a.family == b.family and a.prefix[:8] == b.prefix[:8] and a.prefix != b.prefix
+    again = T.generate(seed=5, sessions=6, turns=3, prefix=(16, 28), suffix=(2, 4), output=(2, 4), vocab=cfg.vocab, families=2)
+    assert [s.prefix for s in again] == [s.prefix for s in sessions]                 # one seed, one workload
+    sched = Scheduler(make(tokens=cfg.page_size * 96), chunk=32)
+    res = T.replay(sched, sessions, concurrent=3, deadline_s=60)
+    assert res["requests_served"] == 18 and res["unfinished"] == 0
+    assert res["prefix_cache_share"] > 0.3, res                                      # turns 2 and 3 find their history
+    assert res["ttft_ms_p50"] is not None and res["output_tokens"] > 0
+    # exactness: the last turn of a session, alone on a fresh engine, gives the same answer
+    s0 = sessions[0]
+    turn = s0.turns[-1]
+    # rebuild the last request: history before the last answer = prompt of the last turn
+    # (history = prompt + out of the last turn)
+    n_out = None
+    for n in range(1, turn.max_tokens + 1):
+        prompt = s0.history[: len(s0.history) - n]
+        if prompt[-len(turn.suffix):] == turn.suffix:
+            n_out = n
+            break
+    assert n_out is not None
+    prompt = s0.history[: len(s0.history) - n_out]
+    assert alone(make, prompt, n_out) == s0.history[len(prompt):]
