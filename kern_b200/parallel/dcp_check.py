@@ -14,6 +14,7 @@ import argparse
 import json
 import os
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -83,25 +84,51 @@ def check_model(rank: int, world: int, local: int, steps: int = 6, cpu: bool = F
                         page, rank, world)
     if not cpu:
         torch.cuda.synchronize()
-    worst, agree, length = 0.0, 0, [len(p) for p in prompts]
+    # The decode calls are staged by the serving host's own code (`serve/ranks.py`, a by-position group): it leases every
+    # member its share of each sequence, and builds the member's item with its own page table and dealt slots. The
+    # member pools it keeps account of are the ones filled above, so its leases must name the same pages.
+    from types import SimpleNamespace
+
+    from ..serve.ranks import Ranks
+
+    ranks = Ranks(member.p, member.unit, [nxt + 4] * world, [8] * world, tp=world, by_position=True)
+    seqs_g = []
+    for i, p in enumerate(prompts):
+        gl = ranks.lease(0, len(p) + steps + 2)
+        seqs_g.append(SimpleNamespace(lease=gl, length=len(p), sampling=seqs[i].sampling))
+    mine = [list(sg.lease.members[rank].pages) for sg in seqs_g]
+    # re-deal into the pages the host's leases name (the hand-made tables above only sized the pool)
+    dst_table.zero_()
+    for i, pg in enumerate(mine):
+        dst_table[i, : len(pg)] = torch.tensor(pg, dtype=torch.int32)
+    for i in range(cfg.layers):
+        if cpu:
+            CPU_KERNELS["kern_deal_rows_bf16"]((1, len(prompts), 1), full.states[f"kv.l{i}"], rt.states[f"kv.l{i}"], src_table,
+                                               dst_table, lens, len(prompts), W, W, cfg.kv_heads, cfg.head_dim, page, rank,
+                                               world, 0, None)
+        else:
+            A.deal_rows(full.tensor(f"kv.l{i}"), rt.tensor(f"kv.l{i}"), src_table, dst_table, lens, cfg.kv_heads, cfg.head_dim,
+                        page, rank, world)
+    if not cpu:
+        torch.cuda.synchronize()
+    worst, agree = 0.0, 0
     for _ in range(steps):
         ref_next = eng.step([(s, [t]) for s, t in zip(seqs, toks)])
         ref_logits = full.tensor("logits")[: len(prompts)].float().clone()
-        entries = [fills.Entry(length=length[i], new=[toks[i]], pages=local_pages[i], slot=0,
-                               slots=[dense_dcp.dealt_slot(length[i], local_pages[i], page, rank, world)], sampling=seqs[i].sampling)
-                   for i in range(len(prompts))]
-        call = fills.build(member.p, member.unit, entries)
-        for name, (dtype, col) in call.columns.items():
-            member._write(name, dtype, col)
-        rt.issue(call.forward["name"], call.vars)
-        got_next = member.read_tokens(call.forward, call.groups)[: len(prompts)]
+        staged = ranks.stage(0, [(sg, [t]) for sg, t in zip(seqs_g, toks)])
+        item = ranks.item_for(staged, rank)
+        for name, (dtype, col) in item["rows"].items():
+            member._write(name, dtype, np.asarray(col))
+        rt.issue(item["program"], item["vars"])
+        got_next = member.read_tokens(staged.call.forward, staged.call.groups)[: len(prompts)]
         if not cpu:
             rt.check_error()
         logits = rt.tensor("logits")[: len(prompts)].float()
         worst = max(worst, float((logits - ref_logits).abs().max()))
         agree += sum(int(a[0] == b[0]) for a, b in zip(got_next, ref_next))
         toks = [n[0] for n in ref_next]
-        length = [l + 1 for l in length]
+        for sg in seqs_g:
+            sg.length += 1
     return {"check": "dcp_model", "world": world, "steps": steps, "max_logit_diff": round(worst, 4),
             "tokens_agree": agree, "of": steps * len(prompts), "ok": worst < 0.1}
 

@@ -121,8 +121,16 @@ class Staged:
 
 
 class Ranks:
-    def __init__(self, protocol: dict, unit: int, pages: list[int], slots: list[int], tp: int = 1):
+    """`by_position`: the groups are decode context-parallel groups (a member manifest of `models/dense_dcp.py`): the
+    batch is replicated like a tensor-parallel group's, but member m of w holds positions p = m (mod w) at local position
+    p // w, so its lease covers its own share of the tokens, its page table is its own, and a new token's slot is its
+    dealt slot on the owner and -1 (skipped by the append kernel) on the others. Prefix checkpoints are whole-sequence
+    objects and are not taken for such groups (a request's context arrives by a dealt push from a prefill tier).
+    Reference: crates/kern-serve/src/ranks.rs:313-369 (replicated groups)."""
+
+    def __init__(self, protocol: dict, unit: int, pages: list[int], slots: list[int], tp: int = 1, by_position: bool = False):
         self.p, self.unit = protocol, unit
+        self.by_position = by_position
         self.groups = Groups(len(pages), tp)
         row_pages = min((t["width"] * t["stride"] // unit for t in protocol["page_tables"]), default=0)
         # every member of a group gets the group's smallest geometry: identical pools fed identical operations
@@ -162,20 +170,31 @@ class Ranks:
         return {"pages": per_member[0]["pages"], "slot": per_member[0]["slot"], "members": per_member}
 
     def lease(self, g: int, tokens: int) -> GroupLease:
+        if self.by_position:
+            w = self.groups.tp
+            # member m's share of the first `tokens` positions: tokens // w, one more for the first tokens % w members
+            return GroupLease(g, self._each(g, lambda m, q: self.pools[q].lease(max(1, tokens // w + (1 if m < tokens % w else 0)))))
         leases = self._each(g, lambda m, q: self.pools[q].lease(tokens))
         if any(l.slot != leases[0].slot or l.pages != leases[0].pages for l in leases[1:]):
             raise RuntimeError(f"group {g}: member pools have diverged")
         return GroupLease(g, leases)
 
+    def _whole_sequences_only(self, what: str) -> None:
+        if self.by_position:
+            raise NotImplementedError(f"{what}: a group that deals positions over its members keeps no whole-sequence prefixes")
+
     def checkpoint(self, lease: GroupLease, n: int):
+        self._whole_sequences_only("checkpoint")
         got = [self.pools[q].checkpoint(l, n) for q, l in zip(self.groups.members(lease.group), lease.members)]
         return GroupKept(lease.group, [c for c, _ in got]), self._copies([cp for _, cp in got])
 
     def restore(self, kept: GroupKept, n: int, tokens: int):
+        self._whole_sequences_only("restore")
         got = self._each(kept.group, lambda m, q: self.pools[q].restore(kept.members[m], n, tokens))
         return GroupLease(kept.group, [l for l, _ in got]), self._copies([cp for _, cp in got])
 
     def fork(self, lease: GroupLease, n: int, tokens: int):
+        self._whole_sequences_only("fork")
         got = self._each(lease.group, lambda m, q: self.pools[q].fork(lease.members[m], n, tokens))
         return GroupLease(lease.group, [l for l, _ in got]), self._copies([cp for _, cp in got])
 
@@ -186,10 +205,15 @@ class Ranks:
     # ---- one call ----
     def _entries(self, batch, member: int) -> list[fills.Entry]:
         out = []
+        w = self.groups.tp
         for sq, new in batch:
             l = sq.lease.members[member]
-            out.append(fills.Entry(length=sq.length, new=new, pages=l.pages, slot=l.slot,
-                                   slots=l.slots_of(sq.length, sq.length + len(new)), sampling=sq.sampling))
+            if self.by_position:
+                # position p lives on member p % w at local position p // w; the other members skip the row
+                slots = [l.slot_of(p // w) if p % w == member else -1 for p in range(sq.length, sq.length + len(new))]
+            else:
+                slots = l.slots_of(sq.length, sq.length + len(new))
+            out.append(fills.Entry(length=sq.length, new=new, pages=l.pages, slot=l.slot, slots=slots, sampling=sq.sampling))
         return out
 
     def stage(self, g: int, batch: list, pad: int = 0, round: bool = False) -> Staged:
@@ -271,9 +295,10 @@ class GroupEngine:
         def zero_slot(self, slot: int) -> None:
             self.ranks.queue_zero(self.g, slot)
 
-    def __init__(self, executors, protocol: dict, unit: int, tp: int = 1, group: int = 0, ranks: Ranks | None = None):
+    def __init__(self, executors, protocol: dict, unit: int, tp: int = 1, group: int = 0, ranks: Ranks | None = None,
+                 by_position: bool = False):
         self.ex, self.p, self.unit, self.g = executors, protocol, unit, group
-        self.ranks = ranks or Ranks(protocol, unit, executors.pages, executors.slots, tp)
+        self.ranks = ranks or Ranks(protocol, unit, executors.pages, executors.slots, tp, by_position=by_position)
         self.pool = GroupPool(self.ranks, group)
         self.rt = self._Acts(self.ranks, group)
         self.rows_max, self.groups_max = protocol["rows"]["max"], protocol["groups"]["max"]

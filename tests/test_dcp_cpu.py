@@ -46,3 +46,38 @@ def test_dense_decoder_as_a_two_rank_decode_group_over_gloo():
     assert p.returncode == 0, (p.stdout[-2000:], p.stderr[-2000:])
     line = next(json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))
     assert line["ok"] and line["world"] == 2 and line["tokens_agree"] == line["of"], line
+
+
+def test_ranks_stage_a_by_position_group():
+    """The serving host's staging for a decode group that deals positions over its members: every member leases its own
+    share of a sequence, its item carries its own page table, and a new token's slot is its dealt slot on the owner and
+    -1 on the others."""
+    from types import SimpleNamespace
+
+    import pytest
+
+    from kern_b200.serve.ranks import Ranks
+
+    world = 4
+    doc = dense_dcp.build_manifest_dcp(dense.TINY, world)
+    m, _ = verify(doc)
+    proto = json.loads(m.protocol(sampled=False))
+    page = dense.TINY.page_size
+    ranks = Ranks(proto, page, [64] * world, [8] * world, tp=world, by_position=True)
+    lease = ranks.lease(0, 70)                                  # 70 positions: members hold 18, 18, 17, 17
+    assert [l.capacity >= n for l, n in zip(lease.members, (18, 18, 17, 17))] == [True] * 4
+    assert [len(l.pages) for l in lease.members] == [2, 2, 2, 2]
+    seq = SimpleNamespace(lease=lease, length=37, sampling=None)
+    from kern_b200.fills import Sampling
+    seq.sampling = Sampling()
+    staged = ranks.stage(0, [(seq, [5])])
+    slot_name = next(f["name"] for f in proto["fills"] if f["fill"] == "slot")
+    for member in range(world):
+        item = ranks.item_for(staged, member)
+        slot = item["rows"][slot_name][1][0]
+        if 37 % world == member:
+            assert slot == dense_dcp.dealt_slot(37, list(lease.members[member].pages), page, member, world) >= 0
+        else:
+            assert slot == -1
+    with pytest.raises(NotImplementedError):
+        ranks.checkpoint(lease, 32)
