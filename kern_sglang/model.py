@@ -46,6 +46,7 @@ class KernForCausalLM(nn.Module):
                 states[name] = pool.get_kv_buffer(i) if hasattr(pool, "get_kv_buffer") else pool.kv_buffer[i]
             else:                               # conv / recurrent state pools of hybrid models
                 states[name] = forward_batch.req_to_token_pool.get_state_buffer(kind, i)
+        self._host_states = states
         self.model.bind(states)
 
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor, forward_batch, **kw):
@@ -53,11 +54,16 @@ class KernForCausalLM(nn.Module):
             self._bind(forward_batch)
         tokens, seqs = input_ids.numel(), int(forward_batch.batch_size)
         decode = forward_batch.forward_mode.is_decode()
-        cu = None if decode else torch.nn.functional.pad(torch.cumsum(forward_batch.extend_seq_lens, 0), (1, 0)).int()
-        hidden = self.model.forward("decode" if decode else "prefill", tokens, seqs, torch.cuda.current_stream().cuda_stream,
-                                    token_ids=input_ids, positions=positions, slot_mapping=forward_batch.out_cache_loc,
-                                    seq_lens=forward_batch.seq_lens, cu_seqlens=cu,
-                                    block_table=forward_batch.req_to_token_pool.req_to_token[forward_batch.req_pool_indices])
+        rows = torch.ones(seqs, dtype=torch.int32) if decode else forward_batch.extend_seq_lens.int().cpu()
+        cu = torch.nn.functional.pad(torch.cumsum(rows, 0), (1, 0)).int()
+        # state pools of hybrid models are indexed by the request's pool index: a request that starts here gets a slot
+        # SGLang has not cleared
+        if any(self.doc["states"][n].get("bytes_per_seq") for n in self.host_states):
+            self.model.zero_fresh_states(self._host_states, positions, cu, forward_batch.req_pool_indices)
+        # a batch above the manifest's bounds is cut at request boundaries (`kern_b200.hosted.plan_runs`)
+        hidden = self.model.forward_batch(cu, torch.cuda.current_stream().cuda_stream, token_ids=input_ids, positions=positions,
+                                          slot_mapping=forward_batch.out_cache_loc, seq_lens=forward_batch.seq_lens,
+                                          block_table=forward_batch.req_to_token_pool.req_to_token[forward_batch.req_pool_indices])
         return self.model.logits(hidden.shape[0] if decode else seqs, torch.cuda.current_stream().cuda_stream)
 
 

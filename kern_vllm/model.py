@@ -2,8 +2,9 @@
 
 vLLM calls ``forward(input_ids, positions)`` inside its own forward context (which carries the attention metadata
 and the KV-cache tensors it allocated through `KernAttentionBackend`) and ``compute_logits(hidden)``. On the first
-call the KV tensors of every layer are bound to the manifest's host states ``kv.l<i>``; a call with one row per
-sequence runs `decode`, anything else `prefill`; fresh state pages of a recurrent layer are zeroed on their first use.
+call the KV tensors of every layer are bound to the manifest's host states ``kv.l<i>``; the batch is cut into
+runs (`kern_b200.hosted.plan_runs`): stretches of one-row sequences run `decode`, the rest `prefill`, and a batch above
+the manifest's bounds is cut at sequence boundaries; per-sequence state slots of sequences that start in the call are zeroed.
 Under tensor parallelism every rank runs its shard's manifest and the logits are all-gathered by vLLM.
 Reference counterpart: crates/kern-py/python/kern_vllm/model.py:179-374.
 """
@@ -32,6 +33,7 @@ class KernForCausalLM(nn.Module):
         self.model: HostedModel | None = None
         self.kv_states = sorted((n for n, s in self.doc["states"].items() if s.get("host")), key=lambda n: (len(n), n))
         self._anchor = nn.Parameter(torch.zeros(1), requires_grad=False)      # vLLM moves the module; this marks the device
+        self._host_states: dict[str, torch.Tensor] = {}
 
     def load_weights(self, weights) -> set[str]:
         """vLLM's loader offers (name, tensor) pairs; the runtime reads the checkpoint itself (bind rules need whole files)."""
@@ -42,7 +44,8 @@ class KernForCausalLM(nn.Module):
         return {n for n, _ in weights}
 
     def _bind(self, kv_caches: list[torch.Tensor]) -> None:
-        self.model.bind({name: kv for name, kv in zip(self.kv_states, kv_caches)})
+        self._host_states = {name: kv for name, kv in zip(self.kv_states, kv_caches)}
+        self.model.bind(self._host_states)
 
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor, intermediate_tensors=None, inputs_embeds=None):
         from vllm.forward_context import get_forward_context
@@ -53,13 +56,18 @@ class KernForCausalLM(nn.Module):
             md = next(iter(md.values()))
         if not self.model.bound:
             self._bind([layer.kv_cache[ctx.virtual_engine] for layer in ctx.no_compile_layers.values() if hasattr(layer, "kv_cache")])
-        tokens = input_ids.numel()
-        seqs = int(md.seq_lens.numel())
-        program = "decode" if tokens == seqs else "prefill"
         stream = torch.cuda.current_stream().cuda_stream
-        return self.model.forward(program, tokens, seqs, stream, token_ids=input_ids, positions=positions,
-                                  slot_mapping=md.slot_mapping, seq_lens=md.seq_lens, cu_seqlens=md.query_start_loc,
-                                  block_table=md.block_table_tensor)
+        cu = md.query_start_loc
+        # the host's per-sequence state slots (recurrent / conv state of hybrid models): a sequence that starts in this
+        # call gets a slot the host has not cleared
+        state_slots = getattr(md, "state_indices_tensor", None)
+        if state_slots is not None and self._host_states:
+            self.model.zero_fresh_states(self._host_states, positions, cu, state_slots)
+        # decode rows and prompt chunks of one vLLM batch run as a graph-replayed `decode` call plus a ragged `prefill`
+        # call; a batch above the manifest's bounds is cut at sequence boundaries
+        more = {"state_slots": state_slots} if state_slots is not None else {}
+        return self.model.forward_batch(cu, stream, token_ids=input_ids, positions=positions, slot_mapping=md.slot_mapping,
+                                        seq_lens=md.seq_lens, block_table=md.block_table_tensor, **more)
 
     def compute_logits(self, hidden_states: torch.Tensor, sampling_metadata=None) -> torch.Tensor:
         rows = hidden_states.shape[0]
