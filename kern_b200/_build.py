@@ -149,6 +149,20 @@ def build_cli(force: bool = False) -> Path:
     return out
 
 
+def build_runner(force: bool = False) -> Path:
+    """The native `kern-run` binary: manifest + pool + runtime (the CUDA driver and NCCL are reached by dlopen at run
+    time, so it builds and links without a GPU) behind a single-sequence caller."""
+    out = PKG / "bin" / "kern-run"
+    srcs = [CSRC / "cli" / "kern_run.cpp", *sorted((CSRC / "manifest").glob("*.cpp")), *sorted((CSRC / "runtime").glob("*.cpp"))]
+    headers = [p for p in CSRC.rglob("*.hpp")]
+    if not force and not _newer([*srcs, *headers], out):
+        return out
+    out.parent.mkdir(exist_ok=True)
+    _run([CXX, "-O2", "-std=c++17", "-Wall", "-Wno-unused-function", "-I", str(CSRC), "-I", "/usr/local/cuda/include", "-o", str(out),
+          *map(str, srcs), "-ldl", "-lpthread"])
+    return out
+
+
 def build_host_libs(force: bool = False) -> list[Path]:
     """Shared libraries with host code compiled by nvcc (C entry points reached through ctypes)."""
     outs = []
@@ -169,6 +183,7 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
             build_kernels(force, verbose)
             build_native(force)
             build_cli(force)
+            build_runner(force)
             build_host_libs(force)
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)

@@ -270,3 +270,49 @@ def test_push_dealt_rows_and_slot_parts_between_two_runtimes(cuda):
         assert torch.equal(halves[m][3 * nb // 2:4 * nb // 2].view(2, nb // 4), whole[:, m])
     with pytest.raises(RuntimeError):
         p_rt.push_rows(paged[0], ranks[0].region(paged[0])[0], 64, [(0, 2, 0, 4)], doc["states"][paged[0]]["bytes_per_token"])
+
+
+@pytest.mark.gpu
+def test_native_runner_executes_manifests_without_python(cuda, tmp_path):
+    """`kern_b200/bin/kern-run` (C++ only: manifest, pool and runtime behind a single-sequence caller) produces the tokens
+    of the exact integer model's Python twin, with and without a per-sequence state, and of the dense toy decoder served
+    by the Python engine from the same safetensors checkpoint."""
+    import json
+    import os
+    import subprocess
+
+    from safetensors.torch import save_file
+
+    from kern_b200.engine import Engine
+    from kern_b200.models import dense, toy_int
+    from kern_b200.runtime import Runtime
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = os.path.join(root, "kern_b200", "bin", "kern-run")
+    kernels = os.path.join(root, "kern_b200", "kernels")
+    assert os.path.exists(exe), "the native runner was not built"
+
+    def run(manifest, prompt, steps, extra=()):
+        p = subprocess.run([exe, str(manifest), "--kernels", kernels, "--prompt", ",".join(map(str, prompt)), "--steps", str(steps), *extra],
+                           capture_output=True, text=True, timeout=120)
+        assert p.returncode == 0, p.stderr[-2000:]
+        return json.loads(p.stdout.strip().splitlines()[-1])
+
+    prompt = [5, 6, 7, 8, 9, 200, 31]
+    for lined in (False, True):
+        path = tmp_path / f"toy_int_{int(lined)}.json"
+        path.write_text(json.dumps(toy_int.build_manifest(lined=lined)))
+        got = run(path, prompt, 6, ("--chunk", "4"))
+        assert got["tokens"] == toy_int.generate(prompt, 6, lined), (lined, got)
+        assert got["launches"] > 0
+    cfg = dense.TOY
+    w = dense.random_weights(cfg, seed=3, std=0.08)
+    save_file({k: v.contiguous() for k, v in w.items()}, str(tmp_path / "model.safetensors"))
+    doc = dense.build_manifest(cfg)
+    (tmp_path / "dense.json").write_text(json.dumps(doc))
+    rt = Runtime(doc, tokens=cfg.page_size * 16)
+    rt.load_tensors(lambda name: w[name].to(cuda))
+    rt.once()
+    want = Engine(rt).generate(prompt, 5)
+    got = run(tmp_path / "dense.json", prompt, 5, ("--weights", str(tmp_path / "model.safetensors")))
+    assert got["tokens"] == want and got["graphs"] >= 1
