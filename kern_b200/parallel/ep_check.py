@@ -141,7 +141,7 @@ def manifest_fused(world: int, rows_max: int, hidden: int, inter: int, experts: 
                          "step_graph": {"batch": {"groups": 1, "rows": "rows"}, "graph": True, "calls": calls}}}
 
 
-def check_model(rank: int, world: int, dev) -> dict:
+def check_model(rank: int, world: int, dev, traffic: int | None = None) -> dict:
     """The MoE decoder with tokens sharded over the group (`models/moe_ep.py::build_manifest_ep_sharded`): every rank
     serves its own prompts, the routed layers are the fused kernels; logits against the one-GPU fp32 oracle."""
     import dataclasses
@@ -159,7 +159,7 @@ def check_model(rank: int, world: int, dev) -> dict:
     group.start(rt)
     eng = Engine(rt)
     oracle = moe.MoeOracle(cfg, weights, device="cuda")
-    g = torch.Generator().manual_seed(100 + rank)                       # every rank has its own traffic
+    g = torch.Generator().manual_seed(100 + (rank if traffic is None else traffic))     # every rank has its own traffic
     prompts = [torch.randint(0, cfg.vocab, (int(n),), generator=g).tolist() for n in torch.randint(3, 90, (3,), generator=g)]
     seqs = [eng.open(140) for _ in prompts]
     caches = [oracle.new_cache() for _ in prompts]
@@ -180,7 +180,14 @@ def check_model(rank: int, world: int, dev) -> dict:
     ok = torch.tensor([int(worst < 0.3 and mean < 0.05)], device=dev)
     if world > 1:
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    return {"max_logit_diff": round(worst, 4), "mean_logit_diff": round(mean, 4), "graphs": rt.graphs, "ok": bool(ok.item())}
+    mine = torch.tensor([worst, mean], device=dev)
+    every = [torch.zeros_like(mine) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(every, mine)
+    else:
+        every = [mine]
+    return {"max_logit_diff": round(worst, 4), "mean_logit_diff": round(mean, 4), "graphs": rt.graphs, "ok": bool(ok.item()),
+            "by_rank": [[round(float(x[0]), 4), round(float(x[1]), 4)] for x in every]}
 
 
 def main(argv=None) -> int:
@@ -193,6 +200,7 @@ def main(argv=None) -> int:
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--fused", action="store_true", help="dispatch inside FC1, combine inside FC2 (five launches per layer)")
     ap.add_argument("--bn", type=int, default=None, choices=[64, 128, 256], help="tile width of the fused routed GEMMs (default: by row count)")
+    ap.add_argument("--traffic", type=int, default=None, help="the model check with the prompts rank N of a larger group would get")
     ap.add_argument("--model", action="store_true", help="also run the MoE decoder with sharded tokens and fused routed layers")
     a = ap.parse_args(argv)
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
@@ -289,7 +297,7 @@ def main(argv=None) -> int:
     if rank == 0:
         print(json.dumps(line), flush=True)
     if a.model:
-        m = check_model(rank, world, dev)
+        m = check_model(rank, world, dev, a.traffic)
         if rank == 0:
             print(json.dumps({"check": "expert_parallel_sharded_decoder", "world": world, **m}), flush=True)
     allok = all(r["ok"] for r in results)
