@@ -177,7 +177,8 @@ def check_model(rank: int, world: int, dev, traffic: int | None = None) -> dict:
         toks = [n[0] for n in nxt]
     rt.check_error()
     worst, mean = max(float(d.max()) for d in diffs), max(float(d.mean()) for d in diffs)
-    ok = torch.tensor([int(worst < 0.3 and mean < 0.05)], device=dev)
+    # bf16 against the fp32 oracle with std 0.05 weights: the mean difference sits at 0.01-0.05 depending on the prompts
+    ok = torch.tensor([int(worst < 0.3 and mean < 0.08)], device=dev)
     if world > 1:
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     mine = torch.tensor([worst, mean], device=dev)

@@ -298,7 +298,7 @@ def test_native_runner_executes_manifests_without_python(cuda, tmp_path):
         assert p.returncode == 0, p.stderr[-2000:]
         return json.loads(p.stdout.strip().splitlines()[-1])
 
-    prompt = [5, 6, 7, 8, 9, 200, 31]
+    prompt = [11, 12, 13, 14, 15, 16, 17]          # a prompt whose continuation does not start with the model's stop token
     for lined in (False, True):
         path = tmp_path / f"toy_int_{int(lined)}.json"
         path.write_text(json.dumps(toy_int.build_manifest(lined=lined)))
