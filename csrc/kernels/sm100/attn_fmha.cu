@@ -266,7 +266,9 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a) {
       // P and O may be touched once P(j-1) V is done
       if (j > 0 && !mbar_wait_ns(p_empty, (j - 1) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_EMPTY); *abort_flag = 1; ok = false; break; }
       tc_fence_after();
-      if (moved && j > 0) {
+      // tcgen05.ld / st are warp-wide (.sync.aligned): the pass over O runs for the whole warp when any of its rows
+      // moved (alpha is 1 for the rows that did not), never under a per-lane branch
+      if (__any_sync(0xffffffffu, moved && j > 0)) {
         const uint32_t o_tmem = tmem_base + lane_addr + 2 * FN;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {

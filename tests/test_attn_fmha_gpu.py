@@ -56,6 +56,46 @@ def test_fmha_prefill_matches_fp32(cuda, hq, hk, page_size, new, prefix):
         torch.testing.assert_close(out[lo:hi].float(), ref, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("hq,hk", [(8, 2), (32, 8)])
+def test_fmha_prefill_rescales_rows_whose_maximum_moves_late(cuda, hq, hk):
+    """Keys that grow with their position: the running maximum of a row outgrows its lazy reference by more than 2^8 at
+    some later KV tile, at a different tile for different rows of a warp, so the pass that rescales O in TMEM runs with
+    only some of the warp's rows moving (the pass itself must run for the whole warp: `tcgen05.ld` / `st` are
+    warp-wide instructions)."""
+    from kern_b200.ops import attention as A
+    from kern_b200.ops.launcher import Kernels
+
+    d, page_size = 128, 64
+    torch.manual_seed(41)
+    new, prefix = [384, 200], [512, 0]
+    lens = [n + p for n, p in zip(new, prefix)]
+    pool, table, ks, vs = _build_cache(cuda, lens, hk, d, page_size)
+    # scale every key by a ramp over its position: 1x at the start, 12x at the end of its sequence
+    for s, l in enumerate(lens):
+        ramp = torch.linspace(1.0, 12.0, l, device=cuda).view(l, 1, 1)
+        knew = bf(ks[s].float() * ramp)
+        ks[s] = knew
+        for p in range((l + page_size - 1) // page_size):
+            lo, hi = p * page_size, min(l, (p + 1) * page_size)
+            pool[int(table[s, p]), 0, :, : hi - lo] = knew[lo:hi].transpose(0, 1)
+    cu = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=cuda)
+    q = bf(torch.randn(int(cu[-1]), hq * d, device=cuda))
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=cuda)
+    # the premise: scores (log2 domain) whose per-tile maxima differ by more than 8 between tiles, row by row
+    s0 = (q[:8].view(8, hq, d)[:, 0].float() @ ks[0][:, 0].float().T) * (d ** -0.5) * 1.4427
+    tiles = s0[:, :512].view(8, 4, 128).max(-1).values
+    assert bool(((tiles[:, 1:] - tiles[:, :-1]).abs() > 8).any())
+    out = A.fmha_prefill(q, pool, table, seq_lens, hq, cu)
+    torch.cuda.synchronize()
+    Kernels.get(cuda).check_error()
+    for s in range(len(lens)):
+        lo, hi = int(cu[s]), int(cu[s + 1])
+        qs = q[lo:hi].reshape(hi - lo, hq, d)
+        pos = torch.arange(prefix[s], lens[s], device=cuda)
+        ref = A.attention_reference(qs, ks[s], vs[s], pos)
+        torch.testing.assert_close(out[lo:hi].float(), ref, rtol=3e-2, atol=3e-2)
+
+
 def test_dense_decoder_with_head_dim_128_uses_the_tcgen05_prefill_kernel(cuda, monkeypatch):
     """A small dense decoder with head_dim 128 through the runtime and the engine: ragged calls that mix prompt chunks
     (the tcgen05 kernel's list) with decode rows (the token-parallel kernel's list), against the fp32 oracle."""
