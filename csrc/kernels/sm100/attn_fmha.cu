@@ -26,7 +26,9 @@
 namespace kern {
 
 constexpr int FM = 128;   // query rows per CTA
-constexpr int FN = 128;   // tokens per KV tile
+// FN, the tokens per KV tile, is a template parameter: 128 (one CTA per SM: all 512 TMEM columns, 193 KB of shared
+// memory) or 64 (S buffers of 64 columns: 256 TMEM columns and 113 KB, so two CTAs share an SM and one's MMAs run under
+// the other's softmax, which is the critical path of this kernel).
 
 // Shared-memory descriptor of an MN-major operand tile written by TMA with the 128-byte swizzle: rows are K (tokens),
 // each 128 bytes = 64 MN elements; 8 rows form a 1024-byte swizzle atom; the next 64 MN elements are `mn_block_bytes`
@@ -54,14 +56,17 @@ KERN_DEVICE void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
 }
 KERN_DEVICE void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-template <int D>
+template <int D, int FN>
 struct FmhaCfg {
   static constexpr int kQBytes = FM * D * 2;              // D / 64 column blocks of [128 rows][128 bytes]
-  static constexpr int kPBytes = FM * FN * 2;             // two blocks of 64 tokens
+  static constexpr int kPBytes = FM * FN * 2;             // FN / 64 blocks of 64 tokens
   static constexpr int kTileBytes = FN * D * 2;           // K or V
   static constexpr int kStages = 2;
-  static constexpr int kSmem = 1024 + kQBytes + kPBytes + kStages * 2 * kTileBytes + 256;
-  static constexpr int kTmemCols = 512;                   // S0 | S1 | O
+  // room to bring the tiles to a 1024-byte boundary: the two-per-SM form has 768 bytes to spare under the SM's 228 KB
+  // and checks that its (1024-aligned in practice) base needs no more
+  static constexpr int kSlack = FN == 64 ? 768 : 1024;
+  static constexpr int kSmem = kSlack + kQBytes + kPBytes + kStages * 2 * kTileBytes + 256;
+  static constexpr int kTmemCols = 2 * FN + D <= 256 ? 256 : 512;   // S0 | S1 | O
 };
 
 struct FmhaArgs {
@@ -77,12 +82,16 @@ struct FmhaArgs {
   float scale_log2;
 };
 
-template <int D>
+template <int D, int FN>
 KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a) {
-  using Cfg = FmhaCfg<D>;
+  using Cfg = FmhaCfg<D, FN>;
   constexpr int kStages = Cfg::kStages;
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if ((int)(smem - smem_raw) > Cfg::kSlack) {             // uniform per CTA, before any barrier or allocation
+    if (threadIdx.x == 0) set_error(a.err, ERR_BOUNDS);
+    return;
+  }
   uint8_t* q_s = smem;
   uint8_t* p_s = q_s + Cfg::kQBytes;
   uint8_t* kv_s = p_s + Cfg::kPBytes;
@@ -370,5 +379,15 @@ extern "C" __global__ void __launch_bounds__(192, 1)
                                 int page_size, int pool_pages, float scale_log2, int* err) {
   FmhaArgs a{q, out, block_table, seq_lens, cu_q, work, work_count, err, hq, hk, q_stride, out_stride, max_pages, page_size,
              pool_pages, scale_log2};
-  fmha_body<128>(&kv_map, a);
+  fmha_body<128, 128>(&kv_map, a);
+}
+
+extern "C" __global__ void __launch_bounds__(192, 2)
+    kern_attn_fmha_prefill_d128_t64(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* q, __nv_bfloat16* out,
+                                    const int* block_table, const int* seq_lens, const int* cu_q, const int* work,
+                                    const int* work_count, int hq, int hk, int q_stride, int out_stride, int max_pages,
+                                    int page_size, int pool_pages, float scale_log2, int* err) {
+  FmhaArgs a{q, out, block_table, seq_lens, cu_q, work, work_count, err, hq, hk, q_stride, out_stride, max_pages, page_size,
+             pool_pages, scale_log2};
+  fmha_body<128, 64>(&kv_map, a);
 }

@@ -414,6 +414,7 @@ def _attention_ragged(g, kv, q, out, table, seq_lens, cu_q, work_p, count_p, wor
 
 
 CPU_KERNELS["kern_attn_fmha_prefill_d128"] = _attention_fmha
+CPU_KERNELS["kern_attn_fmha_prefill_d128_t64"] = _attention_fmha
 for _d in (64, 128):
     CPU_KERNELS[f"kern_attn_ragged_paged_d{_d}"] = _attention_ragged
 for _d in (16, 32, 64, 128, 256):

@@ -376,9 +376,12 @@ def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, 
     # many-row sequences: row-parallel causal kernel (on the 5th-generation tensor cores for head_dim 128); few-row
     # sequences (decode rows riding in the ragged call): token-parallel kernel, so their KV streams at full bandwidth
     if fmha:
-        many = {"module": "attn_fmha", "entry": "kern_attn_fmha_prefill_d128", "block": [192, 1, 1],
+        import os
+
+        tile = int(os.environ.get("KERN_B200_FMHA_TILE", "64"))      # tokens per KV tile: 64 (two CTAs per SM) or 128
+        many = {"module": "attn_fmha", "entry": "kern_attn_fmha_prefill_d128" + ("_t64" if tile == 64 else ""), "block": [192, 1, 1],
                 "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1],
-                "shared_mem": 1024 + 128 * d * 2 + 128 * 128 * 2 + 2 * 2 * (128 * d * 2) + 256,
+                "shared_mem": (768 if tile == 64 else 1024) + 128 * d * 2 + 128 * tile * 2 + 2 * 2 * (tile * d * 2) + 256,
                 "params": ["bytes<128>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "in buffer<i32>",
                            "in buffer<i32>", "in buffer<i32>"] + ["i32"] * 7 + ["f32", "out buffer<i32>"],
                 "args": [_kv_map(d, page_size, 1), {"param": 0}, {"param": 2}, {"param": 3}, {"param": 4}, {"param": 5}, {"param": 6},

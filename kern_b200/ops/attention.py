@@ -135,6 +135,11 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tens
     return out
 
 
+def fmha_smem(d: int, tile: int) -> int:
+    """Dynamic shared memory of the tcgen05 prefill kernel: Q and P tiles, a two-stage K/V ring, barriers, alignment room."""
+    return (768 if tile == 64 else 1024) + 128 * d * 2 + 128 * tile * 2 + 2 * 2 * (tile * d * 2) + 256
+
+
 def ragged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor, hq: int,
                      cu_q: torch.Tensor, *, out: torch.Tensor | None = None, seqs: int | None = None,
                      scale: float | None = None, one_launch: bool = True) -> torch.Tensor:
@@ -177,8 +182,9 @@ def ragged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Ten
 
 def fmha_prefill(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor, hq: int,
                  cu_q: torch.Tensor, *, out: torch.Tensor | None = None, seqs: int | None = None,
-                 scale: float | None = None) -> torch.Tensor:
-    """Causal prefill attention of a ragged call on the tcgen05 kernel (csrc/kernels/sm100/attn_fmha.cu): head_dim 128,
+                 scale: float | None = None, tile: int = 64) -> torch.Tensor:
+    """`tile`: tokens per KV tile, 128 (one CTA per SM) or 64 (two CTAs per SM: one's MMAs under the other's softmax).
+    Causal prefill attention of a ragged call on the tcgen05 kernel (csrc/kernels/sm100/attn_fmha.cu): head_dim 128,
     128 query rows per CTA (128 / group tokens x the group's heads), S and O in TMEM. Same operands as
     ``paged_attention(..., prefill=True, cu_q=...)``."""
     k = Kernels.get(q.device)
@@ -199,8 +205,9 @@ def fmha_prefill(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
     view = pool.view(pages * 2 * hk * page_size, d)
     kv_map = k.tensor_map_2d(view, min(page_size, 64), 64)
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
-    smem = 1024 + 128 * d * 2 + 128 * 128 * 2 + 2 * 2 * (128 * d * 2) + 256
-    k.launch("attn_fmha", "kern_attn_fmha_prefill_d128", (hk, items, 1), (192,),
+    assert tile in (64, 128)
+    smem = fmha_smem(d, tile)
+    k.launch("attn_fmha", "kern_attn_fmha_prefill_d128" + ("_t64" if tile == 64 else ""), (hk, items, 1), (192,),
              [kv_map, ptr(q), ptr(out), ptr(block_table), ptr(seq_lens), ptr(cu_q), ptr(work), ptr(count), i32(hq), i32(hk),
               i32(q.stride(0)), i32(out.stride(0)), i32(block_table.shape[1]), i32(page_size), i32(pages),
               f32(scale * 1.4426950408889634), ptr(k.err_word())], shared_mem=smem)

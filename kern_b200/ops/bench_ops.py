@@ -277,13 +277,13 @@ def bench_attn_prefill(a):
     if a.fmha:
         from .attention import fmha_prefill
 
-        ms = timeit(lambda: fmha_prefill(q, pool, table, lens, a.hq, cu, out=out), a.iters)
+        ms = timeit(lambda: fmha_prefill(q, pool, table, lens, a.hq, cu, out=out, tile=a.fmha_tile), a.iters)
     else:
         ms = timeit(lambda: paged_attention(q, pool, table, lens, a.hq, out=out, prefill=True, cu_q=cu, max_rows=a.rows), a.iters)
     Kernels.get().check_error()
     # causal: row r of a chunk sees prefix + r + 1 keys
     keys = a.rows * a.prefix + a.rows * (a.rows + 1) / 2
-    report("attn_fmha_prefill_tcgen05" if a.fmha else "attn_prefill_paged", ms, flops=4.0 * a.seqs * a.hq * a.d * keys, seqs=a.seqs,
+    report(f"attn_fmha_prefill_tcgen05_t{a.fmha_tile}" if a.fmha else "attn_prefill_paged", ms, flops=4.0 * a.seqs * a.hq * a.d * keys, seqs=a.seqs,
            rows=a.rows, prefix=a.prefix)
 
 
@@ -352,6 +352,7 @@ def main(argv=None):
     d.add_argument("--ctx", type=int, default=2432); d.add_argument("--splits", type=int, default=None)
     p.add_argument("--prefix", type=int, default=0)
     p.add_argument("--fmha", action="store_true", help="the tcgen05 kernel (head_dim 128) instead of the mma.sync one")
+    p.add_argument("--fmha-tile", type=int, default=64, choices=[64, 128], help="tokens per KV tile of the tcgen05 kernel")
     rg = sub.add_parser("attn_ragged")
     rg.add_argument("--seqs", type=int, default=256); rg.add_argument("--hq", type=int, default=32); rg.add_argument("--hk", type=int, default=8)
     rg.add_argument("--d", type=int, default=128); rg.add_argument("--page", type=int, default=64); rg.add_argument("--rows", type=int, default=2304)

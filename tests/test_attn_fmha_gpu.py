@@ -30,9 +30,10 @@ def _build_cache(cuda, lens, hk, d, page_size):
     return pool, table, ks, vs
 
 
+@pytest.mark.parametrize("tile", [64, 128])
 @pytest.mark.parametrize("hq,hk,page_size", [(8, 2, 64), (4, 4, 16), (16, 2, 128), (4, 1, 64)])
 @pytest.mark.parametrize("new,prefix", [([128], [0]), ([5, 64, 130, 257], [0, 17, 64, 300]), ([700, 33], [1000, 0])])
-def test_fmha_prefill_matches_fp32(cuda, hq, hk, page_size, new, prefix):
+def test_fmha_prefill_matches_fp32(cuda, hq, hk, page_size, new, prefix, tile):
     from kern_b200.ops import attention as A
     from kern_b200.ops.launcher import Kernels
 
@@ -45,7 +46,7 @@ def test_fmha_prefill_matches_fp32(cuda, hq, hk, page_size, new, prefix):
     wide = bf(torch.randn(total, (hq + 2 * hk) * d, device=cuda))
     q = wide[:, : hq * d]
     seq_lens = torch.tensor(lens, dtype=torch.int32, device=cuda)
-    out = A.fmha_prefill(q, pool, table, seq_lens, hq, cu)
+    out = A.fmha_prefill(q, pool, table, seq_lens, hq, cu, tile=tile)
     torch.cuda.synchronize()
     Kernels.get(cuda).check_error()
     for s in range(len(lens)):
@@ -56,8 +57,9 @@ def test_fmha_prefill_matches_fp32(cuda, hq, hk, page_size, new, prefix):
         torch.testing.assert_close(out[lo:hi].float(), ref, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("tile", [64, 128])
 @pytest.mark.parametrize("hq,hk", [(8, 2), (32, 8)])
-def test_fmha_prefill_rescales_rows_whose_maximum_moves_late(cuda, hq, hk):
+def test_fmha_prefill_rescales_rows_whose_maximum_moves_late(cuda, hq, hk, tile):
     """Keys that grow with their position: the running maximum of a row outgrows its lazy reference by more than 2^8 at
     some later KV tile, at a different tile for different rows of a warp, so the pass that rescales O in TMEM runs with
     only some of the warp's rows moving (the pass itself must run for the whole warp: `tcgen05.ld` / `st` are
@@ -81,11 +83,13 @@ def test_fmha_prefill_rescales_rows_whose_maximum_moves_late(cuda, hq, hk):
     cu = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=cuda)
     q = bf(torch.randn(int(cu[-1]), hq * d, device=cuda))
     seq_lens = torch.tensor(lens, dtype=torch.int32, device=cuda)
-    # the premise: scores (log2 domain) whose per-tile maxima differ by more than 8 between tiles, row by row
-    s0 = (q[:8].view(8, hq, d)[:, 0].float() @ ks[0][:, 0].float().T) * (d ** -0.5) * 1.4427
-    tiles = s0[:, :512].view(8, 4, 128).max(-1).values
-    assert bool(((tiles[:, 1:] - tiles[:, :-1]).abs() > 8).any())
-    out = A.fmha_prefill(q, pool, table, seq_lens, hq, cu)
+    # the premise: for the first 32 query rows of sequence 0 (one warp's rows; all of the 512-token prefix is visible to
+    # them), the KV tile at which the running maximum first exceeds the first tile's by 8 (log2 domain) differs by row
+    s0 = (q[:32].view(32, hq, d)[:, 0].float() @ ks[0][:512, 0].float().T) * (d ** -0.5) * 1.4427
+    run = torch.cummax(s0.view(32, 4, 128).max(-1).values, dim=1).values
+    first_move = ((run - run[:, :1]) > 8).float().argmax(1)                 # 0: never within these four tiles
+    assert len(set(first_move.tolist())) >= 2, first_move.tolist()
+    out = A.fmha_prefill(q, pool, table, seq_lens, hq, cu, tile=tile)
     torch.cuda.synchronize()
     Kernels.get(cuda).check_error()
     for s in range(len(lens)):
