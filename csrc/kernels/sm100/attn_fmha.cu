@@ -21,7 +21,8 @@
 // tensor map with 64-column boxes; block_table, seq_lens, cu_q, the planner's work list).
 // The reference takes prefill attention as a prebuilt trtllm-gen FMHA blob (kernel_index/trtllm_fmha_*.toml); it has no
 // source counterpart.
-#include "common.cuh"
+#define KERN_ATTN_NO_ENTRIES
+#include "attn_paged.cu"      // attn_body: the token-parallel kernel that shares an SM with this one in the ragged entry
 
 namespace kern {
 
@@ -82,8 +83,9 @@ struct FmhaArgs {
   float scale_log2;
 };
 
+// `y`: the CTA's index into the work list (blockIdx.y unless the caller maps it)
 template <int D, int FN>
-KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a) {
+KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const int y) {
   using Cfg = FmhaCfg<D, FN>;
   constexpr int kStages = Cfg::kStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -108,9 +110,9 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = a.hq / a.hk;
-  if ((int)blockIdx.y >= *a.work_count) return;          // uniform per CTA, before any barrier or allocation
+  if (y >= *a.work_count) return;          // uniform per CTA, before any barrier or allocation
   if (*reinterpret_cast<volatile int*>(a.err) != 0) return;   // an earlier CTA (or kernel) gave up: the call is lost, do not wait again
-  const int seq = a.work[2 * blockIdx.y], blk = a.work[2 * blockIdx.y + 1];
+  const int seq = a.work[2 * y], blk = a.work[2 * y + 1];
   const int kvh = blockIdx.x;
   const int L = a.seq_lens[seq];
   const int row0_tok = a.cu_q[seq];
@@ -379,7 +381,7 @@ extern "C" __global__ void __launch_bounds__(192, 1)
                                 int page_size, int pool_pages, float scale_log2, int* err) {
   FmhaArgs a{q, out, block_table, seq_lens, cu_q, work, work_count, err, hq, hk, q_stride, out_stride, max_pages, page_size,
              pool_pages, scale_log2};
-  fmha_body<128, 128>(&kv_map, a);
+  fmha_body<128, 128>(&kv_map, a, (int)blockIdx.y);
 }
 
 extern "C" __global__ void __launch_bounds__(192, 2)
@@ -389,5 +391,32 @@ extern "C" __global__ void __launch_bounds__(192, 2)
                                     int page_size, int pool_pages, float scale_log2, int* err) {
   FmhaArgs a{q, out, block_table, seq_lens, cu_q, work, work_count, err, hq, hk, q_stride, out_stride, max_pages, page_size,
              pool_pages, scale_log2};
-  fmha_body<128, 64>(&kv_map, a);
+  fmha_body<128, 64>(&kv_map, a, (int)blockIdx.y);
+}
+
+// Both lists of a ragged call in one launch: the CTAs of this kernel (list p: prompt chunks, 64-token KV tiles) and of
+// the token-parallel mma.sync kernel (list d: decode rows, a two-stage ring) alternate in launch order while both
+// lists last. Either kind takes half an SM (113 KB / 84 KB of shared memory, 256 TMEM columns for this one, none for
+// the other), so a prompt tile's tensor-core work and softmax share the SM with a decode sequence's KV stream.
+// block = 192: a decode CTA retires its sixth warp at once. grid = (hk, at least count_p + count_d).
+extern "C" __global__ void __launch_bounds__(192, 2)
+    kern_attn_ragged_fmha_d128(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* q, __nv_bfloat16* out,
+                               const int* block_table, const int* seq_lens, const int* cu_q, const int* work_p,
+                               const int* count_p, const int* work_d, const int* count_d, int hq, int hk, int q_stride,
+                               int out_stride, int max_pages, int page_size, int pool_pages, float scale_log2, int* err) {
+  const int np = *count_p, nd = *count_d, m = np < nd ? np : nd;
+  const int y = blockIdx.y;
+  if (y >= np + nd) return;
+  const bool is_p = y < 2 * m ? !(y & 1) : np > nd;
+  const int idx = y < 2 * m ? (y >> 1) : y - m;
+  if (is_p) {
+    FmhaArgs a{q, out, block_table, seq_lens, cu_q, work_p, count_p, err, hq, hk, q_stride, out_stride, max_pages, page_size,
+               pool_pages, scale_log2};
+    fmha_body<128, 64>(&kv_map, a, idx);
+  } else {
+    if (threadIdx.x >= 160) return;          // the token-parallel kernel is written for five warps
+    AttnArgs a{q, out, nullptr, nullptr, block_table, seq_lens, cu_q, work_d, count_d, err, 0x7fffffff, hq, hk, q_stride,
+               out_stride, max_pages, page_size, 1, 1, pool_pages, scale_log2};
+    attn_body<128, false, 2>(&kv_map, a, idx);
+  }
 }

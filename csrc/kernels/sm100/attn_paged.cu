@@ -81,7 +81,7 @@ KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a, const i
   constexpr int kStages = Cfg::kStages;
   constexpr int NT = PREFILL ? 8 : 2;        // 8-token n-tiles of S per warp per KV tile
   constexpr int ROWS = PREFILL ? 64 : 16;    // query rows per CTA
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   uint8_t* stages = smem;
@@ -380,6 +380,7 @@ KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a, const i
 
 }  // namespace kern
 
+#ifndef KERN_ATTN_NO_ENTRIES      // a file that includes this one for attn_body alone defines it
 using namespace kern;
 
 #define KERN_ATTN_ENTRY(name, D, PREFILL)                                                        \
@@ -578,3 +579,4 @@ extern "C" __global__ void __launch_bounds__(128)
         reinterpret_cast<const uint4*>(sb + (size_t)blk * page_size * d)[v];
   }
 }
+#endif  // KERN_ATTN_NO_ENTRIES

@@ -417,6 +417,7 @@ CPU_KERNELS["kern_attn_fmha_prefill_d128"] = _attention_fmha
 CPU_KERNELS["kern_attn_fmha_prefill_d128_t64"] = _attention_fmha
 for _d in (64, 128):
     CPU_KERNELS[f"kern_attn_ragged_paged_d{_d}"] = _attention_ragged
+CPU_KERNELS["kern_attn_ragged_fmha_d128"] = _attention_ragged
 for _d in (16, 32, 64, 128, 256):
     CPU_KERNELS[f"kern_attn_prefill_paged_d{_d}"] = _attention(True)
     CPU_KERNELS[f"kern_attn_decode_paged_d{_d}"] = _attention(False)

@@ -337,29 +337,43 @@ def _kv_map(d: int, page_size: int, state_param: int) -> dict:
         "swizzle": 128, "l2_promotion": 256}}]}}
 
 
-def fmha_prefill(hq: int, hk: int, d: int) -> bool:
-    """Whether the many-row list of a ragged call goes to the tcgen05 kernel (attn_fmha.cu): head_dim 128, a group size
-    that divides its 128-row tile, and `KERN_B200_FMHA=1` in the environment. Off by default: the kernel passes its
-    numerics tests (grids of one wave), but a serving step of the 8B decoder, whose attention grids run several waves
-    of CTAs per SM, did not finish with it, and the cause has not been found by reading the code."""
+def attn_mode(hq: int, hk: int, d: int) -> str:
+    """How a ragged call's attention runs (`KERN_B200_ATTN`, for A/B):
+    `ragged`  one launch, the mma.sync causal kernel's CTAs next to the token-parallel kernel's (head_dim 64 / 128; default);
+    `fmha`    one launch, the tcgen05 causal kernel's CTAs (64-token KV tiles) next to the token-parallel kernel's (head_dim 128);
+    `fmha2`   the tcgen05 causal kernel, then the token-parallel kernel (`KERN_B200_FMHA_TILE` = 64 | 128);
+    `two`     the mma.sync causal kernel, then the token-parallel kernel.
+    `KERN_B200_FMHA=1` reads as `fmha`, `KERN_B200_ATTN_RAGGED=0` as `two`."""
     import os
 
-    return d == 128 and 128 % (hq // hk) == 0 and os.environ.get("KERN_B200_FMHA", "0") == "1"
+    mode = os.environ.get("KERN_B200_ATTN")
+    if mode is None:
+        mode = "fmha" if os.environ.get("KERN_B200_FMHA", "0") == "1" else ("two" if os.environ.get("KERN_B200_ATTN_RAGGED", "1") == "0" else "ragged")
+    if mode in ("fmha", "fmha2") and not (d == 128 and 128 % (hq // hk) == 0):
+        mode = "ragged"
+    if mode == "ragged" and d not in (64, 128):
+        mode = "two"
+    if mode not in ("ragged", "fmha", "fmha2", "two"):
+        raise ValueError(f"KERN_B200_ATTN={mode!r}: expected ragged, fmha, fmha2 or two")
+    return mode
+
+
+def fmha_prefill(hq: int, hk: int, d: int) -> bool:
+    """Whether the many-row list of a ragged call goes to the tcgen05 kernel (attn_fmha.cu), whose blocks are 128 rows."""
+    return attn_mode(hq, hk, d) in ("fmha", "fmha2")
 
 
 def attn_ragged(d: int) -> bool:
-    """Whether a ragged call's two work lists run as one launch (head_dim 64 or 128; `KERN_B200_ATTN_RAGGED=0` keeps
-    the two launches, for A/B)."""
-    import os
-
-    return d in (64, 128) and os.environ.get("KERN_B200_ATTN_RAGGED", "1") != "0"
+    """Whether head_dim `d` has a one-launch form of the ragged call."""
+    return d in (64, 128)
 
 
 def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, q_stride: int) -> dict:
     """Ragged causal attention over the paged context.
     Interface [q(kv) buffer, kv state, out, block_table, seq_lens, cu_seqlens, work, work_count, err]."""
     g = hq // hk
-    fmha = fmha_prefill(hq, hk, d)
+    mode = attn_mode(hq, hk, d)
+    fmha = mode in ("fmha", "fmha2")
     tpb = (128 if fmha else 64) // g
     iface = ["in buffer<bf16>", "in state", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "in buffer<i32>",
              "in buffer<i32>", "in buffer<i32>", "out buffer<i32>"]
@@ -375,7 +389,21 @@ def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, 
 
     # many-row sequences: row-parallel causal kernel (on the 5th-generation tensor cores for head_dim 128); few-row
     # sequences (decode rows riding in the ragged call): token-parallel kernel, so their KV streams at full bandwidth
-    if fmha:
+    ragged_params = ["bytes<128>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "in buffer<i32>",
+                     "in buffer<i32>", "in buffer<i32>", "in buffer<i32>", "in buffer<i32>"] + ["i32"] * 7 + ["f32", "out buffer<i32>"]
+    ragged_args = [_kv_map(d, page_size, 1), {"param": 0}, {"param": 2}, {"param": 3}, {"param": 4}, {"param": 5}, {"param": 6},
+                   {"param": 7}, {"param": 9}, {"param": 10}, {"i32": hq}, {"i32": hk}, {"i32": q_stride}, {"i32": hq * d},
+                   {"i32": table_width}, {"i32": page_size}, {"i32": I32_MAX}, {"f32": (d ** -0.5) * 1.4426950408889634},
+                   {"param": 8}]
+    if mode == "fmha":
+        # both lists in one launch, the prompt rows on the 5th-generation tensor cores: a tcgen05 CTA (64-token KV tiles,
+        # 113 KB, 256 TMEM columns) and a token-parallel CTA share an SM
+        return {"params": iface, "impl": {"launches": [{
+            "module": "attn_fmha", "entry": "kern_attn_ragged_fmha_d128", "block": [192, 1, 1],
+            "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1],
+            "shared_mem": 768 + 128 * d * 2 + 128 * 64 * 2 + 2 * 2 * (64 * d * 2) + 256,
+            "params": ragged_params, "args": ragged_args}]}}
+    if mode == "fmha2":
         import os
 
         tile = int(os.environ.get("KERN_B200_FMHA_TILE", "64"))      # tokens per KV tile: 64 (two CTAs per SM) or 128
@@ -387,18 +415,13 @@ def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, 
                 "args": [_kv_map(d, page_size, 1), {"param": 0}, {"param": 2}, {"param": 3}, {"param": 4}, {"param": 5}, {"param": 6},
                          {"param": 7}, {"i32": hq}, {"i32": hk}, {"i32": q_stride}, {"i32": hq * d}, {"i32": table_width},
                          {"i32": page_size}, {"i32": I32_MAX}, {"f32": (d ** -0.5) * 1.4426950408889634}, {"param": 8}]}
-    elif attn_ragged(d):
+    elif mode == "ragged":
         # both lists in one launch: the two kernels' CTAs alternate, two per SM, so the decode rows' KV streams under
         # the prompt rows' tensor-core work (a sequence is on one list only, so the grid bound is unchanged)
         return {"params": iface, "impl": {"launches": [{
             "module": "attn_paged", "entry": f"kern_attn_ragged_paged_d{d}", "block": [160, 1, 1],
             "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1], "shared_mem": attn_smem(d, prefill=True),
-            "params": ["bytes<128>", "in buffer<bf16>", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "in buffer<i32>",
-                       "in buffer<i32>", "in buffer<i32>", "in buffer<i32>", "in buffer<i32>"] + ["i32"] * 7 + ["f32", "out buffer<i32>"],
-            "args": [_kv_map(d, page_size, 1), {"param": 0}, {"param": 2}, {"param": 3}, {"param": 4}, {"param": 5}, {"param": 6},
-                     {"param": 7}, {"param": 9}, {"param": 10}, {"i32": hq}, {"i32": hk}, {"i32": q_stride}, {"i32": hq * d},
-                     {"i32": table_width}, {"i32": page_size}, {"i32": I32_MAX}, {"f32": (d ** -0.5) * 1.4426950408889634},
-                     {"param": 8}]}]}}
+            "params": ragged_params, "args": ragged_args}]}}
     else:
         many = {"module": "attn_paged", "entry": f"kern_attn_prefill_paged_d{d}", "block": [160, 1, 1],
                 "grid": [hk, {"add": [{"ceil_div": ["tokens", tpb]}, "seqs"]}, 1], "shared_mem": attn_smem(d, prefill=True),

@@ -142,11 +142,12 @@ def fmha_smem(d: int, tile: int) -> int:
 
 def ragged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor, hq: int,
                      cu_q: torch.Tensor, *, out: torch.Tensor | None = None, seqs: int | None = None,
-                     scale: float | None = None, one_launch: bool = True) -> torch.Tensor:
+                     scale: float | None = None, one_launch: bool = True, fmha: bool = False) -> torch.Tensor:
     """A ragged call (prompt chunks and decode rows together) as a model's `attn_prefill` op runs it: the planner
     splits the sequences by their row count into the row-parallel causal kernel's list and the token-parallel kernel's
     list, and either one launch runs both kernels' CTAs side by side (`kern_attn_ragged_paged_d*`, head_dim 64 / 128)
-    or two launches run one after the other."""
+    or two launches run one after the other. `fmha` (head_dim 128, one launch): the prompt rows' CTAs are the tcgen05
+    kernel's (`kern_attn_ragged_fmha_d128`, blocks of 128 rows)."""
     k = Kernels.get(q.device)
     pages, _, hk, page_size, d = pool.shape
     g = hq // hk
@@ -154,7 +155,8 @@ def ragged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Ten
     n_seqs = block_table.shape[0] if seqs is None else seqs
     if out is None:
         out = torch.empty(q.shape[0], hq * d, dtype=torch.bfloat16, device=q.device)
-    tpb, tpd = 64 // g, max(1, 16 // g)
+    assert not fmha or (one_launch and d == 128 and 128 % g == 0)
+    tpb, tpd = (128 if fmha else 64) // g, max(1, 16 // g)
     items = (q.shape[0] + tpb - 1) // tpb + n_seqs
     work_p = torch.empty(2 * items, dtype=torch.int32, device=q.device)
     work_d = torch.empty(2 * items, dtype=torch.int32, device=q.device)
@@ -167,10 +169,11 @@ def ragged_attention(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Ten
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
     common = [i32(hq), i32(hk), i32(q.stride(0)), i32(out.stride(0)), i32(block_table.shape[1]), i32(page_size)]
     if one_launch:
-        k.launch("attn_paged", f"kern_attn_ragged_paged_d{d}", (hk, items, 1), (160,),
+        k.launch("attn_fmha" if fmha else "attn_paged", "kern_attn_ragged_fmha_d128" if fmha else f"kern_attn_ragged_paged_d{d}",
+                 (hk, items, 1), (192 if fmha else 160,),
                  [kv_map, ptr(q), ptr(out), ptr(block_table), ptr(seq_lens), ptr(cu_q), ptr(work_p), ptr(count), ptr(work_d),
                   ptr(count[1:])] + common + [i32(pages), f32(scale * 1.4426950408889634), ptr(k.err_word())],
-                 shared_mem=_attn_smem(d, True))
+                 shared_mem=fmha_smem(d, 64) if fmha else _attn_smem(d, True))
         return out
     for prefill, work, cnt, gy in ((True, work_p, count, items), (False, work_d, count[1:], n_seqs)):
         k.launch("attn_paged", f"kern_attn_{'prefill' if prefill else 'decode'}_paged_d{d}", (hk, gy, 1), (160,),

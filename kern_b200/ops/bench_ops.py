@@ -301,10 +301,10 @@ def bench_attn_ragged(a):
     lens = torch.tensor([a.rows] + [a.ctx] * a.seqs, dtype=torch.int32, device="cuda")
     cu = torch.tensor([0] + [a.rows + i for i in range(a.seqs + 1)], dtype=torch.int32, device="cuda")
     out = torch.empty_like(q)
-    ms = timeit(lambda: ragged_attention(q, pool, table, lens, a.hq, cu, out=out, one_launch=not a.two_launches), a.iters)
+    ms = timeit(lambda: ragged_attention(q, pool, table, lens, a.hq, cu, out=out, one_launch=not a.two_launches, fmha=a.fmha), a.iters)
     Kernels.get().check_error()
     kv_bytes = a.seqs * a.ctx * 2 * a.hk * a.d * 2
-    report("attn_ragged_two_launches" if a.two_launches else "attn_ragged_one_launch", ms, nbytes=kv_bytes,
+    report("attn_ragged_two_launches" if a.two_launches else ("attn_ragged_one_launch_tcgen05" if a.fmha else "attn_ragged_one_launch"), ms, nbytes=kv_bytes,
            flops=4.0 * a.hq * a.d * a.rows * (a.rows + 1) / 2, prompt_rows=a.rows, decode_seqs=a.seqs, ctx=a.ctx)
 
 
@@ -357,6 +357,7 @@ def main(argv=None):
     rg.add_argument("--seqs", type=int, default=256); rg.add_argument("--hq", type=int, default=32); rg.add_argument("--hk", type=int, default=8)
     rg.add_argument("--d", type=int, default=128); rg.add_argument("--page", type=int, default=64); rg.add_argument("--rows", type=int, default=2304)
     rg.add_argument("--ctx", type=int, default=2432); rg.add_argument("--two-launches", action="store_true")
+    rg.add_argument("--fmha", action="store_true", help="the prompt rows' CTAs on the tcgen05 kernel (head_dim 128)")
     ml = sub.add_parser("mla_decode")
     ml.add_argument("--seqs", type=int, default=64); ml.add_argument("--ctx", type=int, default=8192)
     ml.add_argument("--heads", type=int, default=16); ml.add_argument("--page", type=int, default=64)

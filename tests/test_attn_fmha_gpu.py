@@ -113,7 +113,7 @@ def test_dense_decoder_with_head_dim_128_uses_the_tcgen05_prefill_kernel(cuda, m
     cfg = dataclasses.replace(dense.TINY, name="tiny-d128", head_dim=128, heads=8, kv_heads=2, hidden=256, max_tokens=512,
                               max_context=512, page_size=64)
     doc = dense.build_manifest(cfg)
-    assert doc["ops"]["attn_prefill"]["impl"]["launches"][0]["entry"] == "kern_attn_fmha_prefill_d128"
+    assert doc["ops"]["attn_prefill"]["impl"]["launches"][0]["entry"] == "kern_attn_ragged_fmha_d128"
     w = dense.random_weights(cfg, seed=0, std=0.05)
     rt = Runtime(doc, tokens=cfg.page_size * 40)
     rt.load_tensors(lambda name: w[name].cuda())
@@ -139,3 +139,32 @@ def test_dense_decoder_with_head_dim_128_uses_the_tcgen05_prefill_kernel(cuda, m
     logits = rt.tensor("logits")[:3].float()
     for i in range(3):
         assert float((logits[i] - refs[i]).abs().max()) < 0.12
+
+
+@pytest.mark.parametrize("hq,hk,page_size", [(32, 8, 64), (8, 2, 16), (4, 4, 128)])
+def test_ragged_attention_with_tcgen05_prompt_rows(cuda, hq, hk, page_size):
+    """Prompt chunks (the tcgen05 kernel's CTAs) and decode rows (the token-parallel kernel's CTAs) in one launch,
+    against the fp32 statement; more decode sequences than prompt blocks and the reverse."""
+    from kern_b200.ops import attention as A
+    from kern_b200.ops.launcher import Kernels
+
+    d = 128
+    torch.manual_seed(17)
+    small = max(1, 16 // (hq // hk))
+    for new, prefix in (([300, 1, 1, small, 70, 1, 1, 1, 1, 1, 1, 1], [0, 500, 63, 200, 64, 1, 127, 128, 129, 900, 31, 5]),
+                        ([1, 257, 130, 5, 64], [40, 300, 0, 17, 64])):
+        lens = [n + p for n, p in zip(new, prefix)]
+        pool, table, ks, vs = _build_cache(cuda, lens, hk, d, page_size)
+        cu = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=cuda)
+        wide = bf(torch.randn(int(cu[-1]), (hq + 2 * hk) * d, device=cuda))
+        q = wide[:, : hq * d]
+        seq_lens = torch.tensor(lens, dtype=torch.int32, device=cuda)
+        out = A.ragged_attention(q, pool, table, seq_lens, hq, cu, fmha=True)
+        torch.cuda.synchronize()
+        Kernels.get(cuda).check_error()
+        for s in range(len(lens)):
+            lo, hi = int(cu[s]), int(cu[s + 1])
+            qs = q[lo:hi].reshape(hi - lo, hq, d)
+            pos = torch.arange(prefix[s], lens[s], device=cuda)
+            ref = A.attention_reference(qs, ks[s], vs[s], pos)
+            torch.testing.assert_close(out[lo:hi].float(), ref, rtol=2e-2, atol=2e-2)
