@@ -48,6 +48,7 @@ KERN_DEVICE uint32_t kv_off(int tok, int chunk) {
 // Prefill with head_dim <= 128 runs a two-stage ring so that two CTAs (eight math warps) fit one SM: the row-parallel
 // kernel is bound by mma.sync issue, not by the depth of its KV ring; decode keeps the deep ring (it is bandwidth-bound).
 // ST > 0 fixes the depth of the ring (the ragged entry runs both kernels' CTAs side by side at two stages each).
+constexpr int kAttnThreads = 160;     // the body's five warps, whatever block it runs in (a host kernel may have more and retire them)
 template <int D, bool PREFILL = false, int ST = 0>
 struct AttnCfg {
   static constexpr int kTileBytes = TK * D * 2;         // one of K or V
@@ -140,7 +141,7 @@ KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a, const i
   const int ntiles = tile_hi - tile_lo;
 
   // ---- q tile -> shared (all 5 warps help) ----
-  for (int i = threadIdx.x; i < ROWS * (D / 8); i += blockDim.x) {
+  for (int i = threadIdx.x; i < ROWS * (D / 8); i += kAttnThreads) {
     const int r = i / (D / 8), c = i % (D / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < valid_rows) {
@@ -330,7 +331,7 @@ KERN_DEVICE void attn_body(const CUtensorMap* kv_map, const AttnArgs& a, const i
       }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < 16 * D; i += blockDim.x) {
+    for (int i = threadIdx.x; i < 16 * D; i += kAttnThreads) {
       const int r = i / D, c = i % D;
       if (r >= valid_rows) continue;
       float m = -INFINITY;
