@@ -165,6 +165,57 @@ def prometheus_lines(recorder: Recorder, steps_by: dict | None = None) -> list[s
 
 
 # ---- kernel activity through CUPTI --------------------------------------------------------------------------------------
+def launch_plan(doc: dict, program: str, vars: dict[str, int]) -> list[dict]:
+    """The kernel launches one issue of `program` makes, in order, with the call they belong to: every launch of every
+    call's op whose `when` range admits the var's value. [{call, label, op, entry}] — what `fold` lines kernel records
+    up against. Reference counterpart: crates/kern-runtime/src/trace.rs:171-230 (launch tags)."""
+    out = []
+    for ci, c in enumerate(doc["programs"][program]["calls"]):
+        for l in doc["ops"][c["op"]]["impl"]["launches"]:
+            w = l.get("when")
+            if w is not None:
+                v = vars.get(w["var"])
+                if v is None or v < w.get("min", 1) or v > w.get("max", 1 << 62):
+                    continue
+            out.append({"call": ci, "label": c.get("label", ""), "op": c["op"], "entry": l["entry"]})
+    return out
+
+
+def fold(records: list[dict], issues: list[tuple[str, list[dict]]]) -> list[dict]:
+    """Attribute kernel activity records to (step, call): `issues` are the program issues in the order they were made,
+    each a (step tag, `launch_plan`), and `records` the kernels the device ran (any order; sorted here by start). A
+    plan's launches take the next records in order; a record whose kernel name does not contain the planned entry
+    (externs carry library names and are not checked) ends the folding with an error rather than mis-attributing the
+    rest. Returns one row per launch: step, call, label, op, entry, start_ns, end_ns, us.
+    Reference counterpart: crates/kern-runtime/src/trace.rs:232-283 (fold into steps)."""
+    recs = sorted(records, key=lambda r: r["start_ns"])
+    rows, at = [], 0
+    for step, plan in issues:
+        for l in plan:
+            if at >= len(recs):
+                raise ValueError(f"step {step}: the trace ends {len(plan)} launches short (at `{l['entry']}` of call `{l['label']}`)")
+            r = recs[at]
+            if not l["entry"].startswith("extern:") and l["entry"] not in r["name"]:
+                raise ValueError(f"step {step}: launch {at} is `{r['name']}`, the plan expected `{l['entry']}` (call `{l['label']}`)")
+            rows.append({"step": step, **l, "start_ns": r["start_ns"], "end_ns": r["end_ns"], "us": (r["end_ns"] - r["start_ns"]) / 1e3})
+            at += 1
+    return rows
+
+
+def by_call(rows: list[dict]) -> dict[str, dict]:
+    """Folded launches summed by op: {op: {launches, total_us, calls}} longest first (one step or many)."""
+    out: dict[str, dict] = {}
+    seen = set()
+    for r in rows:
+        d = out.setdefault(r["op"], {"launches": 0, "total_us": 0.0, "calls": 0})
+        d["launches"] += 1
+        d["total_us"] += r["us"]
+        if (r["step"], r["call"]) not in seen:
+            seen.add((r["step"], r["call"]))
+            d["calls"] += 1
+    return dict(sorted(out.items(), key=lambda kv: -kv[1]["total_us"]))
+
+
 class KernelTrace:
     """Every kernel this process launches while the trace is on, with its device start and end (CUPTI activity records,
     `csrc/runtime/cupti_trace.hpp`): no events around launches, graph replays included.

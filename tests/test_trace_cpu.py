@@ -69,3 +69,35 @@ def test_counters_sampler_reads_only(tmp_path):
     f = next(p for p in rec.rotate() if ".counters." in p.name)
     t = pq.ParquetFile(f).read().to_pydict()
     assert len(t["t_ns"]) >= 3 and set(t["sm_mhz"]) == {1965} and t["power_w"][0] == 612.0
+
+
+def test_kernel_records_fold_into_steps_and_calls():
+    """Kernel activity records attributed to (step, call) by the launch plan of each issue: `when` ranges pick the
+    launch an issue really makes, a name that does not match the plan stops the folding."""
+    import pytest
+
+    from kern_b200 import trace
+    from kern_b200.models import dense
+
+    doc = dense.build_manifest(dense.TOY)
+    plan1 = trace.launch_plan(doc, "decode", {"seqs": 1, "tokens": 1})
+    plan4 = trace.launch_plan(doc, "decode", {"seqs": 4, "tokens": 4})
+    assert len(plan1) == len(plan4) > 10
+    # one row: the weight-streaming kernel; four rows: a tensor-core tile (the op's `when` ranges)
+    e1 = {l["label"]: l["entry"] for l in plan1}
+    e4 = {l["label"]: l["entry"] for l in plan4}
+    assert e1["l0.qkv"].startswith("kern_gemv_bf16") and e4["l0.qkv"].startswith("kern_gem") and e1["l0.qkv"] != e4["l0.qkv"]
+    t, records = 1000, []
+    for plan in (plan1, plan4):
+        for l in plan:
+            records.append({"name": f"void {l['entry']}<...>(...)", "start_ns": t, "end_ns": t + 2000})
+            t += 2500
+    rows = trace.fold(list(reversed(records)), [("s0", plan1), ("s1", plan4)])
+    assert len(rows) == len(plan1) + len(plan4) and rows[0]["step"] == "s0" and rows[-1]["step"] == "s1"
+    assert all(r["us"] == 2.0 for r in rows)
+    ops = trace.by_call(rows)
+    assert ops["attn_decode"]["calls"] == 2 * dense.TOY.layers
+    with pytest.raises(ValueError, match="expected"):
+        trace.fold(records, [("s0", plan4), ("s1", plan1)])        # the plans in the wrong order: names disagree
+    with pytest.raises(ValueError, match="short"):
+        trace.fold(records[:5], [("s0", plan1)])
