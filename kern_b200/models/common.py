@@ -339,7 +339,9 @@ def _kv_map(d: int, page_size: int, state_param: int) -> dict:
 
 def attn_mode(hq: int, hk: int, d: int) -> str:
     """How a ragged call's attention runs (`KERN_B200_ATTN`, for A/B):
-    `ragged`  one launch, the mma.sync causal kernel's CTAs next to the token-parallel kernel's (head_dim 64 / 128; default);
+    `auto`    (default for head_dim 128) by the call's sequence count: up to `FMHA_SEQS` sequences — prompt chunks with few or
+              no decode rows beside them, where the causal kernel is the whole cost — as `fmha2`, more as `ragged`;
+    `ragged`  one launch, the mma.sync causal kernel's CTAs next to the token-parallel kernel's (head_dim 64 / 128);
     `fmha`    one launch, the tcgen05 causal kernel's CTAs (64-token KV tiles) next to the token-parallel kernel's (head_dim 128);
     `fmha2`   the tcgen05 causal kernel, then the token-parallel kernel (`KERN_B200_FMHA_TILE` = 64 | 128);
     `two`     the mma.sync causal kernel, then the token-parallel kernel.
@@ -348,18 +350,21 @@ def attn_mode(hq: int, hk: int, d: int) -> str:
 
     mode = os.environ.get("KERN_B200_ATTN")
     if mode is None:
-        mode = "fmha" if os.environ.get("KERN_B200_FMHA", "0") == "1" else ("two" if os.environ.get("KERN_B200_ATTN_RAGGED", "1") == "0" else "ragged")
-    if mode in ("fmha", "fmha2") and not (d == 128 and 128 % (hq // hk) == 0):
+        mode = "fmha" if os.environ.get("KERN_B200_FMHA", "0") == "1" else ("two" if os.environ.get("KERN_B200_ATTN_RAGGED", "1") == "0" else "auto")
+    if mode in ("auto", "fmha", "fmha2") and not (d == 128 and 128 % (hq // hk) == 0):
         mode = "ragged"
     if mode == "ragged" and d not in (64, 128):
         mode = "two"
-    if mode not in ("ragged", "fmha", "fmha2", "two"):
-        raise ValueError(f"KERN_B200_ATTN={mode!r}: expected ragged, fmha, fmha2 or two")
+    if mode not in ("auto", "ragged", "fmha", "fmha2", "two"):
+        raise ValueError(f"KERN_B200_ATTN={mode!r}: expected auto, ragged, fmha, fmha2 or two")
     return mode
 
 
+FMHA_SEQS = 8      # `auto`: calls of up to this many sequences take the tcgen05 causal kernel
+
+
 def fmha_prefill(hq: int, hk: int, d: int) -> bool:
-    """Whether the many-row list of a ragged call goes to the tcgen05 kernel (attn_fmha.cu), whose blocks are 128 rows."""
+    """Whether every ragged call's many-row list goes to the tcgen05 kernel (attn_fmha.cu), whose blocks are 128 rows."""
     return attn_mode(hq, hk, d) in ("fmha", "fmha2")
 
 
@@ -373,6 +378,26 @@ def attn_prefill_op(hq: int, hk: int, d: int, page_size: int, table_width: int, 
     Interface [q(kv) buffer, kv state, out, block_table, seq_lens, cu_seqlens, work, work_count, err]."""
     g = hq // hk
     mode = attn_mode(hq, hk, d)
+    if mode == "auto":
+        # few sequences: the tcgen05 causal kernel, then the token-parallel kernel for whatever decode rows there are;
+        # many: the one-launch form whose decode CTAs stream KV next to the mma.sync prompt CTAs
+        import os
+
+        few = {"var": "seqs", "max": FMHA_SEQS}
+        saved = os.environ.get("KERN_B200_ATTN")
+        try:
+            os.environ["KERN_B200_ATTN"] = "fmha2"
+            a = attn_prefill_op(hq, hk, d, page_size, table_width, q_stride)
+            os.environ["KERN_B200_ATTN"] = "ragged"
+            b = attn_prefill_op(hq, hk, d, page_size, table_width, q_stride)
+        finally:
+            if saved is None:
+                os.environ.pop("KERN_B200_ATTN", None)
+            else:
+                os.environ["KERN_B200_ATTN"] = saved
+        launches = [dict(l, when=few) for l in a["impl"]["launches"]] + \
+                   [dict(l, when={"var": "seqs", "min": FMHA_SEQS + 1}) for l in b["impl"]["launches"]]
+        return {"params": a["params"], "impl": {"launches": launches}}
     fmha = mode in ("fmha", "fmha2")
     tpb = (128 if fmha else 64) // g
     iface = ["in buffer<bf16>", "in state", "out buffer<bf16>", "in buffer<i32>", "in buffer<i32>", "in buffer<i32>",
@@ -476,14 +501,27 @@ def attn_plan_op(hq: int, hk: int, seqs_max: int, d: int = 0) -> dict:
     work list. A call passes ``{"var": "seqs"}`` and ``attn_plan_items(...)``. `d`: the head_dim, which decides the
     block of the many-row list (the tcgen05 kernel's tile is 128 rows)."""
     g = hq // hk
-    tpb, tpd = (128 if fmha_prefill(hq, hk, d) else 64) // g, max(1, 16 // g)
+    tpd = max(1, 16 // g)
+    mode = attn_mode(hq, hk, d)
+
+    def plan(tpb: int, when: dict | None) -> dict:
+        l = {"module": "attn_paged", "entry": "kern_attn_plan", "block": [256, 1, 1], "grid": [1, 1, 1],
+             "params": ["in buffer<i32>", "i32", "i32", "i32", "i32", "out buffer<i32>", "out buffer<i32>", "i32",
+                        "out buffer<i32>", "out buffer<i32>", "i32"],
+             "args": [{"param": 0}, {"param": 3}, {"i32": tpb}, {"i32": tpd}, {"i32": tpd}, {"param": 1}, {"param": 2},
+                      {"param": 4}, {"param": 5}, {"param": 6}, {"param": 3}]}
+        if when:
+            l["when"] = when
+        return l
+
+    if mode == "auto" and seqs_max > FMHA_SEQS:
+        # the many-row list in blocks of the kernel that will read it: 128 rows for the tcgen05 kernel (few sequences),
+        # 64 for the mma.sync kernel
+        launches = [plan(128 // g, {"var": "seqs", "max": FMHA_SEQS}), plan(64 // g, {"var": "seqs", "min": FMHA_SEQS + 1})]
+    else:
+        launches = [plan((128 if mode in ("auto", "fmha", "fmha2") else 64) // g, None)]
     return {"params": ["in buffer<i32>", "out buffer<i32>", "out buffer<i32>", "i32", "i32", "out buffer<i32>", "out buffer<i32>"],
-            "impl": {"launches": [{
-                "module": "attn_paged", "entry": "kern_attn_plan", "block": [256, 1, 1], "grid": [1, 1, 1],
-                "params": ["in buffer<i32>", "i32", "i32", "i32", "i32", "out buffer<i32>", "out buffer<i32>", "i32",
-                           "out buffer<i32>", "out buffer<i32>", "i32"],
-                "args": [{"param": 0}, {"param": 3}, {"i32": tpb}, {"i32": tpd}, {"i32": tpd}, {"param": 1}, {"param": 2},
-                         {"param": 4}, {"param": 5}, {"param": 6}, {"param": 3}]}]}}
+            "impl": {"launches": launches}}
 
 
 def attn_plan_items(hq: int, hk: int) -> dict:
