@@ -305,7 +305,7 @@ def test_native_runner_executes_manifests_without_python(cuda, tmp_path):
         got = run(path, prompt, 6, ("--chunk", "4"))
         assert got["tokens"] == toy_int.generate(prompt, 6, lined), (lined, got)
         assert got["launches"] > 0
-    cfg = dense.TOY
+    cfg = dense.TINY
     w = dense.random_weights(cfg, seed=3, std=0.08)
     save_file({k: v.contiguous() for k, v in w.items()}, str(tmp_path / "model.safetensors"))
     doc = dense.build_manifest(cfg)
