@@ -443,6 +443,26 @@ def cmd_server(args) -> int:
 
     setup_logging()
     tok = HFTokenizer(args.tokenizer) if args.tokenizer else ByteTokenizer()
+    if getattr(args, "pp", 1) > 1:
+        # a pipeline of stage processes: this process is the head (stage 0), the manifest is cut at layer boundaries
+        from .serve import launch
+
+        if args.model:
+            from .models import registry
+
+            cfg, build, _load, _make = registry.resolve(args.model)
+            doc = build(cfg)
+        else:
+            doc = json.loads(Path(args.manifest).read_text())
+        spec = {"manifest": doc, "weights": args.weights, "model": args.model, "cpu": args.cpu, "tokens": args.capacity or 0,
+                "slots": args.max_seqs or 0}
+        sched, pipe, procs = launch.launch_pp(spec, args.pp, chunk=args.chunk, max_seqs=args.max_seqs or None)
+        srv = Server(sched, tok, model_name=doc["model"], host=args.host, port=args.port)
+        try:
+            srv.serve_forever()
+        finally:
+            launch.shutdown_pp(pipe, procs)
+        return 0
     if args.world > 1:
         # rank processes (one per GPU) behind this head: one tensor-parallel group, or a data-parallel tier of them
         from .serve import launch
@@ -523,6 +543,7 @@ def main(argv=None) -> int:
     s.add_argument("--host", default="127.0.0.1"); s.add_argument("--port", type=int, default=8000); s.add_argument("--rows", type=int)
     s.add_argument("--world", type=int, default=1, help="rank processes (one per GPU)")
     s.add_argument("--tp", type=int, default=1, help="ranks per tensor-parallel group; world / tp groups form a data-parallel tier")
+    s.add_argument("--pp", type=int, default=1, help="pipeline stages (one process per GPU; this process is the head): the manifest is cut at layer boundaries")
     args = ap.parse_args(argv)
     if args.cmd in ("run", "test", "bench", "server", "e2e-logits", "gate"):
         path, cfg = find_config()

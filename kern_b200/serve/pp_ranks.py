@@ -481,3 +481,44 @@ class Pipeline:
                 self._collect(self.k - 1)
             self._announce(Item(k=self.k, program="", vars={}, columns={}, stop=True))
         self.stage.drain()
+
+
+class HeadEngine:
+    """The engine interface (open / close / step, `.pool`, bounds) over a `Pipeline`, for the scheduler that runs in the
+    head's process: a step is one announced item; a step whose tokens nobody wants (`read=False`: unfinished prompt
+    chunks) is not waited for, so a long prompt's chunks follow one another through the stages.
+    Prefix checkpoints copy pages on every stage's own pool: not carried over the pipeline, so the scheduler above runs
+    with `prefix_cache=False`."""
+
+    class _NoCopies:
+        def run_copies(self, copies: dict) -> None:
+            if copies.get("pages") or copies.get("slot") is not None:
+                raise NotImplementedError("page copies are not carried over a pipeline: run its scheduler with prefix_cache=False")
+
+        def zero_slot(self, slot: int) -> None:
+            raise NotImplementedError("per-sequence state slots are not zeroed over a pipeline yet")
+
+    def __init__(self, pipe: Pipeline):
+        self.pipe, self.p, self.pool, self.unit = pipe, pipe.p, pipe.pool, pipe.unit
+        self.rt = self._NoCopies()
+        self.rows_max, self.groups_max = self.p["rows"]["max"], self.p["groups"]["max"]
+        self.forwards, self.page_tables = self.p["forwards"], self.p["page_tables"]
+        self.steps = 0
+
+    def open(self, tokens_capacity: int, sampling=None):
+        return self.pipe.open(tokens_capacity, sampling)
+
+    def close(self, seq) -> None:
+        seq.lease.release()
+
+    def step(self, batch, eager: bool = False, read: bool = True, timed: bool = False, pad: int = 0, round: bool = False):
+        if not batch or sum(len(t) for _, t in batch) == 0:
+            return []
+        k = self.pipe.submit(batch, pad=pad, round=round)
+        self.steps += 1
+        if not read:
+            return None
+        toks = self.pipe.tokens(k)
+        for old in [x for x in self.pipe.results if x < k]:       # reports of calls nobody read
+            del self.pipe.results[old]
+        return toks[: len(batch)] if toks is not None else None

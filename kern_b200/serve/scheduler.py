@@ -249,8 +249,14 @@ class Scheduler:
         if plan is None:
             return []
         for pre in plan.get("pre", []):
-            pre["toks"] = self.eng.step(pre["batch"])
-        return self.finish(plan, self.eng.step(plan["batch"], pad=plan["pad"], round=plan["round"]))
+            pre["toks"] = self.eng.step(pre["batch"], read=self._emits(pre["kinds"]))
+        return self.finish(plan, self.eng.step(plan["batch"], pad=plan["pad"], round=plan["round"], read=self._emits(plan["kinds"])))
+
+    def _emits(self, kinds) -> bool:
+        """Whether any token of this call is wanted: a decode row, or a chunk that completes its prompt. A call of
+        unfinished chunks only is issued without reading anything back, so the next chunk (or a pipeline's next item)
+        follows it without a host round trip."""
+        return any(kind != "prefill" or (self.prefill_emits and r.fed + n >= self._target(r)) for r, kind, n in kinds)
 
     def plan(self) -> dict | None:
         """Admit, then decide this step's call: {batch, kinds, pad, round}. None when there is nothing to run.

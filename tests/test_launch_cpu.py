@@ -31,3 +31,20 @@ def test_two_rank_processes_serve_exactly():
     finally:
         launch.shutdown(ex, procs)
     assert all(not p.is_alive() for p in procs)
+
+
+@pytest.mark.timeout(300)
+def test_pipeline_of_stage_processes_under_the_scheduler():
+    """`launch_pp`: the launching process is the head, the second stage a process of its own (gloo, host-memory runtimes);
+    chunked prompts and decode steps of several requests give the tokens of one engine."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-m", "kern_b200.serve.launch", "--stages", "2", "--cpu"], cwd=root, capture_output=True, text=True,
+                       timeout=280, env=dict(os.environ, PYTHONPATH=root))
+    assert p.returncode == 0, (p.stdout[-1500:], p.stderr[-3000:])
+    line = json.loads([l for l in p.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["ok"] and line["stages"] == 2 and line["tokens"] == 20
