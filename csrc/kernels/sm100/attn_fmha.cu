@@ -254,16 +254,30 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
       const uint32_t s_tmem = tmem_base + lane_addr + (j & 1) * FN;
       const int tok0 = j * FN;
       const bool diag = tok0 + FN - 1 > pos;                        // some column of the tile is above this row's limit
-      // pass 1: the row maximum of the tile
+      // pass 1: the row maximum of the tile. With 64-token tiles the row's 64 scores stay in registers for pass 2 (one
+      // read of S instead of two), and the S buffer is handed back to the MMA warp at once.
+      constexpr bool kKeep = FN <= 64;
+      uint32_t keep[kKeep ? FN : 1];
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < FN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_tmem + c * 32, r);
+      if constexpr (kKeep) {
+#pragma unroll
+        for (int c = 0; c < FN / 32; ++c) tmem_ld_32x32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&keep[c * 32]));
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (!diag || tok0 + c * 32 + i <= pos) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < FN; ++i)
+          if (!diag || tok0 + i <= pos) mx = fmaxf(mx, __uint_as_float(keep[i]));
+        tc_fence_before();
+        mbar_arrive(&s_empty[j & 1]);
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < FN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(s_tmem + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (!diag || tok0 + c * 32 + i <= pos) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
       }
       mx *= a.scale_log2;
       // lazy reference maximum: move it (and rescale O and l) only when the running maximum outgrew it by 2^8
@@ -296,11 +310,16 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
       // pass 2: exponentials -> P (bf16, K-major swizzled, the A operand of P V), row sum
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
       float sum = 0.f;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < FN / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32(s_tmem + c * 32, r);
-        tmem_ld_wait();
+        if constexpr (kKeep) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = keep[c * 32 + i];
+        } else {
+          tmem_ld_32x32(s_tmem + c * 32, r);
+          tmem_ld_wait();
+        }
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -321,7 +340,7 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
       l_run += sum;
       tc_fence_before();
       fence_proxy_async();
-      mbar_arrive(&s_empty[j & 1]);
+      if constexpr (!kKeep) mbar_arrive(&s_empty[j & 1]);
       mbar_arrive(p_full);
     }
     // ---- epilogue: O / l -> out ----
