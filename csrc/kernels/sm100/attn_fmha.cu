@@ -389,6 +389,295 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
   }
 }
 
+
+// ---- context attention over contiguous ragged K / V with unequal head dims (qk 192 / v 128) -------------------------------
+// The prefill of a latent-attention (MLA) layer in its un-absorbed form: every head has its own keys (128 up-projected
+// columns + 64 shared positional ones = 192) and values (128), freshly computed for the call, so K and V are plain
+// ragged tensors [kv tokens][heads * dim], not pages. One CTA = (head, sequence, block of 128 query tokens); S = Q K^T
+// over 192, O += P V over 128 columns, the same pipeline as above with 64-token KV tiles (256 TMEM columns).
+// A query token i of a sequence with R new rows and L keys attends keys 0 .. L - R + i.
+// Reference bar: kernel_index/trtllm_fmha_ctx_h192_v128.toml (a prebuilt blob there; no source counterpart).
+struct CtxArgs {
+  const __nv_bfloat16* q;       // [q tokens][q_stride], head h at column h * DQK
+  __nv_bfloat16* out;           // [q tokens][out_stride], head h at column h * DV
+  const int* cu_q;              // [seqs + 1]
+  const int* cu_k;              // [seqs + 1]
+  const int* work;
+  const int* work_count;
+  int* err;
+  int q_stride, out_stride;
+  float scale_log2;
+};
+
+// ST: stages of the K / V ring. 2: one CTA per SM (146 KB), the next tile's scores are issued before this tile's P V.
+// 1: 106 KB, two CTAs per SM, each strictly load -> S -> softmax -> P V, overlapping one another.
+template <int DQK, int DV, int FN, int ST>
+struct CtxCfg {
+  static constexpr int kQBytes = FM * DQK * 2;
+  static constexpr int kPBytes = FM * FN * 2;
+  static constexpr int kKBytes = FN * DQK * 2;
+  static constexpr int kVBytes = FN * DV * 2;
+  static constexpr int kStages = ST;
+  static constexpr int kSlack = ST == 1 ? 768 : 1024;
+  static constexpr int kSmem = kSlack + kQBytes + kPBytes + kStages * (kKBytes + kVBytes) + 256;
+  static constexpr int kTmemCols = 2 * FN + DV <= 256 ? 256 : 512;
+};
+
+template <int DQK, int DV, int FN, int ST>
+KERN_DEVICE void fmha_ctx_body(const CUtensorMap* k_map, const CUtensorMap* v_map, const CtxArgs& a) {
+  using Cfg = CtxCfg<DQK, DV, FN, ST>;
+  constexpr int kStages = Cfg::kStages;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if ((int)(smem - smem_raw) > Cfg::kSlack) {             // uniform per CTA, before any barrier or allocation
+    if (threadIdx.x == 0) set_error(a.err, ERR_BOUNDS);
+    return;
+  }
+  uint8_t* q_s = smem;
+  uint8_t* p_s = q_s + Cfg::kQBytes;
+  uint8_t* kv_s = p_s + Cfg::kPBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + kStages * (Cfg::kKBytes + Cfg::kVBytes));
+  uint64_t* kv_full = bars;
+  uint64_t* kv_empty = bars + kStages;
+  uint64_t* s_full = kv_empty + kStages;
+  uint64_t* s_empty = s_full + 2;
+  uint64_t* p_full = s_empty + 2;
+  uint64_t* p_empty = p_full + 1;
+  uint64_t* o_full = p_empty + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int y = blockIdx.y, head = blockIdx.x;
+  if (y >= *a.work_count) return;                           // uniform per CTA, before any barrier or allocation
+  if (*reinterpret_cast<volatile int*>(a.err) != 0) return;
+  const int seq = a.work[2 * y], blk = a.work[2 * y + 1];
+  const int row0_tok = a.cu_q[seq], R = a.cu_q[seq + 1] - row0_tok;
+  const int k0 = a.cu_k[seq], L = a.cu_k[seq + 1] - k0;
+  const int tok_lo = blk * FM;
+  if (tok_lo >= R || L <= 0) return;
+  const int valid_rows = min(FM, R - tok_lo);
+  const int last_pos = min(L - 1, L - R + tok_lo + valid_rows - 1);
+  if (last_pos < 0) return;                                 // more new rows than keys: these rows see nothing (left as they are)
+  const int ntiles = last_pos / FN + 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 128); }
+    mbar_init(p_full, 128);
+    mbar_init(p_empty, 1);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(k_map);
+    tma_prefetch_desc(v_map);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  // Q tile -> shared memory, K-major with the 128-byte swizzle (DQK / 64 column blocks of [128 rows][128 bytes])
+  for (int i = threadIdx.x; i < FM * (DQK / 8); i += blockDim.x) {
+    const int r = i / (DQK / 8), c = i % (DQK / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < valid_rows)
+      v = *reinterpret_cast<const uint4*>(a.q + (size_t)(row0_tok + tok_lo + r) * a.q_stride + (size_t)head * DQK + c * 8);
+    const int cb = c >> 3, cc = c & 7;
+    *reinterpret_cast<uint4*>(q_s + cb * (FM * 128) + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+  }
+  fence_proxy_async();
+  __syncthreads();
+
+
+  if (warp == 0) {
+    // ---------------- producer: K (DQK / 64 boxes) and V (DV / 64 boxes) of every 64-token tile ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = 0; t < ntiles; ++t) {
+        if (!mbar_wait_ns(&kv_empty[stage], phase ^ 1, abort_flag)) {
+          set_error(a.err, ERR_WAIT_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        uint8_t* sk = kv_s + stage * (Cfg::kKBytes + Cfg::kVBytes);
+        uint8_t* sv = sk + Cfg::kKBytes;
+        mbar_expect_tx(&kv_full[stage], Cfg::kKBytes + Cfg::kVBytes);
+        const int krow = k0 + t * FN;                 // rows past the sequence's end belong to the next one (or are out of
+                                                      // range and read as zero): the causal limit masks them
+#pragma unroll
+        for (int cb = 0; cb < DQK / 64; ++cb) tma_load_2d(sk + cb * (FN * 128), k_map, head * DQK + cb * 64, krow, &kv_full[stage]);
+#pragma unroll
+        for (int cb = 0; cb < DV / 64; ++cb) tma_load_2d(sv + cb * (FN * 128), v_map, head * DV + cb * 64, krow, &kv_full[stage]);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(FM, FN);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(FM, DV) | (1u << 16);      // B (= V) is MN-major
+      const uint32_t o_tmem = tmem_base + 2 * FN;
+      bool ok = true;
+      auto issue_qk = [&](int j) {
+        const int stage = j % kStages;
+        if (!mbar_wait_ns(&kv_full[stage], (j / kStages) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
+        if (!mbar_wait_ns(&s_empty[j & 1], ((j >> 1) & 1) ^ 1, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_EMPTY); return false; }
+        tc_fence_after();
+        const uint32_t sq = smem_u32(q_s), sk = smem_u32(kv_s + stage * (Cfg::kKBytes + Cfg::kVBytes));
+#pragma unroll
+        for (int k = 0; k < DQK / 16; ++k)
+          umma_bf16(tmem_base + (j & 1) * FN, umma_desc_sw128(sq + (k >> 2) * (FM * 128) + (k & 3) * 32),
+                    umma_desc_sw128(sk + (k >> 2) * (FN * 128) + (k & 3) * 32), idesc_qk, k != 0);
+        tc_commit(&s_full[j & 1]);
+        return true;
+      };
+      auto issue_pv = [&](int j) {
+        const int stage = j % kStages;
+        if (!mbar_wait_ns(p_full, j & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
+        tc_fence_after();
+        const uint32_t sp = smem_u32(p_s), sv = smem_u32(kv_s + stage * (Cfg::kKBytes + Cfg::kVBytes) + Cfg::kKBytes);
+#pragma unroll
+        for (int k = 0; k < FN / 16; ++k)
+          umma_bf16(o_tmem, umma_desc_sw128(sp + (k >> 2) * (FM * 128) + (k & 3) * 32),
+                    umma_desc_sw128_mn(sv + k * 16 * 128, FN * 128), idesc_pv, (j | k) != 0);
+        tc_commit(&kv_empty[stage]);
+        tc_commit(p_empty);
+        if (j == ntiles - 1) tc_commit(o_full);
+        return true;
+      };
+      ok = issue_qk(0);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        if constexpr (kStages >= 2) {          // the next tile's scores first: they overlap this tile's softmax
+          if (j + 1 < ntiles) ok = issue_qk(j + 1);
+          if (ok) ok = issue_pv(j);
+        } else {                               // one stage: the next tile can only be loaded once this tile's P V has read V
+          ok = issue_pv(j);
+          if (ok && j + 1 < ntiles) ok = issue_qk(j + 1);
+        }
+      }
+      if (!ok) *abort_flag = 1;
+    }
+    __syncwarp();
+  } else {
+    // ---------------- softmax warps 2..5: one thread per query row (the scores of a 64-token tile stay in registers) ----------------
+    static_assert(FN == 64, "the context kernel keeps a tile's scores in registers");
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int pos = row < valid_rows ? (L - R + tok_lo + row) : -1;
+    float m_ref = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < ntiles && ok; ++j) {
+      if (!mbar_wait_ns(&s_full[j & 1], (j >> 1) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_FULL); *abort_flag = 1; ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_tmem = tmem_base + lane_addr + (j & 1) * FN;
+      const int tok0 = j * FN;
+      const bool diag = tok0 + FN - 1 > pos;
+      uint32_t keep[FN];
+#pragma unroll
+      for (int c = 0; c < FN / 32; ++c) tmem_ld_32x32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&keep[c * 32]));
+      tmem_ld_wait();
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < FN; ++i)
+        if (!diag || tok0 + i <= pos) mx = fmaxf(mx, __uint_as_float(keep[i]));
+      tc_fence_before();
+      mbar_arrive(&s_empty[j & 1]);
+      mx *= a.scale_log2;
+      float alpha = 1.f;
+      bool moved = false;
+      if (mx > m_ref + 8.f) {
+        alpha = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
+        m_ref = mx;
+        moved = true;
+      }
+      if (j > 0 && !mbar_wait_ns(p_empty, (j - 1) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_EMPTY); *abort_flag = 1; ok = false; break; }
+      tc_fence_after();
+      if (__any_sync(0xffffffffu, moved && j > 0)) {        // warp-wide instructions: never under a per-row branch
+        const uint32_t o_tmem = tmem_base + lane_addr + 2 * FN;
+#pragma unroll 1
+        for (int c = 0; c < DV / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(o_tmem + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_32x32(o_tmem + c * 32, r);
+        }
+        tmem_st_wait();
+      }
+      l_run *= alpha;
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < FN / 32; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int t = tok0 + c * 32 + 2 * i;
+          const float p0 = (!diag || t <= pos) ? exp2f(__uint_as_float(keep[c * 32 + 2 * i]) * a.scale_log2 - m_use) : 0.f;
+          const float p1 = (!diag || t + 1 <= pos) ? exp2f(__uint_as_float(keep[c * 32 + 2 * i + 1]) * a.scale_log2 - m_use) : 0.f;
+          sum += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = c * 4 + q, cb = chunk >> 3, cc = chunk & 7;
+          *reinterpret_cast<uint4*>(p_s + cb * (FM * 128) + row * 128 + ((cc ^ (row & 7)) << 4)) =
+              make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+        }
+      }
+      l_run += sum;
+      tc_fence_before();
+      fence_proxy_async();
+      mbar_arrive(p_full);
+    }
+    if (ok && !mbar_wait_ns(o_full, 0, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_FULL); *abort_flag = 1; ok = false; }
+    if (__all_sync(0xffffffffu, ok)) {
+      tc_fence_after();
+      const uint32_t o_tmem = tmem_base + lane_addr + 2 * FN;
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* dst = row < valid_rows ? a.out + (size_t)(row0_tok + tok_lo + row) * a.out_stride + (size_t)head * DV : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < DV / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(o_tmem + c * 32, r);
+        tmem_ld_wait();
+        if (dst != nullptr) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[v * 8]) * inv, __uint_as_float(r[v * 8 + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * inv, __uint_as_float(r[v * 8 + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * inv, __uint_as_float(r[v * 8 + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * inv, __uint_as_float(r[v * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o;
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0 && threadIdx.x == 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) { __nanosleep(1000); }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
 }  // namespace kern
 
 using namespace kern;
@@ -439,3 +728,16 @@ extern "C" __global__ void __launch_bounds__(192, 2)
     attn_body<128, false, 2>(&kv_map, a, idx);
   }
 }
+
+// grid = (heads, work items), block 192, dynamic shared memory CtxCfg<192, 128, 64, ST>::kSmem
+#define KERN_FMHA_CTX_ENTRY(name, ST, PER_SM)                                                                                  \
+  extern "C" __global__ void __launch_bounds__(192, PER_SM)                                                                    \
+      name(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, const __nv_bfloat16* q,        \
+           __nv_bfloat16* out, const int* cu_q, const int* cu_k, const int* work, const int* work_count, int q_stride,          \
+           int out_stride, float scale_log2, int* err) {                                                                       \
+    CtxArgs a{q, out, cu_q, cu_k, work, work_count, err, q_stride, out_stride, scale_log2};                                     \
+    fmha_ctx_body<192, 128, 64, ST>(&k_map, &v_map, a);                                                                        \
+  }
+
+KERN_FMHA_CTX_ENTRY(kern_attn_fmha_ctx_qk192_v128, 2, 1)
+KERN_FMHA_CTX_ENTRY(kern_attn_fmha_ctx_qk192_v128_x2, 1, 2)

@@ -217,6 +217,58 @@ def fmha_prefill(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
     return out
 
 
+def fmha_context(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_q: torch.Tensor, cu_k: torch.Tensor, heads: int, *,
+                 out: torch.Tensor | None = None, scale: float | None = None, two_per_sm: bool = True) -> torch.Tensor:
+    """Causal context attention over contiguous ragged K / V with a 192-wide q.k and 128-wide values: the prefill of a
+    latent-attention layer in its un-absorbed form (csrc/kernels/sm100/attn_fmha.cu, `kern_attn_fmha_ctx_qk192_v128`).
+    `q` [q tokens, heads * 192], `k` [kv tokens, heads * 192], `v` [kv tokens, heads * 128], bf16, rows of a sequence
+    contiguous (`cu_q`, `cu_k` cumulative counts, int32); query i of a sequence with R rows and L keys sees keys
+    0 .. L - R + i. Returns [q tokens, heads * 128]. `two_per_sm`: the one-stage form, two CTAs per SM."""
+    kk = Kernels.get(q.device)
+    dqk, dv, fn = 192, 128, 64
+    assert q.shape[1] == heads * dqk and k.shape[1] == heads * dqk and v.shape[1] == heads * dv
+    assert k.is_contiguous() and v.is_contiguous() and q.stride(1) == 1
+    n_seqs = cu_q.numel() - 1
+    if out is None:
+        out = torch.empty(q.shape[0], heads * dv, dtype=torch.bfloat16, device=q.device)
+    items = (q.shape[0] + 127) // 128 + n_seqs
+    work = torch.empty(2 * items, dtype=torch.int32, device=q.device)
+    count = torch.zeros(2, dtype=torch.int32, device=q.device)
+    kk.launch("attn_paged", "kern_attn_plan", (1,), (256,),
+              [ptr(cu_q), i32(n_seqs), i32(128), i32(1), i32(0), ptr(work), ptr(count), i32(items), ptr(work), ptr(count[1:]), i32(0)])
+    k_map = kk.tensor_map_2d(k, fn, 64)
+    v_map = kk.tensor_map_2d(v, fn, 64)
+    scale = (1.0 / math.sqrt(dqk)) if scale is None else scale
+    stages = 1 if two_per_sm else 2
+    smem = (768 if two_per_sm else 1024) + 128 * dqk * 2 + 128 * fn * 2 + stages * (fn * dqk * 2 + fn * dv * 2) + 256
+    kk.launch("attn_fmha", "kern_attn_fmha_ctx_qk192_v128" + ("_x2" if two_per_sm else ""), (heads, items, 1), (192,),
+              [k_map, v_map, ptr(q), ptr(out), ptr(cu_q), ptr(cu_k), ptr(work), ptr(count), i32(q.stride(0)), i32(out.stride(0)),
+               f32(scale * 1.4426950408889634), ptr(kk.err_word())], shared_mem=smem)
+    return out
+
+
+def context_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_q, cu_k, heads: int, scale: float | None = None) -> torch.Tensor:
+    """fp32 statement of `fmha_context`."""
+    dqk, dv = q.shape[1] // heads, v.shape[1] // heads
+    scale = (1.0 / math.sqrt(dqk)) if scale is None else scale
+    out = torch.zeros(q.shape[0], heads * dv, dtype=torch.float32, device=q.device)
+    for s in range(len(cu_q) - 1):
+        q0, q1, k0, k1 = int(cu_q[s]), int(cu_q[s + 1]), int(cu_k[s]), int(cu_k[s + 1])
+        R, L = q1 - q0, k1 - k0
+        if R <= 0 or L <= 0:
+            continue
+        qq = q[q0:q1].float().view(R, heads, dqk)
+        kk = k[k0:k1].float().view(L, heads, dqk)
+        vv = v[k0:k1].float().view(L, heads, dv)
+        sc = torch.einsum("rhd,lhd->hrl", qq, kk) * scale
+        limit = torch.arange(L - R, L, device=q.device)
+        mask = torch.arange(L, device=q.device)[None, :] <= limit[:, None]
+        sc = sc.masked_fill(~mask[None], float("-inf"))
+        pr = torch.softmax(sc, -1).nan_to_num(0.0)
+        out[q0:q1] = torch.einsum("hrl,lhd->rhd", pr, vv).reshape(R, heads * dv)
+    return out
+
+
 def new_partials(rows: int, hq: int, d: int, total: int, device) -> tuple[torch.Tensor, torch.Tensor]:
     """A workspace of `total` partial slots per (row, head), every slot neutral (m = -inf, l = 0): a rank whose share
     of a sequence is empty leaves its slots as they are."""

@@ -308,6 +308,26 @@ def bench_attn_ragged(a):
            flops=4.0 * a.hq * a.d * a.rows * (a.rows + 1) / 2, prompt_rows=a.rows, decode_seqs=a.seqs, ctx=a.ctx)
 
 
+def bench_attn_context(a):
+    """Context attention qk 192 / v 128 over contiguous K / V (un-absorbed latent-attention prefill): `seqs` sequences of
+    `rows` new rows each over `prefix` earlier keys, `heads` heads."""
+    from .attention import fmha_context
+    from .launcher import Kernels
+
+    L = a.prefix + a.rows
+    q = torch.randn(a.seqs * a.rows, a.heads * 192, device="cuda").to(torch.bfloat16)
+    k = (torch.randn(a.seqs * L, a.heads * 192, device="cuda") * 0.5).to(torch.bfloat16)
+    v = (torch.randn(a.seqs * L, a.heads * 128, device="cuda") * 0.5).to(torch.bfloat16)
+    cu_q = (torch.arange(a.seqs + 1, device="cuda") * a.rows).to(torch.int32)
+    cu_k = (torch.arange(a.seqs + 1, device="cuda") * L).to(torch.int32)
+    out = torch.empty(q.shape[0], a.heads * 128, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: fmha_context(q, k, v, cu_q, cu_k, a.heads, out=out, two_per_sm=not a.one_per_sm), a.iters)
+    Kernels.get().check_error()
+    keys = a.rows * a.prefix + a.rows * (a.rows + 1) / 2
+    report("attn_fmha_ctx_qk192_v128" + ("" if a.one_per_sm else "_x2"), ms, flops=2.0 * a.seqs * a.heads * (192 + 128) * keys,
+           seqs=a.seqs, rows=a.rows, prefix=a.prefix, heads=a.heads)
+
+
 def bench_norm(a):
     from .basic import rms_norm
 
@@ -358,16 +378,19 @@ def main(argv=None):
     rg.add_argument("--d", type=int, default=128); rg.add_argument("--page", type=int, default=64); rg.add_argument("--rows", type=int, default=2304)
     rg.add_argument("--ctx", type=int, default=2432); rg.add_argument("--two-launches", action="store_true")
     rg.add_argument("--fmha", action="store_true", help="the prompt rows' CTAs on the tcgen05 kernel (head_dim 128)")
+    cx = sub.add_parser("attn_context")
+    cx.add_argument("--seqs", type=int, default=2); cx.add_argument("--rows", type=int, default=4096); cx.add_argument("--prefix", type=int, default=0)
+    cx.add_argument("--heads", type=int, default=16); cx.add_argument("--one-per-sm", action="store_true", help="the two-stage form, one CTA per SM")
     ml = sub.add_parser("mla_decode")
     ml.add_argument("--seqs", type=int, default=64); ml.add_argument("--ctx", type=int, default=8192)
     ml.add_argument("--heads", type=int, default=16); ml.add_argument("--page", type=int, default=64)
     ml.add_argument("--splits", type=int, default=None)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=4096); n.add_argument("--n", type=int, default=4096)
-    for s in (g, d, p, n, g8, mo, gd, ml, gx, mx, rg):
+    for s in (g, d, p, n, g8, mo, gd, ml, gx, mx, rg, cx):
         s.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "gemm_mx": bench_gemm_mx, "moe_mx": bench_moe_mx, "gdn": bench_gdn, "gemm_fp8": bench_gemm_fp8, "moe": bench_moe, "attn_decode": bench_attn_decode, "mla_decode": bench_mla_decode, "attn_prefill": bench_attn_prefill, "attn_ragged": bench_attn_ragged, "norm": bench_norm}[a.op](a)
+    {"gemm": bench_gemm, "gemm_mx": bench_gemm_mx, "moe_mx": bench_moe_mx, "gdn": bench_gdn, "gemm_fp8": bench_gemm_fp8, "moe": bench_moe, "attn_decode": bench_attn_decode, "mla_decode": bench_mla_decode, "attn_prefill": bench_attn_prefill, "attn_ragged": bench_attn_ragged, "attn_context": bench_attn_context, "norm": bench_norm}[a.op](a)
 
 
 if __name__ == "__main__":

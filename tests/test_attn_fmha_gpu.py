@@ -168,3 +168,27 @@ def test_ragged_attention_with_tcgen05_prompt_rows(cuda, hq, hk, page_size):
             pos = torch.arange(prefix[s], lens[s], device=cuda)
             ref = A.attention_reference(qs, ks[s], vs[s], pos)
             torch.testing.assert_close(out[lo:hi].float(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("two_per_sm", [True, False])
+@pytest.mark.parametrize("heads,new,prefix", [(4, [128], [0]), (16, [5, 64, 130, 257], [0, 17, 64, 300]), (2, [700, 33], [1000, 0]), (8, [1, 200], [0, 0])])
+def test_fmha_context_qk192_v128_matches_fp32(cuda, heads, new, prefix, two_per_sm):
+    """Context attention with a 192-wide q.k and 128-wide values over contiguous ragged K / V (the un-absorbed prefill of a
+    latent-attention layer): ragged lengths, prefixes, tiles that run into the next sequence's rows and past the tensor's end."""
+    from kern_b200.ops import attention as A
+    from kern_b200.ops.launcher import Kernels
+
+    torch.manual_seed(23 + heads)
+    lens = [n + p for n, p in zip(new, prefix)]
+    cu_q = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=cuda)
+    cu_k = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=cuda)
+    q = bf(torch.randn(int(cu_q[-1]), heads * 192, device=cuda))
+    k = bf(torch.randn(int(cu_k[-1]), heads * 192, device=cuda) * 0.6)
+    v = bf(torch.randn(int(cu_k[-1]), heads * 128, device=cuda) * 0.5)
+    # keys that grow along one sequence: rows whose maximum moves at a later tile (the O rescale pass)
+    k[: lens[0]] = bf(k[: lens[0]].float() * torch.linspace(1.0, 6.0, lens[0], device=cuda)[:, None])
+    out = A.fmha_context(q, k, v, cu_q, cu_k, heads, two_per_sm=two_per_sm)
+    torch.cuda.synchronize()
+    Kernels.get(cuda).check_error()
+    ref = A.context_reference(q, k, v, cu_q, cu_k, heads)
+    torch.testing.assert_close(out.float(), ref, rtol=3e-2, atol=3e-2)
