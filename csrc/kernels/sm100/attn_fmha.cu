@@ -263,9 +263,17 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
 #pragma unroll
         for (int c = 0; c < FN / 32; ++c) tmem_ld_32x32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&keep[c * 32]));
         tmem_ld_wait();
+        if (diag) {       // the causal limit, once, on the scores themselves (a per-row branch: no warp-wide instruction inside)
 #pragma unroll
-        for (int i = 0; i < FN; ++i)
-          if (!diag || tok0 + i <= pos) mx = fmaxf(mx, __uint_as_float(keep[i]));
+          for (int i = 0; i < FN; ++i)
+            if (tok0 + i > pos) keep[i] = 0xff800000u;      // -inf
+        }
+        {
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: a single one is 64 dependent steps
+#pragma unroll
+          for (int i = 0; i < FN; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(keep[i]));
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        }
         tc_fence_before();
         mbar_arrive(&s_empty[j & 1]);
       } else {
@@ -309,7 +317,7 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
       l_run *= alpha;
       // pass 2: exponentials -> P (bf16, K-major swizzled, the A operand of P V), row sum
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      float sum = 0.f;
+      float sum = 0.f, sum_b = 0.f;
 #pragma unroll
       for (int c = 0; c < FN / 32; ++c) {
         uint32_t r[32];
@@ -324,9 +332,10 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int t = tok0 + c * 32 + 2 * i;
-          const float p0 = (!diag || t <= pos) ? exp2f(__uint_as_float(r[2 * i]) * a.scale_log2 - m_use) : 0.f;
-          const float p1 = (!diag || t + 1 <= pos) ? exp2f(__uint_as_float(r[2 * i + 1]) * a.scale_log2 - m_use) : 0.f;
-          sum += p0 + p1;
+          // (kept scores carry the causal limit already: a masked one is -inf and its exponential 0)
+          const float p0 = (kKeep || !diag || t <= pos) ? exp2f(__uint_as_float(r[2 * i]) * a.scale_log2 - m_use) : 0.f;
+          const float p1 = (kKeep || !diag || t + 1 <= pos) ? exp2f(__uint_as_float(r[2 * i + 1]) * a.scale_log2 - m_use) : 0.f;
+          if (i & 1) sum_b += p0 + p1; else sum += p0 + p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
         // 32 tokens = four 16-byte chunks of this row: chunks 4c .. 4c+3 of 16, block (4c) >> 3
@@ -337,7 +346,7 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
               make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
         }
       }
-      l_run += sum;
+      l_run += sum + sum_b;
       tc_fence_before();
       fence_proxy_async();
       if constexpr (!kKeep) mbar_arrive(&s_empty[j & 1]);
@@ -584,10 +593,18 @@ KERN_DEVICE void fmha_ctx_body(const CUtensorMap* k_map, const CUtensorMap* v_ma
 #pragma unroll
       for (int c = 0; c < FN / 32; ++c) tmem_ld_32x32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&keep[c * 32]));
       tmem_ld_wait();
-      float mx = -INFINITY;
+      if (diag) {         // the causal limit, once, on the scores themselves (a per-row branch: no warp-wide instruction inside)
 #pragma unroll
-      for (int i = 0; i < FN; ++i)
-        if (!diag || tok0 + i <= pos) mx = fmaxf(mx, __uint_as_float(keep[i]));
+        for (int i = 0; i < FN; ++i)
+          if (tok0 + i > pos) keep[i] = 0xff800000u;        // -inf
+      }
+      float mx;
+      {
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};        // four chains: a single one is 64 dependent steps
+#pragma unroll
+        for (int i = 0; i < FN; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(keep[i]));
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      }
       tc_fence_before();
       mbar_arrive(&s_empty[j & 1]);
       mx *= a.scale_log2;
@@ -615,16 +632,15 @@ KERN_DEVICE void fmha_ctx_body(const CUtensorMap* k_map, const CUtensorMap* v_ma
       }
       l_run *= alpha;
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      float sum = 0.f;
+      float sum = 0.f, sum_b = 0.f;
 #pragma unroll
       for (int c = 0; c < FN / 32; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const int t = tok0 + c * 32 + 2 * i;
-          const float p0 = (!diag || t <= pos) ? exp2f(__uint_as_float(keep[c * 32 + 2 * i]) * a.scale_log2 - m_use) : 0.f;
-          const float p1 = (!diag || t + 1 <= pos) ? exp2f(__uint_as_float(keep[c * 32 + 2 * i + 1]) * a.scale_log2 - m_use) : 0.f;
-          sum += p0 + p1;
+          const float p0 = exp2f(__uint_as_float(keep[c * 32 + 2 * i]) * a.scale_log2 - m_use);      // a masked score is -inf: 0
+          const float p1 = exp2f(__uint_as_float(keep[c * 32 + 2 * i + 1]) * a.scale_log2 - m_use);
+          if (i & 1) sum_b += p0 + p1; else sum += p0 + p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
 #pragma unroll
@@ -634,7 +650,7 @@ KERN_DEVICE void fmha_ctx_body(const CUtensorMap* k_map, const CUtensorMap* v_ma
               make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
         }
       }
-      l_run += sum;
+      l_run += sum + sum_b;
       tc_fence_before();
       fence_proxy_async();
       mbar_arrive(p_full);
