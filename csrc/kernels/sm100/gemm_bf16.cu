@@ -180,8 +180,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
   // AG: blocks per rank, this rank's first block, and the counter value that says "every CTA's share of the block is in"
   const int ag_bpr = AG ? ((EP == 1 || ag.ready != nullptr) ? 0 : num_m_of(M, ag.nranks)) : 0;
   // the block this rank's tile order and pulls start from: its own rows (contiguous slices), or a rank-dependent
-  // offset so that the ranks pull from different owners at any one time (sequence-parallel sub-blocks)
-  const int ag_first = AG ? (ag_bpr ? ag.rank * ag_bpr : (int)(((long long)ag.rank * num_m) / ag.nranks)) : 0;
+  // offset so that the ranks pull from different owners at any one time (sequence-parallel sub-blocks); the routed
+  // form pulls its expert-sorted rows in ascending order, so its tiles start at block 0
+  const int ag_first = (AG && EP != 1) ? (ag_bpr ? ag.rank * ag_bpr : (int)(((long long)ag.rank * num_m) / ag.nranks)) : 0;
   const int bpr_div = ag_bpr ? ag_bpr : 1;     // divisor where the blocks-per-rank form of the expression is not taken
   uint32_t ag_want = 0;
   if constexpr (AG) {

@@ -86,11 +86,43 @@ KERN_DEVICE void tmem_cp_sf(uint32_t taddr, uint64_t desc) {
 // the matching up columns; the epilogue computes silu(gate) * up and writes it as MXFP8 — an epilogue thread holds a
 // whole 32-element block of its row, so the block's scale needs no exchange between threads — with the scales in the
 // atom layout, ready to be the A operand of the second expert GEMM. C is then e4m3 bytes [rows, N / 2].
-template <int BN, bool B_FP4, bool GROUPED, int EPI = 0>
+//
+// Expert parallel over sharded tokens (both forms GROUPED, over the aligned plan of moe.cu::kern_moe_plan_ep):
+//   EP == 1, dispatch fused into the first expert GEMM: every home rank quantises its activations once (MXFP8 bytes and
+//     row-major scales, kern_quant_mxfp8_rows, both buffers exported); four extra warps pull row r of the expert-sorted
+//     operand (token src_tok[r]) out of its home rank — the K e4m3 bytes into `xq`, the K / 32 scale bytes word by
+//     word into the row's place in the local scale atoms — and count the row into its 128-row block's arrival counter.
+//     The producer waits (bounded) for a block's BM arrivals before the first load of a tile; counters only grow (every
+//     launch adds BM to each), so graphs replay. Half the bytes of the bf16 dispatch cross NVLink.
+//   EPI == 2, combine fused into the second expert GEMM: row r of the bf16 result goes from TMEM, through a
+//     shared-memory staging block so that every peer store covers a 128-byte line, into slot (token, choice) of the
+//     return buffer on the token's home rank; the last CTA to finish publishes this rank's epoch into every rank's
+//     `done` words (moe.cu::kern_ep_finalize waits for them and forms the weighted sum).
+struct MxEpArgs {
+  const unsigned long long* x_peers = nullptr;    // dispatch: every rank's quantised activations [rows_per_rank, K] e4m3
+  const unsigned long long* sf_peers = nullptr;   //           and their scales [rows_per_rank, K / 32], row-major
+  uint8_t* xq = nullptr;                          //           this rank's expert-sorted rows (the A operand)
+  uint8_t* sfa = nullptr;                         //           and their scale atoms
+  uint32_t* flags = nullptr;                      //           [max_blocks] rows arrived per 128-row block
+  uint32_t* epochs = nullptr;                     //           [grid] launches seen by each CTA
+  int max_blocks = 0;
+  const int* src_tok = nullptr;                   // both: global token of each expert-sorted row, -1 for padding
+  const int* row_choice = nullptr;                // combine: which of its token's k choices the row is
+  const unsigned long long* ret_peers = nullptr;  //          every rank's return buffer [rows_per_rank, k, N] bf16
+  const unsigned long long* done_peers = nullptr; //          every rank's done words [nranks]
+  uint32_t* state = nullptr;                      //          {CTAs finished, epoch}
+  int rows_per_rank = 1, rank = 0, nranks = 1, k = 1;
+};
+constexpr int kMxGatherWarps = 4;
+constexpr int kMxWindow = 8;                      // 128-row blocks per window of the dispatch form's tile order
+constexpr int kMxSlotStage = 4 * (32 * 144 + 256);   // shared memory of the combine form's row staging
+
+template <int BN, bool B_FP4, bool GROUPED, int EPI = 0, int EP = 0>
 __device__ __forceinline__ void mx_gemm_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b, const uint8_t* sfa,
                                              const uint8_t* sfw, void* Cv, int M, int N, int K, int ldc, int* err,
                                              const int* tile_table, const int* tile_count, long long sfw_expert_bytes,
-                                             uint8_t* sf_out = nullptr) {
+                                             uint8_t* sf_out = nullptr, MxEpArgs ep = MxEpArgs()) {
+  static_assert((EP == 0 && EPI != 2) || GROUPED, "the expert-parallel forms are routed GEMMs");
   __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(Cv);
   using Cfg = MxCfg<BN>;
   constexpr int kStages = Cfg::kStages;
@@ -125,9 +157,23 @@ __device__ __forceinline__ void mx_gemm_body(const CUtensorMap* tma_a, const CUt
   pdl_wait();
   const int num_m = GROUPED ? *tile_count : (M + MX_BM - 1) / MX_BM;
   const int num_tiles = num_m * num_n;
+  uint32_t ep_want = 0;
+  if constexpr (EP == 1) {
+    ep_want = (ep.epochs[blockIdx.x] + 1u) * (uint32_t)MX_BM;
+    __syncthreads();      // every thread has read this CTA's launch count before the gather warps write the next one
+  }
   auto tile_of = [&](int t, int& row0, int& row_end, int& n_blk, int& expert) {
-    const int mt = t % num_m;
+    int mt = t % num_m;
     n_blk = t / num_m;
+    if constexpr (EP == 1) {
+      // blocks in the order their rows arrive, kMxWindow at a time with the row blocks fastest inside a window: the
+      // first wave needs only the first few blocks, and CTAs that run together share W tiles through L2
+      const int per_win = kMxWindow * num_n;
+      const int w = t / per_win, r = t - w * per_win;
+      const int m0 = w * kMxWindow, wm = min(kMxWindow, num_m - m0);
+      mt = m0 + r % wm;
+      n_blk = r / wm;
+    }
     if constexpr (GROUPED) {
       const int4 e = reinterpret_cast<const int4*>(tile_table)[mt];
       expert = e.x; row0 = e.y; row_end = min(M, e.y + e.z);
@@ -145,6 +191,20 @@ __device__ __forceinline__ void mx_gemm_body(const CUtensorMap* tma_a, const CUt
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int row0, row_end, n_blk, expert;
         tile_of(t, row0, row_end, n_blk, expert);
+        if constexpr (EP == 1) {
+          const int blk = row0 / MX_BM;
+          bool here = false;
+          for (uint32_t i = 0; i < (1u << 22) && !here; ++i) {
+            here = ld_acquire_sys(ep.flags + blk) >= ep_want;
+            if (!here) { if ((i & 0xff) == 0xff && *abort_flag != 0) break; __nanosleep(100); }
+          }
+          if (!here) {
+            set_error(err, ERR_WAIT_PEER + ep.nranks);
+            *abort_flag = 1;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");   // rows and scales were written by ordinary stores; bulk copies read them
+        }
         const uint8_t* sfa_row = sfa + (size_t)(row0 / MX_BM) * num_kb * MX_SF_ATOM;
         const uint8_t* sfw_base = sfw + (GROUPED ? (size_t)expert * sfw_expert_bytes : 0);
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -220,6 +280,62 @@ __device__ __forceinline__ void mx_gemm_body(const CUtensorMap* tma_a, const CUt
       }
     }
     __syncwarp();
+  } else if (warp >= 6) {
+    // ---------------- gather warps 6..9 (dispatch form): a warp per expert-sorted row ----------------
+    if constexpr (EP == 1) {
+      const int gw = blockIdx.x * kMxGatherWarps + (warp - 6), GW = gridDim.x * kMxGatherWarps;
+      const int row_vecs = K / 16, sf_words = K / 128, total_rows = num_m * MX_BM;
+      for (int b = num_m + gw * 32 + lane; b < ep.max_blocks; b += GW * 32) atomicAdd(ep.flags + b, (uint32_t)MX_BM);   // unused this launch
+      auto ld8 = [&](const uint8_t* src, int v0, uint4 (&x)[8]) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int v = v0 + q * 32;
+          if (v < row_vecs)
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(x[q].x), "=r"(x[q].y), "=r"(x[q].z), "=r"(x[q].w) : "l"(src + (size_t)v * 16));
+        }
+      };
+      for (int r = gw; r < total_rows && *abort_flag == 0; r += GW) {
+        const int tok = ep.src_tok[r];
+        if (tok >= 0) {
+          const int home = tok / ep.rows_per_rank, lr = tok % ep.rows_per_rank;
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(ep.x_peers[home]) + (size_t)lr * K;
+          const uint32_t* ssrc = reinterpret_cast<const uint32_t*>(ep.sf_peers[home]) + (size_t)lr * sf_words;
+          uint32_t sw[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            if (lane + q * 32 < sf_words)
+              asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(sw[q]) : "l"(ssrc + lane + q * 32));
+          uint4* dst = reinterpret_cast<uint4*>(ep.xq + (size_t)r * K);
+          uint4 xa[8], xb[8];
+          ld8(src, lane, xa);
+          for (int v0 = lane; v0 < row_vecs; v0 += 256) {
+            if (v0 + 256 < row_vecs) ld8(src, v0 + 256, xb);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              if (v0 + q * 32 < row_vecs) dst[v0 + q * 32] = xa[q];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) xa[q] = xb[q];
+          }
+          // the row's four scale bytes of K block w sit in atom (r / 128, w)
+          uint8_t* sdst = ep.sfa + (size_t)(r / MX_BM) * num_kb * MX_SF_ATOM + (r % 32) * 16 + ((r / 32) % 4) * 4;
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            if (lane + q * 32 < sf_words) *reinterpret_cast<uint32_t*>(sdst + (size_t)(lane + q * 32) * MX_SF_ATOM) = sw[q];
+          for (int w = lane + 128; w < sf_words; w += 32) {      // K beyond 16384
+            uint32_t v;
+            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ssrc + w));
+            *reinterpret_cast<uint32_t*>(sdst + (size_t)w * MX_SF_ATOM) = v;
+          }
+          __threadfence();
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        __syncwarp();
+        if (lane == 0) atomicAdd(ep.flags + (r >> 7), 1u);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kMxGatherWarps * 32) : "memory");
+      if (threadIdx.x == 192) ep.epochs[blockIdx.x] = ep_want / MX_BM;
+    }
   } else {
     // ---------------- epilogue warps 2..5 ----------------
     const int quarter = warp & 3;
@@ -280,6 +396,57 @@ __device__ __forceinline__ void mx_gemm_body(const CUtensorMap* tma_a, const CUt
                 (uint8_t)(e + 127);
           }
         }
+      } else if constexpr (EPI == 2) {
+        // A lane first works out where its own row lands (once per tile); then, 64 columns at a time, the warp parks its
+        // 32 x 64 block in shared memory and writes it out four rows per instruction, eight lanes per row.
+        static_assert(Cfg::kSmemBytes + 512 + kMxSlotStage <= 232448, "stages plus the row staging fit a CTA's shared memory");
+        uint8_t* stage = smem + kStages * Cfg::kStageBytes + 512 + quarter * (32 * 144 + 256);
+        unsigned long long* rowptr = reinterpret_cast<unsigned long long*>(stage + 32 * 144);
+        {
+          unsigned long long dst = 0;
+          if (row < row_end) {
+            const int tok = ep.src_tok[row];
+            if (tok >= 0)
+              dst = ep.ret_peers[tok / ep.rows_per_rank] +
+                    2ull * (((size_t)(tok % ep.rows_per_rank) * ep.k + ep.row_choice[row]) * (size_t)N);
+          }
+          rowptr[lane] = dst;
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_row + c * 64, r0);
+          tmem_ld_32x32(t_row + c * 64 + 32, r1);
+          tmem_ld_wait();
+          uint4* mine = reinterpret_cast<uint4*>(stage + lane * 144);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r0[v * 8]), __uint_as_float(r0[v * 8 + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r0[v * 8 + 2]), __uint_as_float(r0[v * 8 + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r0[v * 8 + 4]), __uint_as_float(r0[v * 8 + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r0[v * 8 + 6]), __uint_as_float(r0[v * 8 + 7]));
+            mine[v] = o;
+            o.x = pack_bf16x2(__uint_as_float(r1[v * 8]), __uint_as_float(r1[v * 8 + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r1[v * 8 + 2]), __uint_as_float(r1[v * 8 + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r1[v * 8 + 4]), __uint_as_float(r1[v * 8 + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r1[v * 8 + 6]), __uint_as_float(r1[v * 8 + 7]));
+            mine[4 + v] = o;
+          }
+          __syncwarp();
+          const int col = n_blk * BN + c * 64 + (lane & 7) * 8;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3);
+            const unsigned long long dst = rowptr[rr];
+            if (dst != 0 && col < N) {
+              const uint4 val = *reinterpret_cast<const uint4*>(stage + rr * 144 + (lane & 7) * 16);
+              *reinterpret_cast<uint4*>(dst + 2ull * col) = val;
+            }
+          }
+          __syncwarp();
+        }
       } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -311,9 +478,23 @@ __device__ __forceinline__ void mx_gemm_body(const CUtensorMap* tma_a, const CUt
   }
 
   // ---------------- teardown ----------------
+  if constexpr (EPI == 2) __threadfence_system();   // the pushed rows are on their way before the kernel is done
   pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
+  if constexpr (EPI == 2) {
+    // the last CTA to get here publishes this rank's epoch: every store of this launch is ordered before it
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      if (atomicAdd(ep.state, 1u) == gridDim.x - 1) {
+        ep.state[0] = 0;
+        const uint32_t e = ep.state[1] + 1;
+        ep.state[1] = e;
+        __threadfence_system();
+        for (int r = 0; r < ep.nranks; ++r) st_release_sys(reinterpret_cast<uint32_t*>(ep.done_peers[r]) + ep.rank, e);
+      }
+    }
+  }
   if (*abort_flag != 0 && threadIdx.x == 0) {
     const uint64_t t0 = globaltimer_ns();       // let copies in flight land before the shared memory goes away
     while (globaltimer_ns() - t0 < 2000000ull) { __nanosleep(1000); }
@@ -353,6 +534,42 @@ KERN_MX_GROUPED_ENTRY(kern_moe_gemm_mxfp8_mxfp4_n256, 256, true, 0)
 KERN_MX_GROUPED_ENTRY(kern_moe_gemm_mxfp8_mxfp4_swiglu_mxfp8_n128, 128, true, 1)
 KERN_MX_GROUPED_ENTRY(kern_moe_gemm_mxfp8_mxfp4_swiglu_mxfp8_n256, 256, true, 1)
 
+// The expert-parallel pair (dispatch inside the first routed GEMM, combine inside the second).
+#define KERN_EP_MX_FC1_ENTRY(name, BN)                                                                             \
+  extern "C" __global__ void __launch_bounds__(320, 1)                                                             \
+      name(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, uint8_t* sfa,         \
+           const uint8_t* sfw, void* C, int M, int N, int K, int ldc, int* err, const int* tile_table,               \
+           const int* tile_count, long long sfw_expert_bytes, uint8_t* sf_out, const unsigned long long* x_peers,   \
+           const unsigned long long* sf_peers, uint8_t* xq, const int* src_tok, uint32_t* flags,                     \
+           uint32_t* cta_epochs, int rows_per_rank, int max_blocks, int nranks) {                                  \
+    kern::MxEpArgs ep;                                                                                             \
+    ep.x_peers = x_peers; ep.sf_peers = sf_peers; ep.xq = xq; ep.sfa = sfa; ep.flags = flags; ep.epochs = cta_epochs; \
+    ep.max_blocks = max_blocks; ep.src_tok = src_tok; ep.rows_per_rank = rows_per_rank; ep.nranks = nranks;        \
+    if (*tile_count > max_blocks || (K % 128) != 0) { /* every 128-row block needs its counter */                  \
+      if (threadIdx.x == 0 && blockIdx.x == 0) kern::set_error(err, kern::ERR_BOUNDS);                             \
+      return;                                                                                                      \
+    }                                                                                                              \
+    kern::mx_gemm_body<BN, true, true, 1, 1>(&tma_a, &tma_b, sfa, sfw, C, M, N, K, ldc, err, tile_table, tile_count,  \
+                                             sfw_expert_bytes, sf_out, ep);                                        \
+  }
+#define KERN_EP_MX_FC2_ENTRY(name, BN)                                                                             \
+  extern "C" __global__ void __launch_bounds__(192, 1)                                                             \
+      name(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const uint8_t* sfa,   \
+           const uint8_t* sfw, int M, int N, int K, int* err, const int* tile_table, const int* tile_count,          \
+           long long sfw_expert_bytes, const unsigned long long* ret_peers, const int* src_tok,                     \
+           const int* row_choice, uint32_t* state, const unsigned long long* done_peers, int rows_per_rank, int k,  \
+           int rank, int nranks) {                                                                                 \
+    kern::MxEpArgs ep;                                                                                             \
+    ep.ret_peers = ret_peers; ep.src_tok = src_tok; ep.row_choice = row_choice; ep.state = state;                  \
+    ep.done_peers = done_peers; ep.rows_per_rank = rows_per_rank; ep.k = k; ep.rank = rank; ep.nranks = nranks;    \
+    kern::mx_gemm_body<BN, true, true, 2>(&tma_a, &tma_b, sfa, sfw, nullptr, M, N, K, N, err, tile_table, tile_count, \
+                                          sfw_expert_bytes, nullptr, ep);                                          \
+  }
+KERN_EP_MX_FC1_ENTRY(kern_ep_fc1_mxfp8_mxfp4_swiglu_mxfp8_n128, 128)
+KERN_EP_MX_FC1_ENTRY(kern_ep_fc1_mxfp8_mxfp4_swiglu_mxfp8_n256, 256)
+KERN_EP_MX_FC2_ENTRY(kern_ep_fc2_mxfp8_mxfp4_combine_n128, 128)
+KERN_EP_MX_FC2_ENTRY(kern_ep_fc2_mxfp8_mxfp4_combine_n256, 256)
+
 // ---- quantiser: bf16 rows -> MXFP8 (e4m3 + one UE8M0 scale per 32 elements, scales in the atom layout) -------------
 // scale = 2^ceil(log2(amax / 448)) (the smallest power of two that brings the block into e4m3's range), clamped to the
 // UE8M0 range; an all-zero block gets scale 1. One warp per (row, 32-element block): lane = element.
@@ -378,6 +595,47 @@ extern "C" __global__ void kern_quant_mxfp8(const __nv_bfloat16* x, uint8_t* q, 
     if (lane == 0)
       sf[((size_t)(row / 128) * katoms + kb / 4) * MX_SF_ATOM + (row % 32) * 16 + ((row / 32) % 4) * 4 + kb % 4] =
           (uint8_t)(e + 127);
+  }
+}
+
+// The same quantiser with the scales row-major ([M, K / 32] bytes): what a home rank exports for the fused expert-parallel
+// dispatch — a peer pulls a row's K / 32 scale bytes as K / 128 words and drops each into its atom. Four threads share a
+// 32-element block (8 elements each, one 16-byte load). grid = rows (any), block 128; K a multiple of 32.
+extern "C" __global__ void __launch_bounds__(128)
+    kern_quant_mxfp8_rows(const __nv_bfloat16* x, uint8_t* q, uint8_t* sf_rows, int M, int K, int ldx) {
+  pdl_wait();
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)row * ldx);
+    for (int v = threadIdx.x; v < K / 8; v += 128) {
+      const uint4 p = src[v];
+      float f[8];
+      float2 t;
+      t = unpack_bf16x2(p.x); f[0] = t.x; f[1] = t.y;
+      t = unpack_bf16x2(p.y); f[2] = t.x; f[3] = t.y;
+      t = unpack_bf16x2(p.z); f[4] = t.x; f[5] = t.y;
+      t = unpack_bf16x2(p.w); f[6] = t.x; f[7] = t.y;
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      int e = 0;
+      if (amax > 0.f) {
+        int ex;
+        const float mant = frexpf(amax, &ex);
+        e = mant <= 0.875f ? ex - 9 : ex - 8;
+        e = max(-127, min(127, e));
+      }
+      const float inv = exp2f((float)-e);
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        lo |= (uint32_t)__nv_cvt_float_to_fp8(f[j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+        hi |= (uint32_t)__nv_cvt_float_to_fp8(f[4 + j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+      }
+      *reinterpret_cast<uint2*>(q + (size_t)row * K + v * 8) = make_uint2(lo, hi);
+      if ((v & 3) == 0) sf_rows[(size_t)row * (K / 32) + v / 4] = (uint8_t)(e + 127);
+    }
   }
 }
 

@@ -204,11 +204,122 @@ def ep_fused_ops(world: int, rows_max: int, hidden: int, inter: int, e_n: int, k
     return ops
 
 
-def ep_fused_calls(ids: str, w: str, x: str, w1: str, w2: str, out: str, rows_var: str, label: str = "") -> list[dict]:
+def mx_smem(bn: int) -> int:
+    """Shared memory of a block-scaled GEMM CTA (gemm_mx.cu::MxCfg)."""
+    stages = 4 if bn == 256 else 6
+    return 1024 + stages * (128 * 128 + bn * 128 + (2048 if bn == 256 else 1024)) + 256
+
+
+def ep_fused_buffers_mx(world: int, rows_max: int, hidden: int, inter: int, e_n: int, k: int, group: str = "ep") -> dict:
+    """Buffers of the block-scaled form of the fused layer: the home rank's quantised rows and row-major scales are what
+    the peers pull (exported), the expert-sorted operands are e4m3 bytes with scale atoms."""
+    from ..ops.gemm_mx import atom_bytes
+
+    assert hidden % 128 == 0 and inter % 128 == 0, "block-scaled experts need hidden and intermediate multiples of 128"
+    bufs = ep_fused_buffers(world, rows_max, hidden, inter, e_n, k, "ep.q8", group)
+    max_rows = bufs["ep.src_tok"]["shape"][0]
+    buf = lambda dt, shape, kind="workspace", **kw: {"dtype": dt, "shape": shape, "kind": kind, **kw}
+    peer = lambda of: {"dtype": "u64", "shape": [world], "kind": "peer", "of": of, "group": group}
+    bufs.update({
+        "ep.q8": buf("u8", [rows_max, hidden], "carry", export=True),
+        "ep.sf8": buf("u8", [rows_max, hidden // 32], "carry", export=True), "ep.sf8_peers": peer("ep.sf8"),
+        "ep.xp": buf("u8", [max_rows, hidden], "carry"), "ep.sfp": buf("u8", [atom_bytes(max_rows, hidden)], "carry"),
+        "ep.act": buf("u8", [max_rows, inter]), "ep.sfact": buf("u8", [atom_bytes(max_rows, inter)]),
+    })
+    return bufs
+
+
+def ep_fused_ops_mx(world: int, rows_max: int, hidden: int, inter: int, e_n: int, k: int, rows_var: str, group: str = "ep",
+                    accumulate: bool = False, timeout_ns: int = 2_000_000_000, bn: int | None = None) -> dict:
+    """The fused layer with MXFP4 expert weights and MXFP8 activations (gemm_mx.cu, the `kern_ep_*_mxfp8_mxfp4_*`
+    entries): publish, plan and finalize are the bf16 form's; the home rank quantises its rows once (`ep_quant`), FC1
+    pulls e4m3 rows and scale words from the home ranks, FC2 stores bf16 rows into the home ranks' slots. Interfaces:
+    ep_quant [x, q8, sf8, rows];
+    ep_fc1 [xp, w1, act, tiles, tile_count, q8_peers, src_tok, blocks, cta_epochs, err, sfp, sf1, sfact, sf8_peers];
+    ep_fc2 [act, w2, tiles, tile_count, ret_peers, src_tok, row_choice, state, done_peers, err, sfact, sf2]."""
+    from ..ops.gemm_mx import atom_bytes
+
+    ops = ep_fused_ops(world, rows_max, hidden, inter, e_n, k, rows_var, group, accumulate, timeout_ns, bn)
+    T = rows_max * world
+    max_tiles = T * k // C.BM + e_n
+    max_rows = max_tiles * C.BM
+    L = lambda module, entry, block, grid, lp, args, **kw: {"module": module, "entry": entry, "block": block, "grid": grid,
+                                                            "params": lp, "args": args, **kw}
+    P = lambda i: {"param": i}
+    rank = {"rank": group}
+    ops["ep_quant"] = {"params": ["in buffer<bf16>", "out buffer<u8>", "out buffer<u8>", "i32"], "impl": {"launches": [L(
+        "gemm_mx", "kern_quant_mxfp8_rows", [128, 1, 1], [rows_var, 1, 1],
+        ["in buffer<bf16>", "out buffer<u8>", "out buffer<u8>", "i32", "i32", "i32"],
+        [P(0), P(1), P(2), P(3), {"i32": hidden}, {"i32": hidden}])]}}
+
+    def maps(kk, n, bn_):
+        a_map = {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+            "param": 0, "dtype": "u8", "dims": [kk, 0], "strides": [kk], "box": [128, C.BM], "swizzle": 128, "l2_promotion": 256}}]}}
+        b_map = {"pack": {"size": 128, "fields": [{"at": 0, "tensormap": {
+            "param": 1, "dtype": "u4", "dims": [kk, n, e_n], "strides": [kk // 2, n * kk // 2],
+            "box": [128, bn_, 1], "swizzle": 128, "l2_promotion": 256}}]}}
+        return a_map, b_map
+
+    def widths(n: int) -> list[tuple[int, dict | None]]:
+        if bn is not None:
+            return [(256 if bn == 256 and n % 256 == 0 else 128, None)]
+        if n % 256 != 0 or rows_max <= EP_WIDE_FROM:
+            return [(128, None)]
+        return [(128, {"var": rows_var, "max": EP_WIDE_FROM}), (256, {"var": rows_var, "min": EP_WIDE_FROM + 1})]
+
+    def with_when(launch: dict, when: dict | None) -> dict:
+        if when is not None:
+            launch["when"] = when
+        return launch
+
+    fc1 = []
+    for bn1, when in widths(2 * inter):
+        a1, b1 = maps(hidden, 2 * inter, bn1)
+        fc1.append(with_when(L(
+            "gemm_mx", f"kern_ep_fc1_mxfp8_mxfp4_swiglu_mxfp8_n{bn1}", [320, 1, 1], [C.SMS, 1, 1],
+            ["bytes<128>", "bytes<128>", "inout buffer<u8>", "in buffer<u8>", "out buffer<u8>", "i32", "i32", "i32", "i32",
+             "out buffer<i32>", "in buffer<i32>", "in buffer<i32>", "i64", "out buffer<u8>", "in buffer<u64>", "in buffer<u64>",
+             "inout buffer<u8>", "in buffer<i32>", "inout buffer<u32>", "inout buffer<u32>", "i32", "i32", "i32"],
+            [a1, b1, P(10), P(11), P(2), {"i32": max_rows}, {"i32": 2 * inter}, {"i32": hidden}, {"i32": inter}, P(9), P(3), P(4),
+             {"i64": atom_bytes(2 * inter, hidden)}, P(12), P(5), P(13), P(0), P(6), P(7), P(8), {"i32": rows_max},
+             {"i32": max_tiles}, {"i32": world}], shared_mem=mx_smem(bn1)), when))
+    ops["ep_fc1"] = {"params": ["inout buffer<u8>", "in buffer<u8>", "out buffer<u8>", "in buffer<i32>", "in buffer<i32>",
+                                "in buffer<u64>", "in buffer<i32>", "inout buffer<u32>", "inout buffer<u32>", "out buffer<i32>",
+                                "inout buffer<u8>", "in buffer<u8>", "out buffer<u8>", "in buffer<u64>"],
+                     "impl": {"launches": fc1}}
+    fc2 = []
+    for bn2, when in widths(hidden):
+        a2, b2 = maps(inter, hidden, bn2)
+        fc2.append(with_when(L(
+            "gemm_mx", f"kern_ep_fc2_mxfp8_mxfp4_combine_n{bn2}", [192, 1, 1], [C.SMS, 1, 1],
+            ["bytes<128>", "bytes<128>", "in buffer<u8>", "in buffer<u8>", "i32", "i32", "i32", "out buffer<i32>", "in buffer<i32>",
+             "in buffer<i32>", "i64", "in buffer<u64>", "in buffer<i32>", "in buffer<i32>", "inout buffer<u32>", "in buffer<u64>",
+             "i32", "i32", "i32", "i32"],
+            [a2, b2, P(10), P(11), {"i32": max_rows}, {"i32": hidden}, {"i32": inter}, P(9), P(2), P(3),
+             {"i64": atom_bytes(hidden, inter)}, P(4), P(5), P(6), P(7), P(8), {"i32": rows_max}, {"i32": k}, rank, {"i32": world}],
+            shared_mem=mx_smem(bn2) + 20480), when))     # + the epilogue's row staging
+    ops["ep_fc2"] = {"params": ["in buffer<u8>", "in buffer<u8>", "in buffer<i32>", "in buffer<i32>", "in buffer<u64>",
+                                "in buffer<i32>", "in buffer<i32>", "inout buffer<u32>", "in buffer<u64>", "out buffer<i32>",
+                                "in buffer<u8>", "in buffer<u8>"],
+                     "impl": {"launches": fc2}}
+    return ops
+
+
+def ep_fused_calls(ids: str, w: str, x: str, w1: str, w2: str, out: str, rows_var: str, label: str = "",
+                   mx: tuple[str, str] | None = None) -> list[dict]:
     """The five calls of one fused layer: routing of this rank's rows in `ids` / `w`, activations in the exported `x`,
     this rank's expert weights `w1` / `w2`, the experts' weighted sum into `out`."""
     B = lambda n: {"buf": n}
     err = B("error")
+    if mx is not None:
+        # `mx`: the scale atoms of w1 and of w2. The rows are quantised before the publish: a peer that has seen this
+        # rank's ready word may pull them.
+        sf1, sf2 = mx
+        calls = ep_fused_calls(ids, w, "ep.q8", w1, w2, out, rows_var, label)
+        calls.insert(0, {"op": "ep_quant", "label": label + "quant", "args": [B(x), B("ep.q8"), B("ep.sf8"), {"var": rows_var}]})
+        calls[3]["args"] += [B("ep.sfp"), B(sf1), B("ep.sfact"), B("ep.sf8_peers")]
+        calls[4]["args"] += [B("ep.sfact"), B(sf2)]
+        return calls
     return [
         {"op": "ep_publish", "label": label + "publish", "args": [B(ids), B("ep.ids_peers"), B("ep.ready_peers"), B("ep.pub_epoch"),
                                                                   {"var": rows_var}]},

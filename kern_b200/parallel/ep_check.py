@@ -116,15 +116,35 @@ def manifest(world: int, rows_max: int, hidden: int, inter: int, experts: int, k
                          "step_graph": {"batch": {"groups": 1, "rows": "rows"}, "graph": True, "calls": calls}}}
 
 
-def manifest_fused(world: int, rows_max: int, hidden: int, inter: int, experts: int, k: int, bn: int | None = None) -> dict:
+def manifest_fused(world: int, rows_max: int, hidden: int, inter: int, experts: int, k: int, bn: int | None = None,
+                   mx: bool = False) -> dict:
     """The same layer with the dispatch inside FC1 and the combine inside FC2 (`moe.cu`, the `kern_ep_*` entries): five
-    launches, no barrier kernel, no NCCL call. `rows_max`: tokens per rank."""
+    launches, no barrier kernel, no NCCL call. `rows_max`: tokens per rank. `mx`: MXFP4 expert weights and MXFP8
+    activations (`gemm_mx.cu`): a sixth launch quantises this rank's rows once, and e4m3 rows cross NVLink."""
     from ..models import common as C
     from ..models import moe_ep
 
     assert experts % world == 0 and hidden % 8 == 0
     e_n = experts // world
     buf = lambda dt, shape, kind="workspace", **kw: {"dtype": dt, "shape": shape, "kind": kind, **kw}
+    if mx:
+        from ..ops.gemm_mx import atom_bytes
+
+        bufs = {
+            "x": buf("bf16", ["rows", hidden], "input"),
+            "ids": buf("i32", ["rows", k], "input"), "w": buf("f32", ["rows", k], "input"),
+            "w1": buf("u8", [e_n, 2 * inter, hidden // 2], "input"), "sf1": buf("u8", [e_n, atom_bytes(2 * inter, hidden)], "input"),
+            "w2": buf("u8", [e_n, hidden, inter // 2], "input"), "sf2": buf("u8", [e_n, atom_bytes(hidden, inter)], "input"),
+            "out": buf("bf16", ["rows", hidden], "output"), "error": buf("i32", [1], "output"),
+            **moe_ep.ep_fused_buffers_mx(world, rows_max, hidden, inter, e_n, k),
+        }
+        ops = moe_ep.ep_fused_ops_mx(world, rows_max, hidden, inter, e_n, k, "rows", bn=bn)
+        calls = moe_ep.ep_fused_calls("ids", "w", "x", "w1", "w2", "out", "rows", mx=("sf1", "sf2"))
+        return {"schema_version": 7, "model": "ep-fused-mx-check", "vars": {"rows": {"max": rows_max, "axis": "rows"}},
+                "topology": {"groups": {"ep": world}}, "states": {}, "buffers": bufs,
+                "modules": C.modules_for(["moe", "gemm_mx"]), "ops": ops,
+                "programs": {"step": {"calls": calls},
+                             "step_graph": {"batch": {"groups": 1, "rows": "rows"}, "graph": True, "calls": calls}}}
     bufs = {
         "ep.x": buf("bf16", [rows_max, hidden], "inout", export=True),
         "ids": buf("i32", ["rows", k], "input"), "w": buf("f32", ["rows", k], "input"),
@@ -200,6 +220,7 @@ def main(argv=None) -> int:
     ap.add_argument("--top-k", type=int, default=4)
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--fused", action="store_true", help="dispatch inside FC1, combine inside FC2 (five launches per layer)")
+    ap.add_argument("--mx", action="store_true", help="with --fused: MXFP4 expert weights, MXFP8 activations (block-scaled tcgen05 GEMMs)")
     ap.add_argument("--bn", type=int, default=None, choices=[64, 128, 256], help="tile width of the fused routed GEMMs (default: by row count)")
     ap.add_argument("--traffic", type=int, default=None, help="the model check with the prompts rank N of a larger group would get")
     ap.add_argument("--model", action="store_true", help="also run the MoE decoder with sharded tokens and fused routed layers")
@@ -215,16 +236,31 @@ def main(argv=None) -> int:
     h, I, E, k = a.hidden, a.inter, a.experts, a.top_k
     e_n = E // world
     rows_max = max(a.rows)
-    doc = manifest_fused(world, rows_max, h, I, E, k, bn=a.bn) if a.fused else manifest(world, rows_max, h, I, E, k)
+    doc = manifest_fused(world, rows_max, h, I, E, k, bn=a.bn, mx=a.mx) if a.fused else manifest(world, rows_max, h, I, E, k)
+    xname = "x" if a.fused and a.mx else "ep.x"
     rt = Runtime(doc, gpu=local, topology={"ep": (rank, world)},
                  guard_bands=True)      # canary bands around every allocation: the peers' adds and stores land in this rank's memory
     group.start(rt)
     g = torch.Generator().manual_seed(21)
     w1 = (torch.randn(E, 2 * I, h, generator=g) * 0.05).to(torch.bfloat16)       # [gate rows ; up rows] per expert
     w2 = (torch.randn(E, h, I, generator=g) * 0.05).to(torch.bfloat16)
-    rt.tensor("w1").copy_(w1[rank * e_n:(rank + 1) * e_n].to(dev))
-    rt.tensor("w2").copy_(w2[rank * e_n:(rank + 1) * e_n].to(dev))
-    w1d, w2d = w1.to(dev).float(), w2.to(dev).float()
+    if a.fused and a.mx:
+        from ..ops import gemm_mx as G
+        from ..ops import moe as M
+
+        mine = slice(rank * e_n, (rank + 1) * e_n)
+        q1, s1, q2, s2 = M.prepare_expert_weights_mx(w1[mine].to(dev).float(), w2[mine].to(dev).float())
+        for name, t in (("w1", q1), ("sf1", s1), ("w2", q2), ("sf2", s2)):
+            rt.tensor(name).copy_(t.reshape(rt.tensor(name).shape))
+        # the statement: every expert's weights through MXFP4 and back, activations through MXFP8 before each GEMM
+        w1d = torch.stack([G.dequant_mxfp4(*G.quantize_mxfp4_torch(w1[e].to(dev).float())) for e in range(E)])
+        w2d = torch.stack([G.dequant_mxfp4(*G.quantize_mxfp4_torch(w2[e].to(dev).float())) for e in range(E)])
+        q8 = lambda t: G.dequant_mxfp8(*G.quantize_mxfp8_torch(t))
+    else:
+        rt.tensor("w1").copy_(w1[rank * e_n:(rank + 1) * e_n].to(dev))
+        rt.tensor("w2").copy_(w2[rank * e_n:(rank + 1) * e_n].to(dev))
+        w1d, w2d = w1.to(dev).float(), w2.to(dev).float()
+        q8 = None
     results = []
     for it, tr in enumerate(a.rows + a.rows[:1]):
         program = "step_graph" if it >= len(a.rows) else "step"
@@ -232,7 +268,7 @@ def main(argv=None) -> int:
         xs = [(torch.randn(tr, h, generator=gi) * 0.5).to(torch.bfloat16) for _ in range(world)]
         ids = [torch.stack([torch.randperm(E, generator=gi)[:k] for _ in range(tr)]).to(torch.int32) for _ in range(world)]
         ws = [torch.rand(tr, k, generator=gi) for _ in range(world)]
-        rt.tensor("ep.x")[:tr].copy_(xs[rank].to(dev))
+        rt.tensor(xname)[:tr].copy_(xs[rank].to(dev))
         rt.tensor("ids").view(-1)[: tr * k].copy_(ids[rank].reshape(-1).to(dev))
         rt.tensor("w").view(-1)[: tr * k].copy_(ws[rank].reshape(-1).to(dev))
         if not a.fused:
@@ -243,12 +279,15 @@ def main(argv=None) -> int:
         rt.check_error()
         got = rt.tensor("out")[:tr].float()
         x = xs[rank].to(dev).float()
+        if q8 is not None:
+            x = q8(x)
         want = torch.zeros(tr, h, device=dev)
         for t in range(tr):
             for j in range(k):
                 e = int(ids[rank][t, j])
                 gu = w1d[e] @ x[t]
-                act = (torch.nn.functional.silu(gu[:I]) * gu[I:]).to(torch.bfloat16).float()
+                act = torch.nn.functional.silu(gu[:I]) * gu[I:]
+                act = q8(act[None])[0] if q8 is not None else act.to(torch.bfloat16).float()
                 want[t] += float(ws[rank][t, j]) * (w2d[e] @ act).to(torch.bfloat16).float()
         err = float((got - want).abs().max())
         tol = 0.05 * max(1.0, float(want.abs().max()))
@@ -260,7 +299,7 @@ def main(argv=None) -> int:
         dist.barrier()
     bad = rt.check_guards()
     results.append({"guard_bands_overwritten": bad, "ok": not bad})
-    line = {"check": "expert_parallel_fused" if a.fused else "expert_parallel_all_to_all", "world": world, "experts": E, "top_k": k, "hidden": h, "results": results}
+    line = {"check": ("expert_parallel_fused_mx" if a.mx else "expert_parallel_fused") if a.fused else "expert_parallel_all_to_all", "world": world, "experts": E, "top_k": k, "hidden": h, "results": results}
     if a.time:
         stream = torch.cuda.ExternalStream(rt.stream)
         times = []

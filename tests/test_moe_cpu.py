@@ -96,6 +96,15 @@ def test_fused_expert_parallel_manifests_verify(world):
         ls = wide["ops"][op]["impl"]["launches"]
         assert [l["entry"] for l in ls] == [small, big]
         assert ls[0]["when"] == {"var": "rows", "max": 192} and ls[1]["when"] == {"var": "rows", "min": 193}
+    # block-scaled form: one more launch (this rank's rows quantised once), the routed pair out of the MX module
+    mx = ep_check.manifest_fused(world, 1024, 1024, 512, 16, 4, mx=True)
+    m, errs = _native.verify(json.dumps(mx))
+    assert m is not None, errs
+    entries = [l["entry"] for c in mx["programs"]["step"]["calls"] for l in mx["ops"][c["op"]]["impl"]["launches"]]
+    assert entries == ["kern_quant_mxfp8_rows", "kern_ep_publish", "kern_moe_plan_ep", "kern_ep_fc1_mxfp8_mxfp4_swiglu_mxfp8_n128",
+                       "kern_ep_fc1_mxfp8_mxfp4_swiglu_mxfp8_n256", "kern_ep_fc2_mxfp8_mxfp4_combine_n128",
+                       "kern_ep_fc2_mxfp8_mxfp4_combine_n256", "kern_ep_finalize"]
+    assert mx["buffers"]["ep.q8"]["export"] and mx["buffers"]["ep.sf8"]["shape"] == [1024, 1024 // 32]
     cfg = dataclasses.replace(moe.TINY_MOE, experts=16, top_k=4)
     doc = moe_ep.build_manifest_ep_sharded(cfg, world)
     m, errs = _native.verify(json.dumps(doc))
