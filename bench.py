@@ -93,6 +93,8 @@ def main():
                          "8 GPUs default to `fused`), the same with the all-gather pulled inside the next "
                          "GEMM, replicated rows with the GEMM epilogue pushing partials to the all-reduce, or replicated rows with a "
                          "plain GEMM and the all-reduce kernel pushing them (A/B)")
+    ap.add_argument("--experts", default="mx", choices=["mx", "bf16"],
+                    help="config d: MXFP4 expert weights with MXFP8 expert activations (the config's own formats), or bf16 experts")
     ap.add_argument("--profile", action="store_true", help="after the timed region, run one more step with per-call timing and print the cost by op to stderr")
     args = ap.parse_args()
     if args.tp_layout is None:

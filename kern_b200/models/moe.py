@@ -66,7 +66,8 @@ def random_weights(cfg: MoeConfig, seed: int = 0, device: str = "cpu", std: floa
     return out
 
 
-def load_random_weights(rt, cfg: MoeConfig, seed: int = 0, std: float = 0.02) -> None:
+def load_random_weights(rt, cfg: MoeConfig, seed: int = 0, std: float = 0.02, skip=None) -> None:
+    """`skip(name)`: checkpoint tensors the caller fills itself (buffers that bind only such tensors are left alone)."""
     shapes = weight_names(cfg)
     order = {n: i for i, n in enumerate(shapes)}
 
@@ -77,7 +78,7 @@ def load_random_weights(rt, cfg: MoeConfig, seed: int = 0, std: float = 0.02) ->
         t = torch.randn(shapes[name], generator=g, device=dev) * (0.1 if name.endswith("norm.weight") else scale)
         return ((1.0 + t) if name.endswith("norm.weight") else t).to(torch.bfloat16)
 
-    rt.load_tensors(provider)
+    rt.load_tensors(provider, skip=skip)
 
 
 def _moe_ops(cfg: MoeConfig, e_lo: int, e_n: int, ep_group: str | None = None, accumulate: bool = True) -> dict:

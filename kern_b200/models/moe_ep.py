@@ -338,7 +338,8 @@ def build_manifest_ep_sharded(cfg: MoeConfig, world: int) -> dict:
     """The MoE decoder with tokens sharded over an expert-parallel group: every rank serves its own sequences (attention,
     norms, router and head are whole on every rank: data parallel), rank r keeps experts [r E/n, (r+1) E/n), and every
     routed layer is the fused pair of kernels — dispatch inside FC1, combine inside FC2. The ranks step in lockstep: a
-    layer's kernels wait for every rank's publish and done words. `cfg.max_tokens` is the rows per rank."""
+    layer's kernels wait for every rank's publish and done words. `cfg.max_tokens` is the rows per rank.
+    `cfg.mx_experts`: MXFP4 expert weights and MXFP8 expert activations (the block-scaled pair of `gemm_mx.cu`)."""
     from . import moe
 
     assert world >= 1 and cfg.experts % world == 0
@@ -352,12 +353,28 @@ def build_manifest_ep_sharded(cfg: MoeConfig, world: int) -> dict:
         ops.pop(name)
     for name in ("moe.perm", "moe.offsets", "moe.tiles", "moe.tile_count", "moe.rows", "moe.x", "moe.act", "moe.y"):
         bufs.pop(name)
-    bufs["xn"]["export"] = True
-    bufs.update(ep_fused_buffers(world, T, h, I, el, k, "xn"))
-    ops.update(ep_fused_ops(world, T, h, I, el, k, "tokens", accumulate=True))
+    mx = bool(getattr(cfg, "mx_experts", False))
+    if mx:
+        from ..ops.gemm_mx import atom_bytes
+
+        bufs.update(ep_fused_buffers_mx(world, T, h, I, el, k))
+        ops.update(ep_fused_ops_mx(world, T, h, I, el, k, "tokens", accumulate=True))
+    else:
+        bufs["xn"]["export"] = True
+        bufs.update(ep_fused_buffers(world, T, h, I, el, k, "xn"))
+        ops.update(ep_fused_ops(world, T, h, I, el, k, "tokens", accumulate=True))
     ranked = lambda fmt: {"group": "ep", "tensors": [fmt(r) for r in range(world)]}
+    mine = {"group": "ep", "ranges": [[r * el, (r + 1) * el] for r in range(world)]}
     for i in range(cfg.layers):
         p = f"model.layers.{i}.mlp."
+        if mx:
+            # this rank's range of the stacked block-scaled tensors (`moe.mx_checkpoint`)
+            for name, shape, tensor in ((f"w.l{i}.w1", [el, 2 * I, h // 2], "experts.w1_mxfp4"),
+                                        (f"w.l{i}.sf1", [el, atom_bytes(2 * I, h)], "experts.w1_scales"),
+                                        (f"w.l{i}.w2", [el, h, I // 2], "experts.w2_mxfp4"),
+                                        (f"w.l{i}.sf2", [el, atom_bytes(h, I)], "experts.w2_scales")):
+                bufs[name] = {"dtype": "u8", "shape": shape, "kind": "weight", "bind": [{"tensor": p + tensor, "rows": mine}]}
+            continue
         bufs[f"w.l{i}.w1"] = {"dtype": "bf16", "shape": [el, 2 * I, h], "kind": "weight",
                               "bind": [{"tensor": ranked(lambda r, j=j, part=part: p + f"experts.{r * el + j}.{part}_proj.weight")}
                                        for j in range(el) for part in ("gate", "up")]}
@@ -372,8 +389,9 @@ def build_manifest_ep_sharded(cfg: MoeConfig, world: int) -> dict:
                 continue
             if lbl.endswith(".combine"):
                 i = int(lbl[1:lbl.index(".")])
-                out += ep_fused_calls("moe.ids", "moe.w", "xn", f"w.l{i}.w1", f"w.l{i}.w2", "x", "tokens", label=f"l{i}.ep_")
+                out += ep_fused_calls("moe.ids", "moe.w", "xn", f"w.l{i}.w1", f"w.l{i}.w2", "x", "tokens", label=f"l{i}.ep_",
+                                      mx=(f"w.l{i}.sf1", f"w.l{i}.sf2") if mx else None)
             else:
                 out.append(c)
         prog["calls"] = out
-    return doc
+    return C.ensure_modules(doc)

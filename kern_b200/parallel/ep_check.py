@@ -161,9 +161,11 @@ def manifest_fused(world: int, rows_max: int, hidden: int, inter: int, experts: 
                          "step_graph": {"batch": {"groups": 1, "rows": "rows"}, "graph": True, "calls": calls}}}
 
 
-def check_model(rank: int, world: int, dev, traffic: int | None = None) -> dict:
+def check_model(rank: int, world: int, dev, traffic: int | None = None, mx: bool = False) -> dict:
     """The MoE decoder with tokens sharded over the group (`models/moe_ep.py::build_manifest_ep_sharded`): every rank
-    serves its own prompts, the routed layers are the fused kernels; logits against the one-GPU fp32 oracle."""
+    serves its own prompts, the routed layers are the fused kernels; logits against the one-GPU fp32 oracle. `mx`: the
+    decoder with MXFP4 experts; its logits against the one-GPU manifest of the same block-scaled checkpoint on this
+    GPU (the same quantisation points, so only the order of the sums differs)."""
     import dataclasses
 
     from ..engine import Engine
@@ -173,30 +175,43 @@ def check_model(rank: int, world: int, dev, traffic: int | None = None) -> dict:
 
     cfg = dataclasses.replace(moe.TINY_MOE, name="tiny-moe-eps", experts=16, top_k=4)
     weights = moe.random_weights(cfg, seed=0, std=0.05)
+    if mx:
+        cfg = dataclasses.replace(cfg, name="tiny-moe-eps-mx", mx_experts=True, moe_intermediate=128)
+        weights = moe.mx_checkpoint(cfg, moe.random_weights(cfg, seed=0, std=0.05))
     doc = moe_ep.build_manifest_ep_sharded(cfg, world)
     rt = Runtime(doc, gpu=dev.index, topology=group.topology(doc["topology"]["groups"], rank, world), tokens=cfg.page_size * 64)
     rt.load_tensors(lambda name: weights[name].to(dev))
     group.start(rt)
     eng = Engine(rt)
-    oracle = moe.MoeOracle(cfg, weights, device="cuda")
     g = torch.Generator().manual_seed(100 + (rank if traffic is None else traffic))     # every rank has its own traffic
     prompts = [torch.randint(0, cfg.vocab, (int(n),), generator=g).tolist() for n in torch.randint(3, 90, (3,), generator=g)]
     seqs = [eng.open(140) for _ in prompts]
-    caches = [oracle.new_cache() for _ in prompts]
+    if mx:
+        ref_rt = Runtime(moe.build_manifest(cfg), gpu=dev.index, tokens=cfg.page_size * 64)
+        ref_rt.load_tensors(lambda name: weights[name].to(dev))
+        ref_rt.once()
+        ref = Engine(ref_rt)
+        rseqs = [ref.open(140) for _ in prompts]
+
+        def want(batch):
+            ref.step(list(zip(rseqs, batch)))
+            ref_rt.check_error()
+            return ref_rt.tensor("logits")[:3].float().clone()
+    else:
+        oracle = moe.MoeOracle(cfg, weights, device="cuda")
+        caches = [oracle.new_cache() for _ in prompts]
+        want = lambda batch: torch.stack([oracle.forward(p, c)[-1] for p, c in zip(batch, caches)])
+    refs = want(prompts)
     first = eng.step(list(zip(seqs, prompts)))
-    diffs = []
-    logits = rt.tensor("logits")[:3].float()
-    for i, (p, c) in enumerate(zip(prompts, caches)):
-        diffs.append((logits[i] - oracle.forward(p, c)[-1]).abs())
+    diffs = [(rt.tensor("logits")[:3].float() - refs).abs()]
     toks = [f[0] for f in first]
     for _ in range(4):                                                   # the same number of steps on every rank
-        refs = [oracle.forward([t], c)[-1] for t, c in zip(toks, caches)]
+        refs = want([[t] for t in toks])
         nxt = eng.step([(s, [t]) for s, t in zip(seqs, toks)])
-        logits = rt.tensor("logits")[:3].float()
-        diffs += [(logits[i] - refs[i]).abs() for i in range(3)]
+        diffs.append((rt.tensor("logits")[:3].float() - refs).abs())
         toks = [n[0] for n in nxt]
     rt.check_error()
-    worst, mean = max(float(d.max()) for d in diffs), max(float(d.mean()) for d in diffs)
+    worst, mean = max(float(d.max()) for d in diffs), max(float(d.mean(-1).max()) for d in diffs)
     # bf16 against the fp32 oracle with std 0.05 weights: the mean difference sits at 0.01-0.05 depending on the prompts
     ok = torch.tensor([int(worst < 0.3 and mean < 0.08)], device=dev)
     if world > 1:
@@ -336,11 +351,13 @@ def main(argv=None) -> int:
         line["by_call_us"] = {"rows_per_rank": tr, **{l: round(sorted(v)[len(v) // 2], 1) for l, v in by.items()}}
     if rank == 0:
         print(json.dumps(line), flush=True)
+    model_ok = True
     if a.model:
-        m = check_model(rank, world, dev, a.traffic)
+        m = check_model(rank, world, dev, a.traffic, mx=a.mx)
+        model_ok = m["ok"]
         if rank == 0:
-            print(json.dumps({"check": "expert_parallel_sharded_decoder", "world": world, **m}), flush=True)
-    allok = all(r["ok"] for r in results)
+            print(json.dumps({"check": "expert_parallel_sharded_decoder" + ("_mx" if a.mx else ""), "world": world, **m}), flush=True)
+    allok = all(r["ok"] for r in results) and model_ok
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

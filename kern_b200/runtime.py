@@ -80,9 +80,10 @@ class Runtime:
             raise FileNotFoundError(f"no safetensors files under {weights}")
         self._rt.load_weights(paths)
 
-    def load_tensors(self, provider) -> None:
+    def load_tensors(self, provider, skip=None) -> None:
         """Bind the weights from tensors already on the device: ``provider(name)`` returns the checkpoint
-        tensor of that name (device-to-device copies by segment, the same `bind` rules as a file load)."""
+        tensor of that name (device-to-device copies by segment, the same `bind` rules as a file load).
+        ``skip(name)``: a buffer bound only to such tensors is left for the caller to fill."""
         ranks = lambda g: self._rt.rank(g)
         pick = lambda t: t if isinstance(t, str) else t["tensors"][ranks(t["group"])]
         rng = lambda r, whole: (0, whole) if r is None else (tuple(r) if isinstance(r, list) else tuple(r["ranges"][ranks(r["group"])]))
@@ -95,6 +96,8 @@ class Runtime:
 
         for name, b in self.doc["buffers"].items():
             if b["kind"] not in ("weight", "source") or b.get("placement") == "host":
+                continue
+            if skip is not None and all(skip(pick(seg["tensor"])) for seg in b["bind"]):
                 continue
             dst = self.tensor(name).view(-1)
             at = 0

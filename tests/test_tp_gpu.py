@@ -171,3 +171,31 @@ def test_expert_parallel_all_to_all(world):
     assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
     line = next(json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))
     assert line["world"] == world and all(r["ok"] for r in line["results"]), line
+
+
+@pytest.mark.parametrize("form", ["bf16", "mx"])
+def test_expert_parallel_fused_one_rank(cuda, form):
+    """Dispatch inside FC1, combine inside FC2, with a group of one (every pull and slot store goes through the peer
+    tables, which hold this rank's own addresses): the layer against the dense mixture at three sizes and as a graph,
+    then the MoE decoder over it. `mx`: MXFP4 expert weights, MXFP8 activations (the block-scaled tcgen05 pair)."""
+    from kern_b200.parallel import ep_check
+
+    assert ep_check.main(["--fused", "--model", "--rows", "8", "200", "64"] + (["--mx"] if form == "mx" else [])) == 0
+
+
+@pytest.mark.parametrize("form", ["bf16", "mx"])
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_fused(world, form):
+    """The fused dispatch / combine layer and the sharded-token decoder on 2 and 4 ranks: rows cross NVLink inside the
+    routed GEMMs (peer loads in FC1's gather warps, peer stores in FC2's epilogue), no barrier kernel, no NCCL call in
+    the layer; guard bands around every allocation stay intact."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29620 + world), "-m", "kern_b200.parallel.ep_check", "--fused", "--model"]
+    p = subprocess.run(cmd + (["--mx"] if form == "mx" else []), cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
+    lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
+    assert lines[0]["world"] == world and all(r["ok"] for r in lines[0]["results"]), lines[0]
+    assert lines[1]["ok"], lines[1]
