@@ -463,6 +463,28 @@ def cmd_server(args) -> int:
         finally:
             launch.shutdown_pp(pipe, procs)
         return 0
+    if getattr(args, "pd", False):
+        # prefill / decode disaggregation: this process is the prefill tier, the decode tier a process on its own GPU
+        from .serve import launch
+
+        if args.model:
+            from .models import registry
+
+            cfg, build, _load, _make = registry.resolve(args.model)
+            doc = build(cfg)
+        else:
+            doc = json.loads(Path(args.manifest).read_text())
+        spec = {"manifest": doc, "weights": args.weights, "model": args.model, "cpu": args.cpu, "tokens": args.capacity or 0,
+                "slots": args.max_seqs or 0}
+        dspec = dict(spec, tokens=args.decode_capacity or spec["tokens"])
+        tier, worker = launch.launch_pd(spec, dspec, chunk=args.chunk, max_seqs=args.max_seqs or None, prefill_gpu=args.gpu or 0,
+                                        decode_gpu=args.decode_gpu)
+        srv = Server(tier, tok, model_name=doc["model"], host=args.host, port=args.port)
+        try:
+            srv.serve_forever()
+        finally:
+            launch.shutdown_pd(tier, worker)
+        return 0
     if args.world > 1:
         # rank processes (one per GPU) behind this head: one tensor-parallel group, or a data-parallel tier of them
         from .serve import launch
@@ -544,6 +566,8 @@ def main(argv=None) -> int:
     s.add_argument("--world", type=int, default=1, help="rank processes (one per GPU)")
     s.add_argument("--tp", type=int, default=1, help="ranks per tensor-parallel group; world / tp groups form a data-parallel tier")
     s.add_argument("--pp", type=int, default=1, help="pipeline stages (one process per GPU; this process is the head): the manifest is cut at layer boundaries")
+    s.add_argument("--pd", action="store_true", help="prefill/decode disaggregation: this process prefills (on --gpu), a decode process on --decode-gpu takes every request over with its first token")
+    s.add_argument("--decode-gpu", type=int, default=1); s.add_argument("--decode-capacity", type=int, help="token capacity of the decode tier's paged states")
     args = ap.parse_args(argv)
     if args.cmd in ("run", "test", "bench", "server", "e2e-logits", "gate"):
         path, cfg = find_config()

@@ -186,6 +186,81 @@ def shutdown_pp(pipe, procs) -> None:
             p.terminate()
 
 
+# ---- prefill / decode disaggregation: this process is the prefill tier, the decode tier a process on its own GPU ----
+def _pd_decode_main(addr, spec: dict, gpu: int, max_seqs: int | None, stop_ids: tuple) -> None:
+    from ..engine import Engine
+    from ..utils.logline import setup_logging
+    from . import pd_serve
+
+    setup_logging()
+    rt = _make_runtime(dict(spec, gpus=1 << 30), gpu, 1)          # `gpu` is the device index itself
+    rt.once()
+    eng = Engine(rt)
+    sock = wire.connect(tuple(addr))
+    max_seq = eng.pool.total_pages * rt.page_unit
+    wire.send(sock, pd_serve.hello_of(rt, spec["manifest"], max_seq, handles=rt.export_states()))
+    calls = pd_serve.decode_loop(sock, eng, max_seqs=max_seqs, stop_ids=stop_ids)
+    if hasattr(rt, "check_error"):
+        rt.check_error()
+    log.info("decode tier made %d decode calls", calls)
+
+
+def launch_pd(spec: dict, decode_spec: dict | None = None, chunk: int | None = None, max_seqs: int | None = None,
+              decode_max_seqs: int | None = None, stop_ids: tuple = (), prefill_gpu: int = 0, decode_gpu: int = 1,
+              timeout: float = 600.0, context: str = "spawn"):
+    """Prefill and decode on two GPUs: THIS process is the prefill tier (its own runtime, pool, prefix cache and
+    scheduler on `prefill_gpu`), the decode tier is a spawned process on `decode_gpu` that exports its pools; a prompt's
+    pages and slot are pushed into the seats the decode tier granted (device copies over NVLink) and the request goes
+    on there. `decode_spec`: the decode tier's own spec (capacity, slots; default: `spec`). With `spec["cpu"]` both
+    tiers are host-memory executors in this process (the decode tier a thread), the frames still travel over a socket.
+    -> (scheduler-like prefill tier, worker). `shutdown_pd` ends it.
+    Reference counterpart: crates/kern-serve/src/lib.rs:317-404 (tiers by flags), pd/handoff.rs, pd/decoder.rs."""
+    import threading
+
+    from ..engine import Engine
+    from . import pd_serve
+
+    dspec = decode_spec or spec
+    lsock = wire.listen()
+    addr = lsock.getsockname()
+    pools = None
+    if spec.get("cpu"):
+        d_rt = _make_runtime(dspec, 0, 1)
+        d_rt.once()
+        d_eng = Engine(d_rt)
+        pools = d_rt.export_states()
+
+        def d_main():
+            sock = wire.connect(tuple(addr))
+            wire.send(sock, pd_serve.hello_of(d_rt, dspec["manifest"], d_eng.pool.total_pages * d_rt.page_unit))
+            pd_serve.decode_loop(sock, d_eng, max_seqs=decode_max_seqs, stop_ids=stop_ids, idle_wait=0.02)
+            sock.close()
+
+        worker = threading.Thread(target=d_main, daemon=True, name="kern-decode-tier")
+    else:
+        ctx = mp.get_context(context)
+        worker = ctx.Process(target=_pd_decode_main, args=(addr, dspec, decode_gpu, decode_max_seqs, tuple(stop_ids)), daemon=True)
+    worker.start()
+    try:
+        rt = _make_runtime(dict(spec, gpus=1 << 30), prefill_gpu, 1)
+        rt.once()
+        lsock.settimeout(timeout)
+        sock = wire.accept(lsock)
+    finally:
+        lsock.close()
+    sched = Scheduler(Engine(rt), chunk=chunk, max_seqs=max_seqs)
+    tier = pd_serve.connect_tiers(sched, rt, spec["manifest"], sock, pools=pools, timeout=timeout)
+    log.info("serving a prefill tier on gpu %d and a decode tier on gpu %d", prefill_gpu, decode_gpu)
+    return tier, worker
+
+
+def shutdown_pd(tier, worker) -> None:
+    tier.close()
+    worker.join(10)
+    if worker.is_alive() and hasattr(worker, "terminate"):
+        worker.terminate()
+
+
 def shutdown(ex, procs) -> None:
     if ex.watch:
         ex.watch.stop()
@@ -199,7 +274,8 @@ def shutdown(ex, procs) -> None:
 def _pp_selftest(argv=None) -> int:
     """`python -m kern_b200.serve.launch --stages S [--cpu]`: a small dense decoder served by a pipeline of S stage
     processes under the scheduler (long prompts in chunks, several requests, decode steps), compared token for token
-    with the same requests on one engine. Prints one JSON line."""
+    with the same requests on one engine; `--pd`: the same requests through a prefill tier and a decode tier on two
+    GPUs (`--cpu`: two host-memory executors). Prints one JSON line."""
     import argparse
     import dataclasses
 
@@ -211,6 +287,7 @@ def _pp_selftest(argv=None) -> int:
 
     ap = argparse.ArgumentParser()
     ap.add_argument("--stages", type=int, default=2)
+    ap.add_argument("--pd", action="store_true", help="a prefill tier and a decode tier instead of a pipeline")
     ap.add_argument("--cpu", action="store_true")
     a = ap.parse_args(argv)
     cfg = dataclasses.replace(dense.TOY if a.cpu else dense.TINY, layers=2 * a.stages, name="tiny-deep")
@@ -245,6 +322,18 @@ def _pp_selftest(argv=None) -> int:
     spec = {"manifest": doc, "cpu": a.cpu, "tokens": tokens, "weights": weights if a.cpu else None}
     if not a.cpu:
         spec["tensors"] = weights
+    if a.pd:
+        # the decode tier holds two sequences at a time: later requests wait for a seat (Busy, then a grant)
+        tier, worker = launch_pd(spec, dict(spec, tokens=cfg.page_size * 8), chunk=chunk, max_seqs=3, decode_max_seqs=2, timeout=60.0)
+        try:
+            got, idle = serve(tier)
+            served = tier.metrics()
+        finally:
+            shutdown_pd(tier, worker)
+        ok = got == want and idle and not worker.is_alive()
+        print(json.dumps({"check": "prefill_decode_tiers_under_scheduler", "ok": ok, "requests": len(prompts),
+                          "tokens": sum(map(len, got)), "prefix_cache_entries": served["prefix_cache"]["entries"]}), flush=True)
+        return 0 if ok else 1
     sched, pipe, procs = launch_pp(spec, a.stages, chunk=chunk, max_seqs=3, timeout=30.0)
     try:
         got, idle = serve(sched)

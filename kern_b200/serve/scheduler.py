@@ -100,6 +100,7 @@ class Scheduler:
         self._last_stats = time.monotonic()
         self._stats_every = stats_every
         self._last_counts = (0, 0)
+        self.on_finish = None        # called with a finished request while its lease is still held (a hand-over to another tier)
 
     # ---- the three calls of the Scheduler interface: submit / step / metrics ----
     def submit(self, req: Request) -> None:
@@ -230,6 +231,8 @@ class Scheduler:
     def _finish(self, req: Request, why: str, keep: bool = True) -> None:
         req.finished = why
         self.running.remove(req)
+        if self.on_finish is not None and req.seq is not None:
+            self.on_finish(req)
         if keep:
             self._keep(req)
         elif req.seq is not None:

@@ -202,3 +202,37 @@ def test_agent_traffic_replay_reuses_prefixes_and_is_exact(toy):
     assert n_out is not None
     prompt = s0.history[: len(s0.history) - n_out]
     assert alone(make, prompt, n_out) == s0.history[len(prompt):]
+
+
+def test_http_front_over_prefill_and_decode_tiers(toy):
+    """The OpenAI-style front over `launch_pd`: completions come out of the decode tier, token for token those of one
+    engine; a repeated prompt hits the prefill tier's prefix cache; the metrics page carries the tiers' counters."""
+    from kern_b200.serve import launch
+
+    cfg, make = toy
+    weights = dense.random_weights(cfg, seed=0, std=0.05)
+    spec = {"manifest": dense.build_manifest(cfg), "cpu": True, "weights": weights, "tokens": cfg.page_size * 24}
+    tier, worker = launch.launch_pd(spec, dict(spec, tokens=cfg.page_size * 12), chunk=16, max_seqs=3, decode_max_seqs=2, timeout=60)
+    srv = Server(tier, model_name="toy-pd", port=0).start()
+    base = f"http://127.0.0.1:{srv.port}"
+    try:
+        def post(path, body):
+            req = urllib.request.Request(base + path, data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+            return urllib.request.urlopen(req, timeout=60)
+
+        prompt = list(range(3, 40))
+        want = alone(make, prompt, 6)
+        out = json.load(post("/v1/completions", {"prompt": prompt, "max_tokens": 6, "return_token_ids": True, "ignore_eos": True}))
+        assert out["choices"][0]["token_ids"] == want and out["usage"]["completion_tokens"] == 6
+        again = json.load(post("/v1/completions", {"prompt": prompt, "max_tokens": 6, "return_token_ids": True, "ignore_eos": True}))
+        assert again["choices"][0]["token_ids"] == want and again["usage"]["prompt_tokens_details"]["cached_tokens"] == 32
+        chunks = post("/v1/completions", {"prompt": prompt[:9], "max_tokens": 4, "stream": True, "return_token_ids": True,
+                                          "ignore_eos": True}).read().decode()
+        events = [json.loads(l[6:]) for l in chunks.splitlines() if l.startswith("data: {")]
+        ids = [t for e in events for t in e["choices"][0].get("token_ids", [])]
+        assert ids == alone(make, prompt[:9], 4) and chunks.rstrip().endswith("data: [DONE]")
+        assert tier.metrics()["pd"]["decoding"] == 0 and tier.idle()
+    finally:
+        srv.stop()
+        launch.shutdown_pd(tier, worker)
+    assert not worker.is_alive()

@@ -199,3 +199,18 @@ def test_expert_parallel_fused(world, form):
     lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
     assert lines[0]["world"] == world and all(r["ok"] for r in lines[0]["results"]), lines[0]
     assert lines[1]["ok"], lines[1]
+
+
+@pytest.mark.parametrize("shape", ["pd", "pp"])
+def test_deployments_from_the_launcher(shape):
+    """`serve/launch.py` on two GPUs: a prefill tier in the launching process with a decode tier as a spawned process
+    (pools exported and mapped, pages pushed by device copies), and a pipeline with a process per stage; both under the
+    scheduler, token for token the output of one engine."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "kern_b200.serve.launch"] + (["--pd"] if shape == "pd" else ["--stages", "2"])
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
+    line = json.loads([l for l in p.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["ok"] and line["tokens"] == 20, line
