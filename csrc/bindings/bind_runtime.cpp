@@ -132,6 +132,8 @@ void bind_runtime(py::module_& m) {
         r.connect(group, ms);
       })
       .def("check_guards", &Runtime::check_guards)
+      .def("checked_failures", &Runtime::checked_failures)
+      .def_property_readonly("checked", &Runtime::checked)
       .def("export_region", [](Runtime& r, const std::string& name) { return py::bytes(r.export_region(name)); })
       .def("import_region", [](Runtime& r, py::bytes h) { return r.import_region(std::string(h)); })
       .def("push_unit", &Runtime::push_unit)

@@ -54,6 +54,7 @@ extern "C" __global__ void __launch_bounds__(128)
       const int kvh = is_k ? h - hq : h - hq - hk;
       dst = kv + (size_t)page * page_elems + ((size_t)(is_k ? 0 : 1) * hk + kvh) * page_size * d +
             (size_t)off * d;
+      if (!KERN_CHECK(dst, (size_t)d * 2, SITE_KV_APPEND)) continue;
     }
     if (!is_q && !is_k) {  // v: straight copy
       for (int i = lane; i < d / 8; i += 32)

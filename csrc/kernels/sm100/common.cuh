@@ -30,6 +30,51 @@ KERN_DEVICE void set_error(int* err, int code) {
   if (err != nullptr) atomicCAS(err, 0, code);
 }
 
+// ---- checked builds -------------------------------------------------------------------------
+// With -DKERN_CHECKED every module carries a table of the address ranges the runtime allocated or mapped (sorted by
+// base, filled when the programs are compiled and again when peers connect). KERN_CHECK(p, bytes, site) is then a
+// binary search: an access of `bytes` at `p` that lies in no range is recorded (first one wins: site and address) and
+// the macro is false, so the caller skips the access instead of faulting. The sites are the accesses whose address
+// comes from data — a token id, a slot, a page, a permutation entry, a peer table. Without the define the macro is
+// the constant true and the table does not exist. An empty table (the module loaded by something other than the
+// runtime) passes everything.
+#ifdef KERN_CHECKED
+}  // namespace kern
+extern "C" {
+__device__ unsigned long long kern_spans[2 * 2048];
+__device__ int kern_span_count;
+__device__ unsigned long long kern_check_fail[2];
+}
+namespace kern {
+__device__ __noinline__ bool checked_access(const void* p, unsigned long long bytes, int site) {
+  const unsigned long long a = reinterpret_cast<unsigned long long>(p);
+  const int n = kern_span_count;
+  if (n == 0) return true;
+  int lo = 0, hi = n;                      // the last range whose base is <= a
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (kern_spans[2 * mid] <= a) lo = mid + 1; else hi = mid;
+  }
+  if (lo > 0 && a + bytes <= kern_spans[2 * (lo - 1) + 1]) return true;
+  if (atomicCAS(&kern_check_fail[0], 0ull, ((unsigned long long)site << 32) | 1ull) == 0ull) kern_check_fail[1] = a;
+  return false;
+}
+#define KERN_CHECK(p, bytes, site) ::kern::checked_access((p), (bytes), (site))
+#else
+#define KERN_CHECK(p, bytes, site) true
+#endif
+// check sites
+enum : int {
+  SITE_EMBED_ROW = 1,       // embedding row of a token id
+  SITE_KV_APPEND = 2,       // the cache row a new token's K / V go to
+  SITE_MOE_GATHER = 3,      // expert-sorted row written from a permutation entry
+  SITE_MOE_COMBINE = 4,     // expert-sorted row read back through the permutation
+  SITE_EP_PULL = 5,         // a routed row pulled from its home rank
+  SITE_EP_SLOT = 6,         // a result row stored into its (token, choice) slot
+  SITE_STATE_SLOT = 7,      // a per-sequence recurrent state addressed by slot
+  SITE_LATENT_ROW = 8,      // a latent cache row addressed through a page table
+};
+
 // ---- address helpers ------------------------------------------------------------------------
 KERN_DEVICE uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

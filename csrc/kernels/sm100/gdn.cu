@@ -61,7 +61,8 @@ extern "C" __global__ void __launch_bounds__(256)
 #pragma unroll
     for (int i = 0; i < 4; ++i) hist[d][i] = 0.f;
   auto seed = [&](int r) {
-    const int line = lines[s];
+    int line = lines[s];
+  if (line > 0 && !KERN_CHECK(state + (size_t)line * line_bytes, (size_t)line_bytes, SITE_STATE_SLOT)) line = 0;   // checked builds: a slot outside the pool is the null line
     const __nv_bfloat16* win = reinterpret_cast<const __nv_bfloat16*>(state + (size_t)line * line_bytes);
 #pragma unroll
     for (int d = 1; d <= 3; ++d) {
@@ -109,7 +110,9 @@ extern "C" __global__ void __launch_bounds__(256)
     const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
     o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
   };
-  const int line = lines[s], keep = width - 1;
+  int line = lines[s];
+  if (line > 0 && !KERN_CHECK(state + (size_t)line * line_bytes, (size_t)line_bytes, SITE_STATE_SLOT)) line = 0;   // checked builds: a slot outside the pool is the null line
+  const int keep = width - 1;
   __nv_bfloat16* win = reinterpret_cast<__nv_bfloat16*>(state + (size_t)line * line_bytes);
   float hist[3][4];        // right-aligned: hist[2] is the previous row
   uint2 raw[3];
@@ -157,7 +160,8 @@ extern "C" __global__ void __launch_bounds__(256)
   const int s = blockIdx.x;
   const int c = blockIdx.y * 256 + threadIdx.x;
   if (s >= seqs || c >= conv_dim) return;
-  const int line = lines[s];
+  int line = lines[s];
+  if (line > 0 && !KERN_CHECK(state + (size_t)line * line_bytes, (size_t)line_bytes, SITE_STATE_SLOT)) line = 0;   // checked builds: a slot outside the pool is the null line
   const int r0 = cu_q ? cu_q[s] : s, r1 = cu_q ? cu_q[s + 1] : s + 1;
   const int n = r1 - r0, keep = width - 1;
   if (line <= 0 || n <= 0) return;
@@ -209,7 +213,8 @@ __device__ __forceinline__ void gdn_body(const __nv_bfloat16* qkv, const __nv_bf
   constexpr int PARTS = DV / ROWS;
   const int h = blockIdx.x / PARTS, row0 = (blockIdx.x % PARTS) * ROWS, s = blockIdx.y;
   if (s >= seqs) return;
-  const int line = lines[s];
+  int line = lines[s];
+  if (line > 0 && !KERN_CHECK(state + (size_t)line * line_bytes, (size_t)line_bytes, SITE_STATE_SLOT)) line = 0;   // checked builds: a slot outside the pool is the null line
   const int r0 = cu_q ? cu_q[s] : s, r1 = cu_q ? cu_q[s + 1] : s + 1;
   if (r1 <= r0) return;
   const int kh = h / (hv / hk);
@@ -449,7 +454,8 @@ __device__ __forceinline__ void gdn_step_body(const __nv_bfloat16* qkv, const __
   const int h = blockIdx.x, s = blockIdx.y;
   if (s >= seqs) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int line = lines[s];
+  int line = lines[s];
+  if (line > 0 && !KERN_CHECK(state + (size_t)line * line_bytes, (size_t)line_bytes, SITE_STATE_SLOT)) line = 0;   // checked builds: a slot outside the pool is the null line
   uint8_t* Sg8 = state + (size_t)line * line_bytes + s_offset + (size_t)h * STATE_BYTES;
   if (tid == 0) {
     mbar_init(bar, 1);

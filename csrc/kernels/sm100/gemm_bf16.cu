@@ -338,8 +338,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
                                  (size_t)(tok % ep.rows_per_rank) * row_vecs * 16;
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(ep.xg) + (size_t)r * row_vecs * 16);
             uint4 xa[8], xb[8];
-            ld8(src, lane, xa);
-            for (int v0 = lane; v0 < row_vecs; v0 += 256) {
+            const bool ok_row = KERN_CHECK(src, (size_t)row_vecs * 16, SITE_EP_PULL) && KERN_CHECK(dst, (size_t)row_vecs * 16, SITE_MOE_GATHER);
+            if (ok_row) ld8(src, lane, xa);
+            for (int v0 = lane; ok_row && v0 < row_vecs; v0 += 256) {
               if (v0 + 256 < row_vecs) ld8(src, v0 + 256, xb);
 #pragma unroll
               for (int q = 0; q < 8; ++q)
@@ -509,6 +510,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tma_a, const CUtens
               if (tok >= 0)
                 dst = ep.ret_peers[tok / ep.rows_per_rank] +
                       2ull * (((size_t)(tok % ep.rows_per_rank) * ep.k + ep.row_choice[row]) * (size_t)N);
+              if (dst != 0 && !KERN_CHECK(reinterpret_cast<const void*>(dst), (size_t)N * 2, SITE_EP_SLOT)) dst = 0;
             }
           } else if (row < row_end) {
             int j, owner, idx;

@@ -175,6 +175,7 @@ extern "C" __global__ void __launch_bounds__(128)
   if (r < 0) return;
   const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(i / k) * hidden);
   uint4* dst = reinterpret_cast<uint4*>(x_perm + (size_t)r * hidden);
+  if (!KERN_CHECK(dst, (size_t)hidden * 2, SITE_MOE_GATHER)) return;
   for (int v = threadIdx.x; v < hidden / 8; v += 128) dst[v] = src[v];
 }
 
@@ -196,7 +197,8 @@ extern "C" __global__ void __launch_bounds__(128)
     if (shared) add(reinterpret_cast<const uint4*>(shared + (size_t)t * hidden)[v], 1.f);
     for (int j = 0; j < k; ++j) {
       const int r = perm[(size_t)t * k + j];
-      if (r >= 0) add(reinterpret_cast<const uint4*>(y_perm + (size_t)r * hidden)[v], topk_w[(size_t)t * k + j]);
+      if (r >= 0 && KERN_CHECK(y_perm + (size_t)r * hidden, (size_t)hidden * 2, SITE_MOE_COMBINE))
+        add(reinterpret_cast<const uint4*>(y_perm + (size_t)r * hidden)[v], topk_w[(size_t)t * k + j]);
     }
     uint4 o;
     o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
@@ -241,6 +243,7 @@ extern "C" __global__ void __launch_bounds__(128)
   const int t = i / k;
   const uint8_t* src = reinterpret_cast<const uint8_t*>(x_peers[t / rows_per_rank]) + (size_t)(t % rows_per_rank) * hidden * 2;
   uint4* dst = reinterpret_cast<uint4*>(x_perm + (size_t)r * hidden);
+  if (!KERN_CHECK(src, (size_t)hidden * 2, SITE_EP_PULL) || !KERN_CHECK(dst, (size_t)hidden * 2, SITE_MOE_GATHER)) return;
   const int vecs = hidden / 8;
   for (int v0 = threadIdx.x; v0 < vecs; v0 += 128 * 4) {
     uint4 x[4];
@@ -272,6 +275,7 @@ extern "C" __global__ void __launch_bounds__(128)
   uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(ret_peers[t / rows_per_rank]) +
                                         ((size_t)(t % rows_per_rank) * k + j) * hidden * 2);
   const uint4* src = reinterpret_cast<const uint4*>(y_perm + (size_t)r * hidden);
+  if (!KERN_CHECK(dst, (size_t)hidden * 2, SITE_EP_SLOT) || !KERN_CHECK(src, (size_t)hidden * 2, SITE_MOE_COMBINE)) return;
   for (int v = threadIdx.x; v < hidden / 8; v += 128) dst[v] = src[v];
 }
 

@@ -21,6 +21,7 @@ KERN_DEVICE void embedding_body(const IdT* __restrict__ ids, const __nv_bfloat16
   }
   const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)id * hidden);
   uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * hidden);
+  if (!KERN_CHECK(src, (size_t)hidden * 2, SITE_EMBED_ROW)) return;
   for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
 }
 

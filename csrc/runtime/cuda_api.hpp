@@ -34,6 +34,7 @@ namespace kern {
   X(cuModuleLoadData)               \
   X(cuModuleUnload)                 \
   X(cuModuleGetFunction)            \
+  X(cuModuleGetGlobal)              \
   X(cuModuleGetFunctionCount)       \
   X(cuModuleEnumerateFunctions)     \
   X(cuFuncGetName)                  \

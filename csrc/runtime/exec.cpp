@@ -42,6 +42,7 @@ void Runtime::compile_all() {
     lane_events_.push_back(dev_->event_create(false));
   }
   if (lane_events_.size() < lanes) lane_events_.push_back(dev_->event_create(false));   // one for lane 0
+  publish_spans();
   compiled_ = true;
 }
 
@@ -723,6 +724,7 @@ void Runtime::connect(const std::string& group, const std::vector<std::map<std::
     dev_->stream_sync(stream_);
     imported_[kv.first] = addrs;
   }
+  publish_spans();
   if (nccl_groups().count(group) && !nccl_comms_.count(group)) {
     // every member calls this with the same offers: member 0's id joins them into one communicator
     auto h = members.at(0).find("nccl_id." + group);

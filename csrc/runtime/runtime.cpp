@@ -1,6 +1,9 @@
 // Runtime: load, allocation, weights (see runtime.hpp). Compilation and execution live in exec.cpp.
 #include "runtime.hpp"
 
+#include <algorithm>
+#include <cstdio>
+
 #include <cstdio>
 #include <cstdlib>
 
@@ -123,6 +126,14 @@ void Runtime::load_modules() {
       throw std::runtime_error("module `" + kv.first + "` (" + kv.second.source + "): no file under " + kernels_dir_ +
                                " has sha256 " + kv.second.sha256);
     modules_[kv.first] = dev_->load_module(read_file(it->second));
+    // a checked build's module carries the range table and the failure record
+    auto& cu = Cuda::get();
+    CUdeviceptr spans = 0, count = 0, fail = 0;
+    size_t sb = 0, cb = 0, fb = 0;
+    if (cu.cuModuleGetGlobal_ && cu.cuModuleGetGlobal_(&spans, &sb, modules_[kv.first], "kern_spans") == CUDA_SUCCESS &&
+        cu.cuModuleGetGlobal_(&count, &cb, modules_[kv.first], "kern_span_count") == CUDA_SUCCESS &&
+        cu.cuModuleGetGlobal_(&fail, &fb, modules_[kv.first], "kern_check_fail") == CUDA_SUCCESS)
+      checked_.push_back({kv.first, (uint64_t)spans, (uint64_t)count, (uint64_t)fail, (uint64_t)sb / 16});
   }
   // the built-in GEMM serves the `extern:cublaslt_*` / `extern:cublas_*` vocabulary
   bool needs_gemm = false;
@@ -243,6 +254,58 @@ void Runtime::allocate() {
       a.ptr = zero_alloc(a.bytes, kv.first);
     }
   }
+}
+
+void Runtime::publish_spans() {
+  if (checked_.empty()) return;
+  std::vector<std::pair<uint64_t, uint64_t>> spans;
+  auto add = [&](uint64_t p, uint64_t bytes) {
+    if (p && bytes) spans.push_back({p, p + (bytes + 255) / 256 * 256});
+  };
+  add(err_word_, 256);
+  for (auto& kv : buffers_) add(kv.second.ptr, kv.second.bytes);
+  for (auto& o : scratch_) for (auto& kv : o.second) add(kv.second.ptr, kv.second.bytes);
+  for (auto& kv : states_) add(kv.second.ptr, kv.second.bytes);
+  for (auto& kv : imported_) {          // a peer's copy of an exported buffer is as large as this rank's own
+    auto b = m_.buffers.find(kv.first);
+    if (b == m_.buffers.end() || !b->second.of) continue;
+    auto own = buffers_.find(*b->second.of);
+    if (own == buffers_.end()) continue;
+    for (uint64_t a : kv.second) add(a, own->second.bytes);
+  }
+  std::sort(spans.begin(), spans.end());
+  std::vector<uint64_t> flat;
+  for (auto& s : spans) { flat.push_back(s.first); flat.push_back(s.second); }
+  dev_->make_current();
+  for (auto& c : checked_) {
+    if (spans.size() > c.capacity)
+      throw std::runtime_error("checked module `" + c.name + "`: " + std::to_string(spans.size()) + " address ranges, room for " + std::to_string(c.capacity));
+    const int32_t n = (int32_t)spans.size();
+    dev_->h2d(c.spans, flat.data(), flat.size() * 8, stream_);
+    dev_->h2d(c.count, &n, 4, stream_);
+  }
+  dev_->stream_sync(stream_);
+}
+
+std::vector<std::string> Runtime::checked_failures() {
+  std::vector<std::string> out;
+  if (checked_.empty()) return out;
+  dev_->make_current();
+  dev_->stream_sync(stream_);
+  for (auto& c : checked_) {
+    uint64_t rec[2] = {0, 0};
+    dev_->d2h(rec, c.fail, 16, stream_);
+    dev_->stream_sync(stream_);
+    if (rec[0] == 0) continue;
+    char buf[160];
+    std::snprintf(buf, sizeof buf, "module `%s`: check site %llu caught an access at 0x%llx outside every allocation (skipped)",
+                  c.name.c_str(), (unsigned long long)(rec[0] >> 32), (unsigned long long)rec[1]);
+    out.push_back(buf);
+    const uint64_t zero[2] = {0, 0};
+    dev_->h2d(c.fail, zero, 16, stream_);
+    dev_->stream_sync(stream_);
+  }
+  return out;
 }
 
 std::vector<std::string> Runtime::check_guards() {

@@ -155,6 +155,13 @@ class Runtime {
   // Names of the allocations whose canary bands no longer hold their pattern ("x (after)", "op.scratch (before)"); empty
   // when guard bands are off. Synchronises the stream.
   std::vector<std::string> check_guards();
+  // Checked kernel builds (compiled with KERN_CHECKED): every module of such a build carries a table of the address
+  // ranges its kernels may touch, which the runtime fills with every allocation it made or mapped (buffers, scratch,
+  // states, peers' regions, bound host states); a checked access outside every range is skipped by the kernel and
+  // recorded in the module. `checked_failures` reads the records: one line per module that caught something.
+  void publish_spans();
+  std::vector<std::string> checked_failures();
+  bool checked() const { return !checked_.empty(); }
   bool peers_connected() const;
   // Another process's pool, for pushing pages and slots into it (prefill tier -> decode tier): the owner exports the
   // region of a state, the pusher maps it and copies whole units (a page of a paged state, a slot of a per-sequence one).
@@ -200,6 +207,8 @@ class Runtime {
   std::vector<uint64_t> imported_ptrs_;
   struct Guard { std::string name; uint64_t base, bytes; };     // base = start of the leading band; bytes = payload size
   std::vector<Guard> guards_;
+  struct CheckedModule { std::string name; uint64_t spans, count, fail; uint64_t capacity; };
+  std::vector<CheckedModule> checked_;
   uint64_t guard_ = 0;                                            // band size in bytes (0: off)
   std::map<std::string, void*> nccl_comms_;      // group -> communicator of the `extern:nccl_*` launches
   std::map<std::string, NcclUniqueId> nccl_ids_;  // ids this rank (index 0 of the group) created and offers

@@ -27,6 +27,7 @@ PKG = ROOT / "kern_b200"
 CSRC = ROOT / "csrc"
 KSRC = CSRC / "kernels" / "sm100"
 KOUT = PKG / "kernels"
+KOUT_CHECKED = PKG / "kernels_checked"
 BUILD = ROOT / "build"
 
 NVCC = os.environ.get("KERN_NVCC", "/usr/local/cuda/bin/nvcc")
@@ -59,8 +60,20 @@ def kernel_sources() -> list[Path]:
     return sorted(KSRC.glob("*.cu"))
 
 
-def build_kernels(force: bool = False, verbose: bool = False) -> dict[str, dict]:
-    """Compile every kernel source to ``kernels/<stem>.cubin``; return the module index."""
+def checked() -> bool:
+    """KERN_B200_CHECKED=1 selects the checked kernel build (``kernels_checked/``: every data-derived address is
+    looked up in the runtime's table of allocations before it is used; common.cuh, KERN_CHECK)."""
+    return os.environ.get("KERN_B200_CHECKED", "0") not in ("", "0")
+
+
+def kernels_dir(checked_build: bool | None = None) -> Path:
+    return KOUT_CHECKED if (checked() if checked_build is None else checked_build) else KOUT
+
+
+def build_kernels(force: bool = False, verbose: bool = False, checked_build: bool = False) -> dict[str, dict]:
+    """Compile every kernel source to ``kernels/<stem>.cubin`` (``kernels_checked/`` with -DKERN_CHECKED for the checked
+    build); return the module index."""
+    KOUT = kernels_dir(checked_build)
     KOUT.mkdir(parents=True, exist_ok=True)
     headers = sorted(KSRC.glob("*.cuh"))
     jobs = []
@@ -73,8 +86,8 @@ def build_kernels(force: bool = False, verbose: bool = False) -> dict[str, dict]
 
     def one(job):
         src, out = job
-        cmd = [NVCC, *ARCH, *NVCC_FLAGS, "-cubin", "-I", str(KSRC), "-o", str(out), str(src)]
-        text = _run(cmd, BUILD / "ptxas" / (src.stem + ".log"))
+        cmd = [NVCC, *ARCH, *NVCC_FLAGS, *(["-DKERN_CHECKED"] if checked_build else []), "-cubin", "-I", str(KSRC), "-o", str(out), str(src)]
+        text = _run(cmd, BUILD / ("ptxas_checked" if checked_build else "ptxas") / (src.stem + ".log"))
         if verbose:
             print(text)
 
@@ -181,6 +194,8 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
         fcntl.flock(lock, fcntl.LOCK_EX)
         try:
             build_kernels(force, verbose)
+            if checked() or "--checked" in sys.argv:
+                build_kernels(force, verbose, checked_build=True)
             build_native(force)
             build_cli(force)
             build_runner(force)

@@ -9,12 +9,14 @@ program helper), tools/once.py (load programs), tools/toy/gen.py:238-246 (safete
 from __future__ import annotations
 
 import json
+import os
 import struct
 from pathlib import Path
 
 import torch
 
-KERNELS_DIR = Path(__file__).resolve().parent.parent / "kernels"
+# KERN_B200_CHECKED=1: the checked kernel build (its own directory, its own hashes in the manifests' module pins)
+KERNELS_DIR = Path(__file__).resolve().parent.parent / ("kernels_checked" if os.environ.get("KERN_B200_CHECKED", "0") not in ("", "0") else "kernels")
 SMS = 148                      # B200: the persistent kernels launch one CTA per SM
 I64_MAX = (1 << 63) - 1
 I32_MAX = (1 << 31) - 1

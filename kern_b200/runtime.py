@@ -275,6 +275,10 @@ class Runtime:
                 code = int(self.read(f["name"], 1)[0])
                 if code:
                     raise RuntimeError(f"device error word `{f['name']}` = {code}")
+        if self._rt.checked:          # a checked kernel build: accesses it refused since the last call
+            caught = list(self._rt.checked_failures())
+            if caught:
+                raise RuntimeError("checked kernels skipped accesses: " + "; ".join(caught))
 
     # ---- pool support ----
     def zero_slot(self, slot: int) -> None:
