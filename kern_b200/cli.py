@@ -477,8 +477,17 @@ def cmd_server(args) -> int:
         spec = {"manifest": doc, "weights": args.weights, "model": args.model, "cpu": args.cpu, "tokens": args.capacity or 0,
                 "slots": args.max_seqs or 0}
         dspec = dict(spec, tokens=args.decode_capacity or spec["tokens"])
+        extra = {}
+        if args.dcp > 1:
+            # the decode tier is a context-parallel group: positions dealt over --dcp ranks on GPUs decode-gpu, decode-gpu + 1, ..
+            from .models import dense, dense_dcp
+
+            if not args.model or not isinstance(cfg, dense.DenseConfig):
+                raise SystemExit("--dcp needs --model of the dense family (the member manifest is generated from its config)")
+            dspec["manifest"] = dense_dcp.build_manifest_dcp(cfg, args.dcp)
+            extra = {"decode_gpus": [args.decode_gpu + i for i in range(args.dcp)], "dealer": dense_dcp.dealer(cfg)}
         tier, worker = launch.launch_pd(spec, dspec, chunk=args.chunk, max_seqs=args.max_seqs or None, prefill_gpu=args.gpu or 0,
-                                        decode_gpu=args.decode_gpu)
+                                        decode_gpu=args.decode_gpu, **extra)
         srv = Server(tier, tok, model_name=doc["model"], host=args.host, port=args.port)
         try:
             srv.serve_forever()
@@ -567,6 +576,7 @@ def main(argv=None) -> int:
     s.add_argument("--tp", type=int, default=1, help="ranks per tensor-parallel group; world / tp groups form a data-parallel tier")
     s.add_argument("--pp", type=int, default=1, help="pipeline stages (one process per GPU; this process is the head): the manifest is cut at layer boundaries")
     s.add_argument("--pd", action="store_true", help="prefill/decode disaggregation: this process prefills (on --gpu), a decode process on --decode-gpu takes every request over with its first token")
+    s.add_argument("--dcp", type=int, default=1, help="with --pd: the decode tier is a context-parallel group of this many ranks (dense family)")
     s.add_argument("--decode-gpu", type=int, default=1); s.add_argument("--decode-capacity", type=int, help="token capacity of the decode tier's paged states")
     args = ap.parse_args(argv)
     if args.cmd in ("run", "test", "bench", "server", "e2e-logits", "gate"):

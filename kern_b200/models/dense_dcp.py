@@ -44,3 +44,34 @@ def dealt_slot(position: int, pages: list[int], page_size: int, rank: int, world
         return -1
     li = position // world
     return pages[li // page_size] * page_size + li % page_size
+
+
+def dealer(cfg: dense.DenseConfig):
+    """How a prefill tier hands a prompt to a decode group of this family: the KV pages are [k|v][kv_head][page][d], not
+    token-contiguous, so the rows are dealt by `kern_deal_rows_bf16` reading the prefill runtime's pool and writing every
+    member's mapped pool (plain stores into peer memory), one launch per layer and member. -> f(rt, mirrors, src_pages,
+    seats, length) for `serve/pd_serve.py`."""
+    import torch
+
+    from ..ops import attention as A
+    from ..runtime import _CudaView
+
+    def run(rt, mirrors, src_pages: list[int], seats: list[dict], length: int) -> None:
+        dev = torch.device(f"cuda:{rt.gpu}")
+        W = cfg.table_width
+        world = len(seats)
+        src_table = torch.zeros(1, W, dtype=torch.int32, device=dev)
+        src_table[0, : len(src_pages)] = torch.tensor(src_pages, dtype=torch.int32)
+        lens = torch.tensor([length], dtype=torch.int32, device=dev)
+        rt.synchronize()                              # the prompt's rows are in this tier's pool
+        with torch.cuda.device(dev):
+            for m, seat in enumerate(seats):
+                dst_table = torch.zeros(1, W, dtype=torch.int32, device=dev)
+                dst_table[0, : len(seat["pages"])] = torch.tensor(seat["pages"], dtype=torch.int32)
+                for i in range(cfg.layers):
+                    name = f"kv.l{i}"
+                    dst = torch.as_tensor(_CudaView(mirrors.mapped[m][name], (mirrors.sizes[m][name],), "|u1"), device=dev)
+                    A.deal_rows(rt.tensor(name), dst, src_table, dst_table, lens, cfg.kv_heads, cfg.head_dim, cfg.page_size, m, world)
+            torch.cuda.synchronize(dev)               # every member's share has landed before Start leaves
+
+    return run

@@ -66,9 +66,10 @@ class Executor:
         return ans
 
 
-def serve_rank(head: tuple[str, int], rank: int, world: int, make_runtime, watch=None) -> None:
+def serve_rank(head: tuple[str, int], rank: int, world: int, make_runtime, watch=None, export_pools: bool = False) -> None:
     """A rank process's whole life. ``make_runtime() -> runtime`` builds and loads this rank's runtime (its
-    place in every group is ``parallel.group.topology(groups, rank, world)``)."""
+    place in every group is ``parallel.group.topology(groups, rank, world)``). ``export_pools``: the Hello also carries
+    a handle and the size of every state of this rank's pools, for a prefill tier that pushes into them."""
     sock = wire.connect(head)
     try:
         rt = make_runtime()
@@ -78,7 +79,10 @@ def serve_rank(head: tuple[str, int], rank: int, world: int, make_runtime, watch
         sock.close()
         return
     offer = rt.offer() if hasattr(rt, "offer") else {}
-    wire.send(sock, {"hello": {"rank": rank, "pages": rt.pages, "slots": rt.slots, "unit": rt.page_unit, "offer": offer}})
+    hello = {"rank": rank, "pages": rt.pages, "slots": rt.slots, "unit": rt.page_unit, "offer": offer}
+    if export_pools:
+        hello["pools"] = {"handles": rt.export_states(), "sizes": rt.state_bytes()}
+    wire.send(sock, {"hello": hello})
     table = wire.recv(sock)
     if table is None:
         return

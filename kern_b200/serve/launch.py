@@ -40,10 +40,10 @@ def _make_runtime(spec: dict, rank: int, world: int):
         return rt
     from ..runtime import Runtime
 
-    rt = Runtime(doc, weights=spec.get("weights"), gpu=rank % max(1, spec.get("gpus", world)), topology=topo,
-                 tokens=spec.get("tokens") or 0, slots=spec.get("slots", 0))
+    gpu = spec["gpu_of_rank"][rank] if spec.get("gpu_of_rank") else rank % max(1, spec.get("gpus", world))
+    rt = Runtime(doc, weights=spec.get("weights"), gpu=gpu, topology=topo, tokens=spec.get("tokens") or 0, slots=spec.get("slots", 0))
     if spec.get("tensors"):          # a checkpoint handed over as tensors (tests, self-checks)
-        dev = f"cuda:{rank % max(1, spec.get('gpus', world))}"
+        dev = f"cuda:{gpu}"
         rt.load_tensors(lambda name: spec["tensors"][name].to(dev))
     elif spec.get("model") and not spec.get("weights"):
         from ..models import registry
@@ -57,12 +57,14 @@ def _rank_main(addr, rank: int, world: int, spec: dict) -> None:
     from ..utils.logline import setup_logging
 
     setup_logging()
-    serve_rank(tuple(addr), rank, world, lambda: _make_runtime(spec, rank, world))
+    serve_rank(tuple(addr), rank, world, lambda: _make_runtime(spec, rank, world), export_pools=bool(spec.get("export_pools")))
 
 
 def launch(spec: dict, world: int, tp: int = 1, chunk: int | None = None, max_seqs: int | None = None, timeout: float = 600.0,
-           context: str = "spawn"):
-    """-> (scheduler-like, executors, processes). The scheduler-like object has submit / step / idle / abort / metrics / stats."""
+           context: str = "spawn", by_position: bool = False, engine_only: bool = False):
+    """-> (scheduler-like, executors, processes). The scheduler-like object has submit / step / idle / abort / metrics / stats.
+    `by_position`: the group is a decode context-parallel group (a member manifest that deals positions over its ranks);
+    `engine_only`: return the group's engine instead of a scheduler (a decode tier drives it itself)."""
     from .. import _native
 
     m, errs = _native.verify(json.dumps(spec["manifest"]))
@@ -79,10 +81,14 @@ def launch(spec: dict, world: int, tp: int = 1, chunk: int | None = None, max_se
     for p in procs:
         p.start()
     try:
-        ex = Executors(lsock, world, {"tp": tp}, watch=Watch(), timeout=timeout)
+        # the groups the manifest names (a tensor-parallel decoder: {"tp": n}; a context-parallel member: {"dcp": n})
+        groups = dict(spec["manifest"].get("topology", {}).get("groups", {})) or {"tp": tp}
+        ex = Executors(lsock, world, groups, watch=Watch(), timeout=timeout)
     finally:
         lsock.close()
     unit = ex.hellos[0]["unit"]
+    if engine_only:
+        return GroupEngine(ex, protocol, unit, tp=tp, by_position=by_position), ex, procs
     if world // tp > 1:
         sched = DpTier(ex, protocol, unit, tp=tp, chunk=chunk, max_seqs=max_seqs)
     else:
@@ -207,12 +213,16 @@ def _pd_decode_main(addr, spec: dict, gpu: int, max_seqs: int | None, stop_ids: 
 
 def launch_pd(spec: dict, decode_spec: dict | None = None, chunk: int | None = None, max_seqs: int | None = None,
               decode_max_seqs: int | None = None, stop_ids: tuple = (), prefill_gpu: int = 0, decode_gpu: int = 1,
-              timeout: float = 600.0, context: str = "spawn"):
+              timeout: float = 600.0, context: str = "spawn", decode_gpus: list[int] | None = None, dealer=None):
     """Prefill and decode on two GPUs: THIS process is the prefill tier (its own runtime, pool, prefix cache and
     scheduler on `prefill_gpu`), the decode tier is a spawned process on `decode_gpu` that exports its pools; a prompt's
     pages and slot are pushed into the seats the decode tier granted (device copies over NVLink) and the request goes
     on there. `decode_spec`: the decode tier's own spec (capacity, slots; default: `spec`). With `spec["cpu"]` both
     tiers are host-memory executors in this process (the decode tier a thread), the frames still travel over a socket.
+    `decode_gpus` (two or more): the decode tier is a group of rank processes, one per listed GPU, whose manifest
+    (`decode_spec["manifest"]`) deals every sequence's positions over the members (decode context parallelism); its head
+    (seats, steps, accounting) is a thread of this process; `dealer`: how the prompt's rows reach the members when a
+    state's pages are not token-contiguous (`pd_serve`).
     -> (scheduler-like prefill tier, worker). `shutdown_pd` ends it.
     Reference counterpart: crates/kern-serve/src/lib.rs:317-404 (tiers by flags), pd/handoff.rs, pd/decoder.rs."""
     import threading
@@ -224,7 +234,25 @@ def launch_pd(spec: dict, decode_spec: dict | None = None, chunk: int | None = N
     lsock = wire.listen()
     addr = lsock.getsockname()
     pools = None
-    if spec.get("cpu"):
+    if decode_gpus and len(decode_gpus) > 1:
+        from . import pd
+
+        n = len(decode_gpus)
+        d_eng, ex, procs = launch(dict(dspec, export_pools=True, gpu_of_rank=list(decode_gpus)), world=n, tp=n, timeout=timeout,
+                                  context=context, by_position=True, engine_only=True)
+        unit = ex.hellos[0]["unit"]
+        hello = pd.pools_message(dspec["manifest"], unit, n, d_eng.pool.total_pages * unit * n)
+        hello["members"] = [h["pools"] for h in ex.hellos]
+
+        def g_main():
+            sock = wire.connect(tuple(addr))
+            wire.send(sock, {"hello": hello})
+            pd_serve.decode_loop(sock, d_eng, max_seqs=decode_max_seqs, stop_ids=stop_ids, idle_wait=0.02)
+            sock.close()
+
+        thread = threading.Thread(target=g_main, daemon=True, name="kern-decode-group")
+        worker = _DecodeGroup(thread, ex, procs)
+    elif spec.get("cpu"):
         d_rt = _make_runtime(dspec, 0, 1)
         d_rt.once()
         d_eng = Engine(d_rt)
@@ -249,9 +277,26 @@ def launch_pd(spec: dict, decode_spec: dict | None = None, chunk: int | None = N
     finally:
         lsock.close()
     sched = Scheduler(Engine(rt), chunk=chunk, max_seqs=max_seqs)
-    tier = pd_serve.connect_tiers(sched, rt, spec["manifest"], sock, pools=pools, timeout=timeout)
+    tier = pd_serve.connect_tiers(sched, rt, spec["manifest"], sock, pools=pools, timeout=timeout, dealer=dealer)
     log.info("serving a prefill tier on gpu %d and a decode tier on gpu %d", prefill_gpu, decode_gpu)
     return tier, worker
+
+
+class _DecodeGroup:
+    """A decode group's head thread with its rank processes, behind the start / join / is_alive of a worker."""
+
+    def __init__(self, thread, ex, procs):
+        self.thread, self.ex, self.procs = thread, ex, procs
+
+    def start(self) -> None:
+        self.thread.start()
+
+    def join(self, timeout: float | None = None) -> None:
+        self.thread.join(timeout)
+        shutdown(self.ex, self.procs)
+
+    def is_alive(self) -> bool:
+        return self.thread.is_alive() or any(p.is_alive() for p in self.procs)
 
 
 def shutdown_pd(tier, worker) -> None:
@@ -288,6 +333,7 @@ def _pp_selftest(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--stages", type=int, default=2)
     ap.add_argument("--pd", action="store_true", help="a prefill tier and a decode tier instead of a pipeline")
+    ap.add_argument("--dcp", type=int, default=0, help="with --pd: the decode tier is a context-parallel group of this many ranks")
     ap.add_argument("--cpu", action="store_true")
     a = ap.parse_args(argv)
     cfg = dataclasses.replace(dense.TOY if a.cpu else dense.TINY, layers=2 * a.stages, name="tiny-deep")
@@ -324,15 +370,32 @@ def _pp_selftest(argv=None) -> int:
         spec["tensors"] = weights
     if a.pd:
         # the decode tier holds two sequences at a time: later requests wait for a seat (Busy, then a grant)
-        tier, worker = launch_pd(spec, dict(spec, tokens=cfg.page_size * 8), chunk=chunk, max_seqs=3, decode_max_seqs=2, timeout=60.0)
+        if a.dcp > 1:
+            # a decode group that deals positions over its members; its ranks go round the GPUs of the box (rank 0 shares
+            # GPU 0 with the prefill tier when there are no more GPUs than ranks)
+            from ..models import dense_dcp
+
+            n_gpu = max(1, torch.cuda.device_count())
+            first = 1 if n_gpu > a.dcp else 0
+            dspec = dict(spec, manifest=dense_dcp.build_manifest_dcp(cfg, a.dcp), tokens=cfg.page_size * 8)
+            tier, worker = launch_pd(spec, dspec, chunk=chunk, max_seqs=3, decode_max_seqs=2, timeout=120.0,
+                                     decode_gpus=[(first + i) % n_gpu for i in range(a.dcp)], dealer=dense_dcp.dealer(cfg))
+        else:
+            tier, worker = launch_pd(spec, dict(spec, tokens=cfg.page_size * 8), chunk=chunk, max_seqs=3, decode_max_seqs=2, timeout=60.0)
         try:
             got, idle = serve(tier)
             served = tier.metrics()
         finally:
             shutdown_pd(tier, worker)
-        ok = got == want and idle and not worker.is_alive()
-        print(json.dumps({"check": "prefill_decode_tiers_under_scheduler", "ok": ok, "requests": len(prompts),
-                          "tokens": sum(map(len, got)), "prefix_cache_entries": served["prefix_cache"]["entries"]}), flush=True)
+        flat = lambda xs: [t for x in xs for t in x]
+        agree = sum(int(x == y) for x, y in zip(flat(got), flat(want)))
+        # a context-parallel group merges partial attention in another order: the first token of every request (the prefill
+        # tier's) is exact, the decode tier's may differ where two logits are within rounding of each other
+        exact = got == want if a.dcp <= 1 else ([g[:1] for g in got] == [w[:1] for w in want] and agree >= 0.85 * len(flat(want)))
+        ok = exact and idle and not worker.is_alive()
+        print(json.dumps({"check": "prefill_decode_tiers_under_scheduler", "ok": ok, "requests": len(prompts), "decode_ranks": max(1, a.dcp),
+                          "tokens": sum(map(len, got)), "tokens_agree": agree,
+                          "prefix_cache_entries": served["prefix_cache"]["entries"]}), flush=True)
         return 0 if ok else 1
     sched, pipe, procs = launch_pp(spec, a.stages, chunk=chunk, max_seqs=3, timeout=30.0)
     try:

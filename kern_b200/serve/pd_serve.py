@@ -8,6 +8,13 @@
                      (device copies into the mapped pools), Start ->  decode steps
       tokens of every decode step  <----------------------------  Tokens{[req, tok, last]}
 
+A decode tier may be a group that deals every sequence's positions over its members (decode context parallelism, a
+`models/dense_dcp.py` member manifest behind `ranks.GroupEngine(by_position=True)`): the Hello then lists every member's
+handles and sizes, a grant holds one seat per member, and the hand-over deals the prompt's rows — position p to member
+p mod w at local position p // w — by `pd.group_moves` + `pd.Mirrors` (token-contiguous states), or by the model's own
+`dealer` where a page is not token-contiguous (the dense KV pages: `dense_dcp.dealer`, the deal kernel writing into the
+members' mapped pools).
+
 The decode tier says Hello once with its pools' geometry and export handles; the prefill tier checks that its own
 manifest covers them (`pd.cover`) and maps them (`Runtime.map_pool`). The prefill scheduler keeps its prefix cache: a
 finished prompt's pages stay behind as on one GPU. A request whose first token ends it never reaches the decode tier
@@ -82,8 +89,9 @@ class PrefillTier:
     for a seat on the decode tier, are prefilled by the local scheduler, handed over with their first token, and
     receive the decode tier's tokens."""
 
-    def __init__(self, sched: Scheduler, rt, sock, mapped, poll_wait: float = 0.002):
+    def __init__(self, sched: Scheduler, rt, sock, mapped, poll_wait: float = 0.002, mirrors=None, dealer=None):
         self.sched, self.rt, self.sock, self.mapped = sched, rt, sock, mapped
+        self.mirrors, self.dealer = mirrors, dealer      # a decode group that deals positions over its members
         self.hand = pd.Handoffs(sched.pool.unit)
         self.asking: dict[str, Request] = {}       # Reserve sent, no seat yet
         self.prefilling: dict[str, Request] = {}   # in the local scheduler (by the user's request id)
@@ -151,8 +159,17 @@ class PrefillTier:
                 wire.send(self.sock, msg)
             return
         length = inner.seq.length
-        for plan in self.hand.prefilled(inner.id, inner.seq.lease, length):
-            self.rt.push(self.mapped, plan)
+        if self.mirrors is not None:
+            h = self.hand.items[inner.id]
+            lease = inner.seq.lease
+            if self.dealer is not None:
+                self.dealer(self.rt, self.mirrors, list(lease.pages), h.seats, length)
+            else:
+                self.mirrors.push(pd.group_moves(list(lease.pages), h.seats, length, self.pool.unit, lease.slot, by_position=True))
+            h.state = "pushing"
+        else:
+            for plan in self.hand.prefilled(inner.id, inner.seq.lease, length):
+                self.rt.push(self.mapped, plan)
         self.rt.synchronize()                          # the pages are in the decode tier's pool before Start leaves
         smp = user.sampling if getattr(user.sampling, "temperature", 0.0) else None
         wire.send(self.sock, self.hand.pushed(inner.id, first, length, user.max_tokens - 1, tokens=list(user.prompt),
@@ -235,7 +252,7 @@ class PrefillTier:
         self.sock.close()
 
 
-def connect_tiers(sched: Scheduler, rt, doc: dict, sock, pools=None, timeout: float = 600.0) -> PrefillTier:
+def connect_tiers(sched: Scheduler, rt, doc: dict, sock, pools=None, timeout: float = 600.0, dealer=None) -> PrefillTier:
     """Read the decode tier's Hello from `sock`, check that this tier's manifest covers its pools, map them (or take
     `pools`, the decode runtime's exported states, when both tiers share a process) and return the prefill tier."""
     ready, _, _ = select.select([sock], [], [], timeout)
@@ -248,5 +265,8 @@ def connect_tiers(sched: Scheduler, rt, doc: dict, sock, pools=None, timeout: fl
     why = pd.cover(doc, rt.page_unit, hello)
     if why:
         raise ValueError("the prefill manifest does not cover the decode tier's pools: " + "; ".join(why))
+    if "members" in hello:                  # a decode group: every member's pools, mapped once
+        mirrors = pd.Mirrors(rt, [m["handles"] for m in hello["members"]], [m["sizes"] for m in hello["members"]])
+        return PrefillTier(sched, rt, sock, None, mirrors=mirrors, dealer=dealer)
     mapped = rt.map_pool(pools if pools is not None else hello["handles"])
     return PrefillTier(sched, rt, sock, mapped)

@@ -201,15 +201,17 @@ def test_expert_parallel_fused(world, form):
     assert lines[1]["ok"], lines[1]
 
 
-@pytest.mark.parametrize("shape", ["pd", "pp"])
+@pytest.mark.parametrize("shape", ["pd", "pd-dcp", "pp"])
 def test_deployments_from_the_launcher(shape):
     """`serve/launch.py` on two GPUs: a prefill tier in the launching process with a decode tier as a spawned process
-    (pools exported and mapped, pages pushed by device copies), and a pipeline with a process per stage; both under the
-    scheduler, token for token the output of one engine."""
+    (pools exported and mapped, pages pushed by device copies); the same with the decode tier a context-parallel group
+    of two rank processes (the prompt's rows dealt into both members' mapped pools); and a pipeline with a process per
+    stage. All under the scheduler, token for token the output of one engine (the context-parallel group: the first
+    token of every request exactly, the rest up to rounding in the merge of partial attention)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
-    cmd = [sys.executable, "-m", "kern_b200.serve.launch"] + (["--pd"] if shape == "pd" else ["--stages", "2"])
+    cmd = [sys.executable, "-m", "kern_b200.serve.launch"] + {"pd": ["--pd"], "pd-dcp": ["--pd", "--dcp", "2"], "pp": ["--stages", "2"]}[shape]
     p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, (p.stdout[-3000:], p.stderr[-3000:])
     line = json.loads([l for l in p.stdout.splitlines() if l.startswith("{")][-1])
