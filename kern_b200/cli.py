@@ -522,11 +522,39 @@ def cmd_server(args) -> int:
             launch.shutdown(ex, procs)
         return 0
     rt = make_runtime(args)
-    sched = Scheduler(Engine(rt), chunk=args.chunk, max_seqs=args.max_seqs or None, rows=args.rows)
-    srv = Server(sched, tok, model_name=rt.doc["model"], host=args.host, port=args.port)
+    eng, rec, sampler = trace_setup(args, Engine(rt))
+    sched = Scheduler(eng, chunk=args.chunk, max_seqs=args.max_seqs or None, rows=args.rows)
+    srv = Server(sched, tok, model_name=rt.doc["model"], host=args.host, port=args.port, on_rotate=rec.rotate if rec else None)
     logging.getLogger("kern.serve").info("listening host=%s port=%d model=%s", args.host, srv.port, rt.doc["model"])
-    srv.serve_forever()
+    try:
+        srv.serve_forever()
+    finally:
+        if sampler is not None:
+            sampler.stop()
+        if rec is not None:
+            rec.close()
     return 0
+
+
+def trace_setup(args, engine, nvml=None):
+    """--trace-dir: every step of the engine goes to <dir>/date=../rank=0/*.steps.parquet (device and host time, shape,
+    launches); --trace-sample N: every N-th step runs eagerly with an event between calls, its cost by call goes to
+    *.kernels.parquet; --trace-pm-us P: a sampler thread writes clocks, power and the SM / tensor / DRAM busy shares to
+    *.counters.parquet every P microseconds (at least 50). POST /kern/trace/rotate closes the files in use.
+    -> (engine to schedule, recorder | None, sampler | None).
+    Reference counterpart: crates/kern-serve/src/lib.rs:118-137 (--trace, --trace-dir, --trace-pm-us)."""
+    if not getattr(args, "trace_dir", None):
+        return engine, None, None
+    from . import trace
+
+    rec = trace.Recorder(args.trace_dir, rank=0)
+    eng = trace.TracedEngine(engine, rec, sample_every=getattr(args, "trace_sample", 0) or 0)
+    sampler = None
+    pm = getattr(args, "trace_pm_us", 0) or 0
+    if pm and (nvml is not None or not getattr(args, "cpu", False)):
+        sampler = trace.Counters(rec, gpu=getattr(args, "gpu", None) or 0, period=max(50, pm) / 1e6, nvml=nvml)
+        sampler.start()
+    return eng, rec, sampler
 
 
 def main(argv=None) -> int:
@@ -575,6 +603,9 @@ def main(argv=None) -> int:
     s.add_argument("--world", type=int, default=1, help="rank processes (one per GPU)")
     s.add_argument("--tp", type=int, default=1, help="ranks per tensor-parallel group; world / tp groups form a data-parallel tier")
     s.add_argument("--pp", type=int, default=1, help="pipeline stages (one process per GPU; this process is the head): the manifest is cut at layer boundaries")
+    s.add_argument("--trace-dir", help="record every step (and sampled steps by call, and counters) as Parquet files under this directory")
+    s.add_argument("--trace-sample", type=int, default=0, help="with --trace-dir: every N-th step runs eagerly with per-call device times")
+    s.add_argument("--trace-pm-us", type=int, default=0, help="with --trace-dir: sample clocks, power and SM / tensor / DRAM busy shares every this many microseconds (>= 50)")
     s.add_argument("--pd", action="store_true", help="prefill/decode disaggregation: this process prefills (on --gpu), a decode process on --decode-gpu takes every request over with its first token")
     s.add_argument("--dcp", type=int, default=1, help="with --pd: the decode tier is a context-parallel group of this many ranks (dense family)")
     s.add_argument("--decode-gpu", type=int, default=1); s.add_argument("--decode-capacity", type=int, help="token capacity of the decode tier's paged states")

@@ -21,7 +21,10 @@ from pathlib import Path
 
 STEP_FIELDS = ("seq", "t_ns", "program", "groups", "rows", "context", "graph", "device_us", "host_us", "launches")
 KERNEL_FIELDS = ("seq", "call", "label", "op", "start_us", "end_us", "launches")
-COUNTER_FIELDS = ("t_ns", "sm_mhz", "mem_mhz", "gpu_util", "mem_util", "power_w")
+# sm_active / tensor_active / dram_bw: per mille of peak over the sampling interval, from the driver's performance
+# monitoring samples (NVML GPM: SM utilisation, any-tensor-pipe utilisation, DRAM bandwidth utilisation); -1 where the
+# device or the driver does not offer them
+COUNTER_FIELDS = ("t_ns", "sm_mhz", "mem_mhz", "gpu_util", "mem_util", "power_w", "sm_active_pm", "tensor_active_pm", "dram_bw_pm")
 
 
 def shape_of(groups: int, rows: int) -> str:
@@ -54,9 +57,11 @@ class Recorder:
                 at += ms * 1e3
         return seq
 
-    def counters(self, sm_mhz: int, mem_mhz: int, gpu_util: int, mem_util: int, power_w: float) -> None:
+    def counters(self, sm_mhz: int, mem_mhz: int, gpu_util: int, mem_util: int, power_w: float, sm_active_pm: int = -1,
+                 tensor_active_pm: int = -1, dram_bw_pm: int = -1) -> None:
         with self._lock:
-            self._rows["counters"].append((self.clock(), sm_mhz, mem_mhz, gpu_util, mem_util, power_w))
+            self._rows["counters"].append((self.clock(), sm_mhz, mem_mhz, gpu_util, mem_util, power_w, int(sm_active_pm),
+                                           int(tensor_active_pm), int(dram_bw_pm)))
 
     # ---- files ----
     def _path(self, kind: str, now: datetime) -> Path:
@@ -93,13 +98,43 @@ class Recorder:
 
 
 class Counters(threading.Thread):
-    """Samples NVML (read only: clocks, utilisation, power) into a recorder every `period` seconds."""
+    """Samples NVML (read only) into a recorder every `period` seconds: clocks, utilisation, power, and — where the
+    device offers performance-monitoring samples (GPM) — the share of the interval the SMs, the tensor pipes and the DRAM
+    interface were busy, computed by the driver from two consecutive samples. Nothing is set: streaming mode, clocks and
+    every other setting stay as found. Reference counterpart: crates/kern-runtime/src/counters.rs:25-31,93-214 (SM MHz,
+    SM / tensor active per mille, DRAM traffic every --trace-pm-us)."""
 
     def __init__(self, recorder: Recorder, gpu: int = 0, period: float = 0.2, nvml=None):
         super().__init__(name="kern-counters", daemon=True)
         self.rec, self.gpu, self.period = recorder, gpu, max(0.00005, period)
         self._halt = threading.Event()
         self.nvml = nvml
+        self.gpm = False           # whether the last run found performance-monitoring samples
+
+    def _gpm_open(self, nv, h):
+        """Two sample buffers when the device supports GPM, else None."""
+        try:
+            if not nv.nvmlGpmQueryDeviceSupport(h).isSupportedDevice:
+                return None
+            a, b = nv.nvmlGpmSampleAlloc(), nv.nvmlGpmSampleAlloc()
+            nv.nvmlGpmSampleGet(h, a)
+            return [a, b]
+        except Exception:
+            return None
+
+    def _gpm_read(self, nv, h, pair) -> tuple[int, int, int]:
+        """Metrics between the previous sample and a new one (the buffers swap roles)."""
+        nv.nvmlGpmSampleGet(h, pair[1])
+        get = nv.c_nvmlGpmMetricsGet_t()
+        get.version = nv.NVML_GPM_METRICS_GET_VERSION
+        ids = (nv.NVML_GPM_METRIC_SM_UTIL, nv.NVML_GPM_METRIC_ANY_TENSOR_UTIL, nv.NVML_GPM_METRIC_DRAM_BW_UTIL)
+        get.numMetrics = len(ids)
+        get.sample1, get.sample2 = pair[0], pair[1]
+        for i, m in enumerate(ids):
+            get.metrics[i].metricId = m
+        nv.nvmlGpmMetricsGet(get)
+        pair[0], pair[1] = pair[1], pair[0]
+        return tuple(int(round(10.0 * get.metrics[i].value)) for i in range(len(ids)))      # percent -> per mille
 
     def run(self) -> None:
         nv = self.nvml
@@ -107,13 +142,27 @@ class Counters(threading.Thread):
             import pynvml as nv
         nv.nvmlInit()
         h = nv.nvmlDeviceGetHandleByIndex(self.gpu)
+        pair = self._gpm_open(nv, h)
+        self.gpm = pair is not None
         while not self._halt.wait(self.period):
             try:
                 u = nv.nvmlDeviceGetUtilizationRates(h)
+                pm = (-1, -1, -1)
+                if pair is not None:
+                    try:
+                        pm = self._gpm_read(nv, h, pair)
+                    except Exception:
+                        pair, self.gpm = None, False          # not offered after all (permissions, MIG): go on without
                 self.rec.counters(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_MEM),
-                                  u.gpu, u.memory, nv.nvmlDeviceGetPowerUsage(h) / 1000.0)
+                                  u.gpu, u.memory, nv.nvmlDeviceGetPowerUsage(h) / 1000.0, *pm)
             except Exception:
                 self.rec.dropped += 1
+        if pair is not None:
+            for smp in pair:
+                try:
+                    nv.nvmlGpmSampleFree(smp)
+                except Exception:
+                    pass
 
     def stop(self) -> None:
         self._halt.set()

@@ -71,6 +71,70 @@ def test_counters_sampler_reads_only(tmp_path):
     assert len(t["t_ns"]) >= 3 and set(t["sm_mhz"]) == {1965} and t["power_w"][0] == 612.0
 
 
+class FakeNvmlGpm(FakeNvml):
+    """NVML with performance-monitoring samples: a sample is a counter reading; the metrics call turns two of them into
+    percentages. Records every call so the test can see that nothing was set."""
+    NVML_GPM_METRICS_GET_VERSION, NVML_GPM_METRIC_SM_UTIL, NVML_GPM_METRIC_ANY_TENSOR_UTIL, NVML_GPM_METRIC_DRAM_BW_UTIL = 1, 2, 5, 10
+
+    class _Metric:
+        metricId, value = 0, 0.0
+
+    class c_nvmlGpmMetricsGet_t:
+        def __init__(self):
+            self.version = self.numMetrics = 0
+            self.sample1 = self.sample2 = None
+            self.metrics = [FakeNvmlGpm._Metric() for _ in range(16)]
+
+    def __init__(self, supported=True):
+        self.calls, self.n, self.supported = [], 0, supported
+
+    def nvmlGpmQueryDeviceSupport(self, h):
+        self.calls.append("query")
+        return type("S", (), {"isSupportedDevice": int(self.supported)})()
+
+    def nvmlGpmSampleAlloc(self):
+        self.calls.append("alloc")
+        return {"at": None}
+
+    def nvmlGpmSampleGet(self, h, smp):
+        self.n += 1
+        smp["at"] = self.n
+        self.calls.append("sample")
+
+    def nvmlGpmMetricsGet(self, get):
+        assert get.sample2["at"] == get.sample1["at"] + 1          # consecutive samples, older first
+        for i, v in zip(range(get.numMetrics), (93.5, 61.25, 40.0)):
+            assert get.metrics[i].metricId in (2, 5, 10)
+            get.metrics[i].value = v
+        self.calls.append("metrics")
+
+    def nvmlGpmSampleFree(self, smp):
+        self.calls.append("free")
+
+
+def test_counters_sampler_reads_performance_monitoring_samples(tmp_path):
+    """SM / tensor / DRAM busy shares per interval from the driver's samples, written per mille beside the clocks; a device
+    without them gives -1 in those columns. The sampler only reads: no call that sets anything is made."""
+    nv = FakeNvmlGpm()
+    rec = trace.Recorder(tmp_path)
+    c = trace.Counters(rec, period=0.01, nvml=nv)
+    c.start()
+    time.sleep(0.15)
+    c.stop()
+    c.join(2)
+    assert c.gpm and set(nv.calls) == {"query", "alloc", "sample", "metrics", "free"} and nv.calls.count("free") == 2
+    t = pq.ParquetFile(next(p for p in rec.rotate() if ".counters." in p.name)).read().to_pydict()
+    assert len(t["t_ns"]) >= 3 and set(t["sm_active_pm"]) == {935} and set(t["tensor_active_pm"]) == {612} and set(t["dram_bw_pm"]) == {400}
+    rec2 = trace.Recorder(tmp_path / "b")
+    c2 = trace.Counters(rec2, period=0.01, nvml=FakeNvmlGpm(supported=False))
+    c2.start()
+    time.sleep(0.08)
+    c2.stop()
+    c2.join(2)
+    t2 = pq.ParquetFile(next(p for p in rec2.rotate() if ".counters." in p.name)).read().to_pydict()
+    assert not c2.gpm and set(t2["sm_active_pm"]) == {-1} and set(t2["sm_mhz"]) == {1965}
+
+
 def test_kernel_records_fold_into_steps_and_calls():
     """Kernel activity records attributed to (step, call) by the launch plan of each issue: `when` ranges pick the
     launch an issue really makes, a name that does not match the plan stops the folding."""
@@ -101,3 +165,38 @@ def test_kernel_records_fold_into_steps_and_calls():
         trace.fold(records, [("s0", plan4), ("s1", plan1)])        # the plans in the wrong order: names disagree
     with pytest.raises(ValueError, match="short"):
         trace.fold(records[:5], [("s0", plan1)])
+
+
+def test_server_trace_flags_record_steps_calls_and_counters(tmp_path):
+    """`kern server --trace-dir D --trace-sample 2 --trace-pm-us 10000`: the engine the scheduler drives is the traced
+    one, sampled steps carry their cost by call, the sampler thread writes counters, and a rotate closes the files."""
+    from types import SimpleNamespace
+
+    from kern_b200 import cli
+    from kern_b200.cpu import CpuRuntime
+    from kern_b200.engine import Engine
+    from kern_b200.models import dense
+    from kern_b200.serve.scheduler import Request, Scheduler
+
+    cfg = dense.TOY
+    rt = CpuRuntime(dense.build_manifest(cfg), weights=dense.random_weights(cfg, seed=0, std=0.05), tokens=cfg.page_size * 16)
+    rt.once()
+    args = SimpleNamespace(trace_dir=str(tmp_path), trace_sample=2, trace_pm_us=10000, cpu=True, gpu=0)
+    eng, rec, sampler = cli.trace_setup(args, Engine(rt), nvml=FakeNvmlGpm())
+    assert rec is not None and sampler is not None
+    sched = Scheduler(eng, chunk=16, max_seqs=2)
+    for i in range(3):
+        sched.submit(Request(id=str(i), prompt=list(range(2, 20 + i)), max_tokens=4))
+    sched.run_until_idle()
+    time.sleep(0.05)
+    sampler.stop()
+    sampler.join(2)
+    kinds = {p.name.split(".")[1]: p for p in rec.rotate()}
+    assert {"steps", "counters"} <= set(kinds)
+    steps = pq.ParquetFile(kinds["steps"]).read().to_pydict()
+    assert len(steps["seq"]) >= sched.stats.steps          # a scheduler step is one engine call, or several when it splits
+    assert {"prefill", "decode"} <= set(steps["program"])
+    assert set(pq.ParquetFile(kinds["counters"]).read().to_pydict()["tensor_active_pm"]) == {612}
+    # without the flag nothing is wrapped
+    plain = cli.trace_setup(SimpleNamespace(trace_dir=None), "engine")
+    assert plain == ("engine", None, None)
