@@ -44,9 +44,10 @@ def main(argv=None) -> int:
     rt = Runtime(stages[rank], gpu=local, tokens=cfg.page_size * 64, slots=8)
     rt.load_tensors(lambda name: weights[name].to(dev))
     rt.once()
-    # what crosses into this stage: its exported buffers that the previous stage writes
-    prev_outs = {n for n, x in stages[rank - 1]["buffers"].items() if x["kind"] in ("output", "inout") and not x.get("fill")} if rank else set()
-    landing = [n for n, x in stages[rank]["buffers"].items() if x.get("export") and n in prev_outs]
+    # what crosses into this stage: its exported buffers that the previous stage holds — written there, or relayed (a
+    # table made in the first stage that a later stage reads travels through every stage in between as an input)
+    prev = stages[rank - 1]["buffers"] if rank else {}
+    landing = [n for n, x in stages[rank]["buffers"].items() if x.get("export") and n in prev and not prev[n].get("fill")]
     handles = [None] * world
     dist.all_gather_object(handles, rt.export_buffers(landing))
     nxt = {n: rt._rt.import_region(h) for n, h in handles[rank + 1].items()} if rank + 1 < world else {}
