@@ -487,7 +487,7 @@ def cmd_server(args) -> int:
             dspec["manifest"] = dense_dcp.build_manifest_dcp(cfg, args.dcp)
             extra = {"decode_gpus": [args.decode_gpu + i for i in range(args.dcp)], "dealer": dense_dcp.dealer(cfg)}
         tier, worker = launch.launch_pd(spec, dspec, chunk=args.chunk, max_seqs=args.max_seqs or None, prefill_gpu=args.gpu or 0,
-                                        decode_gpu=args.decode_gpu, **extra)
+                                        decode_gpu=args.decode_gpu, front=True, **extra)
         srv = Server(tier, tok, model_name=doc["model"], host=args.host, port=args.port)
         try:
             srv.serve_forever()

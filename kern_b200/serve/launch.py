@@ -213,7 +213,8 @@ def _pd_decode_main(addr, spec: dict, gpu: int, max_seqs: int | None, stop_ids: 
 
 def launch_pd(spec: dict, decode_spec: dict | None = None, chunk: int | None = None, max_seqs: int | None = None,
               decode_max_seqs: int | None = None, stop_ids: tuple = (), prefill_gpu: int = 0, decode_gpu: int = 1,
-              timeout: float = 600.0, context: str = "spawn", decode_gpus: list[int] | None = None, dealer=None):
+              timeout: float = 600.0, context: str = "spawn", decode_gpus: list[int] | None = None, dealer=None,
+              front: bool = False):
     """Prefill and decode on two GPUs: THIS process is the prefill tier (its own runtime, pool, prefix cache and
     scheduler on `prefill_gpu`), the decode tier is a spawned process on `decode_gpu` that exports its pools; a prompt's
     pages and slot are pushed into the seats the decode tier granted (device copies over NVLink) and the request goes
@@ -222,7 +223,8 @@ def launch_pd(spec: dict, decode_spec: dict | None = None, chunk: int | None = N
     `decode_gpus` (two or more): the decode tier is a group of rank processes, one per listed GPU, whose manifest
     (`decode_spec["manifest"]`) deals every sequence's positions over the members (decode context parallelism); its head
     (seats, steps, accounting) is a thread of this process; `dealer`: how the prompt's rows reach the members when a
-    state's pages are not token-contiguous (`pd_serve`).
+    state's pages are not token-contiguous (`pd_serve`). `front`: the prefill scheduler runs on a head thread and the
+    returned object only relays (`front.Front`), so decode tokens are not held behind a prefill step.
     -> (scheduler-like prefill tier, worker). `shutdown_pd` ends it.
     Reference counterpart: crates/kern-serve/src/lib.rs:317-404 (tiers by flags), pd/handoff.rs, pd/decoder.rs."""
     import threading
@@ -277,7 +279,7 @@ def launch_pd(spec: dict, decode_spec: dict | None = None, chunk: int | None = N
     finally:
         lsock.close()
     sched = Scheduler(Engine(rt), chunk=chunk, max_seqs=max_seqs)
-    tier = pd_serve.connect_tiers(sched, rt, spec["manifest"], sock, pools=pools, timeout=timeout, dealer=dealer)
+    tier = pd_serve.connect_tiers(sched, rt, spec["manifest"], sock, pools=pools, timeout=timeout, dealer=dealer, front=front)
     log.info("serving a prefill tier on gpu %d and a decode tier on gpu %d", prefill_gpu, decode_gpu)
     return tier, worker
 
@@ -334,6 +336,7 @@ def _pp_selftest(argv=None) -> int:
     ap.add_argument("--stages", type=int, default=2)
     ap.add_argument("--pd", action="store_true", help="a prefill tier and a decode tier instead of a pipeline")
     ap.add_argument("--dcp", type=int, default=0, help="with --pd: the decode tier is a context-parallel group of this many ranks")
+    ap.add_argument("--front", action="store_true", help="with --pd: the prefill scheduler on a head thread (serve/front.py)")
     ap.add_argument("--cpu", action="store_true")
     a = ap.parse_args(argv)
     cfg = dataclasses.replace(dense.TOY if a.cpu else dense.TINY, layers=2 * a.stages, name="tiny-deep")
@@ -378,10 +381,11 @@ def _pp_selftest(argv=None) -> int:
             n_gpu = max(1, torch.cuda.device_count())
             first = 1 if n_gpu > a.dcp else 0
             dspec = dict(spec, manifest=dense_dcp.build_manifest_dcp(cfg, a.dcp), tokens=cfg.page_size * 8)
-            tier, worker = launch_pd(spec, dspec, chunk=chunk, max_seqs=3, decode_max_seqs=2, timeout=120.0,
+            tier, worker = launch_pd(spec, dspec, chunk=chunk, max_seqs=3, decode_max_seqs=2, timeout=120.0, front=a.front,
                                      decode_gpus=[(first + i) % n_gpu for i in range(a.dcp)], dealer=dense_dcp.dealer(cfg))
         else:
-            tier, worker = launch_pd(spec, dict(spec, tokens=cfg.page_size * 8), chunk=chunk, max_seqs=3, decode_max_seqs=2, timeout=60.0)
+            tier, worker = launch_pd(spec, dict(spec, tokens=cfg.page_size * 8), chunk=chunk, max_seqs=3, decode_max_seqs=2, timeout=60.0,
+                                     front=a.front)
         try:
             got, idle = serve(tier)
             served = tier.metrics()

@@ -63,7 +63,10 @@ def decode_loop(sock, engine, max_seqs: int | None = None, stop_ids: tuple = (),
     calls = 0
     while True:
         live = any(s.started for s in dec.seats.values())
-        msgs = _drain(sock, 0.0 if live else idle_wait)
+        try:
+            msgs = _drain(sock, 0.0 if live else idle_wait)
+        except (ConnectionError, OSError):
+            msgs = None
         if msgs is None:
             break
         out = []
@@ -77,8 +80,11 @@ def decode_loop(sock, engine, max_seqs: int | None = None, stop_ids: tuple = (),
             break
         step = dec.step()
         calls += bool(step)
-        for m in out + step:
-            wire.send(sock, m)
+        try:
+            for m in out + step:
+                wire.send(sock, m)
+        except (ConnectionError, OSError):        # the prefill tier went away in the middle of a step
+            break
     for seat in list(dec.seats.values()):          # whatever was in flight when the front went away
         engine.close(seat.seq)
     return calls
@@ -252,9 +258,11 @@ class PrefillTier:
         self.sock.close()
 
 
-def connect_tiers(sched: Scheduler, rt, doc: dict, sock, pools=None, timeout: float = 600.0, dealer=None) -> PrefillTier:
+def connect_tiers(sched: Scheduler, rt, doc: dict, sock, pools=None, timeout: float = 600.0, dealer=None, front: bool = False):
     """Read the decode tier's Hello from `sock`, check that this tier's manifest covers its pools, map them (or take
-    `pools`, the decode runtime's exported states, when both tiers share a process) and return the prefill tier."""
+    `pools`, the decode runtime's exported states, when both tiers share a process) and return the prefill tier:
+    `PrefillTier` (one loop steps the scheduler and relays tokens), or with `front` a `front.Front` (the scheduler on a
+    head thread, tokens relayed as they come)."""
     ready, _, _ = select.select([sock], [], [], timeout)
     if not ready:
         raise TimeoutError("the decode tier did not say hello")
@@ -265,8 +273,12 @@ def connect_tiers(sched: Scheduler, rt, doc: dict, sock, pools=None, timeout: fl
     why = pd.cover(doc, rt.page_unit, hello)
     if why:
         raise ValueError("the prefill manifest does not cover the decode tier's pools: " + "; ".join(why))
+    if front:                               # the prefill scheduler on a head thread of its own (`front.py`)
+        from .front import Front as Tier
+    else:
+        Tier = PrefillTier
     if "members" in hello:                  # a decode group: every member's pools, mapped once
         mirrors = pd.Mirrors(rt, [m["handles"] for m in hello["members"]], [m["sizes"] for m in hello["members"]])
-        return PrefillTier(sched, rt, sock, None, mirrors=mirrors, dealer=dealer)
+        return Tier(sched, rt, sock, None, mirrors=mirrors, dealer=dealer)
     mapped = rt.map_pool(pools if pools is not None else hello["handles"])
-    return PrefillTier(sched, rt, sock, mapped)
+    return Tier(sched, rt, sock, mapped)

@@ -50,14 +50,44 @@ def test_pipeline_of_stage_processes_under_the_scheduler():
     assert line["ok"] and line["stages"] == 2 and line["tokens"] == 20
 
 
+def test_clients_state_machine_who_answers_a_client():
+    """The head answers from submission until it finishes, rejects or hands over; the front after. Tokens of a request
+    the front has retired are dropped; a client that leaves a decoding request retires it at once and has the head free
+    its seats; the head is told once of any other."""
+    from kern_b200.serve.front import Clients
+
+    c = Clients()
+    for rid in ("a", "b", "c", "d"):
+        c.submit(rid)
+    with pytest.raises(ValueError):
+        c.submit("a")
+    assert c.note(("admit", "a", 32)) == [] and c.note(("emit", "a", 7)) == [("token", "a", 7)]
+    assert c.tokens("a", 9, False) == []                       # not handed over yet: nothing of the decode tier's is its
+    assert c.note(("decode", "a")) == [] and c.decoding() == 1
+    assert c.tokens("a", 9, False) == [("token", "a", 9)]
+    with pytest.raises(RuntimeError):
+        c.note(("emit", "a", 1))                               # the head does not write to a request it handed over
+    assert c.tokens("a", 4, True, "stop") == [("token", "a", 4), ("finish", "a", "stop")] and c.open() == 3
+    assert c.tokens("a", 5, False) == [] and c.note(("emit", "a", 5)) == []      # retired: late words are dropped
+    assert c.note(("emit", "b", 3)) == [("token", "b", 3)] and c.note(("finish", "b", "length")) == [("finish", "b", "length")]
+    assert c.note(("reject", "c", "exceeds_pool")) == [("finish", "c", "abort")]
+    # d's client leaves while the head still has it: told once; after the hand-over the front retires it itself
+    gone = lambda rid: rid == "d"
+    assert c.sweep(gone) == ([], [("gone", "d")]) and c.sweep(gone) == ([], [])
+    c.note(("decode", "d"))
+    assert c.sweep(gone) == ([("finish", "d", "abort")], [("abort", "d")]) and c.open() == 0
+
+
 @pytest.mark.timeout(300)
-def test_prefill_and_decode_tiers_under_the_scheduler():
+@pytest.mark.parametrize("front", [False, True])
+def test_prefill_and_decode_tiers_under_the_scheduler(front):
     """`launch_pd` with host-memory executors: requests wait for a seat on the decode tier (it holds two at a time), are
     prefilled in chunks by the local scheduler, pushed into the granted seats and finished by the decode tier; the
-    tokens are those of one engine, and the exact integer model with a per-sequence state slot agrees with its twin."""
+    tokens are those of one engine, and the exact integer model with a per-sequence state slot agrees with its twin.
+    `front`: the prefill scheduler on a head thread, the tier object only relaying (`serve/front.py`)."""
     spec = {"manifest": toy_int.build_manifest(True), "cpu": True, "tokens": 16 * 30, "slots": 6}
     tier, worker = launch.launch_pd(spec, dict(spec, tokens=16 * 12, slots=3), chunk=32, max_seqs=3, decode_max_seqs=2,
-                                    stop_ids=(toy_int.EOS,), timeout=60)
+                                    stop_ids=(toy_int.EOS,), timeout=60, front=front)
     try:
         rng = random.Random(7)
         reqs = [Request(id=f"r{i}", prompt=[rng.randrange(256) for _ in range(rng.randint(3, 60))], max_tokens=6,
@@ -72,7 +102,7 @@ def test_prefill_and_decode_tiers_under_the_scheduler():
             if tier.idle():
                 break
             tier.step()
-            seen_waiting = max(seen_waiting, tier.metrics()["pd"]["waiting_for_seat"])
+            seen_waiting = max(seen_waiting, tier.metrics()["pd"].get("waiting_for_seat", 1))
         assert tier.idle() and seen_waiting > 0
         for r in reqs:
             assert r.finished in ("stop", "length"), (r.id, r.finished)
@@ -86,7 +116,12 @@ def test_prefill_and_decode_tiers_under_the_scheduler():
             tier.step()
             if len(late.out) >= 3:
                 break
-        assert tier.abort("late") and late.finished == "abort" and tier.idle()
+        assert tier.abort("late")
+        for _ in range(2000):
+            if tier.idle():
+                break
+            tier.step()
+        assert late.finished == "abort" and tier.idle() and 3 <= len(late.out) < 50
     finally:
         launch.shutdown_pd(tier, worker)
     assert not worker.is_alive()

@@ -204,7 +204,8 @@ def test_agent_traffic_replay_reuses_prefixes_and_is_exact(toy):
     assert alone(make, prompt, n_out) == s0.history[len(prompt):]
 
 
-def test_http_front_over_prefill_and_decode_tiers(toy):
+@pytest.mark.parametrize("front", [False, True])
+def test_http_front_over_prefill_and_decode_tiers(toy, front):
     """The OpenAI-style front over `launch_pd`: completions come out of the decode tier, token for token those of one
     engine; a repeated prompt hits the prefill tier's prefix cache; the metrics page carries the tiers' counters."""
     from kern_b200.serve import launch
@@ -212,7 +213,8 @@ def test_http_front_over_prefill_and_decode_tiers(toy):
     cfg, make = toy
     weights = dense.random_weights(cfg, seed=0, std=0.05)
     spec = {"manifest": dense.build_manifest(cfg), "cpu": True, "weights": weights, "tokens": cfg.page_size * 24}
-    tier, worker = launch.launch_pd(spec, dict(spec, tokens=cfg.page_size * 12), chunk=16, max_seqs=3, decode_max_seqs=2, timeout=60)
+    tier, worker = launch.launch_pd(spec, dict(spec, tokens=cfg.page_size * 12), chunk=16, max_seqs=3, decode_max_seqs=2, timeout=60,
+                                    front=front)
     srv = Server(tier, model_name="toy-pd", port=0).start()
     base = f"http://127.0.0.1:{srv.port}"
     try:
