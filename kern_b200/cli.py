@@ -457,7 +457,7 @@ def cmd_server(args) -> int:
         spec = {"manifest": doc, "weights": args.weights, "model": args.model, "cpu": args.cpu, "tokens": args.capacity or 0,
                 "slots": args.max_seqs or 0}
         sched, pipe, procs = launch.launch_pp(spec, args.pp, chunk=args.chunk, max_seqs=args.max_seqs or None)
-        srv = Server(sched, tok, model_name=doc["model"], host=args.host, port=args.port)
+        srv = Server(sched, tok, model_name=doc["model"], host=args.host, port=args.port, tool_parser=_tool_parser(args, doc))
         try:
             srv.serve_forever()
         finally:
@@ -488,7 +488,7 @@ def cmd_server(args) -> int:
             extra = {"decode_gpus": [args.decode_gpu + i for i in range(args.dcp)], "dealer": dense_dcp.dealer(cfg)}
         tier, worker = launch.launch_pd(spec, dspec, chunk=args.chunk, max_seqs=args.max_seqs or None, prefill_gpu=args.gpu or 0,
                                         decode_gpu=args.decode_gpu, front=True, **extra)
-        srv = Server(tier, tok, model_name=doc["model"], host=args.host, port=args.port)
+        srv = Server(tier, tok, model_name=doc["model"], host=args.host, port=args.port, tool_parser=_tool_parser(args, doc))
         try:
             srv.serve_forever()
         finally:
@@ -515,7 +515,7 @@ def cmd_server(args) -> int:
         spec = {"manifest": doc, "weights": args.weights, "model": args.model, "cpu": args.cpu, "tokens": args.capacity or 0,
                 "slots": args.max_seqs or 0}
         sched, ex, procs = launch.launch(spec, world=args.world, tp=args.tp, chunk=args.chunk, max_seqs=args.max_seqs or None)
-        srv = Server(sched, tok, model_name=doc["model"], host=args.host, port=args.port)
+        srv = Server(sched, tok, model_name=doc["model"], host=args.host, port=args.port, tool_parser=_tool_parser(args, doc))
         try:
             srv.serve_forever()
         finally:
@@ -524,7 +524,8 @@ def cmd_server(args) -> int:
     rt = make_runtime(args)
     eng, rec, sampler = trace_setup(args, Engine(rt))
     sched = Scheduler(eng, chunk=args.chunk, max_seqs=args.max_seqs or None, rows=args.rows)
-    srv = Server(sched, tok, model_name=rt.doc["model"], host=args.host, port=args.port, on_rotate=rec.rotate if rec else None)
+    srv = Server(sched, tok, model_name=rt.doc["model"], host=args.host, port=args.port, on_rotate=rec.rotate if rec else None,
+                 tool_parser=_tool_parser(args, rt.doc))
     logging.getLogger("kern.serve").info("listening host=%s port=%d model=%s", args.host, srv.port, rt.doc["model"])
     try:
         srv.serve_forever()
@@ -534,6 +535,13 @@ def cmd_server(args) -> int:
         if rec is not None:
             rec.close()
     return 0
+
+
+def _tool_parser(args, doc: dict) -> str:
+    """--tool-call-parser when it says more than `auto`, else the manifest's `chat.tool_parser`, else recognition by syntax."""
+    from .serve.chat import select_parser
+
+    return select_parser(getattr(args, "tool_call_parser", None), (doc.get("chat") or {}).get("tool_parser"))
 
 
 def trace_setup(args, engine, nvml=None):
@@ -603,6 +611,7 @@ def main(argv=None) -> int:
     s.add_argument("--world", type=int, default=1, help="rank processes (one per GPU)")
     s.add_argument("--tp", type=int, default=1, help="ranks per tensor-parallel group; world / tp groups form a data-parallel tier")
     s.add_argument("--pp", type=int, default=1, help="pipeline stages (one process per GPU; this process is the head): the manifest is cut at layer boundaries")
+    s.add_argument("--tool-call-parser", default="auto", help="auto | none | hermes | qwen3_coder: how chat completions with `tools` get structured tool_calls (auto: the manifest's chat.tool_parser, else by syntax)")
     s.add_argument("--trace-dir", help="record every step (and sampled steps by call, and counters) as Parquet files under this directory")
     s.add_argument("--trace-sample", type=int, default=0, help="with --trace-dir: every N-th step runs eagerly with per-call device times")
     s.add_argument("--trace-pm-us", type=int, default=0, help="with --trace-dir: sample clocks, power and SM / tensor / DRAM busy shares every this many microseconds (>= 50)")

@@ -35,8 +35,10 @@ class ByteTokenizer:
     def decode(self, ids) -> str:
         return bytes(int(i) & 0xFF for i in ids if int(i) != 0).decode("utf-8", errors="replace")
 
-    def chat(self, messages) -> list[int]:
-        text = "".join(f"<{m.get('role', 'user')}>{m.get('content', '')}\n" for m in messages) + "<assistant>"
+    def chat(self, messages, tools=None) -> list[int]:
+        text = ("<tools>" + json.dumps(tools) + "\n" if tools else "") + \
+            "".join(f"<{m.get('role', 'user')}>{m.get('content', '')}{json.dumps(m['tool_calls']) if m.get('tool_calls') else ''}\n"
+                    for m in messages) + "<assistant>"
         return self.encode(text)
 
 
@@ -55,8 +57,8 @@ class HFTokenizer:
     def decode(self, ids) -> str:
         return self.tok.decode(list(ids), skip_special_tokens=True)
 
-    def chat(self, messages) -> list[int]:
-        return self.tok.apply_chat_template(messages, add_generation_prompt=True, tokenize=True)
+    def chat(self, messages, tools=None) -> list[int]:
+        return self.tok.apply_chat_template(messages, tools=tools or None, add_generation_prompt=True, tokenize=True)
 
 
 class Driver(threading.Thread):
@@ -168,7 +170,7 @@ def prometheus(driver: Driver, model: str) -> str:
     return "\n".join(lines) + "\n"
 
 
-def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None):
+def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None, tool_parser: str = "auto"):
     class Handler(BaseHTTPRequestHandler):
         protocol_version = "HTTP/1.1"
 
@@ -217,14 +219,17 @@ def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None):
                 return self._json(503, {"error": {"message": f"engine failed: {driver.failed}"}})
             try:
                 history = None
+                tools = body.get("tools") if chat else None
                 if chat:
-                    msgs = body["messages"]
-                    prompt = tokenizer.chat(msgs)
+                    from .chat import messages_for_template
+
+                    msgs = messages_for_template(body["messages"])
+                    prompt = tokenizer.chat(msgs, tools) if tools else tokenizer.chat(msgs)
                     # the turn boundary: the rendering of everything before the last message is a prefix of the whole
                     # prompt when the template is prefix-stable; a model with per-sequence state snapshots it there
                     if len(msgs) > 1:
                         try:
-                            head = tokenizer.chat(msgs[:-1])
+                            head = tokenizer.chat(msgs[:-1], tools) if tools else tokenizer.chat(msgs[:-1])
                             n = 0
                             while n < min(len(head), len(prompt)) and head[n] == prompt[n]:
                                 n += 1
@@ -262,6 +267,13 @@ def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None):
                 self.send_header("Connection", "close")
                 self.end_headers()
             text_ids: list[int] = []
+            # with tools in the request, the model's tool-call syntax becomes structured `tool_calls`
+            tstream = None
+            if chat and tools and tool_parser != "none":
+                from .chat import ToolStream, parse_tool_calls
+
+                tstream = ToolStream(tool_parser)
+            called = False
             try:
                 while True:
                     try:
@@ -277,7 +289,11 @@ def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None):
                         text_ids.extend(what)
                         if stream:
                             piece = tokenizer.decode(what)
-                            delta = {"delta": {"content": piece}} if chat else {"text": piece}
+                            calls = []
+                            if tstream is not None:
+                                piece, calls = tstream.feed(piece)
+                                called = called or bool(calls)
+                            delta = {"delta": {"content": piece, **({"tool_calls": calls} if calls else {})}} if chat else {"text": piece}
                             chunk = {"id": req.id, "object": obj + ".chunk", "created": created, "model": model_name,
                                      "choices": [{"index": 0, **delta, "finish_reason": None, **({"token_ids": what} if with_ids else {})}]}
                             self.wfile.write(f"data: {json.dumps(chunk)}\n\n".encode())
@@ -290,13 +306,26 @@ def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None):
                 return
             text = tokenizer.decode(text_ids)
             if stream:
+                tail = {}
+                if tstream is not None:
+                    rest, calls = tstream.finish()
+                    called = called or bool(calls)
+                    tail = {**({"content": rest} if rest else {}), **({"tool_calls": calls} if calls else {})}
+                    if called and finish == "stop":
+                        finish = "tool_calls"
                 last = {"id": req.id, "object": obj + ".chunk", "created": created, "model": model_name,
-                        "choices": [{"index": 0, **({"delta": {}} if chat else {"text": ""}), "finish_reason": finish}], "usage": usage()}
+                        "choices": [{"index": 0, **({"delta": tail} if chat else {"text": ""}), "finish_reason": finish}], "usage": usage()}
                 self.wfile.write(f"data: {json.dumps(last)}\n\ndata: [DONE]\n\n".encode())
                 return
             choice = {"index": 0, "finish_reason": finish}
             if chat:
                 choice["message"] = {"role": "assistant", "content": text}
+                if tstream is not None:
+                    content, calls = parse_tool_calls(text, tool_parser)
+                    if calls:
+                        choice["message"] = {"role": "assistant", "content": content or None, "tool_calls": calls}
+                        if finish == "stop":
+                            choice["finish_reason"] = "tool_calls"
             else:
                 choice["text"] = text
             if with_ids:
@@ -309,9 +338,12 @@ def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None):
 
 class Server:
     def __init__(self, sched: Scheduler, tokenizer=None, model_name: str = "kern", host: str = "127.0.0.1", port: int = 8000,
-                 on_rotate=None):
+                 on_rotate=None, tool_parser: str = "auto"):
+        """`tool_parser`: `chat.select_parser`'s answer (auto | none | hermes | qwen3_coder): how a chat completion whose
+        request carries `tools` has the model's tool-call syntax turned into `tool_calls`."""
         self.driver = Driver(sched)
-        self.httpd = ThreadingHTTPServer((host, port), make_handler(self.driver, tokenizer or ByteTokenizer(), model_name, on_rotate))
+        self.httpd = ThreadingHTTPServer((host, port), make_handler(self.driver, tokenizer or ByteTokenizer(), model_name, on_rotate,
+                                                                    tool_parser))
         self.httpd.daemon_threads = True
         self.port = self.httpd.server_address[1]
         self._thread = None
