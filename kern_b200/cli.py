@@ -305,8 +305,11 @@ def load_workload(path: str | None) -> dict:
 
 
 def cmd_bench(args) -> int:
-    """Each sweep point: contexts built once, then `samples` timed calls of the forward program (device-synchronised
-    wall time per call; graph programs replay their captured graph); min / p10 / p50 / p90 / max / cv."""
+    """Each sweep point: contexts built once, then `samples` timed calls of the forward program, each from the same
+    pre-image (paged rows rewound, per-sequence states put back from a spare slot) and, on a GPU, behind an L2 flush and
+    timed by CUDA events on the runtime's stream (graph programs replay their captured graph); min / p10 / p50 / p90 /
+    max / cv and the raw samples.
+    Reference counterpart: crates/kern-run/src/bench/mod.rs:1-17, crates/kern-runtime/src/profile.rs:30-150."""
     from .engine import Engine
 
     wl = load_workload(args.workload)
@@ -357,6 +360,32 @@ def bench_candidate(args, wl) -> int:
     return 0
 
 
+def _bench_device(rt):
+    """On a GPU: (flush, events) — `flush(k)` writes a buffer larger than L2 so the next sample starts cold, `events()`
+    records a start event on the runtime's stream and returns (start, end, stream). (None, None) on the host executor."""
+    try:
+        import torch
+
+        if not (torch.cuda.is_available() and hasattr(rt, "stream") and hasattr(rt, "gpu")):
+            return None, None
+        dev = torch.device(f"cuda:{rt.gpu}")
+        stream = torch.cuda.ExternalStream(rt.stream, device=dev)
+        buf = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+
+        def flush(k: int) -> None:
+            with torch.cuda.stream(stream):
+                buf.fill_(k & 0xFF)
+
+        def events():
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            return a, b, stream
+
+        return flush, events
+    except Exception:
+        return None, None
+
+
 def bench_points(rt, wl, by_op: bool = False, quiet: bool = False) -> dict:
     from .engine import Engine
     import numpy as np
@@ -375,24 +404,45 @@ def bench_points(rt, wl, by_op: bool = False, quiet: bool = False) -> dict:
             for i in range(0, pre, eng.rows_max // max(1, g)):
                 n = min(eng.rows_max // max(1, g), pre - i)
                 eng.step([(s, rng.integers(1, 200, n).tolist()) for s in seqs])
-        times = []
+        # the pre-image of what a sample changes: paged rows are overwritten in place by the next sample (a slot is its
+        # position), a per-sequence recurrent state is not — it is kept in a spare slot and put back before every sample
+        shadows = []
+        for s in seqs:
+            if s.lease.slot >= 0:
+                sh = eng.open(1)
+                rt.run_copies({"pages": [], "slot": (s.lease.slot, sh.lease.slot)})
+                shadows.append(sh)
+        flush, events = _bench_device(rt)
+        times, host_times = [], []
         for k in range(4 + wl["samples"]):                       # WARMUP = 4
             batch = [(s, rng.integers(1, 200, rows).tolist()) for s in seqs]
+            for s, sh in zip(seqs, shadows):
+                rt.run_copies({"pages": [], "slot": (sh.lease.slot, s.lease.slot)})
+            if flush is not None:
+                flush(k)                                         # every sample starts with a cold L2
             rt.synchronize()
+            ev = events() if events is not None else None
             t0 = time.perf_counter()
             eng.step(batch)
+            if ev is not None:
+                ev[1].record(ev[2])
             rt.synchronize()
+            host_ms = (time.perf_counter() - t0) * 1e3
             if k >= 4:
-                times.append((time.perf_counter() - t0) * 1e3)
+                host_times.append(host_ms)
+                times.append(ev[0].elapsed_time(ev[1]) if ev is not None else host_ms)
             for s in seqs:                                       # rewind: every sample runs at the same context
-                s.length -= rows                                 # (a paged slot is its position: the rows are overwritten)
+                s.length -= rows
                 del s.tokens[-rows:]
-        for s in seqs:
+        for s in seqs + shadows:
             eng.close(s)
+        raw = list(times)
         times.sort()
         q = lambda f: times[min(len(times) - 1, int(f * len(times)))]
         point = {"groups": g, "rows": rows, "context": ctx, "weight": pt.get("weight", 1.0), "min_ms": times[0], "p10_ms": q(0.1),
-                 "p50_ms": q(0.5), "p90_ms": q(0.9), "max_ms": times[-1], "cv": statistics.pstdev(times) / max(1e-9, statistics.mean(times))}
+                 "p50_ms": q(0.5), "p90_ms": q(0.9), "max_ms": times[-1], "cv": statistics.pstdev(times) / max(1e-9, statistics.mean(times)),
+                 "clock": "device" if events is not None else "host", "l2_flushed": flush is not None,
+                 "host_p50_ms": sorted(host_times)[len(host_times) // 2], "samples_ms": [round(t, 4) for t in raw]}
         if by_op and hasattr(rt, "issue_timed"):
             # one more call of the same shape, eagerly, with an event between calls: the cost by op
             seqs2 = [eng.open(ctx) for _ in range(g)]

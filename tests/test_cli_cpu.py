@@ -76,6 +76,8 @@ def test_bench_and_kernels(pkg, capsys):
     assert cli.main(["bench", "--cpu", "--manifest", str(d / "manifest.json"), "--weights", str(d), "--capacity", "1024"]) == 0
     pts = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
     assert len(pts) == 2 and all(p["p50_ms"] > 0 and p["min_ms"] <= p["p50_ms"] <= p["max_ms"] for p in pts)
+    # the raw samples are kept; on the host executor the clock is the host's and nothing is flushed
+    assert all(len(p["samples_ms"]) >= 3 and p["clock"] == "host" and not p["l2_flushed"] and p["host_p50_ms"] > 0 for p in pts)
     assert cli.main(["kernels"]) == 0
     assert "gemm_bf16.cubin" in capsys.readouterr().out
 
@@ -165,3 +167,27 @@ def test_run_with_activation_probes(tmp_path, capsys):
     first = next(e for e in index if e["label"] == "l0.ln1")
     t = torch.load(d / first["file"])
     assert list(t.shape) == first["shape"] and t.shape[0] == 5 and bool(torch.isfinite(t.float()).all())
+
+
+def test_bench_samples_start_from_the_same_recurrent_state(capsys, tmp_path):
+    """A model with a per-sequence state: every sample of a sweep point runs from the pre-image (the state is kept in a
+    spare slot and put back), so the slot's bytes after the bench equal those after the context alone plus one call."""
+    import numpy as np
+
+    from kern_b200.cli import bench_points
+    from kern_b200.cpu import CpuRuntime
+    from kern_b200.models import hybrid
+
+    cfg = hybrid.TOY_HYBRID
+    w = hybrid.random_weights(cfg, seed=1, std=0.05)
+    make = lambda: CpuRuntime(hybrid.build_manifest(cfg), weights=w, tokens=cfg.page_size * 16, slots=6)
+    wl = {"seed": 3, "samples": 3, "sweep": [{"groups": 1, "rows": 1, "context": 9}]}
+    rt = make()
+    rt.once()
+    seen = []
+    real = rt.run_copies
+    rt.run_copies = lambda c: (seen.append(c["slot"]), real(c))[1]
+    rep = bench_points(rt, wl, quiet=True)
+    assert len(rep["points"][0]["samples_ms"]) == 3
+    # one copy out to the spare slot, then one back before each of the 4 + 3 calls
+    assert len(seen) == 1 + 7 and seen[0] == tuple(reversed(seen[1])) and len(set(seen[1:])) == 1
