@@ -387,6 +387,7 @@ def _bench_device(rt):
 
 
 def bench_points(rt, wl, by_op: bool = False, quiet: bool = False) -> dict:
+    from . import _native
     from .engine import Engine
     import numpy as np
 
@@ -394,7 +395,7 @@ def bench_points(rt, wl, by_op: bool = False, quiet: bool = False) -> dict:
     rng = np.random.default_rng(wl["seed"])
     report = {"version": 5, "points": []}
     for pt in wl["sweep"]:
-        g, ctx = int(pt.get("groups", 1)), int(pt.get("context", 64))
+        g, ctx = min(int(pt.get("groups", 1)), eng.groups_max), int(pt.get("context", 64))     # no more sequences than a call takes
         rows = min(int(pt.get("chunk", pt.get("rows", 1))), eng.rows_max // max(1, g))
         longest = min((t["width"] * t["stride"] for t in eng.page_tables), default=ctx)
         ctx = max(rows, min(ctx, longest))          # a context the manifest's page-table row can hold
@@ -407,11 +408,18 @@ def bench_points(rt, wl, by_op: bool = False, quiet: bool = False) -> dict:
         # the pre-image of what a sample changes: paged rows are overwritten in place by the next sample (a slot is its
         # position), a per-sequence recurrent state is not — it is kept in a spare slot and put back before every sample
         shadows = []
-        for s in seqs:
-            if s.lease.slot >= 0:
-                sh = eng.open(1)
-                rt.run_copies({"pages": [], "slot": (s.lease.slot, sh.lease.slot)})
-                shadows.append(sh)
+        stateful = any(s.lease.slot >= 0 for s in seqs)
+        try:
+            for s in seqs:
+                if s.lease.slot >= 0:
+                    sh = eng.open(1)
+                    shadows.append(sh)
+                    rt.run_copies({"pages": [], "slot": (s.lease.slot, sh.lease.slot)})
+        except _native.Denied:              # no spare slots for all of them: the samples run on from one another's state
+            for sh in shadows:
+                eng.close(sh)
+            shadows = []
+        pre_image = bool(shadows) or not stateful
         flush, events = _bench_device(rt)
         times, host_times = [], []
         for k in range(4 + wl["samples"]):                       # WARMUP = 4
@@ -442,6 +450,7 @@ def bench_points(rt, wl, by_op: bool = False, quiet: bool = False) -> dict:
         point = {"groups": g, "rows": rows, "context": ctx, "weight": pt.get("weight", 1.0), "min_ms": times[0], "p10_ms": q(0.1),
                  "p50_ms": q(0.5), "p90_ms": q(0.9), "max_ms": times[-1], "cv": statistics.pstdev(times) / max(1e-9, statistics.mean(times)),
                  "clock": "device" if events is not None else "host", "l2_flushed": flush is not None,
+                 "pre_image": pre_image,
                  "host_p50_ms": sorted(host_times)[len(host_times) // 2], "samples_ms": [round(t, 4) for t in raw]}
         if by_op and hasattr(rt, "issue_timed"):
             # one more call of the same shape, eagerly, with an event between calls: the cost by op
