@@ -272,7 +272,7 @@ def cmd_e2e(args) -> int:
     if args.record:
         vocab = max((b.get("domain", {}).get("max", 0) for b in side.doc["buffers"].values() if b.get("fill") == "token"), default=255) + 1
         qs = e2e.plan(args.seed, args.prompts, vocab, max_tokens=args.decode_steps)
-        e2e.record(side, qs, source=side.doc["model"], chunk=args.chunk or 256).save(args.out)
+        e2e.record(side, qs, source=side.doc["model"], chunk=args.chunk or 256, batch=args.batch).save(args.out)
         print(f"recorded {len(qs)} questions -> {args.out}")
         return 0
     text, code = e2e.summary(e2e.judge(e2e.Recording.load(args.recording), side, kl_limit=args.logit_kl, chunk=args.chunk or 256))
@@ -660,6 +660,7 @@ def main(argv=None) -> int:
     e = sub.add_parser("e2e-logits", help="record an engine's answers, or judge an engine against a recording")
     common(e); e.add_argument("recording", nargs="?"); e.add_argument("--record", action="store_true"); e.add_argument("--out")
     e.add_argument("--seed", type=int, default=0); e.add_argument("--prompts", type=int, default=8)
+    e.add_argument("--batch", type=int, default=4, help="--record: the noise of a question is measured along its own tokens alone, in batches of this many and of half as many")
     e.add_argument("--decode-steps", type=int, default=16); e.add_argument("--logit-kl", type=float, default=0.01)
     b = sub.add_parser("bench"); common(b); b.add_argument("--workload"); b.add_argument("--out")
     b.add_argument("--by-op", action="store_true", help="add each point's cost by op (one eager call with an event between calls)")

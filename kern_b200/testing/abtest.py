@@ -250,11 +250,32 @@ class EngineSide:
             self.eng.close(seq)
         return rows
 
-    def _logits_row(self):
+    def batched_forced_run(self, prompts, forced: list[list[int]], chunk: int, batch: int):
+        """Teacher-forced like `forced_run`, but the decode steps of up to `batch` sequences run as one call: the same
+        positions through other batch shapes (other tiles, other reduction orders). Rows per prompt, as `forced_run`
+        returns them flattened."""
+        rows: list[list] = [[] for _ in prompts]
+        for g0 in range(0, len(prompts), max(1, batch)):
+            idx = list(range(g0, min(len(prompts), g0 + max(1, batch))))
+            seqs = {i: self.eng.open(len(prompts[i]) + len(forced[i])) for i in idx}
+            for i in idx:
+                for c in range(0, len(prompts[i]), chunk):
+                    self.eng.step([(seqs[i], prompts[i][c:c + chunk])])
+                rows[i].append(self._logits_row())
+            for t in range(max(len(forced[i]) for i in idx) - 1):
+                live = [i for i in idx if t < len(forced[i]) - 1]
+                self.eng.step([(seqs[i], [forced[i][t]]) for i in live])
+                for j, i in enumerate(live):
+                    rows[i].append(self._logits_row(j))
+            for i in idx:
+                self.eng.close(seqs[i])
+        return rows
+
+    def _logits_row(self, j: int = 0):
         if self.logits is None:
             return None
         t = self.rt.tensor(self.logits)
-        return t[0].float().cpu().numpy().copy()
+        return t[j].float().cpu().numpy().copy()
 
     def snapshot(self, names) -> dict[str, bytes]:
         out = {}

@@ -84,9 +84,11 @@ class Recording:
         return cls(source=d["source"][0] if d["source"] else "", rows=rows)
 
 
-def record(side, questions: list[Question], source: str, chunk: int = 256, top: int = TOP) -> Recording:
-    """`side`: an EngineSide (free_run / forced_run). The noise of a question is the largest KL between two runs of
-    the same engine along the same tokens (0 for a deterministic engine)."""
+def record(side, questions: list[Question], source: str, chunk: int = 256, top: int = TOP, batch: int = 4) -> Recording:
+    """`side`: an EngineSide (free_run / forced_run / batched_forced_run). The noise of a question is the largest KL
+    between the recorded distribution and what the same engine gives along the same tokens again — alone, with the
+    decode steps of `batch` questions run as one call, and in batches half that size: what the engine's own batch
+    shapes move a distribution by (0 for an engine whose arithmetic does not depend on the batch)."""
     rec = Recording(source=source)
     for q in questions:
         outs, rows, _ = side.free_run([q.prompt], q.max_tokens, chunk)
@@ -95,6 +97,12 @@ def record(side, questions: list[Question], source: str, chunk: int = 256, top: 
         noise = max((kl_top(ids, lp, r2) for (ids, lp), r2 in zip(tops, again)), default=0.0)
         rec.rows.append({"question": q.id, "prompt": list(q.prompt), "output": [int(t) for t in outs[0]],
                          "top_ids": [t[0] for t in tops], "top_logprobs": [t[1] for t in tops], "noise": noise})
+    if batch > 1 and len(rec.rows) > 1 and hasattr(side, "batched_forced_run"):
+        prompts, outs = [r["prompt"] for r in rec.rows], [r["output"] for r in rec.rows]
+        for b in sorted({batch, max(1, batch // 2)} - {1}, reverse=True):
+            for r, rows in zip(rec.rows, side.batched_forced_run(prompts, outs, chunk, b)):
+                kls = [kl_top(ids, lp, row) for ids, lp, row in zip(r["top_ids"], r["top_logprobs"], rows)]
+                r["noise"] = max([r["noise"]] + kls)
     return rec
 
 
