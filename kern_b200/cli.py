@@ -583,7 +583,7 @@ def cmd_server(args) -> int:
     rt = make_runtime(args)
     eng, rec, sampler = trace_setup(args, Engine(rt))
     sched = Scheduler(eng, chunk=args.chunk, max_seqs=args.max_seqs or None, rows=args.rows)
-    srv = Server(sched, tok, model_name=rt.doc["model"], host=args.host, port=args.port, on_rotate=rec.rotate if rec else None,
+    srv = Server(sched, tok, model_name=rt.doc["model"], host=args.host, port=args.port, recorder=rec,
                  tool_parser=_tool_parser(args, rt.doc))
     logging.getLogger("kern.serve").info("listening host=%s port=%d model=%s", args.host, srv.port, rt.doc["model"])
     try:
@@ -592,6 +592,7 @@ def cmd_server(args) -> int:
         if sampler is not None:
             sampler.stop()
         if rec is not None:
+            rec.rotator.stop()
             rec.close()
     return 0
 
@@ -614,8 +615,11 @@ def trace_setup(args, engine, nvml=None):
         return engine, None, None
     from . import trace
 
-    rec = trace.Recorder(args.trace_dir, rank=0)
+    doc = getattr(getattr(engine, "rt", None), "doc", None) or {}
+    rec = trace.Recorder(args.trace_dir, rank=0, comm=trace.comm_ops(doc))
     eng = trace.TracedEngine(engine, rec, sample_every=getattr(args, "trace_sample", 0) or 0)
+    rec.rotator = trace.Rotator(rec)              # files close at every quarter hour of the wall clock
+    rec.rotator.start()
     sampler = None
     pm = getattr(args, "trace_pm_us", 0) or 0
     if pm and (nvml is not None or not getattr(args, "cpu", False)):

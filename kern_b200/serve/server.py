@@ -143,9 +143,15 @@ class Driver(threading.Thread):
                 q.put(("error", self.failed))
 
 
-def prometheus(driver: Driver, model: str) -> str:
+def prometheus(driver: Driver, model: str, recorder=None) -> str:
     m = driver.sched.metrics()
     st = driver.sched.stats
+    if recorder is not None:          # a traced engine: the board comes from what the recorder saw, step by step
+        from ..trace import prometheus_lines
+
+        board = prometheus_lines(recorder)
+    else:
+        board = None
     lines = [
         "# TYPE kern_device_seconds_total counter",
         f'kern_device_seconds_total{{class="compute"}} {driver.device_seconds["compute"]:.6f}',
@@ -157,6 +163,10 @@ def prometheus(driver: Driver, model: str) -> str:
         f'kern_steps_total{{program="step",shape="mixed",kv="paged"}} {st.steps}',
         "# TYPE kern_trace_dropped_records_total counter",
         "kern_trace_dropped_records_total 0",
+    ]
+    if board is not None:
+        lines = board
+    lines += [
         "# TYPE kern_kv_used_blocks gauge",
         f"kern_kv_used_blocks {m['kv_used_blocks']}",
         f"kern_kv_total_blocks {m['kv_total_blocks']}",
@@ -170,7 +180,7 @@ def prometheus(driver: Driver, model: str) -> str:
     return "\n".join(lines) + "\n"
 
 
-def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None, tool_parser: str = "auto"):
+def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None, tool_parser: str = "auto", recorder=None):
     class Handler(BaseHTTPRequestHandler):
         protocol_version = "HTTP/1.1"
 
@@ -199,7 +209,7 @@ def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None, too
             if self.path == "/v1/models":
                 return self._json(200, {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "kern_b200"}]})
             if self.path == "/kern/metrics":
-                return self._text(200, prometheus(driver, model_name))
+                return self._text(200, prometheus(driver, model_name, recorder))
             self._json(404, {"error": {"message": f"no route {self.path}"}})
 
         def do_POST(self):
@@ -338,12 +348,14 @@ def make_handler(driver: Driver, tokenizer, model_name: str, on_rotate=None, too
 
 class Server:
     def __init__(self, sched: Scheduler, tokenizer=None, model_name: str = "kern", host: str = "127.0.0.1", port: int = 8000,
-                 on_rotate=None, tool_parser: str = "auto"):
+                 on_rotate=None, tool_parser: str = "auto", recorder=None):
         """`tool_parser`: `chat.select_parser`'s answer (auto | none | hermes | qwen3_coder): how a chat completion whose
         request carries `tools` has the model's tool-call syntax turned into `tool_calls`."""
         self.driver = Driver(sched)
+        if recorder is not None and on_rotate is None:
+            on_rotate = recorder.rotate
         self.httpd = ThreadingHTTPServer((host, port), make_handler(self.driver, tokenizer or ByteTokenizer(), model_name, on_rotate,
-                                                                    tool_parser))
+                                                                    tool_parser, recorder))
         self.httpd.daemon_threads = True
         self.port = self.httpd.server_address[1]
         self._thread = None

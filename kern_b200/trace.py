@@ -33,14 +33,36 @@ def shape_of(groups: int, rows: int) -> str:
     return "decode" if per <= 1 else ("round" if per <= 16 else "prefill")
 
 
+def comm_ops(doc: dict) -> set[str]:
+    """The ops of a manifest that count as communication on the kernels board: a launch that is one of the
+    `extern:nccl_*` built-ins, or a call that is handed a `peer` buffer (the table of a buffer's copies on the other
+    ranks). Reference: crates/kern-serve/src/kernels.rs:141-150."""
+    peers = {n for n, b in doc.get("buffers", {}).items() if b.get("kind") == "peer"}
+    out = {name for name, op in doc.get("ops", {}).items()
+           if any(str(l.get("entry", "")).startswith("extern:nccl") for l in op.get("impl", {}).get("launches", []))}
+    for prog in doc.get("programs", {}).values():
+        for c in prog.get("calls", []):
+            if any(a.get("buf") in peers for a in c.get("args", []) if isinstance(a, dict)):
+                out.add(c["op"])
+    return out
+
+
 class Recorder:
-    def __init__(self, directory: str | Path, rank: int = 0, clock=time.time_ns):
+    def __init__(self, directory: str | Path, rank: int = 0, clock=time.time_ns, comm: set[str] | None = None):
+        """`comm`: the ops whose time is communication (`comm_ops(doc)`); sampled steps split their device time by it."""
         self.dir, self.rank, self.clock = Path(directory), rank, clock
         self._lock = threading.Lock()
         self._rows = {"steps": [], "kernels": [], "counters": []}
         self.seq = 0
         self.dropped = 0
         self.written: list[Path] = []
+        self.comm = set(comm or ())
+        # the kernels board's running totals (never reset by a rotate)
+        self.steps_by: dict[tuple[str, str], int] = {}             # (program, shape) -> steps
+        self.device_seconds = {"compute": 0.0, "comm": 0.0}
+        self.comm_share = 0.0                                       # of the sampled steps' device time
+        self._sampled = [0.0, 0.0]                                  # [comm ms, all ms] over the sampled steps
+        self.started = time.monotonic()
 
     # ---- feeding ----
     def step(self, program: str, groups: int, rows: int, context: int, graph: bool, device_us: float, host_us: float,
@@ -51,10 +73,20 @@ class Recorder:
             seq = self.seq
             self._rows["steps"].append((seq, self.clock(), program, groups, rows, context, bool(graph), float(device_us),
                                         float(host_us), int(launches)))
+            key = (program, shape_of(groups, rows))
+            self.steps_by[key] = self.steps_by.get(key, 0) + 1
             at = 0.0
             for i, (label, op, ms, n) in enumerate(calls or []):
                 self._rows["kernels"].append((seq, i, label or "", op, at, at + ms * 1e3, int(n)))
                 at += ms * 1e3
+                self._sampled[1] += ms
+                if op in self.comm:
+                    self._sampled[0] += ms
+            # a step's device time goes to compute and comm by the share the sampled steps have shown so far
+            self.comm_share = self._sampled[0] / self._sampled[1] if self._sampled[1] > 0 else 0.0
+            sec = float(device_us or host_us) / 1e6
+            self.device_seconds["comm"] += sec * self.comm_share
+            self.device_seconds["compute"] += sec * (1.0 - self.comm_share)
         return seq
 
     def counters(self, sm_mhz: int, mem_mhz: int, gpu_util: int, mem_util: int, power_w: float, sm_active_pm: int = -1,
@@ -209,8 +241,51 @@ class TracedEngine:
         return out
 
 
-def prometheus_lines(recorder: Recorder, steps_by: dict | None = None) -> list[str]:
-    return ["# TYPE kern_trace_dropped_records_total counter", f"kern_trace_dropped_records_total {recorder.dropped}"]
+def prometheus_lines(recorder: Recorder, kv: str = "paged") -> list[str]:
+    """The kernels board of one rank from its recorder: device seconds by class (comm = the share of the sampled steps'
+    time spent in `recorder.comm` ops; idle = wall clock not covered by a step), steps by program and shape, dropped
+    records. Reference: crates/kern-serve/src/kernels.rs:188-222."""
+    wall = time.monotonic() - recorder.started
+    busy = recorder.device_seconds["compute"] + recorder.device_seconds["comm"]
+    lines = ["# TYPE kern_device_seconds_total counter",
+             f'kern_device_seconds_total{{class="compute"}} {recorder.device_seconds["compute"]:.6f}',
+             f'kern_device_seconds_total{{class="comm"}} {recorder.device_seconds["comm"]:.6f}',
+             f'kern_device_seconds_total{{class="idle"}} {max(0.0, wall - busy):.6f}',
+             "# TYPE kern_step_compute_seconds_total counter", f"kern_step_compute_seconds_total {busy:.6f}",
+             "# TYPE kern_steps_total counter"]
+    for (program, shape), n in sorted(recorder.steps_by.items()):
+        lines.append(f'kern_steps_total{{program="{program}",shape="{shape}",kv="{kv}"}} {n}')
+    lines += ["# TYPE kern_trace_dropped_records_total counter", f"kern_trace_dropped_records_total {recorder.dropped}"]
+    return lines
+
+
+class Rotator(threading.Thread):
+    """Closes the recorder's files at every boundary of `every_s` seconds of the wall clock (a quarter hour: the files of
+    one directory line up across ranks), looking every `period` seconds, and whenever more than `max_rows` rows are
+    buffered. Reference: crates/kern-serve/src/kernels.rs:294-343 (the 200 ms collector), kern-trace/src/lib.rs:154-204."""
+
+    def __init__(self, recorder: Recorder, every_s: float = 900.0, period: float = 0.2, max_rows: int = 1_000_000, clock=time.time):
+        super().__init__(name="kern-trace-rotate", daemon=True)
+        self.rec, self.every_s, self.period, self.max_rows, self.clock = recorder, every_s, period, max_rows, clock
+        self._halt = threading.Event()
+        self.rotations = 0
+
+    def due(self, last_slot: int) -> tuple[bool, int]:
+        slot = int(self.clock() // self.every_s)
+        rows = sum(len(v) for v in self.rec._rows.values())
+        return (slot != last_slot and rows > 0) or rows > self.max_rows, slot
+
+    def run(self) -> None:
+        last = int(self.clock() // self.every_s)
+        while not self._halt.wait(self.period):
+            go, slot = self.due(last)
+            if go:
+                self.rec.rotate()
+                self.rotations += 1
+            last = slot
+
+    def stop(self) -> None:
+        self._halt.set()
 
 
 # ---- kernel activity through CUPTI --------------------------------------------------------------------------------------

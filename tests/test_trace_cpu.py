@@ -191,6 +191,7 @@ def test_server_trace_flags_record_steps_calls_and_counters(tmp_path):
     time.sleep(0.05)
     sampler.stop()
     sampler.join(2)
+    rec.rotator.stop()
     kinds = {p.name.split(".")[1]: p for p in rec.rotate()}
     assert {"steps", "counters"} <= set(kinds)
     steps = pq.ParquetFile(kinds["steps"]).read().to_pydict()
@@ -200,3 +201,36 @@ def test_server_trace_flags_record_steps_calls_and_counters(tmp_path):
     # without the flag nothing is wrapped
     plain = cli.trace_setup(SimpleNamespace(trace_dir=None), "engine")
     assert plain == ("engine", None, None)
+
+
+def test_kernels_board_from_the_recorder_and_the_rotator(tmp_path):
+    """The board of a traced rank: steps by program and shape, device seconds split into compute and comm by the share
+    the sampled steps' calls show (comm = ops that run a collective built-in or take a peer table), idle = the rest of
+    the wall clock; the rotator closes files at a boundary of its period and when too many rows are buffered."""
+    from kern_b200.models import dense, dense_tp
+
+    doc = dense_tp.build_manifest_tp(__import__("dataclasses").replace(dense.TOY, tp=2))
+    comm = trace.comm_ops(doc)
+    # the fused all-reduce + norm, and the two GEMMs whose epilogue pushes rows into the peers' staging buffers
+    assert comm == {"allreduce_norm", "o_proj", "down_proj"}
+    assert trace.comm_ops(dense.build_manifest(dense.TOY)) == set()
+    rec = trace.Recorder(tmp_path, comm={"allreduce"})
+    rec.step("decode", 8, 8, 100, True, 1000.0, 1100.0, 10)                       # nothing sampled yet: all compute
+    rec.step("prefill", 1, 64, 64, False, 3000.0, 3100.0, 40, calls=[("a", "gemm", 2.0, 1), ("b", "allreduce", 1.0, 1)])
+    rec.step("decode", 8, 8, 101, True, 3000.0, 3100.0, 10)
+    lines = trace.prometheus_lines(rec)
+    assert 'kern_steps_total{program="decode",shape="decode",kv="paged"} 2' in lines
+    assert 'kern_steps_total{program="prefill",shape="prefill",kv="paged"} 1' in lines
+    val = lambda cls: float(next(l for l in lines if f'class="{cls}"' in l).split()[-1])
+    assert abs(val("comm") - 0.002) < 1e-9 and abs(val("compute") - 0.005) < 1e-9 and val("idle") >= 0.0
+    # the rotator: a boundary of the period with rows buffered, or too many rows
+    now = [1000.0]
+    rot = trace.Rotator(rec, every_s=900.0, max_rows=5, clock=lambda: now[0])
+    assert rot.due(int(1000 // 900)) == (False, 1)
+    now[0] = 1801.0
+    assert rot.due(1) == (True, 2)
+    rec.rotate()
+    assert rot.due(1) == (False, 2)                                               # nothing buffered: no empty files
+    for _ in range(6):
+        rec.step("decode", 1, 1, 5, True, 10.0, 11.0, 1)
+    assert rot.due(2) == (True, 2)
