@@ -275,7 +275,8 @@ def cmd_e2e(args) -> int:
         e2e.record(side, qs, source=side.doc["model"], chunk=args.chunk or 256, batch=args.batch).save(args.out)
         print(f"recorded {len(qs)} questions -> {args.out}")
         return 0
-    text, code = e2e.summary(e2e.judge(e2e.Recording.load(args.recording), side, kl_limit=args.logit_kl, chunk=args.chunk or 256))
+    rec = e2e.Recording.load(args.recording)
+    text, code = e2e.summary(e2e.judge(rec, side, kl_limit=args.logit_kl, chunk=args.chunk or 256), noise_mean=rec.noise_mean)
     print(text)
     return code
 

@@ -28,10 +28,17 @@ def test_record_save_load_judge(tmp_path):
     assert e2e.record(side(w), qs[:2], source="solo", batch=1).rows[0]["noise"] == 0.0      # alone twice: the same bits
     text, code = e2e.summary(e2e.judge(back, side(w)))
     assert code == 0 and "PASS: 3/3" in text
+    # the verdict over all positions: mean KL against the recording's own noise + 3 standard errors, with the means by
+    # decode step and context depth
+    assert 0.0 <= back.noise_mean < 1e-4
+    text, code = e2e.summary(e2e.judge(back, side(w)), noise_mean=back.noise_mean)
+    last = text.splitlines()[-1]
+    assert code == 0 and last.startswith("PASS      mean KL") and "over 18 scored positions" in last
+    assert "mean KL by decode step" in text and "mean KL by context depth" in text
     w2 = dict(w)
     w2["lm_head.weight"] = (w["lm_head.weight"].float() + 0.2 * (np.random.default_rng(0).standard_normal(w["lm_head.weight"].shape)).astype(np.float32)).to(w["lm_head.weight"].dtype)
-    text, code = e2e.summary(e2e.judge(back, side(w2)))
-    assert code == 1 and "FAIL" in text
+    text, code = e2e.summary(e2e.judge(back, side(w2)), noise_mean=back.noise_mean)
+    assert code == 1 and text.splitlines()[-1].startswith("FAIL      mean KL")
 
 
 def test_kl_top_is_zero_on_itself_and_positive_off():
