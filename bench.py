@@ -76,7 +76,7 @@ def main():
     ap.add_argument("--steps", type=int, default=256, help="timed steps (256 = every live sequence turns over once)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="b", choices=["b", "c", "d", "toy"],
+    ap.add_argument("--config", default="b", choices=["b", "c", "d", "e", "toy"],
                     help="b: dense GQA 8B-class at concurrency 256 (the headline); c: the hybrid 27B-class decoder under agent-style "
                          "traffic on one GPU; d: decode of a routed-experts decoder with the experts sharded over the GPUs "
                          "(fused dispatch / combine); toy: the reference's own toy-paged package "
@@ -112,6 +112,15 @@ def main():
         from kern_b200.testing import bench_agent
 
         return bench_agent.main(args)
+    if args.config == "e":
+        # pipeline-parallel prefill of long prompts, then decode of the batch, a process per stage (torchrun ranks = stages)
+        from kern_b200.parallel import pp_pipeline_check
+
+        os.environ.setdefault("RANK", "0"); os.environ.setdefault("WORLD_SIZE", "1")
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29571")
+        return pp_pipeline_check.main(["--bench", "--json-line", "--model", "latent-48b-a3b", "--prompt", "32768", "--chunk", "2048",
+                                       "--requests", str(max(1, min(args.concurrency, 4))), "--decode-steps", str(min(args.steps, 64)),
+                                       "--timeout", "120"] + (["--layers", str(args.layers)] if args.layers != 36 else []))
     if args.config == "d":
         from kern_b200.testing import bench_ep
 
