@@ -79,7 +79,8 @@ def main():
     ap.add_argument("--config", default="b", choices=["b", "c", "d", "e", "toy"],
                     help="b: dense GQA 8B-class at concurrency 256 (the headline); c: the hybrid 27B-class decoder under agent-style "
                          "traffic on one GPU; d: decode of a routed-experts decoder with the experts sharded over the GPUs "
-                         "(fused dispatch / combine); toy: the reference's own toy-paged package "
+                         "(fused dispatch / combine); e: pipelined prefill of 32k-token prompts, then decode, over the KDA + latent-attention + "
+                         "routed-experts decoder, a stage per GPU; toy: the reference's own toy-paged package "
                          "(its manifest and cubin) served by this engine, the workload of the reference arm")
     ap.add_argument("--concurrency", type=int, default=256)
     ap.add_argument("--layers", type=int, default=36, help="for quick functional checks only; the headline is 36")
