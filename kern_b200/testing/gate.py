@@ -9,7 +9,8 @@ same request produces alone.
 so a difference is a bug and not noise (on bf16 models near-ties may flip between batch shapes: a scenario then reports
 the first differing position and how close the two logits were is left to `kern test`).
 Reference: tools/e2e/e2e.py (scenarios `conc1_equals_run`, `rows1_equals_run`, `repeat_hit`, `turn2_*`, `concurrent`,
-`abort`, `slot_pressure`), tools/e2e/README.md.
+`abort` by a client that hangs up mid-stream, `slot_pressure`, `kept_nothing`, `spec_acceptance` / `rows1_vs_spec`),
+tools/e2e/README.md.
 """
 from __future__ import annotations
 
@@ -143,7 +144,97 @@ class Gate:
                 return Result("slot_pressure", False, f"{r.id}: {d}")
         return Result("slot_pressure", True, f"{len(reqs)} requests through {tokens // self.page} pages, {s.stats.evictions} evictions")
 
-    SCENARIOS = ("conc1_equals_run", "rows1_equals_run", "repeat_hit", "turn2", "concurrent", "abort", "slot_pressure")
+    def kept_nothing(self) -> Result:
+        """After a mix of sessions, aborts and cache hits, letting go of every cached prefix leaves the pool as it
+        started: every page and slot free (nothing leaked by a finished, aborted or evicted request)."""
+        s = Scheduler(self.make(self.capacity))
+        prompts = [self.prompt(self.page + 2 + 3 * i) for i in range(4)]
+        reqs = [Request(id=f"r{i}", prompt=p, max_tokens=self.n) for i, p in enumerate(prompts)]
+        for r in reqs:
+            s.submit(r)
+        for _ in range(2):
+            s.step()
+        s.abort("r1")
+        s.run_until_idle(3000)
+        again = Request(id="again", prompt=prompts[0], max_tokens=self.n)        # a hit on what r0 left behind
+        self.serve(s, [again])
+        total_pages, free_before = s.pool.total_pages, s.pool.free_pages
+        if s.prefix is not None:
+            while len(s.prefix):                                                 # whatever the cache still keeps goes
+                s.prefix.evict()
+        pad = int(getattr(s.eng, "pad_pages", 0))                                 # the engine's own page for padding rows
+        ok = s.idle() and s.pool.free_pages == total_pages - pad
+        return Result("kept_nothing", ok, f"free {s.pool.free_pages} of {total_pages} ({pad} held for padding rows; "
+                                          f"before letting the cache go: {free_before})")
+
+    def http_hang_up(self) -> Result:
+        """A client that streams a few chunks and closes its connection: the request is aborted, its pages come back,
+        and a request that shared the batch finishes with the tokens it has alone."""
+        import http.client
+        import json
+        import time
+
+        from ..serve.server import Server
+
+        s = Scheduler(self.make(self.capacity), prefix_cache=False)
+        srv = Server(s, model_name="gate", port=0).start()
+        try:
+            pa, pb = self.prompt(self.page + 4), self.prompt(self.page + 9)
+            conn = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=60)
+            conn.request("POST", "/v1/completions", json.dumps({"prompt": pa, "max_tokens": 6 * self.n, "stream": True, "ignore_eos": True}),
+                         {"Content-Type": "application/json"})
+            resp = conn.getresponse()
+            got = 0
+            while got < 2:                                   # two streamed chunks, then the client leaves
+                line = resp.readline()
+                if not line:
+                    break
+                got += line.startswith(b"data: {")
+            resp.close()
+            conn.close()
+            other = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=60)
+            other.request("POST", "/v1/completions", json.dumps({"prompt": pb, "max_tokens": self.n, "return_token_ids": True, "ignore_eos": True}),
+                          {"Content-Type": "application/json"})
+            body = json.loads(other.getresponse().read())
+            other.close()
+            d = self.differ(body["choices"][0]["token_ids"], self.alone(pb))
+            deadline = time.monotonic() + 20
+            while time.monotonic() < deadline and not (s.idle() and s.pool.free_pages == s.pool.total_pages):
+                time.sleep(0.02)
+            pad = int(getattr(s.eng, "pad_pages", 0))
+            gone = any(r.id != body["id"] and r.finished == "abort" for r in s.done)      # the hung-up request was aborted, not served out
+            ok = got == 2 and not d and gone and s.idle() and s.pool.free_pages == s.pool.total_pages - pad
+            return Result("http_hang_up", ok, d or f"chunks read {got}, aborted {gone}, free {s.pool.free_pages} of {s.pool.total_pages} after the client left")
+        finally:
+            srv.stop()
+
+    def spec_acceptance(self) -> Result:
+        """A package with speculative rounds: the tokens of a round-by-round run equal the one-row-per-step run's
+        (`rows1_vs_spec`), and a burst of concurrent requests keeps the acceptance rate of a single one within bounds."""
+        eng = self.make(self.capacity)
+        rounds = [f for f in eng.forwards if f["rows"] != "var" and f["rows"] > 1]
+        if not rounds:
+            return Result("spec_acceptance", True, "no round program in this package (skipped)")
+        p = self.prompt(self.page + 6)
+        s1 = Scheduler(eng)
+        a = Request(id="a", prompt=p, max_tokens=4 * self.n)
+        self.serve(s1, [a])
+        base = s1.stats.accepted / max(1, s1.stats.proposed)
+        plain = Scheduler(self.make(self.capacity), rows=1)
+        b = Request(id="b", prompt=p, max_tokens=4 * self.n)
+        self.serve(plain, [b])
+        d = self.differ(a.out, b.out)
+        s2 = Scheduler(self.make(self.capacity))
+        burst = [Request(id=f"c{i}", prompt=self.prompt(self.page + i), max_tokens=4 * self.n) for i in range(3)] + \
+                [Request(id="same", prompt=p, max_tokens=4 * self.n)]
+        self.serve(s2, burst, steps=5000)
+        rate = s2.stats.accepted / max(1, s2.stats.proposed)
+        d = d or self.differ(burst[-1].out, a.out)
+        ok = not d and s1.stats.proposed > 0 and all(r.finished == "length" for r in burst)
+        return Result("spec_acceptance", ok, d or f"acceptance {base:.2f} alone, {rate:.2f} in a burst of {len(burst)}")
+
+    SCENARIOS = ("conc1_equals_run", "rows1_equals_run", "repeat_hit", "turn2", "concurrent", "abort", "slot_pressure",
+                 "kept_nothing", "http_hang_up", "spec_acceptance")
 
     def run(self, only: list[str] | None = None) -> list[Result]:
         out = []
