@@ -227,11 +227,40 @@ def cmd_gate(args) -> int:
 
 
 def cmd_kernels(args) -> int:
+    """`kern kernels`: the modules of the build in use; `index` / `check` / `pick`: the kernel registry (`kernel_registry.py`)."""
     from .models.common import kernel_index
 
-    for name, e in sorted(kernel_index().items()):
-        print(f"{e['sha256']}  {e['source']}")
-    return 0
+    what = getattr(args, "what", None)
+    if what in (None, "list"):
+        for name, e in sorted(kernel_index().items()):
+            print(f"{e['sha256']}  {e['source']}")
+        return 0
+    from . import kernel_registry as R
+
+    if what == "index":
+        paths = R.write_all()
+        print(f"{len(paths)} families -> {R.INDEX}")
+        return 0
+    if what == "check":
+        errs = R.check(require_reports=not args.no_reports)
+        for e in errs:
+            print(e)
+        print(f"{len([p for p in R.INDEX.glob('*.toml') if p != R.PICKS])} families, {len(R.load_picks())} picks, {len(errs)} findings")
+        return 1 if errs else 0
+    if what == "pick":
+        if len(args.rest) != 5:
+            print("usage: kern kernels pick <family> <op> <shape> <variant> <bench.json> [--entry NAME]")
+            return 2
+        family, op, shape, variant, report = args.rest
+        try:
+            rec = R.pick(family, op, shape, variant, report, entry=args.entry)
+        except ValueError as e:
+            print(e)
+            return 1
+        print(f"{family}: {op} on {shape} -> {variant}" + (f" / {rec['entry']}" if "entry" in rec else "") + f" (report @{rec['report'][:12]})")
+        return 0
+    print(f"unknown: kernels {what}")
+    return 2
 
 
 def _prompt_ids(args, tok=None):
@@ -646,7 +675,11 @@ def main(argv=None) -> int:
 
     v = sub.add_parser("verify"); v.add_argument("manifest")
     c = sub.add_parser("cut"); c.add_argument("manifest"); c.add_argument("--at", required=True); c.add_argument("--out", required=True)
-    sub.add_parser("kernels")
+    kn = sub.add_parser("kernels")
+    kn.add_argument("what", nargs="?", choices=["list", "index", "check", "pick"])
+    kn.add_argument("rest", nargs="*", help="pick: <family> <op> <shape> <variant> <bench.json>")
+    kn.add_argument("--entry", help="pick: the entry of the variant that was measured best")
+    kn.add_argument("--no-reports", action="store_true", help="check: do not require the picks' reports to be in the local store")
     gt = sub.add_parser("gate", help="the serving scenarios every model target must pass"); common(gt)
     gt.add_argument("--only", help="comma-separated scenario names"); gt.add_argument("--seed", type=int, default=0)
     gt.add_argument("--vocab", type=int, help="token id range when the manifest declares no domain")
