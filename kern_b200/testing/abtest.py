@@ -303,6 +303,69 @@ def _buffer_bytes(doc: dict, name: str) -> tuple:
     return None if b is None else (b["dtype"], tuple(b["shape"]))
 
 
+class DeltaImages:
+    """Images of buffers, by (key, name), kept as deltas: a buffer's first image in full, every later one as the 64-byte
+    blocks that differ from the image before it (most of a workspace does not change between two looks at it, and a
+    recording of every span of every step in full would be many times the model's activations). `get` rebuilds an
+    image by applying the deltas in order from the last image it rebuilt (the replay asks in recording order, so each
+    `get` applies one delta); any earlier key is rebuilt from the buffer's first image.
+    Reference: crates/kern-test/src/harness.rs:130-220 (delta snapshots, changed blocks)."""
+
+    BLOCK = 64
+
+    def __init__(self):
+        self._chain: dict[str, list] = {}          # name -> [(key, None, full image) | (key, block indices, block bytes)]
+        self._last: dict[str, "torch.Tensor"] = {}  # name -> the latest image put (what the next delta is against)
+        self._cursor: dict[str, tuple[int, "torch.Tensor"]] = {}      # name -> (position in the chain, image there)
+        self.full_bytes = 0                        # what whole images would have taken
+        self.kept_bytes = 0                        # what is kept
+
+    def put(self, key, name: str, img) -> None:
+        import torch
+
+        img = img.contiguous().view(-1).view(torch.uint8)
+        self.full_bytes += img.numel()
+        prev = self._last.get(name)
+        if prev is None or prev.numel() != img.numel():
+            self._chain.setdefault(name, []).append((key, None, img.clone()))
+            self.kept_bytes += img.numel()
+        else:
+            n, B = img.numel(), self.BLOCK
+            whole = n // B * B
+            changed = (img[:whole].view(-1, B) != prev[:whole].view(-1, B)).any(1).nonzero().flatten()
+            blocks = img[:whole].view(-1, B)[changed].clone()
+            tail = img[whole:].clone()             # the odd bytes at the end travel whole
+            self._chain[name].append((key, changed.to(torch.int32), (blocks, tail)))
+            self.kept_bytes += blocks.numel() + tail.numel() + 4 * changed.numel()
+        self._last[name] = img.clone()
+
+    def get(self, key, name: str):
+        chain = self._chain[name]
+        at = next((i for i, e in enumerate(chain) if e[0] == key), None)
+        if at is None:
+            raise KeyError((key, name))
+        pos, img = self._cursor.get(name, (-1, None))
+        if pos > at or img is None:
+            pos, img = -1, None
+        while pos < at:
+            pos += 1
+            _k, idx, payload = chain[pos]
+            if idx is None:
+                img = payload.clone()
+            else:
+                blocks, tail = payload
+                whole = img.numel() // self.BLOCK * self.BLOCK
+                if idx.numel():
+                    img[:whole].view(-1, self.BLOCK)[idx.long()] = blocks
+                if tail.numel():
+                    img[whole:] = tail
+        self._cursor[name] = (pos, img)
+        return img.clone()
+
+    def has(self, key, name: str) -> bool:
+        return any(e[0] == key for e in self._chain.get(name, []))
+
+
 class SpanTap:
     """An engine probe (``Engine.probe``) that runs a program in call ranges around its changed spans.
 
@@ -316,6 +379,7 @@ class SpanTap:
 
     def __init__(self, mine: dict, other: dict, spans_by_program: dict, side: str, store: dict, results: list | None = None):
         self.doc, self.other, self.side, self.store = mine, other, side, store
+        self.images: DeltaImages = store.setdefault("__images__", DeltaImages())      # shared by the two sides' taps
         self.results = results if results is not None else []
         self.spans = {p: [sp for sp in ss if sp["a"] and sp["b"]] for p, ss in spans_by_program.items()}
         self.step = 0
@@ -348,9 +412,12 @@ class SpanTap:
             n += rt.issue_range(program, vars, lo, first)
             key = key_step + (k,)
             if self.side == "a":
-                self.store[key] = {"in": self._image(rt, reads)}
+                self.store[key] = {"in": list(reads), "out": list(writes)}
+                for name, img in self._image(rt, reads).items():
+                    self.images.put(key + ("in",), name, img)
                 n += rt.issue_range(program, vars, first, last)
-                self.store[key]["out"] = self._image(rt, writes)
+                for name, img in self._image(rt, writes).items():
+                    self.images.put(key + ("out",), name, img)
             else:
                 rec = self.store.get(key)
                 if rec is None:
@@ -359,13 +426,14 @@ class SpanTap:
                 else:
                     if hasattr(rt, "synchronize"):
                         rt.synchronize()
-                    for name, img in rec["in"].items():
+                    for name in rec["in"]:
                         t = rt.tensor(name)
-                        t.view(-1).view(torch.uint8).copy_(img.to(t.device))
+                        t.view(-1).view(torch.uint8).copy_(self.images.get(key + ("in",), name).to(t.device))
                     n += rt.issue_range(program, vars, first, last)
                     got = self._image(rt, writes)
                     for name in writes:
-                        c = compare_bytes(self.doc["buffers"][name]["dtype"], rec["out"][name].numpy().tobytes(), got[name].numpy().tobytes())
+                        want = self.images.get(key + ("out",), name)
+                        c = compare_bytes(self.doc["buffers"][name]["dtype"], want.numpy().tobytes(), got[name].numpy().tobytes())
                         self.results.append({"program": program, "span": k, "step": key_step[2], "buffer": name,
                                              "identical": c.identical, "value_identical": c.value_identical,
                                              "differing": c.n_diff, "max_abs": c.max_abs, "max_ulp": c.max_ulp})
@@ -391,6 +459,9 @@ def replay_spans(side_a: "EngineSide", side_b: "EngineSide", work: list[list[int
         side_b.forced_run(work, forced, chunk)
     finally:
         side_b.eng.probe = None
+    img = store["__images__"]
+    if results:
+        results[0]["snapshot_bytes"] = {"whole_images": img.full_bytes, "kept_as_deltas": img.kept_bytes}
     return results
 
 
