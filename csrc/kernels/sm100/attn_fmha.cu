@@ -98,9 +98,14 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
   uint8_t* p_s = q_s + Cfg::kQBytes;
   uint8_t* kv_s = p_s + Cfg::kPBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + kStages * 2 * Cfg::kTileBytes);
-  uint64_t* kv_full = bars;                  // [stages]  TMA -> MMA
-  uint64_t* kv_empty = bars + kStages;       // [stages]  P V done with the stage
-  uint64_t* s_full = kv_empty + kStages;     // [2]       S buffer written
+  // K and V of a stage have barriers of their own: a stage's K half is free as soon as Q K^T has read it — a whole tile
+  // period before P V lets go of the V half — so the load of the K tile after next starts that much earlier and Q K^T
+  // never waits for a load that was only just issued.
+  uint64_t* k_full = bars;                   // [stages]  TMA -> MMA (K half)
+  uint64_t* v_full = k_full + kStages;       // [stages]  TMA -> MMA (V half)
+  uint64_t* k_empty = v_full + kStages;      // [stages]  Q K^T done with the K half
+  uint64_t* v_empty = k_empty + kStages;     // [stages]  P V done with the V half
+  uint64_t* s_full = v_empty + kStages;      // [2]       S buffer written
   uint64_t* s_empty = s_full + 2;            // [2]       softmax has read the S buffer (128 arrivals)
   uint64_t* p_full = s_empty + 2;            // [1]       P in shared memory (128 arrivals)
   uint64_t* p_empty = p_full + 1;            // [1]       P V has consumed P (and O is quiet)
@@ -126,7 +131,10 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
   const int ntiles = last_pos / FN + 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1);
+      mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+    }
     for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 128); }
     mbar_init(p_full, 128);
     mbar_init(p_empty, 1);
@@ -164,17 +172,19 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
     if (lane == 0) {
       const int box_rows = a.page_size < 64 ? a.page_size : 64;
       const int boxes = FN / box_rows;
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int t = 0; t < ntiles; ++t) {
-        if (!mbar_wait_ns(&kv_empty[stage], phase ^ 1, abort_flag)) {
+      // one half (K: which = 0, V: which = 1) of tile t into its stage, behind the half's own empty barrier
+      auto load_half = [&](int t, int which) -> bool {
+        const int stage = t % kStages;
+        const uint32_t parity = ((t / kStages) & 1) ^ 1;
+        uint64_t* empty = which ? &v_empty[stage] : &k_empty[stage];
+        uint64_t* full = which ? &v_full[stage] : &k_full[stage];
+        if (!mbar_wait_ns(empty, parity, abort_flag)) {
           set_error(a.err, ERR_WAIT_EMPTY);
           *abort_flag = 1;
-          break;
+          return false;
         }
-        uint8_t* sk = kv_s + stage * 2 * Cfg::kTileBytes;
-        uint8_t* sv = sk + Cfg::kTileBytes;
-        mbar_expect_tx(&kv_full[stage], 2 * Cfg::kTileBytes);
+        uint8_t* dst = kv_s + stage * 2 * Cfg::kTileBytes + which * Cfg::kTileBytes;
+        mbar_expect_tx(full, Cfg::kTileBytes);
         for (int b = 0; b < boxes; ++b) {
           const int tok = t * FN + b * box_rows;
           int page = 0, in_page = 0;
@@ -187,15 +197,19 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
             set_error(a.err, ERR_BOUNDS);
             page = 0;
           }
-          const int krow = ((page * 2 + 0) * a.hk + kvh) * a.page_size + in_page;
-          const int vrow = ((page * 2 + 1) * a.hk + kvh) * a.page_size + in_page;
+          const int row = ((page * 2 + which) * a.hk + kvh) * a.page_size + in_page;
 #pragma unroll
-          for (int cb = 0; cb < D / 64; ++cb) {
-            tma_load_2d(sk + cb * (FN * 128) + b * box_rows * 128, kv_map, cb * 64, krow, &kv_full[stage]);
-            tma_load_2d(sv + cb * (FN * 128) + b * box_rows * 128, kv_map, cb * 64, vrow, &kv_full[stage]);
-          }
+          for (int cb = 0; cb < D / 64; ++cb)
+            tma_load_2d(dst + cb * (FN * 128) + b * box_rows * 128, kv_map, cb * 64, row, full);
         }
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
+        return true;
+      };
+      // issue order K(0), then for every tile K(t + 1) before V(t): the waits then come in the order the MMAs complete
+      // (Q K^T of tile t - 1 is issued before P V of tile t - 2)
+      bool ok = load_half(0, 0);
+      for (int t = 0; t < ntiles && ok; ++t) {
+        if (t + 1 < ntiles) ok = load_half(t + 1, 0);
+        if (ok) ok = load_half(t, 1);
       }
     }
   } else if (warp == 1) {
@@ -207,7 +221,7 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
       bool ok = true;
       auto issue_qk = [&](int j) {
         const int stage = j % kStages;
-        if (!mbar_wait_ns(&kv_full[stage], (j / kStages) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
+        if (!mbar_wait_ns(&k_full[stage], (j / kStages) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
         if (!mbar_wait_ns(&s_empty[j & 1], ((j >> 1) & 1) ^ 1, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_EMPTY); return false; }
         tc_fence_after();
         const uint32_t sq = smem_u32(q_s), sk = smem_u32(kv_s + stage * 2 * Cfg::kTileBytes);
@@ -216,10 +230,12 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
           umma_bf16(tmem_base + (j & 1) * FN, umma_desc_sw128(sq + (k >> 2) * (FM * 128) + (k & 3) * 32),
                     umma_desc_sw128(sk + (k >> 2) * (FN * 128) + (k & 3) * 32), idesc_qk, k != 0);
         tc_commit(&s_full[j & 1]);
+        tc_commit(&k_empty[stage]);         // the K half is free once these MMAs have read it
         return true;
       };
       auto issue_pv = [&](int j) {
         const int stage = j % kStages;
+        if (!mbar_wait_ns(&v_full[stage], (j / kStages) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
         if (!mbar_wait_ns(p_full, j & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
         tc_fence_after();
         const uint32_t sp = smem_u32(p_s), sv = smem_u32(kv_s + stage * 2 * Cfg::kTileBytes + Cfg::kTileBytes);
@@ -227,7 +243,7 @@ KERN_DEVICE void fmha_body(const CUtensorMap* kv_map, const FmhaArgs& a, const i
         for (int k = 0; k < FN / 16; ++k)
           umma_bf16(o_tmem, umma_desc_sw128(sp + (k >> 2) * (FM * 128) + (k & 3) * 32),
                     umma_desc_sw128_mn(sv + k * 16 * 128, FN * 128), idesc_pv, (j | k) != 0);
-        tc_commit(&kv_empty[stage]);        // K and V of the stage are free
+        tc_commit(&v_empty[stage]);         // the V half of the stage is free
         tc_commit(p_empty);                 // P is consumed and O is quiet until the next P V
         if (j == ntiles - 1) tc_commit(o_full);
         return true;
