@@ -462,9 +462,13 @@ KERN_DEVICE void fmha_ctx_body(const CUtensorMap* k_map, const CUtensorMap* v_ma
   uint8_t* p_s = q_s + Cfg::kQBytes;
   uint8_t* kv_s = p_s + Cfg::kPBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + kStages * (Cfg::kKBytes + Cfg::kVBytes));
-  uint64_t* kv_full = bars;
-  uint64_t* kv_empty = bars + kStages;
-  uint64_t* s_full = kv_empty + kStages;
+  // K and V of a stage on barriers of their own, as in fmha_body: with one stage that alone lets the next tile's K load
+  // (and Q K^T) run under this tile's softmax and P V
+  uint64_t* k_full = bars;
+  uint64_t* v_full = k_full + kStages;
+  uint64_t* k_empty = v_full + kStages;
+  uint64_t* v_empty = k_empty + kStages;
+  uint64_t* s_full = v_empty + kStages;
   uint64_t* s_empty = s_full + 2;
   uint64_t* p_full = s_empty + 2;
   uint64_t* p_empty = p_full + 1;
@@ -487,7 +491,10 @@ KERN_DEVICE void fmha_ctx_body(const CUtensorMap* k_map, const CUtensorMap* v_ma
   const int ntiles = last_pos / FN + 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1);
+      mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+    }
     for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 128); }
     mbar_init(p_full, 128);
     mbar_init(p_empty, 1);
@@ -523,24 +530,34 @@ KERN_DEVICE void fmha_ctx_body(const CUtensorMap* k_map, const CUtensorMap* v_ma
   if (warp == 0) {
     // ---------------- producer: K (DQK / 64 boxes) and V (DV / 64 boxes) of every 64-token tile ----------------
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int t = 0; t < ntiles; ++t) {
-        if (!mbar_wait_ns(&kv_empty[stage], phase ^ 1, abort_flag)) {
+      auto load_half = [&](int t, int which) -> bool {
+        const int stage = t % kStages;
+        const uint32_t parity = ((t / kStages) & 1) ^ 1;
+        if (!mbar_wait_ns(which ? &v_empty[stage] : &k_empty[stage], parity, abort_flag)) {
           set_error(a.err, ERR_WAIT_EMPTY);
           *abort_flag = 1;
-          break;
+          return false;
         }
         uint8_t* sk = kv_s + stage * (Cfg::kKBytes + Cfg::kVBytes);
-        uint8_t* sv = sk + Cfg::kKBytes;
-        mbar_expect_tx(&kv_full[stage], Cfg::kKBytes + Cfg::kVBytes);
         const int krow = k0 + t * FN;                 // rows past the sequence's end belong to the next one (or are out of
                                                       // range and read as zero): the causal limit masks them
+        if (which == 0) {
+          mbar_expect_tx(&k_full[stage], Cfg::kKBytes);
 #pragma unroll
-        for (int cb = 0; cb < DQK / 64; ++cb) tma_load_2d(sk + cb * (FN * 128), k_map, head * DQK + cb * 64, krow, &kv_full[stage]);
+          for (int cb = 0; cb < DQK / 64; ++cb) tma_load_2d(sk + cb * (FN * 128), k_map, head * DQK + cb * 64, krow, &k_full[stage]);
+        } else {
+          uint8_t* sv = sk + Cfg::kKBytes;
+          mbar_expect_tx(&v_full[stage], Cfg::kVBytes);
 #pragma unroll
-        for (int cb = 0; cb < DV / 64; ++cb) tma_load_2d(sv + cb * (FN * 128), v_map, head * DV + cb * 64, krow, &kv_full[stage]);
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
+          for (int cb = 0; cb < DV / 64; ++cb) tma_load_2d(sv + cb * (FN * 128), v_map, head * DV + cb * 64, krow, &v_full[stage]);
+        }
+        return true;
+      };
+      // K(0), then K(t + 1) before V(t): the waits come in the order the MMAs complete
+      bool ok = load_half(0, 0);
+      for (int t = 0; t < ntiles && ok; ++t) {
+        if (t + 1 < ntiles) ok = load_half(t + 1, 0);
+        if (ok) ok = load_half(t, 1);
       }
     }
   } else if (warp == 1) {
@@ -552,7 +569,7 @@ KERN_DEVICE void fmha_ctx_body(const CUtensorMap* k_map, const CUtensorMap* v_ma
       bool ok = true;
       auto issue_qk = [&](int j) {
         const int stage = j % kStages;
-        if (!mbar_wait_ns(&kv_full[stage], (j / kStages) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
+        if (!mbar_wait_ns(&k_full[stage], (j / kStages) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
         if (!mbar_wait_ns(&s_empty[j & 1], ((j >> 1) & 1) ^ 1, abort_flag)) { set_error(a.err, ERR_WAIT_TMEM_EMPTY); return false; }
         tc_fence_after();
         const uint32_t sq = smem_u32(q_s), sk = smem_u32(kv_s + stage * (Cfg::kKBytes + Cfg::kVBytes));
@@ -561,10 +578,12 @@ KERN_DEVICE void fmha_ctx_body(const CUtensorMap* k_map, const CUtensorMap* v_ma
           umma_bf16(tmem_base + (j & 1) * FN, umma_desc_sw128(sq + (k >> 2) * (FM * 128) + (k & 3) * 32),
                     umma_desc_sw128(sk + (k >> 2) * (FN * 128) + (k & 3) * 32), idesc_qk, k != 0);
         tc_commit(&s_full[j & 1]);
+        tc_commit(&k_empty[stage]);         // the K half is free once these MMAs have read it
         return true;
       };
       auto issue_pv = [&](int j) {
         const int stage = j % kStages;
+        if (!mbar_wait_ns(&v_full[stage], (j / kStages) & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
         if (!mbar_wait_ns(p_full, j & 1, abort_flag)) { set_error(a.err, ERR_WAIT_FULL); return false; }
         tc_fence_after();
         const uint32_t sp = smem_u32(p_s), sv = smem_u32(kv_s + stage * (Cfg::kKBytes + Cfg::kVBytes) + Cfg::kKBytes);
@@ -572,20 +591,17 @@ KERN_DEVICE void fmha_ctx_body(const CUtensorMap* k_map, const CUtensorMap* v_ma
         for (int k = 0; k < FN / 16; ++k)
           umma_bf16(o_tmem, umma_desc_sw128(sp + (k >> 2) * (FM * 128) + (k & 3) * 32),
                     umma_desc_sw128_mn(sv + k * 16 * 128, FN * 128), idesc_pv, (j | k) != 0);
-        tc_commit(&kv_empty[stage]);
+        tc_commit(&v_empty[stage]);
         tc_commit(p_empty);
         if (j == ntiles - 1) tc_commit(o_full);
         return true;
       };
       ok = issue_qk(0);
       for (int j = 0; j < ntiles && ok; ++j) {
-        if constexpr (kStages >= 2) {          // the next tile's scores first: they overlap this tile's softmax
-          if (j + 1 < ntiles) ok = issue_qk(j + 1);
-          if (ok) ok = issue_pv(j);
-        } else {                               // one stage: the next tile can only be loaded once this tile's P V has read V
-          ok = issue_pv(j);
-          if (ok && j + 1 < ntiles) ok = issue_qk(j + 1);
-        }
+        // the next tile's scores first: they overlap this tile's softmax (with one stage too: its K half was free
+        // as soon as this tile's Q K^T had read it)
+        if (j + 1 < ntiles) ok = issue_qk(j + 1);
+        if (ok) ok = issue_pv(j);
       }
       if (!ok) *abort_flag = 1;
     }
