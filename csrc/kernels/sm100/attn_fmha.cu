@@ -435,7 +435,8 @@ struct CtxArgs {
 };
 
 // ST: stages of the K / V ring. 2: one CTA per SM (146 KB), the next tile's scores are issued before this tile's P V.
-// 1: 106 KB, two CTAs per SM, each strictly load -> S -> softmax -> P V, overlapping one another.
+// 1: 106 KB, two CTAs per SM; the K and V halves have barriers of their own, so the next tile's K is loaded (and its
+// scores issued) while this tile's softmax and P V still hold V: the one stage pipelines too.
 template <int DQK, int DV, int FN, int ST>
 struct CtxCfg {
   static constexpr int kQBytes = FM * DQK * 2;
