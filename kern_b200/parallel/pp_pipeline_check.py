@@ -41,6 +41,10 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    if os.environ.get("KERN_LOG"):            # KERN_LOG=debug: every stage writes its `pp item` lines (serve/pp_timeline.py reads them)
+        from ..utils.logline import setup_logging
+
+        setup_logging()
     import datetime
 
     host_timeout = datetime.timedelta(seconds=max(30.0, 4 * a.timeout))

@@ -26,6 +26,7 @@ reference pushes with its own copy kernels and device gates; here the transport 
 from __future__ import annotations
 
 import json
+import logging
 import time
 from dataclasses import dataclass, field
 
@@ -38,6 +39,7 @@ from . import pp as pp_cut
 
 LANDINGS = 2
 TIMEOUT = 60.0
+log = logging.getLogger("kern.serve")
 _NP = {"i32": np.int32, "i64": np.int64, "f32": np.float32}
 
 
@@ -114,6 +116,9 @@ class Stage:
         self.ready = [self.st.event() for _ in range(LANDINGS)]             # a send twin holds item k's outputs
         self.sent = [self.st.event() for _ in range(LANDINGS)]
         self.sends: list = [[] for _ in range(LANDINGS)]                   # outstanding send handles per twin (CPU ranks wait on them)
+        self.timeline: list[tuple[int, int, int, int]] = []                # (item, rows, issued_us, done_us) of every item run here
+        self._stamps: list = []                                            # GPU: items whose end event has not happened yet
+        self._t0 = None                                                    # GPU: (event, host microseconds) the ends are measured from
         self.items = 0
         self.moved_bytes = 0
 
@@ -135,6 +140,7 @@ class Stage:
     # ---- one item ----
     def run(self, item: Item):
         rt, st, j = self.rt, self.st, item.k % LANDINGS
+        issued_us = time.perf_counter_ns() // 1000
         bufs = self.doc["buffers"]
         for name, (dtype, vals) in item.columns.items():
             if name in bufs and bufs[name]["kind"] == "input":
@@ -184,9 +190,40 @@ class Stage:
                     self.outgoing[n][j][:sizes[n]].copy_(self.bufs[n][:sizes[n]])
                 self.sends[j] = [dist.isend(self.outgoing[n][j][:sizes[n]], dst=self._peer(self.rank + 1), group=self.data_pg) for n in self.leave]
         self.items += 1
+        self._stamp(item, issued_us)
         if self.rank == self.world - 1 and item.emits is not None:
             return self._tokens_later(item) if st.cuda else self._tokens(item)
         return None
+
+    def _stamp(self, item: Item, issued_us: int) -> None:
+        """One `pp item` line per item: when this stage issued it and when it left the device (its kernels and the copy
+        into the send twin), on this process's clock. On a GPU the end is an event resolved later, when it has
+        happened, so the stage never waits for its own stamp. `serve/pp_timeline.py` reads the lines of all stages."""
+        rows = int(item.vars.get("tokens", item.vars.get("rows", item.groups)) or 0)
+        if self.st.cuda:
+            if self._t0 is None:
+                self._t0 = (torch.cuda.Event(enable_timing=True), time.perf_counter_ns() // 1000)
+                self._t0[0].record(self.st.compute)
+                self._t0[0].synchronize()
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(self.st.compute)
+            self._stamps.append((item.k, rows, issued_us, ev))
+            while self._stamps and self._stamps[0][3].query():
+                k, r, iu, e = self._stamps.pop(0)
+                self._emit(k, r, iu, self._t0[1] + int(self._t0[0].elapsed_time(e) * 1e3))
+        else:
+            self._emit(item.k, rows, issued_us, time.perf_counter_ns() // 1000)
+
+    def _emit(self, k: int, rows: int, issued_us: int, done_us: int) -> None:
+        self.timeline.append((k, rows, issued_us, max(done_us, issued_us)))
+        log.debug("pp item stage=%d item=%d rows=%d issued_us=%d done_us=%d", self.rank, k, rows, issued_us, max(done_us, issued_us))
+
+    def flush_stamps(self) -> None:
+        """Resolve the stamps still pending (after a synchronize: at the end of a run)."""
+        while self._stamps:
+            k, r, iu, e = self._stamps.pop(0)
+            e.synchronize()
+            self._emit(k, r, iu, self._t0[1] + int(self._t0[0].elapsed_time(e) * 1e3))
 
     def _tokens_later(self, item: Item):
         """GPU: copy the item's outputs to pinned memory behind its kernels and hand back something to wait on — the
@@ -258,6 +295,7 @@ class Stage:
             self._sync(f"stage {self.rank}: drain")
             self.st.send.synchronize()
             self.st.recv.synchronize()
+            self.flush_stamps()                 # the items' end stamps that were still pending
 
 
 @dataclass
