@@ -176,6 +176,17 @@ def build_runner(force: bool = False) -> Path:
     return out
 
 
+def build_capture(force: bool = False) -> Path:
+    """`libkern_capture.so`, the injection library that records a process's module loads, allocations, descriptor encodes
+    and launches (`csrc/capture/kern_capture.cpp`; read by `kern_b200/capture.py`). Opens the driver and the profiling
+    interface at run time, so it builds and loads anywhere."""
+    out = PKG / "libkern_capture.so"
+    src = CSRC / "capture" / "kern_capture.cpp"
+    if force or _newer([src, CSRC / "common" / "sha256.hpp"], out):
+        _run([CXX, "-O2", "-std=c++17", "-Wall", "-shared", "-fPIC", "-I", str(CSRC), "-o", str(out), str(src), "-ldl", "-lpthread"])
+    return out
+
+
 def build_host_libs(force: bool = False) -> list[Path]:
     """Shared libraries with host code compiled by nvcc (C entry points reached through ctypes)."""
     outs = []
@@ -199,6 +210,7 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
             build_native(force)
             build_cli(force)
             build_runner(force)
+            build_capture(force)
             build_host_libs(force)
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)

@@ -716,7 +716,13 @@ def main(argv=None) -> int:
     s.add_argument("--pd", action="store_true", help="prefill/decode disaggregation: this process prefills (on --gpu), a decode process on --decode-gpu takes every request over with its first token")
     s.add_argument("--dcp", type=int, default=1, help="with --pd: the decode tier is a context-parallel group of this many ranks (dense family)")
     s.add_argument("--decode-gpu", type=int, default=1); s.add_argument("--decode-capacity", type=int, help="token capacity of the decode tier's paged states")
+    cp = sub.add_parser("capture", help="lift | mine | path: from a program's captured launches to manifest facts (kern_b200/capture.py)")
+    cp.add_argument("rest", nargs=argparse.REMAINDER)
     args = ap.parse_args(argv)
+    if args.cmd == "capture":
+        from . import capture
+
+        return capture.main(args.rest)
     if args.cmd in ("run", "test", "bench", "server", "e2e-logits", "gate"):
         path, cfg = find_config()
         resolve(args, path, cfg)

@@ -6,7 +6,7 @@
 - the console script and both engine plugins' entry points are declared, and the plugin packages are inside;
 - every kernel source of the tree has its cubin in the wheel, `kernels/index.json` names exactly those, and each cubin's
   bytes hash to the sha256 the index pins (the identity a manifest's module carries);
-- the native module, the `kern` and `kern-run` binaries and the no-alloc host library are inside;
+- the native module, the `kern` and `kern-run` binaries, the no-alloc host library and the capture library are inside;
 - no native file links a CUDA or NVIDIA library (`DT_NEEDED` read straight out of the ELF dynamic section): the runtime
   opens the driver, NCCL and CUPTI at run time, so the wheel imports on a machine that has none of them.
 
@@ -104,10 +104,10 @@ def check(wheel: str | Path) -> list[str]:
         native = [n for n in names if n.startswith("kern_b200/_native") and n.endswith(".so")]
         if not native:
             errs.append("the native module kern_b200/_native*.so is missing")
-        for n in ("kern_b200/bin/kern", "kern_b200/bin/kern-run", "kern_b200/libattn_decode_noalloc.so"):
+        for n in ("kern_b200/bin/kern", "kern_b200/bin/kern-run", "kern_b200/libattn_decode_noalloc.so", "kern_b200/libkern_capture.so"):
             if n not in names:
                 errs.append(f"{n} is missing")
-        for n in native + [x for x in ("kern_b200/bin/kern", "kern_b200/bin/kern-run") if x in names]:
+        for n in native + [x for x in ("kern_b200/bin/kern", "kern_b200/bin/kern-run", "kern_b200/libkern_capture.so") if x in names]:
             try:
                 linked = [l for l in needed(z.read(n)) if l.startswith(("libcu", "libnv", "libnccl"))]
             except ValueError as e:
