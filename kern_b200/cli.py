@@ -253,12 +253,33 @@ def cmd_kernels(args) -> int:
             return 2
         family, op, shape, variant, report = args.rest
         try:
-            rec = R.pick(family, op, shape, variant, report, entry=args.entry)
+            rec = R.pick(family, op, shape, variant, report, entry=(args.entry or [None])[-1])
         except ValueError as e:
             print(e)
             return 1
         print(f"{family}: {op} on {shape} -> {variant}" + (f" / {rec['entry']}" if "entry" in rec else "") + f" (report @{rec['report'][:12]})")
         return 0
+    if what == "import":
+        if len(args.rest) != 2:
+            print("usage: kern kernels import <cubin> <family> [--entry NAME ...] [--capture launches.jsonl] [--origin TEXT]")
+            return 2
+        try:
+            doc = R.import_cubin(args.rest[0], args.rest[1], entries=args.entry, capture_file=args.capture, origin=args.origin)
+        except ValueError as e:
+            print(e)
+            return 1
+        v = doc["variant"][-1]
+        print(f"{args.rest[1]}: {len(doc['variant'])} variant(s); {v['name']} @{v['sha256'][:12]} with {len(v['entries'])} entries")
+        return 0
+    if what == "land":
+        if len(args.rest) != 2:
+            print("usage: kern kernels land <manifest.json> <dir>")
+            return 2
+        landed, missing = R.land(json.loads(Path(args.rest[0]).read_text()), args.rest[1])
+        for m in missing:
+            print("missing:", m)
+        print(f"{len(landed)} landed, {len(missing)} missing")
+        return 1 if missing else 0
     print(f"unknown: kernels {what}")
     return 2
 
@@ -676,9 +697,11 @@ def main(argv=None) -> int:
     v = sub.add_parser("verify"); v.add_argument("manifest")
     c = sub.add_parser("cut"); c.add_argument("manifest"); c.add_argument("--at", required=True); c.add_argument("--out", required=True)
     kn = sub.add_parser("kernels")
-    kn.add_argument("what", nargs="?", choices=["list", "index", "check", "pick"])
+    kn.add_argument("what", nargs="?", choices=["list", "index", "check", "pick", "import", "land"])
     kn.add_argument("rest", nargs="*", help="pick: <family> <op> <shape> <variant> <bench.json>")
-    kn.add_argument("--entry", help="pick: the entry of the variant that was measured best")
+    kn.add_argument("--entry", action="append", help="pick: the entry of the variant that was measured best; import: an entry of the cubin (repeatable)")
+    kn.add_argument("--capture", help="import: a capture file whose launches name the module's entries")
+    kn.add_argument("--origin", help="import: where the cubin came from (URL and commit)")
     kn.add_argument("--no-reports", action="store_true", help="check: do not require the picks' reports to be in the local store")
     gt = sub.add_parser("gate", help="the serving scenarios every model target must pass"); common(gt)
     gt.add_argument("--only", help="comma-separated scenario names"); gt.add_argument("--seed", type=int, default=0)

@@ -20,6 +20,8 @@ under their hash and never replaced.
     python -m kern_b200 kernels index             # (re)write kernel_index/*.toml
     python -m kern_b200 kernels check             # the offline check; exit 1 with one line per finding
     python -m kern_b200 kernels pick moe ep_fc2 "rows>192" normal report.json --entry kern_ep_fc2_bf16_combine_n256
+    python -m kern_b200 kernels import their.cubin their-family [--entry NAME ...] [--capture launches.jsonl] [--origin URL@COMMIT]
+    python -m kern_b200 kernels land manifest.json DIR   # every pinned module into DIR, by content (store, then own build)
 
 Reference counterpart: tools/kernels/index.py (families, variants, picks), pick.py, store.py, check.py, docs/registry.md.
 """
@@ -277,4 +279,129 @@ def check(require_reports: bool = True) -> list[str]:
             errs.append(f"picks.toml: pick {p.get('op')} on {p.get('shape')}: no family `{p.get('family')}`")
     for name in sorted(known - {p.stem for p in (INDEX.glob("*.toml") if INDEX.exists() else [])}):
         errs.append(f"kernel_index/{name}.toml is missing (run `kern kernels index`)")
+    return errs + check_imported()
+
+
+# ---- kernels that were not built here ------------------------------------------------------------------------------
+IMPORTED = INDEX / "imported"      # committed: the hash of somebody else's cubin does not depend on this tree's build
+
+
+def entries_from_capture(capture_file: str | Path, sha256: str) -> list[str]:
+    """The symbols a captured process launched out of the module with this hash (`kern_b200/capture.py`)."""
+    from . import capture
+
+    cap = capture.Capture(capture.load(capture_file))
+    return sorted({r["symbol"] for r in cap.launches if r.get("module") == sha256})
+
+
+def entries_from_driver(path: str | Path) -> list[str]:
+    """Every entry of a cubin, enumerated by the driver after loading it (needs a GPU; nothing is disassembled)."""
+    from . import _native
+
+    dev = _native.Device(0)
+    return sorted(dev.entries(dev.load_module(Path(path).read_bytes())))
+
+
+def import_cubin(path: str | Path, family: str, entries: list[str] | None = None, capture_file: str | Path | None = None,
+                 origin: str | None = None) -> dict:
+    """Register a cubin that another project built: its bytes go into the store under their sha256 and
+    `kernel_index/imported/<family>.toml` records the hash, the size, the entries and where it came from (`origin`: the
+    upstream URL and commit, as the importer states it). The entries come from `entries`, else from a capture of a
+    process that launched the module, else from the driver on a machine with a GPU. Importing another build of the same
+    family adds a variant; importing the same bytes again changes nothing.
+    Reference counterpart: tools/kernels/import_cubin.py (which lists entries with an external dump tool)."""
+    if not re.fullmatch(r"[a-z0-9][a-z0-9_\-]*", family):
+        raise ValueError(f"family `{family}`: lower-case letters, digits, `_` and `-`")
+    if family in families():
+        raise ValueError(f"`{family}` is a family of this tree's own sources")
+    sha = put(path)
+    if not entries and capture_file:
+        entries = entries_from_capture(capture_file, sha)
+        if not entries:
+            raise ValueError(f"the capture holds no launch out of a module with sha256 {sha[:12]}…")
+    if not entries:
+        try:
+            entries = entries_from_driver(path)
+        except Exception as e:
+            raise ValueError(f"no entries given, no capture, and the driver could not list them ({e})") from None
+    doc_path = IMPORTED / f"{family}.toml"
+    doc = tomllib.loads(doc_path.read_text()) if doc_path.exists() else {"family": {"name": family, "kind": "imported"}, "variant": []}
+    if not any(v["sha256"] == sha for v in doc["variant"]):
+        doc["variant"].append({"name": f"v{len(doc['variant'])}", "sha256": sha, "entries": sorted(entries), "bytes": Path(path).stat().st_size,
+                               "file": Path(path).name, "origin": origin or "", "imported": datetime.date.today().isoformat()})
+    q = json.dumps
+    lines = ["[family]"] + [f"{k} = {q(v)}" for k, v in doc["family"].items()]
+    for v in doc["variant"]:
+        lines += ["", "[[variant]]"] + [f"{k} = {q(v[k])}" for k in ("name", "sha256", "entries", "bytes", "file", "origin", "imported")]
+    IMPORTED.mkdir(parents=True, exist_ok=True)
+    doc_path.write_text("\n".join(lines) + "\n")
+    return doc
+
+
+def imported() -> dict[str, dict]:
+    return {p.stem: tomllib.loads(p.read_text()) for p in sorted(IMPORTED.glob("*.toml"))} if IMPORTED.exists() else {}
+
+
+def module_decl(family: str, variant: str | None = None) -> dict:
+    """The `modules` entry a manifest carries for an imported family: {"source", "sha256"} (the last variant by default)."""
+    doc = imported().get(family)
+    if doc is None:
+        raise KeyError(f"no imported family `{family}`")
+    v = doc["variant"][-1] if variant is None else next(x for x in doc["variant"] if x["name"] == variant)
+    return {"source": v["file"], "sha256": v["sha256"]}
+
+
+def check_imported() -> list[str]:
+    errs, seen = [], {}
+    for name, doc in imported().items():
+        if doc.get("family", {}).get("name") != name or doc["family"].get("kind") != "imported":
+            errs.append(f"imported/{name}.toml: the family inside is `{doc.get('family', {}).get('name')}` of kind `{doc.get('family', {}).get('kind')}`")
+        if not doc.get("variant"):
+            errs.append(f"imported/{name}.toml: no variant")
+        for v in doc.get("variant", []):
+            if not HEX64.match(v.get("sha256", "")):
+                errs.append(f"imported/{name}.toml: variant `{v.get('name')}`: sha256 is not 64 hex characters")
+                continue
+            if v["sha256"] in seen:
+                errs.append(f"imported/{name}.toml: variant `{v['name']}` has the sha256 of {seen[v['sha256']]}")
+            seen[v["sha256"]] = (name, v["name"])
+            if not v.get("entries"):
+                errs.append(f"imported/{name}.toml: variant `{v['name']}` lists no entry")
+            blob = blob_path(v["sha256"])
+            if blob.exists() and hashlib.sha256(blob.read_bytes()).hexdigest() != v["sha256"]:
+                errs.append(f"imported/{name}.toml: variant `{v['name']}`: the store's blob does not hash to its name")
     return errs
+
+
+def land(manifest: dict, into: str | Path) -> tuple[list[str], list[str]]:
+    """Put every module a manifest pins into the directory a runtime is pointed at, by content: a file under `into` that
+    already hashes to the pin stays; otherwise the bytes come from the store, else from this package's own kernels. File
+    names are labels (the runtime finds modules by hash), so a landed file is named `<module>-<sha12>.cubin`.
+    -> (landed files, modules nowhere to be found). Reference counterpart: tools/extract_kernels.sh, tools/kernels/store.py."""
+    from . import _build
+
+    into = Path(into)
+    into.mkdir(parents=True, exist_ok=True)
+    have = {hashlib.sha256(p.read_bytes()).hexdigest() for p in into.glob("*.cubin")}
+    own = {}
+    for sub, _ in FLAVOURS.values():
+        for p in (_build.PKG / sub).glob("*.cubin"):
+            own.setdefault(hashlib.sha256(p.read_bytes()).hexdigest(), p)
+    landed, missing = [], []
+    for name, mod in sorted(manifest.get("modules", {}).items()):
+        sha = mod.get("sha256", "")
+        if sha in have:
+            continue
+        src = blob_path(sha) if blob_path(sha).exists() else own.get(sha)
+        if src is None:
+            missing.append(f"{name} ({mod.get('source')}, {sha[:12]}…)")
+            continue
+        data = src.read_bytes()
+        if hashlib.sha256(data).hexdigest() != sha:
+            missing.append(f"{name}: {src} does not hash to its name")
+            continue
+        dst = into / f"{name}-{sha[:12]}.cubin"
+        dst.write_bytes(data)
+        have.add(sha)
+        landed.append(dst.name)
+    return landed, missing

@@ -62,3 +62,49 @@ def test_a_pick_needs_a_variant_an_entry_and_a_report(index, tmp_path):
     R.report_path(R.picked("moe", "ep_fc2", "rows>192")["report"]).unlink()
     R.blob_path(R.picked("moe", "ep_fc2", "rows>192")["report"]).unlink()
     assert any("neither beside the index nor in the store" in e for e in R.check()) and R.check(require_reports=False) == []
+
+
+def test_import_a_foreign_cubin_with_entries_from_a_capture_and_land_it(index, tmp_path, monkeypatch):
+    monkeypatch.setattr(R, "IMPORTED", index / "imported")
+    foreign = tmp_path / "their_fmha.cubin"
+    foreign.write_bytes(b"\x7fELF" + bytes(range(200)))
+    import hashlib
+
+    sha = hashlib.sha256(foreign.read_bytes()).hexdigest()
+    cap = tmp_path / "launches.jsonl"
+    launch = lambda sym, mod: {"kind": "launch", "t_ns": 1, "symbol": sym, "module": mod, "grid": [1, 1, 1], "block": [32, 1, 1], "smem": 0, "params": []}
+    cap.write_text("\n".join(json.dumps(r) for r in [launch("fmha_fwd_d128", sha), launch("fmha_fwd_d64", sha), launch("other", "f" * 64)]) + "\n")
+    with pytest.raises(ValueError, match="own sources"):
+        R.import_cubin(foreign, "moe", entries=["x"])
+    with pytest.raises(ValueError, match="no launch out of a module"):
+        R.import_cubin(_build.KOUT / "moe.cubin", "their-fmha", capture_file=cap)
+    doc = R.import_cubin(foreign, "their-fmha", capture_file=cap, origin="https://example.org/fmha@abc123")
+    assert doc["variant"][0]["entries"] == ["fmha_fwd_d128", "fmha_fwd_d64"] and doc["variant"][0]["sha256"] == sha
+    assert R.import_cubin(foreign, "their-fmha", entries=["ignored"])["variant"] == doc["variant"]      # the same bytes: nothing new
+    assert R.module_decl("their-fmha") == {"source": "their_fmha.cubin", "sha256": sha}
+    R.write_all()
+    assert R.check() == []
+    (index / "imported" / "their-fmha.toml").write_text((index / "imported" / "their-fmha.toml").read_text().replace('entries = ["fmha_fwd_d128", "fmha_fwd_d64"]', "entries = []"))
+    assert any("lists no entry" in e for e in R.check())
+    # landing: the foreign module from the store, one of the package's own from its build, one nowhere
+    own = json.loads((_build.KOUT / "index.json").read_text())["norm_embed"]
+    manifest = {"modules": {"fmha": R.module_decl("their-fmha"), "norm": {"source": own["source"], "sha256": own["sha256"]},
+                            "ghost": {"source": "ghost.cubin", "sha256": "1" * 64}}}
+    landed, missing = R.land(manifest, tmp_path / "pkg")
+    assert sorted(landed) == [f"fmha-{sha[:12]}.cubin", f"norm-{own['sha256'][:12]}.cubin"] and len(missing) == 1 and "ghost" in missing[0]
+    assert (tmp_path / "pkg" / landed[0]).read_bytes() in (foreign.read_bytes(), (_build.KOUT / own["source"]).read_bytes())
+    assert R.land(manifest, tmp_path / "pkg")[0] == []                       # already there by content
+
+
+def test_kernels_import_and_land_commands(index, tmp_path, monkeypatch, capsys):
+    from kern_b200 import cli
+
+    monkeypatch.setattr(R, "IMPORTED", index / "imported")
+    foreign = tmp_path / "k.cubin"
+    foreign.write_bytes(b"\x7fELFxyz")
+    assert cli.main(["kernels", "import", str(foreign), "their-k", "--entry", "a", "--entry", "b"]) == 0
+    assert "2 entries" in capsys.readouterr().out
+    m = tmp_path / "m.json"
+    m.write_text(json.dumps({"modules": {"k": R.module_decl("their-k")}}))
+    assert cli.main(["kernels", "land", str(m), str(tmp_path / "out")]) == 0
+    assert "1 landed, 0 missing" in capsys.readouterr().out
